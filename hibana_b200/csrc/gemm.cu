@@ -1,0 +1,519 @@
+// tcgen05 GEMM for sm_100a: D[ra, rb] = A[ra, K] * B[rb, K]^T with fp32 accumulation in TMEM.
+//
+//   * kind bf16  : tcgen05.mma kind::f16, 64-element (128-byte) K tiles.
+//   * kind nvfp4 : tcgen05.mma kind::mxf4nvf4.block_scale (e2m1 values, ue4m3 scale per 16 elements),
+//                  256-element (128-byte) K tiles; scale factors travel global -> shared by bulk copies of the
+//                  128x4-swizzled blocks and shared -> TMEM by tcgen05.cp.
+//
+// One CTA computes a 128 x BN tile. Warp 0 issues TMA loads into a ring of 128-byte-swizzled stages, one lane
+// of warp 1 issues the MMAs and commits stage releases, warps 2-5 read the accumulator back with tcgen05.ld
+// and run the epilogue. With `swap` the 128-row operand is the weight matrix and the (few) tokens sit on the
+// N side, which keeps decode-sized problems on the tensor cores while streaming each weight byte once.
+// Split-K partials go to an fp32 workspace; the last CTA to arrive on a tile's counter sums them in split
+// order (deterministic) and applies the epilogue.
+//
+// Replaces the reference's library GEMM dispatch (hibana/kernels/ops.py:56-128) for bf16 and NVFP4.
+#include "gemm.cuh"
+
+#include <mutex>
+#include <unordered_map>
+#include <memory>
+#include <cstring>
+
+#include "hb_common.cuh"
+
+namespace hb {
+namespace {
+
+constexpr int BM = 128;
+constexpr int ROW_BYTES = 128;
+constexpr int A_TILE_BYTES = BM * ROW_BYTES;
+constexpr int NUM_THREADS = 192;
+
+template <int KIND, int BN>
+struct Cfg {
+  static constexpr int B_TILE_BYTES = BN * ROW_BYTES;
+  static constexpr int NRB = (BN + 127) / 128;
+  static constexpr int SFA_BYTES = KIND == kGemmNvfp4 ? 4 * 512 : 0;
+  static constexpr int SFB_BYTES = KIND == kGemmNvfp4 ? NRB * 4 * 512 : 0;
+  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TMEM_NEED = BN + (KIND == kGemmNvfp4 ? 16 + 16 * NRB : 0);
+  static constexpr int TMEM_COLS =
+      TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int CH = BN >= 32 ? 32 : 16;  // accumulator columns per tcgen05.ld
+};
+
+struct DevParams {
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  int ra, rb, k_tiles;
+  void* out;
+  long long ldo;
+  const __nv_bfloat16* residual;
+  float alpha;
+  const float* alpha_ptr;
+  int epilogue, swap, splits;
+  float* workspace;
+  int* counters;
+  int* status;
+  int ka_a, ka_b;
+  int out_rows, out_cols;
+};
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+// Applies the epilogue to CH accumulator values of one thread: `row` indexes the A operand, columns
+// [col0, col0 + CH) the B operand.
+template <int CH>
+__device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH], int row, int col0, float alpha,
+                                               int lane) {
+  const bool row_ok = row < p.ra;
+  if (p.swap) {
+    // out[token = col][feature = row]; lanes are consecutive features -> coalesced per token.
+    if (p.epilogue == kEpiSiluMul) {
+      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const float x = v[j] * alpha;
+        const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+        const int col = col0 + j;
+        if (row_ok && col < p.rb && (lane & 1) == 0)
+          out[static_cast<long long>(col) * p.ldo + (row >> 1)] = __float2bfloat16(silu(x) * other);
+      }
+    } else if (p.epilogue == kEpiStoreF32) {
+      float* out = static_cast<float*>(p.out);
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int col = col0 + j;
+        if (row_ok && col < p.rb) out[static_cast<long long>(col) * p.ldo + row] = v[j] * alpha;
+      }
+    } else {
+      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int col = col0 + j;
+        if (row_ok && col < p.rb) {
+          const long long o = static_cast<long long>(col) * p.ldo + row;
+          float x = v[j] * alpha;
+          if (p.epilogue == kEpiResidual) x += __bfloat162float(p.residual[o]);
+          out[o] = __float2bfloat16(x);
+        }
+      }
+    }
+    return;
+  }
+  if (!row_ok) return;
+  // out[token = row][feature = col]; each thread owns CH consecutive features of its row.
+  const long long base = static_cast<long long>(row) * p.ldo;
+  if (p.epilogue == kEpiSiluMul) {
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + base + (col0 >> 1);
+    const bool full = (col0 + CH <= p.rb) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+    if (full) {
+      uint32_t w[CH / 4];
+#pragma unroll
+      for (int j = 0; j < CH / 4; ++j)
+        w[j] = pack_bf16(silu(v[4 * j] * alpha) * (v[4 * j + 1] * alpha),
+                         silu(v[4 * j + 2] * alpha) * (v[4 * j + 3] * alpha));
+#pragma unroll
+      for (int j = 0; j < CH / 16; ++j)
+        reinterpret_cast<uint4*>(out)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < CH / 2; ++j)
+        if (col0 + 2 * j + 1 < p.rb)
+          out[j] = __float2bfloat16(silu(v[2 * j] * alpha) * (v[2 * j + 1] * alpha));
+    }
+  } else if (p.epilogue == kEpiStoreF32) {
+    float* out = static_cast<float*>(p.out) + base + col0;
+#pragma unroll
+    for (int j = 0; j < CH; ++j)
+      if (col0 + j < p.rb) out[j] = v[j] * alpha;
+  } else {
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + base + col0;
+    const __nv_bfloat16* res = p.epilogue == kEpiResidual ? p.residual + base + col0 : nullptr;
+    const bool full = (col0 + CH <= p.rb) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+                      (res == nullptr || (reinterpret_cast<uintptr_t>(res) & 15) == 0);
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < CH / 8; ++j) {
+        float x[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) x[t] = v[8 * j + t] * alpha;
+        if (res != nullptr) {
+          const uint4 r = reinterpret_cast<const uint4*>(res)[j];
+          x[0] += bf16_lo(r.x); x[1] += bf16_hi(r.x); x[2] += bf16_lo(r.y); x[3] += bf16_hi(r.y);
+          x[4] += bf16_lo(r.z); x[5] += bf16_hi(r.z); x[6] += bf16_lo(r.w); x[7] += bf16_hi(r.w);
+        }
+        reinterpret_cast<uint4*>(out)[j] =
+            make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < CH; ++j)
+        if (col0 + j < p.rb) {
+          float x = v[j] * alpha;
+          if (res != nullptr) x += __bfloat162float(res[j]);
+          out[j] = __float2bfloat16(x);
+        }
+    }
+  }
+}
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUtensorMap tmb, const DevParams p) {
+  using C = Cfg<KIND, BN>;
+  constexpr int S = C::STAGES;
+  constexpr int CH = C::CH;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * C::STAGE_BYTES);
+  uint64_t* empty = full + S;
+  uint64_t* accum = empty + S;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = abort + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+  const int kt_per = (p.k_tiles + p.splits - 1) / p.splits;
+  const int kt0 = split * kt_per;
+  const int kt1 = min(kt0 + kt_per, p.k_tiles);
+  const int nkt = max(kt1 - kt0, 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    *abort = 0;
+    *last_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tma);
+    prefetch_tmap(&tmb);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < nkt; ++i) {
+        const int s = i % S;
+        const uint32_t ph = (i / S) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, abort, p.status, kTimeoutEmpty)) break;
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        mbar_expect_tx(&full[s], C::STAGE_BYTES);
+        const int kt = kt0 + i;
+        const int kx = KIND == kGemmNvfp4 ? kt * 128 : kt * 64;
+        tma_load_2d(st, &tma, &full[s], kx, tile_a * BM);
+        tma_load_2d(st + A_TILE_BYTES, &tmb, &full[s], kx, tile_b * BN);
+        if constexpr (KIND == kGemmNvfp4) {
+          uint8_t* sf = st + A_TILE_BYTES + C::B_TILE_BYTES;
+          bulk_load(sf, p.sfa + (static_cast<size_t>(tile_a) * p.ka_a + kt * 4) * 512, 2048, &full[s]);
+#pragma unroll
+          for (int rb = 0; rb < C::NRB; ++rb)
+            bulk_load(sf + C::SFA_BYTES + rb * 2048,
+                      p.sfb + (static_cast<size_t>(tile_b * C::NRB + rb) * p.ka_b + kt * 4) * 512, 2048, &full[s]);
+        }
+        ++issued;
+      }
+      if (*abort) {
+        // Wait (bounded) for the copies still in flight so that none lands after the CTA has gone.
+        volatile int ignore = 0;
+        for (int j = max(issued - S, 0); j < issued; ++j)
+          mbar_wait(&full[j % S], (j / S) & 1, &ignore, nullptr, kTimeoutDrain);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = KIND == kGemmNvfp4 ? make_idesc_nvf4(BM, BN) : make_idesc_bf16(BM, BN);
+      const uint32_t sfa_t = tmem_base + BN;
+      const uint32_t sfb_t = sfa_t + 16;
+      bool ok = true;
+      for (int i = 0; i < nkt; ++i) {
+        const int s = i % S;
+        const uint32_t ph = (i / S) & 1;
+        if (!mbar_wait(&full[s], ph, abort, p.status, kTimeoutFull)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        const uint64_t adesc = make_desc_sw128(smem_u32(st));
+        const uint64_t bdesc = make_desc_sw128(smem_u32(st + A_TILE_BYTES));
+        if constexpr (KIND == kGemmNvfp4) {
+          const uint32_t sf = smem_u32(st + A_TILE_BYTES + C::B_TILE_BYTES);
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            tmem_cp_32x128b_x4(sfa_t + kb * 4, make_desc_sf(sf + kb * 512));
+#pragma unroll
+            for (int rb = 0; rb < C::NRB; ++rb)
+              tmem_cp_32x128b_x4(sfb_t + kb * 4 * C::NRB + rb * 4,
+                                 make_desc_sf(sf + C::SFA_BYTES + rb * 2048 + kb * 512));
+          }
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb)
+            mma_nvf4(tmem_base, adesc + kb * 2, bdesc + kb * 2, idesc, (i > 0 || kb > 0) ? 1u : 0u,
+                     sfa_t + kb * 4, sfb_t + kb * 4 * C::NRB);
+        } else {
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb)
+            mma_f16(tmem_base, adesc + kb * 2, bdesc + kb * 2, idesc, (i > 0 || kb > 0) ? 1u : 0u);
+        }
+        tc_commit(&empty[s]);
+      }
+      if (ok) tc_commit(accum);
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const bool ok = nkt > 0 ? mbar_wait(accum, 0, abort, p.status, kTimeoutAccum) : true;
+    tc_fence_after();
+    const int row = tile_a * BM + q * 32 + lane;
+    const uint32_t tlane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    float alpha = p.alpha;
+    if (p.alpha_ptr != nullptr) alpha *= *p.alpha_ptr;
+    if (ok && p.splits == 1) {
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        uint32_t r[CH];
+        if constexpr (CH == 32) tmem_ld_32x32(tlane + c0, r);
+        else tmem_ld_32x16(tlane + c0, r);
+        tmem_ld_wait();
+        float v[CH];
+#pragma unroll
+        for (int j = 0; j < CH; ++j) v[j] = nkt > 0 ? __uint_as_float(r[j]) : 0.f;
+        epilogue_chunk<CH>(p, v, row, tile_b * BN + c0, alpha, lane);
+      }
+    } else if (ok) {
+      // Split-K: park the raw partial, then the last CTA of this tile reduces all partials in split order.
+      const size_t plane = static_cast<size_t>(p.out_rows) * p.out_cols;
+      float* ws = p.workspace + static_cast<size_t>(split) * plane;
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        uint32_t r[CH];
+        if constexpr (CH == 32) tmem_ld_32x32(tlane + c0, r);
+        else tmem_ld_32x16(tlane + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int col = tile_b * BN + c0 + j;
+          if (row < p.ra && col < p.rb) {
+            const size_t o = p.swap ? static_cast<size_t>(col) * p.out_cols + row
+                                    : static_cast<size_t>(row) * p.out_cols + col;
+            __stcg(ws + o, nkt > 0 ? __uint_as_float(r[j]) : 0.f);
+          }
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        const int prev = atomicAdd(&p.counters[tile_id], 1);
+        if (prev == p.splits - 1) {
+          p.counters[tile_id] = 0;
+          *last_flag = 1;
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*last_flag) {
+        __threadfence();
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          float v[CH];
+#pragma unroll
+          for (int j = 0; j < CH; ++j) v[j] = 0.f;
+          for (int s = 0; s < p.splits; ++s) {
+            const float* w = p.workspace + static_cast<size_t>(s) * plane;
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int col = tile_b * BN + c0 + j;
+              if (row < p.ra && col < p.rb) {
+                const size_t o = p.swap ? static_cast<size_t>(col) * p.out_cols + row
+                                        : static_cast<size_t>(row) * p.out_cols + col;
+                v[j] += __ldcg(w + o);
+              }
+            }
+          }
+          epilogue_chunk<CH>(p, v, row, tile_b * BN + c0, alpha, lane);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+struct KeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    auto mix = [&h](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
+    mix(k.rows); mix(k.cols); mix(k.pitch_bytes); mix(k.box_rows); mix(k.box_cols); mix(k.dtype);
+    return h;
+  }
+};
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess) f = nullptr;
+    return reinterpret_cast<EncodeFn>(f);
+  }();
+  return fn;
+}
+
+std::mutex g_tmap_mu;
+std::unordered_map<TmapKey, std::unique_ptr<CUtensorMap>, KeyHash> g_tmaps;
+
+template <int KIND, int BN>
+cudaError_t launch_t(const GemmArgs& a, const DevParams& p, dim3 grid, const CUtensorMap* ta, const CUtensorMap* tb,
+                     cudaStream_t stream) {
+  using C = Cfg<KIND, BN>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_done = true;
+  }
+  gemm_kernel<KIND, BN><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(*ta, *tb, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+const CUtensorMap* get_tmap_2d(const TmapKey& key) {
+  std::lock_guard<std::mutex> lock(g_tmap_mu);
+  auto it = g_tmaps.find(key);
+  if (it != g_tmaps.end()) return it->second.get();
+  if (g_tmaps.size() > 8192) g_tmaps.clear();
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return nullptr;
+  auto m = std::make_unique<CUtensorMap>();
+  const cuuint64_t dims[2] = {key.cols, key.rows};
+  const cuuint64_t strides[1] = {key.pitch_bytes};
+  const cuuint32_t box[2] = {key.box_cols, key.box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = key.dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUresult r = fn(m.get(), dt, 2, const_cast<void*>(key.ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return nullptr;
+  const CUtensorMap* out = m.get();
+  g_tmaps.emplace(key, std::move(m));
+  return out;
+}
+
+void clear_tmap_cache() {
+  std::lock_guard<std::mutex> lock(g_tmap_mu);
+  g_tmaps.clear();
+}
+
+static void out_dims(const GemmArgs& a, int* rows, int* cols) {
+  *rows = a.swap ? a.rb : a.ra;
+  *cols = a.swap ? a.ra : a.rb;
+}
+
+size_t gemm_workspace_bytes(const GemmArgs& a) {
+  if (a.splits <= 1) return 0;
+  int r, c;
+  out_dims(a, &r, &c);
+  return static_cast<size_t>(a.splits) * r * c * sizeof(float);
+}
+
+int gemm_num_tiles(const GemmArgs& a) { return ((a.ra + BM - 1) / BM) * ((a.rb + a.bn - 1) / a.bn); }
+
+cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
+  const bool fp4 = a.kind == kGemmNvfp4;
+  if (a.ra <= 0 || a.rb <= 0 || a.k <= 0) return cudaErrorInvalidValue;
+  if (fp4 ? (a.k % 32 != 0) : (a.k % 8 != 0)) return cudaErrorInvalidValue;
+  const int kt_elems = fp4 ? 256 : 64;
+  const int k_tiles = (a.k + kt_elems - 1) / kt_elems;
+  const int tiles_a = (a.ra + BM - 1) / BM;
+  const int tiles_b = (a.rb + a.bn - 1) / a.bn;
+  if (fp4 && a.bn < 128 && tiles_b != 1) return cudaErrorInvalidValue;
+  if (fp4 && (a.sf_k_atoms_a < k_tiles * 4 || a.sf_k_atoms_b < k_tiles * 4)) return cudaErrorInvalidValue;
+  int splits = a.splits < 1 ? 1 : a.splits;
+  if (splits > k_tiles) splits = k_tiles;
+  // Every split must own at least one K tile.
+  while (splits > 1 && (splits - 1) * ((k_tiles + splits - 1) / splits) >= k_tiles) --splits;
+  if (splits > 1 && (a.workspace == nullptr || a.counters == nullptr)) return cudaErrorInvalidValue;
+
+  TmapKey ka{a.a, static_cast<uint64_t>(a.ra), static_cast<uint64_t>(fp4 ? a.k / 2 : a.k),
+             static_cast<uint64_t>(fp4 ? a.lda / 2 : a.lda * 2), static_cast<uint32_t>(BM),
+             static_cast<uint32_t>(fp4 ? 128 : 64), fp4 ? 1 : 0};
+  TmapKey kb{a.b, static_cast<uint64_t>(a.rb), static_cast<uint64_t>(fp4 ? a.k / 2 : a.k),
+             static_cast<uint64_t>(fp4 ? a.ldb / 2 : a.ldb * 2), static_cast<uint32_t>(a.bn),
+             static_cast<uint32_t>(fp4 ? 128 : 64), fp4 ? 1 : 0};
+  const CUtensorMap* ta = get_tmap_2d(ka);
+  const CUtensorMap* tb = get_tmap_2d(kb);
+  if (ta == nullptr || tb == nullptr) return cudaErrorInvalidValue;
+
+  DevParams p;
+  p.sfa = static_cast<const uint8_t*>(a.sfa);
+  p.sfb = static_cast<const uint8_t*>(a.sfb);
+  p.ra = a.ra; p.rb = a.rb; p.k_tiles = k_tiles;
+  p.out = a.out; p.ldo = a.ldo;
+  p.residual = static_cast<const __nv_bfloat16*>(a.residual);
+  p.alpha = a.alpha; p.alpha_ptr = a.alpha_ptr;
+  p.epilogue = a.epilogue; p.swap = a.swap; p.splits = splits;
+  p.workspace = a.workspace; p.counters = a.counters; p.status = a.status;
+  p.ka_a = a.sf_k_atoms_a; p.ka_b = a.sf_k_atoms_b;
+  out_dims(a, &p.out_rows, &p.out_cols);
+  const dim3 grid(tiles_a, tiles_b, splits);
+
+#define HB_DISPATCH(KIND)                                                        \
+  switch (a.bn) {                                                                \
+    case 16: return launch_t<KIND, 16>(a, p, grid, ta, tb, stream);              \
+    case 32: return launch_t<KIND, 32>(a, p, grid, ta, tb, stream);              \
+    case 64: return launch_t<KIND, 64>(a, p, grid, ta, tb, stream);              \
+    case 128: return launch_t<KIND, 128>(a, p, grid, ta, tb, stream);            \
+    case 256: return launch_t<KIND, 256>(a, p, grid, ta, tb, stream);            \
+    default: return cudaErrorInvalidValue;                                       \
+  }
+  if (fp4) {
+    HB_DISPATCH(kGemmNvfp4)
+  } else {
+    HB_DISPATCH(kGemmBf16)
+  }
+#undef HB_DISPATCH
+}
+
+}  // namespace hb
+
+#include "hb_api.h"
+
+extern "C" {
+
+int hb_gemm(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int ra, int rb, int k,
+            long long lda, long long ldb, void* out, long long ldo, const void* residual, float alpha,
+            const void* alpha_ptr, int epilogue, int swap, int splits, void* workspace, void* counters,
+            void* status, int bn, int ka_a, int ka_b, void* stream) {
+  hb::GemmArgs g;
+  g.kind = kind; g.a = a; g.b = b; g.sfa = sfa; g.sfb = sfb; g.ra = ra; g.rb = rb; g.k = k;
+  g.lda = lda; g.ldb = ldb; g.out = out; g.ldo = ldo; g.residual = residual; g.alpha = alpha;
+  g.alpha_ptr = static_cast<const float*>(alpha_ptr); g.epilogue = epilogue; g.swap = swap; g.splits = splits;
+  g.workspace = static_cast<float*>(workspace); g.counters = static_cast<int*>(counters);
+  g.status = static_cast<int*>(status); g.bn = bn; g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
+  const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+void hb_clear_tmap_cache(void) { hb::clear_tmap_cache(); }
+
+}  // extern "C"

@@ -1,0 +1,65 @@
+// Host-visible interface of the tcgen05 GEMM family (no torch headers here: plain C++ launchers).
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace hb {
+
+enum GemmKind : int { kGemmBf16 = 0, kGemmNvfp4 = 1 };
+enum GemmEpilogue : int {
+  kEpiStore = 0,      // out = alpha * acc                      (bf16)
+  kEpiResidual = 1,   // out = alpha * acc + residual           (bf16)
+  kEpiSiluMul = 2,    // out[.., j] = silu(acc[2j]) * acc[2j+1] (bf16, gate/up rows interleaved pairwise)
+  kEpiStoreF32 = 3,   // out = alpha * acc                      (fp32)
+};
+
+// D[ra, rb] = sum_k A[ra, k] * B[rb, k]; both operands K-major. `swap` tells the epilogue that A rows are
+// output *columns* (weights on the 128-row side, tokens on the N side): out[rb * ldo + ra].
+struct GemmArgs {
+  int kind;
+  const void* a;        // [RA, K]  (bf16, or packed e2m1 with K/2 bytes per row)
+  const void* b;        // [RB, K]
+  const void* sfa;      // nvfp4 only: scale factors of A, 128x4-swizzled blocks [ceil(RA/128)][KA][512 B]
+  const void* sfb;      // nvfp4 only: scale factors of B
+  int ra, rb, k;
+  int64_t lda, ldb;     // row pitch in elements
+  void* out;
+  int64_t ldo;
+  const void* residual; // bf16, same indexing as out (may be null)
+  float alpha;
+  const float* alpha_ptr;  // optional device scalar multiplied into alpha (dynamic activation scale)
+  int epilogue;
+  int swap;
+  int splits;           // split-K factor (>= 1)
+  float* workspace;     // splits > 1: fp32 [splits][out rows][out cols]
+  int* counters;        // splits > 1: one int per output tile, zero before the first launch, self-resetting
+  int* status;          // device status word (may be null)
+  int bn;               // N tile: 16, 32, 64, 128 or 256
+  int sf_k_atoms_a;     // nvfp4: number of 64-element K atoms per row block in sfa (padded to a multiple of 4)
+  int sf_k_atoms_b;
+};
+
+// Returns cudaSuccess or the launch error. Tensor maps are built (and cached) inside.
+cudaError_t gemm_launch(const GemmArgs& args, cudaStream_t stream);
+
+// Bytes of fp32 workspace and number of counters a launch with these arguments needs.
+size_t gemm_workspace_bytes(const GemmArgs& args);
+int gemm_num_tiles(const GemmArgs& args);
+
+// Tensor-map cache (host). 2-D row-major tensor, box = {box_inner elements, box_rows}, 128-byte swizzle.
+struct TmapKey {
+  const void* ptr;
+  uint64_t rows, cols;   // cols = inner extent in elements
+  uint64_t pitch_bytes;
+  uint32_t box_rows, box_cols;
+  int dtype;             // 0 = bf16, 1 = u8
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && pitch_bytes == o.pitch_bytes &&
+           box_rows == o.box_rows && box_cols == o.box_cols && dtype == o.dtype;
+  }
+};
+const CUtensorMap* get_tmap_2d(const TmapKey& key);
+void clear_tmap_cache();
+
+}  // namespace hb

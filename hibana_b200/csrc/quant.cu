@@ -1,0 +1,271 @@
+// Activation quantisers for sm_100a.
+//
+// NVFP4: e2m1 values packed two per byte, one ue4m3 scale per 16 elements written straight into the
+// 128x4-swizzled block layout that tcgen05.cp moves into TMEM, and a per-tensor fp32 scale supplied by the
+// caller (x ~= q * sf * global_scale). Variants fuse the producer op so the bf16 activation is read once:
+//   plain, RMSNorm -> quant, residual-add + RMSNorm -> quant, SiLU(gate) * up -> quant.
+// FP8: static per-tensor e4m3, dynamic per-row e4m3.
+//
+// Covers what the reference does in hibana/kernels/nvfp4_quant.py:46-156, hibana/kernels/fp8_quant.py:19-88
+// and hibana/kernels/cute/residual_norm.py:62-160.
+#include "hb_common.cuh"
+#include "hb_api.h"
+
+namespace hb {
+namespace {
+
+// Offset of the scale byte of (row, 16-element group g) in the swizzled layout with `ka` K atoms per block row.
+__device__ __forceinline__ size_t sf_offset(int row, int g, int ka) {
+  const int rb = row >> 7, ri = row & 127;
+  return (static_cast<size_t>(rb) * ka + (g >> 2)) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + (g & 3);
+}
+
+// Quantises 16 floats: writes 8 packed bytes and returns the ue4m3 scale byte.
+__device__ __forceinline__ uint32_t quant16(const float (&x)[16], float inv_gs, uint2* packed) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  const uint32_t sfb = float_to_e4m3(amax * (1.f / 6.f) * inv_gs);
+  const float sf = e4m3_to_float(sfb);
+  const float inv = sf > 0.f ? 1.f / (sf * (1.f / inv_gs)) : 0.f;
+  uint32_t w[2] = {0, 0};
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i >> 3] |= float_to_e2m1(x[i] * inv) << (4 * (i & 7));
+  *packed = make_uint2(w[0], w[1]);
+  return sfb;
+}
+
+__device__ __forceinline__ void load16(const __nv_bfloat16* p, float (&x)[16]) {
+  const uint4 a = reinterpret_cast<const uint4*>(p)[0];
+  const uint4 b = reinterpret_cast<const uint4*>(p)[1];
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    x[2 * i] = bf16_lo(w[i]);
+    x[2 * i + 1] = bf16_hi(w[i]);
+  }
+}
+
+// One thread per 16-element group over the padded scale extent (padding scales are written as zero).
+// mode 0: y = x; mode 1: y = silu(x[:, :K]) * x[:, K:2K] (x has 2K columns, gate first);
+// mode 2: gate/up interleaved pairwise (x[:, 2j], x[:, 2j+1]).
+__global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int m, int k, int ka,
+                                   const float* __restrict__ gscale, uint8_t* __restrict__ q,
+                                   uint8_t* __restrict__ sf, int mode) {
+  const int groups_pad = ka * 4;
+  const int rows_pad = ((m + 127) >> 7) << 7;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(rows_pad) * groups_pad) return;
+  const int row = static_cast<int>(idx / groups_pad);
+  const int g = static_cast<int>(idx % groups_pad);
+  if (row >= m || g * 16 >= k) {
+    sf[sf_offset(row, g, ka)] = 0;
+    return;
+  }
+  const float inv_gs = 1.f / *gscale;
+  float v[16];
+  if (mode == 0) {
+    load16(x + row * ldx + g * 16, v);
+  } else if (mode == 1) {
+    float u[16];
+    load16(x + row * ldx + g * 16, v);
+    load16(x + row * ldx + k + g * 16, u);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float s = v[i] / (1.f + __expf(-v[i]));
+      v[i] = __bfloat162float(__float2bfloat16(s * u[i]));
+    }
+  } else {
+    float a[16], b[16];
+    load16(x + row * ldx + g * 32, a);
+    load16(x + row * ldx + g * 32 + 16, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float g0 = a[2 * i], u0 = a[2 * i + 1], g1 = b[2 * i], u1 = b[2 * i + 1];
+      v[i] = __bfloat162float(__float2bfloat16(g0 / (1.f + __expf(-g0)) * u0));
+      v[8 + i] = __bfloat162float(__float2bfloat16(g1 / (1.f + __expf(-g1)) * u1));
+    }
+  }
+  uint2 packed;
+  const uint32_t sfb = quant16(v, inv_gs, &packed);
+  *reinterpret_cast<uint2*>(q + static_cast<size_t>(row) * (k / 2) + g * 8) = packed;
+  sf[sf_offset(row, g, ka)] = static_cast<uint8_t>(sfb);
+}
+
+// (residual add +) RMSNorm -> NVFP4. One CTA per row, blockDim.x * 16 >= K is not required: threads loop.
+// Writes the updated residual (bf16) when `residual` is given, optionally the normalised bf16 row too.
+// gemma != 0 uses weight (1 + w).
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+norm_quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
+                        const __nv_bfloat16* __restrict__ w, float eps, int gemma, int m, int k, int ka,
+                        const float* __restrict__ gscale, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                        __nv_bfloat16* __restrict__ normed) {
+  extern __shared__ float row_s[];  // k floats
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int tid = threadIdx.x;
+  const int groups = k / 16;
+  float ss = 0.f;
+  for (int g = tid; g < groups; g += THREADS) {
+    float v[16];
+    load16(x + static_cast<size_t>(row) * k + g * 16, v);
+    if (residual != nullptr) {
+      float r[16];
+      load16(residual + static_cast<size_t>(row) * k + g * 16, r);
+      uint32_t o[8];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = __bfloat162float(__float2bfloat16(v[i] + r[i]));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+      uint4* dst = reinterpret_cast<uint4*>(residual + static_cast<size_t>(row) * k + g * 16);
+      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      row_s[g * 16 + i] = v[i];
+      ss += v[i] * v[i];
+    }
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  if (tid < 32) {
+    float t = tid < THREADS / 32 ? red[tid] : 0.f;
+    t = warp_sum(t);
+    if (tid == 0) red[0] = rsqrtf(t / k + eps);
+  }
+  __syncthreads();
+  const float rstd = red[0];
+  const float inv_gs = 1.f / *gscale;
+  const int groups_pad = ka * 4;
+  for (int g = tid; g < groups_pad; g += THREADS) {
+    if (g >= groups) {
+      sf[sf_offset(row, g, ka)] = 0;
+      continue;
+    }
+    float wv[16], v[16];
+    load16(w + g * 16, wv);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float ww = gemma ? 1.f + wv[i] : wv[i];
+      v[i] = __bfloat162float(__float2bfloat16(row_s[g * 16 + i] * rstd * ww));
+    }
+    if (normed != nullptr) {
+      uint4* dst = reinterpret_cast<uint4*>(normed + static_cast<size_t>(row) * k + g * 16);
+      dst[0] = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+      dst[1] = make_uint4(pack_bf16(v[8], v[9]), pack_bf16(v[10], v[11]), pack_bf16(v[12], v[13]),
+                          pack_bf16(v[14], v[15]));
+    }
+    uint2 packed;
+    const uint32_t sfb = quant16(v, inv_gs, &packed);
+    *reinterpret_cast<uint2*>(q + static_cast<size_t>(row) * (k / 2) + g * 8) = packed;
+    sf[sf_offset(row, g, ka)] = static_cast<uint8_t>(sfb);
+  }
+}
+
+// Zeroes the scale bytes of the padding rows [m, round_up(m, 128)) (used after the per-row kernel).
+__global__ void sf_pad_rows_kernel(uint8_t* sf, int m, int ka) {
+  const int rows_pad = ((m + 127) >> 7) << 7;
+  const int groups_pad = ka * 4;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long n = static_cast<long long>(rows_pad - m) * groups_pad;
+  if (idx >= n) return;
+  sf[sf_offset(m + static_cast<int>(idx / groups_pad), static_cast<int>(idx % groups_pad), ka)] = 0;
+}
+
+// Static per-tensor FP8 (e4m3): q = sat(x / scale). 8 elements per thread.
+__global__ void quant_fp8_static_kernel(const __nv_bfloat16* __restrict__ x, long long n,
+                                        const float* __restrict__ scale, uint8_t* __restrict__ q) {
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  const float inv = 1.f / *scale;
+  if (i + 8 <= n) {
+    const uint4 a = *reinterpret_cast<const uint4*>(x + i);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+    uint32_t o[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o[j >> 1] |= float_to_e4m3(bf16_lo(w[j]) * inv) << (16 * (j & 1));
+      o[j >> 1] |= float_to_e4m3(bf16_hi(w[j]) * inv) << (16 * (j & 1) + 8);
+    }
+    *reinterpret_cast<uint2*>(q + i) = make_uint2(o[0], o[1]);
+  } else {
+    for (long long j = i; j < n; ++j) q[j] = static_cast<uint8_t>(float_to_e4m3(__bfloat162float(x[j]) * inv));
+  }
+}
+
+// Dynamic per-row FP8: scale[row] = amax / 448, q = x / scale. One warp per row.
+__global__ void quant_fp8_rows_kernel(const __nv_bfloat16* __restrict__ x, int m, int k, uint8_t* __restrict__ q,
+                                      float* __restrict__ scales) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= m) return;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(row) * k;
+  float amax = 0.f;
+  for (int i = lane; i < k; i += 32) amax = fmaxf(amax, fabsf(__bfloat162float(xr[i])));
+  amax = warp_max(amax);
+  const float scale = amax > 0.f ? amax / 448.f : 1.f;
+  const float inv = 1.f / scale;
+  for (int i = lane; i < k; i += 32)
+    q[static_cast<size_t>(row) * k + i] = static_cast<uint8_t>(float_to_e4m3(__bfloat162float(xr[i]) * inv));
+  if (lane == 0) scales[row] = scale;
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" {
+
+int hb_quant_nvfp4(const void* x, long long ldx, int m, int k, int ka, const void* gscale, void* q, void* sf,
+                   int mode, void* stream) {
+  if (k % 16 != 0 || ka * 64 < k) return 1;
+  const int rows_pad = ((m + 127) / 128) * 128;
+  const long long n = static_cast<long long>(rows_pad) * ka * 4;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((n + threads - 1) / threads);
+  quant_nvfp4_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, m, k, ka, static_cast<const float*>(gscale),
+      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), mode);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_norm_quant_nvfp4(const void* x, void* residual, const void* w, float eps, int gemma, int m, int k, int ka,
+                        const void* gscale, void* q, void* sf, void* normed, void* stream) {
+  if (k % 16 != 0 || ka * 64 < k || k * sizeof(float) > 96 * 1024) return 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  constexpr int T = 256;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(norm_quant_nvfp4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    attr = true;
+  }
+  norm_quant_nvfp4_kernel<T><<<m, T, k * sizeof(float), st>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(residual),
+      static_cast<const __nv_bfloat16*>(w), eps, gemma, m, k, ka, static_cast<const float*>(gscale),
+      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), static_cast<__nv_bfloat16*>(normed));
+  const int rows_pad = ((m + 127) / 128) * 128;
+  if (rows_pad > m) {
+    const long long n = static_cast<long long>(rows_pad - m) * ka * 4;
+    sf_pad_rows_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(static_cast<uint8_t*>(sf), m, ka);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_quant_fp8_static(const void* x, long long n, const void* scale, void* q, void* stream) {
+  const long long threads = (n + 7) / 8;
+  quant_fp8_static_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), n, static_cast<const float*>(scale), static_cast<uint8_t*>(q));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_quant_fp8_rows(const void* x, int m, int k, void* q, void* scales, void* stream) {
+  quant_fp8_rows_kernel<<<(m + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), m, k, static_cast<uint8_t*>(q), static_cast<float*>(scales));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+}  // extern "C"

@@ -1,0 +1,114 @@
+"""Linear layers on the tcgen05 GEMM (csrc/gemm.cu): bf16 and NVFP4, with fused epilogues.
+
+Dispatch: up to 256 tokens the weight matrix takes the 128-row MMA operand ("swap") and K is split across
+CTAs until the grid fills the 148 SMs, so a decode step streams every weight byte once at HBM rate; larger
+token counts use 128 x 256 output tiles. The reference's equivalent dispatch (w3 -> verify GEMM -> tuned CUTLASS
+tactic -> FlashInfer mm_fp4, and FP8 GEMV / cuBLASLt) is hibana/kernels/ops.py:56-128.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _native as nv
+from .nvfp4 import Nvfp4Tensor
+
+EPI_STORE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_STORE_F32 = 0, 1, 2, 3
+NUM_SMS = 148
+
+
+def _plan(m: int, n: int, k_tiles: int, max_ws_bytes: int) -> tuple[bool, int, int]:
+    """(swap, bn, splits) for an [m tokens] x [n features] problem."""
+    if m <= 256:
+        bn = next(b for b in (16, 32, 64, 128, 256) if b >= m)
+        tiles = (n + 127) // 128
+        splits = 1
+        if tiles < NUM_SMS:
+            splits = max(1, min(-(-NUM_SMS // tiles), k_tiles // 4, 16))
+            while splits > 1 and splits * m * n * 4 > max_ws_bytes:
+                splits -= 1
+        return True, bn, splits
+    return False, (256 if n >= 256 else 128), 1
+
+
+def _launch(kind: int, a, b, sfa, sfb, ra: int, rb: int, k: int, lda: int, ldb: int, out: torch.Tensor,
+            residual: Optional[torch.Tensor], alpha: float, alpha_ptr: Optional[torch.Tensor], epilogue: int,
+            swap: bool, splits: int, bn: int, ka_a: int, ka_b: int) -> None:
+    st = nv.device_state(out.device)
+    ws = cnt = None
+    if splits > 1:
+        ws, cnt = st.workspace(splits * ra * rb * 4)
+    code = nv.lib().hb_gemm(kind, a.data_ptr(), b.data_ptr(), nv.ptr(sfa), nv.ptr(sfb), ra, rb, k, lda, ldb,
+                            out.data_ptr(), out.stride(0), nv.ptr(residual), alpha, nv.ptr(alpha_ptr), epilogue,
+                            int(swap), splits, nv.ptr(ws), nv.ptr(cnt), st.status.data_ptr(), bn, ka_a, ka_b,
+                            nv.stream())
+    nv.check(code, "hb_gemm")
+
+
+def _out(m: int, n: int, epilogue: int, like: torch.Tensor, out: Optional[torch.Tensor]) -> torch.Tensor:
+    cols = n // 2 if epilogue == EPI_SILU_MUL else n
+    dtype = torch.float32 if epilogue == EPI_STORE_F32 else torch.bfloat16
+    if out is None:
+        out = torch.empty(m, cols, dtype=dtype, device=like.device)
+    assert out.shape == (m, cols) and out.dtype == dtype and out.stride(1) == 1
+    return out
+
+
+def _ref_epilogue(acc: torch.Tensor, epilogue: int, residual: Optional[torch.Tensor]) -> torch.Tensor:
+    if epilogue == EPI_RESIDUAL:
+        return (acc + residual.float()).to(torch.bfloat16)
+    if epilogue == EPI_SILU_MUL:
+        return (torch.nn.functional.silu(acc[:, 0::2]) * acc[:, 1::2]).to(torch.bfloat16)
+    if epilogue == EPI_STORE_F32:
+        return acc
+    return acc.to(torch.bfloat16)
+
+
+def linear_bf16(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE, residual: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None, splits: Optional[int] = None) -> torch.Tensor:
+    """y = x @ w.T for bf16 x [M, K], w [N, K] (fp32 accumulation)."""
+    m, k = x.shape
+    n = w.shape[0]
+    if not nv.use_native(x, w):
+        res = _ref_epilogue(x.float() @ w.float().t(), epilogue, residual)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    out = _out(m, n, epilogue, x, out)
+    swap, bn, auto_splits = _plan(m, n, (k + 63) // 64, nv.WORKSPACE_BYTES)
+    splits = auto_splits if splits is None else splits
+    if swap:
+        _launch(0, w, x, None, None, n, m, k, w.stride(0), x.stride(0), out, residual, 1.0, None, epilogue, True,
+                splits, bn, 0, 0)
+    else:
+        _launch(0, x, w, None, None, m, n, k, x.stride(0), w.stride(0), out, residual, 1.0, None, epilogue, False,
+                splits, bn, 0, 0)
+    return out
+
+
+def linear_nvfp4(x: Nvfp4Tensor, w: Nvfp4Tensor, alpha: torch.Tensor, *, epilogue: int = EPI_STORE,
+                 residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                 splits: Optional[int] = None) -> torch.Tensor:
+    """y = dequant(x) @ dequant(w).T with block-scaled FP4 MMAs; `alpha` = x.gscale * w.gscale (device scalar)."""
+    m, k, n = x.rows, x.k, w.rows
+    assert w.k == k
+    if not nv.use_native(x.q, w.q):
+        acc = x.dequantize() @ w.dequantize().t()
+        res = _ref_epilogue(acc, epilogue, residual)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    out = _out(m, n, epilogue, x.q, out)
+    swap, bn, auto_splits = _plan(m, n, (k + 255) // 256, nv.WORKSPACE_BYTES)
+    splits = auto_splits if splits is None else splits
+    if swap:
+        _launch(1, w.q, x.q, w.sf, x.sf, n, m, k, k, k, out, residual, 1.0, alpha, epilogue, True, splits, bn, w.ka,
+                x.ka)
+    else:
+        _launch(1, x.q, w.q, x.sf, w.sf, m, n, k, k, k, out, residual, 1.0, alpha, epilogue, False, splits, bn, x.ka,
+                w.ka)
+    return out

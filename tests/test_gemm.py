@@ -1,0 +1,147 @@
+"""tcgen05 GEMM and NVFP4 quantiser against plain PyTorch fp32 references."""
+import pytest
+import torch
+
+from hibana_b200 import _native as nv
+from hibana_b200.ops import gemm, nvfp4
+
+
+def test_e2m1_round_trip_cpu():
+    codes = torch.arange(16, dtype=torch.int32)
+    vals = nvfp4.e2m1_values(codes)
+    assert torch.equal(nvfp4.e2m1_codes(vals) & 7, codes & 7)
+    # ties go to the even mantissa
+    x = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+    assert nvfp4.e2m1_values(nvfp4.e2m1_codes(x)).tolist() == [0.0, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0]
+
+
+def test_swizzle_round_trip_cpu():
+    sf = torch.randint(0, 255, (200, 20), dtype=torch.uint8)
+    blocks = nvfp4.swizzle_sf(sf)
+    assert blocks.shape == (2, 8, 512)
+    assert torch.equal(nvfp4.unswizzle_sf(blocks, 200, 20), sf)
+    r, g = 133, 7
+    assert blocks[r // 128, g // 4, (r % 32) * 16 + ((r % 128) // 32) * 4 + g % 4] == sf[r, g]
+
+
+def test_quant_dequant_error_cpu():
+    x = torch.randn(64, 256)
+    gs = float(x.abs().max()) / (6 * 448)
+    q, sfb = nvfp4.quantize_ref(x, gs)
+    y = nvfp4.dequantize_ref(q, sfb, gs)
+    rel = (x - y).norm() / x.norm()
+    assert rel < 0.12
+
+
+def test_linear_nvfp4_cpu_reference():
+    w = torch.randn(96, 128) * 0.02
+    x = torch.randn(5, 128)
+    wq = nvfp4.quantize_weight(w)
+    gs = torch.tensor(float(x.abs().max()) / (6 * 448))
+    xq = nvfp4.quantize(x.bfloat16(), gs)
+    y = gemm.linear_nvfp4(xq, wq, gs * wq.gscale)
+    ref = x @ w.t()
+    assert (y.float() - ref).norm() / ref.norm() < 0.2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (8, 5120, 5120), (64, 1024, 17408), (200, 384, 704),
+                                   (300, 512, 1024), (1024, 2048, 4096)])
+@pytest.mark.parametrize("epi", [gemm.EPI_STORE, gemm.EPI_RESIDUAL, gemm.EPI_SILU_MUL, gemm.EPI_STORE_F32])
+def test_gemm_bf16(m, n, k, epi):
+    dev = torch.device("cuda")
+    x = (torch.randn(m, k, device=dev) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device=dev) * 0.05).bfloat16()
+    res = torch.randn(m, n, device=dev).bfloat16() if epi == gemm.EPI_RESIDUAL else None
+    y = gemm.linear_bf16(x, w, epilogue=epi, residual=res)
+    ref = gemm._ref_epilogue(x.float() @ w.float().t(), epi, res)
+    torch.cuda.synchronize()
+    assert nv.read_status() == 0
+    err = (y.float() - ref.float()).abs().max().item()
+    scale = ref.float().abs().max().item()
+    assert err <= 2e-2 * scale + 1e-3, (err, scale)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k", [(1, 256), (7, 5120), (130, 704), (512, 17408)])
+@pytest.mark.parametrize("mode", [nvfp4.MODE_PLAIN, nvfp4.MODE_SILU_SPLIT, nvfp4.MODE_SILU_PAIRS])
+def test_quant_nvfp4_matches_reference(m, k, mode):
+    dev = torch.device("cuda")
+    cols = k if mode == nvfp4.MODE_PLAIN else 2 * k
+    x = torch.randn(m, cols, device=dev).bfloat16()
+    gs = torch.tensor(4.0 / (6 * 448), device=dev)
+    got = nvfp4.quantize(x, gs, mode)
+    y = x if mode == nvfp4.MODE_PLAIN else nvfp4._silu_mul(x, mode)
+    packed, sfb = nvfp4.quantize_ref(y, gs)
+    sf_got = nvfp4.unswizzle_sf(got.sf, m, k // 16)
+    # silu uses __expf on the device: allow a handful of one-step differences in the fused modes
+    mism_sf = (sf_got != sfb).float().mean().item()
+    mism_q = (got.q != packed).float().mean().item()
+    if mode == nvfp4.MODE_PLAIN:
+        assert mism_sf == 0 and mism_q == 0
+    else:
+        assert mism_sf < 1e-3 and mism_q < 1e-2
+    # padding scales are zero
+    blocks = got.sf
+    full = nvfp4.unswizzle_sf(blocks, blocks.shape[0] * 128, blocks.shape[1] * 4)
+    assert full[m:].sum() == 0 and full[:, k // 16:].sum() == 0
+
+
+@pytest.mark.gpu
+def test_norm_quant_matches_reference():
+    dev = torch.device("cuda")
+    m, k = 37, 5120
+    x = torch.randn(m, k, device=dev).bfloat16()
+    res = torch.randn(m, k, device=dev).bfloat16()
+    w = (torch.randn(k, device=dev) * 0.1 + 1).bfloat16()
+    gs = torch.tensor(8.0 / (6 * 448), device=dev)
+    res_ref = res.clone()
+    ref_q, ref_y = nvfp4.rmsnorm_quantize(x.cpu(), w.cpu(), 1e-6, gs.cpu(), residual=(res_cpu := res_ref.cpu()),
+                                          want_normed=True)
+    got_q, got_y = nvfp4.rmsnorm_quantize(x, w, 1e-6, gs, residual=res, want_normed=True)
+    assert torch.equal(res.cpu(), res_cpu)
+    assert (got_y.cpu().float() - ref_y.float()).abs().max() < 0.05
+    a, b = got_q.dequantize().cpu(), ref_q.dequantize()
+    assert (a - b).norm() / b.norm() < 0.02
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(1, 256, 256), (4, 5120, 5120), (16, 1024, 17408), (64, 34816, 5120),
+                                   (200, 384, 768), (300, 512, 1024), (1024, 5120, 2560), (2048, 768, 640)])
+def test_gemm_nvfp4(m, n, k):
+    dev = torch.device("cuda")
+    x = torch.randn(m, k, device=dev).bfloat16()
+    w = torch.randn(n, k, device=dev) * 0.02
+    wq = nvfp4.quantize_weight(w)
+    gs = torch.tensor(float(x.float().abs().max()) / (6 * 448), device=dev)
+    xq = nvfp4.quantize(x, gs)
+    alpha = (gs * wq.gscale).reshape(1)
+    y = gemm.linear_nvfp4(xq, wq, alpha)
+    torch.cuda.synchronize()
+    assert nv.read_status() == 0
+    ref = xq.dequantize() @ wq.dequantize().t()
+    err = (y.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 1.5e-2 * scale + 1e-4, (err, scale)
+
+
+@pytest.mark.gpu
+def test_gemm_nvfp4_epilogues_and_splitk_deterministic():
+    dev = torch.device("cuda")
+    m, n, k = 8, 1024, 8192
+    x = torch.randn(m, k, device=dev).bfloat16()
+    wq = nvfp4.quantize_weight(torch.randn(n, k, device=dev) * 0.02)
+    gs = torch.tensor(float(x.float().abs().max()) / (6 * 448), device=dev)
+    xq = nvfp4.quantize(x, gs)
+    alpha = (gs * wq.gscale).reshape(1)
+    acc = xq.dequantize() @ wq.dequantize().t()
+    res = torch.randn(m, n, device=dev).bfloat16()
+    for epi in (gemm.EPI_RESIDUAL, gemm.EPI_SILU_MUL):
+        y1 = gemm.linear_nvfp4(xq, wq, alpha, epilogue=epi, residual=res, splits=4)
+        y2 = gemm.linear_nvfp4(xq, wq, alpha, epilogue=epi, residual=res, splits=4)
+        y3 = gemm.linear_nvfp4(xq, wq, alpha, epilogue=epi, residual=res, splits=1)
+        ref = gemm._ref_epilogue(acc, epi, res)
+        assert torch.equal(y1, y2)
+        for y in (y1, y3):
+            assert (y.float() - ref.float()).abs().max() <= 2e-2 * ref.float().abs().max() + 1e-3
+    assert nv.read_status() == 0
