@@ -1,0 +1,394 @@
+// Paged GQA attention over the token-granular KV pool (split-KV, CUDA-core path).
+//
+// The KV pool stores one row per token slot: k_pool / v_pool [slots, kv_heads, D] (bf16 or e4m3). A sequence's
+// context is a row of the block table `kv_indices[b, 0..ctx)` (slot of every position), so radix-tree prefix
+// sharing is token-granular. One CTA owns (sequence, kv head, query-row chunk, KV split): it streams K/V tiles
+// of 64 keys through a cp.async double buffer, scores them for all query rows that share the kv head (GQA
+// group x up to a few tokens), keeps an online softmax, and writes either the final output or a partial with
+// its log-sum-exp for the merge kernel. The KV range of a split is computed on the device from ctx_len, so one
+// captured launch serves any context length.
+//
+// Rows per sequence R >= 1 covers decode (R = 1), speculative verify (R = k + 1 <= 16, causal inside the block)
+// and, as a slow general fallback, chunked prefill. Reference counterparts: FlashInfer decode / paged prefill
+// wrappers planned in hibana/engine/executor.py:161-169 and hibana/kernels/csrc/verify_attn.cu:299-660.
+#include "hb_api.h"
+#include "hb_common.cuh"
+
+namespace hb {
+namespace {
+
+constexpr int TK = 64;         // keys per tile
+constexpr int ATT_THREADS = 128;
+
+struct AttnParams {
+  const __nv_bfloat16* q;      // [T, Hq, D]
+  const void* k_pool;
+  const void* v_pool;
+  long long pool_stride;       // elements between slots (kv_heads * D)
+  const int* kv_indices;       // [B, ld_idx]
+  long long ld_idx;
+  const int* ctx_len;          // [B] keys visible to the last query row of the sequence
+  const int* q_indptr;         // [B + 1] query row offsets; null = one row per sequence
+  __nv_bfloat16* out;          // [T, Hq, D]
+  float* part_o;               // [T, Hq, S, D]
+  float* part_lse;             // [T, Hq, S]
+  int hq, hkv, splits, rows_per_cta;
+  float scale_log2;            // softmax scale * log2(e)
+  float kv_scale;              // dequant scale of fp8 KV
+  int causal;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <bool FP8>
+__device__ __forceinline__ void unpack16(const uint8_t* p, float* f, int* n) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+  if constexpr (FP8) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) f[4 * i + j] = e4m3_to_float((w[i] >> (8 * j)) & 0xFF);
+    }
+    *n = 16;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = bf16_lo(w[i]);
+      f[2 * i + 1] = bf16_hi(w[i]);
+    }
+    *n = 8;
+  }
+}
+
+template <int D, int MAXQ, bool FP8>
+__global__ void __launch_bounds__(ATT_THREADS) attn_splitkv_kernel(const AttnParams p) {
+  constexpr int ESZ = FP8 ? 1 : 2;
+  constexpr int ROW_DATA = D * ESZ;
+  constexpr int ROWB = ROW_DATA + 16;  // padded: conflict-free 16-byte reads down a column of rows
+  constexpr int CHUNKS = ROW_DATA / 16;
+  constexpr int EPC = 16 / ESZ;        // elements per 16-byte chunk
+  constexpr int HALFQ = (MAXQ + 1) / 2;
+  constexpr int DPT = D > 128 ? D / 128 : 1;  // dims per thread in the PV phase
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* kbuf = smem_raw;                              // [2][TK][ROWB]
+  uint8_t* vbuf = kbuf + 2 * TK * ROWB;                  // [2][TK][ROWB]
+  float* qs = reinterpret_cast<float*>(vbuf + 2 * TK * ROWB);  // [MAXQ][D]
+  float* sc = qs + MAXQ * D;                             // [MAXQ][TK + 1]
+  float* pt = sc + MAXQ * (TK + 1);                      // [TK][MAXQ]
+  float* m_s = pt + TK * MAXQ;                           // [MAXQ]
+  float* l_s = m_s + MAXQ;
+  float* a_s = l_s + MAXQ;
+  int* idx_s = reinterpret_cast<int*>(a_s + MAXQ);       // [2][TK]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.x;
+  const int kvh = blockIdx.y % p.hkv;
+  const int rchunk = blockIdx.y / p.hkv;
+  const int split = blockIdx.z;
+  const int g = p.hq / p.hkv;
+  const int row0 = p.q_indptr ? p.q_indptr[b] : b;
+  const int R = p.q_indptr ? p.q_indptr[b + 1] - row0 : 1;
+  const int r0 = rchunk * p.rows_per_cta;
+  if (r0 >= R) return;
+  const int nrows = min(p.rows_per_cta, R - r0);
+  const int nq = nrows * g;
+  const int ctx = p.ctx_len[b];
+  // Keys this CTA needs: causal limit of its last row, then the split's slice.
+  const int need = p.causal ? ctx - R + r0 + nrows : ctx;
+  const int per = (((ctx + p.splits - 1) / p.splits + TK - 1) / TK) * TK;
+  const int k0 = split * per;
+  const int k1 = min(need, k0 + per);
+  const int ntiles = k1 > k0 ? (k1 - k0 + TK - 1) / TK : 0;
+
+  for (int i = tid; i < MAXQ * D; i += ATT_THREADS) {
+    const int qi = i / D, d = i % D;
+    float v = 0.f;
+    if (qi < nq) {
+      const int rr = qi / g, gg = qi % g;
+      v = __bfloat162float(p.q[(static_cast<long long>(row0 + r0 + rr) * p.hq + kvh * g + gg) * D + d]) * p.scale_log2;
+    }
+    qs[i] = v;
+  }
+  if (tid < MAXQ) {
+    m_s[tid] = -INFINITY;
+    l_s[tid] = 0.f;
+  }
+  float acc[MAXQ][DPT];
+#pragma unroll
+  for (int i = 0; i < MAXQ; ++i)
+#pragma unroll
+    for (int j = 0; j < DPT; ++j) acc[i][j] = 0.f;
+
+  const int* idx_row = p.kv_indices + static_cast<long long>(b) * p.ld_idx;
+  const uint8_t* kp = static_cast<const uint8_t*>(p.k_pool);
+  const uint8_t* vp = static_cast<const uint8_t*>(p.v_pool);
+
+  auto load_tile = [&](int t, int buf) {
+    const int base = k0 + t * TK;
+    // Slot ids are read straight from global by every thread for its own chunks (L1/L2 hits).
+    for (int c = tid; c < TK * CHUNKS; c += ATT_THREADS) {
+      const int key = c / CHUNKS, part = c % CHUNKS;
+      const int kpos = base + key;
+      uint8_t* kd = kbuf + (buf * TK + key) * ROWB + part * 16;
+      uint8_t* vd = vbuf + (buf * TK + key) * ROWB + part * 16;
+      if (kpos < k1) {
+        const long long off = (static_cast<long long>(idx_row[kpos]) * p.pool_stride + static_cast<long long>(kvh) * D) * ESZ + part * 16;
+        cp_async16(kd, kp + off);
+        cp_async16(vd, vp + off);
+      } else {
+        *reinterpret_cast<uint4*>(kd) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(vd) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    cp_async_commit();
+  };
+
+  if (ntiles > 0) load_tile(0, 0);
+  for (int t = 0; t < ntiles; ++t) {
+    const int buf = t & 1;
+    if (t + 1 < ntiles) {
+      load_tile(t + 1, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    // ---- scores: two threads per key, each takes every other query row
+    {
+      const int key = tid & (TK - 1);
+      const int qpar = tid >> 6;  // 0 or 1
+      float s[HALFQ];
+#pragma unroll
+      for (int i = 0; i < HALFQ; ++i) s[i] = 0.f;
+      const uint8_t* krow = kbuf + (buf * TK + key) * ROWB;
+#pragma unroll 2
+      for (int c = 0; c < CHUNKS; ++c) {
+        float kf[16];
+        int n;
+        unpack16<FP8>(krow + c * 16, kf, &n);
+#pragma unroll
+        for (int i = 0; i < HALFQ; ++i) {
+          const int qi = 2 * i + qpar;
+          if (qi < nq) {
+            const float4* qv = reinterpret_cast<const float4*>(qs + qi * D + c * EPC);
+#pragma unroll
+            for (int e = 0; e < EPC / 4; ++e) {
+              const float4 qq = qv[e];
+              s[i] += kf[4 * e] * qq.x + kf[4 * e + 1] * qq.y + kf[4 * e + 2] * qq.z + kf[4 * e + 3] * qq.w;
+            }
+          }
+        }
+      }
+      const int kpos = k0 + t * TK + key;
+#pragma unroll
+      for (int i = 0; i < HALFQ; ++i) {
+        const int qi = 2 * i + qpar;
+        if (qi < nq) {
+          const int rr = qi / g;
+          const int limit = p.causal ? ctx - R + r0 + rr + 1 : ctx;  // keys [0, limit) are visible
+          float v = s[i];
+          if (FP8) v *= p.kv_scale;
+          sc[qi * (TK + 1) + key] = (kpos < limit && kpos < k1) ? v : -INFINITY;
+        }
+      }
+    }
+    __syncthreads();
+    // ---- online softmax: one warp per query row
+    for (int qi = warp; qi < nq; qi += ATT_THREADS / 32) {
+      const float s0 = sc[qi * (TK + 1) + lane], s1 = sc[qi * (TK + 1) + lane + 32];
+      const float mx = warp_max(fmaxf(s0, s1));
+      const float m_old = m_s[qi];
+      const float m_new = fmaxf(m_old, mx);
+      float p0 = 0.f, p1 = 0.f, alpha = 1.f;
+      if (m_new > -INFINITY) {
+        p0 = exp2f(s0 - m_new);
+        p1 = exp2f(s1 - m_new);
+        alpha = exp2f(m_old - m_new);
+      }
+      const float sum = warp_sum(p0 + p1);
+      pt[lane * MAXQ + qi] = p0;
+      pt[(lane + 32) * MAXQ + qi] = p1;
+      if (lane == 0) {
+        m_s[qi] = m_new;
+        l_s[qi] = l_s[qi] * alpha + sum;
+        a_s[qi] = alpha;
+      }
+    }
+    __syncthreads();
+    // ---- PV: thread owns output dims, loops over keys
+    if (tid < D || D >= 128) {
+#pragma unroll
+      for (int i = 0; i < MAXQ; ++i) {
+        if (i < nq) {
+          const float a = a_s[i];
+#pragma unroll
+          for (int j = 0; j < DPT; ++j) acc[i][j] *= a;
+        }
+      }
+      const uint8_t* vb = vbuf + buf * TK * ROWB;
+      for (int key = 0; key < TK; ++key) {
+        float vv[DPT];
+#pragma unroll
+        for (int j = 0; j < DPT; ++j) {
+          const int d = tid + j * 128;
+          if constexpr (FP8) vv[j] = e4m3_to_float(vb[key * ROWB + d]);
+          else vv[j] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(vb + key * ROWB + d * 2));
+        }
+        const float* pr = pt + key * MAXQ;
+#pragma unroll
+        for (int i = 0; i < MAXQ; i += 4) {
+          const float4 pp = *reinterpret_cast<const float4*>(pr + i);
+          const float pv[4] = {pp.x, pp.y, pp.z, pp.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (i + e < MAXQ) {
+#pragma unroll
+              for (int j = 0; j < DPT; ++j) acc[i + e][j] += pv[e] * vv[j];
+            }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- epilogue
+  if (tid < D || D >= 128) {
+#pragma unroll
+    for (int i = 0; i < MAXQ; ++i) {
+      if (i < nq) {
+        const int rr = i / g, gg = i % g;
+        const long long row = row0 + r0 + rr;
+        const int head = kvh * g + gg;
+        const float l = l_s[i];
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+        for (int j = 0; j < DPT; ++j) {
+          const int d = tid + j * 128;
+          float o = acc[i][j] * inv;
+          if (FP8) o *= p.kv_scale;
+          if (p.splits == 1) p.out[(row * p.hq + head) * D + d] = __float2bfloat16(o);
+          else p.part_o[((row * p.hq + head) * p.splits + split) * D + d] = o;
+        }
+        if (p.splits > 1 && tid == 0)
+          p.part_lse[(row * p.hq + head) * p.splits + split] = l > 0.f ? m_s[i] + log2f(l) : -INFINITY;
+      }
+    }
+  }
+}
+
+// Merge of split partials: o = sum_s 2^(lse_s - m) o_s / sum_s 2^(lse_s - m). One CTA per (row, head).
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                  __nv_bfloat16* __restrict__ out, int splits, int d) {
+  const long long rh = blockIdx.x;
+  const float* lse = part_lse + rh * splits;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, lse[s]);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float o = 0.f, wsum = 0.f;
+    if (m > -INFINITY) {
+      for (int s = 0; s < splits; ++s) {
+        const float w = exp2f(lse[s] - m);
+        if (w > 0.f) o += w * part_o[(rh * splits + s) * d + i];
+        wsum += w;
+      }
+      o /= wsum;
+    }
+    out[rh * d + i] = __float2bfloat16(o);
+  }
+}
+
+template <int D, int MAXQ, bool FP8>
+size_t attn_smem_bytes() {
+  constexpr int ESZ = FP8 ? 1 : 2;
+  constexpr int ROWB = D * ESZ + 16;
+  return static_cast<size_t>(4) * TK * ROWB + sizeof(float) * (MAXQ * D + MAXQ * (TK + 1) + TK * MAXQ + 3 * MAXQ) +
+         sizeof(int) * 2 * TK;
+}
+
+template <int D, int MAXQ, bool FP8>
+int launch_attn(const AttnParams& p, int batch, int row_chunks, cudaStream_t st) {
+  const size_t smem = attn_smem_bytes<D, MAXQ, FP8>();
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(attn_splitkv_kernel<D, MAXQ, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return 3;
+    attr = true;
+  }
+  const dim3 grid(batch, p.hkv * row_chunks, p.splits);
+  attn_splitkv_kernel<D, MAXQ, FP8><<<grid, ATT_THREADS, smem, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+template <int D, bool FP8>
+int dispatch_q(const AttnParams& p, int batch, int row_chunks, int nq, cudaStream_t st) {
+  if (nq <= 8) return launch_attn<D, 8, FP8>(p, batch, row_chunks, st);
+  if (nq <= 16) return launch_attn<D, 16, FP8>(p, batch, row_chunks, st);
+  return launch_attn<D, 32, FP8>(p, batch, row_chunks, st);
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" {
+
+// max_rows: largest number of query rows of any sequence (1 for decode). Partials are needed when splits > 1.
+int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                  const void* kv_indices, long long ld_idx, const void* ctx_len, const void* q_indptr, void* out,
+                  void* part_o, void* part_lse, int batch, int total_rows, int max_rows, int hq, int hkv, int d,
+                  int splits, float scale, int kv_fp8, float kv_scale, int causal, void* stream) {
+  if (batch <= 0) return 0;
+  if (hq % hkv != 0) return 1;
+  const int g = hq / hkv;
+  if (g > 32) return 1;
+  AttnParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_pool = k_pool; p.v_pool = v_pool; p.pool_stride = pool_stride;
+  p.kv_indices = static_cast<const int*>(kv_indices); p.ld_idx = ld_idx;
+  p.ctx_len = static_cast<const int*>(ctx_len);
+  p.q_indptr = static_cast<const int*>(q_indptr);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.part_o = static_cast<float*>(part_o); p.part_lse = static_cast<float*>(part_lse);
+  p.hq = hq; p.hkv = hkv; p.splits = splits < 1 ? 1 : splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.kv_scale = kv_scale; p.causal = causal;
+  if (p.splits > 1 && (part_o == nullptr || part_lse == nullptr)) return 1;
+  // Query rows per CTA: as many tokens as fit 32 (group x tokens), at most what the batch needs.
+  int rows_per_cta = 32 / g;
+  if (rows_per_cta > max_rows) rows_per_cta = max_rows;
+  if (rows_per_cta < 1) rows_per_cta = 1;
+  p.rows_per_cta = rows_per_cta;
+  const int row_chunks = (max_rows + rows_per_cta - 1) / rows_per_cta;
+  const int nq = rows_per_cta * g;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = 1;
+  if (kv_fp8) {
+    if (d == 64) rc = dispatch_q<64, true>(p, batch, row_chunks, nq, st);
+    else if (d == 128) rc = dispatch_q<128, true>(p, batch, row_chunks, nq, st);
+    else if (d == 256) rc = dispatch_q<256, true>(p, batch, row_chunks, nq, st);
+  } else {
+    if (d == 64) rc = dispatch_q<64, false>(p, batch, row_chunks, nq, st);
+    else if (d == 128) rc = dispatch_q<128, false>(p, batch, row_chunks, nq, st);
+    else if (d == 256) rc = dispatch_q<256, false>(p, batch, row_chunks, nq, st);
+  }
+  if (rc != 0) return rc;
+  if (p.splits > 1) {
+    attn_merge_kernel<<<static_cast<unsigned>(static_cast<long long>(total_rows) * hq), 128, 0, st>>>(
+        p.part_o, p.part_lse, p.out, p.splits, d);
+    if (cudaGetLastError() != cudaSuccess) return 2;
+  }
+  return 0;
+}
+
+}  // extern "C"

@@ -24,6 +24,26 @@ int hb_norm_quant_nvfp4(const void* x, void* residual, const void* w, float eps,
 int hb_quant_fp8_static(const void* x, long long n, const void* scale, void* q, void* stream);
 int hb_quant_fp8_rows(const void* x, int m, int k, void* q, void* scales, void* stream);
 
+// ---- pointwise / row kernels (misc.cu) -----------------------------------------------------------------
+int hb_rmsnorm(const void* x, void* residual, const void* w, void* y, int rows, int h, long long ldx, long long ldy,
+               float eps, int gemma, void* stream);
+int hb_gated_rmsnorm(const void* x, const void* z, const void* w, void* y, int rows, int h, int gs, long long ldx,
+                     long long ldz, float eps, int norm_first, int sigmoid_gate, int gemma, void* stream);
+int hb_rope_kv_write(const void* qkv, long long ld_qkv, const void* positions, const void* slots,
+                     const void* inv_freq, const void* q_norm_w, const void* k_norm_w, float eps, int gemma_norm,
+                     void* q_out, void* k_pool, void* v_pool, long long pool_stride, int tokens, int hq, int hkv,
+                     int d, int rot, int kv_fp8, float kv_inv_scale, int q_gate, void* stream);
+int hb_act_mul(const void* x, const void* gate, void* out, long long rows, int inter, long long ldx, int mode,
+               void* stream);
+int hb_embedding(const void* ids, const void* table, void* out, int tokens, int h, long long vocab, void* stream);
+int hb_add(const void* a, const void* b, void* out, long long n, void* stream);
+
+// ---- paged attention (attn.cu) -------------------------------------------------------------------------
+int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                  const void* kv_indices, long long ld_idx, const void* ctx_len, const void* q_indptr, void* out,
+                  void* part_o, void* part_lse, int batch, int total_rows, int max_rows, int hq, int hkv, int d,
+                  int splits, float scale, int kv_fp8, float kv_scale, int causal, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,297 @@
+// Memory-bound pointwise / row kernels for sm_100a: RMSNorm family, RoPE + q/k norm + KV-pool write,
+// SiLU-mul, ReLU^2, sigmoid gates, embedding gather, residual add.
+//
+// Reference counterparts: hibana/model/norm.py:14-71, hibana/model/nemotron/norm.py:23-84,
+// hibana/kernels/qk_norm_rope.py:16, hibana/model/rope.py:12, hibana/kernels/nemotron_fused.py:20,
+// hibana/cache/kv_pool.py:120-132, hibana/kernels/flashnext_fused.py:624-660, hibana/kernels/mamba2.py:797.
+#include "hb_api.h"
+#include "hb_common.cuh"
+
+namespace hb {
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < nw ? red[l] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// y = rmsnorm(x (+ residual)) * w; when residual != null it is updated in place with x + residual.
+// One CTA per row; 8 bf16 per thread per step; row cached in registers for H <= 8 * 8 * blockDim.
+template <int MAXV>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
+               const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int h, long long ldx,
+               long long ldy, float eps, int gemma) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int nvec = h >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
+  uint4* rr = residual ? reinterpret_cast<uint4*>(residual + static_cast<long long>(row) * h) : nullptr;
+  float v[MAXV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nvec) {
+      const uint4 a = xr[idx];
+      v[i][0] = bf16_lo(a.x); v[i][1] = bf16_hi(a.x); v[i][2] = bf16_lo(a.y); v[i][3] = bf16_hi(a.y);
+      v[i][4] = bf16_lo(a.z); v[i][5] = bf16_hi(a.z); v[i][6] = bf16_lo(a.w); v[i][7] = bf16_hi(a.w);
+      if (rr) {
+        const uint4 b = rr[idx];
+        const float r[8] = {bf16_lo(b.x), bf16_hi(b.x), bf16_lo(b.y), bf16_hi(b.y),
+                            bf16_lo(b.z), bf16_hi(b.z), bf16_lo(b.w), bf16_hi(b.w)};
+#pragma unroll
+        for (int t = 0; t < 8; ++t) v[i][t] = __bfloat162float(__float2bfloat16(v[i][t] + r[t]));
+        rr[idx] = make_uint4(pack_bf16(v[i][0], v[i][1]), pack_bf16(v[i][2], v[i][3]), pack_bf16(v[i][4], v[i][5]),
+                             pack_bf16(v[i][6], v[i][7]));
+      }
+#pragma unroll
+      for (int t = 0; t < 8; ++t) ss += v[i][t] * v[i][t];
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / h + eps);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * ldy);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nvec) {
+      const uint4 b = wr[idx];
+      float ww[8] = {bf16_lo(b.x), bf16_hi(b.x), bf16_lo(b.y), bf16_hi(b.y),
+                     bf16_lo(b.z), bf16_hi(b.z), bf16_lo(b.w), bf16_hi(b.w)};
+      float o[8];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) o[t] = v[i][t] * rstd * (gemma ? 1.f + ww[t] : ww[t]);
+      yr[idx] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+    }
+  }
+}
+
+// Gated grouped RMSNorm (Mamba-2 / GDN output): y = rmsnorm_g(x * silu(z)) * w with groups of `gs` channels,
+// or norm-before-gate when norm_first != 0: y = rmsnorm_g(x) * w * silu(z). One warp per (row, group).
+__global__ void gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ z,
+                                     const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int rows,
+                                     int h, int gs, long long ldx, long long ldz, float eps, int norm_first,
+                                     int sigmoid_gate, int gemma) {
+  const int groups = h / gs;
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= static_cast<long long>(rows) * groups) return;
+  const int row = static_cast<int>(wid / groups), g = static_cast<int>(wid % groups);
+  const __nv_bfloat16* xr = x + row * ldx + g * gs;
+  const __nv_bfloat16* zr = z ? z + row * ldz + g * gs : nullptr;
+  float ss = 0.f;
+  for (int i = lane; i < gs; i += 32) {
+    float v = __bfloat162float(xr[i]);
+    if (zr && !norm_first) {
+      const float zz = __bfloat162float(zr[i]);
+      v *= sigmoid_gate ? 1.f / (1.f + __expf(-zz)) : zz / (1.f + __expf(-zz));
+    }
+    ss += v * v;
+  }
+  const float rstd = rsqrtf(warp_sum(ss) / gs + eps);
+  for (int i = lane; i < gs; i += 32) {
+    float v = __bfloat162float(xr[i]);
+    float gate = 1.f;
+    if (zr) {
+      const float zz = __bfloat162float(zr[i]);
+      gate = sigmoid_gate ? 1.f / (1.f + __expf(-zz)) : zz / (1.f + __expf(-zz));
+    }
+    const float ww = __bfloat162float(w[g * gs + i]);
+    const float wv = gemma ? 1.f + ww : ww;
+    const float o = norm_first ? v * rstd * wv * gate : v * gate * rstd * wv;
+    y[static_cast<long long>(row) * h + g * gs + i] = __float2bfloat16(o);
+  }
+}
+
+// Per token: optional per-head RMSNorm of q and k, NeoX rotary on the first `rot` dims of q and k, q written to
+// q_out [T, Hq, D], k and v rows written into the paged pools at slot[t] (bf16 or e4m3 with scale 1/kv_scale).
+// qkv row layout: [Hq * D | Hkv * D | Hkv * D]. One CTA per token, one warp per head (looping).
+__global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_qkv,
+                                     const int* __restrict__ positions, const int* __restrict__ slots,
+                                     const float* __restrict__ inv_freq, const __nv_bfloat16* __restrict__ q_norm_w,
+                                     const __nv_bfloat16* __restrict__ k_norm_w, float eps, int gemma_norm,
+                                     __nv_bfloat16* __restrict__ q_out, void* __restrict__ k_pool,
+                                     void* __restrict__ v_pool, long long pool_stride, int hq, int hkv, int d, int rot,
+                                     int kv_fp8, float kv_inv_scale, int q_gate) {
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const float pos = static_cast<float>(positions[t]);
+  const int slot = slots ? slots[t] : -1;
+  const int half = rot >> 1;
+  // With q_gate the q block holds [q | gate] per head (2 * D per head); the gate half is left untouched.
+  const int q_head_stride = q_gate ? 2 * d : d;
+  const __nv_bfloat16* row = qkv + t * ld_qkv;
+  for (int hd = warp; hd < hq + 2 * hkv; hd += nw) {
+    const bool is_q = hd < hq, is_k = !is_q && hd < hq + hkv;
+    const __nv_bfloat16* src = is_q ? row + hd * q_head_stride
+                                    : row + hq * q_head_stride + (hd - hq) * d;
+    float rstd = 1.f;
+    const __nv_bfloat16* nw_ptr = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+    if (nw_ptr != nullptr) {
+      float ss = 0.f;
+      for (int i = lane; i < d; i += 32) {
+        const float v = __bfloat162float(src[i]);
+        ss += v * v;
+      }
+      rstd = rsqrtf(warp_sum(ss) / d + eps);
+    }
+    __nv_bfloat16* dst_bf = nullptr;
+    uint8_t* dst_f8 = nullptr;
+    if (is_q) {
+      dst_bf = q_out + (static_cast<long long>(t) * hq + hd) * d;
+    } else {
+      if (slot < 0) continue;
+      const int kh = is_k ? hd - hq : hd - hq - hkv;
+      void* pool = is_k ? k_pool : v_pool;
+      const long long off = static_cast<long long>(slot) * pool_stride + static_cast<long long>(kh) * d;
+      if (kv_fp8) dst_f8 = static_cast<uint8_t*>(pool) + off;
+      else dst_bf = static_cast<__nv_bfloat16*>(pool) + off;
+    }
+    for (int i = lane; i < d; i += 32) {
+      float v = __bfloat162float(src[i]);
+      if (nw_ptr != nullptr) {
+        const float ww = __bfloat162float(nw_ptr[i]);
+        v = __bfloat162float(__float2bfloat16(v * rstd * (gemma_norm ? 1.f + ww : ww)));
+      }
+      float o = v;
+      if ((is_q || is_k) && i < rot) {
+        const int j = i < half ? i : i - half;
+        const int pi = i < half ? i + half : i - half;
+        float pv = __bfloat162float(src[pi]);
+        if (nw_ptr != nullptr) {
+          const float ww = __bfloat162float(nw_ptr[pi]);
+          pv = __bfloat162float(__float2bfloat16(pv * rstd * (gemma_norm ? 1.f + ww : ww)));
+        }
+        float sn, cs;
+        sincosf(pos * inv_freq[j], &sn, &cs);
+        o = i < half ? v * cs - pv * sn : v * cs + pv * sn;
+      }
+      if (dst_f8) dst_f8[i] = static_cast<uint8_t>(float_to_e4m3(o * kv_inv_scale));
+      else dst_bf[i] = __float2bfloat16(o);
+    }
+  }
+}
+
+// out[t, j] = act(x[t, j]) * x[t, I + j] (mode 0: silu split), pairs interleaved (mode 1), relu^2 (mode 2, no mul),
+// x * sigmoid(gate) with separate gate pointer (mode 3).
+__global__ void act_mul_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate,
+                               __nv_bfloat16* __restrict__ out, long long rows, int inter, long long ldx, int mode) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= rows * inter) return;
+  const long long r = idx / inter;
+  const int j = static_cast<int>(idx % inter);
+  float o;
+  if (mode == 0) {
+    const float g = __bfloat162float(x[r * ldx + j]), u = __bfloat162float(x[r * ldx + inter + j]);
+    o = g / (1.f + __expf(-g)) * u;
+  } else if (mode == 1) {
+    const float g = __bfloat162float(x[r * ldx + 2 * j]), u = __bfloat162float(x[r * ldx + 2 * j + 1]);
+    o = g / (1.f + __expf(-g)) * u;
+  } else if (mode == 2) {
+    const float g = fmaxf(__bfloat162float(x[r * ldx + j]), 0.f);
+    o = g * g;
+  } else {
+    const float v = __bfloat162float(x[r * ldx + j]), g = __bfloat162float(gate[r * ldx + j]);
+    o = v / (1.f + __expf(-g));
+  }
+  out[r * inter + j] = __float2bfloat16(o);
+}
+
+__global__ void embedding_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                 __nv_bfloat16* __restrict__ out, int h, long long vocab) {
+  const int t = blockIdx.x;
+  long long id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const uint4* src = reinterpret_cast<const uint4*>(table + id * h);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(t) * h);
+  for (int i = threadIdx.x; i < (h >> 3); i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                           __nv_bfloat16* __restrict__ out, long long n) {
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 2;
+  if (i + 1 < n) {
+    const uint32_t x = *reinterpret_cast<const uint32_t*>(a + i), y = *reinterpret_cast<const uint32_t*>(b + i);
+    *reinterpret_cast<uint32_t*>(out + i) = pack_bf16(bf16_lo(x) + bf16_lo(y), bf16_hi(x) + bf16_hi(y));
+  } else if (i < n) {
+    out[i] = __float2bfloat16(__bfloat162float(a[i]) + __bfloat162float(b[i]));
+  }
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+#define ST(s) static_cast<cudaStream_t>(s)
+#define BF(p) static_cast<const __nv_bfloat16*>(p)
+#define BFM(p) static_cast<__nv_bfloat16*>(p)
+#define OK() (cudaGetLastError() == cudaSuccess ? 0 : 2)
+
+extern "C" {
+
+int hb_rmsnorm(const void* x, void* residual, const void* w, void* y, int rows, int h, long long ldx, long long ldy,
+               float eps, int gemma, void* stream) {
+  if (h % 8 != 0 || rows <= 0) return 1;
+  const int nvec = h / 8;
+  if (nvec <= 256) rmsnorm_kernel<1><<<rows, 256, 0, ST(stream)>>>(BF(x), BFM(residual), BF(w), BFM(y), h, ldx, ldy, eps, gemma);
+  else if (nvec <= 512) rmsnorm_kernel<2><<<rows, 256, 0, ST(stream)>>>(BF(x), BFM(residual), BF(w), BFM(y), h, ldx, ldy, eps, gemma);
+  else if (nvec <= 1024) rmsnorm_kernel<4><<<rows, 256, 0, ST(stream)>>>(BF(x), BFM(residual), BF(w), BFM(y), h, ldx, ldy, eps, gemma);
+  else if (nvec <= 2048) rmsnorm_kernel<8><<<rows, 256, 0, ST(stream)>>>(BF(x), BFM(residual), BF(w), BFM(y), h, ldx, ldy, eps, gemma);
+  else return 1;
+  return OK();
+}
+
+int hb_gated_rmsnorm(const void* x, const void* z, const void* w, void* y, int rows, int h, int gs, long long ldx,
+                     long long ldz, float eps, int norm_first, int sigmoid_gate, int gemma, void* stream) {
+  if (h % gs != 0) return 1;
+  const long long warps = static_cast<long long>(rows) * (h / gs);
+  const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
+  gated_rmsnorm_kernel<<<blocks, 256, 0, ST(stream)>>>(BF(x), BF(z), BF(w), BFM(y), rows, h, gs, ldx, ldz, eps,
+                                                       norm_first, sigmoid_gate, gemma);
+  return OK();
+}
+
+int hb_rope_kv_write(const void* qkv, long long ld_qkv, const void* positions, const void* slots,
+                     const void* inv_freq, const void* q_norm_w, const void* k_norm_w, float eps, int gemma_norm,
+                     void* q_out, void* k_pool, void* v_pool, long long pool_stride, int tokens, int hq, int hkv,
+                     int d, int rot, int kv_fp8, float kv_inv_scale, int q_gate, void* stream) {
+  if (tokens <= 0) return 0;
+  if (rot > d || (rot & 1)) return 1;
+  rope_kv_write_kernel<<<tokens, 256, 0, ST(stream)>>>(
+      BF(qkv), ld_qkv, static_cast<const int*>(positions), static_cast<const int*>(slots),
+      static_cast<const float*>(inv_freq), BF(q_norm_w), BF(k_norm_w), eps, gemma_norm, BFM(q_out), k_pool, v_pool,
+      pool_stride, hq, hkv, d, rot, kv_fp8, kv_inv_scale, q_gate);
+  return OK();
+}
+
+int hb_act_mul(const void* x, const void* gate, void* out, long long rows, int inter, long long ldx, int mode,
+               void* stream) {
+  const long long n = rows * inter;
+  if (n <= 0) return 0;
+  act_mul_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, ST(stream)>>>(BF(x), BF(gate), BFM(out), rows,
+                                                                                inter, ldx, mode);
+  return OK();
+}
+
+int hb_embedding(const void* ids, const void* table, void* out, int tokens, int h, long long vocab, void* stream) {
+  if (tokens <= 0) return 0;
+  if (h % 8 != 0) return 1;
+  embedding_kernel<<<tokens, 128, 0, ST(stream)>>>(static_cast<const long long*>(ids), BF(table), BFM(out), h, vocab);
+  return OK();
+}
+
+int hb_add(const void* a, const void* b, void* out, long long n, void* stream) {
+  if (n <= 0) return 0;
+  const long long threads = (n + 1) / 2;
+  add_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, ST(stream)>>>(BF(a), BF(b), BFM(out), n);
+  return OK();
+}
+
+}  // extern "C"

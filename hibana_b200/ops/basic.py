@@ -1,0 +1,177 @@
+"""Row / pointwise ops: RMSNorm family, RoPE + q/k norm + KV-pool write, activations, embedding.
+
+Each function runs the sm_100a kernel from csrc/misc.cu on CUDA tensors and a plain-PyTorch fp32 reference on
+CPU tensors (the reference is also the oracle of the GPU numerics tests).
+Reference counterparts: hibana/model/norm.py:14-71, hibana/model/rope.py:12, hibana/kernels/qk_norm_rope.py:16,
+hibana/cache/kv_pool.py:120-132, hibana/kernels/flashnext_fused.py:624-660.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from .. import _native as nv
+
+P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
+nv.register("hb_rmsnorm", [P, P, P, P, I, I, L, L, Fl, I, P])
+nv.register("hb_gated_rmsnorm", [P, P, P, P, I, I, I, L, L, Fl, I, I, I, P])
+nv.register("hb_rope_kv_write", [P, L, P, P, P, P, P, Fl, I, P, P, P, L, I, I, I, I, I, I, Fl, I, P])
+nv.register("hb_act_mul", [P, P, P, L, I, L, I, P])
+nv.register("hb_embedding", [P, P, P, I, I, L, P])
+nv.register("hb_add", [P, P, P, L, P])
+
+ACT_SILU_SPLIT, ACT_SILU_PAIRS, ACT_RELU2, ACT_SIGMOID_GATE = 0, 1, 2, 3
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, *, residual: Optional[torch.Tensor] = None,
+            gemma: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = rmsnorm(x [+ residual]) * w (gemma: (1 + w)). `residual` (contiguous) is updated in place."""
+    rows, h = x.shape
+    if nv.use_native(x):
+        out = torch.empty(rows, h, dtype=x.dtype, device=x.device) if out is None else out
+        nv.check(nv.lib().hb_rmsnorm(x.data_ptr(), nv.ptr(residual), weight.data_ptr(), out.data_ptr(), rows, h,
+                                     x.stride(0), out.stride(0), eps, int(gemma), nv.stream()), "hb_rmsnorm")
+        return out
+    hsum = x
+    if residual is not None:
+        residual.copy_((x.float() + residual.float()).to(x.dtype))
+        hsum = residual
+    hf = hsum.float()
+    w = weight.float() + 1.0 if gemma else weight.float()
+    y = (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps) * w).to(x.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def gated_rmsnorm(x: torch.Tensor, z: Optional[torch.Tensor], weight: torch.Tensor, eps: float, group_size: int, *,
+                  norm_first: bool = False, sigmoid_gate: bool = False, gemma: bool = False) -> torch.Tensor:
+    """Grouped RMSNorm with a gate: rmsnorm_g(x * silu(z)) * w, or rmsnorm_g(x) * w * act(z) when norm_first."""
+    rows, h = x.shape
+    if nv.use_native(x):
+        out = torch.empty(rows, h, dtype=x.dtype, device=x.device)
+        nv.check(nv.lib().hb_gated_rmsnorm(x.data_ptr(), nv.ptr(z), weight.data_ptr(), out.data_ptr(), rows, h,
+                                           group_size, x.stride(0), z.stride(0) if z is not None else 0, eps,
+                                           int(norm_first), int(sigmoid_gate), int(gemma), nv.stream()),
+                 "hb_gated_rmsnorm")
+        return out
+    xf = x.float()
+    gate = None
+    if z is not None:
+        gate = torch.sigmoid(z.float()) if sigmoid_gate else F.silu(z.float())
+    if gate is not None and not norm_first:
+        xf = xf * gate
+    g = xf.view(rows, h // group_size, group_size)
+    g = g * torch.rsqrt(g.pow(2).mean(-1, keepdim=True) + eps)
+    w = weight.float() + 1.0 if gemma else weight.float()
+    y = g.view(rows, h) * w
+    if gate is not None and norm_first:
+        y = y * gate
+    return y.to(x.dtype)
+
+
+def rope_inv_freq(rot_dim: int, theta: float, device=None) -> torch.Tensor:
+    return 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float32, device=device) / rot_dim))
+
+
+def _norm_head(t: torch.Tensor, w: Optional[torch.Tensor], eps: float, gemma: bool) -> torch.Tensor:
+    if w is None:
+        return t
+    ww = w.float() + 1.0 if gemma else w.float()
+    return (t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * ww).to(torch.bfloat16).float()
+
+
+def _rope_ref(t: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, rot: int) -> torch.Tensor:
+    """NeoX rotary on the first `rot` dims of t [T, H, D] (fp32)."""
+    if rot == 0:
+        return t
+    ang = pos.float()[:, None] * inv_freq[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    a, b = t[..., : rot // 2], t[..., rot // 2: rot]
+    out = t.clone()
+    out[..., : rot // 2] = a * cos - b * sin
+    out[..., rot // 2: rot] = b * cos + a * sin
+    return out
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor], inv_freq: torch.Tensor,
+                  k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], hq: int, hkv: int, d: int, *,
+                  rot: Optional[int] = None, q_norm: Optional[torch.Tensor] = None,
+                  k_norm: Optional[torch.Tensor] = None, eps: float = 1e-6, gemma_norm: bool = False,
+                  kv_scale: float = 1.0, q_gate: bool = False) -> torch.Tensor:
+    """Splits a fused qkv row, applies per-head q/k RMSNorm and NeoX RoPE, writes K/V rows into the pools.
+
+    qkv [T, Hq*D(*2 with q_gate) + 2*Hkv*D] bf16; positions / slots int32 [T]; pools [slots, Hkv, D] (bf16 or
+    float8_e4m3fn scaled by 1/kv_scale). Returns q [T, Hq, D] bf16. `slots=None` skips the pool write.
+    """
+    t = qkv.shape[0]
+    rot = d if rot is None else rot
+    qw = hq * d * (2 if q_gate else 1)
+    if nv.use_native(qkv):
+        q_out = torch.empty(t, hq, d, dtype=torch.bfloat16, device=qkv.device)
+        fp8 = k_pool is not None and k_pool.dtype != torch.bfloat16
+        nv.check(nv.lib().hb_rope_kv_write(
+            qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), nv.ptr(slots), inv_freq.data_ptr(), nv.ptr(q_norm),
+            nv.ptr(k_norm), eps, int(gemma_norm), q_out.data_ptr(), nv.ptr(k_pool), nv.ptr(v_pool),
+            k_pool.stride(0) if k_pool is not None else 0, t, hq, hkv, d, rot, int(fp8), 1.0 / kv_scale, int(q_gate),
+            nv.stream()), "hb_rope_kv_write")
+        return q_out
+    x = qkv.float()
+    if q_gate:
+        q = x[:, :qw].view(t, hq, 2 * d)[..., :d]
+    else:
+        q = x[:, :qw].view(t, hq, d)
+    k = x[:, qw: qw + hkv * d].view(t, hkv, d)
+    v = x[:, qw + hkv * d:].view(t, hkv, d)
+    q = _rope_ref(_norm_head(q, q_norm, eps, gemma_norm), positions, inv_freq, rot)
+    k = _rope_ref(_norm_head(k, k_norm, eps, gemma_norm), positions, inv_freq, rot)
+    if slots is not None and k_pool is not None:
+        idx = slots.long()
+        if k_pool.dtype == torch.bfloat16:
+            k_pool[idx] = k.to(torch.bfloat16)
+            v_pool[idx] = v.to(torch.bfloat16)
+        else:
+            k_pool[idx] = (k / kv_scale).clamp(-448, 448).to(k_pool.dtype)
+            v_pool[idx] = (v / kv_scale).clamp(-448, 448).to(v_pool.dtype)
+    return q.to(torch.bfloat16)
+
+
+def act_mul(x: torch.Tensor, mode: int = ACT_SILU_SPLIT, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(gate)*up on [T, 2I] (split halves or interleaved pairs), relu(x)^2, or x * sigmoid(gate)."""
+    rows = x.shape[0]
+    inter = x.shape[1] // 2 if mode in (ACT_SILU_SPLIT, ACT_SILU_PAIRS) else x.shape[1]
+    if nv.use_native(x):
+        out = torch.empty(rows, inter, dtype=x.dtype, device=x.device)
+        nv.check(nv.lib().hb_act_mul(x.data_ptr(), nv.ptr(gate), out.data_ptr(), rows, inter, x.stride(0), mode,
+                                     nv.stream()), "hb_act_mul")
+        return out
+    xf = x.float()
+    if mode == ACT_SILU_SPLIT:
+        y = F.silu(xf[:, :inter]) * xf[:, inter:]
+    elif mode == ACT_SILU_PAIRS:
+        y = F.silu(xf[:, 0::2]) * xf[:, 1::2]
+    elif mode == ACT_RELU2:
+        y = torch.relu(xf) ** 2
+    else:
+        y = xf * torch.sigmoid(gate.float())
+    return y.to(x.dtype)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    if nv.use_native(ids, table):
+        out = torch.empty(ids.shape[0], table.shape[1], dtype=table.dtype, device=table.device)
+        nv.check(nv.lib().hb_embedding(ids.data_ptr(), table.data_ptr(), out.data_ptr(), ids.shape[0],
+                                       table.shape[1], table.shape[0], nv.stream()), "hb_embedding")
+        return out
+    return table[ids.clamp(0, table.shape[0] - 1)]
+
+
+def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    if nv.use_native(a, b):
+        out = torch.empty_like(a)
+        nv.check(nv.lib().hb_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), nv.stream()), "hb_add")
+        return out
+    return (a.float() + b.float()).to(a.dtype)

@@ -25,7 +25,9 @@ def _plan(m: int, n: int, k_tiles: int, max_ws_bytes: int) -> tuple[bool, int, i
         tiles = (n + 127) // 128
         splits = 1
         if tiles < NUM_SMS:
-            splits = max(1, min(-(-NUM_SMS // tiles), k_tiles // 4, 16))
+            # One CTA per SM streams ~1/148 of HBM bandwidth, so fill the SMs without spilling into a second,
+            # mostly empty wave; every split keeps at least two K tiles.
+            splits = max(1, min(NUM_SMS // tiles, k_tiles // 2, 16))
             while splits > 1 and splits * m * n * 4 > max_ws_bytes:
                 splits -= 1
         return True, bn, splits
