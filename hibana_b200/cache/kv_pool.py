@@ -1,0 +1,62 @@
+"""Token-granular paged KV pool.
+
+One row ("slot") per cached token and attention layer: k, v [layers][slots, kv_heads, head_dim] in bf16 or
+e4m3. Slot 0 is a dummy that padded graph rows read and write. The pool only allocates and frees; ownership
+and `committed_len` belong to the StateManager. Reference: hibana/cache/kv_pool.py:24-139 (page size 1, free
+list, pad pages, `write`).
+"""
+from __future__ import annotations
+
+from typing import Iterable
+
+import torch
+
+
+class KvPool:
+    def __init__(self, layers: int, slots: int, kv_heads: int, head_dim: int, dtype: torch.dtype = torch.bfloat16,
+                 device: torch.device | str = "cpu", kv_scale: float = 1.0):
+        self.layers, self.slots, self.kv_heads, self.head_dim = layers, slots, kv_heads, head_dim
+        self.dtype, self.device, self.kv_scale = dtype, torch.device(device), kv_scale
+        # One allocation; slot 0 is the dummy row.
+        self.storage = torch.zeros(max(layers, 1), 2, slots + 1, kv_heads, head_dim, dtype=dtype, device=device)
+        self.k = [self.storage[i, 0] for i in range(layers)]
+        self.v = [self.storage[i, 1] for i in range(layers)]
+        self._free = list(range(slots, 0, -1))     # pop() hands out ascending ids (contiguous when fresh)
+        self._owned = bytearray(slots + 1)
+
+    @property
+    def free_count(self) -> int:
+        return len(self._free)
+
+    @property
+    def bytes_per_token(self) -> int:
+        return self.layers * 2 * self.kv_heads * self.head_dim * self.storage.element_size()
+
+    def alloc(self, n: int) -> list[int]:
+        if n > len(self._free):
+            raise MemoryError(f"KV pool exhausted: need {n}, free {len(self._free)}")
+        out = [self._free.pop() for _ in range(n)]
+        for s in out:
+            self._owned[s] = 1
+        return out
+
+    def free(self, ids: Iterable[int]) -> None:
+        for s in ids:
+            if s <= 0 or s > self.slots or not self._owned[s]:
+                raise ValueError(f"double free or foreign slot {s}")
+            self._owned[s] = 0
+            self._free.append(s)
+
+    def check(self) -> None:
+        assert len(set(self._free)) == len(self._free), "duplicate free slots"
+        assert all(not self._owned[s] for s in self._free)
+        assert sum(self._owned) + len(self._free) == self.slots
+
+    def rows(self, ids: list[int]) -> torch.Tensor:
+        """All layers' K and V rows of the given slots: [layers, 2, len(ids), kv_heads, head_dim] (a copy)."""
+        idx = torch.tensor(ids, dtype=torch.long, device=self.device)
+        return self.storage[:, :, idx]
+
+    def write_rows(self, ids: list[int], rows: torch.Tensor) -> None:
+        idx = torch.tensor(ids, dtype=torch.long, device=self.device)
+        self.storage[:, :, idx] = rows.to(self.storage.dtype)

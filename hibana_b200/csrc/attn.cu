@@ -28,6 +28,7 @@ struct AttnParams {
   const int* kv_indices;       // [B, ld_idx]
   long long ld_idx;
   const int* ctx_len;          // [B] keys visible to the last query row of the sequence
+  const int* seq_rows;         // [B] row of each sequence in kv_indices (null = identity)
   const int* q_indptr;         // [B + 1] query row offsets; null = one row per sequence
   __nv_bfloat16* out;          // [T, Hq, D]
   float* part_o;               // [T, Hq, S, D]
@@ -128,7 +129,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_splitkv_kernel(const AttnPar
 #pragma unroll
     for (int j = 0; j < DPT; ++j) acc[i][j] = 0.f;
 
-  const int* idx_row = p.kv_indices + static_cast<long long>(b) * p.ld_idx;
+  const int* idx_row = p.kv_indices + static_cast<long long>(p.seq_rows ? p.seq_rows[b] : b) * p.ld_idx;
   const uint8_t* kp = static_cast<const uint8_t*>(p.k_pool);
   const uint8_t* vp = static_cast<const uint8_t*>(p.v_pool);
 
@@ -345,8 +346,8 @@ extern "C" {
 
 // max_rows: largest number of query rows of any sequence (1 for decode). Partials are needed when splits > 1.
 int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
-                  const void* kv_indices, long long ld_idx, const void* ctx_len, const void* q_indptr, void* out,
-                  void* part_o, void* part_lse, int batch, int total_rows, int max_rows, int hq, int hkv, int d,
+                  const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len, const void* q_indptr,
+                  void* out, void* part_o, void* part_lse, int batch, int total_rows, int max_rows, int hq, int hkv, int d,
                   int splits, float scale, int kv_fp8, float kv_scale, int causal, void* stream) {
   if (batch <= 0) return 0;
   if (hq % hkv != 0) return 1;
@@ -357,6 +358,7 @@ int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long lo
   p.k_pool = k_pool; p.v_pool = v_pool; p.pool_stride = pool_stride;
   p.kv_indices = static_cast<const int*>(kv_indices); p.ld_idx = ld_idx;
   p.ctx_len = static_cast<const int*>(ctx_len);
+  p.seq_rows = static_cast<const int*>(seq_rows);
   p.q_indptr = static_cast<const int*>(q_indptr);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.part_o = static_cast<float*>(part_o); p.part_lse = static_cast<float*>(part_lse);

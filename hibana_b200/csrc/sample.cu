@@ -1,0 +1,328 @@
+// Sampling and speculative verify-and-accept kernels for sm_100a.
+//
+//  * argmax over bf16 / fp32 logits rows (greedy), optional grammar bitmask.
+//  * temperature / top-k / top-p sampling, one CTA per row, counter-based RNG keyed by (seed, offset) so a
+//    request's draws do not depend on batch composition.
+//  * exact greedy acceptance of a drafted block (longest matching prefix + the target's own token), with stop
+//    ids and a token budget, producing device-resident counts.
+//  * rank / logit gap of a drafted token in its verify row (relaxed acceptance).
+//
+// Reference counterparts: hibana/engine/sampler.py:87-123, hibana/engine/accept.py:18-56,
+// hibana/kernels/relaxed_rank.py:13, hibana/kernels/sampled_verify.py:17, hibana/engine/accept_graphs.py.
+#include "hb_api.h"
+#include "hb_common.cuh"
+
+namespace hb {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p, long long i);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p, long long i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, long long i) {
+  return __bfloat162float(p[i]);
+}
+
+__device__ __forceinline__ bool mask_ok(const int* mask, int i) {
+  return mask == nullptr || ((mask[i >> 5] >> (i & 31)) & 1);
+}
+
+// Lowest index wins ties (same as torch.argmax on CPU for exact ties).
+template <typename T>
+__global__ void __launch_bounds__(256)
+argmax_kernel(const T* __restrict__ logits, long long ld, int vocab, const int* __restrict__ bitmask, int mask_words,
+              long long* __restrict__ out, float* __restrict__ out_val) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int row = blockIdx.x;
+  const T* lr = logits + row * ld;
+  const int* mask = bitmask ? bitmask + static_cast<long long>(row) * mask_words : nullptr;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    if (!mask_ok(mask, i)) continue;
+    const float v = ldf<T>(lr, i);
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sv[threadIdx.x >> 5] = best;
+    si[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) {
+        best = sv[w];
+        bi = si[w];
+      }
+    out[row] = bi == 0x7fffffff ? 0 : bi;
+    if (out_val) out_val[row] = best;
+  }
+}
+
+// splitmix64-based counter RNG -> uniform in [0, 1).
+__device__ __forceinline__ float uniform01(unsigned long long seed, unsigned long long offset) {
+  unsigned long long z = seed + 0x9E3779B97F4A7C15ull * (offset + 1);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  return static_cast<float>(z >> 40) * (1.0f / 16777216.0f);
+}
+
+constexpr int SAMPLE_K = 64;  // candidates kept per row (top-k <= 64; top-p is applied inside the candidates)
+
+// One CTA per row. Keeps the SAMPLE_K largest logits by repeated threshold passes (vocab is read a few times from
+// L2), then softmax / top-p / inverse-CDF draw on the candidates. temperature <= 0 means greedy.
+template <typename T>
+__global__ void __launch_bounds__(256)
+sample_kernel(const T* __restrict__ logits, long long ld, int vocab, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ offsets,
+              const int* __restrict__ bitmask, int mask_words, long long* __restrict__ out,
+              float* __restrict__ out_prob) {
+  __shared__ float cv[SAMPLE_K];
+  __shared__ int ci[SAMPLE_K];
+  __shared__ float wv[8];
+  __shared__ int wi[8];
+  __shared__ float s_prev_v;
+  __shared__ int s_prev_i;
+  const int row = blockIdx.x;
+  const T* lr = logits + row * ld;
+  const int* mask = bitmask ? bitmask + static_cast<long long>(row) * mask_words : nullptr;
+  const float temp = temperature ? temperature[row] : 0.f;
+  int k = top_k ? top_k[row] : SAMPLE_K;
+  if (k <= 0 || k > SAMPLE_K) k = SAMPLE_K;
+  if (temp <= 0.f) k = 1;
+  if (threadIdx.x == 0) {
+    s_prev_v = INFINITY;
+    s_prev_i = -1;
+  }
+  __syncthreads();
+  // Selection by successive maxima in (value desc, index asc) order: exact and deterministic.
+  for (int c = 0; c < k; ++c) {
+    const float pv = s_prev_v;
+    const int pi = s_prev_i;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      if (!mask_ok(mask, i)) continue;
+      const float v = ldf<T>(lr, i);
+      const bool after_prev = v < pv || (v == pv && i > pi);
+      if (after_prev && (v > best || (v == best && i < bi))) {
+        best = v;
+        bi = i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if ((threadIdx.x & 31) == 0) {
+      wv[threadIdx.x >> 5] = best;
+      wi[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < 8; ++w)
+        if (wv[w] > best || (wv[w] == best && wi[w] < bi)) {
+          best = wv[w];
+          bi = wi[w];
+        }
+      cv[c] = best;
+      ci[c] = bi == 0x7fffffff ? 0 : bi;
+      s_prev_v = best;
+      s_prev_i = bi;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    if (k == 1) {
+      out[row] = ci[0];
+      if (out_prob) out_prob[row] = 1.f;
+      return;
+    }
+    const float inv_t = 1.f / temp;
+    const float m = cv[0];
+    float sum = 0.f;
+    for (int c = 0; c < k; ++c) {
+      cv[c] = (cv[c] == -INFINITY) ? 0.f : __expf((cv[c] - m) * inv_t);
+      sum += cv[c];
+    }
+    const float p_lim = top_p ? top_p[row] : 1.f;
+    int keep = k;
+    if (p_lim < 1.f) {
+      float acc = 0.f;
+      for (int c = 0; c < k; ++c) {
+        acc += cv[c] / sum;
+        if (acc >= p_lim) {
+          keep = c + 1;
+          break;
+        }
+      }
+    }
+    float ksum = 0.f;
+    for (int c = 0; c < keep; ++c) ksum += cv[c];
+    const float u = uniform01(seeds ? seeds[row] : 0ull, offsets ? offsets[row] : 0ull) * ksum;
+    float acc = 0.f;
+    int pick = keep - 1;
+    for (int c = 0; c < keep; ++c) {
+      acc += cv[c];
+      if (u < acc) {
+        pick = c;
+        break;
+      }
+    }
+    out[row] = ci[pick];
+    if (out_prob) out_prob[row] = cv[pick] / ksum;
+  }
+}
+
+// Exact greedy acceptance. Row layout: request b owns rows [b*(k+1), (b+1)*(k+1)); row j holds the target's
+// argmax after consuming [pending, draft_1..draft_j]. Accept drafts while draft[j] == target[j-1]; emit the
+// accepted drafts plus the target token of the first mismatch (or the bonus token). Emission stops at a stop id
+// (inclusive) or when `budget[b]` tokens are out. Writes emitted[b, 0..count) and count[b].
+__global__ void accept_greedy_kernel(const long long* __restrict__ target, const long long* __restrict__ drafts,
+                                     const long long* __restrict__ stop_ids, int n_stop,
+                                     const int* __restrict__ budget, const int* __restrict__ depth, int k_max, int batch,
+                                     long long* __restrict__ emitted, int* __restrict__ count,
+                                     int* __restrict__ accepted) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  const int k = depth ? min(depth[b], k_max) : k_max;
+  const long long* t = target + static_cast<long long>(b) * (k_max + 1);
+  const long long* d = drafts + static_cast<long long>(b) * k_max;
+  long long* e = emitted + static_cast<long long>(b) * (k_max + 1);
+  const int lim = budget ? budget[b] : k + 1;
+  int n = 0, acc = 0;
+  bool stopped = false;
+  for (int j = 0; j <= k && n < lim && !stopped; ++j) {
+    const long long tok = t[j];
+    e[n++] = tok;
+    for (int s = 0; s < n_stop; ++s)
+      if (stop_ids[static_cast<long long>(b) * n_stop + s] == tok) stopped = true;
+    if (j < k && d[j] == tok) ++acc;
+    else break;
+  }
+  count[b] = n;
+  if (accepted) accepted[b] = acc;
+}
+
+// Rank (number of strictly larger logits) and gap to the row maximum of token ids[row].
+template <typename T>
+__global__ void __launch_bounds__(256)
+rank_gap_kernel(const T* __restrict__ logits, long long ld, int vocab, const long long* __restrict__ ids,
+                int* __restrict__ rank, float* __restrict__ gap) {
+  __shared__ float smax[8];
+  __shared__ int scnt[8];
+  const int row = blockIdx.x;
+  const T* lr = logits + row * ld;
+  const float mine = ldf<T>(lr, ids[row]);
+  float mx = -INFINITY;
+  int cnt = 0;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = ldf<T>(lr, i);
+    mx = fmaxf(mx, v);
+    cnt += v > mine;
+  }
+  mx = warp_max(mx);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  if ((threadIdx.x & 31) == 0) {
+    smax[threadIdx.x >> 5] = mx;
+    scnt[threadIdx.x >> 5] = cnt;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) {
+      mx = fmaxf(mx, smax[w]);
+      cnt += scnt[w];
+    }
+    rank[row] = cnt;
+    gap[row] = mx - mine;
+  }
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" {
+
+int hb_argmax(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* bitmask, int mask_words,
+              void* out, void* out_val, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_f32)
+    argmax_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float*>(logits), ld, vocab,
+                                               static_cast<const int*>(bitmask), mask_words,
+                                               static_cast<long long*>(out), static_cast<float*>(out_val));
+  else
+    argmax_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), ld, vocab,
+                                                       static_cast<const int*>(bitmask), mask_words,
+                                                       static_cast<long long*>(out), static_cast<float*>(out_val));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_sample(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* temperature,
+              const void* top_k, const void* top_p, const void* seeds, const void* offsets, const void* bitmask,
+              int mask_words, void* out, void* out_prob, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define HB_SAMPLE_ARGS                                                                                     \
+  ld, vocab, static_cast<const float*>(temperature), static_cast<const int*>(top_k),                       \
+      static_cast<const float*>(top_p), static_cast<const unsigned long long*>(seeds),                     \
+      static_cast<const unsigned long long*>(offsets), static_cast<const int*>(bitmask), mask_words,       \
+      static_cast<long long*>(out), static_cast<float*>(out_prob)
+  if (is_f32) sample_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float*>(logits), HB_SAMPLE_ARGS);
+  else sample_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), HB_SAMPLE_ARGS);
+#undef HB_SAMPLE_ARGS
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_accept_greedy(const void* target, const void* drafts, const void* stop_ids, int n_stop, const void* budget,
+                     const void* depth, int k_max, int batch, void* emitted, void* count, void* accepted,
+                     void* stream) {
+  if (batch <= 0) return 0;
+  accept_greedy_kernel<<<(batch + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const long long*>(target), static_cast<const long long*>(drafts),
+      static_cast<const long long*>(stop_ids), n_stop, static_cast<const int*>(budget),
+      static_cast<const int*>(depth), k_max, batch, static_cast<long long*>(emitted), static_cast<int*>(count),
+      static_cast<int*>(accepted));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_rank_gap(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* ids, void* rank,
+                void* gap, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_f32)
+    rank_gap_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float*>(logits), ld, vocab,
+                                                 static_cast<const long long*>(ids), static_cast<int*>(rank),
+                                                 static_cast<float*>(gap));
+  else
+    rank_gap_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), ld, vocab,
+                                                         static_cast<const long long*>(ids),
+                                                         static_cast<int*>(rank), static_cast<float*>(gap));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+}  // extern "C"

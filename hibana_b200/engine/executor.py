@@ -1,0 +1,198 @@
+"""Executor: turns scheduler decisions (admit / prefill chunk / decode step / release) into model forwards.
+
+Owns the model, the KV and recurrent-state pools, the StateManager (resource ownership + radix prefix cache) and
+the ModelRunner (device block table, graphs). All methods run on the single engine thread.
+Reference: hibana/engine/executor.py:51-884 (`admit`, `prefill_batch`, `decode_step`, `release`,
+`capture_graphs`, `warmup`, `generate_batch`).
+"""
+from __future__ import annotations
+
+import time
+from typing import Optional, Sequence
+
+import torch
+
+from .. import config as cfgmod
+from ..cache.kv_pool import KvPool
+from ..target import Target
+from .context import PREFILL
+from .request import Request, SamplingParams, State
+from .runner import ModelRunner
+
+
+def _sampling_rows(reqs: Sequence[Request]) -> Optional[dict]:
+    if all(r.params.greedy for r in reqs):
+        return None
+    return {
+        "temp": [0.0 if r.params.greedy else r.params.temperature for r in reqs],
+        "top_k": [r.params.top_k for r in reqs],
+        "top_p": [r.params.top_p for r in reqs],
+        "seed": [r.seed & 0x7FFFFFFFFFFFFFFF for r in reqs],
+        "offs": [r.draws for r in reqs],
+    }
+
+
+class Executor:
+    def __init__(self, model, *, max_batch: int = 64, max_ctx: int = 4096, kv_slots: int = 0,
+                 use_graphs: bool = True, buckets: Optional[Sequence[int]] = None, state_manager=None,
+                 comm=None, kv_dtype: Optional[torch.dtype] = None, attn_splits: int = 0):
+        t: Target = model.target
+        self.model, self.target = model, t
+        self.device = model.device
+        self.max_batch, self.max_ctx = max_batch, max_ctx
+        if kv_slots <= 0:
+            kv_slots = max_batch * max_ctx
+        dtype = kv_dtype or (torch.float8_e4m3fn if t.kv_dtype == "fp8" else torch.bfloat16)
+        self.kv = KvPool(t.attn_layers, kv_slots, t.kv_heads, t.head_dim, dtype, self.device) if t.attn_layers \
+            else KvPool(0, kv_slots, 1, 1, dtype, self.device)
+        buckets = buckets or tuple(b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_batch)
+        self.runner = ModelRunner(model, self.kv, max_batch=max_batch, max_ctx=max_ctx, buckets=buckets,
+                                  use_graphs=use_graphs, comm=comm, attn_splits=attn_splits)
+        self.state = state_manager
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "prefill_chunks": 0,
+                      "cached_tokens": 0}
+
+    # ---- lifecycle
+    def validate_request(self, req: Request) -> None:
+        if not req.prompt_ids:
+            raise ValueError("empty prompt")
+        if req.total_len + req.params.max_tokens > self.max_ctx:
+            raise ValueError(f"prompt + max_tokens exceeds the context limit {self.max_ctx}")
+        if any(i < 0 or i >= self.target.vocab for i in req.prompt_ids):
+            raise ValueError("token id out of range")
+
+    def can_admit(self, req: Request) -> bool:
+        if self.state is not None:
+            return self.state.can_admit(req)
+        need = len(req.prompt_ids) + min(req.params.max_tokens, 64)
+        return self.kv.free_count >= need and bool(self.runner._free_rows)
+
+    def admit(self, req: Request) -> None:
+        """Takes a block-table row (and, with a cache, the matched prefix) for the request."""
+        req.table_row = self.runner.alloc_row()
+        if self.state is not None:
+            try:
+                self.state.admit(req)
+            except Exception:
+                self.runner.free_row(req.table_row)
+                req.table_row = -1
+                raise
+            if req.cached_len:
+                self.runner.set_table(req.table_row, 0, req.kv_slots[:req.cached_len])
+                self.stats["cached_tokens"] += req.cached_len
+        req.prefilled = req.cached_len
+        req.state = State.PREFILL
+
+    def release(self, req: Request) -> None:
+        if req.table_row < 0:
+            return
+        if self.state is not None:
+            self.state.release(req)
+        else:
+            self.kv.free(req.kv_slots)
+            req.kv_slots = []
+        self.runner.free_row(req.table_row)
+        req.table_row = -1
+
+    def retract(self, req: Request) -> None:
+        """Drops physical resources; the emitted history stays and is replayed on re-admission."""
+        if self.state is not None:
+            self.state.retract(req)
+        else:
+            self.kv.free(req.kv_slots)
+            req.kv_slots = []
+        self.runner.free_row(req.table_row)
+        req.table_row, req.prefilled, req.committed_len, req.cached_len = -1, 0, 0, 0
+        req.state = State.WAITING
+
+    # ---- steps
+    def _alloc(self, req: Request, n: int) -> list[int]:
+        if self.state is not None:
+            return self.state.extend(req, n)
+        slots = self.kv.alloc(n)
+        req.kv_slots.extend(slots)
+        return slots
+
+    def prefill_batch(self, chunks: Sequence[tuple[Request, int]]) -> None:
+        """Runs `count` more prompt (or replayed) tokens of each request; samples when a prompt completes."""
+        rows, toks, starts, slot_lists, finals = [], [], [], [], []
+        for req, count in chunks:
+            seq = req.all_ids if req.output_ids else req.prompt_ids
+            # After a retraction the emitted history is replayed; the last emitted token stays pending.
+            target_len = len(seq) - (1 if req.output_ids else 0)
+            count = min(count, target_len - req.prefilled)
+            tokens = seq[req.prefilled:req.prefilled + count]
+            slots = self._alloc(req, count)
+            rows.append(req.table_row)
+            toks.append(tokens)
+            starts.append(req.prefilled)
+            slot_lists.append(slots)
+            finals.append(req.prefilled + count >= target_len)
+        any_final = any(finals)
+        out = self.runner.forward_rows(rows, toks, starts, slot_lists, mode=PREFILL,
+                                       want="last" if any_final else "none",
+                                       sampling_rows=_sampling_rows([r for r, _ in chunks]) if any_final else None)
+        for i, (req, _) in enumerate(chunks):
+            n = len(toks[i])
+            req.prefilled += n
+            req.committed_len = req.prefilled
+            self.stats["prefill_tokens"] += n
+            if self.state is not None:
+                self.state.after_prefill(req, final=finals[i])
+            if finals[i]:
+                req.state = State.RUNNING
+                if not req.output_ids:      # a replayed request already holds its pending token
+                    req.draws += 1
+                    req.push(out[i])
+        self.stats["prefill_chunks"] += 1
+
+    def decode_step(self, reqs: Sequence[Request]) -> None:
+        """One token for every running request (the pending token goes in, the next one comes out)."""
+        slots = [self._alloc(r, 1)[0] for r in reqs]
+        rows = [r.table_row for r in reqs]
+        tokens = [r.output_ids[-1] for r in reqs]
+        positions = [r.total_len - 1 for r in reqs]
+        out = self.runner.decode(rows, tokens, positions, slots, _sampling_rows(reqs))
+        for r, tok in zip(reqs, out):
+            r.committed_len = r.total_len
+            r.draws += 1
+            r.push(tok)
+        self.stats["decode_steps"] += 1
+        self.stats["decode_tokens"] += len(reqs)
+
+    def capture_graphs(self) -> None:
+        self.runner.capture()
+
+    # ---- offline batch API
+    def generate_batch(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams],
+                       prefill_budget: int = 4096) -> list[Request]:
+        """Runs prompts to completion with a simple loop (admit all, chunked prefill, lock-step decode)."""
+        plist = params if isinstance(params, (list, tuple)) else [params] * len(prompts)
+        reqs = [Request(prompt_ids=list(p), params=sp) for p, sp in zip(prompts, plist)]
+        for r in reqs:
+            self.validate_request(r)
+        pending = list(reqs)
+        active: list[Request] = []
+        while pending or active:
+            while pending and len(active) < self.max_batch and self.can_admit(pending[0]):
+                r = pending.pop(0)
+                self.admit(r)
+                active.append(r)
+            pre = [r for r in active if r.state == State.PREFILL]
+            if pre:
+                budget, chunks = prefill_budget, []
+                for r in pre:
+                    if budget <= 0:
+                        break
+                    c = min(len(r.prompt_ids) - r.prefilled, budget)
+                    chunks.append((r, c))
+                    budget -= c
+                self.prefill_batch(chunks)
+            else:
+                run = [r for r in active if r.state == State.RUNNING]
+                if run:
+                    self.decode_step(run)
+            for r in [r for r in active if r.done]:
+                self.release(r)
+                active.remove(r)
+        return reqs

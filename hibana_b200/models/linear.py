@@ -1,0 +1,110 @@
+"""Linear layers over the quantised weight formats (bf16, NVFP4; w3 and FP8 plug in through the same interface).
+
+A `Linear` owns one weight matrix [N, K] in its storage format plus the static activation scale NVFP4 needs.
+`norm_linear` runs (residual add +) RMSNorm and the following projection with the norm fused into the
+activation quantiser when the projection is NVFP4. The reference's equivalents are Fp8Linear / Nvfp4Linear
+(hibana/weights/modelopt.py:108-184) called through hibana/kernels/ops.py:56-128.
+"""
+from __future__ import annotations
+
+from typing import Optional, Union
+
+import torch
+
+from ..ops import basic, gemm, nvfp4
+from ..ops.nvfp4 import Nvfp4Tensor
+
+Activation = Union[torch.Tensor, Nvfp4Tensor]
+
+
+def interleave_pairs(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[I, K] gate and up -> [2I, K] with rows g0, u0, g1, u1, ... (what the SiLU-mul GEMM epilogue expects)."""
+    return torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], gate.shape[1]).contiguous()
+
+
+class Linear:
+    """y = x @ W.T. `fmt` is 'bf16' or 'nvfp4'. `input_amax` is the calibrated activation range (NVFP4 only)."""
+
+    def __init__(self, weight: torch.Tensor, fmt: str = "bf16", input_amax: float = 8.0, name: str = ""):
+        self.fmt = fmt
+        self.name = name
+        self.out_features, self.in_features = weight.shape
+        self.calibrating = False
+        self.seen_amax = 0.0
+        if fmt == "bf16":
+            self.weight = weight.to(torch.bfloat16).contiguous()
+            self.wq = None
+        elif fmt == "nvfp4":
+            self.wq = nvfp4.quantize_weight(weight)
+            self.weight = None
+            self.set_input_amax(input_amax)
+        else:
+            raise ValueError(f"unknown linear format {fmt!r}")
+
+    @classmethod
+    def from_nvfp4(cls, wq: Nvfp4Tensor, input_scale: torch.Tensor, name: str = "") -> "Linear":
+        """Wraps tensors loaded from a checkpoint (packed values, swizzled scales, weight_scale_2, input_scale)."""
+        self = cls.__new__(cls)
+        self.fmt, self.name, self.wq, self.weight = "nvfp4", name, wq, None
+        self.out_features, self.in_features = wq.rows, wq.k
+        self.calibrating, self.seen_amax = False, 0.0
+        self.input_scale = input_scale.reshape(1).float()
+        self.alpha = (self.input_scale * wq.gscale).reshape(1)
+        return self
+
+    def set_input_amax(self, amax: float) -> None:
+        dev = self.wq.q.device
+        self.input_scale = torch.tensor([max(amax, 1e-6) / (6.0 * 448.0)], dtype=torch.float32, device=dev)
+        self.alpha = (self.input_scale * self.wq.gscale).reshape(1)
+
+    def to(self, device) -> "Linear":
+        if self.weight is not None:
+            self.weight = self.weight.to(device)
+        if self.wq is not None:
+            w = self.wq
+            self.wq = Nvfp4Tensor(w.q.to(device), w.sf.to(device), w.gscale.to(device), w.rows, w.k)
+            self.input_scale = self.input_scale.to(device)
+            self.alpha = self.alpha.to(device)
+        return self
+
+    def nbytes(self) -> int:
+        if self.weight is not None:
+            return self.weight.numel() * 2
+        return self.wq.q.numel() + self.wq.sf.numel()
+
+    def dequantized(self) -> torch.Tensor:
+        return self.weight.float() if self.weight is not None else self.wq.dequantize()
+
+    def quantize_input(self, x: torch.Tensor, mode: int = nvfp4.MODE_PLAIN) -> Activation:
+        if self.fmt != "nvfp4":
+            if mode != nvfp4.MODE_PLAIN:
+                return basic.act_mul(x, basic.ACT_SILU_SPLIT if mode == nvfp4.MODE_SILU_SPLIT
+                                     else basic.ACT_SILU_PAIRS)
+            return x
+        if self.calibrating:
+            y = x if mode == nvfp4.MODE_PLAIN else nvfp4._silu_mul(x, mode)
+            self.seen_amax = max(self.seen_amax, float(y.float().abs().max()))
+        return nvfp4.quantize(x, self.input_scale, mode)
+
+    def __call__(self, x: Activation, *, epilogue: int = gemm.EPI_STORE, residual: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.fmt == "bf16":
+            return gemm.linear_bf16(x, self.weight, epilogue=epilogue, residual=residual, out=out)
+        xq = x if isinstance(x, Nvfp4Tensor) else self.quantize_input(x)
+        return gemm.linear_nvfp4(xq, self.wq, self.alpha, epilogue=epilogue, residual=residual, out=out)
+
+
+def norm_linear(x: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
+                lin: Linear, *, gemma: bool = False, epilogue: int = gemm.EPI_STORE,
+                add_residual: bool = True) -> torch.Tensor:
+    """lin(rmsnorm(x + residual)); `residual` is updated in place with the sum when add_residual."""
+    res = residual if add_residual else None
+    if lin.fmt == "nvfp4":
+        if lin.calibrating:
+            y = basic.rmsnorm(x, norm_weight, eps, residual=res, gemma=gemma)
+            lin.seen_amax = max(lin.seen_amax, float(y.float().abs().max()))
+            return lin(nvfp4.quantize(y, lin.input_scale), epilogue=epilogue)
+        xq, _ = nvfp4.rmsnorm_quantize(x, norm_weight, eps, lin.input_scale, residual=res, gemma=gemma)
+        return lin(xq, epilogue=epilogue)
+    y = basic.rmsnorm(x, norm_weight, eps, residual=res, gemma=gemma)
+    return lin(y, epilogue=epilogue)

@@ -1,0 +1,99 @@
+"""Paged GQA attention over the token-granular KV pool (decode, speculative verify, chunked prefill).
+
+`paged_attention` is the single entry: query rows of a ragged batch attend to their sequence's context through
+the block table. Kernel: csrc/attn.cu (split-KV, LSE merge). The plain-PyTorch reference below is the CPU path
+and the GPU tests' oracle. Reference counterparts: hibana/kernels/ops.py:131-161 (ragged prefill),
+hibana/model/attention.py:69-126, hibana/kernels/csrc/verify_attn.cu.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import _native as nv
+
+P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
+nv.register("hb_attn_paged", [P, P, P, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, Fl, I, Fl, I, P])
+
+NUM_SMS = 148
+
+
+def choose_splits(batch: int, hkv: int, max_ctx: int, row_chunks: int = 1) -> int:
+    """KV splits so the grid covers the SMs about twice; a split never gets fewer than 256 keys."""
+    ctas = max(1, batch * hkv * row_chunks)
+    want = max(1, (2 * NUM_SMS + ctas - 1) // ctas)
+    return int(max(1, min(want, max(1, max_ctx // 256), 64)))
+
+
+class AttnWorkspace:
+    """Split-KV partial buffers, allocated once (stable addresses for CUDA graphs)."""
+
+    def __init__(self, rows: int, hq: int, d: int, splits: int, device: torch.device):
+        self.rows, self.splits = rows, splits
+        self.part_o = torch.empty(rows, hq, splits, d, dtype=torch.float32, device=device)
+        self.part_lse = torch.empty(rows, hq, splits, dtype=torch.float32, device=device)
+
+
+def paged_attention_ref(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, kv_indices: torch.Tensor,
+                        ctx_len: torch.Tensor, q_indptr: Optional[torch.Tensor], scale: float, kv_scale: float = 1.0,
+                        causal: bool = True) -> torch.Tensor:
+    t, hq, d = q.shape
+    hkv = k_pool.shape[1]
+    g = hq // hkv
+    out = torch.zeros(t, hq, d, dtype=torch.float32, device=q.device)
+    b = ctx_len.shape[0]
+    for i in range(b):
+        r0 = int(q_indptr[i]) if q_indptr is not None else i
+        r1 = int(q_indptr[i + 1]) if q_indptr is not None else i + 1
+        rows = r1 - r0
+        ctx = int(ctx_len[i])
+        if rows == 0 or ctx == 0:
+            continue
+        idx = kv_indices[i, :ctx].long()
+        k = k_pool[idx].float() * kv_scale     # [ctx, hkv, d]
+        v = v_pool[idx].float() * kv_scale
+        qq = q[r0:r1].float().view(rows, hkv, g, d)
+        s = torch.einsum("rhgd,chd->rhgc", qq, k) * scale
+        if causal:
+            pos = torch.arange(ctx, device=q.device)[None, :]
+            lim = (ctx - rows + torch.arange(rows, device=q.device))[:, None]
+            s = s.masked_fill((pos > lim)[:, None, None, :], float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        out[r0:r1] = torch.einsum("rhgc,chd->rhgd", p, v).reshape(rows, hq, d)
+    return out.to(q.dtype)
+
+
+def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, kv_indices: torch.Tensor,
+                    ctx_len: torch.Tensor, *, q_indptr: Optional[torch.Tensor] = None, max_rows: int = 1,
+                    seq_rows: Optional[torch.Tensor] = None,
+                    scale: Optional[float] = None, kv_scale: float = 1.0, causal: bool = True, splits: int = 1,
+                    workspace: Optional[AttnWorkspace] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [T, Hq, D] bf16; pools [slots, Hkv, D]; kv_indices [B, max_ctx] int32; ctx_len [B] int32.
+
+    Row r of sequence b (rows q_indptr[b]..q_indptr[b+1], or exactly one row when q_indptr is None) sees keys
+    [0, ctx_len[b] - rows_b + r + 1) when causal. `max_rows` bounds rows per sequence (host value).
+    `seq_rows` int32 [B] selects each sequence's row of kv_indices (identity when None).
+    """
+    t, hq, d = q.shape
+    hkv = k_pool.shape[1]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    if not nv.use_native(q, k_pool):
+        idx = kv_indices if seq_rows is None else kv_indices[seq_rows.long()]
+        res = paged_attention_ref(q, k_pool, v_pool, idx, ctx_len, q_indptr, scale, kv_scale, causal)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    b = ctx_len.shape[0]
+    out = torch.empty_like(q) if out is None else out
+    if splits > 1 and (workspace is None or workspace.rows < t or workspace.splits != splits):
+        workspace = AttnWorkspace(t, hq, d, splits, q.device)
+    fp8 = k_pool.dtype != torch.bfloat16
+    nv.check(nv.lib().hb_attn_paged(
+        q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), kv_indices.data_ptr(),
+        kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), nv.ptr(q_indptr), out.data_ptr(),
+        workspace.part_o.data_ptr() if splits > 1 else None, workspace.part_lse.data_ptr() if splits > 1 else None,
+        b, t, max_rows, hq, hkv, d, splits, scale, int(fp8), kv_scale, int(causal), nv.stream()), "hb_attn_paged")
+    return out

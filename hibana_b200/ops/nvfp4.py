@@ -114,9 +114,14 @@ class Nvfp4Tensor:
 
 def quantize_weight(w: torch.Tensor, global_scale: Optional[float] = None) -> Nvfp4Tensor:
     """Quantises a weight matrix [N, K] (any float dtype) the way ModelOpt does: global = amax / (6 * 448)."""
-    wf = w.float()
     if global_scale is None:
-        global_scale = max(float(wf.abs().max()) / (6.0 * 448.0), 1e-12)
+        global_scale = max(float(w.abs().max()) / (6.0 * 448.0), 1e-12)
+    if w.is_cuda and nv.available():
+        # Large matrices: the device quantiser (same arithmetic on the bf16-rounded weights).
+        gs = torch.tensor(global_scale, dtype=torch.float32, device=w.device)
+        t = quantize(w.to(torch.bfloat16).contiguous(), gs)
+        return Nvfp4Tensor(t.q, t.sf, gs, w.shape[0], w.shape[1])
+    wf = w.float()
     packed, sfb = quantize_ref(wf, global_scale)
     return Nvfp4Tensor(packed, swizzle_sf(sfb), torch.tensor(global_scale, dtype=torch.float32, device=w.device),
                        w.shape[0], w.shape[1])
@@ -131,7 +136,9 @@ MODE_PLAIN, MODE_SILU_SPLIT, MODE_SILU_PAIRS = 0, 1, 2
 def _alloc(m: int, k: int, device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
     ka = k_atoms(k)
     q = torch.empty(m, k // 2, dtype=torch.uint8, device=device)
-    sf = torch.empty((m + 127) // 128, ka, 512, dtype=torch.uint8, device=device)
+    rb = (m + 127) // 128
+    rb += rb & 1 if rb > 1 else 0
+    sf = torch.empty(rb, ka, 512, dtype=torch.uint8, device=device)
     return q, sf
 
 

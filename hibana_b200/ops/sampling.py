@@ -1,0 +1,163 @@
+"""Sampling and speculative-acceptance ops (csrc/sample.cu) with plain-PyTorch references.
+
+Reference counterparts: hibana/engine/sampler.py:87-123, hibana/engine/accept.py:18-56,
+hibana/kernels/relaxed_rank.py:13.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _native as nv
+
+P, I, L = nv.P, nv.I, nv.L
+nv.register("hb_argmax", [P, L, I, I, I, P, I, P, P, P])
+nv.register("hb_sample", [P, L, I, I, I, P, P, P, P, P, P, I, P, P, P])
+nv.register("hb_accept_greedy", [P, P, P, I, P, P, I, I, P, P, P, P])
+nv.register("hb_rank_gap", [P, L, I, I, I, P, P, P, P])
+
+MASK64 = (1 << 64) - 1
+
+
+def _apply_bitmask(logits: torch.Tensor, bitmask: Optional[torch.Tensor]) -> torch.Tensor:
+    if bitmask is None:
+        return logits.float()
+    vocab = logits.shape[1]
+    idx = torch.arange(vocab, device=logits.device)
+    allowed = ((bitmask[:, (idx >> 5).long()] >> (idx & 31)) & 1).bool()
+    return logits.float().masked_fill(~allowed, float("-inf"))
+
+
+def argmax(logits: torch.Tensor, bitmask: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Greedy token per row (int64). `bitmask` int32 [rows, ceil(vocab/32)] allows token i when bit i is set."""
+    rows, vocab = logits.shape
+    if nv.use_native(logits):
+        out = torch.empty(rows, dtype=torch.int64, device=logits.device) if out is None else out
+        nv.check(nv.lib().hb_argmax(logits.data_ptr(), logits.stride(0), rows, vocab,
+                                    int(logits.dtype == torch.float32), nv.ptr(bitmask),
+                                    bitmask.shape[1] if bitmask is not None else 0, out.data_ptr(), None,
+                                    nv.stream()), "hb_argmax")
+        return out
+    res = _apply_bitmask(logits, bitmask).argmax(dim=-1)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def uniform01(seed: int, offset: int) -> float:
+    """Host copy of the device counter RNG (splitmix64 finaliser) so tests can predict draws."""
+    z = (seed + 0x9E3779B97F4A7C15 * (offset + 1)) & MASK64
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & MASK64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & MASK64
+    z ^= z >> 31
+    return (z >> 40) / 16777216.0
+
+
+def sample_ref(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+               seeds: torch.Tensor, offsets: torch.Tensor, bitmask: Optional[torch.Tensor] = None,
+               max_k: int = 64) -> torch.Tensor:
+    lg = _apply_bitmask(logits, bitmask)
+    rows = lg.shape[0]
+    out = torch.zeros(rows, dtype=torch.int64)
+    for r in range(rows):
+        t = float(temperature[r])
+        if t <= 0:
+            out[r] = int(lg[r].argmax())
+            continue
+        k = int(top_k[r])
+        k = max_k if k <= 0 or k > max_k else k
+        vals, idx = torch.sort(lg[r].cpu(), descending=True, stable=True)
+        vals, idx = vals[:k], idx[:k]
+        w = torch.exp((vals - vals[0]) / t)
+        w[vals == float("-inf")] = 0
+        cum = torch.cumsum(w / w.sum(), 0)
+        p = float(top_p[r])
+        keep = k
+        if p < 1.0:
+            over = (cum >= p).nonzero()
+            keep = int(over[0]) + 1 if len(over) else k
+        w = w[:keep]
+        u = uniform01(int(seeds[r]), int(offsets[r])) * float(w.sum())
+        acc = torch.cumsum(w, 0)
+        pick = int((u < acc).nonzero()[0]) if bool((u < acc).any()) else keep - 1
+        out[r] = int(idx[pick])
+    return out.to(logits.device)
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           seeds: torch.Tensor, offsets: torch.Tensor, bitmask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Temperature / top-k (<= 64) / top-p sampling; temperature <= 0 is greedy. seeds/offsets are uint64-as-int64."""
+    rows, vocab = logits.shape
+    if nv.use_native(logits):
+        out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+        nv.check(nv.lib().hb_sample(logits.data_ptr(), logits.stride(0), rows, vocab,
+                                    int(logits.dtype == torch.float32), temperature.data_ptr(), top_k.data_ptr(),
+                                    top_p.data_ptr(), seeds.data_ptr(), offsets.data_ptr(), nv.ptr(bitmask),
+                                    bitmask.shape[1] if bitmask is not None else 0, out.data_ptr(), None,
+                                    nv.stream()), "hb_sample")
+        return out
+    return sample_ref(logits, temperature, top_k, top_p, seeds, offsets, bitmask)
+
+
+def accept_greedy_ref(target: torch.Tensor, drafts: torch.Tensor, stop_ids: Optional[torch.Tensor],
+                      budget: Optional[torch.Tensor], depth: Optional[torch.Tensor]):
+    b, k1 = target.shape
+    kmax = k1 - 1
+    emitted = torch.zeros(b, k1, dtype=torch.int64)
+    count = torch.zeros(b, dtype=torch.int32)
+    accepted = torch.zeros(b, dtype=torch.int32)
+    for i in range(b):
+        k = min(int(depth[i]), kmax) if depth is not None else kmax
+        lim = int(budget[i]) if budget is not None else k + 1
+        n = acc = 0
+        for j in range(k + 1):
+            if n >= lim:
+                break
+            tok = int(target[i, j])
+            emitted[i, n] = tok
+            n += 1
+            if stop_ids is not None and tok in stop_ids[i].tolist():
+                if j < k and int(drafts[i, j]) == tok:
+                    acc += 1
+                break
+            if j < k and int(drafts[i, j]) == tok:
+                acc += 1
+            else:
+                break
+        count[i], accepted[i] = n, acc
+    return emitted, count, accepted
+
+
+def accept_greedy(target: torch.Tensor, drafts: torch.Tensor, stop_ids: Optional[torch.Tensor] = None,
+                  budget: Optional[torch.Tensor] = None, depth: Optional[torch.Tensor] = None):
+    """target [B, k+1] (argmax of every verify row), drafts [B, k] -> (emitted [B, k+1], count [B], accepted [B])."""
+    b, k1 = target.shape
+    if nv.use_native(target):
+        emitted = torch.zeros(b, k1, dtype=torch.int64, device=target.device)
+        count = torch.empty(b, dtype=torch.int32, device=target.device)
+        accepted = torch.empty(b, dtype=torch.int32, device=target.device)
+        nv.check(nv.lib().hb_accept_greedy(target.data_ptr(), drafts.data_ptr(), nv.ptr(stop_ids),
+                                           stop_ids.shape[1] if stop_ids is not None else 0, nv.ptr(budget),
+                                           nv.ptr(depth), k1 - 1, b, emitted.data_ptr(), count.data_ptr(),
+                                           accepted.data_ptr(), nv.stream()), "hb_accept_greedy")
+        return emitted, count, accepted
+    e, c, a = accept_greedy_ref(target.cpu(), drafts.cpu(), stop_ids, budget, depth)
+    return e.to(target.device), c.to(target.device), a.to(target.device)
+
+
+def rank_gap(logits: torch.Tensor, ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Rank (count of strictly larger logits) and logit gap to the maximum of token ids[row] in its row."""
+    rows, vocab = logits.shape
+    if nv.use_native(logits):
+        rank = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        gap = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        nv.check(nv.lib().hb_rank_gap(logits.data_ptr(), logits.stride(0), rows, vocab,
+                                      int(logits.dtype == torch.float32), ids.data_ptr(), rank.data_ptr(),
+                                      gap.data_ptr(), nv.stream()), "hb_rank_gap")
+        return rank, gap
+    lg = logits.float()
+    mine = lg.gather(1, ids.view(-1, 1))
+    return (lg > mine).sum(1).int(), (lg.max(1).values - mine.squeeze(1))

@@ -1,0 +1,66 @@
+"""Dense decoder end to end through the Executor: CPU self-consistency and GPU-vs-CPU agreement."""
+import pytest
+import torch
+
+from hibana_b200.engine.executor import Executor
+from hibana_b200.engine.request import SamplingParams
+from hibana_b200.models.dense import DenseModel
+from hibana_b200.target import dense_tiny, scaled
+
+
+def _prompts(n, length, vocab, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def test_chunked_prefill_matches_single_pass_cpu():
+    t = scaled(dense_tiny(), weight_format="bf16")
+    model = DenseModel(t, "cpu", seed=0)
+    prompts = _prompts(3, 21, t.vocab)
+    sp = SamplingParams(max_tokens=6)
+    a = Executor(model, max_batch=4, max_ctx=64, use_graphs=False).generate_batch(prompts, sp, prefill_budget=4096)
+    b = Executor(model, max_batch=4, max_ctx=64, use_graphs=False).generate_batch(prompts, sp, prefill_budget=8)
+    assert [r.output_ids for r in a] == [r.output_ids for r in b]
+    assert all(len(r.output_ids) == 6 and r.finish_reason == "length" for r in a)
+
+
+def test_nvfp4_model_runs_cpu():
+    t = dense_tiny()
+    model = DenseModel(t, "cpu", seed=1)
+    ex = Executor(model, max_batch=2, max_ctx=64, use_graphs=False)
+    out = ex.generate_batch(_prompts(2, 9, t.vocab), SamplingParams(max_tokens=3))
+    assert all(len(r.output_ids) == 3 for r in out)
+    assert ex.kv.free_count == ex.kv.slots
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["bf16", "nvfp4"])
+def test_gpu_matches_cpu_tokens(fmt):
+    t = scaled(dense_tiny(), weight_format=fmt)
+    cpu = DenseModel(t, "cpu", seed=0)
+    gpu = DenseModel(t, "cuda", seed=0, init_device="cpu")
+    prompts = _prompts(4, 33, t.vocab)
+    sp = SamplingParams(max_tokens=8)
+    a = Executor(cpu, max_batch=4, max_ctx=128, use_graphs=False).generate_batch(prompts, sp)
+    ex = Executor(gpu, max_batch=4, max_ctx=128, use_graphs=True)
+    ex.capture_graphs()
+    b = ex.generate_batch(prompts, sp)
+    agree = sum(x == y for ra, rb in zip(a, b) for x, y in zip(ra.output_ids, rb.output_ids))
+    # random-init logits are nearly flat, so a bf16-level difference may flip an argmax now and then;
+    # the first token of each request sees identical inputs and must match
+    assert all(ra.output_ids[0] == rb.output_ids[0] for ra, rb in zip(a, b))
+    assert agree >= 0.6 * 32
+
+
+@pytest.mark.gpu
+def test_graph_equals_eager_gpu():
+    t = dense_tiny()
+    model = DenseModel(t, "cuda", seed=0, init_device="cpu")
+    prompts = _prompts(3, 40, t.vocab)
+    sp = SamplingParams(max_tokens=10)
+    e1 = Executor(model, max_batch=4, max_ctx=128, use_graphs=False)
+    a = e1.generate_batch(prompts, sp)
+    e2 = Executor(model, max_batch=4, max_ctx=128, use_graphs=True)
+    e2.capture_graphs()
+    b = e2.generate_batch(prompts, sp)
+    assert [r.output_ids for r in a] == [r.output_ids for r in b]

@@ -1,0 +1,193 @@
+"""Row / attention / sampling kernels against the plain-PyTorch references (which run on CPU)."""
+import math
+
+import pytest
+import torch
+
+from hibana_b200.ops import attention, basic, sampling
+
+
+def _close(a, b, tol):
+    a, b = a.float().cpu(), b.float().cpu()
+    assert (a - b).abs().max().item() <= tol * max(1.0, b.abs().max().item()), (a - b).abs().max().item()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("h", [256, 2560, 5120, 8192])
+@pytest.mark.parametrize("gemma", [False, True])
+def test_rmsnorm(h, gemma):
+    x = torch.randn(37, h).bfloat16()
+    r = torch.randn(37, h).bfloat16()
+    w = (torch.randn(h) * 0.1).bfloat16()
+    rc, rg = r.clone(), r.clone().cuda()
+    ref = basic.rmsnorm(x, w, 1e-6, residual=rc, gemma=gemma)
+    got = basic.rmsnorm(x.cuda(), w.cuda(), 1e-6, residual=rg, gemma=gemma)
+    _close(got, ref, 2e-2)
+    assert torch.equal(rg.cpu(), rc)
+    _close(basic.rmsnorm(x.cuda(), w.cuda(), 1e-6), basic.rmsnorm(x, w, 1e-6), 2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("norm_first,sig", [(False, False), (True, False), (True, True)])
+def test_gated_rmsnorm(norm_first, sig):
+    x, z = torch.randn(19, 1024).bfloat16(), torch.randn(19, 1024).bfloat16()
+    w = torch.randn(1024).bfloat16()
+    ref = basic.gated_rmsnorm(x, z, w, 1e-5, 128, norm_first=norm_first, sigmoid_gate=sig)
+    got = basic.gated_rmsnorm(x.cuda(), z.cuda(), w.cuda(), 1e-5, 128, norm_first=norm_first, sigmoid_gate=sig)
+    _close(got, ref, 2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("d,rot,qk_norm,fp8,q_gate", [(128, 128, False, False, False), (256, 64, True, True, True),
+                                                      (64, 64, False, False, False), (128, 0, False, False, False)])
+def test_rope_kv_write(d, rot, qk_norm, fp8, q_gate):
+    hq, hkv, t = 6, 2, 23
+    width = hq * d * (2 if q_gate else 1) + 2 * hkv * d
+    qkv = torch.randn(t, width).bfloat16()
+    pos = torch.randint(0, 100000, (t,), dtype=torch.int32)
+    slots = torch.randperm(64)[:t].int() + 1
+    inv = basic.rope_inv_freq(max(rot, 2), 1e6)
+    dt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    qn = (torch.randn(d) * 0.1).bfloat16() if qk_norm else None
+    kn = (torch.randn(d) * 0.1).bfloat16() if qk_norm else None
+    outs = []
+    for dev in ("cpu", "cuda"):
+        kp = torch.zeros(80, hkv, d, dtype=dt, device=dev)
+        vp = torch.zeros(80, hkv, d, dtype=dt, device=dev)
+        q = basic.rope_kv_write(qkv.to(dev), pos.to(dev), slots.to(dev), inv.to(dev), kp, vp, hq, hkv, d, rot=rot,
+                                q_norm=None if qn is None else qn.to(dev), k_norm=None if kn is None else kn.to(dev),
+                                gemma_norm=qk_norm, kv_scale=0.5 if fp8 else 1.0, q_gate=q_gate)
+        outs.append((q, kp, vp))
+    _close(outs[1][0], outs[0][0], 3e-2)
+    _close(outs[1][1].float(), outs[0][1].float(), 7e-2 if fp8 else 3e-2)
+    _close(outs[1][2].float(), outs[0][2].float(), 7e-2 if fp8 else 3e-2)
+
+
+@pytest.mark.gpu
+def test_act_embedding_add():
+    x = torch.randn(33, 512).bfloat16()
+    for mode in (basic.ACT_SILU_SPLIT, basic.ACT_SILU_PAIRS, basic.ACT_RELU2):
+        _close(basic.act_mul(x.cuda(), mode), basic.act_mul(x, mode), 2e-2)
+    g = torch.randn(33, 512).bfloat16()
+    _close(basic.act_mul(x.cuda(), basic.ACT_SIGMOID_GATE, g.cuda()), basic.act_mul(x, basic.ACT_SIGMOID_GATE, g), 2e-2)
+    table = torch.randn(100, 256).bfloat16()
+    ids = torch.randint(0, 100, (17,))
+    assert torch.equal(basic.embedding(ids.cuda(), table.cuda()).cpu(), basic.embedding(ids, table))
+    _close(basic.add(x.cuda(), g.cuda()), basic.add(x, g), 1e-2)
+
+
+def _attn_case(b, rows, ctxs, hq, hkv, d, dtype=torch.bfloat16, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    total = sum(ctxs)
+    slots_n = total + 8
+    kp = (torch.randn(slots_n, hkv, d, generator=g) * 0.7)
+    vp = torch.randn(slots_n, hkv, d, generator=g)
+    perm = torch.randperm(slots_n - 1, generator=g) + 1
+    kv_idx = torch.zeros(b + 2, max(ctxs) + 3, dtype=torch.int32)
+    seq_rows = torch.arange(b, dtype=torch.int32).flip(0) + 1   # non-identity rows
+    o = 0
+    for i, c in enumerate(ctxs):
+        kv_idx[seq_rows[i], :c] = perm[o:o + c].int()
+        o += c
+    q = torch.randn(sum(rows), hq, d, generator=g).bfloat16()
+    indptr = torch.tensor([0] + list(torch.tensor(rows).cumsum(0)), dtype=torch.int32)
+    ctx = torch.tensor(ctxs, dtype=torch.int32)
+    if dtype == torch.bfloat16:
+        kp, vp = kp.bfloat16(), vp.bfloat16()
+    else:
+        kp, vp = (kp / 0.25).to(dtype), (vp / 0.25).to(dtype)
+    return q, kp, vp, kv_idx, ctx, indptr, seq_rows
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("hq,hkv,d", [(40, 8, 128), (4, 2, 64), (24, 2, 256), (32, 2, 128)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_paged_attention_decode(hq, hkv, d, splits):
+    ctxs = [1, 63, 64, 65, 300, 1000]
+    q, kp, vp, idx, ctx, indptr, sr = _attn_case(6, [1] * 6, ctxs, hq, hkv, d)
+    ref = attention.paged_attention(q, kp, vp, idx, ctx, seq_rows=sr)
+    got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(), seq_rows=sr.cuda(),
+                                    splits=splits)
+    _close(got, ref, 2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fp8", [False, True])
+def test_paged_attention_ragged_rows(fp8):
+    rows, ctxs = [4, 1, 16, 33, 7], [10, 200, 16, 150, 500]
+    dt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    q, kp, vp, idx, ctx, indptr, sr = _attn_case(5, rows, ctxs, 10, 2, 128, dtype=dt)
+    scale = 0.25 if fp8 else 1.0
+    ref = attention.paged_attention(q, kp, vp, idx, ctx, q_indptr=indptr, max_rows=33, seq_rows=sr, kv_scale=scale)
+    for splits in (1, 3):
+        got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(),
+                                        q_indptr=indptr.cuda(), max_rows=33, seq_rows=sr.cuda(), kv_scale=scale,
+                                        splits=splits)
+        _close(got, ref, 3e-2)
+
+
+@pytest.mark.gpu
+def test_argmax_and_sampling():
+    logits = torch.randn(9, 5000)
+    logits[3, 77] = logits[3, 4000] = 50.0          # exact tie -> lowest index
+    assert sampling.argmax(logits.cuda()).cpu().tolist() == sampling.argmax(logits).tolist()
+    assert sampling.argmax(logits.cuda())[3].item() == 77
+    bits = torch.zeros(9, (5000 + 31) // 32, dtype=torch.int32)
+    allowed = torch.randint(0, 5000, (9, 40))
+    for r in range(9):
+        for a in allowed[r].tolist():
+            bits[r, a // 32] |= (1 << (a % 32)) if a % 32 != 31 else -(1 << 31)
+    assert sampling.argmax(logits.cuda(), bits.cuda()).cpu().tolist() == sampling.argmax(logits, bits).tolist()
+    temp = torch.tensor([0.0, 0.7, 1.0, 1.3, 0.0, 1.0, 1.0, 2.0, 0.5])
+    top_k = torch.tensor([0, 5, 64, 0, 1, 1, 20, 50, 3], dtype=torch.int32)
+    top_p = torch.tensor([1.0, 0.9, 1.0, 0.5, 1.0, 1.0, 0.8, 1.0, 0.99])
+    seeds = torch.arange(9, dtype=torch.int64) * 7919 + 13
+    offs = torch.arange(9, dtype=torch.int64)
+    ref = sampling.sample(logits, temp, top_k, top_p, seeds, offs)
+    got = sampling.sample(logits.cuda(), temp.cuda(), top_k.cuda(), top_p.cuda(), seeds.cuda(), offs.cuda())
+    assert got.cpu().tolist() == ref.tolist()
+
+
+def test_sampling_distribution_cpu():
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).repeat(4000, 1)
+    n = 4000
+    out = sampling.sample(logits, torch.ones(n), torch.zeros(n, dtype=torch.int32), torch.ones(n),
+                          torch.full((n,), 5, dtype=torch.int64), torch.arange(n, dtype=torch.int64))
+    freq = torch.bincount(out, minlength=4).float() / n
+    assert (freq - torch.softmax(logits[0], 0)).abs().max() < 0.03
+
+
+def test_accept_greedy_cpu_and_rank_gap():
+    target = torch.tensor([[5, 6, 7, 8], [5, 6, 7, 8], [1, 2, 3, 4], [9, 9, 9, 9]])
+    drafts = torch.tensor([[5, 6, 7], [5, 0, 7], [0, 2, 3], [9, 9, 9]])
+    e, c, a = sampling.accept_greedy(target, drafts)
+    assert c.tolist() == [4, 2, 1, 4] and a.tolist() == [3, 1, 0, 3]
+    assert e[1, :2].tolist() == [5, 6]
+    e, c, a = sampling.accept_greedy(target, drafts, stop_ids=torch.tensor([[6], [6], [6], [6]]))
+    assert c.tolist() == [2, 2, 1, 4]
+    e, c, a = sampling.accept_greedy(target, drafts, budget=torch.tensor([2, 9, 9, 3], dtype=torch.int32))
+    assert c.tolist() == [2, 2, 1, 3]
+    lg = torch.tensor([[1.0, 3.0, 2.0, 0.5]])
+    r, g = sampling.rank_gap(lg, torch.tensor([2]))
+    assert r.tolist() == [1] and abs(g.item() - 1.0) < 1e-6
+
+
+@pytest.mark.gpu
+def test_accept_greedy_and_rank_gap_gpu():
+    g = torch.Generator().manual_seed(3)
+    target = torch.randint(0, 4, (64, 6), generator=g)
+    drafts = torch.randint(0, 4, (64, 5), generator=g)
+    stops = torch.randint(0, 8, (64, 2), generator=g)
+    budget = torch.randint(1, 7, (64,), generator=g, dtype=torch.int32)
+    depth = torch.randint(0, 6, (64,), generator=g, dtype=torch.int32)
+    ref = sampling.accept_greedy(target, drafts, stops, budget, depth)
+    got = sampling.accept_greedy(target.cuda(), drafts.cuda(), stops.cuda(), budget.cuda(), depth.cuda())
+    assert got[1].cpu().tolist() == ref[1].tolist() and got[2].cpu().tolist() == ref[2].tolist()
+    for i in range(64):
+        n = int(ref[1][i])
+        assert got[0][i, :n].cpu().tolist() == ref[0][i, :n].tolist()
+    lg = torch.randn(11, 3000)
+    ids = torch.randint(0, 3000, (11,))
+    r1, g1 = sampling.rank_gap(lg, ids)
+    r2, g2 = sampling.rank_gap(lg.cuda(), ids.cuda())
+    assert r1.tolist() == r2.cpu().tolist() and torch.allclose(g1, g2.cpu(), atol=1e-5)
