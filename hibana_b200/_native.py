@@ -98,7 +98,14 @@ def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def check(code: int, what: str) -> None:
+CALLS = 0      # native entry points called
+LAUNCHES = 0   # kernels those calls launched (each call launches at least one)
+
+
+def check(code: int, what: str, launches: int = 1) -> None:
+    global CALLS, LAUNCHES
+    CALLS += 1
+    LAUNCHES += launches
     if code != 0:
         raise RuntimeError(f"{what} failed with code {code}")
 

@@ -13,6 +13,7 @@ from typing import Optional, Sequence
 import numpy as np
 import torch
 
+from .. import _native as nv
 from ..ops import attention, sampling
 from .context import DECODE, PREFILL, VERIFY, ForwardContext
 
@@ -60,7 +61,7 @@ class ModelRunner:
         if self.buckets[-1] < max_batch:
             self.buckets = self.buckets + (max_batch,)
         self.bufs = {b: StepBuffers(b, self.device) for b in self.buckets}
-        self.launches = 0           # kernels launched through this runner's own ops (counted per step kind)
+        self.graph_launches: dict[int, int] = {}   # kernels of this library inside each bucket's graph
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -126,8 +127,10 @@ class ModelRunner:
             torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
+            before = nv.LAUNCHES
             with torch.cuda.graph(g):
                 self._decode_body(buf)
+            self.graph_launches[b] = nv.LAUNCHES - before
             buf.graph = g
 
     def decode(self, rows: Sequence[int], tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int],

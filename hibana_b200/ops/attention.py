@@ -95,5 +95,6 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), kv_indices.data_ptr(),
         kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), nv.ptr(q_indptr), out.data_ptr(),
         workspace.part_o.data_ptr() if splits > 1 else None, workspace.part_lse.data_ptr() if splits > 1 else None,
-        b, t, max_rows, hq, hkv, d, splits, scale, int(fp8), kv_scale, int(causal), nv.stream()), "hb_attn_paged")
+        b, t, max_rows, hq, hkv, d, splits, scale, int(fp8), kv_scale, int(causal), nv.stream()), "hb_attn_paged",
+             launches=2 if splits > 1 else 1)
     return out
