@@ -393,4 +393,13 @@ int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long lo
   return 0;
 }
 
+int hb_attn_merge(const void* part_o, const void* part_lse, void* out, long long rows_heads, int splits, int d,
+                  void* stream) {
+  if (rows_heads <= 0) return 0;
+  attn_merge_kernel<<<static_cast<unsigned>(rows_heads), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(part_o), static_cast<const float*>(part_lse), static_cast<__nv_bfloat16*>(out), splits,
+      d);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
 }  // extern "C"

@@ -1,0 +1,354 @@
+// Flash-decoding for paged GQA attention with up to 16 query rows per (sequence, kv head): decode (one token x
+// GQA group <= 16) and short speculative verify blocks. Bandwidth-bound by design:
+//
+//   * every K / V row (one token, one kv head: D bf16) is fetched by ONE bulk async copy (cp.async.bulk) straight
+//     from its slot in the token-granular pool into a padded shared-memory row, completion tracked by an mbarrier;
+//   * each of the 4 warps of a CTA owns a private 3-stage ring of KT-key tiles and walks its own share of the keys,
+//     so the main loop has no block-wide barrier: a warp waits only on its own mbarrier;
+//   * S = Q K^T and O += P V run on the tensor cores (m16n8k16 bf16, fp32 accumulate) with the query rows padded to
+//     one 16-row tile; the online softmax lives in registers; the 4 warps' partial (m, l, O) merge through shared
+//     memory at the end, and KV splits merge through the LSE kernel of attn.cu.
+//
+// The KV range of a split is derived on the device from ctx_len, so one captured launch serves any context.
+// Replaces the FlashInfer decode wrapper the reference plans per step (hibana/engine/graphs.py:55,
+// hibana/engine/executor.py:161-169) and the multi-row verify kernel (hibana/kernels/csrc/verify_attn.cu:469).
+#include "hb_api.h"
+#include "hb_common.cuh"
+
+namespace hb {
+namespace {
+
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_STAGES = 3;
+
+struct DecParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k_pool;
+  const __nv_bfloat16* v_pool;
+  long long pool_stride;
+  const int* kv_indices;
+  long long ld_idx;
+  const int* seq_rows;
+  const int* ctx_len;
+  const int* q_indptr;
+  __nv_bfloat16* out;
+  float* part_o;
+  float* part_lse;
+  int hq, hkv, splits;
+  float scale_log2;
+  int causal;
+  int* status;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int D>
+struct DecCfg {
+  static constexpr int KT = D >= 256 ? 16 : 32;        // keys per warp tile
+  static constexpr int ROWB = D * 2 + 16;               // padded row: conflict-free ldmatrix
+  static constexpr int TILE_BYTES = KT * ROWB;          // one of K or V
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  static constexpr int WARP_BYTES = DEC_STAGES * STAGE_BYTES;
+  static constexpr int Q_BYTES = 16 * ROWB;
+  static constexpr int SMEM = DEC_WARPS * WARP_BYTES + Q_BYTES + 256;
+  static_assert(16 * D * 4 + 16 * 8 <= WARP_BYTES, "merge scratch must fit a warp's ring");
+};
+
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const DecParams p) {
+  using C = DecCfg<D>;
+  constexpr int KT = C::KT, ROWB = C::ROWB;
+  constexpr int NB = KT / 8;     // score n-blocks per tile
+  constexpr int KS = D / 16;     // k-steps of Q K^T
+  constexpr int ONB = D / 8;     // output n-blocks
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g4 = lane >> 2, t4 = lane & 3;
+  uint8_t* ring = smem + warp * C::WARP_BYTES;
+  uint8_t* qs = smem + DEC_WARPS * C::WARP_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(qs + C::Q_BYTES);   // [DEC_WARPS][DEC_STAGES]
+  volatile int* abort = reinterpret_cast<volatile int*>(bars + DEC_WARPS * DEC_STAGES);
+
+  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int g = p.hq / p.hkv;
+  const int row0 = p.q_indptr ? p.q_indptr[b] : b;
+  const int R = p.q_indptr ? p.q_indptr[b + 1] - row0 : 1;
+  const int nq = R * g;   // <= 16 guaranteed by the host
+  const int ctx = p.ctx_len[b];
+  const int per = (((ctx + p.splits - 1) / p.splits + KT - 1) / KT) * KT;
+  const int k0 = split * per;
+  const int k1 = min(ctx, k0 + per);
+  const int ntiles = k1 > k0 ? (k1 - k0 + KT - 1) / KT : 0;
+
+  if (tid == 0) {
+    for (int i = 0; i < DEC_WARPS * DEC_STAGES; ++i) mbar_init(&bars[i], 1);
+    *abort = 0;
+    fence_mbar_init();
+  }
+  // Q rows (zero padded to 16) into shared memory.
+  for (int i = tid; i < 16 * (D / 8); i += DEC_WARPS * 32) {
+    const int qi = i / (D / 8), c = i % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (qi < nq) {
+      const int rr = qi / g, gg = qi % g;
+      v = *reinterpret_cast<const uint4*>(p.q + (static_cast<long long>(row0 + rr) * p.hq + kvh * g + gg) * D + c * 8);
+    }
+    *reinterpret_cast<uint4*>(qs + qi * ROWB + c * 16) = v;
+  }
+  __syncthreads();
+
+  uint32_t qf[KS][4];
+  {
+    const uint32_t base = smem_u32(qs) + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) ldsm_x4(qf[ks], base + ks * 32);
+  }
+
+  const int* idx_row = p.kv_indices + static_cast<long long>(p.seq_rows ? p.seq_rows[b] : b) * p.ld_idx;
+  uint64_t* mybar = bars + warp * DEC_STAGES;
+
+  // Issues the copies of this warp's `it`-th tile into its ring stage; lanes own keys (KT <= 32).
+  auto issue = [&](int it) {
+    const int tile = warp + it * DEC_WARPS;
+    if (tile >= ntiles) return;
+    const int st = it % DEC_STAGES;
+    const int base = k0 + tile * KT;
+    const int valid = min(KT, k1 - base);
+    uint8_t* kdst = ring + st * C::STAGE_BYTES;
+    uint8_t* vdst = kdst + C::TILE_BYTES;
+    if (lane == 0) mbar_expect_tx(&mybar[st], static_cast<uint32_t>(valid) * 2u * D * 2u);
+    __syncwarp();
+    if (lane < KT) {
+      if (lane < valid) {
+        const long long off = static_cast<long long>(idx_row[base + lane]) * p.pool_stride + static_cast<long long>(kvh) * D;
+        bulk_load(kdst + lane * ROWB, p.k_pool + off, D * 2, &mybar[st]);
+        bulk_load(vdst + lane * ROWB, p.v_pool + off, D * 2, &mybar[st]);
+      } else {
+        for (int c = 0; c < D / 8; ++c) {
+          *reinterpret_cast<uint4*>(kdst + lane * ROWB + c * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(vdst + lane * ROWB + c * 16) = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+  };
+
+  float o[ONB][4];
+#pragma unroll
+  for (int i = 0; i < ONB; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  // Causal limits of this thread's two rows (keys [0, limit) visible).
+  const int lim_lo = p.causal ? ctx - R + (g4 / g) + 1 : ctx;
+  const int lim_hi = p.causal ? ctx - R + ((g4 + 8) / g) + 1 : ctx;
+
+  issue(0);
+  issue(1);
+  bool ok = true;
+  for (int it = 0; warp + it * DEC_WARPS < ntiles; ++it) {
+    // Stage (it + 2) % 3 was read in iteration it - 1: every lane is past it, order it before the async writes.
+    __syncwarp();
+    fence_proxy_async_smem();
+    issue(it + 2);
+    const int st = it % DEC_STAGES;
+    if (!mbar_wait(&mybar[st], (it / DEC_STAGES) & 1, abort, p.status, kTimeoutFull)) {
+      ok = false;
+      break;
+    }
+    __syncwarp();
+    const uint32_t kbase = smem_u32(ring + st * C::STAGE_BYTES);
+    const uint32_t vbase = kbase + C::TILE_BYTES;
+    const int tile = warp + it * DEC_WARPS;
+    const int kpos0 = k0 + tile * KT;
+
+    float s[NB][4];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      const uint32_t a = kbase + (j * 8 + (lane & 7)) * ROWB + (lane >> 3) * 16;
+#pragma unroll
+      for (int ks = 0; ks < KS; ks += 2) {
+        uint32_t kb[4];
+        ldsm_x4(kb, a + ks * 32);
+        mma_bf16(s[j], qf[ks], kb[0], kb[1]);
+        mma_bf16(s[j], qf[ks + 1], kb[2], kb[3]);
+      }
+    }
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int kp = kpos0 + j * 8 + 2 * t4 + e;
+        const bool in = kp < k1;
+        s[j][e] = (in && kp < lim_lo) ? s[j][e] * p.scale_log2 : -INFINITY;
+        s[j][2 + e] = (in && kp < lim_hi) ? s[j][2 + e] * p.scale_log2 : -INFINITY;
+        mx_lo = fmaxf(mx_lo, s[j][e]);
+        mx_hi = fmaxf(mx_hi, s[j][2 + e]);
+      }
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    const float a_lo = mn_lo == -INFINITY ? 1.f : exp2f(m_lo - mn_lo);
+    const float a_hi = mn_hi == -INFINITY ? 1.f : exp2f(m_hi - mn_hi);
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    l_lo *= a_lo;
+    l_hi *= a_hi;
+    uint32_t pf[NB / 2][4];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      const float p0 = mn_lo == -INFINITY ? 0.f : exp2f(s[j][0] - mn_lo);
+      const float p1 = mn_lo == -INFINITY ? 0.f : exp2f(s[j][1] - mn_lo);
+      const float p2 = mn_hi == -INFINITY ? 0.f : exp2f(s[j][2] - mn_hi);
+      const float p3 = mn_hi == -INFINITY ? 0.f : exp2f(s[j][3] - mn_hi);
+      l_lo += p0 + p1;
+      l_hi += p2 + p3;
+      pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+      pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int nb = 0; nb < ONB; ++nb) {
+      o[nb][0] *= a_lo;
+      o[nb][1] *= a_lo;
+      o[nb][2] *= a_hi;
+      o[nb][3] *= a_hi;
+    }
+#pragma unroll
+    for (int kk = 0; kk < KT / 16; ++kk) {
+      const uint32_t a = vbase + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * ROWB + (lane >> 4) * 16;
+#pragma unroll
+      for (int nb = 0; nb < ONB; nb += 2) {
+        uint32_t vb[4];
+        ldsm_x4_t(vb, a + nb * 16);
+        mma_bf16(o[nb], pf[kk], vb[0], vb[1]);
+        mma_bf16(o[nb + 1], pf[kk], vb[2], vb[3]);
+      }
+    }
+  }
+  // Row sums live split over the 4 threads of a row group.
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  if (!ok) {
+    // Copies that never landed would write into the ring later; nothing more is issued and the result is dropped.
+    m_lo = m_hi = -INFINITY;
+    l_lo = l_hi = 0.f;
+  }
+  __syncwarp();
+  // ---- merge the 4 warps through each warp's own (now idle) ring
+  float* mo = reinterpret_cast<float*>(ring);          // [16][D]
+  float* ml = mo + 16 * D;                             // [16][2] (m, l)
+#pragma unroll
+  for (int nb = 0; nb < ONB; ++nb) {
+    *reinterpret_cast<float2*>(mo + g4 * D + nb * 8 + 2 * t4) = make_float2(o[nb][0], o[nb][1]);
+    *reinterpret_cast<float2*>(mo + (g4 + 8) * D + nb * 8 + 2 * t4) = make_float2(o[nb][2], o[nb][3]);
+  }
+  if (t4 == 0) {
+    ml[g4 * 2] = m_lo;
+    ml[g4 * 2 + 1] = l_lo;
+    ml[(g4 + 8) * 2] = m_hi;
+    ml[(g4 + 8) * 2 + 1] = l_hi;
+  }
+  __syncthreads();
+  for (int i = tid; i < nq * D; i += DEC_WARPS * 32) {
+    const int qi = i / D, d = i % D;
+    float mt = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w)
+      mt = fmaxf(mt, reinterpret_cast<const float*>(smem + w * C::WARP_BYTES)[16 * D + qi * 2]);
+    float acc = 0.f, lt = 0.f;
+    if (mt > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) {
+        const float* wo = reinterpret_cast<const float*>(smem + w * C::WARP_BYTES);
+        const float mw = wo[16 * D + qi * 2];
+        const float sc = mw == -INFINITY ? 0.f : exp2f(mw - mt);
+        acc += sc * wo[qi * D + d];
+        lt += sc * wo[16 * D + qi * 2 + 1];
+      }
+    }
+    const float val = lt > 0.f ? acc / lt : 0.f;
+    const int rr = qi / g, gg = qi % g;
+    const long long rh = static_cast<long long>(row0 + rr) * p.hq + kvh * g + gg;
+    if (p.splits == 1) {
+      p.out[rh * D + d] = __float2bfloat16(val);
+    } else {
+      p.part_o[(rh * p.splits + split) * D + d] = val;
+      if (d == 0) p.part_lse[rh * p.splits + split] = lt > 0.f ? mt + log2f(lt) : -INFINITY;
+    }
+  }
+}
+
+template <int D>
+int launch_decode(const DecParams& p, int batch, cudaStream_t st) {
+  using C = DecCfg<D>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) !=
+        cudaSuccess)
+      return 3;
+    attr = true;
+  }
+  attn_decode_kernel<D><<<dim3(batch, p.hkv, p.splits), DEC_WARPS * 32, C::SMEM, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" {
+
+// bf16 KV only; rows_per_seq * (hq / hkv) must be <= 16. Partials go through hb_attn_merge when splits > 1.
+int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                   const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
+                   const void* q_indptr, void* out, void* part_o, void* part_lse, int batch, int max_rows, int hq,
+                   int hkv, int d, int splits, float scale, int causal, void* status, void* stream) {
+  if (batch <= 0) return 0;
+  if (hq % hkv != 0 || max_rows * (hq / hkv) > 16) return 1;
+  DecParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_pool = static_cast<const __nv_bfloat16*>(k_pool);
+  p.v_pool = static_cast<const __nv_bfloat16*>(v_pool);
+  p.pool_stride = pool_stride;
+  p.kv_indices = static_cast<const int*>(kv_indices);
+  p.ld_idx = ld_idx;
+  p.seq_rows = static_cast<const int*>(seq_rows);
+  p.ctx_len = static_cast<const int*>(ctx_len);
+  p.q_indptr = static_cast<const int*>(q_indptr);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.part_o = static_cast<float*>(part_o);
+  p.part_lse = static_cast<float*>(part_lse);
+  p.hq = hq; p.hkv = hkv; p.splits = splits < 1 ? 1 : splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.status = static_cast<int*>(status);
+  if (p.splits > 1 && (part_o == nullptr || part_lse == nullptr)) return 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (d == 64) return launch_decode<64>(p, batch, st);
+  if (d == 128) return launch_decode<128>(p, batch, st);
+  if (d == 256) return launch_decode<256>(p, batch, st);
+  return 1;
+}
+
+}  // extern "C"

@@ -43,13 +43,23 @@ int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long lo
                   const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len, const void* q_indptr,
                   void* out, void* part_o, void* part_lse, int batch, int total_rows, int max_rows, int hq, int hkv, int d,
                   int splits, float scale, int kv_fp8, float kv_scale, int causal, void* stream);
+int hb_attn_merge(const void* part_o, const void* part_lse, void* out, long long rows_heads, int splits, int d,
+                  void* stream);
+// Tensor-core flash-decoding (attn_decode.cu): bf16 KV, rows_per_sequence * (hq / hkv) <= 16.
+int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                   const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
+                   const void* q_indptr, void* out, void* part_o, void* part_lse, int batch, int max_rows, int hq,
+                   int hkv, int d, int splits, float scale, int causal, void* status, void* stream);
 
 // ---- sampling and speculative acceptance (sample.cu) -----------------------------------------------------
 int hb_argmax(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* bitmask, int mask_words,
               void* out, void* out_val, void* stream);
 int hb_sample(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* temperature,
               const void* top_k, const void* top_p, const void* seeds, const void* offsets, const void* bitmask,
-              int mask_words, void* out, void* out_prob, void* stream);
+              int mask_words, void* out, void* out_prob, int skip_greedy, void* stream);
+int hb_argmax2(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* bitmask, int mask_words,
+               int nch, void* scratch_v, void* scratch_i, const void* temperature, void* out, void* out_val,
+               void* stream);
 int hb_accept_greedy(const void* target, const void* drafts, const void* stop_ids, int n_stop, const void* budget,
                      const void* depth, int k_max, int batch, void* emitted, void* count, void* accepted,
                      void* stream);

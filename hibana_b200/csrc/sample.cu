@@ -73,6 +73,86 @@ argmax_kernel(const T* __restrict__ logits, long long ld, int vocab, const int* 
   }
 }
 
+// Two-stage argmax for wide vocabularies: `nch` CTAs per row each scan a slice, then one warp per row combines.
+template <typename T>
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const T* __restrict__ logits, long long ld, int vocab, const int* __restrict__ bitmask,
+                      int mask_words, int nch, float* __restrict__ pv, int* __restrict__ pi) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int row = blockIdx.x, ch = blockIdx.y;
+  const T* lr = logits + row * ld;
+  const int* mask = bitmask ? bitmask + static_cast<long long>(row) * mask_words : nullptr;
+  const int per = (vocab + nch - 1) / nch;
+  const int lo = ch * per, hi = min(vocab, lo + per);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    if (!mask_ok(mask, i)) continue;
+    const float v = ldf<T>(lr, i);
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sv[threadIdx.x >> 5] = best;
+    si[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) {
+        best = sv[w];
+        bi = si[w];
+      }
+    pv[row * nch + ch] = best;
+    pi[row * nch + ch] = bi;
+  }
+}
+
+// One warp per row. Rows whose temperature is > 0 are left to the sampling kernel.
+__global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int nch, int rows,
+                                    const float* __restrict__ temperature, long long* __restrict__ out,
+                                    float* __restrict__ out_val) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  if (temperature != nullptr && temperature[row] > 0.f) return;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = lane; c < nch; c += 32) {
+    const float v = pv[row * nch + c];
+    const int i = pi[row * nch + c];
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (lane == 0) {
+    out[row] = bi == 0x7fffffff ? 0 : bi;
+    if (out_val) out_val[row] = best;
+  }
+}
+
 // splitmix64-based counter RNG -> uniform in [0, 1).
 __device__ __forceinline__ float uniform01(unsigned long long seed, unsigned long long offset) {
   unsigned long long z = seed + 0x9E3779B97F4A7C15ull * (offset + 1);
@@ -92,7 +172,7 @@ sample_kernel(const T* __restrict__ logits, long long ld, int vocab, const float
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ offsets,
               const int* __restrict__ bitmask, int mask_words, long long* __restrict__ out,
-              float* __restrict__ out_prob) {
+              float* __restrict__ out_prob, int skip_greedy) {
   __shared__ float cv[SAMPLE_K];
   __shared__ int ci[SAMPLE_K];
   __shared__ float wv[8];
@@ -103,6 +183,7 @@ sample_kernel(const T* __restrict__ logits, long long ld, int vocab, const float
   const T* lr = logits + row * ld;
   const int* mask = bitmask ? bitmask + static_cast<long long>(row) * mask_words : nullptr;
   const float temp = temperature ? temperature[row] : 0.f;
+  if (skip_greedy && temp <= 0.f) return;   // the two-stage argmax owns greedy rows
   int k = top_k ? top_k[row] : SAMPLE_K;
   if (k <= 0 || k > SAMPLE_K) k = SAMPLE_K;
   if (temp <= 0.f) k = 1;
@@ -284,14 +365,14 @@ int hb_argmax(const void* logits, long long ld, int rows, int vocab, int is_f32,
 
 int hb_sample(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* temperature,
               const void* top_k, const void* top_p, const void* seeds, const void* offsets, const void* bitmask,
-              int mask_words, void* out, void* out_prob, void* stream) {
+              int mask_words, void* out, void* out_prob, int skip_greedy, void* stream) {
   if (rows <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define HB_SAMPLE_ARGS                                                                                     \
   ld, vocab, static_cast<const float*>(temperature), static_cast<const int*>(top_k),                       \
       static_cast<const float*>(top_p), static_cast<const unsigned long long*>(seeds),                     \
       static_cast<const unsigned long long*>(offsets), static_cast<const int*>(bitmask), mask_words,       \
-      static_cast<long long*>(out), static_cast<float*>(out_prob)
+      static_cast<long long*>(out), static_cast<float*>(out_prob), skip_greedy
   if (is_f32) sample_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float*>(logits), HB_SAMPLE_ARGS);
   else sample_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), HB_SAMPLE_ARGS);
 #undef HB_SAMPLE_ARGS
@@ -322,6 +403,29 @@ int hb_rank_gap(const void* logits, long long ld, int rows, int vocab, int is_f3
     rank_gap_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), ld, vocab,
                                                          static_cast<const long long*>(ids),
                                                          static_cast<int*>(rank), static_cast<float*>(gap));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// Two-stage greedy argmax. scratch_v / scratch_i hold rows * nch partials. With `temperature` given, rows whose
+// temperature is > 0 are skipped (their token comes from hb_sample with skip_greedy).
+int hb_argmax2(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* bitmask, int mask_words,
+               int nch, void* scratch_v, void* scratch_i, const void* temperature, void* out, void* out_val,
+               void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 grid(rows, nch);
+  if (is_f32)
+    argmax_partial_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(logits), ld, vocab,
+                                                       static_cast<const int*>(bitmask), mask_words, nch,
+                                                       static_cast<float*>(scratch_v), static_cast<int*>(scratch_i));
+  else
+    argmax_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(logits), ld, vocab, static_cast<const int*>(bitmask), mask_words, nch,
+        static_cast<float*>(scratch_v), static_cast<int*>(scratch_i));
+  argmax_final_kernel<<<(rows + 3) / 4, 128, 0, st>>>(static_cast<const float*>(scratch_v),
+                                                      static_cast<const int*>(scratch_i), nch, rows,
+                                                      static_cast<const float*>(temperature),
+                                                      static_cast<long long*>(out), static_cast<float*>(out_val));
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -17,14 +17,23 @@ from .. import _native as nv
 P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
 nv.register("hb_attn_paged", [P, P, P, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, Fl, I, Fl, I, P])
 
+nv.register("hb_attn_merge", [P, P, P, L, I, I, P])
+nv.register("hb_attn_decode", [P, P, P, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, P, P])
+
 NUM_SMS = 148
 
 
 def choose_splits(batch: int, hkv: int, max_ctx: int, row_chunks: int = 1) -> int:
-    """KV splits so the grid covers the SMs about twice; a split never gets fewer than 256 keys."""
+    """KV splits that fill whole waves of one CTA per SM; a split never gets fewer than 256 keys."""
     ctas = max(1, batch * hkv * row_chunks)
-    want = max(1, (2 * NUM_SMS + ctas - 1) // ctas)
-    return int(max(1, min(want, max(1, max_ctx // 256), 64)))
+    cap = int(max(1, min(max_ctx // 256, 64)))
+    best, best_eff = 1, 0.0
+    for s in range(1, cap + 1):
+        n = ctas * s
+        eff = n / (-(-n // NUM_SMS) * NUM_SMS)
+        if eff > best_eff + 0.02:     # prefer fewer splits unless the wave efficiency clearly improves
+            best, best_eff = s, eff
+    return best
 
 
 class AttnWorkspace:
@@ -91,6 +100,18 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     if splits > 1 and (workspace is None or workspace.rows < t or workspace.splits != splits):
         workspace = AttnWorkspace(t, hq, d, splits, q.device)
     fp8 = k_pool.dtype != torch.bfloat16
+    if not fp8 and max_rows * (hq // hkv) <= 16 and d in (64, 128, 256):
+        st = nv.device_state(q.device)
+        nv.check(nv.lib().hb_attn_decode(
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), kv_indices.data_ptr(),
+            kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), nv.ptr(q_indptr), out.data_ptr(),
+            workspace.part_o.data_ptr() if splits > 1 else None,
+            workspace.part_lse.data_ptr() if splits > 1 else None, b, max_rows, hq, hkv, d, splits, scale,
+            int(causal), st.status.data_ptr(), nv.stream()), "hb_attn_decode")
+        if splits > 1:
+            nv.check(nv.lib().hb_attn_merge(workspace.part_o.data_ptr(), workspace.part_lse.data_ptr(),
+                                            out.data_ptr(), t * hq, splits, d, nv.stream()), "hb_attn_merge")
+        return out
     nv.check(nv.lib().hb_attn_paged(
         q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), kv_indices.data_ptr(),
         kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), nv.ptr(q_indptr), out.data_ptr(),

@@ -13,7 +13,10 @@ from .. import _native as nv
 
 P, I, L = nv.P, nv.I, nv.L
 nv.register("hb_argmax", [P, L, I, I, I, P, I, P, P, P])
-nv.register("hb_sample", [P, L, I, I, I, P, P, P, P, P, P, I, P, P, P])
+nv.register("hb_sample", [P, L, I, I, I, P, P, P, P, P, P, I, P, P, I, P])
+nv.register("hb_argmax2", [P, L, I, I, I, P, I, I, P, P, P, P, P, P])
+
+ARGMAX_CHUNKS = 32
 nv.register("hb_accept_greedy", [P, P, P, I, P, P, I, I, P, P, P, P])
 nv.register("hb_rank_gap", [P, L, I, I, I, P, P, P, P])
 
@@ -35,16 +38,25 @@ def argmax(logits: torch.Tensor, bitmask: Optional[torch.Tensor] = None,
     rows, vocab = logits.shape
     if nv.use_native(logits):
         out = torch.empty(rows, dtype=torch.int64, device=logits.device) if out is None else out
-        nv.check(nv.lib().hb_argmax(logits.data_ptr(), logits.stride(0), rows, vocab,
-                                    int(logits.dtype == torch.float32), nv.ptr(bitmask),
-                                    bitmask.shape[1] if bitmask is not None else 0, out.data_ptr(), None,
-                                    nv.stream()), "hb_argmax")
+        _argmax2(logits, bitmask, None, out)
         return out
     res = _apply_bitmask(logits, bitmask).argmax(dim=-1)
     if out is not None:
         out.copy_(res)
         return out
     return res
+
+
+def _argmax2(logits: torch.Tensor, bitmask: Optional[torch.Tensor], temperature: Optional[torch.Tensor],
+             out: torch.Tensor) -> None:
+    rows, vocab = logits.shape
+    nch = ARGMAX_CHUNKS if vocab >= 8192 else 1
+    sv = torch.empty(rows, nch, dtype=torch.float32, device=logits.device)
+    si = torch.empty(rows, nch, dtype=torch.int32, device=logits.device)
+    nv.check(nv.lib().hb_argmax2(logits.data_ptr(), logits.stride(0), rows, vocab, int(logits.dtype == torch.float32),
+                                 nv.ptr(bitmask), bitmask.shape[1] if bitmask is not None else 0, nch, sv.data_ptr(),
+                                 si.data_ptr(), nv.ptr(temperature), out.data_ptr(), None, nv.stream()), "hb_argmax2",
+             launches=2)
 
 
 def uniform01(seed: int, offset: int) -> float:
@@ -93,11 +105,12 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     rows, vocab = logits.shape
     if nv.use_native(logits):
         out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+        _argmax2(logits, bitmask, temperature, out)      # greedy rows
         nv.check(nv.lib().hb_sample(logits.data_ptr(), logits.stride(0), rows, vocab,
                                     int(logits.dtype == torch.float32), temperature.data_ptr(), top_k.data_ptr(),
                                     top_p.data_ptr(), seeds.data_ptr(), offsets.data_ptr(), nv.ptr(bitmask),
-                                    bitmask.shape[1] if bitmask is not None else 0, out.data_ptr(), None,
-                                    nv.stream()), "hb_sample")
+                                    bitmask.shape[1] if bitmask is not None else 0, out.data_ptr(), None, 1,
+                                    nv.stream()), "hb_sample")   # rows with temperature > 0
         return out
     return sample_ref(logits, temperature, top_k, top_p, seeds, offsets, bitmask)
 

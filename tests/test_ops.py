@@ -191,3 +191,17 @@ def test_accept_greedy_and_rank_gap_gpu():
     r1, g1 = sampling.rank_gap(lg, ids)
     r2, g2 = sampling.rank_gap(lg.cuda(), ids.cuda())
     assert r1.tolist() == r2.cpu().tolist() and torch.allclose(g1, g2.cpu(), atol=1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("hq,hkv,d,rows", [(40, 8, 128, [3, 1, 2, 3]), (4, 2, 64, [8, 1, 5, 2]), (12, 2, 256, [2, 1, 2, 1])])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_tensor_core_decode_verify_rows(hq, hkv, d, rows, splits):
+    ctxs = [40, 700, 129, 2500]
+    q, kp, vp, idx, ctx, indptr, sr = _attn_case(4, rows, ctxs, hq, hkv, d, seed=5)
+    ref = attention.paged_attention(q, kp, vp, idx, ctx, q_indptr=indptr, max_rows=max(rows), seq_rows=sr)
+    got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(), q_indptr=indptr.cuda(),
+                                    max_rows=max(rows), seq_rows=sr.cuda(), splits=splits)
+    _close(got, ref, 2e-2)
+    from hibana_b200 import _native as nv
+    assert nv.read_status() == 0
