@@ -1,0 +1,63 @@
+"""Recurrent-state pool: one slot per running sequence or cached snapshot.
+
+Per recurrent layer a slot holds the causal-conv window (last conv_width - 1 raw rows, bf16) and the SSM /
+delta-rule state (fp32; fp16 with stochastic rounding or int8 windows as options). Slot 0 is the dummy row padded
+graph rows use. Reference: hibana/cache/state_pool.py:25-103 (`conv_all`, `ssm_all`, `copy_slot`).
+"""
+from __future__ import annotations
+
+import torch
+
+
+class StatePool:
+    def __init__(self, layers: int, slots: int, conv_dim: int, conv_width: int, state_shape: tuple,
+                 device: torch.device | str = "cpu", state_dtype: torch.dtype = torch.float32):
+        self.layers, self.slots = layers, slots
+        self.device = torch.device(device)
+        self.conv = torch.zeros(max(layers, 1), slots + 1, conv_dim, max(conv_width - 1, 1), dtype=torch.bfloat16,
+                                device=device)
+        self.ssm = torch.zeros(max(layers, 1), slots + 1, *state_shape, dtype=state_dtype, device=device)
+        self._free = list(range(slots, 0, -1))
+        self._owned = bytearray(slots + 1)
+
+    @property
+    def free_count(self) -> int:
+        return len(self._free)
+
+    @property
+    def bytes_per_slot(self) -> int:
+        return (self.conv[:, 0].numel() * 2 + self.ssm[:, 0].numel() * self.ssm.element_size())
+
+    def alloc(self) -> int:
+        if not self._free:
+            raise MemoryError("state pool exhausted")
+        s = self._free.pop()
+        self._owned[s] = 1
+        return s
+
+    def free(self, slot: int) -> None:
+        if slot <= 0:
+            return
+        if not self._owned[slot]:
+            raise ValueError(f"double free of state slot {slot}")
+        self._owned[slot] = 0
+        self._free.append(slot)
+
+    def copy_slot(self, src: int, dst: int) -> None:
+        self.conv[:, dst].copy_(self.conv[:, src])
+        self.ssm[:, dst].copy_(self.ssm[:, src])
+
+    def zero_slot(self, slot: int) -> None:
+        self.conv[:, slot].zero_()
+        self.ssm[:, slot].zero_()
+
+    def export_slot(self, slot: int) -> tuple[torch.Tensor, torch.Tensor]:
+        return self.conv[:, slot].clone(), self.ssm[:, slot].clone()
+
+    def import_slot(self, slot: int, conv: torch.Tensor, ssm: torch.Tensor) -> None:
+        self.conv[:, slot].copy_(conv)
+        self.ssm[:, slot].copy_(ssm)
+
+    def check(self) -> None:
+        assert len(set(self._free)) == len(self._free)
+        assert sum(self._owned) + len(self._free) == self.slots

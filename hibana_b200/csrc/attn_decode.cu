@@ -1,10 +1,11 @@
 // Flash-decoding for paged GQA attention with up to 16 query rows per (sequence, kv head): decode (one token x
 // GQA group <= 16) and short speculative verify blocks. Bandwidth-bound by design:
 //
-//   * every K / V row (one token, one kv head: D bf16) is fetched by ONE bulk async copy (cp.async.bulk) straight
-//     from its slot in the token-granular pool into a padded shared-memory row, completion tracked by an mbarrier;
+//   * K / V rows (one token, one kv head: D bf16) stream from their slots in the token-granular pool into padded
+//     shared-memory rows with 16-byte cp.async (the TMA unit retires only about one small bulk copy per ~30 cycles,
+//     which capped 256-byte row copies near 16 GB/s per SM; the LSU path has no such limit);
 //   * each of the 4 warps of a CTA owns a private 3-stage ring of KT-key tiles and walks its own share of the keys,
-//     so the main loop has no block-wide barrier: a warp waits only on its own mbarrier;
+//     so the main loop has no block-wide barrier and no flag wait: a warp waits only on its own cp.async groups;
 //   * S = Q K^T and O += P V run on the tensor cores (m16n8k16 bf16, fp32 accumulate) with the query rows padded to
 //     one 16-row tile; the online softmax lives in registers; the 4 warps' partial (m, l, O) merge through shared
 //     memory at the end, and KV splits merge through the LSE kernel of attn.cu.
@@ -58,6 +59,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void cp16(uint32_t saddr, const void* g) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_wait2() { asm volatile("cp.async.wait_group 2;" ::: "memory"); }
+
 template <int D>
 struct DecCfg {
   static constexpr int KT = D >= 256 ? 16 : 32;        // keys per warp tile
@@ -82,8 +89,6 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const De
   const int g4 = lane >> 2, t4 = lane & 3;
   uint8_t* ring = smem + warp * C::WARP_BYTES;
   uint8_t* qs = smem + DEC_WARPS * C::WARP_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(qs + C::Q_BYTES);   // [DEC_WARPS][DEC_STAGES]
-  volatile int* abort = reinterpret_cast<volatile int*>(bars + DEC_WARPS * DEC_STAGES);
 
   const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int g = p.hq / p.hkv;
@@ -96,11 +101,6 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const De
   const int k1 = min(ctx, k0 + per);
   const int ntiles = k1 > k0 ? (k1 - k0 + KT - 1) / KT : 0;
 
-  if (tid == 0) {
-    for (int i = 0; i < DEC_WARPS * DEC_STAGES; ++i) mbar_init(&bars[i], 1);
-    *abort = 0;
-    fence_mbar_init();
-  }
   // Q rows (zero padded to 16) into shared memory.
   for (int i = tid; i < 16 * (D / 8); i += DEC_WARPS * 32) {
     const int qi = i / (D / 8), c = i % (D / 8);
@@ -121,31 +121,39 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const De
   }
 
   const int* idx_row = p.kv_indices + static_cast<long long>(p.seq_rows ? p.seq_rows[b] : b) * p.ld_idx;
-  uint64_t* mybar = bars + warp * DEC_STAGES;
 
-  // Issues the copies of this warp's `it`-th tile into its ring stage; lanes own keys (KT <= 32).
+  // Issues the copies of this warp's `it`-th tile into its ring stage. A warp instruction moves two rows' worth
+  // of 16-byte chunks (D = 128); slot ids of the tile's keys are fetched once per lane and shuffled.
   auto issue = [&](int it) {
     const int tile = warp + it * DEC_WARPS;
-    if (tile >= ntiles) return;
-    const int st = it % DEC_STAGES;
-    const int base = k0 + tile * KT;
-    const int valid = min(KT, k1 - base);
-    uint8_t* kdst = ring + st * C::STAGE_BYTES;
-    uint8_t* vdst = kdst + C::TILE_BYTES;
-    if (lane == 0) mbar_expect_tx(&mybar[st], static_cast<uint32_t>(valid) * 2u * D * 2u);
-    __syncwarp();
-    if (lane < KT) {
-      if (lane < valid) {
-        const long long off = static_cast<long long>(idx_row[base + lane]) * p.pool_stride + static_cast<long long>(kvh) * D;
-        bulk_load(kdst + lane * ROWB, p.k_pool + off, D * 2, &mybar[st]);
-        bulk_load(vdst + lane * ROWB, p.v_pool + off, D * 2, &mybar[st]);
-      } else {
-        for (int c = 0; c < D / 8; ++c) {
-          *reinterpret_cast<uint4*>(kdst + lane * ROWB + c * 16) = make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(vdst + lane * ROWB + c * 16) = make_uint4(0, 0, 0, 0);
+    if (tile < ntiles) {
+      const int st = it % DEC_STAGES;
+      const int base = k0 + tile * KT;
+      const uint32_t kdst = smem_u32(ring + st * C::STAGE_BYTES);
+      const uint32_t vdst = kdst + C::TILE_BYTES;
+      constexpr int CPR = D / 8;            // 16-byte chunks per row
+      constexpr int RPI = 32 / CPR > 0 ? 32 / CPR : 1;   // rows per warp instruction
+      const int my_slot = (lane < KT && base + lane < k1) ? idx_row[base + lane] : -1;
+      if constexpr (CPR <= 32) {
+        const int part = lane % CPR, sub = lane / CPR;
+#pragma unroll
+        for (int r = 0; r < KT; r += RPI) {
+          const int key = r + sub;
+          const int slot = __shfl_sync(0xffffffffu, my_slot, key);
+          const uint32_t so = key * ROWB + part * 16;
+          if (slot >= 0) {
+            const __nv_bfloat16* src = p.k_pool + static_cast<long long>(slot) * p.pool_stride +
+                                       static_cast<long long>(kvh) * D + part * 8;
+            cp16(kdst + so, src);
+            cp16(vdst + so, p.v_pool + (src - p.k_pool));
+          } else {
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(kdst + so), "r"(0) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(vdst + so), "r"(0) : "memory");
+          }
         }
       }
     }
+    cp_commit();
   };
 
   float o[ONB][4];
@@ -158,18 +166,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const De
 
   issue(0);
   issue(1);
-  bool ok = true;
   for (int it = 0; warp + it * DEC_WARPS < ntiles; ++it) {
     // Stage (it + 2) % 3 was read in iteration it - 1: every lane is past it, order it before the async writes.
     __syncwarp();
-    fence_proxy_async_smem();
     issue(it + 2);
-    const int st = it % DEC_STAGES;
-    if (!mbar_wait(&mybar[st], (it / DEC_STAGES) & 1, abort, p.status, kTimeoutFull)) {
-      ok = false;
-      break;
-    }
+    cp_wait2();
     __syncwarp();
+    const int st = it % DEC_STAGES;
     const uint32_t kbase = smem_u32(ring + st * C::STAGE_BYTES);
     const uint32_t vbase = kbase + C::TILE_BYTES;
     const int tile = warp + it * DEC_WARPS;
@@ -248,11 +251,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const De
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-  if (!ok) {
-    // Copies that never landed would write into the ring later; nothing more is issued and the result is dropped.
-    m_lo = m_hi = -INFINITY;
-    l_lo = l_hi = 0.f;
-  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncwarp();
   // ---- merge the 4 warps through each warp's own (now idle) ring
   float* mo = reinterpret_cast<float*>(ring);          // [16][D]

@@ -106,6 +106,10 @@ norm_quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __re
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
   const int groups = k / 16;
+  if (row >= m) {   // padding rows of the last 128-row scale block: zero scales, nothing else
+    for (int g = tid; g < ka * 4; g += THREADS) sf[sf_offset(row, g, ka)] = 0;
+    return;
+  }
   float ss = 0.f;
   for (int g = tid; g < groups; g += THREADS) {
     float v[16];
@@ -243,15 +247,11 @@ int hb_norm_quant_nvfp4(const void* x, void* residual, const void* w, float eps,
     cudaFuncSetAttribute(norm_quant_nvfp4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     attr = true;
   }
-  norm_quant_nvfp4_kernel<T><<<m, T, k * sizeof(float), st>>>(
+  const int rows_pad = ((m + 127) / 128) * 128;
+  norm_quant_nvfp4_kernel<T><<<rows_pad, T, k * sizeof(float), st>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(residual),
       static_cast<const __nv_bfloat16*>(w), eps, gemma, m, k, ka, static_cast<const float*>(gscale),
       static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), static_cast<__nv_bfloat16*>(normed));
-  const int rows_pad = ((m + 127) / 128) * 128;
-  if (rows_pad > m) {
-    const long long n = static_cast<long long>(rows_pad - m) * ka * 4;
-    sf_pad_rows_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(static_cast<uint8_t*>(sf), m, ka);
-  }
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

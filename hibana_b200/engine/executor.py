@@ -14,6 +14,7 @@ import torch
 
 from .. import config as cfgmod
 from ..cache.kv_pool import KvPool
+from ..cache.request_state import StateManager
 from ..target import Target
 from .context import PREFILL
 from .request import Request, SamplingParams, State
@@ -34,8 +35,9 @@ def _sampling_rows(reqs: Sequence[Request]) -> Optional[dict]:
 
 class Executor:
     def __init__(self, model, *, max_batch: int = 64, max_ctx: int = 4096, kv_slots: int = 0,
-                 use_graphs: bool = True, buckets: Optional[Sequence[int]] = None, state_manager=None,
-                 comm=None, kv_dtype: Optional[torch.dtype] = None, attn_splits: int = 0):
+                 use_graphs: bool = True, buckets: Optional[Sequence[int]] = None, radix_cache: bool = True,
+                 state_pool=None, comm=None, kv_dtype: Optional[torch.dtype] = None, attn_splits: int = 0,
+                 decode_reserve: int = 64):
         t: Target = model.target
         self.model, self.target = model, t
         self.device = model.device
@@ -47,8 +49,8 @@ class Executor:
             else KvPool(0, kv_slots, 1, 1, dtype, self.device)
         buckets = buckets or tuple(b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_batch)
         self.runner = ModelRunner(model, self.kv, max_batch=max_batch, max_ctx=max_ctx, buckets=buckets,
-                                  use_graphs=use_graphs, comm=comm, attn_splits=attn_splits)
-        self.state = state_manager
+                                  use_graphs=use_graphs, comm=comm, attn_splits=attn_splits, state_pool=state_pool)
+        self.state = StateManager(self.kv, state_pool, cache=radix_cache, decode_reserve=decode_reserve)
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "prefill_chunks": 0,
                       "cached_tokens": 0}
 
@@ -62,56 +64,40 @@ class Executor:
             raise ValueError("token id out of range")
 
     def can_admit(self, req: Request) -> bool:
-        if self.state is not None:
-            return self.state.can_admit(req)
-        need = len(req.prompt_ids) + min(req.params.max_tokens, 64)
-        return self.kv.free_count >= need and bool(self.runner._free_rows)
+        return bool(self.runner._free_rows) and self.state.can_admit(req)
 
     def admit(self, req: Request) -> None:
         """Takes a block-table row (and, with a cache, the matched prefix) for the request."""
         req.table_row = self.runner.alloc_row()
-        if self.state is not None:
-            try:
-                self.state.admit(req)
-            except Exception:
-                self.runner.free_row(req.table_row)
-                req.table_row = -1
-                raise
-            if req.cached_len:
-                self.runner.set_table(req.table_row, 0, req.kv_slots[:req.cached_len])
-                self.stats["cached_tokens"] += req.cached_len
+        try:
+            self.state.admit(req)
+        except Exception:
+            self.runner.free_row(req.table_row)
+            req.table_row = -1
+            raise
+        if req.cached_len:
+            self.runner.set_table(req.table_row, 0, req.kv_slots[:req.cached_len])
+            self.stats["cached_tokens"] += req.cached_len
         req.prefilled = req.cached_len
         req.state = State.PREFILL
 
     def release(self, req: Request) -> None:
         if req.table_row < 0:
             return
-        if self.state is not None:
-            self.state.release(req)
-        else:
-            self.kv.free(req.kv_slots)
-            req.kv_slots = []
+        self.state.release(req)
         self.runner.free_row(req.table_row)
         req.table_row = -1
 
     def retract(self, req: Request) -> None:
         """Drops physical resources; the emitted history stays and is replayed on re-admission."""
-        if self.state is not None:
-            self.state.retract(req)
-        else:
-            self.kv.free(req.kv_slots)
-            req.kv_slots = []
+        self.state.retract(req)
         self.runner.free_row(req.table_row)
         req.table_row, req.prefilled, req.committed_len, req.cached_len = -1, 0, 0, 0
         req.state = State.WAITING
 
     # ---- steps
     def _alloc(self, req: Request, n: int) -> list[int]:
-        if self.state is not None:
-            return self.state.extend(req, n)
-        slots = self.kv.alloc(n)
-        req.kv_slots.extend(slots)
-        return slots
+        return self.state.extend(req, n)
 
     def prefill_batch(self, chunks: Sequence[tuple[Request, int]]) -> None:
         """Runs `count` more prompt (or replayed) tokens of each request; samples when a prompt completes."""
@@ -137,8 +123,7 @@ class Executor:
             req.prefilled += n
             req.committed_len = req.prefilled
             self.stats["prefill_tokens"] += n
-            if self.state is not None:
-                self.state.after_prefill(req, final=finals[i])
+            self.state.after_prefill(req, final=finals[i])
             if finals[i]:
                 req.state = State.RUNNING
                 if not req.output_ids:      # a replayed request already holds its pending token

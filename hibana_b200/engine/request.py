@@ -62,6 +62,8 @@ class RequestState:
     table_row: int = -1                              # row in the device block table
     committed_len: int = 0                           # tokens whose KV / state are final
     cached_len: int = 0                              # prefix length served from the radix cache at admission
+    shared_len: int = 0                              # kv_slots[:shared_len] belong to the radix tree
+    branch_at: int = 0                               # where the prompt left an existing cached path
     lock: Any = None                                 # radix TreeLock
     cacheable: bool = True
     reserved: int = 0                                # slots reserved for the step in flight

@@ -182,8 +182,7 @@ def rmsnorm_quantize(x: torch.Tensor, weight: torch.Tensor, eps: float, gscale: 
         normed = torch.empty_like(x) if want_normed else None
         nv.check(nv.lib().hb_norm_quant_nvfp4(x.data_ptr(), nv.ptr(residual), weight.data_ptr(), eps, int(gemma), m, k,
                                               sf.shape[1], gscale.data_ptr(), q.data_ptr(), sf.data_ptr(),
-                                              nv.ptr(normed), nv.stream()), "hb_norm_quant_nvfp4",
-                 launches=2 if m % 128 else 1)
+                                              nv.ptr(normed), nv.stream()), "hb_norm_quant_nvfp4")
         return Nvfp4Tensor(q, sf, gscale, m, k), normed
     h = x
     if residual is not None:

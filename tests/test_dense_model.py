@@ -30,6 +30,8 @@ def test_nvfp4_model_runs_cpu():
     ex = Executor(model, max_batch=2, max_ctx=64, use_graphs=False)
     out = ex.generate_batch(_prompts(2, 9, t.vocab), SamplingParams(max_tokens=3))
     assert all(len(r.output_ids) == 3 for r in out)
+    ex.state.check()
+    ex.state.cache.flush()
     assert ex.kv.free_count == ex.kv.slots
 
 
