@@ -102,13 +102,22 @@ class Executor:
     def prefill_batch(self, chunks: Sequence[tuple[Request, int]]) -> None:
         """Runs `count` more prompt (or replayed) tokens of each request; samples when a prompt completes."""
         rows, toks, starts, slot_lists, finals = [], [], [], [], []
+        taken: list[tuple[Request, int]] = []
         for req, count in chunks:
             seq = req.all_ids if req.output_ids else req.prompt_ids
             # After a retraction the emitted history is replayed; the last emitted token stays pending.
             target_len = len(seq) - (1 if req.output_ids else 0)
             count = min(count, target_len - req.prefilled)
             tokens = seq[req.prefilled:req.prefilled + count]
-            slots = self._alloc(req, count)
+            try:
+                slots = self._alloc(req, count)
+            except MemoryError:
+                for r, n in taken:      # all or nothing: a half-allocated step is never run
+                    drop = r.kv_slots[len(r.kv_slots) - n:]
+                    del r.kv_slots[len(r.kv_slots) - n:]
+                    self.kv.free(drop)
+                raise
+            taken.append((req, count))
             rows.append(req.table_row)
             toks.append(tokens)
             starts.append(req.prefilled)
@@ -133,13 +142,13 @@ class Executor:
 
     def decode_step(self, reqs: Sequence[Request]) -> None:
         """One token for every running request (the pending token goes in, the next one comes out)."""
-        slots = [self._alloc(r, 1)[0] for r in reqs]
+        slots = [s[0] for s in self.state.reserve(reqs, 1)]   # all or nothing; MemoryError -> scheduler retracts
         rows = [r.table_row for r in reqs]
         tokens = [r.output_ids[-1] for r in reqs]
         positions = [r.total_len - 1 for r in reqs]
         out = self.runner.decode(rows, tokens, positions, slots, _sampling_rows(reqs))
         for r, tok in zip(reqs, out):
-            r.committed_len = r.total_len
+            self.state.commit(r, 1)
             r.draws += 1
             r.push(tok)
         self.stats["decode_steps"] += 1

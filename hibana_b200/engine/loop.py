@@ -1,0 +1,193 @@
+"""Engine loop: one engine thread owns the scheduler and everything below it; other threads only enqueue.
+
+`submit` returns a `Ticket` whose queue receives `("tokens", [ids])` events and finally `("done", reason)` or
+`("error", message)`. With tensor parallelism rank 0 owns the inbox and broadcasts the commands it applied at
+every publish point, so all ranks step their schedulers identically; a failure fails every ticket and marks the
+engine unhealthy. Reference: hibana/engine/loop.py:47-320.
+"""
+from __future__ import annotations
+
+import itertools
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable, Optional
+
+from .request import Request, SamplingParams
+from .scheduler import QueueFull, Scheduler
+
+
+@dataclass
+class Ticket:
+    tid: int
+    request: Optional[Request] = None
+    events: "queue.Queue" = field(default_factory=queue.Queue)
+    notify: Optional[Callable[[], None]] = None     # e.g. loop.call_soon_threadsafe wakeup for asyncio consumers
+    cursor: int = 0
+    closed: bool = False
+
+    def put(self, item) -> None:
+        self.events.put(item)
+        if self.notify is not None:
+            self.notify()
+
+
+class EngineUnavailable(RuntimeError):
+    pass
+
+
+class EngineLoop:
+    def __init__(self, scheduler: Scheduler, channel=None, rank: int = 0, idle_sleep: float = 0.002):
+        self.sched = scheduler
+        self.channel = channel          # lockstep command channel (None = single rank)
+        self.rank = rank
+        self.idle_sleep = idle_sleep
+        self.inbox: "queue.Queue" = queue.Queue()
+        self.tickets: dict[int, Ticket] = {}
+        self._by_rid: dict[int, Ticket] = {}
+        self._ids = itertools.count(1)
+        self.healthy = True
+        self.failure: Optional[str] = None
+        self.stopping = False
+        self.draining = False
+        self.thread: Optional[threading.Thread] = None
+        self.steps = 0
+        self._applied: list = []
+
+    # ---- any thread
+    def start(self) -> "EngineLoop":
+        self.thread = threading.Thread(target=self._run, name="hibana-engine", daemon=True)
+        self.thread.start()
+        return self
+
+    def submit(self, prompt_ids, params: SamplingParams, *, eos_id=None, media=None, constraint=None,
+               notify=None) -> Ticket:
+        if not self.healthy:
+            raise EngineUnavailable(self.failure or "engine failed")
+        if self.draining or self.stopping:
+            raise EngineUnavailable("engine is shutting down")
+        if self.inbox.qsize() + len(self.sched.waiting) >= self.sched.cfg.max_queue:
+            raise QueueFull("queue full")
+        t = Ticket(next(self._ids), notify=notify)
+        self.tickets[t.tid] = t
+        self.inbox.put(("submit", t.tid, list(prompt_ids), params, eos_id, media, constraint))
+        return t
+
+    def cancel(self, ticket: Ticket) -> None:
+        self.inbox.put(("cancel", ticket.tid))
+
+    def drain(self, timeout: float = 30.0) -> bool:
+        """Stops intake and waits until every admitted request has finished."""
+        self.draining = True
+        end = time.monotonic() + timeout
+        while time.monotonic() < end:
+            if self.sched.idle() and self.inbox.empty():
+                return True
+            time.sleep(0.01)
+        return False
+
+    def stop(self, timeout: float = 10.0) -> None:
+        self.stopping = True
+        self.inbox.put(("stop",))
+        if self.thread is not None:
+            self.thread.join(timeout)
+
+    def stats(self) -> dict:
+        d = self.sched.metrics.as_dict()
+        d.update({"healthy": self.healthy, "queued": len(self.sched.waiting), "active": len(self.sched.active),
+                  "engine_steps": self.steps})
+        ex_state = getattr(self.sched.ex, "state", None)
+        if ex_state is not None:
+            d["cache"] = ex_state.stats()
+        return d
+
+    # ---- engine thread
+    def _apply(self, cmd) -> None:
+        kind = cmd[0]
+        if kind == "submit":
+            _, tid, ids, params, eos_id, media, constraint = cmd
+            ticket = self.tickets.get(tid)
+            req = Request(prompt_ids=ids, params=params, eos_id=eos_id, media=media, constraint=constraint)
+            try:
+                self.sched.submit(req)
+            except (ValueError, QueueFull) as e:
+                if ticket is not None:
+                    ticket.put(("error", str(e)))
+                    ticket.closed = True
+                return
+            if ticket is not None:
+                ticket.request = req
+                self._by_rid[req.rid] = ticket
+        elif kind == "cancel":
+            ticket = self.tickets.get(cmd[1])
+            if ticket is not None and ticket.request is not None:
+                self.sched.cancel(ticket.request)
+        elif kind == "stop":
+            self.stopping = True
+
+    def _gather_commands(self) -> list:
+        cmds = []
+        while True:
+            try:
+                cmds.append(self.inbox.get_nowait())
+            except queue.Empty:
+                break
+        return cmds
+
+    def _publish_commands(self, cmds: list) -> list:
+        """Rank 0 broadcasts what it is about to apply; other ranks receive the same list."""
+        if self.channel is None:
+            return cmds
+        if self.rank == 0:
+            # tickets and notifiers stay local: ship only plain data
+            self.channel.broadcast(cmds)
+            return cmds
+        return self.channel.broadcast(None)
+
+    def _deliver(self, touched) -> None:
+        for req in touched:
+            ticket = self._by_rid.get(req.rid)
+            if ticket is None or ticket.closed:
+                continue
+            new = req.output_ids[ticket.cursor:]
+            if new:
+                ticket.cursor += len(new)
+                ticket.put(("tokens", list(new)))
+            if req.done:
+                ticket.put(("done", req.finish_reason))
+                ticket.closed = True
+                self._by_rid.pop(req.rid, None)
+                self.tickets.pop(ticket.tid, None)
+
+    def _fail(self, message: str) -> None:
+        self.healthy = False
+        self.failure = message
+        for req in self.sched.fail_all(message):
+            ticket = self._by_rid.pop(req.rid, None)
+            if ticket is not None and not ticket.closed:
+                ticket.put(("error", message))
+                ticket.closed = True
+        for ticket in list(self.tickets.values()):
+            if not ticket.closed:
+                ticket.put(("error", message))
+                ticket.closed = True
+        self.tickets.clear()
+
+    def _run(self) -> None:
+        try:
+            while True:
+                cmds = self._publish_commands(self._gather_commands())
+                for c in cmds:
+                    self._apply(c)
+                if self.stopping:
+                    break
+                if self.sched.idle():
+                    if self.channel is None:
+                        time.sleep(self.idle_sleep)
+                    continue
+                touched = self.sched.step()
+                self.steps += 1
+                self._deliver(touched)
+        except Exception as e:  # noqa: BLE001 - every failure takes the engine down cleanly
+            self._fail(f"{type(e).__name__}: {e}")
