@@ -100,7 +100,7 @@ class ModelRunner:
                              attn_workspace=buf.workspace, comm=self.comm,
                              state_slots=v["row"])
         h = self.model.forward(v["ids"].long(), ctx, self.kv)
-        logits = self.model.logits(h)
+        logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
         tok = sampling.sample(logits, v["temp"], v["top_k"], v["top_p"], v["seed"], v["offs"])
         buf.out.copy_(tok)
 
@@ -222,7 +222,7 @@ class ModelRunner:
         h = self.model.forward(ids_d, ctx, self.kv)
         if want == "none":
             return None
-        logits = self.model.logits(h)
+        logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
         if sampling_rows is None or want == "all":
             tok = sampling.argmax(logits)
         else:

@@ -20,7 +20,11 @@ from .linear import Linear, interleave_pairs, norm_linear
 
 
 class DenseLayer:
-    def __init__(self, t: Target, idx: int, gen: torch.Generator, device, std: float = 0.02):
+    def __init__(self, t: Target, idx: int, gen: torch.Generator, device, std: float = 0.02, tp: int = 1,
+                 rank: int = 0):
+        """`t` is the unsharded target; with tp > 1 the full matrices are generated (same seed on every rank) and
+        this rank's shard is cut out: q/k/v by head and gate/up by column (column-parallel), o_proj and down by
+        input feature (row-parallel)."""
         h, d = t.hidden, t.head_dim
         fmt = "nvfp4" if t.weight_format == "nvfp4" else "bf16"
 
@@ -30,35 +34,67 @@ class DenseLayer:
         self.idx = idx
         self.input_norm = torch.ones(h, dtype=torch.bfloat16, device=device)
         self.post_norm = torch.ones(h, dtype=torch.bfloat16, device=device)
-        self.qkv = Linear(rnd((t.q_heads + 2 * t.kv_heads) * d, h), fmt, name=f"l{idx}.qkv").to(device)
-        self.o = Linear(rnd(h, t.q_heads * d), fmt, name=f"l{idx}.o").to(device)
-        self.gate_up = Linear(interleave_pairs(rnd(t.ffn, h), rnd(t.ffn, h)), fmt, name=f"l{idx}.gate_up").to(device)
-        self.down = Linear(rnd(h, t.ffn), fmt, name=f"l{idx}.down").to(device)
+        wqkv, wo = rnd((t.q_heads + 2 * t.kv_heads) * d, h), rnd(h, t.q_heads * d)
+        wgu, wd = interleave_pairs(rnd(t.ffn, h), rnd(t.ffn, h)), rnd(h, t.ffn)
+        if tp == 1:
+            self.qkv = Linear(wqkv, fmt, name=f"l{idx}.qkv").to(device)
+            self.o = Linear(wo, fmt, name=f"l{idx}.o").to(device)
+            self.gate_up = Linear(wgu, fmt, name=f"l{idx}.gate_up").to(device)
+            self.down = Linear(wd, fmt, name=f"l{idx}.down").to(device)
+            return
+        hq, hkv = t.q_heads // tp, max(t.kv_heads // tp, 1)
+        kv0 = (rank * t.kv_heads) // tp            # kv heads replicate when there are fewer than ranks
+        qrows = torch.arange(rank * hq * d, (rank + 1) * hq * d)
+        krows = t.q_heads * d + torch.arange(kv0 * d, (kv0 + hkv) * d)
+        vrows = (t.q_heads + t.kv_heads) * d + torch.arange(kv0 * d, (kv0 + hkv) * d)
+        f = t.ffn // tp
+        # index tensors select rows; the quantised full matrix is sliced so shards are bitwise slices
+        sel = torch.cat((qrows, krows, vrows)).to(wqkv.device)
+        self.qkv = _shard(wqkv, fmt, rows=sel, name=f"l{idx}.qkv").to(device)
+        self.o = _shard(wo, fmt, cols=slice(rank * hq * d, (rank + 1) * hq * d), name=f"l{idx}.o").to(device)
+        self.gate_up = _shard(wgu, fmt, rows=slice(2 * rank * f, 2 * (rank + 1) * f), name=f"l{idx}.gate_up").to(device)
+        self.down = _shard(wd, fmt, cols=slice(rank * f, (rank + 1) * f), name=f"l{idx}.down").to(device)
 
     def linears(self):
         return [self.qkv, self.o, self.gate_up, self.down]
 
 
-class DenseModel:
-    """Random-init (N(0, 0.02), seeded) dense decoder. `forward` returns the final hidden rows to sample from."""
+def _shard(w, fmt, rows=None, cols=None, name=""):
+    return Linear.sharded(w, fmt, rows=rows, cols=cols, name=name)
 
-    def __init__(self, t: Target, device="cpu", seed: int = 0, init_device=None):
+
+class DenseModel:
+    """Random-init (N(0, 0.02), seeded) dense decoder. `forward` returns the final hidden rows to sample from.
+
+    `target` is this rank's (sharded) geometry; `full` the unsharded one the weights are generated from."""
+
+    def __init__(self, t: Target, device="cpu", seed: int = 0, init_device=None, *, full: Optional[Target] = None):
         self.target = t
+        full = full or t
+        tp, rank = t.tp_size, t.tp_rank
         self.device = torch.device(device)
         init_device = self.device if init_device is None else torch.device(init_device)
         gen = torch.Generator(device=init_device)
         gen.manual_seed(seed)
-        self.embed = (torch.randn(t.vocab, t.hidden, generator=gen, dtype=torch.float32, device=init_device)
+        self.embed = (torch.randn(full.vocab, full.hidden, generator=gen, dtype=torch.float32, device=init_device)
                       * 0.02).to(torch.bfloat16).to(self.device)
-        self.layers = [DenseLayer(t, i, gen, self.device) for i in range(len(t.layers))]
-        self.final_norm = torch.ones(t.hidden, dtype=torch.bfloat16, device=self.device)
-        self.lm_head = self.embed if t.tie_embeddings else (
-            torch.randn(t.vocab, t.hidden, generator=gen, dtype=torch.float32, device=init_device) * 0.02
+        self.layers = [DenseLayer(full, i, gen, self.device, tp=tp, rank=rank) for i in range(len(full.layers))]
+        self.final_norm = torch.ones(full.hidden, dtype=torch.bfloat16, device=self.device)
+        head = self.embed if full.tie_embeddings else (
+            torch.randn(full.vocab, full.hidden, generator=gen, dtype=torch.float32, device=init_device) * 0.02
         ).to(torch.bfloat16).to(self.device)
+        self.vocab_shard = full.vocab // tp if tp > 1 and full.vocab % tp == 0 else 0
+        # vocab-parallel head: each rank scores vocab/tp tokens (reference: hibana/model/qwen38.py:181-182)
+        self.lm_head = head[rank * self.vocab_shard:(rank + 1) * self.vocab_shard].contiguous() \
+            if self.vocab_shard else head
         self.inv_freq = basic.rope_inv_freq(t.rot_dim, t.rope_theta, device=self.device) if t.rot_dim else \
             torch.zeros(1, device=self.device)
         self.scale = 1.0 / math.sqrt(t.head_dim)
         self.kv_layers = len(self.layers)
+
+    @classmethod
+    def sharded(cls, full: Target, tp: int, rank: int, device, seed: int = 0, init_device=None) -> "DenseModel":
+        return cls(full.shard(tp, rank), device, seed, init_device, full=full)
 
     # ---- bookkeeping
     def linears(self):
@@ -70,9 +106,9 @@ class DenseModel:
             n += self.lm_head.numel() * 2
         return n
 
-    def calibrate(self, run_forward) -> None:
+    def calibrate(self, run_forward, comm=None) -> None:
         """Sets the static NVFP4 activation scales from one forward over sample tokens (random-init stand-in
-        for the `input_scale` tensors a ModelOpt checkpoint ships)."""
+        for the `input_scale` tensors a ModelOpt checkpoint ships). Ranks agree on the maximum."""
         lins = [lin for lin in self.linears() if lin.fmt == "nvfp4"]
         for lin in lins:
             lin.calibrating, lin.seen_amax = True, 0.0
@@ -82,35 +118,71 @@ class DenseModel:
             for lin in lins:
                 lin.calibrating = False
         for lin in lins:
-            lin.set_input_amax(max(lin.seen_amax, 1e-3) * 1.5)
+            amax = max(lin.seen_amax, 1e-3)
+            if comm is not None:
+                amax = comm.max_float(amax)
+            lin.set_input_amax(amax * 1.5)
 
     # ---- forward
+    def _reduce_norm_linear(self, h, slot, res, norm_w, lin, ctx, epilogue=gemm.EPI_STORE):
+        """lin(rmsnorm(allreduce(h) + res)). `h` is this rank's partial; with the fused path it already sits in
+        heap slot `slot` and one kernel does all-reduce + add + norm + quant."""
+        t = self.target
+        comm = ctx.comm
+        if comm is not None and slot is not None and not lin.calibrating:
+            rows = h.shape[0]
+            qs = lin.input_scale if lin.fmt == "nvfp4" else None
+            y, xq = comm.allreduce_norm(slot, rows, t.hidden, residual=res, weight=norm_w, eps=t.norm_eps,
+                                        quant_scale=qs, want_bf16=qs is None)
+            return lin(xq if xq is not None else y, epilogue=epilogue)
+        if comm is not None:
+            h = comm.all_reduce(h)
+        return norm_linear(h, res, norm_w, t.norm_eps, lin, epilogue=epilogue)
+
+    def _row_parallel(self, lin, x, ctx):
+        """Row-parallel projection; returns (partial, heap slot or None)."""
+        comm = ctx.comm
+        if comm is not None and comm.fits(x.shape[0] if not hasattr(x, "rows") else x.rows, self.target.hidden):
+            slot = comm.next_slot()
+            rows = x.shape[0] if not hasattr(x, "rows") else x.rows
+            return lin(x, out=comm.slot_buffer(slot, rows, self.target.hidden)), slot
+        return lin(x), None
+
     def forward(self, ids: torch.Tensor, ctx: ForwardContext, kv) -> torch.Tensor:
         """ids int64 [T]; kv = KvPool. Returns normed hidden states of ctx.sample_rows (or of all rows)."""
         t = self.target
         res = basic.embedding(ids, self.embed)
         h: Optional[torch.Tensor] = None
+        slot = None
         for i, layer in enumerate(self.layers):
             if h is None:
                 qkv = norm_linear(res, None, layer.input_norm, t.norm_eps, layer.qkv, add_residual=False)
             else:
-                qkv = norm_linear(h, res, layer.input_norm, t.norm_eps, layer.qkv)
+                qkv = self._reduce_norm_linear(h, slot, res, layer.input_norm, layer.qkv, ctx)
             q = basic.rope_kv_write(qkv, ctx.positions, ctx.slots, self.inv_freq, kv.k[i], kv.v[i], t.q_heads,
                                     t.kv_heads, t.head_dim, rot=t.rot_dim, kv_scale=kv.kv_scale)
             att = attention.paged_attention(q, kv.k[i], kv.v[i], ctx.kv_indices, ctx.ctx_len, q_indptr=ctx.q_indptr,
-                                            max_rows=ctx.max_rows, seq_rows=ctx.seq_rows, scale=self.scale, kv_scale=kv.kv_scale,
-                                            splits=ctx.attn_splits, workspace=ctx.attn_workspace)
-            h = layer.o(att.view(att.shape[0], -1))
-            if ctx.comm is not None:
-                h = ctx.comm.all_reduce(h)
-            act = norm_linear(h, res, layer.post_norm, t.norm_eps, layer.gate_up, epilogue=gemm.EPI_SILU_MUL)
-            h = layer.down(act)
-            if ctx.comm is not None:
-                h = ctx.comm.all_reduce(h)
+                                            max_rows=ctx.max_rows, seq_rows=ctx.seq_rows, scale=self.scale,
+                                            kv_scale=kv.kv_scale, splits=ctx.attn_splits,
+                                            workspace=ctx.attn_workspace)
+            h, slot = self._row_parallel(layer.o, att.view(att.shape[0], -1), ctx)
+            act = self._reduce_norm_linear(h, slot, res, layer.post_norm, layer.gate_up, ctx,
+                                           epilogue=gemm.EPI_SILU_MUL)
+            h, slot = self._row_parallel(layer.down, act, ctx)
+        comm = ctx.comm
+        if comm is not None and slot is not None:
+            y, _ = comm.allreduce_norm(slot, h.shape[0], t.hidden, residual=res, weight=self.final_norm,
+                                       eps=t.norm_eps)
+            return y.index_select(0, ctx.sample_rows) if ctx.sample_rows is not None else y
         if ctx.sample_rows is not None:
             h = h.index_select(0, ctx.sample_rows)
             res = res.index_select(0, ctx.sample_rows)
+        if comm is not None:
+            h = comm.all_reduce(h)
         return basic.rmsnorm(h, self.final_norm, t.norm_eps, residual=res)
 
-    def logits(self, normed: torch.Tensor) -> torch.Tensor:
-        return gemm.linear_bf16(normed, self.lm_head, epilogue=gemm.EPI_STORE_F32)
+    def logits(self, normed: torch.Tensor, comm=None) -> torch.Tensor:
+        lg = gemm.linear_bf16(normed, self.lm_head, epilogue=gemm.EPI_STORE_F32)
+        if self.vocab_shard and comm is not None:
+            lg = comm.all_gather_last(lg)
+        return lg

@@ -42,6 +42,28 @@ class Linear:
             raise ValueError(f"unknown linear format {fmt!r}")
 
     @classmethod
+    def sharded(cls, weight: torch.Tensor, fmt: str, rows: Optional[slice] = None, cols: Optional[slice] = None,
+                name: str = "") -> "Linear":
+        """A tensor-parallel shard that is bitwise a slice of the unsharded layer: the full matrix is quantised
+        with its own per-tensor scale and then rows (output features) and / or columns (input features, on
+        16-element block boundaries) are cut out. Reference: hibana/weights/sharding.py:15-19,
+        hibana/model/flashnext/linear.py:31-43."""
+        rows = slice(None) if rows is None else rows
+        cols = slice(None) if cols is None else cols
+        if fmt != "nvfp4":
+            return cls(weight[rows][:, cols], fmt, name=name)
+        full = nvfp4.quantize_weight(weight)
+        sfb = nvfp4.unswizzle_sf(full.sf, full.rows, full.k // 16)
+        c0 = cols.start or 0
+        c1 = cols.stop if cols.stop is not None else full.k
+        assert c0 % 16 == 0 and c1 % 16 == 0
+        q = full.q[rows][:, c0 // 2:c1 // 2].contiguous()
+        sf = nvfp4.swizzle_sf(sfb[rows][:, c0 // 16:c1 // 16].contiguous())
+        wq = Nvfp4Tensor(q, sf, full.gscale, q.shape[0], c1 - c0)
+        self = cls.from_nvfp4(wq, torch.tensor([8.0 / (6.0 * 448.0)], device=q.device), name=name)
+        return self
+
+    @classmethod
     def from_nvfp4(cls, wq: Nvfp4Tensor, input_scale: torch.Tensor, name: str = "") -> "Linear":
         """Wraps tensors loaded from a checkpoint (packed values, swizzled scales, weight_scale_2, input_scale)."""
         self = cls.__new__(cls)

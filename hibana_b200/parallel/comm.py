@@ -1,0 +1,224 @@
+"""Communicator of one NVSwitch box: symmetric peer-mapped heap + fused collectives, NCCL as bootstrap/baseline.
+
+One process per GPU. `Communicator.create` cudaMallocs this rank's heap, exchanges CUDA IPC handles over the
+`torch.distributed` process group and maps every peer heap, after which the fused kernels in csrc/comm.cu reach
+peer memory directly over NVLink. `all_reduce` (NCCL) is the baseline path; `slot_buffer` + `allreduce_norm` is
+the fused path (the row-parallel GEMM writes its partial into a heap slot, then one kernel does all-reduce +
+residual + RMSNorm (+ NVFP4 quantisation)). A CPU `FakeCommunicator` runs the same interface over gloo / in
+process for tests. Reference: hibana/distributed.py:53-183.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native as nv
+from ..ops import basic, nvfp4
+from ..ops.nvfp4 import Nvfp4Tensor
+
+P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
+nv.register("hb_comm_ctrl_bytes", [])
+nv.register("hb_comm_nslot", [])
+nv.register("hb_comm_alloc", [L, ctypes.POINTER(ctypes.c_void_p)])
+nv.register("hb_comm_free", [P])
+nv.register("hb_comm_ipc_handle", [P, P])
+nv.register("hb_comm_ipc_open", [P, ctypes.POINTER(ctypes.c_void_p)])
+nv.register("hb_comm_ipc_close", [P])
+nv.register("hb_ar_norm", [P, I, I, I, L, I, I, P, P, Fl, I, P, P, P, P, I, L, P, P])
+nv.register("hb_barrier", [P, I, I, I, L, P, P])
+
+
+class _RawCuda:
+    """Exposes a raw device pointer to torch through __cuda_array_interface__ (zero copy)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+class CommTimeout(RuntimeError):
+    pass
+
+
+class Communicator:
+    def __init__(self, rank: int, world: int, device: torch.device, heap_ptr: int, heap_bytes: int, peer_ptrs: list,
+                 slot_bytes: int, timeout_ms: int, group=None, fused: bool = True):
+        self.rank, self.world, self.device = rank, world, device
+        self.heap_ptr, self.heap_bytes, self.peer_ptrs = heap_ptr, heap_bytes, peer_ptrs
+        self.slot_bytes = slot_bytes
+        self.timeout_ns = int(timeout_ms) * 1_000_000
+        self.group = group
+        self.fused = fused
+        self.nslot = nv.lib().hb_comm_nslot()
+        self.ctrl_bytes = nv.lib().hb_comm_ctrl_bytes()
+        self._bases = (ctypes.c_void_p * world)(*peer_ptrs)
+        self.heap = torch.as_tensor(_RawCuda(heap_ptr, heap_bytes), device=device)
+        self._next_slot = 0
+        self.status = nv.device_state(device).status
+
+    @classmethod
+    def create(cls, rank: int, world: int, device: torch.device, *, slot_mb: int = 8, timeout_ms: int = 2000,
+               group=None, fused: bool = True) -> "Communicator":
+        """Collective: every rank of `group` (default: the world group) must call it."""
+        lib = nv.lib()
+        torch.cuda.set_device(device)
+        slot_bytes = slot_mb << 20
+        heap_bytes = lib.hb_comm_ctrl_bytes() + lib.hb_comm_nslot() * slot_bytes
+        out = ctypes.c_void_p()
+        nv.check(lib.hb_comm_alloc(heap_bytes, ctypes.byref(out)), "hb_comm_alloc", launches=0)
+        handle = ctypes.create_string_buffer(64)
+        nv.check(lib.hb_comm_ipc_handle(out, handle), "hb_comm_ipc_handle", launches=0)
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        peers = []
+        for r in range(world):
+            if r == rank:
+                peers.append(out.value)
+            else:
+                p = ctypes.c_void_p()
+                nv.check(lib.hb_comm_ipc_open(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(p)),
+                         "hb_comm_ipc_open", launches=0)
+                peers.append(p.value)
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        return cls(rank, world, device, out.value, heap_bytes, peers, slot_bytes, timeout_ms, group, fused)
+
+    # ---- slots
+    def slot_offset(self, slot: int) -> int:
+        return self.ctrl_bytes + slot * self.slot_bytes
+
+    def next_slot(self) -> int:
+        """Round-robin slot for the next collective call site (the same order on every rank)."""
+        s = self._next_slot
+        self._next_slot = (s + 1) % self.nslot
+        return s
+
+    def slot_buffer(self, slot: int, rows: int, cols: int, dtype=torch.bfloat16) -> torch.Tensor:
+        """A [rows, cols] tensor inside this rank's heap slot (what the producing GEMM writes into)."""
+        nbytes = rows * cols * torch.tensor([], dtype=dtype).element_size()
+        if nbytes > self.slot_bytes:
+            raise ValueError(f"message of {nbytes} bytes exceeds the {self.slot_bytes}-byte heap slot")
+        off = self.slot_offset(slot)
+        return self.heap[off:off + nbytes].view(dtype).view(rows, cols)
+
+    def fits(self, rows: int, cols: int) -> bool:
+        return self.fused and rows * cols * 2 <= self.slot_bytes
+
+    # ---- collectives
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """NCCL all-reduce (sum), in place: the baseline path."""
+        dist.all_reduce(x, group=self.group)
+        return x
+
+    def all_gather_last(self, x: torch.Tensor) -> torch.Tensor:
+        """Gathers shards along the last dim (vocab-parallel logits)."""
+        parts = [torch.empty_like(x) for _ in range(self.world)]
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+    def allreduce_norm(self, slot: int, rows: int, h: int, *, residual: Optional[torch.Tensor],
+                       weight: Optional[torch.Tensor], eps: float = 1e-6, gemma: bool = False,
+                       quant_scale: Optional[torch.Tensor] = None, want_bf16: bool = True):
+        """Fused one-shot all-reduce of the partial in `slot` + residual add + RMSNorm (+ NVFP4 quant).
+
+        Returns (bf16 output or None, Nvfp4Tensor or None). `residual` is updated in place with sum + residual.
+        """
+        out = torch.empty(rows, h, dtype=torch.bfloat16, device=self.device) if want_bf16 else None
+        q = sf = None
+        ka = 0
+        if quant_scale is not None:
+            q, sf = nvfp4._alloc(rows, h, self.device)
+            ka = sf.shape[1]
+        nv.check(nv.lib().hb_ar_norm(self._bases, self.world, self.rank, slot, self.slot_offset(slot), rows, h,
+                                     nv.ptr(residual), nv.ptr(weight), eps, int(gemma), nv.ptr(out), nv.ptr(q),
+                                     nv.ptr(sf), nv.ptr(quant_scale), ka, self.timeout_ns, self.status.data_ptr(),
+                                     nv.stream()), "hb_ar_norm")
+        xq = Nvfp4Tensor(q, sf, quant_scale, rows, h) if q is not None else None
+        return out, xq
+
+    def barrier(self, slot: Optional[int] = None) -> None:
+        slot = self.next_slot() if slot is None else slot
+        nv.check(nv.lib().hb_barrier(self._bases, self.world, self.rank, slot, self.timeout_ns,
+                                     self.status.data_ptr(), nv.stream()), "hb_barrier")
+
+    def check_status(self) -> None:
+        """Host check at a publish point: raises CommTimeout when a bounded device wait gave up."""
+        code = nv.read_status(self.device)
+        if code:
+            raise CommTimeout(f"device-side wait ran out (status {code})")
+
+    # ---- host scalars (control plane)
+    def min_int(self, v: int) -> int:
+        t = torch.tensor([v], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+        return int(t.item())
+
+    def max_float(self, v: float) -> float:
+        t = torch.tensor([v], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return float(t.item())
+
+    def broadcast(self, obj=None, src: int = 0):
+        box = [obj]
+        dist.broadcast_object_list(box, src=src, group=self.group)
+        return box[0]
+
+
+class FakeCommunicator:
+    """Single-process stand-in with the Communicator interface over CPU tensors: holds every rank's partial so
+    tests can play all ranks of a tensor-parallel model in one process (no GPU, no process group)."""
+
+    def __init__(self, world: int):
+        self.world, self.rank, self.fused = world, 0, False
+        self.pending: list = []
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+    def fits(self, rows: int, cols: int) -> bool:
+        return False
+
+    def check_status(self) -> None:
+        return None
+
+
+class GlooCommunicator:
+    """CPU ranks over a gloo process group: the host-side logic of tensor parallelism without a GPU."""
+
+    def __init__(self, rank: int, world: int, group=None):
+        self.rank, self.world, self.group, self.fused = rank, world, group, False
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        y = x.float()
+        dist.all_reduce(y, group=self.group)
+        x.copy_(y.to(x.dtype))
+        return x
+
+    def all_gather_last(self, x: torch.Tensor) -> torch.Tensor:
+        parts = [torch.empty_like(x) for _ in range(self.world)]
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+    def fits(self, rows: int, cols: int) -> bool:
+        return False
+
+    def min_int(self, v: int) -> int:
+        t = torch.tensor([v], dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+        return int(t.item())
+
+    def max_float(self, v: float) -> float:
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return float(t.item())
+
+    def broadcast(self, obj=None, src: int = 0):
+        box = [obj]
+        dist.broadcast_object_list(box, src=src, group=self.group)
+        return box[0]
+
+    def check_status(self) -> None:
+        return None
