@@ -95,7 +95,7 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         from hibana_b200.parallel.comm import Communicator
-        comm = Communicator.create(rank, world, dev)
+        comm = Communicator.create(rank, world, dev, slot_mb=4)
     warmup = max(args.warmup, 3)
     steps = args.steps
 
@@ -119,7 +119,7 @@ def main() -> None:
         ex.admit(r)
         ex.prefill_batch([(r, 256)])
         ex.release(r)
-    model.calibrate(calib)
+    model.calibrate(calib, comm)
 
     def sync_all():
         if world > 1:
@@ -221,7 +221,9 @@ def main() -> None:
         print(json.dumps(res))
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)   # NCCL teardown with peer-mapped heaps alive can hang; the measurement is already printed
 
 
 if __name__ == "__main__":
