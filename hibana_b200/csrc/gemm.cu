@@ -61,6 +61,10 @@ struct DevParams {
   int* status;
   int ka_a, ka_b;
   int out_rows, out_cols;
+  // grouped (MoE) mode: grid.z = expert, grid.y = chunk of BN tokens of that expert's segment
+  const int* grp_start;   // [E] first row of the expert's segment in the sorted activation buffer (multiple of 128)
+  const int* grp_cnt;     // [E] rows routed to the expert
+  int grp_rows_a;         // weight rows per expert (multiple of 128)
 };
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
@@ -68,9 +72,9 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); 
 // Applies the epilogue to CH accumulator values of one thread: `row` indexes the A operand, columns
 // [col0, col0 + CH) the B operand.
 template <int CH>
-__device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH], int row, int col0, float alpha,
-                                               int lane) {
-  const bool row_ok = row < p.ra;
+__device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH], int row, int row_lim, int col0,
+                                               int col_lim, float alpha, int lane) {
+  const bool row_ok = row < row_lim;
   if (p.swap) {
     // out[token = col][feature = row]; lanes are consecutive features -> coalesced per token.
     if (p.epilogue == kEpiSiluMul) {
@@ -80,7 +84,7 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
         const float x = v[j] * alpha;
         const float other = __shfl_xor_sync(0xffffffffu, x, 1);
         const int col = col0 + j;
-        if (row_ok && col < p.rb && (lane & 1) == 0)
+        if (row_ok && col < col_lim && (lane & 1) == 0)
           out[static_cast<long long>(col) * p.ldo + (row >> 1)] = __float2bfloat16(silu(x) * other);
       }
     } else if (p.epilogue == kEpiStoreF32) {
@@ -88,14 +92,14 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
 #pragma unroll
       for (int j = 0; j < CH; ++j) {
         const int col = col0 + j;
-        if (row_ok && col < p.rb) out[static_cast<long long>(col) * p.ldo + row] = v[j] * alpha;
+        if (row_ok && col < col_lim) out[static_cast<long long>(col) * p.ldo + row] = v[j] * alpha;
       }
     } else {
       __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
 #pragma unroll
       for (int j = 0; j < CH; ++j) {
         const int col = col0 + j;
-        if (row_ok && col < p.rb) {
+        if (row_ok && col < col_lim) {
           const long long o = static_cast<long long>(col) * p.ldo + row;
           float x = v[j] * alpha;
           if (p.epilogue == kEpiResidual) x += __bfloat162float(p.residual[o]);
@@ -110,7 +114,7 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
   const long long base = static_cast<long long>(row) * p.ldo;
   if (p.epilogue == kEpiSiluMul) {
     __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + base + (col0 >> 1);
-    const bool full = (col0 + CH <= p.rb) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+    const bool full = (col0 + CH <= col_lim) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
     if (full) {
       uint32_t w[CH / 4];
 #pragma unroll
@@ -123,18 +127,18 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
     } else {
 #pragma unroll
       for (int j = 0; j < CH / 2; ++j)
-        if (col0 + 2 * j + 1 < p.rb)
+        if (col0 + 2 * j + 1 < col_lim)
           out[j] = __float2bfloat16(silu(v[2 * j] * alpha) * (v[2 * j + 1] * alpha));
     }
   } else if (p.epilogue == kEpiStoreF32) {
     float* out = static_cast<float*>(p.out) + base + col0;
 #pragma unroll
     for (int j = 0; j < CH; ++j)
-      if (col0 + j < p.rb) out[j] = v[j] * alpha;
+      if (col0 + j < col_lim) out[j] = v[j] * alpha;
   } else {
     __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + base + col0;
     const __nv_bfloat16* res = p.epilogue == kEpiResidual ? p.residual + base + col0 : nullptr;
-    const bool full = (col0 + CH <= p.rb) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+    const bool full = (col0 + CH <= col_lim) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
                       (res == nullptr || (reinterpret_cast<uintptr_t>(res) & 15) == 0);
     if (full) {
 #pragma unroll
@@ -153,7 +157,7 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
     } else {
 #pragma unroll
       for (int j = 0; j < CH; ++j)
-        if (col0 + j < p.rb) {
+        if (col0 + j < col_lim) {
           float x = v[j] * alpha;
           if (res != nullptr) x += __bfloat162float(res[j]);
           out[j] = __float2bfloat16(x);
@@ -179,7 +183,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+  const int tile_a = blockIdx.x;
+  int tile_b = blockIdx.y, split = blockIdx.z;
+  int a_row0 = tile_a * BM, b_row0 = tile_b * BN, row_lim = p.ra, col_lim = p.rb;
+  const float* alpha_ptr = p.alpha_ptr;
+  if (p.grp_cnt != nullptr) {
+    const int e = blockIdx.z, cnt = p.grp_cnt[e];
+    if (static_cast<int>(blockIdx.y) * BN >= cnt) return;   // uniform: before any barrier or TMEM allocation
+    a_row0 = e * p.grp_rows_a + tile_a * BM;
+    b_row0 = p.grp_start[e] + blockIdx.y * BN;
+    row_lim = p.grp_rows_a;
+    col_lim = b_row0 + min(BN, cnt - static_cast<int>(blockIdx.y) * BN);
+    if (alpha_ptr != nullptr) alpha_ptr += e;
+    split = 0;
+    tile_b = 0;
+  }
   const int kt_per = (p.k_tiles + p.splits - 1) / p.splits;
   const int kt0 = split * kt_per;
   const int kt1 = min(kt0 + kt_per, p.k_tiles);
@@ -217,15 +235,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         mbar_expect_tx(&full[s], C::STAGE_BYTES);
         const int kt = kt0 + i;
         const int kx = KIND == kGemmNvfp4 ? kt * 128 : kt * 64;
-        tma_load_2d(st, &tma, &full[s], kx, tile_a * BM);
-        tma_load_2d(st + A_TILE_BYTES, &tmb, &full[s], kx, tile_b * BN);
+        tma_load_2d(st, &tma, &full[s], kx, a_row0);
+        tma_load_2d(st + A_TILE_BYTES, &tmb, &full[s], kx, b_row0);
         if constexpr (KIND == kGemmNvfp4) {
           uint8_t* sf = st + A_TILE_BYTES + C::B_TILE_BYTES;
-          bulk_load(sf, p.sfa + (static_cast<size_t>(tile_a) * p.ka_a + kt * 4) * 512, 2048, &full[s]);
+          bulk_load(sf, p.sfa + (static_cast<size_t>(a_row0 >> 7) * p.ka_a + kt * 4) * 512, 2048, &full[s]);
 #pragma unroll
           for (int rb = 0; rb < C::NRB; ++rb)
             bulk_load(sf + C::SFA_BYTES + rb * 2048,
-                      p.sfb + (static_cast<size_t>(tile_b * C::NRB + rb) * p.ka_b + kt * 4) * 512, 2048, &full[s]);
+                      p.sfb + (static_cast<size_t>((b_row0 >> 7) + rb) * p.ka_b + kt * 4) * 512, 2048, &full[s]);
         }
         ++issued;
       }
@@ -280,10 +298,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const bool ok = nkt > 0 ? mbar_wait(accum, 0, abort, p.status, kTimeoutAccum) : true;
     tc_fence_after();
-    const int row = tile_a * BM + q * 32 + lane;
+    const int row = tile_a * BM + q * 32 + lane;   // feature index (within the expert in grouped mode)
     const uint32_t tlane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     float alpha = p.alpha;
-    if (p.alpha_ptr != nullptr) alpha *= *p.alpha_ptr;
+    if (alpha_ptr != nullptr) alpha *= *alpha_ptr;
     if (ok && p.splits == 1) {
       for (int c0 = 0; c0 < BN; c0 += CH) {
         uint32_t r[CH];
@@ -293,7 +311,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         float v[CH];
 #pragma unroll
         for (int j = 0; j < CH; ++j) v[j] = nkt > 0 ? __uint_as_float(r[j]) : 0.f;
-        epilogue_chunk<CH>(p, v, row, tile_b * BN + c0, alpha, lane);
+        epilogue_chunk<CH>(p, v, row, row_lim, b_row0 + c0, col_lim, alpha, lane);
       }
     } else if (ok) {
       // Split-K: park the raw partial, then the last CTA of this tile reduces all partials in split order.
@@ -307,7 +325,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
           const int col = tile_b * BN + c0 + j;
-          if (row < p.ra && col < p.rb) {
+          if (row < p.ra && col < col_lim) {
             const size_t o = p.swap ? static_cast<size_t>(col) * p.out_cols + row
                                     : static_cast<size_t>(row) * p.out_cols + col;
             __stcg(ws + o, nkt > 0 ? __uint_as_float(r[j]) : 0.f);
@@ -336,14 +354,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
               const int col = tile_b * BN + c0 + j;
-              if (row < p.ra && col < p.rb) {
+              if (row < p.ra && col < col_lim) {
                 const size_t o = p.swap ? static_cast<size_t>(col) * p.out_cols + row
                                         : static_cast<size_t>(row) * p.out_cols + col;
                 v[j] += __ldcg(w + o);
               }
             }
           }
-          epilogue_chunk<CH>(p, v, row, tile_b * BN + c0, alpha, lane);
+          epilogue_chunk<CH>(p, v, row, row_lim, b_row0 + c0, col_lim, alpha, lane);
         }
       }
     }
@@ -446,9 +464,13 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   const int k_tiles = (a.k + kt_elems - 1) / kt_elems;
   const int tiles_a = (a.ra + BM - 1) / BM;
   const int tiles_b = (a.rb + a.bn - 1) / a.bn;
-  if (fp4 && a.bn < 128 && tiles_b != 1) return cudaErrorInvalidValue;
+  const bool grouped = a.grp_cnt != nullptr;
+  if (grouped && (!a.swap || a.grp_rows_a % BM != 0 || a.grp_experts < 1 || a.grp_chunks < 1))
+    return cudaErrorInvalidValue;
+  if (fp4 && a.bn < 128 && tiles_b != 1 && !grouped) return cudaErrorInvalidValue;
+  if (fp4 && grouped && a.bn < 128 && a.grp_chunks != 1) return cudaErrorInvalidValue;
   if (fp4 && (a.sf_k_atoms_a < k_tiles * 4 || a.sf_k_atoms_b < k_tiles * 4)) return cudaErrorInvalidValue;
-  int splits = a.splits < 1 ? 1 : a.splits;
+  int splits = a.splits < 1 || grouped ? 1 : a.splits;
   if (splits > k_tiles) splits = k_tiles;
   // Every split must own at least one K tile.
   while (splits > 1 && (splits - 1) * ((k_tiles + splits - 1) / splits) >= k_tiles) --splits;
@@ -475,7 +497,8 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   p.workspace = a.workspace; p.counters = a.counters; p.status = a.status;
   p.ka_a = a.sf_k_atoms_a; p.ka_b = a.sf_k_atoms_b;
   out_dims(a, &p.out_rows, &p.out_cols);
-  const dim3 grid(tiles_a, tiles_b, splits);
+  p.grp_start = a.grp_start; p.grp_cnt = a.grp_cnt; p.grp_rows_a = a.grp_rows_a;
+  const dim3 grid = grouped ? dim3(a.grp_rows_a / BM, a.grp_chunks, a.grp_experts) : dim3(tiles_a, tiles_b, splits);
 
 #define HB_DISPATCH(KIND)                                                        \
   switch (a.bn) {                                                                \
@@ -510,6 +533,30 @@ int hb_gemm(int kind, const void* a, const void* b, const void* sfa, const void*
   g.alpha_ptr = static_cast<const float*>(alpha_ptr); g.epilogue = epilogue; g.swap = swap; g.splits = splits;
   g.workspace = static_cast<float*>(workspace); g.counters = static_cast<int*>(counters);
   g.status = static_cast<int*>(status); g.bn = bn; g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
+  g.grp_start = nullptr; g.grp_cnt = nullptr; g.grp_rows_a = 0; g.grp_experts = 0; g.grp_chunks = 0;
+  const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// Grouped (mixture-of-experts) GEMM, weights on the 128-row side: for expert e and its `cnt[e]` rows starting at
+// `start[e]` (a multiple of 128) of the sorted activation buffer b [rows, K]:
+//   out[start[e] + j, n] = sum_k b[start[e] + j, k] * a[e * n_per_expert + n, k]      (n < n_per_expert)
+// `max_rows_per_expert` bounds cnt[] (it sizes the grid); alpha_ptr holds one scale per expert (may be null).
+int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int experts,
+                    int n_per_expert, int b_rows, int k, void* out, long long ldo, const void* alpha_ptr,
+                    int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status, int ka_a,
+                    int ka_b, void* stream) {
+  hb::GemmArgs g;
+  int bn = 16;
+  while (bn < max_rows_per_expert && bn < 256) bn *= 2;
+  g.kind = kind; g.a = a; g.b = b; g.sfa = sfa; g.sfb = sfb;
+  g.ra = experts * n_per_expert; g.rb = b_rows; g.k = k; g.lda = k; g.ldb = k;
+  g.out = out; g.ldo = ldo; g.residual = nullptr; g.alpha = 1.f;
+  g.alpha_ptr = static_cast<const float*>(alpha_ptr); g.epilogue = epilogue; g.swap = 1; g.splits = 1;
+  g.workspace = nullptr; g.counters = nullptr; g.status = static_cast<int*>(status); g.bn = bn;
+  g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
+  g.grp_start = static_cast<const int*>(start); g.grp_cnt = static_cast<const int*>(cnt);
+  g.grp_rows_a = n_per_expert; g.grp_experts = experts; g.grp_chunks = (max_rows_per_expert + bn - 1) / bn;
   const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

@@ -38,6 +38,10 @@ struct GemmArgs {
   int bn;               // N tile: 16, 32, 64, 128 or 256
   int sf_k_atoms_a;     // nvfp4: number of 64-element K atoms per row block in sfa (padded to a multiple of 4)
   int sf_k_atoms_b;
+  // grouped mode (null grp_cnt = off); see hb_gemm_grouped
+  const int* grp_start;
+  const int* grp_cnt;
+  int grp_rows_a, grp_experts, grp_chunks;
 };
 
 // Returns cudaSuccess or the launch error. Tensor maps are built (and cached) inside.

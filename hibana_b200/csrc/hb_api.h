@@ -14,11 +14,17 @@ int hb_gemm(int kind, const void* a, const void* b, const void* sfa, const void*
             long long lda, long long ldb, void* out, long long ldo, const void* residual, float alpha,
             const void* alpha_ptr, int epilogue, int swap, int splits, void* workspace, void* counters,
             void* status, int bn, int ka_a, int ka_b, void* stream);
+int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int experts,
+                    int n_per_expert, int b_rows, int k, void* out, long long ldo, const void* alpha_ptr,
+                    int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status, int ka_a,
+                    int ka_b, void* stream);
 void hb_clear_tmap_cache(void);
 
 // ---- quantisers (quant.cu) -----------------------------------------------------------------------------
 int hb_quant_nvfp4(const void* x, long long ldx, int m, int k, int ka, const void* gscale, void* q, void* sf,
                    int mode, void* stream);
+int hb_quant_nvfp4_rows(const void* x, long long ldx, int m, int k, int ka, const void* gscale, void* q, void* sf,
+                        int mode, const void* src_rows, const void* total_rows, void* stream);
 int hb_norm_quant_nvfp4(const void* x, void* residual, const void* w, float eps, int gemma, int m, int k, int ka,
                         const void* gscale, void* q, void* sf, void* normed, void* stream);
 int hb_quant_fp8_static(const void* x, long long n, const void* scale, void* q, void* stream);
@@ -65,6 +71,44 @@ int hb_accept_greedy(const void* target, const void* drafts, const void* stop_id
                      void* stream);
 int hb_rank_gap(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* ids, void* rank,
                 void* gap, void* stream);
+
+// ---- recurrent layers (ssm.cu) ---------------------------------------------------------------------------
+int hb_conv1d(const void* x, long long ldx, const void* w, const void* bias, void* y, long long ldy, void* state,
+              long long state_stride, const void* q_indptr, const void* slot_in, const void* slot_out,
+              const void* has_init, int batch, int channels, int width, int act_silu, void* stream);
+int hb_mamba2_scan(const void* x, const void* bmat, const void* cmat, const void* dt, long long ldx, long long ldb,
+                   long long lddt, const void* a_log, const void* dt_bias, const void* dskip, void* y, long long ldy,
+                   void* state, long long state_stride, const void* q_indptr, const void* slot_in,
+                   const void* slot_out, const void* has_init, int batch, int heads, int groups, int head_dim,
+                   int d_state, void* stream);
+int hb_gdn_scan(const void* q, const void* k, const void* v, const void* g, const void* beta, long long ldq,
+                long long ldv, void* o, long long ldo, void* state, long long state_stride, const void* q_indptr,
+                const void* slot_in, const void* slot_out, const void* has_init, int batch, int k_heads,
+                int v_heads, int kdim, int vdim, float scale, int l2norm, void* stream);
+
+// ---- communicator (comm.cu) ------------------------------------------------------------------------------
+int hb_comm_ctrl_bytes(void);
+int hb_comm_nslot(void);
+int hb_comm_alloc(long long bytes, void** out);
+int hb_comm_free(void* p);
+int hb_comm_ipc_handle(void* p, void* handle64);
+int hb_comm_ipc_open(const void* handle64, void** out);
+int hb_comm_ipc_close(void* p);
+int hb_ar_norm(const void* const* peer_bases, int world, int rank, int slot, long long data_offset, int rows, int h,
+               void* residual, const void* weight, float eps, int gemma, void* out, void* q, void* sf,
+               const void* gscale, int ka, long long limit_ns, void* status, void* stream);
+int hb_barrier(const void* const* peer_bases, int world, int rank, int slot, long long limit_ns, void* status,
+               void* stream);
+
+// ---- mixture of experts (moe.cu) -------------------------------------------------------------------------
+int hb_moe_route(const void* logits, long long ld, const void* sel_bias, int tokens, int experts, int topk,
+                 int sigmoid, int renorm, float scale, void* ids, void* weights, void* stream);
+int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, int e_n, void* cnt, void* start,
+                void* pos, void* src_row, int rows_cap, void* total_rows, void* stream);
+int hb_moe_gather(const void* x, long long ldx, const void* src_row, const void* total_rows, void* out, int rows_cap,
+                  int h, void* stream);
+int hb_moe_combine(const void* y, long long ldy, const void* pos, const void* weights, const void* shared,
+                   long long ld_shared, void* out, long long ldo, int tokens, int topk, int h, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,264 @@
+// Mixture-of-experts routing, planning, row gather and combine for sm_100a.
+//
+//   route   : per token, softmax (or sigmoid + selection bias) over E router logits, top-k, renormalise, scale.
+//   plan    : counts per expert, 128-row-aligned segment starts, and a deterministic position of every
+//             (token, k) pair inside its expert's segment (pairs keep token order, so sums are reproducible).
+//   gather  : bf16 rows of the sorted activation buffer (padding rows zero) for bf16 experts; NVFP4 experts
+//             quantise through the row-indirect mode of the activation quantiser instead.
+//   combine : out[t] = sum_k w[t, k] * y[pos[t, k]] (+ shared expert output) in selection order.
+//
+// The grouped GEMMs between plan and combine are the grouped mode of csrc/gemm.cu. Reference counterparts:
+// hibana/kernels/flashnext_fused.py:279-620 (route_topk, moe_combine*), hibana/model/nemotron/moe.py:76-306,
+// hibana/kernels/csrc/w3_gemm.cu:711-1289 (prep / combine), hibana/kernels/csrc/nemotron_moe.cu:496-618.
+#include "hb_api.h"
+#include "hb_common.cuh"
+
+namespace hb {
+namespace {
+
+constexpr int MAX_TOPK = 32;
+
+// One warp per token; E <= 1024.
+__global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ sel_bias,
+                                 int tokens, int experts, int topk, int sigmoid, int renorm, float scale,
+                                 int* __restrict__ ids, float* __restrict__ weights) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  constexpr int PER = 32;  // values per lane (E <= 1024)
+  float score[PER], sel[PER];
+  const float* lr = logits + t * ld;
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane + i * 32;
+    score[i] = e < experts ? lr[e] : -INFINITY;
+    mx = fmaxf(mx, score[i]);
+  }
+  if (sigmoid) {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = lane + i * 32;
+      if (e < experts) {
+        score[i] = 1.f / (1.f + __expf(-score[i]));
+        sel[i] = score[i] + (sel_bias ? sel_bias[e] : 0.f);
+      } else {
+        score[i] = 0.f;
+        sel[i] = -INFINITY;
+      }
+    }
+  } else {
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = lane + i * 32;
+      score[i] = e < experts ? __expf(score[i] - mx) : 0.f;
+      sum += score[i];
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = lane + i * 32;
+      score[i] *= inv;
+      sel[i] = e < experts ? score[i] : -INFINITY;
+    }
+  }
+  float wsum = 0.f;
+  float my_w = 0.f;
+  int my_id = 0;
+  for (int k = 0; k < topk; ++k) {
+    // lane-local best (lowest index wins ties), then warp argmax
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = lane + i * 32;
+      if (sel[i] > bv || (sel[i] == bv && e < bi)) {
+        bv = sel[i];
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    // the owner lane removes it and reports its score
+    float sc = 0.f;
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < PER; ++i)
+        if (lane + i * 32 == bi) {
+          sc = score[i];
+          sel[i] = -INFINITY;
+        }
+    }
+    sc = __shfl_sync(0xffffffffu, sc, bi & 31);
+    wsum += sc;
+    if (lane == k) {
+      my_w = sc;
+      my_id = bi;
+    }
+  }
+  if (lane < topk) {
+    const float w = (renorm ? my_w / fmaxf(wsum, 1e-20f) : my_w) * scale;
+    ids[static_cast<long long>(t) * topk + lane] = my_id;
+    weights[static_cast<long long>(t) * topk + lane] = w;
+  }
+}
+
+// Single CTA. e_lo / e_n restrict planning to the experts [e_lo, e_lo + e_n) this rank owns (expert parallelism):
+// pairs routed elsewhere get pos = -1 and are skipped by the combine.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ ids, int pairs, int topk, int experts, int e_lo, int e_n,
+                int* __restrict__ cnt, int* __restrict__ start, int* __restrict__ pos, int* __restrict__ src_row,
+                int rows_cap, int* __restrict__ total_rows) {
+  extern __shared__ int sm[];   // [experts] counts, [experts] starts
+  int* c = sm;
+  int* s = sm + experts;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) c[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= e_lo && e < e_lo + e_n) atomicAdd(&c[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < experts; ++e) {
+      s[e] = acc;
+      acc += ((c[e] + 127) >> 7) << 7;
+    }
+    *total_rows = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    cnt[e] = c[e];
+    start[e] = s[e];
+  }
+  for (int r = threadIdx.x; r < rows_cap; r += blockDim.x) src_row[r] = -1;
+  __syncthreads();
+  // Deterministic positions: thread e walks the pairs in order and numbers its own.
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    if (c[e] == 0) continue;
+    int n = 0;
+    const int base = s[e];
+    for (int i = 0; i < pairs; ++i) {
+      if (ids[i] == e) {
+        const int r = base + n++;
+        if (r < rows_cap) {
+          pos[i] = r;
+          src_row[r] = i / topk;
+        } else {
+          pos[i] = -1;
+        }
+      }
+    }
+  }
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e < e_lo || e >= e_lo + e_n) pos[i] = -1;
+  }
+}
+
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ src_row,
+                                  const int* __restrict__ total_rows, __nv_bfloat16* __restrict__ out, int h) {
+  const int r = blockIdx.x;
+  if (r >= *total_rows) return;
+  const int src = src_row[r];
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(r) * h);
+  if (src < 0) {
+    for (int i = threadIdx.x; i < (h >> 3); i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+  } else {
+    const uint4* s = reinterpret_cast<const uint4*>(x + src * ldx);
+    for (int i = threadIdx.x; i < (h >> 3); i += blockDim.x) dst[i] = s[i];
+  }
+}
+
+// out[t, :] = sum_k w[t, k] * y[pos[t, k], :] (+ shared[t, :] * shared_scale). One CTA per token.
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, long long ldy, const int* __restrict__ pos,
+                                   const float* __restrict__ weights, const __nv_bfloat16* __restrict__ shared,
+                                   long long ld_shared, __nv_bfloat16* __restrict__ out, long long ldo, int topk,
+                                   int h) {
+  const int t = blockIdx.x;
+  __shared__ int ps[MAX_TOPK];
+  __shared__ float ws[MAX_TOPK];
+  if (threadIdx.x < topk) {
+    ps[threadIdx.x] = pos[static_cast<long long>(t) * topk + threadIdx.x];
+    ws[threadIdx.x] = weights[static_cast<long long>(t) * topk + threadIdx.x];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x * 2; i < h; i += blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int k = 0; k < topk; ++k) {
+      if (ps[k] < 0) continue;
+      const uint32_t v = *reinterpret_cast<const uint32_t*>(y + ps[k] * ldy + i);
+      a0 += ws[k] * bf16_lo(v);
+      a1 += ws[k] * bf16_hi(v);
+    }
+    if (shared != nullptr) {
+      const uint32_t v = *reinterpret_cast<const uint32_t*>(shared + t * ld_shared + i);
+      a0 += bf16_lo(v);
+      a1 += bf16_hi(v);
+    }
+    *reinterpret_cast<uint32_t*>(out + t * ldo + i) = pack_bf16(a0, a1);
+  }
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+#define ST(s) static_cast<cudaStream_t>(s)
+
+extern "C" {
+
+int hb_moe_route(const void* logits, long long ld, const void* sel_bias, int tokens, int experts, int topk,
+                 int sigmoid, int renorm, float scale, void* ids, void* weights, void* stream) {
+  if (tokens <= 0) return 0;
+  if (experts > 1024 || topk > MAX_TOPK || topk > experts) return 1;
+  moe_route_kernel<<<(tokens + 3) / 4, 128, 0, ST(stream)>>>(static_cast<const float*>(logits), ld,
+                                                             static_cast<const float*>(sel_bias), tokens, experts,
+                                                             topk, sigmoid, renorm, scale, static_cast<int*>(ids),
+                                                             static_cast<float*>(weights));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, int e_n, void* cnt, void* start,
+                void* pos, void* src_row, int rows_cap, void* total_rows, void* stream) {
+  if (tokens <= 0) return 0;
+  moe_plan_kernel<<<1, 1024, 2 * experts * sizeof(int), ST(stream)>>>(
+      static_cast<const int*>(ids), tokens * topk, topk, experts, e_lo, e_n, static_cast<int*>(cnt),
+      static_cast<int*>(start), static_cast<int*>(pos), static_cast<int*>(src_row), rows_cap,
+      static_cast<int*>(total_rows));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_moe_gather(const void* x, long long ldx, const void* src_row, const void* total_rows, void* out, int rows_cap,
+                  int h, void* stream) {
+  if (rows_cap <= 0) return 0;
+  moe_gather_kernel<<<rows_cap, 128, 0, ST(stream)>>>(static_cast<const __nv_bfloat16*>(x), ldx,
+                                                      static_cast<const int*>(src_row),
+                                                      static_cast<const int*>(total_rows),
+                                                      static_cast<__nv_bfloat16*>(out), h);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_moe_combine(const void* y, long long ldy, const void* pos, const void* weights, const void* shared,
+                   long long ld_shared, void* out, long long ldo, int tokens, int topk, int h, void* stream) {
+  if (tokens <= 0) return 0;
+  if (topk > MAX_TOPK || (h & 1)) return 1;
+  moe_combine_kernel<<<tokens, 256, 0, ST(stream)>>>(static_cast<const __nv_bfloat16*>(y), ldy,
+                                                     static_cast<const int*>(pos), static_cast<const float*>(weights),
+                                                     static_cast<const __nv_bfloat16*>(shared), ld_shared,
+                                                     static_cast<__nv_bfloat16*>(out), ldo, topk, h);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+}  // extern "C"

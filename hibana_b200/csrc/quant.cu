@@ -51,25 +51,29 @@ __device__ __forceinline__ void load16(const __nv_bfloat16* p, float (&x)[16]) {
 // mode 2: gate/up interleaved pairwise (x[:, 2j], x[:, 2j+1]).
 __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int m, int k, int ka,
                                    const float* __restrict__ gscale, uint8_t* __restrict__ q,
-                                   uint8_t* __restrict__ sf, int mode) {
+                                   uint8_t* __restrict__ sf, int mode, const int* __restrict__ src_rows,
+                                   const int* __restrict__ total_rows) {
   const int groups_pad = ka * 4;
   const int rows_pad = ((m + 127) >> 7) << 7;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(rows_pad) * groups_pad) return;
   const int row = static_cast<int>(idx / groups_pad);
   const int g = static_cast<int>(idx % groups_pad);
-  if (row >= m || g * 16 >= k) {
+  if (total_rows != nullptr && row >= *total_rows) return;   // beyond the planned segments: never read
+  // Row-indirect mode (MoE): output row `row` of the sorted buffer takes input row src_rows[row] (-1 = padding).
+  const int in_row = src_rows != nullptr ? (row < m ? src_rows[row] : -1) : row;
+  if (row >= m || in_row < 0 || g * 16 >= k) {
     sf[sf_offset(row, g, ka)] = 0;
     return;
   }
   const float inv_gs = 1.f / *gscale;
   float v[16];
   if (mode == 0) {
-    load16(x + row * ldx + g * 16, v);
+    load16(x + in_row * ldx + g * 16, v);
   } else if (mode == 1) {
     float u[16];
-    load16(x + row * ldx + g * 16, v);
-    load16(x + row * ldx + k + g * 16, u);
+    load16(x + in_row * ldx + g * 16, v);
+    load16(x + in_row * ldx + k + g * 16, u);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const float s = v[i] / (1.f + __expf(-v[i]));
@@ -77,8 +81,8 @@ __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long lon
     }
   } else {
     float a[16], b[16];
-    load16(x + row * ldx + g * 32, a);
-    load16(x + row * ldx + g * 32 + 16, b);
+    load16(x + in_row * ldx + g * 32, a);
+    load16(x + in_row * ldx + g * 32 + 16, b);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float g0 = a[2 * i], u0 = a[2 * i + 1], g1 = b[2 * i], u1 = b[2 * i + 1];
@@ -224,6 +228,20 @@ using namespace hb;
 
 extern "C" {
 
+// src_rows / total_rows (both may be null): row-indirect mode for MoE sorted buffers; m is then the row capacity.
+int hb_quant_nvfp4_rows(const void* x, long long ldx, int m, int k, int ka, const void* gscale, void* q, void* sf,
+                        int mode, const void* src_rows, const void* total_rows, void* stream) {
+  if (k % 16 != 0 || ka * 64 < k) return 1;
+  const int rows_pad = ((m + 127) / 128) * 128;
+  const long long n = static_cast<long long>(rows_pad) * ka * 4;
+  const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
+  quant_nvfp4_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, m, k, ka, static_cast<const float*>(gscale),
+      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), mode, static_cast<const int*>(src_rows),
+      static_cast<const int*>(total_rows));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
 int hb_quant_nvfp4(const void* x, long long ldx, int m, int k, int ka, const void* gscale, void* q, void* sf,
                    int mode, void* stream) {
   if (k % 16 != 0 || ka * 64 < k) return 1;
@@ -233,7 +251,7 @@ int hb_quant_nvfp4(const void* x, long long ldx, int m, int k, int ka, const voi
   const unsigned blocks = static_cast<unsigned>((n + threads - 1) / threads);
   quant_nvfp4_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ldx, m, k, ka, static_cast<const float*>(gscale),
-      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), mode);
+      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), mode, nullptr, nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -1,0 +1,70 @@
+"""MoE routing and grouped expert GEMMs against plain-PyTorch references; EP ranges sum to the whole."""
+import pytest
+import torch
+
+from hibana_b200.ops import moe
+
+
+def test_route_ref_properties_cpu():
+    lg = torch.randn(7, 16)
+    ids, w = moe.route(lg, 4)
+    assert ids.shape == (7, 4) and torch.allclose(w.sum(-1), torch.ones(7), atol=1e-5)
+    top = torch.topk(torch.softmax(lg, -1), 4).indices
+    assert torch.equal(ids.long().sort(-1).values, top.sort(-1).values)
+    ids2, w2 = moe.route(lg, 3, sigmoid=True, sel_bias=torch.zeros(16), scale=2.5)
+    assert torch.allclose(w2.sum(-1), torch.full((7,), 2.5), atol=1e-4)
+
+
+def _weights(e, h, inter, act, fmt, dev, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    n1 = 2 * inter if act == "swiglu" else inter
+    fc1 = torch.randn(e, n1, h, generator=g) * 0.05
+    fc2 = torch.randn(e, h, inter, generator=g) * 0.05
+    return moe.ExpertWeights.create(fc1.to(dev), fc2.to(dev), act, fmt, in_amax=5.0, mid_amax=2.0)
+
+
+def test_experts_ref_ep_halves_sum_cpu():
+    ew = _weights(8, 64, 128, "swiglu", "bf16", "cpu")
+    x = torch.randn(5, 64).bfloat16()
+    ids, w = moe.route(torch.randn(5, 8), 2)
+    whole = moe.experts_forward(x, ids, w, ew).float()
+    parts = sum(moe.experts_forward(x, ids, w, ew, e_lo=lo, e_n=4).float() for lo in (0, 4))
+    assert (whole - parts).abs().max() < 2e-2 * whole.abs().max() + 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("e,k,sig", [(8, 2, False), (512, 10, False), (512, 22, True), (60, 6, True)])
+def test_route_gpu(e, k, sig):
+    lg = torch.randn(33, e)
+    bias = torch.randn(e) * 0.1 if sig else None
+    ids, w = moe.route(lg, k, sigmoid=sig, sel_bias=bias, scale=1.7)
+    ids_g, w_g = moe.route(lg.cuda(), k, sigmoid=sig, sel_bias=None if bias is None else bias.cuda(), scale=1.7)
+    assert torch.equal(ids_g.cpu(), ids)
+    assert torch.allclose(w_g.cpu(), w, atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["bf16", "nvfp4"])
+@pytest.mark.parametrize("t,e,k,h,inter,act", [(4, 8, 2, 256, 512, "swiglu"), (37, 16, 4, 256, 128, "relu2"),
+                                               (300, 8, 2, 128, 256, "swiglu")])
+def test_experts_forward_gpu(fmt, t, e, k, h, inter, act):
+    ew = _weights(e, h, inter, act, fmt, "cpu", seed=1)
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(t, h, generator=g).bfloat16()
+    ids, w = moe.route(torch.randn(t, e, generator=g), k)
+    shared = torch.randn(t, h, generator=g).bfloat16()
+    ref = moe.experts_forward(x, ids, w, ew, shared=shared).float()
+    ewg = ew.to("cuda")
+    got = moe.experts_forward(x.cuda(), ids.cuda(), w.cuda(), ewg, shared=shared.cuda()).float().cpu()
+    tol = 3e-2 if fmt == "bf16" else 6e-2
+    assert (got - ref).abs().max() <= tol * ref.abs().max() + 2e-3, (got - ref).abs().max()
+    # expert-parallel ranges produce partial sums that add up to the whole
+    lo = moe.experts_forward(x.cuda(), ids.cuda(), w.cuda(), ewg, e_lo=0, e_n=e // 2).float()
+    hi = moe.experts_forward(x.cuda(), ids.cuda(), w.cuda(), ewg, e_lo=e // 2, e_n=e // 2).float()
+    whole = moe.experts_forward(x.cuda(), ids.cuda(), w.cuda(), ewg).float()
+    assert (lo + hi - whole).abs().max() <= 2e-2 * whole.abs().max() + 2e-3
+    # deterministic
+    again = moe.experts_forward(x.cuda(), ids.cuda(), w.cuda(), ewg).float()
+    assert torch.equal(again, whole)
+    from hibana_b200 import _native as nv
+    assert nv.read_status() == 0
