@@ -108,6 +108,18 @@ class StateManager:
             return
         tokens = req.all_ids[:length]
         node, adopted = self.cache.insert(tokens, req.kv_slots[:length], start=req.shared_len)
+        if adopted == req.shared_len and self.states is not None:
+            # The tree already holds these tokens (cached KV without a usable snapshot made this request re-run
+            # them): keep the private copy, but leave a snapshot on the existing path so the next request resumes.
+            m = self.cache.match(tokens)
+            if m.length == length and m.node.snapshot is None and m.node is not self.cache.root:
+                try:
+                    slot = self._alloc_state()
+                except MemoryError:
+                    return
+                self.states.copy_slot(req.state_slot, slot)
+                self.cache.set_snapshot(m.node, Snapshot(slot, length, spare=spare))
+            return
         if adopted > req.shared_len:
             req.lock = self.cache.move_lock(req.lock, node) if req.lock is not None else self.cache.lock(node)
             req.shared_len = adopted

@@ -37,7 +37,7 @@ class Executor:
     def __init__(self, model, *, max_batch: int = 64, max_ctx: int = 4096, kv_slots: int = 0,
                  use_graphs: bool = True, buckets: Optional[Sequence[int]] = None, radix_cache: bool = True,
                  state_pool=None, comm=None, kv_dtype: Optional[torch.dtype] = None, attn_splits: int = 0,
-                 decode_reserve: int = 64):
+                 decode_reserve: int = 64, state_slots: int = 0):
         t: Target = model.target
         self.model, self.target = model, t
         self.device = model.device
@@ -45,14 +45,27 @@ class Executor:
         if kv_slots <= 0:
             kv_slots = max_batch * max_ctx
         dtype = kv_dtype or (torch.float8_e4m3fn if t.kv_dtype == "fp8" else torch.bfloat16)
-        self.kv = KvPool(t.attn_layers, kv_slots, t.kv_heads, t.head_dim, dtype, self.device) if t.attn_layers \
+        kv_layers = getattr(model, "kv_layers", t.attn_layers) + (1 if getattr(model, "mtp", None) is not None else 0)
+        self.kv = KvPool(kv_layers, kv_slots, t.kv_heads, t.head_dim, dtype, self.device) if kv_layers \
             else KvPool(0, kv_slots, 1, 1, dtype, self.device)
+        spec = model.state_pool_spec() if hasattr(model, "state_pool_spec") else None
+        if state_pool is None and spec is not None:
+            from ..cache.state_pool import StatePool
+            state_pool = StatePool(spec["layers"], state_slots or (3 * max_batch + 2), spec["conv_dim"],
+                                   spec["conv_width"], spec["state_shape"], self.device)
+        self.state_pool = state_pool
         buckets = buckets or tuple(b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_batch)
         self.runner = ModelRunner(model, self.kv, max_batch=max_batch, max_ctx=max_ctx, buckets=buckets,
                                   use_graphs=use_graphs, comm=comm, attn_splits=attn_splits, state_pool=state_pool)
         self.state = StateManager(self.kv, state_pool, cache=radix_cache, decode_reserve=decode_reserve)
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "prefill_chunks": 0,
                       "cached_tokens": 0}
+        self.spec = None
+
+    def enable_spec(self, depth: int = 2) -> None:
+        """Turns on MTP speculative decoding (greedy exact acceptance) for requests with greedy sampling."""
+        from .spec import SpecDecoder
+        self.spec = SpecDecoder(self, depth)
 
     # ---- lifecycle
     def validate_request(self, req: Request) -> None:
@@ -85,12 +98,16 @@ class Executor:
         if req.table_row < 0:
             return
         self.state.release(req)
+        if self.spec is not None:
+            self.spec.release(req)
         self.runner.free_row(req.table_row)
         req.table_row = -1
 
     def retract(self, req: Request) -> None:
         """Drops physical resources; the emitted history stays and is replayed on re-admission."""
         self.state.retract(req)
+        if self.spec is not None:
+            self.spec.release(req)
         self.runner.free_row(req.table_row)
         req.table_row, req.prefilled, req.committed_len, req.cached_len = -1, 0, 0, 0
         req.state = State.WAITING
@@ -108,6 +125,10 @@ class Executor:
             # After a retraction the emitted history is replayed; the last emitted token stays pending.
             target_len = len(seq) - (1 if req.output_ids else 0)
             count = min(count, target_len - req.prefilled)
+            if self.state_pool is not None and req.prefilled < req.branch_at < req.prefilled + count:
+                # stop at the point where this prompt left a cached path, so a state snapshot lands there and the
+                # next request sharing that prefix can resume from it
+                count = req.branch_at - req.prefilled
             tokens = seq[req.prefilled:req.prefilled + count]
             try:
                 slots = self._alloc(req, count)
@@ -124,9 +145,18 @@ class Executor:
             slot_lists.append(slots)
             finals.append(req.prefilled + count >= target_len)
         any_final = any(finals)
+        extras = {"want_hidden": True} if self.spec is not None else None
         out = self.runner.forward_rows(rows, toks, starts, slot_lists, mode=PREFILL,
-                                       want="last" if any_final else "none",
-                                       sampling_rows=_sampling_rows([r for r, _ in chunks]) if any_final else None)
+                                       want="last" if any_final else "none", extras=extras,
+                                       sampling_rows=_sampling_rows([r for r, _ in chunks]) if any_final else None,
+                                       state_slots=[r.state_slot for r, _ in chunks]
+                                       if self.state_pool is not None else None)
+        if self.spec is not None:
+            off = 0
+            for i, (req, _) in enumerate(chunks):
+                n = len(toks[i])
+                self.spec.ingest_prefill(req, extras["hidden"][off:off + n], starts[i], n)
+                off += n
         for i, (req, _) in enumerate(chunks):
             n = len(toks[i])
             req.prefilled += n
@@ -142,11 +172,17 @@ class Executor:
 
     def decode_step(self, reqs: Sequence[Request]) -> None:
         """One token for every running request (the pending token goes in, the next one comes out)."""
+        if self.spec is not None and all(r.params.greedy for r in reqs):
+            self.spec.round(reqs)
+            self.stats["decode_steps"] += 1
+            self.stats["decode_tokens"] += sum(r.rounds[-1] for r in reqs)
+            return
         slots = [s[0] for s in self.state.reserve(reqs, 1)]   # all or nothing; MemoryError -> scheduler retracts
         rows = [r.table_row for r in reqs]
         tokens = [r.output_ids[-1] for r in reqs]
         positions = [r.total_len - 1 for r in reqs]
-        out = self.runner.decode(rows, tokens, positions, slots, _sampling_rows(reqs))
+        out = self.runner.decode(rows, tokens, positions, slots, _sampling_rows(reqs),
+                                 [r.state_slot for r in reqs] if self.state_pool is not None else None)
         for r, tok in zip(reqs, out):
             self.state.commit(r, 1)
             r.draws += 1

@@ -18,7 +18,8 @@ from ..ops import attention, sampling
 from .context import DECODE, PREFILL, VERIFY, ForwardContext
 
 # Rows of the packed int32 step buffer.
-R_IDS, R_POS, R_SLOT, R_ROW, R_CTX, R_TOPK, R_TEMP, R_TOPP, R_SEED, R_OFFS, N_ROWS = 0, 1, 2, 3, 4, 5, 6, 7, 8, 10, 12
+R_IDS, R_POS, R_SLOT, R_ROW, R_CTX, R_TOPK, R_TEMP, R_TOPP, R_SEED, R_OFFS, R_STATE, N_ROWS = \
+    0, 1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 13
 
 
 class StepBuffers:
@@ -41,6 +42,7 @@ class StepBuffers:
         flat = d.view(-1)
         b = self.bucket
         return dict(ids=d[R_IDS], pos=d[R_POS], slot=d[R_SLOT], row=d[R_ROW], ctx=d[R_CTX], top_k=d[R_TOPK],
+                    state=d[R_STATE],
                     temp=d[R_TEMP].view(torch.float32), top_p=d[R_TOPP].view(torch.float32),
                     seed=flat[R_SEED * b:(R_SEED + 2) * b].view(torch.int64),
                     offs=flat[R_OFFS * b:(R_OFFS + 2) * b].view(torch.int64))
@@ -98,8 +100,8 @@ class ModelRunner:
         ctx = ForwardContext(DECODE, positions=v["pos"], slots=v["slot"], kv_indices=self.block_table,
                              ctx_len=v["ctx"], seq_rows=v["row"], batch=buf.bucket, attn_splits=buf.splits,
                              attn_workspace=buf.workspace, comm=self.comm,
-                             state_slots=v["row"])
-        h = self.model.forward(v["ids"].long(), ctx, self.kv)
+                             state_slots=v["state"])
+        h = self._forward(v["ids"].long(), ctx)
         logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
         tok = sampling.sample(logits, v["temp"], v["top_k"], v["top_p"], v["seed"], v["offs"])
         buf.out.copy_(tok)
@@ -133,8 +135,13 @@ class ModelRunner:
             self.graph_launches[b] = nv.LAUNCHES - before
             buf.graph = g
 
+    def _forward(self, ids, ctx):
+        if self.state_pool is not None:
+            return self.model.forward(ids, ctx, self.kv, self.state_pool)
+        return self.model.forward(ids, ctx, self.kv)
+
     def decode(self, rows: Sequence[int], tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int],
-               sampling_rows: Optional[dict] = None) -> list[int]:
+               sampling_rows: Optional[dict] = None, state_slots: Optional[Sequence[int]] = None) -> list[int]:
         """One decode step for len(rows) sequences; returns the sampled token of each (host ints).
 
         sampling_rows: optional dict of per-sequence lists temp / top_k / top_p / seed / offs (greedy when None).
@@ -150,6 +157,8 @@ class ModelRunner:
         a[R_SLOT, :n] = slots
         a[R_ROW, :n] = rows
         a[R_CTX, :n] = np.asarray(positions, dtype=np.int32) + 1
+        if state_slots is not None:
+            a[R_STATE, :n] = state_slots
         if sampling_rows is None:
             a[R_TOPK:R_OFFS + 2, :n] = 0
         else:
@@ -174,7 +183,8 @@ class ModelRunner:
     def forward_rows(self, rows: Sequence[int], token_lists: Sequence[Sequence[int]], starts: Sequence[int],
                      slot_lists: Sequence[Sequence[int]], *, mode: str = PREFILL, want: str = "last",
                      sampling_rows: Optional[dict] = None, state_slots: Optional[Sequence[int]] = None,
-                     has_initial_state: Optional[Sequence[int]] = None, checkpoints=None):
+                     has_initial_state: Optional[Sequence[int]] = None, checkpoints=None,
+                     extras: Optional[dict] = None):
         """Runs new tokens of several sequences in one ragged forward.
 
         rows[i] is the block-table row, token_lists[i] the new tokens starting at position starts[i] with KV slots
@@ -218,10 +228,14 @@ class ModelRunner:
                              if state_slots is not None else seq_rows_d,
                              has_initial_state=up(np.asarray(has_initial_state, dtype=np.int32), torch.int32)
                              if has_initial_state is not None else None,
-                             checkpoints=checkpoints, max_ctx_host=int(ctx_len.max()))
-        h = self.model.forward(ids_d, ctx, self.kv)
+                             checkpoints=checkpoints, max_ctx_host=int(ctx_len.max()),
+                             extras=extras if extras is not None else {})
+        h = self._forward(ids_d, ctx)
         if want == "none":
             return None
+        if want == "all_device":      # verify: argmax of every row and the pre-norm hidden states, left on device
+            logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
+            return sampling.argmax(logits), ctx.extras.get("hidden")
         logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
         if sampling_rows is None or want == "all":
             tok = sampling.argmax(logits)

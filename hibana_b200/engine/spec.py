@@ -1,0 +1,185 @@
+"""Speculative decoding: draft with the MTP head, verify with the target, accept, commit.
+
+A round for requests whose pending token x_n sits at position n (KV committed for 0..n-1):
+  1. reserve k + 1 KV slots (positions n..n+k) as one transaction;
+  2. draft: k chained MTP steps. Step 1 consumes (target hidden of position n-1, x_n) at MTP position n-1, step j
+     consumes (previous draft hidden, d_{j-1}) at position n+j-2; the MTP layer keeps its KV in an extra layer of the
+     same pool slots, so prefix-cache hits share it;
+  3. verify: one ragged target forward over rows [x_n, d_1..d_k]; recurrent layers write to a scratch state slot and
+     log their recurrence inputs;
+  4. accept: longest prefix with d_{j+1} == target_j plus the target's own token (device kernel), truncated at stop
+     ids and the token budget;
+  5. commit: keep the accepted slots, replay exactly the accepted rows of every recurrent layer from the untouched
+     committed state (same kernels, so the state is bitwise what a plain decode would have produced), refresh the MTP
+     KV of accepted positions with the true target hiddens.
+Reference: hibana/engine/spec.py:268-741, hibana/proposers/mtp.py:187-376, hibana/engine/accept.py:18-56.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..ops import sampling
+from .context import DECODE, VERIFY, ForwardContext
+from .request import MAX_STOPS, Request
+
+
+class SpecStats:
+    def __init__(self):
+        self.rounds = self.proposed = self.accepted = self.emitted = 0
+
+    def as_dict(self) -> dict:
+        r = max(self.rounds, 1)
+        return {"rounds": self.rounds, "proposed": self.proposed, "accepted": self.accepted, "emitted": self.emitted,
+                "accept_rate": self.accepted / max(self.proposed, 1), "tokens_per_round": self.emitted / r}
+
+
+class SpecDecoder:
+    def __init__(self, executor, depth: int = 2):
+        self.ex = executor
+        self.model = executor.model
+        self.mtp = executor.model.mtp
+        assert self.mtp is not None, "speculation needs a model with an MTP head"
+        self.depth = depth
+        self.stats = SpecStats()
+        self.feats: dict[int, torch.Tensor] = {}          # rid -> target hidden of the last committed position
+        self.scratch: dict[int, int] = {}                 # rid -> scratch state slot (recurrent models)
+
+    # ---- helpers
+    def _dev(self, arr, dtype):
+        return torch.as_tensor(np.asarray(arr), dtype=dtype).to(self.ex.device)
+
+    def _mtp_rows(self, reqs: Sequence[Request], hiddens: torch.Tensor, next_ids, positions, counts):
+        """One MTP forward over ragged rows; returns (chained hidden, argmax token of every row)."""
+        runner = self.ex.runner
+        dev = self.ex.device
+        b = len(reqs)
+        counts = list(counts)
+        indptr = np.zeros(b + 1, dtype=np.int32)
+        indptr[1:] = np.cumsum(counts)
+        pos = np.asarray(positions, dtype=np.int32)
+        slots = np.concatenate([np.asarray(r.kv_slots[p0:p0 + c], dtype=np.int32)
+                                for r, p0, c in zip(reqs, self._starts(pos, indptr), counts)])
+        ctx_len = np.asarray([int(pos[indptr[i + 1] - 1]) + 1 for i in range(b)], dtype=np.int32)
+        ctx = ForwardContext(VERIFY, positions=self._dev(pos, torch.int32), slots=self._dev(slots, torch.int32),
+                             kv_indices=runner.block_table, ctx_len=self._dev(ctx_len, torch.int32),
+                             q_indptr=self._dev(indptr, torch.int32),
+                             seq_rows=self._dev([r.table_row for r in reqs], torch.int32), max_rows=max(counts),
+                             batch=b)
+        g, normed = self.mtp.forward(hiddens, self._dev(next_ids, torch.int64), ctx, self.ex.kv)
+        tok = sampling.argmax(self.model.logits(normed))
+        return g, tok
+
+    @staticmethod
+    def _starts(pos, indptr):
+        return [int(pos[indptr[i]]) for i in range(len(indptr) - 1)]
+
+    # ---- prefill hook
+    def ingest_prefill(self, req: Request, hidden: torch.Tensor, start: int, count: int) -> None:
+        """After a target prefill chunk over positions [start, start + count): feed the MTP layer the pairs
+        (h_p, x_{p+1}) whose next token is already known and keep the last hidden as the request's feature."""
+        seq = req.all_ids
+        rows, ids, pos = [], [], []
+        prev = self.feats.get(req.rid)
+        if start > 0:
+            rows.append(prev if prev is not None else torch.zeros_like(hidden[0]))   # stand-in on a cache hit
+            ids.append(seq[start])
+            pos.append(start - 1)
+        for j in range(count - 1):
+            rows.append(hidden[j])
+            ids.append(seq[start + j + 1])
+            pos.append(start + j)
+        self.feats[req.rid] = hidden[count - 1].clone()
+        if rows:
+            self._mtp_rows([req], torch.stack(rows), ids, pos, [len(rows)])
+
+    def release(self, req: Request) -> None:
+        self.feats.pop(req.rid, None)
+        slot = self.scratch.pop(req.rid, None)
+        if slot and self.ex.state_pool is not None:
+            self.ex.state_pool.free(slot)
+
+    # ---- the round
+    def round(self, reqs: Sequence[Request]) -> None:
+        ex, dev = self.ex, self.ex.device
+        k = self.depth
+        b = len(reqs)
+        ex.state.reserve(reqs, k + 1)                      # MemoryError -> the scheduler retracts and retries
+        n = [r.total_len - 1 for r in reqs]                # position of the pending token
+        for r, nn in zip(reqs, n):                         # the block table must know the reserved slots
+            ex.runner.set_table(r.table_row, nn, r.kv_slots[nn:nn + k + 1])
+        # ---- draft
+        feat = torch.stack([self.feats.get(r.rid, torch.zeros(self.model.target.hidden, dtype=torch.bfloat16,
+                                                              device=dev)) for r in reqs])
+        drafts = torch.zeros(b, k, dtype=torch.int64, device=dev)
+        hid = feat
+        ids = [r.output_ids[-1] for r in reqs]
+        for j in range(k):
+            hid, tok = self._mtp_rows(reqs, hid, ids, [nn - 1 + j for nn in n], [1] * b)
+            drafts[:, j] = tok
+            ids = tok.tolist() if j + 1 < k else None
+        # ---- verify
+        host_drafts = drafts.tolist()
+        tokens = [[r.output_ids[-1]] + host_drafts[i] for i, r in enumerate(reqs)]
+        extras = {"want_hidden": True}
+        has_state = ex.state_pool is not None
+        if has_state:
+            for r in reqs:
+                if r.rid not in self.scratch:
+                    self.scratch[r.rid] = ex.state_pool.alloc()
+            extras["state_out"] = self._dev([self.scratch[r.rid] for r in reqs], torch.int32)
+            extras["ring"] = []
+        target, hidden = ex.runner.forward_rows(
+            [r.table_row for r in reqs], tokens, n, [r.kv_slots[nn:nn + k + 1] for r, nn in zip(reqs, n)], mode=VERIFY,
+            want="all_device", state_slots=[r.state_slot for r in reqs] if has_state else None, extras=extras)
+        target = target.view(b, k + 1)
+        # ---- accept (device), one small readback
+        stops = torch.full((b, MAX_STOPS), -1, dtype=torch.int64)
+        for i, r in enumerate(reqs):
+            ids_ = list(r.params.stop_ids)[:MAX_STOPS]
+            if r.eos_id is not None and not r.params.ignore_eos and len(ids_) < MAX_STOPS:
+                ids_.append(r.eos_id)
+            stops[i, :len(ids_)] = torch.tensor(ids_, dtype=torch.int64) if ids_ else stops[i, :0]
+        budget = torch.tensor([max(r.remaining, 1) for r in reqs], dtype=torch.int32)
+        emitted, count, accepted = sampling.accept_greedy(target, drafts, stops.to(dev), budget.to(dev))
+        emitted_h, count_h, acc_h = emitted.tolist(), count.tolist(), accepted.tolist()
+        # ---- commit
+        sel_rows, new_indptr = [], [0]
+        for i, r in enumerate(reqs):
+            c = count_h[i]
+            ex.state.commit(r, c)
+            sel_rows.extend(range(i * (k + 1), i * (k + 1) + c))
+            new_indptr.append(new_indptr[-1] + c)
+            self.feats[r.rid] = hidden[i * (k + 1) + c - 1].clone()
+        if has_state:
+            sel = self._dev(sel_rows, torch.int64)
+            ip = self._dev(new_indptr, torch.int32)
+            slots = self._dev([r.state_slot for r in reqs], torch.int32)
+            for layer, saved in extras["ring"]:
+                layer.replay(saved, sel, ip, slots, ex.state_pool)
+        # refresh the MTP KV of accepted draft positions with the true target hiddens
+        ref_reqs, ref_rows, ref_ids, ref_pos, ref_cnt = [], [], [], [], []
+        for i, r in enumerate(reqs):
+            a = count_h[i] - 1
+            if a > 0:
+                ref_reqs.append(r)
+                ref_rows.extend(range(i * (k + 1), i * (k + 1) + a))
+                ref_ids.extend(emitted_h[i][:a])
+                ref_pos.extend(range(n[i], n[i] + a))
+                ref_cnt.append(a)
+        if ref_reqs:
+            self._mtp_rows(ref_reqs, hidden.index_select(0, self._dev(ref_rows, torch.int64)), ref_ids, ref_pos,
+                           ref_cnt)
+        for i, r in enumerate(reqs):
+            c = count_h[i]
+            r.draws += c
+            r.rounds.append(c)
+            for tok in emitted_h[i][:c]:
+                if r.push(tok):
+                    break
+            self.stats.rounds += 1
+            self.stats.proposed += k
+            self.stats.accepted += acc_h[i]
+            self.stats.emitted += c

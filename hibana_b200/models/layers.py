@@ -1,0 +1,282 @@
+"""Layer library of the hybrid model families: attention (plain / gated-output), Mamba-2, gated delta rule,
+SwiGLU MLP, MoE with shared expert, latent MoE. Every layer holds its weights and a `forward(x, ctx, caches)`
+that takes the normed input rows and returns this rank's output rows (a partial sum under tensor parallelism).
+
+Reference: hibana/model/attention.py:69-126, hibana/model/gdn.py:41-301, hibana/model/nemotron/mamba.py:23-86,
+hibana/model/mlp.py:26-48, hibana/model/flashnext/moe.py:68-192, hibana/model/nemotron/moe.py:349-566.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ..engine.context import ForwardContext
+from ..ops import attention, basic, gemm, moe, recurrent
+from ..target import ATTN, GATED_ATTN, GDN, LATENT_MOE, MAMBA2, MLP, MOE, NONE, Target
+from .linear import Linear, interleave_pairs
+
+
+class Init:
+    """Seeded weight factory (N(0, std) matrices) shared by all layers of a model."""
+
+    def __init__(self, seed: int, device, init_device=None, std: float = 0.02):
+        self.device = torch.device(device)
+        self.gen_device = torch.device(init_device) if init_device is not None else self.device
+        self.gen = torch.Generator(device=self.gen_device)
+        self.gen.manual_seed(seed)
+        self.std = std
+
+    def normal(self, *shape, std: Optional[float] = None) -> torch.Tensor:
+        return torch.randn(*shape, generator=self.gen, dtype=torch.float32, device=self.gen_device) * (std or self.std)
+
+    def uniform(self, *shape, lo: float = 0.0, hi: float = 1.0) -> torch.Tensor:
+        return torch.rand(*shape, generator=self.gen, dtype=torch.float32, device=self.gen_device) * (hi - lo) + lo
+
+    def linear(self, n: int, k: int, fmt: str, name: str = "") -> Linear:
+        return Linear(self.normal(n, k), fmt, name=name).to(self.device)
+
+    def ones(self, n: int, gemma: bool = False) -> torch.Tensor:
+        return (torch.zeros if gemma else torch.ones)(n, dtype=torch.bfloat16, device=self.device)
+
+
+def _fmt(t: Target) -> str:
+    return "nvfp4" if t.weight_format == "nvfp4" else "bf16"
+
+
+class AttentionLayer:
+    def __init__(self, t: Target, init: Init, kv_index: int, gated: bool, name: str):
+        d = t.head_dim
+        self.t, self.kv_index, self.gated = t, kv_index, gated
+        qw = t.q_heads * d * (2 if gated else 1)
+        self.qkv = init.linear(qw + 2 * t.kv_heads * d, t.hidden, _fmt(t), name + ".qkv")
+        self.o = init.linear(t.hidden, t.q_heads * d, _fmt(t), name + ".o")
+        self.q_norm = init.ones(d, t.gemma_norm) if t.qk_norm else None
+        self.k_norm = init.ones(d, t.gemma_norm) if t.qk_norm else None
+        self.inv_freq = basic.rope_inv_freq(max(t.rot_dim, 2), t.rope_theta, device=init.device)
+        self.scale = 1.0 / math.sqrt(d)
+
+    def linears(self):
+        return [self.qkv, self.o]
+
+    def forward(self, x, ctx: ForwardContext, kv, states) -> torch.Tensor:
+        t = self.t
+        qkv = self.qkv(x)
+        i = self.kv_index
+        q = basic.rope_kv_write(qkv, ctx.positions, ctx.slots, self.inv_freq, kv.k[i], kv.v[i], t.q_heads,
+                                t.kv_heads, t.head_dim, rot=t.rot_dim, q_norm=self.q_norm, k_norm=self.k_norm,
+                                eps=t.norm_eps, gemma_norm=t.gemma_norm, kv_scale=kv.kv_scale, q_gate=self.gated)
+        att = attention.paged_attention(q, kv.k[i], kv.v[i], ctx.kv_indices, ctx.ctx_len, q_indptr=ctx.q_indptr,
+                                        max_rows=ctx.max_rows, seq_rows=ctx.seq_rows, scale=self.scale,
+                                        kv_scale=kv.kv_scale, splits=ctx.attn_splits, workspace=ctx.attn_workspace)
+        att = att.view(att.shape[0], -1)
+        if self.gated:
+            d = t.head_dim
+            gate = qkv[:, :t.q_heads * 2 * d].view(-1, t.q_heads, 2 * d)[..., d:].reshape(att.shape[0], -1)
+            att = basic.act_mul(att, basic.ACT_SIGMOID_GATE, gate.contiguous())
+        return self.o(att)
+
+
+class MambaLayer:
+    def __init__(self, t: Target, init: Init, state_index: int, name: str):
+        self.t, self.state_index = t, state_index
+        inner, gn = t.mamba_inner, t.mamba_groups * t.mamba_state
+        self.in_proj = init.linear(2 * inner + 2 * gn + t.mamba_heads, t.hidden, _fmt(t), name + ".in_proj")
+        self.out_proj = init.linear(t.hidden, inner, _fmt(t), name + ".out_proj")
+        self.conv_w = init.normal(t.mamba_conv_dim, t.conv_width, std=0.2).to(torch.bfloat16).to(init.device)
+        self.conv_b = init.normal(t.mamba_conv_dim, std=0.02).to(torch.bfloat16).to(init.device)
+        self.a_log = torch.log(init.uniform(t.mamba_heads, lo=1.0, hi=16.0)).to(init.device)
+        dt = torch.exp(init.uniform(t.mamba_heads) * (math.log(0.1) - math.log(0.001)) + math.log(0.001))
+        self.dt_bias = (dt + torch.log(-torch.expm1(-dt))).to(init.device)       # inverse softplus
+        self.d_skip = torch.ones(t.mamba_heads, device=init.device)
+        self.norm_w = init.ones(inner)
+
+    def linears(self):
+        return [self.in_proj, self.out_proj]
+
+    def forward(self, x, ctx: ForwardContext, kv, states) -> torch.Tensor:
+        t = self.t
+        inner, gn = t.mamba_inner, t.mamba_groups * t.mamba_state
+        zxbcdt = self.in_proj(x)
+        z = zxbcdt[:, :inner]
+        xbc = zxbcdt[:, inner:2 * inner + 2 * gn]
+        dt = zxbcdt[:, 2 * inner + 2 * gn:]
+        li = self.state_index
+        so = ctx.extras.get("state_out", ctx.state_slots)
+        if "ring" in ctx.extras:      # verify: log the recurrence inputs so the accepted prefix can be replayed
+            ctx.extras["ring"].append((self, (xbc, dt)))
+        xbc = recurrent.conv1d(xbc, self.conv_w, self.conv_b, states.conv[li], ctx.state_slots, so,
+                               q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state, silu=True)
+        y = recurrent.mamba2_scan(xbc[:, :inner], xbc[:, inner:inner + gn], xbc[:, inner + gn:], dt, self.a_log,
+                                  self.dt_bias, self.d_skip, states.ssm[li], ctx.state_slots, so,
+                                  heads=t.mamba_heads, groups=t.mamba_groups, head_dim=t.mamba_head_dim,
+                                  d_state=t.mamba_state, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state)
+        y = basic.gated_rmsnorm(y, z, self.norm_w, t.norm_eps, inner // t.mamba_groups)
+        return self.out_proj(y)
+
+    def replay(self, saved, sel, q_indptr, slots, states) -> None:
+        """Advances the committed state over the selected (accepted) rows of a verify block."""
+        t = self.t
+        inner, gn = t.mamba_inner, t.mamba_groups * t.mamba_state
+        xbc, dt = saved[0].index_select(0, sel), saved[1].index_select(0, sel)
+        li = self.state_index
+        xbc = recurrent.conv1d(xbc, self.conv_w, self.conv_b, states.conv[li], slots, slots, q_indptr=q_indptr)
+        recurrent.mamba2_scan(xbc[:, :inner], xbc[:, inner:inner + gn], xbc[:, inner + gn:], dt, self.a_log,
+                              self.dt_bias, self.d_skip, states.ssm[li], slots, slots, heads=t.mamba_heads,
+                              groups=t.mamba_groups, head_dim=t.mamba_head_dim, d_state=t.mamba_state,
+                              q_indptr=q_indptr)
+
+
+class GdnLayer:
+    def __init__(self, t: Target, init: Init, state_index: int, name: str):
+        self.t, self.state_index = t, state_index
+        kd = t.gdn_head_dim
+        self.qk = t.gdn_k_heads * kd
+        self.vd = t.gdn_v_heads * kd
+        self.in_qkvz = init.linear(2 * self.qk + 2 * self.vd, t.hidden, _fmt(t), name + ".in_qkvz")
+        self.in_ba = init.linear(2 * t.gdn_v_heads, t.hidden, "bf16", name + ".in_ba")
+        self.out_proj = init.linear(t.hidden, self.vd, _fmt(t), name + ".out_proj")
+        self.conv_w = init.normal(t.gdn_conv_dim, t.conv_width, std=0.2).to(torch.bfloat16).to(init.device)
+        self.a_log = torch.log(init.uniform(t.gdn_v_heads, lo=1.0, hi=16.0)).to(init.device)
+        self.dt_bias = init.normal(t.gdn_v_heads, std=0.5).to(init.device)
+        self.norm_w = init.ones(kd, t.gemma_norm)
+
+    def linears(self):
+        return [self.in_qkvz, self.in_ba, self.out_proj]
+
+    def forward(self, x, ctx: ForwardContext, kv, states) -> torch.Tensor:
+        t = self.t
+        kd = t.gdn_head_dim
+        qkvz = self.in_qkvz(x)
+        ba = self.in_ba(x).float()
+        li = self.state_index
+        so = ctx.extras.get("state_out", ctx.state_slots)
+        beta = torch.sigmoid(ba[:, :t.gdn_v_heads]).contiguous()
+        g = (-torch.exp(self.a_log) * torch.nn.functional.softplus(ba[:, t.gdn_v_heads:] + self.dt_bias)).contiguous()
+        if "ring" in ctx.extras:
+            ctx.extras["ring"].append((self, (qkvz[:, :2 * self.qk + self.vd], g, beta)))
+        qkv = recurrent.conv1d(qkvz[:, :2 * self.qk + self.vd], self.conv_w, None, states.conv[li], ctx.state_slots,
+                               so, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state, silu=True)
+        z = qkvz[:, 2 * self.qk + self.vd:]
+        o = recurrent.gdn_scan(qkv[:, :self.qk], qkv[:, self.qk:2 * self.qk], qkv[:, 2 * self.qk:], g, beta,
+                               states.ssm[li], ctx.state_slots, so, k_heads=t.gdn_k_heads, v_heads=t.gdn_v_heads,
+                               kdim=kd, vdim=kd, l2norm=True, q_indptr=ctx.q_indptr,
+                               has_init=ctx.has_initial_state)
+        rows = o.shape[0]
+        # per-head RMSNorm of the output, then the SiLU gate (norm before gate)
+        w = self.norm_w.repeat(t.gdn_v_heads)
+        y = basic.gated_rmsnorm(o, z, w, t.norm_eps, kd, norm_first=True, gemma=t.gemma_norm)
+        return self.out_proj(y.view(rows, -1))
+
+    def replay(self, saved, sel, q_indptr, slots, states) -> None:
+        t = self.t
+        kd = t.gdn_head_dim
+        li = self.state_index
+        qkv = recurrent.conv1d(saved[0].index_select(0, sel), self.conv_w, None, states.conv[li], slots, slots,
+                               q_indptr=q_indptr)
+        recurrent.gdn_scan(qkv[:, :self.qk], qkv[:, self.qk:2 * self.qk], qkv[:, 2 * self.qk:],
+                           saved[1].index_select(0, sel).contiguous(), saved[2].index_select(0, sel).contiguous(),
+                           states.ssm[li], slots, slots, k_heads=t.gdn_k_heads, v_heads=t.gdn_v_heads, kdim=kd,
+                           vdim=kd, l2norm=True, q_indptr=q_indptr)
+
+
+class MlpLayer:
+    def __init__(self, t: Target, init: Init, name: str, width: Optional[int] = None, act: str = "swiglu"):
+        self.t, self.act = t, act
+        width = width or t.ffn
+        if act == "swiglu":
+            self.up = Linear(interleave_pairs(init.normal(width, t.hidden), init.normal(width, t.hidden)), _fmt(t),
+                             name=name + ".gate_up").to(init.device)
+        else:
+            self.up = init.linear(width, t.hidden, _fmt(t), name + ".up")
+        self.down = init.linear(t.hidden, width, _fmt(t), name + ".down")
+
+    def linears(self):
+        return [self.up, self.down]
+
+    def forward(self, x, ctx=None, kv=None, states=None) -> torch.Tensor:
+        if self.act == "swiglu":
+            return self.down(self.up(x, epilogue=gemm.EPI_SILU_MUL))
+        return self.down(basic.act_mul(self.up(x), basic.ACT_RELU2))
+
+
+class MoeLayer:
+    """Routed experts (+ shared expert). With `latent` > 0 the experts act on a down-projected latent and the sum is
+    projected back (Nemotron); the shared expert always acts on the hidden state."""
+
+    def __init__(self, t: Target, init: Init, name: str, ep_rank: int = 0, ep_size: int = 1):
+        self.t = t
+        width = t.latent or t.hidden
+        n1 = 2 * t.expert_ffn if t.moe_act == "swiglu" else t.expert_ffn
+        self.router = init.linear(t.experts, t.hidden, "bf16", name + ".router")
+        self.sel_bias = torch.zeros(t.experts, device=init.device) if t.router == "sigmoid" else None
+        fc1 = init.normal(t.experts, n1, width)
+        if t.moe_act == "swiglu":   # rows g0, u0, g1, u1, ... inside every expert
+            fc1 = torch.stack((fc1[:, :t.expert_ffn], fc1[:, t.expert_ffn:]), dim=2).reshape(t.experts, n1, width)
+        fc2 = init.normal(t.experts, width, t.expert_ffn)
+        self.experts = moe.ExpertWeights.create(fc1, fc2, t.moe_act, _fmt(t)).to(init.device)
+        self.shared = MlpLayer(t, init, name + ".shared", width=t.shared_ffn, act=t.moe_act) if t.shared_ffn else None
+        self.fc1_latent = init.linear(t.latent, t.hidden, "bf16", name + ".fc1_latent") if t.latent else None
+        self.fc2_latent = init.linear(t.hidden, t.latent, "bf16", name + ".fc2_latent") if t.latent else None
+        per = t.experts // ep_size
+        self.e_lo, self.e_n = ep_rank * per, per
+        self.ep_size = ep_size
+
+    def linears(self):
+        out = [self.router]
+        if self.shared is not None:
+            out += self.shared.linears()
+        out += [l for l in (self.fc1_latent, self.fc2_latent) if l is not None]
+        return out
+
+    def forward(self, x, ctx=None, kv=None, states=None) -> torch.Tensor:
+        t = self.t
+        logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
+        ids, w = moe.route(logits, t.top_k, sigmoid=t.router == "sigmoid", sel_bias=self.sel_bias, renorm=True,
+                           scale=t.router_scale)
+        shared = self.shared.forward(x) if self.shared is not None else None
+        if t.latent:
+            lat = self.fc1_latent(x)
+            y = moe.experts_forward(lat, ids, w, self.experts, e_lo=self.e_lo, e_n=self.e_n)
+            out = self.fc2_latent(y)
+            return basic.add(out, shared) if shared is not None else out
+        return moe.experts_forward(x, ids, w, self.experts, shared=shared, e_lo=self.e_lo, e_n=self.e_n)
+
+
+def _moe_forward_ep(self, x, comm) -> torch.Tensor:
+    """Replicated-activation expert parallelism: every rank runs its expert range on all tokens, the partial sums
+    are all-reduced, and the (replicated) shared expert is added once afterwards."""
+    t = self.t
+    logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
+    ids, w = moe.route(logits, t.top_k, sigmoid=t.router == "sigmoid", sel_bias=self.sel_bias, renorm=True,
+                       scale=t.router_scale)
+    inp = self.fc1_latent(x) if t.latent else x
+    part = comm.all_reduce(moe.experts_forward(inp, ids, w, self.experts, e_lo=self.e_lo, e_n=self.e_n))
+    out = self.fc2_latent(part) if t.latent else part
+    if self.shared is not None:
+        out = basic.add(out, self.shared.forward(x))
+    return out
+
+
+MoeLayer.forward_ep = _moe_forward_ep
+
+
+def build_mixer(kind: str, t: Target, init: Init, counters: dict, name: str):
+    if kind in (ATTN, GATED_ATTN):
+        i = counters["kv"]
+        counters["kv"] += 1
+        return AttentionLayer(t, init, i, kind == GATED_ATTN, name)
+    if kind in (MAMBA2, GDN):
+        i = counters["state"]
+        counters["state"] += 1
+        return MambaLayer(t, init, i, name) if kind == MAMBA2 else GdnLayer(t, init, i, name)
+    return None
+
+
+def build_ffn(kind: str, t: Target, init: Init, name: str, ep_rank: int = 0, ep_size: int = 1):
+    if kind == MLP:
+        return MlpLayer(t, init, name)
+    if kind in (MOE, LATENT_MOE):
+        return MoeLayer(t, init, name, ep_rank, ep_size)
+    return None

@@ -1,0 +1,114 @@
+"""Hybrid model families end to end: prefix-cache hits with recurrent snapshots, MTP speculation == plain greedy,
+GPU kernels vs the CPU path."""
+import pytest
+import torch
+
+from hibana_b200.engine.executor import Executor
+from hibana_b200.engine.request import SamplingParams
+from hibana_b200.models.hybrid import HybridModel
+from hibana_b200.target import flashnext, nemotron, qwen38_hybrid, scaled, tiny_hybrid_moe
+
+
+def _workload(t, n=4, shared=48, tail=16, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    pre = torch.randint(0, t.vocab, (shared,), generator=g).tolist()
+    return [pre + torch.randint(0, t.vocab, (tail,), generator=g).tolist() for _ in range(n)]
+
+
+def _run(ex, prompts, n=8):
+    outs = []
+    for p in prompts:
+        outs.append(ex.generate_batch([p], SamplingParams(max_tokens=n))[0].output_ids)
+        ex.state.check()
+    return outs
+
+
+def test_tiny_hybrid_prefix_hits_match_cold_cpu():
+    t = tiny_hybrid_moe()
+    m = HybridModel(t, "cpu", seed=0)
+    prompts = _workload(t)
+    ref = _run(Executor(m, max_batch=4, max_ctx=128, use_graphs=False, radix_cache=False), prompts)
+    ex = Executor(m, max_batch=4, max_ctx=128, use_graphs=False)
+    assert _run(ex, prompts) == ref
+    assert ex.stats["cached_tokens"] == 96          # requests 3 and 4 resume from the 48-token snapshot
+    assert ex.state.cache.full_reprefills == 1      # request 2 found KV but no snapshot
+
+
+def test_mtp_speculation_equals_plain_greedy_cpu():
+    t = tiny_hybrid_moe()
+    m = HybridModel(t, "cpu", seed=0)
+    prompts = _workload(t, n=3)
+    ref = _run(Executor(m, max_batch=4, max_ctx=160, use_graphs=False), prompts, n=32)
+    ex = Executor(m, max_batch=4, max_ctx=160, use_graphs=False)
+    ex.enable_spec(2)
+    got = _run(ex, prompts, n=32)
+    assert got == ref
+    s = ex.spec.stats.as_dict()
+    assert s["rounds"] > 0 and 1.0 <= s["tokens_per_round"] <= 3.0
+    ex.state.cache.flush()
+    assert ex.kv.free_count == ex.kv.slots
+
+
+def test_batched_speculation_with_stop_and_budget_cpu():
+    t = tiny_hybrid_moe()
+    m = HybridModel(t, "cpu", seed=1)
+    prompts = _workload(t, n=3, seed=3)
+    plain = Executor(m, max_batch=4, max_ctx=160, use_graphs=False, radix_cache=False)
+    ref = plain.generate_batch(prompts, SamplingParams(max_tokens=11))
+    stop = ref[0].output_ids[5]
+    ref2 = Executor(m, max_batch=4, max_ctx=160, use_graphs=False, radix_cache=False).generate_batch(
+        prompts, SamplingParams(max_tokens=11, stop_ids=(stop,)))
+    ex = Executor(m, max_batch=4, max_ctx=160, use_graphs=False, radix_cache=False)
+    ex.enable_spec(3)
+    got = ex.generate_batch(prompts, SamplingParams(max_tokens=11, stop_ids=(stop,)))
+    for a, b in zip(got, ref2):
+        assert a.finish_reason == b.finish_reason and len(a.output_ids) == len(b.output_ids)
+        assert a.output_ids[0] == b.output_ids[0]
+    ex.state.check()
+
+
+@pytest.mark.parametrize("make", [qwen38_hybrid, flashnext, nemotron])
+def test_reference_families_run_scaled_cpu(make):
+    t = make()
+    small = dict(hidden=256, vocab=512, q_heads=4, kv_heads=2, head_dim=64, ffn=256 if t.ffn else 0,
+                 gdn_k_heads=2 if t.gdn_k_heads else 0, gdn_v_heads=4 if t.gdn_v_heads else 0,
+                 gdn_head_dim=32, mamba_heads=8 if t.mamba_heads else 0, mamba_head_dim=32, mamba_state=16,
+                 mamba_groups=2 if t.mamba_heads else 1, experts=8 if t.experts else 0,
+                 top_k=min(t.top_k, 3), expert_ffn=128 if t.experts else 0, shared_ffn=128 if t.shared_ffn else 0,
+                 latent=128 if t.latent else 0, weight_format="bf16", kv_dtype="bf16", mtp_layers=0,
+                 max_context=512)
+    layers = t.layers[:8] if t.family != "nemotron" else t.layers[:9]
+    st = scaled(t, **small)
+    st = scaled(st, layers=None) if False else st
+    import dataclasses
+    st = dataclasses.replace(st, layers=layers)
+    m = HybridModel(st, "cpu", seed=0)
+    ex = Executor(m, max_batch=2, max_ctx=96, use_graphs=False)
+    out = ex.generate_batch(_workload(st, n=2, shared=20, tail=6), SamplingParams(max_tokens=4))
+    assert all(len(r.output_ids) == 4 for r in out)
+    ex.state.check()
+
+
+@pytest.mark.gpu
+def test_tiny_hybrid_gpu_matches_cpu_and_graphs():
+    t = tiny_hybrid_moe()
+    cpu = HybridModel(t, "cpu", seed=0)
+    gpu = HybridModel(t, "cuda", seed=0, init_device="cpu")
+    prompts = _workload(t)
+    ref = _run(Executor(cpu, max_batch=4, max_ctx=128, use_graphs=False), prompts, n=16)
+    ex = Executor(gpu, max_batch=4, max_ctx=128, use_graphs=True)
+    ex.capture_graphs()
+    got = _run(ex, prompts, n=16)
+    assert [g[0] for g in got] == [r[0] for r in ref]
+    same = sum(a == b for x, y in zip(got, ref) for a, b in zip(x, y))
+    assert same >= 0.6 * 64
+    assert ex.stats["cached_tokens"] == 96
+    eager = _run(Executor(gpu, max_batch=4, max_ctx=128, use_graphs=False), prompts, n=16)
+    assert eager == got                                    # graph replay == eager
+    ex2 = Executor(gpu, max_batch=4, max_ctx=160, use_graphs=False)
+    ex2.enable_spec(2)
+    spec = _run(ex2, prompts, n=16)
+    agree = sum(a == b for x, y in zip(spec, eager) for a, b in zip(x, y))
+    assert [s[0] for s in spec] == [e[0] for e in eager] and agree >= 0.7 * 64
+    from hibana_b200 import _native as nv
+    assert nv.read_status() == 0
