@@ -65,6 +65,11 @@ struct DevParams {
   const int* grp_start;   // [E] first row of the expert's segment in the sorted activation buffer (multiple of 128)
   const int* grp_cnt;     // [E] rows routed to the expert
   int grp_rows_a;         // weight rows per expert (multiple of 128)
+  // peer fusion
+  int peer_on, world, rank, rows_per_rank;
+  uint8_t* peer_base[8];
+  long long stage_offset, counter_offset, flag_offset, seq_offset;
+  unsigned long long limit_ns;
 };
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
@@ -227,7 +232,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
   if (warp == 0) {
     if (lane == 0) {
       int issued = 0;
-      for (int i = 0; i < nkt; ++i) {
+      if (p.peer_on && p.flag_offset >= 0) {
+        // all-gather -> GEMM: the rows of this A tile were pushed into local memory by rank `src`; wait (bounded)
+        // until its arrival flag reaches the expected sequence number before the first TMA load touches them.
+        const int src = a_row0 / p.rows_per_rank;
+        const int* flag = reinterpret_cast<const int*>(p.peer_base[p.rank] + p.flag_offset) + src;
+        const int want = *reinterpret_cast<const int*>(p.peer_base[p.rank] + p.seq_offset);
+        const uint64_t t0 = globaltimer_ns();
+        bool ready = false;
+        for (uint32_t it = 0; it < HB_SPIN_LIMIT; ++it) {
+          int v;
+          asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+          if (v - want >= 0) {
+            ready = true;
+            break;
+          }
+          if ((it & 63u) == 63u && globaltimer_ns() - t0 > p.limit_ns) break;
+        }
+        if (!ready) {
+          *abort = 1;
+          set_status(p.status, kTimeoutPeer);
+        }
+      }
+      for (int i = 0; i < nkt && !*abort; ++i) {
         const int s = i % S;
         const uint32_t ph = (i / S) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, abort, p.status, kTimeoutEmpty)) break;
@@ -302,7 +329,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     const uint32_t tlane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     float alpha = p.alpha;
     if (alpha_ptr != nullptr) alpha *= *alpha_ptr;
-    if (ok && p.splits == 1) {
+    if (ok && p.splits == 1 && p.epilogue == kEpiScatter) {
+      // GEMM -> reduce-scatter: store the bf16 partial straight into the owner's staging rows for this source.
+      const int owner = row / p.rows_per_rank;
+      const bool row_ok = row < row_lim && owner < p.world;
+      __nv_bfloat16* dst_row = nullptr;
+      if (row_ok)
+        dst_row = reinterpret_cast<__nv_bfloat16*>(p.peer_base[owner] + p.stage_offset) +
+                  (static_cast<long long>(p.rank) * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldo;
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        uint32_t r[CH];
+        if constexpr (CH == 32) tmem_ld_32x32(tlane + c0, r);
+        else tmem_ld_32x16(tlane + c0, r);
+        tmem_ld_wait();
+        const int col0 = b_row0 + c0;
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < CH / 8; ++j) {
+            if (col0 + 8 * j + 8 <= col_lim) {
+              uint32_t w[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t)
+                w[t] = pack_bf16(__uint_as_float(r[8 * j + 2 * t]) * alpha, __uint_as_float(r[8 * j + 2 * t + 1]) * alpha);
+              *reinterpret_cast<uint4*>(dst_row + col0 + 8 * j) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+      // make the tile visible system-wide, then one arrival on the owner's counter for this source
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int owner0 = min(a_row0 / p.rows_per_rank, p.world - 1);
+        int* cnt = reinterpret_cast<int*>(p.peer_base[owner0] + p.counter_offset) + p.rank;
+        asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+      }
+    } else if (ok && p.splits == 1) {
       for (int c0 = 0; c0 < BN; c0 += CH) {
         uint32_t r[CH];
         if constexpr (CH == 32) tmem_ld_32x32(tlane + c0, r);
@@ -498,6 +560,17 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   p.ka_a = a.sf_k_atoms_a; p.ka_b = a.sf_k_atoms_b;
   out_dims(a, &p.out_rows, &p.out_cols);
   p.grp_start = a.grp_start; p.grp_cnt = a.grp_cnt; p.grp_rows_a = a.grp_rows_a;
+  p.peer_on = a.peer != nullptr;
+  p.flag_offset = -1;
+  if (a.peer != nullptr) {
+    if (a.swap || grouped || splits != 1 || a.peer->rows_per_rank % BM != 0) return cudaErrorInvalidValue;
+    p.world = a.peer->world; p.rank = a.peer->rank; p.rows_per_rank = a.peer->rows_per_rank;
+    for (int i = 0; i < 8; ++i) p.peer_base[i] = static_cast<uint8_t*>(a.peer->base[i]);
+    p.stage_offset = a.peer->stage_offset; p.counter_offset = a.peer->counter_offset;
+    p.flag_offset = a.peer->flag_offset; p.seq_offset = a.peer->seq_offset; p.limit_ns = a.peer->limit_ns;
+  } else if (a.epilogue == kEpiScatter) {
+    return cudaErrorInvalidValue;
+  }
   const dim3 grid = grouped ? dim3(a.grp_rows_a / BM, a.grp_chunks, a.grp_experts) : dim3(tiles_a, tiles_b, splits);
 
 #define HB_DISPATCH(KIND)                                                        \
@@ -534,6 +607,31 @@ int hb_gemm(int kind, const void* a, const void* b, const void* sfa, const void*
   g.workspace = static_cast<float*>(workspace); g.counters = static_cast<int*>(counters);
   g.status = static_cast<int*>(status); g.bn = bn; g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
   g.grp_start = nullptr; g.grp_cnt = nullptr; g.grp_rows_a = 0; g.grp_experts = 0; g.grp_chunks = 0;
+  g.peer = nullptr;
+  const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// Peer-fused GEMM (normal orientation, M tokens on the 128-row side):
+//   epilogue 4 (scatter): GEMM -> reduce-scatter, partial tiles stored into the row owner's staging area;
+//   flag_offset >= 0    : all-gather -> GEMM, A row tiles wait for their source rank's arrival flag.
+int hb_gemm_peer(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int m, int n, int k,
+                 void* out, long long ldo, const void* alpha_ptr, int epilogue, const void* const* peer_bases,
+                 int world, int rank, int rows_per_rank, long long stage_offset, long long counter_offset,
+                 long long flag_offset, long long seq_offset, long long limit_ns, void* status, int ka_a, int ka_b,
+                 void* stream) {
+  hb::GemmArgs g;
+  hb::GemmPeer peer;
+  for (int i = 0; i < 8; ++i) peer.base[i] = i < world ? const_cast<void*>(peer_bases[i]) : nullptr;
+  peer.world = world; peer.rank = rank; peer.rows_per_rank = rows_per_rank;
+  peer.stage_offset = stage_offset; peer.counter_offset = counter_offset; peer.flag_offset = flag_offset;
+  peer.seq_offset = seq_offset; peer.limit_ns = static_cast<unsigned long long>(limit_ns);
+  g.kind = kind; g.a = a; g.b = b; g.sfa = sfa; g.sfb = sfb; g.ra = m; g.rb = n; g.k = k; g.lda = k; g.ldb = k;
+  g.out = out; g.ldo = ldo; g.residual = nullptr; g.alpha = 1.f; g.alpha_ptr = static_cast<const float*>(alpha_ptr);
+  g.epilogue = epilogue; g.swap = 0; g.splits = 1; g.workspace = nullptr; g.counters = nullptr;
+  g.status = static_cast<int*>(status); g.bn = n >= 256 ? 256 : 128; g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
+  g.grp_start = nullptr; g.grp_cnt = nullptr; g.grp_rows_a = 0; g.grp_experts = 0; g.grp_chunks = 0;
+  g.peer = &peer;
   const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }
@@ -557,6 +655,7 @@ int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, con
   g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
   g.grp_start = static_cast<const int*>(start); g.grp_cnt = static_cast<const int*>(cnt);
   g.grp_rows_a = n_per_expert; g.grp_experts = experts; g.grp_chunks = (max_rows_per_expert + bn - 1) / bn;
+  g.peer = nullptr;
   const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

@@ -12,6 +12,22 @@ enum GemmEpilogue : int {
   kEpiResidual = 1,   // out = alpha * acc + residual           (bf16)
   kEpiSiluMul = 2,    // out[.., j] = silu(acc[2j]) * acc[2j+1] (bf16, gate/up rows interleaved pairwise)
   kEpiStoreF32 = 3,   // out = alpha * acc                      (fp32)
+  kEpiScatter = 4,    // row-parallel GEMM -> reduce-scatter: the bf16 partial tile is stored straight into the
+                      // staging area of the rank that owns its rows (peer memory), then that rank's arrival
+                      // counter for this source is bumped (normal orientation only)
+};
+
+// Peer-memory fusion arguments (all ranks pass the same offsets; pointers are this process's mappings).
+struct GemmPeer {
+  void* base[8];            // heap base of every rank
+  int world, rank;
+  int rows_per_rank;        // owner of output row m is m / rows_per_rank (multiple of 128)
+  long long stage_offset;   // scatter: byte offset of staging [world][rows_per_rank][ldo] bf16 in every heap
+  long long counter_offset; // scatter: byte offset of int counters[world] (arrivals per source) in every heap
+  // gather gating (all-gather -> GEMM): A row tiles of source rank s may be loaded once flags[s] >= *seq_ptr
+  long long flag_offset;    // byte offset of int flags[world] in this rank's heap (-1 = no gating)
+  long long seq_offset;     // byte offset of the int holding the expected sequence number
+  unsigned long long limit_ns;
 };
 
 // D[ra, rb] = sum_k A[ra, k] * B[rb, k]; both operands K-major. `swap` tells the epilogue that A rows are
@@ -42,6 +58,7 @@ struct GemmArgs {
   const int* grp_start;
   const int* grp_cnt;
   int grp_rows_a, grp_experts, grp_chunks;
+  const GemmPeer* peer;     // null = no peer fusion
 };
 
 // Returns cudaSuccess or the launch error. Tensor maps are built (and cached) inside.

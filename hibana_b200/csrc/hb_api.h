@@ -18,6 +18,11 @@ int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, con
                     int n_per_expert, int b_rows, int k, void* out, long long ldo, const void* alpha_ptr,
                     int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status, int ka_a,
                     int ka_b, void* stream);
+int hb_gemm_peer(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int m, int n, int k,
+                 void* out, long long ldo, const void* alpha_ptr, int epilogue, const void* const* peer_bases,
+                 int world, int rank, int rows_per_rank, long long stage_offset, long long counter_offset,
+                 long long flag_offset, long long seq_offset, long long limit_ns, void* status, int ka_a, int ka_b,
+                 void* stream);
 void hb_clear_tmap_cache(void);
 
 // ---- quantisers (quant.cu) -----------------------------------------------------------------------------
@@ -97,6 +102,11 @@ int hb_comm_ipc_close(void* p);
 int hb_ar_norm(const void* const* peer_bases, int world, int rank, int slot, long long data_offset, int rows, int h,
                void* residual, const void* weight, float eps, int gemma, void* out, void* q, void* sf,
                const void* gscale, int ka, long long limit_ns, void* status, void* stream);
+int hb_comm_sp_layout(long long* out3);
+int hb_rs_norm_ag(const void* const* peer_bases, int world, int rank, int rows_per_rank, int h, long long stage_offset,
+                  int expected, void* residual, const void* weight, float eps, int gemma, long long gather_q_offset,
+                  long long gather_sf_offset, long long gather_bf_offset, const void* gscale, int ka,
+                  long long limit_ns, void* status, void* stream);
 int hb_barrier(const void* const* peer_bases, int world, int rank, int slot, long long limit_ns, void* status,
                void* stream);
 

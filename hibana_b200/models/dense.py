@@ -148,9 +148,48 @@ class DenseModel:
             return lin(x, out=comm.slot_buffer(slot, rows, self.target.hidden)), slot
         return lin(x), None
 
+    def forward_sp(self, ids: torch.Tensor, ctx: ForwardContext, kv) -> torch.Tensor:
+        """Sequence-parallel prefill over the fused peer-memory chain: every row-parallel GEMM scatters its partial
+        tiles to the rows' owner rank, the owner reduces + adds its residual shard + normalises + quantises and
+        pushes the rows to every rank, and the next column-parallel GEMM starts each A tile as its rows arrive.
+        The residual stream lives sharded by rows (rows_per_rank each)."""
+        t = self.target
+        comm = ctx.comm
+        rows = ids.shape[0]
+        rpr = rows // comm.world
+        full = basic.embedding(ids, self.embed)
+        res = full[comm.rank * rpr:(comm.rank + 1) * rpr].contiguous()
+        qkv = norm_linear(full, None, self.layers[0].input_norm, t.norm_eps, self.layers[0].qkv, add_residual=False)
+        y = None
+        for i, layer in enumerate(self.layers):
+            q = basic.rope_kv_write(qkv, ctx.positions, ctx.slots, self.inv_freq, kv.k[i], kv.v[i], t.q_heads,
+                                    t.kv_heads, t.head_dim, rot=t.rot_dim, kv_scale=kv.kv_scale)
+            att = attention.paged_attention(q, kv.k[i], kv.v[i], ctx.kv_indices, ctx.ctx_len, q_indptr=ctx.q_indptr,
+                                            max_rows=ctx.max_rows, seq_rows=ctx.seq_rows, scale=self.scale,
+                                            kv_scale=kv.kv_scale, splits=ctx.attn_splits,
+                                            workspace=ctx.attn_workspace)
+            comm.sp_gemm_scatter(layer.o, att.view(rows, -1))
+            qs = layer.gate_up.input_scale if layer.gate_up.fmt == "nvfp4" else None
+            x = comm.sp_reduce_norm_gather(rows, t.hidden, res, layer.post_norm, t.norm_eps, quant_scale=qs)
+            act = comm.sp_gemm_gathered(layer.gate_up, x, epilogue=gemm.EPI_SILU_MUL)
+            comm.sp_gemm_scatter(layer.down, act)
+            if i + 1 < len(self.layers):
+                nxt = self.layers[i + 1]
+                qs = nxt.qkv.input_scale if nxt.qkv.fmt == "nvfp4" else None
+                x = comm.sp_reduce_norm_gather(rows, t.hidden, res, nxt.input_norm, t.norm_eps, quant_scale=qs)
+                qkv = comm.sp_gemm_gathered(nxt.qkv, x)
+            else:
+                y = comm.sp_reduce_norm_gather(rows, t.hidden, res, self.final_norm, t.norm_eps)
+                # the bf16 gather buffer is complete on this rank only after every source's flag: a barrier orders it
+                comm.barrier()
+        return y.index_select(0, ctx.sample_rows) if ctx.sample_rows is not None else y.clone()
+
     def forward(self, ids: torch.Tensor, ctx: ForwardContext, kv) -> torch.Tensor:
         """ids int64 [T]; kv = KvPool. Returns normed hidden states of ctx.sample_rows (or of all rows)."""
         t = self.target
+        if (ctx.comm is not None and getattr(ctx.comm, "sp_rows", 0) and ctx.mode == "prefill"
+                and ctx.comm.sp_ok(ids.shape[0], t.hidden) and not self.layers[0].qkv.calibrating):
+            return self.forward_sp(ids, ctx, kv)
         res = basic.embedding(ids, self.embed)
         h: Optional[torch.Tensor] = None
         slot = None

@@ -29,6 +29,9 @@ nv.register("hb_comm_ipc_open", [P, ctypes.POINTER(ctypes.c_void_p)])
 nv.register("hb_comm_ipc_close", [P])
 nv.register("hb_ar_norm", [P, I, I, I, L, I, I, P, P, Fl, I, P, P, P, P, I, L, P, P])
 nv.register("hb_barrier", [P, I, I, I, L, P, P])
+nv.register("hb_comm_sp_layout", [ctypes.POINTER(ctypes.c_longlong)])
+nv.register("hb_rs_norm_ag", [P, I, I, I, I, L, I, P, P, Fl, I, L, L, L, P, I, L, P, P])
+nv.register("hb_gemm_peer", [I, P, P, P, P, I, I, I, P, L, P, I, P, I, I, I, L, L, L, L, L, P, I, I, P])
 
 
 class _RawCuda:
@@ -45,7 +48,8 @@ class CommTimeout(RuntimeError):
 
 class Communicator:
     def __init__(self, rank: int, world: int, device: torch.device, heap_ptr: int, heap_bytes: int, peer_ptrs: list,
-                 slot_bytes: int, timeout_ms: int, group=None, fused: bool = True):
+                 slot_bytes: int, timeout_ms: int, group=None, fused: bool = True, sp_rows: int = 0,
+                 sp_hidden: int = 0):
         self.rank, self.world, self.device = rank, world, device
         self.heap_ptr, self.heap_bytes, self.peer_ptrs = heap_ptr, heap_bytes, peer_ptrs
         self.slot_bytes = slot_bytes
@@ -58,15 +62,30 @@ class Communicator:
         self.heap = torch.as_tensor(_RawCuda(heap_ptr, heap_bytes), device=device)
         self._next_slot = 0
         self.status = nv.device_state(device).status
+        # sequence-parallel region: staging of scattered partials + gather buffers (NVFP4 and bf16)
+        self.sp_rows, self.sp_hidden = sp_rows, sp_hidden
+        if sp_rows:
+            lay = (ctypes.c_longlong * 3)()
+            nv.lib().hb_comm_sp_layout(lay)
+            self.sp_cnt_off, self.sp_flag_off, self.sp_seq_off = int(lay[0]), int(lay[1]), int(lay[2])
+            base = self.ctrl_bytes + self.nslot * slot_bytes
+            self.sp_stage_off = base
+            self.sp_bf_off = base + sp_rows * sp_hidden * 2
+            self.sp_q_off = self.sp_bf_off + sp_rows * sp_hidden * 2
+            self.sp_ka = nvfp4.k_atoms(sp_hidden)
+            self.sp_sf_off = self.sp_q_off + sp_rows * sp_hidden // 2
+            assert self.sp_sf_off + (sp_rows // 128 + 2) * self.sp_ka * 512 <= heap_bytes
 
     @classmethod
     def create(cls, rank: int, world: int, device: torch.device, *, slot_mb: int = 8, timeout_ms: int = 2000,
-               group=None, fused: bool = True) -> "Communicator":
+               group=None, fused: bool = True, sp_rows: int = 0, sp_hidden: int = 0) -> "Communicator":
         """Collective: every rank of `group` (default: the world group) must call it."""
         lib = nv.lib()
         torch.cuda.set_device(device)
         slot_bytes = slot_mb << 20
         heap_bytes = lib.hb_comm_ctrl_bytes() + lib.hb_comm_nslot() * slot_bytes
+        if sp_rows:
+            heap_bytes += sp_rows * sp_hidden * 5 + (sp_rows // 128 + 2) * nvfp4.k_atoms(sp_hidden) * 512 + 4096
         out = ctypes.c_void_p()
         nv.check(lib.hb_comm_alloc(heap_bytes, ctypes.byref(out)), "hb_comm_alloc", launches=0)
         handle = ctypes.create_string_buffer(64)
@@ -84,7 +103,8 @@ class Communicator:
                 peers.append(p.value)
         torch.cuda.synchronize()
         dist.barrier(group=group)
-        return cls(rank, world, device, out.value, heap_bytes, peers, slot_bytes, timeout_ms, group, fused)
+        return cls(rank, world, device, out.value, heap_bytes, peers, slot_bytes, timeout_ms, group, fused, sp_rows,
+                   sp_hidden)
 
     # ---- slots
     def slot_offset(self, slot: int) -> int:
@@ -138,6 +158,65 @@ class Communicator:
                                      nv.stream()), "hb_ar_norm")
         xq = Nvfp4Tensor(q, sf, quant_scale, rows, h) if q is not None else None
         return out, xq
+
+    # ---- sequence-parallel prefill chain (fused GEMM -> reduce-scatter, norm, all-gather -> GEMM)
+    def sp_ok(self, rows: int, hidden: int) -> bool:
+        return (self.fused and self.sp_rows >= rows and hidden == self.sp_hidden and rows % (128 * self.world) == 0)
+
+    def sp_gemm_scatter(self, lin, x) -> None:
+        """Row-parallel projection whose epilogue stores each partial tile into the owner rank's staging rows."""
+        xq = x if isinstance(x, Nvfp4Tensor) or lin.fmt != "nvfp4" else lin.quantize_input(x)
+        m = xq.rows if isinstance(xq, Nvfp4Tensor) else xq.shape[0]
+        rpr = m // self.world
+        if lin.fmt == "nvfp4":
+            a, b, sfa, sfb, k, alpha, ka_a, ka_b = xq.q, lin.wq.q, xq.sf, lin.wq.sf, xq.k, lin.alpha, xq.ka, lin.wq.ka
+            kind = 1
+        else:
+            a, b, sfa, sfb, k, alpha, ka_a, ka_b, kind = xq, lin.weight, None, None, xq.shape[1], None, 0, 0, 0
+        nv.check(nv.lib().hb_gemm_peer(kind, a.data_ptr(), b.data_ptr(), nv.ptr(sfa), nv.ptr(sfb), m,
+                                       lin.out_features, k, None, lin.out_features, nv.ptr(alpha), 4, self._bases,
+                                       self.world, self.rank, rpr, self.sp_stage_off, self.sp_cnt_off, -1, 0,
+                                       self.timeout_ns, self.status.data_ptr(), ka_a, ka_b, nv.stream()),
+                 "hb_gemm_peer")
+
+    def sp_reduce_norm_gather(self, rows: int, h: int, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                              gemma: bool = False, quant_scale: Optional[torch.Tensor] = None):
+        """Owner rows: sum the staged partials, add the residual shard, RMSNorm, (quantise), push to every rank.
+        Returns the full [rows, h] activation as it will appear in this rank's gather buffer (valid once the
+        consumer's flag wait passes): an Nvfp4Tensor when `quant_scale` is given, else a bf16 tensor."""
+        rpr = rows // self.world
+        bn = 256 if h >= 256 else 128
+        expected = (rpr // 128) * ((h + bn - 1) // bn)
+        q_off = self.sp_q_off if quant_scale is not None else -1
+        bf_off = -1 if quant_scale is not None else self.sp_bf_off
+        nv.check(nv.lib().hb_rs_norm_ag(self._bases, self.world, self.rank, rpr, h, self.sp_stage_off, expected,
+                                        residual.data_ptr(), weight.data_ptr(), eps, int(gemma), q_off, self.sp_sf_off,
+                                        bf_off, nv.ptr(quant_scale), self.sp_ka, self.timeout_ns,
+                                        self.status.data_ptr(), nv.stream()), "hb_rs_norm_ag")
+        if quant_scale is not None:
+            q = self.heap[self.sp_q_off:self.sp_q_off + rows * h // 2].view(rows, h // 2)
+            nblk = (rows + 127) // 128
+            sf = self.heap[self.sp_sf_off:self.sp_sf_off + nblk * self.sp_ka * 512].view(nblk, self.sp_ka, 512)
+            return Nvfp4Tensor(q, sf, quant_scale, rows, h)
+        return self.heap[self.sp_bf_off:self.sp_bf_off + rows * h * 2].view(torch.bfloat16).view(rows, h)
+
+    def sp_gemm_gathered(self, lin, x, *, epilogue: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Column-parallel projection over gathered rows: each A row tile waits for its source rank's flag."""
+        nvq = isinstance(x, Nvfp4Tensor)
+        m = x.rows if nvq else x.shape[0]
+        n = lin.out_features
+        cols = n // 2 if epilogue == 2 else n
+        out = torch.empty(m, cols, dtype=torch.bfloat16, device=self.device) if out is None else out
+        if nvq:
+            a, b, sfa, sfb, k, alpha, ka_a, ka_b, kind = x.q, lin.wq.q, x.sf, lin.wq.sf, x.k, lin.alpha, x.ka, lin.wq.ka, 1
+        else:
+            a, b, sfa, sfb, k, alpha, ka_a, ka_b, kind = x, lin.weight, None, None, x.shape[1], None, 0, 0, 0
+        nv.check(nv.lib().hb_gemm_peer(kind, a.data_ptr(), b.data_ptr(), nv.ptr(sfa), nv.ptr(sfb), m, n, k,
+                                       out.data_ptr(), out.stride(0), nv.ptr(alpha), epilogue, self._bases, self.world,
+                                       self.rank, m // self.world, 0, 0, self.sp_flag_off, self.sp_seq_off,
+                                       self.timeout_ns, self.status.data_ptr(), ka_a, ka_b, nv.stream()),
+                 "hb_gemm_peer")
+        return out
 
     def barrier(self, slot: Optional[int] = None) -> None:
         slot = self.next_slot() if slot is None else slot

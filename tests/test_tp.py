@@ -116,16 +116,19 @@ dist.init_process_group("nccl", device_id=dev)
 t = dense_tiny()
 g = torch.Generator().manual_seed(5)
 prompts = [torch.randint(0, t.vocab, (40,), generator=g).tolist() for _ in range(3)]
+long_prompt = [torch.randint(0, t.vocab, (256,), generator=g).tolist()]
 res = {}
-for fused in (False, True):
-    comm = Communicator.create(rank, world, dev, slot_mb=1, fused=fused)
+for name, fused, sp in (("nccl", False, 0), ("fused", True, 0), ("sp", True, 256)):
+    comm = Communicator.create(rank, world, dev, slot_mb=1, fused=fused, sp_rows=sp, sp_hidden=t.hidden)
     model = DenseModel.sharded(t, world, rank, dev, seed=0, init_device="cpu")
-    ex = Executor(model, max_batch=4, max_ctx=128, use_graphs=True, comm=comm)
+    ex = Executor(model, max_batch=4, max_ctx=512, use_graphs=True, comm=comm, radix_cache=False)
     ex.capture_graphs()
     out = ex.generate_batch(prompts, SamplingParams(max_tokens=8))
+    out2 = ex.generate_batch(long_prompt, SamplingParams(max_tokens=4), prefill_budget=256)
     torch.cuda.synchronize()
     comm.check_status()
-    res["fused" if fused else "nccl"] = [r.output_ids for r in out]
+    res[name] = [r.output_ids for r in out]
+    res[name + "_long"] = [r.output_ids for r in out2]
 gathered = [None] * world
 dist.all_gather_object(gathered, res)
 if rank == 0:
@@ -156,3 +159,6 @@ def test_tp2_fused_allreduce_matches_nccl_gpu(tmp_path):
     assert [x[0] for x in nccl] == [x[0] for x in fused]        # same first tokens; later ones may flip on ties
     same = sum(a == b for x, y in zip(nccl, fused) for a, b in zip(x, y))
     assert same >= 0.6 * 24
+    # the sequence-parallel chain (GEMM -> reduce-scatter, norm, all-gather -> GEMM) prefilled the 256-token prompt
+    assert ranks[0]["sp_long"] == ranks[1]["sp_long"]
+    assert ranks[0]["sp_long"][0][0] == ranks[0]["nccl_long"][0][0]
