@@ -75,12 +75,13 @@ __device__ __forceinline__ bool wait_peers(Ctrl* mine, int world, int slot, int 
     const unsigned long long t0 = globaltimer_ns();
     bool ok = false;
     for (unsigned it = 0; it < HB_SPIN_LIMIT; ++it) {
-      if (ld_acquire_sys(&mine->flags[slot][threadIdx.x]) - seq >= 0) {
+      if (ld_relaxed_sys(&mine->flags[slot][threadIdx.x]) - seq >= 0) {
         ok = true;
         break;
       }
       if ((it & 63u) == 63u && globaltimer_ns() - t0 > limit_ns) break;
     }
+    __threadfence_system();   // acquire: order the peer data reads after the flag observation
     if (!ok) {
       *ok_smem = 0;
       set_status(status, kTimeoutPeer);
@@ -274,12 +275,13 @@ __global__ void __launch_bounds__(T) rs_norm_ag_kernel(const RsNormAgParams p) {
     const unsigned long long t0 = globaltimer_ns();
     bool ok = false;
     for (unsigned it = 0; it < HB_SPIN_LIMIT; ++it) {
-      if (ld_acquire_sys(&mine->sp_cnt[threadIdx.x]) >= want) {
+      if (ld_relaxed_sys(&mine->sp_cnt[threadIdx.x]) >= want) {
         ok = true;
         break;
       }
       if ((it & 63u) == 63u && globaltimer_ns() - t0 > p.limit_ns) break;
     }
+    __threadfence_system();
     if (!ok) {
       ok_s = 0;
       set_status(p.status, kTimeoutPeer);
@@ -480,8 +482,8 @@ int hb_ar_norm(const void* const* peer_bases, int world, int rank, int slot, lon
     cudaFuncSetAttribute(ar_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     attr = true;
   }
-  const int grid = q ? ((rows + 127) / 128) * 128 : rows;
-  ar_norm_kernel<T><<<grid, T, h * sizeof(float), static_cast<cudaStream_t>(stream)>>>(p);
+  // The caller keeps persistent output buffers whose padding scale rows were zeroed once, so only real rows run.
+  ar_norm_kernel<T><<<rows, T, h * sizeof(float), static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

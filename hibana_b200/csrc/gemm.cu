@@ -329,40 +329,82 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     const uint32_t tlane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     float alpha = p.alpha;
     if (alpha_ptr != nullptr) alpha *= *alpha_ptr;
-    if (ok && p.splits == 1 && p.epilogue == kEpiScatter) {
-      // GEMM -> reduce-scatter: store the bf16 partial straight into the owner's staging rows for this source.
-      const int owner = row / p.rows_per_rank;
-      const bool row_ok = row < row_lim && owner < p.world;
-      __nv_bfloat16* dst_row = nullptr;
-      if (row_ok)
-        dst_row = reinterpret_cast<__nv_bfloat16*>(p.peer_base[owner] + p.stage_offset) +
-                  (static_cast<long long>(p.rank) * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldo;
+    if (ok && p.splits == 1 && !p.swap && p.epilogue != kEpiStoreF32 && BN >= 64 && (p.rb & 7) == 0 &&
+        (p.ldo & 7) == 0) {
+      // Staged epilogue (tokens on the 128-row side): every thread parks its row chunk as bf16 in shared memory
+      // (the stage ring is idle once the accumulator is complete), then each warp writes its 32 rows with
+      // fully coalesced 16-byte stores: to the local output, or (scatter) to the staging rows of the rank that
+      // owns them, over NVLink.
+      const bool silu_mul = p.epilogue == kEpiSiluMul;
+      constexpr int PITCH = BN * 2 + 16;
+      uint8_t* tile = smem + static_cast<size_t>(q) * 32 * PITCH;
+      uint8_t* my_row = tile + lane * PITCH;
       for (int c0 = 0; c0 < BN; c0 += CH) {
         uint32_t r[CH];
         if constexpr (CH == 32) tmem_ld_32x32(tlane + c0, r);
         else tmem_ld_32x16(tlane + c0, r);
         tmem_ld_wait();
-        const int col0 = b_row0 + c0;
-        if (row_ok) {
+        if (silu_mul) {
+          uint32_t w[CH / 4];
 #pragma unroll
-          for (int j = 0; j < CH / 8; ++j) {
-            if (col0 + 8 * j + 8 <= col_lim) {
-              uint32_t w[4];
+          for (int t = 0; t < CH / 4; ++t)
+            w[t] = pack_bf16(silu(__uint_as_float(r[4 * t]) * alpha) * (__uint_as_float(r[4 * t + 1]) * alpha),
+                             silu(__uint_as_float(r[4 * t + 2]) * alpha) * (__uint_as_float(r[4 * t + 3]) * alpha));
 #pragma unroll
-              for (int t = 0; t < 4; ++t)
-                w[t] = pack_bf16(__uint_as_float(r[8 * j + 2 * t]) * alpha, __uint_as_float(r[8 * j + 2 * t + 1]) * alpha);
-              *reinterpret_cast<uint4*>(dst_row + col0 + 8 * j) = make_uint4(w[0], w[1], w[2], w[3]);
+          for (int t = 0; t < CH / 16; ++t)
+            *reinterpret_cast<uint4*>(my_row + c0 + 16 * t) = make_uint4(w[4 * t], w[4 * t + 1], w[4 * t + 2], w[4 * t + 3]);
+        } else {
+          uint32_t w[CH / 2];
+#pragma unroll
+          for (int t = 0; t < CH / 2; ++t)
+            w[t] = pack_bf16(__uint_as_float(r[2 * t]) * alpha, __uint_as_float(r[2 * t + 1]) * alpha);
+#pragma unroll
+          for (int t = 0; t < CH / 8; ++t)
+            *reinterpret_cast<uint4*>(my_row + c0 * 2 + 16 * t) = make_uint4(w[4 * t], w[4 * t + 1], w[4 * t + 2], w[4 * t + 3]);
+        }
+      }
+      __syncwarp();
+      const int out_cols = silu_mul ? BN / 2 : BN;            // columns this tile produces
+      const int chunks = out_cols / 8;                          // 16-byte chunks per row
+      const int rows_per_instr = 32 / chunks > 0 ? 32 / chunks : 1;
+      const int col_base = silu_mul ? (b_row0 >> 1) : b_row0;   // first output column of the tile
+      const int col_end = silu_mul ? (col_lim >> 1) : col_lim;
+      for (int r0 = 0; r0 < 32; r0 += rows_per_instr) {
+        for (int cc = 0; cc < chunks; cc += 32) {
+          const int lr = r0 + (chunks >= 32 ? 0 : lane / chunks);
+          const int ch = chunks >= 32 ? cc + lane : lane % chunks;
+          const int grow = tile_a * BM + q * 32 + lr;
+          const int gcol = col_base + ch * 8;
+          if (lr < 32 && grow < row_lim && gcol + 8 <= col_end) {
+            uint4 v = *reinterpret_cast<const uint4*>(tile + lr * PITCH + ch * 16);
+            __nv_bfloat16* dst;
+            if (p.epilogue == kEpiScatter) {
+              const int owner = grow / p.rows_per_rank;
+              dst = reinterpret_cast<__nv_bfloat16*>(p.peer_base[owner] + p.stage_offset) +
+                    (static_cast<long long>(p.rank) * p.rows_per_rank + (grow - owner * p.rows_per_rank)) * p.ldo + gcol;
+            } else {
+              dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(grow) * p.ldo + gcol;
+              if (p.epilogue == kEpiResidual) {
+                const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(grow) * p.ldo + gcol);
+                v.x = pack_bf16(bf16_lo(v.x) + bf16_lo(rr.x), bf16_hi(v.x) + bf16_hi(rr.x));
+                v.y = pack_bf16(bf16_lo(v.y) + bf16_lo(rr.y), bf16_hi(v.y) + bf16_hi(rr.y));
+                v.z = pack_bf16(bf16_lo(v.z) + bf16_lo(rr.z), bf16_hi(v.z) + bf16_hi(rr.z));
+                v.w = pack_bf16(bf16_lo(v.w) + bf16_lo(rr.w), bf16_hi(v.w) + bf16_hi(rr.w));
+              }
             }
+            *reinterpret_cast<uint4*>(dst) = v;
           }
         }
       }
-      // make the tile visible system-wide, then one arrival on the owner's counter for this source
-      __threadfence_system();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) {
-        const int owner0 = min(a_row0 / p.rows_per_rank, p.world - 1);
-        int* cnt = reinterpret_cast<int*>(p.peer_base[owner0] + p.counter_offset) + p.rank;
-        asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+      if (p.epilogue == kEpiScatter) {
+        // make the tile visible system-wide, then one arrival on the owner's counter for this source
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const int owner0 = min(a_row0 / p.rows_per_rank, p.world - 1);
+          int* cnt = reinterpret_cast<int*>(p.peer_base[owner0] + p.counter_offset) + p.rank;
+          asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+        }
       }
     } else if (ok && p.splits == 1) {
       for (int c0 = 0; c0 < BN; c0 += CH) {
@@ -564,6 +606,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   p.flag_offset = -1;
   if (a.peer != nullptr) {
     if (a.swap || grouped || splits != 1 || a.peer->rows_per_rank % BM != 0) return cudaErrorInvalidValue;
+    if (a.epilogue == kEpiScatter && (a.bn < 64 || a.rb % 8 != 0 || a.ldo % 8 != 0)) return cudaErrorInvalidValue;
     p.world = a.peer->world; p.rank = a.peer->rank; p.rows_per_rank = a.peer->rows_per_rank;
     for (int i = 0; i < 8; ++i) p.peer_base[i] = static_cast<uint8_t*>(a.peer->base[i]);
     p.stage_offset = a.peer->stage_offset; p.counter_offset = a.peer->counter_offset;

@@ -61,6 +61,7 @@ class Communicator:
         self._bases = (ctypes.c_void_p * world)(*peer_ptrs)
         self.heap = torch.as_tensor(_RawCuda(heap_ptr, heap_bytes), device=device)
         self._next_slot = 0
+        self._q_bufs: dict = {}
         self.status = nv.device_state(device).status
         # sequence-parallel region: staging of scattered partials + gather buffers (NVFP4 and bf16)
         self.sp_rows, self.sp_hidden = sp_rows, sp_hidden
@@ -150,7 +151,15 @@ class Communicator:
         q = sf = None
         ka = 0
         if quant_scale is not None:
-            q, sf = nvfp4._alloc(rows, h, self.device)
+            # persistent per-shape buffers: the padding scale rows are zeroed once, the kernel writes real rows only
+            key = (rows, h)
+            bufs = self._q_bufs.get(key)
+            if bufs is None:
+                q, sf = nvfp4._alloc(rows, h, self.device)
+                sf.zero_()
+                self._q_bufs[key] = (q, sf)
+            else:
+                q, sf = bufs
             ka = sf.shape[1]
         nv.check(nv.lib().hb_ar_norm(self._bases, self.world, self.rank, slot, self.slot_offset(slot), rows, h,
                                      nv.ptr(residual), nv.ptr(weight), eps, int(gemma), nv.ptr(out), nv.ptr(q),
