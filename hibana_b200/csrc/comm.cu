@@ -17,6 +17,7 @@
 // separate residual+norm kernel that follows it (hibana/kernels/cute/residual_norm.py).
 #include "hb_api.h"
 #include "hb_common.cuh"
+#include "rownorm.cuh"
 #include <cstddef>
 
 namespace hb {
@@ -114,116 +115,56 @@ __device__ __forceinline__ size_t sf_off(int row, int g, int ka) {
   return (static_cast<size_t>(rb) * ka + (g >> 2)) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + (g & 3);
 }
 
-// One CTA per row. Thread t owns 16-element groups t, t + T, ...
-template <int T>
+// One CTA per row on the register-resident row core: all peers' chunks of the row are loaded at once.
+template <int T, int MAXC>
 __global__ void __launch_bounds__(T) ar_norm_kernel(const ArNormParams p) {
-  extern __shared__ float row_s[];   // h floats
-  __shared__ float red[32];
+  __shared__ float red[40];
   __shared__ int ok_s;
   Ctrl* mine = reinterpret_cast<Ctrl*>(p.peers.base[p.rank]);
   const int seq = ld_relaxed_sys(&mine->seq[p.slot]) + 1;
   const int row = blockIdx.x;
   if (blockIdx.x == 0) signal_peers(p.peers, p.world, p.rank, p.slot, seq);
   const bool ok = wait_peers(mine, p.world, p.slot, seq, p.limit_ns, p.status, &ok_s);
-  const int groups = p.h / 16;
-  const int rows_pad = p.q ? ((p.rows + 127) / 128) * 128 : p.rows;
-  if (ok && row < p.rows) {
-    float ss = 0.f;
-    for (int g = threadIdx.x; g < groups; g += T) {
-      float acc[16];
+  const int nchunk = p.h >> 3;
+  if (ok) {
+    float v[MAXC][8];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-      for (int r = 0; r < p.world; ++r) {   // fixed rank order: bitwise identical on every rank
-        const uint4* src = reinterpret_cast<const uint4*>(p.peers.base[r] + p.data_offset +
-                                                          (static_cast<size_t>(row) * p.h + g * 16) * 2);
-        const uint4 a = src[0], b = src[1];
-        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = threadIdx.x + i * T;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          acc[2 * i] += bf16_lo(w[i]);
-          acc[2 * i + 1] += bf16_hi(w[i]);
+      for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+      if (c < nchunk) {
+        uint4 part[MAX_WORLD];
+#pragma unroll
+        for (int r = 0; r < MAX_WORLD; ++r)
+          if (r < p.world)
+            part[r] = reinterpret_cast<const uint4*>(p.peers.base[r] + p.data_offset +
+                                                     static_cast<size_t>(row) * p.h * 2)[c];
+#pragma unroll
+        for (int r = 0; r < MAX_WORLD; ++r)     // fixed rank order: bitwise identical on every rank
+          if (r < p.world) {
+            float f[8];
+            unpack8(part[r], f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[i][e] += f[e];
+          }
+        // the reduced sum is rounded to bf16 first, like an unfused all-reduce followed by an add
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] = __bfloat162float(__float2bfloat16(v[i][e]));
+        if (p.residual != nullptr) {
+          uint4* rp = reinterpret_cast<uint4*>(p.residual + static_cast<size_t>(row) * p.h) + c;
+          float f[8];
+          unpack8(*rp, f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[i][e] = __bfloat162float(__float2bfloat16(v[i][e] + f[e]));
+          *rp = pack8(v[i]);
         }
       }
-      if (p.residual != nullptr) {
-        uint4* rp = reinterpret_cast<uint4*>(p.residual + static_cast<size_t>(row) * p.h + g * 16);
-        const uint4 a = rp[0], b = rp[1];
-        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        uint32_t o[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          // the reduced sum is rounded to bf16 first, like an unfused all-reduce followed by add
-          const float s0 = __bfloat162float(__float2bfloat16(acc[2 * i])) + bf16_lo(w[i]);
-          const float s1 = __bfloat162float(__float2bfloat16(acc[2 * i + 1])) + bf16_hi(w[i]);
-          o[i] = pack_bf16(s0, s1);
-          acc[2 * i] = bf16_lo(o[i]);
-          acc[2 * i + 1] = bf16_hi(o[i]);
-        }
-        rp[0] = make_uint4(o[0], o[1], o[2], o[3]);
-        rp[1] = make_uint4(o[4], o[5], o[6], o[7]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc[i] = __bfloat162float(__float2bfloat16(acc[i]));
-      }
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        row_s[g * 16 + i] = acc[i];
-        ss += acc[i] * acc[i];
-      }
     }
-    float rstd = 1.f;
-    if (p.weight != nullptr) {
-      ss = warp_sum(ss);
-      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-      __syncthreads();
-      if (threadIdx.x < 32) {
-        float t = threadIdx.x < T / 32 ? red[threadIdx.x] : 0.f;
-        t = warp_sum(t);
-        if (threadIdx.x == 0) red[0] = rsqrtf(t / p.h + p.eps);
-      }
-      __syncthreads();
-      rstd = red[0];
-    } else {
-      __syncthreads();
-    }
-    const float inv_gs = p.q ? 1.f / *p.gscale : 0.f;
-    const int groups_pad = p.q ? p.ka * 4 : groups;
-    for (int g = threadIdx.x; g < groups_pad; g += T) {
-      if (g >= groups) {
-        p.sf[sf_off(row, g, p.ka)] = 0;
-        continue;
-      }
-      float v[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float x = row_s[g * 16 + i];
-        if (p.weight != nullptr) {
-          const float w = __bfloat162float(p.weight[g * 16 + i]);
-          x = x * rstd * (p.gemma ? 1.f + w : w);
-        }
-        v[i] = __bfloat162float(__float2bfloat16(x));
-      }
-      if (p.out != nullptr) {
-        uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<size_t>(row) * p.h + g * 16);
-        dst[0] = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-        dst[1] = make_uint4(pack_bf16(v[8], v[9]), pack_bf16(v[10], v[11]), pack_bf16(v[12], v[13]),
-                            pack_bf16(v[14], v[15]));
-      }
-      if (p.q != nullptr) {
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-        const uint32_t sfb = float_to_e4m3(amax * (1.f / 6.f) * inv_gs);
-        const float sfv = e4m3_to_float(sfb);
-        const float inv = sfv > 0.f ? 1.f / (sfv * (1.f / inv_gs)) : 0.f;
-        uint32_t w[2] = {0, 0};
-#pragma unroll
-        for (int i = 0; i < 16; ++i) w[i >> 3] |= float_to_e2m1(v[i] * inv) << (4 * (i & 7));
-        *reinterpret_cast<uint2*>(p.q + static_cast<size_t>(row) * (p.h / 2) + g * 8) = make_uint2(w[0], w[1]);
-        p.sf[sf_off(row, g, p.ka)] = static_cast<uint8_t>(sfb);
-      }
-    }
-  } else if (ok && p.q != nullptr && row < rows_pad) {
-    for (int g = threadIdx.x; g < p.ka * 4; g += T) p.sf[sf_off(row, g, p.ka)] = 0;   // scale padding rows
+    RowOut out;
+    out.n = 1;
+    out.q[0] = p.q; out.sf[0] = p.sf; out.bf[0] = p.out;
+    row_finish<T, MAXC>(v, p.h, p.weight, p.eps, p.gemma, red, out, row, p.ka, p.gscale);
   }
   // The last CTA to finish completes the collective on this slot.
   __syncthreads();
@@ -258,10 +199,9 @@ struct RsNormAgParams {
 
 // One CTA per owned row: waits for every source's tiles, sums the partials in rank order, adds the residual,
 // normalises, quantises and pushes the row into every rank's gather buffer; the last CTA publishes the flag.
-template <int T>
+template <int T, int MAXC>
 __global__ void __launch_bounds__(T) rs_norm_ag_kernel(const RsNormAgParams p) {
-  extern __shared__ float row_s[];
-  __shared__ float red[32];
+  __shared__ float red[40];
   __shared__ int ok_s;
   Ctrl* mine = reinterpret_cast<Ctrl*>(p.peers.base[p.rank]);
   const int sseq = ld_relaxed_sys(&mine->sp_seq_scatter) + 1;
@@ -288,97 +228,49 @@ __global__ void __launch_bounds__(T) rs_norm_ag_kernel(const RsNormAgParams p) {
     }
   }
   __syncthreads();
-  const bool ok = ok_s != 0;
-  const int groups = p.h / 16;
-  if (ok) {
-    float ss = 0.f;
+  const int nchunk = p.h >> 3;
+  if (ok_s) {
+    float v[MAXC][8];
     const uint8_t* stage = p.peers.base[p.rank] + p.stage_offset;
-    for (int g = threadIdx.x; g < groups; g += T) {
-      float acc[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-      for (int r = 0; r < p.world; ++r) {
-        const uint4* src = reinterpret_cast<const uint4*>(
-            stage + ((static_cast<size_t>(r) * p.rows_per_rank + row) * p.h + g * 16) * 2);
-        const uint4 a = src[0], b = src[1];
-        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    for (int i = 0; i < MAXC; ++i) {
+      const int c = threadIdx.x + i * T;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          acc[2 * i] += bf16_lo(w[i]);
-          acc[2 * i + 1] += bf16_hi(w[i]);
-        }
-      }
-      uint4* rp = reinterpret_cast<uint4*>(p.residual + static_cast<size_t>(row) * p.h + g * 16);
-      const uint4 a = rp[0], b = rp[1];
-      const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-      uint32_t o[8];
+      for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+      if (c < nchunk) {
+        uint4 part[MAX_WORLD];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float s0 = __bfloat162float(__float2bfloat16(acc[2 * i])) + bf16_lo(w[i]);
-        const float s1 = __bfloat162float(__float2bfloat16(acc[2 * i + 1])) + bf16_hi(w[i]);
-        o[i] = pack_bf16(s0, s1);
-        acc[2 * i] = bf16_lo(o[i]);
-        acc[2 * i + 1] = bf16_hi(o[i]);
-      }
-      rp[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      rp[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        for (int r = 0; r < MAX_WORLD; ++r)
+          if (r < p.world)
+            part[r] = reinterpret_cast<const uint4*>(stage + (static_cast<size_t>(r) * p.rows_per_rank + row) * p.h * 2)[c];
+        uint4* rp = reinterpret_cast<uint4*>(p.residual + static_cast<size_t>(row) * p.h) + c;
+        const uint4 rv = *rp;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        row_s[g * 16 + i] = acc[i];
-        ss += acc[i] * acc[i];
+        for (int r = 0; r < MAX_WORLD; ++r)
+          if (r < p.world) {
+            float f[8];
+            unpack8(part[r], f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[i][e] += f[e];
+          }
+        float f[8];
+        unpack8(rv, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          v[i][e] = __bfloat162float(__float2bfloat16(__bfloat162float(__float2bfloat16(v[i][e])) + f[e]));
+        *rp = pack8(v[i]);
       }
     }
-    ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-      float t = threadIdx.x < T / 32 ? red[threadIdx.x] : 0.f;
-      t = warp_sum(t);
-      if (threadIdx.x == 0) red[0] = rsqrtf(t / p.h + p.eps);
+    RowOut out;
+    out.n = p.world;
+    for (int r = 0; r < ROW_MAX_DST; ++r) {
+      const bool on = r < p.world;
+      out.q[r] = on && p.gather_q_offset >= 0 ? p.peers.base[r] + p.gather_q_offset : nullptr;
+      out.sf[r] = on && p.gather_q_offset >= 0 ? p.peers.base[r] + p.gather_sf_offset : nullptr;
+      out.bf[r] = on && p.gather_bf_offset >= 0
+                      ? reinterpret_cast<__nv_bfloat16*>(p.peers.base[r] + p.gather_bf_offset) : nullptr;
     }
-    __syncthreads();
-    const float rstd = red[0];
-    const float inv_gs = p.gather_q_offset >= 0 ? 1.f / *p.gscale : 0.f;
-    const int groups_pad = p.gather_q_offset >= 0 ? p.ka * 4 : groups;
-    for (int g = threadIdx.x; g < groups_pad; g += T) {
-      if (g >= groups) {
-        for (int r = 0; r < p.world; ++r) (p.peers.base[r] + p.gather_sf_offset)[sf_off(grow, g, p.ka)] = 0;
-        continue;
-      }
-      float v[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float w = __bfloat162float(p.weight[g * 16 + i]);
-        v[i] = __bfloat162float(__float2bfloat16(row_s[g * 16 + i] * rstd * (p.gemma ? 1.f + w : w)));
-      }
-      if (p.gather_bf_offset >= 0) {
-        const uint4 lo = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-        const uint4 hi = make_uint4(pack_bf16(v[8], v[9]), pack_bf16(v[10], v[11]), pack_bf16(v[12], v[13]), pack_bf16(v[14], v[15]));
-        for (int r = 0; r < p.world; ++r) {
-          uint4* dst = reinterpret_cast<uint4*>(p.peers.base[r] + p.gather_bf_offset +
-                                                (static_cast<size_t>(grow) * p.h + g * 16) * 2);
-          dst[0] = lo;
-          dst[1] = hi;
-        }
-      }
-      if (p.gather_q_offset >= 0) {
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-        const uint32_t sfb = float_to_e4m3(amax * (1.f / 6.f) * inv_gs);
-        const float sfv = e4m3_to_float(sfb);
-        const float inv = sfv > 0.f ? 1.f / (sfv * (1.f / inv_gs)) : 0.f;
-        uint32_t w[2] = {0, 0};
-#pragma unroll
-        for (int i = 0; i < 16; ++i) w[i >> 3] |= float_to_e2m1(v[i] * inv) << (4 * (i & 7));
-        const uint2 packed = make_uint2(w[0], w[1]);
-        const size_t so = sf_off(grow, g, p.ka);
-        for (int r = 0; r < p.world; ++r) {
-          *reinterpret_cast<uint2*>(p.peers.base[r] + p.gather_q_offset + static_cast<size_t>(grow) * (p.h / 2) + g * 8) = packed;
-          (p.peers.base[r] + p.gather_sf_offset)[so] = static_cast<uint8_t>(sfb);
-        }
-      }
-    }
+    row_finish<T, MAXC>(v, p.h, p.weight, p.eps, p.gemma, red, out, grow, p.ka, p.gscale);
   }
   // The last CTA publishes this rank's rows to every peer and completes both sequence numbers.
   __threadfence_system();
@@ -463,7 +355,7 @@ int hb_ar_norm(const void* const* peer_bases, int world, int rank, int slot, lon
                void* residual, const void* weight, float eps, int gemma, void* out, void* q, void* sf,
                const void* gscale, int ka, long long limit_ns, void* status, void* stream) {
   if (world < 1 || world > MAX_WORLD || slot < 0 || slot >= NSLOT || h % 16 != 0 || rows <= 0) return 1;
-  if (static_cast<size_t>(h) * sizeof(float) > 96 * 1024) return 1;
+  if (h > 8192) return 1;
   ArNormParams p;
   for (int i = 0; i < MAX_WORLD; ++i)
     p.peers.base[i] = i < world ? static_cast<uint8_t*>(const_cast<void*>(peer_bases[i])) : nullptr;
@@ -477,13 +369,13 @@ int hb_ar_norm(const void* const* peer_bases, int world, int rank, int slot, lon
   p.limit_ns = static_cast<unsigned long long>(limit_ns);
   p.status = static_cast<int*>(status);
   constexpr int T = 256;
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(ar_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    attr = true;
-  }
   // The caller keeps persistent output buffers whose padding scale rows were zeroed once, so only real rows run.
-  ar_norm_kernel<T><<<rows, T, h * sizeof(float), static_cast<cudaStream_t>(stream)>>>(p);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nchunk = h / 8;
+  if (nchunk <= T) ar_norm_kernel<T, 1><<<rows, T, 0, st>>>(p);
+  else if (nchunk <= 2 * T) ar_norm_kernel<T, 2><<<rows, T, 0, st>>>(p);
+  else if (nchunk <= 3 * T) ar_norm_kernel<T, 3><<<rows, T, 0, st>>>(p);
+  else ar_norm_kernel<T, 4><<<rows, T, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
@@ -513,7 +405,7 @@ int hb_rs_norm_ag(const void* const* peer_bases, int world, int rank, int rows_p
                   long long gather_sf_offset, long long gather_bf_offset, const void* gscale, int ka,
                   long long limit_ns, void* status, void* stream) {
   if (world < 1 || world > MAX_WORLD || h % 16 != 0 || rows_per_rank <= 0) return 1;
-  if (static_cast<size_t>(h) * sizeof(float) > 96 * 1024) return 1;
+  if (h > 8192) return 1;
   RsNormAgParams p;
   for (int i = 0; i < MAX_WORLD; ++i)
     p.peers.base[i] = i < world ? static_cast<uint8_t*>(const_cast<void*>(peer_bases[i])) : nullptr;
@@ -524,12 +416,12 @@ int hb_rs_norm_ag(const void* const* peer_bases, int world, int rank, int rows_p
   p.gscale = static_cast<const float*>(gscale); p.ka = ka;
   p.limit_ns = static_cast<unsigned long long>(limit_ns); p.status = static_cast<int*>(status);
   constexpr int T = 256;
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(rs_norm_ag_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    attr = true;
-  }
-  rs_norm_ag_kernel<T><<<rows_per_rank, T, h * sizeof(float), static_cast<cudaStream_t>(stream)>>>(p);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nchunk = h / 8;
+  if (nchunk <= T) rs_norm_ag_kernel<T, 1><<<rows_per_rank, T, 0, st>>>(p);
+  else if (nchunk <= 2 * T) rs_norm_ag_kernel<T, 2><<<rows_per_rank, T, 0, st>>>(p);
+  else if (nchunk <= 3 * T) rs_norm_ag_kernel<T, 3><<<rows_per_rank, T, 0, st>>>(p);
+  else rs_norm_ag_kernel<T, 4><<<rows_per_rank, T, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -10,6 +10,7 @@
 // and hibana/kernels/cute/residual_norm.py:62-160.
 #include "hb_common.cuh"
 #include "hb_api.h"
+#include "rownorm.cuh"
 
 namespace hb {
 namespace {
@@ -96,81 +97,52 @@ __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long lon
   sf[sf_offset(row, g, ka)] = static_cast<uint8_t>(sfb);
 }
 
-// (residual add +) RMSNorm -> NVFP4. One CTA per row, blockDim.x * 16 >= K is not required: threads loop.
-// Writes the updated residual (bf16) when `residual` is given, optionally the normalised bf16 row too.
-// gemma != 0 uses weight (1 + w).
-template <int THREADS>
-__global__ void __launch_bounds__(THREADS)
+// (residual add +) RMSNorm -> NVFP4 (and / or bf16). One CTA per row on the register-resident row core.
+// Writes the updated residual (bf16) when `residual` is given. gemma != 0 uses weight (1 + w).
+template <int T, int MAXC>
+__global__ void __launch_bounds__(T)
 norm_quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                         const __nv_bfloat16* __restrict__ w, float eps, int gemma, int m, int k, int ka,
                         const float* __restrict__ gscale, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
                         __nv_bfloat16* __restrict__ normed) {
-  extern __shared__ float row_s[];  // k floats
-  __shared__ float red[32];
+  __shared__ float red[40];
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
-  const int groups = k / 16;
   if (row >= m) {   // padding rows of the last 128-row scale block: zero scales, nothing else
-    for (int g = tid; g < ka * 4; g += THREADS) sf[sf_offset(row, g, ka)] = 0;
+    for (int g = tid; g < ka * 4; g += T) sf[sf_offset(row, g, ka)] = 0;
     return;
   }
-  float ss = 0.f;
-  for (int g = tid; g < groups; g += THREADS) {
-    float v[16];
-    load16(x + static_cast<size_t>(row) * k + g * 16, v);
-    if (residual != nullptr) {
-      float r[16];
-      load16(residual + static_cast<size_t>(row) * k + g * 16, r);
-      uint32_t o[8];
+  const int nchunk = k >> 3;
+  float v[MAXC][8];
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * k);
+  uint4* rr = residual ? reinterpret_cast<uint4*>(residual + static_cast<size_t>(row) * k) : nullptr;
+  uint4 xa[MAXC], ra[MAXC];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = __bfloat162float(__float2bfloat16(v[i] + r[i]));
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
-      uint4* dst = reinterpret_cast<uint4*>(residual + static_cast<size_t>(row) * k + g * 16);
-      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-    }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      row_s[g * 16 + i] = v[i];
-      ss += v[i] * v[i];
+  for (int i = 0; i < MAXC; ++i) {
+    const int c = tid + i * T;
+    if (c < nchunk) {
+      xa[i] = xr[c];
+      if (rr) ra[i] = rr[c];
     }
   }
-  ss = warp_sum(ss);
-  if ((tid & 31) == 0) red[tid >> 5] = ss;
-  __syncthreads();
-  if (tid < 32) {
-    float t = tid < THREADS / 32 ? red[tid] : 0.f;
-    t = warp_sum(t);
-    if (tid == 0) red[0] = rsqrtf(t / k + eps);
-  }
-  __syncthreads();
-  const float rstd = red[0];
-  const float inv_gs = 1.f / *gscale;
-  const int groups_pad = ka * 4;
-  for (int g = tid; g < groups_pad; g += THREADS) {
-    if (g >= groups) {
-      sf[sf_offset(row, g, ka)] = 0;
-      continue;
-    }
-    float wv[16], v[16];
-    load16(w + g * 16, wv);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float ww = gemma ? 1.f + wv[i] : wv[i];
-      v[i] = __bfloat162float(__float2bfloat16(row_s[g * 16 + i] * rstd * ww));
+  for (int i = 0; i < MAXC; ++i) {
+    const int c = tid + i * T;
+    if (c < nchunk) {
+      unpack8(xa[i], v[i]);
+      if (rr) {
+        float r[8];
+        unpack8(ra[i], r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] = __bfloat162float(__float2bfloat16(v[i][e] + r[e]));
+        rr[c] = pack8(v[i]);
+      }
     }
-    if (normed != nullptr) {
-      uint4* dst = reinterpret_cast<uint4*>(normed + static_cast<size_t>(row) * k + g * 16);
-      dst[0] = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-      dst[1] = make_uint4(pack_bf16(v[8], v[9]), pack_bf16(v[10], v[11]), pack_bf16(v[12], v[13]),
-                          pack_bf16(v[14], v[15]));
-    }
-    uint2 packed;
-    const uint32_t sfb = quant16(v, inv_gs, &packed);
-    *reinterpret_cast<uint2*>(q + static_cast<size_t>(row) * (k / 2) + g * 8) = packed;
-    sf[sf_offset(row, g, ka)] = static_cast<uint8_t>(sfb);
   }
+  RowOut out;
+  out.n = 1;
+  out.q[0] = q; out.sf[0] = sf; out.bf[0] = normed;
+  row_finish<T, MAXC>(v, k, w, eps, gemma, red, out, row, ka, gscale);
 }
 
 // Zeroes the scale bytes of the padding rows [m, round_up(m, 128)) (used after the per-row kernel).
@@ -257,19 +229,21 @@ int hb_quant_nvfp4(const void* x, long long ldx, int m, int k, int ka, const voi
 
 int hb_norm_quant_nvfp4(const void* x, void* residual, const void* w, float eps, int gemma, int m, int k, int ka,
                         const void* gscale, void* q, void* sf, void* normed, void* stream) {
-  if (k % 16 != 0 || ka * 64 < k || k * sizeof(float) > 96 * 1024) return 1;
+  if (k % 16 != 0 || (q != nullptr && ka * 64 < k) || k > 8192) return 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   constexpr int T = 256;
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(norm_quant_nvfp4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    attr = true;
-  }
-  const int rows_pad = ((m + 127) / 128) * 128;
-  norm_quant_nvfp4_kernel<T><<<rows_pad, T, k * sizeof(float), st>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(residual),
-      static_cast<const __nv_bfloat16*>(w), eps, gemma, m, k, ka, static_cast<const float*>(gscale),
-      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), static_cast<__nv_bfloat16*>(normed));
+  const int rows_pad = q != nullptr ? ((m + 127) / 128) * 128 : m;
+  const int nchunk = k / 8;
+#define HB_NQ(MAXC)                                                                                              \
+  norm_quant_nvfp4_kernel<T, MAXC><<<rows_pad, T, 0, st>>>(                                                      \
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(residual),                               \
+      static_cast<const __nv_bfloat16*>(w), eps, gemma, m, k, ka, static_cast<const float*>(gscale),             \
+      static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), static_cast<__nv_bfloat16*>(normed))
+  if (nchunk <= T) HB_NQ(1);
+  else if (nchunk <= 2 * T) HB_NQ(2);
+  else if (nchunk <= 3 * T) HB_NQ(3);
+  else HB_NQ(4);
+#undef HB_NQ
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

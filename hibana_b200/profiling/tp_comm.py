@@ -61,7 +61,12 @@ def main() -> None:
     ap.add_argument("--ffn", type=int, default=17408)
     ap.add_argument("--rows", type=int, nargs="*", default=[1, 16, 64, 256])
     ap.add_argument("--sp-rows", type=int, nargs="*", default=[2048])
+    ap.add_argument("--once", action="store_true", help="run each fused op once, no timing (for ncu on one GPU)")
     args = ap.parse_args()
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29599")
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
@@ -87,7 +92,17 @@ def main() -> None:
         def nccl():
             dist.all_reduce(part)
             nvfp4.rmsnorm_quantize(part, w, 1e-6, gs, residual=res)
-        tf, tn = graph_time(fused, 20), graph_time(nccl, 20)
+        if args.once:
+            for _ in range(2):
+                fused()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            fused()
+            nccl()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+            continue
+        tf, tn = graph_time(fused, 200), graph_time(nccl, 200)
         nv_bytes = (world - 1) * rows * h * 2           # one-shot: every rank pulls every peer's partial
         roof = nv_bytes / (NVLINK_GBS * 1e3) if world > 1 else 0.0
         out.append({"op": "ar_norm", "rows": rows, "hidden": h, "world": world, "fused_us": round(tf, 2),
@@ -116,7 +131,18 @@ def main() -> None:
             dist.all_reduce(part)
             a, _ = nvfp4.rmsnorm_quantize(part, w, 1e-6, gate_up.input_scale, residual=res_full)
             gate_up(a, epilogue=gemm.EPI_SILU_MUL)
-        tf, tn = graph_time(fused_chain, 4), graph_time(nccl_chain, 4)
+        if args.once:
+            for _ in range(2):
+                fused_chain()
+                nccl_chain()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            fused_chain()
+            nccl_chain()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+            continue
+        tf, tn = graph_time(fused_chain, 20), graph_time(nccl_chain, 20)
         flops = 2.0 * m * h * kin + 2.0 * m * nout * h
         t_math = flops / (peaks["bf16_tflops"] * 4 * 1e12) * 1e6
         nv_bytes = (world - 1) / world * m * h * 2 + (world - 1) * rpr * (h // 2 + h // 16)
