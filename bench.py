@@ -95,7 +95,7 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         from hibana_b200.parallel.comm import Communicator
-        comm = Communicator.create(rank, world, dev, slot_mb=4)
+        comm = Communicator.create(rank, world, dev, slot_mb=32, sp_rows=args.prompt, sp_hidden=5120)
     warmup = max(args.warmup, 3)
     steps = args.steps
 

@@ -76,13 +76,12 @@ __device__ __forceinline__ bool wait_peers(Ctrl* mine, int world, int slot, int 
     const unsigned long long t0 = globaltimer_ns();
     bool ok = false;
     for (unsigned it = 0; it < HB_SPIN_LIMIT; ++it) {
-      if (ld_relaxed_sys(&mine->flags[slot][threadIdx.x]) - seq >= 0) {
+      if (ld_acquire_sys(&mine->flags[slot][threadIdx.x]) - seq >= 0) {
         ok = true;
         break;
       }
       if ((it & 63u) == 63u && globaltimer_ns() - t0 > limit_ns) break;
     }
-    __threadfence_system();   // acquire: order the peer data reads after the flag observation
     if (!ok) {
       *ok_smem = 0;
       set_status(status, kTimeoutPeer);
@@ -167,6 +166,113 @@ __global__ void __launch_bounds__(T) ar_norm_kernel(const ArNormParams p) {
     row_finish<T, MAXC>(v, p.h, p.weight, p.eps, p.gemma, red, out, row, p.ka, p.gscale);
   }
   // The last CTA to finish completes the collective on this slot.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int prev = atomicAdd(&mine->done[p.slot], 1);
+    if (prev == static_cast<int>(gridDim.x) - 1) {
+      mine->done[p.slot] = 0;
+      __threadfence();
+      mine->seq[p.slot] = seq;
+    }
+  }
+}
+
+// Low-latency variant for small messages: every rank pushes its partial into all peers as 8-byte words
+// {two bf16 values, sequence number}; the receiver spins on the words themselves, so a collective costs one
+// one-way NVLink hop and needs neither flags nor fences. The LL area of a slot is ll[src][row][h / 2] words and
+// lives at `ll_offset` in every heap; stale words carry an older sequence number and are never mistaken for data.
+struct ArNormLlParams {
+  ArNormParams base;
+  long long ll_offset;
+  int ll_rows;                  // row capacity of the LL area (stride between sources)
+};
+
+template <int T, int MAXC>
+__global__ void __launch_bounds__(T) ar_norm_ll_kernel(const ArNormLlParams pp) {
+  const ArNormParams& p = pp.base;
+  __shared__ float red[40];
+  __shared__ int bad_s;
+  Ctrl* mine = reinterpret_cast<Ctrl*>(p.peers.base[p.rank]);
+  const int seq = ld_relaxed_sys(&mine->seq[p.slot]) + 1;
+  const int row = blockIdx.x;
+  const int nchunk = p.h >> 3;
+  if (threadIdx.x == 0) bad_s = 0;
+  // ---- push my chunks to every other rank
+  uint4 own[MAXC];
+#pragma unroll
+  for (int i = 0; i < MAXC; ++i) {
+    const int c = threadIdx.x + i * T;
+    if (c < nchunk) {
+      own[i] = reinterpret_cast<const uint4*>(p.peers.base[p.rank] + p.data_offset + static_cast<size_t>(row) * p.h * 2)[c];
+      const size_t word = (static_cast<size_t>(p.rank) * pp.ll_rows + row) * (p.h >> 1) + static_cast<size_t>(c) * 4;
+      for (int d = 0; d < p.world; ++d) {
+        if (d == p.rank) continue;
+        uint2* dst = reinterpret_cast<uint2*>(p.peers.base[d] + pp.ll_offset) + word;
+        asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(own[i].x), "r"(seq) : "memory");
+        asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst + 1), "r"(own[i].y), "r"(seq) : "memory");
+        asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst + 2), "r"(own[i].z), "r"(seq) : "memory");
+        asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst + 3), "r"(own[i].w), "r"(seq) : "memory");
+      }
+    }
+  }
+  __syncthreads();
+  // ---- collect every source's chunks (spin on the data words), sum in rank order
+  float v[MAXC][8];
+  const unsigned long long t0 = globaltimer_ns();
+#pragma unroll
+  for (int i = 0; i < MAXC; ++i) {
+    const int c = threadIdx.x + i * T;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+    if (c < nchunk) {
+      for (int r = 0; r < p.world; ++r) {
+        uint4 part = own[i];
+        if (r != p.rank) {
+          const uint2* src = reinterpret_cast<const uint2*>(p.peers.base[p.rank] + pp.ll_offset) +
+                             (static_cast<size_t>(r) * pp.ll_rows + row) * (p.h >> 1) + static_cast<size_t>(c) * 4;
+          uint32_t w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint32_t data = 0, flag = 0;
+            bool got = false;
+            for (unsigned it = 0; it < HB_SPIN_LIMIT; ++it) {
+              asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(data), "=r"(flag) : "l"(src + k) : "memory");
+              if (static_cast<int>(flag) == seq) {
+                got = true;
+                break;
+              }
+              if ((it & 255u) == 255u && (bad_s || globaltimer_ns() - t0 > p.limit_ns)) break;
+            }
+            if (!got) {
+              bad_s = 1;
+              set_status(p.status, kTimeoutPeer);
+            }
+            w[k] = data;
+          }
+          part = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        float f[8];
+        unpack8(part, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += f[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[i][e] = __bfloat162float(__float2bfloat16(v[i][e]));
+      if (p.residual != nullptr) {
+        uint4* rp = reinterpret_cast<uint4*>(p.residual + static_cast<size_t>(row) * p.h) + c;
+        float f[8];
+        unpack8(*rp, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] = __bfloat162float(__float2bfloat16(v[i][e] + f[e]));
+        *rp = pack8(v[i]);
+      }
+    }
+  }
+  RowOut out;
+  out.n = 1;
+  out.q[0] = p.q; out.sf[0] = p.sf; out.bf[0] = p.out;
+  row_finish<T, MAXC>(v, p.h, p.weight, p.eps, p.gemma, red, out, row, p.ka, p.gscale);
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -353,7 +459,8 @@ int hb_comm_ipc_close(void* p) { return static_cast<int>(cudaIpcCloseMemHandle(p
 // peer_bases: host array of `world` heap base pointers as seen from this process (own heap at index rank).
 int hb_ar_norm(const void* const* peer_bases, int world, int rank, int slot, long long data_offset, int rows, int h,
                void* residual, const void* weight, float eps, int gemma, void* out, void* q, void* sf,
-               const void* gscale, int ka, long long limit_ns, void* status, void* stream) {
+               const void* gscale, int ka, long long limit_ns, void* status, long long ll_offset, int ll_rows,
+               void* stream) {
   if (world < 1 || world > MAX_WORLD || slot < 0 || slot >= NSLOT || h % 16 != 0 || rows <= 0) return 1;
   if (h > 8192) return 1;
   ArNormParams p;
@@ -372,6 +479,17 @@ int hb_ar_norm(const void* const* peer_bases, int world, int rank, int slot, lon
   // The caller keeps persistent output buffers whose padding scale rows were zeroed once, so only real rows run.
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int nchunk = h / 8;
+  if (ll_offset >= 0 && rows <= ll_rows && world > 1) {
+    ArNormLlParams pp;
+    pp.base = p;
+    pp.ll_offset = ll_offset;
+    pp.ll_rows = ll_rows;
+    if (nchunk <= T) ar_norm_ll_kernel<T, 1><<<rows, T, 0, st>>>(pp);
+    else if (nchunk <= 2 * T) ar_norm_ll_kernel<T, 2><<<rows, T, 0, st>>>(pp);
+    else if (nchunk <= 3 * T) ar_norm_ll_kernel<T, 3><<<rows, T, 0, st>>>(pp);
+    else ar_norm_ll_kernel<T, 4><<<rows, T, 0, st>>>(pp);
+    return cudaGetLastError() == cudaSuccess ? 0 : 2;
+  }
   if (nchunk <= T) ar_norm_kernel<T, 1><<<rows, T, 0, st>>>(p);
   else if (nchunk <= 2 * T) ar_norm_kernel<T, 2><<<rows, T, 0, st>>>(p);
   else if (nchunk <= 3 * T) ar_norm_kernel<T, 3><<<rows, T, 0, st>>>(p);

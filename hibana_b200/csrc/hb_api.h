@@ -101,7 +101,8 @@ int hb_comm_ipc_open(const void* handle64, void** out);
 int hb_comm_ipc_close(void* p);
 int hb_ar_norm(const void* const* peer_bases, int world, int rank, int slot, long long data_offset, int rows, int h,
                void* residual, const void* weight, float eps, int gemma, void* out, void* q, void* sf,
-               const void* gscale, int ka, long long limit_ns, void* status, void* stream);
+               const void* gscale, int ka, long long limit_ns, void* status, long long ll_offset, int ll_rows,
+               void* stream);
 int hb_comm_sp_layout(long long* out3);
 int hb_rs_norm_ag(const void* const* peer_bases, int world, int rank, int rows_per_rank, int h, long long stage_offset,
                   int expected, void* residual, const void* weight, float eps, int gemma, long long gather_q_offset,

@@ -27,7 +27,7 @@ nv.register("hb_comm_free", [P])
 nv.register("hb_comm_ipc_handle", [P, P])
 nv.register("hb_comm_ipc_open", [P, ctypes.POINTER(ctypes.c_void_p)])
 nv.register("hb_comm_ipc_close", [P])
-nv.register("hb_ar_norm", [P, I, I, I, L, I, I, P, P, Fl, I, P, P, P, P, I, L, P, P])
+nv.register("hb_ar_norm", [P, I, I, I, L, I, I, P, P, Fl, I, P, P, P, P, I, L, P, L, I, P])
 nv.register("hb_barrier", [P, I, I, I, L, P, P])
 nv.register("hb_comm_sp_layout", [ctypes.POINTER(ctypes.c_longlong)])
 nv.register("hb_rs_norm_ag", [P, I, I, I, I, L, I, P, P, Fl, I, L, L, L, P, I, L, P, P])
@@ -62,6 +62,7 @@ class Communicator:
         self.heap = torch.as_tensor(_RawCuda(heap_ptr, heap_bytes), device=device)
         self._next_slot = 0
         self._q_bufs: dict = {}
+        self.low_latency = True
         self.status = nv.device_state(device).status
         # sequence-parallel region: staging of scattered partials + gather buffers (NVFP4 and bf16)
         self.sp_rows, self.sp_hidden = sp_rows, sp_hidden
@@ -120,13 +121,13 @@ class Communicator:
     def slot_buffer(self, slot: int, rows: int, cols: int, dtype=torch.bfloat16) -> torch.Tensor:
         """A [rows, cols] tensor inside this rank's heap slot (what the producing GEMM writes into)."""
         nbytes = rows * cols * torch.tensor([], dtype=dtype).element_size()
-        if nbytes > self.slot_bytes:
-            raise ValueError(f"message of {nbytes} bytes exceeds the {self.slot_bytes}-byte heap slot")
+        if nbytes > self.slot_bytes // 2:
+            raise ValueError(f"message of {nbytes} bytes exceeds half of the {self.slot_bytes}-byte heap slot")
         off = self.slot_offset(slot)
         return self.heap[off:off + nbytes].view(dtype).view(rows, cols)
 
     def fits(self, rows: int, cols: int) -> bool:
-        return self.fused and rows * cols * 2 <= self.slot_bytes
+        return self.fused and rows * cols * 2 <= self.slot_bytes // 2
 
     # ---- collectives
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -161,10 +162,13 @@ class Communicator:
             else:
                 q, sf = bufs
             ka = sf.shape[1]
+        # small messages take the low-latency push protocol: the second half of the slot is its landing area
+        ll_rows = (self.slot_bytes // 2) // (self.world * h * 4) if self.low_latency else 0
+        ll_off = self.slot_offset(slot) + self.slot_bytes // 2 if ll_rows >= rows else -1
         nv.check(nv.lib().hb_ar_norm(self._bases, self.world, self.rank, slot, self.slot_offset(slot), rows, h,
                                      nv.ptr(residual), nv.ptr(weight), eps, int(gemma), nv.ptr(out), nv.ptr(q),
                                      nv.ptr(sf), nv.ptr(quant_scale), ka, self.timeout_ns, self.status.data_ptr(),
-                                     nv.stream()), "hb_ar_norm")
+                                     ll_off, ll_rows, nv.stream()), "hb_ar_norm")
         xq = Nvfp4Tensor(q, sf, quant_scale, rows, h) if q is not None else None
         return out, xq
 

@@ -119,7 +119,7 @@ prompts = [torch.randint(0, t.vocab, (40,), generator=g).tolist() for _ in range
 long_prompt = [torch.randint(0, t.vocab, (256,), generator=g).tolist()]
 res = {}
 for name, fused, sp in (("nccl", False, 0), ("fused", True, 0), ("sp", True, 256)):
-    comm = Communicator.create(rank, world, dev, slot_mb=1, fused=fused, sp_rows=sp, sp_hidden=t.hidden)
+    comm = Communicator.create(rank, world, dev, slot_mb=4, fused=fused, sp_rows=sp, sp_hidden=t.hidden)
     model = DenseModel.sharded(t, world, rank, dev, seed=0, init_device="cpu")
     ex = Executor(model, max_batch=4, max_ctx=512, use_graphs=True, comm=comm, radix_cache=False)
     ex.capture_graphs()
