@@ -34,6 +34,10 @@ nv.register("hb_rs_norm_ag", [P, I, I, I, I, L, I, P, P, Fl, I, L, L, L, P, I, L
 nv.register("hb_gemm_peer", [I, P, P, P, P, I, I, I, P, L, P, I, P, I, I, I, L, L, L, L, L, P, I, I, P])
 
 
+# Up to this many rows the push ("LL") protocol wins; above it the flag-based one-shot moves half the bytes.
+LL_MAX_ROWS = 32
+
+
 class _RawCuda:
     """Exposes a raw device pointer to torch through __cuda_array_interface__ (zero copy)."""
 
@@ -164,7 +168,7 @@ class Communicator:
             ka = sf.shape[1]
         # small messages take the low-latency push protocol: the second half of the slot is its landing area
         ll_rows = (self.slot_bytes // 2) // (self.world * h * 4) if self.low_latency else 0
-        ll_off = self.slot_offset(slot) + self.slot_bytes // 2 if ll_rows >= rows else -1
+        ll_off = self.slot_offset(slot) + self.slot_bytes // 2 if (ll_rows >= rows and rows <= LL_MAX_ROWS) else -1
         nv.check(nv.lib().hb_ar_norm(self._bases, self.world, self.rank, slot, self.slot_offset(slot), rows, h,
                                      nv.ptr(residual), nv.ptr(weight), eps, int(gemma), nv.ptr(out), nv.ptr(q),
                                      nv.ptr(sf), nv.ptr(quant_scale), ka, self.timeout_ns, self.status.data_ptr(),
