@@ -9,8 +9,13 @@
 // of warp 1 issues the MMAs and commits stage releases, warps 2-5 read the accumulator back with tcgen05.ld
 // and run the epilogue. With `swap` the 128-row operand is the weight matrix and the (few) tokens sit on the
 // N side, which keeps decode-sized problems on the tensor cores while streaming each weight byte once.
-// Split-K partials go to an fp32 workspace; the last CTA to arrive on a tile's counter sums them in split
-// order (deterministic) and applies the epilogue.
+// Split-K runs as one thread-block cluster per output tile (cluster dims 1 x 1 x splits): every CTA parks its raw
+// fp32 partial in its own shared memory, and after a cluster barrier each CTA sums a slice of the tile's columns
+// over all partials through distributed shared memory, in split order (deterministic), and applies the epilogue.
+// No global workspace, counters or fences are involved.
+// The producer issues the weight-side loads of the first ring of stages before `griddepcontrol.wait`, so with
+// programmatic dependent launch the weight stream starts while the kernel that produces the activations is
+// still running.
 //
 // Replaces the reference's library GEMM dispatch (hibana/kernels/ops.py:56-128) for bf16 and NVFP4.
 #include "gemm.cuh"
@@ -184,7 +189,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
   uint64_t* accum = empty + S;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* last_flag = abort + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -215,7 +219,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     }
     mbar_init(accum, 1);
     *abort = 0;
-    *last_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tma);
     prefetch_tmap(&tmb);
@@ -254,24 +257,48 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
           set_status(p.status, kTimeoutPeer);
         }
       }
-      for (int i = 0; i < nkt && !*abort; ++i) {
+      // side 0 = A operand (+ its scales), side 1 = B operand (+ its scales) of K tile i into stage i % S
+      auto load_side = [&](int i, int side) {
+        const int s = i % S;
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        const int kt = kt0 + i;
+        const int kx = KIND == kGemmNvfp4 ? kt * 128 : kt * 64;
+        if (side == 0) {
+          tma_load_2d(st, &tma, &full[s], kx, a_row0);
+          if constexpr (KIND == kGemmNvfp4)
+            bulk_load(st + A_TILE_BYTES + C::B_TILE_BYTES,
+                      p.sfa + (static_cast<size_t>(a_row0 >> 7) * p.ka_a + kt * 4) * 512, 2048, &full[s]);
+        } else {
+          tma_load_2d(st + A_TILE_BYTES, &tmb, &full[s], kx, b_row0);
+          if constexpr (KIND == kGemmNvfp4) {
+#pragma unroll
+            for (int rb = 0; rb < C::NRB; ++rb)
+              bulk_load(st + A_TILE_BYTES + C::B_TILE_BYTES + C::SFA_BYTES + rb * 2048,
+                        p.sfb + (static_cast<size_t>((b_row0 >> 7) + rb) * p.ka_b + kt * 4) * 512, 2048, &full[s]);
+          }
+        }
+      };
+      // First ring of stages (their `empty` barriers are trivially free): weights first, then wait for the
+      // producing grid, then the activations.
+      const int wside = p.swap ? 0 : 1;
+      const int pre = *abort ? 0 : min(S, nkt);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full[i], C::STAGE_BYTES);
+        if (!p.peer_on) load_side(i, wside);
+      }
+      grid_dep_wait();
+      for (int i = 0; i < pre; ++i) {
+        if (p.peer_on) load_side(i, wside);
+        load_side(i, wside ^ 1);
+        ++issued;
+      }
+      for (int i = pre; i < nkt && !*abort; ++i) {
         const int s = i % S;
         const uint32_t ph = (i / S) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, abort, p.status, kTimeoutEmpty)) break;
-        uint8_t* st = smem + s * C::STAGE_BYTES;
         mbar_expect_tx(&full[s], C::STAGE_BYTES);
-        const int kt = kt0 + i;
-        const int kx = KIND == kGemmNvfp4 ? kt * 128 : kt * 64;
-        tma_load_2d(st, &tma, &full[s], kx, a_row0);
-        tma_load_2d(st + A_TILE_BYTES, &tmb, &full[s], kx, b_row0);
-        if constexpr (KIND == kGemmNvfp4) {
-          uint8_t* sf = st + A_TILE_BYTES + C::B_TILE_BYTES;
-          bulk_load(sf, p.sfa + (static_cast<size_t>(a_row0 >> 7) * p.ka_a + kt * 4) * 512, 2048, &full[s]);
-#pragma unroll
-          for (int rb = 0; rb < C::NRB; ++rb)
-            bulk_load(sf + C::SFA_BYTES + rb * 2048,
-                      p.sfb + (static_cast<size_t>((b_row0 >> 7) + rb) * p.ka_b + kt * 4) * 512, 2048, &full[s]);
-        }
+        load_side(i, 0);
+        load_side(i, 1);
         ++issued;
       }
       if (*abort) {
@@ -323,6 +350,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     }
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    grid_dep_wait();
     const bool ok = nkt > 0 ? mbar_wait(accum, 0, abort, p.status, kTimeoutAccum) : true;
     tc_fence_after();
     const int row = tile_a * BM + q * 32 + lane;   // feature index (within the expert in grouped mode)
@@ -418,57 +446,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         epilogue_chunk<CH>(p, v, row, row_lim, b_row0 + c0, col_lim, alpha, lane);
       }
     } else if (ok) {
-      // Split-K: park the raw partial, then the last CTA of this tile reduces all partials in split order.
-      const size_t plane = static_cast<size_t>(p.out_rows) * p.out_cols;
-      float* ws = p.workspace + static_cast<size_t>(split) * plane;
+      // Split-K: park the raw partial in this CTA's shared memory as [column][row] fp32 (the stage ring is idle
+      // once the accumulator is complete); lanes are consecutive rows, so the stores are conflict-free.
+      float* part = reinterpret_cast<float*>(smem);
+      const int lrow = q * 32 + lane;
       for (int c0 = 0; c0 < BN; c0 += CH) {
         uint32_t r[CH];
         if constexpr (CH == 32) tmem_ld_32x32(tlane + c0, r);
         else tmem_ld_32x16(tlane + c0, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          const int col = tile_b * BN + c0 + j;
-          if (row < p.ra && col < col_lim) {
-            const size_t o = p.swap ? static_cast<size_t>(col) * p.out_cols + row
-                                    : static_cast<size_t>(row) * p.out_cols + col;
-            __stcg(ws + o, nkt > 0 ? __uint_as_float(r[j]) : 0.f);
-          }
-        }
-      }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) {
-        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-        const int prev = atomicAdd(&p.counters[tile_id], 1);
-        if (prev == p.splits - 1) {
-          p.counters[tile_id] = 0;
-          *last_flag = 1;
-        }
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*last_flag) {
-        __threadfence();
-        for (int c0 = 0; c0 < BN; c0 += CH) {
-          float v[CH];
-#pragma unroll
-          for (int j = 0; j < CH; ++j) v[j] = 0.f;
-          for (int s = 0; s < p.splits; ++s) {
-            const float* w = p.workspace + static_cast<size_t>(s) * plane;
-#pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              const int col = tile_b * BN + c0 + j;
-              if (row < p.ra && col < col_lim) {
-                const size_t o = p.swap ? static_cast<size_t>(col) * p.out_cols + row
-                                        : static_cast<size_t>(row) * p.out_cols + col;
-                v[j] += __ldcg(w + o);
-              }
-            }
-          }
-          epilogue_chunk<CH>(p, v, row, row_lim, b_row0 + c0, col_lim, alpha, lane);
-        }
+        for (int j = 0; j < CH; ++j) part[(c0 + j) * BM + lrow] = nkt > 0 ? __uint_as_float(r[j]) : 0.f;
       }
     }
+  }
+  if (p.splits > 1) {
+    // Every thread of every CTA of the cluster arrives, whatever happened to its pipeline (all waits above are
+    // bounded), so the barrier cannot hang; a timed-out CTA has already raised the status word.
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int q = warp & 3;
+      const int lrow = q * 32 + lane;
+      const int row = tile_a * BM + lrow;
+      float alpha = p.alpha;
+      if (alpha_ptr != nullptr) alpha *= *alpha_ptr;
+      const int ncols = min(BN, col_lim - b_row0);
+      int per = (ncols + p.splits - 1) / p.splits;
+      if (!p.swap) per = (per + 15) & ~15;      // feature pairs and 16-byte stores stay inside one slice
+      const int c_begin = split * per;
+      const int c_end = min(ncols, c_begin + per);
+      const uint32_t part_local = smem_u32(smem);
+      for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        for (int s = 0; s < p.splits; ++s) {
+          const uint32_t src = map_to_cta(part_local, static_cast<uint32_t>(s)) + (c0 * BM + lrow) * 4;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < c_end) v[j] += ld_dsmem_f32(src + j * BM * 4);
+        }
+        epilogue_chunk<16>(p, v, row, row_lim, b_row0 + c0, b_row0 + c_end, alpha, lane);
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();   // nobody leaves while a peer may still read its partial
   }
   tc_fence_before();
   __syncthreads();
@@ -502,19 +525,68 @@ EncodeFn encode_fn() {
 std::mutex g_tmap_mu;
 std::unordered_map<TmapKey, std::unique_ptr<CUtensorMap>, KeyHash> g_tmaps;
 
+int g_pdl = 0;   // launch with programmatic stream serialisation (set through hb_gemm_set_pdl)
+
 template <int KIND, int BN>
-cudaError_t launch_t(const GemmArgs& a, const DevParams& p, dim3 grid, const CUtensorMap* ta, const CUtensorMap* tb,
+cudaError_t launch_t(const GemmArgs& a, DevParams& p, dim3 grid, const CUtensorMap* ta, const CUtensorMap* tb,
                      cudaStream_t stream) {
   using C = Cfg<KIND, BN>;
   static bool attr_done = false;
+  static int max_clusters[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};   // co-resident clusters per cluster size (0 = unknown)
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
-  gemm_kernel<KIND, BN><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(*ta, *tb, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  int splits = p.splits;
+  if (splits > 1) {
+    // One cluster per output tile; shrink the split count until all clusters of the grid are co-resident
+    // (clusters live inside one GPC, so odd sizes can strand SMs).
+    const int tiles = grid.x * grid.y;
+    for (; splits > 1; --splits) {
+      if (splits > 1 && (splits - 1) * ((p.k_tiles + splits - 1) / splits) >= p.k_tiles) continue;
+      if (max_clusters[splits] == 0) {
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3(1, 1, splits);
+        q.blockDim = dim3(NUM_THREADS);
+        q.dynamicSmemBytes = C::SMEM_BYTES;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = 1; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = splits;
+        q.attrs = qa; q.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_kernel<KIND, BN>, &q) != cudaSuccess || n < 1) {
+          (void)cudaGetLastError();
+          n = -1;
+        }
+        max_clusters[splits] = n;
+      }
+      if (max_clusters[splits] >= tiles) break;
+    }
+    p.splits = splits;
+    grid.z = splits;
+    if (splits > 1) {
+      attrs[na].id = cudaLaunchAttributeClusterDimension;
+      attrs[na].val.clusterDim.x = 1; attrs[na].val.clusterDim.y = 1; attrs[na].val.clusterDim.z = splits;
+      ++na;
+    }
+  }
+  if (g_pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.gridDim = grid;
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, gemm_kernel<KIND, BN>, *ta, *tb, static_cast<const DevParams&>(p));
 }
 
 }  // namespace
@@ -578,7 +650,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   if (splits > k_tiles) splits = k_tiles;
   // Every split must own at least one K tile.
   while (splits > 1 && (splits - 1) * ((k_tiles + splits - 1) / splits) >= k_tiles) --splits;
-  if (splits > 1 && (a.workspace == nullptr || a.counters == nullptr)) return cudaErrorInvalidValue;
+  if (splits > 8) splits = 8;   // portable cluster size
 
   TmapKey ka{a.a, static_cast<uint64_t>(a.ra), static_cast<uint64_t>(fp4 ? a.k / 2 : a.k),
              static_cast<uint64_t>(fp4 ? a.lda / 2 : a.lda * 2), static_cast<uint32_t>(BM),
@@ -704,5 +776,8 @@ int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, con
 }
 
 void hb_clear_tmap_cache(void) { hb::clear_tmap_cache(); }
+
+void hb_gemm_set_pdl(int on) { hb::g_pdl = on != 0; }
+int hb_gemm_get_pdl(void) { return hb::g_pdl; }
 
 }  // extern "C"

@@ -24,6 +24,9 @@ int hb_gemm_peer(int kind, const void* a, const void* b, const void* sfa, const 
                  long long flag_offset, long long seq_offset, long long limit_ns, void* status, int ka_a, int ka_b,
                  void* stream);
 void hb_clear_tmap_cache(void);
+// GEMM launches use programmatic dependent launch (weight prefetch overlaps the preceding kernel) when on.
+void hb_gemm_set_pdl(int on);
+int hb_gemm_get_pdl(void);
 
 // ---- quantisers (quant.cu) -----------------------------------------------------------------------------
 int hb_quant_nvfp4(const void* x, long long ldx, int m, int k, int ka, const void* gscale, void* q, void* sf,

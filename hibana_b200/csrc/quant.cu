@@ -54,6 +54,7 @@ __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long lon
                                    const float* __restrict__ gscale, uint8_t* __restrict__ q,
                                    uint8_t* __restrict__ sf, int mode, const int* __restrict__ src_rows,
                                    const int* __restrict__ total_rows) {
+  grid_dep_launch();   // a GEMM launched as a programmatic dependent may start prefetching its weights
   const int groups_pad = ka * 4;
   const int rows_pad = ((m + 127) >> 7) << 7;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -105,6 +106,7 @@ norm_quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __re
                         const __nv_bfloat16* __restrict__ w, float eps, int gemma, int m, int k, int ka,
                         const float* __restrict__ gscale, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
                         __nv_bfloat16* __restrict__ normed) {
+  grid_dep_launch();   // a GEMM launched as a programmatic dependent may start prefetching its weights
   __shared__ float red[40];
   const int row = blockIdx.x;
   const int tid = threadIdx.x;

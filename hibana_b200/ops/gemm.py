@@ -7,6 +7,7 @@ tactic -> FlashInfer mm_fp4, and FP8 GEMV / cuBLASLt) is hibana/kernels/ops.py:5
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -16,6 +17,20 @@ from .nvfp4 import Nvfp4Tensor
 
 EPI_STORE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_STORE_F32 = 0, 1, 2, 3
 NUM_SMS = 148
+
+nv.register("hb_gemm_set_pdl", [nv.I], void=True)
+
+
+_PDL_INIT = False
+
+
+def set_pdl(on: bool) -> None:
+    """GEMMs launch as programmatic dependents: their weight prefetch overlaps the kernel before them."""
+    global _PDL_INIT
+    _PDL_INIT = True
+    if nv.available():
+        nv.lib().hb_gemm_set_pdl(int(on))
+
 
 
 def _plan(m: int, n: int, k_tiles: int, max_ws_bytes: int) -> tuple[bool, int, int]:
@@ -27,9 +42,7 @@ def _plan(m: int, n: int, k_tiles: int, max_ws_bytes: int) -> tuple[bool, int, i
         if tiles < NUM_SMS:
             # One CTA per SM streams ~1/148 of HBM bandwidth, so fill the SMs without spilling into a second,
             # mostly empty wave; every split keeps at least two K tiles.
-            splits = max(1, min(NUM_SMS // tiles, k_tiles // 2, 16))
-            while splits > 1 and splits * m * n * 4 > max_ws_bytes:
-                splits -= 1
+            splits = max(1, min(NUM_SMS // tiles, k_tiles // 2, 8))     # 8 = portable cluster size
         return True, bn, splits
     return False, (256 if n >= 256 else 128), 1
 
@@ -37,10 +50,10 @@ def _plan(m: int, n: int, k_tiles: int, max_ws_bytes: int) -> tuple[bool, int, i
 def _launch(kind: int, a, b, sfa, sfb, ra: int, rb: int, k: int, lda: int, ldb: int, out: torch.Tensor,
             residual: Optional[torch.Tensor], alpha: float, alpha_ptr: Optional[torch.Tensor], epilogue: int,
             swap: bool, splits: int, bn: int, ka_a: int, ka_b: int) -> None:
+    if not _PDL_INIT:
+        set_pdl(os.environ.get("HIBANA_PDL", "1") != "0")
     st = nv.device_state(out.device)
-    ws = cnt = None
-    if splits > 1:
-        ws, cnt = st.workspace(splits * ra * rb * 4)
+    ws = cnt = None     # split-K reduces through distributed shared memory; no global scratch
     code = nv.lib().hb_gemm(kind, a.data_ptr(), b.data_ptr(), nv.ptr(sfa), nv.ptr(sfb), ra, rb, k, lda, ldb,
                             out.data_ptr(), out.stride(0), nv.ptr(residual), alpha, nv.ptr(alpha_ptr), epilogue,
                             int(swap), splits, nv.ptr(ws), nv.ptr(cnt), st.status.data_ptr(), bn, ka_a, ka_b,

@@ -26,7 +26,9 @@ def main() -> None:
     ap.add_argument("--once", action="store_true", help="single launch per shape, no timing loop (for ncu)")
     ap.add_argument("--graph", action="store_true",
                     help="time a CUDA-graph replay that cycles through weight copies larger than L2 in total")
+    ap.add_argument("--pdl", action="store_true", help="launch GEMMs as programmatic dependents")
     args = ap.parse_args()
+    gemm.set_pdl(args.pdl)
     peaks = measured_peaks()
     dev = torch.device("cuda")
     for spec in args.shapes:
