@@ -60,6 +60,11 @@ int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long lo
 int hb_attn_merge(const void* part_o, const void* part_lse, void* out, long long rows_heads, int splits, int d,
                   void* stream);
 // Tensor-core flash-decoding (attn_decode.cu): bf16 KV, rows_per_sequence * (hq / hkv) <= 16.
+// Prefill / chunked-prefill attention on tcgen05 (bf16 KV, head dim 64 or 128); any number of new rows per sequence.
+int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                    const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
+                    const void* q_indptr, void* out, int batch, int max_rows, int hq, int hkv, int d, float scale,
+                    int causal, void* status, void* stream);
 int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
                    const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
                    const void* q_indptr, void* out, void* part_o, void* part_lse, int batch, int max_rows, int hq,

@@ -1,13 +1,15 @@
 """Paged GQA attention over the token-granular KV pool (decode, speculative verify, chunked prefill).
 
 `paged_attention` is the single entry: query rows of a ragged batch attend to their sequence's context through
-the block table. Kernel: csrc/attn.cu (split-KV, LSE merge). The plain-PyTorch reference below is the CPU path
+the block table. Kernels: csrc/attn_prefill.cu (tcgen05 prefill), csrc/attn_decode.cu (tensor-core flash-decoding,
+up to 16 query rows per kv head), csrc/attn.cu (general split-KV + LSE merge; fp8 KV, head dim 256 prefill). The plain-PyTorch reference below is the CPU path
 and the GPU tests' oracle. Reference counterparts: hibana/kernels/ops.py:131-161 (ragged prefill),
 hibana/model/attention.py:69-126, hibana/kernels/csrc/verify_attn.cu.
 """
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -19,6 +21,8 @@ nv.register("hb_attn_paged", [P, P, P, L, P, L, P, P, P, P, P, P, I, I, I, I, I,
 
 nv.register("hb_attn_merge", [P, P, P, L, I, I, P])
 nv.register("hb_attn_decode", [P, P, P, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, P, P])
+
+nv.register("hb_attn_prefill", [P, P, P, L, P, L, P, P, P, P, I, I, I, I, I, Fl, I, P, P])
 
 NUM_SMS = 148
 
@@ -111,6 +115,13 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         if splits > 1:
             nv.check(nv.lib().hb_attn_merge(workspace.part_o.data_ptr(), workspace.part_lse.data_ptr(),
                                             out.data_ptr(), t * hq, splits, d, nv.stream()), "hb_attn_merge")
+        return out
+    if not fp8 and d in (64, 128) and q_indptr is not None and os.environ.get("HIBANA_PREFILL_ATTN", "tc") == "tc":
+        st = nv.device_state(q.device)
+        nv.check(nv.lib().hb_attn_prefill(
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), kv_indices.data_ptr(),
+            kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), q_indptr.data_ptr(), out.data_ptr(), b,
+            max_rows, hq, hkv, d, scale, int(causal), st.status.data_ptr(), nv.stream()), "hb_attn_prefill")
         return out
     nv.check(nv.lib().hb_attn_paged(
         q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), kv_indices.data_ptr(),

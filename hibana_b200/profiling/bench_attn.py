@@ -1,0 +1,75 @@
+"""Attention micro-benchmark: python -m hibana_b200.profiling.bench_attn [--mode prefill|decode] ...
+
+prefill: `--batch` sequences of `--rows` new tokens on top of `--prefix` cached tokens; reports TFLOP/s of the causal
+         work (4 * D * visible (query, key) pairs per query head) against the measured bf16 GEMM peak.
+decode : one token per sequence at context `--ctx`; reports KV bytes / time against the measured copy bandwidth.
+The KV pool is token-granular with shuffled slots, exactly as the engine lays it out.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from ..ops import attention
+from .timing import measured_peaks, time_cuda
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mode", default="prefill")
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--rows", type=int, default=2048)
+    ap.add_argument("--prefix", type=int, default=0)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--hq", type=int, default=40)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--d", type=int, default=128)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--once", action="store_true", help="single launch, no timing loop (for ncu)")
+    args = ap.parse_args()
+    dev = torch.device("cuda")
+    peaks = measured_peaks()
+    b, hq, hkv, d = args.batch, args.hq, args.hkv, args.d
+    if args.mode == "prefill":
+        rows, ctx_n = args.rows, args.prefix + args.rows
+    else:
+        rows, ctx_n = 1, args.ctx
+    slots = b * ctx_n + 1
+    kp = torch.randn(slots, hkv, d, device=dev).bfloat16()
+    vp = torch.randn(slots, hkv, d, device=dev).bfloat16()
+    perm = (torch.randperm(slots - 1, device=dev) + 1).int()
+    idx = perm.view(b, ctx_n).contiguous()
+    ctx = torch.full((b,), ctx_n, dtype=torch.int32, device=dev)
+    q = torch.randn(b * rows, hq, d, device=dev).bfloat16()
+    out = torch.empty_like(q)
+    if args.mode == "prefill":
+        indptr = (torch.arange(b + 1, device=dev) * rows).int()
+        fn = lambda: attention.paged_attention(q, kp, vp, idx, ctx, q_indptr=indptr, max_rows=rows, out=out)  # noqa
+        pairs = b * (rows * args.prefix + rows * (rows + 1) // 2)
+        flops = 4.0 * d * pairs * hq
+    else:
+        splits = attention.choose_splits(b, hkv, ctx_n)
+        ws = attention.AttnWorkspace(b, hq, d, splits, dev)
+        fn = lambda: attention.paged_attention(q, kp, vp, idx, ctx, splits=splits, workspace=ws, out=out)  # noqa
+        flops = 4.0 * d * b * ctx_n * hq
+    if args.once:
+        fn()
+        torch.cuda.synchronize()
+        return
+    t = time_cuda(fn, iters=args.iters)
+    ms = t["median_ms"]
+    kv_bytes = 2.0 * b * ctx_n * hkv * d * 2
+    res = {"mode": args.mode, "batch": b, "rows": rows, "ctx": ctx_n, "hq": hq, "hkv": hkv, "d": d,
+           "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "kv_gbs": round(kv_bytes / ms / 1e6, 1),
+           "peaks": peaks["source"]}
+    if args.mode == "prefill":
+        res["frac_of_bf16_peak"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 3)
+    else:
+        res["frac_of_hbm"] = round(kv_bytes / ms / 1e6 / peaks["hbm_gbs"], 3)
+    print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()

@@ -205,3 +205,23 @@ def test_tensor_core_decode_verify_rows(hq, hkv, d, rows, splits):
     _close(got, ref, 2e-2)
     from hibana_b200 import _native as nv
     assert nv.read_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("hq,hkv,d", [(40, 8, 128), (4, 2, 64), (32, 2, 128), (3, 1, 64)])
+def test_tcgen05_prefill_attention(hq, hkv, d):
+    """Ragged prefill / chunked prefill over cached prefixes: tile edges, partial query blocks, 1-row sequences."""
+    rows, ctxs = [300, 17, 128, 1, 257], [300, 500, 1200, 77, 257]
+    q, kp, vp, idx, ctx, indptr, sr = _attn_case(5, rows, ctxs, hq, hkv, d, seed=11)
+    ref = attention.paged_attention(q, kp, vp, idx, ctx, q_indptr=indptr, max_rows=max(rows), seq_rows=sr)
+    got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(), q_indptr=indptr.cuda(),
+                                    max_rows=max(rows), seq_rows=sr.cuda())
+    _close(got, ref, 2e-2)
+    from hibana_b200 import _native as nv
+    assert nv.read_status() == 0
+    # non-causal (encoder-style) rows see the whole context
+    ref = attention.paged_attention(q, kp, vp, idx, ctx, q_indptr=indptr, max_rows=max(rows), seq_rows=sr,
+                                    causal=False)
+    got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(), q_indptr=indptr.cuda(),
+                                    max_rows=max(rows), seq_rows=sr.cuda(), causal=False)
+    _close(got, ref, 2e-2)
