@@ -5,18 +5,24 @@
 // gathered once from the token-granular pool serves the whole GQA group. Per 128-key tile:
 //
 //   producers (3 warps)   gather K and V rows by slot id with 16-byte cp.async into 128-byte-swizzled tiles
-//                         (the layout TMA would produce; rows of a paged pool are not a TMA box), 2 stages;
-//   issuer (1 lane)       S = Q K^T (kind::f16, both operands K-major) into TMEM columns [0, 128); after the
-//                         softmax warps have published P, PV = P V (V as MN-major B operand) into [128, 128 + D);
-//   softmax (4 warps)     thread r owns query row r = TMEM lane r: two passes over S (row max, then exp2 and the
-//                         bf16 P tile into swizzled shared memory), then O = O * alpha + PV in registers.
+//                         (the layout TMA would produce; rows of a paged pool are not a TMA box). K and V have
+//                         separate 2-stage rings: a K stage is free as soon as its S MMA has run, so K runs one
+//                         tile ahead of V;
+//   issuer (1 lane)       S = Q K^T (kind::f16, both operands K-major) into one of two TMEM score buffers, two
+//                         tiles ahead of the softmax; once the softmax warps have published P, O += P V (V as
+//                         MN-major B operand) accumulates in TMEM;
+//   softmax (4 warps)     thread r owns query row r = TMEM lane r: one tcgen05.ld of the whole score row, row max,
+//                         exp2, bf16 P tile into swizzled shared memory. The running maximum that O and the row
+//                         sum refer to is only raised (and O rescaled in TMEM) when the new maximum exceeds it by
+//                         more than 2^8, so the rescale is rare and the tensor pipe overlaps the softmax.
 //
-// S for tile t + 1 is issued right after PV for tile t, so it overlaps the O update. Causal masking follows the
-// ragged-batch rule of the engine: row token j of a sequence with R new rows and context ctx sees keys
-// [0, ctx - R + j]. All waits are bounded; a timeout raises the status word and every role leaves.
+// Causal masking follows the ragged-batch rule of the engine: row token j of a sequence with R new rows and
+// context ctx sees keys [0, ctx - R + j]. All waits are bounded; a timeout raises the status word and every role
+// leaves.
 //
 // Replaces the reference's FlashInfer ragged-prefill wrapper + prefix kernel + LSE merge
 // (hibana/kernels/ops.py:131-161, hibana/model/attention.py:73-96, hibana/kernels/csrc/verify_attn.cu prefix_kernel).
+#include "gemm.cuh"
 #include "hb_api.h"
 #include "hb_common.cuh"
 
@@ -41,21 +47,23 @@ struct PfParams {
   const int* q_indptr;
   __nv_bfloat16* out;
   int hq, hkv;
+  int use_tma;                // pools are TMA-addressable: contiguous slot runs travel as bulk tensor copies
   float scale_log2;
   int causal;
   int* status;
+  unsigned long long* prof;   // optional cycle counters (null = off)
 };
 
 template <int D>
 struct PfCfg {
   static constexpr int HALVES = D / 64;                      // 64-element (128-byte) column blocks of a row
   static constexpr int Q_BYTES = PF_ROWS * D * 2;
-  static constexpr int KV_TILE = PF_KT * D * 2;              // one of K or V
-  static constexpr int STAGE_BYTES = 2 * KV_TILE;
+  static constexpr int KV_TILE = PF_KT * D * 2;              // one stage of K or of V
   static constexpr int P_BYTES = PF_ROWS * PF_KT * 2;
-  static constexpr int BAR_OFF = Q_BYTES + PF_STAGES * STAGE_BYTES + P_BYTES;
+  static constexpr int BAR_OFF = Q_BYTES + 2 * PF_STAGES * KV_TILE + P_BYTES;
   static constexpr int SMEM = BAR_OFF + 256 + 1024;
-  static constexpr int TMEM_COLS = PF_KT + D <= 256 ? 256 : 512;
+  static constexpr int TMEM_COLS = 512;                      // S0 [0,128) S1 [128,256) O [256, 256 + D)
+  static constexpr float RESCALE_GAP = 8.f;                  // log2 units
 };
 
 __device__ __forceinline__ void cp16(uint32_t saddr, const void* g) {
@@ -65,6 +73,15 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// Cycle accounting of one representative thread per role (softmax thread 0, producer 0, the issuer), summed over
+// CTAs into p.prof: where each role's time goes. Costs one predictable branch per site when off.
+#define PF_T0() const long long _t0 = p.prof ? clock64() : 0
+#define PF_ACC(slot, cond) do { if (p.prof && (cond)) atomicAdd(p.prof + (slot), (unsigned long long)(clock64() - _t0)); } while (0)
+
+// Bounded wait with a warp-uniform verdict, for warps that go on to warp-wide tcgen05.ld / st.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort, int* status, int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort, status, code));
 }
 __device__ __forceinline__ void st_zero16(uint32_t saddr) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(saddr), "r"(0) : "memory");
@@ -77,18 +94,22 @@ __device__ __forceinline__ uint32_t sw_off(int r, int part, int rows) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfParams p) {
+__global__ void __launch_bounds__(PF_THREADS, 1)
+attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, const PfParams p) {
   using C = PfCfg<D>;
   constexpr int CPR = D / 8;   // 16-byte chunks per row
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;
-  uint8_t* kv_s = smem + C::Q_BYTES;
-  uint8_t* p_s = kv_s + PF_STAGES * C::STAGE_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF);
-  uint64_t* empty = full + PF_STAGES;
-  uint64_t* s_ready = empty + PF_STAGES;
-  uint64_t* p_ready = s_ready + 1;
+  uint8_t* k_s = smem + C::Q_BYTES;
+  uint8_t* v_s = k_s + PF_STAGES * C::KV_TILE;
+  uint8_t* p_s = v_s + PF_STAGES * C::KV_TILE;
+  uint64_t* kfull = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF);
+  uint64_t* vfull = kfull + PF_STAGES;
+  uint64_t* kempty = vfull + PF_STAGES;
+  uint64_t* vempty = kempty + PF_STAGES;
+  uint64_t* s_ready = vempty + PF_STAGES;   // [2], one per score buffer
+  uint64_t* p_ready = s_ready + 2;
   uint64_t* pv_ready = p_ready + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_ready + 1);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -111,14 +132,21 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfPar
 
   if (tid == 0) {
     for (int s = 0; s < PF_STAGES; ++s) {
-      mbar_init(&full[s], PF_PRODUCERS);
-      mbar_init(&empty[s], 1);
+      mbar_init(&kfull[s], PF_PRODUCERS);
+      mbar_init(&vfull[s], PF_PRODUCERS);
+      mbar_init(&kempty[s], 1);
+      mbar_init(&vempty[s], 1);
     }
-    mbar_init(s_ready, 1);
+    mbar_init(&s_ready[0], 1);
+    mbar_init(&s_ready[1], 1);
     mbar_init(p_ready, PF_ROWS);
     mbar_init(pv_ready, 1);
     *abort = 0;
     fence_mbar_init();
+    if (p.use_tma) {
+      prefetch_tmap(&tmk);
+      prefetch_tmap(&tmv);
+    }
   }
   if (warp == 7) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -128,14 +156,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfPar
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t s_tmem = tmem_base;
-  const uint32_t pv_tmem = tmem_base + PF_KT;
+  const uint32_t o_tmem = tmem_base + 2 * PF_KT;
 
   if (warp >= 4 && warp < 7) {
     // ------------------------------------------------------------------ producers
     const int ptid = tid - 128;
     const int* idx_row = p.kv_indices + static_cast<long long>(p.seq_rows ? p.seq_rows[b] : b) * p.ld_idx;
-    // Q rows (zero padded), covered by the first stage's barrier.
+    // Q rows (zero padded); they travel in the first cp.async group, i.e. with K tile 0.
     for (int c = ptid; c < PF_ROWS * CPR; c += PF_PRODUCERS) {
       const int r = c / CPR, part = c % CPR;
       const uint32_t dst = smem_u32(q_s) + sw_off(r, part, PF_ROWS);
@@ -146,96 +173,168 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfPar
         st_zero16(dst);
       }
     }
-    bool live = true;
-    // Thread layout of a tile copy: 16 consecutive threads move one 256-byte (D = 128) row, so a thread keeps its
-    // 16-byte column `part` and walks rows rg, rg + RG, ...; the rows' slot ids are fetched (one broadcast load
-    // per row) before the stage wait, so their latency hides behind it.
-    constexpr int RG = PF_PRODUCERS / CPR;                    // rows per pass over the producer threads
-    constexpr int NR = (PF_KT + RG - 1) / RG;                 // rows per thread and tile
-    const int part = ptid % CPR, rg = ptid / CPR;
-    const uint32_t part_off = static_cast<uint32_t>((part >> 3) * PF_KT * 128);
-    const long long col = static_cast<long long>(kvh) * D + part * 8;
-    for (int t = 0; t < ntiles; ++t) {
-      const int s = t % PF_STAGES;
-      const int k0 = t * PF_KT;
-      int slot[NR];
+    // A tile is moved as four 32-key sub-blocks, one producer warp each (warp j % 3). Lane l fetches the slot id
+    // of key l of the sub-block. Slots of a sequence are handed out in ascending runs, so most sub-blocks sit in
+    // 32 consecutive pool rows: then one lane issues a bulk tensor copy per 128-byte column block (box = 32 rows
+    // x 64 elements, 128-byte swizzle, row pitch = one pool slot) that completes on the tile's barrier by
+    // transaction bytes. Otherwise (fragmented pool, tail of the context) the warp gathers the rows with 16-byte
+    // cp.async: the LSU path keeps only ~16 KB in flight per SM, an order of magnitude less than the TMA unit.
+    const int pw = warp - 4;
+    constexpr int SB = (PF_KT / 32 + 2) / 3;   // sub-blocks per warp and tile
+    // Slot ids of this warp's sub-blocks of tile t (one per lane); -1 beyond the visible keys.
+    auto fetch_slots = [&](int t, int (&sl)[SB]) {
 #pragma unroll
-      for (int i = 0; i < NR; ++i) {
-        const int r = rg + i * RG;
-        slot[i] = (r < PF_KT && k0 + r < kmax) ? __ldg(idx_row + k0 + r) : -1;
+      for (int i = 0; i < SB; ++i) {
+        const int j = pw + 3 * i;
+        const int key = t * PF_KT + j * 32 + lane;
+        sl[i] = (j < PF_KT / 32 && t < ntiles && key < kmax) ? __ldg(idx_row + key) : -1;
       }
-      if (t >= 1) {
-        // Tile t - 1 was issued a whole tile period ago: it has landed. Make it visible to the tensor-core proxy
-        // and signal it before (possibly) sleeping on this tile's stage.
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        fence_proxy_async_smem();
-        mbar_arrive(&full[(t - 1) % PF_STAGES]);
-      }
-      if (t >= PF_STAGES && !mbar_wait(&empty[s], ((t / PF_STAGES) - 1) & 1, abort, p.status, kTimeoutEmpty)) {
-        live = false;
-        break;
-      }
-      const uint32_t kdst = smem_u32(kv_s + s * C::STAGE_BYTES) + part_off;
-      const uint32_t vdst = kdst + C::KV_TILE;
+    };
+    auto copy_tile = [&](int t, const int (&sl)[SB], const __nv_bfloat16* pool, const CUtensorMap* tm, uint8_t* ring,
+                         uint64_t* bar) {
+      uint8_t* tile = ring + (t % PF_STAGES) * C::KV_TILE;
 #pragma unroll
-      for (int i = 0; i < NR; ++i) {
-        const int r = rg + i * RG;
-        if (r < PF_KT) {
-          const uint32_t off = static_cast<uint32_t>(r * 128 + (((part & 7) ^ (r & 7)) << 4));
-          if (slot[i] >= 0) {
-            const long long src = static_cast<long long>(slot[i]) * p.pool_stride + col;
-            cp16(kdst + off, p.k_pool + src);
-            cp16(vdst + off, p.v_pool + src);
-          } else {
-            st_zero16(kdst + off);
-            st_zero16(vdst + off);
+      for (int i = 0; i < SB; ++i) {
+        const int j = pw + 3 * i;
+        if (j >= PF_KT / 32) break;
+        const int slot = sl[i];
+        const int slot0 = __shfl_sync(0xffffffffu, slot, 0);
+        const bool run = p.use_tma && __all_sync(0xffffffffu, slot >= 0 && slot == slot0 + lane);
+        if (run) {
+          if (lane == 0) {
+            mbar_add_tx(bar, 32 * D * 2);   // bytes only: this lane's arrival comes with the other producers'
+#pragma unroll
+            for (int h = 0; h < C::HALVES; ++h)
+              tma_load_2d(tile + h * (PF_KT * 128) + j * (32 * 128), tm, bar, kvh * D + h * 64, slot0);
+          }
+        } else {
+          // lane -> (row = i * (32 / CPR) + lane / CPR, 16-byte column = lane % CPR)
+          constexpr int RPI = 32 / CPR;
+          const int part = lane % CPR;
+          const uint32_t dst0 = smem_u32(tile) + (part >> 3) * (PF_KT * 128);
+#pragma unroll
+          for (int ii = 0; ii < 32 / RPI; ++ii) {
+            const int rr = ii * RPI + lane / CPR;
+            const int s1 = __shfl_sync(0xffffffffu, slot, rr);
+            const int r = j * 32 + rr;
+            const uint32_t dst = dst0 + r * 128 + (((part & 7) ^ (r & 7)) << 4);
+            if (s1 >= 0) cp16(dst, pool + static_cast<long long>(s1) * p.pool_stride + kvh * D + part * 8);
+            else st_zero16(dst);
           }
         }
       }
+    };
+    // cp.async groups in order: K0, [K1, V0], [K2, V1], ...  After iteration t commits V(t), "at most two groups
+    // pending" means K(t) and V(t - 1) have landed: fence them for the tensor-core proxy and signal.
+    bool live = ntiles > 0;
+    int sl_v[SB], sl_k[SB], sl_pre[SB];   // slots of tile t (V copy), t + 1 (K copy), t + 2 (in flight)
+    fetch_slots(0, sl_v);
+    fetch_slots(1, sl_k);
+    if (live) copy_tile(0, sl_v, p.k_pool, &tmk, k_s, &kfull[0]);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int t = 0; live && t < ntiles; ++t) {
+      fetch_slots(t + 2, sl_pre);   // latency hides behind the stage waits below
+      if (t + 1 < ntiles) {
+        {
+          PF_T0();
+          if (t + 1 >= PF_STAGES && !mbar_wait(&kempty[(t + 1) % PF_STAGES], (((t + 1) / PF_STAGES) - 1) & 1, abort,
+                                               p.status, kTimeoutEmpty)) {
+            live = false;
+            break;
+          }
+          PF_ACC(6, ptid == 0);
+        }
+        {
+          PF_T0();
+          copy_tile(t + 1, sl_k, p.k_pool, &tmk, k_s, &kfull[(t + 1) % PF_STAGES]);
+          PF_ACC(8, ptid == 0);
+        }
+      }
       asm volatile("cp.async.commit_group;" ::: "memory");
+      {
+        PF_T0();
+        if (t >= PF_STAGES &&
+            !mbar_wait(&vempty[t % PF_STAGES], ((t / PF_STAGES) - 1) & 1, abort, p.status, kTimeoutEmpty)) {
+          live = false;
+          break;
+        }
+        PF_ACC(7, ptid == 0);
+      }
+      {
+        PF_T0();
+        copy_tile(t, sl_v, p.v_pool, &tmv, v_s, &vfull[t % PF_STAGES]);
+        PF_ACC(8, ptid == 0);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      PF_T0();
+      asm volatile("cp.async.wait_group 2;" ::: "memory");
+      PF_ACC(9, ptid == 0);
+      fence_proxy_async_smem();
+      mbar_arrive(&kfull[t % PF_STAGES]);
+      if (t >= 1) mbar_arrive(&vfull[(t - 1) % PF_STAGES]);
+#pragma unroll
+      for (int i = 0; i < SB; ++i) {
+        sl_v[i] = sl_k[i];
+        sl_k[i] = sl_pre[i];
+      }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");   // nothing may land after the CTA has gone
     fence_proxy_async_smem();
-    if (live && ntiles > 0) mbar_arrive(&full[(ntiles - 1) % PF_STAGES]);
+    if (live) mbar_arrive(&vfull[(ntiles - 1) % PF_STAGES]);
   } else if (warp == 7) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(PF_ROWS, PF_KT);
       constexpr uint32_t idesc_pv = make_idesc_bf16(PF_ROWS, D, 0, 1);
       const uint32_t q_a = smem_u32(q_s), p_a = smem_u32(p_s);
-      auto issue_qk = [&](int t) {
-        const uint32_t k_a = smem_u32(kv_s + (t % PF_STAGES) * C::STAGE_BYTES);
+      // S(t) = Q K(t)^T into score buffer t % 2; releases the K stage and publishes the scores when done.
+      auto issue_qk = [&](int t) -> bool {
+        const int s = t % PF_STAGES;
+        {
+          PF_T0();
+          if (!mbar_wait(&kfull[s], (t / PF_STAGES) & 1, abort, p.status, kTimeoutFull)) return false;
+          PF_ACC(5, true);
+        }
+        tc_fence_after();
+        const uint32_t k_a = smem_u32(k_s + s * C::KV_TILE);
+        const uint32_t s_t = tmem_base + (t & 1) * PF_KT;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t in_row = (ks & 3) * 32;   // 16 elements = 32 bytes inside the 128-byte swizzled row
-          mma_f16(s_tmem, make_desc_sw128(q_a + (ks >> 2) * (PF_ROWS * 128) + in_row),
+          mma_f16(s_t, make_desc_sw128(q_a + (ks >> 2) * (PF_ROWS * 128) + in_row),
                   make_desc_sw128(k_a + (ks >> 2) * (PF_KT * 128) + in_row), idesc_qk, ks > 0 ? 1u : 0u);
         }
-        tc_commit(s_ready);
+        tc_commit(&kempty[s]);
+        tc_commit(&s_ready[t & 1]);
+        return true;
       };
-      bool ok = ntiles > 0 && mbar_wait(&full[0], 0, abort, p.status, kTimeoutFull);
-      if (ok) {
-        tc_fence_after();
-        issue_qk(0);
-      }
+      bool ok = ntiles > 0 && issue_qk(0);
+      if (ok && ntiles > 1) ok = issue_qk(1);
       for (int t = 0; ok && t < ntiles; ++t) {
-        if (!mbar_wait(p_ready, t & 1, abort, p.status, kTimeoutAccum)) break;
+        const int s = t % PF_STAGES;
+        {
+          PF_T0();
+          if (!mbar_wait(p_ready, t & 1, abort, p.status, kTimeoutAccum)) break;
+          PF_ACC(3, true);
+        }
+        {
+          PF_T0();
+          if (!mbar_wait(&vfull[s], (t / PF_STAGES) & 1, abort, p.status, kTimeoutFull)) break;
+          PF_ACC(4, true);
+        }
         tc_fence_after();
-        const uint32_t v_a = smem_u32(kv_s + (t % PF_STAGES) * C::STAGE_BYTES) + C::KV_TILE;
+        const uint32_t v_a = smem_u32(v_s + s * C::KV_TILE);
 #pragma unroll
         for (int kk = 0; kk < PF_KT / 16; ++kk) {
           const uint64_t adesc = make_desc_sw128(p_a + (kk >> 2) * (PF_ROWS * 128) + (kk & 3) * 32);
           // 16 keys = two 8-row groups 1024 bytes apart; the D / 64 column blocks are PF_KT * 128 bytes apart
           const uint64_t bdesc = make_desc_sw128_mn(v_a + kk * 2048, PF_KT * 128, 1024);
-          mma_f16(pv_tmem, adesc, bdesc, idesc_pv, kk > 0 ? 1u : 0u);
+          mma_f16(o_tmem, adesc, bdesc, idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
         }
+        tc_commit(&vempty[s]);
         tc_commit(pv_ready);
-        tc_commit(&empty[t % PF_STAGES]);
-        if (t + 1 < ntiles) {
-          if (!mbar_wait(&full[(t + 1) % PF_STAGES], ((t + 1) / PF_STAGES) & 1, abort, p.status, kTimeoutFull)) break;
-          tc_fence_after();
-          issue_qk(t + 1);
-        }
+        // score buffer t % 2 was read completely before p_ready(t): refill it two tiles ahead
+        if (t + 2 < ntiles) ok = issue_qk(t + 2);
       }
     }
   } else {
@@ -246,68 +345,83 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfPar
     const int tok = tok0 + r / g;
     // last visible key position (inclusive)
     const int lim = row_ok ? (p.causal ? ctx - R + tok : ctx - 1) : -1;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    float m_ref = -INFINITY, l = 0.f;   // O and l are relative to 2^m_ref
     const uint32_t p_row = smem_u32(p_s) + r * 128;
     bool ok = true;
+    const long long t_begin = p.prof ? clock64() : 0;
     for (int t = 0; t < ntiles; ++t) {
-      if (!mbar_wait(s_ready, t & 1, abort, p.status, kTimeoutAccum)) {
-        ok = false;
-        break;
+      {
+        PF_T0();
+        if (!warp_wait(&s_ready[t & 1], (t >> 1) & 1, abort, p.status, kTimeoutAccum)) {
+          ok = false;
+          break;
+        }
+        PF_ACC(0, tid == 0);
       }
       tc_fence_after();
       const int k0 = t * PF_KT;
-      // A tile entirely at or before the row's last visible key needs no masking (the common case); four
-      // independent accumulators keep the dependency chains short (one softmax warp per scheduler: no other
-      // warp hides ALU latency).
-      const bool full_vis = k0 + PF_KT - 1 <= lim;
-      // pass 1: row maximum of the visible scores
+      const uint32_t s_t = tmem_base + (t & 1) * PF_KT + tlane;
+      // The two passes over the score row are rolled loops over 32-column chunks: fully unrolled, the softmax body
+      // alone is several thousand instructions, and streaming that through the instruction cache every tile cost
+      // more than the arithmetic. `rel` = last visible column of this tile for this row (>= 127: no masking).
+      const int rel = lim - k0;
+      const long long t_math = p.prof ? clock64() : 0;
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
+#pragma unroll 1
       for (int c0 = 0; c0 < PF_KT; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(s_tmem + tlane + c0, v);
+        tmem_ld_32x32(s_t + c0, v);
         tmem_ld_wait();
-        if (full_vis) {
+        const int rc = rel - c0;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[j]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (k0 + c0 + j <= lim) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[j]));
-        }
+        for (int j = 0; j < 32; ++j)
+          mx4[j & 3] = fmaxf(mx4[j & 3], j <= rc ? __uint_as_float(v[j]) : -INFINITY);
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float m_new = fmaxf(m, mx * p.scale_log2);
-      const float alpha = m_new == -INFINITY ? 1.f : ex2(m - m_new);
-      const float neg_m = m_new == -INFINITY ? 0.f : -m_new;
-      m = m_new;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      // pass 2: probabilities, row sum, bf16 P tile (K-major, swizzled) for the second MMA
+      const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      // P(t) overwrites the buffer O += P(t - 1) V(t - 1) reads, and a rescale touches O: both need that MMA done.
+      {
+        PF_T0();
+        if (t > 0 && !warp_wait(pv_ready, (t - 1) & 1, abort, p.status, kTimeoutAccum)) {
+          ok = false;
+          break;
+        }
+        PF_ACC(1, tid == 0);
+      }
+      if (t == 0) {
+        m_ref = m_tile;
+      } else if (__any_sync(0xffffffffu, m_tile > m_ref + C::RESCALE_GAP)) {
+        // Raise the reference (all lanes of the warp: tcgen05.ld / st are warp-wide) and rescale O and l.
+        const float m_new = fmaxf(m_ref, m_tile);
+        const float alpha = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);
+        m_ref = m_new;
+        l *= alpha;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(o_tmem + tlane + c0, o);
+          tmem_ld_wait();
 #pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          tmem_st_32x32(o_tmem + tlane + c0, o);
+        }
+        tmem_st_wait();
+      }
+      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
       for (int c0 = 0; c0 < PF_KT; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(s_tmem + tlane + c0, v);
+        tmem_ld_32x32(s_t + c0, v);
         tmem_ld_wait();
+        const int rc = rel - c0;
         uint32_t w[16];
-        if (full_vis) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float p0 = ex2(fmaf(__uint_as_float(v[j]), p.scale_log2, neg_m));
-            const float p1 = ex2(fmaf(__uint_as_float(v[j + 1]), p.scale_log2, neg_m));
-            sum4[(j >> 1) & 3] += p0 + p1;
-            w[j >> 1] = pack_bf16(p0, p1);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float p0 = k0 + c0 + j <= lim ? ex2(fmaf(__uint_as_float(v[j]), p.scale_log2, neg_m)) : 0.f;
-            const float p1 = k0 + c0 + j + 1 <= lim ? ex2(fmaf(__uint_as_float(v[j + 1]), p.scale_log2, neg_m)) : 0.f;
-            sum4[(j >> 1) & 3] += p0 + p1;
-            w[j >> 1] = pack_bf16(p0, p1);
-          }
+        for (int j = 0; j < 32; j += 2) {
+          const float p0 = j <= rc ? ex2(fmaf(__uint_as_float(v[j]), p.scale_log2, neg_m)) : 0.f;
+          const float p1 = j + 1 <= rc ? ex2(fmaf(__uint_as_float(v[j + 1]), p.scale_log2, neg_m)) : 0.f;
+          sum4[(j >> 1) & 3] += p0 + p1;
+          w[j >> 1] = pack_bf16(p0, p1);
         }
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
@@ -318,34 +432,46 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfPar
                        : "memory");
         }
       }
-      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      l = l * alpha + sum;
-      tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(p_ready);
-      if (!mbar_wait(pv_ready, t & 1, abort, p.status, kTimeoutAccum)) {
-        ok = false;
-        break;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      if (p.prof && tid == 0) atomicAdd(p.prof + 13, (unsigned long long)(clock64() - t_math));
+      {
+        PF_T0();
+        tc_fence_before();
+        fence_proxy_async_smem();
+        mbar_arrive(p_ready);
+        PF_ACC(14, tid == 0);
       }
-      tc_fence_after();
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(pv_tmem + tlane + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o[c0 + j] = fmaf(o[c0 + j], alpha, __uint_as_float(v[j]));
-      }
-      tc_fence_before();
     }
-    if (ok && row_ok) {
+    if (p.prof && tid == 0) {
+      atomicAdd(p.prof + 10, (unsigned long long)(clock64() - t_begin));
+      atomicAdd(p.prof + 11, (unsigned long long)ntiles);
+    }
+    if (ok && ntiles > 0) ok = warp_wait(pv_ready, (ntiles - 1) & 1, abort, p.status, kTimeoutAccum);
+    if (ok) {
+      tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* dst = p.out + (static_cast<long long>(row0 + tok) * p.hq + kvh * g + r % g) * D;
 #pragma unroll
-      for (int c = 0; c < D; c += 8)
-        *reinterpret_cast<uint4*>(dst + c) =
-            make_uint4(pack_bf16(o[c] * inv, o[c + 1] * inv), pack_bf16(o[c + 2] * inv, o[c + 3] * inv),
-                       pack_bf16(o[c + 4] * inv, o[c + 5] * inv), pack_bf16(o[c + 6] * inv, o[c + 7] * inv));
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t o[32];
+        if (ntiles > 0) {
+          tmem_ld_32x32(o_tmem + tlane + c0, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8)
+            *reinterpret_cast<uint4*>(dst + c0 + j) =
+                make_uint4(pack_bf16(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv),
+                           pack_bf16(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv),
+                           pack_bf16(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv),
+                           pack_bf16(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv));
+        }
+      }
+      tc_fence_before();
     }
   }
   tc_fence_before();
@@ -354,7 +480,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfPar
 }
 
 template <int D>
-int launch_prefill(const PfParams& p, int qblocks, int batch, cudaStream_t st) {
+int launch_prefill(const PfParams& p, const CUtensorMap* tk, const CUtensorMap* tv, int qblocks, int batch,
+                   cudaStream_t st) {
   using C = PfCfg<D>;
   static bool attr = false;
   if (!attr) {
@@ -363,7 +490,7 @@ int launch_prefill(const PfParams& p, int qblocks, int batch, cudaStream_t st) {
       return 3;
     attr = true;
   }
-  attn_prefill_kernel<D><<<dim3(qblocks, p.hkv, batch), PF_THREADS, C::SMEM, st>>>(p);
+  attn_prefill_kernel<D><<<dim3(qblocks, p.hkv, batch), PF_THREADS, C::SMEM, st>>>(*tk, *tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
@@ -372,13 +499,22 @@ int launch_prefill(const PfParams& p, int qblocks, int batch, cudaStream_t st) {
 
 using namespace hb;
 
+static unsigned long long* g_pf_prof = nullptr;
+
 extern "C" {
+
+// Cycle counters of the prefill kernel's roles: `buf` = 16 zeroed uint64 on the device (null switches it off).
+// [0] softmax waits for scores, [1] softmax waits for the previous O update, [3] issuer waits for P,
+// [4] issuer waits for V, [5] issuer waits for K, [6] / [7] producer waits for a free K / V stage,
+// [8] producer issues copies, [9] producer waits for landed copies, [10] softmax loop total, [11] tiles,
+// [12] softmax score load, [13] softmax math incl. the wait for the previous O update, [14] publish P.
+void hb_attn_prefill_profile(void* buf) { g_pf_prof = static_cast<unsigned long long*>(buf); }
 
 // bf16 KV, head dim 64 or 128, group size hq / hkv <= 128. `max_rows` bounds the new rows of any sequence.
 int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
                     const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
                     const void* q_indptr, void* out, int batch, int max_rows, int hq, int hkv, int d, float scale,
-                    int causal, void* status, void* stream) {
+                    int causal, long long pool_slots, void* status, void* stream) {
   if (batch <= 0 || max_rows <= 0) return 0;
   if (hq % hkv != 0 || hq / hkv > PF_ROWS) return 1;
   PfParams p;
@@ -396,11 +532,30 @@ int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal;
   p.status = static_cast<int*>(status);
+  p.prof = g_pf_prof;
   const int tok_per_blk = PF_ROWS / (hq / hkv);
   const int qblocks = (max_rows + tok_per_blk - 1) / tok_per_blk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (d == 64) return launch_prefill<64>(p, qblocks, batch, st);
-  if (d == 128) return launch_prefill<128>(p, qblocks, batch, st);
+  // Bulk tensor copies need 16-byte aligned rows; the map covers the pool as [slots, pool_stride] bf16.
+  static const CUtensorMap dummy = {};
+  const CUtensorMap *tk = &dummy, *tv = &dummy;
+  p.use_tma = 0;
+  if (pool_slots >= 32 && pool_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(k_pool) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(v_pool) & 15) == 0 && static_cast<long long>(hkv) * d <= pool_stride) {
+    TmapKey kk{k_pool, static_cast<uint64_t>(pool_slots), static_cast<uint64_t>(hkv) * d,
+               static_cast<uint64_t>(pool_stride) * 2, 32u, 64u, 0};
+    TmapKey kv = kk;
+    kv.ptr = v_pool;
+    const CUtensorMap* a = get_tmap_2d(kk);
+    const CUtensorMap* b2 = get_tmap_2d(kv);
+    if (a != nullptr && b2 != nullptr) {
+      tk = a;
+      tv = b2;
+      p.use_tma = 1;
+    }
+  }
+  if (d == 64) return launch_prefill<64>(p, tk, tv, qblocks, batch, st);
+  if (d == 128) return launch_prefill<128>(p, tk, tv, qblocks, batch, st);
   return 1;
 }
 

@@ -64,7 +64,8 @@ int hb_attn_merge(const void* part_o, const void* part_lse, void* out, long long
 int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
                     const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
                     const void* q_indptr, void* out, int batch, int max_rows, int hq, int hkv, int d, float scale,
-                    int causal, void* status, void* stream);
+                    int causal, long long pool_slots, void* status, void* stream);
+void hb_attn_prefill_profile(void* buf);
 int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
                    const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
                    const void* q_indptr, void* out, void* part_o, void* part_lse, int batch, int max_rows, int hq,

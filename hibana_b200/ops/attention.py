@@ -22,7 +22,8 @@ nv.register("hb_attn_paged", [P, P, P, L, P, L, P, P, P, P, P, P, I, I, I, I, I,
 nv.register("hb_attn_merge", [P, P, P, L, I, I, P])
 nv.register("hb_attn_decode", [P, P, P, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, P, P])
 
-nv.register("hb_attn_prefill", [P, P, P, L, P, L, P, P, P, P, I, I, I, I, I, Fl, I, P, P])
+nv.register("hb_attn_prefill_profile", [P], void=True)
+nv.register("hb_attn_prefill", [P, P, P, L, P, L, P, P, P, P, I, I, I, I, I, Fl, I, L, P, P])
 
 NUM_SMS = 148
 
@@ -121,7 +122,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         nv.check(nv.lib().hb_attn_prefill(
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), kv_indices.data_ptr(),
             kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), q_indptr.data_ptr(), out.data_ptr(), b,
-            max_rows, hq, hkv, d, scale, int(causal), st.status.data_ptr(), nv.stream()), "hb_attn_prefill")
+            max_rows, hq, hkv, d, scale, int(causal), k_pool.shape[0], st.status.data_ptr(), nv.stream()),
+                 "hb_attn_prefill")
         return out
     nv.check(nv.lib().hb_attn_paged(
         q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), kv_indices.data_ptr(),

@@ -3,11 +3,12 @@
 prefill: `--batch` sequences of `--rows` new tokens on top of `--prefix` cached tokens; reports TFLOP/s of the causal
          work (4 * D * visible (query, key) pairs per query head) against the measured bf16 GEMM peak.
 decode : one token per sequence at context `--ctx`; reports KV bytes / time against the measured copy bandwidth.
-The KV pool is token-granular with shuffled slots, exactly as the engine lays it out.
+The KV pool is token-granular; slots ascend per sequence as a fresh pool hands them out (--shuffled: random order).
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 
 import torch
@@ -27,6 +28,8 @@ def main() -> None:
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--d", type=int, default=128)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--shuffled", action="store_true", help="random slot order (worst case: every row is gathered)")
+    ap.add_argument("--roles", action="store_true", help="prefill: cycles per tile each kernel role spends waiting")
     ap.add_argument("--once", action="store_true", help="single launch, no timing loop (for ncu)")
     args = ap.parse_args()
     dev = torch.device("cuda")
@@ -39,7 +42,10 @@ def main() -> None:
     slots = b * ctx_n + 1
     kp = torch.randn(slots, hkv, d, device=dev).bfloat16()
     vp = torch.randn(slots, hkv, d, device=dev).bfloat16()
-    perm = (torch.randperm(slots - 1, device=dev) + 1).int()
+    if args.shuffled:
+        perm = (torch.randperm(slots - 1, device=dev) + 1).int()
+    else:       # ascending runs per sequence, as the pool hands them out to a prefill
+        perm = torch.arange(1, slots, device=dev).int()
     idx = perm.view(b, ctx_n).contiguous()
     ctx = torch.full((b,), ctx_n, dtype=torch.int32, device=dev)
     q = torch.randn(b * rows, hq, d, device=dev).bfloat16()
@@ -60,6 +66,21 @@ def main() -> None:
         return
     t = time_cuda(fn, iters=args.iters)
     ms = t["median_ms"]
+    roles = None
+    if args.roles and args.mode == "prefill":
+        from .. import _native as nv
+        buf = torch.zeros(16, dtype=torch.int64, device=dev)
+        nv.lib().hb_attn_prefill_profile(ctypes.c_void_p(buf.data_ptr()))
+        fn()
+        torch.cuda.synchronize()
+        nv.lib().hb_attn_prefill_profile(None)
+        c = buf.tolist()
+        tiles = max(c[11], 1)
+        names = {0: "softmax_wait_scores", 1: "softmax_wait_prev_pv", 3: "issuer_wait_p", 4: "issuer_wait_v",
+                 5: "issuer_wait_k", 6: "producer_wait_k_stage", 7: "producer_wait_v_stage", 8: "producer_issue",
+                 9: "producer_wait_landed", 10: "softmax_loop_total", 12: "softmax_load_scores",
+                 13: "softmax_math", 14: "softmax_publish"}
+        roles = {v: round(c[k] / tiles) for k, v in names.items()}
     kv_bytes = 2.0 * b * ctx_n * hkv * d * 2
     res = {"mode": args.mode, "batch": b, "rows": rows, "ctx": ctx_n, "hq": hq, "hkv": hkv, "d": d,
            "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "kv_gbs": round(kv_bytes / ms / 1e6, 1),
@@ -68,6 +89,8 @@ def main() -> None:
         res["frac_of_bf16_peak"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 3)
     else:
         res["frac_of_hbm"] = round(kv_bytes / ms / 1e6 / peaks["hbm_gbs"], 3)
+    if roles is not None:
+        res["cycles_per_tile"] = roles
     print(json.dumps(res))
 
 

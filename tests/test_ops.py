@@ -76,13 +76,16 @@ def test_act_embedding_add():
     _close(basic.add(x.cuda(), g.cuda()), basic.add(x, g), 1e-2)
 
 
-def _attn_case(b, rows, ctxs, hq, hkv, d, dtype=torch.bfloat16, seed=0):
+def _attn_case(b, rows, ctxs, hq, hkv, d, dtype=torch.bfloat16, seed=0, contiguous=False):
     g = torch.Generator().manual_seed(seed)
     total = sum(ctxs)
     slots_n = total + 8
     kp = (torch.randn(slots_n, hkv, d, generator=g) * 0.7)
     vp = torch.randn(slots_n, hkv, d, generator=g)
     perm = torch.randperm(slots_n - 1, generator=g) + 1
+    if contiguous:      # ascending runs, as a fresh pool hands them out (bulk-copy path), with one hole
+        perm = torch.arange(1, slots_n)
+        perm[40], perm[41] = perm[41].clone(), perm[40].clone()
     kv_idx = torch.zeros(b + 2, max(ctxs) + 3, dtype=torch.int32)
     seq_rows = torch.arange(b, dtype=torch.int32).flip(0) + 1   # non-identity rows
     o = 0
@@ -209,10 +212,11 @@ def test_tensor_core_decode_verify_rows(hq, hkv, d, rows, splits):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("hq,hkv,d", [(40, 8, 128), (4, 2, 64), (32, 2, 128), (3, 1, 64)])
-def test_tcgen05_prefill_attention(hq, hkv, d):
+@pytest.mark.parametrize("contiguous", [False, True])
+def test_tcgen05_prefill_attention(hq, hkv, d, contiguous):
     """Ragged prefill / chunked prefill over cached prefixes: tile edges, partial query blocks, 1-row sequences."""
     rows, ctxs = [300, 17, 128, 1, 257], [300, 500, 1200, 77, 257]
-    q, kp, vp, idx, ctx, indptr, sr = _attn_case(5, rows, ctxs, hq, hkv, d, seed=11)
+    q, kp, vp, idx, ctx, indptr, sr = _attn_case(5, rows, ctxs, hq, hkv, d, seed=11, contiguous=contiguous)
     ref = attention.paged_attention(q, kp, vp, idx, ctx, q_indptr=indptr, max_rows=max(rows), seq_rows=sr)
     got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(), q_indptr=indptr.cuda(),
                                     max_rows=max(rows), seq_rows=sr.cuda())
