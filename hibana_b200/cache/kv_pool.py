@@ -1,7 +1,11 @@
 """Token-granular paged KV pool.
 
 One row ("slot") per cached token and attention layer: k, v [layers][slots, kv_heads, head_dim] in bf16 or
-e4m3. Slot 0 is a dummy that padded graph rows read and write. The pool only allocates and frees; ownership
+e4m3. Physically the pool is head-major ([kv_heads, slots, head_dim]; the tensors handed out are strided views):
+an attention CTA walks one kv head, so the tokens of a run of consecutive slots are one contiguous stream and
+travel as bulk tensor copies with full DRAM page locality. Slots are handed out in ascending runs and freed
+slots are re-sorted before large allocations, so sequences keep such runs. Slot 0 is a dummy that padded graph
+rows read and write. The pool only allocates and frees; ownership
 and `committed_len` belong to the StateManager. Reference: hibana/cache/kv_pool.py:24-139 (page size 1, free
 list, pad pages, `write`).
 """
@@ -18,11 +22,12 @@ class KvPool:
         self.layers, self.slots, self.kv_heads, self.head_dim = layers, slots, kv_heads, head_dim
         self.dtype, self.device, self.kv_scale = dtype, torch.device(device), kv_scale
         # One allocation; slot 0 is the dummy row.
-        self.storage = torch.zeros(max(layers, 1), 2, slots + 1, kv_heads, head_dim, dtype=dtype, device=device)
-        self.k = [self.storage[i, 0] for i in range(layers)]
-        self.v = [self.storage[i, 1] for i in range(layers)]
+        self.storage = torch.zeros(max(layers, 1), 2, kv_heads, slots + 1, head_dim, dtype=dtype, device=device)
+        self.k = [self.storage[i, 0].transpose(0, 1) for i in range(layers)]   # [slots + 1, kv_heads, head_dim]
+        self.v = [self.storage[i, 1].transpose(0, 1) for i in range(layers)]
         self._free = list(range(slots, 0, -1))     # pop() hands out ascending ids (contiguous when fresh)
         self._owned = bytearray(slots + 1)
+        self._shuffled = False                     # frees since the last sort
 
     @property
     def free_count(self) -> int:
@@ -35,6 +40,9 @@ class KvPool:
     def alloc(self, n: int) -> list[int]:
         if n > len(self._free):
             raise MemoryError(f"KV pool exhausted: need {n}, free {len(self._free)}")
+        if self._shuffled and n >= 32:
+            self._free.sort(reverse=True)          # a prefill-sized request gets ascending runs again
+            self._shuffled = False
         out = [self._free.pop() for _ in range(n)]
         for s in out:
             self._owned[s] = 1
@@ -46,6 +54,7 @@ class KvPool:
                 raise ValueError(f"double free or foreign slot {s}")
             self._owned[s] = 0
             self._free.append(s)
+            self._shuffled = True
 
     def check(self) -> None:
         assert len(set(self._free)) == len(self._free), "duplicate free slots"
@@ -55,8 +64,8 @@ class KvPool:
     def rows(self, ids: list[int]) -> torch.Tensor:
         """All layers' K and V rows of the given slots: [layers, 2, len(ids), kv_heads, head_dim] (a copy)."""
         idx = torch.tensor(ids, dtype=torch.long, device=self.device)
-        return self.storage[:, :, idx]
+        return self.storage[:, :, :, idx].transpose(2, 3).contiguous()
 
     def write_rows(self, ids: list[int], rows: torch.Tensor) -> None:
         idx = torch.tensor(ids, dtype=torch.long, device=self.device)
-        self.storage[:, :, idx] = rows.to(self.storage.dtype)
+        self.storage[:, :, :, idx] = rows.to(self.storage.dtype).transpose(2, 3)

@@ -24,7 +24,8 @@ struct AttnParams {
   const __nv_bfloat16* q;      // [T, Hq, D]
   const void* k_pool;
   const void* v_pool;
-  long long pool_stride;       // elements between slots (kv_heads * D)
+  long long pool_stride;       // elements between slots
+  long long head_stride;       // elements between kv heads
   const int* kv_indices;       // [B, ld_idx]
   long long ld_idx;
   const int* ctx_len;          // [B] keys visible to the last query row of the sequence
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_splitkv_kernel(const AttnPar
       uint8_t* kd = kbuf + (buf * TK + key) * ROWB + part * 16;
       uint8_t* vd = vbuf + (buf * TK + key) * ROWB + part * 16;
       if (kpos < k1) {
-        const long long off = (static_cast<long long>(idx_row[kpos]) * p.pool_stride + static_cast<long long>(kvh) * D) * ESZ + part * 16;
+        const long long off = (static_cast<long long>(idx_row[kpos]) * p.pool_stride + static_cast<long long>(kvh) * p.head_stride) * ESZ + part * 16;
         cp_async16(kd, kp + off);
         cp_async16(vd, vp + off);
       } else {
@@ -346,6 +347,7 @@ extern "C" {
 
 // max_rows: largest number of query rows of any sequence (1 for decode). Partials are needed when splits > 1.
 int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                  long long head_stride,
                   const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len, const void* q_indptr,
                   void* out, void* part_o, void* part_lse, int batch, int total_rows, int max_rows, int hq, int hkv, int d,
                   int splits, float scale, int kv_fp8, float kv_scale, int causal, void* stream) {
@@ -355,7 +357,7 @@ int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long lo
   if (g > 32) return 1;
   AttnParams p;
   p.q = static_cast<const __nv_bfloat16*>(q);
-  p.k_pool = k_pool; p.v_pool = v_pool; p.pool_stride = pool_stride;
+  p.k_pool = k_pool; p.v_pool = v_pool; p.pool_stride = pool_stride; p.head_stride = head_stride;
   p.kv_indices = static_cast<const int*>(kv_indices); p.ld_idx = ld_idx;
   p.ctx_len = static_cast<const int*>(ctx_len);
   p.seq_rows = static_cast<const int*>(seq_rows);

@@ -1,9 +1,12 @@
 // Flash-decoding for paged GQA attention with up to 16 query rows per (sequence, kv head): decode (one token x
 // GQA group <= 16) and short speculative verify blocks. Bandwidth-bound by design:
 //
-//   * K / V rows (one token, one kv head: D bf16) stream from their slots in the token-granular pool into padded
-//     shared-memory rows with 16-byte cp.async (the TMA unit retires only about one small bulk copy per ~30 cycles,
-//     which capped 256-byte row copies near 16 GB/s per SM; the LSU path has no such limit);
+//   * K / V tiles of KT keys live in shared memory as 128-byte-swizzled column blocks ([KT rows x 128 bytes] per
+//     64 head-dim elements), the layout a bulk tensor copy produces. The pool hands a sequence its slots in
+//     ascending runs, so most tiles are KT consecutive pool rows and travel as one TMA box per column block
+//     (row pitch = one pool slot): the TMA unit keeps far more bytes in flight than the LSU path, which tops out
+//     near 16 KB outstanding per SM (~3.5 TB/s over the chip). Tiles that are not one run (fragmented pool, the
+//     tail of the context) are gathered row by row with 16-byte cp.async into the same layout;
 //   * each of the 4 warps of a CTA owns a private 3-stage ring of KT-key tiles and walks its own share of the keys,
 //     so the main loop has no block-wide barrier and no flag wait: a warp waits only on its own cp.async groups;
 //   * S = Q K^T and O += P V run on the tensor cores (m16n8k16 bf16, fp32 accumulate) with the query rows padded to
@@ -13,6 +16,7 @@
 // The KV range of a split is derived on the device from ctx_len, so one captured launch serves any context.
 // Replaces the FlashInfer decode wrapper the reference plans per step (hibana/engine/graphs.py:55,
 // hibana/engine/executor.py:161-169) and the multi-row verify kernel (hibana/kernels/csrc/verify_attn.cu:469).
+#include "kv_tma.cuh"
 #include "hb_api.h"
 #include "hb_common.cuh"
 
@@ -26,7 +30,9 @@ struct DecParams {
   const __nv_bfloat16* q;
   const __nv_bfloat16* k_pool;
   const __nv_bfloat16* v_pool;
-  long long pool_stride;
+  long long pool_stride;      // elements between slots
+  long long head_stride;      // elements between kv heads
+  int tma_xh, tma_yh;         // tensor-map coordinates per kv head (kv_tma.cuh)
   const int* kv_indices;
   long long ld_idx;
   const int* seq_rows;
@@ -38,6 +44,7 @@ struct DecParams {
   int hq, hkv, splits;
   float scale_log2;
   int causal;
+  int use_tma;
   int* status;
 };
 
@@ -68,27 +75,46 @@ __device__ __forceinline__ void cp_wait2() { asm volatile("cp.async.wait_group 2
 template <int D>
 struct DecCfg {
   static constexpr int KT = D >= 256 ? 16 : 32;        // keys per warp tile
-  static constexpr int ROWB = D * 2 + 16;               // padded row: conflict-free ldmatrix
-  static constexpr int TILE_BYTES = KT * ROWB;          // one of K or V
+  static constexpr int HALVES = D / 64;                 // 128-byte column blocks per row
+  static constexpr int BLOCK_BYTES = KT * 128;          // one column block of a tile
+  static constexpr int TILE_BYTES = KT * D * 2;         // one of K or V
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
   static constexpr int WARP_BYTES = DEC_STAGES * STAGE_BYTES;
-  static constexpr int Q_BYTES = 16 * ROWB;
-  static constexpr int SMEM = DEC_WARPS * WARP_BYTES + Q_BYTES + 256;
+  static constexpr int QROWB = D * 2 + 16;              // padded Q row: conflict-free ldmatrix
+  static constexpr int Q_BYTES = 16 * QROWB;
+  static constexpr int BAR_OFF = DEC_WARPS * WARP_BYTES + Q_BYTES;
+  static constexpr int SMEM = BAR_OFF + 256 + 1024;
   static_assert(16 * D * 4 + 16 * 8 <= WARP_BYTES, "merge scratch must fit a warp's ring");
+  static_assert(BLOCK_BYTES % 1024 == 0, "column blocks must keep the swizzle atom alignment");
 };
 
+// Byte offset of 16-byte chunk c of row `row` in a swizzled tile of KT rows.
+template <int KT>
+__device__ __forceinline__ uint32_t dsw(int row, int c) {
+  return static_cast<uint32_t>((c >> 3) * (KT * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+}
+
 template <int D>
-__global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const DecParams p) {
+__global__ void __launch_bounds__(DEC_WARPS * 32, 1)
+attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, const DecParams p) {
   using C = DecCfg<D>;
-  constexpr int KT = C::KT, ROWB = C::ROWB;
+  constexpr int KT = C::KT, ROWB = C::QROWB;
   constexpr int NB = KT / 8;     // score n-blocks per tile
   constexpr int KS = D / 16;     // k-steps of Q K^T
   constexpr int ONB = D / 8;     // output n-blocks
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g4 = lane >> 2, t4 = lane & 3;
   uint8_t* ring = smem + warp * C::WARP_BYTES;
   uint8_t* qs = smem + DEC_WARPS * C::WARP_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF) + warp * DEC_STAGES;   // this warp's barriers
+  volatile int* abort = reinterpret_cast<volatile int*>(smem + C::BAR_OFF + DEC_WARPS * DEC_STAGES * 8) + warp;
+  if (lane == 0) {
+    for (int s = 0; s < DEC_STAGES; ++s) mbar_init(&full[s], 1);
+    *abort = 0;
+    fence_mbar_init();
+  }
 
   const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int g = p.hq / p.hkv;
@@ -122,33 +148,52 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const De
 
   const int* idx_row = p.kv_indices + static_cast<long long>(p.seq_rows ? p.seq_rows[b] : b) * p.ld_idx;
 
-  // Issues the copies of this warp's `it`-th tile into its ring stage. A warp instruction moves two rows' worth
-  // of 16-byte chunks (D = 128); slot ids of the tile's keys are fetched once per lane and shuffled.
+  // Issues the copies of this warp's `it`-th tile into its ring stage: one bulk tensor copy per column block of
+  // K and of V when the tile's slots are KT consecutive pool rows, else a row-by-row cp.async gather. `tma_mode`
+  // remembers per stage which way the tile in flight travels, `tma_phase` the parity of the stage's barrier.
+  uint32_t tma_mode = 0, tma_phase = 0;
   auto issue = [&](int it) {
     const int tile = warp + it * DEC_WARPS;
     if (tile < ntiles) {
       const int st = it % DEC_STAGES;
       const int base = k0 + tile * KT;
-      const uint32_t kdst = smem_u32(ring + st * C::STAGE_BYTES);
+      uint8_t* kt = ring + st * C::STAGE_BYTES;
+      const uint32_t kdst = smem_u32(kt);
       const uint32_t vdst = kdst + C::TILE_BYTES;
       constexpr int CPR = D / 8;            // 16-byte chunks per row
       constexpr int RPI = 32 / CPR > 0 ? 32 / CPR : 1;   // rows per warp instruction
       const int my_slot = (lane < KT && base + lane < k1) ? idx_row[base + lane] : -1;
-      if constexpr (CPR <= 32) {
-        const int part = lane % CPR, sub = lane / CPR;
+      const int slot0 = __shfl_sync(0xffffffffu, my_slot, 0);
+      const bool run = p.use_tma && __all_sync(0xffffffffu, lane >= KT || (my_slot >= 0 && my_slot == slot0 + lane));
+      if (run) {
+        tma_mode |= 1u << st;
+        if (lane == 0) {
+          mbar_expect_tx(&full[st], 2 * C::TILE_BYTES);
 #pragma unroll
-        for (int r = 0; r < KT; r += RPI) {
-          const int key = r + sub;
-          const int slot = __shfl_sync(0xffffffffu, my_slot, key);
-          const uint32_t so = key * ROWB + part * 16;
-          if (slot >= 0) {
-            const __nv_bfloat16* src = p.k_pool + static_cast<long long>(slot) * p.pool_stride +
-                                       static_cast<long long>(kvh) * D + part * 8;
-            cp16(kdst + so, src);
-            cp16(vdst + so, p.v_pool + (src - p.k_pool));
-          } else {
-            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(kdst + so), "r"(0) : "memory");
-            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(vdst + so), "r"(0) : "memory");
+          for (int h = 0; h < C::HALVES; ++h) {
+            tma_load_2d(kt + h * C::BLOCK_BYTES, &tmk, &full[st], kvh * p.tma_xh + h * 64, kvh * p.tma_yh + slot0);
+            tma_load_2d(kt + C::TILE_BYTES + h * C::BLOCK_BYTES, &tmv, &full[st], kvh * p.tma_xh + h * 64,
+                        kvh * p.tma_yh + slot0);
+          }
+        }
+      } else {
+        tma_mode &= ~(1u << st);
+        if constexpr (CPR <= 32) {
+          const int part = lane % CPR, sub = lane / CPR;
+#pragma unroll
+          for (int r = 0; r < KT; r += RPI) {
+            const int key = r + sub;
+            const int slot = __shfl_sync(0xffffffffu, my_slot, key);
+            const uint32_t so = dsw<KT>(key, part);
+            if (slot >= 0) {
+              const __nv_bfloat16* src = p.k_pool + static_cast<long long>(slot) * p.pool_stride +
+                                         static_cast<long long>(kvh) * p.head_stride + part * 8;
+              cp16(kdst + so, src);
+              cp16(vdst + so, p.v_pool + (src - p.k_pool));
+            } else {
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(kdst + so), "r"(0) : "memory");
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(vdst + so), "r"(0) : "memory");
+            }
           }
         }
       }
@@ -171,8 +216,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const De
     __syncwarp();
     issue(it + 2);
     cp_wait2();
-    __syncwarp();
     const int st = it % DEC_STAGES;
+    if (tma_mode & (1u << st)) {
+      const bool got = mbar_wait(&full[st], (tma_phase >> st) & 1u, abort, p.status, kTimeoutFull);
+      tma_phase ^= 1u << st;
+      if (!__all_sync(0xffffffffu, got)) break;
+    }
+    __syncwarp();
     const uint32_t kbase = smem_u32(ring + st * C::STAGE_BYTES);
     const uint32_t vbase = kbase + C::TILE_BYTES;
     const int tile = warp + it * DEC_WARPS;
@@ -182,11 +232,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const De
 #pragma unroll
     for (int j = 0; j < NB; ++j) {
       s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-      const uint32_t a = kbase + (j * 8 + (lane & 7)) * ROWB + (lane >> 3) * 16;
 #pragma unroll
       for (int ks = 0; ks < KS; ks += 2) {
         uint32_t kb[4];
-        ldsm_x4(kb, a + ks * 32);
+        ldsm_x4(kb, kbase + dsw<KT>(j * 8 + (lane & 7), ks * 2 + (lane >> 3)));
         mma_bf16(s[j], qf[ks], kb[0], kb[1]);
         mma_bf16(s[j], qf[ks + 1], kb[2], kb[3]);
       }
@@ -236,11 +285,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const De
     }
 #pragma unroll
     for (int kk = 0; kk < KT / 16; ++kk) {
-      const uint32_t a = vbase + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * ROWB + (lane >> 4) * 16;
 #pragma unroll
       for (int nb = 0; nb < ONB; nb += 2) {
         uint32_t vb[4];
-        ldsm_x4_t(vb, a + nb * 16);
+        ldsm_x4_t(vb, vbase + dsw<KT>(kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), nb + (lane >> 4)));
         mma_bf16(o[nb], pf[kk], vb[0], vb[1]);
         mma_bf16(o[nb + 1], pf[kk], vb[2], vb[3]);
       }
@@ -298,7 +346,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) attn_decode_kernel(const De
 }
 
 template <int D>
-int launch_decode(const DecParams& p, int batch, cudaStream_t st) {
+int launch_decode(const DecParams& p0, const void* k_pool, const void* v_pool, long long pool_slots, int batch,
+                  cudaStream_t st) {
+  DecParams p = p0;
   using C = DecCfg<D>;
   static bool attr = false;
   if (!attr) {
@@ -307,7 +357,17 @@ int launch_decode(const DecParams& p, int batch, cudaStream_t st) {
       return 3;
     attr = true;
   }
-  attn_decode_kernel<D><<<dim3(batch, p.hkv, p.splits), DEC_WARPS * 32, C::SMEM, st>>>(p);
+  static const CUtensorMap dummy = {};
+  const CUtensorMap *tk = &dummy, *tv = &dummy;
+  const KvTma t = make_kv_tma(k_pool, v_pool, p.pool_stride, p.head_stride, pool_slots, p.hkv, D, C::KT);
+  p.use_tma = t.ok;
+  p.tma_xh = t.xh;
+  p.tma_yh = t.yh;
+  if (t.ok) {
+    tk = t.k;
+    tv = t.v;
+  }
+  attn_decode_kernel<D><<<dim3(batch, p.hkv, p.splits), DEC_WARPS * 32, C::SMEM, st>>>(*tk, *tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
@@ -320,9 +380,11 @@ extern "C" {
 
 // bf16 KV only; rows_per_seq * (hq / hkv) must be <= 16. Partials go through hb_attn_merge when splits > 1.
 int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                   long long head_stride,
                    const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
                    const void* q_indptr, void* out, void* part_o, void* part_lse, int batch, int max_rows, int hq,
-                   int hkv, int d, int splits, float scale, int causal, void* status, void* stream) {
+                   int hkv, int d, int splits, float scale, int causal, long long pool_slots, void* status,
+                   void* stream) {
   if (batch <= 0) return 0;
   if (hq % hkv != 0 || max_rows * (hq / hkv) > 16) return 1;
   DecParams p;
@@ -330,6 +392,7 @@ int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long l
   p.k_pool = static_cast<const __nv_bfloat16*>(k_pool);
   p.v_pool = static_cast<const __nv_bfloat16*>(v_pool);
   p.pool_stride = pool_stride;
+  p.head_stride = head_stride;
   p.kv_indices = static_cast<const int*>(kv_indices);
   p.ld_idx = ld_idx;
   p.seq_rows = static_cast<const int*>(seq_rows);
@@ -344,9 +407,9 @@ int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long l
   p.status = static_cast<int*>(status);
   if (p.splits > 1 && (part_o == nullptr || part_lse == nullptr)) return 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (d == 64) return launch_decode<64>(p, batch, st);
-  if (d == 128) return launch_decode<128>(p, batch, st);
-  if (d == 256) return launch_decode<256>(p, batch, st);
+  if (d == 64) return launch_decode<64>(p, k_pool, v_pool, pool_slots, batch, st);
+  if (d == 128) return launch_decode<128>(p, k_pool, v_pool, pool_slots, batch, st);
+  if (d == 256) return launch_decode<256>(p, k_pool, v_pool, pool_slots, batch, st);
   return 1;
 }
 

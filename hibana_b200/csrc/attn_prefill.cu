@@ -22,7 +22,7 @@
 //
 // Replaces the reference's FlashInfer ragged-prefill wrapper + prefix kernel + LSE merge
 // (hibana/kernels/ops.py:131-161, hibana/model/attention.py:73-96, hibana/kernels/csrc/verify_attn.cu prefix_kernel).
-#include "gemm.cuh"
+#include "kv_tma.cuh"
 #include "hb_api.h"
 #include "hb_common.cuh"
 
@@ -39,7 +39,9 @@ struct PfParams {
   const __nv_bfloat16* q;
   const __nv_bfloat16* k_pool;
   const __nv_bfloat16* v_pool;
-  long long pool_stride;
+  long long pool_stride;      // elements between slots
+  long long head_stride;      // elements between kv heads
+  int tma_xh, tma_yh;         // tensor-map coordinates per kv head (kv_tma.cuh)
   const int* kv_indices;
   long long ld_idx;
   const int* seq_rows;
@@ -205,7 +207,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
             mbar_add_tx(bar, 32 * D * 2);   // bytes only: this lane's arrival comes with the other producers'
 #pragma unroll
             for (int h = 0; h < C::HALVES; ++h)
-              tma_load_2d(tile + h * (PF_KT * 128) + j * (32 * 128), tm, bar, kvh * D + h * 64, slot0);
+              tma_load_2d(tile + h * (PF_KT * 128) + j * (32 * 128), tm, bar, kvh * p.tma_xh + h * 64,
+                          kvh * p.tma_yh + slot0);
           }
         } else {
           // lane -> (row = i * (32 / CPR) + lane / CPR, 16-byte column = lane % CPR)
@@ -218,7 +221,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
             const int s1 = __shfl_sync(0xffffffffu, slot, rr);
             const int r = j * 32 + rr;
             const uint32_t dst = dst0 + r * 128 + (((part & 7) ^ (r & 7)) << 4);
-            if (s1 >= 0) cp16(dst, pool + static_cast<long long>(s1) * p.pool_stride + kvh * D + part * 8);
+            if (s1 >= 0)
+              cp16(dst, pool + static_cast<long long>(s1) * p.pool_stride + kvh * p.head_stride + part * 8);
             else st_zero16(dst);
           }
         }
@@ -512,6 +516,7 @@ void hb_attn_prefill_profile(void* buf) { g_pf_prof = static_cast<unsigned long 
 
 // bf16 KV, head dim 64 or 128, group size hq / hkv <= 128. `max_rows` bounds the new rows of any sequence.
 int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                    long long head_stride,
                     const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
                     const void* q_indptr, void* out, int batch, int max_rows, int hq, int hkv, int d, float scale,
                     int causal, long long pool_slots, void* status, void* stream) {
@@ -522,6 +527,7 @@ int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long 
   p.k_pool = static_cast<const __nv_bfloat16*>(k_pool);
   p.v_pool = static_cast<const __nv_bfloat16*>(v_pool);
   p.pool_stride = pool_stride;
+  p.head_stride = head_stride;
   p.kv_indices = static_cast<const int*>(kv_indices);
   p.ld_idx = ld_idx;
   p.seq_rows = static_cast<const int*>(seq_rows);
@@ -536,23 +542,15 @@ int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long 
   const int tok_per_blk = PF_ROWS / (hq / hkv);
   const int qblocks = (max_rows + tok_per_blk - 1) / tok_per_blk;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // Bulk tensor copies need 16-byte aligned rows; the map covers the pool as [slots, pool_stride] bf16.
   static const CUtensorMap dummy = {};
   const CUtensorMap *tk = &dummy, *tv = &dummy;
-  p.use_tma = 0;
-  if (pool_slots >= 32 && pool_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(k_pool) & 15) == 0 &&
-      (reinterpret_cast<uintptr_t>(v_pool) & 15) == 0 && static_cast<long long>(hkv) * d <= pool_stride) {
-    TmapKey kk{k_pool, static_cast<uint64_t>(pool_slots), static_cast<uint64_t>(hkv) * d,
-               static_cast<uint64_t>(pool_stride) * 2, 32u, 64u, 0};
-    TmapKey kv = kk;
-    kv.ptr = v_pool;
-    const CUtensorMap* a = get_tmap_2d(kk);
-    const CUtensorMap* b2 = get_tmap_2d(kv);
-    if (a != nullptr && b2 != nullptr) {
-      tk = a;
-      tv = b2;
-      p.use_tma = 1;
-    }
+  const KvTma t = make_kv_tma(k_pool, v_pool, pool_stride, head_stride, pool_slots, hkv, d, 32);
+  p.use_tma = t.ok;
+  p.tma_xh = t.xh;
+  p.tma_yh = t.yh;
+  if (t.ok) {
+    tk = t.k;
+    tv = t.v;
   }
   if (d == 64) return launch_prefill<64>(p, tk, tv, qblocks, batch, st);
   if (d == 128) return launch_prefill<128>(p, tk, tv, qblocks, batch, st);

@@ -43,10 +43,11 @@ int hb_rmsnorm(const void* x, void* residual, const void* w, void* y, int rows, 
                float eps, int gemma, void* stream);
 int hb_gated_rmsnorm(const void* x, const void* z, const void* w, void* y, int rows, int h, int gs, long long ldx,
                      long long ldz, float eps, int norm_first, int sigmoid_gate, int gemma, void* stream);
+// KV pools are [slots, kv_heads, D] with `pool_stride` elements between slots and `head_stride` between heads.
 int hb_rope_kv_write(const void* qkv, long long ld_qkv, const void* positions, const void* slots,
                      const void* inv_freq, const void* q_norm_w, const void* k_norm_w, float eps, int gemma_norm,
-                     void* q_out, void* k_pool, void* v_pool, long long pool_stride, int tokens, int hq, int hkv,
-                     int d, int rot, int kv_fp8, float kv_inv_scale, int q_gate, void* stream);
+                     void* q_out, void* k_pool, void* v_pool, long long pool_stride, long long head_stride, int tokens,
+                     int hq, int hkv, int d, int rot, int kv_fp8, float kv_inv_scale, int q_gate, void* stream);
 int hb_act_mul(const void* x, const void* gate, void* out, long long rows, int inter, long long ldx, int mode,
                void* stream);
 int hb_embedding(const void* ids, const void* table, void* out, int tokens, int h, long long vocab, void* stream);
@@ -54,6 +55,7 @@ int hb_add(const void* a, const void* b, void* out, long long n, void* stream);
 
 // ---- paged attention (attn.cu) -------------------------------------------------------------------------
 int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                  long long head_stride,
                   const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len, const void* q_indptr,
                   void* out, void* part_o, void* part_lse, int batch, int total_rows, int max_rows, int hq, int hkv, int d,
                   int splits, float scale, int kv_fp8, float kv_scale, int causal, void* stream);
@@ -62,14 +64,17 @@ int hb_attn_merge(const void* part_o, const void* part_lse, void* out, long long
 // Tensor-core flash-decoding (attn_decode.cu): bf16 KV, rows_per_sequence * (hq / hkv) <= 16.
 // Prefill / chunked-prefill attention on tcgen05 (bf16 KV, head dim 64 or 128); any number of new rows per sequence.
 int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                    long long head_stride,
                     const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
                     const void* q_indptr, void* out, int batch, int max_rows, int hq, int hkv, int d, float scale,
                     int causal, long long pool_slots, void* status, void* stream);
 void hb_attn_prefill_profile(void* buf);
 int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                   long long head_stride,
                    const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
                    const void* q_indptr, void* out, void* part_o, void* part_lse, int batch, int max_rows, int hq,
-                   int hkv, int d, int splits, float scale, int causal, void* status, void* stream);
+                   int hkv, int d, int splits, float scale, int causal, long long pool_slots, void* status,
+                   void* stream);
 
 // ---- sampling and speculative acceptance (sample.cu) -----------------------------------------------------
 int hb_argmax(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* bitmask, int mask_words,

@@ -118,7 +118,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
                                      const float* __restrict__ inv_freq, const __nv_bfloat16* __restrict__ q_norm_w,
                                      const __nv_bfloat16* __restrict__ k_norm_w, float eps, int gemma_norm,
                                      __nv_bfloat16* __restrict__ q_out, void* __restrict__ k_pool,
-                                     void* __restrict__ v_pool, long long pool_stride, int hq, int hkv, int d, int rot,
+                                     void* __restrict__ v_pool, long long pool_stride, long long head_stride, int hq, int hkv,
+                                     int d, int rot,
                                      int kv_fp8, float kv_inv_scale, int q_gate) {
   const int t = blockIdx.x;
   const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -151,7 +152,7 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
       if (slot < 0) continue;
       const int kh = is_k ? hd - hq : hd - hq - hkv;
       void* pool = is_k ? k_pool : v_pool;
-      const long long off = static_cast<long long>(slot) * pool_stride + static_cast<long long>(kh) * d;
+      const long long off = static_cast<long long>(slot) * pool_stride + static_cast<long long>(kh) * head_stride;
       if (kv_fp8) dst_f8 = static_cast<uint8_t*>(pool) + off;
       else dst_bf = static_cast<__nv_bfloat16*>(pool) + off;
     }
@@ -261,7 +262,8 @@ int hb_gated_rmsnorm(const void* x, const void* z, const void* w, void* y, int r
 
 int hb_rope_kv_write(const void* qkv, long long ld_qkv, const void* positions, const void* slots,
                      const void* inv_freq, const void* q_norm_w, const void* k_norm_w, float eps, int gemma_norm,
-                     void* q_out, void* k_pool, void* v_pool, long long pool_stride, int tokens, int hq, int hkv,
+                     void* q_out, void* k_pool, void* v_pool, long long pool_stride, long long head_stride, int tokens,
+                     int hq, int hkv,
                      int d, int rot, int kv_fp8, float kv_inv_scale, int q_gate, void* stream) {
   if (tokens <= 0) return 0;
   if (rot > d || (rot & 1)) return 1;
@@ -272,7 +274,7 @@ int hb_rope_kv_write(const void* qkv, long long ld_qkv, const void* positions, c
   rope_kv_write_kernel<<<dim3(tokens, ysplit), 256, 0, ST(stream)>>>(
       BF(qkv), ld_qkv, static_cast<const int*>(positions), static_cast<const int*>(slots),
       static_cast<const float*>(inv_freq), BF(q_norm_w), BF(k_norm_w), eps, gemma_norm, BFM(q_out), k_pool, v_pool,
-      pool_stride, hq, hkv, d, rot, kv_fp8, kv_inv_scale, q_gate);
+      pool_stride, head_stride, hq, hkv, d, rot, kv_fp8, kv_inv_scale, q_gate);
   return OK();
 }
 

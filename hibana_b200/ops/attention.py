@@ -17,13 +17,13 @@ import torch
 from .. import _native as nv
 
 P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
-nv.register("hb_attn_paged", [P, P, P, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, Fl, I, Fl, I, P])
+nv.register("hb_attn_paged", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, Fl, I, Fl, I, P])
 
 nv.register("hb_attn_merge", [P, P, P, L, I, I, P])
-nv.register("hb_attn_decode", [P, P, P, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, P, P])
+nv.register("hb_attn_decode", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, L, P, P])
 
 nv.register("hb_attn_prefill_profile", [P], void=True)
-nv.register("hb_attn_prefill", [P, P, P, L, P, L, P, P, P, P, I, I, I, I, I, Fl, I, L, P, P])
+nv.register("hb_attn_prefill", [P, P, P, L, L, P, L, P, P, P, P, I, I, I, I, I, Fl, I, L, P, P])
 
 NUM_SMS = 148
 
@@ -108,11 +108,11 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     if not fp8 and max_rows * (hq // hkv) <= 16 and d in (64, 128, 256):
         st = nv.device_state(q.device)
         nv.check(nv.lib().hb_attn_decode(
-            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), kv_indices.data_ptr(),
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), k_pool.stride(1), kv_indices.data_ptr(),
             kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), nv.ptr(q_indptr), out.data_ptr(),
             workspace.part_o.data_ptr() if splits > 1 else None,
             workspace.part_lse.data_ptr() if splits > 1 else None, b, max_rows, hq, hkv, d, splits, scale,
-            int(causal), st.status.data_ptr(), nv.stream()), "hb_attn_decode")
+            int(causal), k_pool.shape[0], st.status.data_ptr(), nv.stream()), "hb_attn_decode")
         if splits > 1:
             nv.check(nv.lib().hb_attn_merge(workspace.part_o.data_ptr(), workspace.part_lse.data_ptr(),
                                             out.data_ptr(), t * hq, splits, d, nv.stream()), "hb_attn_merge")
@@ -120,13 +120,13 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     if not fp8 and d in (64, 128) and q_indptr is not None and os.environ.get("HIBANA_PREFILL_ATTN", "tc") == "tc":
         st = nv.device_state(q.device)
         nv.check(nv.lib().hb_attn_prefill(
-            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), kv_indices.data_ptr(),
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), k_pool.stride(1), kv_indices.data_ptr(),
             kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), q_indptr.data_ptr(), out.data_ptr(), b,
             max_rows, hq, hkv, d, scale, int(causal), k_pool.shape[0], st.status.data_ptr(), nv.stream()),
                  "hb_attn_prefill")
         return out
     nv.check(nv.lib().hb_attn_paged(
-        q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), kv_indices.data_ptr(),
+        q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), k_pool.stride(1), kv_indices.data_ptr(),
         kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), nv.ptr(q_indptr), out.data_ptr(),
         workspace.part_o.data_ptr() if splits > 1 else None, workspace.part_lse.data_ptr() if splits > 1 else None,
         b, t, max_rows, hq, hkv, d, splits, scale, int(fp8), kv_scale, int(causal), nv.stream()), "hb_attn_paged",

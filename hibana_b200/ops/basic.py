@@ -17,7 +17,7 @@ from .. import _native as nv
 P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
 nv.register("hb_rmsnorm", [P, P, P, P, I, I, L, L, Fl, I, P])
 nv.register("hb_gated_rmsnorm", [P, P, P, P, I, I, I, L, L, Fl, I, I, I, P])
-nv.register("hb_rope_kv_write", [P, L, P, P, P, P, P, Fl, I, P, P, P, L, I, I, I, I, I, I, Fl, I, P])
+nv.register("hb_rope_kv_write", [P, L, P, P, P, P, P, Fl, I, P, P, P, L, L, I, I, I, I, I, I, Fl, I, P])
 nv.register("hb_act_mul", [P, P, P, L, I, L, I, P])
 nv.register("hb_embedding", [P, P, P, I, I, L, P])
 nv.register("hb_add", [P, P, P, L, P])
@@ -116,8 +116,8 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[to
         nv.check(nv.lib().hb_rope_kv_write(
             qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), nv.ptr(slots), inv_freq.data_ptr(), nv.ptr(q_norm),
             nv.ptr(k_norm), eps, int(gemma_norm), q_out.data_ptr(), nv.ptr(k_pool), nv.ptr(v_pool),
-            k_pool.stride(0) if k_pool is not None else 0, t, hq, hkv, d, rot, int(fp8), 1.0 / kv_scale, int(q_gate),
-            nv.stream()), "hb_rope_kv_write")
+            k_pool.stride(0) if k_pool is not None else 0, k_pool.stride(1) if k_pool is not None else 0, t, hq,
+            hkv, d, rot, int(fp8), 1.0 / kv_scale, int(q_gate), nv.stream()), "hb_rope_kv_write")
         return q_out
     x = qkv.float()
     if q_gate:

@@ -29,6 +29,7 @@ def main() -> None:
     ap.add_argument("--d", type=int, default=128)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--shuffled", action="store_true", help="random slot order (worst case: every row is gathered)")
+    ap.add_argument("--slot-major", action="store_true", help="pool stored [slots, heads, D] instead of head-major")
     ap.add_argument("--roles", action="store_true", help="prefill: cycles per tile each kernel role spends waiting")
     ap.add_argument("--once", action="store_true", help="single launch, no timing loop (for ncu)")
     args = ap.parse_args()
@@ -40,8 +41,12 @@ def main() -> None:
     else:
         rows, ctx_n = 1, args.ctx
     slots = b * ctx_n + 1
-    kp = torch.randn(slots, hkv, d, device=dev).bfloat16()
-    vp = torch.randn(slots, hkv, d, device=dev).bfloat16()
+    if args.slot_major:
+        kp = torch.randn(slots, hkv, d, device=dev).bfloat16()
+        vp = torch.randn(slots, hkv, d, device=dev).bfloat16()
+    else:       # the engine's pools: head-major storage behind a [slots, heads, D] view
+        kp = torch.randn(hkv, slots, d, device=dev).bfloat16().transpose(0, 1)
+        vp = torch.randn(hkv, slots, d, device=dev).bfloat16().transpose(0, 1)
     if args.shuffled:
         perm = (torch.randperm(slots - 1, device=dev) + 1).int()
     else:       # ascending runs per sequence, as the pool hands them out to a prefill

@@ -99,15 +99,19 @@ def _attn_case(b, rows, ctxs, hq, hkv, d, dtype=torch.bfloat16, seed=0, contiguo
         kp, vp = kp.bfloat16(), vp.bfloat16()
     else:
         kp, vp = (kp / 0.25).to(dtype), (vp / 0.25).to(dtype)
+    if contiguous is True:      # head-major storage behind the [slots, heads, D] view, as the engine's pool
+        kp = kp.transpose(0, 1).contiguous().transpose(0, 1)
+        vp = vp.transpose(0, 1).contiguous().transpose(0, 1)
     return q, kp, vp, kv_idx, ctx, indptr, seq_rows
 
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("hq,hkv,d", [(40, 8, 128), (4, 2, 64), (24, 2, 256), (32, 2, 128)])
 @pytest.mark.parametrize("splits", [1, 4])
-def test_paged_attention_decode(hq, hkv, d, splits):
+@pytest.mark.parametrize("contiguous", [False, True])
+def test_paged_attention_decode(hq, hkv, d, splits, contiguous):
     ctxs = [1, 63, 64, 65, 300, 1000]
-    q, kp, vp, idx, ctx, indptr, sr = _attn_case(6, [1] * 6, ctxs, hq, hkv, d)
+    q, kp, vp, idx, ctx, indptr, sr = _attn_case(6, [1] * 6, ctxs, hq, hkv, d, contiguous=contiguous)
     ref = attention.paged_attention(q, kp, vp, idx, ctx, seq_rows=sr)
     got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(), seq_rows=sr.cuda(),
                                     splits=splits)
@@ -199,9 +203,10 @@ def test_accept_greedy_and_rank_gap_gpu():
 @pytest.mark.gpu
 @pytest.mark.parametrize("hq,hkv,d,rows", [(40, 8, 128, [3, 1, 2, 3]), (4, 2, 64, [8, 1, 5, 2]), (12, 2, 256, [2, 1, 2, 1])])
 @pytest.mark.parametrize("splits", [1, 3])
-def test_tensor_core_decode_verify_rows(hq, hkv, d, rows, splits):
+@pytest.mark.parametrize("contiguous", [False, True, "slot-major"])
+def test_tensor_core_decode_verify_rows(hq, hkv, d, rows, splits, contiguous):
     ctxs = [40, 700, 129, 2500]
-    q, kp, vp, idx, ctx, indptr, sr = _attn_case(4, rows, ctxs, hq, hkv, d, seed=5)
+    q, kp, vp, idx, ctx, indptr, sr = _attn_case(4, rows, ctxs, hq, hkv, d, seed=5, contiguous=contiguous)
     ref = attention.paged_attention(q, kp, vp, idx, ctx, q_indptr=indptr, max_rows=max(rows), seq_rows=sr)
     got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(), q_indptr=indptr.cuda(),
                                     max_rows=max(rows), seq_rows=sr.cuda(), splits=splits)
@@ -212,7 +217,7 @@ def test_tensor_core_decode_verify_rows(hq, hkv, d, rows, splits):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("hq,hkv,d", [(40, 8, 128), (4, 2, 64), (32, 2, 128), (3, 1, 64)])
-@pytest.mark.parametrize("contiguous", [False, True])
+@pytest.mark.parametrize("contiguous", [False, True, "slot-major"])
 def test_tcgen05_prefill_attention(hq, hkv, d, contiguous):
     """Ragged prefill / chunked prefill over cached prefixes: tile edges, partial query blocks, 1-row sequences."""
     rows, ctxs = [300, 17, 128, 1, 257], [300, 500, 1200, 77, 257]
