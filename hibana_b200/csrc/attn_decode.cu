@@ -46,6 +46,7 @@ struct DecParams {
   int causal;
   int use_tma;
   int* status;
+  unsigned long long* prof;   // optional cycle counters of warp 0 (null = off)
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -152,7 +153,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
   // K and of V when the tile's slots are KT consecutive pool rows, else a row-by-row cp.async gather. `tma_mode`
   // remembers per stage which way the tile in flight travels, `tma_phase` the parity of the stage's barrier.
   uint32_t tma_mode = 0, tma_phase = 0;
-  auto issue = [&](int it) {
+  // Slot id of key `lane` of this warp's tile `it` (-1 beyond the split). Fetched one tile ahead of its use so
+  // that the index load's latency is not on the issue path.
+  auto fetch_slot = [&](int it) -> int {
+    const int base = k0 + (warp + it * DEC_WARPS) * KT;
+    return (warp + it * DEC_WARPS < ntiles && lane < KT && base + lane < k1) ? __ldg(idx_row + base + lane) : -1;
+  };
+  auto issue = [&](int it, int my_slot) {
     const int tile = warp + it * DEC_WARPS;
     if (tile < ntiles) {
       const int st = it % DEC_STAGES;
@@ -162,19 +169,17 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
       const uint32_t vdst = kdst + C::TILE_BYTES;
       constexpr int CPR = D / 8;            // 16-byte chunks per row
       constexpr int RPI = 32 / CPR > 0 ? 32 / CPR : 1;   // rows per warp instruction
-      const int my_slot = (lane < KT && base + lane < k1) ? idx_row[base + lane] : -1;
       const int slot0 = __shfl_sync(0xffffffffu, my_slot, 0);
       const bool run = p.use_tma && __all_sync(0xffffffffu, lane >= KT || (my_slot >= 0 && my_slot == slot0 + lane));
       if (run) {
         tma_mode |= 1u << st;
-        if (lane == 0) {
-          mbar_expect_tx(&full[st], 2 * C::TILE_BYTES);
-#pragma unroll
-          for (int h = 0; h < C::HALVES; ++h) {
-            tma_load_2d(kt + h * C::BLOCK_BYTES, &tmk, &full[st], kvh * p.tma_xh + h * 64, kvh * p.tma_yh + slot0);
-            tma_load_2d(kt + C::TILE_BYTES + h * C::BLOCK_BYTES, &tmv, &full[st], kvh * p.tma_xh + h * 64,
-                        kvh * p.tma_yh + slot0);
-          }
+        // lane 0 posts the byte count, then 2 * HALVES lanes issue one box each (K / V x column block)
+        if (lane == 0) mbar_expect_tx(&full[st], 2 * C::TILE_BYTES);
+        __syncwarp();
+        if (lane < 2 * C::HALVES) {
+          const int h = lane >> 1, is_v = lane & 1;
+          tma_load_2d(kt + is_v * C::TILE_BYTES + h * C::BLOCK_BYTES, is_v ? &tmv : &tmk, &full[st],
+                      kvh * p.tma_xh + h * 64, kvh * p.tma_yh + slot0);
         }
       } else {
         tma_mode &= ~(1u << st);
@@ -209,12 +214,19 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
   const int lim_lo = p.causal ? ctx - R + (g4 / g) + 1 : ctx;
   const int lim_hi = p.causal ? ctx - R + ((g4 + 8) / g) + 1 : ctx;
 
-  issue(0);
-  issue(1);
+  const bool prof = p.prof != nullptr && tid == 0;
+  const long long t_start = prof ? clock64() : 0;
+  long long c_issue = 0, c_wait = 0, c_math = 0;
+  issue(0, fetch_slot(0));
+  issue(1, fetch_slot(1));
+  int slot_next = fetch_slot(2);
   for (int it = 0; warp + it * DEC_WARPS < ntiles; ++it) {
     // Stage (it + 2) % 3 was read in iteration it - 1: every lane is past it, order it before the async writes.
     __syncwarp();
-    issue(it + 2);
+    long long t0 = prof ? clock64() : 0;
+    issue(it + 2, slot_next);
+    slot_next = fetch_slot(it + 3);
+    long long t1 = prof ? clock64() : 0;
     cp_wait2();
     const int st = it % DEC_STAGES;
     if (tma_mode & (1u << st)) {
@@ -223,6 +235,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
       if (!__all_sync(0xffffffffu, got)) break;
     }
     __syncwarp();
+    const long long t2 = prof ? clock64() : 0;
+    c_issue += t1 - t0;
+    c_wait += t2 - t1;
+    c_math -= t2;
     const uint32_t kbase = smem_u32(ring + st * C::STAGE_BYTES);
     const uint32_t vbase = kbase + C::TILE_BYTES;
     const int tile = warp + it * DEC_WARPS;
@@ -293,7 +309,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
         mma_bf16(o[nb + 1], pf[kk], vb[2], vb[3]);
       }
     }
+    if (prof) c_math += clock64();
   }
+  const long long t_loop_end = prof ? clock64() : 0;
   // Row sums live split over the 4 threads of a row group.
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
@@ -343,6 +361,16 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
       if (d == 0) p.part_lse[rh * p.splits + split] = lt > 0.f ? mt + log2f(lt) : -INFINITY;
     }
   }
+  if (prof) {
+    const long long t_end = clock64();
+    atomicAdd(p.prof + 0, static_cast<unsigned long long>(c_issue));
+    atomicAdd(p.prof + 1, static_cast<unsigned long long>(c_wait));
+    atomicAdd(p.prof + 2, static_cast<unsigned long long>(c_math));
+    atomicAdd(p.prof + 3, static_cast<unsigned long long>(t_loop_end - t_start));
+    atomicAdd(p.prof + 4, static_cast<unsigned long long>(t_end - t_loop_end));
+    atomicAdd(p.prof + 5, static_cast<unsigned long long>((ntiles + DEC_WARPS - 1 - warp) / DEC_WARPS));
+    atomicAdd(p.prof + 6, 1ull);
+  }
 }
 
 template <int D>
@@ -376,7 +404,14 @@ int launch_decode(const DecParams& p0, const void* k_pool, const void* v_pool, l
 
 using namespace hb;
 
+static unsigned long long* g_dec_prof = nullptr;
+
 extern "C" {
+
+// Cycle counters of warp 0 of every CTA, summed: `buf` = 8 zeroed uint64 on the device (null switches it off).
+// [0] issuing copies, [1] waiting for a tile, [2] tile math, [3] main loop, [4] merge + store, [5] tiles of warp 0,
+// [6] CTAs.
+void hb_attn_decode_profile(void* buf) { g_dec_prof = static_cast<unsigned long long*>(buf); }
 
 // bf16 KV only; rows_per_seq * (hq / hkv) must be <= 16. Partials go through hb_attn_merge when splits > 1.
 int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
@@ -405,6 +440,7 @@ int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long l
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal;
   p.status = static_cast<int*>(status);
+  p.prof = g_dec_prof;
   if (p.splits > 1 && (part_o == nullptr || part_lse == nullptr)) return 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (d == 64) return launch_decode<64>(p, k_pool, v_pool, pool_slots, batch, st);

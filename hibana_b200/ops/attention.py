@@ -23,6 +23,7 @@ nv.register("hb_attn_merge", [P, P, P, L, I, I, P])
 nv.register("hb_attn_decode", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, L, P, P])
 
 nv.register("hb_attn_prefill_profile", [P], void=True)
+nv.register("hb_attn_decode_profile", [P], void=True)
 nv.register("hb_attn_prefill", [P, P, P, L, L, P, L, P, P, P, P, I, I, I, I, I, Fl, I, L, P, P])
 
 NUM_SMS = 148

@@ -94,6 +94,18 @@ def main() -> None:
         res["frac_of_bf16_peak"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 3)
     else:
         res["frac_of_hbm"] = round(kv_bytes / ms / 1e6 / peaks["hbm_gbs"], 3)
+    if args.roles and args.mode == "decode":
+        from .. import _native as nv
+        buf = torch.zeros(8, dtype=torch.int64, device=dev)
+        nv.lib().hb_attn_decode_profile(ctypes.c_void_p(buf.data_ptr()))
+        fn()
+        torch.cuda.synchronize()
+        nv.lib().hb_attn_decode_profile(None)
+        c = buf.tolist()
+        tiles, ctas = max(c[5], 1), max(c[6], 1)
+        res["warp0_cycles"] = {"issue_per_tile": round(c[0] / tiles), "wait_per_tile": round(c[1] / tiles),
+                               "math_per_tile": round(c[2] / tiles), "loop_per_cta": round(c[3] / ctas),
+                               "merge_per_cta": round(c[4] / ctas), "tiles_per_cta_warp": round(tiles / ctas, 1)}
     if roles is not None:
         res["cycles_per_tile"] = roles
     print(json.dumps(res))
