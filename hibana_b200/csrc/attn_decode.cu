@@ -67,6 +67,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Transposes an 8x8 matrix of 16-bit elements held one 32-bit pair per lane (the mma fragment layout).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+
 __device__ __forceinline__ void cp16(uint32_t saddr, const void* g) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(g) : "memory");
 }
@@ -95,7 +102,7 @@ __device__ __forceinline__ uint32_t dsw(int row, int c) {
   return static_cast<uint32_t>((c >> 3) * (KT * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4));
 }
 
-template <int D>
+template <int D, bool T8>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 1)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, const DecParams p) {
   using C = DecCfg<D>;
@@ -140,11 +147,26 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
   }
   __syncthreads();
 
-  uint32_t qf[KS][4];
-  {
+  // Up to 8 query rows (T8): the tile math runs transposed, S^T = K Q^T and O^T = V^T P^T, so the keys (resp. the
+  // head dim) take the 16-row side of m16n8k16 and the query rows its 8 columns: half the MMAs of the 16-row
+  // form. Q is then the B operand (n = query row, k = head dim).
+  uint32_t qf[T8 ? 1 : KS][4];
+  uint32_t qb[T8 ? KS : 1][2];
+  if constexpr (!T8) {
     const uint32_t base = smem_u32(qs) + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) ldsm_x4(qf[ks], base + ks * 32);
+  } else {
+    const uint32_t base = smem_u32(qs) + (lane & 7) * ROWB + (lane >> 3) * 16;
+#pragma unroll
+    for (int ks = 0; ks < KS; ks += 2) {
+      uint32_t r[4];
+      ldsm_x4(r, base + ks * 32);
+      qb[ks][0] = r[0];
+      qb[ks][1] = r[1];
+      qb[ks + 1][0] = r[2];
+      qb[ks + 1][1] = r[3];
+    }
   }
 
   const int* idx_row = p.kv_indices + static_cast<long long>(p.seq_rows ? p.seq_rows[b] : b) * p.ld_idx;
@@ -206,13 +228,17 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
     cp_commit();
   };
 
-  float o[ONB][4];
+  // 16-row form: o[n-block][4], rows g4 / g4 + 8. Transposed form: o[16-wide head-dim block][4] = (d g4 | g4 + 8)
+  // x (query rows 2 t4, 2 t4 + 1); "lo" / "hi" then name those two query rows.
+  constexpr int OB = T8 ? D / 16 : ONB;
+  float o[OB][4];
 #pragma unroll
-  for (int i = 0; i < ONB; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  for (int i = 0; i < OB; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   // Causal limits of this thread's two rows (keys [0, limit) visible).
-  const int lim_lo = p.causal ? ctx - R + (g4 / g) + 1 : ctx;
-  const int lim_hi = p.causal ? ctx - R + ((g4 + 8) / g) + 1 : ctx;
+  const int row_lo = T8 ? 2 * t4 : g4, row_hi = T8 ? 2 * t4 + 1 : g4 + 8;
+  const int lim_lo = p.causal ? ctx - R + (row_lo / g) + 1 : ctx;
+  const int lim_hi = p.causal ? ctx - R + (row_hi / g) + 1 : ctx;
 
   const bool prof = p.prof != nullptr && tid == 0;
   const long long t_start = prof ? clock64() : 0;
@@ -244,94 +270,185 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
     const int tile = warp + it * DEC_WARPS;
     const int kpos0 = k0 + tile * KT;
 
+    if constexpr (!T8) {
     float s[NB][4];
 #pragma unroll
-    for (int j = 0; j < NB; ++j) {
-      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      for (int j = 0; j < NB; ++j) {
+        s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < KS; ks += 2) {
-        uint32_t kb[4];
-        ldsm_x4(kb, kbase + dsw<KT>(j * 8 + (lane & 7), ks * 2 + (lane >> 3)));
-        mma_bf16(s[j], qf[ks], kb[0], kb[1]);
-        mma_bf16(s[j], qf[ks + 1], kb[2], kb[3]);
+        for (int ks = 0; ks < KS; ks += 2) {
+          uint32_t kb[4];
+          ldsm_x4(kb, kbase + dsw<KT>(j * 8 + (lane & 7), ks * 2 + (lane >> 3)));
+          mma_bf16(s[j], qf[ks], kb[0], kb[1]);
+          mma_bf16(s[j], qf[ks + 1], kb[2], kb[3]);
+        }
       }
-    }
-    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < NB; ++j) {
+      for (int j = 0; j < NB; ++j) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int kp = kpos0 + j * 8 + 2 * t4 + e;
-        const bool in = kp < k1;
-        s[j][e] = (in && kp < lim_lo) ? s[j][e] * p.scale_log2 : -INFINITY;
-        s[j][2 + e] = (in && kp < lim_hi) ? s[j][2 + e] * p.scale_log2 : -INFINITY;
-        mx_lo = fmaxf(mx_lo, s[j][e]);
-        mx_hi = fmaxf(mx_hi, s[j][2 + e]);
+        for (int e = 0; e < 2; ++e) {
+          const int kp = kpos0 + j * 8 + 2 * t4 + e;
+          const bool in = kp < k1;
+          s[j][e] = (in && kp < lim_lo) ? s[j][e] * p.scale_log2 : -INFINITY;
+          s[j][2 + e] = (in && kp < lim_hi) ? s[j][2 + e] * p.scale_log2 : -INFINITY;
+          mx_lo = fmaxf(mx_lo, s[j][e]);
+          mx_hi = fmaxf(mx_hi, s[j][2 + e]);
+        }
       }
-    }
-    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-    const float a_lo = mn_lo == -INFINITY ? 1.f : exp2f(m_lo - mn_lo);
-    const float a_hi = mn_hi == -INFINITY ? 1.f : exp2f(m_hi - mn_hi);
-    m_lo = mn_lo;
-    m_hi = mn_hi;
-    l_lo *= a_lo;
-    l_hi *= a_hi;
-    uint32_t pf[NB / 2][4];
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      const float a_lo = mn_lo == -INFINITY ? 1.f : exp2f(m_lo - mn_lo);
+      const float a_hi = mn_hi == -INFINITY ? 1.f : exp2f(m_hi - mn_hi);
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+      l_lo *= a_lo;
+      l_hi *= a_hi;
+      uint32_t pf[NB / 2][4];
 #pragma unroll
-    for (int j = 0; j < NB; ++j) {
-      const float p0 = mn_lo == -INFINITY ? 0.f : exp2f(s[j][0] - mn_lo);
-      const float p1 = mn_lo == -INFINITY ? 0.f : exp2f(s[j][1] - mn_lo);
-      const float p2 = mn_hi == -INFINITY ? 0.f : exp2f(s[j][2] - mn_hi);
-      const float p3 = mn_hi == -INFINITY ? 0.f : exp2f(s[j][3] - mn_hi);
-      l_lo += p0 + p1;
-      l_hi += p2 + p3;
-      pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
-      pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
-    }
+      for (int j = 0; j < NB; ++j) {
+        const float p0 = mn_lo == -INFINITY ? 0.f : exp2f(s[j][0] - mn_lo);
+        const float p1 = mn_lo == -INFINITY ? 0.f : exp2f(s[j][1] - mn_lo);
+        const float p2 = mn_hi == -INFINITY ? 0.f : exp2f(s[j][2] - mn_hi);
+        const float p3 = mn_hi == -INFINITY ? 0.f : exp2f(s[j][3] - mn_hi);
+        l_lo += p0 + p1;
+        l_hi += p2 + p3;
+        pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+        pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
 #pragma unroll
-    for (int nb = 0; nb < ONB; ++nb) {
-      o[nb][0] *= a_lo;
-      o[nb][1] *= a_lo;
-      o[nb][2] *= a_hi;
-      o[nb][3] *= a_hi;
-    }
+      for (int nb = 0; nb < ONB; ++nb) {
+        o[nb][0] *= a_lo;
+        o[nb][1] *= a_lo;
+        o[nb][2] *= a_hi;
+        o[nb][3] *= a_hi;
+      }
 #pragma unroll
-    for (int kk = 0; kk < KT / 16; ++kk) {
+      for (int kk = 0; kk < KT / 16; ++kk) {
 #pragma unroll
-      for (int nb = 0; nb < ONB; nb += 2) {
-        uint32_t vb[4];
-        ldsm_x4_t(vb, vbase + dsw<KT>(kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), nb + (lane >> 4)));
-        mma_bf16(o[nb], pf[kk], vb[0], vb[1]);
-        mma_bf16(o[nb + 1], pf[kk], vb[2], vb[3]);
+        for (int nb = 0; nb < ONB; nb += 2) {
+          uint32_t vb[4];
+          ldsm_x4_t(vb, vbase + dsw<KT>(kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), nb + (lane >> 4)));
+          mma_bf16(o[nb], pf[kk], vb[0], vb[1]);
+          mma_bf16(o[nb + 1], pf[kk], vb[2], vb[3]);
+        }
+      }
+    } else {
+      constexpr int MT = KT / 16;   // 16-key blocks of the tile
+      float st[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        st[mt][0] = st[mt][1] = st[mt][2] = st[mt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          uint32_t ka[4];
+          ldsm_x4(ka, kbase + dsw<KT>(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+          mma_bf16(st[mt], ka, qb[ks][0], qb[ks][1]);
+        }
+      }
+      // st[mt] = {key g4: rows lo, hi | key g4 + 8: rows lo, hi} of key block mt
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int kp = kpos0 + mt * 16 + g4 + 8 * e;
+          const bool in = kp < k1;
+          st[mt][2 * e] = (in && kp < lim_lo) ? st[mt][2 * e] * p.scale_log2 : -INFINITY;
+          st[mt][2 * e + 1] = (in && kp < lim_hi) ? st[mt][2 * e + 1] * p.scale_log2 : -INFINITY;
+          mx_lo = fmaxf(mx_lo, st[mt][2 * e]);
+          mx_hi = fmaxf(mx_hi, st[mt][2 * e + 1]);
+        }
+      }
+#pragma unroll
+      for (int sh = 4; sh < 32; sh <<= 1) {   // keys live across the g4 lane groups
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, sh));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, sh));
+      }
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      const float a_lo = mn_lo == -INFINITY ? 1.f : exp2f(m_lo - mn_lo);
+      const float a_hi = mn_hi == -INFINITY ? 1.f : exp2f(m_hi - mn_hi);
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+      l_lo *= a_lo;
+      l_hi *= a_hi;
+      uint32_t pb[MT][2];   // P^T as B operand: (k = key, n = query row)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float p0 = mn_lo == -INFINITY ? 0.f : exp2f(st[mt][2 * e] - mn_lo);
+          const float p1 = mn_hi == -INFINITY ? 0.f : exp2f(st[mt][2 * e + 1] - mn_hi);
+          l_lo += p0;
+          l_hi += p1;
+          pb[mt][e] = movmatrix_trans(pack_bf16(p0, p1));
+        }
+      }
+#pragma unroll
+      for (int ob = 0; ob < OB; ++ob) {
+        o[ob][0] *= a_lo;
+        o[ob][1] *= a_hi;
+        o[ob][2] *= a_lo;
+        o[ob][3] *= a_hi;
+      }
+#pragma unroll
+      for (int kk = 0; kk < MT; ++kk) {
+#pragma unroll
+        for (int ob = 0; ob < OB; ++ob) {
+          uint32_t va[4];   // V^T block (16 head-dim x 16 keys) through transposing loads
+          ldsm_x4_t(va, vbase + dsw<KT>(kk * 16 + ((lane >> 4) & 1) * 8 + (lane & 7), ob * 2 + ((lane >> 3) & 1)));
+          mma_bf16(o[ob], va, pb[kk][0], pb[kk][1]);
+        }
       }
     }
     if (prof) c_math += clock64();
   }
   const long long t_loop_end = prof ? clock64() : 0;
-  // Row sums live split over the 4 threads of a row group.
-  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncwarp();
   // ---- merge the 4 warps through each warp's own (now idle) ring
   float* mo = reinterpret_cast<float*>(ring);          // [16][D]
   float* ml = mo + 16 * D;                             // [16][2] (m, l)
+  if constexpr (!T8) {
+    // Row sums live split over the 4 threads of a row group.
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
 #pragma unroll
-  for (int nb = 0; nb < ONB; ++nb) {
-    *reinterpret_cast<float2*>(mo + g4 * D + nb * 8 + 2 * t4) = make_float2(o[nb][0], o[nb][1]);
-    *reinterpret_cast<float2*>(mo + (g4 + 8) * D + nb * 8 + 2 * t4) = make_float2(o[nb][2], o[nb][3]);
-  }
-  if (t4 == 0) {
-    ml[g4 * 2] = m_lo;
-    ml[g4 * 2 + 1] = l_lo;
-    ml[(g4 + 8) * 2] = m_hi;
-    ml[(g4 + 8) * 2 + 1] = l_hi;
+    for (int nb = 0; nb < OB; ++nb) {
+      *reinterpret_cast<float2*>(mo + g4 * D + nb * 8 + 2 * t4) = make_float2(o[nb][0], o[nb][1]);
+      *reinterpret_cast<float2*>(mo + (g4 + 8) * D + nb * 8 + 2 * t4) = make_float2(o[nb][2], o[nb][3]);
+    }
+    if (t4 == 0) {
+      ml[g4 * 2] = m_lo;
+      ml[g4 * 2 + 1] = l_lo;
+      ml[(g4 + 8) * 2] = m_hi;
+      ml[(g4 + 8) * 2 + 1] = l_hi;
+    }
+  } else {
+    // Row sums live split over the 8 lane groups that hold different keys.
+#pragma unroll
+    for (int sh = 4; sh < 32; sh <<= 1) {
+      l_lo += __shfl_xor_sync(0xffffffffu, l_lo, sh);
+      l_hi += __shfl_xor_sync(0xffffffffu, l_hi, sh);
+    }
+#pragma unroll
+    for (int ob = 0; ob < OB; ++ob) {
+      mo[row_lo * D + ob * 16 + g4] = o[ob][0];
+      mo[row_hi * D + ob * 16 + g4] = o[ob][1];
+      mo[row_lo * D + ob * 16 + g4 + 8] = o[ob][2];
+      mo[row_hi * D + ob * 16 + g4 + 8] = o[ob][3];
+    }
+    if (g4 == 0) {
+      ml[row_lo * 2] = m_lo;
+      ml[row_lo * 2 + 1] = l_lo;
+      ml[row_hi * 2] = m_hi;
+      ml[row_hi * 2 + 1] = l_hi;
+    }
   }
   __syncthreads();
   for (int i = tid; i < nq * D; i += DEC_WARPS * 32) {
@@ -373,14 +490,14 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
   }
 }
 
-template <int D>
+template <int D, bool T8>
 int launch_decode(const DecParams& p0, const void* k_pool, const void* v_pool, long long pool_slots, int batch,
                   cudaStream_t st) {
   DecParams p = p0;
   using C = DecCfg<D>;
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) !=
+    if (cudaFuncSetAttribute(attn_decode_kernel<D, T8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) !=
         cudaSuccess)
       return 3;
     attr = true;
@@ -395,7 +512,7 @@ int launch_decode(const DecParams& p0, const void* k_pool, const void* v_pool, l
     tk = t.k;
     tv = t.v;
   }
-  attn_decode_kernel<D><<<dim3(batch, p.hkv, p.splits), DEC_WARPS * 32, C::SMEM, st>>>(*tk, *tv, p);
+  attn_decode_kernel<D, T8><<<dim3(batch, p.hkv, p.splits), DEC_WARPS * 32, C::SMEM, st>>>(*tk, *tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
@@ -443,9 +560,13 @@ int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long l
   p.prof = g_dec_prof;
   if (p.splits > 1 && (part_o == nullptr || part_lse == nullptr)) return 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (d == 64) return launch_decode<64>(p, k_pool, v_pool, pool_slots, batch, st);
-  if (d == 128) return launch_decode<128>(p, k_pool, v_pool, pool_slots, batch, st);
-  if (d == 256) return launch_decode<256>(p, k_pool, v_pool, pool_slots, batch, st);
+  const bool t8 = max_rows * (hq / hkv) <= 8;
+  if (d == 64) return t8 ? launch_decode<64, true>(p, k_pool, v_pool, pool_slots, batch, st)
+                         : launch_decode<64, false>(p, k_pool, v_pool, pool_slots, batch, st);
+  if (d == 128) return t8 ? launch_decode<128, true>(p, k_pool, v_pool, pool_slots, batch, st)
+                          : launch_decode<128, false>(p, k_pool, v_pool, pool_slots, batch, st);
+  if (d == 256) return t8 ? launch_decode<256, true>(p, k_pool, v_pool, pool_slots, batch, st)
+                          : launch_decode<256, false>(p, k_pool, v_pool, pool_slots, batch, st);
   return 1;
 }
 
