@@ -38,7 +38,8 @@ struct Ctrl {
   int sp_seq_scatter;            // scatters completed on this rank
   int sp_seq_gather;             // gathers this rank has pushed
   int sp_done;                   // CTAs of the running reduce kernel that have finished
-  int pad[13];
+  int sp_target;                 // tile arrivals every source owes after the scatters completed so far
+  int pad[12];
 };
 static_assert(sizeof(Ctrl) <= CTRL_BYTES, "control block too large");
 
@@ -80,7 +81,9 @@ __device__ __forceinline__ bool wait_peers(Ctrl* mine, int world, int slot, int 
         ok = true;
         break;
       }
-      if ((it & 63u) == 63u && globaltimer_ns() - t0 > limit_ns) break;
+      // once any wait of this job has timed out, later waits give up at their first check instead of each
+      // spending the full limit (thousands of CTAs x the limit would look like a hang)
+      if ((it & 63u) == 63u && (globaltimer_ns() - t0 > limit_ns || *reinterpret_cast<volatile int*>(status) != 0)) break;
     }
     if (!ok) {
       *ok_smem = 0;
@@ -242,11 +245,13 @@ __global__ void __launch_bounds__(T) ar_norm_ll_kernel(const ArNormLlParams pp) 
                 got = true;
                 break;
               }
-              if ((it & 255u) == 255u && (bad_s || globaltimer_ns() - t0 > p.limit_ns)) break;
+              if ((it & 255u) == 255u && (bad_s || globaltimer_ns() - t0 > p.limit_ns ||
+                                          *reinterpret_cast<volatile int*>(p.status) != 0))
+                break;
             }
             if (!got) {
               bad_s = 1;
-              set_status(p.status, kTimeoutPeer);
+              set_status(p.status, kTimeoutLowLatency);
             }
             w[k] = data;
           }
@@ -317,20 +322,21 @@ __global__ void __launch_bounds__(T) rs_norm_ag_kernel(const RsNormAgParams p) {
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
   if (threadIdx.x < p.world) {
-    const long long want = static_cast<long long>(sseq) * p.expected;
+    // cumulative, so calls with different row counts can follow one another
+    const int want = ld_relaxed_sys(&mine->sp_target) + p.expected;
     const unsigned long long t0 = globaltimer_ns();
     bool ok = false;
     for (unsigned it = 0; it < HB_SPIN_LIMIT; ++it) {
-      if (ld_relaxed_sys(&mine->sp_cnt[threadIdx.x]) >= want) {
+      if (ld_relaxed_sys(&mine->sp_cnt[threadIdx.x]) - want >= 0) {
         ok = true;
         break;
       }
-      if ((it & 63u) == 63u && globaltimer_ns() - t0 > p.limit_ns) break;
+      if ((it & 63u) == 63u && (globaltimer_ns() - t0 > p.limit_ns || *reinterpret_cast<volatile int*>(p.status) != 0)) break;
     }
     __threadfence_system();
     if (!ok) {
       ok_s = 0;
-      set_status(p.status, kTimeoutPeer);
+      set_status(p.status, kTimeoutCounter);
     }
   }
   __syncthreads();
@@ -393,6 +399,7 @@ __global__ void __launch_bounds__(T) rs_norm_ag_kernel(const RsNormAgParams p) {
     }
     if (threadIdx.x == 0) {
       mine->sp_done = 0;
+      mine->sp_target += p.expected;
       mine->sp_seq_scatter = sseq;
       mine->sp_seq_gather = gseq;
     }

@@ -250,11 +250,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
             ready = true;
             break;
           }
-          if ((it & 63u) == 63u && globaltimer_ns() - t0 > p.limit_ns) break;
+          if ((it & 63u) == 63u && (globaltimer_ns() - t0 > p.limit_ns || *reinterpret_cast<volatile int*>(p.status) != 0)) break;
         }
         if (!ready) {
           *abort = 1;
-          set_status(p.status, kTimeoutPeer);
+          set_status(p.status, kTimeoutGate);
         }
       }
       // side 0 = A operand (+ its scales), side 1 = B operand (+ its scales) of K tile i into stage i % S

@@ -23,6 +23,8 @@ enum Status : int {
   kTimeoutCounter = 5,  // a wait on an arrival counter ran out
   kBadShape = 6,
   kTimeoutDrain = 7,
+  kTimeoutLowLatency = 8,   // the low-latency all-reduce never saw a peer's word
+  kTimeoutGate = 9,         // a flag-gated GEMM tile never saw its source rank's rows
 };
 
 #ifndef HB_SPIN_LIMIT
