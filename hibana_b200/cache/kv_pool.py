@@ -61,6 +61,27 @@ class KvPool:
         assert all(not self._owned[s] for s in self._free)
         assert sum(self._owned) + len(self._free) == self.slots
 
+    def copy_payload(self, ids: torch.Tensor, payload: torch.Tensor, to_pool: bool) -> None:
+        """Moves the rows of slots `ids` (int32, on the pool's device) of all layers between the pool and a linear
+        payload [len(ids), layers * 2 * kv_heads * head_dim] (device or pinned host memory): one kernel launch on
+        CUDA (csrc/kv_copy.cu), indexing on CPU."""
+        n = ids.numel()
+        if n == 0:
+            return
+        if self.storage.is_cuda:
+            from .. import _native as nv
+            nv.register("hb_kv_copy", [nv.P, nv.P, nv.P, nv.I, nv.I, nv.I, nv.L, nv.I, nv.I, nv.I, nv.P])
+            nv.check(nv.lib().hb_kv_copy(self.storage.data_ptr(), payload.data_ptr(), ids.data_ptr(), n,
+                                         self.storage.shape[0], self.kv_heads, self.slots + 1, self.head_dim,
+                                         self.storage.element_size(), int(to_pool), nv.stream()), "hb_kv_copy")
+            return
+        view = payload.view(self.storage.dtype).view(n, self.storage.shape[0], 2, self.kv_heads, self.head_dim)
+        idx = ids.long()
+        if to_pool:
+            self.storage[:, :, :, idx] = view.permute(1, 2, 3, 0, 4)
+        else:
+            view.copy_(self.storage[:, :, :, idx].permute(3, 0, 1, 2, 4))
+
     def rows(self, ids: list[int]) -> torch.Tensor:
         """All layers' K and V rows of the given slots: [layers, 2, len(ids), kv_heads, head_dim] (a copy)."""
         idx = torch.tensor(ids, dtype=torch.long, device=self.device)

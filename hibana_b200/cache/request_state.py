@@ -79,6 +79,42 @@ class StateManager:
         req.committed_len = req.cached_len
         self.live[req.rid] = req
 
+    def restore_from_ssd(self, tokens: Sequence[int], tier) -> int:
+        """Before admission: when the SSD tier holds at least `tier.min_gain` more tokens of this prompt than the
+        GPU cache, allocates slots, scatters the blocks into them and publishes them in the tree, so that the
+        admission that follows simply hits. KV-only models (a recurrent model also needs the state snapshot of
+        the tail object; without one the restored KV could not be resumed from). Returns tokens restored."""
+        if self.cache is None or self.states is not None or tier is None:
+            return 0
+        tokens = list(tokens[:max(len(tokens) - 1, 0)])
+        m = self.cache.match(tokens, split=False)
+        have = m.length
+        n = tier.worth(tokens, have)
+        if not n:
+            return 0
+        m = self.cache.match(tokens[:have])            # split so that a node ends exactly at `have`
+        lock = self.cache.lock(m.node)                  # the allocation below must not evict the matched path
+        try:
+            try:
+                fresh = self._alloc_kv(n - have)
+            except MemoryError:
+                return 0
+            from .ssd_store import BLOCK_TOKENS
+            start = have // BLOCK_TOKENS * BLOCK_TOKENS
+            ids = [0] * (have - start) + fresh          # rows the tree already has land in the dummy slot
+            good = max(tier.restore(tokens, start, n, ids), have)
+            if good < n:
+                self.kv.free(fresh[good - have:])
+                fresh = fresh[:good - have]
+            if fresh:
+                path = m.node.path_slots()[:have]
+                _node, adopted = self.cache.insert(tokens[:good], path + fresh, start=have)
+                if adopted < good:                      # someone cached the same tokens meanwhile
+                    self.kv.free(fresh[adopted - have:])
+            return max(good - have, 0)
+        finally:
+            self.cache.unlock(lock)
+
     def _alloc_state(self) -> int:
         if self.states.free_count == 0 and self.cache is not None:
             self.cache.evict_snapshots(1)

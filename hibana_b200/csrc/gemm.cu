@@ -75,6 +75,12 @@ struct DevParams {
   uint8_t* peer_base[8];
   long long stage_offset, counter_offset, flag_offset, seq_offset;
   unsigned long long limit_ns;
+  // expert-parallel fusion (grouped mode)
+  const int* ep_gate_flags;
+  const int* ep_seq_ptr;
+  const int* ep_row_ret;
+  long long ep_ret_offset, ep_ret_flag_offset;
+  int* ep_done;
 };
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
@@ -103,6 +109,19 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
       for (int j = 0; j < CH; ++j) {
         const int col = col0 + j;
         if (row_ok && col < col_lim) out[static_cast<long long>(col) * p.ldo + row] = v[j] * alpha;
+      }
+    } else if (p.epilogue == kEpiReturn) {
+      // column = one routed row; it goes home to the rank it came from (plain stores over NVLink, lanes are
+      // consecutive features of that row)
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int col = col0 + j;
+        if (row_ok && col < col_lim) {
+          const int meta = p.ep_row_ret[col];
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peer_base[(meta >> 24) & 7] + p.ep_ret_offset) +
+                               static_cast<long long>(meta & 0xFFFFFF) * p.ldo + row;
+          *dst = __float2bfloat16(v[j] * alpha);
+        }
       }
     } else {
       __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
@@ -176,6 +195,22 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
   }
 }
 
+// kEpiReturn: one thread per CTA reports in after its stores are fenced system-wide; the last CTA of the grid
+// publishes this rank's sequence number on every rank's return flag and re-arms the counter.
+__device__ __forceinline__ void ep_cta_done(const DevParams& p) {
+  __threadfence_system();
+  const int total = static_cast<int>(gridDim.x * gridDim.y * gridDim.z);
+  if (atomicAdd(p.ep_done, 1) == total - 1) {
+    *p.ep_done = 0;
+    const int seq = *reinterpret_cast<const volatile int*>(p.ep_seq_ptr) + 1;
+    __threadfence_system();
+    for (int r = 0; r < p.world; ++r) {
+      int* f = reinterpret_cast<int*>(p.peer_base[r] + p.ep_ret_flag_offset) + p.rank;
+      asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
+    }
+  }
+}
+
 template <int KIND, int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUtensorMap tmb, const DevParams p) {
@@ -198,7 +233,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
   const float* alpha_ptr = p.alpha_ptr;
   if (p.grp_cnt != nullptr) {
     const int e = blockIdx.z, cnt = p.grp_cnt[e];
-    if (static_cast<int>(blockIdx.y) * BN >= cnt) return;   // uniform: before any barrier or TMEM allocation
+    if (static_cast<int>(blockIdx.y) * BN >= cnt) {   // uniform: before any barrier or TMEM allocation
+      if (p.epilogue == kEpiReturn && threadIdx.x == 0) ep_cta_done(p);
+      return;
+    }
     a_row0 = e * p.grp_rows_a + tile_a * BM;
     b_row0 = p.grp_start[e] + blockIdx.y * BN;
     row_lim = p.grp_rows_a;
@@ -235,28 +273,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
   if (warp == 0) {
     if (lane == 0) {
       int issued = 0;
-      if (p.peer_on && p.flag_offset >= 0) {
-        // all-gather -> GEMM: the rows of this A tile were pushed into local memory by rank `src`; wait (bounded)
-        // until its arrival flag reaches the expected sequence number before the first TMA load touches them.
-        const int src = a_row0 / p.rows_per_rank;
-        const int* flag = reinterpret_cast<const int*>(p.peer_base[p.rank] + p.flag_offset) + src;
-        const int want = *reinterpret_cast<const int*>(p.peer_base[p.rank] + p.seq_offset);
-        const uint64_t t0 = globaltimer_ns();
-        bool ready = false;
-        for (uint32_t it = 0; it < HB_SPIN_LIMIT; ++it) {
-          int v;
-          asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-          if (v - want >= 0) {
-            ready = true;
-            break;
-          }
-          if ((it & 63u) == 63u && (globaltimer_ns() - t0 > p.limit_ns || *reinterpret_cast<volatile int*>(p.status) != 0)) break;
-        }
-        if (!ready) {
-          *abort = 1;
-          set_status(p.status, kTimeoutGate);
-        }
-      }
       // side 0 = A operand (+ its scales), side 1 = B operand (+ its scales) of K tile i into stage i % S
       auto load_side = [&](int i, int side) {
         const int s = i % S;
@@ -278,17 +294,58 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
           }
         }
       };
-      // First ring of stages (their `empty` barriers are trivially free): weights first, then wait for the
-      // producing grid, then the activations.
+      // First ring of stages (their `empty` barriers are trivially free): the weights go first; they depend on
+      // nothing. Then the waits for whoever produces the activations: the preceding grid (programmatic
+      // dependent launch), the source rank of a gathered row tile, or every sender of an expert-parallel
+      // dispatch. Then the activations.
       const int wside = p.swap ? 0 : 1;
-      const int pre = *abort ? 0 : min(S, nkt);
+      const int pre = min(S, nkt);
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full[i], C::STAGE_BYTES);
-        if (!p.peer_on) load_side(i, wside);
+        load_side(i, wside);
       }
       grid_dep_wait();
+      bool ready = true;
+      if (p.peer_on && p.flag_offset >= 0) {
+        // all-gather -> GEMM: the rows of this A tile were pushed into local memory by rank `src`
+        const int src = a_row0 / p.rows_per_rank;
+        const int* flag = reinterpret_cast<const int*>(p.peer_base[p.rank] + p.flag_offset) + src;
+        const int want = *reinterpret_cast<const volatile int*>(p.peer_base[p.rank] + p.seq_offset);
+        const uint64_t t0 = globaltimer_ns();
+        ready = false;
+        for (uint32_t it = 0; it < HB_SPIN_LIMIT; ++it) {
+          int v;
+          asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+          if (v - want >= 0) {
+            ready = true;
+            break;
+          }
+          if ((it & 63u) == 63u && (globaltimer_ns() - t0 > p.limit_ns || *reinterpret_cast<volatile int*>(p.status) != 0)) break;
+        }
+      } else if (p.ep_gate_flags != nullptr) {
+        // expert-parallel dispatch -> grouped GEMM: every sender has published its rows
+        const int want = *reinterpret_cast<const volatile int*>(p.ep_seq_ptr) + 1;
+        const uint64_t t0 = globaltimer_ns();
+        for (int r = 0; r < p.world && ready; ++r) {
+          ready = false;
+          for (uint32_t it = 0; it < HB_SPIN_LIMIT; ++it) {
+            int v;
+            asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p.ep_gate_flags + r) : "memory");
+            if (v - want >= 0) {
+              ready = true;
+              break;
+            }
+            if ((it & 63u) == 63u && (globaltimer_ns() - t0 > p.limit_ns || *reinterpret_cast<volatile int*>(p.status) != 0)) break;
+          }
+        }
+      }
+      if (!ready) {
+        *abort = 1;
+        set_status(p.status, kTimeoutGate);
+      }
+      // On a failed wait the activation side is still loaded (whatever is there): the stages then complete, the
+      // barriers balance and no copy is left in flight; the status word tells the host the result is void.
       for (int i = 0; i < pre; ++i) {
-        if (p.peer_on) load_side(i, wside);
         load_side(i, wside ^ 1);
         ++issued;
       }
@@ -493,8 +550,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     __syncwarp();
     cluster_sync_all();   // nobody leaves while a peer may still read its partial
   }
+  if (p.epilogue == kEpiReturn && warp >= 2) __threadfence_system();   // this thread's remote stores
   tc_fence_before();
   __syncthreads();
+  if (p.epilogue == kEpiReturn && threadIdx.x == 0) ep_cta_done(p);
   if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
@@ -686,6 +745,18 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   } else if (a.epilogue == kEpiScatter) {
     return cudaErrorInvalidValue;
   }
+  p.ep_gate_flags = nullptr; p.ep_seq_ptr = nullptr; p.ep_row_ret = nullptr; p.ep_done = nullptr;
+  p.ep_ret_offset = 0; p.ep_ret_flag_offset = 0;
+  if (a.ep != nullptr) {
+    if (!grouped || a.peer != nullptr) return cudaErrorInvalidValue;
+    if (a.epilogue == kEpiReturn && (a.ep->row_ret == nullptr || a.ep->done_counter == nullptr)) return cudaErrorInvalidValue;
+    p.world = a.ep->world; p.rank = a.ep->rank; p.limit_ns = a.ep->limit_ns;
+    for (int i = 0; i < 8; ++i) p.peer_base[i] = static_cast<uint8_t*>(a.ep->base[i]);
+    p.ep_gate_flags = a.ep->gate_flags; p.ep_seq_ptr = a.ep->seq_ptr; p.ep_row_ret = a.ep->row_ret;
+    p.ep_ret_offset = a.ep->ret_offset; p.ep_ret_flag_offset = a.ep->ret_flag_offset; p.ep_done = a.ep->done_counter;
+  } else if (a.epilogue == kEpiReturn) {
+    return cudaErrorInvalidValue;
+  }
   const dim3 grid = grouped ? dim3(a.grp_rows_a / BM, a.grp_chunks, a.grp_experts) : dim3(tiles_a, tiles_b, splits);
 
 #define HB_DISPATCH(KIND)                                                        \
@@ -771,6 +842,39 @@ int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, con
   g.grp_start = static_cast<const int*>(start); g.grp_cnt = static_cast<const int*>(cnt);
   g.grp_rows_a = n_per_expert; g.grp_experts = experts; g.grp_chunks = (max_rows_per_expert + bn - 1) / bn;
   g.peer = nullptr;
+  const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// Grouped GEMM with expert-parallel fusion: `gate_flags` (may be null) delays the activation loads until every
+// sender's flag has reached *seq_ptr + 1; epilogue 5 sends every output row back to its source rank (see
+// hb::GemmEp) and raises this rank's flag on every rank when the whole grid is done.
+int hb_gemm_grouped_ep(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int experts,
+                       int n_per_expert, int b_rows, int k, void* out, long long ldo, const void* alpha_ptr,
+                       int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status,
+                       int ka_a, int ka_b, const void* const* bases, int world, int rank, const void* gate_flags,
+                       const void* seq_ptr, const void* row_ret, long long ret_offset, void* done_counter,
+                       long long ret_flag_offset, long long limit_ns, void* stream) {
+  hb::GemmArgs g;
+  hb::GemmEp ep;
+  int bn = 16;
+  while (bn < max_rows_per_expert && bn < 256) bn *= 2;
+  for (int i = 0; i < 8; ++i) ep.base[i] = i < world ? const_cast<void*>(bases[i]) : nullptr;
+  ep.world = world; ep.rank = rank;
+  ep.gate_flags = static_cast<const int*>(gate_flags); ep.seq_ptr = static_cast<const int*>(seq_ptr);
+  ep.row_ret = static_cast<const int*>(row_ret); ep.ret_offset = ret_offset;
+  ep.done_counter = static_cast<int*>(done_counter); ep.ret_flag_offset = ret_flag_offset;
+  ep.limit_ns = static_cast<unsigned long long>(limit_ns);
+  g.kind = kind; g.a = a; g.b = b; g.sfa = sfa; g.sfb = sfb;
+  g.ra = experts * n_per_expert; g.rb = b_rows; g.k = k; g.lda = k; g.ldb = k;
+  g.out = out; g.ldo = ldo; g.residual = nullptr; g.alpha = 1.f;
+  g.alpha_ptr = static_cast<const float*>(alpha_ptr); g.epilogue = epilogue; g.swap = 1; g.splits = 1;
+  g.workspace = nullptr; g.counters = nullptr; g.status = static_cast<int*>(status); g.bn = bn;
+  g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
+  g.grp_start = static_cast<const int*>(start); g.grp_cnt = static_cast<const int*>(cnt);
+  g.grp_rows_a = n_per_expert; g.grp_experts = experts; g.grp_chunks = (max_rows_per_expert + bn - 1) / bn;
+  g.peer = nullptr;
+  g.ep = &ep;
   const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

@@ -15,6 +15,9 @@ enum GemmEpilogue : int {
   kEpiScatter = 4,    // row-parallel GEMM -> reduce-scatter: the bf16 partial tile is stored straight into the
                       // staging area of the rank that owns its rows (peer memory), then that rank's arrival
                       // counter for this source is bumped (normal orientation only)
+  kEpiReturn = 5,     // expert-parallel fc2 (grouped, weights on the 128-row side): column j of the output (one
+                      // routed row) is stored into the return buffer of the rank the row came from, at the row
+                      // that rank asked for; when every CTA is done the kernel raises a flag on every rank
 };
 
 // Peer-memory fusion arguments (all ranks pass the same offsets; pointers are this process's mappings).
@@ -27,6 +30,20 @@ struct GemmPeer {
   // gather gating (all-gather -> GEMM): A row tiles of source rank s may be loaded once flags[s] >= *seq_ptr
   long long flag_offset;    // byte offset of int flags[world] in this rank's heap (-1 = no gating)
   long long seq_offset;     // byte offset of the int holding the expected sequence number
+  unsigned long long limit_ns;
+};
+
+// Expert-parallel fusion of the grouped GEMM (all-to-all dispatch -> fc1, fc2 -> return).
+struct GemmEp {
+  void* base[8];              // heap base of every rank
+  int world, rank;
+  const int* gate_flags;      // this rank's int flags[world]: activations may be read once every flag has reached
+                              // *seq_ptr + 1 (the senders' rows have landed); null = no gating
+  const int* seq_ptr;         // this rank's count of completed expert-parallel calls
+  const int* row_ret;         // kEpiReturn: per sorted row (source rank << 24) | row in that rank's return buffer
+  long long ret_offset;       // kEpiReturn: byte offset of the return buffer [rows, ldo] bf16 in every heap
+  int* done_counter;          // kEpiReturn: this rank's int, zero between launches
+  long long ret_flag_offset;  // kEpiReturn: byte offset of int flags[world] in every heap
   unsigned long long limit_ns;
 };
 
@@ -59,6 +76,7 @@ struct GemmArgs {
   const int* grp_cnt;
   int grp_rows_a, grp_experts, grp_chunks;
   const GemmPeer* peer;     // null = no peer fusion
+  const GemmEp* ep = nullptr;   // null = no expert-parallel fusion (grouped mode only)
 };
 
 // Returns cudaSuccess or the launch error. Tensor maps are built (and cached) inside.

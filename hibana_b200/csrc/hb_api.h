@@ -23,6 +23,28 @@ int hb_gemm_peer(int kind, const void* a, const void* b, const void* sfa, const 
                  int world, int rank, int rows_per_rank, long long stage_offset, long long counter_offset,
                  long long flag_offset, long long seq_offset, long long limit_ns, void* status, int ka_a, int ka_b,
                  void* stream);
+int hb_gemm_grouped_ep(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int experts,
+                       int n_per_expert, int b_rows, int k, void* out, long long ldo, const void* alpha_ptr,
+                       int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status,
+                       int ka_a, int ka_b, const void* const* bases, int world, int rank, const void* gate_flags,
+                       const void* seq_ptr, const void* row_ret, long long ret_offset, void* done_counter,
+                       long long ret_flag_offset, long long limit_ns, void* stream);
+// Expert-parallel all-to-all (csrc/ep.cu); heaps come from hb_comm_alloc / hb_comm_ipc_open.
+int hb_ep_ctrl_bytes(void);
+void hb_ep_ctrl_layout(long long* out4);
+int hb_ep_count(const void* ids, int pairs, int experts, const void* const* bases, int world, int rank,
+                long long cnt_mat_off, void* stream);
+int hb_ep_plan(const void* ids, int pairs, int experts, const void* const* bases, int world, int rank,
+               long long cnt_mat_off, int rows_cap, void* grp_cnt, void* grp_start, void* total_rows, void* dst_rank,
+               void* dst_row, long long limit_ns, void* status, void* stream);
+int hb_ep_dispatch(const void* x, long long ldx, int tokens, int topk, int h, int ka, const void* dst_rank,
+                   const void* dst_row, const void* gscale, const void* const* bases, int world, int rank,
+                   long long q_off, long long sf_off, long long bf_off, long long row_ret_off, void* stream);
+int hb_ep_combine(const void* weights, const void* dst_rank, const void* shared, long long ld_shared, void* out,
+                  long long ldo, int tokens, int topk, int h, const void* const* bases, int world, int rank,
+                  long long ret_off, long long limit_ns, void* status, void* stream);
+int hb_kv_copy(void* pool, void* payload, const void* slots, int tokens, int layers, int kv_heads,
+               long long slots_dim, int d, int esize, int to_pool, void* stream);
 void hb_clear_tmap_cache(void);
 // GEMM launches use programmatic dependent launch (weight prefetch overlaps the preceding kernel) when on.
 void hb_gemm_set_pdl(int on);

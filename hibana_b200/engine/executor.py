@@ -57,6 +57,8 @@ class Executor:
         buckets = buckets or tuple(b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_batch)
         self.runner = ModelRunner(model, self.kv, max_batch=max_batch, max_ctx=max_ctx, buckets=buckets,
                                   use_graphs=use_graphs, comm=comm, attn_splits=attn_splits, state_pool=state_pool)
+        self.comm = comm
+        self.ssd = None
         self.state = StateManager(self.kv, state_pool, cache=radix_cache, decode_reserve=decode_reserve)
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "prefill_chunks": 0,
                       "cached_tokens": 0}
@@ -79,8 +81,30 @@ class Executor:
     def can_admit(self, req: Request) -> bool:
         return bool(self.runner._free_rows) and self.state.can_admit(req)
 
+    def enable_ssd_tier(self, directory: str, *, budget_bytes: int = 200 << 30, min_prefix: Optional[int] = None,
+                        min_gain: Optional[int] = None, identity: Optional[dict] = None) -> None:
+        """Long prefixes are backed up to `directory` when a request is released and restored on admission when
+        that gains enough tokens over the GPU cache (cache/ssd.py). With tensor parallelism every rank stores its
+        own heads and the ranks agree on how far a restore got."""
+        from ..cache import ssd, ssd_store
+        t = self.model.target
+        ident = {"target": t.name, "layers": len(t.layers), "kv_heads": t.kv_heads, "head_dim": t.head_dim,
+                 "kv_dtype": str(self.kv.dtype), "kv_bytes_per_token": self.kv.bytes_per_token,
+                 "weight_format": getattr(t, "weight_format", ""),
+                 "tp_rank": self.comm.rank if self.comm is not None else 0,
+                 "tp_size": self.comm.world if self.comm is not None else 1}
+        ident.update(identity or {})
+        store = ssd_store.SsdStore(directory, ident, budget_bytes=budget_bytes)
+        agree = (lambda n: self.comm.min_int(n)) if self.comm is not None else None
+        self.ssd = ssd.SsdTier(store, self.kv, min_prefix=ssd.MIN_PREFIX if min_prefix is None else min_prefix,
+                               min_gain=ssd.MIN_GAIN if min_gain is None else min_gain, agree=agree)
+
     def admit(self, req: Request) -> None:
         """Takes a block-table row (and, with a cache, the matched prefix) for the request."""
+        if getattr(self, "ssd", None) is not None and req.cacheable:
+            self.ssd.step()
+            got = self.state.restore_from_ssd(req.all_ids if req.output_ids else req.prompt_ids, self.ssd)
+            self.stats["ssd_restored_tokens"] = self.stats.get("ssd_restored_tokens", 0) + got
         req.table_row = self.runner.alloc_row()
         try:
             self.state.admit(req)
@@ -97,6 +121,10 @@ class Executor:
     def release(self, req: Request) -> None:
         if req.table_row < 0:
             return
+        if getattr(self, "ssd", None) is not None and req.cacheable and req.reserved == 0:
+            n = req.committed_len
+            self.ssd.backup(req.all_ids[:n], req.kv_slots[:n])
+            self.ssd.step()
         self.state.release(req)
         if self.spec is not None:
             self.spec.release(req)

@@ -1,0 +1,88 @@
+"""Expert-parallel all-to-all (parallel/ep.py): fused peer-memory path vs the NCCL counterpart vs a CPU oracle."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from hibana_b200.ops import moe
+
+WORKER = r"""
+import os, sys, json, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["HB_ROOT"])
+from hibana_b200 import _native as nv
+from hibana_b200.ops import moe
+from hibana_b200.parallel.ep import ExpertParallel
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+res = {}
+for fmt, act, E, topk, H, I, toks in (("nvfp4", "swiglu", 16, 4, 256, 128, (37, 50)), ("bf16", "relu2", 8, 2, 128, 64, (5, 0)),
+                                      ("nvfp4", "swiglu", 64, 6, 512, 256, (300, 290))):
+    g = torch.Generator().manual_seed(3)
+    n1 = 2 * I if act == "swiglu" else I
+    fc1 = torch.randn(E, n1, H, generator=g) * 0.05
+    fc2 = torch.randn(E, H, I, generator=g) * 0.05
+    e_per = E // world
+    ew = moe.ExpertWeights.create(fc1[rank * e_per:(rank + 1) * e_per].to(dev), fc2[rank * e_per:(rank + 1) * e_per].to(dev), act, fmt)
+    full = moe.ExpertWeights.create(fc1.to(dev), fc2.to(dev), act, fmt)
+    ep = ExpertParallel.create(rank, world, dev, tokens=max(toks), topk=topk, experts=E, hidden=H, fmt=fmt)
+    outs = []
+    for call in range(3):                      # consecutive calls reuse the single buffers
+        gt = torch.Generator().manual_seed(100 * rank + call)
+        t = toks[rank]
+        x = (torch.randn(t, H, generator=gt)).bfloat16().to(dev)
+        ids, w = moe.route(torch.randn(t, E, generator=gt).to(dev), topk) if t else (torch.empty(0, topk, dtype=torch.int32, device=dev), torch.empty(0, topk, device=dev))
+        shared = torch.randn(t, H, generator=gt).bfloat16().to(dev) if call == 1 else None
+        a = ep.forward(x, ids, w, ew, shared=shared)
+        b = ep.forward_nccl(x, ids, w, ew, shared=shared)
+        c = moe.experts_forward(x, ids, w, full, shared=shared) if t else a   # all experts on one GPU
+        torch.cuda.synchronize()
+        def err(u, v):
+            return float((u.float() - v.float()).abs().max() / v.float().abs().max().clamp_min(1e-6)) if u.numel() else 0.0
+        outs.append([err(a, b), err(a, c)])
+    res[f"{fmt}-{act}-{E}"] = outs
+res["status"] = nv.read_status(dev)
+gathered = [None] * world
+dist.all_gather_object(gathered, res)
+if rank == 0:
+    print("RESULT " + json.dumps(gathered), flush=True)
+dist.barrier()
+torch.cuda.synchronize()
+os._exit(0)
+"""
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_ep_all_to_all_matches_nccl_and_single_gpu(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, HB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), NCCL_NVLS_ENABLE="0")
+    proc = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                           "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
+                          capture_output=True, text=True, env=env, timeout=240)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    line = [l for l in proc.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    ranks = json.loads(line[len("RESULT "):])
+    for r in ranks:
+        assert r.pop("status") == 0
+        for name, outs in r.items():
+            for e_nccl, e_single in outs:
+                assert e_nccl < 3e-2 and e_single < 3e-2, (name, outs)
+
+
+def test_layout_is_aligned_and_disjoint():
+    from hibana_b200 import _native as nv
+    if not nv.available():
+        pytest.skip("native library not built")
+    from hibana_b200.parallel.ep import ExpertParallel
+    off, total = ExpertParallel.plan_layout(8, 64, 10, 512, 2560, 2560, "nvfp4", 8192)
+    vals = sorted(off.values())
+    assert all(v % 1024 == 0 for v in vals) and vals[0] >= 128 and total > vals[-1]
+    assert len({v for k, v in off.items() if k != "recv_bf"}) == len(off) - 1   # only the unused buffer aliases
