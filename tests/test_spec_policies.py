@@ -1,0 +1,100 @@
+"""Sampled acceptance (rejection sampling), relaxed greedy acceptance, depth policies, the n-gram proposer."""
+import math
+
+import pytest
+import torch
+
+from hibana_b200.engine import depth as dp
+from hibana_b200.engine import rejection as rj
+from hibana_b200.engine.contracts import Capabilities, ProposerRequirements, check_capabilities
+from hibana_b200.proposers import make_proposer
+
+
+def test_distribution_truncation():
+    lg = torch.tensor([[2.0, 1.0, 0.0, -1.0], [0.0, 0.0, 5.0, 0.0]])
+    d = rj.distribution(lg, temperature=1.0, top_k=2)
+    assert torch.count_nonzero(d[0]) == 2 and abs(float(d[0].sum()) - 1) < 1e-6
+    d = rj.distribution(lg, temperature=torch.tensor([1.0, 0.0]), top_k=0, top_p=torch.tensor([0.7, 1.0]))
+    assert torch.count_nonzero(d[0]) == 2          # 0.64 + the token that crosses 0.7
+    assert d[1].tolist() == [0, 0, 1, 0]           # temperature 0 = argmax
+
+
+def test_batch_matches_row_rule():
+    g = torch.Generator().manual_seed(0)
+    b, k, v = 64, 4, 50
+    p = rj.distribution(torch.randn(b * (k + 1), v, generator=g) * 2, 0.9, 20, 0.95).view(b, k + 1, v)
+    q = rj.distribution(torch.randn(b * k, v, generator=g) * 2, 1.0).view(b, k, v)
+    drafts = torch.multinomial(q.view(-1, v), 1, generator=g).view(b, k)
+    u = torch.rand(b, k + 1, generator=g)
+    ru = torch.rand(b, k + 1, generator=g)
+    for soft in (0.0, 0.5):
+        ver = rj.verify_batch(p, q, drafts, u, ru, soft=soft)
+        for i in range(b):
+            em, acc = rj.verify_row(list(p[i]), list(q[i]), drafts[i].tolist(), u[i].tolist(), ru[i].tolist(), soft)
+            assert int(ver.accepted[i]) == acc and ver.emitted[i, :acc + 1].tolist() == em
+    # slack can only accept more
+    assert int(rj.verify_batch(p, q, drafts, u, ru, 0.5).accepted.sum()) >= int(rj.verify_batch(p, q, drafts, u, ru).accepted.sum())
+
+
+def test_speculative_sampling_preserves_the_target_law():
+    """First emitted token ~ p_0 whatever the draft law is (the defining property)."""
+    g = torch.Generator().manual_seed(1)
+    v, n = 6, 40000
+    p0 = torch.tensor([0.4, 0.25, 0.15, 0.1, 0.07, 0.03])
+    q1 = torch.tensor([0.05, 0.05, 0.3, 0.3, 0.2, 0.1])
+    p = torch.stack([p0, torch.full((v,), 1 / v)]).expand(n, 2, v).contiguous()
+    q = q1.expand(n, 1, v).contiguous()
+    drafts = torch.multinomial(q1, n, replacement=True, generator=g).view(n, 1)
+    ver = rj.verify_batch(p, q, drafts, torch.rand(n, 2, generator=g), torch.rand(n, 2, generator=g))
+    freq = torch.bincount(ver.emitted[:, 0], minlength=v).float() / n
+    assert float((freq - p0).abs().max()) < 0.012
+    assert 0.3 < float(ver.accepted.float().mean()) < 0.7      # sum min(p, q) = 0.5
+
+
+def test_relaxed_greedy():
+    rank = torch.tensor([[0, 1, 3], [2, 0, 1]])
+    gap = torch.tensor([[0.0, 0.4, 0.1], [0.2, 0.0, 2.0]])
+    got = rj.relaxed_greedy(rank, gap, top_k=3, margin=0.5)
+    assert got.tolist() == [[True, True, False], [True, True, False]]
+    assert rj.relaxed_greedy(rank, gap, top_k=1, margin=0.0).tolist() == [[True, False, False], [False, True, False]]
+
+
+class _Req:
+    def __init__(self, rid, ids=()):
+        self.rid, self.all_ids = rid, list(ids)
+
+
+def test_depth_policies():
+    assert dp.parse_depths("8:4, 1:6,32:2") == [(1, 6), (8, 4), (32, 2)]
+    with pytest.raises(ValueError):
+        dp.parse_depths("4")
+    bd = dp.BatchDepth("1:6,8:4,32:0")
+    assert [bd.depth_for(n) for n in (1, 7, 8, 31, 32, 200)] == [6, 6, 4, 4, 0, 0]
+    ad = dp.AcceptanceDepth(max_depth=8, row_cost=0.3)
+    r = _Req(1)
+    d0 = ad.depth_for(r)
+    for _ in range(40):
+        ad.observe(r, 4, 0)                      # always rejected at the first position
+    low = ad.depth_for(r)
+    for _ in range(80):
+        ad.observe(r, 4, 4)
+    high = ad.depth_for(r)
+    assert low < d0 < high <= 8 and low >= 1
+    assert abs(dp.expected_tokens(0.5, 3) - 1.875) < 1e-9
+    rb = dp.RowBudget(rows=8)
+    kept = rb.choose([[0.9, 0.9, 0.9, 0.9], [0.5, 0.1, 0.1, 0.1], [0.95, 0.2, 0.9, 0.9]])
+    assert sum(kept) == 8 - 3 and kept == [4, 0, 1]      # 0.9^4 = 0.656 still beats 0.5
+    assert dp.ragged_budgets(4, 16, 8) == 3
+
+
+def test_ngram_proposer_and_capabilities():
+    pr = make_proposer("ngram")
+    seq = [5, 6, 7, 8, 9, 1, 2, 5, 6, 7]
+    out = pr.propose([_Req(1, seq), _Req(2, [1, 2, 3])], 3)
+    assert out.tokens[0].tolist() == [8, 9, 1] and out.lengths == [3, 0]
+    assert float(out.scores[1].sum()) == 0.0
+    check_capabilities(pr.capabilities, ProposerRequirements(row_budget=True, depth=8))
+    with pytest.raises(ValueError):
+        check_capabilities(Capabilities(max_depth=4), ProposerRequirements(depth=6, row_budget=True))
+    with pytest.raises(ValueError):
+        make_proposer("nope")
