@@ -20,7 +20,7 @@ torch.cuda.set_device(rank)
 dev = torch.device("cuda", rank)
 dist.init_process_group("nccl", device_id=dev)
 res = {}
-for fmt, act, E, topk, H, I, toks in (("nvfp4", "swiglu", 16, 4, 256, 128, (37, 50)), ("bf16", "relu2", 8, 2, 128, 64, (5, 0)),
+for fmt, act, E, topk, H, I, toks in (("nvfp4", "swiglu", 16, 4, 256, 128, (37, 50)), ("bf16", "relu2", 8, 2, 128, 128, (5, 0)),
                                       ("nvfp4", "swiglu", 64, 6, 512, 256, (300, 290))):
     g = torch.Generator().manual_seed(3)
     n1 = 2 * I if act == "swiglu" else I
