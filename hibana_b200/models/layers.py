@@ -259,7 +259,26 @@ def _moe_forward_ep(self, x, comm) -> torch.Tensor:
     return out
 
 
+def _moe_forward_a2a(self, x, ep) -> torch.Tensor:
+    """All-to-all expert parallelism (parallel/ep.py): `x` holds THIS rank's tokens only (attention ran data- or
+    sequence-parallel); rows travel to the owners of their experts and the results come back. Every rank must
+    call it, with an empty batch when it has no tokens."""
+    t = self.t
+    if getattr(self, "_local_experts", None) is None:
+        self._local_experts = self.experts.slice(ep.rank * ep.e_per, ep.e_per)
+    logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
+    ids, w = moe.route(logits, t.top_k, sigmoid=t.router == "sigmoid", sel_bias=self.sel_bias, renorm=True,
+                       scale=t.router_scale)
+    shared = self.shared.forward(x) if self.shared is not None and x.shape[0] else None
+    if t.latent:
+        y = ep.forward(self.fc1_latent(x), ids, w, self._local_experts)
+        out = self.fc2_latent(y)
+        return basic.add(out, shared) if shared is not None else out
+    return ep.forward(x, ids, w, self._local_experts, shared=shared)
+
+
 MoeLayer.forward_ep = _moe_forward_ep
+MoeLayer.forward_a2a = _moe_forward_a2a
 
 
 def build_mixer(kind: str, t: Target, init: Init, counters: dict, name: str):

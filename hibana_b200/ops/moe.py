@@ -119,6 +119,21 @@ class ExpertWeights:
     def fc2_rows(self) -> int:
         return (self.fc2.shape[0] if self.fmt == "bf16" else self.fc2.rows) // self.experts
 
+    def slice(self, e_lo: int, e_n: int) -> "ExpertWeights":
+        """The experts [e_lo, e_lo + e_n) as views (what one expert-parallel rank keeps)."""
+        n1, n2 = self.n1, self.fc2_rows
+
+        def rows(w, n):
+            if self.fmt == "bf16":
+                return w[e_lo * n:(e_lo + e_n) * n]
+            assert n % 128 == 0, "scale blocks cover 128 rows: expert boundaries must fall on them"
+            return nvfp4.Nvfp4Tensor(w.q[e_lo * n:(e_lo + e_n) * n], w.sf[e_lo * n // 128:(e_lo + e_n) * n // 128],
+                                     w.gscale[e_lo:e_lo + e_n], e_n * n, w.k)
+
+        cut = (lambda v: v[e_lo:e_lo + e_n].contiguous()) if self.fmt != "bf16" else (lambda v: v)
+        return ExpertWeights(e_n, self.hidden, self.inter, self.act, self.fmt, rows(self.fc1, n1), rows(self.fc2, n2),
+                             cut(self.fc1_alpha), cut(self.fc2_alpha), self.fc1_in_scale, self.fc2_in_scale)
+
     def to(self, device) -> "ExpertWeights":
         def mv(x):
             if isinstance(x, nvfp4.Nvfp4Tensor):
