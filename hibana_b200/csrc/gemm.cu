@@ -5,6 +5,9 @@
 //                  256-element (128-byte) K tiles; scale factors travel global -> shared by bulk copies of the
 //                  128x4-swizzled blocks and shared -> TMEM by tcgen05.cp.
 //
+//   * kind fp8   : tcgen05.mma kind::f8f6f4 on e4m3 operands, 128-element (128-byte) K tiles; per-tensor scales
+//                  fold into alpha, a per-token scale vector (dynamic activation quantisation) into the epilogue.
+//
 // One CTA computes a 128 x BN tile. Warp 0 issues TMA loads into a ring of 128-byte-swizzled stages, one lane
 // of warp 1 issues the MMAs and commits stage releases, warps 2-5 read the accumulator back with tcgen05.ld
 // and run the epilogue. With `swap` the 128-row operand is the weight matrix and the (few) tokens sit on the
@@ -81,6 +84,7 @@ struct DevParams {
   const int* ep_row_ret;
   long long ep_ret_offset, ep_ret_flag_offset;
   int* ep_done;
+  const float* tok_scale;
 };
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
@@ -92,6 +96,10 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
                                                int col_lim, float alpha, int lane) {
   const bool row_ok = row < row_lim;
   if (p.swap) {
+    if (p.tok_scale != nullptr) {   // tokens are the columns here
+#pragma unroll
+      for (int j = 0; j < CH; ++j) v[j] *= col0 + j < col_lim ? p.tok_scale[col0 + j] : 0.f;
+    }
     // out[token = col][feature = row]; lanes are consecutive features -> coalesced per token.
     if (p.epilogue == kEpiSiluMul) {
       __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
@@ -278,7 +286,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         const int s = i % S;
         uint8_t* st = smem + s * C::STAGE_BYTES;
         const int kt = kt0 + i;
-        const int kx = KIND == kGemmNvfp4 ? kt * 128 : kt * 64;
+        const int kx = KIND == kGemmBf16 ? kt * 64 : kt * 128;
         if (side == 0) {
           tma_load_2d(st, &tma, &full[s], kx, a_row0);
           if constexpr (KIND == kGemmNvfp4)
@@ -367,7 +375,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = KIND == kGemmNvfp4 ? make_idesc_nvf4(BM, BN) : make_idesc_bf16(BM, BN);
+      constexpr uint32_t idesc = KIND == kGemmNvfp4 ? make_idesc_nvf4(BM, BN)
+                                 : KIND == kGemmFp8 ? make_idesc_e4m3(BM, BN) : make_idesc_bf16(BM, BN);
       const uint32_t sfa_t = tmem_base + BN;
       const uint32_t sfb_t = sfa_t + 16;
       bool ok = true;
@@ -396,6 +405,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
           for (int kb = 0; kb < 4; ++kb)
             mma_nvf4(tmem_base, adesc + kb * 2, bdesc + kb * 2, idesc, (i > 0 || kb > 0) ? 1u : 0u,
                      sfa_t + kb * 4, sfb_t + kb * 4 * C::NRB);
+        } else if constexpr (KIND == kGemmFp8) {
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb)
+            mma_f8(tmem_base, adesc + kb * 2, bdesc + kb * 2, idesc, (i > 0 || kb > 0) ? 1u : 0u);
         } else {
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb)
@@ -414,6 +427,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     const uint32_t tlane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     float alpha = p.alpha;
     if (alpha_ptr != nullptr) alpha *= *alpha_ptr;
+    if (p.tok_scale != nullptr && !p.swap && row < row_lim) alpha *= p.tok_scale[row];   // tokens are the rows
     if (ok && p.splits == 1 && !p.swap && p.epilogue != kEpiStoreF32 && BN >= 64 && (p.rb & 7) == 0 &&
         (p.ldo & 7) == 0) {
       // Staged epilogue (tokens on the 128-row side): every thread parks its row chunk as bf16 in shared memory
@@ -528,6 +542,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
       const int row = tile_a * BM + lrow;
       float alpha = p.alpha;
       if (alpha_ptr != nullptr) alpha *= *alpha_ptr;
+      if (p.tok_scale != nullptr && !p.swap && row < row_lim) alpha *= p.tok_scale[row];
       const int ncols = min(BN, col_lim - b_row0);
       int per = (ncols + p.splits - 1) / p.splits;
       if (!p.swap) per = (per + 15) & ~15;      // feature pairs and 16-byte stores stay inside one slice
@@ -693,9 +708,10 @@ int gemm_num_tiles(const GemmArgs& a) { return ((a.ra + BM - 1) / BM) * ((a.rb +
 
 cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   const bool fp4 = a.kind == kGemmNvfp4;
+  const bool fp8 = a.kind == kGemmFp8;
   if (a.ra <= 0 || a.rb <= 0 || a.k <= 0) return cudaErrorInvalidValue;
-  if (fp4 ? (a.k % 32 != 0) : (a.k % 8 != 0)) return cudaErrorInvalidValue;
-  const int kt_elems = fp4 ? 256 : 64;
+  if (fp4 ? (a.k % 32 != 0) : fp8 ? (a.k % 16 != 0) : (a.k % 8 != 0)) return cudaErrorInvalidValue;
+  const int kt_elems = fp4 ? 256 : fp8 ? 128 : 64;
   const int k_tiles = (a.k + kt_elems - 1) / kt_elems;
   const int tiles_a = (a.ra + BM - 1) / BM;
   const int tiles_b = (a.rb + a.bn - 1) / a.bn;
@@ -711,12 +727,14 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   while (splits > 1 && (splits - 1) * ((k_tiles + splits - 1) / splits) >= k_tiles) --splits;
   if (splits > 8) splits = 8;   // portable cluster size
 
+  // byte-typed maps (packed e2m1 or e4m3): inner extent and pitch in bytes, 128-byte boxes
+  const bool bytes = fp4 || fp8;
   TmapKey ka{a.a, static_cast<uint64_t>(a.ra), static_cast<uint64_t>(fp4 ? a.k / 2 : a.k),
-             static_cast<uint64_t>(fp4 ? a.lda / 2 : a.lda * 2), static_cast<uint32_t>(BM),
-             static_cast<uint32_t>(fp4 ? 128 : 64), fp4 ? 1 : 0};
+             static_cast<uint64_t>(fp4 ? a.lda / 2 : fp8 ? a.lda : a.lda * 2), static_cast<uint32_t>(BM),
+             static_cast<uint32_t>(bytes ? 128 : 64), bytes ? 1 : 0};
   TmapKey kb{a.b, static_cast<uint64_t>(a.rb), static_cast<uint64_t>(fp4 ? a.k / 2 : a.k),
-             static_cast<uint64_t>(fp4 ? a.ldb / 2 : a.ldb * 2), static_cast<uint32_t>(a.bn),
-             static_cast<uint32_t>(fp4 ? 128 : 64), fp4 ? 1 : 0};
+             static_cast<uint64_t>(fp4 ? a.ldb / 2 : fp8 ? a.ldb : a.ldb * 2), static_cast<uint32_t>(a.bn),
+             static_cast<uint32_t>(bytes ? 128 : 64), bytes ? 1 : 0};
   const CUtensorMap* ta = get_tmap_2d(ka);
   const CUtensorMap* tb = get_tmap_2d(kb);
   if (ta == nullptr || tb == nullptr) return cudaErrorInvalidValue;
@@ -745,6 +763,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   } else if (a.epilogue == kEpiScatter) {
     return cudaErrorInvalidValue;
   }
+  p.tok_scale = a.tok_scale;
   p.ep_gate_flags = nullptr; p.ep_seq_ptr = nullptr; p.ep_row_ret = nullptr; p.ep_done = nullptr;
   p.ep_ret_offset = 0; p.ep_ret_flag_offset = 0;
   if (a.ep != nullptr) {
@@ -770,6 +789,8 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   }
   if (fp4) {
     HB_DISPATCH(kGemmNvfp4)
+  } else if (fp8) {
+    HB_DISPATCH(kGemmFp8)
   } else {
     HB_DISPATCH(kGemmBf16)
   }
@@ -875,6 +896,23 @@ int hb_gemm_grouped_ep(int kind, const void* a, const void* b, const void* sfa, 
   g.grp_rows_a = n_per_expert; g.grp_experts = experts; g.grp_chunks = (max_rows_per_expert + bn - 1) / bn;
   g.peer = nullptr;
   g.ep = &ep;
+  const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// e4m3 x e4m3 GEMM: out = alpha * (*alpha_ptr) * tok_scale[token] * A B^T. lda / ldb in elements (= bytes).
+int hb_gemm_fp8(const void* a, const void* b, int ra, int rb, int k, long long lda, long long ldb, void* out,
+                long long ldo, const void* residual, float alpha, const void* alpha_ptr, const void* tok_scale,
+                int epilogue, int swap, int splits, void* status, int bn, void* stream) {
+  hb::GemmArgs g;
+  g.kind = hb::kGemmFp8; g.a = a; g.b = b; g.sfa = nullptr; g.sfb = nullptr; g.ra = ra; g.rb = rb; g.k = k;
+  g.lda = lda; g.ldb = ldb; g.out = out; g.ldo = ldo; g.residual = residual; g.alpha = alpha;
+  g.alpha_ptr = static_cast<const float*>(alpha_ptr); g.epilogue = epilogue; g.swap = swap; g.splits = splits;
+  g.workspace = nullptr; g.counters = nullptr; g.status = static_cast<int*>(status); g.bn = bn;
+  g.sf_k_atoms_a = 0; g.sf_k_atoms_b = 0;
+  g.grp_start = nullptr; g.grp_cnt = nullptr; g.grp_rows_a = 0; g.grp_experts = 0; g.grp_chunks = 0;
+  g.peer = nullptr;
+  g.tok_scale = static_cast<const float*>(tok_scale);
   const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

@@ -6,7 +6,7 @@
 
 namespace hb {
 
-enum GemmKind : int { kGemmBf16 = 0, kGemmNvfp4 = 1 };
+enum GemmKind : int { kGemmBf16 = 0, kGemmNvfp4 = 1, kGemmFp8 = 2 };   // fp8 = e4m3 x e4m3, 128-element K tiles
 enum GemmEpilogue : int {
   kEpiStore = 0,      // out = alpha * acc                      (bf16)
   kEpiResidual = 1,   // out = alpha * acc + residual           (bf16)
@@ -77,6 +77,8 @@ struct GemmArgs {
   int grp_rows_a, grp_experts, grp_chunks;
   const GemmPeer* peer;     // null = no peer fusion
   const GemmEp* ep = nullptr;   // null = no expert-parallel fusion (grouped mode only)
+  const float* tok_scale = nullptr;   // optional per-token factor (dynamic per-row activation scale): indexed by
+                                      // the token, i.e. the B row with `swap`, else the A row
 };
 
 // Returns cudaSuccess or the launch error. Tensor maps are built (and cached) inside.

@@ -45,6 +45,9 @@ int hb_ep_combine(const void* weights, const void* dst_rank, const void* shared,
                   long long ret_off, long long limit_ns, void* status, void* stream);
 int hb_kv_copy(void* pool, void* payload, const void* slots, int tokens, int layers, int kv_heads,
                long long slots_dim, int d, int esize, int to_pool, void* stream);
+int hb_gemm_fp8(const void* a, const void* b, int ra, int rb, int k, long long lda, long long ldb, void* out,
+                long long ldo, const void* residual, float alpha, const void* alpha_ptr, const void* tok_scale,
+                int epilogue, int swap, int splits, void* status, int bn, void* stream);
 void hb_clear_tmap_cache(void);
 // GEMM launches use programmatic dependent launch (weight prefetch overlaps the preceding kernel) when on.
 void hb_gemm_set_pdl(int on);

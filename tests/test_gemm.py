@@ -145,3 +145,29 @@ def test_gemm_nvfp4_epilogues_and_splitk_deterministic():
         for y in (y1, y3):
             assert (y.float() - ref.float()).abs().max() <= 2e-2 * ref.float().abs().max() + 1e-3
     assert nv.read_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(1, 512, 1024), (4, 1280, 2560), (64, 768, 1152), (300, 640, 512), (2048, 1024, 2048)])
+@pytest.mark.parametrize("dynamic", [False, True])
+def test_fp8_gemm_matches_reference(m, n, k, dynamic):
+    """e4m3 x e4m3 on tcgen05 (kind::f8f6f4) vs the fp32 product of the dequantised operands."""
+    from hibana_b200.ops import fp8
+    g = torch.Generator().manual_seed(m + n)
+    x = (torch.randn(m, k, generator=g) * 1.5).bfloat16()
+    w = fp8.Fp8Weight.quantize(torch.randn(n, k, generator=g) * 0.05)
+    wc = fp8.Fp8Weight(w.q.cuda(), w.scale.cuda())
+    if dynamic:
+        q_ref, s_ref = fp8.quantize_rows(x)
+        q, s = fp8.quantize_rows(x.cuda())
+        assert torch.allclose(s.cpu(), s_ref, rtol=1e-3)
+        ref = fp8.linear_fp8(q.cpu(), w, row_scales=s.cpu())
+        got = fp8.linear_fp8(q, wc, row_scales=s)
+    else:
+        scale = torch.tensor([float(x.float().abs().max()) / 448.0])
+        q = fp8.quantize_static(x.cuda(), scale.cuda())
+        assert torch.equal(q.cpu().float(), fp8.quantize_static(x, scale).float())
+        ref = fp8.linear_fp8(q.cpu(), w, x_scale=scale)
+        got = fp8.linear_fp8(q, wc, x_scale=scale.cuda())
+    err = (got.float().cpu() - ref.float()).abs().max() / ref.float().abs().max()
+    assert float(err) < 1e-2, float(err)
