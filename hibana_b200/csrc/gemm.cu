@@ -7,6 +7,12 @@
 //
 //   * kind fp8   : tcgen05.mma kind::f8f6f4 on e4m3 operands, 128-element (128-byte) K tiles; per-tensor scales
 //                  fold into alpha, a per-token scale vector (dynamic activation quantisation) into the epilogue.
+//   * kind w3    : the A operand is a 3-bit weight copy (asymmetric integer codes, groups of 64 along K, bf16 scale
+//                  and zero per row and group) stored as one 4096-byte tile per (128 rows, 64 columns). A bulk copy
+//                  brings the tile into the stage, the four epilogue warps (one thread per row) expand it to the
+//                  128-byte-swizzled bf16 A tile of the same stage - two codes per logic op through the bf16 bit
+//                  pattern of 128 + code, then one packed subtract and one packed fma - and the MMA is kind::f16.
+//                  HBM sees 4 bits per weight; the tensor cores see bf16.
 //
 // One CTA computes a 128 x BN tile. Warp 0 issues TMA loads into a ring of 128-byte-swizzled stages, one lane
 // of warp 1 issues the MMAs and commits stage releases, warps 2-5 read the accumulator back with tcgen05.ld
@@ -44,7 +50,9 @@ struct Cfg {
   static constexpr int NRB = (BN + 127) / 128;
   static constexpr int SFA_BYTES = KIND == kGemmNvfp4 ? 4 * 512 : 0;
   static constexpr int SFB_BYTES = KIND == kGemmNvfp4 ? NRB * 4 * 512 : 0;
-  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int PACK_BYTES = KIND == kGemmW3 ? 4096 : 0;   // packed 3-bit tile, behind the operand tiles
+  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + SFA_BYTES + SFB_BYTES + PACK_BYTES;
+  static constexpr int TX_BYTES = KIND == kGemmW3 ? B_TILE_BYTES + PACK_BYTES : STAGE_BYTES;   // bytes copies deliver
   static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TMEM_NEED = BN + (KIND == kGemmNvfp4 ? 16 + 16 * NRB : 0);
@@ -85,6 +93,7 @@ struct DevParams {
   long long ep_ret_offset, ep_ret_flag_offset;
   int* ep_done;
   const float* tok_scale;
+  const uint8_t* w3_tiles;   // kind w3: [row blocks][k_tiles][4096]
 };
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
@@ -229,7 +238,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * C::STAGE_BYTES);
   uint64_t* empty = full + S;
-  uint64_t* accum = empty + S;
+  uint64_t* dq = empty + S;       // kind w3: the A tile of the stage has been expanded (128 arrivals)
+  uint64_t* accum = dq + S;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -262,6 +272,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+      mbar_init(&dq[s], 128);
     }
     mbar_init(accum, 1);
     *abort = 0;
@@ -286,8 +297,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         const int s = i % S;
         uint8_t* st = smem + s * C::STAGE_BYTES;
         const int kt = kt0 + i;
-        const int kx = KIND == kGemmBf16 ? kt * 64 : kt * 128;
+        const int kx = (KIND == kGemmBf16 || KIND == kGemmW3) ? kt * 64 : kt * 128;
         if (side == 0) {
+          if constexpr (KIND == kGemmW3) {
+            bulk_load(st + A_TILE_BYTES + C::B_TILE_BYTES,
+                      p.w3_tiles + (static_cast<size_t>(a_row0 >> 7) * p.k_tiles + kt) * 4096, 4096, &full[s]);
+            return;
+          }
           tma_load_2d(st, &tma, &full[s], kx, a_row0);
           if constexpr (KIND == kGemmNvfp4)
             bulk_load(st + A_TILE_BYTES + C::B_TILE_BYTES,
@@ -309,7 +325,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
       const int wside = p.swap ? 0 : 1;
       const int pre = min(S, nkt);
       for (int i = 0; i < pre; ++i) {
-        mbar_expect_tx(&full[i], C::STAGE_BYTES);
+        mbar_expect_tx(&full[i], C::TX_BYTES);
         load_side(i, wside);
       }
       grid_dep_wait();
@@ -361,7 +377,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         const int s = i % S;
         const uint32_t ph = (i / S) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, abort, p.status, kTimeoutEmpty)) break;
-        mbar_expect_tx(&full[s], C::STAGE_BYTES);
+        mbar_expect_tx(&full[s], C::TX_BYTES);
         load_side(i, 0);
         load_side(i, 1);
         ++issued;
@@ -386,6 +402,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         if (!mbar_wait(&full[s], ph, abort, p.status, kTimeoutFull)) {
           ok = false;
           break;
+        }
+        if constexpr (KIND == kGemmW3) {
+          if (!mbar_wait(&dq[s], ph, abort, p.status, kTimeoutFull)) {
+            ok = false;
+            break;
+          }
         }
         tc_fence_after();
         uint8_t* st = smem + s * C::STAGE_BYTES;
@@ -420,6 +442,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     }
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    if constexpr (KIND == kGemmW3) {
+      // Expand the packed tile of every stage into its bf16 A tile: thread = row. Word w of the row's 28 code
+      // bytes holds codes 10 w + 2 i (low half, bits 3 i ..) and 10 w + 2 i + 1 (high half); OR-ing 0x4300 into
+      // both halves makes the bf16 numbers 128 + code, exact, so (x - 128) * scale + bias is two packed ops.
+      const int r = q * 32 + lane;
+      const __nv_bfloat162 k128 = __floats2bfloat162_rn(128.f, 128.f);
+      for (int i = 0; i < nkt; ++i) {
+        const int s = i % S;
+        if (!mbar_wait(&full[s], (i / S) & 1, abort, p.status, kTimeoutFull)) break;
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        const uint8_t* pk = st + A_TILE_BYTES + C::B_TILE_BYTES;
+        const uint32_t sz = *reinterpret_cast<const uint32_t*>(pk + 128 * 28 + r * 4);
+        __nv_bfloat162 sc2, bias2;
+        *reinterpret_cast<uint32_t*>(&sc2) = (sz & 0xFFFFu) | (sz << 16);
+        *reinterpret_cast<uint32_t*>(&bias2) = (sz >> 16) | (sz & 0xFFFF0000u);
+        uint32_t o[32];
+#pragma unroll
+        for (int w = 0; w < 7; ++w) {
+          const uint32_t x = *reinterpret_cast<const uint32_t*>(pk + r * 28 + w * 4);
+#pragma unroll
+          for (int j = 0; j < 5; ++j) {
+            if (w * 5 + j < 32) {
+              uint32_t m = ((x >> (3 * j)) & 0x00070007u) | 0x43004300u;
+              __nv_bfloat162 v = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&m), k128);
+              v = __hfma2(v, sc2, bias2);
+              o[w * 5 + j] = *reinterpret_cast<uint32_t*>(&v);
+            }
+          }
+        }
+        const uint32_t row_addr = smem_u32(st) + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + ((c ^ (r & 7)) << 4)),
+                       "r"(o[4 * c]), "r"(o[4 * c + 1]), "r"(o[4 * c + 2]), "r"(o[4 * c + 3])
+                       : "memory");
+        fence_proxy_async_smem();
+        mbar_arrive(&dq[s]);
+      }
+    }
     grid_dep_wait();
     const bool ok = nkt > 0 ? mbar_wait(accum, 0, abort, p.status, kTimeoutAccum) : true;
     tc_fence_after();
@@ -709,8 +770,10 @@ int gemm_num_tiles(const GemmArgs& a) { return ((a.ra + BM - 1) / BM) * ((a.rb +
 cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   const bool fp4 = a.kind == kGemmNvfp4;
   const bool fp8 = a.kind == kGemmFp8;
+  const bool w3 = a.kind == kGemmW3;
   if (a.ra <= 0 || a.rb <= 0 || a.k <= 0) return cudaErrorInvalidValue;
-  if (fp4 ? (a.k % 32 != 0) : fp8 ? (a.k % 16 != 0) : (a.k % 8 != 0)) return cudaErrorInvalidValue;
+  if (fp4 ? (a.k % 32 != 0) : fp8 ? (a.k % 16 != 0) : w3 ? (a.k % 64 != 0) : (a.k % 8 != 0)) return cudaErrorInvalidValue;
+  if (w3 && (!a.swap || a.grp_cnt != nullptr || a.peer != nullptr)) return cudaErrorInvalidValue;
   const int kt_elems = fp4 ? 256 : fp8 ? 128 : 64;
   const int k_tiles = (a.k + kt_elems - 1) / kt_elems;
   const int tiles_a = (a.ra + BM - 1) / BM;
@@ -735,8 +798,8 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   TmapKey kb{a.b, static_cast<uint64_t>(a.rb), static_cast<uint64_t>(fp4 ? a.k / 2 : a.k),
              static_cast<uint64_t>(fp4 ? a.ldb / 2 : fp8 ? a.ldb : a.ldb * 2), static_cast<uint32_t>(a.bn),
              static_cast<uint32_t>(bytes ? 128 : 64), bytes ? 1 : 0};
-  const CUtensorMap* ta = get_tmap_2d(ka);
   const CUtensorMap* tb = get_tmap_2d(kb);
+  const CUtensorMap* ta = w3 ? tb : get_tmap_2d(ka);   // the w3 A operand arrives by bulk copies, not through a map
   if (ta == nullptr || tb == nullptr) return cudaErrorInvalidValue;
 
   DevParams p;
@@ -764,6 +827,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   }
   p.tok_scale = a.tok_scale;
+  p.w3_tiles = w3 ? static_cast<const uint8_t*>(a.a) : nullptr;
   p.ep_gate_flags = nullptr; p.ep_seq_ptr = nullptr; p.ep_row_ret = nullptr; p.ep_done = nullptr;
   p.ep_ret_offset = 0; p.ep_ret_flag_offset = 0;
   if (a.ep != nullptr) {
@@ -791,6 +855,8 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     HB_DISPATCH(kGemmNvfp4)
   } else if (fp8) {
     HB_DISPATCH(kGemmFp8)
+  } else if (w3) {
+    HB_DISPATCH(kGemmW3)
   } else {
     HB_DISPATCH(kGemmBf16)
   }
@@ -913,6 +979,21 @@ int hb_gemm_fp8(const void* a, const void* b, int ra, int rb, int k, long long l
   g.grp_start = nullptr; g.grp_cnt = nullptr; g.grp_rows_a = 0; g.grp_experts = 0; g.grp_chunks = 0;
   g.peer = nullptr;
   g.tok_scale = static_cast<const float*>(tok_scale);
+  const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// Dequant-fused 3-bit GEMM: out[m, n] = alpha * sum_k x[m, k] * w[n, k] with w given as 4096-byte tiles
+// [ceil(n / 128)][k / 64] (see hibana_b200/weights/w3.py); x bf16 [m, k], m <= 256 (weights on the 128-row side).
+int hb_gemm_w3(const void* tiles, const void* x, int n, int m, int k, long long ldx, void* out, long long ldo,
+               const void* residual, float alpha, int epilogue, int splits, void* status, int bn, void* stream) {
+  hb::GemmArgs g;
+  g.kind = hb::kGemmW3; g.a = tiles; g.b = x; g.sfa = nullptr; g.sfb = nullptr; g.ra = n; g.rb = m; g.k = k;
+  g.lda = k; g.ldb = ldx; g.out = out; g.ldo = ldo; g.residual = residual; g.alpha = alpha; g.alpha_ptr = nullptr;
+  g.epilogue = epilogue; g.swap = 1; g.splits = splits; g.workspace = nullptr; g.counters = nullptr;
+  g.status = static_cast<int*>(status); g.bn = bn; g.sf_k_atoms_a = 0; g.sf_k_atoms_b = 0;
+  g.grp_start = nullptr; g.grp_cnt = nullptr; g.grp_rows_a = 0; g.grp_experts = 0; g.grp_chunks = 0;
+  g.peer = nullptr;
   const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

@@ -6,7 +6,13 @@
 
 namespace hb {
 
-enum GemmKind : int { kGemmBf16 = 0, kGemmNvfp4 = 1, kGemmFp8 = 2 };   // fp8 = e4m3 x e4m3, 128-element K tiles
+enum GemmKind : int {
+  kGemmBf16 = 0,
+  kGemmNvfp4 = 1,
+  kGemmFp8 = 2,   // e4m3 x e4m3, 128-element K tiles
+  kGemmW3 = 3,    // A = 3-bit asymmetric codes (groups of 64, bf16 scale + zero) in 4096-byte tiles, dequantised to
+                  // bf16 in shared memory by the CTA; B = bf16 activations; weights on the 128-row side only
+};
 enum GemmEpilogue : int {
   kEpiStore = 0,      // out = alpha * acc                      (bf16)
   kEpiResidual = 1,   // out = alpha * acc + residual           (bf16)

@@ -48,6 +48,8 @@ int hb_kv_copy(void* pool, void* payload, const void* slots, int tokens, int lay
 int hb_gemm_fp8(const void* a, const void* b, int ra, int rb, int k, long long lda, long long ldb, void* out,
                 long long ldo, const void* residual, float alpha, const void* alpha_ptr, const void* tok_scale,
                 int epilogue, int swap, int splits, void* status, int bn, void* stream);
+int hb_gemm_w3(const void* tiles, const void* x, int n, int m, int k, long long ldx, void* out, long long ldo,
+               const void* residual, float alpha, int epilogue, int splits, void* status, int bn, void* stream);
 void hb_clear_tmap_cache(void);
 // GEMM launches use programmatic dependent launch (weight prefetch overlaps the preceding kernel) when on.
 void hb_gemm_set_pdl(int on);

@@ -171,3 +171,23 @@ def test_fp8_gemm_matches_reference(m, n, k, dynamic):
         got = fp8.linear_fp8(q, wc, x_scale=scale.cuda())
     err = (got.float().cpu() - ref.float()).abs().max() / ref.float().abs().max()
     assert float(err) < 1e-2, float(err)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(1, 512, 1024), (8, 1280, 2560), (64, 640, 4352), (130, 300, 512), (256, 1024, 1024)])
+def test_w3_dequant_fused_gemm(m, n, k):
+    """3-bit codes expanded in shared memory and multiplied on tcgen05 vs fp32 over the dequantised matrix."""
+    from hibana_b200.ops.w3gemm import W3Linear
+    g = torch.Generator().manual_seed(k + m)
+    w = torch.randn(n, k, generator=g) * 0.05
+    x = torch.randn(m, k, generator=g).bfloat16()
+    lin = W3Linear.from_weight(w, "cuda")
+    ref = x.float() @ lin.w3.dequantize().t()
+    got = lin(x.cuda()).float().cpu()
+    err = (got - ref).abs().max() / ref.abs().max()
+    assert float(err) < 1e-2, float(err)
+    res = torch.randn(m, n, generator=g).bfloat16()
+    got = lin(x.cuda(), epilogue=1, residual=res.cuda()).float().cpu()
+    assert float((got - (ref + res.float())).abs().max() / ref.abs().max()) < 2e-2
+    from hibana_b200 import _native as nv
+    assert nv.read_status() == 0
