@@ -50,6 +50,11 @@ int hb_gemm_fp8(const void* a, const void* b, int ra, int rb, int k, long long l
                 int epilogue, int swap, int splits, void* status, int bn, void* stream);
 int hb_gemm_w3(const void* tiles, const void* x, int n, int m, int k, long long ldx, void* out, long long ldo,
                const void* residual, float alpha, int epilogue, int splits, void* status, int bn, void* stream);
+// Host row gather over sharded table files (csrc/row_gather.cpp).
+void* hb_rows_open(int row_bytes, long long rows_per_shard, int threads);
+int hb_rows_add_shard(void* g, const char* path);
+long long hb_rows_gather(void* g, const long long* rows, long long n, void* dst, long long* cold);
+void hb_rows_close(void* g);
 void hb_clear_tmap_cache(void);
 // GEMM launches use programmatic dependent launch (weight prefetch overlaps the preceding kernel) when on.
 void hb_gemm_set_pdl(int on);
