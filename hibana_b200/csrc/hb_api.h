@@ -55,6 +55,11 @@ void* hb_rows_open(int row_bytes, long long rows_per_shard, int threads);
 int hb_rows_add_shard(void* g, const char* path);
 long long hb_rows_gather(void* g, const long long* rows, long long n, void* dst, long long* cold);
 void hb_rows_close(void* g);
+// Hyper-connection steps (csrc/hyper.cu).
+int hb_hc_norm(const void* hyper, const void* w, void* normed, int tokens, int hc, int h, float eps, void* stream);
+int hb_hc_gate_mean(const void* gate, const void* normed, void* mixed, int tokens, int hc, int h, void* stream);
+int hb_hc_inject(const void* hyper, const void* block_out, const void* inject_logits, void* out, int tokens, int hc,
+                 int h, void* stream);
 void hb_clear_tmap_cache(void);
 // GEMM launches use programmatic dependent launch (weight prefetch overlaps the preceding kernel) when on.
 void hb_gemm_set_pdl(int on);
