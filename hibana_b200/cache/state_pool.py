@@ -17,6 +17,9 @@ class StatePool:
         self.conv = torch.zeros(max(layers, 1), slots + 1, conv_dim, max(conv_width - 1, 1), dtype=torch.bfloat16,
                                 device=device)
         self.ssm = torch.zeros(max(layers, 1), slots + 1, *state_shape, dtype=state_dtype, device=device)
+        # int8 states carry one fp32 scale per state row (last dim is the quantised one)
+        self.ssm_scale = (torch.ones(max(layers, 1), slots + 1, *state_shape[:-1], dtype=torch.float32, device=device)
+                          if state_dtype == torch.int8 else None)
         self._free = list(range(slots, 0, -1))
         self._owned = bytearray(slots + 1)
 
@@ -26,7 +29,8 @@ class StatePool:
 
     @property
     def bytes_per_slot(self) -> int:
-        return (self.conv[:, 0].numel() * 2 + self.ssm[:, 0].numel() * self.ssm.element_size())
+        scale = self.ssm_scale[:, 0].numel() * 4 if self.ssm_scale is not None else 0
+        return self.conv[:, 0].numel() * 2 + self.ssm[:, 0].numel() * self.ssm.element_size() + scale
 
     def alloc(self) -> int:
         if not self._free:
@@ -46,10 +50,14 @@ class StatePool:
     def copy_slot(self, src: int, dst: int) -> None:
         self.conv[:, dst].copy_(self.conv[:, src])
         self.ssm[:, dst].copy_(self.ssm[:, src])
+        if self.ssm_scale is not None:
+            self.ssm_scale[:, dst].copy_(self.ssm_scale[:, src])
 
     def zero_slot(self, slot: int) -> None:
         self.conv[:, slot].zero_()
         self.ssm[:, slot].zero_()
+        if self.ssm_scale is not None:
+            self.ssm_scale[:, slot].fill_(1.0)
 
     def export_slot(self, slot: int) -> tuple[torch.Tensor, torch.Tensor]:
         return self.conv[:, slot].clone(), self.ssm[:, slot].clone()

@@ -133,6 +133,12 @@ int hb_rank_gap(const void* logits, long long ld, int rows, int vocab, int is_f3
 int hb_conv1d(const void* x, long long ldx, const void* w, const void* bias, void* y, long long ldy, void* state,
               long long state_stride, const void* q_indptr, const void* slot_in, const void* slot_out,
               const void* has_init, int batch, int channels, int width, int act_silu, void* stream);
+int hb_mamba2_scan_fmt(const void* x, const void* bmat, const void* cmat, const void* dt, long long ldx,
+                       long long ldb, long long lddt, const void* a_log, const void* dt_bias, const void* dskip,
+                       void* y, long long ldy, void* state, long long state_stride, const void* q_indptr,
+                       const void* slot_in, const void* slot_out, const void* has_init, int batch, int heads,
+                       int groups, int head_dim, int d_state, int state_fmt, void* state_scale, unsigned sr_seed,
+                       void* stream);
 int hb_mamba2_scan(const void* x, const void* bmat, const void* cmat, const void* dt, long long ldx, long long ldb,
                    long long lddt, const void* a_log, const void* dt_bias, const void* dskip, void* y, long long ldy,
                    void* state, long long state_stride, const void* q_indptr, const void* slot_in,

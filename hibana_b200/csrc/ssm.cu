@@ -12,6 +12,8 @@
 //
 // Reference counterparts: hibana/kernels/mamba2.py:226-470 and :854-1139 (Triton conv / SSU / SSD chunk scan),
 // hibana/kernels/fla/* and hibana/kernels/csrc/gdn_verify.cu:172-330 (gated delta rule prefill / verify / commit).
+#include <cuda_fp16.h>
+
 #include "hb_api.h"
 #include "hb_common.cuh"
 
@@ -71,7 +73,9 @@ struct MambaParams {
   const float* dskip;        // [heads]
   __nv_bfloat16* y;          // [T, heads * P]
   long long ldy;
-  float* state;              // [slots, heads, P, N]
+  float* state;              // [slots, heads, P, N] (fp32; __half or int8 with the quantised formats)
+  float* state_scale;        // int8 format: [slots, heads, P] row scales (stride = state_stride / N)
+  unsigned sr_seed;          // fp16 format: 0 = round to nearest, else seed of the stochastic rounding
   long long state_stride;
   const int* q_indptr;
   const int* slot_in;
@@ -82,7 +86,15 @@ struct MambaParams {
 
 // One CTA per (sequence, head). Thread layout: P rows x (THREADS / P) column groups; each thread keeps
 // N / (THREADS / P) state columns of one row in registers for the whole sequence.
-template <int P, int N, int THREADS>
+// State formats: 0 fp32; 1 fp16 (optionally stochastically rounded on store, so that rounding errors do not
+// accumulate as a bias over thousands of steps); 2 int8 with one fp32 scale per state row (absmax / 127).
+// The recurrence itself always runs in fp32 registers; only the pool representation changes.
+__device__ __forceinline__ unsigned mix32(unsigned x) {
+  x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+  return x;
+}
+
+template <int P, int N, int THREADS, int FMT>
 __global__ void __launch_bounds__(THREADS) mamba2_scan_kernel(const MambaParams p) {
   constexpr int CG = THREADS / P;          // column groups
   constexpr int NC = N / CG;               // state columns per thread
@@ -95,10 +107,24 @@ __global__ void __launch_bounds__(THREADS) mamba2_scan_kernel(const MambaParams 
   const int r1 = p.q_indptr ? p.q_indptr[b + 1] : b + 1;
   float s[NC];
   const bool init = p.has_init == nullptr || p.has_init[b] != 0;
-  const float* sin = p.state + static_cast<long long>(p.slot_in[b]) * p.state_stride +
-                     (static_cast<long long>(h) * P + row) * N + cg * NC;
+  {
+    const long long off = static_cast<long long>(p.slot_in[b]) * p.state_stride +
+                          (static_cast<long long>(h) * P + row) * N + cg * NC;
+    if constexpr (FMT == 0) {
 #pragma unroll
-  for (int i = 0; i < NC; ++i) s[i] = init ? sin[i] : 0.f;
+      for (int i = 0; i < NC; ++i) s[i] = init ? p.state[off + i] : 0.f;
+    } else if constexpr (FMT == 1) {
+      const __half* sin = reinterpret_cast<const __half*>(p.state) + off;
+#pragma unroll
+      for (int i = 0; i < NC; ++i) s[i] = init ? __half2float(sin[i]) : 0.f;
+    } else {
+      const int8_t* sin = reinterpret_cast<const int8_t*>(p.state) + off;
+      const float sc = p.state_scale[static_cast<long long>(p.slot_in[b]) * (p.state_stride / N) +
+                                     static_cast<long long>(h) * P + row];
+#pragma unroll
+      for (int i = 0; i < NC; ++i) s[i] = init ? static_cast<float>(sin[i]) * sc : 0.f;
+    }
+  }
   const float a = -__expf(p.a_log[h]);
   const float dtb = p.dt_bias ? p.dt_bias[h] : 0.f;
   const float dsk = p.dskip ? p.dskip[h] : 0.f;
@@ -124,10 +150,40 @@ __global__ void __launch_bounds__(THREADS) mamba2_scan_kernel(const MambaParams 
     if (cg == 0) p.y[t * p.ldy + h * P + row] = __float2bfloat16(acc + dsk * xv);
   }
   if (p.slot_out != nullptr) {
-    float* so = p.state + static_cast<long long>(p.slot_out[b]) * p.state_stride +
-                (static_cast<long long>(h) * P + row) * N + cg * NC;
+    const long long off = static_cast<long long>(p.slot_out[b]) * p.state_stride +
+                          (static_cast<long long>(h) * P + row) * N + cg * NC;
+    if constexpr (FMT == 0) {
 #pragma unroll
-    for (int i = 0; i < NC; ++i) so[i] = s[i];
+      for (int i = 0; i < NC; ++i) p.state[off + i] = s[i];
+    } else if constexpr (FMT == 1) {
+      __half* so = reinterpret_cast<__half*>(p.state) + off;
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        if (p.sr_seed == 0) {
+          so[i] = __float2half_rn(s[i]);
+        } else {
+          // stochastic rounding: up with probability (x - lo) / (hi - lo)
+          const __half lo = __float2half_rd(s[i]), hi = __float2half_ru(s[i]);
+          const float fl = __half2float(lo), fh = __half2float(hi);
+          const unsigned r = mix32(p.sr_seed ^ mix32(static_cast<unsigned>(off + i) * 2654435761u + r1));
+          const float u = (r >> 8) * (1.f / 16777216.f);
+          so[i] = (fh > fl && (s[i] - fl) > u * (fh - fl)) ? hi : lo;
+        }
+      }
+    } else {
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < NC; ++i) amax = fmaxf(amax, fabsf(s[i]));
+#pragma unroll
+      for (int o = CG / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      const float sc = amax > 0.f ? amax / 127.f : 1.f;
+      const float inv = 1.f / sc;
+      int8_t* so = reinterpret_cast<int8_t*>(p.state) + off;
+#pragma unroll
+      for (int i = 0; i < NC; ++i) so[i] = static_cast<int8_t>(__float2int_rn(fminf(fmaxf(s[i] * inv, -127.f), 127.f)));
+      if (cg == 0)
+        p.state_scale[static_cast<long long>(p.slot_out[b]) * (p.state_stride / N) + static_cast<long long>(h) * P + row] = sc;
+    }
   }
 }
 
@@ -235,6 +291,16 @@ using namespace hb;
 #define IP(p) static_cast<const int*>(p)
 #define FP(p) static_cast<const float*>(p)
 
+template <int FMT>
+static int launch_mamba(const MambaParams& p, dim3 grid, int head_dim, int d_state, cudaStream_t st) {
+  if (head_dim == 32 && d_state == 64) mamba2_scan_kernel<32, 64, 128, FMT><<<grid, 128, 0, st>>>(p);
+  else if (head_dim == 64 && d_state == 128) mamba2_scan_kernel<64, 128, 256, FMT><<<grid, 256, 0, st>>>(p);
+  else if (head_dim == 64 && d_state == 64) mamba2_scan_kernel<64, 64, 256, FMT><<<grid, 256, 0, st>>>(p);
+  else if (head_dim == 32 && d_state == 16) mamba2_scan_kernel<32, 16, 128, FMT><<<grid, 128, 0, st>>>(p);
+  else return 1;
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
 extern "C" {
 
 int hb_conv1d(const void* x, long long ldx, const void* w, const void* bias, void* y, long long ldy, void* state,
@@ -249,27 +315,38 @@ int hb_conv1d(const void* x, long long ldx, const void* w, const void* bias, voi
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
-int hb_mamba2_scan(const void* x, const void* bmat, const void* cmat, const void* dt, long long ldx, long long ldb,
-                   long long lddt, const void* a_log, const void* dt_bias, const void* dskip, void* y, long long ldy,
-                   void* state, long long state_stride, const void* q_indptr, const void* slot_in,
-                   const void* slot_out, const void* has_init, int batch, int heads, int groups, int head_dim,
-                   int d_state, void* stream) {
+// state_fmt: 0 fp32, 1 fp16 (sr_seed != 0: stochastic rounding on store), 2 int8 + state_scale [slots, heads, P].
+int hb_mamba2_scan_fmt(const void* x, const void* bmat, const void* cmat, const void* dt, long long ldx,
+                       long long ldb, long long lddt, const void* a_log, const void* dt_bias, const void* dskip,
+                       void* y, long long ldy, void* state, long long state_stride, const void* q_indptr,
+                       const void* slot_in, const void* slot_out, const void* has_init, int batch, int heads,
+                       int groups, int head_dim, int d_state, int state_fmt, void* state_scale, unsigned sr_seed,
+                       void* stream) {
   if (batch <= 0) return 0;
+  if (state_fmt < 0 || state_fmt > 2 || (state_fmt == 2 && state_scale == nullptr)) return 1;
   MambaParams p;
   p.x = BF(x); p.bmat = BF(bmat); p.cmat = BF(cmat); p.dt = BF(dt);
   p.ldx = ldx; p.ldb = ldb; p.lddt = lddt;
   p.a_log = FP(a_log); p.dt_bias = FP(dt_bias); p.dskip = FP(dskip);
   p.y = BFM(y); p.ldy = ldy;
   p.state = static_cast<float*>(state); p.state_stride = state_stride;
+  p.state_scale = static_cast<float*>(state_scale); p.sr_seed = sr_seed;
   p.q_indptr = IP(q_indptr); p.slot_in = IP(slot_in); p.slot_out = IP(slot_out); p.has_init = IP(has_init);
   p.heads = heads; p.groups = groups;
   const dim3 grid(heads, batch);
-  if (head_dim == 32 && d_state == 64) mamba2_scan_kernel<32, 64, 128><<<grid, 128, 0, ST(stream)>>>(p);
-  else if (head_dim == 64 && d_state == 128) mamba2_scan_kernel<64, 128, 256><<<grid, 256, 0, ST(stream)>>>(p);
-  else if (head_dim == 64 && d_state == 64) mamba2_scan_kernel<64, 64, 256><<<grid, 256, 0, ST(stream)>>>(p);
-  else if (head_dim == 32 && d_state == 16) mamba2_scan_kernel<32, 16, 128><<<grid, 128, 0, ST(stream)>>>(p);
-  else return 1;
-  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+  if (state_fmt == 0) return launch_mamba<0>(p, grid, head_dim, d_state, ST(stream));
+  if (state_fmt == 1) return launch_mamba<1>(p, grid, head_dim, d_state, ST(stream));
+  return launch_mamba<2>(p, grid, head_dim, d_state, ST(stream));
+}
+
+int hb_mamba2_scan(const void* x, const void* bmat, const void* cmat, const void* dt, long long ldx, long long ldb,
+                   long long lddt, const void* a_log, const void* dt_bias, const void* dskip, void* y, long long ldy,
+                   void* state, long long state_stride, const void* q_indptr, const void* slot_in,
+                   const void* slot_out, const void* has_init, int batch, int heads, int groups, int head_dim,
+                   int d_state, void* stream) {
+  return hb_mamba2_scan_fmt(x, bmat, cmat, dt, ldx, ldb, lddt, a_log, dt_bias, dskip, y, ldy, state, state_stride,
+                            q_indptr, slot_in, slot_out, has_init, batch, heads, groups, head_dim, d_state, 0, nullptr,
+                            0, stream);
 }
 
 int hb_gdn_scan(const void* q, const void* k, const void* v, const void* g, const void* beta, long long ldq,

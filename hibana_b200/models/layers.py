@@ -111,7 +111,9 @@ class MambaLayer:
         y = recurrent.mamba2_scan(xbc[:, :inner], xbc[:, inner:inner + gn], xbc[:, inner + gn:], dt, self.a_log,
                                   self.dt_bias, self.d_skip, states.ssm[li], ctx.state_slots, so,
                                   heads=t.mamba_heads, groups=t.mamba_groups, head_dim=t.mamba_head_dim,
-                                  d_state=t.mamba_state, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state)
+                                  d_state=t.mamba_state, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state,
+                                  state_scale=states.ssm_scale[li] if getattr(states, "ssm_scale", None) is not None
+                                  else None, sr_seed=ctx.extras.get("sr_seed", 0))
         y = basic.gated_rmsnorm(y, z, self.norm_w, t.norm_eps, inner // t.mamba_groups)
         return self.out_proj(y)
 
@@ -125,7 +127,8 @@ class MambaLayer:
         recurrent.mamba2_scan(xbc[:, :inner], xbc[:, inner:inner + gn], xbc[:, inner + gn:], dt, self.a_log,
                               self.dt_bias, self.d_skip, states.ssm[li], slots, slots, heads=t.mamba_heads,
                               groups=t.mamba_groups, head_dim=t.mamba_head_dim, d_state=t.mamba_state,
-                              q_indptr=q_indptr)
+                              q_indptr=q_indptr, state_scale=states.ssm_scale[li]
+                              if getattr(states, "ssm_scale", None) is not None else None)
 
 
 class GdnLayer:

@@ -7,6 +7,8 @@ Reference: hibana/kernels/mamba2.py, hibana/kernels/fla/*, hibana/kernels/csrc/g
 """
 from __future__ import annotations
 
+import ctypes
+
 from typing import Optional
 
 import torch
@@ -17,6 +19,7 @@ from .. import _native as nv
 P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
 nv.register("hb_conv1d", [P, L, P, P, P, L, P, L, P, P, P, P, I, I, I, I, P])
 nv.register("hb_mamba2_scan", [P, P, P, P, L, L, L, P, P, P, P, L, P, L, P, P, P, P, I, I, I, I, I, P])
+nv.register("hb_mamba2_scan_fmt", [P, P, P, P, L, L, L, P, P, P, P, L, P, L, P, P, P, P, I, I, I, I, I, I, P, ctypes.c_uint, P])
 nv.register("hb_gdn_scan", [P, P, P, P, P, L, L, P, L, P, L, P, P, P, P, I, I, I, I, I, Fl, I, P])
 
 
@@ -61,18 +64,39 @@ def mamba2_scan(x: torch.Tensor, bmat: torch.Tensor, cmat: torch.Tensor, dt: tor
                 dt_bias: Optional[torch.Tensor], dskip: Optional[torch.Tensor], state: torch.Tensor,
                 slot_in: torch.Tensor, slot_out: Optional[torch.Tensor], *, heads: int, groups: int, head_dim: int,
                 d_state: int, q_indptr: Optional[torch.Tensor] = None,
-                has_init: Optional[torch.Tensor] = None) -> torch.Tensor:
+                has_init: Optional[torch.Tensor] = None, state_scale: Optional[torch.Tensor] = None,
+                sr_seed: int = 0) -> torch.Tensor:
     """x [T, heads*P], bmat/cmat [T, groups*N], dt [T, heads] (bf16, column slices allowed);
-    state [slots, heads, P, N] fp32. Returns y [T, heads*P] bf16."""
+    state [slots, heads, P, N] in fp32, fp16 (`sr_seed` != 0: stochastic rounding when the state is written back)
+    or int8 with `state_scale` [slots, heads, P] fp32 row scales. Returns y [T, heads*P] bf16."""
     t = x.shape[0]
     batch = slot_in.shape[0]
+    fmt = {torch.float32: 0, torch.float16: 1, torch.int8: 2}[state.dtype]
     if nv.use_native(x):
         y = torch.empty(t, heads * head_dim, dtype=x.dtype, device=x.device)
-        nv.check(nv.lib().hb_mamba2_scan(
+        nv.check(nv.lib().hb_mamba2_scan_fmt(
             x.data_ptr(), bmat.data_ptr(), cmat.data_ptr(), dt.data_ptr(), x.stride(0), bmat.stride(0), dt.stride(0),
             a_log.data_ptr(), nv.ptr(dt_bias), nv.ptr(dskip), y.data_ptr(), y.stride(0), state.data_ptr(),
             state.stride(0), nv.ptr(q_indptr), slot_in.data_ptr(), nv.ptr(slot_out), nv.ptr(has_init), batch, heads,
-            groups, head_dim, d_state, nv.stream()), "hb_mamba2_scan")
+            groups, head_dim, d_state, fmt, nv.ptr(state_scale), sr_seed & 0xFFFFFFFF, nv.stream()),
+                 "hb_mamba2_scan_fmt")
+        return y
+    if fmt != 0:      # CPU reference: dequantise the slots in use, run in fp32, requantise (round to nearest)
+        work = torch.zeros(state.shape, dtype=torch.float32)
+        used = torch.cat([slot_in.long(), slot_out.long() if slot_out is not None else slot_in.long()]).unique()
+        deq = state[used].float() * (state_scale[used][..., None] if fmt == 2 else 1.0)
+        work[used] = deq
+        y = mamba2_scan(x, bmat, cmat, dt, a_log, dt_bias, dskip, work, slot_in, slot_out, heads=heads, groups=groups,
+                        head_dim=head_dim, d_state=d_state, q_indptr=q_indptr, has_init=has_init)
+        if slot_out is not None:
+            for s_ in slot_out.long().unique().tolist():
+                if fmt == 1:
+                    state[s_] = work[s_].to(torch.float16)
+                else:
+                    sc = (work[s_].abs().amax(-1) / 127.0)
+                    sc = torch.where(sc > 0, sc, torch.ones_like(sc))
+                    state_scale[s_] = sc
+                    state[s_] = torch.round(work[s_] / sc[..., None]).clamp(-127, 127).to(torch.int8)
         return y
     y = torch.empty(t, heads * head_dim, dtype=x.dtype)
     a = -torch.exp(a_log.float())

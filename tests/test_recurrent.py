@@ -138,3 +138,71 @@ def test_gdn_scan_gpu(kh, vh, kd):
                        q_indptr=ip.cuda(), has_init=init.cuda(), **kw)
     _close(got, ref, 3e-2)
     _close(st_g, st_c, 2e-3)
+
+
+def _mamba_case(dtype, slots=5, heads=4, p=32, n=64, groups=1, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    t = 9
+    x = torch.randn(t, heads * p, generator=g).bfloat16()
+    bm = torch.randn(t, groups * n, generator=g).bfloat16()
+    cm = torch.randn(t, groups * n, generator=g).bfloat16()
+    dt = torch.randn(t, heads, generator=g).bfloat16()
+    a_log = torch.randn(heads, generator=g) * 0.3
+    state = torch.randn(slots, heads, p, n, generator=g) * 0.5
+    scale = None
+    if dtype == torch.int8:
+        scale = state.abs().amax(-1) / 127
+        state = torch.round(state / scale[..., None]).to(torch.int8)
+    else:
+        state = state.to(dtype)
+    indptr = torch.tensor([0, 4, 9], dtype=torch.int32)
+    slot_in = torch.tensor([1, 3], dtype=torch.int32)
+    slot_out = torch.tensor([2, 3], dtype=torch.int32)
+    return x, bm, cm, dt, a_log, state, scale, indptr, slot_in, slot_out, dict(heads=heads, groups=groups, head_dim=p, d_state=n)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.int8])
+def test_mamba2_quantised_state_formats(dtype):
+    """fp16 and int8 (+ row scale) pool representations: same recurrence, state requantised on write-back."""
+    from hibana_b200.ops import recurrent
+    x, bm, cm, dt, a_log, st, sc, ip, si, so, kw = _mamba_case(dtype)
+    st_ref, sc_ref = st.clone(), sc.clone() if sc is not None else None
+    y_ref = recurrent.mamba2_scan(x, bm, cm, dt, a_log, None, None, st_ref, si, so, q_indptr=ip, state_scale=sc_ref, **kw)
+    st_g, sc_g = st.cuda(), sc.cuda() if sc is not None else None
+    y = recurrent.mamba2_scan(x.cuda(), bm.cuda(), cm.cuda(), dt.cuda(), a_log.cuda(), None, None, st_g, si.cuda(),
+                              so.cuda(), q_indptr=ip.cuda(), state_scale=sc_g, **kw)
+    assert torch.allclose(y.float().cpu(), y_ref.float(), atol=3e-2, rtol=3e-2)
+    deq = lambda s, c: s.float() * (c[..., None] if c is not None else 1.0)  # noqa: E731
+    a, b = deq(st_g.cpu(), sc_g.cpu() if sc_g is not None else None), deq(st_ref, sc_ref)
+    tol = 2e-2 if dtype == torch.float16 else 4e-2
+    assert float((a[[2, 3]] - b[[2, 3]]).abs().max()) < tol * float(b[[2, 3]].abs().max())
+    assert torch.equal(a[[0, 1, 4]], b[[0, 1, 4]])          # untouched slots
+
+
+@pytest.mark.gpu
+def test_fp16_stochastic_rounding_is_unbiased():
+    """A state of 1.0 decayed by 1 - 0.3 * 2^-11 lies between two fp16 neighbours: round-to-nearest stores 1.0 every
+    time (the decay is lost for ever), stochastic rounding stores the right value on average."""
+    import math
+    from hibana_b200.ops import recurrent
+    heads, p, n = 4, 32, 64
+    raw = torch.tensor([[-8.8125] * heads]).bfloat16()
+    dtv = math.log1p(math.exp(float(raw[0, 0])))
+    decay = math.exp(-dtv)                                   # a = -exp(0) = -1
+    frac = (1.0 - decay) / 2 ** -11
+    assert 0.2 < frac < 0.45
+    x = torch.zeros(1, heads * p).bfloat16().cuda()
+    bm = torch.zeros(1, n).bfloat16().cuda()
+    a_log = torch.zeros(heads).cuda()
+    si, so = torch.tensor([1], dtype=torch.int32).cuda(), torch.tensor([2], dtype=torch.int32).cuda()
+    kw = dict(heads=heads, groups=1, head_dim=p, d_state=n)
+    st = torch.zeros(3, heads, p, n, dtype=torch.float16, device="cuda")
+    st[1] = 1.0
+    recurrent.mamba2_scan(x, bm, bm, raw.cuda(), a_log, None, None, st, si, so, sr_seed=0, **kw)
+    assert float(st[2].float().mean()) == 1.0
+    recurrent.mamba2_scan(x, bm, bm, raw.cuda(), a_log, None, None, st, si, so, sr_seed=1234, **kw)
+    vals = st[2].float()
+    assert set(vals.unique().tolist()) <= {1.0, 1.0 - 2 ** -11}
+    err = abs(float(vals.double().mean()) - decay)
+    assert err < 0.03 * 2 ** -11, (err / 2 ** -11, frac)
