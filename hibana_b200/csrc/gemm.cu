@@ -773,7 +773,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   const bool w3 = a.kind == kGemmW3;
   if (a.ra <= 0 || a.rb <= 0 || a.k <= 0) return cudaErrorInvalidValue;
   if (fp4 ? (a.k % 32 != 0) : fp8 ? (a.k % 16 != 0) : w3 ? (a.k % 64 != 0) : (a.k % 8 != 0)) return cudaErrorInvalidValue;
-  if (w3 && (!a.swap || a.grp_cnt != nullptr || a.peer != nullptr)) return cudaErrorInvalidValue;
+  if (w3 && (!a.swap || a.peer != nullptr)) return cudaErrorInvalidValue;   // grouped (3-bit experts) is fine
   const int kt_elems = fp4 ? 256 : fp8 ? 128 : 64;
   const int k_tiles = (a.k + kt_elems - 1) / kt_elems;
   const int tiles_a = (a.ra + BM - 1) / BM;

@@ -88,6 +88,17 @@ class ExpertWeights:
             return cls(e, h, inter, act, fmt, fc1.reshape(e * n1, h).to(torch.bfloat16).contiguous(),
                        fc2.reshape(e * fc2.shape[1], inter).to(torch.bfloat16).contiguous())
         dev = fc1.device
+        if fmt == "w3":
+            # 3-bit experts (groups of 64, scale + zero): one tile stack over all experts' rows; an expert's rows
+            # are a multiple of 128, so expert boundaries fall on tile boundaries
+            from ..weights.w3 import Int3G64
+            assert n1 % 128 == 0 and fc2.shape[1] % 128 == 0
+            q1 = Int3G64.quantize(fc1.reshape(e * n1, h).float().cpu())
+            q2 = Int3G64.quantize(fc2.reshape(e * fc2.shape[1], inter).float().cpu())
+            out = cls(e, h, inter, act, fmt, q1.tiles().to(dev), q2.tiles().to(dev))
+            out.w3 = (q1, q2)
+            out.fc2_rows_ = fc2.shape[1]
+            return out
 
         def quant(w):   # per-expert scale, stacked rows
             parts = [nvfp4.quantize_weight(w[i]) for i in range(w.shape[0])]
@@ -106,6 +117,8 @@ class ExpertWeights:
         """Dequantised stacked matrix [E, n, k] (fp32) for the reference path."""
         w = self.fc1 if which == 1 else self.fc2
         n = self.n1 if which == 1 else self.fc2_rows
+        if self.fmt == "w3":
+            return self.w3[which - 1].dequantize().view(self.experts, n, -1).to(w.device)
         if self.fmt == "bf16":
             return w.float().view(self.experts, n, -1)
         sfb = nvfp4.unswizzle_sf(w.sf, w.rows, w.k // 16)
@@ -117,6 +130,8 @@ class ExpertWeights:
 
     @property
     def fc2_rows(self) -> int:
+        if self.fmt == "w3":
+            return self.fc2_rows_
         return (self.fc2.shape[0] if self.fmt == "bf16" else self.fc2.rows) // self.experts
 
     def slice(self, e_lo: int, e_n: int) -> "ExpertWeights":
@@ -139,8 +154,11 @@ class ExpertWeights:
             if isinstance(x, nvfp4.Nvfp4Tensor):
                 return nvfp4.Nvfp4Tensor(x.q.to(device), x.sf.to(device), x.gscale.to(device), x.rows, x.k)
             return x.to(device) if isinstance(x, torch.Tensor) else x
-        return ExpertWeights(self.experts, self.hidden, self.inter, self.act, self.fmt, mv(self.fc1), mv(self.fc2),
-                             mv(self.fc1_alpha), mv(self.fc2_alpha), mv(self.fc1_in_scale), mv(self.fc2_in_scale))
+        out = ExpertWeights(self.experts, self.hidden, self.inter, self.act, self.fmt, mv(self.fc1), mv(self.fc2),
+                            mv(self.fc1_alpha), mv(self.fc2_alpha), mv(self.fc1_in_scale), mv(self.fc2_in_scale))
+        if self.fmt == "w3":
+            out.w3, out.fc2_rows_ = self.w3, self.fc2_rows_
+        return out
 
 
 def _act(h1: torch.Tensor, act: str) -> torch.Tensor:
@@ -205,18 +223,19 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
     mid_cols = ew.inter
     h1 = torch.empty(rows_cap, mid_cols if ew.act == "swiglu" else n1, dtype=torch.bfloat16, device=dev)
     y = torch.empty(rows_cap, h_out, dtype=torch.bfloat16, device=dev)
-    if ew.fmt == "bf16":
+    if ew.fmt in ("bf16", "w3"):
+        kind = 0 if ew.fmt == "bf16" else 3      # 3: dequant-fused 3-bit experts (csrc/gemm.cu kind w3, grouped)
         xs = torch.empty(rows_cap, h, dtype=torch.bfloat16, device=dev)
         nv.check(lib.hb_moe_gather(x.data_ptr(), x.stride(0), src.data_ptr(), total.data_ptr(), xs.data_ptr(),
                                    rows_cap, h, nv.stream()), "hb_moe_gather")
-        nv.check(lib.hb_gemm_grouped(0, ew.fc1.data_ptr(), xs.data_ptr(), None, None, e, n1, rows_cap, h,
+        nv.check(lib.hb_gemm_grouped(kind, ew.fc1.data_ptr(), xs.data_ptr(), None, None, e, n1, rows_cap, h,
                                      h1.data_ptr(), h1.stride(0), None, epi1, start.data_ptr(), cnt.data_ptr(),
                                      max_rows, st.data_ptr(), 0, 0, nv.stream()), "hb_gemm_grouped")
         mid = h1
         if ew.act == "relu2":
             from . import basic
             mid = basic.act_mul(h1, basic.ACT_RELU2)
-        nv.check(lib.hb_gemm_grouped(0, ew.fc2.data_ptr(), mid.data_ptr(), None, None, e, h_out, rows_cap,
+        nv.check(lib.hb_gemm_grouped(kind, ew.fc2.data_ptr(), mid.data_ptr(), None, None, e, h_out, rows_cap,
                                      ew.inter, y.data_ptr(), y.stride(0), None, gemm.EPI_STORE, start.data_ptr(),
                                      cnt.data_ptr(), max_rows, st.data_ptr(), 0, 0, nv.stream()), "hb_gemm_grouped")
     else:

@@ -44,7 +44,7 @@ def test_route_gpu(e, k, sig):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("fmt", ["bf16", "nvfp4"])
+@pytest.mark.parametrize("fmt", ["bf16", "nvfp4", "w3"])
 @pytest.mark.parametrize("t,e,k,h,inter,act", [(4, 8, 2, 256, 512, "swiglu"), (37, 16, 4, 256, 128, "relu2"),
                                                (300, 8, 2, 128, 256, "swiglu")])
 def test_experts_forward_gpu(fmt, t, e, k, h, inter, act):
