@@ -1,0 +1,72 @@
+"""Data-parallel replicas: several engines (one per GPU or per tensor-parallel group) behind one front end.
+
+`ReplicaSet` routes every new request to the replica with the least outstanding work, keeps follow-up turns of a
+conversation on the replica whose prefix cache already holds the conversation (prefix affinity by a hash of the
+leading tokens), and drains / reports per replica. With expert parallelism across the replicas (DP attention + EP
+experts) the replicas additionally step in lockstep: `lockstep_plan` tells every replica, from the all-gathered
+"do I have work" bits, whether the step runs and whether it must run with an empty batch (a rank without requests
+still has to take part in the all-to-all of every MoE layer). The reference serves one engine per process
+(hibana/engine/loop.py); data parallelism is new here.
+"""
+from __future__ import annotations
+
+import hashlib
+from typing import Any, Optional, Sequence
+
+
+class ReplicaSet:
+    def __init__(self, loops: Sequence[Any], affinity_tokens: int = 256, affinity_slack: int = 4):
+        """`loops`: objects with submit(request) -> ticket, stats() -> {"running": int, "waiting": int}."""
+        assert loops
+        self.loops = list(loops)
+        self.affinity_tokens, self.affinity_slack = affinity_tokens, affinity_slack
+        self._home: dict[bytes, int] = {}
+        self.routed = [0] * len(self.loops)
+
+    def _load(self, i: int) -> int:
+        st = self.loops[i].stats()
+        return int(st.get("running", 0)) + int(st.get("waiting", 0))
+
+    def _key(self, prompt_ids: Sequence[int]) -> Optional[bytes]:
+        if len(prompt_ids) < self.affinity_tokens:
+            return None
+        head = prompt_ids[:self.affinity_tokens]
+        return hashlib.blake2b(b"".join(int(t).to_bytes(8, "little", signed=True) for t in head), digest_size=16).digest()
+
+    def pick(self, prompt_ids: Sequence[int]) -> int:
+        loads = [self._load(i) for i in range(len(self.loops))]
+        best = min(range(len(loads)), key=lambda i: (loads[i], i))
+        key = self._key(prompt_ids)
+        if key is not None:
+            home = self._home.get(key)
+            # stay with the cached prefix unless that replica is clearly busier than the idlest one
+            if home is not None and loads[home] <= loads[best] + self.affinity_slack:
+                best = home
+            self._home[key] = best
+            if len(self._home) > 65536:
+                self._home.pop(next(iter(self._home)))
+        return best
+
+    def submit(self, request) -> Any:
+        i = self.pick(request.prompt_ids)
+        self.routed[i] += 1
+        return self.loops[i].submit(request)
+
+    def stats(self) -> dict:
+        per = [loop.stats() for loop in self.loops]
+        return {"replicas": len(per), "routed": list(self.routed),
+                "running": sum(int(p.get("running", 0)) for p in per),
+                "waiting": sum(int(p.get("waiting", 0)) for p in per), "per_replica": per}
+
+    def drain(self) -> None:
+        for loop in self.loops:
+            if hasattr(loop, "drain"):
+                loop.drain()
+
+
+def lockstep_plan(has_work: Sequence[bool]) -> tuple[bool, list[bool]]:
+    """(run the step at all, per replica: run with an empty batch). Expert-parallel replicas only skip a step when
+    nobody has work."""
+    if not any(has_work):
+        return False, [False] * len(has_work)
+    return True, [not w for w in has_work]

@@ -92,7 +92,11 @@ class HybridModel:
                     continue
                 x = basic.rmsnorm(res if h is None else h, norm_w, t.norm_eps,
                                   residual=None if h is None else res, gemma=t.gemma_norm)
-                if isinstance(sub, MoeLayer) and sub.ep_size > 1 and ctx.comm is not None:
+                if isinstance(sub, MoeLayer) and ctx.extras.get("ep") is not None:
+                    # data-parallel attention + expert-parallel experts: this rank's own tokens travel to the
+                    # owners of their experts and back (parallel/ep.py); every rank runs every layer each step
+                    h = sub.forward_a2a(x, ctx.extras["ep"])
+                elif isinstance(sub, MoeLayer) and sub.ep_size > 1 and ctx.comm is not None:
                     h = sub.forward_ep(x, ctx.comm)
                 else:
                     h = sub.forward(x, ctx, kv, states)
