@@ -23,7 +23,7 @@
 namespace hb {
 namespace {
 
-constexpr int DEC_WARPS = 4;
+constexpr int DEC_WARPS = 2;   // two CTAs share an SM: one streams while the other runs its prologue or merge
 constexpr int DEC_STAGES = 3;
 
 struct DecParams {
@@ -103,7 +103,7 @@ __device__ __forceinline__ uint32_t dsw(int row, int c) {
 }
 
 template <int D, bool T8>
-__global__ void __launch_bounds__(DEC_WARPS * 32, 1)
+__global__ void __launch_bounds__(DEC_WARPS * 32, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, const DecParams p) {
   using C = DecCfg<D>;
   constexpr int KT = C::KT, ROWB = C::QROWB;
