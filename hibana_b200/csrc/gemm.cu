@@ -916,10 +916,13 @@ int hb_gemm_peer(int kind, const void* a, const void* b, const void* sfa, const 
 int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int experts,
                     int n_per_expert, int b_rows, int k, void* out, long long ldo, const void* alpha_ptr,
                     int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status, int ka_a,
-                    int ka_b, void* stream) {
+                    int ka_b, int bn_hint, void* stream) {
   hb::GemmArgs g;
+  // `bn_hint` (0 = none) sizes the token tile for the EXPECTED rows per expert; the grid still covers
+  // max_rows_per_expert, chunks beyond an expert's rows exit at once.
   int bn = 16;
   while (bn < max_rows_per_expert && bn < 256) bn *= 2;
+  if (bn_hint >= 16 && bn_hint <= 256 && (bn_hint & (bn_hint - 1)) == 0 && bn_hint < bn) bn = bn_hint;
   g.kind = kind; g.a = a; g.b = b; g.sfa = sfa; g.sfb = sfb;
   g.ra = experts * n_per_expert; g.rb = b_rows; g.k = k; g.lda = k; g.ldb = k;
   g.out = out; g.ldo = ldo; g.residual = nullptr; g.alpha = 1.f;
@@ -941,11 +944,12 @@ int hb_gemm_grouped_ep(int kind, const void* a, const void* b, const void* sfa, 
                        int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status,
                        int ka_a, int ka_b, const void* const* bases, int world, int rank, const void* gate_flags,
                        const void* seq_ptr, const void* row_ret, long long ret_offset, void* done_counter,
-                       long long ret_flag_offset, long long limit_ns, void* stream) {
+                       long long ret_flag_offset, long long limit_ns, int bn_hint, void* stream) {
   hb::GemmArgs g;
   hb::GemmEp ep;
   int bn = 16;
   while (bn < max_rows_per_expert && bn < 256) bn *= 2;
+  if (bn_hint >= 16 && bn_hint <= 256 && (bn_hint & (bn_hint - 1)) == 0 && bn_hint < bn) bn = bn_hint;
   for (int i = 0; i < 8; ++i) ep.base[i] = i < world ? const_cast<void*>(bases[i]) : nullptr;
   ep.world = world; ep.rank = rank;
   ep.gate_flags = static_cast<const int*>(gate_flags); ep.seq_ptr = static_cast<const int*>(seq_ptr);

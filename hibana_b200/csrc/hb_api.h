@@ -17,7 +17,7 @@ int hb_gemm(int kind, const void* a, const void* b, const void* sfa, const void*
 int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int experts,
                     int n_per_expert, int b_rows, int k, void* out, long long ldo, const void* alpha_ptr,
                     int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status, int ka_a,
-                    int ka_b, void* stream);
+                    int ka_b, int bn_hint, void* stream);
 int hb_gemm_peer(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int m, int n, int k,
                  void* out, long long ldo, const void* alpha_ptr, int epilogue, const void* const* peer_bases,
                  int world, int rank, int rows_per_rank, long long stage_offset, long long counter_offset,
@@ -28,7 +28,7 @@ int hb_gemm_grouped_ep(int kind, const void* a, const void* b, const void* sfa, 
                        int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status,
                        int ka_a, int ka_b, const void* const* bases, int world, int rank, const void* gate_flags,
                        const void* seq_ptr, const void* row_ret, long long ret_offset, void* done_counter,
-                       long long ret_flag_offset, long long limit_ns, void* stream);
+                       long long ret_flag_offset, long long limit_ns, int bn_hint, void* stream);
 // Expert-parallel all-to-all (csrc/ep.cu); heaps come from hb_comm_alloc / hb_comm_ipc_open.
 int hb_ep_ctrl_bytes(void);
 void hb_ep_ctrl_layout(long long* out4);

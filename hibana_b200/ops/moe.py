@@ -23,7 +23,7 @@ nv.register("hb_moe_route", [P, L, P, I, I, I, I, I, Fl, P, P, P])
 nv.register("hb_moe_plan", [P, I, I, I, I, I, P, P, P, P, I, P, P])
 nv.register("hb_moe_gather", [P, L, P, P, P, I, I, P])
 nv.register("hb_moe_combine", [P, L, P, P, P, L, P, L, I, I, I, P])
-nv.register("hb_gemm_grouped", [I, P, P, P, P, I, I, I, I, P, L, P, I, P, P, I, P, I, I, P])
+nv.register("hb_gemm_grouped", [I, P, P, P, P, I, I, I, I, P, L, P, I, P, P, I, P, I, I, I, P])
 nv.register("hb_quant_nvfp4_rows", [P, L, I, I, I, P, P, P, I, P, P, P])
 
 
@@ -197,6 +197,19 @@ def experts_ref(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: E
     return out.to(torch.bfloat16)
 
 
+def tile_hint(pairs: int, experts: int, max_rows: int, fmt: str) -> int:
+    """Token-tile width for the grouped GEMMs from the EXPECTED rows per expert (the grid still covers the worst
+    case; chunks beyond an expert's rows exit at once). Block-scaled FP4 needs whole 128-row scale blocks per chunk
+    unless the expert fits one chunk."""
+    avg = max(1, -(-pairs // max(experts, 1)))
+    bn = 16
+    while bn < min(avg + avg // 4, 256):
+        bn *= 2
+    if fmt == "nvfp4" and bn < 128 and max_rows > bn:
+        bn = 128
+    return bn
+
+
 def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: ExpertWeights, *,
                     shared: Optional[torch.Tensor] = None, e_lo: int = 0, e_n: Optional[int] = None) -> torch.Tensor:
     """x [T, H] bf16, ids / weights [T, k] -> [T, H_out] bf16 (sum of the routed experts (+ shared))."""
@@ -210,6 +223,7 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
     e = ew.experts
     rows_cap = ((t * topk + 127) // 128) * 128 + min(e_n, t * topk) * 128
     max_rows = min(t, 1 << 30)                  # an expert can receive every token once
+    bn_hint = tile_hint(t * topk, e_n, max_rows, ew.fmt)
     cnt = torch.empty(e, dtype=torch.int32, device=dev)
     start = torch.empty(e, dtype=torch.int32, device=dev)
     pos = torch.empty(t * topk, dtype=torch.int32, device=dev)
@@ -230,14 +244,14 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
                                    rows_cap, h, nv.stream()), "hb_moe_gather")
         nv.check(lib.hb_gemm_grouped(kind, ew.fc1.data_ptr(), xs.data_ptr(), None, None, e, n1, rows_cap, h,
                                      h1.data_ptr(), h1.stride(0), None, epi1, start.data_ptr(), cnt.data_ptr(),
-                                     max_rows, st.data_ptr(), 0, 0, nv.stream()), "hb_gemm_grouped")
+                                     max_rows, st.data_ptr(), 0, 0, bn_hint, nv.stream()), "hb_gemm_grouped")
         mid = h1
         if ew.act == "relu2":
             from . import basic
             mid = basic.act_mul(h1, basic.ACT_RELU2)
         nv.check(lib.hb_gemm_grouped(kind, ew.fc2.data_ptr(), mid.data_ptr(), None, None, e, h_out, rows_cap,
                                      ew.inter, y.data_ptr(), y.stride(0), None, gemm.EPI_STORE, start.data_ptr(),
-                                     cnt.data_ptr(), max_rows, st.data_ptr(), 0, 0, nv.stream()), "hb_gemm_grouped")
+                                     cnt.data_ptr(), max_rows, st.data_ptr(), 0, 0, bn_hint, nv.stream()), "hb_gemm_grouped")
     else:
         q1, sf1 = nvfp4._alloc(rows_cap, h, dev)
         nv.check(lib.hb_quant_nvfp4_rows(x.data_ptr(), x.stride(0), rows_cap, h, sf1.shape[1],
@@ -246,7 +260,7 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         nv.check(lib.hb_gemm_grouped(1, ew.fc1.q.data_ptr(), q1.data_ptr(), ew.fc1.sf.data_ptr(), sf1.data_ptr(), e,
                                      n1, rows_cap, h, h1.data_ptr(), h1.stride(0), ew.fc1_alpha.data_ptr(), epi1,
                                      start.data_ptr(), cnt.data_ptr(), max_rows, st.data_ptr(), ew.fc1.ka,
-                                     sf1.shape[1], nv.stream()), "hb_gemm_grouped")
+                                     sf1.shape[1], bn_hint, nv.stream()), "hb_gemm_grouped")
         mid = h1
         if ew.act == "relu2":
             from . import basic
@@ -258,7 +272,7 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         nv.check(lib.hb_gemm_grouped(1, ew.fc2.q.data_ptr(), q2.data_ptr(), ew.fc2.sf.data_ptr(), sf2.data_ptr(), e,
                                      h_out, rows_cap, ew.inter, y.data_ptr(), y.stride(0), ew.fc2_alpha.data_ptr(),
                                      gemm.EPI_STORE, start.data_ptr(), cnt.data_ptr(), max_rows, st.data_ptr(),
-                                     ew.fc2.ka, sf2.shape[1], nv.stream()), "hb_gemm_grouped")
+                                     ew.fc2.ka, sf2.shape[1], bn_hint, nv.stream()), "hb_gemm_grouped")
     out = torch.empty(t, h_out, dtype=torch.bfloat16, device=dev)
     nv.check(lib.hb_moe_combine(y.data_ptr(), y.stride(0), pos.data_ptr(), weights.data_ptr(), nv.ptr(shared),
                                 shared.stride(0) if shared is not None else 0, out.data_ptr(), out.stride(0), t, topk,

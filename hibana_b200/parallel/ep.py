@@ -31,7 +31,7 @@ nv.register("hb_ep_plan", [P, I, I, P, I, I, L, I, P, P, P, P, P, L, P, P])
 nv.register("hb_ep_dispatch", [P, L, I, I, I, I, P, P, P, P, I, I, L, L, L, L, P])
 nv.register("hb_ep_combine", [P, P, P, L, P, L, I, I, I, P, I, I, L, L, P, P])
 nv.register("hb_gemm_grouped_ep", [I, P, P, P, P, I, I, I, I, P, L, P, I, P, P, I, P, I, I, P, I, I, P, P, P, L, P, L,
-                                   L, P])
+                                   L, I, P])
 
 EPI_RETURN = 5
 
@@ -150,6 +150,8 @@ class ExpertParallel:
         epi1 = gemm.EPI_SILU_MUL if ew.act == "swiglu" else gemm.EPI_STORE
         h1 = torch.empty(rows_cap, ew.inter if ew.act == "swiglu" else n1, dtype=torch.bfloat16, device=dev)
         max_rows = min(self.world * self.tokens, rows_cap)
+        # every rank sends about as many pairs as it has: expected rows per local expert
+        bn_hint = moe.tile_hint(max(pairs, 1) , self.e_per, max_rows, self.fmt)
         gate = self._ptr(self.flag_rows_off)
         seq = self._ptr(self.seq_off)
 
@@ -158,7 +160,7 @@ class ExpertParallel:
                 kind, a, b, sfa, sfb, self.e_per, n_per, rows_cap, k, out, ldo, alpha, epi, self.grp_start.data_ptr(),
                 self.grp_cnt.data_ptr(), max_rows, st.data_ptr(), ka_a, ka_b, self._bases, self.world, self.rank,
                 gate_flags, seq, self._ptr(self.off["row_ret"]) if ret else None, self.off["ret"],
-                self._ptr(self.done_fc2_off) if ret else None, self.flag_ret_off, self.timeout_ns, stream),
+                self._ptr(self.done_fc2_off) if ret else None, self.flag_ret_off, self.timeout_ns, bn_hint, stream),
                 "hb_gemm_grouped_ep")
 
         if nvq:
