@@ -60,6 +60,15 @@ int hb_hc_norm(const void* hyper, const void* w, void* normed, int tokens, int h
 int hb_hc_gate_mean(const void* gate, const void* normed, void* mixed, int tokens, int hc, int h, void* stream);
 int hb_hc_inject(const void* hyper, const void* block_out, const void* inject_logits, void* out, int tokens, int hc,
                  int h, void* stream);
+// Sparse-attention indexer (csrc/qsa.cu).
+int hb_qsa_compress(const void* raw_k, void* ckey, const void* kv_indices, long long ld_idx, const void* seq_rows,
+                    const void* grp_indptr, const void* grp_first, int batch, int total_groups, int ratio,
+                    const void* norm_w, float eps, const void* inv_freq, int rot, void* stream);
+int hb_qsa_score(const void* q, int rows, int heads, const void* ckey, const void* kv_indices, long long ld_idx,
+                 const void* row_seq, const void* row_pos, int ratio, int max_groups, void* scores, void* stream);
+int hb_qsa_expand(const void* chosen, const void* chosen_scores, int rows, int width, const void* kv_indices,
+                  long long ld_idx, const void* row_seq, const void* row_pos, int ratio, void* sel, long long ld_sel,
+                  void* sel_len, void* stream);
 void hb_clear_tmap_cache(void);
 // GEMM launches use programmatic dependent launch (weight prefetch overlaps the preceding kernel) when on.
 void hb_gemm_set_pdl(int on);
