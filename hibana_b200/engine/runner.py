@@ -233,9 +233,11 @@ class ModelRunner:
         h = self._forward(ids_d, ctx)
         if want == "none":
             return None
-        if want == "all_device":      # verify: argmax of every row and the pre-norm hidden states, left on device
+        if want in ("all_device", "logits_device"):
+            # verify: argmax (or the logits themselves, for relaxed / sampled acceptance) of every row and the
+            # pre-norm hidden states, left on the device
             logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
-            return sampling.argmax(logits), ctx.extras.get("hidden")
+            return (logits if want == "logits_device" else sampling.argmax(logits)), ctx.extras.get("hidden")
         logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
         if sampling_rows is None or want == "all":
             tok = sampling.argmax(logits)

@@ -8,7 +8,10 @@ A round for requests whose pending token x_n sits at position n (KV committed fo
   3. verify: one ragged target forward over rows [x_n, d_1..d_k]; recurrent layers write to a scratch state slot and
      log their recurrence inputs;
   4. accept: longest prefix with d_{j+1} == target_j plus the target's own token (device kernel), truncated at stop
-     ids and the token budget;
+     ids and the token budget. Two other rules reuse that kernel by rewriting the "target" row it compares with:
+     relaxed greedy (`accept_top_k` / `accept_margin`: a draft within the target's top-K and within the margin of
+     the argmax counts as a match) and sampled acceptance for non-greedy requests (speculative sampling with the
+     MTP argmax as a one-hot draft law: accept with probability p[d], else draw from p without d; engine/rejection.py);
   5. commit: keep the accepted slots, replay exactly the accepted rows of every recurrent layer from the untouched
      committed state (same kernels, so the state is bitwise what a plain decode would have produced), refresh the MTP
      KV of accepted positions with the true target hiddens.
@@ -72,6 +75,43 @@ class SpecDecoder:
         tok = sampling.argmax(self.model.logits(normed))
         return g, tok
 
+    def _decide(self, reqs: Sequence[Request], logits: torch.Tensor, drafts: torch.Tensor) -> torch.Tensor:
+        """Per request, the token row the exact-match kernel compares the drafts with: the target argmax (exact
+        greedy), the drafts themselves where the relaxed rule accepts them, or the outcome of speculative
+        sampling. Nothing leaves the device."""
+        from . import rejection
+        b, k1, v = logits.shape
+        k = k1 - 1
+        dev = logits.device
+        flat = logits.reshape(b * k1, v)
+        out = sampling.argmax(flat).view(b, k1).clone()
+        greedy = torch.tensor([r.params.greedy for r in reqs], device=dev)
+        rel = torch.tensor([r.params.greedy and (r.params.accept_top_k > 1 or r.params.accept_margin > 0)
+                            for r in reqs], device=dev)
+        if bool(rel.any()) and k:
+            rank, gap = sampling.rank_gap(logits[:, :k].reshape(b * k, v).contiguous(), drafts.reshape(-1))
+            topk = torch.tensor([max(r.params.accept_top_k, 1) for r in reqs], device=dev)[:, None]
+            margin = torch.tensor([r.params.accept_margin for r in reqs], device=dev)[:, None]
+            ok = (rank.view(b, k) < topk) & ((gap.view(b, k) <= margin) | (rank.view(b, k) == 0)) & rel[:, None]
+            out[:, :k] = torch.where(ok, drafts, out[:, :k])
+        if not bool(greedy.all()):
+            temp = torch.tensor([r.params.temperature for r in reqs], device=dev).repeat_interleave(k1)
+            tk = torch.tensor([r.params.top_k for r in reqs], device=dev).repeat_interleave(k1)
+            tp = torch.tensor([r.params.top_p for r in reqs], device=dev).repeat_interleave(k1)
+            laws = rejection.distribution(flat, temp, tk, tp).view(b, k1, v)
+            q = torch.zeros(b, k, v, device=dev)
+            q.scatter_(2, drafts[:, :, None], 1.0)                       # the MTP head drafts its argmax
+            u = torch.empty(b, k1, 2)
+            for i, r in enumerate(reqs):                                 # counter-based: replay-safe
+                for j in range(k1):
+                    u[i, j, 0] = sampling.uniform01(r.seed, 2 * (r.draws + j) + 1)
+                    u[i, j, 1] = sampling.uniform01(r.seed, 2 * (r.draws + j) + 2)
+            u = u.to(dev)
+            ver = rejection.verify_batch(laws, q, drafts, u[..., 0].contiguous(), u[..., 1].contiguous(),
+                                         soft=torch.tensor([r.params.accept_soft for r in reqs], device=dev))
+            out = torch.where(greedy[:, None], out, ver.emitted)
+        return out
+
     @staticmethod
     def _starts(pos, indptr):
         return [int(pos[indptr[i]]) for i in range(len(indptr) - 1)]
@@ -131,9 +171,14 @@ class SpecDecoder:
                     self.scratch[r.rid] = ex.state_pool.alloc()
             extras["state_out"] = self._dev([self.scratch[r.rid] for r in reqs], torch.int32)
             extras["ring"] = []
+        relaxed = any(r.params.greedy and (r.params.accept_top_k > 1 or r.params.accept_margin > 0) for r in reqs)
+        sampled = any(not r.params.greedy for r in reqs)
         target, hidden = ex.runner.forward_rows(
             [r.table_row for r in reqs], tokens, n, [r.kv_slots[nn:nn + k + 1] for r, nn in zip(reqs, n)], mode=VERIFY,
-            want="all_device", state_slots=[r.state_slot for r in reqs] if has_state else None, extras=extras)
+            want="logits_device" if (relaxed or sampled) else "all_device",
+            state_slots=[r.state_slot for r in reqs] if has_state else None, extras=extras)
+        if relaxed or sampled:
+            target = self._decide(reqs, target.view(b, k + 1, -1), drafts)
         target = target.view(b, k + 1)
         # ---- accept (device), one small readback
         stops = torch.full((b, MAX_STOPS), -1, dtype=torch.int64)
