@@ -200,7 +200,7 @@ class Executor:
 
     def decode_step(self, reqs: Sequence[Request]) -> None:
         """One token for every running request (the pending token goes in, the next one comes out)."""
-        if self.spec is not None and all(r.params.greedy for r in reqs):
+        if self.spec is not None:     # greedy, relaxed and sampled requests all verify drafts (engine/spec.py)
             self.spec.round(reqs)
             self.stats["decode_steps"] += 1
             self.stats["decode_tokens"] += sum(r.rounds[-1] for r in reqs)

@@ -112,3 +112,31 @@ def test_tiny_hybrid_gpu_matches_cpu_and_graphs():
     assert [s[0] for s in spec] == [e[0] for e in eager] and agree >= 0.7 * 64
     from hibana_b200 import _native as nv
     assert nv.read_status() == 0
+
+
+def test_relaxed_and_sampled_acceptance_cpu():
+    """Relaxed greedy accepts at least as many drafts as exact greedy; sampled requests run through speculative
+    sampling, reproducibly for a fixed seed, and keep every bookkeeping invariant."""
+    t = tiny_hybrid_moe()
+    m = HybridModel(t, "cpu", seed=0)
+    prompts = _workload(t, n=3)
+
+    def run(params):
+        ex = Executor(m, max_batch=4, max_ctx=160, use_graphs=False)
+        ex.enable_spec(2)
+        out = [r.output_ids for r in ex.generate_batch(prompts, params)]
+        ex.state.check()
+        st = ex.spec.stats.as_dict()
+        ex.state.cache.flush()
+        assert ex.kv.free_count == ex.kv.slots
+        return out, st
+
+    exact, s_exact = run(SamplingParams(max_tokens=24))
+    relaxed, s_rel = run(SamplingParams(max_tokens=24, accept_top_k=4, accept_margin=50.0))
+    assert s_rel["accepted"] >= s_exact["accepted"] and s_rel["tokens_per_round"] >= s_exact["tokens_per_round"]
+    assert [r[0] for r in relaxed] == [r[0] for r in exact] and all(len(r) == 24 for r in relaxed)
+    a, s_a = run(SamplingParams(max_tokens=24, temperature=0.8, top_k=20, top_p=0.95, seed=7))
+    b, _ = run(SamplingParams(max_tokens=24, temperature=0.8, top_k=20, top_p=0.95, seed=7))
+    c, _ = run(SamplingParams(max_tokens=24, temperature=0.8, top_k=20, top_p=0.95, seed=8))
+    assert a == b and a != c and all(len(r) == 24 for r in a)
+    assert s_a["rounds"] > 0 and all(0 <= tok < t.vocab for r in a for tok in r)
