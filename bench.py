@@ -161,6 +161,10 @@ def main() -> None:
             ex.prefill_batch([(r, prompt_len) for r in reqs[i:i + 2]])
         for _ in range(warmup):
             ex.decode_step(reqs)
+        torch.cuda.synchronize()
+        code = nv.read_status(dev)
+        if code != 0:       # a bounded wait ran out in some kernel: every further step would pay its limit again
+            raise SystemExit(f"device status {code} after warm-up; not timing a failing run")
         # e2e: public API, upload + graph + readback every step
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

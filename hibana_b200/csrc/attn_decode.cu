@@ -126,10 +126,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
 
   const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int g = p.hq / p.hkv;
-  const int row0 = p.q_indptr ? p.q_indptr[b] : b;
-  const int R = p.q_indptr ? p.q_indptr[b + 1] - row0 : 1;
+  const int row0 = p.q_indptr ? ldg_keep(p.q_indptr + b) : b;
+  const int R = p.q_indptr ? ldg_keep(p.q_indptr + b + 1) - row0 : 1;
   const int nq = R * g;   // <= 16 guaranteed by the host
-  const int ctx = p.ctx_len[b];
+  const int ctx = ldg_keep(p.ctx_len + b);
   const int per = (((ctx + p.splits - 1) / p.splits + KT - 1) / KT) * KT;
   const int k0 = split * per;
   const int k1 = min(ctx, k0 + per);
@@ -169,7 +169,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
     }
   }
 
-  const int* idx_row = p.kv_indices + static_cast<long long>(p.seq_rows ? p.seq_rows[b] : b) * p.ld_idx;
+  const int* idx_row = p.kv_indices + static_cast<long long>(p.seq_rows ? ldg_keep(p.seq_rows + b) : b) * p.ld_idx;
 
   // Issues the copies of this warp's `it`-th tile into its ring stage: one bulk tensor copy per column block of
   // K and of V when the tile's slots are KT consecutive pool rows, else a row-by-row cp.async gather. `tma_mode`
@@ -179,7 +179,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
   // that the index load's latency is not on the issue path.
   auto fetch_slot = [&](int it) -> int {
     const int base = k0 + (warp + it * DEC_WARPS) * KT;
-    return (warp + it * DEC_WARPS < ntiles && lane < KT && base + lane < k1) ? __ldg(idx_row + base + lane) : -1;
+    return (warp + it * DEC_WARPS < ntiles && lane < KT && base + lane < k1) ? ldg_keep(idx_row + base + lane) : -1;
   };
   auto issue = [&](int it, int my_slot) {
     const int tile = warp + it * DEC_WARPS;

@@ -214,8 +214,10 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
 
 // kEpiReturn: one thread per CTA reports in after its stores are fenced system-wide; the last CTA of the grid
 // publishes this rank's sequence number on every rank's return flag and re-arms the counter.
-__device__ __forceinline__ void ep_cta_done(const DevParams& p) {
-  __threadfence_system();
+// A CTA that wrote nothing (`wrote` false: an expert chunk past the expert's rows) skips the system-wide fence,
+// which costs microseconds over NVLink and would otherwise be paid by every empty chunk of the grid.
+__device__ __forceinline__ void ep_cta_done(const DevParams& p, bool wrote = true) {
+  if (wrote) __threadfence_system();
   const int total = static_cast<int>(gridDim.x * gridDim.y * gridDim.z);
   if (atomicAdd(p.ep_done, 1) == total - 1) {
     *p.ep_done = 0;
@@ -252,7 +254,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
   if (p.grp_cnt != nullptr) {
     const int e = blockIdx.z, cnt = p.grp_cnt[e];
     if (static_cast<int>(blockIdx.y) * BN >= cnt) {   // uniform: before any barrier or TMEM allocation
-      if (p.epilogue == kEpiReturn && threadIdx.x == 0) ep_cta_done(p);
+      if (p.epilogue == kEpiReturn && threadIdx.x == 0) ep_cta_done(p, false);
       return;
     }
     a_row0 = e * p.grp_rows_a + tile_a * BM;

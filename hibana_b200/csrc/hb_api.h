@@ -114,6 +114,12 @@ int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long 
                     const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
                     const void* q_indptr, void* out, int batch, int max_rows, int hq, int hkv, int d, float scale,
                     int causal, long long pool_slots, void* status, void* stream);
+int hb_attn_decode_tc(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
+                      long long head_stride, const void* kv_indices, long long ld_idx, const void* seq_rows,
+                      const void* ctx_len, const void* q_indptr, void* out, void* part_o, void* part_lse, int batch,
+                      int max_rows, int hq, int hkv, int d, int splits, float scale, int causal, long long pool_slots,
+                      void* status, void* stream);
+void hb_attn_decode_tc_profile(void* buf);
 void hb_attn_prefill_profile(void* buf);
 void hb_attn_decode_profile(void* buf);
 int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,

@@ -22,6 +22,8 @@ nv.register("hb_attn_paged", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I,
 nv.register("hb_attn_merge", [P, P, P, L, I, I, P])
 nv.register("hb_attn_decode", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, L, P, P])
 
+nv.register("hb_attn_decode_tc", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, L, P, P])
+nv.register("hb_attn_decode_tc_profile", [P], void=True)
 nv.register("hb_attn_prefill_profile", [P], void=True)
 nv.register("hb_attn_decode_profile", [P], void=True)
 nv.register("hb_attn_prefill", [P, P, P, L, L, P, L, P, P, P, P, I, I, I, I, I, Fl, I, L, P, P])
@@ -108,12 +110,17 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     fp8 = k_pool.dtype != torch.bfloat16
     if not fp8 and max_rows * (hq // hkv) <= 16 and d in (64, 128, 256):
         st = nv.device_state(q.device)
-        nv.check(nv.lib().hb_attn_decode(
-            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), k_pool.stride(1), kv_indices.data_ptr(),
-            kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), nv.ptr(q_indptr), out.data_ptr(),
-            workspace.part_o.data_ptr() if splits > 1 else None,
-            workspace.part_lse.data_ptr() if splits > 1 else None, b, max_rows, hq, hkv, d, splits, scale,
-            int(causal), k_pool.shape[0], st.status.data_ptr(), nv.stream()), "hb_attn_decode")
+        # HIBANA_DECODE_ATTN=tc selects the persistent tcgen05 kernel (head dim 128; csrc/attn_decode_tc.cu). It
+        # matches the mma.sync kernel in isolation (123 vs 122 us at 64 x 2304 keys) but not yet inside the 27B
+        # decode step (18.8 vs 15.8 ms per step), so the mma.sync kernel stays the default.
+        tc = d == 128 and os.environ.get("HIBANA_DECODE_ATTN", "mma") == "tc"
+        args = (q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), k_pool.stride(1),
+                kv_indices.data_ptr(), kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), nv.ptr(q_indptr),
+                out.data_ptr(), workspace.part_o.data_ptr() if splits > 1 else None,
+                workspace.part_lse.data_ptr() if splits > 1 else None, b, max_rows, hq, hkv, d, splits, scale,
+                int(causal), k_pool.shape[0], st.status.data_ptr())
+        fn = nv.lib().hb_attn_decode_tc if tc else nv.lib().hb_attn_decode
+        nv.check(fn(*args, nv.stream()), "hb_attn_decode")
         if splits > 1:
             nv.check(nv.lib().hb_attn_merge(workspace.part_o.data_ptr(), workspace.part_lse.data_ptr(),
                                             out.data_ptr(), t * hq, splits, d, nv.stream()), "hb_attn_merge")
@@ -133,3 +140,29 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         b, t, max_rows, hq, hkv, d, splits, scale, int(fp8), kv_scale, int(causal), nv.stream()), "hb_attn_paged",
              launches=2 if splits > 1 else 1)
     return out
+
+
+TC_PROFILE_FIELDS = ("producer_wait", "tiles_tma", "tiles_gather", "issuer_wait_full", "issuer_wait_p",
+                     "softmax_wait_s", "softmax_wait_pv", "epilogue", "softmax_total", "raises", "tiles", "ctas")
+
+
+class DecodeTcProfile:
+    """Role counters of the tcgen05 decode kernel (csrc/attn_decode_tc.cu), accumulated while the object lives."""
+
+    def __init__(self, device):
+        self.buf = torch.zeros(len(TC_PROFILE_FIELDS), dtype=torch.int64, device=device)
+        nv.lib().hb_attn_decode_tc_profile(self.buf.data_ptr())
+
+    def read(self) -> dict:
+        torch.cuda.synchronize(self.buf.device)
+        c = dict(zip(TC_PROFILE_FIELDS, self.buf.tolist()))
+        tiles, ctas = max(c["tiles"], 1), max(c["ctas"], 1)
+        out = {k: round(c[k] / tiles) for k in ("producer_wait", "issuer_wait_full", "issuer_wait_p",
+                                                "softmax_wait_s", "softmax_wait_pv")}
+        out.update(epilogue_per_cta=round(c["epilogue"] / ctas), total_per_cta=round(c["softmax_total"] / ctas),
+                   tiles_per_cta=round(tiles / ctas, 1), raises_per_tile=round(c["raises"] / tiles, 3),
+                   gather_share=round(c["tiles_gather"] / max(c["tiles_gather"] + c["tiles_tma"], 1), 3))
+        return out
+
+    def close(self) -> None:
+        nv.lib().hb_attn_decode_tc_profile(None)

@@ -10,6 +10,7 @@ from __future__ import annotations
 import argparse
 import ctypes
 import json
+import os
 
 import torch
 
@@ -65,11 +66,14 @@ def main() -> None:
         ws = attention.AttnWorkspace(b, hq, d, splits, dev)
         fn = lambda: attention.paged_attention(q, kp, vp, idx, ctx, splits=splits, workspace=ws, out=out)  # noqa
         flops = 4.0 * d * b * ctx_n * hq
+    kv_bytes = 2.0 * b * ctx_n * hkv * d * 2
     if args.once:
         fn()
         torch.cuda.synchronize()
         return
-    t = time_cuda(fn, iters=args.iters)
+    # decode: bursts of 20 launches per sample when the KV read per launch exceeds L2 (see time_cuda)
+    burst = 20 if args.mode == "decode" and kv_bytes > 256e6 else 1
+    t = time_cuda(fn, iters=args.iters, burst=burst)
     ms = t["median_ms"]
     roles = None
     if args.roles and args.mode == "prefill":
@@ -86,7 +90,6 @@ def main() -> None:
                  9: "producer_wait_landed", 10: "softmax_loop_total", 12: "softmax_load_scores",
                  13: "softmax_math", 14: "softmax_publish"}
         roles = {v: round(c[k] / tiles) for k, v in names.items()}
-    kv_bytes = 2.0 * b * ctx_n * hkv * d * 2
     res = {"mode": args.mode, "batch": b, "rows": rows, "ctx": ctx_n, "hq": hq, "hkv": hkv, "d": d,
            "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "kv_gbs": round(kv_bytes / ms / 1e6, 1),
            "peaks": peaks["source"]}
@@ -94,7 +97,12 @@ def main() -> None:
         res["frac_of_bf16_peak"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 3)
     else:
         res["frac_of_hbm"] = round(kv_bytes / ms / 1e6 / peaks["hbm_gbs"], 3)
-    if args.roles and args.mode == "decode":
+    if args.roles and args.mode == "decode" and d == 128 and os.environ.get("HIBANA_DECODE_ATTN", "mma") == "tc":
+        prof = attention.DecodeTcProfile(dev)
+        fn()
+        res["tc_cycles_per_tile"] = prof.read()
+        prof.close()
+    elif args.roles and args.mode == "decode":
         from .. import _native as nv
         buf = torch.zeros(8, dtype=torch.int64, device=dev)
         nv.lib().hb_attn_decode_profile(ctypes.c_void_p(buf.data_ptr()))

@@ -9,6 +9,8 @@ from typing import Callable
 
 import torch
 
+from .. import _native as nv
+
 _FLUSH: dict[int, torch.Tensor] = {}
 
 
@@ -22,11 +24,18 @@ def flush_l2() -> None:
     buf.zero_()
 
 
-def time_cuda(fn: Callable[[], None], warmup: int = 3, iters: int = 10, flush: bool = True) -> dict:
-    """Returns {'median_ms', 'min_ms', 'all_ms'} for fn() timed alone on the current stream."""
+def time_cuda(fn: Callable[[], None], warmup: int = 3, iters: int = 10, flush: bool = True, burst: int = 1) -> dict:
+    """Returns {'median_ms', 'min_ms', 'all_ms'} for fn() timed alone on the current stream. `burst` > 1 times that
+    many back-to-back calls per sample and reports the mean of each burst: on an idle GPU the first launch of a
+    sample starts tens of microseconds after the start event (host launch latency), which a ~100 us kernel would
+    otherwise carry in full; only for working sets larger than L2 (nothing is flushed inside a burst)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    # a kernel whose bounded wait ran out costs its full limit per launch: never time (or repeat) such a run
+    code = nv.read_status()
+    if code != 0:
+        raise RuntimeError(f"device status {code} after warm-up: a kernel gave up on a wait; not timing it")
     times = []
     for _ in range(iters):
         if flush:
@@ -34,10 +43,11 @@ def time_cuda(fn: Callable[[], None], warmup: int = 3, iters: int = 10, flush: b
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         start.record()
-        fn()
+        for _ in range(burst):
+            fn()
         end.record()
         torch.cuda.synchronize()
-        times.append(start.elapsed_time(end))
+        times.append(start.elapsed_time(end) / burst)
     return {"median_ms": statistics.median(times), "min_ms": min(times), "all_ms": times}
 
 

@@ -216,6 +216,23 @@ def test_tensor_core_decode_verify_rows(hq, hkv, d, rows, splits, contiguous):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("hq,hkv,rows", [(40, 8, [3, 1, 2, 3]), (16, 2, [2, 1, 1, 2]), (8, 8, [1, 1, 1, 1])])
+@pytest.mark.parametrize("splits", [1, 2, 5])
+@pytest.mark.parametrize("contiguous", [False, True, "slot-major"])
+def test_tcgen05_decode_kernel(hq, hkv, rows, splits, contiguous, monkeypatch):
+    """The persistent tcgen05 decode kernel (opt-in): ragged contexts, empty splits, multi-row verify, all layouts."""
+    monkeypatch.setenv("HIBANA_DECODE_ATTN", "tc")
+    ctxs = [40, 700, 129, 2500]
+    q, kp, vp, idx, ctx, indptr, sr = _attn_case(4, rows, ctxs, hq, hkv, 128, seed=7, contiguous=contiguous)
+    ref = attention.paged_attention(q, kp, vp, idx, ctx, q_indptr=indptr, max_rows=max(rows), seq_rows=sr)
+    got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(), q_indptr=indptr.cuda(),
+                                    max_rows=max(rows), seq_rows=sr.cuda(), splits=splits)
+    _close(got, ref, 2e-2)
+    from hibana_b200 import _native as nv
+    assert nv.read_status() == 0
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("hq,hkv,d", [(40, 8, 128), (4, 2, 64), (32, 2, 128), (3, 1, 64)])
 @pytest.mark.parametrize("contiguous", [False, True, "slot-major"])
 def test_tcgen05_prefill_attention(hq, hkv, d, contiguous):
