@@ -31,7 +31,6 @@ namespace {
 
 constexpr int PF_THREADS = 256;
 constexpr int PF_ROWS = 128;      // packed query rows per CTA
-constexpr int PF_KT = 128;        // keys per tile
 constexpr int PF_STAGES = 2;
 constexpr int PF_PRODUCERS = 96;  // warps 4, 5, 6
 
@@ -58,13 +57,14 @@ struct PfParams {
 
 template <int D>
 struct PfCfg {
+  static constexpr int KT = D > 128 ? 64 : 128;               // keys per tile (head dim 256: 64, to fit shared memory)
   static constexpr int HALVES = D / 64;                      // 64-element (128-byte) column blocks of a row
   static constexpr int Q_BYTES = PF_ROWS * D * 2;
-  static constexpr int KV_TILE = PF_KT * D * 2;              // one stage of K or of V
-  static constexpr int P_BYTES = PF_ROWS * PF_KT * 2;
+  static constexpr int KV_TILE = KT * D * 2;              // one stage of K or of V
+  static constexpr int P_BYTES = PF_ROWS * KT * 2;
   static constexpr int BAR_OFF = Q_BYTES + 2 * PF_STAGES * KV_TILE + P_BYTES;
   static constexpr int SMEM = BAR_OFF + 256 + 1024;
-  static constexpr int TMEM_COLS = 512;                      // S0 [0,128) S1 [128,256) O [256, 256 + D)
+  static constexpr int TMEM_COLS = 512;                      // S0 [0, KT) S1 [KT, 2 KT) O [2 KT, 2 KT + D)
   static constexpr float RESCALE_GAP = 8.f;                  // log2 units
 };
 
@@ -99,6 +99,7 @@ template <int D>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, const PfParams p) {
   using C = PfCfg<D>;
+  constexpr int KT = C::KT;
   constexpr int CPR = D / 8;   // 16-byte chunks per row
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -130,7 +131,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
   const int ctx = p.ctx_len[b];
   // keys [0, kmax) are visible to at least one row of the block
   const int kmax = p.causal ? min(ctx, ctx - R + tok0 + ntok) : ctx;
-  const int ntiles = (kmax + PF_KT - 1) / PF_KT;
+  const int ntiles = (kmax + KT - 1) / KT;
 
   if (tid == 0) {
     for (int s = 0; s < PF_STAGES; ++s) {
@@ -158,7 +159,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t o_tmem = tmem_base + 2 * PF_KT;
+  const uint32_t o_tmem = tmem_base + 2 * KT;
 
   if (warp >= 4 && warp < 7) {
     // ------------------------------------------------------------------ producers
@@ -182,14 +183,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
     // transaction bytes. Otherwise (fragmented pool, tail of the context) the warp gathers the rows with 16-byte
     // cp.async: the LSU path keeps only ~16 KB in flight per SM, an order of magnitude less than the TMA unit.
     const int pw = warp - 4;
-    constexpr int SB = (PF_KT / 32 + 2) / 3;   // sub-blocks per warp and tile
+    constexpr int SB = (KT / 32 + 2) / 3;   // sub-blocks per warp and tile
     // Slot ids of this warp's sub-blocks of tile t (one per lane); -1 beyond the visible keys.
     auto fetch_slots = [&](int t, int (&sl)[SB]) {
 #pragma unroll
       for (int i = 0; i < SB; ++i) {
         const int j = pw + 3 * i;
-        const int key = t * PF_KT + j * 32 + lane;
-        sl[i] = (j < PF_KT / 32 && t < ntiles && key < kmax) ? __ldg(idx_row + key) : -1;
+        const int key = t * KT + j * 32 + lane;
+        sl[i] = (j < KT / 32 && t < ntiles && key < kmax) ? __ldg(idx_row + key) : -1;
       }
     };
     auto copy_tile = [&](int t, const int (&sl)[SB], const __nv_bfloat16* pool, const CUtensorMap* tm, uint8_t* ring,
@@ -198,7 +199,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
 #pragma unroll
       for (int i = 0; i < SB; ++i) {
         const int j = pw + 3 * i;
-        if (j >= PF_KT / 32) break;
+        if (j >= KT / 32) break;
         const int slot = sl[i];
         const int slot0 = __shfl_sync(0xffffffffu, slot, 0);
         const bool run = p.use_tma && __all_sync(0xffffffffu, slot >= 0 && slot == slot0 + lane);
@@ -207,14 +208,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
             mbar_add_tx(bar, 32 * D * 2);   // bytes only: this lane's arrival comes with the other producers'
 #pragma unroll
             for (int h = 0; h < C::HALVES; ++h)
-              tma_load_2d(tile + h * (PF_KT * 128) + j * (32 * 128), tm, bar, kvh * p.tma_xh + h * 64,
+              tma_load_2d(tile + h * (KT * 128) + j * (32 * 128), tm, bar, kvh * p.tma_xh + h * 64,
                           kvh * p.tma_yh + slot0);
           }
         } else {
           // lane -> (row = i * (32 / CPR) + lane / CPR, 16-byte column = lane % CPR)
           constexpr int RPI = 32 / CPR;
           const int part = lane % CPR;
-          const uint32_t dst0 = smem_u32(tile) + (part >> 3) * (PF_KT * 128);
+          const uint32_t dst0 = smem_u32(tile) + (part >> 3) * (KT * 128);
 #pragma unroll
           for (int ii = 0; ii < 32 / RPI; ++ii) {
             const int rr = ii * RPI + lane / CPR;
@@ -288,7 +289,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
   } else if (warp == 7) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = make_idesc_bf16(PF_ROWS, PF_KT);
+      constexpr uint32_t idesc_qk = make_idesc_bf16(PF_ROWS, KT);
       constexpr uint32_t idesc_pv = make_idesc_bf16(PF_ROWS, D, 0, 1);
       const uint32_t q_a = smem_u32(q_s), p_a = smem_u32(p_s);
       // S(t) = Q K(t)^T into score buffer t % 2; releases the K stage and publishes the scores when done.
@@ -301,12 +302,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
         }
         tc_fence_after();
         const uint32_t k_a = smem_u32(k_s + s * C::KV_TILE);
-        const uint32_t s_t = tmem_base + (t & 1) * PF_KT;
+        const uint32_t s_t = tmem_base + (t & 1) * KT;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t in_row = (ks & 3) * 32;   // 16 elements = 32 bytes inside the 128-byte swizzled row
           mma_f16(s_t, make_desc_sw128(q_a + (ks >> 2) * (PF_ROWS * 128) + in_row),
-                  make_desc_sw128(k_a + (ks >> 2) * (PF_KT * 128) + in_row), idesc_qk, ks > 0 ? 1u : 0u);
+                  make_desc_sw128(k_a + (ks >> 2) * (KT * 128) + in_row), idesc_qk, ks > 0 ? 1u : 0u);
         }
         tc_commit(&kempty[s]);
         tc_commit(&s_ready[t & 1]);
@@ -329,10 +330,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
         tc_fence_after();
         const uint32_t v_a = smem_u32(v_s + s * C::KV_TILE);
 #pragma unroll
-        for (int kk = 0; kk < PF_KT / 16; ++kk) {
+        for (int kk = 0; kk < KT / 16; ++kk) {
           const uint64_t adesc = make_desc_sw128(p_a + (kk >> 2) * (PF_ROWS * 128) + (kk & 3) * 32);
-          // 16 keys = two 8-row groups 1024 bytes apart; the D / 64 column blocks are PF_KT * 128 bytes apart
-          const uint64_t bdesc = make_desc_sw128_mn(v_a + kk * 2048, PF_KT * 128, 1024);
+          // 16 keys = two 8-row groups 1024 bytes apart; the D / 64 column blocks are KT * 128 bytes apart
+          const uint64_t bdesc = make_desc_sw128_mn(v_a + kk * 2048, KT * 128, 1024);
           mma_f16(o_tmem, adesc, bdesc, idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
         }
         tc_commit(&vempty[s]);
@@ -363,8 +364,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
         PF_ACC(0, tid == 0);
       }
       tc_fence_after();
-      const int k0 = t * PF_KT;
-      const uint32_t s_t = tmem_base + (t & 1) * PF_KT + tlane;
+      const int k0 = t * KT;
+      const uint32_t s_t = tmem_base + (t & 1) * KT + tlane;
       // The two passes over the score row are rolled loops over 32-column chunks: fully unrolled, the softmax body
       // alone is several thousand instructions, and streaming that through the instruction cache every tile cost
       // more than the arithmetic. `rel` = last visible column of this tile for this row (>= 127: no masking).
@@ -372,7 +373,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
       const long long t_math = p.prof ? clock64() : 0;
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
-      for (int c0 = 0; c0 < PF_KT; c0 += 32) {
+      for (int c0 = 0; c0 < KT; c0 += 32) {
         uint32_t v[32];
         tmem_ld_32x32(s_t + c0, v);
         tmem_ld_wait();
@@ -414,7 +415,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_consta
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-      for (int c0 = 0; c0 < PF_KT; c0 += 32) {
+      for (int c0 = 0; c0 < KT; c0 += 32) {
         uint32_t v[32];
         tmem_ld_32x32(s_t + c0, v);
         tmem_ld_wait();
@@ -554,6 +555,7 @@ int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long 
   }
   if (d == 64) return launch_prefill<64>(p, tk, tv, qblocks, batch, st);
   if (d == 128) return launch_prefill<128>(p, tk, tv, qblocks, batch, st);
+  if (d == 256) return launch_prefill<256>(p, tk, tv, qblocks, batch, st);
   return 1;
 }
 

@@ -81,6 +81,8 @@ struct DevParams {
   const int* grp_start;   // [E] first row of the expert's segment in the sorted activation buffer (multiple of 128)
   const int* grp_cnt;     // [E] rows routed to the expert
   int grp_rows_a;         // weight rows per expert (multiple of 128)
+  const int* grp_tiles;   // optional work list: expert * 4096 + chunk (then grid.y = list slot, grid.z = 1)
+  const int* grp_ntiles;
   // peer fusion
   int peer_on, world, rank, rows_per_rank;
   uint8_t* peer_base[8];
@@ -252,15 +254,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
   int a_row0 = tile_a * BM, b_row0 = tile_b * BN, row_lim = p.ra, col_lim = p.rb;
   const float* alpha_ptr = p.alpha_ptr;
   if (p.grp_cnt != nullptr) {
-    const int e = blockIdx.z, cnt = p.grp_cnt[e];
-    if (static_cast<int>(blockIdx.y) * BN >= cnt) {   // uniform: before any barrier or TMEM allocation
+    int e = blockIdx.z, chunk = blockIdx.y;
+    if (p.grp_tiles != nullptr) {
+      if (static_cast<int>(blockIdx.y) >= *p.grp_ntiles) return;   // uniform, before any barrier or TMEM allocation
+      const int code = p.grp_tiles[blockIdx.y];
+      e = code >> 12;
+      chunk = code & 4095;
+    }
+    const int cnt = p.grp_cnt[e];
+    if (chunk * BN >= cnt) {   // uniform: before any barrier or TMEM allocation
       if (p.epilogue == kEpiReturn && threadIdx.x == 0) ep_cta_done(p, false);
       return;
     }
     a_row0 = e * p.grp_rows_a + tile_a * BM;
-    b_row0 = p.grp_start[e] + blockIdx.y * BN;
+    b_row0 = p.grp_start[e] + chunk * BN;
     row_lim = p.grp_rows_a;
-    col_lim = b_row0 + min(BN, cnt - static_cast<int>(blockIdx.y) * BN);
+    col_lim = b_row0 + min(BN, cnt - chunk * BN);
     if (alpha_ptr != nullptr) alpha_ptr += e;
     split = 0;
     tile_b = 0;
@@ -816,6 +825,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   p.ka_a = a.sf_k_atoms_a; p.ka_b = a.sf_k_atoms_b;
   out_dims(a, &p.out_rows, &p.out_cols);
   p.grp_start = a.grp_start; p.grp_cnt = a.grp_cnt; p.grp_rows_a = a.grp_rows_a;
+  p.grp_tiles = grouped && a.ep == nullptr ? a.grp_tiles : nullptr; p.grp_ntiles = a.grp_ntiles;
   p.peer_on = a.peer != nullptr;
   p.flag_offset = -1;
   if (a.peer != nullptr) {
@@ -842,7 +852,9 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   } else if (a.epilogue == kEpiReturn) {
     return cudaErrorInvalidValue;
   }
-  const dim3 grid = grouped ? dim3(a.grp_rows_a / BM, a.grp_chunks, a.grp_experts) : dim3(tiles_a, tiles_b, splits);
+  const dim3 grid = !grouped ? dim3(tiles_a, tiles_b, splits)
+                    : p.grp_tiles != nullptr ? dim3(a.grp_rows_a / BM, a.grp_tile_cap > 0 ? a.grp_tile_cap : 1, 1)
+                                             : dim3(a.grp_rows_a / BM, a.grp_chunks, a.grp_experts);
 
 #define HB_DISPATCH(KIND)                                                        \
   switch (a.bn) {                                                                \
@@ -918,7 +930,7 @@ int hb_gemm_peer(int kind, const void* a, const void* b, const void* sfa, const 
 int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int experts,
                     int n_per_expert, int b_rows, int k, void* out, long long ldo, const void* alpha_ptr,
                     int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status, int ka_a,
-                    int ka_b, int bn_hint, void* stream) {
+                    int ka_b, int bn_hint, const void* tiles, const void* n_tiles, int tile_cap, void* stream) {
   hb::GemmArgs g;
   // `bn_hint` (0 = none) sizes the token tile for the EXPECTED rows per expert; the grid still covers
   // max_rows_per_expert, chunks beyond an expert's rows exit at once.
@@ -933,6 +945,11 @@ int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, con
   g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
   g.grp_start = static_cast<const int*>(start); g.grp_cnt = static_cast<const int*>(cnt);
   g.grp_rows_a = n_per_expert; g.grp_experts = experts; g.grp_chunks = (max_rows_per_expert + bn - 1) / bn;
+  // the work list was built for one tile width (hb_moe_plan's `bn`); it is used only when that is the width chosen
+  if (tiles != nullptr && n_tiles != nullptr && tile_cap > 0 && bn == bn_hint && g.grp_chunks <= 4096) {
+    g.grp_tiles = static_cast<const int*>(tiles); g.grp_ntiles = static_cast<const int*>(n_tiles);
+    g.grp_tile_cap = tile_cap;
+  }
   g.peer = nullptr;
   const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : static_cast<int>(e);

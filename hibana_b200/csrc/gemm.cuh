@@ -81,6 +81,11 @@ struct GemmArgs {
   const int* grp_start;
   const int* grp_cnt;
   int grp_rows_a, grp_experts, grp_chunks;
+  // optional compact work list (see hb_moe_plan): grp_tiles[i] = expert * 4096 + chunk for i < *grp_ntiles; the grid
+  // then has grp_tile_cap entries instead of experts * chunks, most of which would find nothing to do
+  const int* grp_tiles = nullptr;
+  const int* grp_ntiles = nullptr;
+  int grp_tile_cap = 0;
   const GemmPeer* peer;     // null = no peer fusion
   const GemmEp* ep = nullptr;   // null = no expert-parallel fusion (grouped mode only)
   const float* tok_scale = nullptr;   // optional per-token factor (dynamic per-row activation scale): indexed by

@@ -17,7 +17,7 @@ int hb_gemm(int kind, const void* a, const void* b, const void* sfa, const void*
 int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int experts,
                     int n_per_expert, int b_rows, int k, void* out, long long ldo, const void* alpha_ptr,
                     int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status, int ka_a,
-                    int ka_b, int bn_hint, void* stream);
+                    int ka_b, int bn_hint, const void* tiles, const void* n_tiles, int tile_cap, void* stream);
 int hb_gemm_peer(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int m, int n, int k,
                  void* out, long long ldo, const void* alpha_ptr, int epilogue, const void* const* peer_bases,
                  int world, int rank, int rows_per_rank, long long stage_offset, long long counter_offset,
@@ -114,6 +114,9 @@ int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long 
                     const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
                     const void* q_indptr, void* out, int batch, int max_rows, int hq, int hkv, int d, float scale,
                     int causal, long long pool_slots, void* status, void* stream);
+int hb_gdn_chunk_pass(const void* w, const void* qg, const void* kd, const void* m, const void* u, const void* g_end,
+                      const void* s_in, void* s_out, void* o, long long ldo, int heads, int nc, int n, int kdim,
+                      int vdim, void* stream);
 int hb_attn_decode_tc(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
                       long long head_stride, const void* kv_indices, long long ld_idx, const void* seq_rows,
                       const void* ctx_len, const void* q_indptr, void* out, void* part_o, void* part_lse, int batch,
@@ -147,7 +150,7 @@ int hb_rank_gap(const void* logits, long long ld, int rows, int vocab, int is_f3
 // ---- recurrent layers (ssm.cu) ---------------------------------------------------------------------------
 int hb_conv1d(const void* x, long long ldx, const void* w, const void* bias, void* y, long long ldy, void* state,
               long long state_stride, const void* q_indptr, const void* slot_in, const void* slot_out,
-              const void* has_init, int batch, int channels, int width, int act_silu, void* stream);
+              const void* has_init, int batch, int channels, int width, int act_silu, int max_rows, void* stream);
 int hb_mamba2_scan_fmt(const void* x, const void* bmat, const void* cmat, const void* dt, long long ldx,
                        long long ldb, long long lddt, const void* a_log, const void* dt_bias, const void* dskip,
                        void* y, long long ldy, void* state, long long state_stride, const void* q_indptr,
@@ -188,7 +191,8 @@ int hb_barrier(const void* const* peer_bases, int world, int rank, int slot, lon
 int hb_moe_route(const void* logits, long long ld, const void* sel_bias, int tokens, int experts, int topk,
                  int sigmoid, int renorm, float scale, void* ids, void* weights, void* stream);
 int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, int e_n, void* cnt, void* start,
-                void* pos, void* src_row, int rows_cap, void* total_rows, void* stream);
+                void* pos, void* src_row, int rows_cap, void* total_rows, int tile_bn, void* tiles, void* n_tiles,
+                int tile_cap, void* stream);
 int hb_moe_gather(const void* x, long long ldx, const void* src_row, const void* total_rows, void* out, int rows_cap,
                   int h, void* stream);
 int hb_moe_combine(const void* y, long long ldy, const void* pos, const void* weights, const void* shared,

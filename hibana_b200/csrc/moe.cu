@@ -118,8 +118,9 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* __restrict__ ids, int pairs, int topk, int experts, int e_lo, int e_n,
                 int* __restrict__ cnt, int* __restrict__ start, int* __restrict__ pos, int* __restrict__ src_row,
-                int rows_cap, int* __restrict__ total_rows) {
-  extern __shared__ int sm[];   // [experts] counts, [experts] starts
+                int rows_cap, int* __restrict__ total_rows, int tile_bn, int* __restrict__ tiles,
+                int* __restrict__ n_tiles, int tile_cap) {
+  extern __shared__ int sm[];   // [experts] counts, [experts] starts, [experts] running, [warps][experts]
   int* c = sm;
   int* s = sm + experts;
   for (int e = threadIdx.x; e < experts; e += blockDim.x) c[e] = 0;
@@ -142,28 +143,68 @@ moe_plan_kernel(const int* __restrict__ ids, int pairs, int topk, int experts, i
     cnt[e] = c[e];
     start[e] = s[e];
   }
+  // Work list of the grouped GEMMs: one entry (expert * 4096 + chunk) per tile of `tile_bn` rows that has rows.
+  if (tiles != nullptr) {
+    int* tb = s + experts;   // scratch (reused as the running counts below)
+    if (threadIdx.x == 0) {
+      int acc = 0;
+      for (int e = 0; e < experts; ++e) {
+        tb[e] = acc;
+        acc += (c[e] + tile_bn - 1) / tile_bn;
+      }
+      *n_tiles = acc < tile_cap ? acc : tile_cap;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+      const int nt = (c[e] + tile_bn - 1) / tile_bn;
+      for (int k = 0; k < nt; ++k)
+        if (tb[e] + k < tile_cap) tiles[tb[e] + k] = e * 4096 + k;
+    }
+    __syncthreads();
+  }
   for (int r = threadIdx.x; r < rows_cap; r += blockDim.x) src_row[r] = -1;
   __syncthreads();
-  // Deterministic positions: thread e walks the pairs in order and numbers its own.
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-    if (c[e] == 0) continue;
-    int n = 0;
-    const int base = s[e];
-    for (int i = 0; i < pairs; ++i) {
-      if (ids[i] == e) {
-        const int r = base + n++;
+  // Deterministic positions (pairs of an expert keep their order): chunks of blockDim.x pairs; inside a chunk a
+  // warp ranks its 32 pairs by expert with match_any, per-warp counts are prefix-summed over the warps, and a
+  // running count per expert carries from chunk to chunk.
+  int* run = s + experts;                 // [experts] rows handed out so far
+  int* wc = run + experts;                // [warps][experts] pairs of this chunk per warp and expert
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) run[e] = 0;
+  for (int base = 0; base < pairs; base += blockDim.x) {
+    for (int k = threadIdx.x; k < warps * experts; k += blockDim.x) wc[k] = 0;
+    __syncthreads();
+    const int i = base + threadIdx.x;
+    int e = i < pairs ? ids[i] : -1;
+    if (e < e_lo || e >= e_lo + e_n) e = -1;
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) wc[warp * experts + e] = __popc(same);
+    __syncthreads();
+    for (int x = threadIdx.x; x < experts; x += blockDim.x) {   // exclusive prefix over warps, in place
+      int acc = run[x];
+      for (int w = 0; w < warps; ++w) {
+        const int v = wc[w * experts + x];
+        wc[w * experts + x] = acc;
+        acc += v;
+      }
+      run[x] = acc;
+    }
+    __syncthreads();
+    if (i < pairs) {
+      if (e >= 0) {
+        const int r = s[e] + wc[warp * experts + e] + rank;
         if (r < rows_cap) {
           pos[i] = r;
           src_row[r] = i / topk;
         } else {
           pos[i] = -1;
         }
+      } else {
+        pos[i] = -1;
       }
     }
-  }
-  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
-    const int e = ids[i];
-    if (e < e_lo || e >= e_lo + e_n) pos[i] = -1;
+    __syncthreads();
   }
 }
 
@@ -231,12 +272,22 @@ int hb_moe_route(const void* logits, long long ld, const void* sel_bias, int tok
 }
 
 int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, int e_n, void* cnt, void* start,
-                void* pos, void* src_row, int rows_cap, void* total_rows, void* stream) {
+                void* pos, void* src_row, int rows_cap, void* total_rows, int tile_bn, void* tiles, void* n_tiles,
+                int tile_cap, void* stream) {
   if (tokens <= 0) return 0;
-  moe_plan_kernel<<<1, 1024, 2 * experts * sizeof(int), ST(stream)>>>(
+  if (tiles != nullptr && (tile_bn < 16 || n_tiles == nullptr || tile_cap <= 0)) return 1;
+  const size_t smem = static_cast<size_t>(3 + 1024 / 32) * experts * sizeof(int);
+  static size_t attr = 0;
+  if (smem > 48 * 1024 && smem > attr) {
+    if (cudaFuncSetAttribute(moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+        cudaSuccess)
+      return 3;
+    attr = smem;
+  }
+  moe_plan_kernel<<<1, 1024, smem, ST(stream)>>>(
       static_cast<const int*>(ids), tokens * topk, topk, experts, e_lo, e_n, static_cast<int*>(cnt),
       static_cast<int*>(start), static_cast<int*>(pos), static_cast<int*>(src_row), rows_cap,
-      static_cast<int*>(total_rows));
+      static_cast<int*>(total_rows), tile_bn, static_cast<int*>(tiles), static_cast<int*>(n_tiles), tile_cap);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -62,6 +62,78 @@ __global__ void conv1d_kernel(const __nv_bfloat16* __restrict__ x, long long ldx
   }
 }
 
+// Prefill form: one thread per (sequence, channel, tile of CONV_TT tokens), so a long chunk is not walked serially.
+// The window of a tile's first token comes from the rows before it (or the stored state at the sequence start);
+// the new state is written by conv1d_state_kernel afterwards.
+constexpr int CONV_TT = 32;
+template <int W>
+__global__ void conv1d_tiled_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                    const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
+                                    __nv_bfloat16* __restrict__ y, long long ldy, __nv_bfloat16* __restrict__ state,
+                                    long long state_stride, const int* __restrict__ q_indptr,
+                                    const int* __restrict__ slot_in, const int* __restrict__ slot_out,
+                                    const int* __restrict__ has_init, int channels, int act_silu) {
+  const int b = blockIdx.z;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int r0 = q_indptr ? q_indptr[b] : b;
+  const int r1 = q_indptr ? q_indptr[b + 1] : b + 1;
+  const int t0 = r0 + blockIdx.y * CONV_TT;
+  if (t0 >= r1) return;
+  const int t1 = min(t0 + CONV_TT, r1);
+  const bool init = has_init == nullptr || has_init[b] != 0;
+  const __nv_bfloat16* sin = state + static_cast<long long>(slot_in[b]) * state_stride + static_cast<long long>(c) * (W - 1);
+  float win[W - 1];
+#pragma unroll
+  for (int j = 0; j < W - 1; ++j) {
+    const int t = t0 - (W - 1) + j;        // row of the j-th window entry; rows before r0 live in the state
+    if (t >= r0) win[j] = __bfloat162float(x[t * ldx + c]);
+    else win[j] = init ? __bfloat162float(sin[j + (t0 - r0)]) : 0.f;   // state holds rows r0-(W-1) .. r0-1
+  }
+  float wt[W];
+#pragma unroll
+  for (int j = 0; j < W; ++j) wt[j] = __bfloat162float(w[static_cast<long long>(c) * W + j]);
+  const float bs = bias ? __bfloat162float(bias[c]) : 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const float xv = __bfloat162float(x[t * ldx + c]);
+    float acc = bs + wt[W - 1] * xv;
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) acc += wt[j] * win[j];
+#pragma unroll
+    for (int j = 0; j < W - 2; ++j) win[j] = win[j + 1];
+    win[W - 2] = xv;
+    y[t * ldy + c] = __float2bfloat16(act_silu ? silu_f(acc) : acc);
+  }
+}
+
+// New window of every sequence after a tiled pass: the last W - 1 raw inputs (rows before the sequence start come
+// from the old state). One thread per (sequence, channel) reads everything it needs before it writes, so the input
+// and output slots may be the same.
+template <int W>
+__global__ void conv1d_state_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                    __nv_bfloat16* __restrict__ state, long long state_stride,
+                                    const int* __restrict__ q_indptr, const int* __restrict__ slot_in,
+                                    const int* __restrict__ slot_out, const int* __restrict__ has_init,
+                                    int channels) {
+  const int b = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int r0 = q_indptr ? q_indptr[b] : b;
+  const int r1 = q_indptr ? q_indptr[b + 1] : b + 1;
+  const bool init = has_init == nullptr || has_init[b] != 0;
+  const __nv_bfloat16* sin = state + static_cast<long long>(slot_in[b]) * state_stride + static_cast<long long>(c) * (W - 1);
+  __nv_bfloat16 win[W - 1];
+#pragma unroll
+  for (int j = 0; j < W - 1; ++j) {
+    const int t = r1 - (W - 1) + j;
+    if (t >= r0) win[j] = x[t * ldx + c];
+    else win[j] = init ? sin[j + (r1 - r0)] : __float2bfloat16(0.f);
+  }
+  __nv_bfloat16* so = state + static_cast<long long>(slot_out[b]) * state_stride + static_cast<long long>(c) * (W - 1);
+#pragma unroll
+  for (int j = 0; j < W - 1; ++j) so[j] = win[j];
+}
+
 struct MambaParams {
   const __nv_bfloat16* x;    // [T, heads * P]   (row pitch ldx)
   const __nv_bfloat16* bmat; // [T, groups * N]  (row pitch ldb)
@@ -305,9 +377,19 @@ extern "C" {
 
 int hb_conv1d(const void* x, long long ldx, const void* w, const void* bias, void* y, long long ldy, void* state,
               long long state_stride, const void* q_indptr, const void* slot_in, const void* slot_out,
-              const void* has_init, int batch, int channels, int width, int act_silu, void* stream) {
+              const void* has_init, int batch, int channels, int width, int act_silu, int max_rows, void* stream) {
   if (batch <= 0) return 0;
   if (width != 4) return 1;
+  if (max_rows > CONV_TT) {   // prefill: parallel over tiles of tokens, then the new windows
+    const dim3 tg((channels + 127) / 128, (max_rows + CONV_TT - 1) / CONV_TT, batch);
+    conv1d_tiled_kernel<4><<<tg, 128, 0, ST(stream)>>>(BF(x), ldx, BF(w), BF(bias), BFM(y), ldy, BFM(state),
+                                                       state_stride, IP(q_indptr), IP(slot_in), IP(slot_out),
+                                                       IP(has_init), channels, act_silu);
+    if (slot_out != nullptr)
+      conv1d_state_kernel<4><<<dim3((channels + 127) / 128, batch), 128, 0, ST(stream)>>>(
+          BF(x), ldx, BFM(state), state_stride, IP(q_indptr), IP(slot_in), IP(slot_out), IP(has_init), channels);
+    return cudaGetLastError() == cudaSuccess ? 0 : 2;
+  }
   const dim3 grid((channels + 127) / 128, batch);
   conv1d_kernel<4><<<grid, 128, 0, ST(stream)>>>(BF(x), ldx, BF(w), BF(bias), BFM(y), ldy, BFM(state), state_stride,
                                                  IP(q_indptr), IP(slot_in), IP(slot_out), IP(has_init), channels,

@@ -107,7 +107,8 @@ class MambaLayer:
         if "ring" in ctx.extras:      # verify: log the recurrence inputs so the accepted prefix can be replayed
             ctx.extras["ring"].append((self, (xbc, dt)))
         xbc = recurrent.conv1d(xbc, self.conv_w, self.conv_b, states.conv[li], ctx.state_slots, so,
-                               q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state, silu=True)
+                               q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state, silu=True,
+                               max_rows=ctx.max_rows if ctx.q_indptr is not None else 0)
         y = recurrent.mamba2_scan(xbc[:, :inner], xbc[:, inner:inner + gn], xbc[:, inner + gn:], dt, self.a_log,
                                   self.dt_bias, self.d_skip, states.ssm[li], ctx.state_slots, so,
                                   heads=t.mamba_heads, groups=t.mamba_groups, head_dim=t.mamba_head_dim,
@@ -160,12 +161,13 @@ class GdnLayer:
         if "ring" in ctx.extras:
             ctx.extras["ring"].append((self, (qkvz[:, :2 * self.qk + self.vd], g, beta)))
         qkv = recurrent.conv1d(qkvz[:, :2 * self.qk + self.vd], self.conv_w, None, states.conv[li], ctx.state_slots,
-                               so, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state, silu=True)
+                               so, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state, silu=True,
+                               max_rows=ctx.max_rows if ctx.q_indptr is not None else 0)
         z = qkvz[:, 2 * self.qk + self.vd:]
         o = recurrent.gdn_scan(qkv[:, :self.qk], qkv[:, self.qk:2 * self.qk], qkv[:, 2 * self.qk:], g, beta,
                                states.ssm[li], ctx.state_slots, so, k_heads=t.gdn_k_heads, v_heads=t.gdn_v_heads,
                                kdim=kd, vdim=kd, l2norm=True, q_indptr=ctx.q_indptr,
-                               has_init=ctx.has_initial_state)
+                               has_init=ctx.has_initial_state, host_rows=ctx.seq_starts_host)
         rows = o.shape[0]
         # per-head RMSNorm of the output, then the SiLU gate (norm before gate)
         w = self.norm_w.repeat(t.gdn_v_heads)

@@ -125,7 +125,7 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
             nv.check(nv.lib().hb_attn_merge(workspace.part_o.data_ptr(), workspace.part_lse.data_ptr(),
                                             out.data_ptr(), t * hq, splits, d, nv.stream()), "hb_attn_merge")
         return out
-    if not fp8 and d in (64, 128) and q_indptr is not None and os.environ.get("HIBANA_PREFILL_ATTN", "tc") == "tc":
+    if not fp8 and d in (64, 128, 256) and q_indptr is not None and os.environ.get("HIBANA_PREFILL_ATTN", "tc") == "tc":
         st = nv.device_state(q.device)
         nv.check(nv.lib().hb_attn_prefill(
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), k_pool.stride(1), kv_indices.data_ptr(),

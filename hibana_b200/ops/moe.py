@@ -20,10 +20,10 @@ from . import gemm, nvfp4
 
 P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
 nv.register("hb_moe_route", [P, L, P, I, I, I, I, I, Fl, P, P, P])
-nv.register("hb_moe_plan", [P, I, I, I, I, I, P, P, P, P, I, P, P])
+nv.register("hb_moe_plan", [P, I, I, I, I, I, P, P, P, P, I, P, I, P, P, I, P])
 nv.register("hb_moe_gather", [P, L, P, P, P, I, I, P])
 nv.register("hb_moe_combine", [P, L, P, P, P, L, P, L, I, I, I, P])
-nv.register("hb_gemm_grouped", [I, P, P, P, P, I, I, I, I, P, L, P, I, P, P, I, P, I, I, I, P])
+nv.register("hb_gemm_grouped", [I, P, P, P, P, I, I, I, I, P, L, P, I, P, P, I, P, I, I, I, P, P, I, P])
 nv.register("hb_quant_nvfp4_rows", [P, L, I, I, I, P, P, P, I, P, P, P])
 
 
@@ -224,6 +224,15 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
     rows_cap = ((t * topk + 127) // 128) * 128 + min(e_n, t * topk) * 128
     max_rows = min(t, 1 << 30)                  # an expert can receive every token once
     bn_hint = tile_hint(t * topk, e_n, max_rows, ew.fmt)
+    bn_full = 16
+    while bn_full < max_rows and bn_full < 256:
+        bn_full *= 2
+    bn_hint = min(bn_hint, bn_full)            # the tile width the grouped GEMMs will use
+    # compact (expert, chunk) work list: the GEMM grids cover the tiles that have rows, not experts x worst case
+    tile_cap = -(-(t * topk) // bn_hint) + min(e_n, t * topk)
+    tiles = torch.empty(tile_cap, dtype=torch.int32, device=dev)
+    n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    tl = (tiles.data_ptr(), n_tiles.data_ptr(), tile_cap)
     cnt = torch.empty(e, dtype=torch.int32, device=dev)
     start = torch.empty(e, dtype=torch.int32, device=dev)
     pos = torch.empty(t * topk, dtype=torch.int32, device=dev)
@@ -231,7 +240,8 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
     total = torch.empty(1, dtype=torch.int32, device=dev)
     st = nv.device_state(dev).status
     nv.check(lib.hb_moe_plan(ids.data_ptr(), t, topk, e, e_lo, e_n, cnt.data_ptr(), start.data_ptr(), pos.data_ptr(),
-                             src.data_ptr(), rows_cap, total.data_ptr(), nv.stream()), "hb_moe_plan")
+                             src.data_ptr(), rows_cap, total.data_ptr(), bn_hint, tiles.data_ptr(),
+                             n_tiles.data_ptr(), tile_cap, nv.stream()), "hb_moe_plan")
     n1, h_out = ew.n1, ew.fc2_rows
     epi1 = gemm.EPI_SILU_MUL if ew.act == "swiglu" else gemm.EPI_STORE
     mid_cols = ew.inter
@@ -244,14 +254,14 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
                                    rows_cap, h, nv.stream()), "hb_moe_gather")
         nv.check(lib.hb_gemm_grouped(kind, ew.fc1.data_ptr(), xs.data_ptr(), None, None, e, n1, rows_cap, h,
                                      h1.data_ptr(), h1.stride(0), None, epi1, start.data_ptr(), cnt.data_ptr(),
-                                     max_rows, st.data_ptr(), 0, 0, bn_hint, nv.stream()), "hb_gemm_grouped")
+                                     max_rows, st.data_ptr(), 0, 0, bn_hint, *tl, nv.stream()), "hb_gemm_grouped")
         mid = h1
         if ew.act == "relu2":
             from . import basic
             mid = basic.act_mul(h1, basic.ACT_RELU2)
         nv.check(lib.hb_gemm_grouped(kind, ew.fc2.data_ptr(), mid.data_ptr(), None, None, e, h_out, rows_cap,
                                      ew.inter, y.data_ptr(), y.stride(0), None, gemm.EPI_STORE, start.data_ptr(),
-                                     cnt.data_ptr(), max_rows, st.data_ptr(), 0, 0, bn_hint, nv.stream()), "hb_gemm_grouped")
+                                     cnt.data_ptr(), max_rows, st.data_ptr(), 0, 0, bn_hint, *tl, nv.stream()), "hb_gemm_grouped")
     else:
         q1, sf1 = nvfp4._alloc(rows_cap, h, dev)
         nv.check(lib.hb_quant_nvfp4_rows(x.data_ptr(), x.stride(0), rows_cap, h, sf1.shape[1],
@@ -260,7 +270,7 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         nv.check(lib.hb_gemm_grouped(1, ew.fc1.q.data_ptr(), q1.data_ptr(), ew.fc1.sf.data_ptr(), sf1.data_ptr(), e,
                                      n1, rows_cap, h, h1.data_ptr(), h1.stride(0), ew.fc1_alpha.data_ptr(), epi1,
                                      start.data_ptr(), cnt.data_ptr(), max_rows, st.data_ptr(), ew.fc1.ka,
-                                     sf1.shape[1], bn_hint, nv.stream()), "hb_gemm_grouped")
+                                     sf1.shape[1], bn_hint, *tl, nv.stream()), "hb_gemm_grouped")
         mid = h1
         if ew.act == "relu2":
             from . import basic
@@ -272,7 +282,7 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         nv.check(lib.hb_gemm_grouped(1, ew.fc2.q.data_ptr(), q2.data_ptr(), ew.fc2.sf.data_ptr(), sf2.data_ptr(), e,
                                      h_out, rows_cap, ew.inter, y.data_ptr(), y.stride(0), ew.fc2_alpha.data_ptr(),
                                      gemm.EPI_STORE, start.data_ptr(), cnt.data_ptr(), max_rows, st.data_ptr(),
-                                     ew.fc2.ka, sf2.shape[1], bn_hint, nv.stream()), "hb_gemm_grouped")
+                                     ew.fc2.ka, sf2.shape[1], bn_hint, *tl, nv.stream()), "hb_gemm_grouped")
     out = torch.empty(t, h_out, dtype=torch.bfloat16, device=dev)
     nv.check(lib.hb_moe_combine(y.data_ptr(), y.stride(0), pos.data_ptr(), weights.data_ptr(), nv.ptr(shared),
                                 shared.stride(0) if shared is not None else 0, out.data_ptr(), out.stride(0), t, topk,

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 import torch.nn.functional as F
@@ -17,10 +17,13 @@ import torch.nn.functional as F
 from .. import _native as nv
 
 P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
-nv.register("hb_conv1d", [P, L, P, P, P, L, P, L, P, P, P, P, I, I, I, I, P])
+nv.register("hb_conv1d", [P, L, P, P, P, L, P, L, P, P, P, P, I, I, I, I, I, P])
 nv.register("hb_mamba2_scan", [P, P, P, P, L, L, L, P, P, P, P, L, P, L, P, P, P, P, I, I, I, I, I, P])
 nv.register("hb_mamba2_scan_fmt", [P, P, P, P, L, L, L, P, P, P, P, L, P, L, P, P, P, P, I, I, I, I, I, I, P, ctypes.c_uint, P])
 nv.register("hb_gdn_scan", [P, P, P, P, P, L, L, P, L, P, L, P, P, P, P, I, I, I, I, I, Fl, I, P])
+
+
+CHUNKED_MIN_ROWS = 128      # prefill chunks at least this long use the chunked gated delta rule
 
 
 def _ranges(q_indptr, batch):
@@ -32,8 +35,9 @@ def _ranges(q_indptr, batch):
 
 def conv1d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
            slot_in: torch.Tensor, slot_out: Optional[torch.Tensor], *, q_indptr: Optional[torch.Tensor] = None,
-           has_init: Optional[torch.Tensor] = None, silu: bool = True) -> torch.Tensor:
-    """x [T, C] bf16 (may be a column slice), weight [C, W], state [slots, C, W-1] bf16 (raw inputs)."""
+           has_init: Optional[torch.Tensor] = None, silu: bool = True, max_rows: int = 0) -> torch.Tensor:
+    """x [T, C] bf16 (may be a column slice), weight [C, W], state [slots, C, W-1] bf16 (raw inputs). `max_rows`
+    (host bound on rows per sequence; 0 = unknown) lets prefill chunks run parallel over tiles of tokens."""
     t, c = x.shape
     w = weight.shape[1]
     batch = slot_in.shape[0]
@@ -42,7 +46,7 @@ def conv1d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
         nv.check(nv.lib().hb_conv1d(x.data_ptr(), x.stride(0), weight.data_ptr(), nv.ptr(bias), y.data_ptr(),
                                     y.stride(0), state.data_ptr(), state.stride(0), nv.ptr(q_indptr),
                                     slot_in.data_ptr(), nv.ptr(slot_out), nv.ptr(has_init), batch, c, w, int(silu),
-                                    nv.stream()), "hb_conv1d")
+                                    int(max_rows), nv.stream()), "hb_conv1d", launches=2 if max_rows > 32 else 1)
         return y
     y = torch.empty(t, c, dtype=x.dtype)
     wf = weight.float()
@@ -122,12 +126,24 @@ def mamba2_scan(x: torch.Tensor, bmat: torch.Tensor, cmat: torch.Tensor, dt: tor
 def gdn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
              state: torch.Tensor, slot_in: torch.Tensor, slot_out: Optional[torch.Tensor], *, k_heads: int,
              v_heads: int, kdim: int, vdim: int, scale: Optional[float] = None, l2norm: bool = True,
-             q_indptr: Optional[torch.Tensor] = None, has_init: Optional[torch.Tensor] = None) -> torch.Tensor:
+             q_indptr: Optional[torch.Tensor] = None, has_init: Optional[torch.Tensor] = None,
+             host_rows: Optional[Sequence[int]] = None) -> torch.Tensor:
     """Gated delta rule. q, k [T, k_heads*K] (same row pitch), v [T, v_heads*V] bf16; g (log decay), beta
-    [T, v_heads] fp32 contiguous; state [slots, v_heads, V, K] fp32. Returns o [T, v_heads*V] bf16."""
+    [T, v_heads] fp32 contiguous; state [slots, v_heads, V, K] fp32. Returns o [T, v_heads*V] bf16.
+    `host_rows` (rows per sequence, known on the host during prefill) lets long sequences take the chunked form
+    (ops/gdn_chunk.py): tensor-core work parallel over chunks instead of one serial step per token."""
     t = q.shape[0]
     batch = slot_in.shape[0]
     scale = kdim ** -0.5 if scale is None else scale
+    if nv.use_native(q) and host_rows is not None and max(host_rows) >= CHUNKED_MIN_ROWS:
+        from . import gdn_chunk
+        ranges, r = [], 0
+        for n in host_rows:
+            ranges.append((r, r + n))
+            r += n
+        return gdn_chunk.gdn_chunked(q, k, v, g, beta, state, slot_in, slot_out, k_heads=k_heads, v_heads=v_heads,
+                                     kdim=kdim, vdim=vdim, scale=scale, l2norm=l2norm, ranges=ranges,
+                                     has_init=None if has_init is None else has_init.tolist())
     if nv.use_native(q):
         assert q.stride(0) == k.stride(0) and g.is_contiguous() and beta.is_contiguous()
         o = torch.empty(t, v_heads * vdim, dtype=q.dtype, device=q.device)

@@ -233,7 +233,7 @@ def test_tcgen05_decode_kernel(hq, hkv, rows, splits, contiguous, monkeypatch):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("hq,hkv,d", [(40, 8, 128), (4, 2, 64), (32, 2, 128), (3, 1, 64)])
+@pytest.mark.parametrize("hq,hkv,d", [(40, 8, 128), (4, 2, 64), (32, 2, 128), (3, 1, 64), (24, 2, 256), (4, 4, 256)])
 @pytest.mark.parametrize("contiguous", [False, True, "slot-major"])
 def test_tcgen05_prefill_attention(hq, hkv, d, contiguous):
     """Ragged prefill / chunked prefill over cached prefixes: tile edges, partial query blocks, 1-row sequences."""
