@@ -19,7 +19,6 @@ namespace {
 
 constexpr int GC = 64;            // tokens per chunk
 constexpr int GK = 128;           // key dim
-constexpr int GV = 128;           // value dim of a head
 constexpr int VS = 32;            // value columns per CTA
 constexpr int P_K = GK * 2 + 16;  // row pitch (bytes) of the [64, 128] bf16 tiles
 constexpr int P_M = GC * 2 + 16;  // [64, 64] bf16
@@ -36,7 +35,7 @@ constexpr int OFF_ST = OFF_VN + GC * P_V;
 constexpr int G_SMEM = OFF_ST + GK * P_V;
 
 struct ChunkParams {
-  const __nv_bfloat16* w;     // [H, NC, 64, 128]
+  const __nv_bfloat16* w;     // [H, NC, 64, 128]; null: no W term (V' = U, the Mamba-2 / SSD recurrence)
   const __nv_bfloat16* qg;
   const __nv_bfloat16* kd;
   const __nv_bfloat16* m;     // [H, NC, 64, 64]
@@ -47,6 +46,7 @@ struct ChunkParams {
   __nv_bfloat16* o;           // rows of this sequence: o[row * ldo + h * 128 + v]
   long long ldo;
   int nc, n;
+  int vdim;                   // value columns of a head (multiple of 32): 128 for the delta rule, head dim for SSD
 };
 
 __device__ __forceinline__ void cp16g(uint32_t saddr, const void* g) {
@@ -87,6 +87,7 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const ChunkParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.x, v0 = blockIdx.y * VS;
   const int qr = lane >> 2, qc = (lane & 3) * 2;   // accumulator row / first column of this lane inside a tile
+  const int GV = p.vdim;
 
   auto load_chunk = [&](int c, int stage) {
     const long long tile = static_cast<long long>(h) * p.nc + c;
@@ -95,10 +96,11 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const ChunkParams p) {
     const uint8_t* gk = reinterpret_cast<const uint8_t*>(p.kd + tile * GC * GK);
     const uint8_t* gm = reinterpret_cast<const uint8_t*>(p.m + tile * GC * GC);
     const uint8_t* gu = reinterpret_cast<const uint8_t*>(p.u + tile * GC * GV + v0);
+    const bool has_w = p.w != nullptr;
     const uint32_t st = sb + stage * STAGE;
     for (int i = tid; i < GC * 16; i += 128) {
       const int r = i >> 4, ch = (i & 15) * 16;
-      cp16g(st + OFF_W + r * P_K + ch, gw + r * (GK * 2) + ch);
+      if (has_w) cp16g(st + OFF_W + r * P_K + ch, gw + r * (GK * 2) + ch);
       cp16g(st + OFF_Q + r * P_K + ch, gq + r * (GK * 2) + ch);
       cp16g(st + OFF_KD + r * P_K + ch, gk + r * (GK * 2) + ch);
     }
@@ -154,14 +156,15 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const ChunkParams p) {
 #pragma unroll
     for (int ks = 0; ks < GK / 16; ++ks) {
       uint32_t fw[4], fq[4], b[4][2];
-      ldsm_x4(fw, st + OFF_W + a_off + ks * 32);
       ldsm_x4(fq, st + OFF_Q + a_off + ks * 32);
       load_b32(b, sb + OFF_ST, ks * 16, lane);
+      if (p.w != nullptr) {
+        ldsm_x4(fw, st + OFF_W + a_off + ks * 32);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        mma16816(a1[j], fw, b[j][0], b[j][1]);
-        mma16816(a2[j], fq, b[j][0], b[j][1]);
+        for (int j = 0; j < 4; ++j) mma16816(a1[j], fw, b[j][0], b[j][1]);
       }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) mma16816(a2[j], fq, b[j][0], b[j][1]);
     }
     // ---- V' = U - W S^T, to shared memory as bf16
 #pragma unroll
@@ -236,28 +239,28 @@ __global__ void __launch_bounds__(128) gdn_chunk_kernel(const ChunkParams p) {
 
 extern "C" {
 
-// w, qg, kd bf16 [heads, nc, 64, 128]; m bf16 [heads, nc, 64, 64]; u fp32 [heads, nc, 64, 128]; g_end fp32
-// [heads, nc]; s_in / s_out fp32 [heads, 128, 128] (value row, key column; s_in null = zero state, s_out null = do
+// w (may be null: V' = U), qg, kd bf16 [heads, nc, 64, 128]; m bf16 [heads, nc, 64, 64]; u fp32 [heads, nc, 64, vdim];
+// g_end fp32 [heads, nc]; s_in / s_out fp32 [heads, vdim, 128] (value row, key column; s_in null = zero state, s_out null = do
 // not store); o bf16 rows of the sequence (pitch ldo elements), only rows < n are written.
 int hb_gdn_chunk_pass(const void* w, const void* qg, const void* kd, const void* m, const void* u, const void* g_end,
                       const void* s_in, void* s_out, void* o, long long ldo, int heads, int nc, int n, int kdim,
                       int vdim, void* stream) {
   using namespace hb;
-  if (kdim != GK || vdim != GV) return 1;
+  if (kdim != GK || vdim < VS || vdim % VS != 0) return 1;
   if (heads <= 0 || nc <= 0) return 0;
   ChunkParams p;
   p.w = static_cast<const __nv_bfloat16*>(w); p.qg = static_cast<const __nv_bfloat16*>(qg);
   p.kd = static_cast<const __nv_bfloat16*>(kd); p.m = static_cast<const __nv_bfloat16*>(m);
   p.u = static_cast<const float*>(u); p.g_end = static_cast<const float*>(g_end);
   p.s_in = static_cast<const float*>(s_in); p.s_out = static_cast<float*>(s_out);
-  p.o = static_cast<__nv_bfloat16*>(o); p.ldo = ldo; p.nc = nc; p.n = n;
+  p.o = static_cast<__nv_bfloat16*>(o); p.ldo = ldo; p.nc = nc; p.n = n; p.vdim = vdim;
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM) != cudaSuccess)
       return 3;
     attr = true;
   }
-  gdn_chunk_kernel<<<dim3(heads, GV / VS), 128, G_SMEM, static_cast<cudaStream_t>(stream)>>>(p);
+  gdn_chunk_kernel<<<dim3(heads, vdim / VS), 128, G_SMEM, static_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

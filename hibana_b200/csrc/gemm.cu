@@ -151,6 +151,7 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
           const long long o = static_cast<long long>(col) * p.ldo + row;
           float x = v[j] * alpha;
           if (p.epilogue == kEpiResidual) x += __bfloat162float(p.residual[o]);
+          if (p.epilogue == kEpiRelu2) x = x > 0.f ? x * x : 0.f;
           out[o] = __float2bfloat16(x);
         }
       }

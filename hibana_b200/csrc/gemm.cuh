@@ -24,6 +24,7 @@ enum GemmEpilogue : int {
   kEpiReturn = 5,     // expert-parallel fc2 (grouped, weights on the 128-row side): column j of the output (one
                       // routed row) is stored into the return buffer of the rank the row came from, at the row
                       // that rank asked for; when every CTA is done the kernel raises a flag on every rank
+  kEpiRelu2 = 6,      // out = max(alpha * acc, 0)^2            (bf16; weights on the 128-row side only)
 };
 
 // Peer-memory fusion arguments (all ranks pass the same offsets; pointers are this process's mappings).

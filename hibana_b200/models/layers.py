@@ -114,7 +114,7 @@ class MambaLayer:
                                   heads=t.mamba_heads, groups=t.mamba_groups, head_dim=t.mamba_head_dim,
                                   d_state=t.mamba_state, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state,
                                   state_scale=states.ssm_scale[li] if getattr(states, "ssm_scale", None) is not None
-                                  else None, sr_seed=ctx.extras.get("sr_seed", 0))
+                                  else None, sr_seed=ctx.extras.get("sr_seed", 0), host_rows=ctx.seq_starts_host)
         y = basic.gated_rmsnorm(y, z, self.norm_w, t.norm_eps, inner // t.mamba_groups)
         return self.out_proj(y)
 

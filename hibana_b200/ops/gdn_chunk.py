@@ -77,7 +77,7 @@ def state_pass_ref(ph: dict, s0: torch.Tensor) -> tuple[torch.Tensor, torch.Tens
     outs = []
     for c in range(ph["nc"]):
         st = s.transpose(1, 2)                             # [H, K, V]
-        vn = ph["u"][:, c] - ph["w"][:, c] @ st
+        vn = ph["u"][:, c] - ph["w"][:, c] @ st if ph.get("w") is not None else ph["u"][:, c]
         outs.append(ph["qg"][:, c] @ st + ph["m"][:, c] @ vn)
         s = ph["g_end"][:, c].exp()[:, None, None] * s + vn.transpose(1, 2) @ ph["kd"][:, c]
     return torch.stack(outs, 1), s
@@ -87,9 +87,10 @@ def _native_pass(ph: dict, s_in: Optional[torch.Tensor], s_out: Optional[torch.T
                  heads: int, kdim: int, vdim: int) -> None:
     """Phase 2 by csrc/gdn_chunk.cu: writes the sequence's output rows and the final state in place."""
     bf = torch.bfloat16
-    w, qg, kd, m = (ph[name].to(bf).contiguous() for name in ("w", "qg", "kd", "m"))
+    qg, kd, m = (ph[name].to(bf).contiguous() for name in ("qg", "kd", "m"))
+    w = ph["w"].to(bf).contiguous() if ph.get("w") is not None else None     # None: V' = U (Mamba-2 / SSD)
     u, g_end = ph["u"].contiguous(), ph["g_end"].contiguous()
-    nv.check(nv.lib().hb_gdn_chunk_pass(w.data_ptr(), qg.data_ptr(), kd.data_ptr(), m.data_ptr(), u.data_ptr(),
+    nv.check(nv.lib().hb_gdn_chunk_pass(nv.ptr(w), qg.data_ptr(), kd.data_ptr(), m.data_ptr(), u.data_ptr(),
                                         g_end.data_ptr(), nv.ptr(s_in), nv.ptr(s_out), o_rows.data_ptr(),
                                         o_rows.stride(0), heads, ph["nc"], ph["n"], kdim, vdim, nv.stream()),
              "hb_gdn_chunk_pass")

@@ -16,6 +16,7 @@ from .. import _native as nv
 from .nvfp4 import Nvfp4Tensor
 
 EPI_STORE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_STORE_F32 = 0, 1, 2, 3
+EPI_RELU2 = 6       # grouped (weights on the 128-row side) GEMMs only: out = relu(x)^2
 NUM_SMS = 148
 
 nv.register("hb_gemm_set_pdl", [nv.I], void=True)

@@ -243,7 +243,7 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
                              src.data_ptr(), rows_cap, total.data_ptr(), bn_hint, tiles.data_ptr(),
                              n_tiles.data_ptr(), tile_cap, nv.stream()), "hb_moe_plan")
     n1, h_out = ew.n1, ew.fc2_rows
-    epi1 = gemm.EPI_SILU_MUL if ew.act == "swiglu" else gemm.EPI_STORE
+    epi1 = gemm.EPI_SILU_MUL if ew.act == "swiglu" else gemm.EPI_RELU2 if ew.act == "relu2" else gemm.EPI_STORE
     mid_cols = ew.inter
     h1 = torch.empty(rows_cap, mid_cols if ew.act == "swiglu" else n1, dtype=torch.bfloat16, device=dev)
     y = torch.empty(rows_cap, h_out, dtype=torch.bfloat16, device=dev)
@@ -255,10 +255,7 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         nv.check(lib.hb_gemm_grouped(kind, ew.fc1.data_ptr(), xs.data_ptr(), None, None, e, n1, rows_cap, h,
                                      h1.data_ptr(), h1.stride(0), None, epi1, start.data_ptr(), cnt.data_ptr(),
                                      max_rows, st.data_ptr(), 0, 0, bn_hint, *tl, nv.stream()), "hb_gemm_grouped")
-        mid = h1
-        if ew.act == "relu2":
-            from . import basic
-            mid = basic.act_mul(h1, basic.ACT_RELU2)
+        mid = h1                                # the activation (SwiGLU or squared ReLU) ran in the GEMM epilogue
         nv.check(lib.hb_gemm_grouped(kind, ew.fc2.data_ptr(), mid.data_ptr(), None, None, e, h_out, rows_cap,
                                      ew.inter, y.data_ptr(), y.stride(0), None, gemm.EPI_STORE, start.data_ptr(),
                                      cnt.data_ptr(), max_rows, st.data_ptr(), 0, 0, bn_hint, *tl, nv.stream()), "hb_gemm_grouped")
@@ -271,10 +268,7 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
                                      n1, rows_cap, h, h1.data_ptr(), h1.stride(0), ew.fc1_alpha.data_ptr(), epi1,
                                      start.data_ptr(), cnt.data_ptr(), max_rows, st.data_ptr(), ew.fc1.ka,
                                      sf1.shape[1], bn_hint, *tl, nv.stream()), "hb_gemm_grouped")
-        mid = h1
-        if ew.act == "relu2":
-            from . import basic
-            mid = basic.act_mul(h1, basic.ACT_RELU2)
+        mid = h1                                # the activation (SwiGLU or squared ReLU) ran in the GEMM epilogue
         q2, sf2 = nvfp4._alloc(rows_cap, ew.inter, dev)
         nv.check(lib.hb_quant_nvfp4_rows(mid.data_ptr(), mid.stride(0), rows_cap, ew.inter, sf2.shape[1],
                                          ew.fc2_in_scale.data_ptr(), q2.data_ptr(), sf2.data_ptr(), 0, None,

@@ -69,13 +69,24 @@ def mamba2_scan(x: torch.Tensor, bmat: torch.Tensor, cmat: torch.Tensor, dt: tor
                 slot_in: torch.Tensor, slot_out: Optional[torch.Tensor], *, heads: int, groups: int, head_dim: int,
                 d_state: int, q_indptr: Optional[torch.Tensor] = None,
                 has_init: Optional[torch.Tensor] = None, state_scale: Optional[torch.Tensor] = None,
-                sr_seed: int = 0) -> torch.Tensor:
+                sr_seed: int = 0, host_rows: Optional[Sequence[int]] = None) -> torch.Tensor:
     """x [T, heads*P], bmat/cmat [T, groups*N], dt [T, heads] (bf16, column slices allowed);
     state [slots, heads, P, N] in fp32, fp16 (`sr_seed` != 0: stochastic rounding when the state is written back)
     or int8 with `state_scale` [slots, heads, P] fp32 row scales. Returns y [T, heads*P] bf16."""
     t = x.shape[0]
     batch = slot_in.shape[0]
     fmt = {torch.float32: 0, torch.float16: 1, torch.int8: 2}[state.dtype]
+    if (nv.use_native(x) and fmt == 0 and d_state == 128 and host_rows is not None
+            and max(host_rows) >= CHUNKED_MIN_ROWS):
+        # long prefill chunks: the chunked (SSD) form, parallel over 64-token chunks (ops/ssd_chunk.py)
+        from . import ssd_chunk
+        ranges, r = [], 0
+        for n in host_rows:
+            ranges.append((r, r + n))
+            r += n
+        return ssd_chunk.mamba2_chunked(x, bmat, cmat, dt, a_log, dt_bias, dskip, state, slot_in, slot_out,
+                                        heads=heads, groups=groups, head_dim=head_dim, d_state=d_state,
+                                        ranges=ranges, has_init=None if has_init is None else has_init.tolist())
     if nv.use_native(x):
         y = torch.empty(t, heads * head_dim, dtype=x.dtype, device=x.device)
         nv.check(nv.lib().hb_mamba2_scan_fmt(

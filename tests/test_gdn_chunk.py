@@ -60,3 +60,54 @@ def test_chunked_gpu_matches_sequential(rows):
                              k_heads=kh, v_heads=vh, kdim=kd, vdim=vd, q_indptr=indptr.cuda(),
                              has_init=has_init.cuda())
     assert (seq.float() - got.float()).abs().max().item() < 3e-2 * max(1.0, ref.float().abs().max().item())
+
+
+def _mamba_case(rows, heads, groups, p, n, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    t = sum(rows)
+    x = torch.randn(t, heads * p, generator=g).bfloat16()
+    bm = (torch.randn(t, groups * n, generator=g) * 0.3).bfloat16()
+    cm = (torch.randn(t, groups * n, generator=g) * 0.3).bfloat16()
+    dt = torch.randn(t, heads, generator=g).bfloat16()
+    a_log = torch.rand(heads, generator=g)
+    dt_bias = torch.randn(heads, generator=g) * 0.1
+    dskip = torch.randn(heads, generator=g)
+    state = torch.randn(2 * len(rows), heads, p, n, generator=g) * 0.1
+    indptr = torch.tensor([0] + list(torch.tensor(rows).cumsum(0)), dtype=torch.int32)
+    sin = torch.arange(len(rows), dtype=torch.int32)
+    return x, bm, cm, dt, a_log, dt_bias, dskip, state, indptr, sin, sin + len(rows)
+
+
+@pytest.mark.parametrize("rows", [[150], [64, 3, 129]])
+def test_ssd_chunked_matches_sequential_cpu(rows):
+    from hibana_b200.ops import ssd_chunk
+    heads, groups, p, n = 4, 2, 32, 16
+    x, bm, cm, dt, a_log, dtb, dsk, state, indptr, sin, sout = _mamba_case(rows, heads, groups, p, n)
+    has_init = torch.tensor([1, 0, 1][:len(rows)], dtype=torch.int32)
+    st_ref = state.clone()
+    ref = recurrent.mamba2_scan(x, bm, cm, dt, a_log, dtb, dsk, st_ref, sin, sout, heads=heads, groups=groups,
+                                head_dim=p, d_state=n, q_indptr=indptr, has_init=has_init)
+    st = state.clone()
+    got = ssd_chunk.mamba2_chunked(x, bm, cm, dt, a_log, dtb, dsk, st, sin, sout, heads=heads, groups=groups,
+                                   head_dim=p, d_state=n, ranges=recurrent._ranges(indptr, len(rows)),
+                                   has_init=has_init.tolist())
+    assert torch.allclose(got.float(), ref.float(), atol=3e-2, rtol=3e-2)
+    assert torch.allclose(st, st_ref, atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows", [[300], [128, 70, 513]])
+def test_ssd_chunked_gpu_matches_sequential(rows):
+    heads, groups, p, n = 8, 2, 64, 128
+    x, bm, cm, dt, a_log, dtb, dsk, state, indptr, sin, sout = _mamba_case(rows, heads, groups, p, n, seed=4)
+    has_init = torch.tensor([1, 0, 1][:len(rows)], dtype=torch.int32)
+    st_ref = state.clone()
+    ref = recurrent.mamba2_scan(x, bm, cm, dt, a_log, dtb, dsk, st_ref, sin, sout, heads=heads, groups=groups,
+                                head_dim=p, d_state=n, q_indptr=indptr, has_init=has_init)
+    st = state.cuda()
+    got = recurrent.mamba2_scan(x.cuda(), bm.cuda(), cm.cuda(), dt.cuda(), a_log.cuda(), dtb.cuda(), dsk.cuda(), st,
+                                sin.cuda(), sout.cuda(), heads=heads, groups=groups, head_dim=p, d_state=n,
+                                q_indptr=indptr.cuda(), has_init=has_init.cuda(), host_rows=rows)
+    scale = max(1.0, ref.float().abs().max().item())
+    assert (got.float().cpu() - ref.float()).abs().max().item() < 3e-2 * scale
+    assert torch.allclose(st.cpu(), st_ref, atol=3e-2, rtol=3e-2)
