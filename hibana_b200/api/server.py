@@ -58,6 +58,14 @@ def create_app(engine: EngineLoop, tokenizer, *, model_name: str = "hibana-b200"
     template = template or ChatTemplate()
     info = info or {}
     eos_id = getattr(tokenizer, "eos_id", None)
+    _gr: dict = {}
+
+    def grammars():
+        """Grammar compiler for this tokenizer, built on the first constrained request."""
+        if "g" not in _gr:
+            from ..engine.grammar import grammars_for
+            _gr["g"] = grammars_for(tokenizer, getattr(engine, "vocab", None) or tokenizer.vocab_size)
+        return _gr["g"]
 
     def _submit(prompt_ids, params) -> Ticket:
         return engine.submit(prompt_ids, params, eos_id=eos_id)
@@ -151,7 +159,7 @@ def create_app(engine: EngineLoop, tokenizer, *, model_name: str = "hibana-b200"
     # ---- SGLang-style generate
     async def generate(req, body):
         sp_body = dict(body.get("sampling_params") or {})
-        params = sampling_from(sp_body, tokenizer)
+        params = sampling_from(sp_body, tokenizer, grammars=grammars)
         ids = body.get("input_ids")
         if ids is None:
             if "text" not in body:
@@ -182,7 +190,7 @@ def create_app(engine: EngineLoop, tokenizer, *, model_name: str = "hibana-b200"
         prompt = body.get("prompt")
         if prompt is None:
             raise BadRequest("prompt required")
-        params = sampling_from(body, tokenizer)
+        params = sampling_from(body, tokenizer, grammars=grammars)
         ids = prompt if isinstance(prompt, list) and prompt and isinstance(prompt[0], int) else tokenizer.encode(
             prompt if isinstance(prompt, str) else "".join(prompt))
         n = int(body.get("n", 1))
@@ -232,7 +240,7 @@ def create_app(engine: EngineLoop, tokenizer, *, model_name: str = "hibana-b200"
         messages = body.get("messages")
         if not isinstance(messages, list) or not messages:
             raise BadRequest("messages required")
-        params = sampling_from(body, tokenizer)
+        params = sampling_from(body, tokenizer, grammars=grammars)
         tools = body.get("tools")
         ids, kwargs = _render(body, messages, tools)
         n = int(body.get("n", 1))
@@ -313,7 +321,7 @@ def create_app(engine: EngineLoop, tokenizer, *, model_name: str = "hibana-b200"
         b2 = dict(body)
         if "stop_sequences" in body:
             b2["stop"] = body["stop_sequences"]
-        params = sampling_from(b2, tokenizer)
+        params = sampling_from(b2, tokenizer, grammars=grammars)
         ids, _ = _render(body, messages, tools)
         ticket = _submit(ids, params)
         if body.get("stream"):

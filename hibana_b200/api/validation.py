@@ -23,7 +23,8 @@ def _num(body: dict, key: str, default, lo=None, hi=None, kind=float):
     return v
 
 
-def sampling_from(body: dict, tokenizer=None, default_max: int = 256, max_limit: int = 1 << 20) -> SamplingParams:
+def sampling_from(body: dict, tokenizer=None, default_max: int = 256, max_limit: int = 1 << 20,
+                  grammars=None) -> SamplingParams:
     """Accepts OpenAI names (max_tokens / max_completion_tokens, stop) and SGLang names (max_new_tokens,
     stop_token_ids) plus the engine's acceptance knobs."""
     max_tokens = body.get("max_tokens", body.get("max_completion_tokens", body.get("max_new_tokens", default_max)))
@@ -41,8 +42,19 @@ def sampling_from(body: dict, tokenizer=None, default_max: int = 256, max_limit:
     seed = body.get("seed")
     if seed is not None:
         seed = _num(body, "seed", None, 0, (1 << 63) - 1, int)
+    constraint = None
+    if grammars is not None:       # callable: builds the (cached) engine.grammar.Grammars on first use
+        from ..engine.grammar import constraint_from_body
+        wants = any(body.get(k) is not None for k in ("response_format", "json_schema", "regex", "ebnf")) or (
+            body.get("tools") and body.get("tool_choice") not in (None, "auto", "none"))
+        if wants:
+            try:
+                constraint = constraint_from_body(body, grammars() if callable(grammars) else grammars)
+            except Exception as e:     # malformed schema / grammar text
+                raise BadRequest(f"invalid output constraint: {e}") from None
     try:
         return SamplingParams(
+            constraint=constraint,
             temperature=temperature, top_k=_num(body, "top_k", 0, -1, 1 << 20, int) if body.get("top_k", 0) != -1 else 0,
             top_p=_num(body, "top_p", 1.0, 1e-6, 1.0), max_tokens=max_tokens, stop_ids=tuple(int(i) for i in stop_ids),
             ignore_eos=bool(body.get("ignore_eos", False)), seed=seed,

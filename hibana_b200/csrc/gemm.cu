@@ -257,7 +257,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
   if (p.grp_cnt != nullptr) {
     int e = blockIdx.z, chunk = blockIdx.y;
     if (p.grp_tiles != nullptr) {
-      if (static_cast<int>(blockIdx.y) >= *p.grp_ntiles) return;   // uniform, before any barrier or TMEM allocation
+      if (static_cast<int>(blockIdx.y) >= *p.grp_ntiles) {   // uniform, before any barrier or TMEM allocation
+        if (p.epilogue == kEpiReturn && threadIdx.x == 0) ep_cta_done(p, false);
+        return;
+      }
       const int code = p.grp_tiles[blockIdx.y];
       e = code >> 12;
       chunk = code & 4095;
@@ -826,7 +829,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   p.ka_a = a.sf_k_atoms_a; p.ka_b = a.sf_k_atoms_b;
   out_dims(a, &p.out_rows, &p.out_cols);
   p.grp_start = a.grp_start; p.grp_cnt = a.grp_cnt; p.grp_rows_a = a.grp_rows_a;
-  p.grp_tiles = grouped && a.ep == nullptr ? a.grp_tiles : nullptr; p.grp_ntiles = a.grp_ntiles;
+  p.grp_tiles = grouped ? a.grp_tiles : nullptr; p.grp_ntiles = a.grp_ntiles;
   p.peer_on = a.peer != nullptr;
   p.flag_offset = -1;
   if (a.peer != nullptr) {
@@ -964,7 +967,8 @@ int hb_gemm_grouped_ep(int kind, const void* a, const void* b, const void* sfa, 
                        int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status,
                        int ka_a, int ka_b, const void* const* bases, int world, int rank, const void* gate_flags,
                        const void* seq_ptr, const void* row_ret, long long ret_offset, void* done_counter,
-                       long long ret_flag_offset, long long limit_ns, int bn_hint, void* stream) {
+                       long long ret_flag_offset, long long limit_ns, int bn_hint, const void* tiles,
+                       const void* n_tiles, int tile_cap, void* stream) {
   hb::GemmArgs g;
   hb::GemmEp ep;
   int bn = 16;
@@ -984,6 +988,10 @@ int hb_gemm_grouped_ep(int kind, const void* a, const void* b, const void* sfa, 
   g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
   g.grp_start = static_cast<const int*>(start); g.grp_cnt = static_cast<const int*>(cnt);
   g.grp_rows_a = n_per_expert; g.grp_experts = experts; g.grp_chunks = (max_rows_per_expert + bn - 1) / bn;
+  if (tiles != nullptr && n_tiles != nullptr && tile_cap > 0 && bn == bn_hint && g.grp_chunks <= 4096) {
+    g.grp_tiles = static_cast<const int*>(tiles); g.grp_ntiles = static_cast<const int*>(n_tiles);
+    g.grp_tile_cap = tile_cap;
+  }
   g.peer = nullptr;
   g.ep = &ep;
   const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));

@@ -28,7 +28,8 @@ int hb_gemm_grouped_ep(int kind, const void* a, const void* b, const void* sfa, 
                        int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status,
                        int ka_a, int ka_b, const void* const* bases, int world, int rank, const void* gate_flags,
                        const void* seq_ptr, const void* row_ret, long long ret_offset, void* done_counter,
-                       long long ret_flag_offset, long long limit_ns, int bn_hint, void* stream);
+                       long long ret_flag_offset, long long limit_ns, int bn_hint, const void* tiles, const void* n_tiles,
+                       int tile_cap, void* stream);
 // Expert-parallel all-to-all (csrc/ep.cu); heaps come from hb_comm_alloc / hb_comm_ipc_open.
 int hb_ep_ctrl_bytes(void);
 void hb_ep_ctrl_layout(long long* out4);
@@ -193,6 +194,7 @@ int hb_moe_route(const void* logits, long long ld, const void* sel_bias, int tok
 int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, int e_n, void* cnt, void* start,
                 void* pos, void* src_row, int rows_cap, void* total_rows, int tile_bn, void* tiles, void* n_tiles,
                 int tile_cap, void* stream);
+int hb_moe_tiles(const void* cnt, int experts, int tile_bn, void* tiles, void* n_tiles, int tile_cap, void* stream);
 int hb_moe_gather(const void* x, long long ldx, const void* src_row, const void* total_rows, void* out, int rows_cap,
                   int h, void* stream);
 int hb_moe_combine(const void* y, long long ldy, const void* pos, const void* weights, const void* shared,

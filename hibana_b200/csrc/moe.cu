@@ -208,6 +208,27 @@ moe_plan_kernel(const int* __restrict__ ids, int pairs, int topk, int experts, i
   }
 }
 
+// Work list from per-expert row counts alone (for plans made elsewhere, e.g. the expert-parallel one): one entry
+// expert * 4096 + chunk per tile of `tile_bn` rows that has rows. Single CTA.
+__global__ void moe_tiles_kernel(const int* __restrict__ cnt, int experts, int tile_bn, int* __restrict__ tiles,
+                                 int* __restrict__ n_tiles, int tile_cap) {
+  extern __shared__ int base[];
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < experts; ++e) {
+      base[e] = acc;
+      acc += (cnt[e] + tile_bn - 1) / tile_bn;
+    }
+    *n_tiles = acc < tile_cap ? acc : tile_cap;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int nt = (cnt[e] + tile_bn - 1) / tile_bn;
+    for (int k = 0; k < nt; ++k)
+      if (base[e] + k < tile_cap) tiles[base[e] + k] = e * 4096 + k;
+  }
+}
+
 __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ src_row,
                                   const int* __restrict__ total_rows, __nv_bfloat16* __restrict__ out, int h) {
   const int r = blockIdx.x;
@@ -288,6 +309,14 @@ int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, in
       static_cast<const int*>(ids), tokens * topk, topk, experts, e_lo, e_n, static_cast<int*>(cnt),
       static_cast<int*>(start), static_cast<int*>(pos), static_cast<int*>(src_row), rows_cap,
       static_cast<int*>(total_rows), tile_bn, static_cast<int*>(tiles), static_cast<int*>(n_tiles), tile_cap);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_moe_tiles(const void* cnt, int experts, int tile_bn, void* tiles, void* n_tiles, int tile_cap, void* stream) {
+  if (experts <= 0 || tile_bn < 16 || tile_cap <= 0) return 1;
+  moe_tiles_kernel<<<1, 256, experts * sizeof(int), ST(stream)>>>(static_cast<const int*>(cnt), experts, tile_bn,
+                                                                  static_cast<int*>(tiles),
+                                                                  static_cast<int*>(n_tiles), tile_cap);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

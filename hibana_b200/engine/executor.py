@@ -117,6 +117,9 @@ class Executor:
             self.stats["cached_tokens"] += req.cached_len
         req.prefilled = req.cached_len
         req.state = State.PREFILL
+        if req.params.constraint is not None and req.grammar is None:
+            from .grammar import GrammarState
+            req.grammar = GrammarState(req.params.constraint, self.target.vocab)
 
     def release(self, req: Request) -> None:
         if req.table_row < 0:
@@ -174,8 +177,13 @@ class Executor:
             finals.append(req.prefilled + count >= target_len)
         any_final = any(finals)
         extras = {"want_hidden": True} if self.spec is not None else None
+        masks = None
+        if any_final and any(r.grammar is not None for r, _ in chunks):
+            from .grammar import stack_masks
+            masks = stack_masks([r.grammar.mask() if r.grammar is not None and not r.output_ids else None
+                                 for r, _ in chunks], (self.target.vocab + 31) // 32)
         out = self.runner.forward_rows(rows, toks, starts, slot_lists, mode=PREFILL,
-                                       want="last" if any_final else "none", extras=extras,
+                                       want="last" if any_final else "none", extras=extras, masks=masks,
                                        sampling_rows=_sampling_rows([r for r, _ in chunks]) if any_final else None,
                                        state_slots=[r.state_slot for r, _ in chunks]
                                        if self.state_pool is not None else None)
@@ -201,16 +209,24 @@ class Executor:
     def decode_step(self, reqs: Sequence[Request]) -> None:
         """One token for every running request (the pending token goes in, the next one comes out)."""
         if self.spec is not None:     # greedy, relaxed and sampled requests all verify drafts (engine/spec.py)
-            self.spec.round(reqs)
-            self.stats["decode_steps"] += 1
-            self.stats["decode_tokens"] += sum(r.rounds[-1] for r in reqs)
-            return
+            # grammar-constrained requests decode one masked token per step (drafts are not walked through the
+            # grammar here; GrammarState.verify_masks is the building block for that)
+            free = [r for r in reqs if r.grammar is None]
+            reqs = [r for r in reqs if r.grammar is not None]
+            if free:
+                self.spec.round(free)
+                self.stats["decode_steps"] += 1
+                self.stats["decode_tokens"] += sum(r.rounds[-1] for r in free)
+            if not reqs:
+                return
         slots = [s[0] for s in self.state.reserve(reqs, 1)]   # all or nothing; MemoryError -> scheduler retracts
         rows = [r.table_row for r in reqs]
         tokens = [r.output_ids[-1] for r in reqs]
         positions = [r.total_len - 1 for r in reqs]
+        masks = [r.grammar.mask() if r.grammar is not None else None for r in reqs]
         out = self.runner.decode(rows, tokens, positions, slots, _sampling_rows(reqs),
-                                 [r.state_slot for r in reqs] if self.state_pool is not None else None)
+                                 [r.state_slot for r in reqs] if self.state_pool is not None else None,
+                                 masks if any(m is not None for m in masks) else None)
         for r, tok in zip(reqs, out):
             self.state.commit(r, 1)
             r.draws += 1

@@ -7,6 +7,7 @@ engine unhealthy. Reference: hibana/engine/loop.py:47-320.
 """
 from __future__ import annotations
 
+import dataclasses
 import itertools
 import queue
 import threading
@@ -48,6 +49,7 @@ class EngineLoop:
         self._by_rid: dict[int, Ticket] = {}
         self._ids = itertools.count(1)
         self.healthy = True
+        self.grammars = None      # engine.grammar.Grammars (or a factory); needed on every rank when a channel is set
         self.failure: Optional[str] = None
         self.stopping = False
         self.draining = False
@@ -71,6 +73,11 @@ class EngineLoop:
             raise QueueFull("queue full")
         t = Ticket(next(self._ids), notify=notify)
         self.tickets[t.tid] = t
+        constraint = constraint if constraint is not None else params.constraint
+        if constraint is not None and self.channel is not None:
+            # a compiled grammar does not pickle: other ranks get its source and compile it again (self.grammars)
+            constraint = ("source", constraint.kind, constraint.source, constraint.think_end)
+            params = dataclasses.replace(params, constraint=None)
         self.inbox.put(("submit", t.tid, list(prompt_ids), params, eos_id, media, constraint))
         return t
 
@@ -108,7 +115,12 @@ class EngineLoop:
         if kind == "submit":
             _, tid, ids, params, eos_id, media, constraint = cmd
             ticket = self.tickets.get(tid)
-            req = Request(prompt_ids=ids, params=params, eos_id=eos_id, media=media, constraint=constraint)
+            if isinstance(constraint, tuple):       # rebuilt on every rank from the broadcast source
+                gr = self.grammars() if callable(self.grammars) else self.grammars
+                constraint = gr.recompile(*constraint[1:]) if gr is not None else None
+            if constraint is not None and params.constraint is not constraint:
+                params = dataclasses.replace(params, constraint=constraint)
+            req = Request(prompt_ids=ids, params=params, eos_id=eos_id, media=media)
             try:
                 self.sched.submit(req)
             except (ValueError, QueueFull) as e:

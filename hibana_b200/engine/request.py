@@ -28,6 +28,7 @@ class SamplingParams:
     accept_margin: float = 0.0       # ... and within this many logits of the argmax
     accept_soft: float = 0.0         # sampled acceptance slack s: accept when u*q < e^s * p
     logprobs: int = 0
+    constraint: Any = None           # engine.grammar.Constraint: the output must match this grammar
 
     def __post_init__(self) -> None:
         if self.temperature < 0 or self.top_p <= 0 or self.top_p > 1 or self.top_k < 0:
@@ -80,7 +81,7 @@ class Request(RequestState):
     finish_reason: Optional[str] = None
     eos_id: Optional[int] = None
     media: Any = None
-    constraint: Any = None                           # grammar state
+    grammar: Any = None                              # engine.grammar.GrammarState of a constrained request
     arrival: float = field(default_factory=time.monotonic)
     first_token_time: Optional[float] = None
     finish_time: Optional[float] = None
@@ -116,6 +117,8 @@ class Request(RequestState):
         if self.first_token_time is None:
             self.first_token_time = time.monotonic()
         self.output_ids.append(int(token))
+        if self.grammar is not None:
+            self.grammar.push(int(token))
         stop = int(token) in self.params.stop_ids or (
             self.eos_id is not None and not self.params.ignore_eos and int(token) == self.eos_id)
         if stop:

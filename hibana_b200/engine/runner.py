@@ -36,6 +36,8 @@ class StepBuffers:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.workspace = None
         self.splits = 1
+        self.mask: Optional[torch.Tensor] = None      # grammar bitmask [bucket, ceil(vocab / 32)], all ones = free
+        self.mask_dirty: list = []
 
     def views(self):
         d = self.dev
@@ -103,7 +105,7 @@ class ModelRunner:
                              state_slots=v["state"])
         h = self._forward(v["ids"].long(), ctx)
         logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
-        tok = sampling.sample(logits, v["temp"], v["top_k"], v["top_p"], v["seed"], v["offs"])
+        tok = sampling.sample(logits, v["temp"], v["top_k"], v["top_p"], v["seed"], v["offs"], bitmask=buf.mask)
         buf.out.copy_(tok)
 
     def _prepare_bucket(self, buf: StepBuffers) -> None:
@@ -112,6 +114,8 @@ class ModelRunner:
             buf.splits = self.attn_splits or attention.choose_splits(buf.bucket, t.kv_heads, self.max_ctx)
             if buf.splits > 1 and self.device.type == "cuda":
                 buf.workspace = attention.AttnWorkspace(buf.bucket, t.q_heads, t.head_dim, buf.splits, self.device)
+        if buf.mask is None:      # read by the sampling kernels next to the logits; rows of constrained requests
+            buf.mask = torch.full((buf.bucket, (t.vocab + 31) // 32), -1, dtype=torch.int32, device=self.device)
 
     def capture(self, buckets: Optional[Sequence[int]] = None) -> None:
         """Captures one decode graph per bucket (after a warm-up run of the same body)."""
@@ -141,8 +145,10 @@ class ModelRunner:
         return self.model.forward(ids, ctx, self.kv)
 
     def decode(self, rows: Sequence[int], tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int],
-               sampling_rows: Optional[dict] = None, state_slots: Optional[Sequence[int]] = None) -> list[int]:
+               sampling_rows: Optional[dict] = None, state_slots: Optional[Sequence[int]] = None,
+               masks: Optional[Sequence] = None) -> list[int]:
         """One decode step for len(rows) sequences; returns the sampled token of each (host ints).
+        `masks[i]` (host int32 [ceil(vocab / 32)] or None) restricts sequence i's token to a grammar.
 
         sampling_rows: optional dict of per-sequence lists temp / top_k / top_p / seed / offs (greedy when None).
         """
@@ -169,6 +175,15 @@ class ModelRunner:
             a[R_OFFS:R_OFFS + 2].reshape(-1).view(np.int64)[:n] = sampling_rows["offs"]
         buf.dev.copy_(buf.host, non_blocking=True)
         self.h2d_bytes += buf.host.numel() * 4
+        for i in buf.mask_dirty:           # rows a previous step constrained are free again
+            buf.mask[i].fill_(-1)
+        buf.mask_dirty = []
+        if masks is not None:
+            for i, m in enumerate(masks):
+                if m is not None:
+                    buf.mask[i].copy_(m, non_blocking=True)
+                    buf.mask_dirty.append(i)
+                    self.h2d_bytes += m.numel() * 4
         if buf.graph is not None:
             buf.graph.replay()
         else:
@@ -184,7 +199,7 @@ class ModelRunner:
                      slot_lists: Sequence[Sequence[int]], *, mode: str = PREFILL, want: str = "last",
                      sampling_rows: Optional[dict] = None, state_slots: Optional[Sequence[int]] = None,
                      has_initial_state: Optional[Sequence[int]] = None, checkpoints=None,
-                     extras: Optional[dict] = None):
+                     extras: Optional[dict] = None, masks: Optional[torch.Tensor] = None):
         """Runs new tokens of several sequences in one ragged forward.
 
         rows[i] is the block-table row, token_lists[i] the new tokens starting at position starts[i] with KV slots
@@ -239,13 +254,15 @@ class ModelRunner:
             logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
             return (logits if want == "logits_device" else sampling.argmax(logits)), ctx.extras.get("hidden")
         logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
+        if masks is not None:      # grammar bitmask per sampled row (host int32 [rows, ceil(vocab / 32)])
+            masks = masks.to(dev, non_blocking=True)
         if sampling_rows is None or want == "all":
-            tok = sampling.argmax(logits)
+            tok = sampling.argmax(logits, masks if want == "last" else None)
         else:
             sr = {k: up(np.asarray(v), dt) for (k, v), dt in zip(
                 ((k, sampling_rows[k]) for k in ("temp", "top_k", "top_p", "seed", "offs")),
                 (torch.float32, torch.int32, torch.float32, torch.int64, torch.int64))}
-            tok = sampling.sample(logits, sr["temp"], sr["top_k"], sr["top_p"], sr["seed"], sr["offs"])
+            tok = sampling.sample(logits, sr["temp"], sr["top_k"], sr["top_p"], sr["seed"], sr["offs"], bitmask=masks)
         out = tok.cpu()
         self.d2h_bytes += out.numel() * 8
         return out.tolist()

@@ -31,7 +31,8 @@ nv.register("hb_ep_plan", [P, I, I, P, I, I, L, I, P, P, P, P, P, L, P, P])
 nv.register("hb_ep_dispatch", [P, L, I, I, I, I, P, P, P, P, I, I, L, L, L, L, P])
 nv.register("hb_ep_combine", [P, P, P, L, P, L, I, I, I, P, I, I, L, L, P, P])
 nv.register("hb_gemm_grouped_ep", [I, P, P, P, P, I, I, I, I, P, L, P, I, P, P, I, P, I, I, P, I, I, P, P, P, L, P, L,
-                                   L, I, P])
+                                   L, I, P, P, I, P])
+nv.register("hb_moe_tiles", [P, I, I, P, P, I, P])
 
 EPI_RETURN = 5
 
@@ -152,6 +153,16 @@ class ExpertParallel:
         max_rows = min(self.world * self.tokens, rows_cap)
         # every rank sends about as many pairs as it has: expected rows per local expert
         bn_hint = moe.tile_hint(max(pairs, 1) , self.e_per, max_rows, self.fmt)
+        bn_full = 16
+        while bn_full < max_rows and bn_full < 256:
+            bn_full *= 2
+        bn_hint = min(bn_hint, bn_full)
+        # compact (expert, chunk) work list from the planned row counts: the GEMM grids cover tiles that have rows
+        tile_cap = -(-rows_cap // bn_hint) + self.e_per
+        tiles = torch.empty(tile_cap, dtype=torch.int32, device=dev)
+        n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+        nv.check(lib.hb_moe_tiles(self.grp_cnt.data_ptr(), self.e_per, bn_hint, tiles.data_ptr(), n_tiles.data_ptr(),
+                                  tile_cap, stream), "hb_moe_tiles")
         gate = self._ptr(self.flag_rows_off)
         seq = self._ptr(self.seq_off)
 
@@ -160,7 +171,8 @@ class ExpertParallel:
                 kind, a, b, sfa, sfb, self.e_per, n_per, rows_cap, k, out, ldo, alpha, epi, self.grp_start.data_ptr(),
                 self.grp_cnt.data_ptr(), max_rows, st.data_ptr(), ka_a, ka_b, self._bases, self.world, self.rank,
                 gate_flags, seq, self._ptr(self.off["row_ret"]) if ret else None, self.off["ret"],
-                self._ptr(self.done_fc2_off) if ret else None, self.flag_ret_off, self.timeout_ns, bn_hint, stream),
+                self._ptr(self.done_fc2_off) if ret else None, self.flag_ret_off, self.timeout_ns, bn_hint,
+                tiles.data_ptr(), n_tiles.data_ptr(), tile_cap, stream),
                 "hb_gemm_grouped_ep")
 
         if nvq:

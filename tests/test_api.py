@@ -145,3 +145,27 @@ def test_parsers_and_detok():
         {"role": "user", "content": [{"type": "tool_result", "tool_use_id": "t1", "content": "42"}]}],
         "tools": [{"name": "f", "input_schema": {"type": "object"}}]})
     assert [m["role"] for m in msgs] == ["system", "user", "assistant", "tool"] and tools[0]["function"]["name"] == "f"
+
+
+def test_constrained_output_over_http(stack):
+    """`regex` / `response_format` reach the engine as grammar masks; a malformed schema is a 400."""
+    pytest.importorskip("xgrammar")
+    import re
+    app, loop, tok = stack
+
+    async def go():
+        async with _client(app) as c:
+            r = await c.post("/generate", json={"text": "go", "sampling_params": {"regex": "(ab|cd){2,3}!",
+                                                                                   "max_new_tokens": 24}})
+            assert r.status_code == 200, r.text
+            assert re.fullmatch(r"(ab|cd){2,3}!", r.json()["text"]), r.json()
+            r2 = await c.post("/v1/chat/completions", json={
+                "model": "tiny", "messages": [{"role": "user", "content": "json"}], "max_tokens": 48,
+                "response_format": {"type": "json_schema", "json_schema": {"schema": {
+                    "type": "object", "properties": {"a": {"type": "boolean"}}, "required": ["a"],
+                    "additionalProperties": False}}}})
+            assert r2.status_code == 200, r2.text
+            assert json.loads(r2.json()["choices"][0]["message"]["content"]) in ({"a": True}, {"a": False})
+            r3 = await c.post("/generate", json={"text": "x", "sampling_params": {"ebnf": "root ::= ("}})
+            assert r3.status_code == 400
+    _run(go())
