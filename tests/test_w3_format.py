@@ -46,3 +46,29 @@ def test_codebook_planes_roundtrip():
     assert torch.allclose(d, want)
     refit = cb.to_int3g64().dequantize()
     assert float((refit - d).abs().mean() / d.abs().mean()) < 0.25
+
+
+def test_codebook_fit_beats_uniform_levels_and_gptq_beats_rounding():
+    """Calibration tools: Lloyd codebook vs plain int3 on bell-shaped weights; GPTQ vs round-to-nearest on the
+    layer output error with correlated inputs."""
+    import torch
+    from hibana_b200.weights import w3_calibrate as cal
+    from hibana_b200.weights.w3 import Int3G64
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(96, 256, generator=g) * 0.05
+    cb = cal.fit_codebook(w)
+    assert cb.codes().max() <= 7 and len(cb.codebook) == 8
+    err_cb = (cb.dequantize() - w).norm() / w.norm()
+    err_rt = (Int3G64.quantize(w).dequantize() - w).norm() / w.norm()
+    assert err_cb < 0.25 and err_cb < err_rt * 1.05, (float(err_cb), float(err_rt))
+    # correlated activations: a few strong directions
+    basis = torch.randn(256, 16, generator=g)
+    x = torch.randn(512, 16, generator=g) @ basis.t() + 0.1 * torch.randn(512, 256, generator=g)
+    h = cal.collect_hessian([x[:256], x[256:]], 256)
+    q = cal.gptq_int3g64(w, h)
+    e_gptq = cal.layer_error(w, q.dequantize(), x)
+    e_rtn = cal.layer_error(w, Int3G64.quantize(w).dequantize(), x)
+    assert e_gptq < e_rtn, (e_gptq, e_rtn)
+    # the Hessian-weighted codebook is at least as good on the outputs as the unweighted one
+    cbw = cal.fit_codebook(w, hessian_diag=torch.diag(h))
+    assert cal.layer_error(w, cbw.dequantize(), x) < cal.layer_error(w, cb.dequantize(), x) * 1.1
