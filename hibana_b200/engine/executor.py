@@ -64,10 +64,17 @@ class Executor:
                       "cached_tokens": 0}
         self.spec = None
 
-    def enable_spec(self, depth: int = 2) -> None:
-        """Turns on MTP speculative decoding (greedy exact acceptance) for requests with greedy sampling."""
+    def enable_spec(self, depth: int = 2, proposer=None) -> None:
+        """Turns on speculative decoding. Drafts come from the model's MTP head, or from `proposer` (a name known
+        to proposers.make_proposer, or an object with the engine/contracts.py Proposer interface)."""
         from .spec import SpecDecoder
-        self.spec = SpecDecoder(self, depth)
+        if isinstance(proposer, str):
+            if proposer == "mtp":
+                proposer = None
+            else:
+                from ..proposers import make_proposer
+                proposer = make_proposer(proposer, executor=self)
+        self.spec = SpecDecoder(self, depth, proposer=proposer)
 
     # ---- lifecycle
     def validate_request(self, req: Request) -> None:

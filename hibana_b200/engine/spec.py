@@ -40,11 +40,16 @@ class SpecStats:
 
 
 class SpecDecoder:
-    def __init__(self, executor, depth: int = 2):
+    def __init__(self, executor, depth: int = 2, proposer=None):
         self.ex = executor
         self.model = executor.model
-        self.mtp = executor.model.mtp
-        assert self.mtp is not None, "speculation needs a model with an MTP head"
+        self.mtp = getattr(executor.model, "mtp", None)
+        # `proposer` (engine/contracts.py Proposer: n-gram lookup, block drafter, ...) replaces the built-in MTP
+        # drafting; verification, acceptance and state replay are the same for every source of drafts
+        self.proposer = proposer
+        assert self.mtp is not None or proposer is not None, "speculation needs an MTP head or a proposer"
+        self._started: set = set()
+        self._laws = None
         self.depth = depth
         self.stats = SpecStats()
         self.feats: dict[int, torch.Tensor] = {}          # rid -> target hidden of the last committed position
@@ -99,8 +104,11 @@ class SpecDecoder:
             tk = torch.tensor([r.params.top_k for r in reqs], device=dev).repeat_interleave(k1)
             tp = torch.tensor([r.params.top_p for r in reqs], device=dev).repeat_interleave(k1)
             laws = rejection.distribution(flat, temp, tk, tp).view(b, k1, v)
-            q = torch.zeros(b, k, v, device=dev)
-            q.scatter_(2, drafts[:, :, None], 1.0)                       # the MTP head drafts its argmax
+            if self._laws is not None:                                   # the proposer sampled from these
+                q = self._laws.view(b, k, v).float()
+            else:
+                q = torch.zeros(b, k, v, device=dev)
+                q.scatter_(2, drafts[:, :, None], 1.0)                   # deterministic drafts: a point mass
             u = torch.empty(b, k1, 2)
             for i, r in enumerate(reqs):                                 # counter-based: replay-safe
                 for j in range(k1):
@@ -120,6 +128,10 @@ class SpecDecoder:
     def ingest_prefill(self, req: Request, hidden: torch.Tensor, start: int, count: int) -> None:
         """After a target prefill chunk over positions [start, start + count): feed the MTP layer the pairs
         (h_p, x_{p+1}) whose next token is already known and keep the last hidden as the request's feature."""
+        if self.proposer is not None:
+            self.proposer.ingest_prefill(req, hidden, start, count)
+            self.feats[req.rid] = hidden[count - 1].clone()
+            return
         seq = req.all_ids
         rows, ids, pos = [], [], []
         prev = self.feats.get(req.rid)
@@ -137,6 +149,9 @@ class SpecDecoder:
 
     def release(self, req: Request) -> None:
         self.feats.pop(req.rid, None)
+        if self.proposer is not None:
+            self._started.discard(req.rid)
+            self.proposer.release(req)
         slot = self.scratch.pop(req.rid, None)
         if slot and self.ex.state_pool is not None:
             self.ex.state_pool.free(slot)
@@ -154,12 +169,24 @@ class SpecDecoder:
         feat = torch.stack([self.feats.get(r.rid, torch.zeros(self.model.target.hidden, dtype=torch.bfloat16,
                                                               device=dev)) for r in reqs])
         drafts = torch.zeros(b, k, dtype=torch.int64, device=dev)
-        hid = feat
-        ids = [r.output_ids[-1] for r in reqs]
-        for j in range(k):
-            hid, tok = self._mtp_rows(reqs, hid, ids, [nn - 1 + j for nn in n], [1] * b)
-            drafts[:, j] = tok
-            ids = tok.tolist() if j + 1 < k else None
+        self._laws = None
+        if self.proposer is not None:
+            for r in reqs:
+                if r.rid not in self._started:
+                    self._started.add(r.rid)
+                    self.proposer.start(r)
+            prop = self.proposer.propose(reqs, k)
+            toks = prop if isinstance(prop, torch.Tensor) else prop.tokens
+            drafts.copy_(toks.view(b, k))           # short drafts arrive padded: a padded token is simply refused
+            if not isinstance(prop, torch.Tensor) and prop.laws is not None:
+                self._laws = prop.laws.to(dev)
+        else:
+            hid = feat
+            ids = [r.output_ids[-1] for r in reqs]
+            for j in range(k):
+                hid, tok = self._mtp_rows(reqs, hid, ids, [nn - 1 + j for nn in n], [1] * b)
+                drafts[:, j] = tok
+                ids = tok.tolist() if j + 1 < k else None
         # ---- verify
         host_drafts = drafts.tolist()
         tokens = [[r.output_ids[-1]] + host_drafts[i] for i, r in enumerate(reqs)]
@@ -204,9 +231,13 @@ class SpecDecoder:
             slots = self._dev([r.state_slot for r in reqs], torch.int32)
             for layer, saved in extras["ring"]:
                 layer.replay(saved, sel, ip, slots, ex.state_pool)
+        if self.proposer is not None:
+            from .contracts import VerifiedFeatures
+            self.proposer.accepted_batch(reqs, [emitted_h[i][:count_h[i]] for i in range(b)],
+                                         VerifiedFeatures(hidden, count_h, k + 1))
         # refresh the MTP KV of accepted draft positions with the true target hiddens
         ref_reqs, ref_rows, ref_ids, ref_pos, ref_cnt = [], [], [], [], []
-        for i, r in enumerate(reqs):
+        for i, r in enumerate(reqs if self.proposer is None else []):
             a = count_h[i] - 1
             if a > 0:
                 ref_reqs.append(r)

@@ -213,6 +213,8 @@ class DenseModel:
             y, _ = comm.allreduce_norm(slot, h.shape[0], t.hidden, residual=res, weight=self.final_norm,
                                        eps=t.norm_eps)
             return y.index_select(0, ctx.sample_rows) if ctx.sample_rows is not None else y
+        if ctx.extras.get("want_hidden") is not None and comm is None:
+            ctx.extras["hidden"] = basic.add(h, res)      # pre-norm hidden of every row: the drafters' feature
         if ctx.sample_rows is not None:
             h = h.index_select(0, ctx.sample_rows)
             res = res.index_select(0, ctx.sample_rows)

@@ -98,3 +98,64 @@ def test_ngram_proposer_and_capabilities():
         check_capabilities(Capabilities(max_depth=4), ProposerRequirements(depth=6, row_budget=True))
     with pytest.raises(ValueError):
         make_proposer("nope")
+
+
+def test_ngram_proposer_in_the_engine_is_exact_cpu():
+    """Any proposer plugs into the speculative round: n-gram drafts are verified by the target, so the output equals
+    plain greedy decoding token for token, and repeated text gets several tokens per round."""
+    import torch
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.dense import DenseModel
+    from hibana_b200.target import dense_tiny, scaled
+    t = scaled(dense_tiny(), weight_format="bf16")
+    model = DenseModel(t, "cpu", seed=0)
+    g = torch.Generator().manual_seed(3)
+    base = torch.randint(0, t.vocab, (12,), generator=g).tolist()
+    prompts = [base * 3, torch.randint(0, t.vocab, (20,), generator=g).tolist()]
+    sp = SamplingParams(max_tokens=16)
+    plain = Executor(model, max_batch=4, max_ctx=128, use_graphs=False).generate_batch(prompts, sp)
+    ex = Executor(model, max_batch=4, max_ctx=128, use_graphs=False)
+    ex.enable_spec(depth=4, proposer="ngram")
+    spec = ex.generate_batch(prompts, sp)
+    assert [r.output_ids for r in spec] == [r.output_ids for r in plain]
+    assert ex.spec.stats.rounds > 0 and ex.spec.stats.emitted >= ex.spec.stats.rounds
+
+
+def test_block_drafter_lattice_and_engine_exactness_cpu():
+    """Block drafter: one forward gives a candidate lattice; greedy / sampled walks agree with their definitions;
+    through the engine the output equals plain decoding (greedy) whatever the random drafter proposes."""
+    import torch
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.dense import DenseModel
+    from hibana_b200.models.parallel_draft import greedy_lattice, sample_lattice
+    from hibana_b200.target import dense_tiny, scaled
+    g = torch.Generator().manual_seed(0)
+    cand = torch.randint(0, 50, (2, 3, 4), generator=g)
+    scores = torch.randn(2, 3, 4, 4, generator=g)
+    toks, idx = greedy_lattice(cand, scores)
+    for b in range(2):
+        prev = 0
+        for j in range(3):
+            prev = int(scores[b, j, prev].argmax())
+            assert int(idx[b, j]) == prev and int(toks[b, j]) == int(cand[b, j, prev])
+    u = torch.rand(2, 3, generator=g)
+    st, laws = sample_lattice(cand, scores, torch.tensor([1.0, 0.7]), u, 50)
+    assert laws.shape == (2, 3, 50) and torch.allclose(laws.sum(-1), torch.ones(2, 3), atol=1e-5)
+    assert (laws.gather(2, st[..., None]) > 0).all()
+    t = scaled(dense_tiny(), weight_format="bf16")
+    model = DenseModel(t, "cpu", seed=0)
+    prompts = [torch.randint(0, t.vocab, (n,), generator=g).tolist() for n in (19, 33)]
+    sp = SamplingParams(max_tokens=12)
+    plain = Executor(model, max_batch=4, max_ctx=128, use_graphs=False).generate_batch(prompts, sp)
+    ex = Executor(model, max_batch=4, max_ctx=128, use_graphs=False)
+    ex.enable_spec(depth=5, proposer=make_proposer("dflash2", executor=ex, layers=1, heads=4, window=32))
+    spec = ex.generate_batch(prompts, sp)
+    assert [r.output_ids for r in spec] == [r.output_ids for r in plain]
+    assert ex.spec.stats.rounds > 0
+    # sampled requests: drafts come with their laws and the round still terminates with valid tokens
+    ex2 = Executor(model, max_batch=4, max_ctx=128, use_graphs=False)
+    ex2.enable_spec(depth=3, proposer=make_proposer("dflash2", executor=ex2, layers=1, heads=4, window=32))
+    out = ex2.generate_batch(prompts, SamplingParams(max_tokens=8, temperature=0.8, seed=11))
+    assert all(len(r.output_ids) == 8 and all(0 <= x < t.vocab for x in r.output_ids) for r in out)
