@@ -265,3 +265,247 @@ int hb_gdn_chunk_pass(const void* w, const void* qg, const void* kd, const void*
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// Phase 1 of the chunked gated delta rule: everything of a 64-token chunk that does not depend on the incoming
+// state, for all chunks and heads in parallel (one CTA per (chunk, value head), 128 threads, 4 warps of 16 rows).
+//   Kn, Qn  = l2norm(k), l2norm(q) * scale                    (bf16 in shared memory)
+//   gamma_t = running sum of g inside the chunk
+//   A[t,i]  = beta_t e^(gamma_t - gamma_i) <Kn_t, Kn_i>  (i < t)      T = (I + A)^-1   (fp32, forward substitution)
+//   M[t,i]  = e^(gamma_t - gamma_i) <Qn_t, Kn_i>         (i <= t)
+//   U = T (beta V)     W = T (beta e^gamma Kn)     Qg = e^gamma Qn     Kd = e^(gamma_C - gamma) Kn
+// The four 64-wide products run on mma.sync with bf16 operands (as the reference's chunk kernels do); the
+// triangular inverse stays in fp32. Outputs are laid out [head, chunk, 64, *] for gdn_chunk_kernel.
+namespace hb {
+namespace {
+
+constexpr int P1_PK = GK * 2 + 16;     // pitch of the [64, 128] bf16 tiles
+constexpr int P1_PA = GC + 4;          // floats per row of A / T
+constexpr int P1_PT = GC * 2 + 16;     // pitch of T in bf16
+constexpr int P1_KN = 0;
+constexpr int P1_QN = P1_KN + GC * P1_PK;
+constexpr int P1_VB = P1_QN + GC * P1_PK;
+constexpr int P1_KB = P1_VB + GC * P1_PK;
+constexpr int P1_A = P1_KB + GC * P1_PK;
+constexpr int P1_TB = P1_A + GC * P1_PA * 4;
+constexpr int P1_G = P1_TB + GC * P1_PT;          // gamma[64], beta[64]
+constexpr int P1_SMEM = P1_G + 2 * GC * 4;
+
+struct Phase1Params {
+  const __nv_bfloat16* q;   // [n, k_heads * 128] (pitch ldq)
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;   // [n, v_heads * 128] (pitch ldv)
+  const float* g;           // [n, v_heads]
+  const float* beta;
+  long long ldq, ldv;
+  __nv_bfloat16 *w, *qg, *kd, *m;   // outputs, see gdn_chunk_kernel
+  float* u;
+  float* g_end;
+  int n, nc, k_heads, v_heads;
+  float scale;
+  int l2norm;
+};
+
+__global__ void __launch_bounds__(128, 2) gdn_phase1_kernel(const Phase1Params p) {
+  extern __shared__ __align__(16) uint8_t sm[];
+  const uint32_t sb = smem_u32(sm);
+  float* a_s = reinterpret_cast<float*>(sm + P1_A);
+  float* gam = reinterpret_cast<float*>(sm + P1_G);
+  float* bet = gam + GC;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, h = blockIdx.y;
+  const int hk = h / (p.v_heads / p.k_heads);
+  const int qr = lane >> 2, qc = (lane & 3) * 2;
+  const int t0 = c * GC;
+
+  // ---- gamma, beta
+  if (warp == 0) {
+    float g0 = 0.f, g1 = 0.f;
+    const int ta = t0 + lane, tb = t0 + 32 + lane;
+    if (ta < p.n) g0 = p.g[static_cast<long long>(ta) * p.v_heads + h];
+    if (tb < p.n) g1 = p.g[static_cast<long long>(tb) * p.v_heads + h];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float x0 = __shfl_up_sync(0xffffffffu, g0, o), x1 = __shfl_up_sync(0xffffffffu, g1, o);
+      if (lane >= o) {
+        g0 += x0;
+        g1 += x1;
+      }
+    }
+    g1 += __shfl_sync(0xffffffffu, g0, 31);
+    gam[lane] = g0;
+    gam[32 + lane] = g1;
+    bet[lane] = ta < p.n ? p.beta[static_cast<long long>(ta) * p.v_heads + h] : 0.f;
+    bet[32 + lane] = tb < p.n ? p.beta[static_cast<long long>(tb) * p.v_heads + h] : 0.f;
+  }
+  // ---- q, k rows: (l2norm,) scale, to shared memory; 16 rows per warp, a lane holds 4 of a row's 128 values
+  for (int r = warp * 16; r < warp * 16 + 16; ++r) {
+    const int t = t0 + r;
+    float qv[4] = {0, 0, 0, 0}, kv[4] = {0, 0, 0, 0};
+    if (t < p.n) {
+      const uint2 qq = *reinterpret_cast<const uint2*>(p.q + t * p.ldq + hk * GK + lane * 4);
+      const uint2 kk = *reinterpret_cast<const uint2*>(p.k + t * p.ldq + hk * GK + lane * 4);
+      qv[0] = bf16_lo(qq.x); qv[1] = bf16_hi(qq.x); qv[2] = bf16_lo(qq.y); qv[3] = bf16_hi(qq.y);
+      kv[0] = bf16_lo(kk.x); kv[1] = bf16_hi(kk.x); kv[2] = bf16_lo(kk.y); kv[3] = bf16_hi(kk.y);
+    }
+    float qs = p.scale, ks = 1.f;
+    if (p.l2norm) {
+      float q2 = qv[0] * qv[0] + qv[1] * qv[1] + qv[2] * qv[2] + qv[3] * qv[3];
+      float k2 = kv[0] * kv[0] + kv[1] * kv[1] + kv[2] * kv[2] + kv[3] * kv[3];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        q2 += __shfl_xor_sync(0xffffffffu, q2, o);
+        k2 += __shfl_xor_sync(0xffffffffu, k2, o);
+      }
+      qs *= rsqrtf(q2 + 1e-6f);
+      ks = rsqrtf(k2 + 1e-6f);
+    }
+    *reinterpret_cast<uint2*>(sm + P1_QN + r * P1_PK + lane * 8) =
+        make_uint2(pack_bf16(qv[0] * qs, qv[1] * qs), pack_bf16(qv[2] * qs, qv[3] * qs));
+    *reinterpret_cast<uint2*>(sm + P1_KN + r * P1_PK + lane * 8) =
+        make_uint2(pack_bf16(kv[0] * ks, kv[1] * ks), pack_bf16(kv[2] * ks, kv[3] * ks));
+  }
+  __syncthreads();
+  const float g_last = gam[GC - 1];
+  // ---- beta V, beta e^gamma Kn, and the decayed copies that go straight to global memory
+  const long long tile = static_cast<long long>(h) * p.nc + c;
+  for (int r = warp * 16; r < warp * 16 + 16; ++r) {
+    const int t = t0 + r;
+    const float b = bet[r], eg = __expf(gam[r]), ed = __expf(g_last - gam[r]);
+    float vv[4] = {0, 0, 0, 0};
+    if (t < p.n) {
+      const uint2 x = *reinterpret_cast<const uint2*>(p.v + t * p.ldv + h * GK + lane * 4);
+      vv[0] = bf16_lo(x.x); vv[1] = bf16_hi(x.x); vv[2] = bf16_lo(x.y); vv[3] = bf16_hi(x.y);
+    }
+    const uint2 kn = *reinterpret_cast<const uint2*>(sm + P1_KN + r * P1_PK + lane * 8);
+    const uint2 qn = *reinterpret_cast<const uint2*>(sm + P1_QN + r * P1_PK + lane * 8);
+    const float k0 = bf16_lo(kn.x), k1 = bf16_hi(kn.x), k2 = bf16_lo(kn.y), k3 = bf16_hi(kn.y);
+    *reinterpret_cast<uint2*>(sm + P1_VB + r * P1_PK + lane * 8) =
+        make_uint2(pack_bf16(vv[0] * b, vv[1] * b), pack_bf16(vv[2] * b, vv[3] * b));
+    const float be = b * eg;
+    *reinterpret_cast<uint2*>(sm + P1_KB + r * P1_PK + lane * 8) =
+        make_uint2(pack_bf16(k0 * be, k1 * be), pack_bf16(k2 * be, k3 * be));
+    const long long o = (tile * GC + r) * GK + lane * 4;
+    *reinterpret_cast<uint2*>(p.kd + o) = make_uint2(pack_bf16(k0 * ed, k1 * ed), pack_bf16(k2 * ed, k3 * ed));
+    *reinterpret_cast<uint2*>(p.qg + o) =
+        make_uint2(pack_bf16(bf16_lo(qn.x) * eg, bf16_hi(qn.x) * eg), pack_bf16(bf16_lo(qn.y) * eg, bf16_hi(qn.y) * eg));
+  }
+  if (tid == 0) p.g_end[tile] = g_last;
+  // ---- Kn Kn^T and Qn Kn^T for this warp's 16 rows
+  {
+    float akk[8][4] = {}, aqk[8][4] = {};
+    const uint32_t a_off = (16 * warp + (lane & 15)) * P1_PK + (lane >> 4) * 16;
+    const int mi = lane >> 3;
+#pragma unroll
+    for (int ks = 0; ks < GK / 16; ++ks) {
+      uint32_t fk[4], fq[4];
+      ldsm_x4(fk, sb + P1_KN + a_off + ks * 32);
+      ldsm_x4(fq, sb + P1_QN + a_off + ks * 32);
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {     // two 8-column tiles of the other tokens per load
+        uint32_t fb[4];
+        ldsm_x4(fb, sb + P1_KN + (16 * jp + (mi >> 1) * 8 + (lane & 7)) * P1_PK + ks * 32 + (mi & 1) * 16);
+        mma16816(akk[2 * jp], fk, fb[0], fb[1]);
+        mma16816(akk[2 * jp + 1], fk, fb[2], fb[3]);
+        mma16816(aqk[2 * jp], fq, fb[0], fb[1]);
+        mma16816(aqk[2 * jp + 1], fq, fb[2], fb[3]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int t = 16 * warp + qr + (e >> 1) * 8, i = 8 * j + qc + (e & 1);
+        const float d = i <= t ? __expf(gam[t] - gam[i]) : 0.f;
+        a_s[t * P1_PA + i] = i < t ? bet[t] * d * akk[j][e] : 0.f;
+        aqk[j][e] *= d;
+      }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; e += 2) {
+        const int t = 16 * warp + qr + (e >> 1) * 8, i = 8 * j + qc;
+        *reinterpret_cast<uint32_t*>(p.m + (tile * GC + t) * GC + i) = pack_bf16(aqk[j][e], aqk[j][e + 1]);
+      }
+  }
+  __syncthreads();
+  // ---- T = (I + A)^-1 by forward substitution, in place (row i of A is replaced by row i of T): thread j owns
+  // column j; row i needs rows < i of T and row i of A, so every row is "all read, barrier, all write, barrier"
+  if (tid < GC) {
+    const int j = tid;
+    for (int i = 0; i < GC; ++i) {
+      float acc = i == j ? 1.f : 0.f;
+      for (int k2 = j; k2 < i; ++k2) acc -= a_s[i * P1_PA + k2] * a_s[k2 * P1_PA + j];
+      asm volatile("bar.sync 2, 64;" ::: "memory");
+      a_s[i * P1_PA + j] = j <= i ? acc : 0.f;
+      asm volatile("bar.sync 2, 64;" ::: "memory");
+    }
+  }
+  __syncthreads();
+  // bf16 copy of T as the A operand of the two products
+  for (int x = tid; x < GC * GC / 2; x += 128) {
+    const int t = x / (GC / 2), i = (x % (GC / 2)) * 2;
+    *reinterpret_cast<uint32_t*>(sm + P1_TB + t * P1_PT + i * 2) = pack_bf16(a_s[t * P1_PA + i], a_s[t * P1_PA + i + 1]);
+  }
+  __syncthreads();
+  // ---- U = T (beta V) (fp32 out) and W = T (beta e^gamma Kn) (bf16 out): 16 rows per warp, 128 columns, K = 64
+  const uint32_t t_off = (16 * warp + (lane & 15)) * P1_PT + (lane >> 4) * 16;
+#pragma unroll 1
+  for (int which = 0; which < 2; ++which) {
+    const uint32_t bsrc = sb + (which == 0 ? P1_VB : P1_KB);
+    float acc[16][4] = {};
+#pragma unroll
+    for (int ks = 0; ks < GC / 16; ++ks) {
+      uint32_t ft[4];
+      ldsm_x4(ft, sb + P1_TB + t_off + ks * 32);
+#pragma unroll
+      for (int jp = 0; jp < 8; ++jp) {     // B = [64 tokens, 128] row-major: transposed loads, two 8-column tiles each
+        uint32_t fb[4];
+        ldsm_x4_t(fb, bsrc + (ks * 16 + (lane & 15)) * P1_PK + jp * 32 + (lane >> 4) * 16);
+        mma16816(acc[2 * jp], ft, fb[0], fb[1]);
+        mma16816(acc[2 * jp + 1], ft, fb[2], fb[3]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; e += 2) {
+        const int t = 16 * warp + qr + (e >> 1) * 8, col = 8 * j + qc;
+        const long long o = (tile * GC + t) * GK + col;
+        if (which == 0) *reinterpret_cast<float2*>(p.u + o) = make_float2(acc[j][e], acc[j][e + 1]);
+        else *reinterpret_cast<uint32_t*>(p.w + o) = pack_bf16(acc[j][e], acc[j][e + 1]);
+      }
+  }
+}
+
+}  // namespace
+}  // namespace hb
+
+extern "C" {
+
+// Phase 1 for the n rows of one sequence (value and key dim 128). Outputs [v_heads, nc, 64, *] with nc = ceil(n / 64):
+// w, qg, kd bf16 [.., 128], m bf16 [.., 64], u fp32 [.., 128], g_end fp32 [v_heads, nc].
+int hb_gdn_phase1(const void* q, const void* k, const void* v, const void* g, const void* beta, long long ldq,
+                  long long ldv, int n, int k_heads, int v_heads, float scale, int l2norm, void* w, void* qg, void* kd,
+                  void* m, void* u, void* g_end, void* stream) {
+  using namespace hb;
+  if (n <= 0) return 0;
+  if (k_heads <= 0 || v_heads % k_heads != 0 || (ldq & 3) || (ldv & 3)) return 1;
+  Phase1Params p;
+  p.q = static_cast<const __nv_bfloat16*>(q); p.k = static_cast<const __nv_bfloat16*>(k);
+  p.v = static_cast<const __nv_bfloat16*>(v); p.g = static_cast<const float*>(g);
+  p.beta = static_cast<const float*>(beta); p.ldq = ldq; p.ldv = ldv;
+  p.w = static_cast<__nv_bfloat16*>(w); p.qg = static_cast<__nv_bfloat16*>(qg); p.kd = static_cast<__nv_bfloat16*>(kd);
+  p.m = static_cast<__nv_bfloat16*>(m); p.u = static_cast<float*>(u); p.g_end = static_cast<float*>(g_end);
+  p.n = n; p.nc = (n + GC - 1) / GC; p.k_heads = k_heads; p.v_heads = v_heads; p.scale = scale; p.l2norm = l2norm;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(gdn_phase1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P1_SMEM) != cudaSuccess)
+      return 3;
+    attr = true;
+  }
+  gdn_phase1_kernel<<<dim3(p.nc, v_heads), 128, P1_SMEM, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+}  // extern "C"

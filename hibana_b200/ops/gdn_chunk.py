@@ -8,7 +8,8 @@ chunks at once. With gamma_t the running sum of g inside the chunk and D[t, i] =
     U  = T (beta * V)          W = T (beta * e^gamma * K)     V' = U - W S0^T
     O  = (e^gamma * Q) S0^T + lower(D * Q K^T) V'             S_C = e^gamma_C S0 + V'^T (e^(gamma_C - gamma) * K)
 
-Phase 1 (all chunks and heads in parallel: batched GEMMs and one triangular solve) produces U, W, the masked
+Phase 1 (all chunks and heads in parallel: `gdn_phase1_kernel` on the GPU for head dim 128, batched GEMMs and one
+triangular solve in PyTorch otherwise) produces U, W, the masked
 score matrix and the decayed Q / K; phase 2 walks the chunks of a sequence carrying S (three small products per
 chunk; csrc/gdn_chunk.cu on the GPU, `state_pass_ref` here). Padding rows of the last chunk carry g = 0 and
 beta = 0, which leaves the state untouched. Reference: hibana/kernels/fla/chunk.py (chunk_gated_delta_rule),
@@ -16,6 +17,7 @@ hibana/kernels/fla/wy_fast.py, hibana/kernels/fla/chunk_delta_h.py.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -24,6 +26,7 @@ from .. import _native as nv
 
 P, I, L = nv.P, nv.I, nv.L
 nv.register("hb_gdn_chunk_pass", [P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, P])
+nv.register("hb_gdn_phase1", [P, P, P, P, P, L, L, I, I, I, nv.F, I, P, P, P, P, P, P, P])
 
 CHUNK = 64
 
@@ -96,6 +99,24 @@ def _native_pass(ph: dict, s_in: Optional[torch.Tensor], s_out: Optional[torch.T
              "hb_gdn_chunk_pass")
 
 
+def prepare_native(q, k, v, g, beta, *, k_heads: int, v_heads: int, scale: float, l2norm: bool) -> dict:
+    """Phase 1 by csrc/gdn_chunk.cu (`gdn_phase1_kernel`): one CTA per (chunk, head); key / value dim 128."""
+    n = q.shape[0]
+    nc = (n + CHUNK - 1) // CHUNK
+    dev, bf = q.device, torch.bfloat16
+    out = {name: torch.empty(v_heads, nc, CHUNK, 128, dtype=bf, device=dev) for name in ("w", "qg", "kd")}
+    out["m"] = torch.empty(v_heads, nc, CHUNK, CHUNK, dtype=bf, device=dev)
+    out["u"] = torch.empty(v_heads, nc, CHUNK, 128, dtype=torch.float32, device=dev)
+    out["g_end"] = torch.empty(v_heads, nc, dtype=torch.float32, device=dev)
+    out.update(n=n, nc=nc)
+    nv.check(nv.lib().hb_gdn_phase1(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                                    q.stride(0), v.stride(0), n, k_heads, v_heads, scale, int(l2norm),
+                                    out["w"].data_ptr(), out["qg"].data_ptr(), out["kd"].data_ptr(),
+                                    out["m"].data_ptr(), out["u"].data_ptr(), out["g_end"].data_ptr(), nv.stream()),
+             "hb_gdn_phase1")
+    return out
+
+
 def gdn_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
                 state: torch.Tensor, slot_in: torch.Tensor, slot_out: Optional[torch.Tensor], *, k_heads: int,
                 v_heads: int, kdim: int, vdim: int, scale: float, l2norm: bool,
@@ -109,8 +130,14 @@ def gdn_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tens
     for b, (r0, r1) in enumerate(ranges):
         if r1 <= r0:
             continue
-        ph = prepare(q[r0:r1], k[r0:r1], v[r0:r1], g[r0:r1], beta[r0:r1], k_heads=k_heads, v_heads=v_heads,
-                     kdim=kdim, vdim=vdim, scale=scale, l2norm=l2norm)
+        fused = (native and os.environ.get("HIBANA_GDN_PHASE1", "cuda") == "cuda" and q.stride(0) == k.stride(0)
+                 and q.stride(0) % 4 == 0 and v.stride(0) % 4 == 0 and g.is_contiguous() and beta.is_contiguous())
+        if fused:
+            ph = prepare_native(q[r0:r1], k[r0:r1], v[r0:r1], g[r0:r1], beta[r0:r1], k_heads=k_heads,
+                                v_heads=v_heads, scale=scale, l2norm=l2norm)
+        else:
+            ph = prepare(q[r0:r1], k[r0:r1], v[r0:r1], g[r0:r1], beta[r0:r1], k_heads=k_heads, v_heads=v_heads,
+                         kdim=kdim, vdim=vdim, scale=scale, l2norm=l2norm)
         init = has_init is None or bool(has_init[b])
         if native:
             _native_pass(ph, state[sin[b]] if init else None, state[sout[b]] if sout is not None else None,

@@ -111,3 +111,22 @@ def test_ssd_chunked_gpu_matches_sequential(rows):
     scale = max(1.0, ref.float().abs().max().item())
     assert (got.float().cpu() - ref.float()).abs().max().item() < 3e-2 * scale
     assert torch.allclose(st.cpu(), st_ref, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [64, 200])
+def test_phase1_kernel_matches_batched_reference(n):
+    """gdn_phase1_kernel (bf16 tensor-core products, fp32 triangular inverse) against the fp32 PyTorch phase 1."""
+    kh, vh = 2, 4
+    q, k, v, gl, beta, *_ = _case([n], kh, vh, 128, 128, seed=9)
+    qkv = torch.cat([q, k, v], 1).cuda()                      # column slices of one buffer, as in the model
+    qd, kd_, vd = qkv[:, :kh * 128], qkv[:, kh * 128:2 * kh * 128], qkv[:, 2 * kh * 128:]
+    ref = gdn_chunk.prepare(qd, kd_, vd, gl.cuda(), beta.cuda(), k_heads=kh, v_heads=vh, kdim=128, vdim=128,
+                            scale=128 ** -0.5, l2norm=True)
+    got = gdn_chunk.prepare_native(qd, kd_, vd, gl.cuda(), beta.cuda(), k_heads=kh, v_heads=vh, scale=128 ** -0.5,
+                                   l2norm=True)
+    assert got["nc"] == ref["nc"]
+    for name, tol in (("g_end", 1e-4), ("qg", 1e-2), ("kd", 1e-2), ("m", 2e-2), ("u", 3e-2), ("w", 3e-2)):
+        a, b = got[name].float(), ref[name].float()
+        err = (a - b).abs().max().item()
+        assert err <= tol * max(1.0, b.abs().max().item()), (name, err, b.abs().max().item())
