@@ -216,16 +216,10 @@ class Executor:
     def decode_step(self, reqs: Sequence[Request]) -> None:
         """One token for every running request (the pending token goes in, the next one comes out)."""
         if self.spec is not None:     # greedy, relaxed and sampled requests all verify drafts (engine/spec.py)
-            # grammar-constrained requests decode one masked token per step (drafts are not walked through the
-            # grammar here; GrammarState.verify_masks is the building block for that)
-            free = [r for r in reqs if r.grammar is None]
-            reqs = [r for r in reqs if r.grammar is not None]
-            if free:
-                self.spec.round(free)
-                self.stats["decode_steps"] += 1
-                self.stats["decode_tokens"] += sum(r.rounds[-1] for r in free)
-            if not reqs:
-                return
+            self.spec.round(reqs)
+            self.stats["decode_steps"] += 1
+            self.stats["decode_tokens"] += sum(r.rounds[-1] for r in reqs)
+            return
         slots = [s[0] for s in self.state.reserve(reqs, 1)]   # all or nothing; MemoryError -> scheduler retracts
         rows = [r.table_row for r in reqs]
         tokens = [r.output_ids[-1] for r in reqs]

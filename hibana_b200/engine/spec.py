@@ -80,7 +80,8 @@ class SpecDecoder:
         tok = sampling.argmax(self.model.logits(normed))
         return g, tok
 
-    def _decide(self, reqs: Sequence[Request], logits: torch.Tensor, drafts: torch.Tensor) -> torch.Tensor:
+    def _decide(self, reqs: Sequence[Request], logits: torch.Tensor, drafts: torch.Tensor,
+                bitmask: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Per request, the token row the exact-match kernel compares the drafts with: the target argmax (exact
         greedy), the drafts themselves where the relaxed rule accepts them, or the outcome of speculative
         sampling. Nothing leaves the device."""
@@ -89,7 +90,10 @@ class SpecDecoder:
         k = k1 - 1
         dev = logits.device
         flat = logits.reshape(b * k1, v)
-        out = sampling.argmax(flat).view(b, k1).clone()
+        out = sampling.argmax(flat, bitmask).view(b, k1).clone()      # grammar rows: argmax over the allowed tokens
+        if bitmask is not None:
+            flat = sampling._apply_bitmask(flat, bitmask)               # the rules below see -inf for forbidden tokens
+            logits = flat.view(b, k1, v)
         greedy = torch.tensor([r.params.greedy for r in reqs], device=dev)
         rel = torch.tensor([r.params.greedy and (r.params.accept_top_k > 1 or r.params.accept_margin > 0)
                             for r in reqs], device=dev)
@@ -200,12 +204,24 @@ class SpecDecoder:
             extras["ring"] = []
         relaxed = any(r.params.greedy and (r.params.accept_top_k > 1 or r.params.accept_margin > 0) for r in reqs)
         sampled = any(not r.params.greedy for r in reqs)
+        # grammar-constrained requests: the drafted tokens are walked through the grammar on the host, one mask per
+        # verified row (the state after the drafted prefix before it); acceptance then runs on the masked logits,
+        # so a drafted token the grammar forbids can never be accepted and the correction comes from a masked row
+        bitmask = None
+        if any(r.grammar is not None for r in reqs):
+            from .grammar import stack_masks
+            rows_m = []
+            for i, r in enumerate(reqs):
+                rows_m.extend(r.grammar.verify_masks(host_drafts[i]) if r.grammar is not None else [None] * (k + 1))
+            bitmask = stack_masks(rows_m, (self.model.target.vocab + 31) // 32)
+            if bitmask is not None:
+                bitmask = bitmask.to(dev)
         target, hidden = ex.runner.forward_rows(
             [r.table_row for r in reqs], tokens, n, [r.kv_slots[nn:nn + k + 1] for r, nn in zip(reqs, n)], mode=VERIFY,
-            want="logits_device" if (relaxed or sampled) else "all_device",
+            want="logits_device" if (relaxed or sampled or bitmask is not None) else "all_device",
             state_slots=[r.state_slot for r in reqs] if has_state else None, extras=extras)
-        if relaxed or sampled:
-            target = self._decide(reqs, target.view(b, k + 1, -1), drafts)
+        if relaxed or sampled or bitmask is not None:
+            target = self._decide(reqs, target.view(b, k + 1, -1), drafts, bitmask)
         target = target.view(b, k + 1)
         # ---- accept (device), one small readback
         stops = torch.full((b, MAX_STOPS), -1, dtype=torch.int64)

@@ -97,3 +97,28 @@ def test_constrained_generation_end_to_end_cpu():
     text2 = bytes(i for i in out[2].output_ids if i < 256).decode()
     assert re.fullmatch(r"(ab|cd){2,4}!", text2), text2
     assert len(out[1].output_ids) == 12 and out[1].grammar is None
+
+
+def test_constrained_output_with_speculation_matches_plain_cpu():
+    """Drafts are walked through the grammar (verify_masks): constrained greedy output is the same with and without
+    speculative decoding, and always inside the grammar."""
+    import re
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.dense import DenseModel
+    from hibana_b200.target import dense_tiny, scaled
+
+    t = scaled(dense_tiny(), weight_format="bf16", vocab=259)
+    model = DenseModel(t, "cpu", seed=0)
+    gs = _grammars()
+    pat = r"((ab|cd)x){3,6}!"
+    sp = [SamplingParams(max_tokens=40, constraint=gs.regex(pat), stop_ids=(EOS,)), SamplingParams(max_tokens=10)]
+    prompts = [list(b"abxabxabx repeat"), list(b"free")]
+    plain = Executor(model, max_batch=4, max_ctx=128, use_graphs=False).generate_batch(prompts, sp)
+    ex = Executor(model, max_batch=4, max_ctx=128, use_graphs=False)
+    ex.enable_spec(depth=4, proposer="ngram")
+    spec = ex.generate_batch(prompts, sp)
+    assert [r.output_ids for r in spec] == [r.output_ids for r in plain]
+    text = bytes(i for i in spec[0].output_ids if i < 256).decode()
+    assert re.fullmatch(pat, text), text
+    assert not spec[0].grammar.failed
