@@ -34,16 +34,20 @@ def set_pdl(on: bool) -> None:
 
 
 
+MAX_SPLITS = int(os.environ.get("HIBANA_MAX_SPLITS", "8"))     # 8 = portable cluster size
+
+
 def _plan(m: int, n: int, k_tiles: int, max_ws_bytes: int) -> tuple[bool, int, int]:
     """(swap, bn, splits) for an [m tokens] x [n features] problem."""
     if m <= 256:
         bn = next(b for b in (16, 32, 64, 128, 256) if b >= m)
         tiles = (n + 127) // 128
         splits = 1
-        if tiles < NUM_SMS:
-            # One CTA per SM streams ~1/148 of HBM bandwidth, so fill the SMs without spilling into a second,
-            # mostly empty wave; every split keeps at least two K tiles.
-            splits = max(1, min(NUM_SMS // tiles, k_tiles // 2, 8))     # 8 = portable cluster size
+        slots = NUM_SMS * (2 if bn <= 64 else 1)     # token tiles <= 64 run two CTAs per SM (csrc/gemm.cu Cfg)
+        if tiles < slots:
+            # Fill the resident CTA slots without spilling into a second, mostly empty wave; every split keeps at
+            # least two K tiles.
+            splits = max(1, min(slots // tiles, k_tiles // 2, MAX_SPLITS))
         return True, bn, splits
     return False, (256 if n >= 256 else 128), 1
 
