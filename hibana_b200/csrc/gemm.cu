@@ -55,7 +55,9 @@ struct Cfg {
   static constexpr int TX_BYTES = KIND == kGemmW3 ? B_TILE_BYTES + PACK_BYTES : STAGE_BYTES;   // bytes copies deliver
   // Token tiles of up to 64 (decode) keep the ring under ~100 KB so that two CTAs share an SM: the second CTA's
   // prologue and epilogue overlap the first one's streaming, and grids of up to 2 x 148 CTAs are one wave.
-  static constexpr int SMEM_BUDGET = BN <= 64 ? 100 * 1024 : 200 * 1024;
+  // 128-token tiles (the grouped MoE GEMMs at prefill) get three stages for the same reason: thousands of short
+  // CTAs whose fixed cost would otherwise be paid one after the other on every SM.
+  static constexpr int SMEM_BUDGET = BN <= 64 ? 100 * 1024 : BN == 128 ? 110 * 1024 : 200 * 1024;
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TMEM_NEED = BN + (KIND == kGemmNvfp4 ? 16 + 16 * NRB : 0);

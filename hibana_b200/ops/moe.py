@@ -203,7 +203,7 @@ def tile_hint(pairs: int, experts: int, max_rows: int, fmt: str) -> int:
     unless the expert fits one chunk."""
     avg = max(1, -(-pairs // max(experts, 1)))
     bn = 16
-    while bn < min(avg + avg // 4, 256):
+    while bn < min(avg + avg // 4, 128):     # 128 at most: up to that width two CTAs share an SM (csrc/gemm.cu Cfg)
         bn *= 2
     if fmt == "nvfp4" and bn < 128 and max_rows > bn:
         bn = 128
