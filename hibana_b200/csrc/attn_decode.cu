@@ -509,8 +509,8 @@ int launch_decode(const DecParams& p0, const void* k_pool, const void* v_pool, l
   p.tma_xh = t.xh;
   p.tma_yh = t.yh;
   if (t.ok) {
-    tk = t.k;
-    tv = t.v;
+    tk = &t.k;
+    tv = &t.v;
   }
   attn_decode_kernel<D, T8><<<dim3(batch, p.hkv, p.splits), DEC_WARPS * 32, C::SMEM, st>>>(*tk, *tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;

@@ -633,8 +633,8 @@ int hb_attn_decode_tc(const void* q, const void* k_pool, const void* v_pool, lon
   const KvTma t = make_kv_tma(k_pool, v_pool, pool_stride, head_stride, pool_slots, hkv, d, 32);
   p.use_tma = t.ok; p.tma_xh = t.xh; p.tma_yh = t.yh;
   if (t.ok) {
-    tk = t.k;
-    tv = t.v;
+    tk = &t.k;
+    tv = &t.v;
   }
   static bool attr = false;
   if (!attr) {

@@ -550,8 +550,8 @@ int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long 
   p.tma_xh = t.xh;
   p.tma_yh = t.yh;
   if (t.ok) {
-    tk = t.k;
-    tv = t.v;
+    tk = &t.k;
+    tv = &t.v;
   }
   if (d == 64) return launch_prefill<64>(p, tk, tv, qblocks, batch, st);
   if (d == 128) return launch_prefill<128>(p, tk, tv, qblocks, batch, st);

@@ -746,13 +746,18 @@ cudaError_t launch_t(const GemmArgs& a, DevParams& p, dim3 grid, const CUtensorM
 
 }  // namespace
 
-const CUtensorMap* get_tmap_2d(const TmapKey& key) {
+// Copies the (cached) tensor map of `key` into *out. The copy matters: the cache is dropped when it grows past its
+// limit, so nothing outside this function may hold a pointer into it.
+bool get_tmap_2d(const TmapKey& key, CUtensorMap* out_map) {
   std::lock_guard<std::mutex> lock(g_tmap_mu);
   auto it = g_tmaps.find(key);
-  if (it != g_tmaps.end()) return it->second.get();
+  if (it != g_tmaps.end()) {
+    *out_map = *it->second;
+    return true;
+  }
   if (g_tmaps.size() > 8192) g_tmaps.clear();
   EncodeFn fn = encode_fn();
-  if (fn == nullptr) return nullptr;
+  if (fn == nullptr) return false;
   auto m = std::make_unique<CUtensorMap>();
   const cuuint64_t dims[2] = {key.cols, key.rows};
   const cuuint64_t strides[1] = {key.pitch_bytes};
@@ -762,10 +767,10 @@ const CUtensorMap* get_tmap_2d(const TmapKey& key) {
   const CUresult r = fn(m.get(), dt, 2, const_cast<void*>(key.ptr), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return nullptr;
-  const CUtensorMap* out = m.get();
+  if (r != CUDA_SUCCESS) return false;
+  *out_map = *m;
   g_tmaps.emplace(key, std::move(m));
-  return out;
+  return true;
 }
 
 void clear_tmap_cache() {
@@ -818,9 +823,11 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   TmapKey kb{a.b, static_cast<uint64_t>(a.rb), static_cast<uint64_t>(fp4 ? a.k / 2 : a.k),
              static_cast<uint64_t>(fp4 ? a.ldb / 2 : fp8 ? a.ldb : a.ldb * 2), static_cast<uint32_t>(a.bn),
              static_cast<uint32_t>(bytes ? 128 : 64), bytes ? 1 : 0};
-  const CUtensorMap* tb = get_tmap_2d(kb);
-  const CUtensorMap* ta = w3 ? tb : get_tmap_2d(ka);   // the w3 A operand arrives by bulk copies, not through a map
-  if (ta == nullptr || tb == nullptr) return cudaErrorInvalidValue;
+  CUtensorMap map_a, map_b;
+  if (!get_tmap_2d(kb, &map_b)) return cudaErrorInvalidValue;
+  if (w3) map_a = map_b;                                  // the w3 A operand arrives by bulk copies, not through a map
+  else if (!get_tmap_2d(ka, &map_a)) return cudaErrorInvalidValue;
+  const CUtensorMap *ta = &map_a, *tb = &map_b;
 
   DevParams p;
   p.sfa = static_cast<const uint8_t*>(a.sfa);

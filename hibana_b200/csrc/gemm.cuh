@@ -112,7 +112,7 @@ struct TmapKey {
            box_rows == o.box_rows && box_cols == o.box_cols && dtype == o.dtype;
   }
 };
-const CUtensorMap* get_tmap_2d(const TmapKey& key);
+bool get_tmap_2d(const TmapKey& key, CUtensorMap* out_map);   // copies the cached map (never hand out cache pointers)
 void clear_tmap_cache();
 
 }  // namespace hb

@@ -13,8 +13,8 @@
 namespace hb {
 
 struct KvTma {
-  const CUtensorMap* k = nullptr;
-  const CUtensorMap* v = nullptr;
+  CUtensorMap k = {};     // copies: valid for as long as this struct lives (the launch that follows)
+  CUtensorMap v = {};
   int xh = 0, yh = 0;
   int ok = 0;
 };
@@ -42,9 +42,7 @@ inline KvTma make_kv_tma(const void* k_pool, const void* v_pool, long long slot_
   TmapKey kk{k_pool, rows, cols, static_cast<uint64_t>(slot_stride) * 2, static_cast<uint32_t>(box_rows), 64u, 0};
   TmapKey kv = kk;
   kv.ptr = v_pool;
-  t.k = get_tmap_2d(kk);
-  t.v = get_tmap_2d(kv);
-  t.ok = t.k != nullptr && t.v != nullptr;
+  t.ok = get_tmap_2d(kk, &t.k) && get_tmap_2d(kv, &t.v);
   return t;
 }
 

@@ -53,7 +53,7 @@ def main() -> None:
             continue
         if args.graph:
             wbytes = n * k * (0.5625 if args.kind == "nvfp4" else 2)
-            reps = max(2, int((300 << 20) / wbytes) + 1)
+            reps = min(max(2, int((300 << 20) / wbytes) + 1), 1024)
             if args.kind == "nvfp4":
                 ws = [nvfp4.Nvfp4Tensor(wq.q.clone(), wq.sf.clone(), wq.gscale, wq.rows, wq.k) for _ in range(reps)]
                 calls = [lambda w_=w_: gemm.linear_nvfp4(xq, w_, alpha, out=out) for w_ in ws]
