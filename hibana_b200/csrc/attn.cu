@@ -290,6 +290,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_splitkv_kernel(const AttnPar
 // Merge of split partials: o = sum_s 2^(lse_s - m) o_s / sum_s 2^(lse_s - m). One CTA per (row, head).
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                   __nv_bfloat16* __restrict__ out, int splits, int d) {
+  grid_dep_wait();     // may run as a programmatic dependent of the split kernel
+  grid_dep_launch();
   const long long rh = blockIdx.x;
   const float* lse = part_lse + rh * splits;
   float m = -INFINITY;
@@ -398,7 +400,7 @@ int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long lo
 int hb_attn_merge(const void* part_o, const void* part_lse, void* out, long long rows_heads, int splits, int d,
                   void* stream) {
   if (rows_heads <= 0) return 0;
-  attn_merge_kernel<<<static_cast<unsigned>(rows_heads), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_dep(attn_merge_kernel, dim3(static_cast<unsigned>(rows_heads)), dim3(128), 0, static_cast<cudaStream_t>(stream),
       static_cast<const float*>(part_o), static_cast<const float*>(part_lse), static_cast<__nv_bfloat16*>(out), splits,
       d);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;

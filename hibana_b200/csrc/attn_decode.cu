@@ -106,6 +106,8 @@ template <int D, bool T8>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 2)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, const DecParams p) {
   using C = DecCfg<D>;
+  grid_dep_wait();     // may run as a programmatic dependent of the RoPE + KV-write kernel
+  grid_dep_launch();
   constexpr int KT = C::KT, ROWB = C::QROWB;
   constexpr int NB = KT / 8;     // score n-blocks per tile
   constexpr int KS = D / 16;     // k-steps of Q K^T
@@ -512,7 +514,7 @@ int launch_decode(const DecParams& p0, const void* k_pool, const void* v_pool, l
     tk = &t.k;
     tv = &t.v;
   }
-  attn_decode_kernel<D, T8><<<dim3(batch, p.hkv, p.splits), DEC_WARPS * 32, C::SMEM, st>>>(*tk, *tv, p);
+  launch_dep(attn_decode_kernel<D, T8>, dim3(batch, p.hkv, p.splits), dim3(DEC_WARPS * 32), C::SMEM, st, *tk, *tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -88,6 +88,7 @@ struct DevParams {
   int grp_rows_a;         // weight rows per expert (multiple of 128)
   const int* grp_tiles;   // optional work list: expert * 4096 + chunk (then grid.y = list slot, grid.z = 1)
   const int* grp_ntiles;
+  int early_launch;       // release the next kernel's launch at the start of this one (programmatic launch level 2)
   // peer fusion
   int peer_on, world, rank, rows_per_rank;
   uint8_t* peer_base[8];
@@ -308,6 +309,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Let the kernel after this one be scheduled now (it waits for this grid's completion before it reads anything
+  // this grid writes): its launch latency and prologue overlap this grid's main loop.
+  if (p.early_launch) grid_dep_launch();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -855,6 +859,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   }
   p.tok_scale = a.tok_scale;
+  p.early_launch = g_pdl >= 2;
   p.w3_tiles = w3 ? static_cast<const uint8_t*>(a.a) : nullptr;
   p.ep_gate_flags = nullptr; p.ep_seq_ptr = nullptr; p.ep_row_ret = nullptr; p.ep_done = nullptr;
   p.ep_ret_offset = 0; p.ep_ret_flag_offset = 0;
@@ -1044,7 +1049,7 @@ int hb_gemm_w3(const void* tiles, const void* x, int n, int m, int k, long long 
 
 void hb_clear_tmap_cache(void) { hb::clear_tmap_cache(); }
 
-void hb_gemm_set_pdl(int on) { hb::g_pdl = on != 0; }
+void hb_gemm_set_pdl(int on) { hb::g_pdl = on < 0 ? 0 : on > 2 ? 2 : on; }
 int hb_gemm_get_pdl(void) { return hb::g_pdl; }
 
 }  // extern "C"

@@ -178,6 +178,27 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
       : "memory");
 }
 
+// Launch as a programmatic dependent of the kernel before it in the stream (when the library-wide switch is on,
+// see hb_gemm_set_pdl): the grid may be scheduled while its predecessor drains, which hides launch latency. The
+// kernel MUST call grid_dep_wait() before it touches anything its predecessor wrote (and should call
+// grid_dep_launch() right after, so that its own successor can do the same).
+extern "C" int hb_gemm_get_pdl(void);
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = hb_gemm_get_pdl() >= 2 ? 1 : 0;     // level 1: GEMMs only; level 2: these kernels as well
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {  // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),

@@ -121,6 +121,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
                                      void* __restrict__ v_pool, long long pool_stride, long long head_stride, int hq, int hkv,
                                      int d, int rot,
                                      int kv_fp8, float kv_inv_scale, int q_gate) {
+  grid_dep_wait();     // may run as a programmatic dependent of the QKV projection
+  grid_dep_launch();
   const int t = blockIdx.x;
   const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int nw = gridDim.y * (blockDim.x >> 5);
@@ -271,7 +273,7 @@ int hb_rope_kv_write(const void* qkv, long long ld_qkv, const void* positions, c
   const int heads = hq + 2 * hkv;
   int ysplit = 1;
   if (tokens < 512) ysplit = (heads + 7) / 8;
-  rope_kv_write_kernel<<<dim3(tokens, ysplit), 256, 0, ST(stream)>>>(
+  launch_dep(rope_kv_write_kernel, dim3(tokens, ysplit), dim3(256), 0, ST(stream),
       BF(qkv), ld_qkv, static_cast<const int*>(positions), static_cast<const int*>(slots),
       static_cast<const float*>(inv_freq), BF(q_norm_w), BF(k_norm_w), eps, gemma_norm, BFM(q_out), k_pool, v_pool,
       pool_stride, head_stride, hq, hkv, d, rot, kv_fp8, kv_inv_scale, q_gate);

@@ -54,6 +54,7 @@ __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long lon
                                    const float* __restrict__ gscale, uint8_t* __restrict__ q,
                                    uint8_t* __restrict__ sf, int mode, const int* __restrict__ src_rows,
                                    const int* __restrict__ total_rows) {
+  grid_dep_wait();     // launched as a programmatic dependent: the producer of x must have completed
   grid_dep_launch();   // a GEMM launched as a programmatic dependent may start prefetching its weights
   const int groups_pad = ka * 4;
   const int rows_pad = ((m + 127) >> 7) << 7;
@@ -106,6 +107,7 @@ norm_quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __re
                         const __nv_bfloat16* __restrict__ w, float eps, int gemma, int m, int k, int ka,
                         const float* __restrict__ gscale, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
                         __nv_bfloat16* __restrict__ normed) {
+  grid_dep_wait();     // launched as a programmatic dependent: the producer of x must have completed
   grid_dep_launch();   // a GEMM launched as a programmatic dependent may start prefetching its weights
   __shared__ float red[40];
   const int row = blockIdx.x;
@@ -209,7 +211,7 @@ int hb_quant_nvfp4_rows(const void* x, long long ldx, int m, int k, int ka, cons
   const int rows_pad = ((m + 127) / 128) * 128;
   const long long n = static_cast<long long>(rows_pad) * ka * 4;
   const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
-  quant_nvfp4_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_dep(quant_nvfp4_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(x), ldx, m, k, ka, static_cast<const float*>(gscale),
       static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), mode, static_cast<const int*>(src_rows),
       static_cast<const int*>(total_rows));
@@ -223,7 +225,7 @@ int hb_quant_nvfp4(const void* x, long long ldx, int m, int k, int ka, const voi
   const long long n = static_cast<long long>(rows_pad) * ka * 4;
   const int threads = 256;
   const unsigned blocks = static_cast<unsigned>((n + threads - 1) / threads);
-  quant_nvfp4_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_dep(quant_nvfp4_kernel, dim3(blocks), dim3(threads), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(x), ldx, m, k, ka, static_cast<const float*>(gscale),
       static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), mode, nullptr, nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
@@ -237,7 +239,7 @@ int hb_norm_quant_nvfp4(const void* x, void* residual, const void* w, float eps,
   const int rows_pad = q != nullptr ? ((m + 127) / 128) * 128 : m;
   const int nchunk = k / 8;
 #define HB_NQ(MAXC)                                                                                              \
-  norm_quant_nvfp4_kernel<T, MAXC><<<rows_pad, T, 0, st>>>(                                                      \
+  launch_dep(norm_quant_nvfp4_kernel<T, MAXC>, dim3(rows_pad), dim3(T), 0, st,                                   \
       static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(residual),                               \
       static_cast<const __nv_bfloat16*>(w), eps, gemma, m, k, ka, static_cast<const float*>(gscale),             \
       static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), static_cast<__nv_bfloat16*>(normed))

@@ -25,8 +25,10 @@ nv.register("hb_gemm_set_pdl", [nv.I], void=True)
 _PDL_INIT = False
 
 
-def set_pdl(on: bool) -> None:
-    """GEMMs launch as programmatic dependents: their weight prefetch overlaps the kernel before them."""
+def set_pdl(on) -> None:
+    """Programmatic dependent launch. Level 1 (True): GEMMs launch as dependents, their weight prefetch overlaps the
+    kernel before them. Level 2: the small kernels of a decode step (quantisation, RoPE + KV write, decode
+    attention, merge) do so too and GEMMs release their successor at their start. 0 / False: off."""
     global _PDL_INIT
     _PDL_INIT = True
     if nv.available():
@@ -56,7 +58,7 @@ def _launch(kind: int, a, b, sfa, sfb, ra: int, rb: int, k: int, lda: int, ldb: 
             residual: Optional[torch.Tensor], alpha: float, alpha_ptr: Optional[torch.Tensor], epilogue: int,
             swap: bool, splits: int, bn: int, ka_a: int, ka_b: int) -> None:
     if not _PDL_INIT:
-        set_pdl(os.environ.get("HIBANA_PDL", "1") != "0")
+        set_pdl(int(os.environ.get("HIBANA_PDL", "1")))
     st = nv.device_state(out.device)
     ws = cnt = None     # split-K reduces through distributed shared memory; no global scratch
     code = nv.lib().hb_gemm(kind, a.data_ptr(), b.data_ptr(), nv.ptr(sfa), nv.ptr(sfb), ra, rb, k, lda, ldb,
