@@ -1,4 +1,5 @@
 """Checkpoint round trips: ModelOpt NVFP4 tensors, sharded load, generation equality."""
+import pytest
 import torch
 
 from hibana_b200.engine.executor import Executor
@@ -33,3 +34,42 @@ def test_dense_checkpoint_roundtrip_and_tp_shards(tmp_path):
 def test_unpack_fp4():
     q = torch.tensor([[0x21, 0xF7]], dtype=torch.uint8)
     assert modelopt.unpack_fp4(q).tolist() == [[0.5, 1.0, 6.0, -6.0]]
+
+
+def test_gguf_reader_and_block_codecs(tmp_path):
+    """GGUF container round trip (metadata, alignment, tensor directory) and the Q8_0 / F16 / BF16 codecs; the IQ2
+    decoders run against a synthetic lattice table and a hand-packed block."""
+    import numpy as np
+    from hibana_b200.weights import ggml
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal((6, 64)).astype(np.float32)
+    h = rng.standard_normal((3, 5)).astype(np.float16)
+    bf = (rng.standard_normal(8).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    path = str(tmp_path / "t.gguf")
+    ggml.write_gguf(path, {"a.weight": (ggml.quantize_q8_0(w), ggml.T_Q8_0, (6, 64)),
+                           "b": (h.view(np.uint8).reshape(-1), ggml.T_F16, (3, 5)),
+                           "c": (bf.view(np.uint8), ggml.T_BF16, (8,))},
+                    meta={"general.architecture": "test", "block_count": 7})
+    f = ggml.GgufFile(path)
+    assert f.meta["general.architecture"] == "test" and f.meta["block_count"] == 7 and f.version == 3
+    assert f.tensors["a.weight"].shape == (6, 64) and f.tensors["a.weight"].nbytes == 6 * 2 * 34
+    got = f.load("a.weight")
+    assert np.abs(got - w).max() <= np.abs(w).max() / 127 * 0.51 + 1e-3          # half a quantisation step
+    assert np.array_equal(f.load("b"), h.astype(np.float32))
+    assert np.array_equal(f.load("c"), (bf.astype(np.uint32) << 16).view(np.float32))
+    f.close()
+    # IQ2_XXS: one super-block, all indices -> entry 3 of a synthetic grid, sub-scale 5, signs pattern 0b0000101
+    grid = rng.integers(1, 44, size=(256, 8)).astype(np.uint8)
+    blk = np.zeros(66, dtype=np.uint8)
+    blk[:2] = np.float16(0.5).reshape(1).view(np.uint8)
+    words = np.zeros((8, 2), dtype=np.uint32)
+    words[:, 0] = 3 | (3 << 8) | (3 << 16) | (3 << 24)
+    sidx = 0b0000101
+    words[:, 1] = sidx | (sidx << 7) | (sidx << 14) | (sidx << 21) | (5 << 28)
+    blk[2:] = words.view(np.uint8).reshape(-1)
+    out = ggml.dequantize(blk, ggml.T_IQ2_XXS, (256,), grids={"iq2_xxs": grid})
+    signs = np.array([-1, 1, -1, 1, 1, 1, 1, 1], dtype=np.float32)              # bits 0 and 2 set; parity even -> bit 7 clear
+    expect = np.tile(grid[3].astype(np.float32) * signs * 0.5 * (0.5 + 5) * 0.25, 32)
+    assert np.allclose(out, expect)
+    with pytest.raises(ValueError):
+        ggml.dequantize(blk, ggml.T_IQ2_XXS, (256,))
