@@ -42,6 +42,21 @@ class HybridModel:
             self.device)
         self.kv_layers, self.state_layers = counters["kv"], counters["state"]
         self.ep_size = ep_size
+        # Hyper-connections: one site in front of every sublayer (its gated mix of the residual streams is the
+        # sublayer's input, the sublayer's output is injected back into every stream) and a last site, without
+        # injection, in front of the final norm.
+        self.hyper_sites = None
+        if t.hyper_streams > 1:
+            from .hyper import HyperConnection
+            hc, hh, rk = t.hyper_streams, t.hidden, t.hyper_rank
+            n_sites = sum(1 for b in self.blocks for _, sub in b.sublayers() if sub is not None) + 1
+            self.hyper_sites = []
+            for i in range(n_sites):
+                last = i == n_sites - 1
+                self.hyper_sites.append(HyperConnection(
+                    init.ones(hc * hh, True).to(self.device), init.normal(rk, hc * hh).to(self.device),
+                    init.normal(hc * hh, rk).to(self.device),
+                    None if last else init.normal(hc, hc * hh).to(self.device), hc, hh, t.norm_eps))
         self.mtp = None
         if t.mtp_layers:
             from .mtp import MtpHead
@@ -84,6 +99,8 @@ class HybridModel:
     def hidden_states(self, ids: torch.Tensor, ctx: ForwardContext, kv, states=None):
         """Runs the trunk; returns (h, res) of the last sublayer (the final norm adds them)."""
         t = self.target
+        if self.hyper_sites is not None:
+            return self._hidden_states_hyper(ids, ctx, kv, states)
         res = basic.embedding(ids, self.embed)
         h: Optional[torch.Tensor] = None
         for blk in self.blocks:
@@ -101,6 +118,31 @@ class HybridModel:
                 else:
                     h = sub.forward(x, ctx, kv, states)
         return h, res
+
+    def _run_sublayer(self, sub, x, ctx, kv, states):
+        if isinstance(sub, MoeLayer) and ctx.extras.get("ep") is not None:
+            return sub.forward_a2a(x, ctx.extras["ep"])
+        if isinstance(sub, MoeLayer) and sub.ep_size > 1 and ctx.comm is not None:
+            return sub.forward_ep(x, ctx.comm)
+        return sub.forward(x, ctx, kv, states)
+
+    def _hidden_states_hyper(self, ids: torch.Tensor, ctx: ForwardContext, kv, states=None):
+        """Trunk with hyper-connections: the token's state is `hyper_streams` residual streams [T, hc * H]; a site's
+        per-stream norm and gated mean stand where the pre-norm + residual add stand in the plain trunk.
+        Reference: hibana/model/flashnext/model.py:42-77."""
+        t = self.target
+        hyper = basic.embedding(ids, self.embed).repeat(1, t.hyper_streams)
+        site = 0
+        for blk in self.blocks:
+            for _norm_w, sub in blk.sublayers():
+                if sub is None:
+                    continue
+                hc = self.hyper_sites[site]
+                site += 1
+                x, keep = hc.mix(hyper)
+                hyper = hc.combine(self._run_sublayer(sub, x, ctx, kv, states), keep)
+        x, _ = self.hyper_sites[site].mix(hyper)
+        return x, torch.zeros_like(x)
 
     def forward(self, ids: torch.Tensor, ctx: ForwardContext, kv, states=None) -> torch.Tensor:
         t = self.target

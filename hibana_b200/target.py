@@ -62,6 +62,8 @@ class Target:
     kv_dtype: str = "bf16"           # bf16 | fp8
     norm_eps: float = 1e-6
     max_context: int = 262144
+    hyper_streams: int = 0           # > 1: hyper-connections (that many residual streams per token, models/hyper.py)
+    hyper_rank: int = 64             # width of the low-rank gate projections of a hyper-connection site
     prefill_chunk: int = 2048
     tie_embeddings: bool = False
     tp_size: int = 1
@@ -194,7 +196,8 @@ def flashnext() -> Target:
                   layers=_pattern(48, [GDN, GDN, GDN, GATED_ATTN], MOE), q_heads=24, kv_heads=2, head_dim=256,
                   rope_theta=1e7, rotary_frac=0.25, qk_norm=True, gemma_norm=True, gdn_k_heads=16, gdn_v_heads=48,
                   gdn_head_dim=128, experts=512, top_k=10, expert_ffn=640, shared_ffn=640, router="softmax",
-                  mtp_layers=1, mtp_depth=3, weight_format="nvfp4", kv_dtype="fp8", prefill_chunk=4096)
+                  mtp_layers=1, mtp_depth=3, weight_format="nvfp4", kv_dtype="fp8", prefill_chunk=4096,
+                  hyper_streams=4)
 
 
 NEMOTRON_PATTERN = "MEMEMEM*EMEMEMEM*EMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEM*EMEMEMEME"

@@ -140,3 +140,19 @@ def test_relaxed_and_sampled_acceptance_cpu():
     c, _ = run(SamplingParams(max_tokens=24, temperature=0.8, top_k=20, top_p=0.95, seed=8))
     assert a == b and a != c and all(len(r) == 24 for r in a)
     assert s_a["rounds"] > 0 and all(0 <= tok < t.vocab for r in a for tok in r)
+
+
+def test_hyper_connections_in_the_trunk_cpu():
+    """With hyper_streams > 1 the trunk carries several residual streams per token (models/hyper.py sites around every
+    sublayer). Prefix-cache hits, chunked prefill and MTP speculation must still reproduce the plain run."""
+    t = scaled(tiny_hybrid_moe(), hyper_streams=2, hyper_rank=16)
+    m = HybridModel(t, "cpu", seed=0)
+    assert m.hyper_sites is not None and len(m.hyper_sites) == 2 * len(t.layers) + 1
+    prompts = _workload(t, n=3)
+    ref = _run(Executor(m, max_batch=4, max_ctx=160, use_graphs=False, radix_cache=False), prompts, n=12)
+    ex = Executor(m, max_batch=4, max_ctx=160, use_graphs=False)
+    ex.enable_spec(2)
+    assert _run(ex, prompts, n=12) == ref
+    plain = HybridModel(scaled(tiny_hybrid_moe()), "cpu", seed=0)
+    other = _run(Executor(plain, max_batch=4, max_ctx=160, use_graphs=False, radix_cache=False), prompts[:1], n=12)
+    assert other != ref[:1]                      # the hyper trunk is a different function of the same seed
