@@ -275,7 +275,7 @@ int hb_gdn_chunk_pass(const void* w, const void* qg, const void* kd, const void*
 //   M[t,i]  = e^(gamma_t - gamma_i) <Qn_t, Kn_i>         (i <= t)
 //   U = T (beta V)     W = T (beta e^gamma Kn)     Qg = e^gamma Qn     Kd = e^(gamma_C - gamma) Kn
 // The four 64-wide products run on mma.sync with bf16 operands (as the reference's chunk kernels do); the
-// triangular inverse stays in fp32. Outputs are laid out [head, chunk, 64, *] for gdn_chunk_kernel.
+// triangular inverse stays in fp32 (one thread per column, the column in registers). Outputs are laid out [head, chunk, 64, *] for gdn_chunk_kernel.
 namespace hb {
 namespace {
 
@@ -429,17 +429,21 @@ __global__ void __launch_bounds__(128, 2) gdn_phase1_kernel(const Phase1Params p
       }
   }
   __syncthreads();
-  // ---- T = (I + A)^-1 by forward substitution, in place (row i of A is replaced by row i of T): thread j owns
-  // column j; row i needs rows < i of T and row i of A, so every row is "all read, barrier, all write, barrier"
+  // ---- T = (I + A)^-1 by forward substitution. Column j of T depends only on A and on the earlier rows of the
+  // same column (T[i][j] = delta_ij - sum_{k<i} A[i][k] T[k][j], with T[k][j] = 0 for k < j), so thread j keeps its
+  // column in registers and nobody waits for anybody; A is only read (broadcast loads) until all columns are done.
   if (tid < GC) {
-    const int j = tid;
+    float tcol[GC];
+#pragma unroll
     for (int i = 0; i < GC; ++i) {
-      float acc = i == j ? 1.f : 0.f;
-      for (int k2 = j; k2 < i; ++k2) acc -= a_s[i * P1_PA + k2] * a_s[k2 * P1_PA + j];
-      asm volatile("bar.sync 2, 64;" ::: "memory");
-      a_s[i * P1_PA + j] = j <= i ? acc : 0.f;
-      asm volatile("bar.sync 2, 64;" ::: "memory");
+      float acc = i == tid ? 1.f : 0.f;
+#pragma unroll
+      for (int k2 = 0; k2 < i; ++k2) acc -= a_s[i * P1_PA + k2] * tcol[k2];
+      tcol[i] = acc;
     }
+    asm volatile("bar.sync 2, 64;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < GC; ++i) a_s[i * P1_PA + tid] = tcol[i];
   }
   __syncthreads();
   // bf16 copy of T as the A operand of the two products

@@ -57,7 +57,7 @@ class HyperConnection:
         """hyper [T, hc * H] bf16 -> (block input [T, H], residuals for `combine`)."""
         t = hyper.shape[0]
         n = self.normed(hyper)
-        low = F.silu(gemm.linear_bf16(n, self.down).float()).to(torch.bfloat16)
+        low = F.silu(gemm.linear_bf16(n, self.down))        # one elementwise launch (fp32 math inside, bf16 out)
         gate = gemm.linear_bf16(low, self.up)
         if nv.use_native(hyper):
             mixed = torch.empty(t, self.hidden, dtype=torch.bfloat16, device=hyper.device)
