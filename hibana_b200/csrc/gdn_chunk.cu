@@ -513,3 +513,155 @@ int hb_gdn_phase1(const void* q, const void* k, const void* v, const void* g, co
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// Phase 1 of the chunked Mamba-2 (SSD) scan: the chunk-local factors for gdn_chunk_kernel without its W term. One CTA
+// per (chunk, head), 128 threads. With dt_t = softplus(dt + bias), a_t = -exp(a_log) dt_t and gamma its running sum:
+//   U = dt * X     M[t,i] = e^(gamma_t - gamma_i) <C_t, B_i> (i <= t)     Qg = e^gamma C     Kd = e^(gamma_C - gamma) B
+// B and C are shared by the heads of a group; the 64 x 64 x 128 product is simply recomputed per head (1 MFLOP).
+namespace hb {
+namespace {
+
+struct SsdP1Params {
+  const __nv_bfloat16* x;    // [n, heads * P]   (pitch ldx)
+  const __nv_bfloat16* b;    // [n, groups * 128] (pitch ldb)
+  const __nv_bfloat16* c;
+  const __nv_bfloat16* dt;   // [n, heads]        (pitch lddt)
+  const float* a_log;        // [heads]
+  const float* dt_bias;      // [heads] or null
+  long long ldx, ldb, lddt;
+  __nv_bfloat16 *qg, *kd, *m;
+  float* u;                  // [heads, nc, 64, P]
+  float* g_end;
+  int n, nc, heads, groups, p;
+};
+
+__global__ void __launch_bounds__(128, 2) ssd_phase1_kernel(const SsdP1Params p) {
+  extern __shared__ __align__(16) uint8_t sm[];
+  const uint32_t sb = smem_u32(sm);
+  constexpr int S_C = 0, S_B = GC * P1_PK, S_G = 2 * GC * P1_PK;
+  float* gam = reinterpret_cast<float*>(sm + S_G);
+  float* dtv = gam + GC;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, h = blockIdx.y;
+  const int grp = h / (p.heads / p.groups);
+  const int qr = lane >> 2, qc = (lane & 3) * 2;
+  const int t0 = c * GC;
+  if (warp == 0) {
+    const float a = -__expf(p.a_log[h]);
+    const float bias = p.dt_bias ? p.dt_bias[h] : 0.f;
+    float d0 = 0.f, d1 = 0.f;
+    const int ta = t0 + lane, tb = t0 + 32 + lane;
+    if (ta < p.n) {
+      const float z = __bfloat162float(p.dt[ta * p.lddt + h]) + bias;
+      d0 = z > 20.f ? z : log1pf(__expf(z));
+    }
+    if (tb < p.n) {
+      const float z = __bfloat162float(p.dt[tb * p.lddt + h]) + bias;
+      d1 = z > 20.f ? z : log1pf(__expf(z));
+    }
+    float g0 = d0 * a, g1 = d1 * a;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float x0 = __shfl_up_sync(0xffffffffu, g0, o), x1 = __shfl_up_sync(0xffffffffu, g1, o);
+      if (lane >= o) {
+        g0 += x0;
+        g1 += x1;
+      }
+    }
+    g1 += __shfl_sync(0xffffffffu, g0, 31);
+    gam[lane] = g0; gam[32 + lane] = g1;
+    dtv[lane] = d0; dtv[32 + lane] = d1;
+  }
+  for (int r = warp * 16; r < warp * 16 + 16; ++r) {     // raw B and C rows of the group (zero rows past the end)
+    const int t = t0 + r;
+    uint2 bb = make_uint2(0, 0), cc = make_uint2(0, 0);
+    if (t < p.n) {
+      bb = *reinterpret_cast<const uint2*>(p.b + t * p.ldb + grp * GK + lane * 4);
+      cc = *reinterpret_cast<const uint2*>(p.c + t * p.ldb + grp * GK + lane * 4);
+    }
+    *reinterpret_cast<uint2*>(sm + S_B + r * P1_PK + lane * 8) = bb;
+    *reinterpret_cast<uint2*>(sm + S_C + r * P1_PK + lane * 8) = cc;
+  }
+  __syncthreads();
+  const float g_last = gam[GC - 1];
+  const long long tile = static_cast<long long>(h) * p.nc + c;
+  for (int r = warp * 16; r < warp * 16 + 16; ++r) {
+    const int t = t0 + r;
+    const float eg = __expf(gam[r]), ed = __expf(g_last - gam[r]), d = dtv[r];
+    const uint2 bb = *reinterpret_cast<const uint2*>(sm + S_B + r * P1_PK + lane * 8);
+    const uint2 cc = *reinterpret_cast<const uint2*>(sm + S_C + r * P1_PK + lane * 8);
+    const long long o = (tile * GC + r) * GK + lane * 4;
+    *reinterpret_cast<uint2*>(p.kd + o) = make_uint2(pack_bf16(bf16_lo(bb.x) * ed, bf16_hi(bb.x) * ed),
+                                                     pack_bf16(bf16_lo(bb.y) * ed, bf16_hi(bb.y) * ed));
+    *reinterpret_cast<uint2*>(p.qg + o) = make_uint2(pack_bf16(bf16_lo(cc.x) * eg, bf16_hi(cc.x) * eg),
+                                                     pack_bf16(bf16_lo(cc.y) * eg, bf16_hi(cc.y) * eg));
+    for (int col = lane * 2; col < p.p; col += 64) {       // U = dt * x, two values per lane
+      float2 xv = make_float2(0.f, 0.f);
+      if (t < p.n) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(p.x + t * p.ldx + h * p.p + col);
+        xv = make_float2(bf16_lo(w) * d, bf16_hi(w) * d);
+      }
+      *reinterpret_cast<float2*>(p.u + (tile * GC + r) * p.p + col) = xv;
+    }
+  }
+  if (tid == 0) p.g_end[tile] = g_last;
+  // C B^T for this warp's 16 rows, masked and decayed
+  float acc[8][4] = {};
+  const uint32_t a_off = (16 * warp + (lane & 15)) * P1_PK + (lane >> 4) * 16;
+  const int mi = lane >> 3;
+#pragma unroll
+  for (int ks = 0; ks < GK / 16; ++ks) {
+    uint32_t fc[4];
+    ldsm_x4(fc, sb + S_C + a_off + ks * 32);
+#pragma unroll
+    for (int jp = 0; jp < 4; ++jp) {
+      uint32_t fb[4];
+      ldsm_x4(fb, sb + S_B + (16 * jp + (mi >> 1) * 8 + (lane & 7)) * P1_PK + ks * 32 + (mi & 1) * 16);
+      mma16816(acc[2 * jp], fc, fb[0], fb[1]);
+      mma16816(acc[2 * jp + 1], fc, fb[2], fb[3]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; e += 2) {
+      const int t = 16 * warp + qr + (e >> 1) * 8, i = 8 * j + qc;
+      const float v0 = i <= t ? acc[j][e] * __expf(gam[t] - gam[i]) : 0.f;
+      const float v1 = i + 1 <= t ? acc[j][e + 1] * __expf(gam[t] - gam[i + 1]) : 0.f;
+      *reinterpret_cast<uint32_t*>(p.m + (tile * GC + t) * GC + i) = pack_bf16(v0, v1);
+    }
+}
+
+}  // namespace
+}  // namespace hb
+
+extern "C" {
+
+// Phase 1 of the chunked SSD scan for the n rows of one sequence; state dim 128, head dim `p` (even, <= 128 pitch
+// rules as below). Outputs [heads, nc, 64, *]: qg, kd bf16 [.., 128], m bf16 [.., 64], u fp32 [.., p], g_end fp32.
+int hb_ssd_phase1(const void* x, const void* b, const void* c, const void* dt, const void* a_log, const void* dt_bias,
+                  long long ldx, long long ldb, long long lddt, int n, int heads, int groups, int p, void* qg, void* kd,
+                  void* m, void* u, void* g_end, void* stream) {
+  using namespace hb;
+  if (n <= 0) return 0;
+  if (groups <= 0 || heads % groups != 0 || (p & 1) || (ldx & 1) || (ldb & 3)) return 1;
+  SsdP1Params q;
+  q.x = static_cast<const __nv_bfloat16*>(x); q.b = static_cast<const __nv_bfloat16*>(b);
+  q.c = static_cast<const __nv_bfloat16*>(c); q.dt = static_cast<const __nv_bfloat16*>(dt);
+  q.a_log = static_cast<const float*>(a_log); q.dt_bias = static_cast<const float*>(dt_bias);
+  q.ldx = ldx; q.ldb = ldb; q.lddt = lddt;
+  q.qg = static_cast<__nv_bfloat16*>(qg); q.kd = static_cast<__nv_bfloat16*>(kd); q.m = static_cast<__nv_bfloat16*>(m);
+  q.u = static_cast<float*>(u); q.g_end = static_cast<float*>(g_end);
+  q.n = n; q.nc = (n + GC - 1) / GC; q.heads = heads; q.groups = groups; q.p = p;
+  const int smem = 2 * GC * P1_PK + 2 * GC * 4;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(ssd_phase1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 3;
+    attr = true;
+  }
+  ssd_phase1_kernel<<<dim3(q.nc, heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(q);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+}  // extern "C"

@@ -118,6 +118,9 @@ int hb_attn_prefill(const void* q, const void* k_pool, const void* v_pool, long 
 int hb_gdn_phase1(const void* q, const void* k, const void* v, const void* g, const void* beta, long long ldq,
                   long long ldv, int n, int k_heads, int v_heads, float scale, int l2norm, void* w, void* qg, void* kd,
                   void* m, void* u, void* g_end, void* stream);
+int hb_ssd_phase1(const void* x, const void* b, const void* c, const void* dt, const void* a_log, const void* dt_bias,
+                  long long ldx, long long ldb, long long lddt, int n, int heads, int groups, int p, void* qg, void* kd,
+                  void* m, void* u, void* g_end, void* stream);
 int hb_gdn_chunk_pass(const void* w, const void* qg, const void* kd, const void* m, const void* u, const void* g_end,
                       const void* s_in, void* s_out, void* o, long long ldo, int heads, int nc, int n, int kdim,
                       int vdim, void* stream);

@@ -6,12 +6,13 @@ exp(gamma_t - gamma_i) for i <= t:
     Y   = (L * (C B^T)) (dt * X)  +  (e^gamma * C) h0^T          h_C = e^gamma_C h0 + (e^(gamma_C - gamma) * B)^T (dt * X)
 
 which is the chunk recurrence of the gated delta rule without its W term, so phase 2 is the same state-pass
-kernel (csrc/gdn_chunk.cu, value dim = head dim, key dim = state dim 128) and phase 1 a handful of batched
-products over all chunks at once. The skip term D * x is added at the end. Only the fp32 state format takes this
+kernel (csrc/gdn_chunk.cu, value dim = head dim, key dim = state dim 128) and phase 1 one kernel per (chunk, head)
+(`ssd_phase1_kernel`; a handful of batched PyTorch products on the CPU path). The skip term D * x is added at the end. Only the fp32 state format takes this
 path; quantised states keep the token-serial kernel. Reference: hibana/kernels/mamba2.py (chunked SSD prefill).
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -21,6 +22,9 @@ from .. import _native as nv
 from . import gdn_chunk
 
 CHUNK = gdn_chunk.CHUNK
+
+P, I, L = nv.P, nv.I, nv.L
+nv.register("hb_ssd_phase1", [P, P, P, P, P, P, L, L, L, I, I, I, I, P, P, P, P, P, P])
 
 
 def prepare(x, bmat, cmat, dt, a_log, dt_bias, *, heads: int, groups: int, head_dim: int, d_state: int) -> dict:
@@ -52,6 +56,25 @@ def prepare(x, bmat, cmat, dt, a_log, dt_bias, *, heads: int, groups: int, head_
             "g_end": g_end, "n": n, "nc": nc}
 
 
+def prepare_native(x, bmat, cmat, dt, a_log, dt_bias, *, heads: int, groups: int, head_dim: int) -> dict:
+    """Phase 1 by csrc/gdn_chunk.cu (`ssd_phase1_kernel`): one CTA per (chunk, head); state dim 128."""
+    n = x.shape[0]
+    nc = (n + CHUNK - 1) // CHUNK
+    dev, bf = x.device, torch.bfloat16
+    out = {"w": None, "n": n, "nc": nc,
+           "qg": torch.empty(heads, nc, CHUNK, 128, dtype=bf, device=dev),
+           "kd": torch.empty(heads, nc, CHUNK, 128, dtype=bf, device=dev),
+           "m": torch.empty(heads, nc, CHUNK, CHUNK, dtype=bf, device=dev),
+           "u": torch.empty(heads, nc, CHUNK, head_dim, dtype=torch.float32, device=dev),
+           "g_end": torch.empty(heads, nc, dtype=torch.float32, device=dev)}
+    nv.check(nv.lib().hb_ssd_phase1(x.data_ptr(), bmat.data_ptr(), cmat.data_ptr(), dt.data_ptr(),
+                                    a_log.data_ptr(), nv.ptr(dt_bias), x.stride(0), bmat.stride(0), dt.stride(0), n,
+                                    heads, groups, head_dim, out["qg"].data_ptr(), out["kd"].data_ptr(),
+                                    out["m"].data_ptr(), out["u"].data_ptr(), out["g_end"].data_ptr(), nv.stream()),
+             "hb_ssd_phase1")
+    return out
+
+
 def mamba2_chunked(x, bmat, cmat, dt, a_log, dt_bias, dskip, state, slot_in, slot_out, *, heads: int, groups: int,
                    head_dim: int, d_state: int, ranges: Sequence[tuple[int, int]],
                    has_init: Optional[Sequence[int]] = None) -> torch.Tensor:
@@ -64,8 +87,15 @@ def mamba2_chunked(x, bmat, cmat, dt, a_log, dt_bias, dskip, state, slot_in, slo
     for b, (r0, r1) in enumerate(ranges):
         if r1 <= r0:
             continue
-        ph = prepare(x[r0:r1], bmat[r0:r1], cmat[r0:r1], dt[r0:r1], a_log, dt_bias, heads=heads, groups=groups,
-                     head_dim=head_dim, d_state=d_state)
+        fused = (native and os.environ.get("HIBANA_SSD_PHASE1", "cuda") == "cuda" and dt.dtype == torch.bfloat16
+                 and bmat.stride(0) == cmat.stride(0) and bmat.stride(0) % 4 == 0 and x.stride(0) % 2 == 0
+                 and a_log.dtype == torch.float32 and (dt_bias is None or dt_bias.dtype == torch.float32))
+        if fused:
+            ph = prepare_native(x[r0:r1], bmat[r0:r1], cmat[r0:r1], dt[r0:r1], a_log, dt_bias, heads=heads,
+                                groups=groups, head_dim=head_dim)
+        else:
+            ph = prepare(x[r0:r1], bmat[r0:r1], cmat[r0:r1], dt[r0:r1], a_log, dt_bias, heads=heads, groups=groups,
+                         head_dim=head_dim, d_state=d_state)
         init = has_init is None or bool(has_init[b])
         if native:
             gdn_chunk._native_pass(ph, state[sin[b]] if init else None, state[sout[b]] if sout is not None else None,
