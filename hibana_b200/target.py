@@ -197,7 +197,7 @@ def flashnext() -> Target:
                   rope_theta=1e7, rotary_frac=0.25, qk_norm=True, gemma_norm=True, gdn_k_heads=16, gdn_v_heads=48,
                   gdn_head_dim=128, experts=512, top_k=10, expert_ffn=640, shared_ffn=640, router="softmax",
                   mtp_layers=1, mtp_depth=3, weight_format="nvfp4", kv_dtype="fp8", prefill_chunk=4096,
-                  hyper_streams=4)
+                  hyper_streams=4, hyper_rank=320)
 
 
 NEMOTRON_PATTERN = "MEMEMEM*EMEMEMEM*EMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEM*EMEMEMEME"
