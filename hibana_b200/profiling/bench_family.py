@@ -74,15 +74,25 @@ def main() -> None:
     step_ms = e0.elapsed_time(e1) / args.steps
     depth = len(full.layers)
     scale = depth / args.layers
+    # the output head (lm_head GEMM + argmax) runs once per step whatever the depth: time it alone and keep it out
+    # of the per-block figure
+    from ..ops import sampling
+    from .timing import time_cuda
+    hx = torch.randn(batch, t.hidden, device=dev).to(torch.bfloat16)
+    head_ms = time_cuda(lambda: sampling.argmax(model.logits(hx)), iters=10)["median_ms"]
+    head_ms = min(head_ms, 0.9 * step_ms)
+    block_ms = (step_ms - head_ms) / args.layers
+    full_step_ms = block_ms * depth + head_ms
     pre = sorted(pre_ms)[len(pre_ms) // 2]
     from .. import _native as nv
     print(json.dumps({
         "family": args.family, "layers_built": args.layers, "layers_full": depth, "batch": batch, "prompt": plen,
-        "decode_ms_per_step": round(step_ms, 3), "decode_ms_per_block": round(step_ms / args.layers, 4),
-        "decode_tok_s_at_full_depth": round(batch / (step_ms * scale) * 1e3, 1),
+        "decode_ms_per_step": round(step_ms, 3), "head_ms": round(head_ms, 3),
+        "decode_ms_per_block": round(block_ms, 4),
+        "decode_tok_s_at_full_depth": round(batch / full_step_ms * 1e3, 1),
         "prefill_ms_per_chunk": round(pre, 2), "prefill_chunk": chunk,
         "prefill_tok_s_at_full_depth": round(chunk / (pre * scale) * 1e3, 1),
-        "note": "extrapolated linearly in depth; embedding / lm_head cost counted once per built stack",
+        "note": "decode: (step - output head) / built blocks x full depth + output head; prefill: linear in depth",
         "device_status": nv.read_status(dev)}))
 
 
