@@ -378,6 +378,8 @@ def serve(cfg=None, *, host: Optional[str] = None, port: Optional[int] = None) -
     llm = LLM(cfg)
     if cfg.spec == "mtp" and getattr(llm.model, "mtp", None) is not None:
         llm.executor.enable_spec(cfg.spec_depth)
+    elif cfg.spec in ("dflash2", "ngram"):       # drafts from a pluggable proposer (proposers/factory.py)
+        llm.executor.enable_spec(cfg.spec_depth, proposer=cfg.spec)
     ckpt = cfg.weights if cfg.weights != "random" else None
     tok = load_tokenizer(ckpt, llm.target.vocab)
     engine = EngineLoop(llm.scheduler).start()
