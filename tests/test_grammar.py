@@ -122,3 +122,35 @@ def test_constrained_output_with_speculation_matches_plain_cpu():
     text = bytes(i for i in spec[0].output_ids if i < 256).decode()
     assert re.fullmatch(pat, text), text
     assert not spec[0].grammar.failed
+
+
+@pytest.mark.gpu
+def test_constrained_generation_gpu_graphs_and_speculation():
+    """The grammar bitmask is read by the sampling kernels inside the captured decode graph; with a proposer the
+    verify rows are masked too. Output stays inside the grammar, unconstrained neighbours are untouched."""
+    import re
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.dense import DenseModel
+    from hibana_b200.target import dense_tiny, scaled
+
+    t = scaled(dense_tiny(), weight_format="bf16", vocab=259)
+    model = DenseModel(t, "cuda", seed=0, init_device="cpu")
+    gs = _grammars()
+    pat = r"((ab|cd)x){3,6}!"
+    sp = [SamplingParams(max_tokens=40, constraint=gs.regex(pat), stop_ids=(EOS,)), SamplingParams(max_tokens=10),
+          SamplingParams(max_tokens=40, temperature=0.8, seed=3, constraint=gs.regex(pat), stop_ids=(EOS,))]
+    prompts = [list(b"abxabxabx repeat"), list(b"free"), list(b"sampled")]
+    ex = Executor(model, max_batch=4, max_ctx=128, use_graphs=True)
+    ex.capture_graphs()
+    out = ex.generate_batch(prompts, sp)
+    for i in (0, 2):
+        text = bytes(x for x in out[i].output_ids if x < 256).decode()
+        assert re.fullmatch(pat, text), text
+    free_alone = Executor(model, max_batch=4, max_ctx=128, use_graphs=True)
+    free_alone.capture_graphs()
+    assert free_alone.generate_batch(prompts[1:2], sp[1:2])[0].output_ids == out[1].output_ids
+    ex2 = Executor(model, max_batch=4, max_ctx=128, use_graphs=False)
+    ex2.enable_spec(depth=4, proposer="ngram")
+    spec = ex2.generate_batch(prompts[:2], sp[:2])
+    assert spec[0].output_ids == out[0].output_ids and spec[1].output_ids == out[1].output_ids
