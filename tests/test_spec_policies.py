@@ -159,3 +159,25 @@ def test_block_drafter_lattice_and_engine_exactness_cpu():
     ex2.enable_spec(depth=3, proposer=make_proposer("dflash2", executor=ex2, layers=1, heads=4, window=32))
     out = ex2.generate_batch(prompts, SamplingParams(max_tokens=8, temperature=0.8, seed=11))
     assert all(len(r.output_ids) == 8 and all(0 <= x < t.vocab for x in r.output_ids) for r in out)
+
+
+@pytest.mark.gpu
+def test_block_drafter_on_gpu_is_exact():
+    """The block drafter runs on the device (bf16 weights, shared embedding / head of the target); greedy output with
+    it equals plain greedy decoding on the same GPU model."""
+    import torch
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.dense import DenseModel
+    from hibana_b200.target import dense_tiny, scaled
+    t = scaled(dense_tiny(), weight_format="bf16")
+    model = DenseModel(t, "cuda", seed=0, init_device="cpu")
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, t.vocab, (n,), generator=g).tolist() for n in (40, 70)]
+    sp = SamplingParams(max_tokens=16)
+    plain = Executor(model, max_batch=4, max_ctx=160, use_graphs=False).generate_batch(prompts, sp)
+    ex = Executor(model, max_batch=4, max_ctx=160, use_graphs=False)
+    ex.enable_spec(depth=5, proposer=make_proposer("dflash2", executor=ex, layers=1, heads=4, window=64))
+    spec = ex.generate_batch(prompts, sp)
+    assert [r.output_ids for r in spec] == [r.output_ids for r in plain]
+    assert ex.spec.stats.rounds > 0
