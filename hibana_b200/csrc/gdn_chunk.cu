@@ -338,13 +338,18 @@ __global__ void __launch_bounds__(128, 2) gdn_phase1_kernel(const Phase1Params p
     bet[lane] = ta < p.n ? p.beta[static_cast<long long>(ta) * p.v_heads + h] : 0.f;
     bet[32 + lane] = tb < p.n ? p.beta[static_cast<long long>(tb) * p.v_heads + h] : 0.f;
   }
-  // ---- q, k rows: (l2norm,) scale, to shared memory; 16 rows per warp, a lane holds 4 of a row's 128 values
+  // ---- q, k rows: (l2norm,) scale, to shared memory; 16 rows per warp, a lane holds 4 of a row's 128 values.
+  // (restrict-qualified views and an unroll hint let the loads of several rows be in flight at once)
+  const __nv_bfloat16* __restrict__ gq = p.q;
+  const __nv_bfloat16* __restrict__ gk = p.k;
+  const __nv_bfloat16* __restrict__ gv = p.v;
+#pragma unroll 4
   for (int r = warp * 16; r < warp * 16 + 16; ++r) {
     const int t = t0 + r;
     float qv[4] = {0, 0, 0, 0}, kv[4] = {0, 0, 0, 0};
     if (t < p.n) {
-      const uint2 qq = *reinterpret_cast<const uint2*>(p.q + t * p.ldq + hk * GK + lane * 4);
-      const uint2 kk = *reinterpret_cast<const uint2*>(p.k + t * p.ldq + hk * GK + lane * 4);
+      const uint2 qq = *reinterpret_cast<const uint2*>(gq + t * p.ldq + hk * GK + lane * 4);
+      const uint2 kk = *reinterpret_cast<const uint2*>(gk + t * p.ldq + hk * GK + lane * 4);
       qv[0] = bf16_lo(qq.x); qv[1] = bf16_hi(qq.x); qv[2] = bf16_lo(qq.y); qv[3] = bf16_hi(qq.y);
       kv[0] = bf16_lo(kk.x); kv[1] = bf16_hi(kk.x); kv[2] = bf16_lo(kk.y); kv[3] = bf16_hi(kk.y);
     }
@@ -369,12 +374,13 @@ __global__ void __launch_bounds__(128, 2) gdn_phase1_kernel(const Phase1Params p
   const float g_last = gam[GC - 1];
   // ---- beta V, beta e^gamma Kn, and the decayed copies that go straight to global memory
   const long long tile = static_cast<long long>(h) * p.nc + c;
+#pragma unroll 4
   for (int r = warp * 16; r < warp * 16 + 16; ++r) {
     const int t = t0 + r;
     const float b = bet[r], eg = __expf(gam[r]), ed = __expf(g_last - gam[r]);
     float vv[4] = {0, 0, 0, 0};
     if (t < p.n) {
-      const uint2 x = *reinterpret_cast<const uint2*>(p.v + t * p.ldv + h * GK + lane * 4);
+      const uint2 x = *reinterpret_cast<const uint2*>(gv + t * p.ldv + h * GK + lane * 4);
       vv[0] = bf16_lo(x.x); vv[1] = bf16_hi(x.x); vv[2] = bf16_lo(x.y); vv[3] = bf16_hi(x.y);
     }
     const uint2 kn = *reinterpret_cast<const uint2*>(sm + P1_KN + r * P1_PK + lane * 8);
@@ -573,12 +579,16 @@ __global__ void __launch_bounds__(128, 2) ssd_phase1_kernel(const SsdP1Params p)
     gam[lane] = g0; gam[32 + lane] = g1;
     dtv[lane] = d0; dtv[32 + lane] = d1;
   }
+  const __nv_bfloat16* __restrict__ gb = p.b;
+  const __nv_bfloat16* __restrict__ gc = p.c;
+  const __nv_bfloat16* __restrict__ gx = p.x;
+#pragma unroll 4
   for (int r = warp * 16; r < warp * 16 + 16; ++r) {     // raw B and C rows of the group (zero rows past the end)
     const int t = t0 + r;
     uint2 bb = make_uint2(0, 0), cc = make_uint2(0, 0);
     if (t < p.n) {
-      bb = *reinterpret_cast<const uint2*>(p.b + t * p.ldb + grp * GK + lane * 4);
-      cc = *reinterpret_cast<const uint2*>(p.c + t * p.ldb + grp * GK + lane * 4);
+      bb = *reinterpret_cast<const uint2*>(gb + t * p.ldb + grp * GK + lane * 4);
+      cc = *reinterpret_cast<const uint2*>(gc + t * p.ldb + grp * GK + lane * 4);
     }
     *reinterpret_cast<uint2*>(sm + S_B + r * P1_PK + lane * 8) = bb;
     *reinterpret_cast<uint2*>(sm + S_C + r * P1_PK + lane * 8) = cc;
@@ -586,6 +596,7 @@ __global__ void __launch_bounds__(128, 2) ssd_phase1_kernel(const SsdP1Params p)
   __syncthreads();
   const float g_last = gam[GC - 1];
   const long long tile = static_cast<long long>(h) * p.nc + c;
+#pragma unroll 4
   for (int r = warp * 16; r < warp * 16 + 16; ++r) {
     const int t = t0 + r;
     const float eg = __expf(gam[r]), ed = __expf(g_last - gam[r]), d = dtv[r];
@@ -599,7 +610,7 @@ __global__ void __launch_bounds__(128, 2) ssd_phase1_kernel(const SsdP1Params p)
     for (int col = lane * 2; col < p.p; col += 64) {       // U = dt * x, two values per lane
       float2 xv = make_float2(0.f, 0.f);
       if (t < p.n) {
-        const uint32_t w = *reinterpret_cast<const uint32_t*>(p.x + t * p.ldx + h * p.p + col);
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(gx + t * p.ldx + h * p.p + col);
         xv = make_float2(bf16_lo(w) * d, bf16_hi(w) * d);
       }
       *reinterpret_cast<float2*>(p.u + (tile * GC + r) * p.p + col) = xv;
