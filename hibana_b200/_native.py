@@ -146,6 +146,19 @@ def device_state(device: torch.device) -> _DeviceState:
     return st
 
 
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded device-side wait (peer flag, arrival counter, mbarrier) gave up; the step's results are void."""
+
+    def __init__(self, code: int):
+        super().__init__(f"device-side wait ran out (status {code}: {STATUS_NAMES.get(code, 'unknown')})")
+        self.code = code
+
+
+STATUS_NAMES = {1: "tma stage never arrived", 2: "no free stage", 3: "accumulator never completed",
+                4: "peer flag", 5: "arrival counter", 6: "bad shape", 7: "drain", 8: "low-latency word",
+                9: "gated tile never saw its rows", 10: "expert-parallel receive buffer overflow"}
+
+
 def read_status(device: Optional[torch.device] = None) -> int:
     """Reads (and clears) the device status word; non-zero means a bounded wait gave up (see hb_common.cuh)."""
     device = device or torch.device("cuda", torch.cuda.current_device())

@@ -70,6 +70,13 @@ class EngineConfig:
     w3: bool = False
     stable_numerics: bool = False
     attn_splits: int = 0                   # 0 = automatic
+    fuse_epilogues: bool = True            # requantise / merge inside the producing kernel (decode shapes)
+    decode_attn: str = "mma"               # mma | tc (persistent tcgen05 kernel, head dim 128)
+    prefill_attn: str = "tc"               # tc | general
+    gdn_phase1: str = "cuda"               # cuda | torch
+    ssd_phase1: str = "cuda"               # cuda | torch
+    max_splits: int = 8                    # split-K cluster size cap (8 = portable)
+    pdl: int = 1                           # programmatic dependent launch level (0 off, 1 GEMMs, 2 small kernels too)
     # observability
     trace_dir: str = ""
     trace_cap_gb: float = 32.0

@@ -19,6 +19,7 @@
 #include "kv_tma.cuh"
 #include "hb_api.h"
 #include "hb_common.cuh"
+#include "rownorm.cuh"
 
 namespace hb {
 namespace {
@@ -47,6 +48,15 @@ struct DecParams {
   int use_tma;
   int* status;
   unsigned long long* prof;   // optional cycle counters of warp 0 (null = off)
+  // Fused split merge: one int per (sequence, kv head), zero between launches. The CTA that finds splits - 1
+  // earlier arrivals merges the partials of its (sequence, kv head) itself, so no merge kernel follows.
+  int* split_counter;
+  // Optional NVFP4 output of the merged (or unsplit) rows, the activation operand of the o projection:
+  // q_out [rows, hq * D / 2] packed e2m1, q_sf swizzled ue4m3 scales, *q_gscale the static per-tensor scale.
+  uint8_t* q_out;
+  uint8_t* q_sf;
+  const float* q_gscale;
+  int q_ka;
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -453,31 +463,93 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
     }
   }
   __syncthreads();
-  for (int i = tid; i < nq * D; i += DEC_WARPS * 32) {
-    const int qi = i / D, d = i % D;
-    float mt = -INFINITY;
+  const bool fused_merge = p.splits > 1 && p.split_counter != nullptr;
+  const bool direct = p.splits == 1;
+  // NVFP4 output goes through `fin` (the Q tile's shared memory: Q lives in registers by now) so that one thread
+  // owns a whole 16-element group; values are rounded to bf16 first, as the separate quantiser would see them.
+  __nv_bfloat16* fin = reinterpret_cast<__nv_bfloat16*>(qs);
+  {
+    for (int i = tid; i < nq * D; i += DEC_WARPS * 32) {
+      const int qi = i / D, d = i % D;
+      float mt = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w)
-      mt = fmaxf(mt, reinterpret_cast<const float*>(smem + w * C::WARP_BYTES)[16 * D + qi * 2]);
-    float acc = 0.f, lt = 0.f;
-    if (mt > -INFINITY) {
+      for (int w = 0; w < DEC_WARPS; ++w)
+        mt = fmaxf(mt, reinterpret_cast<const float*>(smem + w * C::WARP_BYTES)[16 * D + qi * 2]);
+      float acc = 0.f, lt = 0.f;
+      if (mt > -INFINITY) {
 #pragma unroll
-      for (int w = 0; w < DEC_WARPS; ++w) {
-        const float* wo = reinterpret_cast<const float*>(smem + w * C::WARP_BYTES);
-        const float mw = wo[16 * D + qi * 2];
-        const float sc = mw == -INFINITY ? 0.f : exp2f(mw - mt);
-        acc += sc * wo[qi * D + d];
-        lt += sc * wo[16 * D + qi * 2 + 1];
+        for (int w = 0; w < DEC_WARPS; ++w) {
+          const float* wo = reinterpret_cast<const float*>(smem + w * C::WARP_BYTES);
+          const float mw = wo[16 * D + qi * 2];
+          const float sc = mw == -INFINITY ? 0.f : exp2f(mw - mt);
+          acc += sc * wo[qi * D + d];
+          lt += sc * wo[16 * D + qi * 2 + 1];
+        }
+      }
+      const float val = lt > 0.f ? acc / lt : 0.f;
+      const int rr = qi / g, gg = qi % g;
+      const long long rh = static_cast<long long>(row0 + rr) * p.hq + kvh * g + gg;
+      if (direct) {
+        if (p.q_out == nullptr) p.out[rh * D + d] = __float2bfloat16(val);
+        else fin[i] = __float2bfloat16(val);
+      } else {
+        p.part_o[(rh * p.splits + split) * D + d] = val;
+        if (d == 0) p.part_lse[rh * p.splits + split] = lt > 0.f ? mt + log2f(lt) : -INFINITY;
       }
     }
-    const float val = lt > 0.f ? acc / lt : 0.f;
-    const int rr = qi / g, gg = qi % g;
-    const long long rh = static_cast<long long>(row0 + rr) * p.hq + kvh * g + gg;
-    if (p.splits == 1) {
-      p.out[rh * D + d] = __float2bfloat16(val);
-    } else {
-      p.part_o[(rh * p.splits + split) * D + d] = val;
-      if (d == 0) p.part_lse[rh * p.splits + split] = lt > 0.f ? mt + log2f(lt) : -INFINITY;
+  }
+  bool finish = direct && p.q_out != nullptr;
+  if (fused_merge) {
+    // Last arriver of this (sequence, kv head) merges: every CTA publishes its partial (fence, then one counted
+    // arrival); the one that counts splits - 1 before it re-arms the counter and reads all partials back from L2.
+    int* last_flag = reinterpret_cast<int*>(smem + C::BAR_OFF + 192);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      int* cnt = p.split_counter + b * p.hkv + kvh;
+      const int old = atomicAdd(cnt, 1);
+      const int last = old == p.splits - 1;
+      if (last) *cnt = 0;
+      *last_flag = last;
+    }
+    __syncthreads();
+    if (*last_flag) {
+      __threadfence();
+      for (int i = tid; i < nq * D; i += DEC_WARPS * 32) {
+        const int qi = i / D, d = i % D;
+        const int rr = qi / g, gg = qi % g;
+        const long long rh = static_cast<long long>(row0 + rr) * p.hq + kvh * g + gg;
+        float m = -INFINITY;
+        for (int s2 = 0; s2 < p.splits; ++s2) m = fmaxf(m, __ldcg(p.part_lse + rh * p.splits + s2));
+        float o = 0.f, wsum = 0.f;
+        if (m > -INFINITY) {
+          for (int s2 = 0; s2 < p.splits; ++s2) {
+            const float w = exp2f(__ldcg(p.part_lse + rh * p.splits + s2) - m);
+            if (w > 0.f) o += w * __ldcg(p.part_o + (rh * p.splits + s2) * D + d);
+            wsum += w;
+          }
+          o /= wsum;
+        }
+        if (p.q_out == nullptr) p.out[rh * D + d] = __float2bfloat16(o);
+        else fin[i] = __float2bfloat16(o);
+      }
+      finish = p.q_out != nullptr;
+    }
+  }
+  if (finish) {
+    __syncthreads();
+    const float inv_gs = 1.f / *p.q_gscale;
+    constexpr int GPR = D / 16;   // groups per (row, head)
+    for (int it = tid; it < nq * GPR; it += DEC_WARPS * 32) {
+      const int qi = it / GPR, gi = it % GPR;
+      float x[16];
+      load16(fin + qi * D + gi * 16, x);
+      uint2 packed;
+      const uint32_t sfb = quant16(x, inv_gs, &packed);
+      const int rr = qi / g, gg = qi % g;
+      const int row = row0 + rr, head = kvh * g + gg;
+      *reinterpret_cast<uint2*>(p.q_out + (static_cast<size_t>(row) * p.hq + head) * (D / 2) + gi * 8) = packed;
+      p.q_sf[row_sf_off(row, head * GPR + gi, p.q_ka)] = static_cast<uint8_t>(sfb);
     }
   }
   if (prof) {
@@ -524,6 +596,14 @@ int launch_decode(const DecParams& p0, const void* k_pool, const void* v_pool, l
 using namespace hb;
 
 static unsigned long long* g_dec_prof = nullptr;
+struct DecFuse {
+  int* counter = nullptr;
+  void* q_out = nullptr;
+  void* q_sf = nullptr;
+  const void* q_gscale = nullptr;
+  int q_ka = 0;
+};
+static thread_local DecFuse g_dec_fuse;
 
 extern "C" {
 
@@ -532,7 +612,17 @@ extern "C" {
 // [6] CTAs.
 void hb_attn_decode_profile(void* buf) { g_dec_prof = static_cast<unsigned long long*>(buf); }
 
-// bf16 KV only; rows_per_seq * (hq / hkv) must be <= 16. Partials go through hb_attn_merge when splits > 1.
+// Arms the fused tail for the NEXT hb_attn_decode call of this thread (consumed by that call): `split_counter`
+// (one zeroed int per sequence x kv head, re-armed by the kernel) makes the last-arriving split CTA merge the
+// partials, so no hb_attn_merge follows; q_out / q_sf / q_gscale (may be null) make the kernel write the rows as
+// NVFP4 instead of bf16 (`out` is then not written).
+void hb_attn_decode_fuse(void* split_counter, void* q_out, void* q_sf, const void* q_gscale, int q_ka) {
+  g_dec_fuse.counter = static_cast<int*>(split_counter);
+  g_dec_fuse.q_out = q_out; g_dec_fuse.q_sf = q_sf; g_dec_fuse.q_gscale = q_gscale; g_dec_fuse.q_ka = q_ka;
+}
+
+// bf16 KV only; rows_per_seq * (hq / hkv) must be <= 16. Partials go through hb_attn_merge when splits > 1 unless
+// hb_attn_decode_fuse armed the in-kernel merge.
 int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
                    long long head_stride,
                    const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len,
@@ -560,6 +650,13 @@ int hb_attn_decode(const void* q, const void* k_pool, const void* v_pool, long l
   p.causal = causal;
   p.status = static_cast<int*>(status);
   p.prof = g_dec_prof;
+  p.split_counter = g_dec_fuse.counter;
+  p.q_out = static_cast<uint8_t*>(g_dec_fuse.q_out);
+  p.q_sf = static_cast<uint8_t*>(g_dec_fuse.q_sf);
+  p.q_gscale = static_cast<const float*>(g_dec_fuse.q_gscale);
+  p.q_ka = g_dec_fuse.q_ka;
+  g_dec_fuse = DecFuse{};
+  if (p.q_out != nullptr && p.splits > 1 && p.split_counter == nullptr) return 1;
   if (p.splits > 1 && (part_o == nullptr || part_lse == nullptr)) return 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool t8 = max_rows * (hq / hkv) <= 8;

@@ -76,7 +76,7 @@ __device__ __forceinline__ bool wait_peers(Ctrl* mine, int world, int slot, int 
   if (threadIdx.x < world) {
     const unsigned long long t0 = globaltimer_ns();
     bool ok = false;
-    for (unsigned it = 0; it < HB_SPIN_LIMIT; ++it) {
+    for (unsigned long long it = 0, cap = spin_cap(limit_ns); it < cap; ++it) {
       if (ld_acquire_sys(&mine->flags[slot][threadIdx.x]) - seq >= 0) {
         ok = true;
         break;
@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(T) ar_norm_ll_kernel(const ArNormLlParams pp) 
           for (int k = 0; k < 4; ++k) {
             uint32_t data = 0, flag = 0;
             bool got = false;
-            for (unsigned it = 0; it < HB_SPIN_LIMIT; ++it) {
+            for (unsigned long long it = 0, cap = spin_cap(p.limit_ns); it < cap; ++it) {
               asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(data), "=r"(flag) : "l"(src + k) : "memory");
               if (static_cast<int>(flag) == seq) {
                 got = true;
@@ -326,7 +326,7 @@ __global__ void __launch_bounds__(T) rs_norm_ag_kernel(const RsNormAgParams p) {
     const int want = ld_relaxed_sys(&mine->sp_target) + p.expected;
     const unsigned long long t0 = globaltimer_ns();
     bool ok = false;
-    for (unsigned it = 0; it < HB_SPIN_LIMIT; ++it) {
+    for (unsigned long long it = 0, cap = spin_cap(p.limit_ns); it < cap; ++it) {
       if (ld_relaxed_sys(&mine->sp_cnt[threadIdx.x]) - want >= 0) {
         ok = true;
         break;

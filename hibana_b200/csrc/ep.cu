@@ -68,7 +68,7 @@ __device__ __forceinline__ bool wait_flags(const int* flags, int world, int seq,
   if (threadIdx.x < world) {
     const unsigned long long t0 = globaltimer_ns();
     bool ok = false;
-    for (unsigned it = 0; it < HB_SPIN_LIMIT; ++it) {
+    for (unsigned long long it = 0, cap = spin_cap(limit_ns); it < cap; ++it) {
       if (ld_acquire_sys(flags + threadIdx.x) - seq >= 0) {
         ok = true;
         break;

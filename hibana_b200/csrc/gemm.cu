@@ -35,6 +35,7 @@
 #include <cstring>
 
 #include "hb_common.cuh"
+#include "rownorm.cuh"
 
 namespace hb {
 namespace {
@@ -102,9 +103,33 @@ struct DevParams {
   int* ep_done;
   const float* tok_scale;
   const uint8_t* w3_tiles;   // kind w3: [row blocks][k_tiles][4096]
+  // kEpiSiluMulQuant
+  uint8_t* q_out;
+  uint8_t* q_sf;
+  const float* q_gscale;
+  int q_ka;
+  long long q_ld;
 };
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+// kEpiSiluMulQuant, second half: `stg` holds bf16 [ntok][64] SiLU-mul outputs of feature tile `tile_a` (64 output
+// features) for tokens tok0 .. tok0 + ntok. The 128 epilogue threads (et = 0..127) quantise one 16-element group
+// each per pass: 8 packed bytes into the token's row and one scale byte into the swizzled block layout.
+__device__ __forceinline__ void quant_stage(const DevParams& p, const __nv_bfloat16* stg, int ntok, int tok0,
+                                            int tile_a, int et) {
+  const float inv_gs = 1.f / *p.q_gscale;
+  for (int it = et; it < ntok * 4; it += 128) {
+    const int t = it >> 2, g = it & 3;
+    float x[16];
+    load16(stg + t * 64 + g * 16, x);
+    uint2 packed;
+    const uint32_t sfb = quant16(x, inv_gs, &packed);
+    const int tok = tok0 + t;
+    *reinterpret_cast<uint2*>(p.q_out + static_cast<size_t>(tok) * p.q_ld + tile_a * 32 + g * 8) = packed;
+    p.q_sf[row_sf_off(tok, tile_a * 4 + g, p.q_ka)] = static_cast<uint8_t>(sfb);
+  }
+}
 
 // Applies the epilogue to CH accumulator values of one thread: `row` indexes the A operand, columns
 // [col0, col0 + CH) the B operand.
@@ -361,7 +386,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         const int want = *reinterpret_cast<const volatile int*>(p.peer_base[p.rank] + p.seq_offset);
         const uint64_t t0 = globaltimer_ns();
         ready = false;
-        for (uint32_t it = 0; it < HB_SPIN_LIMIT; ++it) {
+        for (unsigned long long it = 0, cap = spin_cap(p.limit_ns); it < cap; ++it) {
           int v;
           asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
           if (v - want >= 0) {
@@ -376,7 +401,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         const uint64_t t0 = globaltimer_ns();
         for (int r = 0; r < p.world && ready; ++r) {
           ready = false;
-          for (uint32_t it = 0; it < HB_SPIN_LIMIT; ++it) {
+          for (unsigned long long it = 0, cap = spin_cap(p.limit_ns); it < cap; ++it) {
             int v;
             asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p.ep_gate_flags + r) : "memory");
             if (v - want >= 0) {
@@ -590,6 +615,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
           asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
         }
       }
+    } else if (ok && p.splits == 1 && p.epilogue == kEpiSiluMulQuant) {
+      // Weights on the 128-row side, gate / up rows interleaved: lane pairs hold (gate, up) of one output feature.
+      // Even lanes park the bf16 SiLU-mul result as [token][64 features] in the idle stage ring, then the four
+      // warps quantise the tile together.
+      __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem);
+      const int ncols = min(BN, col_lim - b_row0);
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        uint32_t r[CH];
+        if constexpr (CH == 32) tmem_ld_32x32(tlane + c0, r);
+        else tmem_ld_32x16(tlane + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const float x = nkt > 0 ? __uint_as_float(r[j]) * alpha : 0.f;
+          const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+          if ((lane & 1) == 0 && c0 + j < ncols)
+            stg[(c0 + j) * 64 + ((q * 32 + lane) >> 1)] = __float2bfloat16(silu(x) * other);
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      quant_stage(p, stg, ncols, b_row0, tile_a, static_cast<int>(threadIdx.x) - 64);
     } else if (ok && p.splits == 1) {
       for (int c0 = 0; c0 < BN; c0 += CH) {
         uint32_t r[CH];
@@ -634,6 +680,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
       const int c_begin = split * per;
       const int c_end = min(ncols, c_begin + per);
       const uint32_t part_local = smem_u32(smem);
+      const bool requant = p.epilogue == kEpiSiluMulQuant;
+      // kEpiSiluMulQuant: this CTA's token slice is parked behind the fp32 partial (which peers still read)
+      __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + BN * BM * 4);
       for (int c0 = c_begin; c0 < c_end; c0 += 16) {
         float v[16];
 #pragma unroll
@@ -644,7 +693,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
           for (int j = 0; j < 16; ++j)
             if (c0 + j < c_end) v[j] += ld_dsmem_f32(src + j * BM * 4);
         }
-        epilogue_chunk<16>(p, v, row, row_lim, b_row0 + c0, b_row0 + c_end, alpha, lane);
+        if (requant) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float x = v[j] * alpha;
+            const float other = __shfl_xor_sync(0xffffffffu, x, 1);
+            if ((lane & 1) == 0 && c0 + j < c_end) stg[(c0 - c_begin + j) * 64 + (lrow >> 1)] = __float2bfloat16(silu(x) * other);
+          }
+        } else {
+          epilogue_chunk<16>(p, v, row, row_lim, b_row0 + c0, b_row0 + c_end, alpha, lane);
+        }
+      }
+      if (requant) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (c_end > c_begin) quant_stage(p, stg, c_end - c_begin, b_row0 + c_begin, tile_a, static_cast<int>(threadIdx.x) - 64);
       }
     }
     __syncwarp();
@@ -859,6 +921,15 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   }
   p.tok_scale = a.tok_scale;
+  p.q_out = static_cast<uint8_t*>(a.q_out); p.q_sf = static_cast<uint8_t*>(a.q_sf); p.q_gscale = a.q_gscale;
+  p.q_ka = a.q_ka; p.q_ld = a.q_ld;
+  if (a.epilogue == kEpiSiluMulQuant) {
+    // tokens on the N side, whole 128-row feature tiles, no grouped / peer variants; the staging tile of a split-K
+    // CTA sits behind its fp32 partial, which the smallest ring must still hold
+    if (!a.swap || grouped || a.peer != nullptr || a.tok_scale != nullptr || a.ra % BM != 0 || a.q_out == nullptr ||
+        a.q_sf == nullptr || a.q_gscale == nullptr || a.q_ka * 64 < a.ra / 2 || a.bn > 128)
+      return cudaErrorInvalidValue;
+  }
   p.early_launch = g_pdl >= 2;
   p.w3_tiles = w3 ? static_cast<const uint8_t*>(a.a) : nullptr;
   p.ep_gate_flags = nullptr; p.ep_seq_ptr = nullptr; p.ep_row_ret = nullptr; p.ep_done = nullptr;
@@ -916,6 +987,25 @@ int hb_gemm(int kind, const void* a, const void* b, const void* sfa, const void*
   g.status = static_cast<int*>(status); g.bn = bn; g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
   g.grp_start = nullptr; g.grp_cnt = nullptr; g.grp_rows_a = 0; g.grp_experts = 0; g.grp_chunks = 0;
   g.peer = nullptr;
+  const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// Weights on the 128-row side (a = weights [n, k], b = activations [m, k]) with the SiLU-mul + NVFP4 requant
+// epilogue: writes packed e2m1 [m, n / 4 bytes] to q_out and swizzled scales to q_sf (see hb::kEpiSiluMulQuant).
+int hb_gemm_silu_quant(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int n, int m, int k,
+                       long long lda, long long ldb, const void* alpha_ptr, void* q_out, void* q_sf,
+                       const void* q_gscale, int q_ka, int splits, void* status, int bn, int ka_a, int ka_b,
+                       void* stream) {
+  hb::GemmArgs g;
+  g.kind = kind; g.a = a; g.b = b; g.sfa = sfa; g.sfb = sfb; g.ra = n; g.rb = m; g.k = k;
+  g.lda = lda; g.ldb = ldb; g.out = nullptr; g.ldo = 0; g.residual = nullptr; g.alpha = 1.f;
+  g.alpha_ptr = static_cast<const float*>(alpha_ptr); g.epilogue = hb::kEpiSiluMulQuant; g.swap = 1; g.splits = splits;
+  g.workspace = nullptr; g.counters = nullptr; g.status = static_cast<int*>(status); g.bn = bn;
+  g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
+  g.grp_start = nullptr; g.grp_cnt = nullptr; g.grp_rows_a = 0; g.grp_experts = 0; g.grp_chunks = 0;
+  g.peer = nullptr;
+  g.q_out = q_out; g.q_sf = q_sf; g.q_gscale = static_cast<const float*>(q_gscale); g.q_ka = q_ka; g.q_ld = n / 4;
   const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

@@ -25,6 +25,10 @@ enum GemmEpilogue : int {
                       // routed row) is stored into the return buffer of the rank the row came from, at the row
                       // that rank asked for; when every CTA is done the kernel raises a flag on every rank
   kEpiRelu2 = 6,      // out = max(alpha * acc, 0)^2            (bf16; weights on the 128-row side only)
+  kEpiSiluMulQuant = 7,  // SiLU-mul as in kEpiSiluMul, then requantised to NVFP4 in the same epilogue: packed e2m1
+                         // rows go to q_out, ue4m3 scales to q_sf (128x4-swizzled blocks) with the static per-tensor
+                         // scale *q_gscale of the consuming projection. Weights on the 128-row side only; the next
+                         // GEMM reads the result as its activation operand with no kernel in between.
 };
 
 // Peer-memory fusion arguments (all ranks pass the same offsets; pointers are this process's mappings).
@@ -89,6 +93,13 @@ struct GemmArgs {
   int grp_tile_cap = 0;
   const GemmPeer* peer;     // null = no peer fusion
   const GemmEp* ep = nullptr;   // null = no expert-parallel fusion (grouped mode only)
+  // kEpiSiluMulQuant outputs: q_out [tokens, q_ld bytes] packed e2m1, q_sf swizzled scales with q_ka K atoms per
+  // row block, q_gscale the device scalar x ~= q * sf * gscale. Scale bytes of padding rows / groups are not written.
+  void* q_out = nullptr;
+  void* q_sf = nullptr;
+  const float* q_gscale = nullptr;
+  int q_ka = 0;
+  long long q_ld = 0;
   const float* tok_scale = nullptr;   // optional per-token factor (dynamic per-row activation scale): indexed by
                                       // the token, i.e. the B row with `swap`, else the A row
 };

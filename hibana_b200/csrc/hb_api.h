@@ -14,6 +14,12 @@ int hb_gemm(int kind, const void* a, const void* b, const void* sfa, const void*
             long long lda, long long ldb, void* out, long long ldo, const void* residual, float alpha,
             const void* alpha_ptr, int epilogue, int swap, int splits, void* workspace, void* counters,
             void* status, int bn, int ka_a, int ka_b, void* stream);
+// Decode-shaped gate/up projection (a = weights [n, k] with gate / up rows interleaved, b = activations [m, k]):
+// SiLU-mul and NVFP4 requantisation in the epilogue; q_out [m, n / 4] packed e2m1, q_sf swizzled ue4m3 scales.
+int hb_gemm_silu_quant(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int n, int m, int k,
+                       long long lda, long long ldb, const void* alpha_ptr, void* q_out, void* q_sf,
+                       const void* q_gscale, int q_ka, int splits, void* status, int bn, int ka_a, int ka_b,
+                       void* stream);
 int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int experts,
                     int n_per_expert, int b_rows, int k, void* out, long long ldo, const void* alpha_ptr,
                     int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status, int ka_a,

@@ -43,6 +43,10 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// Iteration cap of a peer wait whose wall limit is `limit_ns`: one poll of peer-visible memory takes far longer than
+// 16 ns, so the nanosecond limit is what ends a failed wait and this cap only backs it up (a `limit_ns` of several
+// seconds is honoured in full).
+__device__ __forceinline__ unsigned long long spin_cap(unsigned long long limit_ns) { return (limit_ns >> 4) + 65536ull; }
 __device__ __forceinline__ void set_status(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }

@@ -15,38 +15,6 @@
 namespace hb {
 namespace {
 
-// Offset of the scale byte of (row, 16-element group g) in the swizzled layout with `ka` K atoms per block row.
-__device__ __forceinline__ size_t sf_offset(int row, int g, int ka) {
-  const int rb = row >> 7, ri = row & 127;
-  return (static_cast<size_t>(rb) * ka + (g >> 2)) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + (g & 3);
-}
-
-// Quantises 16 floats: writes 8 packed bytes and returns the ue4m3 scale byte.
-__device__ __forceinline__ uint32_t quant16(const float (&x)[16], float inv_gs, uint2* packed) {
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
-  const uint32_t sfb = float_to_e4m3(amax * (1.f / 6.f) * inv_gs);
-  const float sf = e4m3_to_float(sfb);
-  const float inv = sf > 0.f ? 1.f / (sf * (1.f / inv_gs)) : 0.f;
-  uint32_t w[2] = {0, 0};
-#pragma unroll
-  for (int i = 0; i < 16; ++i) w[i >> 3] |= float_to_e2m1(x[i] * inv) << (4 * (i & 7));
-  *packed = make_uint2(w[0], w[1]);
-  return sfb;
-}
-
-__device__ __forceinline__ void load16(const __nv_bfloat16* p, float (&x)[16]) {
-  const uint4 a = reinterpret_cast<const uint4*>(p)[0];
-  const uint4 b = reinterpret_cast<const uint4*>(p)[1];
-  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    x[2 * i] = bf16_lo(w[i]);
-    x[2 * i + 1] = bf16_hi(w[i]);
-  }
-}
-
 // One thread per 16-element group over the padded scale extent (padding scales are written as zero).
 // mode 0: y = x; mode 1: y = silu(x[:, :K]) * x[:, K:2K] (x has 2K columns, gate first);
 // mode 2: gate/up interleaved pairwise (x[:, 2j], x[:, 2j+1]).
@@ -66,7 +34,7 @@ __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long lon
   // Row-indirect mode (MoE): output row `row` of the sorted buffer takes input row src_rows[row] (-1 = padding).
   const int in_row = src_rows != nullptr ? (row < m ? src_rows[row] : -1) : row;
   if (row >= m || in_row < 0 || g * 16 >= k) {
-    sf[sf_offset(row, g, ka)] = 0;
+    sf[row_sf_off(row, g, ka)] = 0;
     return;
   }
   const float inv_gs = 1.f / *gscale;
@@ -96,7 +64,7 @@ __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long lon
   uint2 packed;
   const uint32_t sfb = quant16(v, inv_gs, &packed);
   *reinterpret_cast<uint2*>(q + static_cast<size_t>(row) * (k / 2) + g * 8) = packed;
-  sf[sf_offset(row, g, ka)] = static_cast<uint8_t>(sfb);
+  sf[row_sf_off(row, g, ka)] = static_cast<uint8_t>(sfb);
 }
 
 // (residual add +) RMSNorm -> NVFP4 (and / or bf16). One CTA per row on the register-resident row core.
@@ -113,7 +81,7 @@ norm_quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __re
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
   if (row >= m) {   // padding rows of the last 128-row scale block: zero scales, nothing else
-    for (int g = tid; g < ka * 4; g += T) sf[sf_offset(row, g, ka)] = 0;
+    for (int g = tid; g < ka * 4; g += T) sf[row_sf_off(row, g, ka)] = 0;
     return;
   }
   const int nchunk = k >> 3;
@@ -156,7 +124,7 @@ __global__ void sf_pad_rows_kernel(uint8_t* sf, int m, int ka) {
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long n = static_cast<long long>(rows_pad - m) * groups_pad;
   if (idx >= n) return;
-  sf[sf_offset(m + static_cast<int>(idx / groups_pad), static_cast<int>(idx % groups_pad), ka)] = 0;
+  sf[row_sf_off(m + static_cast<int>(idx / groups_pad), static_cast<int>(idx % groups_pad), ka)] = 0;
 }
 
 // Static per-tensor FP8 (e4m3): q = sat(x / scale). 8 elements per thread.

@@ -21,6 +21,33 @@ __device__ __forceinline__ size_t row_sf_off(int row, int g, int ka) {
   return (static_cast<size_t>(rb) * ka + (g >> 2)) * 512 + (ri & 31) * 16 + (ri >> 5) * 4 + (g & 3);
 }
 
+// Quantises 16 floats to NVFP4: writes 8 packed bytes and returns the ue4m3 scale byte (x ~= q * sf * global scale).
+__device__ __forceinline__ uint32_t quant16(const float (&x)[16], float inv_gs, uint2* packed) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  const uint32_t sfb = float_to_e4m3(amax * (1.f / 6.f) * inv_gs);
+  const float sf = e4m3_to_float(sfb);
+  const float inv = sf > 0.f ? 1.f / (sf * (1.f / inv_gs)) : 0.f;
+  uint32_t w[2] = {0, 0};
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i >> 3] |= float_to_e2m1(x[i] * inv) << (4 * (i & 7));
+  *packed = make_uint2(w[0], w[1]);
+  return sfb;
+}
+
+// 16 consecutive bf16 values (32-byte aligned address, global or shared) as floats.
+__device__ __forceinline__ void load16(const __nv_bfloat16* p, float (&x)[16]) {
+  const uint4 a = reinterpret_cast<const uint4*>(p)[0];
+  const uint4 b = reinterpret_cast<const uint4*>(p)[1];
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    x[2 * i] = bf16_lo(w[i]);
+    x[2 * i + 1] = bf16_hi(w[i]);
+  }
+}
+
 __device__ __forceinline__ void unpack8(const uint4& a, float (&f)[8]) {
   f[0] = bf16_lo(a.x); f[1] = bf16_hi(a.x); f[2] = bf16_lo(a.y); f[3] = bf16_hi(a.y);
   f[4] = bf16_lo(a.z); f[5] = bf16_hi(a.z); f[6] = bf16_lo(a.w); f[7] = bf16_hi(a.w);

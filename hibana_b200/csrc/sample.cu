@@ -162,7 +162,175 @@ __device__ __forceinline__ float uniform01(unsigned long long seed, unsigned lon
   return static_cast<float>(z >> 40) * (1.0f / 16777216.0f);
 }
 
-constexpr int SAMPLE_K = 64;  // candidates kept per row (top-k <= 64; top-p is applied inside the candidates)
+// ---- full-vocabulary sampling (top-k off or above SAMPLE_K): softmax over every allowed token, nucleus by an exact
+// threshold search, inverse-CDF draw in index order. Same law as engine/rejection.py `distribution`.
+__device__ __forceinline__ unsigned order_key(float v) {   // order-preserving map float -> uint32
+  const unsigned b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(unsigned k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__device__ __forceinline__ float block_sum256(float v, float* red) {   // 256 threads, deterministic
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) t += red[w];
+  return t;
+}
+
+template <typename T>
+__device__ void sample_full_row(const T* __restrict__ lr, int vocab, const int* __restrict__ mask, float temp,
+                                float p_lim, float u01, long long* out, float* out_prob) {
+  __shared__ float red[8];
+  __shared__ float csum[256];
+  __shared__ int ceq[256];
+  __shared__ int s_pick_thread;
+  __shared__ float s_base;
+  __shared__ int s_eq_base;
+  const int tid = threadIdx.x;
+  const float inv_t = 1.f / temp;
+  float mx = -INFINITY;
+  for (int i = tid; i < vocab; i += 256)
+    if (mask_ok(mask, i)) mx = fmaxf(mx, ldf<T>(lr, i));
+  mx = warp_max(mx);
+  __syncthreads();
+  if ((tid & 31) == 0) red[tid >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
+  float z = 0.f;
+  for (int i = tid; i < vocab; i += 256)
+    if (mask_ok(mask, i)) {
+      const float v = ldf<T>(lr, i);
+      if (v > -INFINITY) z += __expf((v - mx) * inv_t);
+    }
+  z = block_sum256(z, red);
+  // nucleus: the smallest prefix, in (value desc, index asc) order, whose mass reaches p_lim * z. t_key = the value
+  // of the token that crosses the line (largest key whose upper set still holds the mass); tokens above it stay,
+  // and of the tokens equal to it the first `need_eq` in index order.
+  unsigned t_key = 0;
+  int need_eq = 0x7fffffff;
+  float kept = z;
+  if (p_lim < 1.f) {
+    const float want = p_lim * z;
+    unsigned lo = 0, hi = order_key(mx);
+    while (lo < hi) {
+      const unsigned mid = lo + ((hi - lo + 1) >> 1);
+      float mass = 0.f;
+      for (int i = tid; i < vocab; i += 256)
+        if (mask_ok(mask, i)) {
+          const float v = ldf<T>(lr, i);
+          if (v > -INFINITY && order_key(v) >= mid) mass += __expf((v - mx) * inv_t);
+        }
+      mass = block_sum256(mass, red);
+      if (mass >= want) lo = mid;
+      else hi = mid - 1;
+    }
+    t_key = lo;
+    float above = 0.f, eq = 0.f;
+    for (int i = tid; i < vocab; i += 256)
+      if (mask_ok(mask, i)) {
+        const float v = ldf<T>(lr, i);
+        if (v > -INFINITY) {
+          const unsigned k = order_key(v);
+          if (k > t_key) above += __expf((v - mx) * inv_t);
+          else if (k == t_key) eq += 1.f;
+        }
+      }
+    above = block_sum256(above, red);
+    eq = block_sum256(eq, red);
+    const float w_t = __expf((key_value(t_key) - mx) * inv_t);
+    int need = w_t > 0.f ? static_cast<int>(ceilf((want - above) / w_t)) : 1;
+    need = max(1, min(need, static_cast<int>(eq)));
+    need_eq = need;
+    kept = above + need * w_t;
+  }
+  // draw: contiguous chunk per thread, chunk sums scanned by thread 0, the owning thread walks its chunk
+  const int per = (vocab + 255) / 256;
+  const int lo_i = tid * per, hi_i = min(vocab, lo_i + per);
+  float mine = 0.f;
+  int my_eq = 0;
+  for (int i = lo_i; i < hi_i; ++i)
+    if (mask_ok(mask, i)) {
+      const float v = ldf<T>(lr, i);
+      if (v > -INFINITY) {
+        const unsigned k = order_key(v);
+        if (k == t_key && p_lim < 1.f) ++my_eq;
+        else if (k > t_key || p_lim >= 1.f) mine += __expf((v - mx) * inv_t);
+      }
+    }
+  csum[tid] = mine;
+  ceq[tid] = my_eq;
+  __syncthreads();
+  const float u = u01 * kept;
+  if (tid == 0) {
+    const float w_t = p_lim < 1.f ? __expf((key_value(t_key) - mx) * inv_t) : 0.f;
+    float acc = 0.f;
+    int eq_seen = 0, pick = -1, last = 0;
+    float base = 0.f;
+    int eq_base = 0;
+    for (int t = 0; t < 256; ++t) {
+      const int take = max(0, min(ceq[t], need_eq - eq_seen));
+      const float w = csum[t] + take * w_t;
+      if (w > 0.f) last = t;
+      if (pick < 0 && u < acc + w) {
+        pick = t;
+        base = acc;
+        eq_base = eq_seen;
+      }
+      acc += w;
+      eq_seen += ceq[t];
+    }
+    if (pick < 0) {   // rounding: u landed past the last kept token
+      pick = last;
+      base = -1.f;
+    }
+    s_pick_thread = pick;
+    s_base = base;
+    s_eq_base = eq_base;
+  }
+  __syncthreads();
+  if (tid == s_pick_thread) {
+    const float w_t = p_lim < 1.f ? __expf((key_value(t_key) - mx) * inv_t) : 0.f;
+    float acc = s_base;
+    int eq_seen = s_eq_base, chosen = -1, last_kept = -1;
+    float w_chosen = 0.f, w_last = 0.f;
+    for (int i = lo_i; i < hi_i; ++i) {
+      if (!mask_ok(mask, i)) continue;
+      const float v = ldf<T>(lr, i);
+      if (!(v > -INFINITY)) continue;
+      const unsigned k = order_key(v);
+      float w = 0.f;
+      if (p_lim >= 1.f || k > t_key) w = __expf((v - mx) * inv_t);
+      else if (k == t_key) {
+        if (eq_seen < need_eq) w = w_t;
+        ++eq_seen;
+      }
+      if (w <= 0.f) continue;
+      last_kept = i;
+      w_last = w;
+      if (s_base >= 0.f && u < acc + w) {
+        chosen = i;
+        w_chosen = w;
+        break;
+      }
+      acc += w;
+    }
+    if (chosen < 0) {
+      chosen = last_kept < 0 ? 0 : last_kept;
+      w_chosen = w_last;
+    }
+    *out = chosen;
+    if (out_prob) *out_prob = w_chosen / kept;
+  }
+}
+
+constexpr int SAMPLE_K = 64;  // candidates kept per row for 1 <= top-k <= 64 (top-p is applied inside them)
 
 // One CTA per row. Keeps the SAMPLE_K largest logits by repeated threshold passes (vocab is read a few times from
 // L2), then softmax / top-p / inverse-CDF draw on the candidates. temperature <= 0 means greedy.
@@ -184,8 +352,15 @@ sample_kernel(const T* __restrict__ logits, long long ld, int vocab, const float
   const int* mask = bitmask ? bitmask + static_cast<long long>(row) * mask_words : nullptr;
   const float temp = temperature ? temperature[row] : 0.f;
   if (skip_greedy && temp <= 0.f) return;   // the two-stage argmax owns greedy rows
-  int k = top_k ? top_k[row] : SAMPLE_K;
-  if (k <= 0 || k > SAMPLE_K) k = SAMPLE_K;
+  int k = top_k ? top_k[row] : 0;
+  if (temp > 0.f && (k <= 0 || k > SAMPLE_K)) {
+    // top-k off (the API default) or wider than the candidate list: the law is the softmax over the whole
+    // vocabulary (then top-p), not over the SAMPLE_K largest logits
+    sample_full_row<T>(lr, vocab, mask, temp, top_p ? top_p[row] : 1.f,
+                       uniform01(seeds ? seeds[row] : 0ull, offsets ? offsets[row] : 0ull), out + row,
+                       out_prob ? out_prob + row : nullptr);
+    return;
+  }
   if (temp <= 0.f) k = 1;
   if (threadIdx.x == 0) {
     s_prev_v = INFINITY;

@@ -68,6 +68,23 @@ class ModelRunner:
         self.graph_launches: dict[int, int] = {}   # kernels of this library inside each bucket's graph
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        # The device status word travels to the host with every step's sampled tokens (same stream, same
+        # synchronize): a bounded wait that gave up anywhere in the step voids it, and every later collective
+        # would give up at once, so the step raises instead of streaming garbage.
+        self._status_dev = nv.device_state(self.device).status if self.device.type == "cuda" else None
+        self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+
+    def _queue_status_read(self) -> None:
+        if self._status_dev is not None:
+            self._status_host.copy_(self._status_dev[:1], non_blocking=True)
+
+    def _raise_on_status(self) -> None:
+        """Call after the synchronize that follows `_queue_status_read`."""
+        code = int(self._status_host[0]) if self._status_dev is not None else 0
+        if code:
+            self._status_dev.zero_()
+            self._status_host.zero_()
+            raise nv.DeviceWaitTimeout(code)
 
     # ---- block table rows
     def alloc_row(self) -> int:
@@ -189,9 +206,11 @@ class ModelRunner:
         else:
             self._decode_body(buf)
         buf.out_host.copy_(buf.out, non_blocking=True)
+        self._queue_status_read()
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
-        self.d2h_bytes += buf.bucket * 8
+        self.d2h_bytes += buf.bucket * 8 + (4 if self._status_dev is not None else 0)
+        self._raise_on_status()
         return buf.out_host[:n].tolist()
 
     # ---- prefill / verify (eager, ragged)
@@ -263,6 +282,8 @@ class ModelRunner:
                 ((k, sampling_rows[k]) for k in ("temp", "top_k", "top_p", "seed", "offs")),
                 (torch.float32, torch.int32, torch.float32, torch.int64, torch.int64))}
             tok = sampling.sample(logits, sr["temp"], sr["top_k"], sr["top_p"], sr["seed"], sr["offs"], bitmask=masks)
-        out = tok.cpu()
-        self.d2h_bytes += out.numel() * 8
+        self._queue_status_read()
+        out = tok.cpu()         # synchronises the stream: the status word queued before it has landed too
+        self.d2h_bytes += out.numel() * 8 + (4 if self._status_dev is not None else 0)
+        self._raise_on_status()
         return out.tolist()

@@ -13,6 +13,7 @@ from typing import Optional
 
 import torch
 
+from .. import config as cfgmod
 from ..engine.context import ForwardContext
 from ..ops import attention, basic, gemm, nvfp4
 from ..target import Target
@@ -124,7 +125,7 @@ class DenseModel:
             lin.set_input_amax(amax * 1.5)
 
     # ---- forward
-    def _reduce_norm_linear(self, h, slot, res, norm_w, lin, ctx, epilogue=gemm.EPI_STORE):
+    def _reduce_norm_linear(self, h, slot, res, norm_w, lin, ctx, epilogue=gemm.EPI_STORE, requant=None):
         """lin(rmsnorm(allreduce(h) + res)). `h` is this rank's partial; with the fused path it already sits in
         heap slot `slot` and one kernel does all-reduce + add + norm + quant."""
         t = self.target
@@ -134,10 +135,10 @@ class DenseModel:
             qs = lin.input_scale if lin.fmt == "nvfp4" else None
             y, xq = comm.allreduce_norm(slot, rows, t.hidden, residual=res, weight=norm_w, eps=t.norm_eps,
                                         quant_scale=qs, want_bf16=qs is None)
-            return lin(xq if xq is not None else y, epilogue=epilogue)
+            return lin(xq if xq is not None else y, epilogue=epilogue, requant=requant)
         if comm is not None:
             h = comm.all_reduce(h)
-        return norm_linear(h, res, norm_w, t.norm_eps, lin, epilogue=epilogue)
+        return norm_linear(h, res, norm_w, t.norm_eps, lin, epilogue=epilogue, requant=requant)
 
     def _row_parallel(self, lin, x, ctx):
         """Row-parallel projection; returns (partial, heap slot or None)."""
@@ -193,6 +194,8 @@ class DenseModel:
         res = basic.embedding(ids, self.embed)
         h: Optional[torch.Tensor] = None
         slot = None
+        if ctx.comm is not None and hasattr(ctx.comm, "begin_forward"):
+            ctx.comm.begin_forward(2 * len(self.layers))
         for i, layer in enumerate(self.layers):
             if h is None:
                 qkv = norm_linear(res, None, layer.input_norm, t.norm_eps, layer.qkv, add_residual=False)
@@ -200,13 +203,19 @@ class DenseModel:
                 qkv = self._reduce_norm_linear(h, slot, res, layer.input_norm, layer.qkv, ctx)
             q = basic.rope_kv_write(qkv, ctx.positions, ctx.slots, self.inv_freq, kv.k[i], kv.v[i], t.q_heads,
                                     t.kv_heads, t.head_dim, rot=t.rot_dim, kv_scale=kv.kv_scale)
+            # decode-shaped steps hand NVFP4 activations from kernel to kernel: the attention kernel merges its KV
+            # splits and quantises for o_proj, the gate/up GEMM requantises for down in its epilogue
+            fuse = (cfgmod.current().fuse_epilogues and layer.o.fmt == "nvfp4" and not layer.o.calibrating
+                    and q.shape[0] <= 128 and q.is_cuda)
             att = attention.paged_attention(q, kv.k[i], kv.v[i], ctx.kv_indices, ctx.ctx_len, q_indptr=ctx.q_indptr,
                                             max_rows=ctx.max_rows, seq_rows=ctx.seq_rows, scale=self.scale,
                                             kv_scale=kv.kv_scale, splits=ctx.attn_splits,
-                                            workspace=ctx.attn_workspace)
-            h, slot = self._row_parallel(layer.o, att.view(att.shape[0], -1), ctx)
+                                            workspace=ctx.attn_workspace,
+                                            quant_scale=layer.o.input_scale if fuse else None)
+            h, slot = self._row_parallel(layer.o, att if fuse else att.view(att.shape[0], -1), ctx)
             act = self._reduce_norm_linear(h, slot, res, layer.post_norm, layer.gate_up, ctx,
-                                           epilogue=gemm.EPI_SILU_MUL)
+                                           epilogue=gemm.EPI_SILU_MUL,
+                                           requant=layer.down.input_scale if fuse else None)
             h, slot = self._row_parallel(layer.down, act, ctx)
         comm = ctx.comm
         if comm is not None and slot is not None:

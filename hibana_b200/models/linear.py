@@ -109,16 +109,22 @@ class Linear:
         return nvfp4.quantize(x, self.input_scale, mode)
 
     def __call__(self, x: Activation, *, epilogue: int = gemm.EPI_STORE, residual: Optional[torch.Tensor] = None,
-                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 out: Optional[torch.Tensor] = None, requant: Optional[torch.Tensor] = None):
+        """`requant` (the consuming projection's static input scale; SiLU-mul epilogue only): return the result as
+        an Nvfp4Tensor, quantised inside the GEMM epilogue where the shape allows it."""
         if self.fmt == "bf16":
-            return gemm.linear_bf16(x, self.weight, epilogue=epilogue, residual=residual, out=out)
+            y = gemm.linear_bf16(x, self.weight, epilogue=epilogue, residual=residual, out=out)
+            return y if requant is None else nvfp4.quantize(y, requant)
         xq = x if isinstance(x, Nvfp4Tensor) else self.quantize_input(x)
-        return gemm.linear_nvfp4(xq, self.wq, self.alpha, epilogue=epilogue, residual=residual, out=out)
+        if requant is not None and epilogue == gemm.EPI_SILU_MUL:
+            return gemm.linear_nvfp4_silu_quant(xq, self.wq, self.alpha, requant)
+        y = gemm.linear_nvfp4(xq, self.wq, self.alpha, epilogue=epilogue, residual=residual, out=out)
+        return y if requant is None else nvfp4.quantize(y, requant)
 
 
 def norm_linear(x: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
                 lin: Linear, *, gemma: bool = False, epilogue: int = gemm.EPI_STORE,
-                add_residual: bool = True) -> torch.Tensor:
+                add_residual: bool = True, requant: Optional[torch.Tensor] = None):
     """lin(rmsnorm(x + residual)); `residual` is updated in place with the sum when add_residual."""
     res = residual if add_residual else None
     if lin.fmt == "nvfp4":
@@ -127,6 +133,6 @@ def norm_linear(x: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: 
             lin.seen_amax = max(lin.seen_amax, float(y.float().abs().max()))
             return lin(nvfp4.quantize(y, lin.input_scale), epilogue=epilogue)
         xq, _ = nvfp4.rmsnorm_quantize(x, norm_weight, eps, lin.input_scale, residual=res, gemma=gemma)
-        return lin(xq, epilogue=epilogue)
+        return lin(xq, epilogue=epilogue, requant=requant)
     y = basic.rmsnorm(x, norm_weight, eps, residual=res, gemma=gemma)
-    return lin(y, epilogue=epilogue)
+    return lin(y, epilogue=epilogue, requant=requant)

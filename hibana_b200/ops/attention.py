@@ -9,12 +9,13 @@ hibana/model/attention.py:69-126, hibana/kernels/csrc/verify_attn.cu.
 from __future__ import annotations
 
 import math
-import os
 from typing import Optional
 
 import torch
 
 from .. import _native as nv
+from .. import config as cfgmod
+from . import nvfp4
 
 P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
 nv.register("hb_attn_paged", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, Fl, I, Fl, I, P])
@@ -22,6 +23,7 @@ nv.register("hb_attn_paged", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I,
 nv.register("hb_attn_merge", [P, P, P, L, I, I, P])
 nv.register("hb_attn_decode", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, L, P, P])
 
+nv.register("hb_attn_decode_fuse", [P, P, P, P, I], void=True)
 nv.register("hb_attn_decode_tc", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, L, P, P])
 nv.register("hb_attn_decode_tc_profile", [P], void=True)
 nv.register("hb_attn_prefill_profile", [P], void=True)
@@ -51,6 +53,8 @@ class AttnWorkspace:
         self.rows, self.splits = rows, splits
         self.part_o = torch.empty(rows, hq, splits, d, dtype=torch.float32, device=device)
         self.part_lse = torch.empty(rows, hq, splits, dtype=torch.float32, device=device)
+        # arrivals per (sequence, kv head) of the fused split merge: zero between launches (the kernel re-arms it)
+        self.counter = torch.zeros(rows * hq, dtype=torch.int32, device=device)
 
 
 def paged_attention_ref(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, kv_indices: torch.Tensor,
@@ -86,12 +90,16 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     ctx_len: torch.Tensor, *, q_indptr: Optional[torch.Tensor] = None, max_rows: int = 1,
                     seq_rows: Optional[torch.Tensor] = None,
                     scale: Optional[float] = None, kv_scale: float = 1.0, causal: bool = True, splits: int = 1,
-                    workspace: Optional[AttnWorkspace] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    workspace: Optional[AttnWorkspace] = None, out: Optional[torch.Tensor] = None,
+                    quant_scale: Optional[torch.Tensor] = None):
     """q [T, Hq, D] bf16; pools [slots, Hkv, D]; kv_indices [B, max_ctx] int32; ctx_len [B] int32.
 
     Row r of sequence b (rows q_indptr[b]..q_indptr[b+1], or exactly one row when q_indptr is None) sees keys
     [0, ctx_len[b] - rows_b + r + 1) when causal. `max_rows` bounds rows per sequence (host value).
     `seq_rows` int32 [B] selects each sequence's row of kv_indices (identity when None).
+    `quant_scale` (fp32 scalar tensor): return the rows [T, Hq * D] as an Nvfp4Tensor quantised with that static
+    scale (the activation operand of the output projection); on the decode kernel this and the split merge happen
+    inside the attention kernel, elsewhere a quantisation pass follows.
     """
     t, hq, d = q.shape
     hkv = k_pool.shape[1]
@@ -101,31 +109,66 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         res = paged_attention_ref(q, k_pool, v_pool, idx, ctx_len, q_indptr, scale, kv_scale, causal)
         if out is not None:
             out.copy_(res)
-            return out
-        return res
+            res = out
+        return res if quant_scale is None else nvfp4.quantize(res.reshape(t, hq * d), quant_scale)
     b = ctx_len.shape[0]
-    out = torch.empty_like(q) if out is None else out
     if splits > 1 and (workspace is None or workspace.rows < t or workspace.splits != splits):
         workspace = AttnWorkspace(t, hq, d, splits, q.device)
     fp8 = k_pool.dtype != torch.bfloat16
+    cfg = cfgmod.current()
     if not fp8 and max_rows * (hq // hkv) <= 16 and d in (64, 128, 256):
         st = nv.device_state(q.device)
-        # HIBANA_DECODE_ATTN=tc selects the persistent tcgen05 kernel (head dim 128; csrc/attn_decode_tc.cu). It
+        tc = d == 128 and cfg.decode_attn == "tc"
+        fuse = cfg.fuse_epilogues and not tc
+        xq = None
+        if fuse:
+            qb = sfb = None
+            if quant_scale is not None:
+                qb, sfb = _quant_bufs(t, hq * d, q.device)
+                xq = nvfp4.Nvfp4Tensor(qb, sfb, quant_scale, t, hq * d)
+            nv.lib().hb_attn_decode_fuse(workspace.counter.data_ptr() if splits > 1 else None, nv.ptr(qb), nv.ptr(sfb),
+                                         nv.ptr(quant_scale), sfb.shape[1] if sfb is not None else 0)
+        if xq is None:
+            out = torch.empty_like(q) if out is None else out
+        # decode_attn = "tc" selects the persistent tcgen05 kernel (head dim 128; csrc/attn_decode_tc.cu). It
         # matches the mma.sync kernel in isolation (123 vs 122 us at 64 x 2304 keys) but not yet inside the 27B
         # decode step (18.8 vs 15.8 ms per step), so the mma.sync kernel stays the default.
-        tc = d == 128 and os.environ.get("HIBANA_DECODE_ATTN", "mma") == "tc"
         args = (q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), k_pool.stride(1),
                 kv_indices.data_ptr(), kv_indices.stride(0), nv.ptr(seq_rows), ctx_len.data_ptr(), nv.ptr(q_indptr),
-                out.data_ptr(), workspace.part_o.data_ptr() if splits > 1 else None,
+                nv.ptr(out), workspace.part_o.data_ptr() if splits > 1 else None,
                 workspace.part_lse.data_ptr() if splits > 1 else None, b, max_rows, hq, hkv, d, splits, scale,
                 int(causal), k_pool.shape[0], st.status.data_ptr())
         fn = nv.lib().hb_attn_decode_tc if tc else nv.lib().hb_attn_decode
         nv.check(fn(*args, nv.stream()), "hb_attn_decode")
-        if splits > 1:
+        if xq is not None:
+            return xq
+        if splits > 1 and not fuse:
             nv.check(nv.lib().hb_attn_merge(workspace.part_o.data_ptr(), workspace.part_lse.data_ptr(),
                                             out.data_ptr(), t * hq, splits, d, nv.stream()), "hb_attn_merge")
-        return out
-    if not fp8 and d in (64, 128, 256) and q_indptr is not None and os.environ.get("HIBANA_PREFILL_ATTN", "tc") == "tc":
+        return out if quant_scale is None else nvfp4.quantize(out.view(t, hq * d), quant_scale)
+    out = torch.empty_like(q) if out is None else out
+    res = _paged_general(q, k_pool, v_pool, kv_indices, ctx_len, q_indptr, max_rows, seq_rows, scale, kv_scale, causal,
+                         splits, workspace, out, cfg, fp8, b, t, hq, hkv, d)
+    return res if quant_scale is None else nvfp4.quantize(res.view(t, hq * d), quant_scale)
+
+
+_QUANT_BUFS: dict = {}
+
+
+def _quant_bufs(rows: int, k: int, device):
+    """Persistent NVFP4 output buffers per shape (stable addresses for captured graphs); padding scales zeroed once."""
+    key = (device, rows, k)
+    bufs = _QUANT_BUFS.get(key)
+    if bufs is None:
+        qb, sfb = nvfp4._alloc(rows, k, device)
+        sfb.zero_()
+        bufs = _QUANT_BUFS[key] = (qb, sfb)
+    return bufs
+
+
+def _paged_general(q, k_pool, v_pool, kv_indices, ctx_len, q_indptr, max_rows, seq_rows, scale, kv_scale, causal,
+                   splits, workspace, out, cfg, fp8, b, t, hq, hkv, d):
+    if not fp8 and d in (64, 128, 256) and q_indptr is not None and cfg.prefill_attn == "tc":
         st = nv.device_state(q.device)
         nv.check(nv.lib().hb_attn_prefill(
             q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.stride(0), k_pool.stride(1), kv_indices.data_ptr(),

@@ -17,12 +17,12 @@ hibana/kernels/fla/wy_fast.py, hibana/kernels/fla/chunk_delta_h.py.
 """
 from __future__ import annotations
 
-import os
 from typing import Optional, Sequence
 
 import torch
 
 from .. import _native as nv
+from .. import config as cfgmod
 
 P, I, L = nv.P, nv.I, nv.L
 nv.register("hb_gdn_chunk_pass", [P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, P])
@@ -130,7 +130,7 @@ def gdn_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tens
     for b, (r0, r1) in enumerate(ranges):
         if r1 <= r0:
             continue
-        fused = (native and os.environ.get("HIBANA_GDN_PHASE1", "cuda") == "cuda" and q.stride(0) == k.stride(0)
+        fused = (native and cfgmod.current().gdn_phase1 == "cuda" and q.stride(0) == k.stride(0)
                  and q.stride(0) % 4 == 0 and v.stride(0) % 4 == 0 and g.is_contiguous() and beta.is_contiguous())
         if fused:
             ph = prepare_native(q[r0:r1], k[r0:r1], v[r0:r1], g[r0:r1], beta[r0:r1], k_heads=k_heads,

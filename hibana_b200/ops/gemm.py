@@ -7,19 +7,22 @@ tactic -> FlashInfer mm_fp4, and FP8 GEMV / cuBLASLt) is hibana/kernels/ops.py:5
 """
 from __future__ import annotations
 
-import os
 from typing import Optional
 
 import torch
 
 from .. import _native as nv
+from .. import config as cfgmod
 from .nvfp4 import Nvfp4Tensor
 
 EPI_STORE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_STORE_F32 = 0, 1, 2, 3
+EPI_SILU_MUL_QUANT = 7   # decode shapes (tokens <= 128): SiLU-mul, then NVFP4 requantisation in the same epilogue
 EPI_RELU2 = 6       # grouped (weights on the 128-row side) GEMMs only: out = relu(x)^2
 NUM_SMS = 148
 
 nv.register("hb_gemm_set_pdl", [nv.I], void=True)
+nv.register("hb_gemm_silu_quant", [nv.I, nv.P, nv.P, nv.P, nv.P, nv.I, nv.I, nv.I, nv.L, nv.L, nv.P, nv.P, nv.P, nv.P,
+                                   nv.I, nv.I, nv.P, nv.I, nv.I, nv.I, nv.P])
 
 
 _PDL_INIT = False
@@ -36,7 +39,6 @@ def set_pdl(on) -> None:
 
 
 
-MAX_SPLITS = int(os.environ.get("HIBANA_MAX_SPLITS", "8"))     # 8 = portable cluster size
 
 
 def _plan(m: int, n: int, k_tiles: int, max_ws_bytes: int) -> tuple[bool, int, int]:
@@ -49,7 +51,7 @@ def _plan(m: int, n: int, k_tiles: int, max_ws_bytes: int) -> tuple[bool, int, i
         if tiles < slots:
             # Fill the resident CTA slots without spilling into a second, mostly empty wave; every split keeps at
             # least two K tiles.
-            splits = max(1, min(slots // tiles, k_tiles // 2, MAX_SPLITS))
+            splits = max(1, min(slots // tiles, k_tiles // 2, cfgmod.current().max_splits))
         return True, bn, splits
     return False, (256 if n >= 256 else 128), 1
 
@@ -58,7 +60,7 @@ def _launch(kind: int, a, b, sfa, sfb, ra: int, rb: int, k: int, lda: int, ldb: 
             residual: Optional[torch.Tensor], alpha: float, alpha_ptr: Optional[torch.Tensor], epilogue: int,
             swap: bool, splits: int, bn: int, ka_a: int, ka_b: int) -> None:
     if not _PDL_INIT:
-        set_pdl(int(os.environ.get("HIBANA_PDL", "1")))
+        set_pdl(cfgmod.current().pdl)
     st = nv.device_state(out.device)
     ws = cnt = None     # split-K reduces through distributed shared memory; no global scratch
     code = nv.lib().hb_gemm(kind, a.data_ptr(), b.data_ptr(), nv.ptr(sfa), nv.ptr(sfb), ra, rb, k, lda, ldb,
@@ -134,3 +136,43 @@ def linear_nvfp4(x: Nvfp4Tensor, w: Nvfp4Tensor, alpha: torch.Tensor, *, epilogu
         _launch(1, x.q, w.q, x.sf, w.sf, m, n, k, k, k, out, residual, 1.0, alpha, epilogue, False, splits, bn, x.ka,
                 w.ka)
     return out
+
+
+_REQUANT_BUFS: dict = {}
+
+
+def requant_ok(m: int, n: int) -> bool:
+    """Shapes the fused SiLU-mul + requant epilogue covers: weights on the 128-row side, whole feature tiles."""
+    return m <= 128 and n % 128 == 0
+
+
+def linear_nvfp4_silu_quant(x: Nvfp4Tensor, w: Nvfp4Tensor, alpha: torch.Tensor, out_scale: torch.Tensor, *,
+                            splits: Optional[int] = None) -> Nvfp4Tensor:
+    """silu(gate) * up of y = x @ w.T (gate / up rows of `w` interleaved pairwise), requantised to NVFP4 with the
+    static scale `out_scale` inside the GEMM epilogue: the result feeds the next NVFP4 projection directly.
+    Bit-identical to `linear_nvfp4(..., epilogue=EPI_SILU_MUL)` followed by `nvfp4.quantize`.
+    Reference: hibana/kernels/mlp_fusion.py:244-245."""
+    from . import nvfp4
+    m, k, n = x.rows, x.k, w.rows
+    if not nv.use_native(x.q, w.q) or not requant_ok(m, n):
+        return nvfp4.quantize(linear_nvfp4(x, w, alpha, epilogue=EPI_SILU_MUL), out_scale)
+    ko = n // 2
+    key = (x.q.device, m, ko)
+    bufs = _REQUANT_BUFS.get(key)
+    if bufs is None:
+        # persistent per shape (stable addresses inside captured graphs); scale bytes of padding rows and padding
+        # groups are zeroed once, the kernel writes the real ones
+        q, sf = nvfp4._alloc(m, ko, x.q.device)
+        sf.zero_()
+        bufs = _REQUANT_BUFS[key] = (q, sf)
+    q, sf = bufs
+    _, bn, auto_splits = _plan(m, n, (k + 255) // 256, nv.WORKSPACE_BYTES)
+    if not _PDL_INIT:
+        set_pdl(cfgmod.current().pdl)
+    st = nv.device_state(q.device)
+    code = nv.lib().hb_gemm_silu_quant(1, w.q.data_ptr(), x.q.data_ptr(), w.sf.data_ptr(), x.sf.data_ptr(), n, m, k,
+                                       k, k, alpha.data_ptr(), q.data_ptr(), sf.data_ptr(), out_scale.data_ptr(),
+                                       sf.shape[1], auto_splits if splits is None else splits,
+                                       st.status.data_ptr(), bn, w.ka, x.ka, nv.stream())
+    nv.check(code, "hb_gemm_silu_quant")
+    return Nvfp4Tensor(q, sf, out_scale, m, ko)

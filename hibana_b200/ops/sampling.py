@@ -80,7 +80,16 @@ def sample_ref(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Ten
             out[r] = int(lg[r].argmax())
             continue
         k = int(top_k[r])
-        k = max_k if k <= 0 or k > max_k else k
+        if k <= 0 or k > max_k:
+            # top-k off or wider than the kernel's candidate list: the full-vocabulary law (softmax, then nucleus),
+            # drawn by inverse CDF in index order
+            from ..engine.rejection import distribution
+            law = distribution(lg[r:r + 1].cpu(), t, 0, float(top_p[r]))[0].double()
+            u = uniform01(int(seeds[r]), int(offsets[r])) * float(law.sum())
+            acc = torch.cumsum(law, 0)
+            hit = (u < acc).nonzero()
+            out[r] = int(hit[0]) if len(hit) else int((law > 0).nonzero()[-1])
+            continue
         vals, idx = torch.sort(lg[r].cpu(), descending=True, stable=True)
         vals, idx = vals[:k], idx[:k]
         w = torch.exp((vals - vals[0]) / t)
@@ -101,7 +110,9 @@ def sample_ref(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Ten
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
            seeds: torch.Tensor, offsets: torch.Tensor, bitmask: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Temperature / top-k (<= 64) / top-p sampling; temperature <= 0 is greedy. seeds/offsets are uint64-as-int64."""
+    """Temperature / top-k / top-p sampling; temperature <= 0 is greedy. seeds/offsets are uint64-as-int64.
+    1 <= top-k <= 64 draws from the k largest logits; top-k <= 0 (off) or > 64 draws from the softmax over the whole
+    vocabulary (then top-p), the same law `engine.rejection.distribution` gives speculative verification."""
     rows, vocab = logits.shape
     if nv.use_native(logits):
         out = torch.empty(rows, dtype=torch.int64, device=logits.device)

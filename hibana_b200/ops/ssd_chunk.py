@@ -12,13 +12,13 @@ path; quantised states keep the token-serial kernel. Reference: hibana/kernels/m
 """
 from __future__ import annotations
 
-import os
 from typing import Optional, Sequence
 
 import torch
 import torch.nn.functional as F
 
 from .. import _native as nv
+from .. import config as cfgmod
 from . import gdn_chunk
 
 CHUNK = gdn_chunk.CHUNK
@@ -87,7 +87,7 @@ def mamba2_chunked(x, bmat, cmat, dt, a_log, dt_bias, dskip, state, slot_in, slo
     for b, (r0, r1) in enumerate(ranges):
         if r1 <= r0:
             continue
-        fused = (native and os.environ.get("HIBANA_SSD_PHASE1", "cuda") == "cuda" and dt.dtype == torch.bfloat16
+        fused = (native and cfgmod.current().ssd_phase1 == "cuda" and dt.dtype == torch.bfloat16
                  and bmat.stride(0) == cmat.stride(0) and bmat.stride(0) % 4 == 0 and x.stride(0) % 2 == 0
                  and a_log.dtype == torch.float32 and (dt_bias is None or dt_bias.dtype == torch.float32))
         if fused:

@@ -46,8 +46,7 @@ class _RawCuda:
                                          "strides": None}
 
 
-class CommTimeout(RuntimeError):
-    pass
+CommTimeout = nv.DeviceWaitTimeout     # raised by check_status and by the engine's per-step status read
 
 
 class Communicator:
@@ -116,10 +115,31 @@ class Communicator:
     def slot_offset(self, slot: int) -> int:
         return self.ctrl_bytes + slot * self.slot_bytes
 
+    def begin_forward(self, n_collectives: int) -> None:
+        """Fixes the slot phase of a forward (or of the graph being captured): its collectives take slots
+        0, 1, ... cyclically, and the cycle length is chosen so that the LAST collective of the forward never
+        lands on the slot of the FIRST one. A slot's partial buffer (and its low-latency landing area) may be
+        overwritten as soon as the owner has finished the collective, while a slow peer can still be reading it;
+        what protects the peer is that every rank takes part in some other collective before the slot comes round
+        again. Inside a forward that holds because consecutive collectives use different slots; across two
+        forwards (replays of captured graphs in any order, slot ids baked in) it holds because every forward starts
+        on slot 0 and never ends there. The last slot is reserved for `barrier`."""
+        usable = self.nslot - 1
+        self._cycle = next((c for c in (usable, usable - 1, usable - 2)
+                            if n_collectives < 2 or (n_collectives - 1) % c != 0), usable)
+        self._next_slot = 0
+        self._single = n_collectives < 2
+
     def next_slot(self) -> int:
-        """Round-robin slot for the next collective call site (the same order on every rank)."""
+        """Slot of the next collective call site (the same order on every rank); see `begin_forward`."""
         s = self._next_slot
-        self._next_slot = (s + 1) % self.nslot
+        cycle = getattr(self, "_cycle", self.nslot - 1)
+        nxt = (s + 1) % cycle
+        assert cycle < 2 or nxt != s
+        if getattr(self, "_single", False):
+            # a forward with one collective would reuse slot 0 back to back: a barrier separates the two uses
+            self.barrier()
+        self._next_slot = nxt
         return s
 
     def slot_buffer(self, slot: int, rows: int, cols: int, dtype=torch.bfloat16) -> torch.Tensor:
@@ -236,7 +256,8 @@ class Communicator:
         return out
 
     def barrier(self, slot: Optional[int] = None) -> None:
-        slot = self.next_slot() if slot is None else slot
+        """Flag barrier on the reserved last slot (sequence-numbered, >= comparison: safe back to back)."""
+        slot = self.nslot - 1 if slot is None else slot
         nv.check(nv.lib().hb_barrier(self._bases, self.world, self.rank, slot, self.timeout_ns,
                                      self.status.data_ptr(), nv.stream()), "hb_barrier")
 
@@ -244,7 +265,7 @@ class Communicator:
         """Host check at a publish point: raises CommTimeout when a bounded device wait gave up."""
         code = nv.read_status(self.device)
         if code:
-            raise CommTimeout(f"device-side wait ran out (status {code})")
+            raise CommTimeout(code)
 
     # ---- host scalars (control plane)
     def min_int(self, v: int) -> int:

@@ -14,6 +14,7 @@ import os
 
 import torch
 
+from .. import config as cfgmod
 from ..ops import attention
 from .timing import measured_peaks, time_cuda
 
@@ -97,7 +98,7 @@ def main() -> None:
         res["frac_of_bf16_peak"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 3)
     else:
         res["frac_of_hbm"] = round(kv_bytes / ms / 1e6 / peaks["hbm_gbs"], 3)
-    if args.roles and args.mode == "decode" and d == 128 and os.environ.get("HIBANA_DECODE_ATTN", "mma") == "tc":
+    if args.roles and args.mode == "decode" and d == 128 and cfgmod.current().decode_attn == "tc":
         prof = attention.DecodeTcProfile(dev)
         fn()
         res["tc_cycles_per_tile"] = prof.read()

@@ -1,8 +1,10 @@
 """Save / load of the dense decoder as sharded safetensors files in the ModelOpt layout, with tensor-parallel
 shards cut at load time (q/k/v by head, gate/up by column, o_proj/down by input feature) so that every rank reads
-only the bytes it keeps. Names follow the Hugging Face convention of the family
-(`model.layers.<i>.self_attn.qkv_proj`, `.o_proj`, `mlp.gate_up_proj`, `mlp.down_proj`, `input_layernorm`,
-`post_attention_layernorm`, `model.embed_tokens`, `model.norm`, `lm_head`). An index file lists tensor -> file.
+only the bytes it keeps. Two layouts load: the Hugging Face / ModelOpt one with separate projections
+(`model.layers.<i>.self_attn.{q,k,v,o}_proj`, `mlp.{gate,up,down}_proj`; q/k/v are concatenated and gate/up
+interleaved pairwise at load, nothing is requantised) and this engine's pre-fused one (`self_attn.qkv_proj`,
+`mlp.gate_up_proj`, rows already in kernel order). Both carry `input_layernorm`, `post_attention_layernorm`,
+`model.embed_tokens`, `model.norm`, `lm_head`. An index file lists tensor -> file.
 Reference: hibana/weights/safetensors.py:1-61 (SnapshotWeights), hibana/weights/sharding.py:1-88.
 """
 from __future__ import annotations
@@ -28,9 +30,29 @@ def _lin_tensors(lin: Linear, name: str) -> dict:
     return {f"{name}.weight": lin.weight.cpu().contiguous()}
 
 
-def save_dense(model: DenseModel, directory: str, layers_per_file: int = 8) -> None:
-    """Writes an UNSHARDED model (tp = 1)."""
+def _split_rows(lin: Linear, name_rows: list, deinterleave: bool = False) -> dict:
+    """Tensors of the separate projections a fused Linear was built from: [(name, row selector)], or the even / odd
+    rows when `deinterleave`."""
+    out = {}
+    if lin.fmt == "nvfp4":
+        base = modelopt.nvfp4_tensors(lin, "x")
+        for name, sel in name_rows:
+            out[f"{name}.weight"] = base["x.weight"][sel].contiguous()
+            out[f"{name}.weight_scale"] = base["x.weight_scale"].view(torch.uint8)[sel].contiguous().view(torch.float8_e4m3fn)
+            out[f"{name}.weight_scale_2"] = base["x.weight_scale_2"].clone()
+            out[f"{name}.input_scale"] = base["x.input_scale"].clone()
+    else:
+        for name, sel in name_rows:
+            out[f"{name}.weight"] = lin.weight.cpu()[sel].contiguous()
+    return out
+
+
+def save_dense(model: DenseModel, directory: str, layers_per_file: int = 8, hf_layout: bool = False) -> None:
+    """Writes an UNSHARDED model (tp = 1). `hf_layout` writes separate q/k/v and gate/up projections, the layout
+    of published checkpoints; the default keeps the fused kernel-order matrices."""
     assert model.target.tp_size == 1
+    t = model.target
+    nq, nkv = t.q_heads * t.head_dim, t.kv_heads * t.head_dim
     d = Path(directory)
     d.mkdir(parents=True, exist_ok=True)
     index, files = {}, []
@@ -39,9 +61,16 @@ def save_dense(model: DenseModel, directory: str, layers_per_file: int = 8) -> N
         tensors = {}
         for layer in group:
             p = f"model.layers.{layer.idx}"
-            tensors.update(_lin_tensors(layer.qkv, f"{p}.self_attn.qkv_proj"))
+            if hf_layout:
+                tensors.update(_split_rows(layer.qkv, [(f"{p}.self_attn.q_proj", slice(0, nq)),
+                                                       (f"{p}.self_attn.k_proj", slice(nq, nq + nkv)),
+                                                       (f"{p}.self_attn.v_proj", slice(nq + nkv, nq + 2 * nkv))]))
+                tensors.update(_split_rows(layer.gate_up, [(f"{p}.mlp.gate_proj", slice(0, None, 2)),
+                                                           (f"{p}.mlp.up_proj", slice(1, None, 2))]))
+            else:
+                tensors.update(_lin_tensors(layer.qkv, f"{p}.self_attn.qkv_proj"))
+                tensors.update(_lin_tensors(layer.gate_up, f"{p}.mlp.gate_up_proj"))
             tensors.update(_lin_tensors(layer.o, f"{p}.self_attn.o_proj"))
-            tensors.update(_lin_tensors(layer.gate_up, f"{p}.mlp.gate_up_proj"))
             tensors.update(_lin_tensors(layer.down, f"{p}.mlp.down_proj"))
             tensors[f"{p}.input_layernorm.weight"] = layer.input_norm.cpu()
             tensors[f"{p}.post_attention_layernorm.weight"] = layer.post_norm.cpu()
@@ -86,6 +115,22 @@ def _load_lin(snap: Snapshot, name: str, device, rows=None, cols=None) -> Linear
     return Linear(w.contiguous(), "bf16", name=name).to(device)
 
 
+def _load_fused(snap: Snapshot, names: list, device, parts=None, interleave: bool = False, name: str = "") -> Linear:
+    """Separate stored projections -> one Linear (see modelopt.load_nvfp4_fused); bf16 sources are concatenated."""
+    if f"{names[0]}.weight_scale" in snap:
+        return modelopt.load_nvfp4_fused(snap, names, device, parts=parts, interleave=interleave, name=name)
+    ws = []
+    for i, n in enumerate(names):
+        w = snap[f"{n}.weight"]
+        ws.append(w if parts is None or parts[i] is None else w[parts[i]])
+    if interleave:
+        from ..models.linear import interleave_pairs
+        w = interleave_pairs(ws[0], ws[1])
+    else:
+        w = torch.cat(ws, 0)
+    return Linear(w.contiguous(), "bf16", name=name).to(device)
+
+
 def load_dense(full: Target, directory: str, device="cpu", tp: int = 1, rank: int = 0) -> DenseModel:
     """Loads (a shard of) the model; shards are bitwise slices of the stored quantised matrices."""
     snap = Snapshot(directory)
@@ -114,9 +159,21 @@ def load_dense(full: Target, directory: str, device="cpu", tp: int = 1, rank: in
             ocols = slice(rank * hq * d, (rank + 1) * hq * d)
             gurows = slice(2 * rank * f, 2 * (rank + 1) * f)
             dcols = slice(rank * f, (rank + 1) * f)
-        layer.qkv = _load_lin(snap, f"{p}.self_attn.qkv_proj", device, rows=sel)
+        if f"{p}.self_attn.qkv_proj.weight" in snap:
+            layer.qkv = _load_lin(snap, f"{p}.self_attn.qkv_proj", device, rows=sel)
+            layer.gate_up = _load_lin(snap, f"{p}.mlp.gate_up_proj", device, rows=gurows)
+        else:
+            # published layout: separate projections, each rank cuts its heads / columns out of every source
+            qp = kp = gp = None
+            if tp > 1:
+                qp = slice(rank * hq * d, (rank + 1) * hq * d)
+                kp = slice(kv0 * d, (kv0 + hkv) * d)
+                gp = slice(rank * f, (rank + 1) * f)
+            layer.qkv = _load_fused(snap, [f"{p}.self_attn.{x}_proj" for x in "qkv"], device, parts=[qp, kp, kp],
+                                    name=f"{p}.self_attn.qkv_proj")
+            layer.gate_up = _load_fused(snap, [f"{p}.mlp.gate_proj", f"{p}.mlp.up_proj"], device, parts=[gp, gp],
+                                        interleave=True, name=f"{p}.mlp.gate_up_proj")
         layer.o = _load_lin(snap, f"{p}.self_attn.o_proj", device, cols=ocols)
-        layer.gate_up = _load_lin(snap, f"{p}.mlp.gate_up_proj", device, rows=gurows)
         layer.down = _load_lin(snap, f"{p}.mlp.down_proj", device, cols=dcols)
         layer.linears = lambda layer=layer: [layer.qkv, layer.o, layer.gate_up, layer.down]
         model.layers.append(layer)

@@ -44,6 +44,45 @@ def load_nvfp4_linear(tensors: Mapping[str, torch.Tensor], name: str, device="cp
     return Linear.from_nvfp4(wq, tensors[f"{name}.input_scale"].to(device), name=name)
 
 
+def load_nvfp4_fused(tensors: Mapping[str, torch.Tensor], names: list, device="cpu", *, parts=None,
+                      interleave: bool = False, cols=None, name: str = "") -> Linear:
+    """One Linear out of several stored projections (q_proj + k_proj + v_proj, or gate_proj + up_proj), the way real
+    ModelOpt / Hugging Face checkpoints ship them: rows are concatenated along N in the order of `names`
+    (`interleave`: rows of the two sources alternate g0, u0, g1, u1 ..., what the SiLU-mul epilogue expects),
+    `parts[i]` (slice or index tensor, may be None) first cuts this rank's rows out of source i. The sources must
+    share one `weight_scale_2` (they were quantised as one matrix); the static activation scale is their largest
+    `input_scale`. Nothing is requantised. Reference: hibana/weights/modelopt.py:108-184 (`load_nvfp4_linear(w, [q, k, v])`)."""
+    qs, sfs, gss, ins = [], [], [], []
+    for i, n in enumerate(names):
+        q = tensors[f"{n}.weight"]
+        sf = tensors[f"{n}.weight_scale"].view(torch.uint8)
+        sel = parts[i] if parts is not None else None
+        if sel is not None:
+            q, sf = q[sel], sf[sel]
+        if cols is not None:
+            c0, c1 = cols.start or 0, cols.stop
+            assert c0 % 16 == 0 and c1 % 16 == 0
+            q, sf = q[:, c0 // 2:c1 // 2], sf[:, c0 // 16:c1 // 16]
+        qs.append(q)
+        sfs.append(sf)
+        gss.append(float(tensors[f"{n}.weight_scale_2"].reshape(-1)[0]))
+        ins.append(tensors[f"{n}.input_scale"].reshape(1).float())
+    if any(abs(g - gss[0]) > 1e-12 * max(abs(gss[0]), 1e-30) for g in gss):
+        raise ValueError(f"projections {names} do not share one weight_scale_2 ({gss}); they cannot be fused "
+                         "without requantising")
+    if interleave:
+        assert len(qs) == 2 and qs[0].shape == qs[1].shape
+        q = torch.stack((qs[0], qs[1]), dim=1).reshape(2 * qs[0].shape[0], qs[0].shape[1])
+        sf = torch.stack((sfs[0], sfs[1]), dim=1).reshape(2 * sfs[0].shape[0], sfs[0].shape[1])
+    else:
+        q, sf = torch.cat(qs, 0), torch.cat(sfs, 0)
+    n_rows, k = q.shape[0], q.shape[1] * 2
+    gs = torch.tensor([gss[0]], dtype=torch.float32)
+    wq = nvfp4.Nvfp4Tensor(q.contiguous().to(device), nvfp4.swizzle_sf(sf.contiguous()).to(device), gs.to(device),
+                           n_rows, k)
+    return Linear.from_nvfp4(wq, torch.stack(ins).max().reshape(1).to(device), name=name or names[0])
+
+
 def fp8_tensors(w: Fp8Weight, input_scale: torch.Tensor, name: str) -> dict:
     return {f"{name}.weight": w.q.cpu(), f"{name}.weight_scale": w.scale.reshape(()).cpu(),
             f"{name}.input_scale": input_scale.reshape(()).float().cpu()}

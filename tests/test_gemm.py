@@ -191,3 +191,34 @@ def test_w3_dequant_fused_gemm(m, n, k):
     assert float((got - (ref + res.float())).abs().max() / ref.abs().max()) < 2e-2
     from hibana_b200 import _native as nv
     assert nv.read_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (7, 1024, 5120), (64, 4352, 5120), (64, 34816, 1024), (100, 512, 768)])
+def test_silu_mul_requant_epilogue_matches_two_kernels(m, n, k):
+    """gate/up GEMM with the SiLU-mul + NVFP4 requant epilogue == the SiLU-mul GEMM followed by the quantiser,
+    byte for byte (packed values and every scale byte of real rows), for unsplit and cluster split-K launches;
+    and the dequantised result is close to the fp32 reference of the same op."""
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(m * 7 + n)
+    w = torch.randn(n, k, device=dev, generator=g) * 0.05
+    x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+    wq = nvfp4.quantize_weight(w)
+    gs = torch.tensor(6.0 / (6 * 448), device=dev)
+    xq = nvfp4.quantize(x, gs)
+    alpha = (gs * wq.gscale).reshape(1)
+    acc = xq.dequantize() @ wq.dequantize().t()
+    ref = torch.nn.functional.silu(acc[:, 0::2]) * acc[:, 1::2]
+    out_scale = (ref.abs().max() / (6 * 448)).reshape(()).float()      # no clipping: the error is rounding only
+    two = nvfp4.quantize(gemm.linear_nvfp4(xq, wq, alpha, epilogue=gemm.EPI_SILU_MUL), out_scale)
+    one = gemm.linear_nvfp4_silu_quant(xq, wq, alpha, out_scale)
+    torch.cuda.synchronize()
+    assert nv.read_status() == 0
+    assert torch.equal(one.q, two.q)
+    groups = n // 2 // 16
+    assert torch.equal(nvfp4.unswizzle_sf(one.sf, m, groups), nvfp4.unswizzle_sf(two.sf, m, groups))
+    err = (one.dequantize() - ref).norm() / ref.norm().clamp_min(1e-6)
+    assert err < 0.15, err
+    # a second call reuses the persistent buffers and must give the same bytes (captured graphs replay it)
+    again = gemm.linear_nvfp4_silu_quant(xq, wq, alpha, out_scale)
+    assert torch.equal(again.q, two.q)

@@ -219,14 +219,15 @@ def test_tensor_core_decode_verify_rows(hq, hkv, d, rows, splits, contiguous):
 @pytest.mark.parametrize("hq,hkv,rows", [(40, 8, [3, 1, 2, 3]), (16, 2, [2, 1, 1, 2]), (8, 8, [1, 1, 1, 1])])
 @pytest.mark.parametrize("splits", [1, 2, 5])
 @pytest.mark.parametrize("contiguous", [False, True, "slot-major"])
-def test_tcgen05_decode_kernel(hq, hkv, rows, splits, contiguous, monkeypatch):
+def test_tcgen05_decode_kernel(hq, hkv, rows, splits, contiguous):
     """The persistent tcgen05 decode kernel (opt-in): ragged contexts, empty splits, multi-row verify, all layouts."""
-    monkeypatch.setenv("HIBANA_DECODE_ATTN", "tc")
+    from hibana_b200 import config as cfgmod
     ctxs = [40, 700, 129, 2500]
     q, kp, vp, idx, ctx, indptr, sr = _attn_case(4, rows, ctxs, hq, hkv, 128, seed=7, contiguous=contiguous)
     ref = attention.paged_attention(q, kp, vp, idx, ctx, q_indptr=indptr, max_rows=max(rows), seq_rows=sr)
-    got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(), q_indptr=indptr.cuda(),
-                                    max_rows=max(rows), seq_rows=sr.cuda(), splits=splits)
+    with cfgmod.using(decode_attn="tc"):
+        got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(),
+                                        q_indptr=indptr.cuda(), max_rows=max(rows), seq_rows=sr.cuda(), splits=splits)
     _close(got, ref, 2e-2)
     from hibana_b200 import _native as nv
     assert nv.read_status() == 0
@@ -251,3 +252,77 @@ def test_tcgen05_prefill_attention(hq, hkv, d, contiguous):
     got = attention.paged_attention(q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda(), q_indptr=indptr.cuda(),
                                     max_rows=max(rows), seq_rows=sr.cuda(), causal=False)
     _close(got, ref, 2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("hq,hkv,d,rows", [(40, 8, 128, [1, 1, 1, 1]), (40, 8, 128, [3, 1, 2, 3]), (4, 2, 64, [2, 1, 1, 2])])
+@pytest.mark.parametrize("splits", [1, 2, 5])
+def test_decode_attention_fused_merge_and_quant(hq, hkv, d, rows, splits):
+    """In-kernel split merge (last-arriving CTA) and NVFP4 output of the decode kernel: the merged rows match the
+    separate merge kernel's, the NVFP4 rows equal quantising the kernel's bf16 rows afterwards byte for byte, twice in a row
+    (the arrival counters re-arm themselves), and both stay close to the fp32 reference."""
+    from hibana_b200 import _native as nv
+    from hibana_b200 import config as cfgmod
+    from hibana_b200.ops import nvfp4
+    ctxs = [40, 700, 129, 2500]
+    q, kp, vp, idx, ctx, indptr, sr = _attn_case(4, rows, ctxs, hq, hkv, d, seed=11, contiguous=True)
+    ref = attention.paged_attention(q, kp, vp, idx, ctx, q_indptr=indptr, max_rows=max(rows), seq_rows=sr)
+    args = (q.cuda(), kp.cuda(), vp.cuda(), idx.cuda(), ctx.cuda())
+    kw = dict(q_indptr=indptr.cuda(), max_rows=max(rows), seq_rows=sr.cuda(), splits=splits)
+    with cfgmod.using(fuse_epilogues=False):
+        plain = attention.paged_attention(*args, **kw)
+    gs = torch.tensor(2.0 / (6 * 448), device="cuda")
+    ws = attention.AttnWorkspace(q.shape[0], hq, d, splits, torch.device("cuda")) if splits > 1 else None
+    for _ in range(2):
+        fused = attention.paged_attention(*args, workspace=ws, **kw)
+        _close(fused, plain, 8e-3)          # same sums, possibly contracted differently
+        want = nvfp4.quantize(fused.view(fused.shape[0], -1), gs)
+        xq = attention.paged_attention(*args, workspace=ws, quant_scale=gs, **kw)
+        assert torch.equal(xq.q, want.q)
+        groups = hq * d // 16
+        assert torch.equal(nvfp4.unswizzle_sf(xq.sf, xq.rows, groups), nvfp4.unswizzle_sf(want.sf, want.rows, groups))
+    _close(plain, ref, 2e-2)
+    assert nv.read_status() == 0
+
+
+def test_sampling_full_vocab_law_cpu():
+    """top_k = 0 samples the whole vocabulary: the empirical law matches `distribution`, also under top-p."""
+    from hibana_b200.engine.rejection import distribution
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5] + [-3.0] * 95]).repeat(3000, 1)
+    n = 3000
+    for p in (1.0, 0.8):
+        out = sampling.sample(logits, torch.ones(n), torch.zeros(n, dtype=torch.int32), torch.full((n,), p),
+                              torch.full((n,), 11, dtype=torch.int64), torch.arange(n, dtype=torch.int64))
+        freq = torch.bincount(out, minlength=100).float() / n
+        law = distribution(logits[:1], 1.0, 0, p)[0]
+        assert (freq - law).abs().max() < 0.03
+        assert freq[law == 0].sum() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("top_p", [1.0, 0.9, 0.3])
+def test_sampling_full_vocab_kernel_matches_distribution(top_p):
+    """Kernel path for top_k = 0 / > 64: every draw lands inside the law's support, the reported probability of
+    the drawn token equals the law's, the empirical frequencies follow it, and ties at the nucleus edge are cut in
+    index order."""
+    from hibana_b200.engine.rejection import distribution
+    g = torch.Generator().manual_seed(3)
+    vocab, n = 3000, 4096
+    row = torch.randn(vocab, generator=g) * 2.0
+    row[100:110] = row[5]                  # ties
+    logits = row[None, :].repeat(n, 1).cuda()
+    temp = torch.full((n,), 0.8, device="cuda")
+    top_k = torch.zeros(n, dtype=torch.int32, device="cuda")
+    top_k[::2] = 100                        # > 64 takes the same path
+    tp = torch.full((n,), top_p, device="cuda")
+    seeds = torch.full((n,), 77, dtype=torch.int64, device="cuda")
+    offs = torch.arange(n, dtype=torch.int64, device="cuda")
+    out = sampling.sample(logits, temp, top_k, tp, seeds, offs)
+    law = distribution(row[None, :], 0.8, 0, top_p)[0]
+    picks = out.cpu()
+    assert (law[picks] > 0).all()
+    freq = torch.bincount(picks, minlength=vocab).float() / n
+    assert (freq - law).abs().max() < 0.03
+    # the CPU statement of the same rule makes the same draws, up to rounding at CDF edges
+    ref = sampling.sample(logits.cpu(), temp.cpu(), top_k.cpu(), tp.cpu(), seeds.cpu(), offs.cpu())
+    assert (ref == picks).float().mean() > 0.99

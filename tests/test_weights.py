@@ -31,6 +31,36 @@ def test_dense_checkpoint_roundtrip_and_tp_shards(tmp_path):
         assert torch.equal(x.wq.q, y.wq.q) and torch.equal(x.wq.sf, y.wq.sf)
 
 
+def test_hf_layout_checkpoint_with_separate_projections(tmp_path):
+    """A checkpoint in the published layout (separate q/k/v and gate/up projections, row-major scales): loading
+    fuses and interleaves them into the kernel-order matrices bit for bit, for the whole model and for a
+    tensor-parallel shard, and mismatched per-tensor scales are refused."""
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+    t = scaled(dense_tiny(), weight_format="nvfp4")
+    model = DenseModel(t, "cpu", seed=0)
+    for i, lin in enumerate(model.linears()):
+        lin.set_input_amax(3.0 + i)
+    checkpoint.save_dense(model, str(tmp_path), layers_per_file=1, hf_layout=True)
+    snap = checkpoint.Snapshot(str(tmp_path))
+    assert "model.layers.0.self_attn.q_proj.weight" in snap and "model.layers.0.self_attn.qkv_proj.weight" not in snap
+    loaded = checkpoint.load_dense(t, str(tmp_path))
+    for a, b in zip(model.linears(), loaded.linears()):
+        assert torch.equal(a.wq.q, b.wq.q) and torch.equal(a.wq.sf, b.wq.sf) and torch.equal(a.alpha, b.alpha)
+    ref = DenseModel.sharded(t, 2, 1, "cpu", seed=0)
+    shard = checkpoint.load_dense(t, str(tmp_path), tp=2, rank=1)
+    for x, y in zip(ref.linears(), shard.linears()):
+        assert torch.equal(x.wq.q, y.wq.q) and torch.equal(x.wq.sf, y.wq.sf)
+    # k_proj quantised with another per-tensor scale: fusing would need a requantisation, so the load refuses
+    f = tmp_path / snap.map["model.layers.0.self_attn.k_proj.weight_scale_2"]
+    with safe_open(str(f), framework="pt") as h:
+        tensors = {k: h.get_tensor(k) for k in h.keys()}
+    tensors["model.layers.0.self_attn.k_proj.weight_scale_2"] = tensors["model.layers.0.self_attn.k_proj.weight_scale_2"] * 2
+    save_file(tensors, str(f))
+    with pytest.raises(ValueError):
+        checkpoint.load_dense(t, str(tmp_path))
+
+
 def test_unpack_fp4():
     q = torch.tensor([[0x21, 0xF7]], dtype=torch.uint8)
     assert modelopt.unpack_fp4(q).tolist() == [[0.5, 1.0, 6.0, -6.0]]
