@@ -23,7 +23,10 @@ import time
 REF_UNAVAILABLE = ("reference installs offline only with --no-deps and cannot run here: it serves pinned "
                    "HF checkpoints (no network), refuses non-GB10 hosts, needs torch>=2.13 + flashinfer 0.6.17 + "
                    "b12x (absent) and JIT-builds sm_121a-only kernels")
-BASELINE_TOK_S = 165.0   # reference 27B, 4 requests, aggregate tok/s on 1x GB10 (docs/operations.md:220)
+# The reference publishes no number for this configuration (BASELINE.json "published" is empty); its closest figure
+# is a different model on different hardware and is reported as context only, never as a ratio.
+GB10_CONTEXT = {"tok_s": 165.0, "what": "reference hybrid 27B, 4 speculative requests, aggregate, 1x GB10",
+                "source": "docs/operations.md:220"}
 
 
 def _clock_sampler():
@@ -72,6 +75,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the result invalid)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the batch-8, NCCL-only and token-hash extras")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
@@ -108,7 +112,7 @@ def main() -> None:
     batch, prompt_len = args.batch, args.prompt
     max_ctx = prompt_len + warmup + steps + 80
     ex = Executor(model, max_batch=batch, max_ctx=max_ctx, kv_slots=batch * max_ctx + 4096, use_graphs=True,
-                  buckets=(1, batch), comm=comm)
+                  buckets=tuple(sorted({1, min(8, batch), batch})), comm=comm)
 
     g = torch.Generator().manual_seed(1234)
     prompts = [torch.randint(0, t.vocab, (prompt_len,), generator=g).tolist() for _ in range(batch)]
@@ -179,8 +183,10 @@ def main() -> None:
         e2e_ms = max_over_ranks(max(e0.elapsed_time(e1) / steps, wall_ms))
         h2d = (ex.runner.h2d_bytes - h2d0) / steps
         d2h = (ex.runner.d2h_bytes - d2h0) / steps
-        # device-timed: K replays of the captured step (inputs left on the device from the last step)
+        # device-timed: K replays of the captured step (inputs left on the device from the last step); with tensor
+        # parallelism that is the greedy step (per-rank argmax + pair exchange), the one decode_step replays here
         buf = ex.runner.bufs[ex.runner._bucket(nreq)]
+        graph = buf.graph_greedy if getattr(buf, "graph_greedy", None) is not None else buf.graph
         sync_all()
         proc = _clock_sampler() if rank == 0 else None
         time.sleep(0.3)
@@ -188,7 +194,7 @@ def main() -> None:
         sync_all()
         e0.record()
         for _ in range(steps):
-            buf.graph.replay()
+            graph.replay()
         e1.record()
         sync_all()
         dev_ms = max_over_ranks(e0.elapsed_time(e1) / steps)
@@ -202,6 +208,29 @@ def main() -> None:
     devb, e2eb, h2d, d2h, clocks = run_decode(batch)
     status = nv.read_status(dev)
     launches_per_step = getattr(ex.runner, "graph_launches", {}).get(batch, 0)
+    extras = {}
+    if not args.no_extras:
+        import hashlib
+        dev8, e2e8, _, _, _ = run_decode(min(8, batch))
+        extras["decode_tok_s_per_user_b8"] = round(1e3 / dev8, 1)
+        # greedy tokens of a short fixed prompt: the same request on every GPU count (tensor-parallel sums round
+        # differently, so later tokens may legitimately differ between N; the head and the hash make that visible)
+        out = ex.generate_batch([prompts[0][:64]], SamplingParams(max_tokens=16, ignore_eos=True))[0].output_ids
+        extras["tokens_head"] = out[:8]
+        extras["token_hash"] = hashlib.sha1(",".join(map(str, out)).encode()).hexdigest()[:12]
+        if comm is not None:
+            # same model, same engine, collectives through NCCL only (the unfused baseline on this box)
+            comm.fused = False
+            for b_ in ex.runner.bufs.values():
+                b_.graph = None
+                b_.graph_greedy = None
+            split = ex.runner._split_head
+            ex.runner._split_head = lambda: False
+            ex.capture_graphs()
+            devn, _, _, _, _ = run_decode(batch)
+            extras["nccl_only"] = {"value": round(batch / devn * 1e3, 1), "unit": "tok/s", "ms_per_step": round(devn, 4)}
+            ex.runner._split_head = split
+            comm.fused = True
 
     if rank == 0:
         value = batch / devb * 1e3
@@ -209,7 +238,7 @@ def main() -> None:
             "metric": "aggregate decode tok/s (27B-class dense NVFP4, batch 64, 2048 in); also tok/s/user and p50 TTFT",
             "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": round(devb, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / BASELINE_TOK_S, 2), "dtype": "nvfp4 weights, bf16 activations/KV",
+            "vs_baseline": None, "gb10_context": GB10_CONTEXT, "dtype": "nvfp4 weights, bf16 activations/KV",
             "data": "synthetic (uniform-random token ids, random-init N(0,0.02) weights quantised to NVFP4)",
             "config": {"model": t.name, "layers": len(t.layers), "global_batch": batch, "seq_len": prompt_len,
                        "parallelism": f"tp{tp}", "context_during_timed_steps": f"{prompt_len}+",
@@ -221,7 +250,9 @@ def main() -> None:
                     "d2h_bytes_per_step": int(d2h), "tok_s_per_user_b1": round(1e3 / e2e1, 1)},
             "gpu_launches": int(launches_per_step * steps), "launches_per_step": int(launches_per_step),
             "clocks": clocks, "device_status": status, "native_calls_total": nv.CALLS - calls0,
+            "kv_bytes_per_token": int(ex.kv.bytes_per_token) * world,
         }
+        res.update(extras)
         print(json.dumps(res))
     if world > 1:
         dist.barrier()

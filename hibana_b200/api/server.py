@@ -375,11 +375,7 @@ def serve(cfg=None, *, host: Optional[str] = None, port: Optional[int] = None) -
     from ..tokenizer import load_tokenizer
 
     cfg = cfg or cfgmod.current()
-    llm = LLM(cfg)
-    if cfg.spec == "mtp" and getattr(llm.model, "mtp", None) is not None:
-        llm.executor.enable_spec(cfg.spec_depth)
-    elif cfg.spec in ("dflash2", "ngram"):       # drafts from a pluggable proposer (proposers/factory.py)
-        llm.executor.enable_spec(cfg.spec_depth, proposer=cfg.spec)
+    llm = LLM(cfg, warmup=True)      # checkpoint, memory plan, SSD tier, speculation, graphs: all from the settings
     ckpt = cfg.weights if cfg.weights != "random" else None
     tok = load_tokenizer(ckpt, llm.target.vocab)
     engine = EngineLoop(llm.scheduler).start()
@@ -396,3 +392,4 @@ def serve(cfg=None, *, host: Optional[str] = None, port: Optional[int] = None) -
     signal.signal(signal.SIGTERM, _term)
     server.run()
     engine.stop()
+    llm.shutdown()                   # cached prefixes go to the SSD tier before the process leaves

@@ -79,41 +79,61 @@ class StateManager:
         req.committed_len = req.cached_len
         self.live[req.rid] = req
 
-    def restore_from_ssd(self, tokens: Sequence[int], tier) -> int:
+    def begin_ssd_restore(self, tokens: Sequence[int], tier):
         """Before admission: when the SSD tier holds at least `tier.min_gain` more tokens of this prompt than the
-        GPU cache, allocates slots, scatters the blocks into them and publishes them in the tree, so that the
-        admission that follows simply hits. KV-only models (a recurrent model also needs the state snapshot of
-        the tail object; without one the restored KV could not be resumed from). Returns tokens restored."""
+        GPU cache, allocates slots and starts reading the blocks into them (`SsdTier.restore_async`). Returns the
+        job, or None when a restore is not worth it. KV-only models (a recurrent model also needs the state
+        snapshot of the tail object; without one the restored KV could not be resumed from)."""
         if self.cache is None or self.states is not None or tier is None:
-            return 0
+            return None
         tokens = list(tokens[:max(len(tokens) - 1, 0)])
         m = self.cache.match(tokens, split=False)
         have = m.length
         n = tier.worth(tokens, have)
         if not n:
-            return 0
+            return None
         m = self.cache.match(tokens[:have])            # split so that a node ends exactly at `have`
         lock = self.cache.lock(m.node)                  # the allocation below must not evict the matched path
         try:
-            try:
-                fresh = self._alloc_kv(n - have)
-            except MemoryError:
-                return 0
-            from .ssd_store import BLOCK_TOKENS
-            start = have // BLOCK_TOKENS * BLOCK_TOKENS
-            ids = [0] * (have - start) + fresh          # rows the tree already has land in the dummy slot
-            good = max(tier.restore(tokens, start, n, ids), have)
+            fresh = self._alloc_kv(n - have)
+        except MemoryError:
+            self.cache.unlock(lock)
+            return None
+        from .ssd_store import BLOCK_TOKENS
+        start = have // BLOCK_TOKENS * BLOCK_TOKENS
+        ids = [0] * (have - start) + fresh              # rows the tree already has land in the dummy slot
+        job = tier.restore_async(tokens, start, n, ids)
+        job.context = {"lock": lock, "fresh": fresh, "have": have, "node": m.node, "tokens": tokens, "n": n}
+        return job
+
+    def finish_ssd_restore(self, job, tier) -> int:
+        """After the job finished: publishes the restored rows in the tree (the admission that follows simply
+        hits), frees what did not come back, drops the path lock. Returns tokens restored."""
+        c = job.context
+        have, fresh, n = c["have"], c["fresh"], c["n"]
+        try:
+            good = max(tier.finish(job), have)
             if good < n:
                 self.kv.free(fresh[good - have:])
                 fresh = fresh[:good - have]
             if fresh:
-                path = m.node.path_slots()[:have]
-                _node, adopted = self.cache.insert(tokens[:good], path + fresh, start=have)
+                path = c["node"].path_slots()[:have]
+                _node, adopted = self.cache.insert(c["tokens"][:good], path + fresh, start=have)
                 if adopted < good:                      # someone cached the same tokens meanwhile
                     self.kv.free(fresh[adopted - have:])
             return max(good - have, 0)
         finally:
-            self.cache.unlock(lock)
+            self.cache.unlock(c["lock"])
+
+    def restore_from_ssd(self, tokens: Sequence[int], tier) -> int:
+        """Blocking form (offline tools, tests): begin, drive the job to the end, finish. Returns tokens restored."""
+        import time
+        job = self.begin_ssd_restore(tokens, tier)
+        if job is None:
+            return 0
+        while not tier.pump(job):
+            time.sleep(0.0005)
+        return self.finish_ssd_restore(job, tier)
 
     def _alloc_state(self) -> int:
         if self.states.free_count == 0 and self.cache is not None:

@@ -15,6 +15,7 @@ Reference: hibana/cache/ssd.py:96-101,131-246,413-643,764-871,946-1250, docs/cac
 """
 from __future__ import annotations
 
+from concurrent.futures import Future, ThreadPoolExecutor
 from typing import Callable, Optional, Sequence
 
 import torch
@@ -40,9 +41,29 @@ class Staging:
         self.free.append(i)
 
 
+class RestoreJob:
+    """One prefix coming back from disk: blocks [start, end) of `tokens` into `slots`. Reader threads fill staging
+    buffers ahead of the engine thread, which scatters finished blocks in order (`SsdTier.pump`) without ever
+    waiting for a read or for the GPU."""
+
+    def __init__(self, tokens: Sequence[int], start: int, end: int, slots: Sequence[int], keys: list):
+        self.tokens, self.start, self.end, self.slots, self.keys = tokens, start, end, list(slots), keys
+        self.first, self.last = start // BLOCK_TOKENS, end // BLOCK_TOKENS
+        self.next_read = self.next_scatter = self.first
+        self.reads: dict[int, tuple[int, Future]] = {}      # block -> (staging buffer, pending read)
+        self.good = start                                   # first position not yet scattered
+        self.failed = False
+        self.context: dict = {}                             # owner's bookkeeping (locks, fresh slots)
+
+    @property
+    def finished(self) -> bool:
+        return self.failed or self.next_scatter >= self.last
+
+
 class SsdTier:
     def __init__(self, store: SsdStore, kv_pool, *, min_prefix: int = MIN_PREFIX, min_gain: int = MIN_GAIN,
-                 staging_blocks: int = 32, agree: Optional[Callable[[int], int]] = None):
+                 staging_blocks: int = 32, agree: Optional[Callable[[int], int]] = None, readers: int = 4,
+                 read_ahead: int = 8):
         self.store, self.kv = store, kv_pool
         self.min_prefix, self.min_gain = min_prefix, min_gain
         self.agree = agree or (lambda n: n)
@@ -50,6 +71,10 @@ class SsdTier:
         pin = kv_pool.device.type == "cuda"
         self.staging = Staging(staging_blocks, BLOCK_TOKENS * self.token_bytes, pin)
         self.backed_up = self.restored_tokens = self.skipped = 0
+        self.readers = ThreadPoolExecutor(max_workers=readers, thread_name_prefix="hibana-ssd-read")
+        self.read_ahead = read_ahead
+        self._scattered: list = []       # (CUDA event or None, staging buffer) of scatters still in flight
+        self.trace = None                # optional callable(event: str, **fields) (engine/traces.py)
 
     # ---- keys
     def _block_keys(self, tokens: Sequence[int], nblocks: int) -> list[bytes]:
@@ -81,9 +106,12 @@ class SsdTier:
             ids = torch.tensor(slots[b * BLOCK_TOKENS:(b + 1) * BLOCK_TOKENS], dtype=torch.int32, device=dev)
             buf = self.staging.bufs[i]
             self.kv.copy_payload(ids, buf, to_pool=False)
-            if dev.type == "cuda":
-                torch.cuda.current_stream(dev).synchronize()
-            self.store.write_async(key, KIND_KV, BLOCK_TOKENS, memoryview(buf.numpy()), b"", token=i)
+            ready = None
+            if dev.type == "cuda":      # the writer thread waits for the gather; the engine thread moves on, and
+                ev = torch.cuda.Event()  # the slots may be freed at once (later kernels queue behind the gather)
+                ev.record(torch.cuda.current_stream(dev))
+                ready = ev.synchronize
+            self.store.write_async(key, KIND_KV, BLOCK_TOKENS, memoryview(buf.numpy()), b"", token=i, ready=ready)
             queued += 1
         else:
             # tail: the partial last block + the snapshot of the recurrent state at the end of the prefix
@@ -103,12 +131,85 @@ class SsdTier:
         return queued
 
     def step(self) -> int:
-        """Engine-thread poll: returns staging buffers of finished writes. Returns the number completed."""
+        """Engine-thread poll: returns staging buffers of finished writes and of scatters the GPU has completed.
+        Returns the number of writes completed."""
         done = self.store.completions()
         for _key, _ok, token in done:
             if token is not None:
                 self.staging.give(token)
+        keep = []
+        for ev, i in self._scattered:
+            if ev is None or ev.query():
+                self.staging.give(i)
+            else:
+                keep.append((ev, i))
+        self._scattered = keep
         return len(done)
+
+    # ---- asynchronous restore
+    def restore_async(self, tokens: Sequence[int], start: int, end: int, slots: Sequence[int]) -> RestoreJob:
+        """Starts bringing blocks [start, end) (block aligned) back into `slots`; drive it with `pump`."""
+        assert start % BLOCK_TOKENS == 0 and end % BLOCK_TOKENS == 0 and len(slots) == end - start
+        job = RestoreJob(tokens, start, end, slots, self._block_keys(tokens, end // BLOCK_TOKENS))
+        self.pump(job)
+        return job
+
+    def _read_block(self, key: bytes, i: int):
+        return self.store.read_into(key, KIND_KV, memoryview(self.staging.bufs[i].numpy()))
+
+    def pump(self, job: RestoreJob) -> bool:
+        """Engine-thread step of a restore: hands free staging buffers to the reader threads (up to `read_ahead`
+        blocks ahead), scatters every block whose read has finished, in order, with one kernel each, and never
+        blocks: an unfinished read or a busy buffer just means "call again". Returns job.finished."""
+        self.step()
+        while (not job.failed and job.next_read < job.last and len(job.reads) < self.read_ahead):
+            i = self.staging.take()
+            if i is None:
+                break
+            job.reads[job.next_read] = (i, self.readers.submit(self._read_block, job.keys[job.next_read], i))
+            job.next_read += 1
+        dev = self.kv.device
+        while job.next_scatter < job.last and job.next_scatter in job.reads:
+            i, fut = job.reads[job.next_scatter]
+            if not fut.done():
+                break
+            del job.reads[job.next_scatter]
+            hdr = fut.result()
+            if (job.failed or hdr is None or hdr.tokens != BLOCK_TOKENS
+                    or hdr.seg0 != BLOCK_TOKENS * self.token_bytes):
+                job.failed = True            # damaged or missing: the prefix ends before this block
+                self.staging.give(i)
+                continue
+            b = job.next_scatter
+            lo = b * BLOCK_TOKENS - job.start
+            ids = torch.tensor(job.slots[lo:lo + BLOCK_TOKENS], dtype=torch.int32)
+            if dev.type == "cuda":
+                ids = ids.pin_memory().to(dev, non_blocking=True)
+            self.kv.copy_payload(ids, self.staging.bufs[i], to_pool=True)
+            ev = None
+            if dev.type == "cuda":
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream(dev))
+            self._scattered.append((ev, i))
+            job.next_scatter += 1
+            job.good = (b + 1) * BLOCK_TOKENS
+        if job.failed:
+            for b in list(job.reads):        # reads still in flight: give their buffers back once they return
+                i, fut = job.reads[b]
+                if fut.done():
+                    del job.reads[b]
+                    self.staging.give(i)
+            if job.reads:
+                return False
+        if job.finished and self.trace is not None:
+            self.trace("ssd_restore", start=job.start, end=job.end, good=job.good, failed=job.failed)
+        return job.finished
+
+    def finish(self, job: RestoreJob) -> int:
+        """After `pump` returned True: the first position NOT restored, agreed over the ranks."""
+        good = self.agree(job.good)
+        self.restored_tokens += max(good - job.start, 0)
+        return good
 
     # ---- lookup / restore
     def match(self, tokens: Sequence[int]) -> int:
@@ -128,32 +229,16 @@ class SsdTier:
         return n if n - have >= self.min_gain else 0
 
     def restore(self, tokens: Sequence[int], start: int, end: int, slots: Sequence[int]) -> int:
-        """Reads blocks covering positions [start, end) (block aligned) into `slots` (one per position). Returns
-        the first position NOT restored (== end on success; earlier when a block is damaged on any rank)."""
-        assert start % BLOCK_TOKENS == 0 and end % BLOCK_TOKENS == 0 and len(slots) == end - start
-        keys = self._block_keys(tokens, end // BLOCK_TOKENS)
-        dev = self.kv.device
-        good = start
-        i = self.staging.take()
-        if i is None:
-            return self.agree(start)
-        buf = self.staging.bufs[i]
-        try:
-            for b in range(start // BLOCK_TOKENS, end // BLOCK_TOKENS):
-                hdr = self.store.read_into(keys[b], KIND_KV, memoryview(buf.numpy()))
-                if hdr is None or hdr.tokens != BLOCK_TOKENS or hdr.seg0 != BLOCK_TOKENS * self.token_bytes:
-                    break
-                lo = b * BLOCK_TOKENS - start
-                ids = torch.tensor(slots[lo:lo + BLOCK_TOKENS], dtype=torch.int32, device=dev)
-                self.kv.copy_payload(ids, buf, to_pool=True)
-                if dev.type == "cuda":
-                    torch.cuda.current_stream(dev).synchronize()     # the buffer is reused for the next block
-                good = (b + 1) * BLOCK_TOKENS
-        finally:
-            self.staging.give(i)
-        good = self.agree(good)
-        self.restored_tokens += max(good - start, 0)
-        return good
+        """Blocking form of `restore_async` (tests, tools): returns the first position NOT restored (== end on
+        success; earlier when a block is damaged on any rank)."""
+        import time
+        job = self.restore_async(tokens, start, end, slots)
+        while not self.pump(job):
+            time.sleep(0.0005)
+        if self.kv.device.type == "cuda":
+            torch.cuda.current_stream(self.kv.device).synchronize()
+        self.step()
+        return self.finish(job)
 
     def read_tail(self, tokens: Sequence[int]) -> Optional[tuple[int, bytes, Optional[bytes], bytes]]:
         """(tail tokens, their KV payload, state snapshot or None, drafter payload) of the prefix `tokens`."""
@@ -167,6 +252,38 @@ class SsdTier:
         slen = int.from_bytes(meta[:8], "little")
         state = meta[8:8 + slen] if slen else None
         return hdr.tokens, pay, state, meta[8 + slen:]
+
+    # ---- eviction / shutdown
+    def on_evict(self, node) -> None:
+        """Radix-tree hook, called before the KV of an unlocked leaf is freed: the whole path down to the leaf is
+        backed up first (blocks already on disk are skipped), so that an evicted long prefix comes back from NVMe
+        instead of being prefilled again. Copies are queued on the stream; nothing here waits."""
+        tokens, slots, n = [], [], node
+        while n is not None and n.parent is not None:
+            tokens[:0], slots[:0] = n.tokens, n.slots
+            n = n.parent
+        if self.backup(tokens, slots):
+            node.on_ssd = True
+
+    def persist(self, cache) -> int:
+        """Shutdown: backs up every cached path of at least `min_prefix` tokens and waits for the writers."""
+        queued = 0
+        for leaf in list(cache._leaves()):
+            tokens, slots, n = [], [], leaf
+            while n is not None and n.parent is not None:
+                tokens[:0], slots[:0] = n.tokens, n.slots
+                n = n.parent
+            while True:
+                got = self.backup(tokens, slots)
+                queued += got
+                if got == 0 or self.skipped == 0:
+                    break
+                self.store.drain()           # staging was exhausted: let the writers catch up, then continue
+                self.step()
+                self.skipped = 0
+        self.store.drain()
+        self.step()
+        return queued
 
     def stats(self) -> dict:
         return {"backed_up_blocks": self.backed_up, "restored_tokens": self.restored_tokens, "skipped": self.skipped,

@@ -190,11 +190,12 @@ class SsdStore:
 
     # ---- write path
     def write_async(self, key: bytes, kind: int, tokens: int, seg0: bytes | memoryview, seg1: bytes | memoryview = b"",
-                    token: object = None) -> None:
+                    token: object = None, ready=None) -> None:
         """Queues an object; completion (key, ok, token) appears in `completions()`. The segments must stay
-        untouched until then."""
+        untouched until then. `ready` (optional callable) is run by the writer thread before it touches the
+        segments: a CUDA event's `synchronize`, so the engine thread never waits for the gather that fills them."""
         q = self._queues[int.from_bytes(key[:4], "little") % len(self._queues)]
-        q.put((key, kind, tokens, seg0, seg1, token))
+        q.put((key, kind, tokens, seg0, seg1, token, ready))
 
     def completions(self) -> list:
         out = []
@@ -214,7 +215,9 @@ class SsdStore:
             try:
                 if item is None:
                     return
-                key, kind, tokens, seg0, seg1, token = item
+                key, kind, tokens, seg0, seg1, token, ready = item
+                if ready is not None:
+                    ready()
                 ok = self._write(key, kind, tokens, seg0, seg1)
                 self._done.put((key, ok, token))
             finally:

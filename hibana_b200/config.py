@@ -71,6 +71,9 @@ class EngineConfig:
     stable_numerics: bool = False
     attn_splits: int = 0                   # 0 = automatic
     fuse_epilogues: bool = True            # requantise / merge inside the producing kernel (decode shapes)
+    fuse_attn_tail: bool = False           # decode attention merges its KV splits in its last-arriving CTA (measured
+                                           # slower than the merge kernel at batch 64: off; the merge kernel then
+                                           # writes the NVFP4 rows, and an unsplit launch always quantises in-kernel)
     decode_attn: str = "mma"               # mma | tc (persistent tcgen05 kernel, head dim 128)
     prefill_attn: str = "tc"               # tc | general
     gdn_phase1: str = "cuda"               # cuda | torch

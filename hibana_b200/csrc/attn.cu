@@ -13,6 +13,7 @@
 // wrappers planned in hibana/engine/executor.py:161-169 and hibana/kernels/csrc/verify_attn.cu:299-660.
 #include "hb_api.h"
 #include "hb_common.cuh"
+#include "rownorm.cuh"
 
 namespace hb {
 namespace {
@@ -288,10 +289,16 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_splitkv_kernel(const AttnPar
 }
 
 // Merge of split partials: o = sum_s 2^(lse_s - m) o_s / sum_s 2^(lse_s - m). One CTA per (row, head).
+// With q_out the merged row is written as NVFP4 (the activation operand of the output projection) instead of
+// bf16: values are rounded to bf16 first, as a separate quantiser would see them, then one thread per 16-element
+// group packs them and writes the group's scale into the swizzled block layout.
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                                  __nv_bfloat16* __restrict__ out, int splits, int d) {
+                                  __nv_bfloat16* __restrict__ out, int splits, int d, int hq,
+                                  uint8_t* __restrict__ q_out, uint8_t* __restrict__ q_sf,
+                                  const float* __restrict__ q_gscale, int q_ka) {
   grid_dep_wait();     // may run as a programmatic dependent of the split kernel
   grid_dep_launch();
+  __shared__ __align__(32) __nv_bfloat16 fin[256];
   const long long rh = blockIdx.x;
   const float* lse = part_lse + rh * splits;
   float m = -INFINITY;
@@ -306,7 +313,22 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
       }
       o /= wsum;
     }
-    out[rh * d + i] = __float2bfloat16(o);
+    if (q_out == nullptr) out[rh * d + i] = __float2bfloat16(o);
+    else fin[i] = __float2bfloat16(o);
+  }
+  if (q_out != nullptr) {
+    __syncthreads();
+    const int gpr = d >> 4;
+    if (static_cast<int>(threadIdx.x) < gpr) {
+      const int gi = threadIdx.x;
+      const int row = static_cast<int>(rh / hq), head = static_cast<int>(rh % hq);
+      float x[16];
+      load16(fin + gi * 16, x);
+      uint2 packed;
+      const uint32_t sfb = quant16(x, 1.f / *q_gscale, &packed);
+      *reinterpret_cast<uint2*>(q_out + static_cast<size_t>(rh) * (d >> 1) + gi * 8) = packed;
+      q_sf[row_sf_off(row, head * gpr + gi, q_ka)] = static_cast<uint8_t>(sfb);
+    }
   }
 }
 
@@ -391,7 +413,7 @@ int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long lo
   if (rc != 0) return rc;
   if (p.splits > 1) {
     attn_merge_kernel<<<static_cast<unsigned>(static_cast<long long>(total_rows) * hq), 128, 0, st>>>(
-        p.part_o, p.part_lse, p.out, p.splits, d);
+        p.part_o, p.part_lse, p.out, p.splits, d, hq, nullptr, nullptr, nullptr, 0);
     if (cudaGetLastError() != cudaSuccess) return 2;
   }
   return 0;
@@ -402,7 +424,20 @@ int hb_attn_merge(const void* part_o, const void* part_lse, void* out, long long
   if (rows_heads <= 0) return 0;
   launch_dep(attn_merge_kernel, dim3(static_cast<unsigned>(rows_heads)), dim3(128), 0, static_cast<cudaStream_t>(stream),
       static_cast<const float*>(part_o), static_cast<const float*>(part_lse), static_cast<__nv_bfloat16*>(out), splits,
-      d);
+      d, 1, static_cast<uint8_t*>(nullptr), static_cast<uint8_t*>(nullptr), static_cast<const float*>(nullptr), 0);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// Split merge with NVFP4 output: rows [rows, hq * d] packed e2m1 into q_out, swizzled ue4m3 scales into q_sf
+// (q_ka K atoms per row block), static per-tensor scale *q_gscale. d <= 256, a multiple of 16.
+int hb_attn_merge_quant(const void* part_o, const void* part_lse, long long rows, int hq, int splits, int d,
+                        void* q_out, void* q_sf, const void* q_gscale, int q_ka, void* stream) {
+  if (rows <= 0) return 0;
+  if (d > 256 || d % 16 != 0 || q_out == nullptr || q_sf == nullptr || q_gscale == nullptr) return 1;
+  launch_dep(attn_merge_kernel, dim3(static_cast<unsigned>(rows * hq)), dim3(128), 0, static_cast<cudaStream_t>(stream),
+      static_cast<const float*>(part_o), static_cast<const float*>(part_lse), static_cast<__nv_bfloat16*>(nullptr),
+      splits, d, hq, static_cast<uint8_t*>(q_out), static_cast<uint8_t*>(q_sf), static_cast<const float*>(q_gscale),
+      q_ka);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -515,23 +515,56 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
     __syncthreads();
     if (*last_flag) {
       __threadfence();
-      for (int i = tid; i < nq * D; i += DEC_WARPS * 32) {
-        const int qi = i / D, d = i % D;
-        const int rr = qi / g, gg = qi % g;
-        const long long rh = static_cast<long long>(row0 + rr) * p.hq + kvh * g + gg;
-        float m = -INFINITY;
-        for (int s2 = 0; s2 < p.splits; ++s2) m = fmaxf(m, __ldcg(p.part_lse + rh * p.splits + s2));
-        float o = 0.f, wsum = 0.f;
-        if (m > -INFINITY) {
-          for (int s2 = 0; s2 < p.splits; ++s2) {
-            const float w = exp2f(__ldcg(p.part_lse + rh * p.splits + s2) - m);
-            if (w > 0.f) o += w * __ldcg(p.part_o + (rh * p.splits + s2) * D + d);
-            wsum += w;
-          }
-          o /= wsum;
+      // The merge is latency-bound (a few hundred values per CTA, every one a chain of L2 reads), so the reads are
+      // batched: all log-sum-exps of this (sequence, kv head) land in shared memory in one round trip, then every
+      // thread keeps four outputs in flight per pass over the splits.
+      float* lse_s = reinterpret_cast<float*>(smem);          // [nq][splits], the rings are idle
+      const int S = p.splits;
+      for (int i = tid; i < nq * S; i += DEC_WARPS * 32) {
+        const int qi = i / S, s2 = i - qi * S;
+        const long long rh = static_cast<long long>(row0 + qi / g) * p.hq + kvh * g + qi % g;
+        lse_s[i] = __ldcg(p.part_lse + rh * S + s2);
+      }
+      __syncthreads();
+      constexpr int V = 4;
+      for (int base = 0; base < nq * D; base += V * DEC_WARPS * 32) {
+        float o[V], mx[V], wsum[V];
+        long long rhv[V];
+        int qv[V], dv[V];
+        bool live[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          const int i = base + v * DEC_WARPS * 32 + tid;
+          live[v] = i < nq * D;
+          qv[v] = live[v] ? i / D : 0;
+          dv[v] = live[v] ? i % D : 0;
+          rhv[v] = static_cast<long long>(row0 + qv[v] / g) * p.hq + kvh * g + qv[v] % g;
+          float m = -INFINITY;
+          for (int s2 = 0; s2 < S; ++s2) m = fmaxf(m, lse_s[qv[v] * S + s2]);
+          mx[v] = m;
+          o[v] = 0.f;
+          wsum[v] = 0.f;
         }
-        if (p.q_out == nullptr) p.out[rh * D + d] = __float2bfloat16(o);
-        else fin[i] = __float2bfloat16(o);
+#pragma unroll 2
+        for (int s2 = 0; s2 < S; ++s2) {
+          float x[V];
+#pragma unroll
+          for (int v = 0; v < V; ++v) x[v] = live[v] ? __ldcg(p.part_o + (rhv[v] * S + s2) * D + dv[v]) : 0.f;
+#pragma unroll
+          for (int v = 0; v < V; ++v) {
+            const float w = mx[v] > -INFINITY ? exp2f(lse_s[qv[v] * S + s2] - mx[v]) : 0.f;
+            if (w > 0.f) o[v] += w * x[v];
+            wsum[v] += w;
+          }
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          if (!live[v]) continue;
+          const float r = wsum[v] > 0.f ? o[v] / wsum[v] : 0.f;
+          const int i = base + v * DEC_WARPS * 32 + tid;
+          if (p.q_out == nullptr) p.out[rhv[v] * D + dv[v]] = __float2bfloat16(r);
+          else fin[i] = __float2bfloat16(r);
+        }
       }
       finish = p.q_out != nullptr;
     }

@@ -39,7 +39,8 @@ struct Ctrl {
   int sp_seq_gather;             // gathers this rank has pushed
   int sp_done;                   // CTAs of the running reduce kernel that have finished
   int sp_target;                 // tile arrivals every source owes after the scatters completed so far
-  int pad[12];
+  int pick_seq;                  // vocab-parallel (value, index) exchanges completed on this rank
+  int pad[11];
 };
 static_assert(sizeof(Ctrl) <= CTRL_BYTES, "control block too large");
 
@@ -423,12 +424,98 @@ __global__ void barrier_kernel(const BarrierParams p) {
   if (threadIdx.x == 0) mine->seq[p.slot] = seq;
 }
 
+// Vocab-parallel greedy pick: every rank holds, per row, the best (logit, global token id) of its vocabulary shard.
+// Each rank pushes its pairs into every peer's landing area as two 8-byte words {payload, sequence number} (the
+// low-latency protocol: the receiver spins on the words themselves), then takes the best of the world's pairs in
+// (value desc, id asc) order, which is the same choice on every rank. 16 bytes per row and rank cross NVLink
+// instead of the rows x vocabulary fp32 logits of an all-gather.
+struct PickParams {
+  Peers peers;
+  int world, rank, rows, rows_cap;
+  long long area_offset;          // landing area [world][rows_cap] x 16 bytes in every heap
+  const float* val;               // [rows] best local logit
+  const long long* idx;           // [rows] its id inside the shard
+  long long idx_offset;           // first global id of this rank's shard
+  long long* out;                 // [rows] global id of the world's best
+  unsigned long long limit_ns;
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) pick_exchange_kernel(const PickParams p) {
+  Ctrl* mine = reinterpret_cast<Ctrl*>(p.peers.base[p.rank]);
+  const int seq = ld_relaxed_sys(&mine->pick_seq) + 1;
+  const unsigned long long t0 = globaltimer_ns();
+  for (int row = threadIdx.x; row < p.rows; row += blockDim.x) {
+    float best = p.val[row];
+    long long bi = p.idx[row] + p.idx_offset;
+    const size_t slot = static_cast<size_t>(p.rank) * p.rows_cap + row;
+    for (int d = 0; d < p.world; ++d) {
+      if (d == p.rank) continue;
+      uint2* dst = reinterpret_cast<uint2*>(p.peers.base[d] + p.area_offset) + slot * 2;
+      asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(best)), "r"(seq) : "memory");
+      asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst + 1), "r"(static_cast<unsigned>(bi)), "r"(seq) : "memory");
+    }
+    for (int r = 0; r < p.world; ++r) {
+      if (r == p.rank) continue;
+      const uint2* src = reinterpret_cast<const uint2*>(p.peers.base[p.rank] + p.area_offset) +
+                         (static_cast<size_t>(r) * p.rows_cap + row) * 2;
+      unsigned w[2] = {0, 0};
+      bool ok = true;
+      for (int k = 0; k < 2 && ok; ++k) {
+        ok = false;
+        for (unsigned long long it = 0, cap = spin_cap(p.limit_ns); it < cap; ++it) {
+          unsigned data, flag;
+          asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(data), "=r"(flag) : "l"(src + k) : "memory");
+          if (static_cast<int>(flag) == seq) {
+            w[k] = data;
+            ok = true;
+            break;
+          }
+          if ((it & 255u) == 255u &&
+              (globaltimer_ns() - t0 > p.limit_ns || *reinterpret_cast<volatile int*>(p.status) != 0))
+            break;
+        }
+      }
+      if (!ok) {
+        set_status(p.status, kTimeoutLowLatency);
+        continue;
+      }
+      const float v = __uint_as_float(w[0]);
+      const long long i = static_cast<long long>(w[1]);
+      if (v > best || (v == best && i < bi)) {
+        best = v;
+        bi = i;
+      }
+    }
+    p.out[row] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mine->pick_seq = seq;
+}
+
 }  // namespace
 }  // namespace hb
 
 using namespace hb;
 
 extern "C" {
+
+// Vocab-parallel greedy pick (see pick_exchange_kernel). rows <= rows_cap; area_offset + world * rows_cap * 16 bytes
+// must lie inside every heap and must not be a slot another collective writes.
+int hb_pick_exchange(const void* const* peer_bases, int world, int rank, int rows, int rows_cap, long long area_offset,
+                     const void* val, const void* idx, long long idx_offset, void* out, long long limit_ns,
+                     void* status, void* stream) {
+  if (world < 1 || world > MAX_WORLD || rows <= 0 || rows > rows_cap) return 1;
+  PickParams p;
+  for (int i = 0; i < MAX_WORLD; ++i)
+    p.peers.base[i] = i < world ? static_cast<uint8_t*>(const_cast<void*>(peer_bases[i])) : nullptr;
+  p.world = world; p.rank = rank; p.rows = rows; p.rows_cap = rows_cap; p.area_offset = area_offset;
+  p.val = static_cast<const float*>(val); p.idx = static_cast<const long long*>(idx); p.idx_offset = idx_offset;
+  p.out = static_cast<long long*>(out); p.limit_ns = static_cast<unsigned long long>(limit_ns);
+  p.status = static_cast<int*>(status);
+  pick_exchange_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
 
 int hb_comm_ctrl_bytes(void) { return CTRL_BYTES; }
 int hb_comm_nslot(void) { return NSLOT; }

@@ -109,7 +109,16 @@ struct DevParams {
   const float* q_gscale;
   int q_ka;
   long long q_ld;
+  unsigned long long* prof;   // optional phase timers (hb_gemm_profile), null = off
 };
+
+// Phase timers of one epilogue thread per CTA, summed over CTAs: nanoseconds since kernel entry at
+// [0] set-up done, [1] predecessor complete, [2] accumulator complete, [3] partial parked, [4] cluster barrier 1,
+// [5] reduce + stores done, [6] cluster barrier 2; [7] counts CTAs.
+__device__ __forceinline__ void prof_mark(const DevParams& p, int slot, unsigned long long t0) {
+  if (p.prof != nullptr && threadIdx.x == 64)
+    atomicAdd(p.prof + slot, slot == 7 ? 1ull : static_cast<unsigned long long>(globaltimer_ns() - t0));
+}
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
@@ -246,6 +255,60 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
   }
 }
 
+// Epilogue of four consecutive features (rows grow0 .. grow0 + 3 of the weight operand, grow0 a multiple of 4) of one
+// token with the weights on the 128-row side: out[tok][grow0 ..]. The split-K reduce hands its sums over in this
+// shape (one 16-byte distributed-shared-memory load per partial), so gate / up pairs sit in one thread and every
+// store is 4 to 16 bytes wide and contiguous across the warp.
+__device__ __forceinline__ void epilogue_rows4(const DevParams& p, float4 v, int grow0, int row_lim, int tok,
+                                               float alpha, __nv_bfloat16* stg_row) {
+  if (p.tok_scale != nullptr) alpha *= p.tok_scale[tok];
+  float x[4] = {v.x * alpha, v.y * alpha, v.z * alpha, v.w * alpha};
+  const bool full = grow0 + 3 < row_lim && (p.ldo & 3) == 0;
+  if (p.epilogue == kEpiSiluMulQuant) {
+    *reinterpret_cast<uint32_t*>(stg_row) = pack_bf16(silu(x[0]) * x[1], silu(x[2]) * x[3]);
+  } else if (p.epilogue == kEpiSiluMul) {
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(tok) * p.ldo + (grow0 >> 1);
+    if (full) {
+      *reinterpret_cast<uint32_t*>(out) = pack_bf16(silu(x[0]) * x[1], silu(x[2]) * x[3]);
+    } else {
+      if (grow0 + 1 < row_lim) out[0] = __float2bfloat16(silu(x[0]) * x[1]);
+      if (grow0 + 3 < row_lim) out[1] = __float2bfloat16(silu(x[2]) * x[3]);
+    }
+  } else if (p.epilogue == kEpiStoreF32) {
+    float* out = static_cast<float*>(p.out) + static_cast<long long>(tok) * p.ldo + grow0;
+    if (full) {
+      *reinterpret_cast<float4*>(out) = make_float4(x[0], x[1], x[2], x[3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (grow0 + i < row_lim) out[i] = x[i];
+    }
+  } else {
+    const long long o = static_cast<long long>(tok) * p.ldo + grow0;
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + o;
+    if (full) {
+      if (p.epilogue == kEpiResidual) {
+        const uint2 r = *reinterpret_cast<const uint2*>(p.residual + o);
+        x[0] += bf16_lo(r.x); x[1] += bf16_hi(r.x); x[2] += bf16_lo(r.y); x[3] += bf16_hi(r.y);
+      }
+      if (p.epilogue == kEpiRelu2) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = x[i] > 0.f ? x[i] * x[i] : 0.f;
+      }
+      *reinterpret_cast<uint2*>(out) = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (grow0 + i < row_lim) {
+          float y = x[i];
+          if (p.epilogue == kEpiResidual) y += __bfloat162float(p.residual[o + i]);
+          if (p.epilogue == kEpiRelu2) y = y > 0.f ? y * y : 0.f;
+          out[i] = __float2bfloat16(y);
+        }
+    }
+  }
+}
+
 // kEpiReturn: one thread per CTA reports in after its stores are fenced system-wide; the last CTA of the grid
 // publishes this rank's sequence number on every rank's return flag and re-arms the counter.
 // A CTA that wrote nothing (`wrote` false: an expert chunk past the expert's rows) skips the system-wide fence,
@@ -265,11 +328,12 @@ __device__ __forceinline__ void ep_cta_done(const DevParams& p, bool wrote = tru
 }
 
 template <int KIND, int BN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, BN <= 64 ? 2 : 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUtensorMap tmb, const DevParams p) {
   using C = Cfg<KIND, BN>;
   constexpr int S = C::STAGES;
   constexpr int CH = C::CH;
+  const unsigned long long t_entry = p.prof != nullptr ? globaltimer_ns() : 0ull;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * C::STAGE_BYTES);
@@ -309,6 +373,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     split = 0;
     tile_b = 0;
   }
+  // unsplit, ungrouped tiles with the weights on the 128-row side reduce "over one partial" (see below)
+  const bool local_reduce = p.splits == 1 && p.swap && p.grp_cnt == nullptr && p.epilogue != kEpiReturn;
   const int kt_per = (p.k_tiles + p.splits - 1) / p.splits;
   const int kt0 = split * kt_per;
   const int kt1 = min(kt0 + kt_per, p.k_tiles);
@@ -334,6 +400,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  prof_mark(p, 0, t_entry);
   // Let the kernel after this one be scheduled now (it waits for this grid's completion before it reads anything
   // this grid writes): its launch latency and prologue overlap this grid's main loop.
   if (p.early_launch) grid_dep_launch();
@@ -531,8 +598,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
       }
     }
     grid_dep_wait();
+    prof_mark(p, 1, t_entry);
     const bool ok = nkt > 0 ? mbar_wait(accum, 0, abort, p.status, kTimeoutAccum) : true;
     tc_fence_after();
+    prof_mark(p, 2, t_entry);
     const int row = tile_a * BM + q * 32 + lane;   // feature index (within the expert in grouped mode)
     const uint32_t tlane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     float alpha = p.alpha;
@@ -615,28 +684,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
           asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
         }
       }
-    } else if (ok && p.splits == 1 && p.epilogue == kEpiSiluMulQuant) {
-      // Weights on the 128-row side, gate / up rows interleaved: lane pairs hold (gate, up) of one output feature.
-      // Even lanes park the bf16 SiLU-mul result as [token][64 features] in the idle stage ring, then the four
-      // warps quantise the tile together.
-      __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem);
-      const int ncols = min(BN, col_lim - b_row0);
-      for (int c0 = 0; c0 < BN; c0 += CH) {
-        uint32_t r[CH];
-        if constexpr (CH == 32) tmem_ld_32x32(tlane + c0, r);
-        else tmem_ld_32x16(tlane + c0, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          const float x = nkt > 0 ? __uint_as_float(r[j]) * alpha : 0.f;
-          const float other = __shfl_xor_sync(0xffffffffu, x, 1);
-          if ((lane & 1) == 0 && c0 + j < ncols)
-            stg[(c0 + j) * 64 + ((q * 32 + lane) >> 1)] = __float2bfloat16(silu(x) * other);
-        }
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      quant_stage(p, stg, ncols, b_row0, tile_a, static_cast<int>(threadIdx.x) - 64);
-    } else if (ok && p.splits == 1) {
+    } else if (ok && p.splits == 1 && !local_reduce) {
       for (int c0 = 0; c0 < BN; c0 += CH) {
         uint32_t r[CH];
         if constexpr (CH == 32) tmem_ld_32x32(tlane + c0, r);
@@ -662,11 +710,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
       }
     }
   }
-  if (p.splits > 1) {
+  prof_mark(p, 3, t_entry);
+  if (p.splits > 1 || local_reduce) {
     // Every thread of every CTA of the cluster arrives, whatever happened to its pipeline (all waits above are
-    // bounded), so the barrier cannot hang; a timed-out CTA has already raised the status word.
+    // bounded), so the barrier cannot hang; a timed-out CTA has already raised the status word. An unsplit tile
+    // with the weights on the 128-row side takes the same path with one partial (its own): the [column][row]
+    // layout in shared memory is what makes its stores wide and its gate / up pairs thread-local.
     __syncwarp();
-    cluster_sync_all();
+    if (p.splits > 1) cluster_sync_all();
+    else if (warp >= 2) asm volatile("bar.sync 1, 128;" ::: "memory");
+    prof_mark(p, 4, t_entry);
     if (warp >= 2) {
       const int q = warp & 3;
       const int lrow = q * 32 + lane;
@@ -683,6 +736,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
       const bool requant = p.epilogue == kEpiSiluMulQuant;
       // kEpiSiluMulQuant: this CTA's token slice is parked behind the fp32 partial (which peers still read)
       __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + BN * BM * 4);
+      if (p.swap) {
+        // Weights on the 128-row side: the partials are [token column][128 rows] fp32, so four consecutive rows of
+        // one column are one 16-byte load. A thread owns rows 4 r4 .. 4 r4 + 3 of every fourth column of the
+        // slice and keeps the loads of two columns over all splits in flight (the reduce is a chain of
+        // distributed-shared-memory round trips otherwise), then sums in split order (deterministic).
+        const int et = static_cast<int>(threadIdx.x) - 64;
+        const int lrow0 = (et & 31) * 4, cg = et >> 5;
+        const int grow0 = tile_a * BM + lrow0;
+        uint32_t base[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) base[s] = s < p.splits ? map_to_cta(part_local, static_cast<uint32_t>(s)) : part_local;
+        for (int c = c_begin + cg; c < c_end; c += 8) {
+          const bool two = c + 4 < c_end;
+          float4 a[8], b[8];
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            if (s < p.splits) {
+              a[s] = ld_dsmem_v4(base[s] + (c * BM + lrow0) * 4);
+              if (two) b[s] = ld_dsmem_v4(base[s] + ((c + 4) * BM + lrow0) * 4);
+            }
+          float4 sa = make_float4(0.f, 0.f, 0.f, 0.f), sb = sa;
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            if (s < p.splits) {
+              sa.x += a[s].x; sa.y += a[s].y; sa.z += a[s].z; sa.w += a[s].w;
+              if (two) { sb.x += b[s].x; sb.y += b[s].y; sb.z += b[s].z; sb.w += b[s].w; }
+            }
+          epilogue_rows4(p, sa, grow0, row_lim, b_row0 + c, alpha, stg + (c - c_begin) * 64 + (lrow0 >> 1));
+          if (two) epilogue_rows4(p, sb, grow0, row_lim, b_row0 + c + 4, alpha, stg + (c + 4 - c_begin) * 64 + (lrow0 >> 1));
+        }
+      } else {
       for (int c0 = c_begin; c0 < c_end; c0 += 16) {
         float v[16];
 #pragma unroll
@@ -693,25 +777,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
           for (int j = 0; j < 16; ++j)
             if (c0 + j < c_end) v[j] += ld_dsmem_f32(src + j * BM * 4);
         }
-        if (requant) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float x = v[j] * alpha;
-            const float other = __shfl_xor_sync(0xffffffffu, x, 1);
-            if ((lane & 1) == 0 && c0 + j < c_end) stg[(c0 - c_begin + j) * 64 + (lrow >> 1)] = __float2bfloat16(silu(x) * other);
-          }
-        } else {
-          epilogue_chunk<16>(p, v, row, row_lim, b_row0 + c0, b_row0 + c_end, alpha, lane);
-        }
+        epilogue_chunk<16>(p, v, row, row_lim, b_row0 + c0, b_row0 + c_end, alpha, lane);
+      }
       }
       if (requant) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (c_end > c_begin) quant_stage(p, stg, c_end - c_begin, b_row0 + c_begin, tile_a, static_cast<int>(threadIdx.x) - 64);
       }
     }
+    prof_mark(p, 5, t_entry);
     __syncwarp();
-    cluster_sync_all();   // nobody leaves while a peer may still read its partial
+    if (p.splits > 1) cluster_sync_all();   // nobody leaves while a peer may still read its partial
+    prof_mark(p, 6, t_entry);
   }
+  prof_mark(p, 7, t_entry);
   if (p.epilogue == kEpiReturn && warp >= 2) __threadfence_system();   // this thread's remote stores
   tc_fence_before();
   __syncthreads();
@@ -746,6 +825,7 @@ EncodeFn encode_fn() {
 std::mutex g_tmap_mu;
 std::unordered_map<TmapKey, std::unique_ptr<CUtensorMap>, KeyHash> g_tmaps;
 
+unsigned long long* g_gemm_prof = nullptr;
 int g_pdl = 0;   // launch with programmatic stream serialisation (set through hb_gemm_set_pdl)
 
 template <int KIND, int BN>
@@ -923,6 +1003,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   p.tok_scale = a.tok_scale;
   p.q_out = static_cast<uint8_t*>(a.q_out); p.q_sf = static_cast<uint8_t*>(a.q_sf); p.q_gscale = a.q_gscale;
   p.q_ka = a.q_ka; p.q_ld = a.q_ld;
+  p.prof = g_gemm_prof;
   if (a.epilogue == kEpiSiluMulQuant) {
     // tokens on the N side, whole 128-row feature tiles, no grouped / peer variants; the staging tile of a split-K
     // CTA sits behind its fp32 partial, which the smallest ring must still hold
@@ -1136,6 +1217,9 @@ int hb_gemm_w3(const void* tiles, const void* x, int n, int m, int k, long long 
   const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }
+
+// Phase timers (see prof_mark): `buf` = 8 zeroed uint64 on the device, null switches them off.
+void hb_gemm_profile(void* buf) { hb::g_gemm_prof = static_cast<unsigned long long*>(buf); }
 
 void hb_clear_tmap_cache(void) { hb::clear_tmap_cache(); }
 

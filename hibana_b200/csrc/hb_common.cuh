@@ -150,6 +150,14 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
   return v;
 }
+__device__ __forceinline__ float4 ld_dsmem_v4(uint32_t cluster_addr) {   // 16-byte aligned
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
 // The grid this one depends on (programmatic stream serialisation) has completed and its writes are visible.
 // A no-op when the kernel was launched without the attribute.
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

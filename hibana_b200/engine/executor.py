@@ -37,7 +37,8 @@ class Executor:
     def __init__(self, model, *, max_batch: int = 64, max_ctx: int = 4096, kv_slots: int = 0,
                  use_graphs: bool = True, buckets: Optional[Sequence[int]] = None, radix_cache: bool = True,
                  state_pool=None, comm=None, kv_dtype: Optional[torch.dtype] = None, attn_splits: int = 0,
-                 decode_reserve: int = 64, state_slots: int = 0):
+                 decode_reserve: int = 64, state_slots: int = 0, state_dtype: torch.dtype = torch.float32,
+                 debug_sync: bool = False):
         t: Target = model.target
         self.model, self.target = model, t
         self.device = model.device
@@ -52,13 +53,15 @@ class Executor:
         if state_pool is None and spec is not None:
             from ..cache.state_pool import StatePool
             state_pool = StatePool(spec["layers"], state_slots or (3 * max_batch + 2), spec["conv_dim"],
-                                   spec["conv_width"], spec["state_shape"], self.device)
+                                   spec["conv_width"], spec["state_shape"], self.device, state_dtype=state_dtype)
         self.state_pool = state_pool
         buckets = buckets or tuple(b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_batch)
         self.runner = ModelRunner(model, self.kv, max_batch=max_batch, max_ctx=max_ctx, buckets=buckets,
                                   use_graphs=use_graphs, comm=comm, attn_splits=attn_splits, state_pool=state_pool)
         self.comm = comm
+        self.runner.debug_sync = debug_sync
         self.ssd = None
+        self._restores: dict = {}        # rid -> RestoreJob in flight, or None once the question is settled
         self.state = StateManager(self.kv, state_pool, cache=radix_cache, decode_reserve=decode_reserve)
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "decode_steps": 0, "prefill_chunks": 0,
                       "cached_tokens": 0}
@@ -86,13 +89,38 @@ class Executor:
             raise ValueError("token id out of range")
 
     def can_admit(self, req: Request) -> bool:
+        """Pure while no SSD tier is on. With one, the first call for a request may start an asynchronous restore
+        of its prefix; the request then stays in the queue (this returns False) while reader threads and scatter
+        kernels bring the blocks back, and the engine keeps stepping everybody else."""
+        if self.ssd is not None and req.cacheable and not self._restore_settled(req):
+            return False
         return bool(self.runner._free_rows) and self.state.can_admit(req)
+
+    def _restore_settled(self, req: Request) -> bool:
+        if req.rid in self._restores and self._restores[req.rid] is None:
+            return True
+        job = self._restores.get(req.rid)
+        if job is None:
+            self.ssd.step()
+            job = self.state.begin_ssd_restore(req.all_ids if req.output_ids else req.prompt_ids, self.ssd)
+            self._restores[req.rid] = job
+            if job is None:
+                return True
+        done = self.ssd.pump(job)
+        if self.comm is not None:          # ranks finish reads at different times; they move on together
+            done = bool(self.comm.min_int(int(done)))
+        if not done:
+            return False
+        got = self.state.finish_ssd_restore(job, self.ssd)
+        self.stats["ssd_restored_tokens"] = self.stats.get("ssd_restored_tokens", 0) + got
+        self._restores[req.rid] = None
+        return True
 
     def enable_ssd_tier(self, directory: str, *, budget_bytes: int = 200 << 30, min_prefix: Optional[int] = None,
                         min_gain: Optional[int] = None, identity: Optional[dict] = None) -> None:
-        """Long prefixes are backed up to `directory` when a request is released and restored on admission when
-        that gains enough tokens over the GPU cache (cache/ssd.py). With tensor parallelism every rank stores its
-        own heads and the ranks agree on how far a restore got."""
+        """Long prefixes are backed up to `directory` when a request is released and when the radix tree evicts
+        them, and come back on admission when that gains enough tokens over the GPU cache (cache/ssd.py). With
+        tensor parallelism every rank stores its own heads and the ranks agree on how far a restore got."""
         from ..cache import ssd, ssd_store
         t = self.model.target
         ident = {"target": t.name, "layers": len(t.layers), "kv_heads": t.kv_heads, "head_dim": t.head_dim,
@@ -105,13 +133,47 @@ class Executor:
         agree = (lambda n: self.comm.min_int(n)) if self.comm is not None else None
         self.ssd = ssd.SsdTier(store, self.kv, min_prefix=ssd.MIN_PREFIX if min_prefix is None else min_prefix,
                                min_gain=ssd.MIN_GAIN if min_gain is None else min_gain, agree=agree)
+        if self.state.cache is not None:
+            self.state.cache.ssd_hook = self.ssd.on_evict     # backup before the KV of an evicted path is freed
+
+    def rebuild_from_ssd(self) -> dict:
+        """Start-up: indexes what an earlier run left in the tier's directory (objects are content-addressed by the
+        chained hash of their tokens, so finding a prefix needs no rebuilt tree, only the key index)."""
+        if self.ssd is None:
+            return {}
+        self.ssd.store.scan()                     # (the store also scans when it is opened)
+        self.stats["ssd_objects_at_start"] = self.ssd.store.stats()["objects"]
+        return self.ssd.stats()
+
+    def persist_prefixes(self) -> int:
+        """Shutdown: every cached path long enough for the tier goes to disk; returns blocks written."""
+        if self.ssd is None or self.state.cache is None:
+            return 0
+        return self.ssd.persist(self.state.cache)
+
+    def warmup(self, prompt_len: int = 64) -> None:
+        """One short request through prefill and a few decode steps (all code paths, allocator pools, tensor-map
+        cache and graphs touched once) before the first real request pays for it; leaves no trace in the cache."""
+        n = max(8, min(prompt_len, self.max_ctx // 4))
+        r = Request(prompt_ids=[1 + (i % max(self.target.vocab - 2, 1)) for i in range(n)],
+                    params=SamplingParams(max_tokens=4, ignore_eos=True))
+        r.cacheable = False
+        spec, self.spec = self.spec, None
+        try:
+            self.generate_batch_requests([r])
+        finally:
+            self.spec = spec
+        for k in self.stats:
+            self.stats[k] = 0
 
     def admit(self, req: Request) -> None:
         """Takes a block-table row (and, with a cache, the matched prefix) for the request."""
-        if getattr(self, "ssd", None) is not None and req.cacheable:
-            self.ssd.step()
-            got = self.state.restore_from_ssd(req.all_ids if req.output_ids else req.prompt_ids, self.ssd)
-            self.stats["ssd_restored_tokens"] = self.stats.get("ssd_restored_tokens", 0) + got
+        if self.ssd is not None and req.cacheable and req.rid not in self._restores:
+            # offline callers admit without asking `can_admit` first: settle the restore question here, blocking
+            import time
+            while not self._restore_settled(req):
+                time.sleep(0.0005)
+        self._restores.pop(req.rid, None)
         req.table_row = self.runner.alloc_row()
         try:
             self.state.admit(req)
@@ -243,7 +305,10 @@ class Executor:
                        prefill_budget: int = 4096) -> list[Request]:
         """Runs prompts to completion with a simple loop (admit all, chunked prefill, lock-step decode)."""
         plist = params if isinstance(params, (list, tuple)) else [params] * len(prompts)
-        reqs = [Request(prompt_ids=list(p), params=sp) for p, sp in zip(prompts, plist)]
+        return self.generate_batch_requests([Request(prompt_ids=list(p), params=sp) for p, sp in zip(prompts, plist)],
+                                            prefill_budget)
+
+    def generate_batch_requests(self, reqs: list, prefill_budget: int = 4096) -> list[Request]:
         for r in reqs:
             self.validate_request(r)
         pending = list(reqs)

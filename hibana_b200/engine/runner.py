@@ -34,6 +34,7 @@ class StepBuffers:
         self.out = torch.zeros(bucket, dtype=torch.int64, device=device)
         self.out_host = torch.zeros(bucket, dtype=torch.int64, pin_memory=pin)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.graph_greedy: Optional[torch.cuda.CUDAGraph] = None   # tensor parallel: greedy-only step (no logits gather)
         self.workspace = None
         self.splits = 1
         self.mask: Optional[torch.Tensor] = None      # grammar bitmask [bucket, ceil(vocab / 32)], all ones = free
@@ -113,7 +114,9 @@ class ModelRunner:
                 return b
         raise ValueError(f"batch {n} exceeds the largest bucket {self.buckets[-1]}")
 
-    def _decode_body(self, buf: StepBuffers) -> None:
+    def _decode_body(self, buf: StepBuffers, greedy: bool = False) -> None:
+        """`greedy`: every row is greedy and unconstrained; with a vocab-parallel head the ranks then exchange one
+        (value, id) pair per row instead of gathering the logits."""
         v = buf.views()
         self.block_table.index_put_((v["row"].long(), v["pos"].long()), v["slot"])
         ctx = ForwardContext(DECODE, positions=v["pos"], slots=v["slot"], kv_indices=self.block_table,
@@ -121,6 +124,9 @@ class ModelRunner:
                              attn_workspace=buf.workspace, comm=self.comm,
                              state_slots=v["state"])
         h = self._forward(v["ids"].long(), ctx)
+        if greedy:
+            buf.out.copy_(self.model.greedy_tokens(h, self.comm))
+            return
         logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
         tok = sampling.sample(logits, v["temp"], v["top_k"], v["top_p"], v["seed"], v["offs"], bitmask=buf.mask)
         buf.out.copy_(tok)
@@ -155,11 +161,35 @@ class ModelRunner:
                 self._decode_body(buf)
             self.graph_launches[b] = nv.LAUNCHES - before
             buf.graph = g
+            if self._split_head():
+                with torch.cuda.stream(s):
+                    self._decode_body(buf, greedy=True)
+                torch.cuda.current_stream().wait_stream(s)
+                torch.cuda.synchronize()
+                g2 = torch.cuda.CUDAGraph()
+                before = nv.LAUNCHES
+                with torch.cuda.graph(g2):
+                    self._decode_body(buf, greedy=True)
+                self.graph_launches[b] = nv.LAUNCHES - before     # the common step: report this one
+                buf.graph_greedy = g2
+
+    def _split_head(self) -> bool:
+        return (self.comm is not None and getattr(self.model, "vocab_shard", 0) > 0
+                and hasattr(self.model, "greedy_tokens") and hasattr(self.comm, "pick_exchange"))
+
+    debug_sync = False      # synchronise and read the status word after every forward (slow; pins a fault to it)
 
     def _forward(self, ids, ctx):
         if self.state_pool is not None:
-            return self.model.forward(ids, ctx, self.kv, self.state_pool)
-        return self.model.forward(ids, ctx, self.kv)
+            h = self.model.forward(ids, ctx, self.kv, self.state_pool)
+        else:
+            h = self.model.forward(ids, ctx, self.kv)
+        if self.debug_sync and self.device.type == "cuda" and not torch.cuda.is_current_stream_capturing():
+            torch.cuda.synchronize(self.device)
+            code = nv.read_status(self.device)
+            if code:
+                raise nv.DeviceWaitTimeout(code)
+        return h
 
     def decode(self, rows: Sequence[int], tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int],
                sampling_rows: Optional[dict] = None, state_slots: Optional[Sequence[int]] = None,
@@ -201,10 +231,13 @@ class ModelRunner:
                     buf.mask[i].copy_(m, non_blocking=True)
                     buf.mask_dirty.append(i)
                     self.h2d_bytes += m.numel() * 4
-        if buf.graph is not None:
+        greedy = sampling_rows is None and masks is None and self._split_head()
+        if greedy and buf.graph_greedy is not None:
+            buf.graph_greedy.replay()
+        elif buf.graph is not None:
             buf.graph.replay()
         else:
-            self._decode_body(buf)
+            self._decode_body(buf, greedy=greedy)
         buf.out_host.copy_(buf.out, non_blocking=True)
         self._queue_status_read()
         if self.device.type == "cuda":

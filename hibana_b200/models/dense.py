@@ -212,7 +212,8 @@ class DenseModel:
                                             kv_scale=kv.kv_scale, splits=ctx.attn_splits,
                                             workspace=ctx.attn_workspace,
                                             quant_scale=layer.o.input_scale if fuse else None)
-            h, slot = self._row_parallel(layer.o, att if fuse else att.view(att.shape[0], -1), ctx)
+            h, slot = self._row_parallel(layer.o, att if isinstance(att, nvfp4.Nvfp4Tensor)
+                                         else att.view(att.shape[0], -1), ctx)
             act = self._reduce_norm_linear(h, slot, res, layer.post_norm, layer.gate_up, ctx,
                                            epilogue=gemm.EPI_SILU_MUL,
                                            requant=layer.down.input_scale if fuse else None)
@@ -230,6 +231,19 @@ class DenseModel:
         if comm is not None:
             h = comm.all_reduce(h)
         return basic.rmsnorm(h, self.final_norm, t.norm_eps, residual=res)
+
+    def greedy_tokens(self, normed: torch.Tensor, comm=None) -> torch.Tensor:
+        """Greedy token of every row without materialising the full logits on any rank: with a vocab-parallel head
+        each rank takes the maximum of its shard and the ranks exchange one (value, id) pair per row
+        (`Communicator.pick_exchange`). Reference pattern: hibana/proposers/draft_head.py:229-285."""
+        from ..ops import sampling
+        lg = gemm.linear_bf16(normed, self.lm_head, epilogue=gemm.EPI_STORE_F32)
+        if not (self.vocab_shard and comm is not None):
+            return sampling.argmax(lg)
+        idx, val = sampling.argmax_with_value(lg)
+        if hasattr(comm, "pick_exchange"):
+            return comm.pick_exchange(val, idx, self.target.tp_rank * self.vocab_shard)
+        return sampling.argmax(comm.all_gather_last(lg))
 
     def logits(self, normed: torch.Tensor, comm=None) -> torch.Tensor:
         lg = gemm.linear_bf16(normed, self.lm_head, epilogue=gemm.EPI_STORE_F32)

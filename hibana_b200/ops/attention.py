@@ -21,6 +21,7 @@ P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
 nv.register("hb_attn_paged", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, Fl, I, Fl, I, P])
 
 nv.register("hb_attn_merge", [P, P, P, L, I, I, P])
+nv.register("hb_attn_merge_quant", [P, P, L, I, I, I, P, P, P, I, P])
 nv.register("hb_attn_decode", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, L, P, P])
 
 nv.register("hb_attn_decode_fuse", [P, P, P, P, I], void=True)
@@ -119,7 +120,7 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     if not fp8 and max_rows * (hq // hkv) <= 16 and d in (64, 128, 256):
         st = nv.device_state(q.device)
         tc = d == 128 and cfg.decode_attn == "tc"
-        fuse = cfg.fuse_epilogues and not tc
+        fuse = cfg.fuse_epilogues and not tc and (cfg.fuse_attn_tail or splits == 1)
         xq = None
         if fuse:
             qb = sfb = None
@@ -143,6 +144,14 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         if xq is not None:
             return xq
         if splits > 1 and not fuse:
+            if quant_scale is not None and cfg.fuse_epilogues:
+                # the merge kernel writes the NVFP4 rows itself: no separate quantisation pass
+                qb, sfb = _quant_bufs(t, hq * d, q.device)
+                nv.check(nv.lib().hb_attn_merge_quant(workspace.part_o.data_ptr(), workspace.part_lse.data_ptr(), t,
+                                                      hq, splits, d, qb.data_ptr(), sfb.data_ptr(),
+                                                      quant_scale.data_ptr(), sfb.shape[1], nv.stream()),
+                         "hb_attn_merge_quant")
+                return nvfp4.Nvfp4Tensor(qb, sfb, quant_scale, t, hq * d)
             nv.check(nv.lib().hb_attn_merge(workspace.part_o.data_ptr(), workspace.part_lse.data_ptr(),
                                             out.data_ptr(), t * hq, splits, d, nv.stream()), "hb_attn_merge")
         return out if quant_scale is None else nvfp4.quantize(out.view(t, hq * d), quant_scale)

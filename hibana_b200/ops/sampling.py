@@ -47,15 +47,29 @@ def argmax(logits: torch.Tensor, bitmask: Optional[torch.Tensor] = None,
     return res
 
 
+def argmax_with_value(logits: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """(index int64 [rows], value fp32 [rows]) of every row's maximum (lowest index on ties): the per-shard half of
+    a vocab-parallel greedy pick."""
+    rows = logits.shape[0]
+    if nv.use_native(logits):
+        out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+        val = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        _argmax2(logits, None, None, out, val)
+        return out, val
+    val, idx = logits.float().max(dim=-1)
+    return idx, val
+
+
 def _argmax2(logits: torch.Tensor, bitmask: Optional[torch.Tensor], temperature: Optional[torch.Tensor],
-             out: torch.Tensor) -> None:
+             out: torch.Tensor, out_val: Optional[torch.Tensor] = None) -> None:
     rows, vocab = logits.shape
     nch = ARGMAX_CHUNKS if vocab >= 8192 else 1
     sv = torch.empty(rows, nch, dtype=torch.float32, device=logits.device)
     si = torch.empty(rows, nch, dtype=torch.int32, device=logits.device)
     nv.check(nv.lib().hb_argmax2(logits.data_ptr(), logits.stride(0), rows, vocab, int(logits.dtype == torch.float32),
                                  nv.ptr(bitmask), bitmask.shape[1] if bitmask is not None else 0, nch, sv.data_ptr(),
-                                 si.data_ptr(), nv.ptr(temperature), out.data_ptr(), None, nv.stream()), "hb_argmax2",
+                                 si.data_ptr(), nv.ptr(temperature), out.data_ptr(), nv.ptr(out_val), nv.stream()),
+             "hb_argmax2",
              launches=2)
 
 

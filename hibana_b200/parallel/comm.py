@@ -31,6 +31,7 @@ nv.register("hb_ar_norm", [P, I, I, I, L, I, I, P, P, Fl, I, P, P, P, P, I, L, P
 nv.register("hb_barrier", [P, I, I, I, L, P, P])
 nv.register("hb_comm_sp_layout", [ctypes.POINTER(ctypes.c_longlong)])
 nv.register("hb_rs_norm_ag", [P, I, I, I, I, L, I, P, P, Fl, I, L, L, L, P, I, L, P, P])
+nv.register("hb_pick_exchange", [P, I, I, I, I, L, P, P, L, P, L, P, P])
 nv.register("hb_gemm_peer", [I, P, P, P, P, I, I, I, P, L, P, I, P, I, I, I, L, L, L, L, L, P, I, I, P])
 
 
@@ -164,6 +165,22 @@ class Communicator:
         parts = [torch.empty_like(x) for _ in range(self.world)]
         dist.all_gather(parts, x.contiguous(), group=self.group)
         return torch.cat(parts, dim=-1)
+
+    PICK_ROWS = 4096      # row capacity of the greedy-pick landing area (16 bytes per row and rank)
+
+    def pick_exchange(self, val: torch.Tensor, idx: torch.Tensor, idx_offset: int,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Vocab-parallel greedy token: `val` / `idx` [rows] are the best logit of this rank's vocabulary shard and
+        its id inside the shard; returns the global id of the best over all ranks (identical on every rank).
+        The landing area is the data region of the reserved barrier slot, which no other collective writes."""
+        rows = val.shape[0]
+        assert rows <= self.PICK_ROWS and self.world * self.PICK_ROWS * 16 <= self.slot_bytes
+        out = torch.empty(rows, dtype=torch.int64, device=self.device) if out is None else out
+        nv.check(nv.lib().hb_pick_exchange(self._bases, self.world, self.rank, rows, self.PICK_ROWS,
+                                           self.slot_offset(self.nslot - 1), val.data_ptr(), idx.data_ptr(),
+                                           idx_offset, out.data_ptr(), self.timeout_ns, self.status.data_ptr(),
+                                           nv.stream()), "hb_pick_exchange")
+        return out
 
     def allreduce_norm(self, slot: int, rows: int, h: int, *, residual: Optional[torch.Tensor],
                        weight: Optional[torch.Tensor], eps: float = 1e-6, gemma: bool = False,

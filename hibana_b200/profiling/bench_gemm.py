@@ -27,6 +27,10 @@ def main() -> None:
     ap.add_argument("--graph", action="store_true",
                     help="time a CUDA-graph replay that cycles through weight copies larger than L2 in total")
     ap.add_argument("--pdl", action="store_true", help="launch GEMMs as programmatic dependents")
+    ap.add_argument("--phases", action="store_true",
+                    help="also print the kernel's phase timers (ns since kernel entry, mean over CTAs)")
+    ap.add_argument("--epi", default="store", choices=["store", "silu", "silu_quant"],
+                    help="epilogue (nvfp4): plain store, SiLU-mul, SiLU-mul + NVFP4 requant in the epilogue")
     args = ap.parse_args()
     gemm.set_pdl(args.pdl)
     peaks = measured_peaks()
@@ -40,8 +44,15 @@ def main() -> None:
             gs = torch.tensor(float(x.float().abs().max()) / (6 * 448), device=dev)
             xq = nvfp4.quantize(x, gs)
             alpha = (gs * wq.gscale).reshape(1)
-            out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-            fn = lambda: gemm.linear_nvfp4(xq, wq, alpha, out=out)  # noqa: E731
+            out = torch.empty(m, n // 2 if args.epi != "store" else n, dtype=torch.bfloat16, device=dev)
+            oscale = torch.tensor(8.0 / (6 * 448), device=dev)
+
+            def run(w_):
+                if args.epi == "silu_quant":
+                    return gemm.linear_nvfp4_silu_quant(xq, w_, alpha, oscale)
+                return gemm.linear_nvfp4(xq, w_, alpha, out=out,
+                                         epilogue=gemm.EPI_SILU_MUL if args.epi == "silu" else gemm.EPI_STORE)
+            fn = lambda: run(wq)  # noqa: E731
             bytes_moved = n * k * 0.5625 + m * k * 0.5625 + m * n * 2
         else:
             out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
@@ -56,7 +67,7 @@ def main() -> None:
             reps = min(max(2, int((300 << 20) / wbytes) + 1), 1024)
             if args.kind == "nvfp4":
                 ws = [nvfp4.Nvfp4Tensor(wq.q.clone(), wq.sf.clone(), wq.gscale, wq.rows, wq.k) for _ in range(reps)]
-                calls = [lambda w_=w_: gemm.linear_nvfp4(xq, w_, alpha, out=out) for w_ in ws]
+                calls = [lambda w_=w_: run(w_) for w_ in ws]
             else:
                 ws = [w.clone() for _ in range(reps)]
                 calls = [lambda w_=w_: gemm.linear_bf16(x, w_, out=out) for w_ in ws]
@@ -71,6 +82,19 @@ def main() -> None:
             t = {"median_ms": t["median_ms"] / reps}
         else:
             t = time_cuda(fn, iters=args.iters)
+        phases = None
+        if args.phases:
+            from .. import _native as nv
+            nv.register("hb_gemm_profile", [nv.P], void=True)
+            buf = torch.zeros(8, dtype=torch.int64, device=dev)
+            nv.lib().hb_gemm_profile(buf.data_ptr())
+            for _ in range(20):      # eager launches: the timer buffer is a launch argument, not part of a graph
+                fn()
+            torch.cuda.synchronize()
+            nv.lib().hb_gemm_profile(None)
+            c = buf.tolist()
+            names = ("setup", "pred_done", "accum_done", "parked", "cluster1", "reduced", "cluster2")
+            phases = {n: round(c[i] / max(c[7], 1)) for i, n in enumerate(names)}
         tl = time_cuda(lambda: torch.matmul(x, w.t()), iters=args.iters)
         flops = 2.0 * m * n * k
         ms = t["median_ms"]
@@ -79,7 +103,7 @@ def main() -> None:
         print(json.dumps({"kind": args.kind, "m": m, "n": n, "k": k, "ms": round(ms, 4),
                           "tflops": round(flops / ms / 1e9, 1), "gbs": round(bytes_moved / ms / 1e6, 1),
                           "roofline_frac": round(roof_ms / ms, 3), "cublas_bf16_ms": round(tl["median_ms"], 4),
-                          "peaks": peaks["source"]}))
+                          "peaks": peaks["source"], **({"phase_ns": phases} if phases else {})}))
 
 
 if __name__ == "__main__":

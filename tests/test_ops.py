@@ -257,7 +257,8 @@ def test_tcgen05_prefill_attention(hq, hkv, d, contiguous):
 @pytest.mark.gpu
 @pytest.mark.parametrize("hq,hkv,d,rows", [(40, 8, 128, [1, 1, 1, 1]), (40, 8, 128, [3, 1, 2, 3]), (4, 2, 64, [2, 1, 1, 2])])
 @pytest.mark.parametrize("splits", [1, 2, 5])
-def test_decode_attention_fused_merge_and_quant(hq, hkv, d, rows, splits):
+@pytest.mark.parametrize("in_kernel", [True, False])
+def test_decode_attention_fused_merge_and_quant(hq, hkv, d, rows, splits, in_kernel):
     """In-kernel split merge (last-arriving CTA) and NVFP4 output of the decode kernel: the merged rows match the
     separate merge kernel's, the NVFP4 rows equal quantising the kernel's bf16 rows afterwards byte for byte, twice in a row
     (the arrival counters re-arm themselves), and both stay close to the fp32 reference."""
@@ -274,10 +275,12 @@ def test_decode_attention_fused_merge_and_quant(hq, hkv, d, rows, splits):
     gs = torch.tensor(2.0 / (6 * 448), device="cuda")
     ws = attention.AttnWorkspace(q.shape[0], hq, d, splits, torch.device("cuda")) if splits > 1 else None
     for _ in range(2):
-        fused = attention.paged_attention(*args, workspace=ws, **kw)
-        _close(fused, plain, 8e-3)          # same sums, possibly contracted differently
-        want = nvfp4.quantize(fused.view(fused.shape[0], -1), gs)
-        xq = attention.paged_attention(*args, workspace=ws, quant_scale=gs, **kw)
+        # in_kernel: the last-arriving split CTA merges and quantises; else the merge kernel writes the NVFP4 rows
+        with cfgmod.using(fuse_attn_tail=in_kernel):
+            fused = attention.paged_attention(*args, workspace=ws, **kw)
+            _close(fused, plain, 8e-3)          # same sums, possibly contracted differently
+            want = nvfp4.quantize(fused.view(fused.shape[0], -1), gs)
+            xq = attention.paged_attention(*args, workspace=ws, quant_scale=gs, **kw)
         assert torch.equal(xq.q, want.q)
         groups = hq * d // 16
         assert torch.equal(nvfp4.unswizzle_sf(xq.sf, xq.rows, groups), nvfp4.unswizzle_sf(want.sf, want.rows, groups))

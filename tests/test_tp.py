@@ -105,7 +105,7 @@ import os, sys, json, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["HB_ROOT"])
 from hibana_b200 import _native as nv
 from hibana_b200.engine.executor import Executor
-from hibana_b200.engine.request import SamplingParams
+from hibana_b200.engine.request import Request, SamplingParams
 from hibana_b200.models.dense import DenseModel
 from hibana_b200.parallel.comm import Communicator
 from hibana_b200.target import dense_tiny
@@ -118,11 +118,29 @@ g = torch.Generator().manual_seed(5)
 prompts = [torch.randint(0, t.vocab, (40,), generator=g).tolist() for _ in range(3)]
 long_prompt = [torch.randint(0, t.vocab, (256,), generator=g).tolist()]
 res = {}
-for name, fused, sp in (("nccl", False, 0), ("fused", True, 0), ("sp", True, 256)):
+
+def prefill_logits(ex, prompt):
+    r = Request(prompt_ids=list(prompt), params=SamplingParams(max_tokens=1))
+    ex.admit(r)
+    slots = ex._alloc(r, len(prompt))
+    lg, _ = ex.runner.forward_rows([r.table_row], [list(prompt)], [0], [slots], want="logits_device")
+    return lg.float().cpu()
+
+for name, fused, sp in (("nccl", False, 0), ("fused", True, 0), ("gather", True, 0), ("sp", True, 256)):
     comm = Communicator.create(rank, world, dev, slot_mb=4, fused=fused, sp_rows=sp, sp_hidden=t.hidden)
     model = DenseModel.sharded(t, world, rank, dev, seed=0, init_device="cpu")
     ex = Executor(model, max_batch=4, max_ctx=512, use_graphs=True, comm=comm, radix_cache=False)
+    if name == "gather":        # greedy tokens through the gathered logits instead of the (value, id) exchange
+        ex.runner._split_head = lambda: False
     ex.capture_graphs()
+    if name == "fused":
+        res["greedy_graph"] = ex.runner.bufs[ex.runner.buckets[0]].graph_greedy is not None
+        lg2 = prefill_logits(ex, prompts[0])
+        one = DenseModel(t, dev, seed=0, init_device="cpu")
+        ex1 = Executor(one, max_batch=2, max_ctx=512, use_graphs=False, radix_cache=False)
+        lg1 = prefill_logits(ex1, prompts[0])
+        res["logit_err"] = float((lg2 - lg1).abs().max() / lg1.abs().max())
+        res["argmax_same"] = float((lg2.argmax(-1) == lg1.argmax(-1)).float().mean())
     out = ex.generate_batch(prompts, SamplingParams(max_tokens=8))
     out2 = ex.generate_batch(long_prompt, SamplingParams(max_tokens=4), prefill_budget=256)
     torch.cuda.synchronize()
@@ -159,6 +177,10 @@ def test_tp2_fused_allreduce_matches_nccl_gpu(tmp_path):
     assert [x[0] for x in nccl] == [x[0] for x in fused]        # same first tokens; later ones may flip on ties
     same = sum(a == b for x, y in zip(nccl, fused) for a, b in zip(x, y))
     assert same >= 0.6 * 24
+    # the per-rank argmax + (value, id) exchange picks exactly what the argmax over gathered logits picks
+    assert ranks[0]["greedy_graph"] and ranks[0]["gather"] == fused
+    # logits of the sharded model against the unsharded one on the same prompt (different summation order only)
+    assert ranks[0]["logit_err"] < 0.05 and ranks[0]["argmax_same"] > 0.9, (ranks[0]["logit_err"], ranks[0]["argmax_same"])
     # the sequence-parallel chain (GEMM -> reduce-scatter, norm, all-gather -> GEMM) prefilled the 256-token prompt
     assert ranks[0]["sp_long"] == ranks[1]["sp_long"]
     assert ranks[0]["sp_long"][0][0] == ranks[0]["nccl_long"][0][0]
