@@ -20,6 +20,8 @@ from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
 from ..engine.loop import EngineLoop, EngineUnavailable, Ticket
 from ..engine.scheduler import QueueFull
+from . import media as media_api
+from . import refusal_guard
 from .chat_template import ChatTemplate
 from .detok import IncrementalDetok
 from .messages import EventWriter, message_response, stop_reason, to_chat_messages
@@ -67,8 +69,13 @@ def create_app(engine: EngineLoop, tokenizer, *, model_name: str = "hibana-b200"
             _gr["g"] = grammars_for(tokenizer, getattr(engine, "vocab", None) or tokenizer.vocab_size)
         return _gr["g"]
 
-    def _submit(prompt_ids, params) -> Ticket:
-        return engine.submit(prompt_ids, params, eos_id=eos_id)
+    def _submit(prompt_ids, params, media=None) -> Ticket:
+        return engine.submit(prompt_ids, params, eos_id=eos_id, media=media)
+
+    def _vision():
+        """The served model's vision encoder (None: the target takes no images)."""
+        ex = getattr(getattr(engine, "sched", None), "ex", None)
+        return getattr(getattr(ex, "model", None), "vision", None)
 
     def _guard(fn):
         async def wrapped(req: HttpRequest):
@@ -225,9 +232,43 @@ def create_app(engine: EngineLoop, tokenizer, *, model_name: str = "hibana-b200"
 
     # ---- OpenAI chat
     def _render(body, messages, tools):
+        """(prompt ids, template kwargs, media plan or None). Image parts become placeholder ids when the target has
+        a vision encoder, a short note otherwise."""
         kwargs = dict(body.get("chat_template_kwargs") or {})
+        plan = None
+        if media_api.has_images(messages):
+            vision = _vision()
+            if vision is None:
+                messages = media_api.strip_images(messages)
+            else:
+                messages, plan = media_api.prepare(messages)
         text = template.render(messages, tools=tools, add_generation_prompt=True, **kwargs)
-        return tokenizer.encode(text), kwargs
+        if plan is not None and plan.images:
+            return media_api.expand(text, tokenizer, plan, _vision().cfg.tokens_per_image), kwargs, plan
+        return tokenizer.encode(media_api.unescape(text)), kwargs, None
+
+    def _guarded(body, messages):
+        """Refusal guard: ("generate" | "stop", messages (with a reminder appended on a nudge), canned text)."""
+        verdict, found = refusal_guard.decide(messages, body)
+        if verdict == "nudge":
+            return "generate", messages + [refusal_guard.reminder(found)], None
+        if verdict == "stop":
+            return "stop", messages, refusal_guard.stop_text(found)
+        return "generate", messages, None
+
+    def _logprob_entries(ticket, out_ids):
+        """OpenAI `logprobs.content` entries for the sampled tokens (the engine records them per token when the
+        request asked for them)."""
+        lps = getattr(ticket.request, "token_logprobs", None) or []
+        entries = []
+        for i, tid in enumerate(out_ids):
+            rec = lps[i] if i < len(lps) else None
+            tok = tokenizer.decode([tid])
+            e = {"token": tok, "logprob": rec[0] if rec else None, "bytes": list(tok.encode("utf-8"))}
+            e["top_logprobs"] = [{"token": tokenizer.decode([t]), "logprob": lp, "bytes": list(tokenizer.decode([t]).encode("utf-8"))}
+                                 for t, lp in (rec[1] if rec else [])]
+            entries.append(e)
+        return entries
 
     def _split(text: str, thinking: bool):
         rp = ReasoningParser(starts_in_reasoning=False)
@@ -240,15 +281,31 @@ def create_app(engine: EngineLoop, tokenizer, *, model_name: str = "hibana-b200"
         messages = body.get("messages")
         if not isinstance(messages, list) or not messages:
             raise BadRequest("messages required")
+        if body.get("logprobs") is True:             # OpenAI chat form: logprobs: true + top_logprobs: k
+            body = dict(body, logprobs=max(int(body.get("top_logprobs") or 0), 1))
         params = sampling_from(body, tokenizer, grammars=grammars)
         tools = body.get("tools")
-        ids, kwargs = _render(body, messages, tools)
+        verdict, messages, canned = _guarded(body, messages)
+        cid = "chatcmpl-" + uuid.uuid4().hex[:24]
+        created = int(time.time())
+        if verdict == "stop":      # the harness refused the same call again and again: answer without generating
+            if body.get("stream"):
+                async def stopped():
+                    chunk = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model_name,
+                             "choices": [{"index": 0, "delta": {"role": "assistant", "content": canned},
+                                          "finish_reason": "stop"}]}
+                    yield f"data: {json.dumps(chunk)}\n\n"
+                    yield "data: [DONE]\n\n"
+                return StreamingResponse(stopped(), media_type="text/event-stream")
+            return {"id": cid, "object": "chat.completion", "created": created, "model": model_name,
+                    "choices": [{"index": 0, "message": {"role": "assistant", "content": canned},
+                                 "finish_reason": "stop"}],
+                    "usage": {"prompt_tokens": 0, "completion_tokens": 0, "total_tokens": 0}}
+        ids, kwargs, plan = _render(body, messages, tools)
         n = int(body.get("n", 1))
         if n < 1 or n > 16:
             raise BadRequest("n out of range")
-        cid = "chatcmpl-" + uuid.uuid4().hex[:24]
-        tickets = [_submit(ids, params) for _ in range(n)]
-        created = int(time.time())
+        tickets = [_submit(ids, params, plan) for _ in range(n)]
         if body.get("stream"):
             async def gen():
                 for i, t in enumerate(tickets):
@@ -300,7 +357,10 @@ def create_app(engine: EngineLoop, tokenizer, *, model_name: str = "hibana-b200"
             if calls:
                 msg["tool_calls"] = calls
                 finish = "tool_calls"
-            choices.append({"index": i, "message": msg, "finish_reason": finish})
+            choice = {"index": i, "message": msg, "finish_reason": finish}
+            if params.logprobs:
+                choice["logprobs"] = {"content": _logprob_entries(t, _strip_stop(out, params))}
+            choices.append(choice)
         return {"id": cid, "object": "chat.completion", "created": created, "model": model_name, "choices": choices,
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": total, "total_tokens": len(ids) + total}}
     app.post("/v1/chat/completions")(_guard(chat))
@@ -308,7 +368,7 @@ def create_app(engine: EngineLoop, tokenizer, *, model_name: str = "hibana-b200"
     # ---- Anthropic messages
     async def count_tokens(req, body):
         messages, tools = to_chat_messages(body)
-        ids, _ = _render(body, messages, tools)
+        ids, _, _ = _render(body, messages, tools)
         return {"input_tokens": len(ids)}
     app.post("/v1/messages/count_tokens")(_guard(count_tokens))
 
@@ -322,8 +382,18 @@ def create_app(engine: EngineLoop, tokenizer, *, model_name: str = "hibana-b200"
         if "stop_sequences" in body:
             b2["stop"] = body["stop_sequences"]
         params = sampling_from(b2, tokenizer, grammars=grammars)
-        ids, _ = _render(body, messages, tools)
-        ticket = _submit(ids, params)
+        verdict, messages, canned = _guarded(body, messages)
+        if verdict == "stop":
+            if body.get("stream"):
+                async def stopped():
+                    ew = EventWriter(model_name, 0)
+                    yield ew.start()
+                    yield ew.delta("text", canned)
+                    yield ew.finish("end_turn", 0)
+                return StreamingResponse(stopped(), media_type="text/event-stream")
+            return message_response(model_name, canned, "", [], "end_turn", {"input_tokens": 0, "output_tokens": 0})
+        ids, _, plan = _render(body, messages, tools)
+        ticket = _submit(ids, params, plan)
         if body.get("stream"):
             async def gen():
                 ew, detok, rp, full, n = EventWriter(model_name, len(ids)), IncrementalDetok(tokenizer), \

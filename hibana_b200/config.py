@@ -35,6 +35,7 @@ class EngineConfig:
     nvls: bool = True                      # use multimem (NVLS) where the multicast object can be created
     comm_timeout_ms: int = 2000            # bound of every device-side wait on a peer
     comm_buffer_mb: int = 64
+    control_timeout_s: int = 30            # host control plane: broadcast timeout and peer-heartbeat limit
     # scheduler
     prefill_chunk: int = 0                 # 0 = target default
     prefill_budget: int = 4096
@@ -78,6 +79,8 @@ class EngineConfig:
     prefill_attn: str = "tc"               # tc | general
     gdn_phase1: str = "cuda"               # cuda | torch
     ssd_phase1: str = "cuda"               # cuda | torch
+    gemm_local_reduce: bool = True         # unsplit decode tiles: epilogue through the parked partial (wide stores)
+    attn_ctas_per_sm: int = 2              # resident decode-attention CTAs per SM assumed when choosing KV splits
     max_splits: int = 8                    # split-K cluster size cap (8 = portable)
     pdl: int = 1                           # programmatic dependent launch level (0 off, 1 GEMMs, 2 small kernels too)
     # observability

@@ -110,6 +110,7 @@ struct DevParams {
   int q_ka;
   long long q_ld;
   unsigned long long* prof;   // optional phase timers (hb_gemm_profile), null = off
+  int local_reduce;           // unsplit tiles with the weights on the 128-row side go through the parked-partial path
 };
 
 // Phase timers of one epilogue thread per CTA, summed over CTAs: nanoseconds since kernel entry at
@@ -120,7 +121,8 @@ __device__ __forceinline__ void prof_mark(const DevParams& p, int slot, unsigned
     atomicAdd(p.prof + slot, slot == 7 ? 1ull : static_cast<unsigned long long>(globaltimer_ns() - t0));
 }
 
-__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+// x * sigmoid(x) with the approximate divide (two special-function ops): the result is rounded to bf16 anyway
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
 // kEpiSiluMulQuant, second half: `stg` holds bf16 [ntok][64] SiLU-mul outputs of feature tile `tile_a` (64 output
 // features) for tokens tok0 .. tok0 + ntok. The 128 epilogue threads (et = 0..127) quantise one 16-element group
@@ -374,7 +376,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     tile_b = 0;
   }
   // unsplit, ungrouped tiles with the weights on the 128-row side reduce "over one partial" (see below)
-  const bool local_reduce = p.splits == 1 && p.swap && p.grp_cnt == nullptr && p.epilogue != kEpiReturn;
+  const bool local_reduce = p.splits == 1 && p.swap && p.grp_cnt == nullptr && p.epilogue != kEpiReturn &&
+                            (p.local_reduce || p.epilogue == kEpiSiluMulQuant);
   const int kt_per = (p.k_tiles + p.splits - 1) / p.splits;
   const int kt0 = split * kt_per;
   const int kt1 = min(kt0 + kt_per, p.k_tiles);
@@ -747,6 +750,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         uint32_t base[8];
 #pragma unroll
         for (int s = 0; s < 8; ++s) base[s] = s < p.splits ? map_to_cta(part_local, static_cast<uint32_t>(s)) : part_local;
+        if (p.splits == 1) {
+          // one partial, this CTA's own: plain shared-memory loads (no cluster addressing), four columns in flight
+          const float* part = reinterpret_cast<const float*>(smem);
+          for (int c = c_begin + cg; c < c_end; c += 16) {
+            float4 v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (c + 4 * i < c_end) v[i] = *reinterpret_cast<const float4*>(part + (c + 4 * i) * BM + lrow0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (c + 4 * i < c_end)
+                epilogue_rows4(p, v[i], grow0, row_lim, b_row0 + c + 4 * i, alpha,
+                               stg + (c + 4 * i - c_begin) * 64 + (lrow0 >> 1));
+          }
+        } else
         for (int c = c_begin + cg; c < c_end; c += 8) {
           const bool two = c + 4 < c_end;
           float4 a[8], b[8];
@@ -826,6 +844,7 @@ std::mutex g_tmap_mu;
 std::unordered_map<TmapKey, std::unique_ptr<CUtensorMap>, KeyHash> g_tmaps;
 
 unsigned long long* g_gemm_prof = nullptr;
+int g_local_reduce = 1;
 int g_pdl = 0;   // launch with programmatic stream serialisation (set through hb_gemm_set_pdl)
 
 template <int KIND, int BN>
@@ -1004,6 +1023,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   p.q_out = static_cast<uint8_t*>(a.q_out); p.q_sf = static_cast<uint8_t*>(a.q_sf); p.q_gscale = a.q_gscale;
   p.q_ka = a.q_ka; p.q_ld = a.q_ld;
   p.prof = g_gemm_prof;
+  p.local_reduce = g_local_reduce;
   if (a.epilogue == kEpiSiluMulQuant) {
     // tokens on the N side, whole 128-row feature tiles, no grouped / peer variants; the staging tile of a split-K
     // CTA sits behind its fp32 partial, which the smallest ring must still hold
@@ -1220,6 +1240,10 @@ int hb_gemm_w3(const void* tiles, const void* x, int n, int m, int k, long long 
 
 // Phase timers (see prof_mark): `buf` = 8 zeroed uint64 on the device, null switches them off.
 void hb_gemm_profile(void* buf) { hb::g_gemm_prof = static_cast<unsigned long long*>(buf); }
+
+// Unsplit tiles with the weights on the 128-row side: 1 = epilogue through the parked [column][row] partial (wide
+// stores, thread-local gate / up pairs), 0 = straight from the accumulator (one thread per row).
+void hb_gemm_set_local_reduce(int on) { hb::g_local_reduce = on != 0; }
 
 void hb_clear_tmap_cache(void) { hb::clear_tmap_cache(); }
 

@@ -85,7 +85,8 @@ class Executor:
             raise ValueError("empty prompt")
         if req.total_len + req.params.max_tokens > self.max_ctx:
             raise ValueError(f"prompt + max_tokens exceeds the context limit {self.max_ctx}")
-        if any(i < 0 or i >= self.target.vocab for i in req.prompt_ids):
+        has_media = bool(getattr(req.media, "images", None))
+        if any(i >= self.target.vocab or (i < 0 and not has_media) for i in req.prompt_ids):
             raise ValueError("token id out of range")
 
     def can_admit(self, req: Request) -> bool:
@@ -246,13 +247,28 @@ class Executor:
             finals.append(req.prefilled + count >= target_len)
         any_final = any(finals)
         extras = {"want_hidden": True} if self.spec is not None else None
+        if any(getattr(r.media, "images", None) for r, _ in chunks):
+            # image placeholders inside this step's chunks take the vision encoder's rows (encoded once per image)
+            from .media import VisionCache, chunk_embeddings
+            if getattr(self, "_vision_cache", None) is None:
+                if getattr(self.model, "vision", None) is None:
+                    raise ValueError("this target has no vision encoder")
+                self._vision_cache = VisionCache(self.model.vision)
+            rows_img = [chunk_embeddings(r.media, starts[i], len(toks[i]), self._vision_cache)
+                        for i, (r, _) in enumerate(chunks) if getattr(r.media, "images", None)]
+            rows_img = [x for x in rows_img if x is not None]
+            if rows_img:
+                extras = dict(extras or {})
+                extras["image_embeds"] = torch.cat(rows_img, 0)
         masks = None
         if any_final and any(r.grammar is not None for r, _ in chunks):
             from .grammar import stack_masks
             masks = stack_masks([r.grammar.mask() if r.grammar is not None and not r.output_ids else None
                                  for r, _ in chunks], (self.target.vocab + 31) // 32)
+        lps = [r.params.logprobs if f and not r.output_ids else 0 for (r, _), f in zip(chunks, finals)]
         out = self.runner.forward_rows(rows, toks, starts, slot_lists, mode=PREFILL,
                                        want="last" if any_final else "none", extras=extras, masks=masks,
+                                       logprobs=lps if any(lps) else None,
                                        sampling_rows=_sampling_rows([r for r, _ in chunks]) if any_final else None,
                                        state_slots=[r.state_slot for r, _ in chunks]
                                        if self.state_pool is not None else None)
@@ -272,6 +288,8 @@ class Executor:
                 req.state = State.RUNNING
                 if not req.output_ids:      # a replayed request already holds its pending token
                     req.draws += 1
+                    if self.runner.last_logprobs and i in self.runner.last_logprobs:
+                        req.token_logprobs.append(self.runner.last_logprobs[i])
                     req.push(out[i])
         self.stats["prefill_chunks"] += 1
 
@@ -287,12 +305,17 @@ class Executor:
         tokens = [r.output_ids[-1] for r in reqs]
         positions = [r.total_len - 1 for r in reqs]
         masks = [r.grammar.mask() if r.grammar is not None else None for r in reqs]
+        lps = [r.params.logprobs for r in reqs]
         out = self.runner.decode(rows, tokens, positions, slots, _sampling_rows(reqs),
                                  [r.state_slot for r in reqs] if self.state_pool is not None else None,
-                                 masks if any(m is not None for m in masks) else None)
-        for r, tok in zip(reqs, out):
+                                 masks if any(m is not None for m in masks) else None,
+                                 logprobs=lps if any(lps) else None)
+        got = self.runner.last_logprobs or {}
+        for i, (r, tok) in enumerate(zip(reqs, out)):
             self.state.commit(r, 1)
             r.draws += 1
+            if i in got:
+                r.token_logprobs.append(got[i])
             r.push(tok)
         self.stats["decode_steps"] += 1
         self.stats["decode_tokens"] += len(reqs)

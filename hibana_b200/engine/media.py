@@ -61,3 +61,52 @@ def splice_embeddings(ids: torch.Tensor, embeds: torch.Tensor, image_embeds: tor
     out = embeds.clone()
     out[mask] = image_embeds.to(embeds.dtype)
     return out
+
+
+def decode_pixels(image: Image, size: int) -> torch.Tensor:
+    """Encoded bytes (PNG / JPEG / anything Pillow reads) -> [3, size, size] float pixels, resized and normalised to
+    mean 0.5 / std 0.5. Cached on the image."""
+    if image.pixels is not None and image.pixels.shape[-1] == size:
+        return image.pixels
+    import io
+
+    import numpy as np
+    from PIL import Image as PilImage
+    try:
+        pic = PilImage.open(io.BytesIO(image.data)).convert("RGB").resize((size, size), PilImage.BICUBIC)
+    except Exception as e:  # noqa: BLE001
+        raise ValueError(f"image does not decode: {e}") from None
+    arr = torch.from_numpy(np.asarray(pic, dtype=np.float32) / 255.0).permute(2, 0, 1)
+    image.pixels = (arr - 0.5) / 0.5
+    return image.pixels
+
+
+class VisionCache:
+    """Encoder outputs by image content (a conversation sends the same image again with every turn, and a long
+    prefill touches an image's span in several chunks); least recently used entries go first."""
+
+    def __init__(self, encoder, capacity: int = 64):
+        self.encoder, self.capacity = encoder, capacity
+        self.rows: dict = {}
+
+    def embeddings(self, image: Image) -> torch.Tensor:
+        key = hashlib.sha256(image.data).digest()
+        hit = self.rows.pop(key, None)
+        if hit is None:
+            px = decode_pixels(image, self.encoder.cfg.image)
+            hit = self.encoder.encode(px[None])
+            while len(self.rows) >= self.capacity:
+                self.rows.pop(next(iter(self.rows)))
+        self.rows[key] = hit
+        return hit
+
+
+def chunk_embeddings(plan, start: int, count: int, cache: VisionCache) -> Optional[torch.Tensor]:
+    """Image-embedding rows for the placeholder positions inside prompt positions [start, start + count), in
+    order (None when the chunk holds none). `plan` is an api/media.MediaPlan (images + spans)."""
+    rows = []
+    for img, (pos, n) in zip(plan.images, plan.spans):
+        lo, hi = max(pos, start), min(pos + n, start + count)
+        if lo < hi:
+            rows.append(cache.embeddings(img)[lo - pos:hi - pos])
+    return torch.cat(rows, 0) if rows else None

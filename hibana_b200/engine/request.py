@@ -89,6 +89,7 @@ class Request(RequestState):
     draws: int = 0                                   # RNG offset: number of sampling draws consumed
     stream_cursor: int = 0
     rounds: list = field(default_factory=list)       # per speculative round accepted counts (traces)
+    token_logprobs: list = field(default_factory=list)   # per emitted token (logprob, [(token, logprob)]) when asked for
 
     @property
     def all_ids(self) -> list:

@@ -128,6 +128,7 @@ class ModelRunner:
             buf.out.copy_(self.model.greedy_tokens(h, self.comm))
             return
         logits = self.model.logits(h, self.comm) if self.comm is not None else self.model.logits(h)
+        buf.logits = logits          # stable inside a captured graph: read back only for requests that want logprobs
         tok = sampling.sample(logits, v["temp"], v["top_k"], v["top_p"], v["seed"], v["offs"], bitmask=buf.mask)
         buf.out.copy_(tok)
 
@@ -193,9 +194,11 @@ class ModelRunner:
 
     def decode(self, rows: Sequence[int], tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int],
                sampling_rows: Optional[dict] = None, state_slots: Optional[Sequence[int]] = None,
-               masks: Optional[Sequence] = None) -> list[int]:
+               masks: Optional[Sequence] = None, logprobs: Optional[Sequence[int]] = None) -> list[int]:
         """One decode step for len(rows) sequences; returns the sampled token of each (host ints).
         `masks[i]` (host int32 [ceil(vocab / 32)] or None) restricts sequence i's token to a grammar.
+        `logprobs[i]` > 0 asks for the log-probability of sequence i's token and its top-k alternatives; they are
+        left in `self.last_logprobs[i]` = (logprob, [(token, logprob), ...]).
 
         sampling_rows: optional dict of per-sequence lists temp / top_k / top_p / seed / offs (greedy when None).
         """
@@ -231,7 +234,8 @@ class ModelRunner:
                     buf.mask[i].copy_(m, non_blocking=True)
                     buf.mask_dirty.append(i)
                     self.h2d_bytes += m.numel() * 4
-        greedy = sampling_rows is None and masks is None and self._split_head()
+        want_lp = logprobs is not None and any(logprobs)
+        greedy = sampling_rows is None and masks is None and self._split_head() and not want_lp
         if greedy and buf.graph_greedy is not None:
             buf.graph_greedy.replay()
         elif buf.graph is not None:
@@ -244,14 +248,29 @@ class ModelRunner:
             torch.cuda.current_stream().synchronize()
         self.d2h_bytes += buf.bucket * 8 + (4 if self._status_dev is not None else 0)
         self._raise_on_status()
+        self.last_logprobs = self._logprobs(buf.logits, buf.out, logprobs, n) if want_lp else None
         return buf.out_host[:n].tolist()
+
+    last_logprobs = None
+
+    def _logprobs(self, logits: torch.Tensor, tokens: torch.Tensor, ks: Sequence[int], n: int) -> dict:
+        """{row: (logprob of its token, [(token, logprob)] of its ks[row] most likely tokens)} for rows with k > 0."""
+        idx = [i for i in range(n) if ks[i]]
+        sel = torch.tensor(idx, dtype=torch.long, device=logits.device)
+        lp = torch.log_softmax(logits.index_select(0, sel).float(), dim=-1)
+        chosen = lp.gather(1, tokens.index_select(0, sel).view(-1, 1)).squeeze(1).tolist()
+        kmax = min(max(ks[i] for i in idx), lp.shape[1])
+        topv, topi = lp.topk(kmax, dim=-1)
+        topv, topi = topv.tolist(), topi.tolist()
+        return {i: (chosen[j], list(zip(topi[j][:ks[i]], topv[j][:ks[i]]))) for j, i in enumerate(idx)}
 
     # ---- prefill / verify (eager, ragged)
     def forward_rows(self, rows: Sequence[int], token_lists: Sequence[Sequence[int]], starts: Sequence[int],
                      slot_lists: Sequence[Sequence[int]], *, mode: str = PREFILL, want: str = "last",
                      sampling_rows: Optional[dict] = None, state_slots: Optional[Sequence[int]] = None,
                      has_initial_state: Optional[Sequence[int]] = None, checkpoints=None,
-                     extras: Optional[dict] = None, masks: Optional[torch.Tensor] = None):
+                     extras: Optional[dict] = None, masks: Optional[torch.Tensor] = None,
+                     logprobs: Optional[Sequence[int]] = None):
         """Runs new tokens of several sequences in one ragged forward.
 
         rows[i] is the block-table row, token_lists[i] the new tokens starting at position starts[i] with KV slots
@@ -315,6 +334,8 @@ class ModelRunner:
                 ((k, sampling_rows[k]) for k in ("temp", "top_k", "top_p", "seed", "offs")),
                 (torch.float32, torch.int32, torch.float32, torch.int64, torch.int64))}
             tok = sampling.sample(logits, sr["temp"], sr["top_k"], sr["top_p"], sr["seed"], sr["offs"], bitmask=masks)
+        self.last_logprobs = (self._logprobs(logits, tok, logprobs, b)
+                              if want == "last" and logprobs is not None and any(logprobs) else None)
         self._queue_status_read()
         out = tok.cpu()         # synchronises the stream: the status word queued before it has landed too
         self.d2h_bytes += out.numel() * 8 + (4 if self._status_dev is not None else 0)

@@ -30,16 +30,24 @@ class Block:
 
 
 class HybridModel:
-    def __init__(self, t: Target, device="cpu", seed: int = 0, init_device=None, ep_rank: int = 0, ep_size: int = 1):
+    def __init__(self, t: Target, device="cpu", seed: int = 0, init_device=None, ep_rank: int = 0, ep_size: int = 1,
+                 full: Optional[Target] = None):
+        """`t` is this rank's geometry (`Target.shard`), `full` the unsharded target the weights are drawn from
+        (same seeded stream on every rank; a rank keeps its heads / columns / experts)."""
         self.target = t
+        self.full = full = full or t
         self.device = torch.device(device)
-        init = Init(seed, self.device, init_device)
+        init = Init(seed, self.device, init_device, tp=t.tp_size, rank=t.tp_rank, full=full)
         self.embed = init.normal(t.vocab, t.hidden).to(torch.bfloat16).to(self.device)
         counters = {"kv": 0, "state": 0}
         self.blocks = [Block(t, init, i, m, f, counters, ep_rank, ep_size) for i, (m, f) in enumerate(t.layers)]
         self.final_norm = init.ones(t.hidden, t.gemma_norm)
-        self.lm_head = self.embed if t.tie_embeddings else init.normal(t.vocab, t.hidden).to(torch.bfloat16).to(
-            self.device)
+        head = self.embed if t.tie_embeddings else init.normal(t.vocab, t.hidden).to(torch.bfloat16).to(self.device)
+        # vocab-parallel head under tensor parallelism: each rank scores vocab / tp tokens
+        tp, rank = t.tp_size, t.tp_rank
+        self.vocab_shard = t.vocab // tp if tp > 1 and t.vocab % tp == 0 else 0
+        self.lm_head = head[rank * self.vocab_shard:(rank + 1) * self.vocab_shard].contiguous() \
+            if self.vocab_shard else head
         self.kv_layers, self.state_layers = counters["kv"], counters["state"]
         self.ep_size = ep_size
         # Hyper-connections: one site in front of every sublayer (its gated mix of the residual streams is the
@@ -61,6 +69,41 @@ class HybridModel:
         if t.mtp_layers:
             from .mtp import MtpHead
             self.mtp = MtpHead(t, init, self)
+        # vision encoder (targets that take images): built on first use, replicated on every rank
+        self.vision_cfg = None
+        self._vision = None
+        self._seed = seed
+        if t.vision:
+            from .vision import VisionConfig
+            image, patch, width, depth, heads, mlp = t.vision
+            self.vision_cfg = VisionConfig(image=image, patch=patch, width=width, depth=depth, heads=heads, mlp=mlp,
+                                           out_hidden=t.hidden)
+
+    @property
+    def vision(self):
+        """The vision encoder, or None for a text-only target (reference: hibana/model/nemotron/vision.py:91)."""
+        if self.vision_cfg is not None and self._vision is None:
+            from .vision import VisionEncoder
+            self._vision = VisionEncoder(self.vision_cfg, self.device, seed=self._seed + 7)
+        return self._vision
+
+    def embed_tokens(self, ids: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
+        """Token embeddings; rows at negative ids (image placeholders) take the vision encoder's rows handed over
+        in ctx.extras["image_embeds"], in order."""
+        img = ctx.extras.get("image_embeds") if ctx.extras else None
+        if img is None:
+            return basic.embedding(ids, self.embed)
+        from ..engine.media import splice_embeddings
+        return splice_embeddings(ids, basic.embedding(ids.clamp_min(0), self.embed), img.to(self.device))
+
+    @classmethod
+    def sharded(cls, full: Target, tp: int, rank: int, device, seed: int = 0, init_device=None) -> "HybridModel":
+        """Tensor-parallel shard: mixers split by head, dense / shared MLPs by column, routed experts by expert
+        range over the same ranks (activations are replicated, so the experts need no all-to-all), vocabulary
+        split for the head. Reference: hibana/weights/sharding.py:31-88, hibana/model/flashnext/model.py:70-73."""
+        ep = tp if full.experts and full.experts % tp == 0 else 1
+        return cls(full.shard(tp, rank), device, seed, init_device, ep_rank=rank if ep > 1 else 0, ep_size=ep,
+                   full=full)
 
     # ---- bookkeeping
     def linears(self):
@@ -101,14 +144,19 @@ class HybridModel:
         t = self.target
         if self.hyper_sites is not None:
             return self._hidden_states_hyper(ids, ctx, kv, states)
-        res = basic.embedding(ids, self.embed)
+        res = self.embed_tokens(ids, ctx)
         h: Optional[torch.Tensor] = None
+        partial = False          # h is this rank's partial sum (tensor parallel): reduced with the next norm
         for blk in self.blocks:
             for norm_w, sub in blk.sublayers():
                 if sub is None:
                     continue
-                x = basic.rmsnorm(res if h is None else h, norm_w, t.norm_eps,
-                                  residual=None if h is None else res, gemma=t.gemma_norm)
+                if partial:
+                    x = self._reduce_norm(h, res, norm_w, ctx)
+                else:
+                    x = basic.rmsnorm(res if h is None else h, norm_w, t.norm_eps,
+                                      residual=None if h is None else res, gemma=t.gemma_norm)
+                partial = bool(getattr(sub, "partial", False)) and ctx.comm is not None
                 if isinstance(sub, MoeLayer) and ctx.extras.get("ep") is not None:
                     # data-parallel attention + expert-parallel experts: this rank's own tokens travel to the
                     # owners of their experts and back (parallel/ep.py); every rank runs every layer each step
@@ -117,21 +165,40 @@ class HybridModel:
                     h = sub.forward_ep(x, ctx.comm)
                 else:
                     h = sub.forward(x, ctx, kv, states)
+        if partial:
+            h = ctx.comm.all_reduce(h)
         return h, res
+
+    def _reduce_norm(self, h, res, norm_w, ctx):
+        """rmsnorm(all_reduce(h) + res) with `res` updated in place: one fused peer-memory kernel when the
+        communicator has one and the message fits its slot, else NCCL all-reduce + the local norm."""
+        t = self.target
+        comm = ctx.comm
+        rows = h.shape[0]
+        if getattr(comm, "fused", False) and comm.fits(rows, t.hidden):
+            slot = comm.next_slot()
+            comm.slot_buffer(slot, rows, t.hidden).copy_(h)
+            y, _ = comm.allreduce_norm(slot, rows, t.hidden, residual=res, weight=norm_w, eps=t.norm_eps,
+                                       gemma=t.gemma_norm)
+            return y
+        return basic.rmsnorm(comm.all_reduce(h), norm_w, t.norm_eps, residual=res, gemma=t.gemma_norm)
 
     def _run_sublayer(self, sub, x, ctx, kv, states):
         if isinstance(sub, MoeLayer) and ctx.extras.get("ep") is not None:
             return sub.forward_a2a(x, ctx.extras["ep"])
         if isinstance(sub, MoeLayer) and sub.ep_size > 1 and ctx.comm is not None:
             return sub.forward_ep(x, ctx.comm)
-        return sub.forward(x, ctx, kv, states)
+        out = sub.forward(x, ctx, kv, states)
+        if getattr(sub, "partial", False) and ctx.comm is not None:
+            out = ctx.comm.all_reduce(out)
+        return out
 
     def _hidden_states_hyper(self, ids: torch.Tensor, ctx: ForwardContext, kv, states=None):
         """Trunk with hyper-connections: the token's state is `hyper_streams` residual streams [T, hc * H]; a site's
         per-stream norm and gated mean stand where the pre-norm + residual add stand in the plain trunk.
         Reference: hibana/model/flashnext/model.py:42-77."""
         t = self.target
-        hyper = basic.embedding(ids, self.embed).repeat(1, t.hyper_streams)
+        hyper = self.embed_tokens(ids, ctx).repeat(1, t.hyper_streams)
         site = 0
         for blk in self.blocks:
             for _norm_w, sub in blk.sublayers():
@@ -156,4 +223,18 @@ class HybridModel:
         return basic.rmsnorm(h, self.final_norm, t.norm_eps, residual=res, gemma=t.gemma_norm)
 
     def logits(self, normed: torch.Tensor, comm=None) -> torch.Tensor:
-        return gemm.linear_bf16(normed, self.lm_head, epilogue=gemm.EPI_STORE_F32)
+        lg = gemm.linear_bf16(normed, self.lm_head, epilogue=gemm.EPI_STORE_F32)
+        if self.vocab_shard and comm is not None:
+            lg = comm.all_gather_last(lg)
+        return lg
+
+    def greedy_tokens(self, normed: torch.Tensor, comm=None) -> torch.Tensor:
+        """Greedy token per row; with a vocab-parallel head the ranks exchange one (value, id) pair per row."""
+        from ..ops import sampling
+        lg = gemm.linear_bf16(normed, self.lm_head, epilogue=gemm.EPI_STORE_F32)
+        if not (self.vocab_shard and comm is not None):
+            return sampling.argmax(lg)
+        idx, val = sampling.argmax_with_value(lg)
+        if hasattr(comm, "pick_exchange"):
+            return comm.pick_exchange(val, idx, self.target.tp_rank * self.vocab_shard)
+        return sampling.argmax(comm.all_gather_last(lg))

@@ -21,7 +21,12 @@ from .linear import Linear, interleave_pairs
 class Init:
     """Seeded weight factory (N(0, std) matrices) shared by all layers of a model."""
 
-    def __init__(self, seed: int, device, init_device=None, std: float = 0.02):
+    def __init__(self, seed: int, device, init_device=None, std: float = 0.02, tp: int = 1, rank: int = 0,
+                 full: Optional[Target] = None):
+        """`tp` / `rank`: tensor-parallel shard to keep. Every rank draws the FULL matrices from the same seeded
+        stream (so the unsharded model is the same on every rank and for every tp) and keeps its rows / columns;
+        `full` is the unsharded target the shapes come from."""
+        self.tp, self.rank, self.full = tp, rank, full
         self.device = torch.device(device)
         self.gen_device = torch.device(init_device) if init_device is not None else self.device
         self.gen = torch.Generator(device=self.gen_device)
@@ -34,8 +39,30 @@ class Init:
     def uniform(self, *shape, lo: float = 0.0, hi: float = 1.0) -> torch.Tensor:
         return torch.rand(*shape, generator=self.gen, dtype=torch.float32, device=self.gen_device) * (hi - lo) + lo
 
-    def linear(self, n: int, k: int, fmt: str, name: str = "") -> Linear:
-        return Linear(self.normal(n, k), fmt, name=name).to(self.device)
+    def linear(self, n: int, k: int, fmt: str, name: str = "", rows=None, cols=None) -> Linear:
+        """[n, k] projection; `rows` / `cols` (slice or index tensor) keep a tensor-parallel shard that is bitwise a
+        slice of the quantised full matrix."""
+        w = self.normal(n, k)
+        if rows is None and cols is None:
+            return Linear(w, fmt, name=name).to(self.device)
+        if isinstance(rows, torch.Tensor):
+            rows = rows.to(w.device)
+        return Linear.sharded(w, fmt, rows=rows, cols=cols, name=name).to(self.device)
+
+    def span(self, per_rank: int) -> slice:
+        """This rank's contiguous range of `per_rank` items."""
+        return slice(self.rank * per_rank, (self.rank + 1) * per_rank)
+
+    def rows_of(self, *ranges) -> Optional[torch.Tensor]:
+        """Index tensor over several (offset, start, length) row ranges (None without tensor parallelism)."""
+        if self.tp == 1:
+            return None
+        return torch.cat([torch.arange(off + lo, off + lo + n) for off, lo, n in ranges])
+
+    def take(self, x: torch.Tensor, idx) -> torch.Tensor:
+        if idx is None:
+            return x
+        return x[idx.to(x.device) if isinstance(idx, torch.Tensor) else idx]
 
     def ones(self, n: int, gemma: bool = False) -> torch.Tensor:
         return (torch.zeros if gemma else torch.ones)(n, dtype=torch.bfloat16, device=self.device)
@@ -49,9 +76,18 @@ class AttentionLayer:
     def __init__(self, t: Target, init: Init, kv_index: int, gated: bool, name: str):
         d = t.head_dim
         self.t, self.kv_index, self.gated = t, kv_index, gated
-        qw = t.q_heads * d * (2 if gated else 1)
-        self.qkv = init.linear(qw + 2 * t.kv_heads * d, t.hidden, _fmt(t), name + ".qkv")
-        self.o = init.linear(t.hidden, t.q_heads * d, _fmt(t), name + ".o")
+        f = init.full or t                      # unsharded geometry (t holds this rank's head counts)
+        gq = 2 if gated else 1
+        qw = f.q_heads * d * gq
+        # tensor parallel: q (and gate) rows by head, k / v rows by kv head (replicated when kv heads < ranks),
+        # o_proj by input feature; the output is then a partial sum
+        kv0 = (init.rank * f.kv_heads) // init.tp
+        rows = init.rows_of((0, init.rank * t.q_heads * d * gq, t.q_heads * d * gq),
+                            (qw, kv0 * d, t.kv_heads * d), (qw + f.kv_heads * d, kv0 * d, t.kv_heads * d))
+        self.qkv = init.linear(qw + 2 * f.kv_heads * d, t.hidden, _fmt(t), name + ".qkv", rows=rows)
+        self.o = init.linear(t.hidden, f.q_heads * d, _fmt(t), name + ".o",
+                             cols=init.span(t.q_heads * d) if init.tp > 1 else None)
+        self.partial = init.tp > 1
         self.q_norm = init.ones(d, t.gemma_norm) if t.qk_norm else None
         self.k_norm = init.ones(d, t.gemma_norm) if t.qk_norm else None
         self.inv_freq = basic.rope_inv_freq(max(t.rot_dim, 2), t.rope_theta, device=init.device)
@@ -81,16 +117,29 @@ class AttentionLayer:
 class MambaLayer:
     def __init__(self, t: Target, init: Init, state_index: int, name: str):
         self.t, self.state_index = t, state_index
-        inner, gn = t.mamba_inner, t.mamba_groups * t.mamba_state
-        self.in_proj = init.linear(2 * inner + 2 * gn + t.mamba_heads, t.hidden, _fmt(t), name + ".in_proj")
-        self.out_proj = init.linear(t.hidden, inner, _fmt(t), name + ".out_proj")
-        self.conv_w = init.normal(t.mamba_conv_dim, t.conv_width, std=0.2).to(torch.bfloat16).to(init.device)
-        self.conv_b = init.normal(t.mamba_conv_dim, std=0.02).to(torch.bfloat16).to(init.device)
-        self.a_log = torch.log(init.uniform(t.mamba_heads, lo=1.0, hi=16.0)).to(init.device)
-        dt = torch.exp(init.uniform(t.mamba_heads) * (math.log(0.1) - math.log(0.001)) + math.log(0.001))
-        self.dt_bias = (dt + torch.log(-torch.expm1(-dt))).to(init.device)       # inverse softplus
+        f = init.full or t
+        inner, gn = t.mamba_inner, t.mamba_groups * t.mamba_state          # this rank's widths
+        finner, fgn = f.mamba_inner, f.mamba_groups * f.mamba_state
+        # tensor parallel: heads split by rank, B / C groups follow their heads (a group is replicated when there
+        # are fewer groups than ranks); rows of in_proj are z | x | B | C | dt, conv channels x | B | C
+        g0 = (init.rank * f.mamba_groups) // init.tp
+        sel = init.rows_of((0, init.rank * inner, inner), (finner, init.rank * inner, inner),
+                           (2 * finner, g0 * t.mamba_state, gn), (2 * finner + fgn, g0 * t.mamba_state, gn),
+                           (2 * finner + 2 * fgn, init.rank * t.mamba_heads, t.mamba_heads))
+        csel = init.rows_of((0, init.rank * inner, inner), (finner, g0 * t.mamba_state, gn),
+                            (finner + fgn, g0 * t.mamba_state, gn))
+        hsel = init.span(t.mamba_heads) if init.tp > 1 else None
+        self.in_proj = init.linear(2 * finner + 2 * fgn + f.mamba_heads, t.hidden, _fmt(t), name + ".in_proj", rows=sel)
+        self.out_proj = init.linear(t.hidden, finner, _fmt(t), name + ".out_proj",
+                                    cols=init.span(inner) if init.tp > 1 else None)
+        self.conv_w = init.take(init.normal(f.mamba_conv_dim, t.conv_width, std=0.2), csel).to(torch.bfloat16).to(init.device)
+        self.conv_b = init.take(init.normal(f.mamba_conv_dim, std=0.02), csel).to(torch.bfloat16).to(init.device)
+        self.a_log = init.take(torch.log(init.uniform(f.mamba_heads, lo=1.0, hi=16.0)), hsel).to(init.device)
+        dt = torch.exp(init.uniform(f.mamba_heads) * (math.log(0.1) - math.log(0.001)) + math.log(0.001))
+        self.dt_bias = init.take(dt + torch.log(-torch.expm1(-dt)), hsel).to(init.device)       # inverse softplus
         self.d_skip = torch.ones(t.mamba_heads, device=init.device)
         self.norm_w = init.ones(inner)
+        self.partial = init.tp > 1
 
     def linears(self):
         return [self.in_proj, self.out_proj]
@@ -136,15 +185,26 @@ class GdnLayer:
     def __init__(self, t: Target, init: Init, state_index: int, name: str):
         self.t, self.state_index = t, state_index
         kd = t.gdn_head_dim
+        f = init.full or t
         self.qk = t.gdn_k_heads * kd
         self.vd = t.gdn_v_heads * kd
-        self.in_qkvz = init.linear(2 * self.qk + 2 * self.vd, t.hidden, _fmt(t), name + ".in_qkvz")
-        self.in_ba = init.linear(2 * t.gdn_v_heads, t.hidden, "bf16", name + ".in_ba")
-        self.out_proj = init.linear(t.hidden, self.vd, _fmt(t), name + ".out_proj")
-        self.conv_w = init.normal(t.gdn_conv_dim, t.conv_width, std=0.2).to(torch.bfloat16).to(init.device)
-        self.a_log = torch.log(init.uniform(t.gdn_v_heads, lo=1.0, hi=16.0)).to(init.device)
-        self.dt_bias = init.normal(t.gdn_v_heads, std=0.5).to(init.device)
+        fqk, fvd = f.gdn_k_heads * kd, f.gdn_v_heads * kd
+        # tensor parallel: key heads and their value heads split by rank; rows of in_qkvz are q | k | v | z
+        r = init.rank
+        sel = init.rows_of((0, r * self.qk, self.qk), (fqk, r * self.qk, self.qk), (2 * fqk, r * self.vd, self.vd),
+                           (2 * fqk + fvd, r * self.vd, self.vd))
+        csel = init.rows_of((0, r * self.qk, self.qk), (fqk, r * self.qk, self.qk), (2 * fqk, r * self.vd, self.vd))
+        basel = init.rows_of((0, r * t.gdn_v_heads, t.gdn_v_heads), (f.gdn_v_heads, r * t.gdn_v_heads, t.gdn_v_heads))
+        hsel = init.span(t.gdn_v_heads) if init.tp > 1 else None
+        self.in_qkvz = init.linear(2 * fqk + 2 * fvd, t.hidden, _fmt(t), name + ".in_qkvz", rows=sel)
+        self.in_ba = init.linear(2 * f.gdn_v_heads, t.hidden, "bf16", name + ".in_ba", rows=basel)
+        self.out_proj = init.linear(t.hidden, fvd, _fmt(t), name + ".out_proj",
+                                    cols=init.span(self.vd) if init.tp > 1 else None)
+        self.conv_w = init.take(init.normal(f.gdn_conv_dim, t.conv_width, std=0.2), csel).to(torch.bfloat16).to(init.device)
+        self.a_log = init.take(torch.log(init.uniform(f.gdn_v_heads, lo=1.0, hi=16.0)), hsel).to(init.device)
+        self.dt_bias = init.take(init.normal(f.gdn_v_heads, std=0.5), hsel).to(init.device)
         self.norm_w = init.ones(kd, t.gemma_norm)
+        self.partial = init.tp > 1
 
     def linears(self):
         return [self.in_qkvz, self.in_ba, self.out_proj]
@@ -188,14 +248,20 @@ class GdnLayer:
 
 class MlpLayer:
     def __init__(self, t: Target, init: Init, name: str, width: Optional[int] = None, act: str = "swiglu"):
+        """`width` is the UNSHARDED intermediate size; with tensor parallelism this rank keeps width / tp columns of
+        gate / up (rows of the stacked matrix) and the matching input features of down."""
         self.t, self.act = t, act
-        width = width or t.ffn
+        width = width or (init.full or t).ffn
+        local = width // init.tp
         if act == "swiglu":
-            self.up = Linear(interleave_pairs(init.normal(width, t.hidden), init.normal(width, t.hidden)), _fmt(t),
-                             name=name + ".gate_up").to(init.device)
+            w = interleave_pairs(init.normal(width, t.hidden), init.normal(width, t.hidden))
+            self.up = (Linear(w, _fmt(t), name=name + ".gate_up") if init.tp == 1 else
+                       Linear.sharded(w, _fmt(t), rows=slice(2 * init.rank * local, 2 * (init.rank + 1) * local),
+                                      name=name + ".gate_up")).to(init.device)
         else:
-            self.up = init.linear(width, t.hidden, _fmt(t), name + ".up")
-        self.down = init.linear(t.hidden, width, _fmt(t), name + ".down")
+            self.up = init.linear(width, t.hidden, _fmt(t), name + ".up", rows=init.span(local) if init.tp > 1 else None)
+        self.down = init.linear(t.hidden, width, _fmt(t), name + ".down", cols=init.span(local) if init.tp > 1 else None)
+        self.partial = init.tp > 1
 
     def linears(self):
         return [self.up, self.down]
@@ -221,12 +287,17 @@ class MoeLayer:
             fc1 = torch.stack((fc1[:, :t.expert_ffn], fc1[:, t.expert_ffn:]), dim=2).reshape(t.experts, n1, width)
         fc2 = init.normal(t.experts, width, t.expert_ffn)
         self.experts = moe.ExpertWeights.create(fc1, fc2, t.moe_act, _fmt(t)).to(init.device)
-        self.shared = MlpLayer(t, init, name + ".shared", width=t.shared_ffn, act=t.moe_act) if t.shared_ffn else None
+        f = init.full or t
+        # under tensor parallelism the shared expert is column / row split like a dense MLP (its partial sum joins
+        # the routed experts' partial sum before the one all-reduce of the layer)
+        self.shared = MlpLayer(t, init, name + ".shared", width=f.shared_ffn, act=t.moe_act) if t.shared_ffn else None
         self.fc1_latent = init.linear(t.latent, t.hidden, "bf16", name + ".fc1_latent") if t.latent else None
         self.fc2_latent = init.linear(t.hidden, t.latent, "bf16", name + ".fc2_latent") if t.latent else None
         per = t.experts // ep_size
         self.e_lo, self.e_n = ep_rank * per, per
         self.ep_size = ep_size
+        self.tp = init.tp
+        self.partial = False          # the expert-parallel forms reduce inside the layer
 
     def linears(self):
         out = [self.router]
@@ -241,6 +312,8 @@ class MoeLayer:
         ids, w = moe.route(logits, t.top_k, sigmoid=t.router == "sigmoid", sel_bias=self.sel_bias, renorm=True,
                            scale=t.router_scale)
         shared = self.shared.forward(x) if self.shared is not None else None
+        if shared is not None and self.tp > 1 and ctx is not None and ctx.comm is not None:
+            shared = ctx.comm.all_reduce(shared)      # column / row split shared expert beside replicated experts
         if t.latent:
             lat = self.fc1_latent(x)
             y = moe.experts_forward(lat, ids, w, self.experts, e_lo=self.e_lo, e_n=self.e_n)
@@ -257,7 +330,16 @@ def _moe_forward_ep(self, x, comm) -> torch.Tensor:
     ids, w = moe.route(logits, t.top_k, sigmoid=t.router == "sigmoid", sel_bias=self.sel_bias, renorm=True,
                        scale=t.router_scale)
     inp = self.fc1_latent(x) if t.latent else x
-    part = comm.all_reduce(moe.experts_forward(inp, ids, w, self.experts, e_lo=self.e_lo, e_n=self.e_n))
+    part = moe.experts_forward(inp, ids, w, self.experts, e_lo=self.e_lo, e_n=self.e_n)
+    if getattr(self, "tp", 1) > 1:
+        # tensor parallel: the shared expert is column / row split too, so its partial sum joins the routed
+        # experts' before the layer's one all-reduce; the latent up-projection is linear and moves in front of it
+        if t.latent:
+            part = self.fc2_latent(part)
+        if self.shared is not None:
+            part = basic.add(part, self.shared.forward(x))
+        return comm.all_reduce(part)
+    part = comm.all_reduce(part)
     out = self.fc2_latent(part) if t.latent else part
     if self.shared is not None:
         out = basic.add(out, self.shared.forward(x))

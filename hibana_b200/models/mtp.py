@@ -22,7 +22,8 @@ class MtpHead:
         self.hnorm = init.ones(t.hidden, t.gemma_norm)
         self.fc = init.linear(t.hidden, 2 * t.hidden, "bf16", "mtp.fc")
         self.attn = AttentionLayer(t, init, base.kv_layers, False, "mtp.attn")
-        width = t.ffn or max(t.expert_ffn * max(t.top_k, 1) // 2, 128)
+        f = init.full or t
+        width = f.ffn or max(f.expert_ffn * max(f.top_k, 1) // 2, 128)       # unsharded width (MlpLayer splits it)
         self.mlp = MlpLayer(t, init, "mtp.mlp", width=width)
         self.attn_norm = init.ones(t.hidden, t.gemma_norm)
         self.mlp_norm = init.ones(t.hidden, t.gemma_norm)
@@ -40,7 +41,12 @@ class MtpHead:
         res = self.fc(torch.cat((e, h), dim=-1))
         x = basic.rmsnorm(res, self.attn_norm, t.norm_eps, gemma=t.gemma_norm)
         a = self.attn.forward(x, ctx, kv, None)
+        tp = getattr(self.attn, "partial", False) and ctx.comm is not None
+        if tp:                                   # tensor parallel: the head's two partial sums are all-reduced
+            a = ctx.comm.all_reduce(a)
         x = basic.rmsnorm(a, self.mlp_norm, t.norm_eps, residual=res, gemma=t.gemma_norm)
         m = self.mlp.forward(x)
+        if tp:
+            m = ctx.comm.all_reduce(m)
         out = basic.add(m, res)
         return out, basic.rmsnorm(out, self.final_norm, t.norm_eps, gemma=t.gemma_norm)

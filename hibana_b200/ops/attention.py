@@ -34,14 +34,19 @@ nv.register("hb_attn_prefill", [P, P, P, L, L, P, L, P, P, P, P, I, I, I, I, I, 
 NUM_SMS = 148
 
 
-def choose_splits(batch: int, hkv: int, max_ctx: int, row_chunks: int = 1) -> int:
-    """KV splits that fill whole waves of one CTA per SM; a split never gets fewer than 256 keys."""
+DECODE_CTAS_PER_SM = 2      # csrc/attn_decode.cu: 64-thread CTAs with ~100 KB of rings, two share an SM
+
+
+def choose_splits(batch: int, hkv: int, max_ctx: int, row_chunks: int = 1, slots: int = 0) -> int:
+    """KV splits that fill whole waves of the resident CTA slots (the decode kernel streams from every resident
+    CTA at once, so a last wave that is a third full costs a whole wave); a split never gets fewer than 256 keys."""
+    slots = slots or NUM_SMS * max(1, cfgmod.current().attn_ctas_per_sm)
     ctas = max(1, batch * hkv * row_chunks)
     cap = int(max(1, min(max_ctx // 256, 64)))
     best, best_eff = 1, 0.0
     for s in range(1, cap + 1):
         n = ctas * s
-        eff = n / (-(-n // NUM_SMS) * NUM_SMS)
+        eff = n / (-(-n // slots) * slots)
         if eff > best_eff + 0.02:     # prefer fewer splits unless the wave efficiency clearly improves
             best, best_eff = s, eff
     return best

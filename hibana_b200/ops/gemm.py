@@ -21,6 +21,7 @@ EPI_RELU2 = 6       # grouped (weights on the 128-row side) GEMMs only: out = re
 NUM_SMS = 148
 
 nv.register("hb_gemm_set_pdl", [nv.I], void=True)
+nv.register("hb_gemm_set_local_reduce", [nv.I], void=True)
 nv.register("hb_gemm_silu_quant", [nv.I, nv.P, nv.P, nv.P, nv.P, nv.I, nv.I, nv.I, nv.L, nv.L, nv.P, nv.P, nv.P, nv.P,
                                    nv.I, nv.I, nv.P, nv.I, nv.I, nv.I, nv.P])
 
@@ -36,6 +37,7 @@ def set_pdl(on) -> None:
     _PDL_INIT = True
     if nv.available():
         nv.lib().hb_gemm_set_pdl(int(on))
+        nv.lib().hb_gemm_set_local_reduce(int(cfgmod.current().gemm_local_reduce))
 
 
 

@@ -27,46 +27,47 @@ class BroadcastChannel:
 
 
 def serve_rank(cfg) -> int:
-    """One rank of a tensor-parallel server (rank 0 also serves HTTP)."""
+    """One rank of a tensor-parallel server (rank 0 also serves HTTP). Every family serves this way: the dense
+    decoder and the hybrids shard their mixers by head, MLPs by column and experts by expert range over the ranks
+    (`build_model`); the engine stack itself comes from the settings (`LLM`), the same as on one GPU."""
+    import datetime
+
     from ..api.chat_template import ChatTemplate
     from ..api.server import create_app
-    from ..engine.executor import Executor
+    from ..engine.llm import LLM
     from ..engine.loop import EngineLoop
-    from ..engine.scheduler import Scheduler, SchedulerConfig
-    from ..models.dense import DenseModel
-    from ..target import get_target
     from ..tokenizer import load_tokenizer
     from .comm import Communicator
+    from .watchdog import PeerWatchdog
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    control = dist.new_group(backend="gloo")
+    # the control plane has a timeout: a rank that stops answering ends the others' next broadcast with an error
+    control = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=max(cfg.control_timeout_s, 5)))
     cfg = BroadcastChannel(control).broadcast(cfg if rank == 0 else None)     # every rank serves rank 0's settings
     comm = Communicator.create(rank, world, dev, slot_mb=cfg.comm_buffer_mb // 8 or 1, timeout_ms=cfg.comm_timeout_ms,
                                fused=cfg.fused_collectives)
-    target = get_target(cfg.target)
-    if target.family != "dense":
-        raise NotImplementedError("tensor-parallel serving covers the dense family; MoE families use expert parallelism")
-    model = DenseModel.sharded(target, world, rank, dev, seed=cfg.seed)
-    ctx = cfg.max_context or min(target.max_context, 8192)
-    ex = Executor(model, max_batch=cfg.max_batch, max_ctx=ctx, kv_slots=cfg.kv_pages, use_graphs=cfg.cuda_graphs,
-                  buckets=cfg.buckets, radix_cache=cfg.radix_cache, comm=comm)
-    if cfg.cuda_graphs:
-        ex.capture_graphs()
-    sched = Scheduler(ex, SchedulerConfig(prefill_chunk=cfg.prefill_chunk or target.prefill_chunk,
-                                          prefill_budget=cfg.prefill_budget, max_batch=cfg.max_batch,
-                                          max_queue=cfg.max_queue))
-    engine = EngineLoop(sched, channel=BroadcastChannel(control), rank=rank).start()
+    llm = LLM(cfg.replace(tp=world), device=dev, comm=comm, warmup=True)
+    engine = EngineLoop(llm.scheduler, channel=BroadcastChannel(control), rank=rank).start()
+
+    def on_dead(ranks):
+        engine._fail(f"ranks {list(ranks)} stopped answering")
+        os._exit(13)                      # non-zero: the supervisor restarts the whole group
+    store = dist.TCPStore("127.0.0.1", int(os.environ.get("MASTER_PORT", "29500")) + 23, world, rank == 0,
+                          timeout=datetime.timedelta(seconds=60))
+    PeerWatchdog(store, rank, world, interval=1.0, timeout=float(max(cfg.control_timeout_s, 5)),
+                 on_dead=on_dead).start()
     if rank != 0:
         engine.thread.join()
         os._exit(0 if engine.healthy else 1)
     import uvicorn
-    tok = load_tokenizer(cfg.weights if cfg.weights != "random" else None, target.vocab)
-    app = create_app(engine, tok, model_name=target.name, template=ChatTemplate(),
+    tok = load_tokenizer(cfg.weights if cfg.weights != "random" else None, llm.target.vocab)
+    app = create_app(engine, tok, model_name=llm.target.name, template=ChatTemplate(),
                      info={"config": cfg.as_dict(), "tp": world}, api_key=cfg.api_key)
     uvicorn.Server(uvicorn.Config(app, host=cfg.host, port=cfg.port, log_level="warning")).run()
     engine.stop()
+    llm.shutdown()
     os._exit(0)

@@ -66,6 +66,7 @@ class Target:
     hyper_rank: int = 64             # width of the low-rank gate projections of a hyper-connection site
     prefill_chunk: int = 2048
     tie_embeddings: bool = False
+    vision: tuple = ()               # (image, patch, width, depth, heads, mlp) of the vision encoder; () = text only
     tp_size: int = 1
     tp_rank: int = 0
 
@@ -211,7 +212,8 @@ def nemotron() -> Target:
                   kv_heads=2, head_dim=128, rotary_frac=0.0, mamba_heads=128, mamba_head_dim=64, mamba_state=128,
                   mamba_groups=8, conv_width=4, mamba_chunk=128, experts=512, top_k=22, expert_ffn=2688,
                   shared_ffn=5376, router="sigmoid", router_scale=5.0, moe_act="relu2", latent=1024, mtp_layers=1,
-                  mtp_depth=3, weight_format="nvfp4", kv_dtype="fp8", norm_eps=1e-5, prefill_chunk=4096)
+                  mtp_depth=3, weight_format="nvfp4", kv_dtype="fp8", norm_eps=1e-5, prefill_chunk=4096,
+                  vision=(448, 16, 1280, 32, 16, 5120))
 
 
 PRESETS = {

@@ -169,3 +169,73 @@ def test_constrained_output_over_http(stack):
             r3 = await c.post("/generate", json={"text": "x", "sampling_params": {"ebnf": "root ::= ("}})
             assert r3.status_code == 400
     _run(go())
+
+
+def test_refusal_guard_nudges_then_stops():
+    from hibana_b200.api import refusal_guard as rg
+    def convo(n):
+        msgs = [{"role": "user", "content": "please deploy"}]
+        for i in range(n):
+            msgs.append({"role": "assistant", "content": "", "tool_calls": [
+                {"id": f"c{i}", "type": "function", "function": {"name": "bash", "arguments": "{}"}}]})
+            msgs.append({"role": "tool", "tool_call_id": f"c{i}", "content": "This command requires approval"})
+        return msgs
+    assert rg.decide(convo(1), {})[0] == "generate"
+    verdict, found = rg.decide(convo(4), {})
+    assert verdict == "nudge" and found.tool == "bash" and found.count == 4
+    assert "do not call `bash` again" in rg.reminder(found)["content"]
+    assert rg.decide(convo(9), {})[0] == "stop"
+    assert rg.decide(convo(9), {"refusal_guard": False})[0] == "generate"
+    # a new user message resets the count; ordinary tool errors that differ each time never trigger
+    assert rg.decide(convo(9) + [{"role": "user", "content": "try again with sudo"}], {})[0] == "generate"
+    varied = [{"role": "user", "content": "x"}] + [
+        {"role": "tool", "tool_call_id": str(i), "content": f"error {i}: file not found", "is_error": True} for i in range(9)]
+    assert rg.decide(varied, {})[0] == "generate"
+
+
+def test_chat_stops_without_generating_when_refusals_repeat_and_reports_logprobs():
+    from test_scheduler import FakeExecutor
+    loop = EngineLoop(Scheduler(FakeExecutor(), SchedulerConfig(max_batch=4))).start()
+    app = create_app(loop, ByteTokenizer())
+    msgs = [{"role": "user", "content": "go"}]
+    for i in range(8):
+        msgs.append({"role": "assistant", "content": "", "tool_calls": [
+            {"id": f"c{i}", "type": "function", "function": {"name": "write", "arguments": "{}"}}]})
+        msgs.append({"role": "tool", "tool_call_id": f"c{i}", "content": "permission denied"})
+
+    async def go():
+        async with _client(app) as c:
+            r = await c.post("/v1/chat/completions", json={"messages": msgs, "max_tokens": 4})
+            assert r.status_code == 200
+            body = r.json()
+            assert "`write` was refused 8 times" in body["choices"][0]["message"]["content"]
+            assert body["usage"]["completion_tokens"] == 0 and loop.steps == 0
+            r = await c.post("/v1/messages", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3})
+            assert r.status_code == 200
+    _run(go())
+    loop.stop()
+
+
+def test_image_parts_become_placeholders_or_notes():
+    import base64
+    from hibana_b200.api import media as m
+    from hibana_b200.engine.media import placeholder_ids
+    png = base64.b64encode(b"\\x89PNG fake image bytes").decode()
+    messages = [{"role": "user", "content": [
+        {"type": "text", "text": "what is <image> in this? "},
+        {"type": "image_url", "image_url": {"url": f"data:image/png;base64,{png}"}},
+        {"type": "image", "source": {"type": "base64", "media_type": "image/png", "data": png}}]}]
+    assert m.has_images(messages)
+    out, plan = m.prepare(messages)
+    assert len(plan.images) == 2 and out[0]["content"].count(m.MARKER) == 2      # the user's own "<image>" is escaped
+    tok = ByteTokenizer()
+    ids = m.expand("A" + out[0]["content"] + "B", tok, plan, tokens_per_image=5)
+    neg = [i for i in ids if i < 0]
+    assert len(neg) == 10 and neg[:5] == placeholder_ids(plan.images[0], 5) and neg[:5] == neg[5:]   # same bytes
+    assert plan.spans[0][1] == 5 and ids[plan.spans[0][0]] < 0 and ids[plan.spans[0][0] - 1] >= 0
+    assert "<image>" in tok.decode([i for i in ids if i >= 0])                     # user text survives unescaped
+    assert "image omitted" in m.strip_images(messages)[0]["content"]
+    import pytest as _pytest
+    from hibana_b200.api.validation import BadRequest
+    with _pytest.raises(BadRequest):
+        m.prepare([{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "http://x/y.png"}}]}])

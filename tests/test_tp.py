@@ -135,8 +135,14 @@ for name, fused, sp in (("nccl", False, 0), ("fused", True, 0), ("gather", True,
     ex.capture_graphs()
     if name == "fused":
         res["greedy_graph"] = ex.runner.bufs[ex.runner.buckets[0]].graph_greedy is not None
-        lg2 = prefill_logits(ex, prompts[0])
-        one = DenseModel(t, dev, seed=0, init_device="cpu")
+        # logits against the unsharded model, in bf16 weights: NVFP4 requantisation turns rounding-order differences
+        # into flipped 4-bit codes, which says nothing about the sharding; bf16 isolates the summation order
+        from hibana_b200.target import scaled
+        tb = scaled(t, weight_format="bf16")
+        m2 = DenseModel.sharded(tb, world, rank, dev, seed=0, init_device="cpu")
+        ex2 = Executor(m2, max_batch=2, max_ctx=512, use_graphs=False, comm=comm, radix_cache=False)
+        lg2 = prefill_logits(ex2, prompts[0])
+        one = DenseModel(tb, dev, seed=0, init_device="cpu")
         ex1 = Executor(one, max_batch=2, max_ctx=512, use_graphs=False, radix_cache=False)
         lg1 = prefill_logits(ex1, prompts[0])
         res["logit_err"] = float((lg2 - lg1).abs().max() / lg1.abs().max())
@@ -180,7 +186,59 @@ def test_tp2_fused_allreduce_matches_nccl_gpu(tmp_path):
     # the per-rank argmax + (value, id) exchange picks exactly what the argmax over gathered logits picks
     assert ranks[0]["greedy_graph"] and ranks[0]["gather"] == fused
     # logits of the sharded model against the unsharded one on the same prompt (different summation order only)
-    assert ranks[0]["logit_err"] < 0.05 and ranks[0]["argmax_same"] > 0.9, (ranks[0]["logit_err"], ranks[0]["argmax_same"])
+    assert ranks[0]["logit_err"] < 0.03 and ranks[0]["argmax_same"] > 0.9, (ranks[0]["logit_err"], ranks[0]["argmax_same"])
     # the sequence-parallel chain (GEMM -> reduce-scatter, norm, all-gather -> GEMM) prefilled the 256-token prompt
     assert ranks[0]["sp_long"] == ranks[1]["sp_long"]
     assert ranks[0]["sp_long"][0][0] == ranks[0]["nccl_long"][0][0]
+
+
+@pytest.mark.parametrize("family", ["tiny", "qwen38", "nemotron", "flashnext"])
+def test_hybrid_families_shard_and_tp2_matches_tp1_cpu(family):
+    """Hybrid families under tensor parallelism (attention / Mamba-2 / gated delta rule split by head, MLPs by
+    column, experts by expert range, vocabulary split for the head): two ranks played by two threads emit the same
+    tokens as each other, and the first token of every request equals the unsharded model's."""
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import get_target
+    base = get_target(family)
+    small = dict(layers=4, hidden=256, vocab=2048, max_context=512, prefill_chunk=128, weight_format="bf16",
+                 kv_dtype="bf16", mtp_layers=0, hyper_streams=0)
+    if base.q_heads:
+        small.update(q_heads=4, kv_heads=2, head_dim=64)
+    if base.mamba_heads:
+        small.update(mamba_heads=8, mamba_head_dim=32, mamba_state=32, mamba_groups=2, mamba_chunk=64)
+    if base.gdn_v_heads:
+        small.update(gdn_k_heads=2, gdn_v_heads=4, gdn_head_dim=64)
+    if base.experts:
+        small.update(experts=8, top_k=2, expert_ffn=128, shared_ffn=128 if base.shared_ffn else 0,
+                     latent=128 if base.latent else 0)
+    if base.ffn:
+        small.update(ffn=512)
+    if family == "nemotron":
+        small["layers"] = 8            # reach the first attention block of the pattern ("MEMEMEM*")
+    t = scaled(base, **small)
+    full = HybridModel(t, "cpu", seed=0)
+    shards = [HybridModel.sharded(t, 2, r, "cpu", seed=0) for r in range(2)]
+    assert shards[0].target.tp_size == 2 and shards[1].target.tp_rank == 1
+    sp = SamplingParams(max_tokens=4)
+    prompts = _prompts(t, n=2, length=24)
+    ref = Executor(full, max_batch=2, max_ctx=64, use_graphs=False).generate_batch(prompts, sp)
+    comm = ThreadComm(2)
+    outs, errs = [None, None], []
+
+    def run(rank):
+        try:
+            ex = Executor(shards[rank], max_batch=2, max_ctx=64, use_graphs=False, comm=comm.view(rank))
+            outs[rank] = ex.generate_batch(prompts, sp)
+        except Exception as e:  # noqa: BLE001
+            errs.append(repr(e))
+            comm.barrier.abort()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(2)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join(120)
+    assert not errs, errs
+    a = [r.output_ids for r in outs[0]]
+    assert a == [r.output_ids for r in outs[1]]
+    assert sum(x[0] == y.output_ids[0] for x, y in zip(a, ref)) == len(a)

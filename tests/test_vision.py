@@ -46,3 +46,52 @@ def test_encoder_gpu_matches_cpu():
     px = torch.randn(2, 3, 64, 64, generator=torch.Generator().manual_seed(1))
     a, b = cpu.encode(px).float(), gpu.encode(px).float().cpu()
     assert float((a - b).abs().max() / a.abs().max()) < 5e-2
+
+
+def test_images_reach_the_model_through_the_engine():
+    """An image in a prompt: the placeholder span takes the vision encoder's rows at prefill (also when the span is
+    cut by chunked prefill), a different image changes the output, and the same image again hits the prefix cache."""
+    import io
+
+    from PIL import Image as PilImage
+
+    from hibana_b200.api import media as api_media
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import Request, SamplingParams
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import get_target, scaled
+    from hibana_b200.tokenizer import ByteTokenizer
+
+    def png(color):
+        buf = io.BytesIO()
+        PilImage.new("RGB", (40, 30), color).save(buf, format="PNG")
+        return buf.getvalue()
+
+    t = scaled(get_target("tiny"), mtp_layers=0, vision=(64, 16, 64, 1, 2, 128), weight_format="bf16")
+    model = HybridModel(t, "cpu", seed=0)
+    assert model.vision_cfg.tokens_per_image == 4 and model.vision is not None
+    tok = ByteTokenizer()
+
+    def request(data, budget_text="describe: "):
+        plan = api_media.MediaPlan([media.Image(data, None)])
+        ids = api_media.expand(budget_text + api_media.MARKER + " please", tok, plan, 4)
+        return Request(prompt_ids=ids, params=SamplingParams(max_tokens=3), media=plan)
+
+    ex = Executor(model, max_batch=2, max_ctx=128, use_graphs=False)
+    red = ex.generate_batch_requests([request(png("red"))])[0].output_ids
+    again = request(png("red"))
+    # the image span (negative, content-derived ids) is part of the cached prefix of the first request
+    assert ex.state.cache.match(again.prompt_ids[:-1], split=False).length >= 14
+    red2 = ex.generate_batch_requests([again])[0].output_ids
+    assert red2 == red
+    ex2 = Executor(model, max_batch=2, max_ctx=128, use_graphs=False)
+    chunked = ex2.generate_batch_requests([request(png("red"))], prefill_budget=12)[0].output_ids   # cuts the span
+    assert chunked == red
+    blue = Executor(model, max_batch=2, max_ctx=128, use_graphs=False).generate_batch_requests(
+        [request(png("blue"))])[0]
+    assert any(i < 0 for i in blue.prompt_ids)
+    emb_red = ex._vision_cache.embeddings(media.Image(png("red"), None))
+    emb_blue = ex._vision_cache.embeddings(media.Image(png("blue"), None))
+    assert emb_red.shape == (4, t.hidden) and not torch.equal(emb_red, emb_blue)
+    with pytest.raises(ValueError):
+        media.decode_pixels(media.Image(b"not an image", None), 64)
