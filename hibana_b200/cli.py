@@ -1,4 +1,5 @@
-"""`hibana` command line: serve | chat | status | stop | cache | logs | launch | traces | verify | engine | dev.
+"""`hibana` command line: serve | chat | status | stop | cache | logs | launch | traces | verify | engine | dev |
+gate | h2h | eval | cache-trace.
 
 `serve` resolves settings and runs the server in the foreground (with --tp/--dp > 1 under the rank supervisor);
 `launch` does the same detached; `engine` is the per-rank entry the supervisor spawns; `dev` hosts the
@@ -76,6 +77,13 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("-n", type=int, default=40)
     p = sub.add_parser("traces")
     p.add_argument("--dir", required=True)
+    for name in ("gate", "h2h", "eval"):         # quality / speed tooling (hibana_b200/evals): arguments pass through
+        sub.add_parser(name, add_help=False).add_argument("rest", nargs=argparse.REMAINDER)
+    p = sub.add_parser("cache-trace")
+    p.add_argument("target", nargs="?", default="dense-tiny")
+    p.add_argument("--tokens", type=int, default=96)
+    p.add_argument("--prefix", type=int, default=64)
+    p.add_argument("--out", default="cache_trace.json")
     p = sub.add_parser("dev")
     p.add_argument("tool", choices=("bench-gemm", "bench-attn", "tp-comm", "build", "check-host"))
     p.add_argument("rest", nargs=argparse.REMAINDER)
@@ -99,6 +107,24 @@ def main(argv: Optional[list] = None) -> int:
         pid = launch_detached(["serve", *(sys.argv[2:] if argv is None else argv[1:])], cfg.port)
         print(json.dumps({"pid": pid, "port": cfg.port}))
         return 0
+    if args.cmd in ("gate", "h2h", "eval"):
+        from .evals import evaluate, h2h, lossy_gate
+        return {"gate": lossy_gate.main, "h2h": h2h.main, "eval": evaluate.main}[args.cmd](args.rest)
+    if args.cmd == "cache-trace":
+        import pathlib
+
+        import torch
+
+        from . import config as cfgmod
+        from .engine import cache_trace
+        from .engine.llm import LLM
+        cfg = cfgmod.EngineConfig(target=args.target, max_batch=4, cuda_graphs=False, max_context=max(512, 2 * args.tokens))
+        llm = LLM(cfg)
+        g = torch.Generator().manual_seed(0)
+        ids = torch.randint(3, llm.target.vocab, (args.tokens,), generator=g).tolist()
+        rep = cache_trace.run(lambda: LLM(cfg, model=llm.model).executor, ids, args.prefix, pathlib.Path(args.out))
+        print(json.dumps(rep, indent=1))
+        return 0 if all(p["equal"] or p["max_rel_diff"] < 0.05 for p in rep["pairs"].values()) else 1
     from .launch import ctl
     if args.cmd == "status":
         print(json.dumps(ctl.status(args.host, args.port), indent=1, default=str))

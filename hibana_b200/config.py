@@ -46,7 +46,7 @@ class EngineConfig:
     gpu_memory_fraction: float = 0.90
     kv_pages: int = 0                      # 0 = plan from free memory
     state_slots: int = 0
-    kv_dtype: str = ""                     # "" = target default, else bf16 | fp8
+    kv_dtype: str = ""                     # "" = target default, else bf16 | fp8 | nvfp4 (4.5 bits per element)
     ssm_state: str = "fp32"                # fp32 | fp16_sr | int8
     # prefix cache / SSD tier
     radix_cache: bool = True
@@ -80,7 +80,8 @@ class EngineConfig:
     gdn_phase1: str = "cuda"               # cuda | torch
     ssd_phase1: str = "cuda"               # cuda | torch
     gemm_local_reduce: bool = True         # unsplit decode tiles: epilogue through the parked partial (wide stores)
-    attn_ctas_per_sm: int = 2              # resident decode-attention CTAs per SM assumed when choosing KV splits
+    attn_ctas_per_sm: int = 1              # CTA slots per SM assumed when choosing KV splits (the kernel runs two per
+                                           # SM, but modelling both measured slower: more splits, more partials to merge)
     max_splits: int = 8                    # split-K cluster size cap (8 = portable)
     pdl: int = 1                           # programmatic dependent launch level (0 off, 1 GEMMs, 2 small kernels too)
     # observability

@@ -37,8 +37,13 @@ struct AttnParams {
   float* part_lse;             // [T, Hq, S]
   int hq, hkv, splits, rows_per_cta;
   float scale_log2;            // softmax scale * log2(e)
-  float kv_scale;              // dequant scale of fp8 KV
+  float kv_scale;              // dequant scale of fp8 / nvfp4 KV
   int causal;
+  // NVFP4 KV (format 2): k_pool / v_pool hold packed e2m1 rows (D / 2 bytes, strides in bytes); these hold the
+  // ue4m3 scale of every 16 elements, rows of D / 16 bytes
+  const uint8_t* k_sf;
+  const uint8_t* v_sf;
+  long long sf_pool_stride, sf_head_stride;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -50,8 +55,32 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <bool FP8>
+template <int N>
+__device__ __forceinline__ void cp_async_small(void* smem, const void* gmem) {   // N = 4, 8 or 16 bytes
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(smem_u32(smem)), "l"(gmem), "n"(N) : "memory");
+}
+
+// 16 e2m1 codes (8 bytes) times their block scale -> floats.
+__device__ __forceinline__ void unpack_fp4_block(const uint8_t* p, float sf, float* f) {
+  const uint2 a = *reinterpret_cast<const uint2*>(p);
+  const uint32_t w[2] = {a.x, a.y};
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t h2;
+      const uint16_t in = static_cast<uint16_t>((w[i] >> (8 * j)) & 0xFFu);
+      asm("{\n\t.reg .b8 t;\n\tcvt.u8.u16 t, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, t;\n\t}" : "=r"(h2) : "h"(in));
+      const __half2 hv = *reinterpret_cast<const __half2*>(&h2);
+      f[8 * i + 2 * j] = __low2float(hv) * sf;
+      f[8 * i + 2 * j + 1] = __high2float(hv) * sf;
+    }
+  }
+}
+
+template <int FMT>
 __device__ __forceinline__ void unpack16(const uint8_t* p, float* f, int* n) {
+  constexpr bool FP8 = FMT == 1;
   const uint4 a = *reinterpret_cast<const uint4*>(p);
   const uint32_t w[4] = {a.x, a.y, a.z, a.w};
   if constexpr (FP8) {
@@ -71,13 +100,25 @@ __device__ __forceinline__ void unpack16(const uint8_t* p, float* f, int* n) {
   }
 }
 
-template <int D, int MAXQ, bool FP8>
+template <int D, int FMT>
+struct AttRow {
+  static constexpr bool FP4 = FMT == 2;
+  static constexpr int ESZ = FMT == 0 ? 2 : 1;              // bytes per element of the copied row (fp4: per BYTE)
+  static constexpr int VAL_BYTES = FP4 ? D / 2 : D * ESZ;   // packed values of a row
+  static constexpr int SF_BYTES = FP4 ? D / 16 : 0;         // block scales of a row (fp4)
+  static constexpr int ROWB = ((VAL_BYTES + SF_BYTES + 15) / 16) * 16 + 16;   // padded: conflict-free 16-byte reads
+  static constexpr int CHUNKS = VAL_BYTES / 16;
+};
+
+template <int D, int MAXQ, int FMT>
 __global__ void __launch_bounds__(ATT_THREADS) attn_splitkv_kernel(const AttnParams p) {
-  constexpr int ESZ = FP8 ? 1 : 2;
-  constexpr int ROW_DATA = D * ESZ;
-  constexpr int ROWB = ROW_DATA + 16;  // padded: conflict-free 16-byte reads down a column of rows
-  constexpr int CHUNKS = ROW_DATA / 16;
-  constexpr int EPC = 16 / ESZ;        // elements per 16-byte chunk
+  using RL = AttRow<D, FMT>;
+  constexpr bool FP8 = FMT == 1, FP4 = FMT == 2, SCALED = FMT != 0;
+  constexpr int ESZ = RL::ESZ;
+  constexpr int ROWB = RL::ROWB;
+  constexpr int CHUNKS = RL::CHUNKS;
+  constexpr int EPC = FP4 ? 16 : 16 / ESZ;   // elements handled per score step (fp4: one 16-element scale block)
+  constexpr int STEPS = FP4 ? D / 16 : CHUNKS;
   constexpr int HALFQ = (MAXQ + 1) / 2;
   constexpr int DPT = D > 128 ? D / 128 : 1;  // dims per thread in the PV phase
 
@@ -138,15 +179,23 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_splitkv_kernel(const AttnPar
   auto load_tile = [&](int t, int buf) {
     const int base = k0 + t * TK;
     // Slot ids are read straight from global by every thread for its own chunks (L1/L2 hits).
-    for (int c = tid; c < TK * CHUNKS; c += ATT_THREADS) {
-      const int key = c / CHUNKS, part = c % CHUNKS;
+    constexpr int PARTS = CHUNKS + (FP4 ? 1 : 0);      // fp4: one more copy per row for its block scales
+    for (int c = tid; c < TK * PARTS; c += ATT_THREADS) {
+      const int key = c / PARTS, part = c % PARTS;
       const int kpos = base + key;
       uint8_t* kd = kbuf + (buf * TK + key) * ROWB + part * 16;
       uint8_t* vd = vbuf + (buf * TK + key) * ROWB + part * 16;
       if (kpos < k1) {
-        const long long off = (static_cast<long long>(idx_row[kpos]) * p.pool_stride + static_cast<long long>(kvh) * p.head_stride) * ESZ + part * 16;
-        cp_async16(kd, kp + off);
-        cp_async16(vd, vp + off);
+        if (FP4 && part == CHUNKS) {
+          const long long so = static_cast<long long>(idx_row[kpos]) * p.sf_pool_stride +
+                               static_cast<long long>(kvh) * p.sf_head_stride;
+          cp_async_small<RL::SF_BYTES ? RL::SF_BYTES : 4>(kd, p.k_sf + so);
+          cp_async_small<RL::SF_BYTES ? RL::SF_BYTES : 4>(vd, p.v_sf + so);
+        } else {
+          const long long off = (static_cast<long long>(idx_row[kpos]) * p.pool_stride + static_cast<long long>(kvh) * p.head_stride) * ESZ + part * 16;
+          cp_async16(kd, kp + off);
+          cp_async16(vd, vp + off);
+        }
       } else {
         *reinterpret_cast<uint4*>(kd) = make_uint4(0, 0, 0, 0);
         *reinterpret_cast<uint4*>(vd) = make_uint4(0, 0, 0, 0);
@@ -174,10 +223,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_splitkv_kernel(const AttnPar
       for (int i = 0; i < HALFQ; ++i) s[i] = 0.f;
       const uint8_t* krow = kbuf + (buf * TK + key) * ROWB;
 #pragma unroll 2
-      for (int c = 0; c < CHUNKS; ++c) {
+      for (int c = 0; c < STEPS; ++c) {
         float kf[16];
         int n;
-        unpack16<FP8>(krow + c * 16, kf, &n);
+        if constexpr (FP4) unpack_fp4_block(krow + c * 8, e4m3_to_float(krow[RL::VAL_BYTES + c]), kf);
+        else unpack16<FMT>(krow + c * 16, kf, &n);
 #pragma unroll
         for (int i = 0; i < HALFQ; ++i) {
           const int qi = 2 * i + qpar;
@@ -199,7 +249,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_splitkv_kernel(const AttnPar
           const int rr = qi / g;
           const int limit = p.causal ? ctx - R + r0 + rr + 1 : ctx;  // keys [0, limit) are visible
           float v = s[i];
-          if (FP8) v *= p.kv_scale;
+          if (SCALED) v *= p.kv_scale;
           sc[qi * (TK + 1) + key] = (kpos < limit && kpos < k1) ? v : -INFINITY;
         }
       }
@@ -243,7 +293,10 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_splitkv_kernel(const AttnPar
 #pragma unroll
         for (int j = 0; j < DPT; ++j) {
           const int d = tid + j * 128;
-          if constexpr (FP8) vv[j] = e4m3_to_float(vb[key * ROWB + d]);
+          if constexpr (FP4) {
+            const uint8_t byte = vb[key * ROWB + (d >> 1)];
+            vv[j] = e2m1_to_float((byte >> ((d & 1) * 4)) & 0xF) * e4m3_to_float(vb[key * ROWB + RL::VAL_BYTES + (d >> 4)]);
+          } else if constexpr (FP8) vv[j] = e4m3_to_float(vb[key * ROWB + d]);
           else vv[j] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(vb + key * ROWB + d * 2));
         }
         const float* pr = pt + key * MAXQ;
@@ -277,7 +330,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_splitkv_kernel(const AttnPar
         for (int j = 0; j < DPT; ++j) {
           const int d = tid + j * 128;
           float o = acc[i][j] * inv;
-          if (FP8) o *= p.kv_scale;
+          if (SCALED) o *= p.kv_scale;
           if (p.splits == 1) p.out[(row * p.hq + head) * D + d] = __float2bfloat16(o);
           else p.part_o[((row * p.hq + head) * p.splits + split) * D + d] = o;
         }
@@ -332,15 +385,14 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   }
 }
 
-template <int D, int MAXQ, bool FP8>
+template <int D, int MAXQ, int FP8>
 size_t attn_smem_bytes() {
-  constexpr int ESZ = FP8 ? 1 : 2;
-  constexpr int ROWB = D * ESZ + 16;
+  constexpr int ROWB = AttRow<D, FP8>::ROWB;
   return static_cast<size_t>(4) * TK * ROWB + sizeof(float) * (MAXQ * D + MAXQ * (TK + 1) + TK * MAXQ + 3 * MAXQ) +
          sizeof(int) * 2 * TK;
 }
 
-template <int D, int MAXQ, bool FP8>
+template <int D, int MAXQ, int FP8>
 int launch_attn(const AttnParams& p, int batch, int row_chunks, cudaStream_t st) {
   const size_t smem = attn_smem_bytes<D, MAXQ, FP8>();
   static bool attr = false;
@@ -355,7 +407,7 @@ int launch_attn(const AttnParams& p, int batch, int row_chunks, cudaStream_t st)
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
-template <int D, bool FP8>
+template <int D, int FP8>
 int dispatch_q(const AttnParams& p, int batch, int row_chunks, int nq, cudaStream_t st) {
   if (nq <= 8) return launch_attn<D, 8, FP8>(p, batch, row_chunks, st);
   if (nq <= 16) return launch_attn<D, 16, FP8>(p, batch, row_chunks, st);
@@ -369,7 +421,20 @@ using namespace hb;
 
 extern "C" {
 
+// NVFP4 KV (kv_fp8 = 2): scale pools for the NEXT hb_attn_paged call of this thread, strides in bytes.
+struct AttnSf {
+  const uint8_t* k = nullptr;
+  const uint8_t* v = nullptr;
+  long long pool_stride = 0, head_stride = 0;
+};
+static thread_local AttnSf g_attn_sf;
+void hb_attn_fp4_scales(const void* k_sf, const void* v_sf, long long pool_stride, long long head_stride) {
+  g_attn_sf.k = static_cast<const uint8_t*>(k_sf); g_attn_sf.v = static_cast<const uint8_t*>(v_sf);
+  g_attn_sf.pool_stride = pool_stride; g_attn_sf.head_stride = head_stride;
+}
+
 // max_rows: largest number of query rows of any sequence (1 for decode). Partials are needed when splits > 1.
+// kv_fp8: 0 bf16, 1 e4m3 (x = q * kv_scale), 2 NVFP4 (x = code * block scale * kv_scale; hb_attn_fp4_scales first).
 int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long long pool_stride,
                   long long head_stride,
                   const void* kv_indices, long long ld_idx, const void* seq_rows, const void* ctx_len, const void* q_indptr,
@@ -391,6 +456,9 @@ int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long lo
   p.hq = hq; p.hkv = hkv; p.splits = splits < 1 ? 1 : splits;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.kv_scale = kv_scale; p.causal = causal;
+  p.k_sf = g_attn_sf.k; p.v_sf = g_attn_sf.v;
+  p.sf_pool_stride = g_attn_sf.pool_stride; p.sf_head_stride = g_attn_sf.head_stride;
+  g_attn_sf = AttnSf{};
   if (p.splits > 1 && (part_o == nullptr || part_lse == nullptr)) return 1;
   // Query rows per CTA: as many tokens as fit 32 (group x tokens), at most what the batch needs.
   int rows_per_cta = 32 / g;
@@ -401,14 +469,19 @@ int hb_attn_paged(const void* q, const void* k_pool, const void* v_pool, long lo
   const int nq = rows_per_cta * g;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc = 1;
-  if (kv_fp8) {
-    if (d == 64) rc = dispatch_q<64, true>(p, batch, row_chunks, nq, st);
-    else if (d == 128) rc = dispatch_q<128, true>(p, batch, row_chunks, nq, st);
-    else if (d == 256) rc = dispatch_q<256, true>(p, batch, row_chunks, nq, st);
+  if (kv_fp8 == 2) {
+    if (p.k_sf == nullptr || p.v_sf == nullptr) return 1;
+    if (d == 64) rc = dispatch_q<64, 2>(p, batch, row_chunks, nq, st);
+    else if (d == 128) rc = dispatch_q<128, 2>(p, batch, row_chunks, nq, st);
+    else if (d == 256) rc = dispatch_q<256, 2>(p, batch, row_chunks, nq, st);
+  } else if (kv_fp8) {
+    if (d == 64) rc = dispatch_q<64, 1>(p, batch, row_chunks, nq, st);
+    else if (d == 128) rc = dispatch_q<128, 1>(p, batch, row_chunks, nq, st);
+    else if (d == 256) rc = dispatch_q<256, 1>(p, batch, row_chunks, nq, st);
   } else {
-    if (d == 64) rc = dispatch_q<64, false>(p, batch, row_chunks, nq, st);
-    else if (d == 128) rc = dispatch_q<128, false>(p, batch, row_chunks, nq, st);
-    else if (d == 256) rc = dispatch_q<256, false>(p, batch, row_chunks, nq, st);
+    if (d == 64) rc = dispatch_q<64, 0>(p, batch, row_chunks, nq, st);
+    else if (d == 128) rc = dispatch_q<128, 0>(p, batch, row_chunks, nq, st);
+    else if (d == 256) rc = dispatch_q<256, 0>(p, batch, row_chunks, nq, st);
   }
   if (rc != 0) return rc;
   if (p.splits > 1) {

@@ -124,24 +124,6 @@ __device__ __forceinline__ void prof_mark(const DevParams& p, int slot, unsigned
 // x * sigmoid(x) with the approximate divide (two special-function ops): the result is rounded to bf16 anyway
 __device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
-// kEpiSiluMulQuant, second half: `stg` holds bf16 [ntok][64] SiLU-mul outputs of feature tile `tile_a` (64 output
-// features) for tokens tok0 .. tok0 + ntok. The 128 epilogue threads (et = 0..127) quantise one 16-element group
-// each per pass: 8 packed bytes into the token's row and one scale byte into the swizzled block layout.
-__device__ __forceinline__ void quant_stage(const DevParams& p, const __nv_bfloat16* stg, int ntok, int tok0,
-                                            int tile_a, int et) {
-  const float inv_gs = 1.f / *p.q_gscale;
-  for (int it = et; it < ntok * 4; it += 128) {
-    const int t = it >> 2, g = it & 3;
-    float x[16];
-    load16(stg + t * 64 + g * 16, x);
-    uint2 packed;
-    const uint32_t sfb = quant16(x, inv_gs, &packed);
-    const int tok = tok0 + t;
-    *reinterpret_cast<uint2*>(p.q_out + static_cast<size_t>(tok) * p.q_ld + tile_a * 32 + g * 8) = packed;
-    p.q_sf[row_sf_off(tok, tile_a * 4 + g, p.q_ka)] = static_cast<uint8_t>(sfb);
-  }
-}
-
 // Applies the epilogue to CH accumulator values of one thread: `row` indexes the A operand, columns
 // [col0, col0 + CH) the B operand.
 template <int CH>
@@ -261,52 +243,125 @@ __device__ __forceinline__ void epilogue_chunk(const DevParams& p, float (&v)[CH
 // token with the weights on the 128-row side: out[tok][grow0 ..]. The split-K reduce hands its sums over in this
 // shape (one 16-byte distributed-shared-memory load per partial), so gate / up pairs sit in one thread and every
 // store is 4 to 16 bytes wide and contiguous across the warp.
-__device__ __forceinline__ void epilogue_rows4(const DevParams& p, float4 v, int grow0, int row_lim, int tok,
-                                               float alpha, __nv_bfloat16* stg_row) {
-  if (p.tok_scale != nullptr) alpha *= p.tok_scale[tok];
-  float x[4] = {v.x * alpha, v.y * alpha, v.z * alpha, v.w * alpha};
+template <int NC>
+__device__ __forceinline__ void epilogue_rows4(const DevParams& p, const float4 (&v)[NC], const bool (&live)[NC],
+                                               const int (&tok)[NC], int grow0, int row_lim, float alpha,
+                                               float q_inv_gs) {
+  // NC independent columns per call, every stage written as a loop over them: the work per column is a chain of
+  // dependent special-function and conversion instructions, and with four epilogue warps per CTA nothing else
+  // hides their latency, so the columns' chains are interleaved.
+  float x[NC][4];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const float a = p.tok_scale != nullptr && live[c] ? alpha * p.tok_scale[tok[c]] : alpha;
+    x[c][0] = v[c].x * a; x[c][1] = v[c].y * a; x[c][2] = v[c].z * a; x[c][3] = v[c].w * a;
+  }
   const bool full = grow0 + 3 < row_lim && (p.ldo & 3) == 0;
   if (p.epilogue == kEpiSiluMulQuant) {
-    *reinterpret_cast<uint32_t*>(stg_row) = pack_bf16(silu(x[0]) * x[1], silu(x[2]) * x[3]);
+    // This thread holds output features f0, f0 + 1 (f0 = grow0 / 2) of each token; the 8 lanes that share lane / 8
+    // hold one 16-feature NVFP4 group. Group maximum and the 8 packed bytes travel by shuffles (every lane of the
+    // warp is here: the column loop is warp-uniform); lane 0 of the group writes the 8 bytes, lane 0 of the warp
+    // the four scale bytes of the token, which are one aligned 32-bit word of the swizzled block.
+    float y0[NC], y1[NC], amax[NC];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      y0[c] = __bfloat162float(__float2bfloat16(silu(x[c][0]) * x[c][1]));   // rounded as a bf16 store would
+      y1[c] = __bfloat162float(__float2bfloat16(silu(x[c][2]) * x[c][3]));
+      amax[c] = fmaxf(fabsf(y0[c]), fabsf(y1[c]));
+    }
+#pragma unroll
+    for (int sh = 1; sh <= 4; sh <<= 1)
+#pragma unroll
+      for (int c = 0; c < NC; ++c) amax[c] = fmaxf(amax[c], __shfl_xor_sync(0xffffffffu, amax[c], sh));
+    uint32_t sfb[NC], pk[NC], hi[NC], sfw[NC];
+    const int j = threadIdx.x & 7;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      sfb[c] = float_to_e4m3(amax[c] * (1.f / 6.f) * q_inv_gs);
+      const float sf = e4m3_to_float(sfb[c]);
+      const float inv = sf > 0.f ? 1.f / (sf * (1.f / q_inv_gs)) : 0.f;
+      pk[c] = e2m1x2(y0[c] * inv, y1[c] * inv) << (8 * (j & 3));
+      sfw[c] = sfb[c] << (8 * ((threadIdx.x >> 3) & 3));
+    }
+#pragma unroll
+    for (int c = 0; c < NC; ++c) pk[c] |= __shfl_xor_sync(0xffffffffu, pk[c], 1);
+#pragma unroll
+    for (int c = 0; c < NC; ++c) pk[c] |= __shfl_xor_sync(0xffffffffu, pk[c], 2);
+#pragma unroll
+    for (int c = 0; c < NC; ++c) hi[c] = __shfl_xor_sync(0xffffffffu, pk[c], 4);
+#pragma unroll
+    for (int c = 0; c < NC; ++c) sfw[c] |= __shfl_xor_sync(0xffffffffu, sfw[c], 8);
+#pragma unroll
+    for (int c = 0; c < NC; ++c) sfw[c] |= __shfl_xor_sync(0xffffffffu, sfw[c], 16);
+    const int grp = grow0 >> 5;                        // 16-feature group index within a token's row
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      if (!live[c]) continue;
+      if (j == 0)
+        *reinterpret_cast<uint2*>(p.q_out + static_cast<size_t>(tok[c]) * p.q_ld + grp * 8) = make_uint2(pk[c], hi[c]);
+      if ((threadIdx.x & 31) == 0)
+        *reinterpret_cast<uint32_t*>(p.q_sf + row_sf_off(tok[c], grp, p.q_ka)) = sfw[c];
+    }
   } else if (p.epilogue == kEpiSiluMul) {
-    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(tok) * p.ldo + (grow0 >> 1);
-    if (full) {
-      *reinterpret_cast<uint32_t*>(out) = pack_bf16(silu(x[0]) * x[1], silu(x[2]) * x[3]);
-    } else {
-      if (grow0 + 1 < row_lim) out[0] = __float2bfloat16(silu(x[0]) * x[1]);
-      if (grow0 + 3 < row_lim) out[1] = __float2bfloat16(silu(x[2]) * x[3]);
+    uint32_t w[NC];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) w[c] = pack_bf16(silu(x[c][0]) * x[c][1], silu(x[c][2]) * x[c][3]);
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      if (!live[c]) continue;
+      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(tok[c]) * p.ldo + (grow0 >> 1);
+      if (full) {
+        *reinterpret_cast<uint32_t*>(out) = w[c];
+      } else {
+        if (grow0 + 1 < row_lim) out[0] = __float2bfloat16(bf16_lo(w[c]));
+        if (grow0 + 3 < row_lim) out[1] = __float2bfloat16(bf16_hi(w[c]));
+      }
     }
   } else if (p.epilogue == kEpiStoreF32) {
-    float* out = static_cast<float*>(p.out) + static_cast<long long>(tok) * p.ldo + grow0;
-    if (full) {
-      *reinterpret_cast<float4*>(out) = make_float4(x[0], x[1], x[2], x[3]);
-    } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (grow0 + i < row_lim) out[i] = x[i];
+    for (int c = 0; c < NC; ++c) {
+      if (!live[c]) continue;
+      float* out = static_cast<float*>(p.out) + static_cast<long long>(tok[c]) * p.ldo + grow0;
+      if (full) {
+        *reinterpret_cast<float4*>(out) = make_float4(x[c][0], x[c][1], x[c][2], x[c][3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (grow0 + i < row_lim) out[i] = x[c][i];
+      }
     }
   } else {
-    const long long o = static_cast<long long>(tok) * p.ldo + grow0;
-    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + o;
-    if (full) {
-      if (p.epilogue == kEpiResidual) {
-        const uint2 r = *reinterpret_cast<const uint2*>(p.residual + o);
-        x[0] += bf16_lo(r.x); x[1] += bf16_hi(r.x); x[2] += bf16_lo(r.y); x[3] += bf16_hi(r.y);
-      }
-      if (p.epilogue == kEpiRelu2) {
+    uint2 r[NC];
+    if (p.epilogue == kEpiResidual && full) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) x[i] = x[i] > 0.f ? x[i] * x[i] : 0.f;
-      }
-      *reinterpret_cast<uint2*>(out) = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
-    } else {
+      for (int c = 0; c < NC; ++c)
+        r[c] = live[c] ? *reinterpret_cast<const uint2*>(p.residual + static_cast<long long>(tok[c]) * p.ldo + grow0)
+                       : make_uint2(0u, 0u);
+    }
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (grow0 + i < row_lim) {
-          float y = x[i];
-          if (p.epilogue == kEpiResidual) y += __bfloat162float(p.residual[o + i]);
-          if (p.epilogue == kEpiRelu2) y = y > 0.f ? y * y : 0.f;
-          out[i] = __float2bfloat16(y);
+    for (int c = 0; c < NC; ++c) {
+      if (!live[c]) continue;
+      const long long o = static_cast<long long>(tok[c]) * p.ldo + grow0;
+      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + o;
+      if (full) {
+        if (p.epilogue == kEpiResidual) {
+          x[c][0] += bf16_lo(r[c].x); x[c][1] += bf16_hi(r[c].x); x[c][2] += bf16_lo(r[c].y); x[c][3] += bf16_hi(r[c].y);
         }
+        if (p.epilogue == kEpiRelu2) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) x[c][i] = x[c][i] > 0.f ? x[c][i] * x[c][i] : 0.f;
+        }
+        *reinterpret_cast<uint2*>(out) = make_uint2(pack_bf16(x[c][0], x[c][1]), pack_bf16(x[c][2], x[c][3]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (grow0 + i < row_lim) {
+            float y = x[c][i];
+            if (p.epilogue == kEpiResidual) y += __bfloat162float(p.residual[o + i]);
+            if (p.epilogue == kEpiRelu2) y = y > 0.f ? y * y : 0.f;
+            out[i] = __float2bfloat16(y);
+          }
+      }
     }
   }
 }
@@ -736,9 +791,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
       const int c_begin = split * per;
       const int c_end = min(ncols, c_begin + per);
       const uint32_t part_local = smem_u32(smem);
-      const bool requant = p.epilogue == kEpiSiluMulQuant;
-      // kEpiSiluMulQuant: this CTA's token slice is parked behind the fp32 partial (which peers still read)
-      __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + BN * BM * 4);
+      const float q_inv_gs = p.epilogue == kEpiSiluMulQuant ? 1.f / *p.q_gscale : 0.f;
       if (p.swap) {
         // Weights on the 128-row side: the partials are [token column][128 rows] fp32, so four consecutive rows of
         // one column are one 16-byte load. A thread owns rows 4 r4 .. 4 r4 + 3 of every fourth column of the
@@ -753,16 +806,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         if (p.splits == 1) {
           // one partial, this CTA's own: plain shared-memory loads (no cluster addressing), four columns in flight
           const float* part = reinterpret_cast<const float*>(smem);
-          for (int c = c_begin + cg; c < c_end; c += 16) {
-            float4 v[4];
+          constexpr int NC = BN >= 64 ? 8 : 4;      // columns in flight per thread (latency hiding, see epilogue_rows4)
+          for (int c = c_begin + cg; c < c_end; c += 4 * NC) {
+            float4 v[NC];
+            bool live[NC];
+            int tok[NC];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              if (c + 4 * i < c_end) v[i] = *reinterpret_cast<const float4*>(part + (c + 4 * i) * BM + lrow0);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              if (c + 4 * i < c_end)
-                epilogue_rows4(p, v[i], grow0, row_lim, b_row0 + c + 4 * i, alpha,
-                               stg + (c + 4 * i - c_begin) * 64 + (lrow0 >> 1));
+            for (int i = 0; i < NC; ++i) {
+              live[i] = c + 4 * i < c_end;
+              tok[i] = b_row0 + c + 4 * i;
+              v[i] = live[i] ? *reinterpret_cast<const float4*>(part + (c + 4 * i) * BM + lrow0)
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            epilogue_rows4<NC>(p, v, live, tok, grow0, row_lim, alpha, q_inv_gs);
           }
         } else
         for (int c = c_begin + cg; c < c_end; c += 8) {
@@ -781,8 +837,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
               sa.x += a[s].x; sa.y += a[s].y; sa.z += a[s].z; sa.w += a[s].w;
               if (two) { sb.x += b[s].x; sb.y += b[s].y; sb.z += b[s].z; sb.w += b[s].w; }
             }
-          epilogue_rows4(p, sa, grow0, row_lim, b_row0 + c, alpha, stg + (c - c_begin) * 64 + (lrow0 >> 1));
-          if (two) epilogue_rows4(p, sb, grow0, row_lim, b_row0 + c + 4, alpha, stg + (c + 4 - c_begin) * 64 + (lrow0 >> 1));
+          const float4 vs[2] = {sa, sb};
+          const bool live[2] = {true, two};
+          const int tok[2] = {b_row0 + c, b_row0 + c + 4};
+          epilogue_rows4<2>(p, vs, live, tok, grow0, row_lim, alpha, q_inv_gs);
         }
       } else {
       for (int c0 = c_begin; c0 < c_end; c0 += 16) {
@@ -797,10 +855,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         }
         epilogue_chunk<16>(p, v, row, row_lim, b_row0 + c0, b_row0 + c_end, alpha, lane);
       }
-      }
-      if (requant) {
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (c_end > c_begin) quant_stage(p, stg, c_end - c_begin, b_row0 + c_begin, tile_a, static_cast<int>(threadIdx.x) - 64);
       }
     }
     prof_mark(p, 5, t_entry);

@@ -397,6 +397,15 @@ __device__ __forceinline__ uint32_t float_to_e2m1(float x) {
   else c = 7;
   return c | (x < 0.f ? 8u : 0u);
 }
+// Two floats -> one byte of e2m1 codes (low nibble = `lo`), round to nearest even, saturating: the hardware
+// conversion, same grid and tie rule as float_to_e2m1.
+__device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}"
+      : "=r"(r)
+      : "f"(hi), "f"(lo));
+  return r;
+}
 __device__ __forceinline__ float e2m1_to_float(uint32_t c) {
   const float t[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
   const float v = t[c & 7];

@@ -120,7 +120,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
                                      __nv_bfloat16* __restrict__ q_out, void* __restrict__ k_pool,
                                      void* __restrict__ v_pool, long long pool_stride, long long head_stride, int hq, int hkv,
                                      int d, int rot,
-                                     int kv_fp8, float kv_inv_scale, int q_gate) {
+                                     int kv_fp8, float kv_inv_scale, int q_gate, uint8_t* __restrict__ k_sf,
+                                     uint8_t* __restrict__ v_sf, long long sf_pool_stride, long long sf_head_stride) {
   grid_dep_wait();     // may run as a programmatic dependent of the QKV projection
   grid_dep_launch();
   const int t = blockIdx.x;
@@ -148,6 +149,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
     }
     __nv_bfloat16* dst_bf = nullptr;
     uint8_t* dst_f8 = nullptr;
+    uint8_t* dst_f4 = nullptr;      // kv_fp8 == 2: packed e2m1 row (d / 2 bytes) + its d / 16 ue4m3 block scales
+    uint8_t* dst_sf = nullptr;
     if (is_q) {
       dst_bf = q_out + (static_cast<long long>(t) * hq + hd) * d;
     } else {
@@ -155,8 +158,15 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
       const int kh = is_k ? hd - hq : hd - hq - hkv;
       void* pool = is_k ? k_pool : v_pool;
       const long long off = static_cast<long long>(slot) * pool_stride + static_cast<long long>(kh) * head_stride;
-      if (kv_fp8) dst_f8 = static_cast<uint8_t*>(pool) + off;
-      else dst_bf = static_cast<__nv_bfloat16*>(pool) + off;
+      if (kv_fp8 == 2) {
+        dst_f4 = static_cast<uint8_t*>(pool) + off;       // strides of the packed pool are in bytes
+        dst_sf = (is_k ? k_sf : v_sf) + static_cast<long long>(slot) * sf_pool_stride +
+                 static_cast<long long>(kh) * sf_head_stride;
+      } else if (kv_fp8) {
+        dst_f8 = static_cast<uint8_t*>(pool) + off;
+      } else {
+        dst_bf = static_cast<__nv_bfloat16*>(pool) + off;
+      }
     }
     for (int i = lane; i < d; i += 32) {
       float v = __bfloat162float(src[i]);
@@ -177,7 +187,20 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
         sincosf(pos * inv_freq[j], &sn, &cs);
         o = i < half ? v * cs - pv * sn : v * cs + pv * sn;
       }
-      if (dst_f8) dst_f8[i] = static_cast<uint8_t>(float_to_e4m3(o * kv_inv_scale));
+      if (dst_f4) {
+        // NVFP4 row: 16 consecutive elements (16 consecutive lanes) share a ue4m3 scale; x ~= code * scale / kv_inv_scale.
+        // d is a multiple of 32 here, so every lane of the warp takes part in the shuffles.
+        const float ob = __bfloat162float(__float2bfloat16(o));
+        float amax = fabsf(ob);
+#pragma unroll
+        for (int sh = 1; sh < 16; sh <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
+        const uint32_t sfb = float_to_e4m3(amax * (1.f / 6.f) * kv_inv_scale);
+        const float sf = e4m3_to_float(sfb);
+        const float inv = sf > 0.f ? 1.f / (sf * (1.f / kv_inv_scale)) : 0.f;
+        const float other = __shfl_xor_sync(0xffffffffu, ob, 1);
+        if ((lane & 1) == 0) dst_f4[i >> 1] = static_cast<uint8_t>(e2m1x2(ob * inv, other * inv));
+        if ((lane & 15) == 0) dst_sf[i >> 4] = static_cast<uint8_t>(sfb);
+      } else if (dst_f8) dst_f8[i] = static_cast<uint8_t>(float_to_e4m3(o * kv_inv_scale));
       else dst_bf[i] = __float2bfloat16(o);
     }
   }
@@ -262,6 +285,19 @@ int hb_gated_rmsnorm(const void* x, const void* z, const void* w, void* y, int r
   return OK();
 }
 
+// Scale pools of an NVFP4 KV cache for the NEXT hb_rope_kv_write call of this thread (kv_fp8 = 2): ue4m3 scale rows
+// [slots, kv heads, d / 16] of K and V with their strides in bytes. Consumed by that call.
+struct KvSf {
+  uint8_t* k = nullptr;
+  uint8_t* v = nullptr;
+  long long pool_stride = 0, head_stride = 0;
+};
+static thread_local KvSf g_kv_sf;
+void hb_kv_fp4_scales(void* k_sf, void* v_sf, long long pool_stride, long long head_stride) {
+  g_kv_sf.k = static_cast<uint8_t*>(k_sf); g_kv_sf.v = static_cast<uint8_t*>(v_sf);
+  g_kv_sf.pool_stride = pool_stride; g_kv_sf.head_stride = head_stride;
+}
+
 int hb_rope_kv_write(const void* qkv, long long ld_qkv, const void* positions, const void* slots,
                      const void* inv_freq, const void* q_norm_w, const void* k_norm_w, float eps, int gemma_norm,
                      void* q_out, void* k_pool, void* v_pool, long long pool_stride, long long head_stride, int tokens,
@@ -269,6 +305,7 @@ int hb_rope_kv_write(const void* qkv, long long ld_qkv, const void* positions, c
                      int d, int rot, int kv_fp8, float kv_inv_scale, int q_gate, void* stream) {
   if (tokens <= 0) return 0;
   if (rot > d || (rot & 1)) return 1;
+  if (kv_fp8 == 2 && (d % 32 != 0 || g_kv_sf.k == nullptr || g_kv_sf.v == nullptr)) return 1;
   // Few tokens (decode): spread the heads of a token over several CTAs so the grid still fills the SMs.
   const int heads = hq + 2 * hkv;
   int ysplit = 1;
@@ -276,7 +313,9 @@ int hb_rope_kv_write(const void* qkv, long long ld_qkv, const void* positions, c
   launch_dep(rope_kv_write_kernel, dim3(tokens, ysplit), dim3(256), 0, ST(stream),
       BF(qkv), ld_qkv, static_cast<const int*>(positions), static_cast<const int*>(slots),
       static_cast<const float*>(inv_freq), BF(q_norm_w), BF(k_norm_w), eps, gemma_norm, BFM(q_out), k_pool, v_pool,
-      pool_stride, head_stride, hq, hkv, d, rot, kv_fp8, kv_inv_scale, q_gate);
+      pool_stride, head_stride, hq, hkv, d, rot, kv_fp8, kv_inv_scale, q_gate, g_kv_sf.k, g_kv_sf.v,
+      g_kv_sf.pool_stride, g_kv_sf.head_stride);
+  g_kv_sf = KvSf{};
   return OK();
 }
 

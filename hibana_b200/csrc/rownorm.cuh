@@ -31,7 +31,7 @@ __device__ __forceinline__ uint32_t quant16(const float (&x)[16], float inv_gs, 
   const float inv = sf > 0.f ? 1.f / (sf * (1.f / inv_gs)) : 0.f;
   uint32_t w[2] = {0, 0};
 #pragma unroll
-  for (int i = 0; i < 16; ++i) w[i >> 3] |= float_to_e2m1(x[i] * inv) << (4 * (i & 7));
+  for (int i = 0; i < 8; ++i) w[i >> 2] |= e2m1x2(x[2 * i] * inv, x[2 * i + 1] * inv) << (8 * (i & 3));
   *packed = make_uint2(w[0], w[1]);
   return sfb;
 }
@@ -124,7 +124,7 @@ __device__ __forceinline__ void row_finish(float (&v)[MAXC][8], int h, const __n
         const float inv = sfv > 0.f ? 1.f / (sfv * (1.f / inv_gs)) : 0.f;
         uint32_t w = 0;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) w |= float_to_e2m1(y[e] * inv) << (4 * e);
+        for (int e = 0; e < 4; ++e) w |= e2m1x2(y[2 * e] * inv, y[2 * e + 1] * inv) << (8 * e);
         const size_t so = row_sf_off(static_cast<int>(out_row), c >> 1, ka);
         for (int d = 0; d < out.n; ++d) {
           reinterpret_cast<uint32_t*>(out.q[d] + out_row * (h >> 1))[c] = w;

@@ -45,7 +45,7 @@ class Executor:
         self.max_batch, self.max_ctx = max_batch, max_ctx
         if kv_slots <= 0:
             kv_slots = max_batch * max_ctx
-        dtype = kv_dtype or (torch.float8_e4m3fn if t.kv_dtype == "fp8" else torch.bfloat16)
+        dtype = kv_dtype or {"fp8": torch.float8_e4m3fn, "nvfp4": "nvfp4"}.get(t.kv_dtype, torch.bfloat16)
         kv_layers = getattr(model, "kv_layers", t.attn_layers) + (1 if getattr(model, "mtp", None) is not None else 0)
         self.kv = KvPool(kv_layers, kv_slots, t.kv_heads, t.head_dim, dtype, self.device) if kv_layers \
             else KvPool(0, kv_slots, 1, 1, dtype, self.device)
@@ -322,6 +322,8 @@ class Executor:
 
     def capture_graphs(self) -> None:
         self.runner.capture()
+        if self.spec is not None and getattr(self.spec, "graphs", None) is not None:
+            self.spec.graphs.capture()
 
     # ---- offline batch API
     def generate_batch(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams],

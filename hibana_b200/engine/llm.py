@@ -23,7 +23,7 @@ from .request import Request, SamplingParams
 from .scheduler import Scheduler, SchedulerConfig
 
 STATE_DTYPES = {"fp32": torch.float32, "fp16_sr": torch.float16, "int8": torch.int8}
-KV_DTYPES = {"bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn}
+KV_DTYPES = {"bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn, "nvfp4": "nvfp4"}
 
 
 def checkpoint_dir(weights: str) -> Optional[str]:
@@ -62,9 +62,9 @@ def plan_memory(cfg: EngineConfig, target: Target, device: torch.device, *, max_
     the ledger leaves of the memory that is free AFTER the weights were loaded; explicit `kv_pages` / `state_slots`
     win. Without a device (CPU tests) the pools are just large enough for max_batch x max_ctx."""
     tp = max(target.tp_size, 1)
-    esz = {"bf16": 2, "fp8": 1}[cfg.kv_dtype or target.kv_dtype]
+    esz = {"bf16": 2, "fp8": 1, "nvfp4": 0.5625}[cfg.kv_dtype or target.kv_dtype]     # nvfp4: 4 bits + a scale per 16
     layers = target.attn_layers + (1 if target.mtp_layers else 0) if kv_layers is None else kv_layers
-    kv_tok = layers * 2 * max(target.kv_heads, 1) * target.head_dim * esz
+    kv_tok = int(layers * 2 * max(target.kv_heads, 1) * target.head_dim * esz)
     state_slot = target.state_bytes_per_slot
     if cfg.ssm_state != "fp32" and state_slot:
         state_slot = state_slot // (2 if cfg.ssm_state == "fp16_sr" else 4) + target.recurrent_layers * 4096

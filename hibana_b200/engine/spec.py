@@ -54,6 +54,12 @@ class SpecDecoder:
         self.stats = SpecStats()
         self.feats: dict[int, torch.Tensor] = {}          # rid -> target hidden of the last committed position
         self.scratch: dict[int, int] = {}                 # rid -> scratch state slot (recurrent models)
+        # captured verify + device accept (engine/spec_graphs.py): exact greedy rounds of unconstrained requests
+        from .. import config as cfgmod
+        from .spec_graphs import VerifyGraphs
+        self.graphs = VerifyGraphs(executor.runner, depth) if cfgmod.current().device_accept else None
+        if self.graphs is not None and not self.graphs.supported():
+            self.graphs = None
 
     # ---- helpers
     def _dev(self, arr, dtype):
@@ -216,23 +222,34 @@ class SpecDecoder:
             bitmask = stack_masks(rows_m, (self.model.target.vocab + 31) // 32)
             if bitmask is not None:
                 bitmask = bitmask.to(dev)
-        target, hidden = ex.runner.forward_rows(
-            [r.table_row for r in reqs], tokens, n, [r.kv_slots[nn:nn + k + 1] for r, nn in zip(reqs, n)], mode=VERIFY,
-            want="logits_device" if (relaxed or sampled or bitmask is not None) else "all_device",
-            state_slots=[r.state_slot for r in reqs] if has_state else None, extras=extras)
-        if relaxed or sampled or bitmask is not None:
-            target = self._decide(reqs, target.view(b, k + 1, -1), drafts, bitmask)
-        target = target.view(b, k + 1)
-        # ---- accept (device), one small readback
-        stops = torch.full((b, MAX_STOPS), -1, dtype=torch.int64)
-        for i, r in enumerate(reqs):
+        stop_lists = []
+        for r in reqs:
             ids_ = list(r.params.stop_ids)[:MAX_STOPS]
             if r.eos_id is not None and not r.params.ignore_eos and len(ids_) < MAX_STOPS:
                 ids_.append(r.eos_id)
-            stops[i, :len(ids_)] = torch.tensor(ids_, dtype=torch.int64) if ids_ else stops[i, :0]
-        budget = torch.tensor([max(r.remaining, 1) for r in reqs], dtype=torch.int32)
-        emitted, count, accepted = sampling.accept_greedy(target, drafts, stops.to(dev), budget.to(dev))
-        emitted_h, count_h, acc_h = emitted.tolist(), count.tolist(), accepted.tolist()
+            stop_lists.append(ids_)
+        budgets = [max(r.remaining, 1) for r in reqs]
+        slot_lists = [r.kv_slots[nn:nn + k + 1] for r, nn in zip(reqs, n)]
+        if (self.graphs is not None and not (relaxed or sampled or bitmask is not None or has_state)
+                and b <= self.graphs.buckets[-1]):
+            # one upload, one captured verify + accept, one readback (engine/spec_graphs.py)
+            emitted_h, count_h, acc_h, hidden = self.graphs.run([r.table_row for r in reqs], tokens, n, slot_lists,
+                                                                stop_lists, budgets)
+        else:
+            target, hidden = ex.runner.forward_rows(
+                [r.table_row for r in reqs], tokens, n, slot_lists, mode=VERIFY,
+                want="logits_device" if (relaxed or sampled or bitmask is not None) else "all_device",
+                state_slots=[r.state_slot for r in reqs] if has_state else None, extras=extras)
+            if relaxed or sampled or bitmask is not None:
+                target = self._decide(reqs, target.view(b, k + 1, -1), drafts, bitmask)
+            target = target.view(b, k + 1)
+            # ---- accept (device), one small readback
+            stops = torch.full((b, MAX_STOPS), -1, dtype=torch.int64)
+            for i, ids_ in enumerate(stop_lists):
+                stops[i, :len(ids_)] = torch.tensor(ids_, dtype=torch.int64) if ids_ else stops[i, :0]
+            budget = torch.tensor(budgets, dtype=torch.int32)
+            emitted, count, accepted = sampling.accept_greedy(target, drafts, stops.to(dev), budget.to(dev))
+            emitted_h, count_h, acc_h = emitted.tolist(), count.tolist(), accepted.tolist()
         # ---- commit
         sel_rows, new_indptr = [], [0]
         for i, r in enumerate(reqs):

@@ -1,0 +1,172 @@
+"""CUDA-graph verify + device-resident accept for speculative rounds.
+
+A speculative round's verify forward runs k + 1 rows per request (the pending token and k drafted tokens). Run
+eagerly it costs hundreds of host-launched kernels plus numpy packing and several small uploads; here it is one
+captured graph per (batch bucket, depth):
+
+    one pinned upload (token-level rows: ids / positions / KV slots / block-table rows; request-level rows: table
+    row, context length, token budget, stop ids)
+      -> graph: block-table update, ragged verify forward (uniform k + 1 rows per request, static q_indptr),
+         lm_head, argmax of every row, the accept kernel (longest exact prefix + the target's own token, cut at
+         stop ids and the budget)
+      -> one readback of META = [emitted tokens | count | accepted] per request.
+
+The verified hidden states stay on the device for the drafter (MTP feature of the last accepted row). Padded
+requests of a bucket point at block-table row 0 / KV slot 0, as in the decode graphs. On a CPU device the same
+body runs eagerly over the same static buffers, which is what the CPU tests compare with the host round.
+Covers exact greedy acceptance of unconstrained requests on models without recurrent state; relaxed / sampled
+acceptance, grammar masks and recurrent replay take the eager round. Reference: hibana/engine/spec_graphs.py:43-164
+(VerifyGraphs), hibana/engine/accept_graphs.py:50-310 (AcceptGraphs), hibana/proposers/mtp_graphs.py:15 (DraftGraphs).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import _native as nv
+from ..ops import attention, sampling
+from .context import VERIFY, ForwardContext
+from .request import MAX_STOPS
+
+T_IDS, T_POS, T_SLOT, T_ROW, T_FIELDS = 0, 1, 2, 3, 4          # token-level rows
+S_ROW, S_CTX, S_BUDGET, S_STOP0 = 0, 1, 2, 3                  # request-level rows (stop ids follow)
+
+
+class VerifyBuffers:
+    def __init__(self, bucket: int, k1: int, device: torch.device):
+        self.bucket, self.k1 = bucket, k1
+        rows = bucket * k1
+        self.n_tok, self.n_seq = T_FIELDS * rows, (S_STOP0 + MAX_STOPS) * bucket
+        pin = device.type == "cuda"
+        self.host = torch.zeros(self.n_tok + self.n_seq, dtype=torch.int32, pin_memory=pin)
+        self.np = self.host.numpy()
+        self.dev = torch.zeros(self.n_tok + self.n_seq, dtype=torch.int32, device=device)
+        self.tok = self.dev[:self.n_tok].view(T_FIELDS, rows)
+        self.seq = self.dev[self.n_tok:].view(S_STOP0 + MAX_STOPS, bucket)
+        self.tok_np = self.np[:self.n_tok].reshape(T_FIELDS, rows)
+        self.seq_np = self.np[self.n_tok:].reshape(S_STOP0 + MAX_STOPS, bucket)
+        self.indptr = (torch.arange(bucket + 1, dtype=torch.int32) * k1).to(device)
+        self.meta = torch.zeros(bucket, k1 + 2, dtype=torch.int64, device=device)
+        self.meta_host = torch.zeros(bucket, k1 + 2, dtype=torch.int64, pin_memory=pin)
+        self.hidden: Optional[torch.Tensor] = None      # [bucket * k1, H] pre-norm hidden of every verified row
+        self.graph = None
+        self.workspace = None
+        self.splits = 1
+
+
+class VerifyGraphs:
+    def __init__(self, runner, depth: int, buckets: Optional[Sequence[int]] = None):
+        self.runner, self.model = runner, runner.model
+        self.k1 = depth + 1
+        self.device = runner.device
+        self.buckets = tuple(buckets or runner.buckets)
+        self.bufs = {b: VerifyBuffers(b, self.k1, self.device) for b in self.buckets}
+        self.launches: dict = {}
+        self.rounds = 0
+
+    def supported(self) -> bool:
+        return self.runner.state_pool is None
+
+    # ---- the captured body
+    def _body(self, buf: VerifyBuffers) -> None:
+        r = self.runner
+        b, k1 = buf.bucket, buf.k1
+        tok, seq = buf.tok, buf.seq
+        r.block_table.index_put_((tok[T_ROW].long(), tok[T_POS].long()), tok[T_SLOT])
+        ctx = ForwardContext(VERIFY, positions=tok[T_POS], slots=tok[T_SLOT], kv_indices=r.block_table,
+                             ctx_len=seq[S_CTX], q_indptr=buf.indptr, seq_rows=seq[S_ROW], max_rows=k1, batch=b,
+                             attn_splits=buf.splits, attn_workspace=buf.workspace, comm=r.comm,
+                             seq_starts_host=[k1] * b, state_slots=seq[S_ROW], extras={"want_hidden": True})
+        h = r._forward(tok[T_IDS].long(), ctx)
+        buf.hidden = ctx.extras.get("hidden")
+        logits = self.model.logits(h, r.comm) if r.comm is not None else self.model.logits(h)
+        target = sampling.argmax(logits).view(b, k1)
+        drafts = tok[T_IDS].view(b, k1)[:, 1:].long().contiguous()
+        stops = seq[S_STOP0:S_STOP0 + MAX_STOPS].t().long().contiguous()
+        emitted, count, accepted = sampling.accept_greedy(target, drafts, stops, seq[S_BUDGET].contiguous())
+        buf.meta[:, :k1].copy_(emitted)
+        buf.meta[:, k1].copy_(count)
+        buf.meta[:, k1 + 1].copy_(accepted)
+
+    def _prepare(self, buf: VerifyBuffers) -> None:
+        t = self.model.target
+        if buf.workspace is None and t.attn_layers and self.device.type == "cuda":
+            buf.splits = self.runner.attn_splits or attention.choose_splits(buf.bucket, t.kv_heads, self.runner.max_ctx,
+                                                                            row_chunks=1)
+            if buf.splits > 1:
+                buf.workspace = attention.AttnWorkspace(buf.bucket * buf.k1, t.q_heads, t.head_dim, buf.splits,
+                                                        self.device)
+
+    def capture(self) -> None:
+        if self.device.type != "cuda" or not self.runner.use_graphs:
+            return
+        for b, buf in self.bufs.items():
+            self._prepare(buf)
+            buf.dev.zero_()
+            buf.seq[S_CTX].fill_(buf.k1)
+            buf.seq[S_BUDGET].fill_(1)
+            buf.tok[T_POS].copy_(torch.arange(buf.k1, dtype=torch.int32, device=self.device).repeat(b))
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._body(buf)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            before = nv.LAUNCHES
+            with torch.cuda.graph(g):
+                self._body(buf)
+            self.launches[b] = nv.LAUNCHES - before
+            buf.graph = g
+
+    # ---- one round
+    def _bucket(self, n: int) -> int:
+        for b in self.buckets:
+            if b >= n:
+                return b
+        raise ValueError(f"batch {n} exceeds the largest verify bucket {self.buckets[-1]}")
+
+    def run(self, rows: Sequence[int], tokens: Sequence[Sequence[int]], starts: Sequence[int],
+            slot_lists: Sequence[Sequence[int]], stop_lists: Sequence[Sequence[int]], budgets: Sequence[int]):
+        """rows[i]: block-table row; tokens[i]: [pending, d_1 .. d_k]; starts[i]: position of the pending token;
+        slot_lists[i]: the k + 1 reserved KV slots. Returns (emitted [n][k + 1], count [n], accepted [n], hidden)
+        with the three lists on the host and `hidden` [bucket * (k + 1), H] on the device."""
+        n, k1 = len(rows), self.k1
+        buf = self.bufs[self._bucket(n)]
+        self._prepare(buf)
+        tn, sn = buf.tok_np, buf.seq_np
+        tn[:] = 0
+        sn[:] = 0
+        sn[S_CTX] = k1
+        sn[S_BUDGET] = 1
+        sn[S_STOP0:] = -1
+        tn[T_POS] = np.tile(np.arange(k1, dtype=np.int32), buf.bucket)
+        m = n * k1
+        tn[T_IDS, :m] = np.asarray(tokens, dtype=np.int32).reshape(-1)
+        st = np.asarray(starts, dtype=np.int32)
+        tn[T_POS, :m] = (st[:, None] + np.arange(k1, dtype=np.int32)[None, :]).reshape(-1)
+        tn[T_SLOT, :m] = np.asarray(slot_lists, dtype=np.int32).reshape(-1)
+        tn[T_ROW, :m] = np.repeat(np.asarray(rows, dtype=np.int32), k1)
+        sn[S_ROW, :n] = rows
+        sn[S_CTX, :n] = st + k1
+        sn[S_BUDGET, :n] = budgets
+        for i, ids in enumerate(stop_lists):
+            ids = list(ids)[:MAX_STOPS]
+            sn[S_STOP0:S_STOP0 + len(ids), i] = ids
+        buf.dev.copy_(buf.host, non_blocking=True)
+        self.runner.h2d_bytes += buf.host.numel() * 4
+        if buf.graph is not None:
+            buf.graph.replay()
+        else:
+            self._body(buf)
+        buf.meta_host.copy_(buf.meta, non_blocking=True)
+        self.runner._queue_status_read()
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        self.runner.d2h_bytes += buf.meta.numel() * 8
+        self.runner._raise_on_status()
+        self.rounds += 1
+        meta = buf.meta_host[:n].tolist()
+        return ([row[:k1] for row in meta], [row[k1] for row in meta], [row[k1 + 1] for row in meta], buf.hidden)

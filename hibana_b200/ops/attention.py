@@ -21,6 +21,7 @@ P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
 nv.register("hb_attn_paged", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, Fl, I, Fl, I, P])
 
 nv.register("hb_attn_merge", [P, P, P, L, I, I, P])
+nv.register("hb_attn_fp4_scales", [P, P, L, L], void=True)
 nv.register("hb_attn_merge_quant", [P, P, L, I, I, I, P, P, P, I, P])
 nv.register("hb_attn_decode", [P, P, P, L, L, P, L, P, P, P, P, P, P, I, I, I, I, I, I, Fl, I, L, P, P])
 
@@ -79,8 +80,13 @@ def paged_attention_ref(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
         if rows == 0 or ctx == 0:
             continue
         idx = kv_indices[i, :ctx].long()
-        k = k_pool[idx].float() * kv_scale     # [ctx, hkv, d]
-        v = v_pool[idx].float() * kv_scale
+        if getattr(k_pool, "sf", None) is not None:     # NVFP4 pool: packed values + block scales
+            from ..cache.kv_pool import dequant_rows
+            k = dequant_rows(k_pool[idx], k_pool.sf[idx], kv_scale)
+            v = dequant_rows(v_pool[idx], v_pool.sf[idx], kv_scale)
+        else:
+            k = k_pool[idx].float() * kv_scale     # [ctx, hkv, d]
+            v = v_pool[idx].float() * kv_scale
         qq = q[r0:r1].float().view(rows, hkv, g, d)
         s = torch.einsum("rhgd,chd->rhgc", qq, k) * scale
         if causal:
@@ -120,6 +126,7 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     b = ctx_len.shape[0]
     if splits > 1 and (workspace is None or workspace.rows < t or workspace.splits != splits):
         workspace = AttnWorkspace(t, hq, d, splits, q.device)
+    fp4 = getattr(k_pool, "sf", None) is not None
     fp8 = k_pool.dtype != torch.bfloat16
     cfg = cfgmod.current()
     if not fp8 and max_rows * (hq // hkv) <= 16 and d in (64, 128, 256):
@@ -182,6 +189,9 @@ def _quant_bufs(rows: int, k: int, device):
 
 def _paged_general(q, k_pool, v_pool, kv_indices, ctx_len, q_indptr, max_rows, seq_rows, scale, kv_scale, causal,
                    splits, workspace, out, cfg, fp8, b, t, hq, hkv, d):
+    if getattr(k_pool, "sf", None) is not None:
+        fp8 = 2       # NVFP4 pool: the split-KV kernel dequantises rows as it loads them
+        nv.lib().hb_attn_fp4_scales(k_pool.sf.data_ptr(), v_pool.sf.data_ptr(), k_pool.sf.stride(0), k_pool.sf.stride(1))
     if not fp8 and d in (64, 128, 256) and q_indptr is not None and cfg.prefill_attn == "tc":
         st = nv.device_state(q.device)
         nv.check(nv.lib().hb_attn_prefill(

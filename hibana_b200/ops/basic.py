@@ -110,9 +110,14 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[to
     t = qkv.shape[0]
     rot = d if rot is None else rot
     qw = hq * d * (2 if q_gate else 1)
+    k_sf = getattr(k_pool, "sf", None) if k_pool is not None else None      # NVFP4 pool: scale rows ride along
     if nv.use_native(qkv):
         q_out = torch.empty(t, hq, d, dtype=torch.bfloat16, device=qkv.device)
         fp8 = k_pool is not None and k_pool.dtype != torch.bfloat16
+        if k_sf is not None:
+            fp8 = 2
+            nv.register("hb_kv_fp4_scales", [nv.P, nv.P, nv.L, nv.L], void=True)
+            nv.lib().hb_kv_fp4_scales(k_sf.data_ptr(), v_pool.sf.data_ptr(), k_sf.stride(0), k_sf.stride(1))
         nv.check(nv.lib().hb_rope_kv_write(
             qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), nv.ptr(slots), inv_freq.data_ptr(), nv.ptr(q_norm),
             nv.ptr(k_norm), eps, int(gemma_norm), q_out.data_ptr(), nv.ptr(k_pool), nv.ptr(v_pool),
@@ -130,7 +135,14 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[to
     k = _rope_ref(_norm_head(k, k_norm, eps, gemma_norm), positions, inv_freq, rot)
     if slots is not None and k_pool is not None:
         idx = slots.long()
-        if k_pool.dtype == torch.bfloat16:
+        if k_sf is not None:
+            from . import nvfp4
+            for pool, x_ in ((k_pool, k), (v_pool, v)):
+                rows = x_.to(torch.bfloat16).float().reshape(t * hkv, d)
+                packed, sfb = nvfp4.quantize_ref(rows, kv_scale)
+                pool[idx] = packed.view(t, hkv, d // 2)
+                pool.sf[idx] = sfb.view(t, hkv, d // 16)
+        elif k_pool.dtype == torch.bfloat16:
             k_pool[idx] = k.to(torch.bfloat16)
             v_pool[idx] = v.to(torch.bfloat16)
         else:

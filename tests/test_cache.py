@@ -145,3 +145,28 @@ def test_prefix_cache_hit_gives_same_tokens_cpu():
     again = ex.generate_batch([prompts[0]], sp)[0]
     assert again.output_ids == ref[0] and ex.stats["cached_tokens"] - before == 63
     ex.state.check()
+
+
+def test_cache_trace_pins_cache_paths_to_the_cold_run(tmp_path):
+    """The cache trace: a prefix served from the radix cache, and one restored from the SSD tier, give the same
+    first token and bit-equal last-token activations as the cold prefill of an attention-only model."""
+    import torch
+    from hibana_b200.engine import cache_trace
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import ATTN, MLP, get_target, scaled
+    t = scaled(get_target("tiny"), layers=None, mtp_layers=0, weight_format="bf16")
+    t = scaled(t, layers=2)
+    import dataclasses
+    t = dataclasses.replace(t, layers=((ATTN, MLP), (ATTN, MLP)), ffn=256)
+    model = HybridModel(t, "cpu", seed=0)
+    g = torch.Generator().manual_seed(4)
+    ids = torch.randint(3, t.vocab, (600,), generator=g).tolist()
+    make = lambda: Executor(model, max_batch=2, max_ctx=1024, kv_slots=2048, use_graphs=False)  # noqa: E731
+    rep = cache_trace.run(make, ids, 520, tmp_path / "trace.json", chunk=64, ssd_dir=str(tmp_path / "ssd"))
+    assert rep["cached_prefix"] >= 512 and rep["restored_tokens"] >= 512
+    toks = rep["first_tokens"]
+    assert toks["cold"] == toks["cached"] == toks["restored"] == toks["chunked"]
+    assert rep["pairs"]["cached_vs_cold"]["max_rel_diff"] < 2e-2
+    assert rep["pairs"]["restored_vs_cached"]["equal"]            # restore is a byte copy of what the cache held
+    assert (tmp_path / "trace.json").exists() and (tmp_path / "trace.pt").exists()

@@ -68,3 +68,24 @@ def test_graph_equals_eager_gpu():
     e2.capture_graphs()
     b = e2.generate_batch(prompts, sp)
     assert [r.output_ids for r in a] == [r.output_ids for r in b]
+
+
+def test_dense_model_runs_on_an_nvfp4_kv_cache_cpu():
+    """End to end with kv_dtype = nvfp4: the pool holds 4.5 bits per element and generation stays close to the
+    bf16-KV run (first tokens equal on this tiny model)."""
+    import torch
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.dense import DenseModel
+    from hibana_b200.target import dense_tiny, scaled
+    t = scaled(dense_tiny(), weight_format="bf16")
+    model = DenseModel(t, "cpu", seed=0)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, t.vocab, (24,), generator=g).tolist() for _ in range(3)]
+    sp = SamplingParams(max_tokens=4)
+    bf = Executor(model, max_batch=4, max_ctx=64, use_graphs=False).generate_batch(prompts, sp)
+    ex = Executor(model, max_batch=4, max_ctx=64, use_graphs=False, kv_dtype="nvfp4")
+    assert ex.kv.fp4
+    f4 = ex.generate_batch(prompts, sp)
+    assert ex.kv.bytes_per_token == len(t.layers) * 2 * t.kv_heads * (t.head_dim // 2 + t.head_dim // 16)
+    assert sum(a.output_ids[0] == b.output_ids[0] for a, b in zip(bf, f4)) >= 2

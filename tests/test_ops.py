@@ -329,3 +329,61 @@ def test_sampling_full_vocab_kernel_matches_distribution(top_p):
     # the CPU statement of the same rule makes the same draws, up to rounding at CDF edges
     ref = sampling.sample(logits.cpu(), temp.cpu(), top_k.cpu(), tp.cpu(), seeds.cpu(), offs.cpu())
     assert (ref == picks).float().mean() > 0.99
+
+
+def _fp4_case(dev, hq=8, hkv=2, d=128, t=70, seed=3):
+    from hibana_b200.cache.kv_pool import KvPool
+    g = torch.Generator().manual_seed(seed)
+    pool = KvPool(1, 96, hkv, d, "nvfp4", dev)
+    qkv = (torch.randn(t, (hq + 2 * hkv) * d, generator=g) * 1.5).bfloat16().to(dev)
+    pos = torch.arange(t, dtype=torch.int32, device=dev)
+    slots = (torch.randperm(95, generator=g)[:t].int() + 1).to(dev)
+    inv = basic.rope_inv_freq(d, 1e6).to(dev)
+    q = basic.rope_kv_write(qkv, pos, slots, inv, pool.k[0], pool.v[0], hq, hkv, d, kv_scale=pool.kv_scale)
+    return pool, q, slots, qkv
+
+
+def test_nvfp4_kv_pool_write_and_attention_cpu():
+    """NVFP4 KV: rows are quantised on write (4.5 bits per element), attention over the pool equals fp32 attention
+    over the dequantised rows, and the rows stay within NVFP4 rounding of what was written."""
+    from hibana_b200.cache.kv_pool import KvPool
+    pool, q, slots, qkv = _fp4_case("cpu")
+    assert pool.bytes_per_token == 2 * 2 * (64 + 8) and pool.k[0].dtype == torch.uint8
+    kd = pool.dequantized(0, 0, slots.tolist())
+    bf = KvPool(1, 96, 2, 128, torch.bfloat16, "cpu")
+    basic.rope_kv_write(qkv, torch.arange(70, dtype=torch.int32), slots, basic.rope_inv_freq(128, 1e6), bf.k[0],
+                        bf.v[0], 8, 2, 128)
+    want = bf.k[0][slots.long()].float()
+    assert float((kd - want).norm() / want.norm()) < 0.12
+    idx = slots.view(1, -1)
+    ctx = torch.tensor([70], dtype=torch.int32)
+    out = attention.paged_attention(q[-1:], pool.k[0], pool.v[0], idx, ctx, kv_scale=pool.kv_scale)
+    k, v = pool.dequantized(0, 0, slots.tolist()), pool.dequantized(0, 1, slots.tolist())
+    qq = q[-1].float().view(2, 4, 128)
+    s = torch.einsum("hgd,chd->hgc", qq, k) / 128 ** 0.5
+    ref = torch.einsum("hgc,chd->hgd", torch.softmax(s, -1), v).reshape(1, 8, 128)
+    _close(out, ref, 2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows", [1, 3])
+def test_nvfp4_kv_kernels_match_reference(rows):
+    """GPU: the write kernel produces the reference quantiser's bytes, and the attention kernel over the NVFP4
+    pool matches the CPU reference over the same pool (decode and a short verify block, split and unsplit)."""
+    cpu, qc, slots, _ = _fp4_case("cpu")
+    gpu, qg, _, _ = _fp4_case("cuda")
+    sl = slots.long()
+    assert torch.equal(gpu.k[0][sl.cuda()].cpu(), cpu.k[0][sl]) and torch.equal(gpu.k[0].sf[sl.cuda()].cpu(), cpu.k[0].sf[sl])
+    assert torch.equal(gpu.v[0][sl.cuda()].cpu(), cpu.v[0][sl]) and torch.equal(gpu.v[0].sf[sl.cuda()].cpu(), cpu.v[0].sf[sl])
+    _close(qg, qc, 2e-2)
+    idx = slots.view(1, -1)
+    ctx = torch.tensor([70], dtype=torch.int32)
+    indptr = torch.tensor([0, rows], dtype=torch.int32)
+    ref = attention.paged_attention(qc[-rows:], cpu.k[0], cpu.v[0], idx, ctx, q_indptr=indptr, max_rows=rows,
+                                    kv_scale=cpu.kv_scale)
+    for splits in (1, 2):
+        got = attention.paged_attention(qg[-rows:], gpu.k[0], gpu.v[0], idx.cuda(), ctx.cuda(), q_indptr=indptr.cuda(),
+                                        max_rows=rows, kv_scale=gpu.kv_scale, splits=splits)
+        _close(got, ref, 2e-2)
+    from hibana_b200 import _native as nv
+    assert nv.read_status() == 0

@@ -181,3 +181,71 @@ def test_block_drafter_on_gpu_is_exact():
     spec = ex.generate_batch(prompts, sp)
     assert [r.output_ids for r in spec] == [r.output_ids for r in plain]
     assert ex.spec.stats.rounds > 0
+
+
+def test_device_rounds_equal_host_rounds_cpu():
+    """The captured-round form (static buffers, verify + accept kernel in one body, one META readback) makes the
+    same decisions as the host round: same tokens, same tokens per round, stop ids and budgets honoured, padded
+    bucket rows harmless; and it moves one upload and one readback per round."""
+    import torch
+    from hibana_b200 import config as cfgmod
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.dense import DenseModel
+    from hibana_b200.target import dense_tiny, scaled
+    t = scaled(dense_tiny(), weight_format="bf16")
+    model = DenseModel(t, "cpu", seed=0)
+    g = torch.Generator().manual_seed(8)
+    base = torch.randint(0, t.vocab, (10,), generator=g).tolist()
+    prompts = [base * 3, torch.randint(0, t.vocab, (18,), generator=g).tolist(), base * 2 + base[:4]]
+    plain = Executor(model, max_batch=4, max_ctx=160, use_graphs=False).generate_batch(
+        prompts, SamplingParams(max_tokens=20))
+    stop_tok = plain[0].output_ids[7]
+    params = [SamplingParams(max_tokens=20, stop_ids=(stop_tok,)), SamplingParams(max_tokens=11),
+              SamplingParams(max_tokens=20)]
+    outs = {}
+    for on in (False, True):
+        with cfgmod.using(device_accept=on):
+            ex = Executor(model, max_batch=4, max_ctx=160, use_graphs=False, buckets=(1, 4))
+            ex.enable_spec(depth=3, proposer="ngram")
+            assert (ex.spec.graphs is not None) == on
+            res = ex.generate_batch(prompts, params)
+            outs[on] = ([r.output_ids for r in res], [r.rounds for r in res], [r.finish_reason for r in res],
+                        ex.spec.graphs.rounds if on else 0)
+    assert outs[True][:3] == outs[False][:3]
+    assert outs[True][3] > 0
+    assert outs[True][0][0][-1] == stop_tok and outs[True][2][0] == "stop"
+    assert len(outs[True][0][1]) == 11 and outs[True][2][1] == "length"
+    ref = [r.output_ids for r in plain]
+    assert outs[True][0][2] == ref[2] and outs[True][0][1] == ref[1][:11]
+
+
+@pytest.mark.gpu
+def test_captured_verify_rounds_on_gpu_are_exact():
+    """CUDA-graph verify + device accept: the n-gram speculative engine equals plain greedy decoding token for
+    token on the GPU, with the rounds running as graph replays (one upload, one readback each)."""
+    import torch
+    from hibana_b200 import _native as nv
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.dense import DenseModel
+    from hibana_b200.target import dense_tiny
+    t = dense_tiny()
+    model = DenseModel(t, "cuda:0", seed=0)
+    g = torch.Generator().manual_seed(8)
+    base = torch.randint(0, t.vocab, (10,), generator=g).tolist()
+    prompts = [base * 3, torch.randint(0, t.vocab, (18,), generator=g).tolist(), base * 2 + base[:4]]
+    sp = SamplingParams(max_tokens=24)
+    plain = Executor(model, max_batch=4, max_ctx=256, use_graphs=True)
+    plain.capture_graphs()
+    want = [r.output_ids for r in plain.generate_batch(prompts, sp)]
+    ex = Executor(model, max_batch=4, max_ctx=256, use_graphs=True, buckets=(1, 2, 4))
+    ex.enable_spec(depth=2, proposer="ngram")
+    ex.capture_graphs()
+    assert ex.spec.graphs is not None and all(b.graph is not None for b in ex.spec.graphs.bufs.values())
+    h2d0, d2h0 = ex.runner.h2d_bytes, ex.runner.d2h_bytes
+    got = ex.generate_batch(prompts, sp)
+    torch.cuda.synchronize()
+    assert nv.read_status() == 0
+    assert [r.output_ids for r in got] == want
+    assert ex.spec.graphs.rounds > 0 and ex.spec.stats.emitted >= ex.spec.stats.rounds
