@@ -43,6 +43,11 @@ def build_model(target: Target, device, seed: int = 0, comm=None, weights: str =
     ckpt = checkpoint_dir(weights)
     if target.family == "dense":
         from ..models.dense import DenseModel
+        from ..weights import snapshot
+        if ckpt is not None and snapshot.is_snapshot(ckpt):
+            model = DenseModel(target, device, seed=seed) if tp == 1 else DenseModel.sharded(target, tp, rank, device, seed)
+            snapshot.load_state(model, ckpt)
+            return model
         if ckpt is not None:
             from ..weights.checkpoint import load_dense
             return load_dense(target, ckpt, device, tp=tp, rank=rank)

@@ -187,3 +187,13 @@ def load_dense(full: Target, directory: str, device="cpu", tp: int = 1, rank: in
     model.scale = 1.0 / math.sqrt(t.head_dim)
     model.kv_layers = len(model.layers)
     return model
+
+
+def load_hybrid(full: Target, directory: str, device="cpu", tp: int = 1, rank: int = 0, seed: int = 0):
+    """A hybrid-family model from a snapshot directory (weights/snapshot.py): the model is built with this rank's
+    geometry, then every tensor is overwritten with the stored one."""
+    from ..models.hybrid import HybridModel
+    from . import snapshot
+    model = HybridModel(full, device, seed=seed) if tp == 1 else HybridModel.sharded(full, tp, rank, device, seed=seed)
+    snapshot.load_state(model, directory)
+    return model

@@ -249,3 +249,49 @@ def test_captured_verify_rounds_on_gpu_are_exact():
     assert nv.read_status() == 0
     assert [r.output_ids for r in got] == want
     assert ex.spec.graphs.rounds > 0 and ex.spec.stats.emitted >= ex.spec.stats.rounds
+
+
+def test_draft_heads_shortlist_and_vocab_parallel_cpu():
+    """Draft heads: a row subset scores only its rows, a 3-bit copy with rescoring picks the full head's argmax
+    whenever it is shortlisted, and the vocabulary-parallel head (two ranks played by two threads) returns the
+    candidates of the unsharded head on both ranks."""
+    import threading
+    import torch
+    from hibana_b200.proposers import draft_head as dh
+    import sys, os
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_tp import ThreadComm
+    g = torch.Generator().manual_seed(0)
+    head = (torch.randn(512, 128, generator=g) * 0.5).bfloat16()
+    x = torch.randn(9, 128, generator=g).bfloat16()
+    full = (x.float() @ head.float().t())
+    t = dh.TargetHead(lambda h: h.float() @ head.float().t())
+    assert torch.equal(t.argmax(x), full.argmax(-1))
+    ids, vals = t.candidates(x, 3)
+    assert torch.equal(ids, full.topk(3, -1).indices) and t.bytes == 0
+    sub = torch.arange(0, 512, 2)
+    s = dh.ShortlistHead(head, sub)
+    assert torch.equal(s.argmax(x), sub[full[:, ::2].argmax(-1)]) and s.bytes == 256 * 128 * 2
+    w3 = dh.ShortlistHead(head, None, "w3", rescore=8)
+    agree = (w3.argmax(x) == full.argmax(-1)).float().mean()
+    assert agree >= 0.85 and w3.bytes < head.numel() * 2 / 3
+    c_ids, c_vals = w3.candidates(x, 4)
+    assert c_ids.shape == (9, 4) and bool((c_vals[:, :-1] >= c_vals[:, 1:]).all())
+    conf = t.argmax_confidence(x)[1]
+    assert conf.shape == (9, 2) and bool((conf[:, 0] >= conf[:, 1]).all())
+    comm = ThreadComm(2)
+    outs = [None, None]
+
+    def run(rank):
+        vp = dh.VocabParallelHead(head[rank * 256:(rank + 1) * 256].contiguous(), comm.view(rank), rank)
+        outs[rank] = (vp.candidates(x, 3), vp.argmax(x), vp.argmax_confidence(x)[1])
+    th = [threading.Thread(target=run, args=(r,)) for r in range(2)]
+    for a in th:
+        a.start()
+    for a in th:
+        a.join(30)
+    for r in range(2):
+        (ids_r, vals_r), am, cf = outs[r]
+        assert torch.equal(ids_r, full.topk(3, -1).indices) and torch.equal(am, full.argmax(-1))
+        assert torch.allclose(vals_r, full.topk(3, -1).values, atol=1e-4)
+        assert torch.allclose(cf, conf, atol=1e-4)

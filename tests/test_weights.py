@@ -103,3 +103,43 @@ def test_gguf_reader_and_block_codecs(tmp_path):
     assert np.allclose(out, expect)
     with pytest.raises(ValueError):
         ggml.dequantize(blk, ggml.T_IQ2_XXS, (256,))
+
+
+@pytest.mark.parametrize("family", ["tiny", "flashnext"])
+def test_hybrid_snapshot_roundtrip_and_serving_from_weights(tmp_path, family):
+    """Snapshots of hybrid models: every tensor (quantised linears, expert stacks, convolution / recurrence
+    parameters, MTP head) comes back bit for bit, `weights=<dir>` builds the same model through the engine, and a
+    tensor-parallel rank round-trips its own shard."""
+    from hibana_b200 import config as cfgmod
+    from hibana_b200.engine.llm import LLM
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import get_target
+    from hibana_b200.weights import snapshot
+    t = get_target(family)
+    if family != "tiny":
+        t = scaled(t, layers=4, hidden=256, vocab=2048, q_heads=4, kv_heads=2, head_dim=64, gdn_k_heads=2,
+                   gdn_v_heads=4, gdn_head_dim=64, experts=8, top_k=2, expert_ffn=128, shared_ffn=128, hyper_streams=0,
+                   max_context=512, prefill_chunk=128, kv_dtype="bf16")
+    t = scaled(t, weight_format="nvfp4")
+    a = HybridModel(t, "cpu", seed=11)
+    snapshot.save_state(a, str(tmp_path / "ckpt"))
+    b = HybridModel(t, "cpu", seed=99)                           # different weights before loading
+    n = snapshot.load_state(b, str(tmp_path / "ckpt"))
+    ta, tb = snapshot.named_tensors(a), snapshot.named_tensors(b)
+    assert n > 20 and set(ta) == set(tb)
+    assert all(torch.equal(ta[k][2], tb[k][2]) for k in ta)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, t.vocab, (20,), generator=g).tolist() for _ in range(2)]
+    sp = SamplingParams(max_tokens=4)
+    cfg = cfgmod.EngineConfig(max_batch=2, max_context=128, cuda_graphs=False, seed=5)
+    want = [r.output_ids for r in LLM(cfg, target=t, device="cpu", model=a).generate(prompts, sp)]
+    got = [r.output_ids for r in LLM(cfg.replace(weights=str(tmp_path / "ckpt")), target=t, device="cpu").generate(prompts, sp)]
+    assert got == want
+    shard = HybridModel.sharded(t, 2, 1, "cpu", seed=11)
+    snapshot.save_state(shard, str(tmp_path / "tp"))
+    other = HybridModel.sharded(t, 2, 1, "cpu", seed=3)
+    snapshot.load_state(other, str(tmp_path / "tp"))
+    ts, to = snapshot.named_tensors(shard), snapshot.named_tensors(other)
+    assert all(torch.equal(ts[k][2], to[k][2]) for k in ts) and (tmp_path / "tp" / "rank1of2").is_dir()
+    with pytest.raises(ValueError):
+        snapshot.load_state(HybridModel(t, "cpu", seed=0), str(tmp_path / "tp" / "rank1of2"))
