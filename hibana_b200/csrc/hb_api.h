@@ -203,7 +203,8 @@ int hb_barrier(const void* const* peer_bases, int world, int rank, int slot, lon
 // ---- mixture of experts (moe.cu) -------------------------------------------------------------------------
 int hb_moe_route(const void* logits, long long ld, const void* sel_bias, int tokens, int experts, int topk,
                  int sigmoid, int renorm, float scale, void* ids, void* weights, void* stream);
-int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, int e_n, void* cnt, void* start,
+int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, int e_n, int id_base, void* cnt,
+                void* start,
                 void* pos, void* src_row, int rows_cap, void* total_rows, int tile_bn, void* tiles, void* n_tiles,
                 int tile_cap, void* stream);
 int hb_moe_tiles(const void* cnt, int experts, int tile_bn, void* tiles, void* n_tiles, int tile_cap, void* stream);

@@ -116,7 +116,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
 // Single CTA. e_lo / e_n restrict planning to the experts [e_lo, e_lo + e_n) this rank owns (expert parallelism):
 // pairs routed elsewhere get pos = -1 and are skipped by the combine.
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ ids, int pairs, int topk, int experts, int e_lo, int e_n,
+moe_plan_kernel(const int* __restrict__ ids, int pairs, int topk, int experts, int e_lo, int e_n, int id_base,
                 int* __restrict__ cnt, int* __restrict__ start, int* __restrict__ pos, int* __restrict__ src_row,
                 int rows_cap, int* __restrict__ total_rows, int tile_bn, int* __restrict__ tiles,
                 int* __restrict__ n_tiles, int tile_cap) {
@@ -126,7 +126,7 @@ moe_plan_kernel(const int* __restrict__ ids, int pairs, int topk, int experts, i
   for (int e = threadIdx.x; e < experts; e += blockDim.x) c[e] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
-    const int e = ids[i];
+    const int e = ids[i] - id_base;   // `experts` counts the experts held here; ids are global
     if (e >= e_lo && e < e_lo + e_n) atomicAdd(&c[e], 1);
   }
   __syncthreads();
@@ -175,7 +175,7 @@ moe_plan_kernel(const int* __restrict__ ids, int pairs, int topk, int experts, i
     for (int k = threadIdx.x; k < warps * experts; k += blockDim.x) wc[k] = 0;
     __syncthreads();
     const int i = base + threadIdx.x;
-    int e = i < pairs ? ids[i] : -1;
+    int e = i < pairs ? ids[i] - id_base : -1;
     if (e < e_lo || e >= e_lo + e_n) e = -1;
     const unsigned same = __match_any_sync(0xffffffffu, e);
     const int rank = __popc(same & ((1u << lane) - 1u));
@@ -292,7 +292,7 @@ int hb_moe_route(const void* logits, long long ld, const void* sel_bias, int tok
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
-int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, int e_n, void* cnt, void* start,
+int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, int e_n, int id_base, void* cnt, void* start,
                 void* pos, void* src_row, int rows_cap, void* total_rows, int tile_bn, void* tiles, void* n_tiles,
                 int tile_cap, void* stream) {
   if (tokens <= 0) return 0;
@@ -306,7 +306,7 @@ int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, in
     attr = smem;
   }
   moe_plan_kernel<<<1, 1024, smem, ST(stream)>>>(
-      static_cast<const int*>(ids), tokens * topk, topk, experts, e_lo, e_n, static_cast<int*>(cnt),
+      static_cast<const int*>(ids), tokens * topk, topk, experts, e_lo, e_n, id_base, static_cast<int*>(cnt),
       static_cast<int*>(start), static_cast<int*>(pos), static_cast<int*>(src_row), rows_cap,
       static_cast<int*>(total_rows), tile_bn, static_cast<int*>(tiles), static_cast<int*>(n_tiles), tile_cap);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;

@@ -11,7 +11,10 @@ still has to take part in the all-to-all of every MoE layer). The reference serv
 from __future__ import annotations
 
 import hashlib
-from typing import Any, Optional, Sequence
+import threading
+from typing import Any, Callable, Optional, Sequence
+
+RUNNING, FORWARD, LEAVING = 0, 1, 2      # what a rank posts in a round
 
 
 class ReplicaSet:
@@ -70,3 +73,73 @@ def lockstep_plan(has_work: Sequence[bool]) -> tuple[bool, list[bool]]:
     if not any(has_work):
         return False, [False] * len(has_work)
     return True, [not w for w in has_work]
+
+
+class Lockstep:
+    """Round protocol of data-parallel ranks that share expert-parallel layers.
+
+    Ranks schedule their own requests, so their steps differ (one prefills and decodes while another only
+    decodes, a third is idle), but every forward pass runs the all-to-all of every MoE layer and needs all ranks
+    in it. Ranks therefore align FORWARDS, not steps: before each forward a rank posts FORWARD in a round; a rank
+    with nothing to run posts RUNNING (or LEAVING once it has been told to stop and has drained) and, when any
+    other rank posted FORWARD, runs the model on an empty batch. A round is one all-gather of small host objects
+    over the control group; it also carries the messages of the data-parallel front end (commands from rank 0,
+    generated tokens back to it), so steady decoding costs one host collective per step. The loop ends in the
+    first round in which every rank posts LEAVING. The reference steps identical schedulers from broadcast
+    commands (hibana/engine/loop.py:163-182); ranks with different work are new here.
+    """
+
+    def __init__(self, allgather: Callable[[Any], list], rank: int, world: int):
+        self.allgather, self.rank, self.world = allgather, rank, world
+        self.outbox: list = []
+        self.on_items: Optional[Callable[[int, list], None]] = None
+        self.rounds = self.forward_rounds = self.empty_forwards = 0
+
+    def post(self, item) -> None:
+        """Queues a picklable message for every other rank; it travels with the next round."""
+        self.outbox.append(item)
+
+    def round(self, state: int) -> list:
+        mine, self.outbox = (int(state), self.outbox), []
+        got = self.allgather(mine)
+        self.rounds += 1
+        states = [g[0] for g in got]
+        self.forward_rounds += FORWARD in states
+        if self.on_items is not None:
+            for src, (_, items) in enumerate(got):
+                if items and src != self.rank:
+                    self.on_items(src, items)
+        return states
+
+
+class GroupAllGather:
+    """`Lockstep` transport over a torch.distributed group (the CPU control group of the ranks)."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self.world = dist.get_world_size(group)
+
+    def __call__(self, obj) -> list:
+        out = [None] * self.world
+        self.dist.all_gather_object(out, obj, group=self.group)
+        return out
+
+
+class ThreadAllGather:
+    """`Lockstep` transport between threads of one process (tests; replicas that share a GPU never use
+    kernels that wait on one another)."""
+
+    def __init__(self, world: int, timeout: float = 60.0):
+        self.world, self.timeout = world, timeout
+        self.slots: list = [None] * world
+        self.barrier = threading.Barrier(world)
+
+    def view(self, rank: int) -> Callable[[Any], list]:
+        def gather(obj):
+            self.slots[rank] = obj
+            self.barrier.wait(self.timeout)
+            out = list(self.slots)
+            self.barrier.wait(self.timeout)
+            return out
+        return gather

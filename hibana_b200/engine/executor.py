@@ -320,6 +320,10 @@ class Executor:
         self.stats["decode_steps"] += 1
         self.stats["decode_tokens"] += len(reqs)
 
+    def idle_round(self, state: int = 0) -> list:
+        """Data-parallel engine with nothing to run: one lockstep round (and the empty forward it may ask for)."""
+        return self.runner.idle_round(state)
+
     def capture_graphs(self) -> None:
         self.runner.capture()
         if self.spec is not None and getattr(self.spec, "graphs", None) is not None:

@@ -37,10 +37,19 @@ def checkpoint_dir(weights: str) -> Optional[str]:
 
 
 def build_model(target: Target, device, seed: int = 0, comm=None, weights: str = "random", tp: int = 1,
-                rank: int = 0):
+                rank: int = 0, ep: int = 1):
     """The target's model: loaded from the checkpoint directory `weights` (this rank's tensor-parallel shard is
-    cut out of the stored tensors), or random-init N(0, 0.02) from `seed` when `weights` is "random"."""
+    cut out of the stored tensors), or random-init N(0, 0.02) from `seed` when `weights` is "random". `ep` > 1
+    (with tp == 1): a data-parallel replica that keeps experts [rank * E / ep, (rank + 1) * E / ep) of every MoE
+    layer and everything else whole."""
     ckpt = checkpoint_dir(weights)
+    if ep > 1 and tp == 1:
+        if ckpt is not None:
+            raise NotImplementedError("expert-parallel replicas start from random weights or a per-rank snapshot")
+        if not target.experts or target.experts % ep:
+            raise ValueError(f"{target.name}: {target.experts} experts do not divide over ep={ep}")
+        from ..models.hybrid import HybridModel
+        return HybridModel(target, device, seed=seed, ep_rank=rank, ep_size=ep)
     if target.family == "dense":
         from ..models.dense import DenseModel
         from ..weights import snapshot
@@ -107,14 +116,30 @@ def plan_memory(cfg: EngineConfig, target: Target, device: torch.device, *, max_
 
 class LLM:
     def __init__(self, cfg: Optional[EngineConfig] = None, *, target: Optional[Target] = None, device=None,
-                 model=None, max_ctx: Optional[int] = None, comm=None, warmup: bool = False):
+                 model=None, max_ctx: Optional[int] = None, comm=None, warmup: bool = False, control=None,
+                 rank: Optional[int] = None):
+        """`comm`: tensor-parallel communicator (cfg.tp ranks run the same requests). `control` + `rank`: this
+        process is replica `rank` of cfg.dp data-parallel replicas and `control(obj) -> list` all-gathers small
+        host objects between them (engine/dp.py); with cfg.ep == cfg.dp the replicas share every MoE layer's experts
+        through the all-to-all of parallel/ep.py and run their forwards together."""
         self.cfg = cfg = cfg or current()
         full = target or get_target(cfg.target)
         self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
         tp = comm.world if comm is not None and cfg.tp > 1 else 1
-        rank = comm.rank if comm is not None else 0
-        self.model = model or build_model(full, self.device, cfg.seed, comm, cfg.weights, tp=tp, rank=rank)
+        self.lockstep = self.ep = None
+        if cfg.dp > 1:
+            if cfg.tp != 1:
+                raise NotImplementedError("data-parallel replicas of tensor-parallel groups are not supported")
+            if control is None or rank is None:
+                raise ValueError("dp > 1 needs the replicas' control all-gather and this replica's rank")
+            from .dp import Lockstep
+            self.lockstep = Lockstep(control, rank, cfg.dp)
+        rank = comm.rank if comm is not None else (rank or 0)
+        ep = cfg.ep if cfg.dp > 1 and cfg.ep == cfg.dp else 1
+        self.model = model or build_model(full, self.device, cfg.seed, comm, cfg.weights, tp=tp, rank=rank, ep=ep)
         self.target = self.model.target
+        if ep > 1:
+            self.ep = self._expert_parallel(ep, rank, control)
         mem = plan_memory(cfg, self.target, self.device, max_ctx=max_ctx,
                           comm_bytes=getattr(comm, "heap_bytes", 0) if comm is not None else 0,
                           kv_layers=getattr(self.model, "kv_layers", None) if getattr(self.model, "mtp", None) is None
@@ -127,6 +152,7 @@ class LLM:
                                  state_slots=mem["state_slots"],
                                  kv_dtype=KV_DTYPES[cfg.kv_dtype] if cfg.kv_dtype else None,
                                  state_dtype=STATE_DTYPES[cfg.ssm_state], debug_sync=cfg.debug_sync)
+        self.executor.runner.ep = self.ep          # before graphs are captured: the all-to-all is inside them
         if cfg.ssd_dir:
             self.executor.enable_ssd_tier(cfg.ssd_dir, budget_bytes=int(cfg.ssd_budget_gb * (1 << 30)),
                                           min_prefix=cfg.ssd_min_prefix, min_gain=cfg.ssd_min_gain,
@@ -144,6 +170,21 @@ class LLM:
             self.executor.capture_graphs()
         if warmup:
             self.executor.warmup()
+        # graph capture and warm-up ran the same forwards on every replica; from here on they negotiate
+        self.executor.runner.lockstep = self.lockstep
+
+    def _expert_parallel(self, ep: int, rank: int, control):
+        t, cfg = self.target, self.cfg
+        width = t.latent or t.hidden
+        if self.device.type != "cuda":
+            from ..parallel.ep import HostExpertParallel
+            return HostExpertParallel(control, rank, ep, t.experts)
+        from ..parallel.ep import ExpertParallel
+        depth = cfg.spec_depth + 1 if cfg.spec != "off" else 1
+        tokens = max(cfg.prefill_budget, cfg.prefill_chunk or t.prefill_chunk, cfg.max_batch * depth)
+        return ExpertParallel.create(rank, ep, self.device, tokens=tokens, topk=t.top_k, experts=t.experts,
+                                     hidden=width, fmt="nvfp4" if t.weight_format == "nvfp4" else "bf16",
+                                     timeout_ms=cfg.comm_timeout_ms)
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: SamplingParams | Sequence[SamplingParams] = SamplingParams()) -> list[Request]:
@@ -151,6 +192,11 @@ class LLM:
         reqs = [self.scheduler.submit(Request(prompt_ids=list(p), params=sp)) for p, sp in zip(prompts, plist)]
         while not self.scheduler.idle():
             self.scheduler.step()
+        if self.lockstep is not None:
+            # other replicas may still be generating: keep joining their forwards until all have finished
+            from .dp import LEAVING
+            while any(s != LEAVING for s in self.executor.idle_round(LEAVING)):
+                pass
         return reqs
 
     def shutdown(self) -> None:

@@ -3,7 +3,10 @@
 `submit` returns a `Ticket` whose queue receives `("tokens", [ids])` events and finally `("done", reason)` or
 `("error", message)`. With tensor parallelism rank 0 owns the inbox and broadcasts the commands it applied at
 every publish point, so all ranks step their schedulers identically; a failure fails every ticket and marks the
-engine unhealthy. Reference: hibana/engine/loop.py:47-320.
+engine unhealthy. With data-parallel replicas (`dp`, an engine/dp.py Lockstep) rank 0 still owns HTTP and the
+inbox but every request has ONE owner: rank 0 picks the replica (least outstanding work, conversations stay with
+their cached prefix), commands and generated tokens travel with the lockstep rounds, and the replicas schedule
+independently. Reference: hibana/engine/loop.py:47-320.
 """
 from __future__ import annotations
 
@@ -38,11 +41,31 @@ class EngineUnavailable(RuntimeError):
     pass
 
 
+class _Load:
+    """Outstanding requests of one replica, as the router's `stats()` source."""
+
+    def __init__(self):
+        self.n = 0
+
+    def stats(self) -> dict:
+        return {"running": self.n, "waiting": 0}
+
+
 class EngineLoop:
-    def __init__(self, scheduler: Scheduler, channel=None, rank: int = 0, idle_sleep: float = 0.002):
+    def __init__(self, scheduler: Scheduler, channel=None, rank: int = 0, idle_sleep: float = 0.002, dp=None):
         self.sched = scheduler
         self.channel = channel          # lockstep command channel (None = single rank)
+        self.dp = dp                    # engine/dp.py Lockstep of data-parallel replicas (None = one replica)
         self.rank = rank
+        self._mail: list = []           # commands (from rank 0) and outputs (to rank 0) received in rounds
+        self._router = None
+        self._outstanding: dict[int, int] = {}    # rank 0: tid -> owner of every unfinished remote or local request
+        if dp is not None:
+            dp.on_items = lambda src, items: self._mail.extend((src, i) for i in items)
+            if rank == 0:
+                from .dp import ReplicaSet
+                loads = [_Load() for _ in range(dp.world)]
+                self._router = ReplicaSet(loads)
         self.idle_sleep = idle_sleep
         self.inbox: "queue.Queue" = queue.Queue()
         self.tickets: dict[int, Ticket] = {}
@@ -74,7 +97,7 @@ class EngineLoop:
         t = Ticket(next(self._ids), notify=notify)
         self.tickets[t.tid] = t
         constraint = constraint if constraint is not None else params.constraint
-        if constraint is not None and self.channel is not None:
+        if constraint is not None and (self.channel is not None or self.dp is not None):
             # a compiled grammar does not pickle: other ranks get its source and compile it again (self.grammars)
             constraint = ("source", constraint.kind, constraint.source, constraint.think_end)
             params = dataclasses.replace(params, constraint=None)
@@ -115,6 +138,8 @@ class EngineLoop:
         if kind == "submit":
             _, tid, ids, params, eos_id, media, constraint = cmd
             ticket = self.tickets.get(tid)
+            if ticket is None and self.dp is not None and self.rank != 0:
+                ticket = self.tickets[tid] = Ticket(tid)          # stand-in: its events go to rank 0 in rounds
             if isinstance(constraint, tuple):       # rebuilt on every rank from the broadcast source
                 gr = self.grammars() if callable(self.grammars) else self.grammars
                 constraint = gr.recompile(*constraint[1:]) if gr is not None else None
@@ -125,7 +150,12 @@ class EngineLoop:
                 self.sched.submit(req)
             except (ValueError, QueueFull) as e:
                 if ticket is not None:
-                    ticket.put(("error", str(e)))
+                    if self.dp is not None and self.rank != 0:
+                        self.dp.post(("out", tid, [], None, str(e)))
+                        self.tickets.pop(tid, None)
+                    else:
+                        ticket.put(("error", str(e)))
+                        self._finished(tid)
                     ticket.closed = True
                 return
             if ticket is not None:
@@ -163,6 +193,15 @@ class EngineLoop:
             if ticket is None or ticket.closed:
                 continue
             new = req.output_ids[ticket.cursor:]
+            if self.dp is not None and self.rank != 0:      # the ticket's consumer lives on rank 0
+                ticket.cursor += len(new)
+                if new or req.done:
+                    self.dp.post(("out", ticket.tid, list(new), req.finish_reason if req.done else None, None))
+                if req.done:
+                    ticket.closed = True
+                    self._by_rid.pop(req.rid, None)
+                    self.tickets.pop(ticket.tid, None)
+                continue
             if new:
                 ticket.cursor += len(new)
                 ticket.put(("tokens", list(new)))
@@ -171,6 +210,7 @@ class EngineLoop:
                 ticket.closed = True
                 self._by_rid.pop(req.rid, None)
                 self.tickets.pop(ticket.tid, None)
+                self._finished(ticket.tid)
 
     def _fail(self, message: str) -> None:
         self.healthy = False
@@ -186,7 +226,86 @@ class EngineLoop:
                 ticket.closed = True
         self.tickets.clear()
 
+    # ---- data-parallel replicas
+    def _route(self, cmds: list) -> list:
+        """Rank 0: gives every submit an owner and posts the commands of other owners; returns its own."""
+        mine = []
+        for c in cmds:
+            if c[0] == "submit":
+                owner = self._router.pick(c[2])
+                self._router.loops[owner].n += 1
+                self._outstanding[c[1]] = owner
+                if owner == 0:
+                    mine.append(c)
+                else:
+                    self.dp.post(("cmd", owner, c))
+            elif c[0] == "cancel":
+                owner = self._outstanding.get(c[1], 0)
+                if owner == 0:
+                    mine.append(c)
+                else:
+                    self.dp.post(("cmd", owner, c))
+            else:                                   # stop: everyone
+                self.dp.post(("cmd", -1, c))
+                mine.append(c)
+        return mine
+
+    def _finished(self, tid: int) -> None:
+        owner = self._outstanding.pop(tid, None)
+        if owner is not None and self._router is not None:
+            self._router.loops[owner].n -= 1
+
+    def _take_mail(self) -> list:
+        """Commands addressed to this rank; on rank 0 also delivers the other replicas' outputs to the tickets."""
+        mail, self._mail = self._mail, []
+        cmds = []
+        for _src, item in mail:
+            if item[0] == "cmd":
+                if item[1] in (-1, self.rank):
+                    cmds.append(item[2])
+            elif item[0] == "out" and self.rank == 0:
+                _, tid, tokens, done, error = item
+                ticket = self.tickets.get(tid)
+                if ticket is None or ticket.closed:
+                    continue
+                if tokens:
+                    ticket.put(("tokens", tokens))
+                if error is not None or done is not None:
+                    ticket.put(("error", error) if error is not None else ("done", done))
+                    ticket.closed = True
+                    self.tickets.pop(tid, None)
+                    self._finished(tid)
+            elif item[0] == "failed":
+                raise RuntimeError(f"replica {_src} failed: {item[1]}")
+        return cmds
+
+    def _run_dp(self) -> None:
+        from .dp import LEAVING, RUNNING
+        ex = self.sched.ex
+        try:
+            while True:
+                cmds = self._route(self._gather_commands()) if self.rank == 0 else []
+                for c in cmds + self._take_mail():
+                    self._apply(c)
+                if self.sched.idle():
+                    states = ex.idle_round(LEAVING if self.stopping else RUNNING)
+                    if self.stopping and all(s == LEAVING for s in states):
+                        break
+                    if 1 not in states and not self._mail:
+                        time.sleep(self.idle_sleep)
+                    continue
+                touched = self.sched.step()
+                self.steps += 1
+                self._deliver(touched)
+        except Exception as e:  # noqa: BLE001 - every failure takes the engine down cleanly
+            try:
+                self.dp.post(("failed", f"{type(e).__name__}: {e}"))
+            finally:
+                self._fail(f"{type(e).__name__}: {e}")
+
     def _run(self) -> None:
+        if self.dp is not None:
+            return self._run_dp()
         try:
             while True:
                 cmds = self._publish_commands(self._gather_commands())

@@ -179,8 +179,33 @@ class ModelRunner:
                 and hasattr(self.model, "greedy_tokens") and hasattr(self.comm, "pick_exchange"))
 
     debug_sync = False      # synchronise and read the status word after every forward (slow; pins a fault to it)
+    ep = None               # expert-parallel all-to-all handle (parallel/ep.py): MoE layers exchange rows through it
+    lockstep = None         # engine/dp.py Lockstep: data-parallel ranks align their forwards through it
+    _in_round = False
+
+    def _enter_forward(self) -> None:
+        """Data-parallel ranks with expert-parallel layers run every forward together: announce this one."""
+        if self.lockstep is not None and not self._in_round:
+            from .dp import FORWARD
+            self.lockstep.round(FORWARD)
+
+    def idle_round(self, state: int = 0) -> list:
+        """A round for a rank with nothing to run: joins the others' forward with an empty batch when there is
+        one. Returns what every rank posted."""
+        from .dp import FORWARD
+        states = self.lockstep.round(state)
+        if FORWARD in states and self.ep is not None:
+            self._in_round = True
+            try:
+                self.decode([], [], [], [])
+            finally:
+                self._in_round = False
+            self.lockstep.empty_forwards += 1
+        return states
 
     def _forward(self, ids, ctx):
+        if self.ep is not None:
+            ctx.extras["ep"] = self.ep
         if self.state_pool is not None:
             h = self.model.forward(ids, ctx, self.kv, self.state_pool)
         else:
@@ -203,6 +228,7 @@ class ModelRunner:
         sampling_rows: optional dict of per-sequence lists temp / top_k / top_p / seed / offs (greedy when None).
         """
         n = len(rows)
+        self._enter_forward()
         buf = self.bufs[self._bucket(n)]
         self._prepare_bucket(buf)
         a = buf.np
@@ -278,6 +304,7 @@ class ModelRunner:
         every row (verify), 'none' skips the head. Returns a host list (or None).
         """
         dev = self.device
+        self._enter_forward()
         counts = [len(t) for t in token_lists]
         total = sum(counts)
         b = len(rows)

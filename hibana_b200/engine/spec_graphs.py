@@ -134,6 +134,7 @@ class VerifyGraphs:
         slot_lists[i]: the k + 1 reserved KV slots. Returns (emitted [n][k + 1], count [n], accepted [n], hidden)
         with the three lists on the host and `hidden` [bucket * (k + 1), H] on the device."""
         n, k1 = len(rows), self.k1
+        self.runner._enter_forward()
         buf = self.bufs[self._bucket(n)]
         self._prepare(buf)
         tn, sn = buf.tok_np, buf.seq_np

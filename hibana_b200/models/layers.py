@@ -286,15 +286,18 @@ class MoeLayer:
         if t.moe_act == "swiglu":   # rows g0, u0, g1, u1, ... inside every expert
             fc1 = torch.stack((fc1[:, :t.expert_ffn], fc1[:, t.expert_ffn:]), dim=2).reshape(t.experts, n1, width)
         fc2 = init.normal(t.experts, width, t.expert_ffn)
-        self.experts = moe.ExpertWeights.create(fc1, fc2, t.moe_act, _fmt(t)).to(init.device)
+        per = t.experts // ep_size
+        self.e_lo, self.e_n = ep_rank * per, per
+        # an expert-parallel rank draws every expert (one seeded stream for every layout) and keeps its range
+        keep = slice(self.e_lo, self.e_lo + per)
+        self.experts = moe.ExpertWeights.create(fc1[keep], fc2[keep], t.moe_act, _fmt(t)).to(init.device)
+        del fc1, fc2
         f = init.full or t
         # under tensor parallelism the shared expert is column / row split like a dense MLP (its partial sum joins
         # the routed experts' partial sum before the one all-reduce of the layer)
         self.shared = MlpLayer(t, init, name + ".shared", width=f.shared_ffn, act=t.moe_act) if t.shared_ffn else None
         self.fc1_latent = init.linear(t.latent, t.hidden, "bf16", name + ".fc1_latent") if t.latent else None
         self.fc2_latent = init.linear(t.hidden, t.latent, "bf16", name + ".fc2_latent") if t.latent else None
-        per = t.experts // ep_size
-        self.e_lo, self.e_n = ep_rank * per, per
         self.ep_size = ep_size
         self.tp = init.tp
         self.partial = False          # the expert-parallel forms reduce inside the layer
@@ -316,10 +319,10 @@ class MoeLayer:
             shared = ctx.comm.all_reduce(shared)      # column / row split shared expert beside replicated experts
         if t.latent:
             lat = self.fc1_latent(x)
-            y = moe.experts_forward(lat, ids, w, self.experts, e_lo=self.e_lo, e_n=self.e_n)
+            y = moe.experts_forward(lat, ids, w, self.experts, id_base=self.e_lo)
             out = self.fc2_latent(y)
             return basic.add(out, shared) if shared is not None else out
-        return moe.experts_forward(x, ids, w, self.experts, shared=shared, e_lo=self.e_lo, e_n=self.e_n)
+        return moe.experts_forward(x, ids, w, self.experts, shared=shared, id_base=self.e_lo)
 
 
 def _moe_forward_ep(self, x, comm) -> torch.Tensor:
@@ -330,7 +333,7 @@ def _moe_forward_ep(self, x, comm) -> torch.Tensor:
     ids, w = moe.route(logits, t.top_k, sigmoid=t.router == "sigmoid", sel_bias=self.sel_bias, renorm=True,
                        scale=t.router_scale)
     inp = self.fc1_latent(x) if t.latent else x
-    part = moe.experts_forward(inp, ids, w, self.experts, e_lo=self.e_lo, e_n=self.e_n)
+    part = moe.experts_forward(inp, ids, w, self.experts, id_base=self.e_lo)
     if getattr(self, "tp", 1) > 1:
         # tensor parallel: the shared expert is column / row split too, so its partial sum joins the routed
         # experts' before the layer's one all-reduce; the latent up-projection is linear and moves in front of it
@@ -351,17 +354,16 @@ def _moe_forward_a2a(self, x, ep) -> torch.Tensor:
     sequence-parallel); rows travel to the owners of their experts and the results come back. Every rank must
     call it, with an empty batch when it has no tokens."""
     t = self.t
-    if getattr(self, "_local_experts", None) is None:
-        self._local_experts = self.experts.slice(ep.rank * ep.e_per, ep.e_per)
+    assert self.ep_size == ep.world and self.e_lo == ep.rank * ep.e_per, "the layer holds another expert range"
     logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
     ids, w = moe.route(logits, t.top_k, sigmoid=t.router == "sigmoid", sel_bias=self.sel_bias, renorm=True,
                        scale=t.router_scale)
     shared = self.shared.forward(x) if self.shared is not None and x.shape[0] else None
     if t.latent:
-        y = ep.forward(self.fc1_latent(x), ids, w, self._local_experts)
+        y = ep.forward(self.fc1_latent(x), ids, w, self.experts)
         out = self.fc2_latent(y)
         return basic.add(out, shared) if shared is not None else out
-    return ep.forward(x, ids, w, self._local_experts, shared=shared)
+    return ep.forward(x, ids, w, self.experts, shared=shared)
 
 
 MoeLayer.forward_ep = _moe_forward_ep

@@ -20,7 +20,7 @@ from . import gemm, nvfp4
 
 P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
 nv.register("hb_moe_route", [P, L, P, I, I, I, I, I, Fl, P, P, P])
-nv.register("hb_moe_plan", [P, I, I, I, I, I, P, P, P, P, I, P, I, P, P, I, P])
+nv.register("hb_moe_plan", [P, I, I, I, I, I, I, P, P, P, P, I, P, I, P, P, I, P])
 nv.register("hb_moe_gather", [P, L, P, P, P, I, I, P])
 nv.register("hb_moe_combine", [P, L, P, P, P, L, P, L, I, I, I, P])
 nv.register("hb_gemm_grouped", [I, P, P, P, P, I, I, I, I, P, L, P, I, P, P, I, P, I, I, I, P, P, I, P])
@@ -168,7 +168,8 @@ def _act(h1: torch.Tensor, act: str) -> torch.Tensor:
 
 
 def experts_ref(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: ExpertWeights,
-                shared: Optional[torch.Tensor] = None, e_lo: int = 0, e_n: Optional[int] = None) -> torch.Tensor:
+                shared: Optional[torch.Tensor] = None, e_lo: int = 0, e_n: Optional[int] = None,
+                id_base: int = 0) -> torch.Tensor:
     """Plain PyTorch: per (token, k) pair run the selected expert; sum in selection order."""
     e_n = ew.experts if e_n is None else e_n
     t = x.shape[0]
@@ -180,7 +181,7 @@ def experts_ref(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: E
     out = torch.zeros(t, ew.fc2_rows, dtype=torch.float32, device=x.device)
     for ti in range(t):
         for k in range(ids.shape[1]):
-            e = int(ids[ti, k])
+            e = int(ids[ti, k]) - id_base
             if e < e_lo or e >= e_lo + e_n:
                 continue
             h1 = (xf[ti] @ w1[e].t()).to(torch.bfloat16).float() if ew.act != "swiglu" else xf[ti] @ w1[e].t()
@@ -211,11 +212,14 @@ def tile_hint(pairs: int, experts: int, max_rows: int, fmt: str) -> int:
 
 
 def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: ExpertWeights, *,
-                    shared: Optional[torch.Tensor] = None, e_lo: int = 0, e_n: Optional[int] = None) -> torch.Tensor:
-    """x [T, H] bf16, ids / weights [T, k] -> [T, H_out] bf16 (sum of the routed experts (+ shared))."""
+                    shared: Optional[torch.Tensor] = None, e_lo: int = 0, e_n: Optional[int] = None,
+                    id_base: int = 0) -> torch.Tensor:
+    """x [T, H] bf16, ids / weights [T, k] -> [T, H_out] bf16 (sum of the routed experts (+ shared)). `ew` holds
+    the experts `id_base` .. `id_base + ew.experts - 1` of the numbering `ids` use (an expert-parallel rank keeps a
+    range); of those, only [e_lo, e_lo + e_n) run. Pairs routed elsewhere add nothing."""
     e_n = ew.experts if e_n is None else e_n
     if not nv.use_native(x):
-        return experts_ref(x, ids, weights, ew, shared, e_lo, e_n)
+        return experts_ref(x, ids, weights, ew, shared, e_lo, e_n, id_base)
     lib = nv.lib()
     t, h = x.shape
     topk = ids.shape[1]
@@ -239,7 +243,7 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
     src = torch.empty(rows_cap, dtype=torch.int32, device=dev)
     total = torch.empty(1, dtype=torch.int32, device=dev)
     st = nv.device_state(dev).status
-    nv.check(lib.hb_moe_plan(ids.data_ptr(), t, topk, e, e_lo, e_n, cnt.data_ptr(), start.data_ptr(), pos.data_ptr(),
+    nv.check(lib.hb_moe_plan(ids.data_ptr(), t, topk, e, e_lo, e_n, id_base, cnt.data_ptr(), start.data_ptr(), pos.data_ptr(),
                              src.data_ptr(), rows_cap, total.data_ptr(), bn_hint, tiles.data_ptr(),
                              n_tiles.data_ptr(), tile_cap, nv.stream()), "hb_moe_plan")
     n1, h_out = ew.n1, ew.fc2_rows

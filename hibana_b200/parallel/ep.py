@@ -231,3 +231,41 @@ class ExpertParallel:
         if shared is not None:
             out = out + shared.float()
         return out.to(torch.bfloat16)
+
+
+class HostExpertParallel:
+    """The contract of `ExpertParallel.forward` on any device through a host all-gather (`allgather(obj) -> list`
+    over the ranks: engine/dp.py has one over a torch.distributed group and one between threads). Every pair's
+    expert output crosses as the bf16 row the owner computed and the caller sums its pairs in selection order, so
+    the result is bitwise what one process holding every expert computes. For CPU runs of the data-parallel
+    engine and as oracle."""
+
+    def __init__(self, allgather, rank: int, world: int, experts: int):
+        assert experts % world == 0
+        self.allgather, self.rank, self.world = allgather, rank, world
+        self.e_per = experts // world
+        self.calls = 0
+
+    def forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: "moe.ExpertWeights", *,
+                shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+        dev = x.device
+        self.calls += 1
+        sent = self.allgather((x.cpu(), ids.cpu()))
+        back = []
+        for xs, sel in sent:                      # every rank's tokens through this rank's experts, pair by pair
+            ys = torch.zeros(xs.shape[0], sel.shape[1], ew.fc2_rows, dtype=torch.bfloat16)
+            if xs.shape[0]:
+                one = torch.ones(xs.shape[0], 1, dtype=torch.float32, device=dev)
+                for k in range(sel.shape[1]):
+                    ys[:, k] = moe.experts_forward(xs.to(dev), sel[:, k:k + 1].contiguous().to(dev), one, ew,
+                                                   id_base=self.rank * self.e_per).cpu()
+            back.append(ys)
+        got = self.allgather(back)
+        mine = sum(got[r][self.rank].float() for r in range(self.world))      # exactly one owner per pair
+        # selection-order fp32 sum, as the single-process combine does
+        acc = torch.zeros(x.shape[0], ew.fc2_rows, dtype=torch.float32)
+        for k in range(ids.shape[1]):
+            acc += weights.float().cpu()[:, k:k + 1] * mine[:, k]
+        if shared is not None:
+            acc += shared.float().cpu()
+        return acc.to(torch.bfloat16).to(dev)

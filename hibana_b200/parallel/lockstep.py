@@ -1,4 +1,4 @@
-"""Lock-step control plane for tensor-parallel ranks.
+"""Control plane of multi-rank serving: lock-step tensor-parallel ranks, or data-parallel replicas.
 
 Rank 0 owns HTTP and the inbox; at every publish point of the engine loop it broadcasts the list of commands it is
 about to apply over a CPU (gloo) group and every other rank applies the same list, so all schedulers step
@@ -27,9 +27,10 @@ class BroadcastChannel:
 
 
 def serve_rank(cfg) -> int:
-    """One rank of a tensor-parallel server (rank 0 also serves HTTP). Every family serves this way: the dense
-    decoder and the hybrids shard their mixers by head, MLPs by column and experts by expert range over the ranks
-    (`build_model`); the engine stack itself comes from the settings (`LLM`), the same as on one GPU."""
+    """One rank of a multi-GPU server (rank 0 also serves HTTP). Tensor parallel (the default), every family: the
+    dense decoder and the hybrids shard their mixers by head, MLPs by column and experts by expert range over the
+    ranks (`build_model`). With `dp` > 1 the ranks are data-parallel replicas instead. The engine stack itself
+    comes from the settings (`LLM`), the same as on one GPU."""
     import datetime
 
     from ..api.chat_template import ChatTemplate
@@ -48,10 +49,19 @@ def serve_rank(cfg) -> int:
     # the control plane has a timeout: a rank that stops answering ends the others' next broadcast with an error
     control = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=max(cfg.control_timeout_s, 5)))
     cfg = BroadcastChannel(control).broadcast(cfg if rank == 0 else None)     # every rank serves rank 0's settings
-    comm = Communicator.create(rank, world, dev, slot_mb=cfg.comm_buffer_mb // 8 or 1, timeout_ms=cfg.comm_timeout_ms,
-                               fused=cfg.fused_collectives)
-    llm = LLM(cfg.replace(tp=world), device=dev, comm=comm, warmup=True)
-    engine = EngineLoop(llm.scheduler, channel=BroadcastChannel(control), rank=rank).start()
+    if cfg.dp > 1:
+        # data-parallel replicas (one per GPU), expert-parallel MoE layers between them when cfg.ep == cfg.dp: every
+        # replica schedules its own requests; rank 0 routes them and collects the tokens (engine/loop.py, engine/dp.py)
+        if cfg.dp * cfg.tp != world:
+            raise ValueError(f"dp={cfg.dp} x tp={cfg.tp} does not match the {world} ranks that were started")
+        from ..engine.dp import GroupAllGather
+        llm = LLM(cfg, device=dev, control=GroupAllGather(control), rank=rank, warmup=True)
+        engine = EngineLoop(llm.scheduler, rank=rank, dp=llm.lockstep).start()
+    else:
+        comm = Communicator.create(rank, world, dev, slot_mb=cfg.comm_buffer_mb // 8 or 1,
+                                   timeout_ms=cfg.comm_timeout_ms, fused=cfg.fused_collectives)
+        llm = LLM(cfg.replace(tp=world), device=dev, comm=comm, warmup=True)
+        engine = EngineLoop(llm.scheduler, channel=BroadcastChannel(control), rank=rank).start()
 
     def on_dead(ranks):
         engine._fail(f"ranks {list(ranks)} stopped answering")
@@ -66,7 +76,8 @@ def serve_rank(cfg) -> int:
     import uvicorn
     tok = load_tokenizer(cfg.weights if cfg.weights != "random" else None, llm.target.vocab)
     app = create_app(engine, tok, model_name=llm.target.name, template=ChatTemplate(),
-                     info={"config": cfg.as_dict(), "tp": world}, api_key=cfg.api_key)
+                     info={"config": cfg.as_dict(), "tp": cfg.tp if cfg.dp > 1 else world, "dp": cfg.dp},
+                     api_key=cfg.api_key)
     uvicorn.Server(uvicorn.Config(app, host=cfg.host, port=cfg.port, log_level="warning")).run()
     engine.stop()
     llm.shutdown()

@@ -42,3 +42,118 @@ def test_least_loaded_routing_and_prefix_affinity():
 def test_lockstep_plan():
     assert lockstep_plan([False, False]) == (False, [False, False])
     assert lockstep_plan([True, False, True]) == (True, [False, True, False])
+
+
+def test_lockstep_rounds_align_forwards_not_steps():
+    """Three ranks with different amounts of work: every round has all ranks in it, a rank without a forward of
+    its own learns that a peer has one, messages travel with the rounds, and everyone leaves in the same round."""
+    import threading
+    from hibana_b200.engine.dp import FORWARD, LEAVING, RUNNING, Lockstep, ThreadAllGather
+    tg = ThreadAllGather(3, timeout=20)
+    work = [3, 1, 0]                                 # forwards each rank wants
+    log = [[] for _ in range(3)]
+    mail = [[] for _ in range(3)]
+
+    def run(rank):
+        ls = Lockstep(tg.view(rank), rank, 3)
+        ls.on_items = lambda src, items: mail[rank].extend((src, i) for i in items)
+        if rank == 0:
+            ls.post(("hello", 7))
+        left = work[rank]
+        while True:
+            states = ls.round(FORWARD if left else LEAVING)
+            log[rank].append(tuple(states))
+            if left:
+                left -= 1
+            if all(s == LEAVING for s in states):
+                break
+    th = [threading.Thread(target=run, args=(r,)) for r in range(3)]
+    for t in th:
+        t.start()
+    for t in th:
+        t.join(30)
+    assert log[0] == log[1] == log[2]
+    assert [s.count(FORWARD) for s in log[0]] == [2, 1, 1, 0] and RUNNING not in log[0][0]
+    assert mail[1] == [(0, ("hello", 7))] and mail[2] == [(0, ("hello", 7))] and mail[0] == []
+
+
+def test_data_parallel_replicas_with_expert_parallel_layers_match_one_process():
+    """Two replicas (threads, CPU), each holding half of every MoE layer's experts and serving its own prompts
+    (different numbers, lengths and output lengths, one replica idle at the end) produce the tokens one process
+    with all experts produces."""
+    import threading
+    from hibana_b200.config import EngineConfig
+    from hibana_b200.engine.dp import ThreadAllGather
+    from hibana_b200.engine.llm import LLM
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.target import scaled, tiny_hybrid_moe
+    t = scaled(tiny_hybrid_moe(), mtp_layers=0, mtp_depth=0)
+    base = EngineConfig(target="tiny", max_batch=4, cuda_graphs=False, max_context=256, prefill_budget=64,
+                        prefill_chunk=32)
+    prompts = [[[5, 9, 11, 300, 17] * 9, [7, 8, 9]], [[100 + i for i in range(50)]]]
+    params = [[SamplingParams(max_tokens=6, ignore_eos=True), SamplingParams(max_tokens=3, ignore_eos=True)],
+              [SamplingParams(max_tokens=11, ignore_eos=True)]]
+    one = LLM(base, target=t, device="cpu")
+    want = [[r.output_ids for r in one.generate(prompts[i], params[i])] for i in range(2)]
+    tg = ThreadAllGather(2, timeout=120)
+    got, errs, llms = [None, None], [], [None, None]
+
+    def run(rank):
+        try:
+            llm = LLM(base.replace(dp=2, ep=2), target=t, device="cpu", control=tg.view(rank), rank=rank)
+            llms[rank] = llm
+            got[rank] = [r.output_ids for r in llm.generate(prompts[rank], params[rank])]
+        except Exception as e:   # noqa: BLE001 - reported by the assertion below
+            errs.append(repr(e))
+            tg.barrier.abort()
+    th = [threading.Thread(target=run, args=(r,)) for r in range(2)]
+    for x in th:
+        x.start()
+    for x in th:
+        x.join(300)
+    assert not errs, errs
+    assert got == want
+    ls0, ls1 = llms[0].lockstep, llms[1].lockstep
+    assert ls0.rounds == ls1.rounds and ls0.empty_forwards + ls1.empty_forwards > 0
+    assert llms[0].ep.calls == llms[1].ep.calls            # every rank ran every MoE all-to-all
+    assert llms[0].model.blocks[0].ffn.experts.experts == t.experts // 2
+
+
+def test_engine_loops_of_two_replicas_route_requests_and_stream_back_to_rank0():
+    """Rank 0 owns the inbox: it gives every request an owner, the owner generates, tokens come back to rank 0's
+    tickets with the rounds, and `stop` ends both loops in the same round."""
+    from hibana_b200.config import EngineConfig
+    from hibana_b200.engine.dp import ThreadAllGather
+    from hibana_b200.engine.llm import LLM
+    from hibana_b200.engine.loop import EngineLoop
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.target import scaled, tiny_hybrid_moe
+    t = scaled(tiny_hybrid_moe(), mtp_layers=0, mtp_depth=0)
+    base = EngineConfig(target="tiny", max_batch=4, cuda_graphs=False, max_context=256, prefill_budget=64,
+                        prefill_chunk=32)
+    prompts = [[3 + i, 40 + i, 7, 9, 200 + i, 5] * (2 + i) for i in range(5)]
+    sp = SamplingParams(max_tokens=5, ignore_eos=True)
+    want = [r.output_ids for r in LLM(base, target=t, device="cpu").generate(prompts, sp)]
+    tg = ThreadAllGather(2, timeout=120)
+    llms = [LLM(base.replace(dp=2, ep=2), target=t, device="cpu", control=tg.view(r), rank=r) for r in range(2)]
+    loops = [EngineLoop(llms[r].scheduler, rank=r, dp=llms[r].lockstep, idle_sleep=0.001).start() for r in range(2)]
+    tickets = [loops[0].submit(p, sp) for p in prompts]
+    got = []
+    for tk in tickets:
+        toks = []
+        while True:
+            kind, val = tk.events.get(timeout=120)
+            if kind == "tokens":
+                toks += val
+            else:
+                assert kind == "done", (kind, val)
+                break
+        got.append(toks)
+    assert got == want
+    served = [llms[r].scheduler.metrics.finished for r in range(2)]
+    assert sum(served) == 5 and min(served) >= 1, served
+    assert loops[0]._router.loops[0].n == 0 and loops[0]._router.loops[1].n == 0
+    loops[0].stop(timeout=30)
+    loops[1].thread.join(30)
+    assert not loops[0].thread.is_alive() and not loops[1].thread.is_alive()
+    assert loops[0].healthy and loops[1].healthy

@@ -49,11 +49,12 @@ for fmt, act, E, topk, H, I, toks in (("nvfp4", "swiglu", 16, 4, 256, 128, (37, 
 from hibana_b200.models.layers import Init, MoeLayer
 from hibana_b200.target import flashnext, scaled
 t = scaled(flashnext(), hidden=256, experts=16, top_k=4, expert_ffn=128, shared_ffn=128, weight_format="nvfp4")
-layer = MoeLayer(t, Init(0, dev, init_device="cpu"), "moe")
+whole = MoeLayer(t, Init(0, dev, init_device="cpu"), "moe")
+layer = MoeLayer(t, Init(0, dev, init_device="cpu"), "moe", ep_rank=rank, ep_size=world)   # keeps its expert range
 ep = ExpertParallel.create(rank, world, dev, tokens=64, topk=t.top_k, experts=t.experts, hidden=t.hidden)
 xs = torch.randn(40 + 9 * rank, t.hidden, generator=torch.Generator().manual_seed(50 + rank)).bfloat16().to(dev)
 a = layer.forward_a2a(xs, ep)
-c = layer.forward(xs)
+c = whole.forward(xs)
 torch.cuda.synchronize()
 res["layer"] = [[0.0, float((a.float() - c.float()).abs().max() / c.float().abs().max())]]
 res["status"] = nv.read_status(dev)

@@ -30,6 +30,9 @@ def test_experts_ref_ep_halves_sum_cpu():
     whole = moe.experts_forward(x, ids, w, ew).float()
     parts = sum(moe.experts_forward(x, ids, w, ew, e_lo=lo, e_n=4).float() for lo in (0, 4))
     assert (whole - parts).abs().max() < 2e-2 * whole.abs().max() + 1e-3
+    # a rank that keeps only experts 4..7 (global ids, local weights) computes the same partial sum
+    kept = moe.experts_forward(x, ids, w, ew.slice(4, 4), id_base=4).float()
+    assert torch.equal(kept, moe.experts_forward(x, ids, w, ew, e_lo=4, e_n=4).float())
 
 
 @pytest.mark.gpu
@@ -63,6 +66,9 @@ def test_experts_forward_gpu(fmt, t, e, k, h, inter, act):
     hi = moe.experts_forward(x.cuda(), ids.cuda(), w.cuda(), ewg, e_lo=e // 2, e_n=e // 2).float()
     whole = moe.experts_forward(x.cuda(), ids.cuda(), w.cuda(), ewg).float()
     assert (lo + hi - whole).abs().max() <= 2e-2 * whole.abs().max() + 2e-3
+    if fmt != "w3":    # a rank holding only the upper half of the experts: same partial sum from global ids
+        kept = moe.experts_forward(x.cuda(), ids.cuda(), w.cuda(), ewg.slice(e // 2, e // 2), id_base=e // 2).float()
+        assert torch.equal(kept, hi)
     # deterministic
     again = moe.experts_forward(x.cuda(), ids.cuda(), w.cuda(), ewg).float()
     assert torch.equal(again, whole)

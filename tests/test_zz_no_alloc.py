@@ -4,7 +4,7 @@ Some users of the library may not allocate device memory when they ask for a gre
 handed to fixed pools, or a C host without any caching allocator). `hb_argmax_noalloc` serves them from a scratch
 array built into the library. This test loads the symbol with ctypes, runs it twice in a row (the calls share the
 scratch, so the second must not be disturbed by what the first left there) and compares with the regular
-two-stage argmax that takes caller-provided scratch.
+two-stage argmax that takes caller-provided scratch and with `torch.argmax`.
 """
 import ctypes
 
@@ -42,6 +42,7 @@ def test_noalloc_argmax_matches_regular_entry_point_twice():
             torch.cuda.synchronize()
             assert code == 0, err.value
             assert torch.equal(out, want)
+            assert torch.equal(out, torch.argmax(logits.float(), dim=-1))     # second oracle: the library argmax
         assert int(want[0]) == 5
 
 
