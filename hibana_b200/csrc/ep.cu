@@ -150,7 +150,10 @@ ep_plan_kernel(const int* __restrict__ ids, int pairs, int experts, int e_per, E
   __syncthreads();
   for (int e = threadIdx.x; e < e_per; e += blockDim.x) {
     const int ge = rank * e_per + e;
-    const bool in = ge < experts && start[ge] + total[ge] <= rows_cap;   // a segment that does not fit is dropped
+    // a segment that does not fit is left out (nothing is written past the buffer) and the call is marked failed:
+    // the host reads the status word with the step's result and raises
+    const bool in = ge < experts && start[ge] + total[ge] <= rows_cap;
+    if (!in && ge < experts && total[ge] > 0) set_status(status, kOverflow);
     grp_cnt[e] = in ? total[ge] : 0;
     grp_start[e] = in ? start[ge] : 0;
   }
@@ -167,6 +170,7 @@ ep_plan_kernel(const int* __restrict__ ids, int pairs, int experts, int e_per, E
     }
     const int row = atomicAdd(&fill[e], 1);
     const bool in = row < rows_cap && start[e] + total[e] <= rows_cap;
+    if (!in) set_status(status, kOverflow);
     dst_rank[i] = in ? e / e_per : -1;
     dst_row[i] = in ? row : -1;
   }

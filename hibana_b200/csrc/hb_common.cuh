@@ -25,6 +25,7 @@ enum Status : int {
   kTimeoutDrain = 7,
   kTimeoutLowLatency = 8,   // the low-latency all-reduce never saw a peer's word
   kTimeoutGate = 9,         // a flag-gated GEMM tile never saw its source rank's rows
+  kOverflow = 10,           // an expert-parallel receive buffer was too small for the rows routed to it
 };
 
 #ifndef HB_SPIN_LIMIT

@@ -182,10 +182,29 @@ __device__ __forceinline__ float block_sum256(float v, float* red) {   // 256 th
   return t;
 }
 
+__device__ __forceinline__ int block_sum256i(int v, int* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  int t = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) t += red[w];
+  return t;
+}
+
+// The sampling law of one row as engine/rejection.py `distribution` defines it: softmax(logits / temp) over the
+// allowed tokens, cut to the first `k_lim` tokens in (value desc, index asc) order (0 = no cut), then to the
+// smallest prefix of that order whose mass reaches p_lim. Draws one token by inverse CDF in index order from the
+// law with token `exclude` removed (-1: nothing removed; the residual of a point-mass draft in speculative
+// sampling) and reports the probability of token `probe` under the law. 256 threads, whole CTA.
 template <typename T>
-__device__ void sample_full_row(const T* __restrict__ lr, int vocab, const int* __restrict__ mask, float temp,
-                                float p_lim, float u01, long long* out, float* out_prob) {
+__device__ void law_row(const T* __restrict__ lr, int vocab, const int* __restrict__ mask, float temp, int k_lim,
+                        float p_lim, float u01, int exclude, int probe, long long* out, float* out_prob,
+                        float* out_probe) {
   __shared__ float red[8];
+  __shared__ int redi[8];
   __shared__ float csum[256];
   __shared__ int ceq[256];
   __shared__ int s_pick_thread;
@@ -203,24 +222,57 @@ __device__ void sample_full_row(const T* __restrict__ lr, int vocab, const int* 
   mx = red[0];
 #pragma unroll
   for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
-  float z = 0.f;
-  for (int i = tid; i < vocab; i += 256)
-    if (mask_ok(mask, i)) {
-      const float v = ldf<T>(lr, i);
-      if (v > -INFINITY) z += __expf((v - mx) * inv_t);
-    }
-  z = block_sum256(z, red);
-  // nucleus: the smallest prefix, in (value desc, index asc) order, whose mass reaches p_lim * z. t_key = the value
-  // of the token that crosses the line (largest key whose upper set still holds the mass); tokens above it stay,
-  // and of the tokens equal to it the first `need_eq` in index order.
-  unsigned t_key = 0;
-  int need_eq = 0x7fffffff;
-  float kept = z;
-  if (p_lim < 1.f) {
-    const float want = p_lim * z;
+  // ---- top-k cut: tk_key = value of the k-th token, need_k = how many of the tokens equal to it are inside
+  unsigned tk_key = 0;     // finite values have keys above 0x007fffff: 0 keeps everything
+  int need_k = 0x7fffffff;
+  const bool cut_k = k_lim > 0 && k_lim < vocab;
+  if (cut_k) {
     unsigned lo = 0, hi = order_key(mx);
     while (lo < hi) {
       const unsigned mid = lo + ((hi - lo + 1) >> 1);
+      int cnt = 0;
+      for (int i = tid; i < vocab; i += 256)
+        if (mask_ok(mask, i)) {
+          const float v = ldf<T>(lr, i);
+          cnt += v > -INFINITY && order_key(v) >= mid;
+        }
+      cnt = block_sum256i(cnt, redi);
+      if (cnt >= k_lim) lo = mid;
+      else hi = mid - 1;
+    }
+    tk_key = lo;
+    int above = 0;
+    for (int i = tid; i < vocab; i += 256)
+      if (mask_ok(mask, i)) {
+        const float v = ldf<T>(lr, i);
+        above += v > -INFINITY && order_key(v) > tk_key;
+      }
+    need_k = k_lim - block_sum256i(above, redi);
+  }
+  // mass above a key and number of tokens equal to it
+  float m_above = 0.f;
+  int n_eq = 0;
+  for (int i = tid; i < vocab; i += 256)
+    if (mask_ok(mask, i)) {
+      const float v = ldf<T>(lr, i);
+      if (v > -INFINITY) {
+        const unsigned k = order_key(v);
+        if (k > tk_key) m_above += __expf((v - mx) * inv_t);
+        else n_eq += k == tk_key;
+      }
+    }
+  m_above = block_sum256(m_above, red);
+  n_eq = block_sum256i(n_eq, redi);
+  unsigned t_key = tk_key;
+  int need_eq = min(need_k, n_eq);
+  float w_t = cut_k ? __expf((key_value(tk_key) - mx) * inv_t) : 0.f;
+  float kept = m_above + (cut_k ? need_eq * w_t : 0.f);
+  // ---- nucleus inside the cut: the smallest prefix, in the same order, whose mass reaches p_lim * kept
+  if (p_lim < 1.f) {
+    const float want = p_lim * kept;
+    unsigned lo = tk_key, hi = order_key(mx);      // mass(key >= lo) = kept >= want
+    while (lo < hi) {
+      const unsigned mid = lo + ((hi - lo + 1) >> 1);     // mid > tk_key: every token at or above it is inside the cut
       float mass = 0.f;
       for (int i = tid; i < vocab; i += 256)
         if (mask_ok(mask, i)) {
@@ -231,26 +283,63 @@ __device__ void sample_full_row(const T* __restrict__ lr, int vocab, const int* 
       if (mass >= want) lo = mid;
       else hi = mid - 1;
     }
-    t_key = lo;
-    float above = 0.f, eq = 0.f;
-    for (int i = tid; i < vocab; i += 256)
-      if (mask_ok(mask, i)) {
-        const float v = ldf<T>(lr, i);
-        if (v > -INFINITY) {
-          const unsigned k = order_key(v);
-          if (k > t_key) above += __expf((v - mx) * inv_t);
-          else if (k == t_key) eq += 1.f;
+    if (lo != tk_key || !cut_k) {
+      t_key = lo;
+      float above = 0.f;
+      int eq = 0;
+      for (int i = tid; i < vocab; i += 256)
+        if (mask_ok(mask, i)) {
+          const float v = ldf<T>(lr, i);
+          if (v > -INFINITY) {
+            const unsigned k = order_key(v);
+            if (k > t_key) above += __expf((v - mx) * inv_t);
+            else eq += k == t_key;
+          }
         }
-      }
-    above = block_sum256(above, red);
-    eq = block_sum256(eq, red);
-    const float w_t = __expf((key_value(t_key) - mx) * inv_t);
-    int need = w_t > 0.f ? static_cast<int>(ceilf((want - above) / w_t)) : 1;
-    need = max(1, min(need, static_cast<int>(eq)));
-    need_eq = need;
-    kept = above + need * w_t;
+      m_above = block_sum256(above, red);
+      n_eq = block_sum256i(eq, redi);
+      w_t = __expf((key_value(t_key) - mx) * inv_t);
+      need_eq = n_eq;
+    }
+    int need = w_t > 0.f ? static_cast<int>(ceilf((want - m_above) / w_t)) : 1;
+    need_eq = max(1, min(need, need_eq));
+    kept = m_above + need_eq * w_t;
   }
-  // draw: contiguous chunk per thread, chunk sums scanned by thread 0, the owning thread walks its chunk
+  // ---- membership and weight of the probed / excluded token (its rank among equals decides at the threshold)
+  float w_probe = 0.f, w_ex = 0.f;
+  for (int pass = 0; pass < 2; ++pass) {
+    const int tok = pass == 0 ? probe : exclude;
+    if (tok < 0 || tok >= vocab || !mask_ok(mask, tok)) continue;
+    if (pass == 1 && exclude == probe) {
+      w_ex = w_probe;
+      continue;
+    }
+    const float v = ldf<T>(lr, tok);
+    float w = 0.f;
+    if (v > -INFINITY) {
+      const unsigned k = order_key(v);
+      if (k > t_key) w = __expf((v - mx) * inv_t);
+      else if (k == t_key) {
+        int before = 0;
+        for (int i = tid; i < tok; i += 256)
+          if (mask_ok(mask, i)) {
+            const float o = ldf<T>(lr, i);
+            before += o > -INFINITY && order_key(o) == t_key;
+          }
+        before = block_sum256i(before, redi);
+        if (before < need_eq) w = w_t;
+      }
+    }
+    if (pass == 0) w_probe = w;
+    else w_ex = w;
+  }
+  if (out_probe != nullptr && tid == 0) *out_probe = w_probe / kept;
+  if (!(kept - w_ex > kept * 1e-6f)) {      // nothing left beside the excluded token: the law itself is drawn from
+    exclude = -1;
+    w_ex = 0.f;
+  }
+  const float kept_draw = kept - w_ex;
+  // ---- draw: contiguous chunk per thread, chunk sums scanned by thread 0, the owning thread walks its chunk
   const int per = (vocab + 255) / 256;
   const int lo_i = tid * per, hi_i = min(vocab, lo_i + per);
   float mine = 0.f;
@@ -260,23 +349,24 @@ __device__ void sample_full_row(const T* __restrict__ lr, int vocab, const int* 
       const float v = ldf<T>(lr, i);
       if (v > -INFINITY) {
         const unsigned k = order_key(v);
-        if (k == t_key && p_lim < 1.f) ++my_eq;
-        else if (k > t_key || p_lim >= 1.f) mine += __expf((v - mx) * inv_t);
+        if (k > t_key) mine += __expf((v - mx) * inv_t);
+        else if (k == t_key) ++my_eq;
       }
     }
   csum[tid] = mine;
   ceq[tid] = my_eq;
   __syncthreads();
-  const float u = u01 * kept;
+  const float u = u01 * kept_draw;
+  const int ex_thread = exclude >= 0 ? exclude / per : -1;
   if (tid == 0) {
-    const float w_t = p_lim < 1.f ? __expf((key_value(t_key) - mx) * inv_t) : 0.f;
     float acc = 0.f;
     int eq_seen = 0, pick = -1, last = 0;
     float base = 0.f;
     int eq_base = 0;
     for (int t = 0; t < 256; ++t) {
       const int take = max(0, min(ceq[t], need_eq - eq_seen));
-      const float w = csum[t] + take * w_t;
+      float w = csum[t] + take * w_t;
+      if (t == ex_thread) w = fmaxf(w - w_ex, 0.f);
       if (w > 0.f) last = t;
       if (pick < 0 && u < acc + w) {
         pick = t;
@@ -296,7 +386,6 @@ __device__ void sample_full_row(const T* __restrict__ lr, int vocab, const int* 
   }
   __syncthreads();
   if (tid == s_pick_thread) {
-    const float w_t = p_lim < 1.f ? __expf((key_value(t_key) - mx) * inv_t) : 0.f;
     float acc = s_base;
     int eq_seen = s_eq_base, chosen = -1, last_kept = -1;
     float w_chosen = 0.f, w_last = 0.f;
@@ -306,11 +395,12 @@ __device__ void sample_full_row(const T* __restrict__ lr, int vocab, const int* 
       if (!(v > -INFINITY)) continue;
       const unsigned k = order_key(v);
       float w = 0.f;
-      if (p_lim >= 1.f || k > t_key) w = __expf((v - mx) * inv_t);
+      if (k > t_key) w = __expf((v - mx) * inv_t);
       else if (k == t_key) {
         if (eq_seen < need_eq) w = w_t;
         ++eq_seen;
       }
+      if (i == exclude) w = 0.f;
       if (w <= 0.f) continue;
       last_kept = i;
       w_last = w;
@@ -326,8 +416,15 @@ __device__ void sample_full_row(const T* __restrict__ lr, int vocab, const int* 
       w_chosen = w_last;
     }
     *out = chosen;
-    if (out_prob) *out_prob = w_chosen / kept;
+    if (out_prob) *out_prob = w_chosen / kept_draw;
   }
+  __syncthreads();
+}
+
+template <typename T>
+__device__ void sample_full_row(const T* __restrict__ lr, int vocab, const int* __restrict__ mask, float temp,
+                                int k_lim, float p_lim, float u01, long long* out, float* out_prob) {
+  law_row<T>(lr, vocab, mask, temp, k_lim, p_lim, u01, -1, -1, out, out_prob, nullptr);
 }
 
 constexpr int SAMPLE_K = 64;  // candidates kept per row for 1 <= top-k <= 64 (top-p is applied inside them)
@@ -356,7 +453,7 @@ sample_kernel(const T* __restrict__ logits, long long ld, int vocab, const float
   if (temp > 0.f && (k <= 0 || k > SAMPLE_K)) {
     // top-k off (the API default) or wider than the candidate list: the law is the softmax over the whole
     // vocabulary (then top-p), not over the SAMPLE_K largest logits
-    sample_full_row<T>(lr, vocab, mask, temp, top_p ? top_p[row] : 1.f,
+    sample_full_row<T>(lr, vocab, mask, temp, k > SAMPLE_K ? k : 0, top_p ? top_p[row] : 1.f,
                        uniform01(seeds ? seeds[row] : 0ull, offsets ? offsets[row] : 0ull), out + row,
                        out_prob ? out_prob + row : nullptr);
     return;
@@ -448,6 +545,60 @@ sample_kernel(const T* __restrict__ logits, long long ld, int vocab, const float
     }
     out[row] = ci[pick];
     if (out_prob) out_prob[row] = cv[pick] / ksum;
+  }
+}
+
+// Speculative rejection sampling against point-mass drafts, one CTA per verified row. Request b owns logits rows
+// [b * (k + 1), (b + 1) * (k + 1)); row j < k sees draft d = drafts[b][j]: with p the row's law (law_row) the draft
+// stands when u * 1 < p[d] (or, for a relaxed request, u < e^soft * p[d]); otherwise the row's token is a draw from
+// max(p - onehot(d), 0) renormalised. Row k draws the bonus token from p. The kernel writes, per row, the token the
+// target "says" there: d where the draft stands, the draw where it does not; the exact-prefix accept kernel below
+// then yields the emitted tokens, so sampled and greedy rounds share one accept path (greedy requests, temp <= 0,
+// fall out of the same rule: their law is the one-hot argmax). Uniforms are counter draws at (seed, 2 * (draws + j)
+// + 1) for the test and + 2 for the draw.
+template <typename T>
+__global__ void __launch_bounds__(256)
+spec_targets_kernel(const T* __restrict__ logits, long long ld, int vocab, int k, const long long* __restrict__ drafts,
+                    const float* __restrict__ temperature, const int* __restrict__ top_k,
+                    const float* __restrict__ top_p, const unsigned long long* __restrict__ seeds,
+                    const unsigned long long* __restrict__ draws, const float* __restrict__ soft,
+                    const int* __restrict__ bitmask, int mask_words, const long long* __restrict__ greedy_pick,
+                    long long* __restrict__ target, float* __restrict__ p_draft) {
+  __shared__ long long s_tok;
+  __shared__ float s_probe;
+  const int row = blockIdx.x, b = row / (k + 1), j = row - b * (k + 1);
+  const T* lr = logits + row * ld;
+  const int* mask = bitmask ? bitmask + static_cast<long long>(row) * mask_words : nullptr;
+  float temp = temperature ? temperature[b] : 0.f;
+  int k_lim = top_k ? top_k[b] : 0;
+  float p_lim = top_p ? top_p[b] : 1.f;
+  if (temp <= 0.f && greedy_pick != nullptr) {      // the caller already has this row's argmax
+    if (threadIdx.x == 0) {
+      target[row] = greedy_pick[row];
+      if (p_draft) p_draft[row] = j < k && greedy_pick[row] == drafts[static_cast<long long>(b) * k + j] ? 1.f : 0.f;
+    }
+    return;
+  }
+  if (temp <= 0.f) {
+    temp = 1.f;
+    k_lim = 1;
+    p_lim = 1.f;
+  }
+  const unsigned long long seed = seeds ? seeds[b] : 0ull, base = draws ? draws[b] : 0ull;
+  const int d = j < k ? static_cast<int>(drafts[static_cast<long long>(b) * k + j]) : -1;
+  law_row<T>(lr, vocab, mask, temp, k_lim, p_lim, uniform01(seed, 2 * (base + j) + 2), d, d, &s_tok, nullptr,
+             &s_probe);
+  if (threadIdx.x == 0) {
+    long long tok = s_tok;
+    if (j < k) {
+      const float u = uniform01(seed, 2 * (base + j) + 1), pd = s_probe;
+      const float sf = soft ? soft[b] : 0.f;
+      if (u < pd || (sf > 0.f && u < __expf(sf) * pd)) tok = d;
+      if (p_draft) p_draft[row] = pd;
+    } else if (p_draft) {
+      p_draft[row] = 1.f;
+    }
+    target[row] = tok;
   }
 }
 
@@ -551,6 +702,27 @@ int hb_sample(const void* logits, long long ld, int rows, int vocab, int is_f32,
   if (is_f32) sample_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float*>(logits), HB_SAMPLE_ARGS);
   else sample_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), HB_SAMPLE_ARGS);
 #undef HB_SAMPLE_ARGS
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_spec_targets(const void* logits, long long ld, int batch, int k, int vocab, int is_f32, const void* drafts,
+                    const void* temperature, const void* top_k, const void* top_p, const void* seeds,
+                    const void* draws, const void* soft, const void* bitmask, int mask_words,
+                    const void* greedy_pick, void* target, void* p_draft, void* stream) {
+  if (batch <= 0) return 0;
+  if (k < 0 || vocab <= 0) return 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rows = batch * (k + 1);
+#define HB_SPEC_ARGS                                                                                          \
+  ld, vocab, k, static_cast<const long long*>(drafts), static_cast<const float*>(temperature),                \
+      static_cast<const int*>(top_k), static_cast<const float*>(top_p),                                       \
+      static_cast<const unsigned long long*>(seeds), static_cast<const unsigned long long*>(draws),           \
+      static_cast<const float*>(soft), static_cast<const int*>(bitmask), mask_words,                          \
+      static_cast<const long long*>(greedy_pick), static_cast<long long*>(target), static_cast<float*>(p_draft)
+  if (is_f32) spec_targets_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float*>(logits), HB_SPEC_ARGS);
+  else
+    spec_targets_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), HB_SPEC_ARGS);
+#undef HB_SPEC_ARGS
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

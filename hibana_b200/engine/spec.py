@@ -109,6 +109,17 @@ class SpecDecoder:
             margin = torch.tensor([r.params.accept_margin for r in reqs], device=dev)[:, None]
             ok = (rank.view(b, k) < topk) & ((gap.view(b, k) <= margin) | (rank.view(b, k) == 0)) & rel[:, None]
             out[:, :k] = torch.where(ok, drafts, out[:, :k])
+        if not bool(greedy.all()) and self._laws is None and not bool(rel.any()):
+            # deterministic drafts (MTP, n-gram): the whole rejection-sampling rule is one kernel over the logits;
+            # greedy requests of the batch keep the argmax computed above
+            def col(vals, dtype):
+                return torch.tensor(vals, dtype=dtype).to(dev)
+            target, _ = sampling.spec_targets(
+                flat, drafts, col([r.params.temperature for r in reqs], torch.float32),
+                col([r.params.top_k for r in reqs], torch.int32), col([r.params.top_p for r in reqs], torch.float32),
+                col([r.seed & 0x7FFFFFFFFFFFFFFF for r in reqs], torch.int64), col([r.draws for r in reqs], torch.int64),
+                col([r.params.accept_soft for r in reqs], torch.float32), bitmask, greedy_pick=out.view(-1))
+            return target
         if not bool(greedy.all()):
             temp = torch.tensor([r.params.temperature for r in reqs], device=dev).repeat_interleave(k1)
             tk = torch.tensor([r.params.top_k for r in reqs], device=dev).repeat_interleave(k1)
@@ -230,11 +241,16 @@ class SpecDecoder:
             stop_lists.append(ids_)
         budgets = [max(r.remaining, 1) for r in reqs]
         slot_lists = [r.kv_slots[nn:nn + k + 1] for r, nn in zip(reqs, n)]
-        if (self.graphs is not None and not (relaxed or sampled or bitmask is not None or has_state)
-                and b <= self.graphs.buckets[-1]):
+        if (self.graphs is not None and not (relaxed or bitmask is not None or has_state)
+                and (not sampled or self._laws is None) and b <= self.graphs.buckets[-1]):
             # one upload, one captured verify + accept, one readback (engine/spec_graphs.py)
+            srows = None
+            if sampled:
+                srows = {"temp": [r.params.temperature for r in reqs], "top_k": [r.params.top_k for r in reqs],
+                         "top_p": [r.params.top_p for r in reqs], "soft": [r.params.accept_soft for r in reqs],
+                         "seed": [r.seed & 0x7FFFFFFFFFFFFFFF for r in reqs], "draws": [r.draws for r in reqs]}
             emitted_h, count_h, acc_h, hidden = self.graphs.run([r.table_row for r in reqs], tokens, n, slot_lists,
-                                                                stop_lists, budgets)
+                                                                stop_lists, budgets, srows)
         else:
             target, hidden = ex.runner.forward_rows(
                 [r.table_row for r in reqs], tokens, n, slot_lists, mode=VERIFY,

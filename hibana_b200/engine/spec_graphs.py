@@ -14,8 +14,9 @@ captured graph per (batch bucket, depth):
 The verified hidden states stay on the device for the drafter (MTP feature of the last accepted row). Padded
 requests of a bucket point at block-table row 0 / KV slot 0, as in the decode graphs. On a CPU device the same
 body runs eagerly over the same static buffers, which is what the CPU tests compare with the host round.
-Covers exact greedy acceptance of unconstrained requests on models without recurrent state; relaxed / sampled
-acceptance, grammar masks and recurrent replay take the eager round. Reference: hibana/engine/spec_graphs.py:43-164
+Covers greedy and sampled requests (the rejection-sampling rule against the deterministic drafts is one kernel
+after the head, ops/sampling.py `spec_targets`; greedy requests keep their argmax) of unconstrained requests on
+models without recurrent state; relaxed-greedy acceptance, grammar masks and recurrent replay take the eager round. Reference: hibana/engine/spec_graphs.py:43-164
 (VerifyGraphs), hibana/engine/accept_graphs.py:50-310 (AcceptGraphs), hibana/proposers/mtp_graphs.py:15 (DraftGraphs).
 """
 from __future__ import annotations
@@ -31,7 +32,9 @@ from .context import VERIFY, ForwardContext
 from .request import MAX_STOPS
 
 T_IDS, T_POS, T_SLOT, T_ROW, T_FIELDS = 0, 1, 2, 3, 4          # token-level rows
-S_ROW, S_CTX, S_BUDGET, S_STOP0 = 0, 1, 2, 3                  # request-level rows (stop ids follow)
+# request-level rows: table row, context length, token budget, sampling parameters (seed and draw counter are
+# 64-bit: two rows each, on an even row so that the pair is 8-byte aligned for every bucket), then the stop ids
+S_ROW, S_CTX, S_BUDGET, S_TOPK, S_SEED, S_DRAWS, S_TEMP, S_TOPP, S_SOFT, S_STOP0 = 0, 1, 2, 3, 4, 6, 8, 9, 10, 11
 
 
 class VerifyBuffers:
@@ -82,8 +85,13 @@ class VerifyGraphs:
         h = r._forward(tok[T_IDS].long(), ctx)
         buf.hidden = ctx.extras.get("hidden")
         logits = self.model.logits(h, r.comm) if r.comm is not None else self.model.logits(h)
-        target = sampling.argmax(logits).view(b, k1)
         drafts = tok[T_IDS].view(b, k1)[:, 1:].long().contiguous()
+        pick = sampling.argmax(logits)
+        target, _ = sampling.spec_targets(
+            logits, drafts, seq[S_TEMP].view(torch.float32), seq[S_TOPK], seq[S_TOPP].view(torch.float32),
+            seq[S_SEED:S_SEED + 2].reshape(-1).view(torch.int64)[:b],
+            seq[S_DRAWS:S_DRAWS + 2].reshape(-1).view(torch.int64)[:b], seq[S_SOFT].view(torch.float32),
+            greedy_pick=pick)
         stops = seq[S_STOP0:S_STOP0 + MAX_STOPS].t().long().contiguous()
         emitted, count, accepted = sampling.accept_greedy(target, drafts, stops, seq[S_BUDGET].contiguous())
         buf.meta[:, :k1].copy_(emitted)
@@ -129,9 +137,11 @@ class VerifyGraphs:
         raise ValueError(f"batch {n} exceeds the largest verify bucket {self.buckets[-1]}")
 
     def run(self, rows: Sequence[int], tokens: Sequence[Sequence[int]], starts: Sequence[int],
-            slot_lists: Sequence[Sequence[int]], stop_lists: Sequence[Sequence[int]], budgets: Sequence[int]):
+            slot_lists: Sequence[Sequence[int]], stop_lists: Sequence[Sequence[int]], budgets: Sequence[int],
+            sampling_rows: Optional[dict] = None):
         """rows[i]: block-table row; tokens[i]: [pending, d_1 .. d_k]; starts[i]: position of the pending token;
-        slot_lists[i]: the k + 1 reserved KV slots. Returns (emitted [n][k + 1], count [n], accepted [n], hidden)
+        slot_lists[i]: the k + 1 reserved KV slots; sampling_rows: per-request lists temp / top_k / top_p / seed /
+        draws / soft (all greedy when None). Returns (emitted [n][k + 1], count [n], accepted [n], hidden)
         with the three lists on the host and `hidden` [bucket * (k + 1), H] on the device."""
         n, k1 = len(rows), self.k1
         self.runner._enter_forward()
@@ -156,6 +166,14 @@ class VerifyGraphs:
         for i, ids in enumerate(stop_lists):
             ids = list(ids)[:MAX_STOPS]
             sn[S_STOP0:S_STOP0 + len(ids), i] = ids
+        sn[S_TOPP].view(np.float32)[:] = 1.0
+        if sampling_rows is not None:                       # rows left at zero are greedy (temperature 0)
+            sn[S_TEMP].view(np.float32)[:n] = sampling_rows["temp"]
+            sn[S_TOPK, :n] = sampling_rows["top_k"]
+            sn[S_TOPP].view(np.float32)[:n] = sampling_rows["top_p"]
+            sn[S_SOFT].view(np.float32)[:n] = sampling_rows["soft"]
+            sn[S_SEED:S_SEED + 2].reshape(-1).view(np.int64)[:n] = sampling_rows["seed"]
+            sn[S_DRAWS:S_DRAWS + 2].reshape(-1).view(np.int64)[:n] = sampling_rows["draws"]
         buf.dev.copy_(buf.host, non_blocking=True)
         self.runner.h2d_bytes += buf.host.numel() * 4
         if buf.graph is not None:

@@ -5,6 +5,7 @@ hibana/kernels/relaxed_rank.py:13.
 """
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -19,6 +20,7 @@ nv.register("hb_argmax2", [P, L, I, I, I, P, I, I, P, P, P, P, P, P])
 ARGMAX_CHUNKS = 32
 nv.register("hb_accept_greedy", [P, P, P, I, P, P, I, I, P, P, P, P])
 nv.register("hb_rank_gap", [P, L, I, I, I, P, P, P, P])
+nv.register("hb_spec_targets", [P, L, I, I, I, I, P, P, P, P, P, P, P, P, I, P, P, P, P])
 
 MASK64 = (1 << 64) - 1
 
@@ -98,7 +100,7 @@ def sample_ref(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Ten
             # top-k off or wider than the kernel's candidate list: the full-vocabulary law (softmax, then nucleus),
             # drawn by inverse CDF in index order
             from ..engine.rejection import distribution
-            law = distribution(lg[r:r + 1].cpu(), t, 0, float(top_p[r]))[0].double()
+            law = distribution(lg[r:r + 1].cpu(), t, k if k > max_k else 0, float(top_p[r]))[0].double()
             u = uniform01(int(seeds[r]), int(offsets[r])) * float(law.sum())
             acc = torch.cumsum(law, 0)
             hit = (u < acc).nonzero()
@@ -125,8 +127,9 @@ def sample_ref(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Ten
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
            seeds: torch.Tensor, offsets: torch.Tensor, bitmask: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Temperature / top-k / top-p sampling; temperature <= 0 is greedy. seeds/offsets are uint64-as-int64.
-    1 <= top-k <= 64 draws from the k largest logits; top-k <= 0 (off) or > 64 draws from the softmax over the whole
-    vocabulary (then top-p), the same law `engine.rejection.distribution` gives speculative verification."""
+    1 <= top-k <= 64 draws from the k largest logits in candidate order; top-k <= 0 (off) or > 64 draws in index
+    order from the law `engine.rejection.distribution` gives speculative verification (softmax over the whole
+    vocabulary or its k largest tokens, then top-p)."""
     rows, vocab = logits.shape
     if nv.use_native(logits):
         out = torch.empty(rows, dtype=torch.int64, device=logits.device)
@@ -199,3 +202,66 @@ def rank_gap(logits: torch.Tensor, ids: torch.Tensor) -> tuple[torch.Tensor, tor
     lg = logits.float()
     mine = lg.gather(1, ids.view(-1, 1))
     return (lg > mine).sum(1).int(), (lg.max(1).values - mine.squeeze(1))
+
+
+def spec_targets_ref(logits: torch.Tensor, drafts: torch.Tensor, temperature, top_k, top_p, seeds, draws, soft,
+                     bitmask: Optional[torch.Tensor] = None):
+    """Plain PyTorch `spec_targets` (same uniforms, same law, draws by inverse CDF in index order)."""
+    from ..engine.rejection import distribution
+    b, k = drafts.shape
+    k1 = k + 1
+    lg = _apply_bitmask(logits, bitmask).cpu().view(b, k1, -1)
+    target = torch.zeros(b, k1, dtype=torch.int64)
+    p_draft = torch.ones(b, k1, dtype=torch.float32)
+
+    def draw(law, u):
+        acc = torch.cumsum(law.double(), 0)
+        hit = (u * float(acc[-1]) < acc).nonzero()
+        return int(hit[0]) if len(hit) else int((law > 0).nonzero()[-1])
+    for i in range(b):
+        t = float(temperature[i])
+        laws = distribution(lg[i], t, int(top_k[i]) if t > 0 else 1, float(top_p[i]) if t > 0 else 1.0)
+        for j in range(k1):
+            u_res = uniform01(int(seeds[i]), 2 * (int(draws[i]) + j) + 2)
+            if j == k:
+                target[i, j] = draw(laws[j], u_res)
+                continue
+            d = int(drafts[i, j])
+            pd = float(laws[j, d])
+            p_draft[i, j] = pd
+            u = uniform01(int(seeds[i]), 2 * (int(draws[i]) + j) + 1)
+            sf = float(soft[i]) if soft is not None else 0.0
+            if u < pd or (sf > 0 and u < math.exp(sf) * pd):
+                target[i, j] = d
+                continue
+            res = laws[j].clone()
+            res[d] = 0
+            target[i, j] = draw(res if float(res.sum()) > 1e-6 * float(laws[j].sum()) else laws[j], u_res)
+    return target.to(logits.device), p_draft.to(logits.device)
+
+
+def spec_targets(logits: torch.Tensor, drafts: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+                 top_p: torch.Tensor, seeds: torch.Tensor, draws: torch.Tensor, soft: Optional[torch.Tensor] = None,
+                 bitmask: Optional[torch.Tensor] = None,
+                 greedy_pick: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """Speculative rejection sampling against deterministic drafts in one kernel. logits [B * (k + 1), V] (request b
+    owns rows b * (k + 1) ...), drafts int64 [B, k], per-request temperature / top_k / top_p / seeds / draws (the
+    request's draw counter) / soft (relaxed acceptance, e^soft on the test). Returns (target int64 [B, k + 1],
+    p_draft fp32 [B, k + 1]): target[b, j] is drafts[b, j] where the draft stands, the draw from the residual law
+    where it does not, and the bonus draw at j = k, so `accept_greedy(target, drafts, ...)` finishes the round
+    exactly like a greedy one. Requests with temperature <= 0 are greedy (their law is the argmax; `greedy_pick`
+    int64 [B * (k + 1)], when the caller already has every row's argmax, is copied for them instead).
+    Reference: hibana/kernels/sampled_verify.py:17-106, hibana/engine/rejection.py:115-186."""
+    b, k = drafts.shape
+    if nv.use_native(logits):
+        dev = logits.device
+        target = torch.empty(b, k + 1, dtype=torch.int64, device=dev)
+        p_draft = torch.empty(b, k + 1, dtype=torch.float32, device=dev)
+        nv.check(nv.lib().hb_spec_targets(logits.data_ptr(), logits.stride(0), b, k, logits.shape[1],
+                                          int(logits.dtype == torch.float32), drafts.data_ptr(),
+                                          temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(),
+                                          seeds.data_ptr(), draws.data_ptr(), nv.ptr(soft), nv.ptr(bitmask),
+                                          bitmask.shape[1] if bitmask is not None else 0, nv.ptr(greedy_pick),
+                                          target.data_ptr(), p_draft.data_ptr(), nv.stream()), "hb_spec_targets")
+        return target, p_draft
+    return spec_targets_ref(logits, drafts, temperature, top_k, top_p, seeds, draws, soft, bitmask)

@@ -58,6 +58,17 @@ c = whole.forward(xs)
 torch.cuda.synchronize()
 res["layer"] = [[0.0, float((a.float() - c.float()).abs().max() / c.float().abs().max())]]
 res["status"] = nv.read_status(dev)
+# a receive buffer that is too small: nothing is written past it, the call ends, and the status word says why
+small = ExpertParallel.create(rank, world, dev, tokens=300, topk=4, experts=16, hidden=256, fmt="bf16", rows_cap=256)
+g = torch.Generator().manual_seed(9)
+fc1 = torch.randn(16, 256, 256, generator=g) * 0.05
+fc2 = torch.randn(16, 256, 128, generator=g) * 0.05
+ew = moe.ExpertWeights.create(fc1[rank * 8:(rank + 1) * 8].to(dev), fc2[rank * 8:(rank + 1) * 8].to(dev), "swiglu", "bf16")
+x = torch.randn(300, 256, generator=g).bfloat16().to(dev)
+ids, w = moe.route(torch.randn(300, 16, generator=g).to(dev), 4)
+small.forward(x, ids, w, ew)
+torch.cuda.synchronize()
+res["overflow_status"] = nv.read_status(dev)
 gathered = [None] * world
 dist.all_gather_object(gathered, res)
 if rank == 0:
@@ -84,6 +95,7 @@ def test_ep_all_to_all_matches_nccl_and_single_gpu(tmp_path):
     ranks = json.loads(line[len("RESULT "):])
     for r in ranks:
         assert r.pop("status") == 0
+        assert r.pop("overflow_status") == 10          # kOverflow: raised instead of silently dropping rows
         for name, outs in r.items():
             for e_nccl, e_single in outs:
                 assert e_nccl < 3e-2 and e_single < 3e-2, (name, outs)

@@ -321,14 +321,75 @@ def test_sampling_full_vocab_kernel_matches_distribution(top_p):
     seeds = torch.full((n,), 77, dtype=torch.int64, device="cuda")
     offs = torch.arange(n, dtype=torch.int64, device="cuda")
     out = sampling.sample(logits, temp, top_k, tp, seeds, offs)
-    law = distribution(row[None, :], 0.8, 0, top_p)[0]
     picks = out.cpu()
-    assert (law[picks] > 0).all()
-    freq = torch.bincount(picks, minlength=vocab).float() / n
-    assert (freq - law).abs().max() < 0.03
+    for start, k in ((1, 0), (0, 100)):      # odd rows: whole vocabulary; even rows: exactly the 100 largest
+        law = distribution(row[None, :], 0.8, k, top_p)[0]
+        mine = picks[start::2]
+        assert (law[mine] > 0).all()
+        freq = torch.bincount(mine, minlength=vocab).float() / mine.numel()
+        assert (freq - law).abs().max() < 0.04
     # the CPU statement of the same rule makes the same draws, up to rounding at CDF edges
     ref = sampling.sample(logits.cpu(), temp.cpu(), top_k.cpu(), tp.cpu(), seeds.cpu(), offs.cpu())
     assert (ref == picks).float().mean() > 0.99
+
+
+def _spec_case(dev, b=24, k=3, vocab=2000, seed=5):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(b * (k + 1), vocab, generator=g) * 3.0
+    logits[:, 40:48] = logits[:, 7:8]                       # ties around likely thresholds
+    top = logits.view(b, k + 1, vocab)[:, :k].argmax(-1)
+    drafts = torch.where(torch.rand(b, k, generator=g) < 0.6, top, torch.randint(0, vocab, (b, k), generator=g))
+    temp = torch.tensor([0.0 if i % 6 == 0 else 0.7 + 0.1 * (i % 4) for i in range(b)])
+    top_k = torch.tensor([(0, 20, 100, 5)[i % 4] for i in range(b)], dtype=torch.int32)
+    top_p = torch.tensor([(1.0, 0.9, 0.5)[i % 3] for i in range(b)])
+    seeds = torch.arange(b, dtype=torch.int64) + 1000
+    draws = torch.arange(b, dtype=torch.int64) * 3
+    soft = torch.tensor([0.5 if i % 5 == 0 else 0.0 for i in range(b)])
+    return [x.to(dev) for x in (logits, drafts, temp, top_k, top_p, seeds, draws, soft)]
+
+
+def test_spec_targets_reference_is_rejection_sampling_cpu():
+    """The targets rule + exact-prefix accept equals `verify_batch` with point-mass draft laws on the same uniforms."""
+    from hibana_b200.engine import rejection
+    logits, drafts, temp, top_k, top_p, seeds, draws, soft = _spec_case("cpu")
+    soft = torch.zeros_like(soft)
+    b, k = drafts.shape
+    target, p_draft = sampling.spec_targets(logits, drafts, temp, top_k, top_p, seeds, draws, soft)
+    emitted, count, accepted = sampling.accept_greedy(target, drafts)
+    laws = rejection.distribution(logits, temp.repeat_interleave(k + 1), top_k.repeat_interleave(k + 1),
+                                  top_p.repeat_interleave(k + 1)).view(b, k + 1, -1)
+    q = torch.zeros(b, k, logits.shape[1]).scatter_(2, drafts[:, :, None], 1.0)
+    u = torch.tensor([[[sampling.uniform01(int(seeds[i]), 2 * (int(draws[i]) + j) + 1 + t) for t in range(2)]
+                       for j in range(k + 1)] for i in range(b)])
+    ver = rejection.verify_batch(laws, q, drafts, u[..., 0].contiguous(), u[..., 1].contiguous())
+    assert torch.equal(accepted, ver.accepted) and torch.equal(count, ver.count)
+    for i in range(b):
+        assert torch.equal(emitted[i, :int(count[i])], ver.emitted[i, :int(count[i])]), i
+    assert torch.allclose(p_draft[:, :k], laws[:, :k].gather(2, drafts[:, :, None]).squeeze(2), atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_spec_targets_kernel_matches_reference():
+    """One kernel for sampled verification: same law (temperature, top-k with ties, nucleus), same uniforms, same
+    accepted drafts and correction / bonus draws as the PyTorch statement; greedy and relaxed requests included."""
+    args = _spec_case("cuda")
+    target, p_draft = sampling.spec_targets(*args)
+    ref_t, ref_p = sampling.spec_targets(*[a.cpu() for a in args])
+    assert torch.allclose(p_draft.cpu(), ref_p, atol=2e-4, rtol=1e-3)
+    same = (target.cpu() == ref_t)
+    assert same.float().mean() > 0.97, same.float().mean()       # rounding at CDF edges may move a draw
+    drafts = args[1]
+    stands = target[:, :-1] == drafts
+    assert torch.equal(stands.cpu(), ref_t[:, :-1] == drafts.cpu()) or same.float().mean() > 0.99
+    greedy = (args[2] <= 0).cpu()
+    lg = args[0].view(drafts.shape[0], drafts.shape[1] + 1, -1)
+    assert torch.equal(target.cpu()[greedy], lg.argmax(-1).cpu()[greedy])      # temperature 0: the argmax, every row
+    # bf16 logits take the same path
+    t16, _ = sampling.spec_targets(args[0].bfloat16(), *args[1:])
+    r16, _ = sampling.spec_targets(args[0].bfloat16().cpu(), *[a.cpu() for a in args[1:]])
+    assert (t16.cpu() == r16).float().mean() > 0.97
+    from hibana_b200 import _native as nv
+    assert nv.read_status() == 0
 
 
 def _fp4_case(dev, hq=8, hkv=2, d=128, t=70, seed=3):

@@ -218,6 +218,20 @@ def test_device_rounds_equal_host_rounds_cpu():
     assert len(outs[True][0][1]) == 11 and outs[True][2][1] == "length"
     ref = [r.output_ids for r in plain]
     assert outs[True][0][2] == ref[2] and outs[True][0][1] == ref[1][:11]
+    # sampled requests (and a greedy one beside them) take the same device round: the rejection-sampling rule is
+    # the kernel-shaped `spec_targets` in both, so tokens, rounds and the draw counters agree
+    params = [SamplingParams(max_tokens=16, temperature=0.8, top_k=50, top_p=0.9, seed=5), SamplingParams(max_tokens=12),
+              SamplingParams(max_tokens=16, temperature=1.1, seed=9)]
+    outs = {}
+    for on in (False, True):
+        with cfgmod.using(device_accept=on):
+            ex = Executor(model, max_batch=4, max_ctx=160, use_graphs=False, buckets=(1, 4))
+            ex.enable_spec(depth=3, proposer="ngram")
+            res = ex.generate_batch(prompts, params)
+            outs[on] = ([r.output_ids for r in res], [r.rounds for r in res], [r.draws for r in res],
+                        ex.spec.graphs.rounds if on else 0)
+    assert outs[True][:3] == outs[False][:3] and outs[True][3] > 0
+    assert outs[True][0][1] == ref[1][:12]                       # the greedy request is unaffected by its neighbours
 
 
 @pytest.mark.gpu
@@ -249,6 +263,17 @@ def test_captured_verify_rounds_on_gpu_are_exact():
     assert nv.read_status() == 0
     assert [r.output_ids for r in got] == want
     assert ex.spec.graphs.rounds > 0 and ex.spec.stats.emitted >= ex.spec.stats.rounds
+    # sampled requests replay the same graphs (the sampled-verify kernel sits after the head inside them) and are
+    # reproducible from their seeds
+    sp2 = [SamplingParams(max_tokens=20, temperature=0.9, top_p=0.9, seed=3), SamplingParams(max_tokens=20),
+           SamplingParams(max_tokens=20, temperature=0.7, top_k=40, seed=4)]
+    rounds0 = ex.spec.graphs.rounds
+    a = [r.output_ids for r in ex.generate_batch(prompts, sp2)]
+    b = [r.output_ids for r in ex.generate_batch(prompts, sp2)]
+    torch.cuda.synchronize()
+    assert nv.read_status() == 0
+    assert a == b and a[1] == want[1][:20] and ex.spec.graphs.rounds > rounds0
+    assert a[0] != want[0][:20] or a[2] != want[2][:20]         # temperature did something
 
 
 def test_draft_heads_shortlist_and_vocab_parallel_cpu():
