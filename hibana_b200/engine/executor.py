@@ -328,6 +328,8 @@ class Executor:
         self.runner.capture()
         if self.spec is not None and getattr(self.spec, "graphs", None) is not None:
             self.spec.graphs.capture()
+        if self.spec is not None and getattr(self.spec, "draft_graphs", None) is not None:
+            self.spec.draft_graphs.capture()
 
     # ---- offline batch API
     def generate_batch(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams],

@@ -60,6 +60,11 @@ class SpecDecoder:
         self.graphs = VerifyGraphs(executor.runner, depth) if cfgmod.current().device_accept else None
         if self.graphs is not None and not self.graphs.supported():
             self.graphs = None
+        # the MTP head's chained draft steps as one graph per bucket; its drafts feed the verify graph on the device
+        self.draft_graphs = None
+        if self.graphs is not None and self.mtp is not None and proposer is None:
+            from .spec_graphs import DraftGraphs
+            self.draft_graphs = DraftGraphs(executor.runner, self.mtp, depth)
 
     # ---- helpers
     def _dev(self, arr, dtype):
@@ -82,7 +87,8 @@ class SpecDecoder:
                              q_indptr=self._dev(indptr, torch.int32),
                              seq_rows=self._dev([r.table_row for r in reqs], torch.int32), max_rows=max(counts),
                              batch=b)
-        g, normed = self.mtp.forward(hiddens, self._dev(next_ids, torch.int64), ctx, self.ex.kv)
+        ids_t = next_ids if isinstance(next_ids, torch.Tensor) else self._dev(next_ids, torch.int64)
+        g, normed = self.mtp.forward(hiddens, ids_t, ctx, self.ex.kv)
         tok = sampling.argmax(self.model.logits(normed))
         return g, tok
 
@@ -201,15 +207,24 @@ class SpecDecoder:
             drafts.copy_(toks.view(b, k))           # short drafts arrive padded: a padded token is simply refused
             if not isinstance(prop, torch.Tensor) and prop.laws is not None:
                 self._laws = prop.laws.to(dev)
+        elif self.draft_graphs is not None and b <= self.draft_graphs.buckets[-1]:
+            drafts = self.draft_graphs.run([r.table_row for r in reqs], [r.output_ids[-1] for r in reqs],
+                                           [nn - 1 for nn in n], [r.kv_slots[nn - 1:nn - 1 + k] for r, nn in zip(reqs, n)],
+                                           feat)
         else:
             hid = feat
             ids = [r.output_ids[-1] for r in reqs]
             for j in range(k):
                 hid, tok = self._mtp_rows(reqs, hid, ids, [nn - 1 + j for nn in n], [1] * b)
                 drafts[:, j] = tok
-                ids = tok.tolist() if j + 1 < k else None
+                ids = tok if j + 1 < k else None
         # ---- verify
-        host_drafts = drafts.tolist()
+        on_device = (self.draft_graphs is not None and self.proposer is None and self.graphs is not None
+                     and ex.state_pool is None and b <= self.graphs.buckets[-1]
+                     and not any(r.grammar is not None for r in reqs)
+                     and not any(r.params.greedy and (r.params.accept_top_k > 1 or r.params.accept_margin > 0)
+                                 for r in reqs))
+        host_drafts = [[0] * k for _ in reqs] if on_device else drafts.tolist()   # on_device: no wait for the drafts
         tokens = [[r.output_ids[-1]] + host_drafts[i] for i, r in enumerate(reqs)]
         extras = {"want_hidden": True}
         has_state = ex.state_pool is not None
@@ -250,7 +265,8 @@ class SpecDecoder:
                          "top_p": [r.params.top_p for r in reqs], "soft": [r.params.accept_soft for r in reqs],
                          "seed": [r.seed & 0x7FFFFFFFFFFFFFFF for r in reqs], "draws": [r.draws for r in reqs]}
             emitted_h, count_h, acc_h, hidden = self.graphs.run([r.table_row for r in reqs], tokens, n, slot_lists,
-                                                                stop_lists, budgets, srows)
+                                                                stop_lists, budgets, srows,
+                                                                drafts_dev=drafts if on_device else None)
         else:
             target, hidden = ex.runner.forward_rows(
                 [r.table_row for r in reqs], tokens, n, slot_lists, mode=VERIFY,

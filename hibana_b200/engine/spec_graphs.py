@@ -138,10 +138,12 @@ class VerifyGraphs:
 
     def run(self, rows: Sequence[int], tokens: Sequence[Sequence[int]], starts: Sequence[int],
             slot_lists: Sequence[Sequence[int]], stop_lists: Sequence[Sequence[int]], budgets: Sequence[int],
-            sampling_rows: Optional[dict] = None):
+            sampling_rows: Optional[dict] = None, drafts_dev: Optional[torch.Tensor] = None):
         """rows[i]: block-table row; tokens[i]: [pending, d_1 .. d_k]; starts[i]: position of the pending token;
         slot_lists[i]: the k + 1 reserved KV slots; sampling_rows: per-request lists temp / top_k / top_p / seed /
-        draws / soft (all greedy when None). Returns (emitted [n][k + 1], count [n], accepted [n], hidden)
+        draws / soft (all greedy when None); drafts_dev: int64 [n, k] drafts still on the device (tokens[i] then
+        only needs its pending token; the drafted ids are copied into the static buffer on the stream, so the
+        host never waits for them). Returns (emitted [n][k + 1], count [n], accepted [n], hidden)
         with the three lists on the host and `hidden` [bucket * (k + 1), H] on the device."""
         n, k1 = len(rows), self.k1
         self.runner._enter_forward()
@@ -155,7 +157,10 @@ class VerifyGraphs:
         sn[S_STOP0:] = -1
         tn[T_POS] = np.tile(np.arange(k1, dtype=np.int32), buf.bucket)
         m = n * k1
-        tn[T_IDS, :m] = np.asarray(tokens, dtype=np.int32).reshape(-1)
+        if drafts_dev is None:
+            tn[T_IDS, :m] = np.asarray(tokens, dtype=np.int32).reshape(-1)
+        else:
+            tn[T_IDS, :m:k1] = [t[0] for t in tokens]
         st = np.asarray(starts, dtype=np.int32)
         tn[T_POS, :m] = (st[:, None] + np.arange(k1, dtype=np.int32)[None, :]).reshape(-1)
         tn[T_SLOT, :m] = np.asarray(slot_lists, dtype=np.int32).reshape(-1)
@@ -176,6 +181,8 @@ class VerifyGraphs:
             sn[S_DRAWS:S_DRAWS + 2].reshape(-1).view(np.int64)[:n] = sampling_rows["draws"]
         buf.dev.copy_(buf.host, non_blocking=True)
         self.runner.h2d_bytes += buf.host.numel() * 4
+        if drafts_dev is not None:
+            buf.tok[T_IDS].view(buf.bucket, k1)[:n, 1:].copy_(drafts_dev)
         if buf.graph is not None:
             buf.graph.replay()
         else:
@@ -189,3 +196,96 @@ class VerifyGraphs:
         self.rounds += 1
         meta = buf.meta_host[:n].tolist()
         return ([row[:k1] for row in meta], [row[k1] for row in meta], [row[k1 + 1] for row in meta], buf.hidden)
+
+
+D_IDS, D_POS, D_ROW, D_SLOT0 = 0, 1, 2, 3        # rows of the draft graphs' int32 buffer (k slot rows follow)
+
+
+class DraftBuffers:
+    def __init__(self, bucket: int, k: int, hidden: int, device: torch.device):
+        self.bucket = bucket
+        pin = device.type == "cuda"
+        self.host = torch.zeros(D_SLOT0 + k, bucket, dtype=torch.int32, pin_memory=pin)
+        self.np = self.host.numpy()
+        self.dev = torch.zeros(D_SLOT0 + k, bucket, dtype=torch.int32, device=device)
+        self.feat = torch.zeros(bucket, hidden, dtype=torch.bfloat16, device=device)
+        self.drafts = torch.zeros(bucket, k, dtype=torch.int64, device=device)
+        self.indptr = torch.arange(bucket + 1, dtype=torch.int32, device=device)
+        self.graph = None
+
+
+class DraftGraphs:
+    """The MTP head's k chained draft steps (embed + fuse with the previous hidden, attention over the head's own
+    KV, MLP, shared lm_head, argmax; the token feeds the next step) as one captured graph per batch bucket. The
+    drafted ids stay on the device: the verify graph reads them there, so a speculative round is two pinned
+    uploads, two graph replays and one read-back. Reference: hibana/proposers/mtp_graphs.py:15-120."""
+
+    def __init__(self, runner, mtp, depth: int, buckets: Optional[Sequence[int]] = None):
+        self.runner, self.model, self.mtp, self.k = runner, runner.model, mtp, depth
+        self.device = runner.device
+        self.buckets = tuple(buckets or runner.buckets)
+        hidden = self.model.target.hidden
+        self.bufs = {b: DraftBuffers(b, depth, hidden, self.device) for b in self.buckets}
+        self.launches: dict = {}
+        self.rounds = 0
+
+    def _body(self, buf: DraftBuffers) -> None:
+        r, b = self.runner, buf.bucket
+        d = buf.dev
+        hid, ids = buf.feat, d[D_IDS].long()
+        for j in range(self.k):
+            pos = d[D_POS] + j
+            ctx = ForwardContext(VERIFY, positions=pos, slots=d[D_SLOT0 + j], kv_indices=r.block_table,
+                                 ctx_len=pos + 1, q_indptr=buf.indptr, seq_rows=d[D_ROW], max_rows=1, batch=b,
+                                 comm=r.comm, seq_starts_host=[1] * b)
+            hid, normed = self.mtp.forward(hid, ids, ctx, r.kv)
+            logits = self.model.logits(normed, r.comm) if r.comm is not None else self.model.logits(normed)
+            ids = sampling.argmax(logits)
+            buf.drafts[:, j].copy_(ids)
+
+    def capture(self) -> None:
+        if self.device.type != "cuda" or not self.runner.use_graphs:
+            return
+        for buf in self.bufs.values():
+            buf.dev.zero_()
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._body(buf)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            before = nv.LAUNCHES
+            with torch.cuda.graph(g):
+                self._body(buf)
+            self.launches[buf.bucket] = nv.LAUNCHES - before
+            buf.graph = g
+
+    def run(self, rows: Sequence[int], pending: Sequence[int], positions: Sequence[int],
+            slot_lists: Sequence[Sequence[int]], feat: torch.Tensor) -> torch.Tensor:
+        """rows[i]: block-table row; pending[i]: the token whose successor is drafted first; positions[i]: the
+        position of the hidden state `feat[i]` (the pending token sits one further); slot_lists[i]: the head's k KV
+        slots from there. Returns the drafts int64 [n, k], on the device."""
+        n = len(rows)
+        buf = None
+        for b in self.buckets:
+            if b >= n:
+                buf = self.bufs[b]
+                break
+        if buf is None:
+            raise ValueError(f"batch {n} exceeds the largest draft bucket {self.buckets[-1]}")
+        a = buf.np
+        a[:] = 0
+        a[D_IDS, :n] = pending
+        a[D_POS, :n] = positions
+        a[D_ROW, :n] = rows
+        a[D_SLOT0:, :n] = np.asarray(slot_lists, dtype=np.int32).T
+        buf.dev.copy_(buf.host, non_blocking=True)
+        buf.feat[:n].copy_(feat)
+        self.runner.h2d_bytes += buf.host.numel() * 4
+        if buf.graph is not None:
+            buf.graph.replay()
+        else:
+            self._body(buf)
+        self.rounds += 1
+        return buf.drafts[:n]

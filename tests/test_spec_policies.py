@@ -320,3 +320,61 @@ def test_draft_heads_shortlist_and_vocab_parallel_cpu():
         assert torch.equal(ids_r, full.topk(3, -1).indices) and torch.equal(am, full.argmax(-1))
         assert torch.allclose(vals_r, full.topk(3, -1).values, atol=1e-4)
         assert torch.allclose(cf, conf, atol=1e-4)
+
+
+def _attn_mtp_model(device):
+    """Attention-only hybrid with an MTP head (no recurrent state: the whole round can stay on the device)."""
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import ATTN, MLP, Target
+    t = Target(name="attn-mtp", family="hybrid_moe", hidden=256, vocab=2048, layers=((ATTN, MLP),) * 2, q_heads=4,
+               kv_heads=2, head_dim=64, rope_theta=1e4, ffn=512, mtp_layers=1, mtp_depth=3, max_context=512,
+               prefill_chunk=128)
+    return HybridModel(t, device, seed=0)
+
+
+def test_mtp_round_with_draft_graphs_equals_plain_decoding_cpu():
+    """MTP drafting as one chained body per bucket, the drafts handed to the verify body without a host copy:
+    the engine still emits exactly the plain greedy tokens, and sampled requests are reproducible."""
+    import torch
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    model = _attn_mtp_model("cpu")
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (21, 33, 9)]
+    sp = SamplingParams(max_tokens=14, ignore_eos=True)
+    want = [r.output_ids for r in Executor(model, max_batch=4, max_ctx=128, use_graphs=False).generate_batch(prompts, sp)]
+    ex = Executor(model, max_batch=4, max_ctx=128, use_graphs=False, buckets=(1, 4))
+    ex.enable_spec(depth=3)
+    assert ex.spec.draft_graphs is not None
+    got = ex.generate_batch(prompts, sp)
+    assert [r.output_ids for r in got] == want
+    assert ex.spec.draft_graphs.rounds > 0 and ex.spec.graphs.rounds == ex.spec.draft_graphs.rounds
+    sampled = [SamplingParams(max_tokens=10, temperature=0.9, seed=s, ignore_eos=True) for s in (1, 2, 3)]
+    a = [r.output_ids for r in ex.generate_batch(prompts, sampled)]
+    b = [r.output_ids for r in ex.generate_batch(prompts, sampled)]
+    assert a == b
+
+
+@pytest.mark.gpu
+def test_mtp_round_graphs_on_gpu():
+    """Draft graph + verify graph per round on the GPU: tokens equal plain greedy decoding."""
+    import torch
+    from hibana_b200 import _native as nv
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    model = _attn_mtp_model("cuda:0")
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (21, 33, 9)]
+    sp = SamplingParams(max_tokens=20, ignore_eos=True)
+    plain = Executor(model, max_batch=4, max_ctx=256, use_graphs=True)
+    plain.capture_graphs()
+    want = [r.output_ids for r in plain.generate_batch(prompts, sp)]
+    ex = Executor(model, max_batch=4, max_ctx=256, use_graphs=True, buckets=(1, 4))
+    ex.enable_spec(depth=3)
+    ex.capture_graphs()
+    assert all(b.graph is not None for b in ex.spec.draft_graphs.bufs.values())
+    got = ex.generate_batch(prompts, sp)
+    torch.cuda.synchronize()
+    assert nv.read_status() == 0
+    assert [r.output_ids for r in got] == want
+    assert ex.spec.draft_graphs.rounds > 0 and ex.spec.stats.emitted >= ex.spec.stats.rounds
