@@ -548,6 +548,54 @@ sample_kernel(const T* __restrict__ logits, long long ld, int vocab, const float
   }
 }
 
+// Walk of a block drafter's candidate lattice, one warp per request, lane = candidate (width <= 32). Step j scores
+// candidate w as scores[b][j][previous choice][w]; the greedy walk takes the best (lowest index on ties), the
+// sampled walk draws from softmax(row / T) by inverse CDF with the caller's uniform. Writes the chosen tokens and
+// candidate indices, the probability of every candidate at every step (the draft law on its support, what
+// speculative sampling divides by) and the unit-temperature probability of the chosen one (acceptance estimate).
+__global__ void lattice_walk_kernel(const long long* __restrict__ cand, const float* __restrict__ scores,
+                                    const float* __restrict__ temperature, const float* __restrict__ uniforms,
+                                    int batch, int k, int width, long long* __restrict__ tokens,
+                                    int* __restrict__ chosen, float* __restrict__ probs, float* __restrict__ estimate) {
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (b >= batch) return;
+  const float temp = temperature ? temperature[b] : 0.f;
+  const bool sampled = temp > 0.f && uniforms != nullptr;
+  int prev = 0;
+  for (int j = 0; j < k; ++j) {
+    const long long base = (static_cast<long long>(b) * k + j) * width;
+    const float x = lane < width ? scores[(base + prev) * width + lane] : -INFINITY;
+    const float mx = warp_max(x);
+    const float e1 = lane < width ? __expf(x - mx) : 0.f;              // unit temperature: the estimate
+    const float z1 = warp_sum(e1);
+    float p = e1 / z1;
+    int pick;
+    if (sampled) {
+      const float et = lane < width ? __expf((x - mx) / temp) : 0.f;
+      p = et / warp_sum(et);
+      float cdf = p;                                                   // inclusive scan over the lanes
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, cdf, o);
+        if (lane >= o) cdf += up;
+      }
+      const unsigned below = __ballot_sync(0xffffffffu, lane < width && cdf < uniforms[static_cast<long long>(b) * k + j]);
+      pick = min(__popc(below), width - 1);
+    } else {
+      const unsigned best = __ballot_sync(0xffffffffu, lane < width && x == mx);
+      pick = __ffs(best) - 1;
+    }
+    if (probs != nullptr && lane < width) probs[base + lane] = p;
+    const float p1 = __shfl_sync(0xffffffffu, e1 / z1, pick);
+    if (lane == 0) {
+      tokens[static_cast<long long>(b) * k + j] = cand[base + pick];
+      chosen[static_cast<long long>(b) * k + j] = pick;
+      if (estimate != nullptr) estimate[static_cast<long long>(b) * k + j] = p1;
+    }
+    prev = pick;
+  }
+}
+
 // Speculative rejection sampling against point-mass drafts, one CTA per verified row. Request b owns logits rows
 // [b * (k + 1), (b + 1) * (k + 1)); row j < k sees draft d = drafts[b][j]: with p the row's law (law_row) the draft
 // stands when u * 1 < p[d] (or, for a relaxed request, u < e^soft * p[d]); otherwise the row's token is a draw from
@@ -702,6 +750,17 @@ int hb_sample(const void* logits, long long ld, int rows, int vocab, int is_f32,
   if (is_f32) sample_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float*>(logits), HB_SAMPLE_ARGS);
   else sample_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), HB_SAMPLE_ARGS);
 #undef HB_SAMPLE_ARGS
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_lattice_walk(const void* cand, const void* scores, const void* temperature, const void* uniforms, int batch,
+                    int k, int width, void* tokens, void* chosen, void* probs, void* estimate, void* stream) {
+  if (batch <= 0 || k <= 0) return 0;
+  if (width < 1 || width > 32) return 1;
+  lattice_walk_kernel<<<(batch + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const long long*>(cand), static_cast<const float*>(scores), static_cast<const float*>(temperature),
+      static_cast<const float*>(uniforms), batch, k, width, static_cast<long long*>(tokens),
+      static_cast<int*>(chosen), static_cast<float*>(probs), static_cast<float*>(estimate));
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

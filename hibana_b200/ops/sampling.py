@@ -20,6 +20,7 @@ nv.register("hb_argmax2", [P, L, I, I, I, P, I, I, P, P, P, P, P, P])
 ARGMAX_CHUNKS = 32
 nv.register("hb_accept_greedy", [P, P, P, I, P, P, I, I, P, P, P, P])
 nv.register("hb_rank_gap", [P, L, I, I, I, P, P, P, P])
+nv.register("hb_lattice_walk", [P, P, P, P, I, I, I, P, P, P, P, P])
 nv.register("hb_spec_targets", [P, L, I, I, I, I, P, P, P, P, P, P, P, P, I, P, P, P, P])
 
 MASK64 = (1 << 64) - 1
@@ -265,3 +266,44 @@ def spec_targets(logits: torch.Tensor, drafts: torch.Tensor, temperature: torch.
                                           target.data_ptr(), p_draft.data_ptr(), nv.stream()), "hb_spec_targets")
         return target, p_draft
     return spec_targets_ref(logits, drafts, temperature, top_k, top_p, seeds, draws, soft, bitmask)
+
+
+def lattice_walk(cand: torch.Tensor, scores: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+                 uniforms: Optional[torch.Tensor] = None):
+    """Walks a block drafter's candidate lattice. cand int64 [B, k, W], scores fp32 [B, k, W (previous choice), W];
+    greedy when `temperature` / `uniforms` are None or a request's temperature is <= 0, else the path is sampled
+    from softmax(row / T) with uniforms fp32 [B, k]. Returns (tokens int64 [B, k], chosen candidate index int32
+    [B, k], probs fp32 [B, k, W]: the law every token was drawn from on its support, estimate fp32 [B, k]: the
+    unit-temperature probability of the chosen candidate). One warp per request on the GPU (W <= 32).
+    Reference: hibana/kernels/draft_selection.py:14-99."""
+    b, k, w = cand.shape
+    if nv.use_native(scores) and w <= 32:
+        dev = scores.device
+        tokens = torch.empty(b, k, dtype=torch.int64, device=dev)
+        chosen = torch.empty(b, k, dtype=torch.int32, device=dev)
+        probs = torch.empty(b, k, w, dtype=torch.float32, device=dev)
+        est = torch.empty(b, k, dtype=torch.float32, device=dev)
+        scores = scores.float().contiguous()
+        nv.check(nv.lib().hb_lattice_walk(cand.contiguous().data_ptr(), scores.data_ptr(), nv.ptr(temperature),
+                                          nv.ptr(uniforms), b, k, w, tokens.data_ptr(), chosen.data_ptr(),
+                                          probs.data_ptr(), est.data_ptr(), nv.stream()), "hb_lattice_walk")
+        return tokens, chosen, probs, est
+    prev = torch.zeros(b, dtype=torch.long, device=cand.device)
+    toks, idxs, ps, ests = [], [], [], []
+    for j in range(k):
+        row = scores[:, j].float().gather(1, prev[:, None, None].expand(-1, 1, w)).squeeze(1)
+        p1 = torch.softmax(row, -1)
+        pick = row.argmax(-1)
+        p = p1
+        if temperature is not None and uniforms is not None:
+            hot = temperature > 0
+            pt = torch.softmax(row / temperature.clamp_min(1e-6)[:, None], -1)
+            drawn = (pt.cumsum(-1) < uniforms[:, j, None]).sum(-1).clamp_max(w - 1)
+            pick = torch.where(hot, drawn, pick)
+            p = torch.where(hot[:, None], pt, p1)
+        prev = pick
+        idxs.append(pick.int())
+        toks.append(cand[:, j].gather(1, pick[:, None]).squeeze(1))
+        ps.append(p)
+        ests.append(p1.gather(1, pick[:, None]).squeeze(1))
+    return torch.stack(toks, 1), torch.stack(idxs, 1), torch.stack(ps, 1), torch.stack(ests, 1)

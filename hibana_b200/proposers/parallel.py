@@ -15,7 +15,8 @@ from typing import Optional, Sequence
 import torch
 
 from ..engine.contracts import Capabilities, Proposal, VerifiedFeatures
-from ..models.parallel_draft import BlockDrafter, greedy_lattice, sample_lattice
+from ..models.parallel_draft import BlockDrafter
+from ..ops.sampling import lattice_walk
 from ..ops.sampling import uniform01
 
 
@@ -88,20 +89,19 @@ class ParallelProposer:
         hidden = m.forward(anchors, positions, list(ck), list(cv), mask, depth)
         cand, scores = m.select(hidden, anchors)
         greedy = all(r.params.greedy for r in reqs)
-        if greedy:
-            toks, idx = greedy_lattice(cand, scores)
-            laws = None
-        else:
-            temp = torch.tensor([max(r.params.temperature, 1e-6) if not r.params.greedy else 1e-6 for r in reqs],
-                                device=dev)
+        temp = u = None
+        if not greedy:
+            temp = torch.tensor([0.0 if r.params.greedy else max(r.params.temperature, 1e-6) for r in reqs],
+                                dtype=torch.float32, device=dev)
             u = torch.tensor([[uniform01(r.seed ^ 0x5DEECE66D, r.draws + j) for j in range(depth)] for r in reqs],
-                             device=dev)
-            toks, laws = sample_lattice(cand, scores, temp, u, m.vocab)
-            idx = (cand == toks[..., None]).float().argmax(-1)
-        # acceptance estimate: probability mass of the chosen candidate among its alternatives
-        prev = torch.cat([torch.zeros(b, 1, dtype=torch.long, device=dev), idx[:, :-1]], 1)
-        rows = scores.gather(2, prev[:, :, None, None].expand(-1, -1, 1, m.width)).squeeze(2)
-        est = torch.softmax(rows, -1).gather(2, idx[..., None]).squeeze(-1)
+                             dtype=torch.float32, device=dev)
+        # one warp per request walks the lattice (ops/sampling.py `lattice_walk`): tokens, the law each was drawn
+        # from on its candidates, and the acceptance estimate (unit-temperature mass of the choice) in one launch
+        toks, idx, probs, est = lattice_walk(cand, scores, temp, u)
+        laws = None
+        if not greedy:       # speculative sampling wants the draft law dense over the vocabulary
+            laws = torch.zeros(b, depth, m.vocab, device=dev)
+            laws.scatter_add_(2, cand, probs)
         return Proposal(toks, laws=laws, scores=est)
 
     # ---- feedback

@@ -392,6 +392,26 @@ def test_spec_targets_kernel_matches_reference():
     assert nv.read_status() == 0
 
 
+@pytest.mark.gpu
+def test_lattice_walk_kernel_matches_torch():
+    g = torch.Generator().manual_seed(4)
+    b, k, w = 37, 5, 12
+    cand = torch.randint(0, 3000, (b, k, w), generator=g)
+    scores = torch.randn(b, k, w, w, generator=g) * 2
+    scores[3, 1, :, 2] = scores[3, 1, :, 5] = 9.0                 # tie: the lower candidate index wins
+    temp = torch.tensor([0.0 if i % 4 == 0 else 0.6 + 0.05 * i for i in range(b)])
+    u = torch.rand(b, k, generator=g)
+    for args in ((None, None), (temp, u)):
+        ref = sampling.lattice_walk(cand, scores, *args)
+        got = sampling.lattice_walk(cand.cuda(), scores.cuda(), *[a.cuda() if a is not None else None for a in args])
+        same = (got[0].cpu() == ref[0]).float().mean()
+        assert same == 1.0 if args[0] is None else same > 0.97
+        if args[0] is None:
+            assert torch.equal(got[1].cpu(), ref[1])
+            assert torch.allclose(got[2].cpu(), ref[2], atol=1e-5) and torch.allclose(got[3].cpu(), ref[3], atol=1e-5)
+    assert int(sampling.lattice_walk(cand.cuda(), scores.cuda())[1][3, 1]) == 2
+
+
 def _fp4_case(dev, hq=8, hkv=2, d=128, t=70, seed=3):
     from hibana_b200.cache.kv_pool import KvPool
     g = torch.Generator().manual_seed(seed)

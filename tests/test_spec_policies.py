@@ -144,6 +144,14 @@ def test_block_drafter_lattice_and_engine_exactness_cpu():
     st, laws = sample_lattice(cand, scores, torch.tensor([1.0, 0.7]), u, 50)
     assert laws.shape == (2, 3, 50) and torch.allclose(laws.sum(-1), torch.ones(2, 3), atol=1e-5)
     assert (laws.gather(2, st[..., None]) > 0).all()
+    # the one-launch walk (ops/sampling.py) makes the same choices and reports the same laws on the candidates
+    from hibana_b200.ops import sampling
+    wt, wi, wp, we = sampling.lattice_walk(cand, scores)
+    assert torch.equal(wt, toks) and torch.equal(wi.long(), idx)
+    wt, wi, wp, we = sampling.lattice_walk(cand, scores, torch.tensor([1.0, 0.7]), u)
+    assert torch.equal(wt, st)
+    dense = torch.zeros(2, 3, 50).scatter_add_(2, cand, wp)
+    assert torch.allclose(dense, laws, atol=1e-6) and bool(((we > 0) & (we <= 1)).all())
     t = scaled(dense_tiny(), weight_format="bf16")
     model = DenseModel(t, "cpu", seed=0)
     prompts = [torch.randint(0, t.vocab, (n,), generator=g).tolist() for n in (19, 33)]
