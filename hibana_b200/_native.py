@@ -19,6 +19,7 @@ _LIB: Optional[ctypes.CDLL] = None
 _TRIED = False
 _LOCK = threading.Lock()
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libhibana_b200.so"
+BOUNDS_LIB_PATH = LIB_PATH.with_name("libhibana_b200_bounds.so")
 
 P, I, L, F = c_void_p, c_int, c_longlong, c_float
 
@@ -57,15 +58,18 @@ def lib() -> Optional[ctypes.CDLL]:
         if _LIB is not None or _TRIED:
             return _LIB
         _TRIED = True
-        if not LIB_PATH.exists():
+        from . import config
+        bounds = config.current().bounds       # the checked-index flavour (build_native.build(bounds=True))
+        path = BOUNDS_LIB_PATH if bounds else LIB_PATH
+        if not path.exists():
             try:
                 from . import build_native
 
-                build_native.build()
+                build_native.build(bounds=bounds)
             except Exception:  # noqa: BLE001 - reported below when a GPU is present
                 pass
-        if LIB_PATH.exists() and torch.cuda.is_available():
-            loaded = ctypes.CDLL(str(LIB_PATH))
+        if path.exists() and torch.cuda.is_available():
+            loaded = ctypes.CDLL(str(path))
             for name, sig in _SIGS.items():
                 _bind(loaded, name, sig, False)
             for name, sig in _VOID.items():
@@ -73,8 +77,40 @@ def lib() -> Optional[ctypes.CDLL]:
             _LIB = loaded
         elif torch.cuda.is_available():
             raise RuntimeError(
-                f"{LIB_PATH} is missing on a machine with a CUDA device; run `python -m hibana_b200.build_native`")
+                f"{path} is missing on a machine with a CUDA device; run `python -m hibana_b200.build_native`")
     return _LIB
+
+
+BOUND_KV_SLOTS, BOUND_STATE_SLOTS, BOUND_VOCAB, BOUND_ROWS = 0, 1, 2, 3
+BOUND_KERNELS = {1: "rope_kv_write", 2: "kv_copy", 3: "conv1d", 4: "mamba2_scan", 5: "gdn_scan", 6: "attn_decode",
+                 7: "attn_general", 8: "embedding"}
+
+
+def bounds_enabled() -> bool:
+    """True when the loaded library is the checked-index flavour."""
+    loaded = lib()
+    return bool(loaded is not None and hasattr(loaded, "hb_bounds_enabled") and loaded.hb_bounds_enabled())
+
+
+def set_bound(which: int, value: int) -> None:
+    """Tells the checked-index flavour the size of a pool (no-op in the normal build). Pools call it when built."""
+    if _LIB is not None and bounds_enabled():
+        _LIB.hb_bounds_set.argtypes = [c_int, c_longlong]
+        check(_LIB.hb_bounds_set(which, int(value)), "hb_bounds_set", launches=0)
+
+
+def read_bounds() -> Optional[dict]:
+    """The first out-of-range index a kernel was handed since the last read ({"hits", "kernel", "index", "limit"}),
+    or None; the access itself was skipped. Always None in the normal build."""
+    if not bounds_enabled():
+        return None
+    out = (c_longlong * 4)()
+    torch.cuda.synchronize()
+    check(_LIB.hb_bounds_read(out), "hb_bounds_read", launches=0)
+    if not out[0]:
+        return None
+    return {"hits": int(out[0]), "kernel": BOUND_KERNELS.get(int(out[1]), str(out[1])), "index": int(out[2]),
+            "limit": int(out[3])}
 
 
 def available() -> bool:

@@ -7,6 +7,9 @@ JIT-compiles one torch extension per kernel at first use (hibana/kernels/w3.py:2
 hibana/engine/config.py:92).
 
 Run ``python -m hibana_b200.build_native`` to (re)build; ``build()`` is incremental on file mtimes.
+``build(bounds=True)`` (``--bounds``) makes the checked-index flavour ``libhibana_b200_bounds.so``: the same
+sources with ``-DHB_BOUNDS -rdc=true``, in which every pool index a kernel is handed goes through a range check
+that records the first violation and skips the access (csrc/hb_common.cuh ``index_ok``, csrc/bounds.cu).
 """
 from __future__ import annotations
 
@@ -47,8 +50,8 @@ def _headers_mtime() -> float:
     return max((h.stat().st_mtime for h in hs), default=0.0)
 
 
-def _compile(src: Path, nvcc: str, verbose: bool, extra: list[str]) -> tuple[Path, str]:
-    obj = OBJ_DIR / (src.name + ".o")
+def _compile(src: Path, nvcc: str, verbose: bool, extra: list[str], obj_dir: Path = OBJ_DIR) -> tuple[Path, str]:
+    obj = obj_dir / (src.name + ".o")
     newest_dep = max(src.stat().st_mtime, _headers_mtime())
     if obj.exists() and obj.stat().st_mtime >= newest_dep:
         return obj, ""
@@ -63,36 +66,43 @@ def _compile(src: Path, nvcc: str, verbose: bool, extra: list[str]) -> tuple[Pat
     return obj, (proc.stderr if verbose else "")
 
 
-def build(verbose: bool = False, ptxas_info: bool = False) -> Path:
+BOUNDS_LIB_PATH = LIB_DIR / "libhibana_b200_bounds.so"
+
+
+def build(verbose: bool = False, ptxas_info: bool = False, bounds: bool = False) -> Path:
     """Compiles what changed and links the library. Returns its path."""
     nvcc = nvcc_path()
+    lib_path = BOUNDS_LIB_PATH if bounds else LIB_PATH
+    obj_dir = CSRC / "build_bounds" if bounds else OBJ_DIR
     if nvcc is None:
-        if LIB_PATH.exists():
-            return LIB_PATH
-        raise RuntimeError("nvcc not found and no prebuilt libhibana_b200.so")
-    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+        if lib_path.exists():
+            return lib_path
+        raise RuntimeError(f"nvcc not found and no prebuilt {lib_path.name}")
+    obj_dir.mkdir(parents=True, exist_ok=True)
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     extra = ["-Xptxas", "-v"] if ptxas_info else []
+    if bounds:
+        extra += ["-DHB_BOUNDS", "-rdc=true"]      # one device-side record shared by every translation unit
     srcs = _sources()
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as pool:
-        results = list(pool.map(lambda s: _compile(s, nvcc, verbose or ptxas_info, extra), srcs))
+        results = list(pool.map(lambda s: _compile(s, nvcc, verbose or ptxas_info, extra, obj_dir), srcs))
     objs = [o for o, _ in results]
     if verbose or ptxas_info:
         for _, log in results:
             if log:
                 print(log, file=sys.stderr)
     newest_obj = max(o.stat().st_mtime for o in objs)
-    if not LIB_PATH.exists() or LIB_PATH.stat().st_mtime < newest_obj:
-        tmp = LIB_PATH.with_suffix(".so.tmp")
+    if not lib_path.exists() or lib_path.stat().st_mtime < newest_obj:
+        tmp = lib_path.with_suffix(".so.tmp")
         cmd = [nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a",
-               "-Xcompiler", "-fPIC", "-lpthread"]
+               "-Xcompiler", "-fPIC", "-lpthread", *(["-rdc=true"] if bounds else [])]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
-        os.replace(tmp, LIB_PATH)
-    return LIB_PATH
+        os.replace(tmp, lib_path)
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build(verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    path = build(verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv, bounds="--bounds" in sys.argv)
     print(path)

@@ -47,6 +47,10 @@ class KvPool:
             for i in range(layers):
                 self.k[i].sf = self.sf[i, 0].transpose(0, 1)
                 self.v[i].sf = self.sf[i, 1].transpose(0, 1)
+        if self.device.type == "cuda":
+            from .. import _native as nv
+            nv.lib()
+            nv.set_bound(nv.BOUND_KV_SLOTS, slots + 1)          # checked-index build: what a slot id may be
         self._free = list(range(slots, 0, -1))     # pop() hands out ascending ids (contiguous when fresh)
         self._owned = bytearray(slots + 1)
         self._shuffled = False                     # frees since the last sort

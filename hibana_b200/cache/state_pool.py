@@ -20,6 +20,10 @@ class StatePool:
         # int8 states carry one fp32 scale per state row (last dim is the quantised one)
         self.ssm_scale = (torch.ones(max(layers, 1), slots + 1, *state_shape[:-1], dtype=torch.float32, device=device)
                           if state_dtype == torch.int8 else None)
+        if self.device.type == "cuda":
+            from .. import _native as nv
+            nv.lib()
+            nv.set_bound(nv.BOUND_STATE_SLOTS, slots + 1)       # checked-index build: what a state slot may be
         self._free = list(range(slots, 0, -1))
         self._owned = bytearray(slots + 1)
 

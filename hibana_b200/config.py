@@ -88,6 +88,7 @@ class EngineConfig:
     trace_dir: str = ""
     trace_cap_gb: float = 32.0
     debug_sync: bool = False
+    bounds: bool = False                   # load the checked-index build of the native library (debugging; slower)
     ssd_trace: bool = False
     # api
     host: str = "127.0.0.1"

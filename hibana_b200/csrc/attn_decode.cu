@@ -191,7 +191,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constan
   // that the index load's latency is not on the issue path.
   auto fetch_slot = [&](int it) -> int {
     const int base = k0 + (warp + it * DEC_WARPS) * KT;
-    return (warp + it * DEC_WARPS < ntiles && lane < KT && base + lane < k1) ? ldg_keep(idx_row + base + lane) : -1;
+    int slot = (warp + it * DEC_WARPS < ntiles && lane < KT && base + lane < k1) ? ldg_keep(idx_row + base + lane) : -1;
+    if (slot >= 0 && !index_ok(slot, kBoundKvSlots, kKerAttnDecode)) slot = 0;   // reported; the dummy slot is read
+    return slot;
   };
   auto issue = [&](int it, int my_slot) {
     const int tile = warp + it * DEC_WARPS;

@@ -154,6 +154,9 @@ int hb_sample(const void* logits, long long ld, int rows, int vocab, int is_f32,
 int hb_argmax2(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* bitmask, int mask_words,
                int nch, void* scratch_v, void* scratch_i, const void* temperature, void* out, void* out_val,
                void* stream);
+int hb_bounds_enabled();
+int hb_bounds_set(int which, long long value);
+int hb_bounds_read(long long* out);
 int hb_lattice_walk(const void* cand, const void* scores, const void* temperature, const void* uniforms, int batch,
                     int k, int width, void* tokens, void* chosen, void* probs, void* estimate, void* stream);
 int hb_spec_targets(const void* logits, long long ld, int batch, int k, int vocab, int is_f32, const void* drafts,

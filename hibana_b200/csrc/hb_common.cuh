@@ -52,6 +52,38 @@ __device__ __forceinline__ void set_status(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
+// ---------------------------------------------------------------- checked indices (the -DHB_BOUNDS build flavour)
+// Kernels that index a pool with a number they were handed (a KV slot from the block table, a recurrent-state slot,
+// a token id) pass it through `index_ok`. In the normal build that is `true` and compiles away. In the bounds
+// flavour the limits come from a device-side table the host fills (`hb_bounds_set`); an index outside its limit
+// is recorded once (kernel, index, limit) and the caller skips the access, so a bad index shows up as a report
+// the host reads with `hb_bounds_read`, never as a fault.
+enum BoundsWhich : int { kBoundKvSlots = 0, kBoundStateSlots = 1, kBoundVocab = 2, kBoundRows = 3, kBoundKinds = 4 };
+enum BoundsKernel : int {
+  kKerRopeKvWrite = 1, kKerKvCopy = 2, kKerConvState = 3, kKerMambaScan = 4, kKerGdnScan = 5, kKerAttnDecode = 6,
+  kKerAttnGeneral = 7, kKerEmbedding = 8,
+};
+#ifdef HB_BOUNDS
+struct BoundsState {
+  long long limit[kBoundKinds];
+  long long index, bound;
+  int hits, kernel;
+};
+extern __device__ BoundsState g_bounds;
+__device__ __forceinline__ bool index_ok(long long idx, int which, int kernel) {
+  const long long lim = g_bounds.limit[which];
+  if (lim <= 0 || (idx >= 0 && idx < lim)) return true;   // limit never set: unchecked
+  if (atomicAdd(&g_bounds.hits, 1) == 0) {
+    g_bounds.kernel = kernel;
+    g_bounds.index = idx;
+    g_bounds.bound = lim;
+  }
+  return false;
+}
+#else
+__device__ __forceinline__ constexpr bool index_ok(long long, int, int) { return true; }
+#endif
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

@@ -18,7 +18,7 @@ __global__ void kv_copy_kernel(uint8_t* __restrict__ pool, uint8_t* __restrict__
                                const int* __restrict__ slots, long long plane_bytes, long long head_bytes,
                                int row_bytes, int kv_heads, long long token_bytes, int to_pool) {
   const int slot = slots[blockIdx.x];
-  if (slot < 0) return;
+  if (slot < 0 || !index_ok(slot, kBoundKvSlots, kKerKvCopy)) return;
   uint8_t* pl = payload + static_cast<long long>(blockIdx.x) * token_bytes +
                 static_cast<long long>(blockIdx.y) * kv_heads * row_bytes;
   uint8_t* pp = pool + static_cast<long long>(blockIdx.y) * plane_bytes + static_cast<long long>(slot) * row_bytes;

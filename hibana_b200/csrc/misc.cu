@@ -128,7 +128,8 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, long
   const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int nw = gridDim.y * (blockDim.x >> 5);
   const float pos = static_cast<float>(positions[t]);
-  const int slot = slots ? slots[t] : -1;
+  int slot = slots ? slots[t] : -1;
+  if (slot >= 0 && !index_ok(slot, kBoundKvSlots, kKerRopeKvWrite)) slot = -1;   // reported; nothing is written
   const int half = rot >> 1;
   // With q_gate the q block holds [q | gate] per head (2 * D per head); the gate half is left untouched.
   const int q_head_stride = q_gate ? 2 * d : d;
@@ -235,7 +236,7 @@ __global__ void embedding_kernel(const long long* __restrict__ ids, const __nv_b
                                  __nv_bfloat16* __restrict__ out, int h, long long vocab) {
   const int t = blockIdx.x;
   long long id = ids[t];
-  if (id < 0 || id >= vocab) id = 0;
+  if (id < 0 || id >= vocab || !index_ok(id, kBoundVocab, kKerEmbedding)) id = 0;
   const uint4* src = reinterpret_cast<const uint4*>(table + id * h);
   uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(t) * h);
   for (int i = threadIdx.x; i < (h >> 3); i += blockDim.x) dst[i] = src[i];

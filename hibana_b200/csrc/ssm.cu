@@ -34,6 +34,9 @@ __global__ void conv1d_kernel(const __nv_bfloat16* __restrict__ x, long long ldx
   const int b = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= channels) return;
+  if (!index_ok(slot_in[b], kBoundStateSlots, kKerConvState) ||
+      (slot_out != nullptr && !index_ok(slot_out[b], kBoundStateSlots, kKerConvState)))
+    return;   // reported; the sequence is skipped
   const int r0 = q_indptr ? q_indptr[b] : b;
   const int r1 = q_indptr ? q_indptr[b + 1] : b + 1;
   float win[W - 1];
@@ -76,6 +79,9 @@ __global__ void conv1d_tiled_kernel(const __nv_bfloat16* __restrict__ x, long lo
   const int b = blockIdx.z;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= channels) return;
+  if (!index_ok(slot_in[b], kBoundStateSlots, kKerConvState) ||
+      (slot_out != nullptr && !index_ok(slot_out[b], kBoundStateSlots, kKerConvState)))
+    return;   // reported; the sequence is skipped
   const int r0 = q_indptr ? q_indptr[b] : b;
   const int r1 = q_indptr ? q_indptr[b + 1] : b + 1;
   const int t0 = r0 + blockIdx.y * CONV_TT;
@@ -118,6 +124,9 @@ __global__ void conv1d_state_kernel(const __nv_bfloat16* __restrict__ x, long lo
   const int b = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= channels) return;
+  if (!index_ok(slot_in[b], kBoundStateSlots, kKerConvState) ||
+      (slot_out != nullptr && !index_ok(slot_out[b], kBoundStateSlots, kKerConvState)))
+    return;   // reported; the sequence is skipped
   const int r0 = q_indptr ? q_indptr[b] : b;
   const int r1 = q_indptr ? q_indptr[b + 1] : b + 1;
   const bool init = has_init == nullptr || has_init[b] != 0;
@@ -173,6 +182,9 @@ __global__ void __launch_bounds__(THREADS) mamba2_scan_kernel(const MambaParams 
   static_assert(THREADS % P == 0 && N % CG == 0 && CG <= 32 && (CG & (CG - 1)) == 0, "bad Mamba tiling");
   __shared__ float bs[N], cs[N];
   const int b = blockIdx.y, h = blockIdx.x;
+  if (!index_ok(p.slot_in[b], kBoundStateSlots, kKerMambaScan) ||
+      (p.slot_out != nullptr && !index_ok(p.slot_out[b], kBoundStateSlots, kKerMambaScan)))
+    return;   // reported; uniform over the CTA, before any barrier
   const int g = h / (p.heads / p.groups);
   const int row = threadIdx.x / CG, cg = threadIdx.x % CG;
   const int r0 = p.q_indptr ? p.q_indptr[b] : b;
@@ -285,6 +297,9 @@ __global__ void __launch_bounds__(V) gdn_scan_kernel(const GdnParams p) {
   __shared__ float qs[K], ks[K];
   __shared__ float red[2][V / 32];
   const int b = blockIdx.y, hv = blockIdx.x;
+  if (!index_ok(p.slot_in[b], kBoundStateSlots, kKerGdnScan) ||
+      (p.slot_out != nullptr && !index_ok(p.slot_out[b], kBoundStateSlots, kKerGdnScan)))
+    return;   // reported; uniform over the CTA, before any barrier
   const int hk = hv / (p.v_heads / p.k_heads);
   const int v = threadIdx.x;
   const int r0 = p.q_indptr ? p.q_indptr[b] : b;

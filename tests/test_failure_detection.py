@@ -202,3 +202,48 @@ def test_runner_raises_when_the_status_word_is_set():
         ex.generate_batch([[4, 5, 6]], SamplingParams(max_tokens=2))
     assert nv.read_status(torch.device("cuda:0")) == 0
     assert len(ex.generate_batch([[7, 8, 9]], SamplingParams(max_tokens=2))[0].output_ids) == 2
+
+
+@pytest.mark.gpu
+def test_checked_index_flavour_reports_a_bad_slot_and_skips_the_access(tmp_path):
+    """The -DHB_BOUNDS build of the native library: a KV slot beyond the pool handed to the RoPE + KV-write kernel is
+    recorded (kernel, index, limit) and nothing is written; valid calls report nothing and match the normal build.
+    Runs in a child process because a process loads one flavour of the library."""
+    import subprocess
+    import sys
+    script = tmp_path / "bounds_child.py"
+    script.write_text('''
+import json, os, sys, torch
+sys.path.insert(0, os.environ["HB_ROOT"])
+from hibana_b200 import config, _native as nv
+config.install(config.EngineConfig(bounds=True))
+from hibana_b200.cache.kv_pool import KvPool
+from hibana_b200.ops import basic
+assert nv.lib() is not None and nv.bounds_enabled(), "the checked flavour must be the one loaded before a bad index is tried"
+dev = torch.device("cuda")
+pool = KvPool(1, 64, 2, 128, torch.bfloat16, dev)
+g = torch.Generator().manual_seed(0)
+qkv = torch.randn(4, (4 + 2 * 2) * 128, generator=g).bfloat16().to(dev)
+pos = torch.arange(4, dtype=torch.int32, device=dev)
+inv = basic.rope_inv_freq(128, 1e6).to(dev)
+good = torch.tensor([1, 2, 3, 4], dtype=torch.int32, device=dev)
+basic.rope_kv_write(qkv, pos, good, inv, pool.k[0], pool.v[0], 4, 2, 128)
+torch.cuda.synchronize()
+clean = nv.read_bounds()
+before = pool.storage.clone()
+bad = torch.tensor([5, 70, 6, 7], dtype=torch.int32, device=dev)          # 70 > 64 slots + the dummy row
+basic.rope_kv_write(qkv, pos, bad, inv, pool.k[0], pool.v[0], 4, 2, 128)
+torch.cuda.synchronize()
+rep = nv.read_bounds()
+changed = (pool.storage != before).any(-1).any(0).any(0).any(0).nonzero().flatten().tolist()
+print("RESULT " + json.dumps({"clean": clean, "report": rep, "changed_slots": changed, "again": nv.read_bounds(),
+                              "status": nv.read_status(dev)}))
+''')
+    env = dict(os.environ, HB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    proc = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, env=env, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    import json
+    res = json.loads([l for l in proc.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    assert res["clean"] is None and res["again"] is None and res["status"] == 0
+    assert res["report"] == {"hits": res["report"]["hits"], "kernel": "rope_kv_write", "index": 70, "limit": 65}
+    assert res["changed_slots"] == [5, 6, 7]                 # the in-range rows were written, the bad one skipped
