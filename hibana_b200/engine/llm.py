@@ -95,6 +95,13 @@ def plan_memory(cfg: EngineConfig, target: Target, device: torch.device, *, max_
                                   max(target.q_heads, 1) * target.head_dim, cfg.max_batch, target.vocab // tp)
     # block table (int32 per position and row) + split-KV partials of the widest bucket
     workspace = (cfg.max_batch + 1) * ctx * 4 + comm_bytes + cfg.max_batch * max(target.q_heads, 1) * target.head_dim * 4 * 16
+    if cfg.spec != "off":      # what the speculator allocates after the pools exist is set aside now
+        from ..cache.spec_budget import SpecConfig, budget
+        spec_fixed, spec_slot = budget(SpecConfig(cfg.spec, cfg.spec_depth, cfg.spec_state), cfg.max_batch, target,
+                                       buckets=len(cfg.buckets))
+        workspace += spec_fixed
+        if kv_layers is not None:      # the caller counted the model's KV layers without the drafter's
+            kv_tok += spec_slot
     led = ledger.Ledger(free_bytes, fraction=cfg.gpu_memory_fraction)
     notes = []
     while True:

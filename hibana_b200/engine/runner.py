@@ -14,6 +14,7 @@ import numpy as np
 import torch
 
 from .. import _native as nv
+from .. import config as cfgmod
 from ..ops import attention, sampling
 from .context import DECODE, PREFILL, VERIFY, ForwardContext
 
@@ -332,7 +333,9 @@ class ModelRunner:
         t = self.model.target
         max_rows = max(counts)
         splits = 1
-        if t.attn_layers and b * t.kv_heads * max(1, max_rows // max(1, 32 // max(1, t.q_heads // max(t.kv_heads, 1)))) < 148:
+        if cfgmod.current().stable_numerics:
+            pass
+        elif t.attn_layers and b * t.kv_heads * max(1, max_rows // max(1, 32 // max(1, t.q_heads // max(t.kv_heads, 1)))) < 148:
             splits = attention.choose_splits(b, t.kv_heads, int(ctx_len.max()))
         ctx = ForwardContext(mode, positions=pos_d, slots=slots_d, kv_indices=self.block_table, ctx_len=ctx_d,
                              q_indptr=indptr_d, seq_rows=seq_rows_d, max_rows=max_rows, batch=b, sample_rows=last,

@@ -41,6 +41,10 @@ DECODE_CTAS_PER_SM = 2      # csrc/attn_decode.cu: 64-thread CTAs with ~100 KB o
 def choose_splits(batch: int, hkv: int, max_ctx: int, row_chunks: int = 1, slots: int = 0) -> int:
     """KV splits that fill whole waves of the resident CTA slots (the decode kernel streams from every resident
     CTA at once, so a last wave that is a third full costs a whole wave); a split never gets fewer than 256 keys."""
+    if cfgmod.current().stable_numerics:
+        # row-count invariant: one pass over the keys in fixed tiles from position 0, so a token's attention sums
+        # in the same order whether it is the only new row of its sequence or one of several verified rows
+        return 1
     slots = slots or NUM_SMS * max(1, cfgmod.current().attn_ctas_per_sm)
     ctas = max(1, batch * hkv * row_chunks)
     cap = int(max(1, min(max_ctx // 256, 64)))

@@ -50,6 +50,11 @@ def _plan(m: int, n: int, k_tiles: int, max_ws_bytes: int) -> tuple[bool, int, i
         tiles = (n + 127) // 128
         splits = 1
         slots = NUM_SMS * (2 if bn <= 64 else 1)     # token tiles <= 64 run two CTAs per SM (csrc/gemm.cu Cfg)
+        if cfgmod.current().stable_numerics:
+            # the number of K splits (hence the order every output element is summed in) must not depend on how
+            # many rows share the forward: a token then gets the same bits from a decode step, a verify round of
+            # any depth and any batch (reference: hibana/kernels/stable.py, HIBANA_STABLE_NUMERICS)
+            slots = NUM_SMS * 2
         if tiles < slots:
             # Fill the resident CTA slots without spilling into a second, mostly empty wave; every split keeps at
             # least two K tiles.

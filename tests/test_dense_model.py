@@ -89,3 +89,50 @@ def test_dense_model_runs_on_an_nvfp4_kv_cache_cpu():
     f4 = ex.generate_batch(prompts, sp)
     assert ex.kv.bytes_per_token == len(t.layers) * 2 * t.kv_heads * (t.head_dim // 2 + t.head_dim // 16)
     assert sum(a.output_ids[0] == b.output_ids[0] for a, b in zip(bf, f4)) >= 2
+
+
+@pytest.mark.gpu
+def test_stable_numerics_makes_verify_rows_bitwise_equal_to_decode_steps():
+    """With `stable_numerics` a token's logits do not depend on how many rows share its forward: a 4-row verify
+    forward gives, row by row, exactly the bits of four single-token decode steps (split-K and KV-split choices are
+    then functions of the layer shape alone)."""
+    import torch
+    from hibana_b200 import config as cfgmod
+    from hibana_b200.engine.context import VERIFY
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import Request, SamplingParams
+    from hibana_b200.models.dense import DenseModel
+    from hibana_b200.target import dense_tiny
+    t = dense_tiny()
+    model = DenseModel(t, "cuda:0", seed=0)
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, t.vocab, (300,), generator=g).tolist()
+    new = torch.randint(0, t.vocab, (4,), generator=g).tolist()
+
+    def rows_of(stable):
+        with cfgmod.using(stable_numerics=stable):
+            out = {}
+            for mode in ("steps", "verify"):
+                ex = Executor(model, max_batch=2, max_ctx=512, use_graphs=False)
+                r = Request(prompt_ids=list(prompt), params=SamplingParams(max_tokens=8, ignore_eos=True))
+                ex.admit(r)
+                ex.prefill_batch([(r, len(prompt))])
+                n = len(prompt)
+                ex.state.reserve([r], 5)
+                ex.runner.set_table(r.table_row, n, r.kv_slots[n:n + 5])
+                if mode == "verify":
+                    lg, _ = ex.runner.forward_rows([r.table_row], [new], [n], [r.kv_slots[n:n + 4]], mode=VERIFY,
+                                                   want="logits_device")
+                    out[mode] = lg.float().clone()
+                else:
+                    rows = []
+                    for j, tok in enumerate(new):
+                        lg, _ = ex.runner.forward_rows([r.table_row], [[tok]], [n + j], [r.kv_slots[n + j:n + j + 1]],
+                                                       mode=VERIFY, want="logits_device")
+                        rows.append(lg.float().clone())
+                    out[mode] = torch.cat(rows, 0)
+            return out
+    stable = rows_of(True)
+    assert torch.equal(stable["steps"], stable["verify"])
+    loose = rows_of(False)          # the default plans may differ by rounding; both must stay close to each other
+    assert (loose["steps"] - loose["verify"]).abs().max() <= 0.05 * loose["steps"].abs().max()
