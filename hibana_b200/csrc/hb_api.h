@@ -65,8 +65,9 @@ void hb_rows_close(void* g);
 // Hyper-connection steps (csrc/hyper.cu).
 int hb_hc_norm(const void* hyper, const void* w, void* normed, int tokens, int hc, int h, float eps, void* stream);
 int hb_hc_gate_mean(const void* gate, const void* normed, void* mixed, int tokens, int hc, int h, void* stream);
-int hb_hc_inject(const void* hyper, const void* block_out, const void* inject_logits, void* out, int tokens, int hc,
-                 int h, void* stream);
+int hb_hc_inject(const void* hyper, const void* block_out, const void* inject_logits, long long ld_logits, void* out,
+                 int tokens, int hc, int h, void* stream);
+int hb_hc_low(const void* x, long long ldx, void* low, int rows, int rank, void* stream);
 // Sparse-attention indexer (csrc/qsa.cu).
 int hb_qsa_compress(const void* raw_k, void* ckey, const void* kv_indices, long long ld_idx, const void* seq_rows,
                     const void* grp_indptr, const void* grp_first, int batch, int total_groups, int ratio,
@@ -154,6 +155,13 @@ int hb_sample(const void* logits, long long ld, int rows, int vocab, int is_f32,
 int hb_argmax2(const void* logits, long long ld, int rows, int vocab, int is_f32, const void* bitmask, int mask_words,
                int nch, void* scratch_v, void* scratch_i, const void* temperature, void* out, void* out_val,
                void* stream);
+int hb_quant_nvfp4_pairs(const void* x, long long ldx, const void* pos, int pairs, int topk, int k, int ka,
+                         const void* gscale, void* q, void* sf, void* stream);
+int hb_gated_rmsnorm_quant(const void* x, const void* z, const void* w, int rows, int h, int gs, long long ldx,
+                           long long ldz, float eps, int norm_first, int sigmoid_gate, int gemma, void* q, void* sf,
+                           const void* gscale, int ka, void* stream);
+int hb_gdn_gates(const void* ba, long long ld, const void* a_log, const void* dt_bias, int rows, int heads,
+                 void* beta, void* g, void* stream);
 int hb_bounds_enabled();
 int hb_bounds_set(int which, long long value);
 int hb_bounds_read(long long* out);

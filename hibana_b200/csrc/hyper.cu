@@ -85,14 +85,14 @@ __global__ void __launch_bounds__(256) hc_gate_mean_kernel(const __nv_bfloat16* 
 
 __global__ void __launch_bounds__(256) hc_inject_kernel(const __nv_bfloat16* __restrict__ hyper,
                                                         const __nv_bfloat16* __restrict__ block_out,
-                                                        const float* __restrict__ inject_logits,
+                                                        const float* __restrict__ inject_logits, long long ld_logits,
                                                         __nv_bfloat16* __restrict__ out, int hc, int h) {
   const long long base = static_cast<long long>(blockIdx.x) * hc * h;
   for (int c = threadIdx.x; c < (h >> 3); c += blockDim.x) {
     float b[8];
     unpack(reinterpret_cast<const uint4*>(block_out + static_cast<long long>(blockIdx.x) * h)[c], b);
     for (int s = 0; s < hc; ++s) {
-      const float inj = 2.f * sigmoidf(inject_logits[static_cast<long long>(blockIdx.x) * hc + s]);
+      const float inj = 2.f * sigmoidf(inject_logits[static_cast<long long>(blockIdx.x) * ld_logits + s]);
       float x[8];
       unpack(reinterpret_cast<const uint4*>(hyper + base + static_cast<long long>(s) * h)[c], x);
 #pragma unroll
@@ -100,6 +100,17 @@ __global__ void __launch_bounds__(256) hc_inject_kernel(const __nv_bfloat16* __r
       reinterpret_cast<uint4*>(out + base + static_cast<long long>(s) * h)[c] = pack(x);
     }
   }
+}
+
+// low[t][j] = silu(bf16(x[t][j])) for the first `rank` columns of the fp32 rows x (pitch ldx): the activation
+// between the two low-rank gate projections, applied to the bf16-rounded value as a bf16 GEMM output would carry it.
+__global__ void hc_low_kernel(const float* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ low, int rows,
+                              int rank) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * rank) return;
+  const int r = i / rank, j = i - r * rank;
+  const float v = __bfloat162float(__float2bfloat16(x[r * ldx + j]));
+  low[i] = __float2bfloat16(v / (1.f + __expf(-v)));
 }
 
 }  // namespace
@@ -133,13 +144,20 @@ int hb_hc_gate_mean(const void* gate, const void* normed, void* mixed, int token
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 
-int hb_hc_inject(const void* hyper, const void* block_out, const void* inject_logits, void* out, int tokens, int hc,
-                 int h, void* stream) {
+int hb_hc_inject(const void* hyper, const void* block_out, const void* inject_logits, long long ld_logits, void* out,
+                 int tokens, int hc, int h, void* stream) {
   if (tokens <= 0) return 0;
   if (h % 8 != 0) return 1;
   hc_inject_kernel<<<tokens, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(hyper), static_cast<const __nv_bfloat16*>(block_out),
-      static_cast<const float*>(inject_logits), static_cast<__nv_bfloat16*>(out), hc, h);
+      static_cast<const float*>(inject_logits), ld_logits, static_cast<__nv_bfloat16*>(out), hc, h);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_hc_low(const void* x, long long ldx, void* low, int rows, int rank, void* stream) {
+  if (rows <= 0) return 0;
+  hc_low_kernel<<<(rows * rank + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(x), ldx, static_cast<__nv_bfloat16*>(low), rows, rank);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

@@ -6,6 +6,7 @@
 // hibana/cache/kv_pool.py:120-132, hibana/kernels/flashnext_fused.py:624-660, hibana/kernels/mamba2.py:797.
 #include "hb_api.h"
 #include "hb_common.cuh"
+#include "rownorm.cuh"
 
 namespace hb {
 namespace {
@@ -78,8 +79,99 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ 
 __global__ void gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ z,
                                      const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int rows,
                                      int h, int gs, long long ldx, long long ldz, float eps, int norm_first,
-                                     int sigmoid_gate, int gemma) {
+                                     int sigmoid_gate, int gemma, uint8_t* __restrict__ q_out,
+                                     uint8_t* __restrict__ q_sf, const float* __restrict__ q_gscale, int q_ka) {
   const int groups = h / gs;
+  const long long wid0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  // Fast path: the group fits in registers as 16-byte chunks (up to 4 per lane = 1024 features): one read of x and
+  // z, one exp per element, 16-byte stores.
+  if (gs % 8 == 0 && gs <= 1024 && ldx % 8 == 0 && (z == nullptr || ldz % 8 == 0) && h % 8 == 0) {
+    if (wid0 >= static_cast<long long>(rows) * groups) return;
+    const int lane_ = threadIdx.x & 31;
+    const int row_ = static_cast<int>(wid0 / groups), g_ = static_cast<int>(wid0 % groups);
+    const uint4* xr4 = reinterpret_cast<const uint4*>(x + row_ * ldx + g_ * gs);
+    const uint4* zr4 = z ? reinterpret_cast<const uint4*>(z + row_ * ldz + g_ * gs) : nullptr;
+    const uint4* wr4 = reinterpret_cast<const uint4*>(w + g_ * gs);
+    const int nchunk = gs >> 3;
+    float v[4][8], gt[4][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int ci = lane_ + c * 32;
+      if (ci < nchunk) {
+        const uint4 xa = xr4[ci];
+        const uint32_t xw[4] = {xa.x, xa.y, xa.z, xa.w};
+        uint32_t zw[4] = {0, 0, 0, 0};
+        if (zr4) {
+          const uint4 za = zr4[ci];
+          zw[0] = za.x; zw[1] = za.y; zw[2] = za.z; zw[3] = za.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xv = (e & 1) ? bf16_hi(xw[e >> 1]) : bf16_lo(xw[e >> 1]);
+          float gate = 1.f;
+          if (zr4) {
+            const float zz = (e & 1) ? bf16_hi(zw[e >> 1]) : bf16_lo(zw[e >> 1]);
+            gate = sigmoid_gate ? 1.f / (1.f + __expf(-zz)) : zz / (1.f + __expf(-zz));
+          }
+          gt[c][e] = gate;
+          v[c][e] = norm_first ? xv : xv * gate;
+          ss += v[c][e] * v[c][e];
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(ss) / gs + eps);
+    uint4* yr4 = reinterpret_cast<uint4*>(y + static_cast<long long>(row_) * h + g_ * gs);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int ci = lane_ + c * 32;
+      const unsigned act = __ballot_sync(0xffffffffu, ci < nchunk);     // lanes that share the shuffle below
+      if (ci < nchunk) {
+        const uint4 wa = wr4[ci];
+        const uint32_t ww4[4] = {wa.x, wa.y, wa.z, wa.w};
+        uint32_t o4[4];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          float o2[2];
+#pragma unroll
+          for (int d = 0; d < 2; ++d) {
+            const float ww = d ? bf16_hi(ww4[e >> 1]) : bf16_lo(ww4[e >> 1]);
+            const float wv = gemma ? 1.f + ww : ww;
+            o2[d] = norm_first ? v[c][e + d] * rstd * wv * gt[c][e + d] : v[c][e + d] * rstd * wv;
+          }
+          const __nv_bfloat162 pk = __floats2bfloat162_rn(o2[0], o2[1]);
+          o4[e >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+        }
+        if (q_out == nullptr) {
+          yr4[ci] = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+          continue;
+        }
+        // NVFP4 output for the projection that follows: chunks ci and ci ^ 1 (neighbouring lanes) are one
+        // 16-element scale group; values are the bf16-rounded outputs, as a separate quantiser would see them
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          f[2 * e] = bf16_lo(o4[e]);
+          f[2 * e + 1] = bf16_hi(o4[e]);
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+        amax = fmaxf(amax, __shfl_xor_sync(act, amax, 1));
+        const float inv_gs = 1.f / *q_gscale;
+        const uint32_t sfb = float_to_e4m3(amax * (1.f / 6.f) * inv_gs);
+        const float sfv = e4m3_to_float(sfb);
+        const float inv = sfv > 0.f ? 1.f / (sfv * (1.f / inv_gs)) : 0.f;
+        uint32_t wq = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wq |= e2m1x2(f[2 * e] * inv, f[2 * e + 1] * inv) << (8 * e);
+        const int col8 = (g_ * gs >> 3) + ci;                  // 8-element chunk index inside the row
+        reinterpret_cast<uint32_t*>(q_out + static_cast<size_t>(row_) * (h >> 1))[col8] = wq;
+        if ((ci & 1) == 0) q_sf[row_sf_off(row_, col8 >> 1, q_ka)] = static_cast<uint8_t>(sfb);
+      }
+    }
+    return;
+  }
   const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= static_cast<long long>(rows) * groups) return;
@@ -232,6 +324,20 @@ __global__ void act_mul_kernel(const __nv_bfloat16* __restrict__ x, const __nv_b
   out[r * inter + j] = __float2bfloat16(o);
 }
 
+// beta = sigmoid(b), g = -exp(a_log) * softplus(a + dt_bias) from the bf16 b | a projection [T, 2 * heads].
+__global__ void gdn_gates_kernel(const __nv_bfloat16* __restrict__ ba, long long ld, const float* __restrict__ a_log,
+                                 const float* __restrict__ dt_bias, int rows, int heads, float* __restrict__ beta,
+                                 float* __restrict__ g) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * heads) return;
+  const int r = i / heads, hd = i - r * heads;
+  const float b = __bfloat162float(ba[r * ld + hd]);
+  const float a = __bfloat162float(ba[r * ld + heads + hd]) + dt_bias[hd];
+  beta[i] = 1.f / (1.f + __expf(-b));
+  const float sp = a > 20.f ? a : log1pf(__expf(a));
+  g[i] = -__expf(a_log[hd]) * sp;
+}
+
 __global__ void embedding_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                  __nv_bfloat16* __restrict__ out, int h, long long vocab) {
   const int t = blockIdx.x;
@@ -282,7 +388,31 @@ int hb_gated_rmsnorm(const void* x, const void* z, const void* w, void* y, int r
   const long long warps = static_cast<long long>(rows) * (h / gs);
   const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
   gated_rmsnorm_kernel<<<blocks, 256, 0, ST(stream)>>>(BF(x), BF(z), BF(w), BFM(y), rows, h, gs, ldx, ldz, eps,
-                                                       norm_first, sigmoid_gate, gemma);
+                                                       norm_first, sigmoid_gate, gemma, nullptr, nullptr, nullptr, 0);
+  return OK();
+}
+
+int hb_gdn_gates(const void* ba, long long ld, const void* a_log, const void* dt_bias, int rows, int heads,
+                 void* beta, void* g, void* stream) {
+  if (rows <= 0) return 0;
+  gdn_gates_kernel<<<(rows * heads + 255) / 256, 256, 0, ST(stream)>>>(
+      BF(ba), ld, static_cast<const float*>(a_log), static_cast<const float*>(dt_bias), rows, heads,
+      static_cast<float*>(beta), static_cast<float*>(g));
+  return OK();
+}
+
+// Same norm, written as NVFP4 rows (packed codes [rows, h / 2] + swizzled block scales) for the projection that
+// follows. Needs the register-resident path: group size a multiple of 16 and at most 1024, 16-byte aligned rows.
+int hb_gated_rmsnorm_quant(const void* x, const void* z, const void* w, int rows, int h, int gs, long long ldx,
+                           long long ldz, float eps, int norm_first, int sigmoid_gate, int gemma, void* q, void* sf,
+                           const void* gscale, int ka, void* stream) {
+  if (h % gs != 0 || gs % 16 != 0 || gs > 1024 || ldx % 8 != 0 || (z != nullptr && ldz % 8 != 0) || ka * 64 != h)
+    return 1;   // (h a multiple of 64: no scale groups pad the last K tile)
+  const long long warps = static_cast<long long>(rows) * (h / gs);
+  const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
+  gated_rmsnorm_kernel<<<blocks, 256, 0, ST(stream)>>>(BF(x), BF(z), BF(w), nullptr, rows, h, gs, ldx, ldz, eps,
+                                                       norm_first, sigmoid_gate, gemma, static_cast<uint8_t*>(q),
+                                                       static_cast<uint8_t*>(sf), static_cast<const float*>(gscale), ka);
   return OK();
 }
 

@@ -18,15 +18,24 @@ namespace {
 
 constexpr int MAX_TOPK = 32;
 
-// One warp per token; E <= 1024.
+// One warp per token; E <= 32 * PER. Selection order is (value desc, index asc): every candidate is one 64-bit key
+// (order-preserving bits of the value above the complemented index), a lane keeps the best of its PER keys, and
+// each of the top-k rounds is two warp-wide `redux.max` instructions plus a rescan by the one lane that owned the
+// winner, instead of a shuffle tree over (value, index) pairs.
+__device__ __forceinline__ unsigned route_key(float v) {
+  const unsigned b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+template <int PER>
 __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ sel_bias,
                                  int tokens, int experts, int topk, int sigmoid, int renorm, float scale,
                                  int* __restrict__ ids, float* __restrict__ weights) {
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= tokens) return;
-  constexpr int PER = 32;  // values per lane (E <= 1024)
-  float score[PER], sel[PER];
+  float score[PER];
+  unsigned key[PER];     // selection key of entry i (expert lane + 32 i); 0 = taken or absent
   const float* lr = logits + t * ld;
   float mx = -INFINITY;
 #pragma unroll
@@ -41,10 +50,10 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
       const int e = lane + i * 32;
       if (e < experts) {
         score[i] = 1.f / (1.f + __expf(-score[i]));
-        sel[i] = score[i] + (sel_bias ? sel_bias[e] : 0.f);
+        key[i] = route_key(score[i] + (sel_bias ? sel_bias[e] : 0.f));
       } else {
         score[i] = 0.f;
-        sel[i] = -INFINITY;
+        key[i] = 0u;
       }
     }
   } else {
@@ -62,42 +71,40 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
     for (int i = 0; i < PER; ++i) {
       const int e = lane + i * 32;
       score[i] *= inv;
-      sel[i] = e < experts ? score[i] : -INFINITY;
+      key[i] = e < experts ? route_key(score[i]) : 0u;
     }
   }
+  // lane-local best: highest key, lowest slot on ties (slots of a lane ascend with the expert index)
+  // (every index below is a compile-time constant after unrolling: the arrays must stay in registers)
+  unsigned bk = 0u;
+  int bs = 0;
+#define HB_ROUTE_RESCAN()                              \
+  bk = 0u;                                             \
+  bs = 0;                                              \
+  _Pragma("unroll") for (int i = PER - 1; i >= 0; --i) { \
+    const bool better = key[i] >= bk && key[i] != 0u;  \
+    bk = better ? key[i] : bk;                         \
+    bs = better ? i : bs;                              \
+  }
+  HB_ROUTE_RESCAN()
   float wsum = 0.f;
   float my_w = 0.f;
   int my_id = 0;
   for (int k = 0; k < topk; ++k) {
-    // lane-local best (lowest index wins ties), then warp argmax
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-#pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      const int e = lane + i * 32;
-      if (sel[i] > bv || (sel[i] == bv && e < bi)) {
-        bv = sel[i];
-        bi = e;
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) {
-        bv = ov;
-        bi = oi;
-      }
-    }
-    // the owner lane removes it and reports its score
+    const unsigned top = __reduce_max_sync(0xffffffffu, bk);
+    // among the lanes that hold the top key, the lowest expert index: expert = lane + 32 * slot
+    const unsigned cand = (bk == top && top != 0u) ? 0xffffffffu - static_cast<unsigned>(lane + bs * 32) : 0u;
+    const unsigned win = __reduce_max_sync(0xffffffffu, cand);
+    const int bi = top != 0u ? static_cast<int>(0xffffffffu - win) : 0;
     float sc = 0.f;
-    if ((bi & 31) == lane) {
+    if (top != 0u && (bi & 31) == lane) {
+      const int slot = bi >> 5;
 #pragma unroll
-      for (int i = 0; i < PER; ++i)
-        if (lane + i * 32 == bi) {
-          sc = score[i];
-          sel[i] = -INFINITY;
-        }
+      for (int i = 0; i < PER; ++i) {
+        sc = i == slot ? score[i] : sc;
+        key[i] = i == slot ? 0u : key[i];
+      }
+      HB_ROUTE_RESCAN()
     }
     sc = __shfl_sync(0xffffffffu, sc, bi & 31);
     wsum += sc;
@@ -111,6 +118,34 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
     ids[static_cast<long long>(t) * topk + lane] = my_id;
     weights[static_cast<long long>(t) * topk + lane] = w;
   }
+#undef HB_ROUTE_RESCAN
+}
+
+// Exclusive prefix sum over the 1024 threads of the CTA (thread i contributes v); `total` receives the sum.
+__device__ __forceinline__ int block_excl_scan_1024(int v, int* wtot, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += up;
+  }
+  __syncthreads();
+  if (lane == 31) wtot[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    const int w = wtot[lane];
+    int winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += up;
+    }
+    wtot[lane] = winc - w;
+    if (lane == 31 && total != nullptr) *total = winc;
+  }
+  __syncthreads();
+  return wtot[warp] + inc - v;
 }
 
 // Single CTA. e_lo / e_n restrict planning to the experts [e_lo, e_lo + e_n) this rank owns (expert parallelism):
@@ -130,7 +165,16 @@ moe_plan_kernel(const int* __restrict__ ids, int pairs, int topk, int experts, i
     if (e >= e_lo && e < e_lo + e_n) atomicAdd(&c[e], 1);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  __shared__ int wtot[32];
+  __shared__ int s_total;
+  const bool par = experts <= static_cast<int>(blockDim.x) && blockDim.x == 1024;   // one expert per thread
+  if (par) {
+    const int mine = static_cast<int>(threadIdx.x) < experts ? ((c[threadIdx.x] + 127) >> 7) << 7 : 0;
+    const int off = block_excl_scan_1024(mine, wtot, &s_total);
+    if (static_cast<int>(threadIdx.x) < experts) s[threadIdx.x] = off;
+    __syncthreads();
+    if (threadIdx.x == 0) *total_rows = s_total;
+  } else if (threadIdx.x == 0) {
     int acc = 0;
     for (int e = 0; e < experts; ++e) {
       s[e] = acc;
@@ -146,7 +190,13 @@ moe_plan_kernel(const int* __restrict__ ids, int pairs, int topk, int experts, i
   // Work list of the grouped GEMMs: one entry (expert * 4096 + chunk) per tile of `tile_bn` rows that has rows.
   if (tiles != nullptr) {
     int* tb = s + experts;   // scratch (reused as the running counts below)
-    if (threadIdx.x == 0) {
+    if (par) {
+      const int mine = static_cast<int>(threadIdx.x) < experts ? (c[threadIdx.x] + tile_bn - 1) / tile_bn : 0;
+      const int off = block_excl_scan_1024(mine, wtot, &s_total);
+      if (static_cast<int>(threadIdx.x) < experts) tb[threadIdx.x] = off;
+      __syncthreads();
+      if (threadIdx.x == 0) *n_tiles = s_total < tile_cap ? s_total : tile_cap;
+    } else if (threadIdx.x == 0) {
       int acc = 0;
       for (int e = 0; e < experts; ++e) {
         tb[e] = acc;
@@ -285,10 +335,14 @@ int hb_moe_route(const void* logits, long long ld, const void* sel_bias, int tok
                  int sigmoid, int renorm, float scale, void* ids, void* weights, void* stream) {
   if (tokens <= 0) return 0;
   if (experts > 1024 || topk > MAX_TOPK || topk > experts) return 1;
-  moe_route_kernel<<<(tokens + 3) / 4, 128, 0, ST(stream)>>>(static_cast<const float*>(logits), ld,
-                                                             static_cast<const float*>(sel_bias), tokens, experts,
-                                                             topk, sigmoid, renorm, scale, static_cast<int*>(ids),
-                                                             static_cast<float*>(weights));
+#define HB_ROUTE(PER)                                                                                        \
+  moe_route_kernel<PER><<<(tokens + 3) / 4, 128, 0, ST(stream)>>>(                                           \
+      static_cast<const float*>(logits), ld, static_cast<const float*>(sel_bias), tokens, experts, topk, sigmoid, \
+      renorm, scale, static_cast<int*>(ids), static_cast<float*>(weights))
+  if (experts <= 128) HB_ROUTE(4);
+  else if (experts <= 512) HB_ROUTE(16);
+  else HB_ROUTE(32);
+#undef HB_ROUTE
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

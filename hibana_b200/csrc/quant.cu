@@ -67,6 +67,36 @@ __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, long lon
   sf[row_sf_off(row, g, ka)] = static_cast<uint8_t>(sfb);
 }
 
+// MoE sorted buffers at decode sizes: one thread per ((token, expert) pair, group of 16). The pair's row in the
+// sorted buffer is pos[pair] (-1: routed elsewhere); its input row is the pair's token (topk > 0: x holds the
+// tokens) or the sorted row itself (topk == 0: x is already sorted, e.g. the experts' hidden activations). Padding
+// rows of the 128-row expert segments are not touched: the grouped GEMM computes token columns it never stores
+// from them, so their codes and scales may hold anything.
+__global__ void quant_nvfp4_pairs_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                         const int* __restrict__ pos, int pairs, int topk, int k, int ka,
+                                         const float* __restrict__ gscale, uint8_t* __restrict__ q,
+                                         uint8_t* __restrict__ sf) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const int groups_pad = ka * 4;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(pairs) * groups_pad) return;
+  const int pair = static_cast<int>(idx / groups_pad), g = static_cast<int>(idx % groups_pad);
+  const int row = pos[pair];
+  if (row < 0) return;
+  if (g * 16 >= k) {       // scale groups that pad the last K tile read as zero
+    sf[row_sf_off(row, g, ka)] = 0;
+    return;
+  }
+  const long long in_row = topk > 0 ? pair / topk : row;
+  float v[16];
+  load16(x + in_row * ldx + g * 16, v);
+  uint2 packed;
+  const uint32_t sfb = quant16(v, 1.f / *gscale, &packed);
+  *reinterpret_cast<uint2*>(q + static_cast<size_t>(row) * (k / 2) + g * 8) = packed;
+  sf[row_sf_off(row, g, ka)] = static_cast<uint8_t>(sfb);
+}
+
 // (residual add +) RMSNorm -> NVFP4 (and / or bf16). One CTA per row on the register-resident row core.
 // Writes the updated residual (bf16) when `residual` is given. gemma != 0 uses weight (1 + w).
 template <int T, int MAXC>
@@ -183,6 +213,18 @@ int hb_quant_nvfp4_rows(const void* x, long long ldx, int m, int k, int ka, cons
       static_cast<const __nv_bfloat16*>(x), ldx, m, k, ka, static_cast<const float*>(gscale),
       static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf), mode, static_cast<const int*>(src_rows),
       static_cast<const int*>(total_rows));
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_quant_nvfp4_pairs(const void* x, long long ldx, const void* pos, int pairs, int topk, int k, int ka,
+                         const void* gscale, void* q, void* sf, void* stream) {
+  if (pairs <= 0) return 0;
+  if (k % 16 != 0 || ka * 64 < k) return 1;
+  const long long n = static_cast<long long>(pairs) * ka * 4;
+  launch_dep(quant_nvfp4_pairs_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0,
+             static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x), ldx,
+             static_cast<const int*>(pos), pairs, topk, k, ka, static_cast<const float*>(gscale),
+             static_cast<uint8_t*>(q), static_cast<uint8_t*>(sf));
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

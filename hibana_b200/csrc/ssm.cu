@@ -166,7 +166,10 @@ struct MambaParams {
 };
 
 // One CTA per (sequence, head). Thread layout: P rows x (THREADS / P) column groups; each thread keeps
-// N / (THREADS / P) state columns of one row in registers for the whole sequence.
+// N / (THREADS / P) state columns of one row in registers for the whole sequence. The columns of a thread are
+// groups of four interleaved with the other threads of its row (group j of column group cg is columns
+// 4 * (j * CG + cg) ...), so that the CG threads of a row move 16 * CG contiguous bytes per instruction and every
+// sector a warp touches is used whole: a decode step is nothing but this state traffic.
 // State formats: 0 fp32; 1 fp16 (optionally stochastically rounded on store, so that rounding errors do not
 // accumulate as a bias over thousands of steps); 2 int8 with one fp32 scale per state row (absmax / 127).
 // The recurrence itself always runs in fp32 registers; only the pool representation changes.
@@ -179,7 +182,8 @@ template <int P, int N, int THREADS, int FMT>
 __global__ void __launch_bounds__(THREADS) mamba2_scan_kernel(const MambaParams p) {
   constexpr int CG = THREADS / P;          // column groups
   constexpr int NC = N / CG;               // state columns per thread
-  static_assert(THREADS % P == 0 && N % CG == 0 && CG <= 32 && (CG & (CG - 1)) == 0, "bad Mamba tiling");
+  static_assert(THREADS % P == 0 && N % CG == 0 && CG <= 32 && (CG & (CG - 1)) == 0 && NC % 4 == 0, "bad Mamba tiling");
+  auto col = [&](int i, int cg_) { return ((i >> 2) * CG + cg_) * 4 + (i & 3); };   // state column of register i
   __shared__ float bs[N], cs[N];
   const int b = blockIdx.y, h = blockIdx.x;
   if (!index_ok(p.slot_in[b], kBoundStateSlots, kKerMambaScan) ||
@@ -193,20 +197,31 @@ __global__ void __launch_bounds__(THREADS) mamba2_scan_kernel(const MambaParams 
   const bool init = p.has_init == nullptr || p.has_init[b] != 0;
   {
     const long long off = static_cast<long long>(p.slot_in[b]) * p.state_stride +
-                          (static_cast<long long>(h) * P + row) * N + cg * NC;
+                          (static_cast<long long>(h) * P + row) * N;
     if constexpr (FMT == 0) {
 #pragma unroll
-      for (int i = 0; i < NC; ++i) s[i] = init ? p.state[off + i] : 0.f;
+      for (int j = 0; j < NC / 4; ++j) {
+        const float4 v = init ? *reinterpret_cast<const float4*>(p.state + off + col(4 * j, cg)) : make_float4(0, 0, 0, 0);
+        s[4 * j] = v.x; s[4 * j + 1] = v.y; s[4 * j + 2] = v.z; s[4 * j + 3] = v.w;
+      }
     } else if constexpr (FMT == 1) {
       const __half* sin = reinterpret_cast<const __half*>(p.state) + off;
 #pragma unroll
-      for (int i = 0; i < NC; ++i) s[i] = init ? __half2float(sin[i]) : 0.f;
+      for (int j = 0; j < NC / 4; ++j) {
+        const uint2 raw = init ? *reinterpret_cast<const uint2*>(sin + col(4 * j, cg)) : make_uint2(0, 0);
+        const __half2 lo = *reinterpret_cast<const __half2*>(&raw.x), hi = *reinterpret_cast<const __half2*>(&raw.y);
+        s[4 * j] = __low2float(lo); s[4 * j + 1] = __high2float(lo);
+        s[4 * j + 2] = __low2float(hi); s[4 * j + 3] = __high2float(hi);
+      }
     } else {
       const int8_t* sin = reinterpret_cast<const int8_t*>(p.state) + off;
       const float sc = p.state_scale[static_cast<long long>(p.slot_in[b]) * (p.state_stride / N) +
                                      static_cast<long long>(h) * P + row];
 #pragma unroll
-      for (int i = 0; i < NC; ++i) s[i] = init ? static_cast<float>(sin[i]) * sc : 0.f;
+      for (int j = 0; j < NC / 4; ++j) {
+        const char4 raw = init ? *reinterpret_cast<const char4*>(sin + col(4 * j, cg)) : make_char4(0, 0, 0, 0);
+        s[4 * j] = raw.x * sc; s[4 * j + 1] = raw.y * sc; s[4 * j + 2] = raw.z * sc; s[4 * j + 3] = raw.w * sc;
+      }
     }
   }
   const float a = -__expf(p.a_log[h]);
@@ -226,8 +241,8 @@ __global__ void __launch_bounds__(THREADS) mamba2_scan_kernel(const MambaParams 
     float acc = 0.f;
 #pragma unroll
     for (int i = 0; i < NC; ++i) {
-      s[i] = s[i] * decay + dx * bs[cg * NC + i];
-      acc += s[i] * cs[cg * NC + i];
+      s[i] = s[i] * decay + dx * bs[col(i, cg)];
+      acc += s[i] * cs[col(i, cg)];
     }
 #pragma unroll
     for (int o = CG / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -235,24 +250,32 @@ __global__ void __launch_bounds__(THREADS) mamba2_scan_kernel(const MambaParams 
   }
   if (p.slot_out != nullptr) {
     const long long off = static_cast<long long>(p.slot_out[b]) * p.state_stride +
-                          (static_cast<long long>(h) * P + row) * N + cg * NC;
+                          (static_cast<long long>(h) * P + row) * N;
     if constexpr (FMT == 0) {
 #pragma unroll
-      for (int i = 0; i < NC; ++i) p.state[off + i] = s[i];
+      for (int j = 0; j < NC / 4; ++j)
+        *reinterpret_cast<float4*>(p.state + off + col(4 * j, cg)) =
+            make_float4(s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3]);
     } else if constexpr (FMT == 1) {
       __half* so = reinterpret_cast<__half*>(p.state) + off;
 #pragma unroll
-      for (int i = 0; i < NC; ++i) {
-        if (p.sr_seed == 0) {
-          so[i] = __float2half_rn(s[i]);
-        } else {
-          // stochastic rounding: up with probability (x - lo) / (hi - lo)
-          const __half lo = __float2half_rd(s[i]), hi = __float2half_ru(s[i]);
-          const float fl = __half2float(lo), fh = __half2float(hi);
-          const unsigned r = mix32(p.sr_seed ^ mix32(static_cast<unsigned>(off + i) * 2654435761u + r1));
-          const float u = (r >> 8) * (1.f / 16777216.f);
-          so[i] = (fh > fl && (s[i] - fl) > u * (fh - fl)) ? hi : lo;
+      for (int j = 0; j < NC / 4; ++j) {
+        __half r4[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = 4 * j + e;
+          if (p.sr_seed == 0) {
+            r4[e] = __float2half_rn(s[i]);
+          } else {
+            // stochastic rounding: up with probability (x - lo) / (hi - lo)
+            const __half lo = __float2half_rd(s[i]), hi = __float2half_ru(s[i]);
+            const float fl = __half2float(lo), fh = __half2float(hi);
+            const unsigned r = mix32(p.sr_seed ^ mix32(static_cast<unsigned>(off + col(i, cg)) * 2654435761u + r1));
+            const float u = (r >> 8) * (1.f / 16777216.f);
+            r4[e] = (fh > fl && (s[i] - fl) > u * (fh - fl)) ? hi : lo;
+          }
         }
+        *reinterpret_cast<uint2*>(so + col(4 * j, cg)) = *reinterpret_cast<const uint2*>(r4);
       }
     } else {
       float amax = 0.f;
@@ -264,7 +287,14 @@ __global__ void __launch_bounds__(THREADS) mamba2_scan_kernel(const MambaParams 
       const float inv = 1.f / sc;
       int8_t* so = reinterpret_cast<int8_t*>(p.state) + off;
 #pragma unroll
-      for (int i = 0; i < NC; ++i) so[i] = static_cast<int8_t>(__float2int_rn(fminf(fmaxf(s[i] * inv, -127.f), 127.f)));
+      for (int j = 0; j < NC / 4; ++j) {
+        char4 r4;
+        r4.x = static_cast<signed char>(__float2int_rn(fminf(fmaxf(s[4 * j] * inv, -127.f), 127.f)));
+        r4.y = static_cast<signed char>(__float2int_rn(fminf(fmaxf(s[4 * j + 1] * inv, -127.f), 127.f)));
+        r4.z = static_cast<signed char>(__float2int_rn(fminf(fmaxf(s[4 * j + 2] * inv, -127.f), 127.f)));
+        r4.w = static_cast<signed char>(__float2int_rn(fminf(fmaxf(s[4 * j + 3] * inv, -127.f), 127.f)));
+        *reinterpret_cast<char4*>(so + col(4 * j, cg)) = r4;
+      }
       if (cg == 0)
         p.state_scale[static_cast<long long>(p.slot_out[b]) * (p.state_stride / N) + static_cast<long long>(h) * P + row] = sc;
     }
@@ -294,6 +324,12 @@ struct GdnParams {
 // One CTA per (sequence, value head), V threads: thread v holds state row S[v, 0..K) in registers.
 template <int V, int K>
 __global__ void __launch_bounds__(V) gdn_scan_kernel(const GdnParams p) {
+  // The head's [V, K] fp32 state travels through shared memory (rows padded by four floats): global traffic is
+  // then whole rows per warp instruction in both directions, and thread v picks up / drops its own row from the
+  // padded tile without bank conflicts. Reading rows straight from global, 512 bytes apart per lane, used half of
+  // every sector and made a decode step take twice its state traffic.
+  extern __shared__ __align__(16) float gdn_tile[];
+  constexpr int TS = K + 4;
   __shared__ float qs[K], ks[K];
   __shared__ float red[2][V / 32];
   const int b = blockIdx.y, hv = blockIdx.x;
@@ -306,11 +342,22 @@ __global__ void __launch_bounds__(V) gdn_scan_kernel(const GdnParams p) {
   const int r1 = p.q_indptr ? p.q_indptr[b + 1] : b + 1;
   float s[K];
   const bool init = p.has_init == nullptr || p.has_init[b] != 0;
-  const float* sin = p.state + static_cast<long long>(p.slot_in[b]) * p.state_stride +
-                     (static_cast<long long>(hv) * V + v) * K;
+  if (init) {
+    const float* sin = p.state + static_cast<long long>(p.slot_in[b]) * p.state_stride +
+                       static_cast<long long>(hv) * V * K;
+    for (int idx = v; idx < V * K / 4; idx += V) {
+      const int row = idx / (K / 4), c4 = idx % (K / 4);
+      const unsigned dst = smem_u32(gdn_tile + row * TS + c4 * 4);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(sin + static_cast<long long>(idx) * 4)
+                   : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+  }
 #pragma unroll
   for (int i = 0; i < K; i += 4) {
-    const float4 t = init ? *reinterpret_cast<const float4*>(sin + i) : make_float4(0, 0, 0, 0);
+    const float4 t = init ? *reinterpret_cast<const float4*>(gdn_tile + v * TS + i) : make_float4(0, 0, 0, 0);
     s[i] = t.x; s[i + 1] = t.y; s[i + 2] = t.z; s[i + 3] = t.w;
   }
   for (int t = r0; t < r1; ++t) {
@@ -361,10 +408,17 @@ __global__ void __launch_bounds__(V) gdn_scan_kernel(const GdnParams p) {
     p.o[t * p.ldo + hv * V + v] = __float2bfloat16(o);
   }
   if (p.slot_out != nullptr) {
-    float* so = p.state + static_cast<long long>(p.slot_out[b]) * p.state_stride +
-                (static_cast<long long>(hv) * V + v) * K;
+    __syncthreads();
 #pragma unroll
-    for (int i = 0; i < K; i += 4) *reinterpret_cast<float4*>(so + i) = make_float4(s[i], s[i + 1], s[i + 2], s[i + 3]);
+    for (int i = 0; i < K; i += 4)
+      *reinterpret_cast<float4*>(gdn_tile + v * TS + i) = make_float4(s[i], s[i + 1], s[i + 2], s[i + 3]);
+    __syncthreads();
+    float* so = p.state + static_cast<long long>(p.slot_out[b]) * p.state_stride + static_cast<long long>(hv) * V * K;
+    for (int idx = v; idx < V * K / 4; idx += V) {
+      const int row = idx / (K / 4), c4 = idx % (K / 4);
+      *reinterpret_cast<float4*>(so + static_cast<long long>(idx) * 4) =
+          *reinterpret_cast<const float4*>(gdn_tile + row * TS + c4 * 4);
+    }
   }
 }
 
@@ -458,10 +512,23 @@ int hb_gdn_scan(const void* q, const void* k, const void* v, const void* g, cons
   p.q_indptr = IP(q_indptr); p.slot_in = IP(slot_in); p.slot_out = IP(slot_out); p.has_init = IP(has_init);
   p.k_heads = k_heads; p.v_heads = v_heads; p.scale = scale; p.l2norm = l2norm;
   const dim3 grid(v_heads, batch);
-  if (kdim == 128 && vdim == 128) gdn_scan_kernel<128, 128><<<grid, 128, 0, ST(stream)>>>(p);
-  else if (kdim == 64 && vdim == 64) gdn_scan_kernel<64, 64><<<grid, 64, 0, ST(stream)>>>(p);
-  else if (kdim == 32 && vdim == 32) gdn_scan_kernel<32, 32><<<grid, 32, 0, ST(stream)>>>(p);
-  else return 1;
+  if (kdim == 128 && vdim == 128) {
+    constexpr int SMEM = 128 * (128 + 4) * 4;     // above the 48 KB default: opt in once
+    static bool armed = false;
+    if (!armed) {
+      if (cudaFuncSetAttribute(gdn_scan_kernel<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) !=
+          cudaSuccess)
+        return 3;
+      armed = true;
+    }
+    gdn_scan_kernel<128, 128><<<grid, 128, SMEM, ST(stream)>>>(p);
+  } else if (kdim == 64 && vdim == 64) {
+    gdn_scan_kernel<64, 64><<<grid, 64, 64 * 68 * 4, ST(stream)>>>(p);
+  } else if (kdim == 32 && vdim == 32) {
+    gdn_scan_kernel<32, 32><<<grid, 32, 32 * 36 * 4, ST(stream)>>>(p);
+  } else {
+    return 1;
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

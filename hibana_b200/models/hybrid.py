@@ -12,7 +12,8 @@ from typing import Optional
 import torch
 
 from ..engine.context import ForwardContext
-from ..ops import basic, gemm
+from .. import _native as nv
+from ..ops import basic, gemm, nvfp4
 from ..target import GDN, MAMBA2, NONE, Target
 from .layers import Init, MoeLayer, build_ffn, build_mixer
 
@@ -151,8 +152,16 @@ class HybridModel:
             for norm_w, sub in blk.sublayers():
                 if sub is None:
                     continue
+                xq = None
+                first = getattr(sub, "first", None)
                 if partial:
                     x = self._reduce_norm(h, res, norm_w, ctx)
+                elif (first is not None and first.fmt == "nvfp4" and not first.calibrating and t.hidden <= 8192
+                      and nv.use_native(res)):
+                    # the norm writes the first projection's NVFP4 input itself (one kernel instead of norm + quantise)
+                    xq, x = nvfp4.rmsnorm_quantize(res if h is None else h, norm_w, t.norm_eps, first.input_scale,
+                                                   residual=None if h is None else res, gemma=t.gemma_norm,
+                                                   want_normed=sub.needs_x)
                 else:
                     x = basic.rmsnorm(res if h is None else h, norm_w, t.norm_eps,
                                       residual=None if h is None else res, gemma=t.gemma_norm)
@@ -163,6 +172,8 @@ class HybridModel:
                     h = sub.forward_a2a(x, ctx.extras["ep"])
                 elif isinstance(sub, MoeLayer) and sub.ep_size > 1 and ctx.comm is not None:
                     h = sub.forward_ep(x, ctx.comm)
+                elif xq is not None:
+                    h = sub.forward(x, ctx, kv, states, xq=xq)
                 else:
                     h = sub.forward(x, ctx, kv, states)
         if partial:

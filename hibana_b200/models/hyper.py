@@ -16,10 +16,11 @@ import torch.nn.functional as F
 from .. import _native as nv
 from ..ops import gemm
 
-P, I, Fl = nv.P, nv.I, nv.F
+P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
 nv.register("hb_hc_norm", [P, P, P, I, I, I, Fl, P])
 nv.register("hb_hc_gate_mean", [P, P, P, I, I, I, P])
-nv.register("hb_hc_inject", [P, P, P, P, I, I, I, P])
+nv.register("hb_hc_inject", [P, P, P, L, P, I, I, I, P])
+nv.register("hb_hc_low", [P, L, P, I, I, P])
 
 
 def grouped_norm_ref(hyper: torch.Tensor, w: torch.Tensor, hc: int, eps: float) -> torch.Tensor:
@@ -43,6 +44,10 @@ class HyperConnection:
             inj = torch.zeros(16, hc * hidden, dtype=torch.bfloat16, device=inject.device)
             inj[:hc] = (inject / hc).to(torch.bfloat16)
         self.inject = inj
+        # one projection for both readers of the normed streams on the GPU: rows [down | inject] (the rank is padded
+        # to a multiple of 16 rows by the inject block), fp32 out; `low` and the inject logits are cut from it
+        self.rank = self.down.shape[0]
+        self.down_inject = torch.cat((self.down, inj), 0).contiguous() if inj is not None else None
 
     def normed(self, hyper: torch.Tensor) -> torch.Tensor:
         t = hyper.shape[0]
@@ -57,7 +62,14 @@ class HyperConnection:
         """hyper [T, hc * H] bf16 -> (block input [T, H], residuals for `combine`)."""
         t = hyper.shape[0]
         n = self.normed(hyper)
-        low = F.silu(gemm.linear_bf16(n, self.down))        # one elementwise launch (fp32 math inside, bf16 out)
+        both = None
+        if nv.use_native(hyper) and self.down_inject is not None:
+            both = gemm.linear_bf16(n, self.down_inject, epilogue=gemm.EPI_STORE_F32)      # [T, rank + 16] fp32
+            low = torch.empty(t, self.rank, dtype=torch.bfloat16, device=hyper.device)
+            nv.check(nv.lib().hb_hc_low(both.data_ptr(), both.stride(0), low.data_ptr(), t, self.rank, nv.stream()),
+                     "hb_hc_low")
+        else:
+            low = F.silu(gemm.linear_bf16(n, self.down))    # one elementwise launch (fp32 math inside, bf16 out)
         gate = gemm.linear_bf16(low, self.up)
         if nv.use_native(hyper):
             mixed = torch.empty(t, self.hidden, dtype=torch.bfloat16, device=hyper.device)
@@ -66,16 +78,20 @@ class HyperConnection:
         else:
             mixed = (torch.sigmoid(gate.float()).view(t, self.hc, -1) * n.float().view(t, self.hc, -1)).mean(1)
             mixed = mixed.to(torch.bfloat16)
-        return mixed, (hyper, n)
+        return mixed, (hyper, n, both)
 
     def combine(self, block_output: torch.Tensor, residuals) -> torch.Tensor:
-        hyper, n = residuals
+        hyper, n, both = residuals
         t = hyper.shape[0]
-        logits = gemm.linear_bf16(n, self.inject, epilogue=gemm.EPI_STORE_F32)[:, :self.hc].contiguous()
+        if both is not None:          # the inject logits came with the gate's first projection (mix)
+            logits = both[:, self.rank:]
+        else:
+            logits = gemm.linear_bf16(n, self.inject, epilogue=gemm.EPI_STORE_F32)[:, :self.hc]
         if nv.use_native(hyper):
             out = torch.empty_like(hyper)
             nv.check(nv.lib().hb_hc_inject(hyper.data_ptr(), block_output.data_ptr(), logits.data_ptr(),
-                                           out.data_ptr(), t, self.hc, self.hidden, nv.stream()), "hb_hc_inject")
+                                           logits.stride(0), out.data_ptr(), t, self.hc, self.hidden, nv.stream()),
+                     "hb_hc_inject")
             return out
         inj = 2 * torch.sigmoid(logits.float())
         r = hyper.float().view(t, self.hc, -1) + block_output.float()[:, None, :] * inj[:, :, None]

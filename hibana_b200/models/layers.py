@@ -87,6 +87,9 @@ class AttentionLayer:
         self.qkv = init.linear(qw + 2 * f.kv_heads * d, t.hidden, _fmt(t), name + ".qkv", rows=rows)
         self.o = init.linear(t.hidden, f.q_heads * d, _fmt(t), name + ".o",
                              cols=init.span(t.q_heads * d) if init.tp > 1 else None)
+        # the projection that reads the normed rows (the norm can quantise straight into its format) and whether
+        # anything else of the layer still needs them in bf16
+        self.first, self.needs_x = self.qkv, False
         self.partial = init.tp > 1
         self.q_norm = init.ones(d, t.gemma_norm) if t.qk_norm else None
         self.k_norm = init.ones(d, t.gemma_norm) if t.qk_norm else None
@@ -96,9 +99,9 @@ class AttentionLayer:
     def linears(self):
         return [self.qkv, self.o]
 
-    def forward(self, x, ctx: ForwardContext, kv, states) -> torch.Tensor:
+    def forward(self, x, ctx: ForwardContext, kv, states, xq=None) -> torch.Tensor:
         t = self.t
-        qkv = self.qkv(x)
+        qkv = self.qkv(x if xq is None else xq)
         i = self.kv_index
         q = basic.rope_kv_write(qkv, ctx.positions, ctx.slots, self.inv_freq, kv.k[i], kv.v[i], t.q_heads,
                                 t.kv_heads, t.head_dim, rot=t.rot_dim, q_norm=self.q_norm, k_norm=self.k_norm,
@@ -139,15 +142,18 @@ class MambaLayer:
         self.dt_bias = init.take(dt + torch.log(-torch.expm1(-dt)), hsel).to(init.device)       # inverse softplus
         self.d_skip = torch.ones(t.mamba_heads, device=init.device)
         self.norm_w = init.ones(inner)
+        # the projection that reads the normed rows (the norm can quantise straight into its format) and whether
+        # anything else of the layer still needs them in bf16
+        self.first, self.needs_x = self.in_proj, False
         self.partial = init.tp > 1
 
     def linears(self):
         return [self.in_proj, self.out_proj]
 
-    def forward(self, x, ctx: ForwardContext, kv, states) -> torch.Tensor:
+    def forward(self, x, ctx: ForwardContext, kv, states, xq=None) -> torch.Tensor:
         t = self.t
         inner, gn = t.mamba_inner, t.mamba_groups * t.mamba_state
-        zxbcdt = self.in_proj(x)
+        zxbcdt = self.in_proj(x if xq is None else xq)
         z = zxbcdt[:, :inner]
         xbc = zxbcdt[:, inner:2 * inner + 2 * gn]
         dt = zxbcdt[:, 2 * inner + 2 * gn:]
@@ -164,6 +170,10 @@ class MambaLayer:
                                   d_state=t.mamba_state, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state,
                                   state_scale=states.ssm_scale[li] if getattr(states, "ssm_scale", None) is not None
                                   else None, sr_seed=ctx.extras.get("sr_seed", 0), host_rows=ctx.seq_starts_host)
+        if self.out_proj.fmt == "nvfp4" and not self.out_proj.calibrating:
+            # the gated norm writes the output projection's NVFP4 input itself
+            return self.out_proj(basic.gated_rmsnorm_quant(y, z, self.norm_w, t.norm_eps, inner // t.mamba_groups,
+                                                           self.out_proj.input_scale))
         y = basic.gated_rmsnorm(y, z, self.norm_w, t.norm_eps, inner // t.mamba_groups)
         return self.out_proj(y)
 
@@ -204,20 +214,22 @@ class GdnLayer:
         self.a_log = init.take(torch.log(init.uniform(f.gdn_v_heads, lo=1.0, hi=16.0)), hsel).to(init.device)
         self.dt_bias = init.take(init.normal(f.gdn_v_heads, std=0.5), hsel).to(init.device)
         self.norm_w = init.ones(kd, t.gemma_norm)
+        self.norm_w_heads, self._norm_w_key = None, None          # norm_w repeated per head, rebuilt when it changes
+        # the projection that reads the normed rows (the norm can quantise straight into its format) and whether
+        # anything else of the layer still needs them in bf16
+        self.first, self.needs_x = self.in_qkvz, True
         self.partial = init.tp > 1
 
     def linears(self):
         return [self.in_qkvz, self.in_ba, self.out_proj]
 
-    def forward(self, x, ctx: ForwardContext, kv, states) -> torch.Tensor:
+    def forward(self, x, ctx: ForwardContext, kv, states, xq=None) -> torch.Tensor:
         t = self.t
         kd = t.gdn_head_dim
-        qkvz = self.in_qkvz(x)
-        ba = self.in_ba(x).float()
+        qkvz = self.in_qkvz(x if xq is None else xq)
         li = self.state_index
         so = ctx.extras.get("state_out", ctx.state_slots)
-        beta = torch.sigmoid(ba[:, :t.gdn_v_heads]).contiguous()
-        g = (-torch.exp(self.a_log) * torch.nn.functional.softplus(ba[:, t.gdn_v_heads:] + self.dt_bias)).contiguous()
+        beta, g = basic.gdn_gates(self.in_ba(x), self.a_log, self.dt_bias)
         if "ring" in ctx.extras:
             ctx.extras["ring"].append((self, (qkvz[:, :2 * self.qk + self.vd], g, beta)))
         qkv = recurrent.conv1d(qkvz[:, :2 * self.qk + self.vd], self.conv_w, None, states.conv[li], ctx.state_slots,
@@ -230,7 +242,13 @@ class GdnLayer:
                                has_init=ctx.has_initial_state, host_rows=ctx.seq_starts_host)
         rows = o.shape[0]
         # per-head RMSNorm of the output, then the SiLU gate (norm before gate)
-        w = self.norm_w.repeat(t.gdn_v_heads)
+        key = (id(self.norm_w), self.norm_w._version)
+        if self._norm_w_key != key:
+            self.norm_w_heads, self._norm_w_key = self.norm_w.repeat(t.gdn_v_heads), key
+        w = self.norm_w_heads
+        if self.out_proj.fmt == "nvfp4" and not self.out_proj.calibrating:
+            return self.out_proj(basic.gated_rmsnorm_quant(o, z, w, t.norm_eps, kd, self.out_proj.input_scale,
+                                                           norm_first=True, gemma=t.gemma_norm))
         y = basic.gated_rmsnorm(o, z, w, t.norm_eps, kd, norm_first=True, gemma=t.gemma_norm)
         return self.out_proj(y.view(rows, -1))
 
@@ -261,12 +279,16 @@ class MlpLayer:
         else:
             self.up = init.linear(width, t.hidden, _fmt(t), name + ".up", rows=init.span(local) if init.tp > 1 else None)
         self.down = init.linear(t.hidden, width, _fmt(t), name + ".down", cols=init.span(local) if init.tp > 1 else None)
+        # the projection that reads the normed rows (the norm can quantise straight into its format) and whether
+        # anything else of the layer still needs them in bf16
+        self.first, self.needs_x = self.up, False
         self.partial = init.tp > 1
 
     def linears(self):
         return [self.up, self.down]
 
-    def forward(self, x, ctx=None, kv=None, states=None) -> torch.Tensor:
+    def forward(self, x, ctx=None, kv=None, states=None, xq=None) -> torch.Tensor:
+        x = x if xq is None else xq
         if self.act == "swiglu":
             return self.down(self.up(x, epilogue=gemm.EPI_SILU_MUL))
         return self.down(basic.act_mul(self.up(x), basic.ACT_RELU2))

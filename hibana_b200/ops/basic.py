@@ -17,6 +17,8 @@ from .. import _native as nv
 P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
 nv.register("hb_rmsnorm", [P, P, P, P, I, I, L, L, Fl, I, P])
 nv.register("hb_gated_rmsnorm", [P, P, P, P, I, I, I, L, L, Fl, I, I, I, P])
+nv.register("hb_gated_rmsnorm_quant", [P, P, P, I, I, I, L, L, Fl, I, I, I, P, P, P, I, P])
+nv.register("hb_gdn_gates", [P, L, P, P, I, I, P, P, P])
 nv.register("hb_rope_kv_write", [P, L, P, P, P, P, P, Fl, I, P, P, P, L, L, I, I, I, I, I, I, Fl, I, P])
 nv.register("hb_act_mul", [P, P, P, L, I, L, I, P])
 nv.register("hb_embedding", [P, P, P, I, I, L, P])
@@ -71,6 +73,44 @@ def gated_rmsnorm(x: torch.Tensor, z: Optional[torch.Tensor], weight: torch.Tens
     if gate is not None and norm_first:
         y = y * gate
     return y.to(x.dtype)
+
+
+def gated_rmsnorm_quant(x: torch.Tensor, z: Optional[torch.Tensor], weight: torch.Tensor, eps: float, group_size: int,
+                        gscale: torch.Tensor, *, norm_first: bool = False, sigmoid_gate: bool = False,
+                        gemma: bool = False):
+    """`gated_rmsnorm` written as NVFP4 rows for the projection that follows (one kernel instead of norm + quantise)
+    where the shape allows it (group size a multiple of 16 up to 1024, width a multiple of 64); otherwise the two
+    steps. Returns an Nvfp4Tensor."""
+    from . import nvfp4
+    rows, h = x.shape
+    ok = (nv.use_native(x) and group_size % 16 == 0 and group_size <= 1024 and h % 64 == 0 and x.stride(0) % 8 == 0
+          and (z is None or z.stride(0) % 8 == 0))
+    if not ok:
+        return nvfp4.quantize(gated_rmsnorm(x, z, weight, eps, group_size, norm_first=norm_first,
+                                            sigmoid_gate=sigmoid_gate, gemma=gemma), gscale)
+    q, sf = nvfp4._alloc(rows, h, x.device)
+    nv.check(nv.lib().hb_gated_rmsnorm_quant(x.data_ptr(), nv.ptr(z), weight.data_ptr(), rows, h, group_size,
+                                             x.stride(0), z.stride(0) if z is not None else 0, eps, int(norm_first),
+                                             int(sigmoid_gate), int(gemma), q.data_ptr(), sf.data_ptr(),
+                                             gscale.data_ptr(), sf.shape[1], nv.stream()), "hb_gated_rmsnorm_quant")
+    return nvfp4.Nvfp4Tensor(q, sf, gscale, rows, h)
+
+
+def gdn_gates(ba: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Gated delta rule gates from the b | a projection ba [T, 2 * heads] (bf16): beta = sigmoid(b) and the log
+    decay g = -exp(a_log) * softplus(a + dt_bias), both fp32 [T, heads], in one kernel."""
+    rows, two = ba.shape
+    heads = two // 2
+    if nv.use_native(ba):
+        beta = torch.empty(rows, heads, dtype=torch.float32, device=ba.device)
+        g = torch.empty(rows, heads, dtype=torch.float32, device=ba.device)
+        nv.check(nv.lib().hb_gdn_gates(ba.data_ptr(), ba.stride(0), a_log.data_ptr(), dt_bias.data_ptr(), rows, heads,
+                                       beta.data_ptr(), g.data_ptr(), nv.stream()), "hb_gdn_gates")
+        return beta, g
+    f = ba.float()
+    beta = torch.sigmoid(f[:, :heads]).contiguous()
+    g = (-torch.exp(a_log.float()) * F.softplus(f[:, heads:] + dt_bias.float())).contiguous()
+    return beta, g
 
 
 def rope_inv_freq(rot_dim: int, theta: float, device=None) -> torch.Tensor:

@@ -20,6 +20,7 @@ from . import gemm, nvfp4
 
 P, I, L, Fl = nv.P, nv.I, nv.L, nv.F
 nv.register("hb_moe_route", [P, L, P, I, I, I, I, I, Fl, P, P, P])
+nv.register("hb_quant_nvfp4_pairs", [P, L, P, I, I, I, I, P, P, P, P])
 nv.register("hb_moe_plan", [P, I, I, I, I, I, I, P, P, P, P, I, P, I, P, P, I, P])
 nv.register("hb_moe_gather", [P, L, P, P, P, I, I, P])
 nv.register("hb_moe_combine", [P, L, P, P, P, L, P, L, I, I, I, P])
@@ -265,18 +266,31 @@ def experts_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
                                      cnt.data_ptr(), max_rows, st.data_ptr(), 0, 0, bn_hint, *tl, nv.stream()), "hb_gemm_grouped")
     else:
         q1, sf1 = nvfp4._alloc(rows_cap, h, dev)
-        nv.check(lib.hb_quant_nvfp4_rows(x.data_ptr(), x.stride(0), rows_cap, h, sf1.shape[1],
-                                         ew.fc1_in_scale.data_ptr(), q1.data_ptr(), sf1.data_ptr(), 0, src.data_ptr(),
-                                         total.data_ptr(), nv.stream()), "hb_quant_nvfp4_rows")
+        # few pairs (decode, verify): quantise by pair, not by row of the padded buffer (most of which is padding
+        # of the 128-row expert segments that the GEMM never stores from)
+        by_pair = t * topk * 8 <= rows_cap
+        if by_pair:
+            nv.check(lib.hb_quant_nvfp4_pairs(x.data_ptr(), x.stride(0), pos.data_ptr(), t * topk, topk, h,
+                                              sf1.shape[1], ew.fc1_in_scale.data_ptr(), q1.data_ptr(),
+                                              sf1.data_ptr(), nv.stream()), "hb_quant_nvfp4_pairs")
+        else:
+            nv.check(lib.hb_quant_nvfp4_rows(x.data_ptr(), x.stride(0), rows_cap, h, sf1.shape[1],
+                                             ew.fc1_in_scale.data_ptr(), q1.data_ptr(), sf1.data_ptr(), 0,
+                                             src.data_ptr(), total.data_ptr(), nv.stream()), "hb_quant_nvfp4_rows")
         nv.check(lib.hb_gemm_grouped(1, ew.fc1.q.data_ptr(), q1.data_ptr(), ew.fc1.sf.data_ptr(), sf1.data_ptr(), e,
                                      n1, rows_cap, h, h1.data_ptr(), h1.stride(0), ew.fc1_alpha.data_ptr(), epi1,
                                      start.data_ptr(), cnt.data_ptr(), max_rows, st.data_ptr(), ew.fc1.ka,
                                      sf1.shape[1], bn_hint, *tl, nv.stream()), "hb_gemm_grouped")
         mid = h1                                # the activation (SwiGLU or squared ReLU) ran in the GEMM epilogue
         q2, sf2 = nvfp4._alloc(rows_cap, ew.inter, dev)
-        nv.check(lib.hb_quant_nvfp4_rows(mid.data_ptr(), mid.stride(0), rows_cap, ew.inter, sf2.shape[1],
-                                         ew.fc2_in_scale.data_ptr(), q2.data_ptr(), sf2.data_ptr(), 0, None,
-                                         total.data_ptr(), nv.stream()), "hb_quant_nvfp4_rows")
+        if by_pair:
+            nv.check(lib.hb_quant_nvfp4_pairs(mid.data_ptr(), mid.stride(0), pos.data_ptr(), t * topk, 0, ew.inter,
+                                              sf2.shape[1], ew.fc2_in_scale.data_ptr(), q2.data_ptr(),
+                                              sf2.data_ptr(), nv.stream()), "hb_quant_nvfp4_pairs")
+        else:
+            nv.check(lib.hb_quant_nvfp4_rows(mid.data_ptr(), mid.stride(0), rows_cap, ew.inter, sf2.shape[1],
+                                             ew.fc2_in_scale.data_ptr(), q2.data_ptr(), sf2.data_ptr(), 0, None,
+                                             total.data_ptr(), nv.stream()), "hb_quant_nvfp4_rows")
         nv.check(lib.hb_gemm_grouped(1, ew.fc2.q.data_ptr(), q2.data_ptr(), ew.fc2.sf.data_ptr(), sf2.data_ptr(), e,
                                      h_out, rows_cap, ew.inter, y.data_ptr(), y.stride(0), ew.fc2_alpha.data_ptr(),
                                      gemm.EPI_STORE, start.data_ptr(), cnt.data_ptr(), max_rows, st.data_ptr(),

@@ -4,7 +4,7 @@ import math
 import pytest
 import torch
 
-from hibana_b200.ops import attention, basic, sampling
+from hibana_b200.ops import attention, basic, nvfp4, sampling
 
 
 def _close(a, b, tol):
@@ -390,6 +390,35 @@ def test_spec_targets_kernel_matches_reference():
     assert (t16.cpu() == r16).float().mean() > 0.97
     from hibana_b200 import _native as nv
     assert nv.read_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("gs,h,norm_first", [(1024, 4096, False), (128, 1536, True), (512, 1024, False)])
+def test_gated_rmsnorm_quant_equals_norm_then_quantise(gs, h, norm_first):
+    g = torch.Generator().manual_seed(1)
+    rows = 19
+    x = torch.randn(rows, h + 64, generator=g).bfloat16().cuda()[:, :h]          # strided rows
+    z = torch.randn(rows, h, generator=g).bfloat16().cuda()
+    w = (torch.randn(h, generator=g) * 0.1 + 1).bfloat16().cuda()
+    scale = torch.tensor([4.0 / (6 * 448)], device="cuda")
+    ref = basic.gated_rmsnorm(x, z, w, 1e-5, gs, norm_first=norm_first)
+    cpu = basic.gated_rmsnorm(x.cpu(), z.cpu(), w.cpu(), 1e-5, gs, norm_first=norm_first)
+    _close(ref.cpu(), cpu, 2e-2)
+    want = nvfp4.quantize(ref, scale)
+    got = basic.gated_rmsnorm_quant(x, z, w, 1e-5, gs, scale, norm_first=norm_first)
+    assert torch.equal(got.q, want.q)
+    groups = h // 16
+    assert torch.equal(nvfp4.unswizzle_sf(got.sf, rows, groups), nvfp4.unswizzle_sf(want.sf, rows, groups))
+
+
+@pytest.mark.gpu
+def test_gdn_gates_kernel():
+    g = torch.Generator().manual_seed(2)
+    ba = (torch.randn(33, 96, generator=g) * 3).bfloat16()
+    a_log, dtb = torch.randn(48, generator=g), torch.randn(48, generator=g)
+    beta, gg = basic.gdn_gates(ba, a_log, dtb)
+    b2, g2 = basic.gdn_gates(ba.cuda(), a_log.cuda(), dtb.cuda())
+    assert torch.allclose(b2.cpu(), beta, atol=1e-5) and torch.allclose(g2.cpu(), gg, rtol=1e-4, atol=1e-5)
 
 
 @pytest.mark.gpu
