@@ -162,6 +162,8 @@ int hb_gated_rmsnorm_quant(const void* x, const void* z, const void* w, int rows
                            const void* gscale, int ka, void* stream);
 int hb_gdn_gates(const void* ba, long long ld, const void* a_log, const void* dt_bias, int rows, int heads,
                  void* beta, void* g, void* stream);
+int hb_moe_share(void* ids, void* weights, int rows, int k, int experts, int keep, int budget, float scale,
+                 void* stream);
 int hb_bounds_enabled();
 int hb_bounds_set(int which, long long value);
 int hb_bounds_read(long long* out);

@@ -121,6 +121,76 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
 #undef HB_ROUTE_RESCAN
 }
 
+// Budgeted expert sharing for small batches (decode, verify): a step whose rows pick their experts independently
+// streams almost rows x top-k distinct experts' weights; here the call as a whole reads at most `budget` distinct
+// experts. Every row keeps its best `keep` choices; the rest of the budget goes to the experts with the largest
+// summed routing weight over the call (ties: the lower id); a row then uses those of its top-k that made the set, in
+// rank order, with its weights renormalised over them (times `scale`), and fills the slots it lost with its best
+// expert at weight 0 so that shapes stay fixed. ids / weights are the router's output [rows, k], updated in place.
+// One CTA of 1024 threads; experts <= 1024, rows * k <= 16384. Sums are integers (2^-24 units): order-independent.
+__global__ void __launch_bounds__(1024)
+moe_share_kernel(int* __restrict__ ids, float* __restrict__ weights, int rows, int k, int experts, int keep, int budget,
+                 float scale) {
+  __shared__ unsigned score[1024];
+  __shared__ unsigned char in_set[1024];
+  __shared__ int s_core;
+  const int tid = threadIdx.x;
+  if (tid < 1024) {
+    score[tid] = 0u;
+    in_set[tid] = 0;
+  }
+  if (tid == 0) s_core = 0;
+  __syncthreads();
+  for (int i = tid; i < rows * k; i += blockDim.x) {
+    const int r = i / k, j = i - r * k;
+    const int e = ids[i];
+    if (e < 0 || e >= experts) continue;
+    float sum = 0.f;
+    for (int q = 0; q < k; ++q) sum += weights[r * k + q];
+    const float w = sum > 0.f ? weights[i] / sum : 0.f;
+    atomicAdd(&score[e], static_cast<unsigned>(w * 16777216.f));
+    if (j < keep) in_set[e] = 1;
+  }
+  __syncthreads();
+  if (tid < experts && in_set[tid]) atomicAdd(&s_core, 1);
+  __syncthreads();
+  const int need = budget - s_core;
+  bool add = false;
+  if (tid < experts && !in_set[tid] && score[tid] > 0u && need > 0) {
+    const unsigned mine = score[tid];
+    int ahead = 0;
+    for (int e = 0; e < experts; ++e)
+      ahead += !in_set[e] && (score[e] > mine || (score[e] == mine && e < tid));
+    add = ahead < need;
+  }
+  __syncthreads();      // every rank was counted against the guaranteed set alone
+  if (add) in_set[tid] = 2;
+  __syncthreads();
+  for (int r = tid; r < rows; r += blockDim.x) {
+    int* ri = ids + static_cast<long long>(r) * k;
+    float* rw = weights + static_cast<long long>(r) * k;
+    const int first = ri[0];
+    float sum = 0.f;
+    int used = 0;
+    for (int j = 0; j < k; ++j) {
+      const int e = ri[j];
+      const float w = rw[j];
+      if (e >= 0 && e < experts && in_set[e]) {
+        ri[used] = e;
+        rw[used] = w;
+        sum += w;
+        ++used;
+      }
+    }
+    const float inv = sum > 0.f ? scale / sum : 0.f;
+    for (int j = 0; j < used; ++j) rw[j] *= inv;
+    for (int j = used; j < k; ++j) {
+      ri[j] = first;
+      rw[j] = 0.f;
+    }
+  }
+}
+
 // Exclusive prefix sum over the 1024 threads of the CTA (thread i contributes v); `total` receives the sum.
 __device__ __forceinline__ int block_excl_scan_1024(int v, int* wtot, int* total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -343,6 +413,15 @@ int hb_moe_route(const void* logits, long long ld, const void* sel_bias, int tok
   else if (experts <= 512) HB_ROUTE(16);
   else HB_ROUTE(32);
 #undef HB_ROUTE
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int hb_moe_share(void* ids, void* weights, int rows, int k, int experts, int keep, int budget, float scale,
+                 void* stream) {
+  if (rows <= 0) return 0;
+  if (experts > 1024 || k > MAX_TOPK || keep < 0 || keep > k || rows * k > 16384) return 1;
+  moe_share_kernel<<<1, 1024, 0, ST(stream)>>>(static_cast<int*>(ids), static_cast<float*>(weights), rows, k, experts,
+                                               keep, budget, scale);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

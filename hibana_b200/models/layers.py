@@ -12,6 +12,7 @@ from typing import Optional
 
 import torch
 
+from .. import config as cfgmod
 from ..engine.context import ForwardContext
 from ..ops import attention, basic, gemm, moe, recurrent
 from ..target import ATTN, GATED_ATTN, GDN, LATENT_MOE, MAMBA2, MLP, MOE, NONE, Target
@@ -331,11 +332,21 @@ class MoeLayer:
         out += [l for l in (self.fc1_latent, self.fc2_latent) if l is not None]
         return out
 
+    def _route(self, logits: torch.Tensor):
+        """Top-k routing; with `expert_budget` set, decode-sized calls share experts across their rows."""
+        t = self.t
+        ids, w = moe.route(logits, t.top_k, sigmoid=t.router == "sigmoid", sel_bias=self.sel_bias, renorm=True,
+                           scale=t.router_scale)
+        cfg = cfgmod.current()
+        if cfg.expert_budget > 0 and logits.shape[0] * t.top_k <= 16384 and logits.shape[0] <= 256:
+            ids, w = moe.share_experts(ids, w, t.experts, min(cfg.expert_keep, t.top_k), cfg.expert_budget,
+                                       scale=t.router_scale)
+        return ids, w
+
     def forward(self, x, ctx=None, kv=None, states=None) -> torch.Tensor:
         t = self.t
         logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
-        ids, w = moe.route(logits, t.top_k, sigmoid=t.router == "sigmoid", sel_bias=self.sel_bias, renorm=True,
-                           scale=t.router_scale)
+        ids, w = self._route(logits)
         shared = self.shared.forward(x) if self.shared is not None else None
         if shared is not None and self.tp > 1 and ctx is not None and ctx.comm is not None:
             shared = ctx.comm.all_reduce(shared)      # column / row split shared expert beside replicated experts
@@ -352,8 +363,7 @@ def _moe_forward_ep(self, x, comm) -> torch.Tensor:
     are all-reduced, and the (replicated) shared expert is added once afterwards."""
     t = self.t
     logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
-    ids, w = moe.route(logits, t.top_k, sigmoid=t.router == "sigmoid", sel_bias=self.sel_bias, renorm=True,
-                       scale=t.router_scale)
+    ids, w = self._route(logits)
     inp = self.fc1_latent(x) if t.latent else x
     part = moe.experts_forward(inp, ids, w, self.experts, id_base=self.e_lo)
     if getattr(self, "tp", 1) > 1:
@@ -378,8 +388,7 @@ def _moe_forward_a2a(self, x, ep) -> torch.Tensor:
     t = self.t
     assert self.ep_size == ep.world and self.e_lo == ep.rank * ep.e_per, "the layer holds another expert range"
     logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
-    ids, w = moe.route(logits, t.top_k, sigmoid=t.router == "sigmoid", sel_bias=self.sel_bias, renorm=True,
-                       scale=t.router_scale)
+    ids, w = self._route(logits)
     shared = self.shared.forward(x) if self.shared is not None and x.shape[0] else None
     if t.latent:
         y = ep.forward(self.fc1_latent(x), ids, w, self.experts)

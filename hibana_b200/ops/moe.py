@@ -59,6 +59,69 @@ def route(logits: torch.Tensor, topk: int, *, sigmoid: bool = False, sel_bias: O
     return route_ref(logits, topk, sigmoid=sigmoid, sel_bias=sel_bias, renorm=renorm, scale=scale)
 
 
+nv.register("hb_moe_share", [P, P, I, I, I, I, I, nv.F, P])
+
+
+def share_experts_ref(ids: torch.Tensor, weights: torch.Tensor, experts: int, keep: int, budget: int,
+                      scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Plain PyTorch `share_experts` (same integer score sums, same tie rule)."""
+    rows, k = ids.shape
+    ids, weights = ids.clone().cpu(), weights.clone().cpu().float()
+    score = torch.zeros(experts, dtype=torch.int64)
+    core = torch.zeros(experts, dtype=torch.bool)
+    for r in range(rows):
+        tot = torch.zeros((), dtype=torch.float32)
+        for q in range(k):
+            tot = tot + weights[r, q]
+        for j in range(k):
+            e = int(ids[r, j])
+            if 0 <= e < experts:
+                w = weights[r, j] / tot if float(tot) > 0 else torch.zeros(())
+                score[e] += int((w * torch.tensor(16777216.0)).to(torch.int64))
+                if j < keep:
+                    core[e] = True
+    need = budget - int(core.sum())
+    chosen = core.clone()
+    if need > 0:
+        rest = [(-int(score[e]), e) for e in range(experts) if not core[e] and int(score[e]) > 0]
+        for _, e in sorted(rest)[:need]:
+            chosen[e] = True
+    for r in range(rows):
+        first = int(ids[r, 0])
+        kept = [(int(ids[r, j]), weights[r, j].clone()) for j in range(k)
+                if 0 <= int(ids[r, j]) < experts and chosen[int(ids[r, j])]]
+        tot = torch.zeros((), dtype=torch.float32)
+        for _, w in kept:
+            tot = tot + w
+        inv = torch.tensor(scale, dtype=torch.float32) / tot if float(tot) > 0 else torch.zeros(())
+        for j in range(k):
+            if j < len(kept):
+                ids[r, j], weights[r, j] = kept[j][0], kept[j][1] * inv
+            else:
+                ids[r, j], weights[r, j] = first, 0.0
+    return ids, weights
+
+
+def share_experts(ids: torch.Tensor, weights: torch.Tensor, experts: int, keep: int, budget: int,
+                  scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Budgeted expert sharing for decode-sized batches: the call as a whole uses at most `budget` distinct experts
+    (more only when the rows' guaranteed best `keep` choices alone exceed it). Every row keeps its best `keep`;
+    the remaining budget goes to the experts with the largest routing weight summed over the call; a row then uses
+    those of its top-k inside the set, weights renormalised over them (times `scale`), and repeats its best expert
+    at weight 0 in the slots it lost. Lossy by design (fewer experts' weights are streamed per step); rows that
+    keep all their choices keep their weights up to the renormalisation. ids int32 / weights fp32 [rows, k] from
+    `route`; returns new tensors. Reference: hibana/model/nemotron/moe.py:171-306 (`route_budget`),
+    hibana/kernels/flashnext_fused.py:412-506."""
+    rows, k = ids.shape
+    if nv.use_native(ids) and experts <= 1024 and rows * k <= 16384:
+        ids, weights = ids.clone(), weights.clone()
+        nv.check(nv.lib().hb_moe_share(ids.data_ptr(), weights.data_ptr(), rows, k, experts, keep, budget, scale,
+                                       nv.stream()), "hb_moe_share")
+        return ids, weights
+    i2, w2 = share_experts_ref(ids, weights, experts, keep, budget, scale)
+    return i2.to(ids.device), w2.to(weights.device)
+
+
 @dataclass
 class ExpertWeights:
     """Stacked expert matrices. fc1: [E * n1, H] rows (n1 = 2I interleaved for SwiGLU, I for ReLU^2); fc2:

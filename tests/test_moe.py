@@ -74,3 +74,39 @@ def test_experts_forward_gpu(fmt, t, e, k, h, inter, act):
     assert torch.equal(again, whole)
     from hibana_b200 import _native as nv
     assert nv.read_status() == 0
+
+
+def _share_case(seed=0, rows=12, e=64, k=6):
+    g = torch.Generator().manual_seed(seed)
+    ids, w = moe.route(torch.randn(rows, e, generator=g) * 2, k, sigmoid=True, scale=2.5)
+    return ids, w
+
+
+def test_expert_sharing_keeps_the_budget_and_the_guaranteed_choices_cpu():
+    ids, w = _share_case()
+    e, k, keep, budget = 64, 6, 2, 30
+    assert len(set(ids.flatten().tolist())) > budget
+    ids2, w2 = moe.share_experts(ids, w, e, keep, budget, scale=2.5)
+    used = {int(ids2[r, j]) for r in range(ids.shape[0]) for j in range(k) if float(w2[r, j]) > 0}
+    core = {int(x) for x in ids[:, :keep].flatten()}
+    assert core <= used and len(used) <= max(budget, len(core))
+    for r in range(ids.shape[0]):
+        assert ids2[r, :keep].tolist() == ids[r, :keep].tolist()            # every row keeps its best choices
+        live = w2[r] > 0
+        assert abs(float(w2[r][live].sum()) - 2.5) < 1e-5                    # renormalised, router scale kept
+        kept = [int(x) for x in ids2[r][live]]
+        assert kept == [int(x) for x in ids[r] if int(x) in kept]            # rank order preserved
+        assert all(int(x) == int(ids[r, 0]) for x in ids2[r][~live])         # lost slots: best expert, weight 0
+    # a budget that covers everything changes nothing but the renormalisation
+    ids3, w3 = moe.share_experts(ids, w, e, keep, 64, scale=2.5)
+    assert torch.equal(ids3, ids) and torch.allclose(w3, w, atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_expert_sharing_kernel_matches_reference():
+    for seed, rows, e, k, keep, budget in ((0, 12, 64, 6, 2, 20), (1, 16, 512, 22, 4, 128), (2, 3, 512, 10, 1, 8)):
+        ids, w = _share_case(seed, rows, e, k)
+        want_i, want_w = moe.share_experts(ids, w, e, keep, budget, scale=1.7)
+        got_i, got_w = moe.share_experts(ids.cuda(), w.cuda(), e, keep, budget, scale=1.7)
+        assert torch.equal(got_i.cpu(), want_i)
+        assert torch.allclose(got_w.cpu(), want_w, atol=1e-6)
