@@ -317,8 +317,17 @@ class MoeLayer:
         del fc1, fc2
         f = init.full or t
         # under tensor parallelism the shared expert is column / row split like a dense MLP (its partial sum joins
-        # the routed experts' partial sum before the one all-reduce of the layer)
-        self.shared = MlpLayer(t, init, name + ".shared", width=f.shared_ffn, act=t.moe_act) if t.shared_ffn else None
+        # the routed experts' partial sum before the one all-reduce of the layer) when a rank's share of its width is
+        # a whole number of 64-feature K tiles; a narrower shared expert (640 wide over 8 ranks) stays whole on
+        # every rank and is added after the all-reduce
+        self.shared_split = init.tp > 1 and (f.shared_ffn // init.tp) % 64 == 0 and f.shared_ffn % init.tp == 0
+        shared_init = init
+        if init.tp > 1 and not self.shared_split:
+            import copy
+            shared_init = copy.copy(init)          # same seeded stream, no sharding
+            shared_init.tp, shared_init.rank = 1, 0
+        self.shared = (MlpLayer(t, shared_init, name + ".shared", width=f.shared_ffn, act=t.moe_act)
+                       if t.shared_ffn else None)
         self.fc1_latent = init.linear(t.latent, t.hidden, "bf16", name + ".fc1_latent") if t.latent else None
         self.fc2_latent = init.linear(t.hidden, t.latent, "bf16", name + ".fc2_latent") if t.latent else None
         self.ep_size = ep_size
@@ -348,7 +357,7 @@ class MoeLayer:
         logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
         ids, w = self._route(logits)
         shared = self.shared.forward(x) if self.shared is not None else None
-        if shared is not None and self.tp > 1 and ctx is not None and ctx.comm is not None:
+        if shared is not None and self.shared_split and ctx is not None and ctx.comm is not None:
             shared = ctx.comm.all_reduce(shared)      # column / row split shared expert beside replicated experts
         if t.latent:
             lat = self.fc1_latent(x)
@@ -371,9 +380,12 @@ def _moe_forward_ep(self, x, comm) -> torch.Tensor:
         # experts' before the layer's one all-reduce; the latent up-projection is linear and moves in front of it
         if t.latent:
             part = self.fc2_latent(part)
-        if self.shared is not None:
+        if self.shared is not None and self.shared_split:
             part = basic.add(part, self.shared.forward(x))
-        return comm.all_reduce(part)
+        out = comm.all_reduce(part)
+        if self.shared is not None and not self.shared_split:
+            out = basic.add(out, self.shared.forward(x))       # whole on every rank: added once, after the sum
+        return out
     part = comm.all_reduce(part)
     out = self.fc2_latent(part) if t.latent else part
     if self.shared is not None:
