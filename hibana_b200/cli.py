@@ -50,6 +50,19 @@ def run_engine(args) -> int:
     from . import config as cfgmod
     cfg = _resolve(args)
     cfgmod.install(cfg)
+    from .launch import preflight
+    host = preflight.check_host(need_gpus=max(cfg.tp * cfg.dp, 1), require_b200=False)
+    for problem in host.problems:
+        print("preflight:", problem, file=sys.stderr)
+    try:
+        weights = preflight.ensure_weights(cfg, fetch=not getattr(args, "no_fetch", False))
+        w3_dir = preflight.ensure_w3(cfg)
+    except preflight.PreflightError as e:
+        raise SystemExit(f"preflight: {e}") from None
+    if weights is not None:
+        cfg = cfg.replace(weights=str(weights))
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(preflight.summary(cfg, host, weights, w3_dir), file=sys.stderr)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
         from .parallel.lockstep import serve_rank

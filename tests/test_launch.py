@@ -101,3 +101,40 @@ def test_cli_parser():
     assert a.cmd == "serve" and a.target == "27b" and a.tp == 2 and a.cuda_graphs is False
     a = build_parser().parse_args(["cache", "--flush"])
     assert a.flush
+
+
+def test_preflight_snapshot_lookup_w3_link_and_summary(tmp_path):
+    import json
+    import torch
+    from hibana_b200.config import EngineConfig
+    from hibana_b200.launch import preflight as pf
+    from hibana_b200.weights import w3_reference as ref
+    from hibana_b200.weights.w3 import CodebookW3
+    snap = tmp_path / "hub" / "models--org--model" / "snapshots" / "abc123"
+    snap.mkdir(parents=True)
+    (snap / "config.json").write_text("{}")
+    (snap / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"a": "m-1.safetensors"}}))
+    assert pf.snapshot_dir(tmp_path, "org/model", "abc123") is None          # a weight file is missing
+    (snap / "m-1.safetensors").write_bytes(b"x")
+    assert pf.snapshot_dir(tmp_path, "org/model", "abc123") == snap
+    cfg = EngineConfig(target="dense-tiny", weights="org/model@abc123")
+    assert pf.ensure_weights(cfg, cache=tmp_path, fetch=False) == snap
+    assert pf.ensure_weights(EngineConfig(target="dense-tiny"), cache=tmp_path) is None
+    with pytest.raises(pf.PreflightError):
+        pf.ensure_weights(cfg.replace(weights="org/other@ffff"), cache=tmp_path, fetch=False)
+    with pytest.raises(pf.PreflightError):
+        pf.ensure_weights(cfg.replace(weights="nowhere"), cache=tmp_path)
+    # calibrated 3-bit copies: the <target>-current link, verified
+    assert pf.ensure_w3(cfg.replace(w3=True), root=tmp_path) is None
+    with pytest.raises(pf.PreflightError):
+        pf.ensure_w3(cfg.replace(w3=True), root=tmp_path, required=True)
+    w = CodebookW3.pack(torch.zeros(128, 128, dtype=torch.int64), torch.ones(128, 4).to(torch.float8_e4m3fn),
+                        torch.ones(128), (-3.5, -2.5, -1.5, -0.5, 0.5, 1.5, 2.5, 3.5))
+    d = ref.write_directory(tmp_path / "calib", {"layers.0.mlp.down": w})
+    (tmp_path / "dense-tiny-current").symlink_to(d)
+    assert pf.ensure_w3(cfg.replace(w3=True), root=tmp_path) == d.resolve()
+    assert pf.ensure_w3(cfg, root=tmp_path) is None                           # w3 off: nothing to look for
+    host = pf.HostReport(gpus=8, names=["NVIDIA B200"] * 8, free_gib=[170.0] * 8)
+    text = pf.summary(cfg.replace(w3=True, tp=8, spec="ngram"), host, snap, d)
+    assert "tp=8" in text and "ngram depth" in text and str(d) in text
+    assert isinstance(pf.meminfo(), dict)

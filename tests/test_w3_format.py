@@ -1,4 +1,5 @@
 """3-bit weight formats: quantisation error, tile packing, codebook planes."""
+import pytest
 import torch
 
 from hibana_b200.ops.w3gemm import W3Linear
@@ -72,3 +73,54 @@ def test_codebook_fit_beats_uniform_levels_and_gptq_beats_rounding():
     # the Hessian-weighted codebook is at least as good on the outputs as the unweighted one
     cbw = cal.fit_codebook(w, hessian_diag=torch.diag(h))
     assert cal.layer_error(w, cbw.dequantize(), x) < cal.layer_error(w, cb.dequantize(), x) * 1.1
+
+
+def test_reference_directory_round_trip_checksums_and_exact_serving(tmp_path):
+    """The reference's on-disk 3-bit format (fragment-ordered bit planes, e4m3 group scales, row scales, manifest
+    with SHA-256): written and read back bit for bit, a flipped byte is caught, tensor-parallel row ranges load, and
+    the served projection equals the dequantised matrix without any re-fit."""
+    import json
+    import torch
+    from hibana_b200.weights.w3 import CodebookW3
+    from hibana_b200.weights import w3_reference as ref
+    g = torch.Generator().manual_seed(0)
+    lloyd = (-3.5, -2.25, -1.25, -0.40625, 0.40625, 1.25, 2.25, 3.5)
+    n, k = 256, 384
+    codes = torch.randint(0, 8, (n, k), generator=g)
+    scales = (torch.rand(n, k // 32, generator=g) * 200 + 1).to(torch.float8_e4m3fn)
+    row_scale = torch.rand(n, generator=g) * 1e-3 + 1e-4
+    w = CodebookW3.pack(codes, scales, row_scale, lloyd)
+    two = CodebookW3.pack(torch.randint(0, 4, (128, 128), generator=g), scales[:128, :4].contiguous(),
+                          row_scale[:128], (-1.5, -0.4375, 0.4375, 1.5))
+    d = ref.write_directory(tmp_path / "ckpt", {"layers.0.mlp.down": w, "draft.head": two}, revision="rev1")
+    planes = ref.encode_planes(codes)
+    assert planes.shape == (n // 32, k // 128, 3, 32, 4) and planes.dtype == torch.uint32
+    # one element by hand: row 32*1 + 8*2 + 5, column 128*2 + 16*6 + 4*3 + 1 -> lane 4*5 + 3, tile 2, bit 4*1 + b + 18
+    r, c = 32 + 16 + 5, 256 + 96 + 12 + 1
+    for b in range(3):
+        word = int(planes[1, 2, b, 23, 2].to(torch.int64)) & 0xFFFFFFFF
+        assert (word >> ((4 + b + 18) % 32)) & 1 == (int(codes[r, c]) >> b) & 1
+    ck = ref.ReferenceW3Checkpoint(d, revision="rev1")
+    assert ck.names() == ["draft.head", "layers.0.mlp.down"]
+    ck.verify()
+    got = ck.load("layers.0.mlp.down")
+    assert torch.equal(got.codes(), w.codes()) and torch.equal(got.scales, w.scales)
+    assert torch.equal(got.row_scale, w.row_scale) and tuple(got.codebook) == lloyd
+    assert torch.equal(ck.load("draft.head").dequantize(), two.dequantize())
+    part = ck.load("layers.0.mlp.down", rows=slice(64, 192))
+    assert torch.equal(part.dequantize(), w.dequantize()[64:192])
+    lin = ref.CodebookLinear(got)
+    x = torch.randn(5, k, generator=g).bfloat16()
+    want = x.float() @ w.dequantize().t()
+    assert (lin(x).float() - want).abs().max() <= 1e-2 * want.abs().max()
+    with pytest.raises(ValueError):
+        ref.ReferenceW3Checkpoint(d, revision="other")
+    f = d / json.loads((d / "manifest.json").read_text())["weights"]["draft.head"]["file"]
+    raw = bytearray(f.read_bytes())
+    raw[-1] ^= 1
+    f.write_bytes(bytes(raw))
+    with pytest.raises(ValueError, match="checksum"):
+        ck.load("draft.head")
+    assert ref.current_checkpoint(tmp_path, "qwen38") is None
+    (tmp_path / "qwen38-current").symlink_to(d)
+    assert ref.current_checkpoint(tmp_path, "qwen38") == d.resolve()
