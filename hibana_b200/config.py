@@ -56,7 +56,7 @@ class EngineConfig:
     ssd_min_gain: int = 2048
     ssd_block_tokens: int = 256
     # speculation
-    spec: str = "off"                      # off | mtp | dflash2 | ngram
+    spec: str = "off"                      # off | mtp | dflash2 | ngram | lilicorr
     spec_depth: int = 3
     spec_depths: str = ""                  # per-bucket depths "1:4,8:3,64:1"
     spec_state: str = "reconstruct"        # snapshots | reconstruct
@@ -106,7 +106,7 @@ class EngineConfig:
             raise ValueError("ep must equal tp or tp * dp (experts are sharded over the same ranks)")
         if self.profile not in ("exact", "fast", "throughput"):
             raise ValueError(f"unknown profile {self.profile!r}")
-        if self.spec not in ("off", "mtp", "dflash2", "ngram"):
+        if self.spec not in ("off", "mtp", "dflash2", "ngram", "lilicorr"):
             raise ValueError(f"unknown spec {self.spec!r}")
         if self.spec_state not in ("snapshots", "reconstruct"):
             raise ValueError(f"unknown spec_state {self.spec_state!r}")

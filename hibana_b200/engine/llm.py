@@ -167,7 +167,7 @@ class LLM:
             self.executor.rebuild_from_ssd()
         if cfg.spec == "mtp" and getattr(self.model, "mtp", None) is not None:
             self.executor.enable_spec(cfg.spec_depth)
-        elif cfg.spec in ("dflash2", "ngram"):       # drafts from a pluggable proposer (proposers/factory.py)
+        elif cfg.spec in ("dflash2", "ngram", "lilicorr"):       # drafts from a pluggable proposer (proposers/factory.py)
             self.executor.enable_spec(cfg.spec_depth, proposer=cfg.spec)
         self.scheduler = Scheduler(self.executor, SchedulerConfig(
             prefill_chunk=cfg.prefill_chunk or self.target.prefill_chunk,

@@ -386,3 +386,41 @@ def test_mtp_round_graphs_on_gpu():
     assert nv.read_status() == 0
     assert [r.output_ids for r in got] == want
     assert ex.spec.draft_graphs.rounds > 0 and ex.spec.stats.emitted >= ex.spec.stats.rounds
+
+
+def test_lilicorr_drafter_conv_correlator_and_engine_exactness_cpu():
+    """LiLiCorr: the two-tap convolution is causal over block positions, the correlator gives a [k, W, W] lattice
+    whose first slot does not depend on a previous choice, and the engine with it as proposer emits plain greedy
+    tokens."""
+    import torch
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.dense import DenseModel
+    from hibana_b200.models.lilicorr import LiLiCorrDrafter, two_tap_conv
+    from hibana_b200.target import dense_tiny, scaled
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(2, 5, 64, generator=g)
+    coeff = torch.randn(2, 5, 2, 4, generator=g) * 0.1
+    base = torch.randn(2, 64, generator=g)
+    y = two_tap_conv(x, coeff, base)
+    x2 = x.clone()
+    x2[:, 3] += 1.0                                              # position 3 reaches positions 3 and 4 only
+    d = (two_tap_conv(x2, coeff, base) - y).abs().amax(-1)
+    assert bool((d[:, :3] == 0).all()) and bool((d[:, 3:] > 0).all())
+    t = scaled(dense_tiny(), weight_format="bf16")
+    model = DenseModel(t, "cpu", seed=0)
+    dr = LiLiCorrDrafter(t.hidden, t.vocab, model.embed, model.lm_head, topk=4, layers=1, heads=4, window=64)
+    hidden = torch.randn(3, 5, t.hidden, generator=g)
+    dr._anchor_feat = torch.randn(3, t.hidden, generator=g)
+    cand, scores = dr.select(hidden, torch.tensor([1, 2, 3]))
+    assert cand.shape == (3, 5, 4) and scores.shape == (3, 5, 4, 4)
+    assert torch.allclose(scores[:, 0, 0], scores[:, 0, 3])      # slot 0: the same row for every "previous choice"
+    assert not torch.allclose(scores[:, 1, 0], scores[:, 1, 3])
+    prompts = [torch.randint(0, t.vocab, (n,), generator=g).tolist() for n in (19, 33)]
+    sp = SamplingParams(max_tokens=12)
+    plain = Executor(model, max_batch=4, max_ctx=128, use_graphs=False).generate_batch(prompts, sp)
+    ex = Executor(model, max_batch=4, max_ctx=128, use_graphs=False)
+    ex.enable_spec(depth=4, proposer="lilicorr")
+    got = ex.generate_batch(prompts, sp)
+    assert [r.output_ids for r in got] == [r.output_ids for r in plain]
+    assert ex.spec.stats.rounds > 0
