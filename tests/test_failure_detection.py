@@ -67,8 +67,10 @@ attempt = int(store.get("attempt"))
 def on_dead(ranks):
     open(os.environ["HB_LOG"], "a").write(f"rank {rank} attempt {attempt}: silent {list(ranks)}\n")
     os._exit(13)
-wd = PeerWatchdog(store, rank, world, interval=0.05, timeout=0.6, on_dead=on_dead).start()
-for step in range(20):            # the "engine steps"
+store.set(f"ready/{rank}/{attempt}", "1")          # a slow import of another rank is not silence: start together
+store.wait([f"ready/{r}/{attempt}" for r in range(world)])
+wd = PeerWatchdog(store, rank, world, interval=0.05, timeout=1.5, on_dead=on_dead).start()
+for step in range(80):            # the "engine steps" (4 s: a silent peer is noticed while they run)
     time.sleep(0.05)
     if attempt == 1 and rank == 1 and step == 3:
         wd.stop()                 # between steps: stops answering but stays alive (Popen.poll cannot see it)
