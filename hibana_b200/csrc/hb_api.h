@@ -164,6 +164,13 @@ int hb_gdn_gates(const void* ba, long long ld, const void* a_log, const void* dt
                  void* beta, void* g, void* stream);
 int hb_moe_share(void* ids, void* weights, int rows, int k, int experts, int keep, int budget, float scale,
                  void* stream);
+int hb_ggml_gemv(int type, const void* w, long long row_bytes, int n, int k, const void* x, long long ldx, int m,
+                 const void* grid, int relu2, void* y, long long ldy, void* stream);
+int hb_ggml_gemv_pairs(int type, const void* w, long long row_bytes, long long expert_bytes, int n, int k,
+                       const void* x, long long ldx, const void* grid, const void* pair_expert, const void* pair_row,
+                       int pairs, int relu2, void* y, long long ldy, void* stream);
+int hb_ggml_dequant(int type, const void* w, long long row_bytes, int row0, int rows, int k, const void* grid,
+                    void* out, void* stream);
 int hb_bounds_enabled();
 int hb_bounds_set(int which, long long value);
 int hb_bounds_read(long long* out);

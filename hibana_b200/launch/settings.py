@@ -21,6 +21,7 @@ TARGET_SETTINGS = {
     "qwen38": {"port": 30001, "max_batch": 64, "prefill_chunk": 2048, "spec": "mtp"},
     "flashnext": {"port": 30004, "max_batch": 128, "prefill_chunk": 4096, "spec": "mtp", "ep": 8, "tp": 8},
     "nemotron": {"port": 30005, "max_batch": 128, "prefill_chunk": 4096, "spec": "mtp", "ep": 8, "tp": 8},
+    "bolt": {"port": 30007, "max_batch": 16, "prefill_chunk": 2048, "spec": "lilicorr", "spec_depth": 4},
     "tiny-hybrid-moe": {"port": 30006, "max_batch": 8, "prefill_chunk": 256, "spec": "mtp", "spec_depth": 2},
     "dense-tiny": {"port": 30006, "max_batch": 8, "prefill_chunk": 512},
 }

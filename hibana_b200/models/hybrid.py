@@ -22,7 +22,7 @@ class Block:
     def __init__(self, t: Target, init: Init, idx: int, mixer_kind: str, ffn_kind: str, counters: dict,
                  ep_rank: int, ep_size: int):
         self.mixer = build_mixer(mixer_kind, t, init, counters, f"l{idx}.mixer")
-        self.ffn = build_ffn(ffn_kind, t, init, f"l{idx}.ffn", ep_rank, ep_size)
+        self.ffn = build_ffn(ffn_kind, t.block(idx), init, f"l{idx}.ffn", ep_rank, ep_size)
         self.mixer_norm = init.ones(t.hidden, t.gemma_norm) if self.mixer is not None else None
         self.ffn_norm = init.ones(t.hidden, t.gemma_norm) if self.ffn is not None else None
 

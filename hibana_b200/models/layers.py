@@ -42,8 +42,13 @@ class Init:
 
     def linear(self, n: int, k: int, fmt: str, name: str = "", rows=None, cols=None) -> Linear:
         """[n, k] projection; `rows` / `cols` (slice or index tensor) keep a tensor-parallel shard that is bitwise a
-        slice of the quantised full matrix."""
+        slice of the quantised full matrix. fmt "q8_0": GGML Q8_0 blocks served in place (models/bolt.py)."""
         w = self.normal(n, k)
+        if fmt == "q8_0":
+            if rows is not None or cols is not None:
+                raise NotImplementedError("GGML-packed projections are not sharded (the family fits one GPU)")
+            from .bolt import GgmlLinear
+            return GgmlLinear.from_weight(w, name=name).to(self.device)
         if rows is None and cols is None:
             return Linear(w, fmt, name=name).to(self.device)
         if isinstance(rows, torch.Tensor):
@@ -70,7 +75,7 @@ class Init:
 
 
 def _fmt(t: Target) -> str:
-    return "nvfp4" if t.weight_format == "nvfp4" else "bf16"
+    return "nvfp4" if t.weight_format == "nvfp4" else "q8_0" if t.weight_format == "ggml" else "bf16"
 
 
 class AttentionLayer:
@@ -429,5 +434,8 @@ def build_ffn(kind: str, t: Target, init: Init, name: str, ep_rank: int = 0, ep_
     if kind == MLP:
         return MlpLayer(t, init, name)
     if kind in (MOE, LATENT_MOE):
+        if t.weight_format == "ggml":
+            from .bolt import BoltMoeLayer
+            return BoltMoeLayer(t, init, name)
         return MoeLayer(t, init, name, ep_rank, ep_size)
     return None

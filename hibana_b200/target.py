@@ -67,8 +67,16 @@ class Target:
     prefill_chunk: int = 2048
     tie_embeddings: bool = False
     vision: tuple = ()               # (image, patch, width, depth, heads, mlp) of the vision encoder; () = text only
+    moe_specs: tuple = ()            # ((block index, experts, expert width), ...): blocks whose MoE differs from the default
     tp_size: int = 1
     tp_rank: int = 0
+
+    def block(self, index: int) -> "Target":
+        """The geometry block `index` is built with (heterogeneous MoE blocks override experts / width)."""
+        for i, experts, width in self.moe_specs:
+            if i == index:
+                return replace(self, experts=experts, expert_ffn=width)
+        return self
 
     # ---- derived
     @property
@@ -216,10 +224,36 @@ def nemotron() -> Target:
                   vision=(448, 16, 1280, 32, 16, 5120))
 
 
+# Bolt: (block index, routed experts, expert width) of its 40 MoE blocks, and the blocks that are attention
+# (architecture facts of the published config; every other block is Mamba-2).
+BOLT_MOE = ((1, 240, 2048), (3, 240, 1536), (5, 240, 2048), (8, 304, 2304), (10, 240, 2304), (12, 240, 2048),
+            (14, 240, 2048), (17, 304, 2304), (19, 304, 2048), (21, 432, 2560), (23, 432, 2304), (26, 240, 2048),
+            (28, 432, 2304), (30, 304, 2560), (32, 304, 2304), (34, 432, 2304), (37, 368, 2304), (39, 368, 2048),
+            (41, 368, 2304), (43, 432, 2560), (45, 368, 2560), (48, 496, 2560), (50, 432, 2560), (52, 240, 2304),
+            (54, 368, 2304), (56, 368, 2560), (59, 304, 2048), (61, 240, 2304), (63, 240, 2304), (65, 240, 2048),
+            (67, 240, 2048), (70, 368, 2048), (72, 368, 2304), (74, 432, 2304), (76, 432, 2560), (79, 496, 2560),
+            (81, 432, 2560), (83, 432, 2560), (85, 496, 2560), (87, 368, 2560))
+BOLT_ATTENTION = (7, 16, 25, 36, 47, 58, 69, 78)
+
+
+def bolt() -> Target:
+    """Bolt-class 74B-A9B: Nemotron geometry with heterogeneous MoE blocks (240 to 496 experts of width 1536 to
+    2560, top-9), weights in GGML blocks (IQ2 experts, Q8_0 elsewhere) served in place. Reference:
+    hibana/model/bolt/config.py:13-41."""
+    moe = {i for i, _, _ in BOLT_MOE}
+    layers = tuple((ATTN, NONE) if i in BOLT_ATTENTION else (NONE, LATENT_MOE) if i in moe else (MAMBA2, NONE)
+                   for i in range(88))
+    return Target(name="bolt", family="bolt", hidden=4096, vocab=131072, layers=layers, q_heads=32, kv_heads=2,
+                  head_dim=128, rotary_frac=0.0, mamba_heads=128, mamba_head_dim=64, mamba_state=128, mamba_groups=8,
+                  conv_width=4, mamba_chunk=128, experts=240, top_k=9, expert_ffn=2048, shared_ffn=5376,
+                  router="sigmoid", router_scale=5.0, moe_act="relu2", latent=1024, weight_format="ggml",
+                  kv_dtype="fp8", norm_eps=1e-5, prefill_chunk=2048, moe_specs=BOLT_MOE)
+
+
 PRESETS = {
     "tiny": tiny_hybrid_moe, "tiny-hybrid-moe": tiny_hybrid_moe, "dense-27b": dense_27b, "27b-dense": dense_27b,
     "dense-tiny": dense_tiny, "qwen38": qwen38_hybrid, "27b": qwen38_hybrid, "flashnext": flashnext,
-    "nemotron": nemotron,
+    "nemotron": nemotron, "bolt": bolt,
 }
 
 
@@ -234,4 +268,5 @@ def scaled(t: Target, *, layers: Optional[int] = None, **overrides) -> Target:
     """A down-scaled copy (same structure, fewer layers / other dims) for tests."""
     if layers is not None:
         overrides["layers"] = t.layers[:layers]
+        overrides.setdefault("moe_specs", tuple(sp for sp in t.moe_specs if sp[0] < layers))
     return replace(t, **overrides)

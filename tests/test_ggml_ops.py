@@ -1,0 +1,125 @@
+"""GGML block formats served in place: the decode-fused kernels against the numpy decoders."""
+import numpy as np
+import pytest
+import torch
+
+from hibana_b200.ops import ggml as ops
+from hibana_b200.weights import ggml as fmt
+
+
+def _grid(entries, seed=1):
+    rng = np.random.default_rng(seed)
+    return torch.from_numpy(rng.choice(np.array([8, 25, 43], dtype=np.uint8), size=(entries, 8)))
+
+
+def _case(name, n, k, dev):
+    grid = None if name == "q8_0" else _grid(256 if name == "iq2_xxs" else 512)
+    raw = ops.random_blocks(name, n, k, seed=3)
+    return ops.PackedLinear(raw.to(dev), name, n, k, grid)
+
+
+@pytest.mark.parametrize("name", ["q8_0", "iq2_xxs", "iq2_xs"])
+def test_packed_linear_reference_path_cpu(name):
+    lin = _case(name, 24, 512, "cpu")
+    w = lin.dequantize().float()
+    grids = {name: lin.grid.numpy()} if lin.grid is not None else None
+    want = torch.from_numpy(fmt.dequantize(lin.raw.numpy().reshape(-1), lin.gtype, (24, 512), grids))
+    assert torch.equal(w, want.to(torch.bfloat16).float())
+    x = torch.randn(3, 512).bfloat16()
+    y = lin(x)
+    assert (y.float() - x.float() @ w.t()).abs().max() <= 2e-2 * (x.float() @ w.t()).abs().max() + 1e-3
+    with pytest.raises(ValueError):
+        ops.PackedLinear(lin.raw, name, 24, 500)                        # rows hold whole blocks
+    if name != "q8_0":
+        with pytest.raises(ValueError):
+            ops.PackedLinear(lin.raw, name, 24, 512, None)              # no lattice table, no decoding
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["q8_0", "iq2_xxs", "iq2_xs"])
+@pytest.mark.parametrize("m", [1, 3, 8, 40])
+def test_packed_linear_kernels_match_decoders(name, m):
+    n, k = 300, 1024
+    cpu = _case(name, n, k, "cpu")
+    gpu = _case(name, n, k, "cuda")
+    w = cpu.dequantize().float()
+    assert torch.equal(gpu.dequantize().float().cpu(), w)                # expansion kernel: bit-equal to numpy
+    x = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).bfloat16()
+    want = x.float() @ w.t()
+    got = gpu(x.cuda()).float().cpu()
+    assert (got - want).abs().max() <= 1.5e-2 * want.abs().max() + 1e-3
+    r2 = gpu(x.cuda(), relu2=True).float().cpu()
+    assert (r2 - torch.relu(want) ** 2).abs().max() <= 3e-2 * (want ** 2).abs().max() + 1e-3
+
+
+@pytest.mark.gpu
+def test_packed_experts_grouped_decode_matches_reference():
+    e, h, inter = 6, 512, 256
+    grid = _grid(256)
+    fc1 = ops.random_blocks("iq2_xxs", e * inter, h, seed=5, scale=0.01)
+    fc2 = ops.random_blocks("q8_0", e * h, inter, seed=6, scale=0.002)
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(5, h, generator=g).bfloat16()
+    ids = torch.stack([torch.randperm(e, generator=g)[:2] for _ in range(5)]).int()
+    wts = torch.rand(5, 2, generator=g)
+    outs = []
+    for dev in ("cpu", "cuda"):
+        ex = ops.PackedExperts(ops.PackedLinear(fc1.to(dev), "iq2_xxs", e * inter, h, grid),
+                               ops.PackedLinear(fc2.to(dev), "q8_0", e * h, inter), e)
+        outs.append(ex.forward(x.to(dev), ids.to(dev), wts.to(dev)).float().cpu())
+    assert (outs[0] - outs[1]).abs().max() <= 3e-2 * outs[0].abs().max() + 1e-3
+
+
+def _small_bolt():
+    from hibana_b200.target import bolt, scaled
+    t = scaled(bolt(), layers=9, hidden=256, vocab=2048, q_heads=4, kv_heads=2, head_dim=64, mamba_heads=8,
+               mamba_head_dim=32, mamba_state=32, mamba_groups=2, mamba_chunk=64, top_k=3, shared_ffn=256, latent=256,
+               max_context=512, prefill_chunk=128, kv_dtype="bf16",
+               moe_specs=((1, 6, 256), (3, 10, 512), (5, 6, 256), (8, 8, 256)))
+    return t
+
+
+def test_bolt_preset_and_heterogeneous_blocks_cpu():
+    """The Bolt preset: 88 blocks (8 attention, 40 MoE with their own expert count / width, the rest Mamba-2); a
+    scaled copy builds with per-block expert geometry in GGML blocks and decodes through the engine."""
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.bolt import BoltMoeLayer, GgmlLinear
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import ATTN, LATENT_MOE, bolt
+    full = bolt()
+    kinds = [f for _, f in full.layers]
+    assert len(full.layers) == 88 and kinds.count(LATENT_MOE) == 40 and sum(m == ATTN for m, _ in full.layers) == 8
+    assert full.block(48).experts == 496 and full.block(3).expert_ffn == 1536 and full.block(0).experts == 240
+    t = _small_bolt()
+    model = HybridModel(t, "cpu", seed=0)
+    ffns = [b.ffn for b in model.blocks if b.ffn is not None]
+    assert all(isinstance(f, BoltMoeLayer) for f in ffns)
+    assert [f.experts.experts for f in ffns] == [6, 10, 6, 8] and ffns[1].experts.inter == 512
+    assert isinstance(model.blocks[0].mixer.in_proj, GgmlLinear) and model.blocks[0].mixer.in_proj.fmt == "q8_0"
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, t.vocab, (n,), generator=g).tolist() for n in (20, 9)]
+    out = Executor(model, max_batch=2, max_ctx=64, use_graphs=False).generate_batch(prompts, SamplingParams(max_tokens=5))
+    assert all(len(r.output_ids) == 5 for r in out)
+    again = Executor(model, max_batch=2, max_ctx=64, use_graphs=False).generate_batch(prompts, SamplingParams(max_tokens=5))
+    assert [r.output_ids for r in again] == [r.output_ids for r in out]
+
+
+@pytest.mark.gpu
+def test_bolt_decodes_on_gpu_with_graphs():
+    from hibana_b200 import _native as nv
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.hybrid import HybridModel
+    t = _small_bolt()
+    model = HybridModel(t, "cuda:0", seed=0)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, t.vocab, (n,), generator=g).tolist() for n in (20, 9)]
+    sp = SamplingParams(max_tokens=8)
+    eager = Executor(model, max_batch=2, max_ctx=64, use_graphs=False).generate_batch(prompts, sp)
+    ex = Executor(model, max_batch=2, max_ctx=64, use_graphs=True)
+    ex.capture_graphs()
+    got = ex.generate_batch(prompts, sp)
+    torch.cuda.synchronize()
+    assert nv.read_status() == 0
+    assert [r.output_ids for r in got] == [r.output_ids for r in eager]
