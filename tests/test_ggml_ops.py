@@ -73,7 +73,7 @@ def test_packed_experts_grouped_decode_matches_reference():
 def _small_bolt():
     from hibana_b200.target import bolt, scaled
     t = scaled(bolt(), layers=9, hidden=256, vocab=2048, q_heads=4, kv_heads=2, head_dim=64, mamba_heads=8,
-               mamba_head_dim=32, mamba_state=32, mamba_groups=2, mamba_chunk=64, top_k=3, shared_ffn=256, latent=256,
+               mamba_head_dim=32, mamba_state=64, mamba_groups=2, mamba_chunk=64, top_k=3, shared_ffn=256, latent=256,
                max_context=512, prefill_chunk=128, kv_dtype="bf16",
                moe_specs=((1, 6, 256), (3, 10, 512), (5, 6, 256), (8, 8, 256)))
     return t
