@@ -370,17 +370,24 @@ __device__ __forceinline__ void epilogue_rows4(const DevParams& p, const float4 
 // publishes this rank's sequence number on every rank's return flag and re-arms the counter.
 // A CTA that wrote nothing (`wrote` false: an expert chunk past the expert's rows) skips the system-wide fence,
 // which costs microseconds over NVLink and would otherwise be paid by every empty chunk of the grid.
+__device__ __forceinline__ void ep_publish_returned(const DevParams& p) {
+  const int seq = *reinterpret_cast<const volatile int*>(p.ep_seq_ptr) + 1;
+  __threadfence_system();
+  for (int r = 0; r < p.world; ++r) {
+    int* f = reinterpret_cast<int*>(p.peer_base[r] + p.ep_ret_flag_offset) + p.rank;
+    asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
+  }
+}
+// With a work list only the CTAs of list slots that exist take part in the count (grid.x of them per slot): the
+// thousands of CTAs beyond the list return without touching the counter, which otherwise serialised them all on
+// one address.
 __device__ __forceinline__ void ep_cta_done(const DevParams& p, bool wrote = true) {
   if (wrote) __threadfence_system();
-  const int total = static_cast<int>(gridDim.x * gridDim.y * gridDim.z);
+  const int total = p.grp_tiles != nullptr ? static_cast<int>(gridDim.x) * *p.grp_ntiles
+                                           : static_cast<int>(gridDim.x * gridDim.y * gridDim.z);
   if (atomicAdd(p.ep_done, 1) == total - 1) {
     *p.ep_done = 0;
-    const int seq = *reinterpret_cast<const volatile int*>(p.ep_seq_ptr) + 1;
-    __threadfence_system();
-    for (int r = 0; r < p.world; ++r) {
-      int* f = reinterpret_cast<int*>(p.peer_base[r] + p.ep_ret_flag_offset) + p.rank;
-      asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
-    }
+    ep_publish_returned(p);
   }
 }
 
@@ -410,7 +417,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
     int e = blockIdx.z, chunk = blockIdx.y;
     if (p.grp_tiles != nullptr) {
       if (static_cast<int>(blockIdx.y) >= *p.grp_ntiles) {   // uniform, before any barrier or TMEM allocation
-        if (p.epilogue == kEpiReturn && threadIdx.x == 0) ep_cta_done(p, false);
+        // an empty list (no rows routed to this rank) still owes every rank its "returned" flag: one CTA says so
+        if (p.epilogue == kEpiReturn && *p.grp_ntiles == 0 && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+          ep_publish_returned(p);
         return;
       }
       const int code = p.grp_tiles[blockIdx.y];

@@ -333,7 +333,15 @@ moe_plan_kernel(const int* __restrict__ ids, int pairs, int topk, int experts, i
 __global__ void moe_tiles_kernel(const int* __restrict__ cnt, int experts, int tile_bn, int* __restrict__ tiles,
                                  int* __restrict__ n_tiles, int tile_cap) {
   extern __shared__ int base[];
-  if (threadIdx.x == 0) {
+  __shared__ int wtot[32];
+  __shared__ int s_total;
+  if (experts <= 1024 && blockDim.x == 1024) {      // one expert per thread: parallel prefix
+    const int mine = static_cast<int>(threadIdx.x) < experts ? (cnt[threadIdx.x] + tile_bn - 1) / tile_bn : 0;
+    const int off = block_excl_scan_1024(mine, wtot, &s_total);
+    if (static_cast<int>(threadIdx.x) < experts) base[threadIdx.x] = off;
+    __syncthreads();
+    if (threadIdx.x == 0) *n_tiles = s_total < tile_cap ? s_total : tile_cap;
+  } else if (threadIdx.x == 0) {
     int acc = 0;
     for (int e = 0; e < experts; ++e) {
       base[e] = acc;
@@ -447,7 +455,7 @@ int hb_moe_plan(const void* ids, int tokens, int topk, int experts, int e_lo, in
 
 int hb_moe_tiles(const void* cnt, int experts, int tile_bn, void* tiles, void* n_tiles, int tile_cap, void* stream) {
   if (experts <= 0 || tile_bn < 16 || tile_cap <= 0) return 1;
-  moe_tiles_kernel<<<1, 256, experts * sizeof(int), ST(stream)>>>(static_cast<const int*>(cnt), experts, tile_bn,
+  moe_tiles_kernel<<<1, 1024, experts * sizeof(int), ST(stream)>>>(static_cast<const int*>(cnt), experts, tile_bn,
                                                                   static_cast<int*>(tiles),
                                                                   static_cast<int*>(n_tiles), tile_cap);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;

@@ -158,7 +158,8 @@ class ExpertParallel:
             bn_full *= 2
         bn_hint = min(bn_hint, bn_full)
         # compact (expert, chunk) work list from the planned row counts: the GEMM grids cover tiles that have rows
-        tile_cap = -(-rows_cap // bn_hint) + self.e_per
+        # at most one partial tile per local expert beside the full ones of every pair that can arrive here
+        tile_cap = -(-(self.world * self.tokens * self.topk) // bn_hint) + self.e_per
         tiles = torch.empty(tile_cap, dtype=torch.int32, device=dev)
         n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
         nv.check(lib.hb_moe_tiles(self.grp_cnt.data_ptr(), self.e_per, bn_hint, tiles.data_ptr(), n_tiles.data_ptr(),

@@ -32,7 +32,13 @@ def main() -> None:
     ap.add_argument("--inter", type=int, default=640)
     ap.add_argument("--tokens", type=int, nargs="*", default=[32, 256, 2048], help="tokens per rank")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--once", action="store_true", help="run the fused call once inside a profiler range, no timing "
+                                                        "(for ncu on one GPU)")
     args = ap.parse_args()
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29598")
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
@@ -67,6 +73,16 @@ def main() -> None:
             dist.all_reduce(v, op=dist.ReduceOp.MAX)
             return float(v.item())
 
+        if args.once:
+            for _ in range(2):
+                ep.forward(x, ids, w, ew)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            ep.forward(x, ids, w, ew)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+            del ep
+            continue
         fused = timed(lambda: ep.forward(x, ids, w, ew))
         nccl = timed(lambda: ep.forward_nccl(x, ids, w, ew))
         pairs = t * k                                    # per rank; on average as many arrive as leave
