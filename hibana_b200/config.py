@@ -32,7 +32,6 @@ class EngineConfig:
     ep: int = 1
     dp: int = 1
     fused_collectives: bool = True         # peer-memory fused kernels; False = NCCL-only baseline path
-    nvls: bool = True                      # use multimem (NVLS) where the multicast object can be created
     comm_timeout_ms: int = 2000            # bound of every device-side wait on a peer
     comm_buffer_mb: int = 64
     control_timeout_s: int = 30            # host control plane: broadcast timeout and peer-heartbeat limit
@@ -91,7 +90,8 @@ class EngineConfig:
     trace_cap_gb: float = 32.0
     debug_sync: bool = False
     bounds: bool = False                   # load the checked-index build of the native library (debugging; slower)
-    ssd_trace: bool = False
+    ssd_trace: bool = False                # one JSON line per SSD restore / backup in <trace_dir or ssd_dir>/ssd_trace.jsonl
+    nvtx: bool = False                     # NVTX ranges around scheduler steps, prefill chunks, decode steps, rounds
     # api
     host: str = "127.0.0.1"
     port: int = 30001

@@ -17,6 +17,7 @@ from ..cache.kv_pool import KvPool
 from ..cache.request_state import StateManager
 from ..target import Target
 from .context import PREFILL
+from ..utils import nvtx
 from .request import Request, SamplingParams, State
 from .runner import ModelRunner
 
@@ -118,7 +119,8 @@ class Executor:
         return True
 
     def enable_ssd_tier(self, directory: str, *, budget_bytes: int = 200 << 30, min_prefix: Optional[int] = None,
-                        min_gain: Optional[int] = None, identity: Optional[dict] = None) -> None:
+                        min_gain: Optional[int] = None, identity: Optional[dict] = None,
+                        trace_path: Optional[str] = None) -> None:
         """Long prefixes are backed up to `directory` when a request is released and when the radix tree evicts
         them, and come back on admission when that gains enough tokens over the GPU cache (cache/ssd.py). With
         tensor parallelism every rank stores its own heads and the ranks agree on how far a restore got."""
@@ -136,6 +138,16 @@ class Executor:
                                min_gain=ssd.MIN_GAIN if min_gain is None else min_gain, agree=agree)
         if self.state.cache is not None:
             self.state.cache.ssd_hook = self.ssd.on_evict     # backup before the KV of an evicted path is freed
+        if trace_path:
+            # one JSON line per restore (how far it got, whether a block was missing): the tier's own event hook
+            import json
+            import time
+            fh = open(trace_path, "a")
+
+            def trace(event: str, **fields):
+                fh.write(json.dumps({"t": time.time(), "event": event, **fields}) + "\n")
+                fh.flush()
+            self.ssd.trace = trace
 
     def rebuild_from_ssd(self) -> dict:
         """Start-up: indexes what an earlier run left in the tier's directory (objects are content-addressed by the
@@ -217,6 +229,7 @@ class Executor:
     def _alloc(self, req: Request, n: int) -> list[int]:
         return self.state.extend(req, n)
 
+    @nvtx.ranged("prefill")
     def prefill_batch(self, chunks: Sequence[tuple[Request, int]]) -> None:
         """Runs `count` more prompt (or replayed) tokens of each request; samples when a prompt completes."""
         rows, toks, starts, slot_lists, finals = [], [], [], [], []
@@ -293,6 +306,7 @@ class Executor:
                     req.push(out[i])
         self.stats["prefill_chunks"] += 1
 
+    @nvtx.ranged("decode")
     def decode_step(self, reqs: Sequence[Request]) -> None:
         """One token for every running request (the pending token goes in, the next one comes out)."""
         if self.spec is not None:     # greedy, relaxed and sampled requests all verify drafts (engine/spec.py)

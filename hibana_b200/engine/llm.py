@@ -163,7 +163,9 @@ class LLM:
         if cfg.ssd_dir:
             self.executor.enable_ssd_tier(cfg.ssd_dir, budget_bytes=int(cfg.ssd_budget_gb * (1 << 30)),
                                           min_prefix=cfg.ssd_min_prefix, min_gain=cfg.ssd_min_gain,
-                                          identity={"weights": cfg.weights, "seed": cfg.seed})
+                                          identity={"weights": cfg.weights, "seed": cfg.seed},
+                                          trace_path=str(Path(cfg.trace_dir or cfg.ssd_dir) / "ssd_trace.jsonl")
+                                          if cfg.ssd_trace else None)
             self.executor.rebuild_from_ssd()
         if cfg.spec == "mtp" and getattr(self.model, "mtp", None) is not None:
             self.executor.enable_spec(cfg.spec_depth)

@@ -14,6 +14,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Optional, Protocol, Sequence
 
+from ..utils import nvtx
 from .request import Request, State
 
 
@@ -101,6 +102,7 @@ class Scheduler:
         return not self.waiting and not self.active
 
     # ---- the step
+    @nvtx.ranged("scheduler_step")
     def step(self) -> list[Request]:
         """Runs one scheduling step; returns the requests that produced tokens or finished in it."""
         t0 = time.perf_counter()

@@ -24,6 +24,7 @@ from typing import Optional, Sequence
 import numpy as np
 import torch
 
+from ..utils import nvtx
 from ..ops import sampling
 from .context import DECODE, VERIFY, ForwardContext
 from .request import MAX_STOPS, Request
@@ -184,6 +185,7 @@ class SpecDecoder:
             self.ex.state_pool.free(slot)
 
     # ---- the round
+    @nvtx.ranged("spec_round")
     def round(self, reqs: Sequence[Request]) -> None:
         ex, dev = self.ex, self.ex.device
         k = self.depth

@@ -177,3 +177,35 @@ def test_llm_generate_matches_executor_loop_cpu():
     assert same >= 0.7 * 30
     assert all(len(r.output_ids) == 6 for r in out)
     llm.executor.state.check()
+
+
+def test_nvtx_ranges_and_ssd_trace_are_switchable(tmp_path):
+    """`nvtx` wraps scheduler steps / prefill / decode in named ranges (recorded even without a GPU), off by default;
+    `ssd_trace` makes the tier write one JSON line per restore."""
+    import json
+    import torch
+    from hibana_b200 import config as cfgmod
+    from hibana_b200.config import EngineConfig
+    from hibana_b200.engine.llm import LLM
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.target import dense_tiny, scaled
+    from hibana_b200.utils import nvtx
+    t = scaled(dense_tiny(), weight_format="bf16")
+    base = EngineConfig(target="dense-tiny", max_batch=2, cuda_graphs=False, max_context=128)
+    prompt = torch.randint(0, t.vocab, (20,), generator=torch.Generator().manual_seed(0)).tolist()
+    del nvtx.OPEN[:]
+    with cfgmod.using(base):
+        LLM(base, target=t, device="cpu").generate([prompt], SamplingParams(max_tokens=3))
+    assert nvtx.OPEN == []
+    on = base.replace(nvtx=True)
+    with cfgmod.using(on):
+        LLM(on, target=t, device="cpu").generate([prompt], SamplingParams(max_tokens=3))
+    assert {"scheduler_step", "prefill", "decode"} <= set(nvtx.OPEN)
+    cfg = base.replace(ssd_dir=str(tmp_path / "ssd"), ssd_trace=True, ssd_min_prefix=256, ssd_min_gain=256,
+                       max_context=1024)
+    with cfgmod.using(cfg):
+        llm = LLM(cfg, target=t, device="cpu")
+        assert llm.executor.ssd.trace is not None
+        llm.executor.ssd.trace("ssd_restore", start=0, end=256, good=256, failed=False)
+    line = json.loads((tmp_path / "ssd" / "ssd_trace.jsonl").read_text().splitlines()[-1])
+    assert line["event"] == "ssd_restore" and line["good"] == 256
