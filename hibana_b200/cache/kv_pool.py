@@ -51,9 +51,20 @@ class KvPool:
             from .. import _native as nv
             nv.lib()
             nv.set_bound(nv.BOUND_KV_SLOTS, slots + 1)          # checked-index build: what a slot id may be
+        # sparse-attention indexer pools (models/qsa.py): raw and compressed 128-wide index keys per slot and
+        # attention layer, allocated by `enable_index` for targets that use the indexer on long contexts
+        self.idx_raw: list = []
+        self.idx_key: list = []
         self._free = list(range(slots, 0, -1))     # pop() hands out ascending ids (contiguous when fresh)
         self._owned = bytearray(slots + 1)
         self._shuffled = False                     # frees since the last sort
+
+    def enable_index(self, layers: int, dim: int = 128) -> None:
+        if not self.idx_raw:
+            self.idx_raw = [torch.zeros(self.slots + 1, dim, dtype=torch.bfloat16, device=self.device)
+                            for _ in range(layers)]
+            self.idx_key = [torch.zeros(self.slots + 1, dim, dtype=torch.bfloat16, device=self.device)
+                            for _ in range(layers)]
 
     @property
     def free_count(self) -> int:

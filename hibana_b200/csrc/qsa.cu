@@ -27,6 +27,7 @@ __global__ void qsa_compress_kernel(const __nv_bfloat16* __restrict__ raw_k, __n
                                     const __nv_bfloat16* __restrict__ norm_w, float eps,
                                     const float* __restrict__ inv_freq, int rot) {
   const int gi = blockIdx.x;
+  if (gi >= grp_indptr[batch]) return;      // the grid may cover a host-side bound of the number of groups
   int b = 0;
   while (b + 1 < batch && grp_indptr[b + 1] <= gi) ++b;
   const int g = grp_first[b] + (gi - grp_indptr[b]);     // group number inside the sequence

@@ -61,6 +61,11 @@ class Executor:
                                   use_graphs=use_graphs, comm=comm, attn_splits=attn_splits, state_pool=state_pool)
         self.comm = comm
         self.runner.debug_sync = debug_sync
+        # sparse-attention indexer: only where a context can outgrow its budget (below that it equals dense attention
+        # and would only add kernels); needs x in bf16 at the attention layers, so the trunk keeps the normed rows
+        if getattr(t, "qsa_ratio", 0) and max_ctx > t.qsa_budget and kv_layers:
+            self.kv.enable_index(kv_layers)
+            self.runner.qsa = True
         self.ssd = None
         self._restores: dict = {}        # rid -> RestoreJob in flight, or None once the question is settled
         self.state = StateManager(self.kv, state_pool, cache=radix_cache, decode_reserve=decode_reserve)

@@ -180,6 +180,7 @@ class ModelRunner:
                 and hasattr(self.model, "greedy_tokens") and hasattr(self.comm, "pick_exchange"))
 
     debug_sync = False      # synchronise and read the status word after every forward (slow; pins a fault to it)
+    qsa = False             # sparse-attention indexer in use (the target has one and contexts can exceed its budget)
     ep = None               # expert-parallel all-to-all handle (parallel/ep.py): MoE layers exchange rows through it
     lockstep = None         # engine/dp.py Lockstep: data-parallel ranks align their forwards through it
     _in_round = False
@@ -207,6 +208,8 @@ class ModelRunner:
     def _forward(self, ids, ctx):
         if self.ep is not None:
             ctx.extras["ep"] = self.ep
+        if self.qsa:
+            ctx.extras["qsa"], ctx.extras["qsa_max_pos"] = True, self.max_ctx
         if self.state_pool is not None:
             h = self.model.forward(ids, ctx, self.kv, self.state_pool)
         else:

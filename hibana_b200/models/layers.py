@@ -95,15 +95,50 @@ class AttentionLayer:
                              cols=init.span(t.q_heads * d) if init.tp > 1 else None)
         # the projection that reads the normed rows (the norm can quantise straight into its format) and whether
         # anything else of the layer still needs them in bf16
-        self.first, self.needs_x = self.qkv, False
+        self.first, self.needs_x = self.qkv, t.qsa_ratio > 0       # the indexer projects the normed rows too
         self.partial = init.tp > 1
         self.q_norm = init.ones(d, t.gemma_norm) if t.qk_norm else None
         self.k_norm = init.ones(d, t.gemma_norm) if t.qk_norm else None
         self.inv_freq = basic.rope_inv_freq(max(t.rot_dim, 2), t.rope_theta, device=init.device)
         self.scale = 1.0 / math.sqrt(d)
+        # sparse-attention indexer (long contexts): 128-wide index queries / keys beside the real ones
+        self.indexer = None
+        if t.qsa_ratio:
+            from .qsa import QD, QsaIndexer
+            self.idx_q = init.linear(t.qsa_heads * QD, t.hidden, "bf16", name + ".idx_q")
+            self.idx_k = init.linear(QD, t.hidden, "bf16", name + ".idx_k")
+            self.indexer = QsaIndexer(t.qsa_ratio, t.qsa_budget, t.qsa_heads, rot=64, eps=t.norm_eps,
+                                      theta=t.rope_theta, device=init.device)
 
     def linears(self):
-        return [self.qkv, self.o]
+        return [self.qkv, self.o] + ([self.idx_q, self.idx_k] if self.indexer is not None else [])
+
+    def _sparse(self, x, q, ctx: ForwardContext, kv) -> torch.Tensor:
+        """Attention through the indexer: every query row attends to the `qsa_budget` best-scoring KV tokens (whole
+        groups of `qsa_ratio`, chosen by its index queries against the groups' compressed index keys) and the tail
+        of its own group. With no more groups than the budget holds the result is dense causal attention."""
+        from .qsa import QD, _rope
+        t, ix, i = self.t, self.indexer, self.kv_index
+        rows = x.shape[0]
+        kv.idx_raw[i].index_copy_(0, ctx.slots.long(), self.idx_k(x))
+        if ctx.q_indptr is None:
+            per_seq = torch.ones_like(ctx.ctx_len)
+            row_seq = ctx.seq_rows if ctx.seq_rows is not None else torch.arange(rows, dtype=torch.int32, device=x.device)
+        else:
+            per_seq = ctx.q_indptr[1:] - ctx.q_indptr[:-1]
+            seqs = ctx.seq_rows if ctx.seq_rows is not None else torch.arange(per_seq.numel(), dtype=torch.int32,
+                                                                              device=x.device)
+            counts = ctx.seq_starts_host if ctx.seq_starts_host is not None else per_seq.tolist()
+            row_seq = torch.repeat_interleave(seqs, torch.as_tensor(counts, device=x.device), output_size=rows)
+        first = torch.div(ctx.ctx_len - per_seq, ix.ratio, rounding_mode="floor").int()
+        count = torch.div(ctx.ctx_len, ix.ratio, rounding_mode="floor").int() - first
+        ix.compress(kv.idx_raw[i], kv.idx_key[i], ctx.kv_indices, ctx.seq_rows, first, count,
+                    max_total=rows // ix.ratio + per_seq.numel())
+        qi = _rope(self.idx_q(x).view(rows, ix.heads, QD), ctx.positions, ix.rot, ix.inv_freq).to(torch.bfloat16)
+        max_pos = int(ctx.extras.get("qsa_max_pos") or ctx.max_ctx_host or ctx.kv_indices.shape[1]) - 1
+        sel, sel_len = ix.select(qi.contiguous(), kv.idx_key[i], ctx.kv_indices, row_seq.int().contiguous(),
+                                 ctx.positions.int().contiguous(), max_pos)
+        return ix.sparse_attention(q, kv.k[i], kv.v[i], sel, sel_len, scale=self.scale, kv_scale=kv.kv_scale)
 
     def forward(self, x, ctx: ForwardContext, kv, states, xq=None) -> torch.Tensor:
         t = self.t
@@ -112,9 +147,13 @@ class AttentionLayer:
         q = basic.rope_kv_write(qkv, ctx.positions, ctx.slots, self.inv_freq, kv.k[i], kv.v[i], t.q_heads,
                                 t.kv_heads, t.head_dim, rot=t.rot_dim, q_norm=self.q_norm, k_norm=self.k_norm,
                                 eps=t.norm_eps, gemma_norm=t.gemma_norm, kv_scale=kv.kv_scale, q_gate=self.gated)
-        att = attention.paged_attention(q, kv.k[i], kv.v[i], ctx.kv_indices, ctx.ctx_len, q_indptr=ctx.q_indptr,
-                                        max_rows=ctx.max_rows, seq_rows=ctx.seq_rows, scale=self.scale,
-                                        kv_scale=kv.kv_scale, splits=ctx.attn_splits, workspace=ctx.attn_workspace)
+        if self.indexer is not None and ctx.extras.get("qsa") and kv.idx_raw:
+            att = self._sparse(x, q, ctx, kv)
+        else:
+            att = attention.paged_attention(q, kv.k[i], kv.v[i], ctx.kv_indices, ctx.ctx_len, q_indptr=ctx.q_indptr,
+                                            max_rows=ctx.max_rows, seq_rows=ctx.seq_rows, scale=self.scale,
+                                            kv_scale=kv.kv_scale, splits=ctx.attn_splits,
+                                            workspace=ctx.attn_workspace)
         att = att.view(att.shape[0], -1)
         if self.gated:
             d = t.head_dim

@@ -72,16 +72,21 @@ class QsaIndexer:
         self.norm_w = torch.zeros(QD, dtype=torch.bfloat16, device=self.device)
 
     def compress(self, raw_k: torch.Tensor, ckey: torch.Tensor, kv_indices: torch.Tensor,
-                 seq_rows: Optional[torch.Tensor], first: torch.Tensor, count: torch.Tensor) -> None:
+                 seq_rows: Optional[torch.Tensor], first: torch.Tensor, count: torch.Tensor,
+                 max_total: Optional[int] = None) -> None:
         """Writes the compressed keys of groups [first[b], first[b] + count[b]) of every sequence b into `ckey`
-        (row = slot of the group's first token). raw_k / ckey: [slots, 128] bf16 pools."""
+        (row = slot of the group's first token). raw_k / ckey: [slots, 128] bf16 pools. `max_total`: an upper bound
+        of sum(count) known on the host; with it the call needs no device-to-host read (CUDA graphs): the grid
+        covers the bound and CTAs beyond the real total return."""
         if not nv.use_native(raw_k):
             compress_ref(raw_k, kv_indices, seq_rows, first, count, self.ratio, self.norm_w, self.eps, self.inv_freq,
                          self.rot, ckey)
             return
         indptr = torch.zeros(first.numel() + 1, dtype=torch.int32, device=raw_k.device)
         indptr[1:] = count.cumsum(0)
-        total = int(indptr[-1])
+        total = int(indptr[-1]) if max_total is None else int(max_total)
+        if total <= 0:
+            return
         nv.check(nv.lib().hb_qsa_compress(raw_k.data_ptr(), ckey.data_ptr(), kv_indices.data_ptr(),
                                           kv_indices.stride(0), nv.ptr(seq_rows), indptr.data_ptr(),
                                           first.data_ptr(), first.numel(), total, self.ratio, self.norm_w.data_ptr(),
@@ -116,7 +121,8 @@ class QsaIndexer:
 
     @staticmethod
     def sparse_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, sel: torch.Tensor,
-                         sel_len: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
+                         sel_len: torch.Tensor, scale: Optional[float] = None, kv_scale: float = 1.0) -> torch.Tensor:
         """Full attention of every query row over its own slot list (each row is its own one-row 'sequence')."""
         return attention.paged_attention(q, k_pool, v_pool, sel, sel_len, causal=False, scale=scale,
+                                         kv_scale=kv_scale,
                                          splits=attention.choose_splits(q.shape[0], k_pool.shape[1], sel.shape[1]))

@@ -67,6 +67,9 @@ class Target:
     prefill_chunk: int = 2048
     tie_embeddings: bool = False
     vision: tuple = ()               # (image, patch, width, depth, heads, mlp) of the vision encoder; () = text only
+    qsa_ratio: int = 0               # > 0: sparse attention indexer (models/qsa.py): tokens per compressed index key
+    qsa_budget: int = 2048           # KV tokens a query row attends to through the indexer (plus its own group's tail)
+    qsa_heads: int = 4               # index query heads (128 wide)
     moe_specs: tuple = ()            # ((block index, experts, expert width), ...): blocks whose MoE differs from the default
     tp_size: int = 1
     tp_rank: int = 0
@@ -206,7 +209,7 @@ def flashnext() -> Target:
                   rope_theta=1e7, rotary_frac=0.25, qk_norm=True, gemma_norm=True, gdn_k_heads=16, gdn_v_heads=48,
                   gdn_head_dim=128, experts=512, top_k=10, expert_ffn=640, shared_ffn=640, router="softmax",
                   mtp_layers=1, mtp_depth=3, weight_format="nvfp4", kv_dtype="fp8", prefill_chunk=4096,
-                  hyper_streams=4, hyper_rank=320)
+                  hyper_streams=4, hyper_rank=320, qsa_ratio=4, qsa_budget=2048, qsa_heads=4)
 
 
 NEMOTRON_PATTERN = "MEMEMEM*EMEMEMEM*EMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEM*EMEMEMEME"

@@ -69,3 +69,72 @@ def test_kernels_match_reference():
         a, b = set(sel[r, :int(ln[r])].tolist()), set(sel_g[r, :int(ln[r])].cpu().tolist())
         agree += len(a & b) / max(len(a), 1)
     assert agree / q.shape[0] > 0.97
+
+
+def test_indexer_in_the_engine_equals_dense_attention_within_its_budget_cpu():
+    """A target with the sparse-attention indexer, served by the engine: while a context has no more groups than the
+    budget holds, every token equals the dense engine's (the indexer keeps everything); with a budget far below
+    the context the engine still decodes, attending to the selected groups only."""
+    import torch
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import ATTN, MLP, Target
+    from dataclasses import replace
+
+    def target(**kw):
+        return Target(name="qsa-tiny", family="hybrid_moe", hidden=256, vocab=2048, layers=((ATTN, MLP),) * 2,
+                      q_heads=4, kv_heads=2, head_dim=64, rope_theta=1e4, ffn=512, max_context=512,
+                      prefill_chunk=64, **kw)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (70, 37)]
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    wide = target(qsa_ratio=4, qsa_budget=128, qsa_heads=2)
+    model = HybridModel(wide, "cpu", seed=0)
+    ex = Executor(model, max_batch=2, max_ctx=160, use_graphs=False)
+    assert ex.runner.qsa and len(ex.kv.idx_raw) == 2
+    sparse = [r.output_ids for r in ex.generate_batch(prompts, sp)]
+    assert float(ex.kv.idx_key[0].abs().sum()) > 0                 # compressed index keys were written
+    dense_ex = Executor(model, max_batch=2, max_ctx=100, use_graphs=False)          # contexts fit the budget: off
+    assert not dense_ex.runner.qsa
+    dense = [r.output_ids for r in dense_ex.generate_batch(prompts, sp)]
+    assert sparse == dense
+    # a budget of 16 tokens against 70-token contexts: really sparse now
+    model.target = replace(wide, qsa_budget=16)
+    for b in model.blocks:
+        b.mixer.t = model.target
+        b.mixer.indexer.budget = 16
+    tight = Executor(model, max_batch=2, max_ctx=160, use_graphs=False)
+    out = tight.generate_batch(prompts, sp)
+    assert all(len(r.output_ids) == 6 for r in out)
+    assert [r.output_ids for r in out] != dense
+
+
+@pytest.mark.gpu
+def test_indexer_in_the_engine_on_gpu_with_graphs():
+    """Same rule on the GPU (index-key compression, scoring, top-k, per-row slot lists inside the captured decode
+    step): within the budget the tokens are the dense engine's; the status word stays clear."""
+    import torch
+    from hibana_b200 import _native as nv
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import ATTN, MLP, Target
+    t = Target(name="qsa-tiny", family="hybrid_moe", hidden=256, vocab=2048, layers=((ATTN, MLP),) * 2, q_heads=4,
+               kv_heads=2, head_dim=128, rope_theta=1e4, ffn=512, max_context=1024, prefill_chunk=128,
+               qsa_ratio=4, qsa_budget=256, qsa_heads=2)
+    model = HybridModel(t, "cuda:0", seed=0)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (150, 61, 200)]
+    sp = SamplingParams(max_tokens=10, ignore_eos=True)
+    dense_ex = Executor(model, max_batch=4, max_ctx=240, use_graphs=True)
+    dense_ex.capture_graphs()
+    assert not dense_ex.runner.qsa
+    dense = [r.output_ids for r in dense_ex.generate_batch(prompts, sp)]
+    ex = Executor(model, max_batch=4, max_ctx=320, use_graphs=True)
+    assert ex.runner.qsa
+    ex.capture_graphs()
+    got = [r.output_ids for r in ex.generate_batch(prompts, sp)]
+    torch.cuda.synchronize()
+    assert nv.read_status() == 0
+    assert got == dense
