@@ -39,10 +39,13 @@ class StateManager:
         have = self.kv.free_count + (self.cache.evictable_size if self.cache is not None else 0)
         return need, have
 
-    def can_admit(self, req) -> bool:
-        """Pure: budgets the uncached suffix plus a decode reserve against free + evictable memory."""
+    def can_admit(self, req, promised: int = 0) -> bool:
+        """Pure: budgets the uncached suffix plus a decode reserve against free + evictable memory, less `promised`
+        slots: what requests admitted earlier have yet to take for the rest of their prompts (without that term a
+        burst of long prompts is admitted together, none can finish its prefill, and retraction and re-admission
+        chase each other)."""
         need, have = self._budget(req)
-        if need > have:
+        if need > have - promised:
             return False
         if self.states is not None:
             spare = self.states.free_count + (self.cache.state_evictable if self.cache is not None else 0)

@@ -95,13 +95,13 @@ class Executor:
         if any(i >= self.target.vocab or (i < 0 and not has_media) for i in req.prompt_ids):
             raise ValueError("token id out of range")
 
-    def can_admit(self, req: Request) -> bool:
+    def can_admit(self, req: Request, promised: int = 0) -> bool:
         """Pure while no SSD tier is on. With one, the first call for a request may start an asynchronous restore
         of its prefix; the request then stays in the queue (this returns False) while reader threads and scatter
         kernels bring the blocks back, and the engine keeps stepping everybody else."""
         if self.ssd is not None and req.cacheable and not self._restore_settled(req):
             return False
-        return bool(self.runner._free_rows) and self.state.can_admit(req)
+        return bool(self.runner._free_rows) and self.state.can_admit(req, promised)
 
     def _restore_settled(self, req: Request) -> bool:
         if req.rid in self._restores and self._restores[req.rid] is None:

@@ -145,6 +145,8 @@ class LLM:
         ep = cfg.ep if cfg.dp > 1 and cfg.ep == cfg.dp else 1
         self.model = model or build_model(full, self.device, cfg.seed, comm, cfg.weights, tp=tp, rank=rank, ep=ep)
         self.target = self.model.target
+        if cfg.w3 and hasattr(self.model, "attach_w3") and model is None:
+            self.model.attach_w3()          # before the pools are sized: the copies take memory too
         if ep > 1:
             self.ep = self._expert_parallel(ep, rank, control)
         mem = plan_memory(cfg, self.target, self.device, max_ctx=max_ctx,

@@ -152,7 +152,9 @@ class Scheduler:
         """FIFO admission: the head of the queue must fit before anything behind it is considered."""
         while self.waiting and len(self.active) < self.cfg.max_batch:
             req = self.waiting[0]
-            if not self.ex.can_admit(req):
+            # KV slots the admitted requests still have to take for the rest of their prompts
+            promised = sum(max(self._remaining_prefill(r), 0) for r in self.active if r.state == State.PREFILL)
+            if not self._can_admit(req, promised):
                 break
             try:
                 self.ex.admit(req)
@@ -161,6 +163,12 @@ class Scheduler:
             self.waiting.popleft()
             self.active.append(req)
             self.metrics.admitted += 1
+
+    def _can_admit(self, req: Request, promised: int) -> bool:
+        try:
+            return self.ex.can_admit(req, promised) if promised and self.active else self.ex.can_admit(req)
+        except TypeError:               # executors of tests that take the request only
+            return self.ex.can_admit(req)
 
     def _remaining_prefill(self, r: Request) -> int:
         total = r.total_len - (1 if r.output_ids else 0)

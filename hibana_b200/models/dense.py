@@ -101,6 +101,15 @@ class DenseModel:
     def linears(self):
         return [lin for layer in self.layers for lin in layer.linears()]
 
+    def attach_w3(self) -> int:
+        """3-bit decode copies of every projection (settings `w3`): decode and verify steps stream 4 bits per weight,
+        prefill keeps the NVFP4 matrices. Returns the bytes the copies add."""
+        added = 0
+        for lin in self.linears():
+            lin.attach_w3()
+            added += lin.w3.nbytes()
+        return added
+
     def weight_bytes(self) -> int:
         n = sum(lin.nbytes() for lin in self.linears()) + self.embed.numel() * 2
         if self.lm_head is not self.embed:
@@ -132,7 +141,7 @@ class DenseModel:
         comm = ctx.comm
         if comm is not None and slot is not None and not lin.calibrating:
             rows = h.shape[0]
-            qs = lin.input_scale if lin.fmt == "nvfp4" else None
+            qs = lin.input_scale if lin.fmt == "nvfp4" and not lin.takes_w3(rows) else None
             y, xq = comm.allreduce_norm(slot, rows, t.hidden, residual=res, weight=norm_w, eps=t.norm_eps,
                                         quant_scale=qs, want_bf16=qs is None)
             return lin(xq if xq is not None else y, epilogue=epilogue, requant=requant)
@@ -206,7 +215,7 @@ class DenseModel:
             # decode-shaped steps hand NVFP4 activations from kernel to kernel: the attention kernel merges its KV
             # splits and quantises for o_proj, the gate/up GEMM requantises for down in its epilogue
             fuse = (cfgmod.current().fuse_epilogues and layer.o.fmt == "nvfp4" and not layer.o.calibrating
-                    and q.shape[0] <= 128 and q.is_cuda)
+                    and q.shape[0] <= 128 and q.is_cuda and not layer.o.takes_w3(q.shape[0]))
             att = attention.paged_attention(q, kv.k[i], kv.v[i], ctx.kv_indices, ctx.ctx_len, q_indptr=ctx.q_indptr,
                                             max_rows=ctx.max_rows, seq_rows=ctx.seq_rows, scale=self.scale,
                                             kv_scale=kv.kv_scale, splits=ctx.attn_splits,

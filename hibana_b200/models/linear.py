@@ -15,6 +15,7 @@ from ..ops import basic, gemm, nvfp4
 from ..ops.nvfp4 import Nvfp4Tensor
 
 Activation = Union[torch.Tensor, Nvfp4Tensor]
+W3_MAX_ROWS = 256        # token rows up to which the 3-bit copy is used (the dequant-fused kernel's tile limit)
 
 
 def interleave_pairs(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -31,6 +32,7 @@ class Linear:
         self.out_features, self.in_features = weight.shape
         self.calibrating = False
         self.seen_amax = 0.0
+        self.w3 = None              # optional 3-bit decode copy (ops/w3gemm.py W3Linear): rows <= W3_MAX_ROWS use it
         if fmt == "bf16":
             self.weight = weight.to(torch.bfloat16).contiguous()
             self.wq = None
@@ -69,7 +71,7 @@ class Linear:
         self = cls.__new__(cls)
         self.fmt, self.name, self.wq, self.weight = "nvfp4", name, wq, None
         self.out_features, self.in_features = wq.rows, wq.k
-        self.calibrating, self.seen_amax = False, 0.0
+        self.calibrating, self.seen_amax, self.w3 = False, 0.0, None
         self.input_scale = input_scale.reshape(1).float()
         self.alpha = (self.input_scale * wq.gscale).reshape(1)
         return self
@@ -88,6 +90,17 @@ class Linear:
             self.input_scale = self.input_scale.to(device)
             self.alpha = self.alpha.to(device)
         return self
+
+    def attach_w3(self) -> None:
+        """Builds the 3-bit decode copy (int3, groups of 64, dequantisation fused into the GEMM) from this layer's
+        served weights. Decode- and verify-sized calls then stream 4 bits per weight; prefill keeps the layer's own
+        format. Reference: hibana/kernels/w3.py `attach_model` (HIBANA_W3_DECODE)."""
+        from ..ops.w3gemm import W3Linear
+        dev = self.weight.device if self.weight is not None else self.wq.q.device
+        self.w3 = W3Linear.from_weight(self.dequantized(), dev, name=self.name + ".w3", keep_codes=dev.type != "cuda")
+
+    def takes_w3(self, rows: int) -> bool:
+        return self.w3 is not None and rows <= W3_MAX_ROWS and not self.calibrating
 
     def nbytes(self) -> int:
         if self.weight is not None:
@@ -112,6 +125,9 @@ class Linear:
                  out: Optional[torch.Tensor] = None, requant: Optional[torch.Tensor] = None):
         """`requant` (the consuming projection's static input scale; SiLU-mul epilogue only): return the result as
         an Nvfp4Tensor, quantised inside the GEMM epilogue where the shape allows it."""
+        if not isinstance(x, Nvfp4Tensor) and self.takes_w3(x.shape[0]):
+            y = self.w3(x, epilogue=epilogue, residual=residual, out=out)
+            return y if requant is None else nvfp4.quantize(y, requant)
         if self.fmt == "bf16":
             y = gemm.linear_bf16(x, self.weight, epilogue=epilogue, residual=residual, out=out)
             return y if requant is None else nvfp4.quantize(y, requant)
@@ -127,6 +143,8 @@ def norm_linear(x: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: 
                 add_residual: bool = True, requant: Optional[torch.Tensor] = None):
     """lin(rmsnorm(x + residual)); `residual` is updated in place with the sum when add_residual."""
     res = residual if add_residual else None
+    if lin.takes_w3(x.shape[0]):       # the 3-bit copy reads bf16 activations
+        return lin(basic.rmsnorm(x, norm_weight, eps, residual=res, gemma=gemma), epilogue=epilogue, requant=requant)
     if lin.fmt == "nvfp4":
         if lin.calibrating:
             y = basic.rmsnorm(x, norm_weight, eps, residual=res, gemma=gemma)

@@ -18,18 +18,26 @@ nv.register("hb_gemm_w3", [P, P, I, I, I, L, P, L, P, Fl, I, I, P, I, P])
 
 
 class W3Linear:
-    def __init__(self, w3: Int3G64, device="cpu", name: str = ""):
+    def __init__(self, w3: Int3G64, device="cpu", name: str = "", keep_codes: bool = True):
+        """`keep_codes=False`: drop the unpacked codes once the kernel's tiles exist (a byte per weight that only the
+        reference path and `dense()` read); such a layer serves rows <= 256 on the GPU only."""
         self.w3, self.name = w3, name
         self.out_features, self.in_features = w3.shape
         self.device = torch.device(device)
         self.tiles = w3.tiles().to(self.device) if self.device.type == "cuda" else None
         self._dense: Optional[torch.Tensor] = None
+        if not keep_codes and self.tiles is not None:
+            self.w3 = None
 
     @classmethod
-    def from_weight(cls, w: torch.Tensor, device="cpu", name: str = "") -> "W3Linear":
-        return cls(Int3G64.quantize(w.cpu()), device, name)
+    def from_weight(cls, w: torch.Tensor, device="cpu", name: str = "", keep_codes: bool = True) -> "W3Linear":
+        """Quantises on the device the weight is on (the big matrices of a 27B model never visit the host)."""
+        src = w if w.is_cuda else w.cpu()
+        return cls(Int3G64.quantize(src), device, name, keep_codes)
 
     def dense(self) -> torch.Tensor:
+        if self._dense is None and self.w3 is None:
+            raise RuntimeError("this 3-bit copy kept only its kernel tiles: it serves decode-sized calls on the GPU")
         if self._dense is None:
             self._dense = self.w3.dequantize().to(torch.bfloat16).to(self.device)
         return self._dense

@@ -136,3 +136,37 @@ def test_stable_numerics_makes_verify_rows_bitwise_equal_to_decode_steps():
     assert torch.equal(stable["steps"], stable["verify"])
     loose = rows_of(False)          # the default plans may differ by rounding; both must stay close to each other
     assert (loose["steps"] - loose["verify"]).abs().max() <= 0.05 * loose["steps"].abs().max()
+
+
+def test_w3_decode_copies_serve_decode_and_leave_prefill_alone_cpu():
+    """Settings `w3`: every projection gets a 3-bit copy that decode-sized calls use; the prefill chunk above the
+    row limit keeps the layer's own weights; generation stays close to the unquantised engine (same first token on
+    a bf16 tiny model) and is deterministic."""
+    import torch
+    from hibana_b200.config import EngineConfig
+    from hibana_b200.engine.llm import LLM
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models import linear
+    from hibana_b200.target import dense_tiny, scaled
+    t = scaled(dense_tiny(), weight_format="bf16")
+    # (no prefix cache: a cached prefix shortens the second prefill below the row limit, which then runs on the
+    # 3-bit copies: which weights serve a row depends on the call's size, by design of the decode-copy mode)
+    cfg = EngineConfig(target="dense-tiny", max_batch=2, cuda_graphs=False, max_context=512, prefill_chunk=512,
+                       radix_cache=False)
+    g = torch.Generator().manual_seed(4)
+    prompt = torch.randint(0, t.vocab, (300,), generator=g).tolist()
+    plain = LLM(cfg, target=t, device="cpu")
+    w3 = LLM(cfg.replace(w3=True), target=t, device="cpu")
+    lins = w3.model.linears()
+    assert all(l.w3 is not None for l in lins) and all(l.w3 is None for l in plain.model.linears())
+    assert lins[0].takes_w3(1) and lins[0].takes_w3(256) and not lins[0].takes_w3(300)
+    x = torch.randn(3, t.hidden, generator=g).bfloat16()
+    big = torch.randn(linear.W3_MAX_ROWS + 4, t.hidden, generator=g).bfloat16()
+    own = plain.model.linears()[0]
+    assert torch.equal(lins[0](big), own(big))                       # prefill-sized: the layer's own weights
+    err = (lins[0](x).float() - own(x).float()).abs().max() / own(x).float().abs().max()
+    assert 0 < err < 0.2                                             # decode-sized: the 3-bit copy (lossy)
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    a = w3.generate([prompt], sp)[0].output_ids
+    b = w3.generate([prompt], sp)[0].output_ids
+    assert a == b and len(a) == 6
