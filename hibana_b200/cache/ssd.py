@@ -15,6 +15,8 @@ Reference: hibana/cache/ssd.py:96-101,131-246,413-643,764-871,946-1250, docs/cac
 """
 from __future__ import annotations
 
+import time
+
 from concurrent.futures import Future, ThreadPoolExecutor
 from typing import Callable, Optional, Sequence
 
@@ -53,6 +55,7 @@ class RestoreJob:
         self.reads: dict[int, tuple[int, Future]] = {}      # block -> (staging buffer, pending read)
         self.good = start                                   # first position not yet scattered
         self.failed = False
+        self.t0 = time.perf_counter()
         self.context: dict = {}                             # owner's bookkeeping (locks, fresh slots)
 
     @property
@@ -75,6 +78,31 @@ class SsdTier:
         self.read_ahead = read_ahead
         self._scattered: list = []       # (CUDA event or None, staging buffer) of scatters still in flight
         self.trace = None                # optional callable(event: str, **fields) (engine/traces.py)
+        # Cost model: a restore pays only when reading a token's KV back is faster than computing it again. On this
+        # class of GPU a prefill chunk runs at tens of thousands of tokens per second while a token of bf16 KV of a
+        # 27B model is 256 KiB, so whether the tier pays depends on the KV format and the disk. Both rates are
+        # measured while serving (exponential averages); `prefill_tok_s` is fed by the executor. 0 = not known yet:
+        # the tier is then used whenever the prefix policy allows it.
+        self.read_gbs = 0.0
+        self.prefill_tok_s = 0.0
+        self.declined = 0
+
+    def note_read(self, nbytes: int, seconds: float) -> None:
+        if seconds > 0 and nbytes > 0:
+            rate = nbytes / seconds / 1e9
+            self.read_gbs = rate if self.read_gbs == 0 else 0.8 * self.read_gbs + 0.2 * rate
+
+    def note_prefill(self, tokens: int, seconds: float) -> None:
+        if seconds > 0 and tokens >= 256:
+            rate = tokens / seconds
+            self.prefill_tok_s = rate if self.prefill_tok_s == 0 else 0.8 * self.prefill_tok_s + 0.2 * rate
+
+    def pays(self, tokens: int) -> bool:
+        """True when bringing `tokens` tokens back from disk is expected to beat prefilling them again."""
+        if self.read_gbs <= 0 or self.prefill_tok_s <= 0 or tokens <= 0:
+            return True
+        restore_s = tokens * self.token_bytes / (self.read_gbs * 1e9)
+        return restore_s < 0.8 * tokens / self.prefill_tok_s
 
     # ---- keys
     def _block_keys(self, tokens: Sequence[int], nblocks: int) -> list[bytes]:
@@ -201,8 +229,12 @@ class SsdTier:
                     self.staging.give(i)
             if job.reads:
                 return False
-        if job.finished and self.trace is not None:
-            self.trace("ssd_restore", start=job.start, end=job.end, good=job.good, failed=job.failed)
+        if job.finished:
+            took = time.perf_counter() - job.t0
+            self.note_read(max(job.good - job.start, 0) * self.token_bytes, took)
+            if self.trace is not None:
+                self.trace("ssd_restore", start=job.start, end=job.end, good=job.good, failed=job.failed,
+                           seconds=round(took, 4), read_gbs=round(self.read_gbs, 2))
         return job.finished
 
     def finish(self, job: RestoreJob) -> int:
@@ -226,6 +258,9 @@ class SsdTier:
     def worth(self, tokens: Sequence[int], have: int) -> int:
         """Tokens a restore would bring back, or 0 when it gains less than `min_gain` over `have` cached ones."""
         n = self.agree(self.match(tokens))
+        if n - have >= self.min_gain and not self.pays(n - have):
+            self.declined += 1
+            return 0
         return n if n - have >= self.min_gain else 0
 
     def restore(self, tokens: Sequence[int], start: int, end: int, slots: Sequence[int]) -> int:
@@ -262,6 +297,9 @@ class SsdTier:
         while n is not None and n.parent is not None:
             tokens[:0], slots[:0] = n.tokens, n.slots
             n = n.parent
+        if not self.pays(len(tokens)):       # nobody would read it back: computing it again is faster
+            self.declined += 1
+            return
         if self.backup(tokens, slots):
             node.on_ssd = True
 
@@ -287,4 +325,5 @@ class SsdTier:
 
     def stats(self) -> dict:
         return {"backed_up_blocks": self.backed_up, "restored_tokens": self.restored_tokens, "skipped": self.skipped,
-                **self.store.stats()}
+                "declined": self.declined, "read_gbs": round(self.read_gbs, 2),
+                "prefill_tok_s": round(self.prefill_tok_s), **self.store.stats()}

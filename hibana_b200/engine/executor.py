@@ -237,6 +237,7 @@ class Executor:
     @nvtx.ranged("prefill")
     def prefill_batch(self, chunks: Sequence[tuple[Request, int]]) -> None:
         """Runs `count` more prompt (or replayed) tokens of each request; samples when a prompt completes."""
+        t_start = time.perf_counter() if self.ssd is not None else 0.0
         rows, toks, starts, slot_lists, finals = [], [], [], [], []
         taken: list[tuple[Request, int]] = []
         for req, count in chunks:
@@ -290,6 +291,8 @@ class Executor:
                                        sampling_rows=_sampling_rows([r for r, _ in chunks]) if any_final else None,
                                        state_slots=[r.state_slot for r, _ in chunks]
                                        if self.state_pool is not None else None)
+        if self.ssd is not None and any_final:       # a synchronised step: feeds the tier's restore-or-recompute model
+            self.ssd.note_prefill(sum(len(x) for x in toks), time.perf_counter() - t_start)
         if self.spec is not None:
             off = 0
             for i, (req, _) in enumerate(chunks):

@@ -129,3 +129,33 @@ def test_kv_copy_kernel_matches_indexing():
     kv.copy_payload(other, pay, to_pool=True)
     torch.cuda.synchronize()
     assert torch.equal(kv.rows(other.tolist()), want)
+
+
+def test_tier_declines_when_recomputing_is_faster(tmp_path):
+    """Restore-or-recompute: with measured rates that make a disk read slower than a prefill of the same tokens the
+    tier neither restores nor backs up at eviction; unknown rates leave the prefix policy alone."""
+    import torch
+    from hibana_b200.cache import ssd, ssd_store
+    from hibana_b200.cache.kv_pool import KvPool
+    kv = KvPool(2, 2048, 2, 64, torch.bfloat16, "cpu")
+    store = ssd_store.SsdStore(str(tmp_path), {"t": 1}, budget_bytes=1 << 30)
+    tier = ssd.SsdTier(store, kv, min_prefix=256, min_gain=256)
+    assert tier.pays(1000)                                   # nothing measured yet
+    tier.note_read(10 << 20, 1.0)                            # 10 MB/s disk ...
+    tier.note_prefill(4096, 0.05)                            # ... against 82k tokens/s of prefill
+    assert not tier.pays(1000)
+    toks = list(range(600))
+    slots = kv.alloc(600)
+    assert tier.backup(toks, slots) > 0                      # explicit backups still work (shutdown persist)
+    store.drain()
+    tier.step()
+    assert tier.match(toks) == 512 and tier.worth(toks, 0) == 0 and tier.declined == 1
+
+    class Node:
+        def __init__(self, tokens, slots):
+            self.tokens, self.slots, self.parent, self.on_ssd = tokens, slots, type("R", (), {"parent": None})(), False
+    other = Node([7] * 600, kv.alloc(600))
+    tier.on_evict(other)
+    assert not other.on_ssd and tier.declined == 2
+    tier.read_gbs, tier.prefill_tok_s = 50.0, 1000.0         # a fast disk against a slow prefill: the tier pays
+    assert tier.pays(1000) and tier.worth(toks, 0) == 512
