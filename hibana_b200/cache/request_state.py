@@ -285,7 +285,7 @@ class StateManager:
             self.states.check()
             held = [r.state_slot for r in self.live.values() if r.state_slot]
             snaps = self.cache.snapshots if self.cache is not None else 0
-            assert len(held) + snaps + self.states.free_count == self.states.slots
+            assert len(held) + snaps + self.states.reserved + self.states.free_count == self.states.slots
 
     def stats(self) -> dict:
         out = {"kv_free": self.kv.free_count, "kv_slots": self.kv.slots, "live_requests": len(self.live)}

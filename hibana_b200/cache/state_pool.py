@@ -26,6 +26,7 @@ class StatePool:
             nv.set_bound(nv.BOUND_STATE_SLOTS, slots + 1)       # checked-index build: what a state slot may be
         self._free = list(range(slots, 0, -1))
         self._owned = bytearray(slots + 1)
+        self.reserved = 0               # slots held for good by engine parts (captured rounds' scratch), not requests
 
     @property
     def free_count(self) -> int:
@@ -42,6 +43,12 @@ class StatePool:
         s = self._free.pop()
         self._owned[s] = 1
         return s
+
+    def reserve(self, n: int) -> list:
+        """Takes `n` slots for the life of the pool (scratch of captured speculative rounds)."""
+        out = [self.alloc() for _ in range(n)]
+        self.reserved += n
+        return out
 
     def free(self, slot: int) -> None:
         if slot <= 0:

@@ -222,7 +222,7 @@ class SpecDecoder:
                 ids = tok if j + 1 < k else None
         # ---- verify
         on_device = (self.draft_graphs is not None and self.proposer is None and self.graphs is not None
-                     and ex.state_pool is None and b <= self.graphs.buckets[-1]
+                     and b <= self.graphs.buckets[-1]
                      and not any(r.grammar is not None for r in reqs)
                      and not any(r.params.greedy and (r.params.accept_top_k > 1 or r.params.accept_margin > 0)
                                  for r in reqs))
@@ -230,12 +230,6 @@ class SpecDecoder:
         tokens = [[r.output_ids[-1]] + host_drafts[i] for i, r in enumerate(reqs)]
         extras = {"want_hidden": True}
         has_state = ex.state_pool is not None
-        if has_state:
-            for r in reqs:
-                if r.rid not in self.scratch:
-                    self.scratch[r.rid] = ex.state_pool.alloc()
-            extras["state_out"] = self._dev([self.scratch[r.rid] for r in reqs], torch.int32)
-            extras["ring"] = []
         relaxed = any(r.params.greedy and (r.params.accept_top_k > 1 or r.params.accept_margin > 0) for r in reqs)
         sampled = any(not r.params.greedy for r in reqs)
         # grammar-constrained requests: the drafted tokens are walked through the grammar on the host, one mask per
@@ -258,8 +252,15 @@ class SpecDecoder:
             stop_lists.append(ids_)
         budgets = [max(r.remaining, 1) for r in reqs]
         slot_lists = [r.kv_slots[nn:nn + k + 1] for r, nn in zip(reqs, n)]
-        if (self.graphs is not None and not (relaxed or bitmask is not None or has_state)
-                and (not sampled or self._laws is None) and b <= self.graphs.buckets[-1]):
+        in_graph = (self.graphs is not None and not (relaxed or bitmask is not None)
+                    and (not sampled or self._laws is None) and b <= self.graphs.buckets[-1])
+        if has_state and not in_graph:
+            for r in reqs:
+                if r.rid not in self.scratch:
+                    self.scratch[r.rid] = ex.state_pool.alloc()
+            extras["state_out"] = self._dev([self.scratch[r.rid] for r in reqs], torch.int32)
+            extras["ring"] = []
+        if in_graph:
             # one upload, one captured verify + accept, one readback (engine/spec_graphs.py)
             srows = None
             if sampled:
@@ -268,7 +269,9 @@ class SpecDecoder:
                          "seed": [r.seed & 0x7FFFFFFFFFFFFFFF for r in reqs], "draws": [r.draws for r in reqs]}
             emitted_h, count_h, acc_h, hidden = self.graphs.run([r.table_row for r in reqs], tokens, n, slot_lists,
                                                                 stop_lists, budgets, srows,
-                                                                drafts_dev=drafts if on_device else None)
+                                                                drafts_dev=drafts if on_device else None,
+                                                                state_slots=[r.state_slot for r in reqs]
+                                                                if has_state else None)
         else:
             target, hidden = ex.runner.forward_rows(
                 [r.table_row for r in reqs], tokens, n, slot_lists, mode=VERIFY,
@@ -292,7 +295,7 @@ class SpecDecoder:
             sel_rows.extend(range(i * (k + 1), i * (k + 1) + c))
             new_indptr.append(new_indptr[-1] + c)
             self.feats[r.rid] = hidden[i * (k + 1) + c - 1].clone()
-        if has_state:
+        if has_state and not in_graph:              # (a captured round replayed the accepted rows itself)
             sel = self._dev(sel_rows, torch.int64)
             ip = self._dev(new_indptr, torch.int32)
             slots = self._dev([r.state_slot for r in reqs], torch.int32)

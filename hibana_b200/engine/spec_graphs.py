@@ -15,8 +15,11 @@ The verified hidden states stay on the device for the drafter (MTP feature of th
 requests of a bucket point at block-table row 0 / KV slot 0, as in the decode graphs. On a CPU device the same
 body runs eagerly over the same static buffers, which is what the CPU tests compare with the host round.
 Covers greedy and sampled requests (the rejection-sampling rule against the deterministic drafts is one kernel
-after the head, ops/sampling.py `spec_targets`; greedy requests keep their argmax) of unconstrained requests on
-models without recurrent state; relaxed-greedy acceptance, grammar masks and recurrent replay take the eager round. Reference: hibana/engine/spec_graphs.py:43-164
+after the head, ops/sampling.py `spec_targets`; greedy requests keep their argmax) of unconstrained requests, on
+models with recurrent layers too: the verify forward writes its end state to a scratch slot per request row and
+logs every recurrent layer's inputs, and after the accept kernel the same graph replays the accepted rows into the
+requests' own state slots, the row selection and row pointers derived from the device-side counts. Relaxed-greedy
+acceptance and grammar masks take the eager round. Reference: hibana/engine/spec_graphs.py:43-164
 (VerifyGraphs), hibana/engine/accept_graphs.py:50-310 (AcceptGraphs), hibana/proposers/mtp_graphs.py:15 (DraftGraphs).
 """
 from __future__ import annotations
@@ -33,8 +36,9 @@ from .request import MAX_STOPS
 
 T_IDS, T_POS, T_SLOT, T_ROW, T_FIELDS = 0, 1, 2, 3, 4          # token-level rows
 # request-level rows: table row, context length, token budget, sampling parameters (seed and draw counter are
-# 64-bit: two rows each, on an even row so that the pair is 8-byte aligned for every bucket), then the stop ids
-S_ROW, S_CTX, S_BUDGET, S_TOPK, S_SEED, S_DRAWS, S_TEMP, S_TOPP, S_SOFT, S_STOP0 = 0, 1, 2, 3, 4, 6, 8, 9, 10, 11
+# 64-bit: two rows each, on an even row so that the pair is 8-byte aligned for every bucket), the request's
+# recurrent-state slot, then the stop ids
+S_ROW, S_CTX, S_BUDGET, S_TOPK, S_SEED, S_DRAWS, S_TEMP, S_TOPP, S_SOFT, S_STATE, S_STOP0 = 0, 1, 2, 3, 4, 6, 8, 9, 10, 11, 12
 
 
 class VerifyBuffers:
@@ -57,6 +61,7 @@ class VerifyBuffers:
         self.graph = None
         self.workspace = None
         self.splits = 1
+        self.scratch: Optional[torch.Tensor] = None     # recurrent models: one scratch state slot per request row
 
 
 class VerifyGraphs:
@@ -68,9 +73,14 @@ class VerifyGraphs:
         self.bufs = {b: VerifyBuffers(b, self.k1, self.device) for b in self.buckets}
         self.launches: dict = {}
         self.rounds = 0
+        self._scratch: Optional[torch.Tensor] = None
 
     def supported(self) -> bool:
-        return self.runner.state_pool is None
+        """Attention-only models always; recurrent models when the state pool can spare one scratch slot per row
+        of the largest bucket (the verify forward writes the state after its k + 1 rows there, the accepted prefix
+        is then replayed into the request's own slot inside the same graph)."""
+        pool = self.runner.state_pool
+        return pool is None or pool.free_count > 2 * max(self.buckets)
 
     # ---- the captured body
     def _body(self, buf: VerifyBuffers) -> None:
@@ -78,10 +88,13 @@ class VerifyGraphs:
         b, k1 = buf.bucket, buf.k1
         tok, seq = buf.tok, buf.seq
         r.block_table.index_put_((tok[T_ROW].long(), tok[T_POS].long()), tok[T_SLOT])
+        extras = {"want_hidden": True}
+        if buf.scratch is not None:
+            extras["state_out"], extras["ring"] = buf.scratch, []
         ctx = ForwardContext(VERIFY, positions=tok[T_POS], slots=tok[T_SLOT], kv_indices=r.block_table,
                              ctx_len=seq[S_CTX], q_indptr=buf.indptr, seq_rows=seq[S_ROW], max_rows=k1, batch=b,
                              attn_splits=buf.splits, attn_workspace=buf.workspace, comm=r.comm,
-                             seq_starts_host=[k1] * b, state_slots=seq[S_ROW], extras={"want_hidden": True})
+                             seq_starts_host=[k1] * b, state_slots=seq[S_STATE], extras=extras)
         h = r._forward(tok[T_IDS].long(), ctx)
         buf.hidden = ctx.extras.get("hidden")
         logits = self.model.logits(h, r.comm) if r.comm is not None else self.model.logits(h)
@@ -97,9 +110,30 @@ class VerifyGraphs:
         buf.meta[:, :k1].copy_(emitted)
         buf.meta[:, k1].copy_(count)
         buf.meta[:, k1 + 1].copy_(accepted)
+        if buf.scratch is not None:
+            # commit the recurrent state of the accepted prefix without asking the host how long it is: the rows a
+            # request keeps are its first count[i]; a scatter packs them to the front in request order, the row
+            # pointers are the running sum of the counts, and every recurrent layer replays its logged inputs over
+            # exactly those rows into the request's own state slot
+            cnt = count.to(torch.int32)
+            ip = torch.zeros(b + 1, dtype=torch.int32, device=cnt.device)
+            ip[1:] = torch.cumsum(cnt, 0)
+            j = torch.arange(k1, device=cnt.device)[None, :]
+            dest = torch.where(j < cnt[:, None], ip[:-1, None] + j, b * k1).reshape(-1).long()
+            sel = torch.zeros(b * k1 + 1, dtype=torch.int64, device=cnt.device)
+            sel.scatter_(0, dest, torch.arange(b * k1, device=cnt.device))      # dropped rows land in the spare cell
+            sel = sel[:b * k1]
+            for layer, saved in extras["ring"]:
+                layer.replay(saved, sel, ip, seq[S_STATE], r.state_pool)
 
     def _prepare(self, buf: VerifyBuffers) -> None:
         t = self.model.target
+        pool = self.runner.state_pool
+        if pool is not None and buf.scratch is None:
+            if self._scratch is None:                       # one set of scratch slots, shared by every bucket
+                self._scratch = torch.tensor(pool.reserve(max(self.buckets)), dtype=torch.int32,
+                                             device=self.device)
+            buf.scratch = self._scratch[:buf.bucket]
         if buf.workspace is None and t.attn_layers and self.device.type == "cuda":
             buf.splits = self.runner.attn_splits or attention.choose_splits(buf.bucket, t.kv_heads, self.runner.max_ctx,
                                                                             row_chunks=1)
@@ -138,7 +172,8 @@ class VerifyGraphs:
 
     def run(self, rows: Sequence[int], tokens: Sequence[Sequence[int]], starts: Sequence[int],
             slot_lists: Sequence[Sequence[int]], stop_lists: Sequence[Sequence[int]], budgets: Sequence[int],
-            sampling_rows: Optional[dict] = None, drafts_dev: Optional[torch.Tensor] = None):
+            sampling_rows: Optional[dict] = None, drafts_dev: Optional[torch.Tensor] = None,
+            state_slots: Optional[Sequence[int]] = None):
         """rows[i]: block-table row; tokens[i]: [pending, d_1 .. d_k]; starts[i]: position of the pending token;
         slot_lists[i]: the k + 1 reserved KV slots; sampling_rows: per-request lists temp / top_k / top_p / seed /
         draws / soft (all greedy when None); drafts_dev: int64 [n, k] drafts still on the device (tokens[i] then
@@ -168,6 +203,8 @@ class VerifyGraphs:
         sn[S_ROW, :n] = rows
         sn[S_CTX, :n] = st + k1
         sn[S_BUDGET, :n] = budgets
+        if state_slots is not None:                         # padded requests keep the dummy slot 0
+            sn[S_STATE, :n] = state_slots
         for i, ids in enumerate(stop_lists):
             ids = list(ids)[:MAX_STOPS]
             sn[S_STOP0:S_STOP0 + len(ids), i] = ids
@@ -186,6 +223,7 @@ class VerifyGraphs:
         if buf.graph is not None:
             buf.graph.replay()
         else:
+            self._prepare(buf)
             self._body(buf)
         buf.meta_host.copy_(buf.meta, non_blocking=True)
         self.runner._queue_status_read()

@@ -49,6 +49,33 @@ def test_mtp_speculation_equals_plain_greedy_cpu():
     assert ex.kv.free_count == ex.kv.slots
 
 
+def test_captured_rounds_replay_recurrent_state_cpu():
+    """A model with recurrent layers takes the captured-round form too: the verify body writes its end state to
+    scratch slots, logs the recurrent inputs, and replays the accepted rows from the device-side counts. Tokens,
+    tokens per round and finish reasons equal the host round's; the MTP chain runs as its drafting body; the
+    scratch slots are accounted for in the pool's ledger."""
+    from hibana_b200 import config as cfgmod
+    t = tiny_hybrid_moe()
+    m = HybridModel(t, "cpu", seed=0)
+    prompts = _workload(t, n=3, seed=5)
+    params = [SamplingParams(max_tokens=18), SamplingParams(max_tokens=9),
+              SamplingParams(max_tokens=14, temperature=0.8, top_p=0.9, seed=7)]
+    outs = {}
+    for on in (False, True):
+        with cfgmod.using(device_accept=on):
+            ex = Executor(m, max_batch=4, max_ctx=160, use_graphs=False, radix_cache=False, buckets=(1, 4))
+            ex.enable_spec(2)
+            res = ex.generate_batch(prompts, params)
+            ex.state.check()
+            outs[on] = ([r.output_ids for r in res], [r.rounds for r in res], [r.finish_reason for r in res])
+            if on:
+                assert ex.spec.graphs.rounds > 0 and ex.spec.draft_graphs.rounds == ex.spec.graphs.rounds
+                assert ex.state_pool.reserved == 4 and not ex.spec.scratch
+    assert outs[True] == outs[False]
+    ref = Executor(m, max_batch=4, max_ctx=160, use_graphs=False, radix_cache=False).generate_batch(prompts, params[:2])
+    assert outs[True][0][:2] == [r.output_ids for r in ref]
+
+
 def test_batched_speculation_with_stop_and_budget_cpu():
     t = tiny_hybrid_moe()
     m = HybridModel(t, "cpu", seed=1)
@@ -111,6 +138,18 @@ def test_tiny_hybrid_gpu_matches_cpu_and_graphs():
     agree = sum(a == b for x, y in zip(spec, eager) for a, b in zip(x, y))
     assert [s[0] for s in spec] == [e[0] for e in eager] and agree >= 0.7 * 64
     from hibana_b200 import _native as nv
+    assert nv.read_status() == 0
+    # the same rounds as CUDA graphs: MTP chain graph, then verify + accept + recurrent replay in one graph
+    ex3 = Executor(gpu, max_batch=4, max_ctx=160, use_graphs=True, buckets=(1, 4))
+    ex3.enable_spec(2)
+    ex3.capture_graphs()
+    assert all(b.graph is not None for b in ex3.spec.graphs.bufs.values())
+    assert _run(ex3, prompts, n=16) == spec
+    assert ex3.spec.graphs.rounds > 0 and ex3.spec.draft_graphs.rounds == ex3.spec.graphs.rounds
+    batch = ex3.generate_batch(prompts[:3], SamplingParams(max_tokens=12))
+    ex3.state.check()
+    assert [r.output_ids[0] for r in batch] == [s[0] for s in spec[:3]]
+    torch.cuda.synchronize()
     assert nv.read_status() == 0
 
 
