@@ -70,6 +70,8 @@ class EngineConfig:
     w3: bool = False
     stable_numerics: bool = False
     attn_splits: int = 0                   # 0 = automatic
+    gemv: bool = False                     # small NVFP4 projections of up to 4 rows take the register-decode GEMV
+                                           # (ops/gemv.py); measured slower than the tcgen05 GEMM inside the 27B step
     fuse_epilogues: bool = True            # requantise / merge inside the producing kernel (decode shapes)
     fuse_attn_tail: bool = False           # decode attention merges its KV splits in its last-arriving CTA (measured
                                            # slower than the merge kernel at batch 64: off; the merge kernel then

@@ -201,6 +201,8 @@ class DenseModel:
                 and ctx.comm.sp_ok(ids.shape[0], t.hidden) and not self.layers[0].qkv.calibrating):
             return self.forward_sp(ids, ctx, kv)
         res = basic.embedding(ids, self.embed)
+        if ctx.comm is None and self.layers[0].qkv.takes_gemv(ids.shape[0]) and self.layers[0].o.w3 is None:
+            return self._forward_few_rows(res, ctx, kv)
         h: Optional[torch.Tensor] = None
         slot = None
         if ctx.comm is not None and hasattr(ctx.comm, "begin_forward"):
@@ -240,6 +242,35 @@ class DenseModel:
         if comm is not None:
             h = comm.all_reduce(h)
         return basic.rmsnorm(h, self.final_norm, t.norm_eps, residual=res)
+
+    def _forward_few_rows(self, res: torch.Tensor, ctx: ForwardContext, kv) -> torch.Tensor:
+        """Up to four rows on one GPU. The projections small enough for it (qkv and o at the 27B geometry) run the
+        weight-streaming GEMV (ops/gemv.py) on bf16 activations, with the input norm in the qkv GEMV's prologue;
+        every projection back into the hidden size adds its result to the residual stream in its own epilogue, in
+        place, so no kernel of the layer exists only to add or normalise."""
+        t = self.target
+        rows = res.shape[0]
+        for i, layer in enumerate(self.layers):
+            qkv = norm_linear(res, None, layer.input_norm, t.norm_eps, layer.qkv, add_residual=False)
+            q = basic.rope_kv_write(qkv, ctx.positions, ctx.slots, self.inv_freq, kv.k[i], kv.v[i], t.q_heads,
+                                    t.kv_heads, t.head_dim, rot=t.rot_dim, kv_scale=kv.kv_scale)
+            o_gemv = layer.o.takes_gemv(rows)
+            att = attention.paged_attention(q, kv.k[i], kv.v[i], ctx.kv_indices, ctx.ctx_len, q_indptr=ctx.q_indptr,
+                                            max_rows=ctx.max_rows, seq_rows=ctx.seq_rows, scale=self.scale,
+                                            kv_scale=kv.kv_scale, splits=ctx.attn_splits,
+                                            workspace=ctx.attn_workspace,
+                                            quant_scale=None if o_gemv else layer.o.input_scale)
+            layer.o(att if isinstance(att, nvfp4.Nvfp4Tensor) else att.view(rows, -1), epilogue=gemm.EPI_RESIDUAL,
+                    residual=res, out=res)
+            down_gemv = layer.down.takes_gemv(rows)
+            act = norm_linear(res, None, layer.post_norm, t.norm_eps, layer.gate_up, epilogue=gemm.EPI_SILU_MUL,
+                              add_residual=False, requant=None if down_gemv else layer.down.input_scale)
+            layer.down(act, epilogue=gemm.EPI_RESIDUAL, residual=res, out=res)
+        if ctx.extras.get("want_hidden") is not None:
+            ctx.extras["hidden"] = res
+        if ctx.sample_rows is not None:
+            res = res.index_select(0, ctx.sample_rows)
+        return basic.rmsnorm(res, self.final_norm, t.norm_eps)
 
     def greedy_tokens(self, normed: torch.Tensor, comm=None) -> torch.Tensor:
         """Greedy token of every row without materialising the full logits on any rank: with a vocab-parallel head

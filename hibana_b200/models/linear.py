@@ -11,10 +11,15 @@ from typing import Optional, Union
 
 import torch
 
-from ..ops import basic, gemm, nvfp4
+from .. import config as cfgmod
+from ..ops import basic, gemm, gemv, nvfp4
 from ..ops.nvfp4 import Nvfp4Tensor
 
 Activation = Union[torch.Tensor, Nvfp4Tensor]
+# The GEMV decodes weights in registers, which costs ~3 issue slots per weight: above a few tens of MB the tcgen05
+# GEMM streams faster (4.8 vs 2.9 TB/s at 100 MB), below it the GEMM's fixed cost dominates (15 vs 10 us at 20 MB).
+GEMV_MAX_WEIGHTS = 48 * 1024 * 1024
+GEMV_MAX_ROWS = 4
 W3_MAX_ROWS = 256        # token rows up to which the 3-bit copy is used (the dequant-fused kernel's tile limit)
 
 
@@ -102,6 +107,17 @@ class Linear:
     def takes_w3(self, rows: int) -> bool:
         return self.w3 is not None and rows <= W3_MAX_ROWS and not self.calibrating
 
+    def takes_gemv(self, rows: int) -> bool:
+        """Up to eight bf16 rows against NVFP4 weights stream through the GEMV (ops/gemv.py): no activation
+        quantisation, no tensor-memory or cluster state per launch. Off under `stable_numerics` (its results differ
+        in the last bits from the GEMM's, so a request's tokens would depend on how many rows ran beside it)."""
+        if self.fmt != "nvfp4" or self.calibrating or not self.wq.q.is_cuda:
+            return False
+        c = cfgmod.current()
+        if not c.gemv or c.stable_numerics or self.out_features * self.in_features > GEMV_MAX_WEIGHTS:
+            return False
+        return 1 <= rows <= min(GEMV_MAX_ROWS, gemv.max_rows(self.out_features, self.in_features))
+
     def nbytes(self) -> int:
         if self.weight is not None:
             return self.weight.numel() * 2
@@ -131,6 +147,10 @@ class Linear:
         if self.fmt == "bf16":
             y = gemm.linear_bf16(x, self.weight, epilogue=epilogue, residual=residual, out=out)
             return y if requant is None else nvfp4.quantize(y, requant)
+        if (not isinstance(x, Nvfp4Tensor) and epilogue in (gemm.EPI_STORE, gemm.EPI_RESIDUAL, gemm.EPI_SILU_MUL)
+                and self.takes_gemv(x.shape[0])):
+            y = gemv.nvfp4_gemv(x, self.wq, epilogue=epilogue, residual=residual, out=out)
+            return y if requant is None else nvfp4.quantize(y, requant)
         xq = x if isinstance(x, Nvfp4Tensor) else self.quantize_input(x)
         if requant is not None and epilogue == gemm.EPI_SILU_MUL:
             return gemm.linear_nvfp4_silu_quant(xq, self.wq, self.alpha, requant)
@@ -145,6 +165,12 @@ def norm_linear(x: torch.Tensor, residual: Optional[torch.Tensor], norm_weight: 
     res = residual if add_residual else None
     if lin.takes_w3(x.shape[0]):       # the 3-bit copy reads bf16 activations
         return lin(basic.rmsnorm(x, norm_weight, eps, residual=res, gemma=gemma), epilogue=epilogue, requant=requant)
+    if lin.takes_gemv(x.shape[0]) and epilogue in (gemm.EPI_STORE, gemm.EPI_SILU_MUL):
+        if res is not None:            # the sum has to land in the residual before any CTA normalises it
+            y = lin(basic.rmsnorm(x, norm_weight, eps, residual=res, gemma=gemma), epilogue=epilogue)
+        else:                          # the norm runs in the GEMV's prologue
+            y = gemv.nvfp4_gemv(x, lin.wq, norm_weight=norm_weight, eps=eps, gemma=gemma, epilogue=epilogue)
+        return y if requant is None else nvfp4.quantize(y, requant)
     if lin.fmt == "nvfp4":
         if lin.calibrating:
             y = basic.rmsnorm(x, norm_weight, eps, residual=res, gemma=gemma)

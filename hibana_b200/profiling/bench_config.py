@@ -57,7 +57,8 @@ def main() -> None:
     dp = world if args.mode == "dpep" and world > 1 else 1
     per_rank = args.batch // dp
     assert per_rank >= 1 and per_rank * dp == args.batch, "the global batch must divide over the replicas"
-    max_ctx = args.prompt + args.warmup + 2 * args.steps + 64
+    per_round = 1 if args.spec == "off" else max(t.mtp_depth, 3) + 1      # tokens a round can append
+    max_ctx = args.prompt + per_round * (max(args.warmup, 3) + 2 * args.steps) + 64
     cfg = EngineConfig(target=args.family, max_batch=per_rank, max_context=max_ctx, tp=world if dp == 1 else 1, dp=dp,
                        ep=dp if dp > 1 else 1, graph_buckets=f"1,{per_rank}", kv_pages=per_rank * max_ctx + 4096,
                        state_slots=3 * per_rank + 2, spec=args.spec, kv_dtype=args.kv_dtype,
@@ -114,6 +115,7 @@ def main() -> None:
         raise SystemExit(f"device status {status} after warm-up; not timing a failing run")
     steps = args.steps
     sync_all()
+    emitted0 = sum(len(r.output_ids) for r in reqs)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     w0 = time.perf_counter()
     e0.record()
@@ -123,7 +125,8 @@ def main() -> None:
     sync_all()
     wall = (time.perf_counter() - w0) * 1e3 / steps
     e2e_ms = max_over_ranks(max(e0.elapsed_time(e1) / steps, wall))
-    tokens_per_step = sum(len(r.output_ids) for r in reqs) / max(len(reqs), 1)
+    emitted = sum(len(r.output_ids) for r in reqs) - emitted0        # tokens of the timed rounds (this rank)
+    per_round_tokens = emitted / max(len(reqs) * steps, 1)
     dev_ms = None
     if args.spec == "off":
         buf = ex.runner.bufs[ex.runner._bucket(per_rank)]
@@ -143,7 +146,9 @@ def main() -> None:
         pre = sorted(pre_ms)[len(pre_ms) // 2]
         out = {"family": args.family, "mode": args.mode if world > 1 else "single", "n_gpus": world,
                "layers": len(t.layers), "valid": not args.layers, "global_batch": args.batch, "prompt": args.prompt,
-               "ms_per_step_e2e": round(e2e_ms, 3), "tok_s_e2e": round(args.batch / e2e_ms * 1e3, 1),
+               "ms_per_step_e2e": round(e2e_ms, 3),
+               "tok_s_e2e": round(args.batch * per_round_tokens / e2e_ms * 1e3, 1),
+               "tok_s_per_user_e2e": round(per_round_tokens / e2e_ms * 1e3, 1),
                "prefill_ms_per_chunk": round(pre, 2), "prefill_chunk": chunk, "build_s": round(build_s, 1),
                "launches_per_step": ex.runner.graph_launches.get(per_rank, 0), "device_status": status,
                "peak_alloc_gib": round(mem, 1), "spec": args.spec,
@@ -152,9 +157,9 @@ def main() -> None:
             out.update({"ms_per_step": round(dev_ms, 3), "tok_s": round(args.batch / dev_ms * 1e3, 1),
                         "tok_s_per_user": round(1e3 / dev_ms, 1)})
         if args.spec != "off":
-            st = getattr(ex.spec, "stats", None)
-            out["spec_stats"] = dict(st) if isinstance(st, dict) else None
-            out["generated_per_request"] = round(tokens_per_step, 1)
+            out["spec_stats"] = ex.spec.stats.as_dict()
+            out["tokens_per_round"] = round(per_round_tokens, 3)
+            out["rounds_as_graphs"] = ex.spec.graphs.rounds if ex.spec.graphs is not None else 0
         if llm.lockstep is not None:
             out["lockstep_rounds"] = llm.lockstep.rounds
         print(json.dumps(out), flush=True)

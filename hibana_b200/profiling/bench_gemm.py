@@ -1,4 +1,7 @@
-"""GEMM micro-benchmark: python -m hibana_b200.profiling.bench_gemm [--kind nvfp4|bf16] [--shapes m,n,k ...]
+"""GEMM micro-benchmark: python -m hibana_b200.profiling.bench_gemm [--kind nvfp4|bf16|gemv] [--shapes m,n,k ...]
+
+`--kind gemv` times the few-row NVFP4 GEMV (ops/gemv.py; `--epi norm` adds its RMSNorm prologue, `--epi silu` the
+SiLU-mul epilogue) on the same harness.
 
 Prints one JSON line per shape with the CUDA-event time, achieved TFLOP/s and GB/s and the fraction of the
 measured roofline (the slower of FLOPs / bf16 peak and bytes / copy bandwidth), next to torch.matmul (cuBLAS)
@@ -11,7 +14,7 @@ import json
 
 import torch
 
-from ..ops import gemm, nvfp4
+from ..ops import gemm, gemv, nvfp4
 from .timing import measured_peaks, time_cuda
 
 DEFAULT = ["1,5120,5120", "8,5120,17408", "64,34816,5120", "64,5120,17408", "64,7168,5120", "256,5120,17408",
@@ -29,17 +32,32 @@ def main() -> None:
     ap.add_argument("--pdl", action="store_true", help="launch GEMMs as programmatic dependents")
     ap.add_argument("--phases", action="store_true",
                     help="also print the kernel's phase timers (ns since kernel entry, mean over CTAs)")
-    ap.add_argument("--epi", default="store", choices=["store", "silu", "silu_quant"],
+    ap.add_argument("--epi", default="store", choices=["store", "silu", "silu_quant", "norm"],
                     help="epilogue (nvfp4): plain store, SiLU-mul, SiLU-mul + NVFP4 requant in the epilogue")
+    ap.add_argument("--decode", type=int, default=-1, help="gemv: 0 = cvt, 1 = shift-and-mask code decode")
     args = ap.parse_args()
     gemm.set_pdl(args.pdl)
+    if args.decode >= 0:
+        from .. import _native as nv
+        nv.register("hb_nvfp4_gemv_set_decode", [nv.I], void=True)
+        nv.lib().hb_nvfp4_gemv_set_decode(args.decode)
     peaks = measured_peaks()
     dev = torch.device("cuda")
     for spec in args.shapes:
         m, n, k = (int(v) for v in spec.split(","))
         x = torch.randn(m, k, device=dev).bfloat16()
         w = (torch.randn(n, k, device=dev) * 0.02).bfloat16()
-        if args.kind == "nvfp4":
+        if args.kind == "gemv":
+            wq = nvfp4.quantize_weight(w)
+            nw = torch.ones(k, dtype=torch.bfloat16, device=dev) if args.epi == "norm" else None
+            out = torch.empty(m, n // 2 if args.epi == "silu" else n, dtype=torch.bfloat16, device=dev)
+
+            def run(w_):
+                return gemv.nvfp4_gemv(x, w_, norm_weight=nw, out=out,
+                                       epilogue=gemm.EPI_SILU_MUL if args.epi == "silu" else gemm.EPI_STORE)
+            fn = lambda: run(wq)  # noqa: E731
+            bytes_moved = n * k * 0.5625 + m * k * 2 + m * n * 2
+        elif args.kind == "nvfp4":
             wq = nvfp4.quantize_weight(w)
             gs = torch.tensor(float(x.float().abs().max()) / (6 * 448), device=dev)
             xq = nvfp4.quantize(x, gs)
@@ -63,9 +81,9 @@ def main() -> None:
             torch.cuda.synchronize()
             continue
         if args.graph:
-            wbytes = n * k * (0.5625 if args.kind == "nvfp4" else 2)
+            wbytes = n * k * (0.5625 if args.kind in ("nvfp4", "gemv") else 2)
             reps = min(max(2, int((300 << 20) / wbytes) + 1), 1024)
-            if args.kind == "nvfp4":
+            if args.kind in ("nvfp4", "gemv"):
                 ws = [nvfp4.Nvfp4Tensor(wq.q.clone(), wq.sf.clone(), wq.gscale, wq.rows, wq.k) for _ in range(reps)]
                 calls = [lambda w_=w_: run(w_) for w_ in ws]
             else:
@@ -99,10 +117,11 @@ def main() -> None:
         flops = 2.0 * m * n * k
         ms = t["median_ms"]
         peak_fl = peaks["bf16_tflops"] * (4.0 if args.kind == "nvfp4" else 1.0)
+
         roof_ms = max(flops / (peak_fl * 1e12), bytes_moved / (peaks["hbm_gbs"] * 1e9)) * 1e3
         print(json.dumps({"kind": args.kind, "m": m, "n": n, "k": k, "ms": round(ms, 4),
                           "tflops": round(flops / ms / 1e9, 1), "gbs": round(bytes_moved / ms / 1e6, 1),
-                          "roofline_frac": round(roof_ms / ms, 3), "cublas_bf16_ms": round(tl["median_ms"], 4),
+                          "roofline_frac": round(roof_ms / ms, 3), "cublas_bf16_ms": round(tl["median_ms"], 4), "epi": args.epi,
                           "peaks": peaks["source"], **({"phase_ns": phases} if phases else {})}))
 
 
