@@ -24,6 +24,10 @@ class StatePool:
             from .. import _native as nv
             nv.lib()
             nv.set_bound(nv.BOUND_STATE_SLOTS, slots + 1)       # checked-index build: what a state slot may be
+        # auxiliary per-slot state of layers that are not recurrences proper (the per-layer-embedding layer's
+        # convolution window and token history): copied, cleared and snapshotted with the slot
+        self.aux: dict = {}
+        self._aux_fill: dict = {}
         self._free = list(range(slots, 0, -1))
         self._owned = bytearray(slots + 1)
         self.reserved = 0               # slots held for good by engine parts (captured rounds' scratch), not requests
@@ -35,7 +39,16 @@ class StatePool:
     @property
     def bytes_per_slot(self) -> int:
         scale = self.ssm_scale[:, 0].numel() * 4 if self.ssm_scale is not None else 0
-        return self.conv[:, 0].numel() * 2 + self.ssm[:, 0].numel() * self.ssm.element_size() + scale
+        aux = sum(a[0].numel() * a.element_size() for a in self.aux.values())
+        return self.conv[:, 0].numel() * 2 + self.ssm[:, 0].numel() * self.ssm.element_size() + scale + aux
+
+    def register_aux(self, name: str, shape: tuple, dtype: torch.dtype, fill=0) -> torch.Tensor:
+        """A [slots + 1, *shape] tensor that lives and moves with the slots (idempotent per name). Reference:
+        hibana/cache/state_pool.py `register_aux`."""
+        if name not in self.aux:
+            self.aux[name] = torch.full((self.slots + 1, *shape), fill, dtype=dtype, device=self.device)
+            self._aux_fill[name] = fill
+        return self.aux[name]
 
     def alloc(self) -> int:
         if not self._free:
@@ -63,12 +76,16 @@ class StatePool:
         self.ssm[:, dst].copy_(self.ssm[:, src])
         if self.ssm_scale is not None:
             self.ssm_scale[:, dst].copy_(self.ssm_scale[:, src])
+        for a in self.aux.values():
+            a[dst].copy_(a[src])
 
     def zero_slot(self, slot: int) -> None:
         self.conv[:, slot].zero_()
         self.ssm[:, slot].zero_()
         if self.ssm_scale is not None:
             self.ssm_scale[:, slot].fill_(1.0)
+        for name, a in self.aux.items():
+            a[slot].fill_(self._aux_fill[name])
 
     def export_slot(self, slot: int) -> tuple[torch.Tensor, torch.Tensor]:
         return self.conv[:, slot].clone(), self.ssm[:, slot].clone()

@@ -56,6 +56,8 @@ class Executor:
             state_pool = StatePool(spec["layers"], state_slots or (3 * max_batch + 2), spec["conv_dim"],
                                    spec["conv_width"], spec["state_shape"], self.device, state_dtype=state_dtype)
         self.state_pool = state_pool
+        if state_pool is not None and hasattr(model, "register_state"):
+            model.register_state(state_pool)
         buckets = buckets or tuple(b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b <= max_batch)
         self.runner = ModelRunner(model, self.kv, max_batch=max_batch, max_ctx=max_ctx, buckets=buckets,
                                   use_graphs=use_graphs, comm=comm, attn_splits=attn_splits, state_pool=state_pool)

@@ -66,6 +66,12 @@ class HybridModel:
                     init.ones(hc * hh, True).to(self.device), init.normal(rk, hc * hh).to(self.device),
                     init.normal(hc * hh, rk).to(self.device),
                     None if last else init.normal(hc, hc * hh).to(self.device), hc, hh, t.norm_eps))
+        # per-layer n-gram embedding (models/ple.py): added to the streams in front of the listed blocks
+        self.ple = {}
+        # (it reads and writes the hyper-connection streams: a copy of the target without streams runs without it)
+        if t.ple_layers and self.hyper_sites is not None:
+            from .ple import PleLayer
+            self.ple = {i: PleLayer(t, init, f"blocks.{i}.ple") for i in t.ple_layers if i < len(self.blocks)}
         self.mtp = None
         if t.mtp_layers:
             from .mtp import MtpHead
@@ -126,6 +132,11 @@ class HybridModel:
             return {"layers": self.state_layers, "conv_dim": t.gdn_conv_dim, "conv_width": t.conv_width,
                     "state_shape": (t.gdn_v_heads, t.gdn_head_dim, t.gdn_head_dim)}
         return None
+
+    def register_state(self, pool) -> None:
+        """Per-slot state beyond the recurrences' own (called once, before any graph is captured)."""
+        for layer in self.ple.values():
+            layer.register(pool)
 
     def calibrate(self, run_forward, comm=None) -> None:
         lins = [lin for lin in self.linears() if lin.fmt == "nvfp4"]
@@ -211,7 +222,9 @@ class HybridModel:
         t = self.target
         hyper = self.embed_tokens(ids, ctx).repeat(1, t.hyper_streams)
         site = 0
-        for blk in self.blocks:
+        for bi, blk in enumerate(self.blocks):
+            if bi in self.ple:
+                hyper = basic.add(hyper, self.ple[bi].forward(hyper, ids, ctx, states))
             for _norm_w, sub in blk.sublayers():
                 if sub is None:
                     continue

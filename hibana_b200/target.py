@@ -70,6 +70,11 @@ class Target:
     qsa_ratio: int = 0               # > 0: sparse attention indexer (models/qsa.py): tokens per compressed index key
     qsa_budget: int = 2048           # KV tokens a query row attends to through the indexer (plus its own group's tail)
     qsa_heads: int = 4               # index query heads (128 wide)
+    ple_layers: tuple = ()           # block indices that add the per-layer n-gram embedding (models/ple.py) to the streams
+    ple_heads: int = 4               # table heads per n-gram order (2- and 3-grams)
+    ple_kernel: int = 4              # taps of its dilated convolution
+    ple_rows: int = 1 << 18          # table rows per head (the synthetic table; a checkpoint brings its own sizes)
+    ple_eos: int = 1                 # end-of-sequence id that cuts an n-gram context
     moe_specs: tuple = ()            # ((block index, experts, expert width), ...): blocks whose MoE differs from the default
     tp_size: int = 1
     tp_rank: int = 0
@@ -123,6 +128,8 @@ class Target:
             elif mixer == GDN:
                 total += self.gdn_v_heads * self.gdn_head_dim * self.gdn_head_dim * 4
                 total += self.gdn_conv_dim * (self.conv_width - 1) * 2
+        if self.ple_layers:      # the per-layer embedding's convolution window (3 = its dilation) and token history
+            total += max(self.hyper_streams, 1) * self.hidden * (self.ple_kernel - 1) * 3 * 2 + 16
         return total
 
     def param_count(self) -> int:
@@ -209,7 +216,7 @@ def flashnext() -> Target:
                   rope_theta=1e7, rotary_frac=0.25, qk_norm=True, gemma_norm=True, gdn_k_heads=16, gdn_v_heads=48,
                   gdn_head_dim=128, experts=512, top_k=10, expert_ffn=640, shared_ffn=640, router="softmax",
                   mtp_layers=1, mtp_depth=3, weight_format="nvfp4", kv_dtype="fp8", prefill_chunk=4096,
-                  hyper_streams=4, hyper_rank=320, qsa_ratio=4, qsa_budget=2048, qsa_heads=4)
+                  hyper_streams=4, hyper_rank=320, qsa_ratio=4, qsa_budget=2048, qsa_heads=4, ple_layers=(0,))
 
 
 NEMOTRON_PATTERN = "MEMEMEM*EMEMEMEM*EMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEMEM*EMEMEMEM*EMEMEMEME"
@@ -269,6 +276,8 @@ def get_target(name: str) -> Target:
 
 def scaled(t: Target, *, layers: Optional[int] = None, **overrides) -> Target:
     """A down-scaled copy (same structure, fewer layers / other dims) for tests."""
+    if t.ple_layers and overrides.get("hidden", t.hidden) < t.hidden:
+        overrides.setdefault("ple_rows", 4096)        # a narrower copy gets a table to match
     if layers is not None:
         overrides["layers"] = t.layers[:layers]
         overrides.setdefault("moe_specs", tuple(sp for sp in t.moe_specs if sp[0] < layers))
