@@ -97,11 +97,20 @@ class SsdTier:
             rate = tokens / seconds
             self.prefill_tok_s = rate if self.prefill_tok_s == 0 else 0.8 * self.prefill_tok_s + 0.2 * rate
 
+    def disk_gbs(self) -> float:
+        """The rate a restore can expect: measured reads, else what the writers sustained (a disk that takes a
+        block slowly will not give it back fast), else 0 = not known."""
+        if self.read_gbs > 0:
+            return self.read_gbs
+        return getattr(self.store, "write_gbs", 0.0) * max(len(getattr(self.store, "_queues", ())), 1)
+
     def pays(self, tokens: int) -> bool:
-        """True when bringing `tokens` tokens back from disk is expected to beat prefilling them again."""
-        if self.read_gbs <= 0 or self.prefill_tok_s <= 0 or tokens <= 0:
+        """True when bringing `tokens` tokens back from disk is expected to beat prefilling them again. Backups ask
+        the same question (`on_evict`): a block nobody would read back is not worth writing."""
+        rate = self.disk_gbs()
+        if rate <= 0 or self.prefill_tok_s <= 0 or tokens <= 0:
             return True
-        restore_s = tokens * self.token_bytes / (self.read_gbs * 1e9)
+        restore_s = tokens * self.token_bytes / (rate * 1e9)
         return restore_s < 0.8 * tokens / self.prefill_tok_s
 
     # ---- keys
@@ -326,4 +335,5 @@ class SsdTier:
     def stats(self) -> dict:
         return {"backed_up_blocks": self.backed_up, "restored_tokens": self.restored_tokens, "skipped": self.skipped,
                 "declined": self.declined, "read_gbs": round(self.read_gbs, 2),
+                "write_gbs_per_writer": round(getattr(self.store, "write_gbs", 0.0), 2),
                 "prefill_tok_s": round(self.prefill_tok_s), **self.store.stats()}

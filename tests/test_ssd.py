@@ -159,3 +159,13 @@ def test_tier_declines_when_recomputing_is_faster(tmp_path):
     assert not other.on_ssd and tier.declined == 2
     tier.read_gbs, tier.prefill_tok_s = 50.0, 1000.0         # a fast disk against a slow prefill: the tier pays
     assert tier.pays(1000) and tier.worth(toks, 0) == 512
+    # before anything was read back, what the writers sustained stands in for the disk's rate: slow writes stop
+    # further backups at eviction, and every write is one gathered copy (header, payload, checksum never joined)
+    tier.read_gbs, tier.prefill_tok_s = 0.0, 82000.0
+    assert store.write_gbs > 0
+    store.write_gbs = 0.001
+    assert tier.disk_gbs() == pytest.approx(0.001 * len(store._queues)) and not tier.pays(1000)
+    third = Node([9] * 600, kv.alloc(600))
+    tier.on_evict(third)
+    assert not third.on_ssd and tier.declined == 3
+    assert store.read(tier._block_keys(toks, 2)[1], ssd_store.KIND_KV) is not None      # round trip of the new writer
