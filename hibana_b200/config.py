@@ -68,6 +68,8 @@ class EngineConfig:
     graph_buckets: str = "1,2,4,8,16,32,64,128,256"
     # kernels / numerics
     w3: bool = False
+    w3_checkpoint: str = ""                # calibrated decode copies to attach over the nearest-rounded ones
+                                           # (weights/calibrate_model.py)
     stable_numerics: bool = False
     attn_splits: int = 0                   # 0 = automatic
     gemv: bool = False                     # small NVFP4 projections of up to 4 rows take the register-decode GEMV

@@ -147,6 +147,9 @@ class LLM:
         self.target = self.model.target
         if cfg.w3 and hasattr(self.model, "attach_w3") and model is None:
             self.model.attach_w3()          # before the pools are sized: the copies take memory too
+            if cfg.w3_checkpoint:
+                from ..weights import calibrate_model
+                calibrate_model.attach(self.model, cfg.w3_checkpoint)
         if ep > 1:
             self.ep = self._expert_parallel(ep, rank, control)
         mem = plan_memory(cfg, self.target, self.device, max_ctx=max_ctx,

@@ -124,3 +124,55 @@ def test_reference_directory_round_trip_checksums_and_exact_serving(tmp_path):
     assert ref.current_checkpoint(tmp_path, "qwen38") is None
     (tmp_path / "qwen38-current").symlink_to(d)
     assert ref.current_checkpoint(tmp_path, "qwen38") == d.resolve()
+
+
+def test_model_calibration_capture_fit_write_attach_cpu(tmp_path):
+    """The whole calibration loop on the tiny dense model: covariances captured on the serving path, GPTQ fits that
+    beat round-to-nearest on them, a digest-checked directory, and the engine decoding with the calibrated copies."""
+    import json
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.dense import DenseModel
+    from hibana_b200.target import dense_tiny, scaled
+    from hibana_b200.weights import calibrate_model as cm
+    t = scaled(dense_tiny(), weight_format="bf16")
+    model = DenseModel(t, "cpu", seed=0)
+    g = torch.Generator().manual_seed(0)
+    samples = [torch.randint(0, t.vocab, (n,), generator=g).tolist() for n in (96, 80, 120)]
+    cov = cm.capture(model, samples, max_batch=2)
+    names = [lin.name for lin in model.linears()]
+    assert set(cov.matrices) == set(names)
+    assert cov.rows["l0.qkv"] == sum(len(s) for s in samples)            # every prompt row, once
+    assert cov.matrices["l0.down"].shape == (t.ffn, t.ffn)
+    fitted, report = cm.fit(model, cov)
+    assert set(fitted) == set(names)
+    assert all(r["error_gptq"] < r["error_nearest"] for r in report), report
+    d = cm.write_directory(tmp_path / "w3", fitted, target=t.name, report=report)
+    back = cm.load_directory(d)
+    assert all(torch.equal(back[n].codes, fitted[n].codes) and torch.equal(back[n].scale, fitted[n].scale)
+               and torch.equal(back[n].zero, fitted[n].zero) for n in names)
+    served = DenseModel(t, "cpu", seed=0)
+    served.attach_w3()
+    before = served.layers[0].qkv.w3.dense().clone()
+    assert cm.attach(served, d, strict=True) == len(names)
+    after = served.layers[0].qkv.w3.dense()
+    assert not torch.equal(before, after) and torch.allclose(after.float(), fitted["l0.qkv"].dequantize(), atol=1e-6)
+    out = Executor(served, max_batch=2, max_ctx=160, use_graphs=False).generate_batch(samples[:2], SamplingParams(max_tokens=6))
+    assert all(len(r.output_ids) == 6 for r in out)
+    # a damaged file is refused; names the model lacks are refused when asked to be strict
+    manifest = json.loads((d / cm.MANIFEST).read_text())
+    victim = d / manifest["weights"]["l1.o"]["file"]
+    raw = bytearray(victim.read_bytes())
+    raw[-1] ^= 0xFF
+    victim.write_bytes(bytes(raw))
+    with pytest.raises(ValueError):
+        cm.load_directory(d)
+    cm.write_directory(tmp_path / "other", {"nowhere.proj": fitted["l0.o"]})
+    with pytest.raises(ValueError):
+        cm.attach(served, tmp_path / "other", strict=True)
+    assert cm.attach(served, tmp_path / "other") == 0
+    # the command-line driver end to end (two blocks of the tiny target, samples from a file)
+    (tmp_path / "samples.json").write_text(json.dumps({"samples": samples[:2]}))
+    cm.main(["--target", "dense-tiny", "--inputs", str(tmp_path / "samples.json"), "--output", str(tmp_path / "cli"),
+             "--device", "cpu", "--layers", "1"])
+    assert set(cm.load_directory(tmp_path / "cli")) == {"l0.qkv", "l0.o", "l0.gate_up", "l0.down"}
