@@ -66,6 +66,36 @@ def _clock_summary(proc, gpu_index: int) -> dict:
             "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def hybrid_config(args) -> None:
+    """Configs 4 and 5: the full-depth hybrid MoE families through `LLM` (hibana_b200/profiling/bench_config.py),
+    reported in this file's line format."""
+    from hibana_b200.profiling import bench_config
+    family = {4: "flashnext", 5: "nemotron"}[args.config]
+    batch = args.batch if args.batch != 64 else {4: 32, 5: 16}[args.config]
+    prompt = args.prompt if args.prompt != 2048 else {4: 4096, 5: 8192}[args.config]
+    argv = ["--family", family, "--mode", args.mode, "--batch", str(batch), "--prompt", str(prompt),
+            "--steps", str(args.steps), "--warmup", str(max(args.warmup, 3))]
+    if args.layers:
+        argv += ["--layers", str(args.layers)]
+    out = bench_config.main(argv, emit=None)
+    if out is None:
+        return
+    world = out["n_gpus"]
+    print(json.dumps({
+        "metric": f"aggregate decode tok/s ({family} hybrid MoE NVFP4, batch {batch}, {prompt} in); also tok/s/user",
+        "value": out.get("tok_s", out["tok_s_e2e"]), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": out.get("ms_per_step", out["ms_per_step_e2e"]),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 weights, bf16 activations",
+        "data": out["data"],
+        "config": {"model": family, "layers": out["layers"], "global_batch": batch, "seq_len": prompt,
+                   "parallelism": f"{out['mode']}{world}" if world > 1 else "single", "valid": out["valid"],
+                   "l2": "each step streams the routed experts' weights and the KV / state pools (larger than L2)"},
+        "e2e": {"value": out["tok_s_e2e"], "unit": "tok/s", "ms_per_step": out["ms_per_step_e2e"]},
+        "decode_tok_s_per_user": out.get("tok_s_per_user", out["tok_s_per_user_e2e"]),
+        "prefill_ms_per_chunk": out["prefill_ms_per_chunk"], "launches_per_step": out["launches_per_step"],
+        "gpu_launches": out["launches_per_step"] * args.steps, "device_status": out["device_status"]}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -76,10 +106,16 @@ def main() -> None:
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the result invalid)")
     ap.add_argument("--no-extras", action="store_true", help="skip the batch-8, NCCL-only and token-hash extras")
+    ap.add_argument("--config", type=int, default=2, choices=(2, 4, 5),
+                    help="2: 27B dense (the headline, default); 4: Flash-Next-class hybrid MoE; 5: Nemotron-class hybrid MoE")
+    ap.add_argument("--mode", default="tp", choices=("tp", "dpep"),
+                    help="configs 4 and 5 on several GPUs: tensor parallel, or data-parallel replicas + expert parallel")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
         return
+    if args.config != 2:
+        return hybrid_config(args)
 
     import torch
     import torch.distributed as dist

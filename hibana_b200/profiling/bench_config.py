@@ -23,7 +23,8 @@ import torch
 import torch.distributed as dist
 
 
-def main() -> None:
+def main(argv=None, emit=print):
+    """Runs the benchmark; rank 0 emits one JSON line and returns the dict (other ranks return None)."""
     ap = argparse.ArgumentParser()
     ap.add_argument("--family", default="flashnext")
     ap.add_argument("--mode", default="tp", choices=("tp", "dpep"))
@@ -34,7 +35,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer blocks (marks the result invalid)")
     ap.add_argument("--spec", default="off")
     ap.add_argument("--kv-dtype", default="")
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
 
     from .. import _native as nv
     from ..config import EngineConfig
@@ -162,7 +163,10 @@ def main() -> None:
             out["rounds_as_graphs"] = ex.spec.graphs.rounds if ex.spec.graphs is not None else 0
         if llm.lockstep is not None:
             out["lockstep_rounds"] = llm.lockstep.rounds
-        print(json.dumps(out), flush=True)
+        if emit is not None:
+            emit(json.dumps(out))
+        return out
+    return None
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
