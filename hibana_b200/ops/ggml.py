@@ -118,6 +118,14 @@ class PackedExperts:
                                                 rows.data_ptr(), pairs, relu2, out.data_ptr(), out.stride(0),
                                                 nv.stream()), "hb_ggml_gemv_pairs")
             return (y.view(t, k, -1).float() * weights[:, :, None]).sum(1).to(torch.bfloat16)
+        if nv.use_native(x):
+            # prefill-sized: every expert has rows, so the two stacks are expanded to bf16 once (transient: a layer's
+            # experts, a few GB) and the ranked plan + grouped tensor-core GEMMs of the NVFP4 families do the rest.
+            # One kernel per stack reads every block once; nothing visits the host.
+            from . import moe
+            ew = moe.ExpertWeights(self.experts, self.fc1.k, self.inter, "relu2", "bf16",
+                                   self.fc1.dequantize(0, self.fc1.n), self.fc2.dequantize(0, self.fc2.n))
+            return moe.experts_forward(x, ids, weights, ew)
         out = torch.zeros(t, self.hidden, dtype=torch.float32, device=x.device)
         for e in ids.unique().tolist():
             if e < 0:

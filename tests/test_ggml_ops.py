@@ -70,6 +70,27 @@ def test_packed_experts_grouped_decode_matches_reference():
     assert (outs[0] - outs[1]).abs().max() <= 3e-2 * outs[0].abs().max() + 1e-3
 
 
+@pytest.mark.gpu
+def test_packed_experts_prefill_sized_matches_reference():
+    """More (token, expert) pairs than the decode kernel takes: the expert stacks are expanded to bf16 once and the
+    grouped tensor-core GEMMs run them; same result as the per-expert reference."""
+    e, h, inter = 8, 512, 256
+    grid = _grid(256)
+    fc1 = ops.random_blocks("iq2_xxs", e * inter, h, seed=15, scale=0.01)
+    fc2 = ops.random_blocks("q8_0", e * h, inter, seed=16, scale=0.002)
+    g = torch.Generator().manual_seed(17)
+    t, k = 1100, 4
+    x = torch.randn(t, h, generator=g).bfloat16()
+    ids = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]).int()
+    wts = torch.rand(t, k, generator=g)
+    outs = []
+    for dev in ("cpu", "cuda"):
+        ex = ops.PackedExperts(ops.PackedLinear(fc1.to(dev), "iq2_xxs", e * inter, h, grid),
+                               ops.PackedLinear(fc2.to(dev), "q8_0", e * h, inter), e)
+        outs.append(ex.forward(x.to(dev), ids.to(dev), wts.to(dev)).float().cpu())
+    assert (outs[0] - outs[1]).abs().max() <= 3e-2 * outs[0].abs().max() + 1e-3
+
+
 def _small_bolt():
     from hibana_b200.target import bolt, scaled
     t = scaled(bolt(), layers=9, hidden=256, vocab=2048, q_heads=4, kv_heads=2, head_dim=64, mamba_heads=8,
