@@ -87,6 +87,8 @@ class EngineConfig:
                                            # SM, but modelling both measured slower: more splits, more partials to merge)
     max_splits: int = 8                    # split-K cluster size cap (8 = portable)
     pdl: int = 1                           # programmatic dependent launch level (0 off, 1 GEMMs, 2 small kernels too)
+    overlap_rows: int = 64                 # up to this many rows a MoE layer's independent chains (shared expert,
+                                           # latent projection) run on a side stream beside the routed experts; 0 = off
     expert_budget: int = 0                 # > 0: decode-sized MoE calls read at most this many distinct experts
     expert_keep: int = 2                   # with a budget: choices of every row that are always honoured
     # observability

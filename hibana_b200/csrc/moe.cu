@@ -78,13 +78,25 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
   // (every index below is a compile-time constant after unrolling: the arrays must stay in registers)
   unsigned bk = 0u;
   int bs = 0;
-#define HB_ROUTE_RESCAN()                              \
-  bk = 0u;                                             \
-  bs = 0;                                              \
-  _Pragma("unroll") for (int i = PER - 1; i >= 0; --i) { \
-    const bool better = key[i] >= bk && key[i] != 0u;  \
-    bk = better ? key[i] : bk;                         \
-    bs = better ? i : bs;                              \
+  // Lane-local best by a pairwise tree (depth log2 PER instead of a PER-long dependent chain); `>=` keeps the
+  // lower slot on ties, a key of 0 never wins against a live one and leaves bk = 0 when nothing is left.
+#define HB_ROUTE_RESCAN()                                                   \
+  {                                                                          \
+    unsigned tk[PER];                                                        \
+    int ts[PER];                                                             \
+    _Pragma("unroll") for (int i = 0; i < PER; ++i) {                        \
+      tk[i] = key[i];                                                        \
+      ts[i] = i;                                                             \
+    }                                                                        \
+    _Pragma("unroll") for (int w = PER / 2; w >= 1; w >>= 1) {               \
+      _Pragma("unroll") for (int i = 0; i < w; ++i) {                        \
+        const bool left = tk[i] >= tk[i + w];                                \
+        tk[i] = left ? tk[i] : tk[i + w];                                    \
+        ts[i] = left ? ts[i] : ts[i + w];                                    \
+      }                                                                      \
+    }                                                                        \
+    bk = tk[0];                                                              \
+    bs = ts[0];                                                              \
   }
   HB_ROUTE_RESCAN()
   float wsum = 0.f;
@@ -96,16 +108,17 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
     const unsigned cand = (bk == top && top != 0u) ? 0xffffffffu - static_cast<unsigned>(lane + bs * 32) : 0u;
     const unsigned win = __reduce_max_sync(0xffffffffu, cand);
     const int bi = top != 0u ? static_cast<int>(0xffffffffu - win) : 0;
+    // every lane runs the same instructions (no divergent region to reconverge from): only the winner's slot
+    // matches, so only its key is cleared and only its rescan changes anything
+    const bool mine = top != 0u && (bi & 31) == lane;
+    const int slot = mine ? (bi >> 5) : -1;
     float sc = 0.f;
-    if (top != 0u && (bi & 31) == lane) {
-      const int slot = bi >> 5;
 #pragma unroll
-      for (int i = 0; i < PER; ++i) {
-        sc = i == slot ? score[i] : sc;
-        key[i] = i == slot ? 0u : key[i];
-      }
-      HB_ROUTE_RESCAN()
+    for (int i = 0; i < PER; ++i) {
+      sc = i == slot ? score[i] : sc;
+      key[i] = i == slot ? 0u : key[i];
     }
+    HB_ROUTE_RESCAN()
     sc = __shfl_sync(0xffffffffu, sc, bi & 31);
     wsum += sc;
     if (lane == k) {

@@ -88,14 +88,21 @@ class BoltMoeLayer:
 
     def forward(self, x, ctx=None, kv=None, states=None) -> torch.Tensor:
         t = self.t
+        from ..utils import streams
+        from .layers import overlap_ok
+        # decode-sized on one GPU: the latent projection and the shared expert run on a side stream beside the router
+        # and the routed experts (utils/streams.py); otherwise everything is one chain
+        with streams.Branch(x, enabled=overlap_ok(x, ctx)) as br:
+            inp = self.fc1_latent(x) if t.latent else x
+            lat_ready = br.mark()
+            shared = self.shared.forward(x) if self.shared is not None else None
         logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
         ids, w = moe.route(logits, t.top_k, sigmoid=True, sel_bias=self.sel_bias, renorm=True, scale=t.router_scale)
-        inp = self.fc1_latent(x) if t.latent else x
+        br.wait(lat_ready, inp if t.latent else None)
         y = self.experts.forward(inp, ids, w)
         out = self.fc2_latent(y) if t.latent else y
-        if self.shared is not None:
-            out = basic.add(out, self.shared.forward(x))
-        return out
+        br.join(shared)
+        return basic.add(out, shared) if shared is not None else out
 
     def weight_bytes(self) -> int:
         return self.experts.fc1.nbytes() + self.experts.fc2.nbytes()

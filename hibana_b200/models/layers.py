@@ -16,6 +16,7 @@ from .. import config as cfgmod
 from ..engine.context import ForwardContext
 from ..ops import attention, basic, gemm, moe, recurrent
 from ..target import ATTN, GATED_ATTN, GDN, LATENT_MOE, MAMBA2, MLP, MOE, NONE, Target
+from ..utils import streams
 from .linear import Linear, interleave_pairs
 
 
@@ -271,16 +272,20 @@ class GdnLayer:
     def forward(self, x, ctx: ForwardContext, kv, states, xq=None) -> torch.Tensor:
         t = self.t
         kd = t.gdn_head_dim
+        # the gate projection (quantise, GEMM, gate kernel) does not meet the q / k / v chain before the scan: at
+        # decode sizes it runs on a side stream beside in_qkvz and the convolution (utils/streams.py)
+        with streams.Branch(x, enabled=overlap_ok(x, ctx, comm_free=True)) as br:
+            beta, g = basic.gdn_gates(self.in_ba(x), self.a_log, self.dt_bias)
         qkvz = self.in_qkvz(x if xq is None else xq)
         li = self.state_index
         so = ctx.extras.get("state_out", ctx.state_slots)
-        beta, g = basic.gdn_gates(self.in_ba(x), self.a_log, self.dt_bias)
         if "ring" in ctx.extras:
             ctx.extras["ring"].append((self, (qkvz[:, :2 * self.qk + self.vd], g, beta)))
         qkv = recurrent.conv1d(qkvz[:, :2 * self.qk + self.vd], self.conv_w, None, states.conv[li], ctx.state_slots,
                                so, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state, silu=True,
                                max_rows=ctx.max_rows if ctx.q_indptr is not None else 0)
         z = qkvz[:, 2 * self.qk + self.vd:]
+        br.join(beta, g)
         o = recurrent.gdn_scan(qkv[:, :self.qk], qkv[:, self.qk:2 * self.qk], qkv[:, 2 * self.qk:], g, beta,
                                states.ssm[li], ctx.state_slots, so, k_heads=t.gdn_k_heads, v_heads=t.gdn_v_heads,
                                kdim=kd, vdim=kd, l2norm=True, q_indptr=ctx.q_indptr,
@@ -337,6 +342,16 @@ class MlpLayer:
         if self.act == "swiglu":
             return self.down(self.up(x, epilogue=gemm.EPI_SILU_MUL))
         return self.down(basic.act_mul(self.up(x), basic.ACT_RELU2))
+
+
+def overlap_ok(x: torch.Tensor, ctx, comm_free: bool = False) -> bool:
+    """Side-stream branches inside a layer: CUDA tensors and decode-sized row counts. A branch that could reach the
+    communicator needs `ctx.comm` to be absent (its kernels and heap slots are ordered on one stream); a branch of
+    plain local launches (`comm_free`) may run beside a tensor-parallel layer too."""
+    rows = cfgmod.current().overlap_rows
+    if not x.is_cuda or not 0 < x.shape[0] <= rows:
+        return False
+    return comm_free or ctx is None or getattr(ctx, "comm", None) is None
 
 
 class MoeLayer:
@@ -398,6 +413,23 @@ class MoeLayer:
 
     def forward(self, x, ctx=None, kv=None, states=None) -> torch.Tensor:
         t = self.t
+        if overlap_ok(x, ctx):
+            # decode-sized on one GPU: the latent projection and the shared expert do not depend on the routing, so
+            # they run on a side stream beside router -> route -> plan -> grouped GEMMs (utils/streams.py)
+            with streams.Branch(x) as br:
+                lat = self.fc1_latent(x) if t.latent else None
+                lat_ready = br.mark()
+                shared = self.shared.forward(x) if self.shared is not None else None
+            logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
+            ids, w = self._route(logits)
+            if t.latent:
+                br.wait(lat_ready, lat)
+                y = moe.experts_forward(lat, ids, w, self.experts, id_base=self.e_lo)
+                out = self.fc2_latent(y)
+                br.join(shared)
+                return basic.add(out, shared) if shared is not None else out
+            br.join(shared)
+            return moe.experts_forward(x, ids, w, self.experts, shared=shared, id_base=self.e_lo)
         logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
         ids, w = self._route(logits)
         shared = self.shared.forward(x) if self.shared is not None else None
