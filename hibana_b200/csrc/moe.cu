@@ -27,6 +27,86 @@ __device__ __forceinline__ unsigned route_key(float v) {
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
+// Decode-sized routing: one CTA per token, one thread per expert. The k-th largest key is found by a 32-step bit
+// search on block-wide counts (`__syncthreads_count`), ties at the threshold go to the lower expert index, and the
+// at most 32 selected experts rank themselves against each other, so the ids come out in the same order as the
+// round-by-round extraction of `moe_route_kernel` (descending score, lower index first) in ~2 us instead of one
+// dependent round per selected expert in a single warp.
+__global__ void __launch_bounds__(1024) moe_route_block_kernel(
+    const float* __restrict__ logits, long long ld, const float* __restrict__ sel_bias, int experts, int topk,
+    int sigmoid, int renorm, float scale, int* __restrict__ ids, float* __restrict__ weights) {
+  __shared__ float s_red[32];
+  __shared__ int s_warp_tie[32], s_warp_sel[32];
+  __shared__ unsigned s_key[MAX_TOPK];
+  __shared__ int s_id[MAX_TOPK];
+  __shared__ float s_sc[MAX_TOPK], s_sorted[MAX_TOPK];
+  const int t = blockIdx.x, e = threadIdx.x, lane = e & 31, warp = e >> 5, nwarps = blockDim.x >> 5;
+  const bool live = e < experts;
+  const float x = live ? logits[t * ld + e] : -INFINITY;
+  float score;
+  unsigned key;
+  if (sigmoid) {
+    score = live ? 1.f / (1.f + __expf(-x)) : 0.f;
+    key = live ? route_key(score + (sel_bias ? sel_bias[e] : 0.f)) : 0u;
+  } else {
+    float m = warp_max(x);
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    m = lane < nwarps ? s_red[lane] : -INFINITY;
+    m = warp_max(m);
+    __syncthreads();
+    const float ex = live ? __expf(x - m) : 0.f;
+    float sum = warp_sum(ex);
+    if (lane == 0) s_red[warp] = sum;
+    __syncthreads();
+    sum = lane < nwarps ? s_red[lane] : 0.f;
+    sum = warp_sum(sum);
+    score = ex * (1.f / sum);
+    key = live ? route_key(score) : 0u;
+  }
+  unsigned thr = 0u;                       // the largest value with at least topk keys at or above it
+  for (int b = 31; b >= 0; --b) {
+    const unsigned cand = thr | (1u << b);
+    if (__syncthreads_count(key >= cand) >= topk) thr = cand;
+  }
+  const int above = __syncthreads_count(key > thr);
+  const bool tie = key == thr && thr != 0u;
+  // exclusive prefix counts over the expert index: of the ties (who gets the remaining places) and, below, of the
+  // selected (their slot in the shared list)
+  const unsigned tie_mask = __ballot_sync(0xffffffffu, tie);
+  if (lane == 0) s_warp_tie[warp] = __popc(tie_mask);
+  __syncthreads();
+  int tie_rank = __popc(tie_mask & ((1u << lane) - 1u));
+  for (int w = 0; w < warp; ++w) tie_rank += s_warp_tie[w];
+  const bool sel = key > thr || (tie && tie_rank < topk - above);
+  const unsigned sel_mask = __ballot_sync(0xffffffffu, sel);
+  if (lane == 0) s_warp_sel[warp] = __popc(sel_mask);
+  __syncthreads();
+  int slot = __popc(sel_mask & ((1u << lane) - 1u));
+  for (int w = 0; w < warp; ++w) slot += s_warp_sel[w];
+  if (sel && slot < MAX_TOPK) {
+    s_key[slot] = key;
+    s_id[slot] = e;
+    s_sc[slot] = score;
+  }
+  __syncthreads();
+  if (e < topk) {                           // thread j places list entry j: its rank among the selected
+    const unsigned kj = s_key[e];
+    const int ij = s_id[e];
+    int rank = 0;
+    for (int i = 0; i < topk; ++i) rank += (s_key[i] > kj || (s_key[i] == kj && s_id[i] < ij)) ? 1 : 0;
+    s_sorted[rank] = s_sc[e];
+    ids[static_cast<long long>(t) * topk + rank] = ij;
+  }
+  __syncthreads();
+  if (e < topk) {
+    float wsum = 0.f;
+    for (int i = 0; i < topk; ++i) wsum += s_sorted[i];       // in rank order, like the round-by-round kernel
+    const float w = (renorm ? s_sorted[e] / fmaxf(wsum, 1e-20f) : s_sorted[e]) * scale;
+    weights[static_cast<long long>(t) * topk + e] = w;
+  }
+}
+
 template <int PER>
 __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ sel_bias,
                                  int tokens, int experts, int topk, int sigmoid, int renorm, float scale,
@@ -78,25 +158,13 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
   // (every index below is a compile-time constant after unrolling: the arrays must stay in registers)
   unsigned bk = 0u;
   int bs = 0;
-  // Lane-local best by a pairwise tree (depth log2 PER instead of a PER-long dependent chain); `>=` keeps the
-  // lower slot on ties, a key of 0 never wins against a live one and leaves bk = 0 when nothing is left.
-#define HB_ROUTE_RESCAN()                                                   \
-  {                                                                          \
-    unsigned tk[PER];                                                        \
-    int ts[PER];                                                             \
-    _Pragma("unroll") for (int i = 0; i < PER; ++i) {                        \
-      tk[i] = key[i];                                                        \
-      ts[i] = i;                                                             \
-    }                                                                        \
-    _Pragma("unroll") for (int w = PER / 2; w >= 1; w >>= 1) {               \
-      _Pragma("unroll") for (int i = 0; i < w; ++i) {                        \
-        const bool left = tk[i] >= tk[i + w];                                \
-        tk[i] = left ? tk[i] : tk[i + w];                                    \
-        ts[i] = left ? ts[i] : ts[i + w];                                    \
-      }                                                                      \
-    }                                                                        \
-    bk = tk[0];                                                              \
-    bs = ts[0];                                                              \
+#define HB_ROUTE_RESCAN()                              \
+  bk = 0u;                                             \
+  bs = 0;                                              \
+  _Pragma("unroll") for (int i = PER - 1; i >= 0; --i) { \
+    const bool better = key[i] >= bk && key[i] != 0u;  \
+    bk = better ? key[i] : bk;                         \
+    bs = better ? i : bs;                              \
   }
   HB_ROUTE_RESCAN()
   float wsum = 0.f;
@@ -108,17 +176,16 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
     const unsigned cand = (bk == top && top != 0u) ? 0xffffffffu - static_cast<unsigned>(lane + bs * 32) : 0u;
     const unsigned win = __reduce_max_sync(0xffffffffu, cand);
     const int bi = top != 0u ? static_cast<int>(0xffffffffu - win) : 0;
-    // every lane runs the same instructions (no divergent region to reconverge from): only the winner's slot
-    // matches, so only its key is cleared and only its rescan changes anything
-    const bool mine = top != 0u && (bi & 31) == lane;
-    const int slot = mine ? (bi >> 5) : -1;
     float sc = 0.f;
+    if (top != 0u && (bi & 31) == lane) {
+      const int slot = bi >> 5;
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      sc = i == slot ? score[i] : sc;
-      key[i] = i == slot ? 0u : key[i];
+      for (int i = 0; i < PER; ++i) {
+        sc = i == slot ? score[i] : sc;
+        key[i] = i == slot ? 0u : key[i];
+      }
+      HB_ROUTE_RESCAN()
     }
-    HB_ROUTE_RESCAN()
     sc = __shfl_sync(0xffffffffu, sc, bi & 31);
     wsum += sc;
     if (lane == k) {
@@ -426,6 +493,13 @@ int hb_moe_route(const void* logits, long long ld, const void* sel_bias, int tok
                  int sigmoid, int renorm, float scale, void* ids, void* weights, void* stream) {
   if (tokens <= 0) return 0;
   if (experts > 1024 || topk > MAX_TOPK || topk > experts) return 1;
+  if (tokens <= 256 && experts > 128) {      // decode / verify sizes: latency matters, one CTA per token
+    const int threads = (experts + 31) / 32 * 32;
+    moe_route_block_kernel<<<tokens, threads, 0, ST(stream)>>>(
+        static_cast<const float*>(logits), ld, static_cast<const float*>(sel_bias), experts, topk, sigmoid, renorm,
+        scale, static_cast<int*>(ids), static_cast<float*>(weights));
+    return cudaGetLastError() == cudaSuccess ? 0 : 2;
+  }
 #define HB_ROUTE(PER)                                                                                        \
   moe_route_kernel<PER><<<(tokens + 3) / 4, 128, 0, ST(stream)>>>(                                           \
       static_cast<const float*>(logits), ld, static_cast<const float*>(sel_bias), tokens, experts, topk, sigmoid, \

@@ -44,6 +44,15 @@ def test_route_gpu(e, k, sig):
     ids_g, w_g = moe.route(lg.cuda(), k, sigmoid=sig, sel_bias=None if bias is None else bias.cuda(), scale=1.7)
     assert torch.equal(ids_g.cpu(), ids)
     assert torch.allclose(w_g.cpu(), w, atol=1e-5, rtol=1e-4)
+    if sig:
+        # many exactly equal scores around the k-th place: equal scores go to the lower expert index, in both the
+        # one-CTA-per-token form (few tokens) and the one-warp-per-token form (many)
+        for tokens in (7, 300):
+            coarse = (torch.randn(tokens, e) * 2).round() / 2
+            ids, w = moe.route(coarse, k, sigmoid=True, scale=1.0)
+            ids_g, w_g = moe.route(coarse.cuda(), k, sigmoid=True, scale=1.0)
+            assert torch.equal(ids_g.cpu(), ids)
+            assert torch.allclose(w_g.cpu(), w, atol=1e-5, rtol=1e-4)
 
 
 @pytest.mark.gpu
