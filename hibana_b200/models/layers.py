@@ -447,25 +447,34 @@ def _moe_forward_ep(self, x, comm) -> torch.Tensor:
     """Replicated-activation expert parallelism: every rank runs its expert range on all tokens, the partial sums
     are all-reduced, and the (replicated) shared expert is added once afterwards."""
     t = self.t
+    # the shared expert and the latent projection are plain local launches that do not depend on the routing: at
+    # decode sizes they run on a side stream beside router -> route -> grouped GEMMs (the communicator's kernels stay
+    # on the main stream)
+    with streams.Branch(x, enabled=overlap_ok(x, None, comm_free=True)) as br:
+        inp = self.fc1_latent(x) if t.latent else x
+        lat_ready = br.mark()
+        shared = self.shared.forward(x) if self.shared is not None else None
     logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
     ids, w = self._route(logits)
-    inp = self.fc1_latent(x) if t.latent else x
+    br.wait(lat_ready, inp if t.latent else None)
     part = moe.experts_forward(inp, ids, w, self.experts, id_base=self.e_lo)
     if getattr(self, "tp", 1) > 1:
         # tensor parallel: the shared expert is column / row split too, so its partial sum joins the routed
         # experts' before the layer's one all-reduce; the latent up-projection is linear and moves in front of it
         if t.latent:
             part = self.fc2_latent(part)
-        if self.shared is not None and self.shared_split:
-            part = basic.add(part, self.shared.forward(x))
+        br.join(shared)
+        if shared is not None and self.shared_split:
+            part = basic.add(part, shared)
         out = comm.all_reduce(part)
-        if self.shared is not None and not self.shared_split:
-            out = basic.add(out, self.shared.forward(x))       # whole on every rank: added once, after the sum
+        if shared is not None and not self.shared_split:
+            out = basic.add(out, shared)                        # whole on every rank: added once, after the sum
         return out
     part = comm.all_reduce(part)
     out = self.fc2_latent(part) if t.latent else part
-    if self.shared is not None:
-        out = basic.add(out, self.shared.forward(x))
+    br.join(shared)
+    if shared is not None:
+        out = basic.add(out, shared)
     return out
 
 
