@@ -254,6 +254,12 @@ def main() -> None:
         out = ex.generate_batch([prompts[0][:64]], SamplingParams(max_tokens=16, ignore_eos=True))[0].output_ids
         extras["tokens_head"] = out[:8]
         extras["token_hash"] = hashlib.sha1(",".join(map(str, out)).encode()).hexdigest()[:12]
+
+        def first_token_logprobs():
+            """Top-8 (token, logprob) of the first generated token of the fixed prompt (prefill path)."""
+            r = ex.generate_batch([prompts[0][:64]], SamplingParams(max_tokens=1, ignore_eos=True, logprobs=8))[0]
+            return dict(r.token_logprobs[0][1]) if r.token_logprobs else {}
+        fused_lp = first_token_logprobs()
         if comm is not None:
             # same model, same engine, collectives through NCCL only (the unfused baseline on this box)
             comm.fused = False
@@ -265,6 +271,14 @@ def main() -> None:
             ex.capture_graphs()
             devn, _, _, _, _ = run_decode(batch)
             extras["nccl_only"] = {"value": round(batch / devn * 1e3, 1), "unit": "tok/s", "ms_per_step": round(devn, 4)}
+            # the hand-written collectives against NCCL on the run itself: the same prompt through both, compared on
+            # the log-probabilities of the first token (a wrong sum in a fused kernel shows up here, not only as a
+            # status word)
+            nccl_lp = first_token_logprobs()
+            common = set(fused_lp) & set(nccl_lp)
+            extras["fused_vs_nccl"] = {
+                "top8_tokens_in_common": len(common),
+                "max_abs_logprob_diff": round(max((abs(fused_lp[k] - nccl_lp[k]) for k in common), default=-1.0), 5)}
             ex.runner._split_head = split
             comm.fused = True
 
