@@ -173,7 +173,8 @@ class DenseModel:
         y = None
         for i, layer in enumerate(self.layers):
             q = basic.rope_kv_write(qkv, ctx.positions, ctx.slots, self.inv_freq, kv.k[i], kv.v[i], t.q_heads,
-                                    t.kv_heads, t.head_dim, rot=t.rot_dim, kv_scale=kv.kv_scale)
+                                    t.kv_heads, t.head_dim, rot=t.rot_dim, kv_scale=kv.kv_scale,
+                                    table=basic.rope_table(ctx, self.inv_freq, t.rot_dim))
             att = attention.paged_attention(q, kv.k[i], kv.v[i], ctx.kv_indices, ctx.ctx_len, q_indptr=ctx.q_indptr,
                                             max_rows=ctx.max_rows, seq_rows=ctx.seq_rows, scale=self.scale,
                                             kv_scale=kv.kv_scale, splits=ctx.attn_splits,
@@ -213,7 +214,8 @@ class DenseModel:
             else:
                 qkv = self._reduce_norm_linear(h, slot, res, layer.input_norm, layer.qkv, ctx)
             q = basic.rope_kv_write(qkv, ctx.positions, ctx.slots, self.inv_freq, kv.k[i], kv.v[i], t.q_heads,
-                                    t.kv_heads, t.head_dim, rot=t.rot_dim, kv_scale=kv.kv_scale)
+                                    t.kv_heads, t.head_dim, rot=t.rot_dim, kv_scale=kv.kv_scale,
+                                    table=basic.rope_table(ctx, self.inv_freq, t.rot_dim))
             # decode-shaped steps hand NVFP4 activations from kernel to kernel: the attention kernel merges its KV
             # splits and quantises for o_proj, the gate/up GEMM requantises for down in its epilogue
             fuse = (cfgmod.current().fuse_epilogues and layer.o.fmt == "nvfp4" and not layer.o.calibrating
@@ -253,7 +255,8 @@ class DenseModel:
         for i, layer in enumerate(self.layers):
             qkv = norm_linear(res, None, layer.input_norm, t.norm_eps, layer.qkv, add_residual=False)
             q = basic.rope_kv_write(qkv, ctx.positions, ctx.slots, self.inv_freq, kv.k[i], kv.v[i], t.q_heads,
-                                    t.kv_heads, t.head_dim, rot=t.rot_dim, kv_scale=kv.kv_scale)
+                                    t.kv_heads, t.head_dim, rot=t.rot_dim, kv_scale=kv.kv_scale,
+                                    table=basic.rope_table(ctx, self.inv_freq, t.rot_dim))
             o_gemv = layer.o.takes_gemv(rows)
             att = attention.paged_attention(q, kv.k[i], kv.v[i], ctx.kv_indices, ctx.ctx_len, q_indptr=ctx.q_indptr,
                                             max_rows=ctx.max_rows, seq_rows=ctx.seq_rows, scale=self.scale,

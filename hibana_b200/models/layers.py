@@ -147,7 +147,8 @@ class AttentionLayer:
         i = self.kv_index
         q = basic.rope_kv_write(qkv, ctx.positions, ctx.slots, self.inv_freq, kv.k[i], kv.v[i], t.q_heads,
                                 t.kv_heads, t.head_dim, rot=t.rot_dim, q_norm=self.q_norm, k_norm=self.k_norm,
-                                eps=t.norm_eps, gemma_norm=t.gemma_norm, kv_scale=kv.kv_scale, q_gate=self.gated)
+                                eps=t.norm_eps, gemma_norm=t.gemma_norm, kv_scale=kv.kv_scale, q_gate=self.gated,
+                                table=basic.rope_table(ctx, self.inv_freq, t.rot_dim))
         if self.indexer is not None and ctx.extras.get("qsa") and kv.idx_raw:
             att = self._sparse(x, q, ctx, kv)
         else:

@@ -19,6 +19,8 @@ nv.register("hb_rmsnorm", [P, P, P, P, I, I, L, L, Fl, I, P])
 nv.register("hb_gated_rmsnorm", [P, P, P, P, I, I, I, L, L, Fl, I, I, I, P])
 nv.register("hb_gated_rmsnorm_quant", [P, P, P, I, I, I, L, L, Fl, I, I, I, P, P, P, I, P])
 nv.register("hb_gdn_gates", [P, L, P, P, I, I, P, P, P])
+nv.register("hb_rope_table", [P, P, I, I, P, P])
+nv.register("hb_rope_use_table", [P], void=True)
 nv.register("hb_rope_kv_write", [P, L, P, P, P, P, P, Fl, I, P, P, P, L, L, I, I, I, I, I, I, Fl, I, P])
 nv.register("hb_act_mul", [P, P, P, L, I, L, I, P])
 nv.register("hb_embedding", [P, P, P, I, I, L, P])
@@ -137,12 +139,33 @@ def _rope_ref(t: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, rot: i
     return out
 
 
+ROPE_TABLE_MIN_ROWS = 256     # below this a layer's own sincos is cheaper than one more launch per forward
+
+
+def rope_table(ctx, inv_freq: torch.Tensor, rot: int) -> Optional[torch.Tensor]:
+    """(cos, sin) of every row's rotary angles, fp32 [T, rot / 2, 2], computed once per forward (cached in
+    `ctx.extras`) and read by every layer's `rope_kv_write`: a prefill chunk otherwise evaluates the same sincos in
+    each of its layers. None for small row counts and on the CPU path."""
+    pos = ctx.positions
+    if pos is None or not pos.is_cuda or pos.shape[0] < ROPE_TABLE_MIN_ROWS or rot < 2:
+        return None
+    key = ("rope_table", rot)
+    tab = ctx.extras.get(key)
+    if tab is None:
+        tab = torch.empty(pos.shape[0], rot // 2, 2, dtype=torch.float32, device=pos.device)
+        nv.check(nv.lib().hb_rope_table(pos.data_ptr(), inv_freq.data_ptr(), pos.shape[0], rot // 2, tab.data_ptr(),
+                                        nv.stream()), "hb_rope_table")
+        ctx.extras[key] = tab
+    return tab
+
+
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor], inv_freq: torch.Tensor,
                   k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], hq: int, hkv: int, d: int, *,
                   rot: Optional[int] = None, q_norm: Optional[torch.Tensor] = None,
                   k_norm: Optional[torch.Tensor] = None, eps: float = 1e-6, gemma_norm: bool = False,
-                  kv_scale: float = 1.0, q_gate: bool = False) -> torch.Tensor:
+                  kv_scale: float = 1.0, q_gate: bool = False, table: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Splits a fused qkv row, applies per-head q/k RMSNorm and NeoX RoPE, writes K/V rows into the pools.
+    `table` (`rope_table`): the rows' (cos, sin) angles computed once per forward instead of in every layer.
 
     qkv [T, Hq*D(*2 with q_gate) + 2*Hkv*D] bf16; positions / slots int32 [T]; pools [slots, Hkv, D] (bf16 or
     float8_e4m3fn scaled by 1/kv_scale). Returns q [T, Hq, D] bf16. `slots=None` skips the pool write.
@@ -158,6 +181,8 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[to
             fp8 = 2
             nv.register("hb_kv_fp4_scales", [nv.P, nv.P, nv.L, nv.L], void=True)
             nv.lib().hb_kv_fp4_scales(k_sf.data_ptr(), v_pool.sf.data_ptr(), k_sf.stride(0), k_sf.stride(1))
+        if table is not None:
+            nv.lib().hb_rope_use_table(table.data_ptr())
         nv.check(nv.lib().hb_rope_kv_write(
             qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), nv.ptr(slots), inv_freq.data_ptr(), nv.ptr(q_norm),
             nv.ptr(k_norm), eps, int(gemma_norm), q_out.data_ptr(), nv.ptr(k_pool), nv.ptr(v_pool),

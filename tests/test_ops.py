@@ -64,6 +64,46 @@ def test_rope_kv_write(d, rot, qk_norm, fp8, q_gate):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("d,q_gate", [(64, False), (128, False), (256, True)])
+def test_rope_kv_write_with_angle_table(d, q_gate):
+    """Prefill-sized calls take the angles from a per-forward table; the plain case (bf16 pools, full rotary, no
+    q / k norm) runs the vectorised kernel, anything else the generic one with the same table. Both equal the
+    table-free kernel up to the rounding of a fused multiply-add and the CPU reference within tolerance."""
+    from types import SimpleNamespace
+    hq, hkv, t = 6, 2, 300
+    width = hq * d * (2 if q_gate else 1) + 2 * hkv * d
+    qkv = torch.randn(t, width).bfloat16().cuda()
+    pos = torch.randint(0, 100000, (t,), dtype=torch.int32).cuda()
+    slots = (torch.randperm(400)[:t].int() + 1).cuda()
+    inv = basic.rope_inv_freq(d, 1e6).cuda()
+    ctx = SimpleNamespace(positions=pos, extras={})
+    table = basic.rope_table(ctx, inv, d)
+    assert table is not None and table.shape == (t, d // 2, 2) and basic.rope_table(ctx, inv, d) is table
+    assert basic.rope_table(SimpleNamespace(positions=pos[:8], extras={}), inv, d) is None      # decode-sized: no table
+    for norm in (False, True):
+        qn = (torch.randn(d) * 0.1).bfloat16().cuda() if norm else None
+        got, want = [], []
+        for tab, outs in ((table, got), (None, want)):
+            kp = torch.zeros(420, hkv, d, dtype=torch.bfloat16, device="cuda")
+            vp = torch.zeros(420, hkv, d, dtype=torch.bfloat16, device="cuda")
+            q = basic.rope_kv_write(qkv, pos, slots, inv, kp, vp, hq, hkv, d, q_norm=qn, k_norm=qn, q_gate=q_gate,
+                                    table=tab)
+            outs.extend((q, kp, vp))
+        for a, b in zip(got, want):          # same angles; products may contract differently: one bf16 step at most
+            _close(a.float(), b.float(), 1e-2)
+            assert (a.float() != b.float()).float().mean() < 0.02
+    kp = torch.zeros(420, hkv, d, dtype=torch.bfloat16)
+    vp = torch.zeros(420, hkv, d, dtype=torch.bfloat16)
+    q = basic.rope_kv_write(qkv.cpu(), pos.cpu(), slots.cpu(), inv.cpu(), kp, vp, hq, hkv, d, q_gate=q_gate)
+    kp2 = torch.zeros(420, hkv, d, dtype=torch.bfloat16, device="cuda")
+    vp2 = torch.zeros(420, hkv, d, dtype=torch.bfloat16, device="cuda")
+    q2 = basic.rope_kv_write(qkv, pos, slots, inv, kp2, vp2, hq, hkv, d, q_gate=q_gate, table=table)
+    _close(q2, q, 3e-2)
+    _close(kp2.float(), kp.float(), 3e-2)
+    _close(vp2.float(), vp.float(), 3e-2)
+
+
+@pytest.mark.gpu
 def test_act_embedding_add():
     x = torch.randn(33, 512).bfloat16()
     for mode in (basic.ACT_SILU_SPLIT, basic.ACT_SILU_PAIRS, basic.ACT_RELU2):
