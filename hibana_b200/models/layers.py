@@ -485,13 +485,21 @@ def _moe_forward_a2a(self, x, ep) -> torch.Tensor:
     call it, with an empty batch when it has no tokens."""
     t = self.t
     assert self.ep_size == ep.world and self.e_lo == ep.rank * ep.e_per, "the layer holds another expert range"
+    # the shared expert (and the latent projection) are local launches: at decode sizes they run on a side stream
+    # while the main stream routes and exchanges rows with the other ranks
+    with streams.Branch(x, enabled=overlap_ok(x, None, comm_free=True)) as br:
+        lat = self.fc1_latent(x) if t.latent else None
+        lat_ready = br.mark()
+        shared = self.shared.forward(x) if self.shared is not None and x.shape[0] else None
     logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
     ids, w = self._route(logits)
-    shared = self.shared.forward(x) if self.shared is not None and x.shape[0] else None
     if t.latent:
-        y = ep.forward(self.fc1_latent(x), ids, w, self.experts)
+        br.wait(lat_ready, lat)
+        y = ep.forward(lat, ids, w, self.experts)
         out = self.fc2_latent(y)
+        br.join(shared)
         return basic.add(out, shared) if shared is not None else out
+    br.join(shared)
     return ep.forward(x, ids, w, self.experts, shared=shared)
 
 
