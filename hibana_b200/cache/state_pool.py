@@ -11,7 +11,11 @@ import torch
 
 class StatePool:
     def __init__(self, layers: int, slots: int, conv_dim: int, conv_width: int, state_shape: tuple,
-                 device: torch.device | str = "cpu", state_dtype: torch.dtype = torch.float32):
+                 device: torch.device | str = "cpu", state_dtype: torch.dtype = torch.float32, window: int = 0,
+                 groups: int = 1):
+        """`window` > 0 (with int8 states of shape [heads, P, N]): the window-record format of ops/ssm_window.py:
+        the int8 tensor is the boundary state and every slot also holds up to window + 16 committed-token records
+        (B per group, dt * x and the running decay per head)."""
         self.layers, self.slots = layers, slots
         self.device = torch.device(device)
         self.conv = torch.zeros(max(layers, 1), slots + 1, conv_dim, max(conv_width - 1, 1), dtype=torch.bfloat16,
@@ -20,6 +24,17 @@ class StatePool:
         # int8 states carry one fp32 scale per state row (last dim is the quantised one)
         self.ssm_scale = (torch.ones(max(layers, 1), slots + 1, *state_shape[:-1], dtype=torch.float32, device=device)
                           if state_dtype == torch.int8 else None)
+        self.window = window if state_dtype == torch.int8 else 0
+        self._records: list = []
+        if self.window:
+            h, p, n = state_shape
+            cap = self.window + 16
+            nl = max(layers, 1)
+            self.win_b = torch.zeros(nl, slots + 1, groups, cap, n, dtype=torch.float16, device=device)
+            self.win_u = torch.zeros(nl, slots + 1, h, cap, p, dtype=torch.float16, device=device)
+            self.win_c = torch.zeros(nl, slots + 1, h, cap, dtype=torch.float32, device=device)
+            self.win_len = torch.zeros(nl, slots + 1, groups, dtype=torch.int32, device=device)
+            self._records = [self.win_b, self.win_u, self.win_c, self.win_len]
         if self.device.type == "cuda":
             from .. import _native as nv
             nv.lib()
@@ -40,7 +55,14 @@ class StatePool:
     def bytes_per_slot(self) -> int:
         scale = self.ssm_scale[:, 0].numel() * 4 if self.ssm_scale is not None else 0
         aux = sum(a[0].numel() * a.element_size() for a in self.aux.values())
+        aux += sum(r[:, 0].numel() * r.element_size() for r in self._records)
         return self.conv[:, 0].numel() * 2 + self.ssm[:, 0].numel() * self.ssm.element_size() + scale + aux
+
+    def window_state(self, layer: int):
+        """Layer `layer`'s view of the window records (ops/ssm_window.py `WindowState`)."""
+        from ..ops.ssm_window import WindowState
+        return WindowState(self.ssm[layer], self.ssm_scale[layer], self.win_b[layer], self.win_u[layer],
+                           self.win_c[layer], self.win_len[layer], self.window)
 
     def register_aux(self, name: str, shape: tuple, dtype: torch.dtype, fill=0) -> torch.Tensor:
         """A [slots + 1, *shape] tensor that lives and moves with the slots (idempotent per name). Reference:
@@ -78,6 +100,8 @@ class StatePool:
             self.ssm_scale[:, dst].copy_(self.ssm_scale[:, src])
         for a in self.aux.values():
             a[dst].copy_(a[src])
+        for r in self._records:
+            r[:, dst].copy_(r[:, src])
 
     def zero_slot(self, slot: int) -> None:
         self.conv[:, slot].zero_()
@@ -86,6 +110,8 @@ class StatePool:
             self.ssm_scale[:, slot].fill_(1.0)
         for name, a in self.aux.items():
             a[slot].fill_(self._aux_fill[name])
+        for r in self._records:
+            r[:, slot].zero_()
 
     def export_slot(self, slot: int) -> tuple[torch.Tensor, torch.Tensor]:
         return self.conv[:, slot].clone(), self.ssm[:, slot].clone()

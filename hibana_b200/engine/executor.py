@@ -39,6 +39,7 @@ class Executor:
                  use_graphs: bool = True, buckets: Optional[Sequence[int]] = None, radix_cache: bool = True,
                  state_pool=None, comm=None, kv_dtype: Optional[torch.dtype] = None, attn_splits: int = 0,
                  decode_reserve: int = 64, state_slots: int = 0, state_dtype: torch.dtype = torch.float32,
+                 state_window: int = 0,
                  debug_sync: bool = False):
         t: Target = model.target
         self.model, self.target = model, t
@@ -54,7 +55,8 @@ class Executor:
         if state_pool is None and spec is not None:
             from ..cache.state_pool import StatePool
             state_pool = StatePool(spec["layers"], state_slots or (3 * max_batch + 2), spec["conv_dim"],
-                                   spec["conv_width"], spec["state_shape"], self.device, state_dtype=state_dtype)
+                                   spec["conv_width"], spec["state_shape"], self.device, state_dtype=state_dtype,
+                                   window=state_window if "groups" in spec else 0, groups=spec.get("groups", 1))
         self.state_pool = state_pool
         if state_pool is not None and hasattr(model, "register_state"):
             model.register_state(state_pool)

@@ -22,7 +22,7 @@ from .executor import Executor
 from .request import Request, SamplingParams
 from .scheduler import Scheduler, SchedulerConfig
 
-STATE_DTYPES = {"fp32": torch.float32, "fp16_sr": torch.float16, "int8": torch.int8}
+STATE_DTYPES = {"fp32": torch.float32, "fp16_sr": torch.float16, "int8": torch.int8, "int8w": torch.int8}
 KV_DTYPES = {"bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn, "nvfp4": "nvfp4"}
 
 
@@ -81,7 +81,9 @@ def plan_memory(cfg: EngineConfig, target: Target, device: torch.device, *, max_
     kv_tok = int(layers * 2 * max(target.kv_heads, 1) * target.head_dim * esz)
     state_slot = target.state_bytes_per_slot
     if cfg.ssm_state != "fp32" and state_slot:
-        state_slot = state_slot // (2 if cfg.ssm_state == "fp16_sr" else 4) + target.recurrent_layers * 4096
+        # fp16: half; int8: a quarter + row scales; int8w: a quarter + the window's records (about 0.6 of that again)
+        div = {"fp16_sr": 2.0, "int8": 4.0, "int8w": 2.4}.get(cfg.ssm_state, 4.0)
+        state_slot = int(state_slot / div) + target.recurrent_layers * 4096
     if device.type != "cuda" and free_bytes is None:
         ctx = max_ctx or cfg.max_context or min(target.max_context, 8192)
         return {"max_ctx": ctx, "kv_slots": cfg.kv_pages, "state_slots": cfg.state_slots, "plan": None}
@@ -163,7 +165,9 @@ class LLM:
                                  attn_splits=cfg.attn_splits, decode_reserve=cfg.decode_reserve,
                                  state_slots=mem["state_slots"],
                                  kv_dtype=KV_DTYPES[cfg.kv_dtype] if cfg.kv_dtype else None,
-                                 state_dtype=STATE_DTYPES[cfg.ssm_state], debug_sync=cfg.debug_sync)
+                                 state_dtype=STATE_DTYPES[cfg.ssm_state],
+                                 state_window=cfg.ssm_window if cfg.ssm_state == "int8w" else 0,
+                                 debug_sync=cfg.debug_sync)
         self.executor.runner.ep = self.ep          # before graphs are captured: the all-to-all is inside them
         if cfg.ssd_dir:
             self.executor.enable_ssd_tier(cfg.ssd_dir, budget_bytes=int(cfg.ssd_budget_gb * (1 << 30)),

@@ -211,18 +211,47 @@ class MambaLayer:
         xbc = recurrent.conv1d(xbc, self.conv_w, self.conv_b, states.conv[li], ctx.state_slots, so,
                                q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state, silu=True,
                                max_rows=ctx.max_rows if ctx.q_indptr is not None else 0)
-        y = recurrent.mamba2_scan(xbc[:, :inner], xbc[:, inner:inner + gn], xbc[:, inner + gn:], dt, self.a_log,
-                                  self.dt_bias, self.d_skip, states.ssm[li], ctx.state_slots, so,
-                                  heads=t.mamba_heads, groups=t.mamba_groups, head_dim=t.mamba_head_dim,
-                                  d_state=t.mamba_state, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state,
-                                  state_scale=states.ssm_scale[li] if getattr(states, "ssm_scale", None) is not None
-                                  else None, sr_seed=ctx.extras.get("sr_seed", 0), host_rows=ctx.seq_starts_host)
+        if getattr(states, "window", 0):
+            y = self._scan_window(xbc, dt, states, ctx.state_slots, ctx.q_indptr, ctx.has_initial_state,
+                                  ctx.seq_starts_host, commit="state_out" not in ctx.extras)
+        else:
+            y = recurrent.mamba2_scan(xbc[:, :inner], xbc[:, inner:inner + gn], xbc[:, inner + gn:], dt, self.a_log,
+                                      self.dt_bias, self.d_skip, states.ssm[li], ctx.state_slots, so,
+                                      heads=t.mamba_heads, groups=t.mamba_groups, head_dim=t.mamba_head_dim,
+                                      d_state=t.mamba_state, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state,
+                                      state_scale=states.ssm_scale[li] if getattr(states, "ssm_scale", None) is not None
+                                      else None, sr_seed=ctx.extras.get("sr_seed", 0), host_rows=ctx.seq_starts_host)
         if self.out_proj.fmt == "nvfp4" and not self.out_proj.calibrating:
             # the gated norm writes the output projection's NVFP4 input itself
             return self.out_proj(basic.gated_rmsnorm_quant(y, z, self.norm_w, t.norm_eps, inner // t.mamba_groups,
                                                            self.out_proj.input_scale))
         y = basic.gated_rmsnorm(y, z, self.norm_w, t.norm_eps, inner // t.mamba_groups)
         return self.out_proj(y)
+
+    def _scan_window(self, xbc, dt, states, slots, q_indptr, has_init, host_rows, commit: bool) -> torch.Tensor:
+        """The scan over the window-record state format (ops/ssm_window.py). Decode, verify and replay rows read the
+        int8 boundary state and the committed-token records in place (a verify pass writes nothing); a prefill chunk
+        runs the fp32 kernels on a temporary state expanded from the record and folds the result back."""
+        from ..ops import ssm_window
+        t = self.t
+        inner, gn = t.mamba_inner, t.mamba_groups * t.mamba_state
+        ws = states.window_state(self.state_index)
+        xs, bm, cm = xbc[:, :inner], xbc[:, inner:inner + gn], xbc[:, inner + gn:]
+        long_rows = host_rows is not None and q_indptr is not None and max(host_rows) > ssm_window.MAX_ROWS
+        if not long_rows:
+            return ssm_window.step(ws, xs, bm, cm, dt, self.a_log, self.dt_bias, self.d_skip, slots, q_indptr=q_indptr,
+                                   has_init=has_init, commit=commit)
+        b = slots.shape[0]
+        dense = ssm_window.to_dense(ws, slots)
+        if has_init is not None:
+            dense = dense * has_init.to(dense.dtype).view(b, 1, 1, 1)
+        tmp = torch.arange(b, dtype=torch.int32, device=slots.device)
+        y = recurrent.mamba2_scan(xs, bm, cm, dt, self.a_log, self.dt_bias, self.d_skip, dense, tmp, tmp,
+                                  heads=t.mamba_heads, groups=t.mamba_groups, head_dim=t.mamba_head_dim,
+                                  d_state=t.mamba_state, q_indptr=q_indptr, host_rows=host_rows)
+        if commit:
+            ssm_window.from_dense(ws, slots, dense)
+        return y
 
     def replay(self, saved, sel, q_indptr, slots, states) -> None:
         """Advances the committed state over the selected (accepted) rows of a verify block."""
@@ -231,6 +260,9 @@ class MambaLayer:
         xbc, dt = saved[0].index_select(0, sel), saved[1].index_select(0, sel)
         li = self.state_index
         xbc = recurrent.conv1d(xbc, self.conv_w, self.conv_b, states.conv[li], slots, slots, q_indptr=q_indptr)
+        if getattr(states, "window", 0):
+            self._scan_window(xbc, dt, states, slots, q_indptr, None, None, commit=True)
+            return
         recurrent.mamba2_scan(xbc[:, :inner], xbc[:, inner:inner + gn], xbc[:, inner + gn:], dt, self.a_log,
                               self.dt_bias, self.d_skip, states.ssm[li], slots, slots, heads=t.mamba_heads,
                               groups=t.mamba_groups, head_dim=t.mamba_head_dim, d_state=t.mamba_state,
