@@ -35,6 +35,7 @@ def main(argv=None, emit=print):
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer blocks (marks the result invalid)")
     ap.add_argument("--spec", default="off")
     ap.add_argument("--kv-dtype", default="")
+    ap.add_argument("--ssm-state", default="fp32", help="recurrent state format: fp32 | fp16_sr | int8 | int8w")
     args = ap.parse_args(argv)
 
     from .. import _native as nv
@@ -62,7 +63,7 @@ def main(argv=None, emit=print):
     max_ctx = args.prompt + per_round * (max(args.warmup, 3) + 2 * args.steps) + 64
     cfg = EngineConfig(target=args.family, max_batch=per_rank, max_context=max_ctx, tp=world if dp == 1 else 1, dp=dp,
                        ep=dp if dp > 1 else 1, graph_buckets=f"1,{per_rank}", kv_pages=per_rank * max_ctx + 4096,
-                       state_slots=3 * per_rank + 2, spec=args.spec, kv_dtype=args.kv_dtype,
+                       state_slots=3 * per_rank + 2, spec=args.spec, kv_dtype=args.kv_dtype, ssm_state=args.ssm_state,
                        prefill_budget=max(4096, t.prefill_chunk))
     t0 = time.perf_counter()
     if dp > 1:
@@ -152,7 +153,7 @@ def main(argv=None, emit=print):
                "tok_s_per_user_e2e": round(per_round_tokens / e2e_ms * 1e3, 1),
                "prefill_ms_per_chunk": round(pre, 2), "prefill_chunk": chunk, "build_s": round(build_s, 1),
                "launches_per_step": ex.runner.graph_launches.get(per_rank, 0), "device_status": status,
-               "peak_alloc_gib": round(mem, 1), "spec": args.spec,
+               "peak_alloc_gib": round(mem, 1), "spec": args.spec, "ssm_state": args.ssm_state,
                "data": "synthetic (uniform-random token ids, random-init N(0,0.02) weights)"}
         if dev_ms is not None:
             out.update({"ms_per_step": round(dev_ms, 3), "tok_s": round(args.batch / dev_ms * 1e3, 1),
