@@ -47,7 +47,7 @@ class EngineConfig:
     state_slots: int = 0
     kv_dtype: str = ""                     # "" = target default, else bf16 | fp8 | nvfp4 (4.5 bits per element)
     ssm_state: str = "fp32"                # fp32 | fp16_sr | int8 | int8w (int8 boundary state + window of records,
-                                           # Mamba-2 layers; ops/ssm_window.py)
+                                           # Mamba-2 and delta-rule layers; ops/ssm_window.py)
     ssm_window: int = 16                   # committed tokens between two quantisations of an int8w state
     # prefix cache / SSD tier
     radix_cache: bool = True

@@ -1,4 +1,5 @@
-// Mamba-2 recurrent state as a quantised window record: an int8 boundary state plus the tokens committed since.
+// Recurrent state (Mamba-2, and the gated delta rule in mode 1) as a quantised window record: an int8 boundary
+// state plus the tokens committed since.
 //
 //   S_t = G(1..t) * dequant(Z) + sum_j G(j+1..t) * u_j (x) B_j          G(a..b) = exp(sum of the rows' dt * A)
 //
@@ -40,6 +41,10 @@ struct WinParams {
   const int *q_indptr, *slot_in, *has_init;       // q_indptr / has_init nullable
   int batch, heads, groups, p, n, window, cap, commit;
   int* status;
+  // mode 1, gated delta rule: x = v [T, H*P], bmat = k, cmat = q [T, G*N]; log decay and beta fp32 [T, H]
+  int mode, l2norm;
+  float scale;
+  const float *g_log, *beta;
 };
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(__expf(v)); }
@@ -63,7 +68,11 @@ __global__ void __launch_bounds__(1024) mamba2_window_kernel(const WinParams p) 
   float* sCum = sC + N;                                                          // [hg][rec_cap] c_j per head
   float* sW = sCum + hg * rec_cap;                                               // [hg][rec_cap] weight of record j
   float* sDot = sW + hg * rec_cap;                                               // [rec_cap] B_j . C
-  __half* sU = reinterpret_cast<__half*>(sDot + rec_cap);                        // [kWinMaxRows][threads]: this call's u
+  float* sK = sDot + rec_cap;                                                    // [N]   delta rule: the row's k
+  float* sDotK = sK + N;                                                         // [rec_cap] k_j . k_t
+  float* sWk = sDotK + rec_cap;                                                  // [hg][rec_cap]
+  float* sNorm = sWk + hg * rec_cap;                                             // [2]
+  __half* sU = reinterpret_cast<__half*>(sNorm + 2);                             // [kWinMaxRows][threads]: this call's u
   const int b = blockIdx.x, g = blockIdx.y;
   const int tid = threadIdx.x, nthreads = blockDim.x;
   const int hl = tid / P, pv = tid % P;                    // head within the group, value row
@@ -140,48 +149,97 @@ __global__ void __launch_bounds__(1024) mamba2_window_kernel(const WinParams p) 
 
   // ---- the call's rows
   float cum = len > 0 ? sCum[hl * rec_cap + len - 1] : 0.f;
-  const float a_h = -__expf(p.a_log[h]);
-  const float d_h = p.dskip ? p.dskip[h] : 0.f;
+  const float a_h = p.mode == 0 ? -__expf(p.a_log[h]) : 0.f;
+  const float d_h = (p.mode == 0 && p.dskip) ? p.dskip[h] : 0.f;
   for (int r = 0; r < rows; ++r) {
     const long long row = r0 + r;
-    // this row's C and B (B becomes record `len`), the head's step size
-    for (int i = tid; i < N; i += nthreads) {
-      sC[i] = __bfloat162float(p.cmat[row * p.ldb + g * N + i]);
-      sB[static_cast<size_t>(len) * N + i] = __float2half(__bfloat162float(p.bmat[row * p.ldb + g * N + i]));
+    float xv, u_val = 0.f;
+    if (p.mode == 0) {
+      // this row's C and B (B becomes record `len`), the head's step size
+      for (int i = tid; i < N; i += nthreads) {
+        sC[i] = __bfloat162float(p.cmat[row * p.ldb + g * N + i]);
+        sB[static_cast<size_t>(len) * N + i] = __float2half(__bfloat162float(p.bmat[row * p.ldb + g * N + i]));
+      }
+      const float dtv = softplus_f(__bfloat162float(p.dt[row * p.lddt + h]) + (p.dt_bias ? p.dt_bias[h] : 0.f));
+      xv = __bfloat162float(p.x[row * p.ldx + h * P + pv]);
+      cum += dtv * a_h;
+      u_val = __half2float(__float2half(dtv * xv));
+      sU[(len - stored) * nthreads + tid] = __float2half(u_val);
+    } else {
+      // delta rule: q (scaled) and k of this key head, both L2-normalised; k (rounded to fp16) becomes record `len`
+      for (int i = tid; i < N; i += nthreads) {
+        sC[i] = __bfloat162float(p.cmat[row * p.ldb + g * N + i]);
+        sK[i] = __bfloat162float(p.bmat[row * p.ldb + g * N + i]);
+      }
+      __syncthreads();
+      if (warp < 2) {
+        const float* src = warp == 0 ? sC : sK;
+        float ss = 0.f;
+        for (int i = lane; i < N; i += 32) ss += src[i] * src[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) sNorm[warp] = p.l2norm ? rsqrtf(ss + 1e-6f) : 1.f;
+      }
+      __syncthreads();
+      const float nq = sNorm[0] * p.scale, nk = sNorm[1];
+      __syncthreads();
+      for (int i = tid; i < N; i += nthreads) {
+        sC[i] *= nq;
+        const __half kh = __float2half(sK[i] * nk);
+        sK[i] = __half2float(kh);
+        sB[static_cast<size_t>(len) * N + i] = kh;
+      }
+      xv = __bfloat162float(p.x[row * p.ldx + h * P + pv]);
+      cum += p.g_log[row * p.heads + h];
     }
-    const float dtv = softplus_f(__bfloat162float(p.dt[row * p.lddt + h]) + (p.dt_bias ? p.dt_bias[h] : 0.f));
-    const float xv = __bfloat162float(p.x[row * p.ldx + h * P + pv]);
-    cum += dtv * a_h;
-    const __half u_now = __float2half(dtv * xv);
-    sU[(len - stored) * nthreads + tid] = u_now;
     if (pv == 0) sCum[hl * rec_cap + len] = cum;
     __syncthreads();
     for (int j = warp; j <= len; j += nwarps) {
       const float d = warp_dot(sB + static_cast<size_t>(j) * N, sC, N, lane);
       if (lane == 0) sDot[j] = d;
+      if (p.mode == 1 && j < len) {
+        const float dk = warp_dot(sB + static_cast<size_t>(j) * N, sK, N, lane);
+        if (lane == 0) sDotK[j] = dk;
+      }
     }
     __syncthreads();
     for (int i = tid; i < hg * (len + 1); i += nthreads) {
       const int hh = i / (len + 1), j = i % (len + 1);
-      sW[hh * rec_cap + j] = __expf(sCum[hh * rec_cap + len] - sCum[hh * rec_cap + j]) * sDot[j];
+      const float decay = __expf(sCum[hh * rec_cap + len] - sCum[hh * rec_cap + j]);
+      sW[hh * rec_cap + j] = decay * sDot[j];
+      if (p.mode == 1 && j < len) sWk[hh * rec_cap + j] = decay * sDotK[j];
     }
-    // boundary term: this thread's int8 row against C
-    float acc = 0.f;
+    // boundary term: this thread's int8 row against C (and against k for the delta rule)
+    float acc = 0.f, acck = 0.f;
     if (zs != 0.f) {
       for (int n0 = 0; n0 < N; n0 += 16) {
         const uint4 raw = *reinterpret_cast<const uint4*>(zrow + n0);
         const int8_t* zq = reinterpret_cast<const int8_t*>(&raw);
 #pragma unroll
-        for (int e = 0; e < 16; ++e) acc += static_cast<float>(zq[e]) * sC[n0 + e];
+        for (int e = 0; e < 16; ++e) {
+          const float zf = static_cast<float>(zq[e]);
+          acc += zf * sC[n0 + e];
+          if (p.mode == 1) acck += zf * sK[n0 + e];
+        }
       }
-      acc *= zs * __expf(cum);
+      const float gain = zs * __expf(cum);
+      acc *= gain;
+      acck *= gain;
     }
     __syncthreads();
-    for (int j = 0; j <= len; ++j) acc += sW[hl * rec_cap + j] * u_of(j);
-    acc += d_h * xv;
+    if (p.mode == 1) {
+      for (int j = 0; j < len; ++j) acck += sWk[hl * rec_cap + j] * u_of(j);
+      u_val = __half2float(__float2half(p.beta[row * p.heads + h] * (xv - acck)));
+      sU[(len - stored) * nthreads + tid] = __float2half(u_val);
+      for (int j = 0; j < len; ++j) acc += sW[hl * rec_cap + j] * u_of(j);
+      acc += sW[hl * rec_cap + len] * u_val;
+    } else {
+      for (int j = 0; j <= len; ++j) acc += sW[hl * rec_cap + j] * u_of(j);
+      acc += d_h * xv;
+    }
     p.y[row * p.ldy + h * P + pv] = __float2bfloat16(acc);
     if (p.commit) {
-      gU[static_cast<size_t>(len) * P + pv] = u_now;
+      gU[static_cast<size_t>(len) * P + pv] = __float2half(u_val);
       if (pv == 0) gC[len] = cum;
       if (hl == 0)
         for (int i = pv; i < N; i += P) gB[static_cast<size_t>(len) * N + i] = sB[static_cast<size_t>(len) * N + i];
@@ -253,6 +311,21 @@ extern "C" {
 
 int hb_mamba2_window_extra(void) { return hb::kWinExtra; }
 
+// The NEXT hb_mamba2_window call of this thread runs the gated delta rule over the same record format: x = v rows,
+// bmat = k rows, cmat = q rows (heads = value heads, groups = key heads, head_dim = V, d_state = K), with the rows'
+// log decay and beta (fp32 [T, heads]).
+struct WinDelta {
+  bool on = false;
+  int l2norm = 1;
+  float scale = 1.f;
+  const float *g_log = nullptr, *beta = nullptr;
+};
+static thread_local WinDelta g_win_delta;
+void hb_window_delta_rule(const void* g_log, const void* beta, float scale, int l2norm) {
+  g_win_delta.on = true; g_win_delta.g_log = static_cast<const float*>(g_log);
+  g_win_delta.beta = static_cast<const float*>(beta); g_win_delta.scale = scale; g_win_delta.l2norm = l2norm;
+}
+
 // One decode / verify / replay call over the window records (`commit` = 0: read only). State tensors are the layer's
 // [slots, ...] views with the strides of contiguous tensors.
 int hb_mamba2_window(const void* x, const void* bmat, const void* cmat, const void* dt, long long ldx, long long ldb,
@@ -280,8 +353,12 @@ int hb_mamba2_window(const void* x, const void* bmat, const void* cmat, const vo
   p.has_init = static_cast<const int*>(has_init);
   p.batch = batch; p.heads = heads; p.groups = groups; p.p = head_dim; p.n = d_state; p.window = window; p.cap = cap;
   p.commit = commit; p.status = static_cast<int*>(status);
+  p.mode = g_win_delta.on ? 1 : 0; p.l2norm = g_win_delta.l2norm; p.scale = g_win_delta.scale;
+  p.g_log = g_win_delta.g_log; p.beta = g_win_delta.beta;
+  g_win_delta = WinDelta{};
   const int rec_cap = cap + kWinMaxRows;
-  const size_t smem = static_cast<size_t>(rec_cap) * d_state * 2 + (d_state + 2 * hg * rec_cap + rec_cap) * 4 +
+  const size_t smem = static_cast<size_t>(rec_cap) * d_state * 2 +
+                      (2 * d_state + 3 * hg * rec_cap + 2 * rec_cap + 2) * 4 +
                       static_cast<size_t>(kWinMaxRows) * hg * head_dim * 2;
   static size_t attr = 0;
   if (smem > 48 * 1024 && smem > attr) {

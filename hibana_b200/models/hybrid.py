@@ -130,7 +130,7 @@ class HybridModel:
                     "state_shape": (t.mamba_heads, t.mamba_head_dim, t.mamba_state), "groups": t.mamba_groups}
         if GDN in kinds:
             return {"layers": self.state_layers, "conv_dim": t.gdn_conv_dim, "conv_width": t.conv_width,
-                    "state_shape": (t.gdn_v_heads, t.gdn_head_dim, t.gdn_head_dim)}
+                    "state_shape": (t.gdn_v_heads, t.gdn_head_dim, t.gdn_head_dim), "groups": t.gdn_k_heads}
         return None
 
     def register_state(self, pool) -> None:

@@ -319,10 +319,14 @@ class GdnLayer:
                                max_rows=ctx.max_rows if ctx.q_indptr is not None else 0)
         z = qkvz[:, 2 * self.qk + self.vd:]
         br.join(beta, g)
-        o = recurrent.gdn_scan(qkv[:, :self.qk], qkv[:, self.qk:2 * self.qk], qkv[:, 2 * self.qk:], g, beta,
-                               states.ssm[li], ctx.state_slots, so, k_heads=t.gdn_k_heads, v_heads=t.gdn_v_heads,
-                               kdim=kd, vdim=kd, l2norm=True, q_indptr=ctx.q_indptr,
-                               has_init=ctx.has_initial_state, host_rows=ctx.seq_starts_host)
+        if getattr(states, "window", 0):
+            o = self._scan_window(qkv, g, beta, states, ctx.state_slots, ctx.q_indptr, ctx.has_initial_state,
+                                  ctx.seq_starts_host, commit="state_out" not in ctx.extras)
+        else:
+            o = recurrent.gdn_scan(qkv[:, :self.qk], qkv[:, self.qk:2 * self.qk], qkv[:, 2 * self.qk:], g, beta,
+                                   states.ssm[li], ctx.state_slots, so, k_heads=t.gdn_k_heads, v_heads=t.gdn_v_heads,
+                                   kdim=kd, vdim=kd, l2norm=True, q_indptr=ctx.q_indptr,
+                                   has_init=ctx.has_initial_state, host_rows=ctx.seq_starts_host)
         rows = o.shape[0]
         # per-head RMSNorm of the output, then the SiLU gate (norm before gate)
         key = (id(self.norm_w), self.norm_w._version)
@@ -335,12 +339,39 @@ class GdnLayer:
         y = basic.gated_rmsnorm(o, z, w, t.norm_eps, kd, norm_first=True, gemma=t.gemma_norm)
         return self.out_proj(y.view(rows, -1))
 
+    def _scan_window(self, qkv, g, beta, states, slots, q_indptr, has_init, host_rows, commit: bool) -> torch.Tensor:
+        """The delta rule over the window-record state format (ops/ssm_window.py `step_delta`): decode, verify and
+        replay rows in place (verify writes nothing); prefill chunks through a temporary fp32 state."""
+        from ..ops import ssm_window
+        t = self.t
+        kd = t.gdn_head_dim
+        ws = states.window_state(self.state_index)
+        q, k, v = qkv[:, :self.qk], qkv[:, self.qk:2 * self.qk], qkv[:, 2 * self.qk:]
+        long_rows = host_rows is not None and q_indptr is not None and max(host_rows) > ssm_window.MAX_ROWS
+        if not long_rows:
+            return ssm_window.step_delta(ws, q, k, v, g, beta, slots, l2norm=True, q_indptr=q_indptr, has_init=has_init,
+                                         commit=commit)
+        b = slots.shape[0]
+        dense = ssm_window.to_dense(ws, slots)
+        if has_init is not None:
+            dense = dense * has_init.to(dense.dtype).view(b, 1, 1, 1)
+        tmp = torch.arange(b, dtype=torch.int32, device=slots.device)
+        o = recurrent.gdn_scan(q, k, v, g, beta, dense, tmp, tmp, k_heads=t.gdn_k_heads, v_heads=t.gdn_v_heads,
+                               kdim=kd, vdim=kd, l2norm=True, q_indptr=q_indptr, host_rows=host_rows)
+        if commit:
+            ssm_window.from_dense(ws, slots, dense)
+        return o
+
     def replay(self, saved, sel, q_indptr, slots, states) -> None:
         t = self.t
         kd = t.gdn_head_dim
         li = self.state_index
         qkv = recurrent.conv1d(saved[0].index_select(0, sel), self.conv_w, None, states.conv[li], slots, slots,
                                q_indptr=q_indptr)
+        if getattr(states, "window", 0):
+            self._scan_window(qkv, saved[1].index_select(0, sel).contiguous(),
+                              saved[2].index_select(0, sel).contiguous(), states, slots, q_indptr, None, None, True)
+            return
         recurrent.gdn_scan(qkv[:, :self.qk], qkv[:, self.qk:2 * self.qk], qkv[:, 2 * self.qk:],
                            saved[1].index_select(0, sel).contiguous(), saved[2].index_select(0, sel).contiguous(),
                            states.ssm[li], slots, slots, k_heads=t.gdn_k_heads, v_heads=t.gdn_v_heads, kdim=kd,

@@ -22,6 +22,7 @@ from .. import _native as nv
 P_, I, L = nv.P, nv.I, nv.L
 nv.register("hb_mamba2_window", [P_, P_, P_, P_, L, L, L, P_, P_, P_, P_, L, P_, P_, P_, P_, P_, P_, P_, P_, P_,
                                  I, I, I, I, I, I, I, I, P_, P_])
+nv.register("hb_window_delta_rule", [P_, P_, nv.F, I], void=True)
 nv.register("hb_mamba2_window_io", [P_, P_, P_, P_, P_, P_, P_, P_, I, I, I, I, I, I, I, P_])
 
 EXTRA = 16          # records a call may append beyond the window before the next committing call folds
@@ -132,6 +133,82 @@ def step(ws: WindowState, x: torch.Tensor, bmat: torch.Tensor, cmat: torch.Tenso
                     ws.win_c[slot, g * hg:(g + 1) * hg, j] = cum
             if commit:
                 ws.win_len[slot, g] = len(rec_b)
+    return y
+
+
+def step_delta(ws: WindowState, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
+               beta: torch.Tensor, slots: torch.Tensor, *, scale: Optional[float] = None, l2norm: bool = True,
+               q_indptr: Optional[torch.Tensor] = None, has_init: Optional[torch.Tensor] = None,
+               commit: bool = True) -> torch.Tensor:
+    """The gated delta rule over the same record: heads = value heads, groups = key heads, a record is the row's
+    (normalised, fp16) key, its correction u = beta (v - (decayed state) k) and the running log decay. q, k
+    [T, key heads * K] (same row pitch), v [T, value heads * V] bf16; g, beta fp32 [T, value heads] contiguous."""
+    h, groups, p, n = ws.dims
+    t = q.shape[0]
+    batch = slots.shape[0]
+    scale = n ** -0.5 if scale is None else scale
+    if nv.use_native(q, ws.z):
+        assert q.stride(0) == k.stride(0) and g.is_contiguous() and beta.is_contiguous()
+        y = torch.empty(t, h * p, dtype=torch.bfloat16, device=q.device)
+        st = nv.device_state(q.device)
+        lib = nv.lib()
+        lib.hb_window_delta_rule(g.data_ptr(), beta.data_ptr(), float(scale), int(l2norm))
+        nv.check(lib.hb_mamba2_window(
+            v.data_ptr(), k.data_ptr(), q.data_ptr(), None, v.stride(0), k.stride(0), 0, None, None, None,
+            y.data_ptr(), y.stride(0), ws.z.data_ptr(), ws.zscale.data_ptr(), ws.win_b.data_ptr(), ws.win_u.data_ptr(),
+            ws.win_c.data_ptr(), ws.win_len.data_ptr(), nv.ptr(q_indptr), slots.data_ptr(), nv.ptr(has_init), batch, h,
+            groups, p, n, ws.window, ws.cap, int(commit), st.status.data_ptr(), nv.stream()), "hb_mamba2_window")
+        return y
+    hg = h // groups
+    y = torch.empty(t, h * p, dtype=torch.bfloat16)
+    ip = q_indptr.tolist() if q_indptr is not None else list(range(batch + 1))
+    for b in range(batch):
+        slot = int(slots[b])
+        fresh = has_init is not None and int(has_init[b]) == 0
+        rows = range(ip[b], ip[b + 1])
+        assert len(rows) <= MAX_ROWS
+        for gi in range(groups):
+            hs = slice(gi * hg, (gi + 1) * hg)
+            ln = 0 if fresh else int(ws.win_len[slot, gi])
+            if commit and (ln >= ws.window or fresh):
+                _fold_ref(ws, slot, gi, fresh)
+                ln = 0
+            zs = torch.zeros(hg, p) if (fresh and not commit) else ws.zscale[slot, hs].clone()
+            zq = ws.z[slot, hs].float()
+            rec_k = [ws.win_b[slot, gi, j].float() for j in range(ln)]
+            rec_u = [ws.win_u[slot, hs, j].float() for j in range(ln)]
+            rec_c = [ws.win_c[slot, hs, j].clone() for j in range(ln)]
+            cum = rec_c[-1].clone() if ln else torch.zeros(hg)
+            for r in rows:
+                qv = q[r].float().view(groups, n)[gi]
+                kv = k[r].float().view(groups, n)[gi]
+                if l2norm:
+                    qv = qv * torch.rsqrt(qv.pow(2).sum() + 1e-6)
+                    kv = kv * torch.rsqrt(kv.pow(2).sum() + 1e-6)
+                qv = qv * scale
+                kv = kv.to(torch.float16).float()
+                vv = v[r].float().view(h, p)[hs]
+                cum = cum + g[r].float()[hs]
+                gain = torch.exp(cum)[:, None] * zs
+                sk = gain * (zq @ kv)
+                out = gain * (zq @ qv)
+                for j in range(len(rec_k)):
+                    dec = torch.exp(cum - rec_c[j])
+                    sk = sk + (dec * (rec_k[j] @ kv))[:, None] * rec_u[j]
+                    out = out + (dec * (rec_k[j] @ qv))[:, None] * rec_u[j]
+                u = (beta[r].float()[hs][:, None] * (vv - sk)).to(torch.float16).float()
+                out = out + (kv @ qv) * u
+                rec_k.append(kv)
+                rec_u.append(u)
+                rec_c.append(cum.clone())
+                y[r].view(h, p)[hs] = out.to(torch.bfloat16)
+                if commit:
+                    j = len(rec_k) - 1
+                    ws.win_b[slot, gi, j] = kv.to(torch.float16)
+                    ws.win_u[slot, hs, j] = u.to(torch.float16)
+                    ws.win_c[slot, hs, j] = cum
+            if commit:
+                ws.win_len[slot, gi] = len(rec_k)
     return y
 
 

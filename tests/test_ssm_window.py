@@ -170,3 +170,94 @@ def test_engine_window_state_gpu():
     assert agree >= 0.4 * 72, agree
     torch.cuda.synchronize()
     assert nv.read_status() == 0
+
+
+def _gdn_inputs(t, kh, vh, kd, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    q = (torch.randn(t, kh * kd, generator=gen) * 0.5).bfloat16()
+    k = (torch.randn(t, kh * kd, generator=gen) * 0.5).bfloat16()
+    v = (torch.randn(t, vh * kd, generator=gen) * 0.5).bfloat16()
+    g = -torch.rand(t, vh, generator=gen) * 0.2
+    beta = torch.rand(t, vh, generator=gen)
+    return q, k, v, g, beta
+
+
+def test_delta_rule_over_window_records_cpu():
+    kh, vh, kd, w = 2, 4, 16, 5
+    q, k, v, g, beta = _gdn_inputs(30, kh, vh, kd)
+    pool = _pool(vh, kh, kd, kd, w)
+    ws = pool.window_state(0)
+    ref = torch.zeros(7, vh, kd, kd)
+    slot = torch.tensor([2], dtype=torch.int32)
+    ys, yr = [], []
+    for r in range(30):
+        init = torch.tensor([0 if r == 0 else 1], dtype=torch.int32)
+        sl = slice(r, r + 1)
+        ys.append(ssm_window.step_delta(ws, q[sl], k[sl], v[sl], g[sl], beta[sl], slot, has_init=init))
+        yr.append(recurrent.gdn_scan(q[sl], k[sl], v[sl], g[sl], beta[sl], ref, slot, slot, k_heads=kh, v_heads=vh,
+                                     kdim=kd, vdim=kd, has_init=init))
+    ys, yr = torch.cat(ys).float(), torch.cat(yr).float()
+    assert (ys - yr).abs().max() <= 0.04 * yr.abs().max()
+    dense = ssm_window.to_dense(ws, slot)[0]
+    assert (dense - ref[2]).abs().max() <= 0.04 * ref[2].abs().max()
+    # read-only rows equal the committing replay up to the fold the replay starts with
+    q2, k2, v2, g2, b2 = _gdn_inputs(4, kh, vh, kd, seed=5)
+    ip = torch.tensor([0, 4], dtype=torch.int32)
+    before = ws.win_len.clone()
+    ro = ssm_window.step_delta(ws, q2, k2, v2, g2, b2, slot, q_indptr=ip, commit=False)
+    assert torch.equal(before, ws.win_len)
+    co = ssm_window.step_delta(ws, q2, k2, v2, g2, b2, slot, q_indptr=ip)
+    assert (ro.float() - co.float()).abs().max() <= 0.04 * ro.float().abs().max()
+
+
+@pytest.mark.gpu
+def test_delta_rule_window_kernel_and_engine_gpu():
+    """The delta-rule mode of the kernel against its CPU reference (Flash-Next head geometry), and a Qwen3.8-hybrid
+    style stack decoding with the int8w state through graphs and captured speculative rounds."""
+    from hibana_b200 import _native as nv
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import qwen38_hybrid, scaled
+    kh, vh, kd, w = 4, 12, 128, 8
+    q, k, v, g, beta = _gdn_inputs(2 * (w + 6), kh, vh, kd, seed=2)
+    cpu, gpu = _pool(vh, kh, kd, kd, w), _pool(vh, kh, kd, kd, w, "cuda")
+    wc, wg = cpu.window_state(0), gpu.window_state(0)
+    slots = torch.tensor([1, 3], dtype=torch.int32)
+    r = 0
+    for step in range(w + 4):
+        sl = slice(r, r + 2)
+        init = torch.tensor([0, 0] if step == 0 else [1, 1], dtype=torch.int32)
+        yc = ssm_window.step_delta(wc, q[sl], k[sl], v[sl], g[sl], beta[sl], slots, has_init=init)
+        yg = ssm_window.step_delta(wg, q[sl].cuda(), k[sl].cuda(), v[sl].cuda(), g[sl].cuda().contiguous(),
+                                   beta[sl].cuda().contiguous(), slots.cuda(), has_init=init.cuda())
+        assert (yg.float().cpu() - yc.float()).abs().max() <= 3e-2 * max(yc.float().abs().max().item(), 1e-3)
+        r += 2
+    ip = torch.tensor([0, 3, 4], dtype=torch.int32)
+    sl = slice(r, r + 4)
+    for commit in (False, True):
+        yc = ssm_window.step_delta(wc, q[sl], k[sl], v[sl], g[sl], beta[sl], slots, q_indptr=ip, commit=commit)
+        yg = ssm_window.step_delta(wg, q[sl].cuda(), k[sl].cuda(), v[sl].cuda(), g[sl].cuda().contiguous(),
+                                   beta[sl].cuda().contiguous(), slots.cuda(), q_indptr=ip.cuda(), commit=commit)
+        assert (yg.float().cpu() - yc.float()).abs().max() <= 3e-2 * max(yc.float().abs().max().item(), 1e-3)
+    assert torch.equal(wg.win_len.cpu(), wc.win_len)
+    torch.cuda.synchronize()
+    assert nv.read_status() == 0
+    t = scaled(qwen38_hybrid(), layers=4, hidden=512, vocab=2048, q_heads=4, kv_heads=2, head_dim=128, ffn=1024,
+               gdn_k_heads=2, gdn_v_heads=4, gdn_head_dim=128, mtp_layers=1, mtp_depth=2, kv_dtype="bf16")
+    m = HybridModel(t, "cuda", seed=0, init_device="cpu")
+    gen = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, t.vocab, (n,), generator=gen).tolist() for n in (40, 27)]
+    sp = SamplingParams(max_tokens=16)
+    kw = dict(max_batch=2, max_ctx=128, state_dtype=torch.int8, state_window=8, radix_cache=False)
+    eager = [r_.output_ids for r_ in Executor(m, use_graphs=False, **kw).generate_batch(prompts, sp)]
+    ex = Executor(m, use_graphs=True, buckets=(1, 2), **kw)
+    ex.capture_graphs()
+    assert [r_.output_ids for r_ in ex.generate_batch(prompts, sp)] == eager
+    spec = Executor(m, use_graphs=True, buckets=(1, 2), **kw)
+    spec.enable_spec(2)
+    spec.capture_graphs()
+    out = [r_.output_ids for r_ in spec.generate_batch(prompts, sp)]
+    assert all(len(o) == 16 for o in out) and spec.spec.graphs.rounds > 0
+    torch.cuda.synchronize()
+    assert nv.read_status() == 0
