@@ -97,6 +97,43 @@ def main() -> None:
     # sampling over the 27B vocabulary
     lg = torch.randn(64, 151936, generator=g, device=dev)
     op("argmax rows=64 vocab=151936", 64 * 151936 * 4, lambda: sampling.argmax(lg))
+    # weight formats beside NVFP4 at a decode batch: FP8 (tcgen05 kind::f8f6f4), 3-bit (dequantisation fused into the
+    # GEMM), GGML IQ2_XXS (decode fused into the GEMV)
+    from ..ops import ggml as ggml_ops
+    from ..ops.w3gemm import W3Linear
+    wm, wn, wk = 64, 5120, 17408
+    xa = rnd(wm, wk)
+    wf = fp8.Fp8Weight.quantize(rnd(wn, wk, scale=0.02))
+    xq8, xs8 = fp8.quantize_rows(xa)
+    op(f"fp8 GEMM {wm} x {wn} x {wk}", wn * wk, lambda: fp8.linear_fp8(xq8, wf, row_scales=xs8))
+    w3 = W3Linear.from_weight(rnd(wn, wk, scale=0.02).float().cpu(), dev, keep_codes=False)
+    op(f"3-bit GEMM {wm} x {wn} x {wk} (codes + scale / zero per 64)", wn * wk * (3 / 8 + 4 / 64), lambda: w3(xa))
+    gn, gk = 4096, 4096
+    grid = (torch.arange(256 * 8, dtype=torch.int64) % 3 * 8 + 1).view(256, 8).to(torch.uint8)
+    pl = ggml_ops.PackedLinear(ggml_ops.random_blocks("iq2_xxs", gn, gk, seed=1).to(dev), "iq2_xxs", gn, gk, grid)
+    x1 = rnd(1, gk)
+    op(f"GGML IQ2_XXS GEMV 1 x {gn} x {gk}", gn * gk * 66 / 256, lambda: pl(x1))
+    q8 = ggml_ops.PackedLinear(ggml_ops.random_blocks("q8_0", gn, gk, seed=2).to(dev), "q8_0", gn, gk)
+    op(f"GGML Q8_0 GEMV 1 x {gn} x {gk}", gn * gk * 34 / 32, lambda: q8(x1))
+    # SSD tier gather: 256 token rows of all layers of a 27B-shaped bf16 KV pool into one staging buffer
+    from ..cache.kv_pool import KvPool
+    kvp = KvPool(64, 4096, 8, 128, torch.bfloat16, dev)
+    ids = torch.randperm(4000, device=dev)[:256].int() + 1
+    stage = torch.empty(256 * kvp.bytes_per_token, dtype=torch.uint8, device=dev)
+    op("kv gather 256 tokens x 64 layers (pool -> staging)", 2 * 256 * kvp.bytes_per_token,
+       lambda: kvp.copy_payload(ids, stage, to_pool=False))
+    # hyper-connection site at Flash-Next width
+    from ..models.hyper import HyperConnection
+    hc_, hh_, rk_ = 4, 2560, 320
+    site = HyperConnection(torch.zeros(hc_ * hh_, device=dev), rnd(rk_, hc_ * hh_, scale=0.02), rnd(hc_ * hh_, rk_, scale=0.02),
+                           rnd(hc_, hc_ * hh_, scale=0.02), hc_, hh_)
+    hyp, blk = rnd(32, hc_ * hh_), rnd(32, hh_)
+
+    def hyper_site():
+        mixed, keep = site.mix(hyp)
+        return site.combine(blk, keep)
+    op("hyper-connection mix + combine, 32 rows x 4 streams x 2560 (6 launches)",
+       (rk_ + 16 + hc_ * hh_) * hc_ * hh_ * 2 * 0 + (site.down_inject.numel() + site.up.numel()) * 2, hyper_site)
     for name, nbytes, fn in ops:
         if args.only and args.only not in name:
             continue
