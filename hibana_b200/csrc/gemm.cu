@@ -681,6 +681,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
       // fully coalesced 16-byte stores: to the local output, or (scatter) to the staging rows of the rank that
       // owns them, over NVLink.
       const bool silu_mul = p.epilogue == kEpiSiluMul;
+      const bool quant = p.epilogue == kEpiSiluMulQuant;
+      const float q_inv_gs = quant ? 1.f / *p.q_gscale : 0.f;
       constexpr int PITCH = BN * 2 + 16;
       uint8_t* tile = smem + static_cast<size_t>(q) * 32 * PITCH;
       uint8_t* my_row = tile + lane * PITCH;
@@ -689,7 +691,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         if constexpr (CH == 32) tmem_ld_32x32(tlane + c0, r);
         else tmem_ld_32x16(tlane + c0, r);
         tmem_ld_wait();
-        if (silu_mul) {
+        if (quant) {
+          // SiLU-mul + NVFP4 requantisation: a thread's 32 accumulator columns are 16 gate / up pairs, exactly one
+          // 16-feature group of its token: 8 packed bytes at [c0 / 4] of the parked row and one scale byte behind
+          // the BN / 4 packed bytes. Same arithmetic, in the same order, as the swapped epilogue (epilogue_rows4)
+          // and the stand-alone quantiser.
+          if constexpr (CH == 32) {
+            float y[16];
+#pragma unroll
+            for (int t = 0; t < 16; ++t)
+              y[t] = __bfloat162float(__float2bfloat16(silu(__uint_as_float(r[2 * t]) * alpha) *
+                                                       (__uint_as_float(r[2 * t + 1]) * alpha)));
+            const uint32_t sfb = quant16(y, q_inv_gs, reinterpret_cast<uint2*>(my_row + c0 / 4));
+            my_row[BN / 4 + c0 / 32] = static_cast<uint8_t>(sfb);
+          }
+        } else if (silu_mul) {
           uint32_t w[CH / 4];
 #pragma unroll
           for (int t = 0; t < CH / 4; ++t)
@@ -709,12 +725,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUt
         }
       }
       __syncwarp();
+      if (quant) {
+        // packed bytes: BN / 4 per row = BN / 64 16-byte chunks of two groups each, whole rows per store instruction
+        constexpr int QCH = BN >= 64 ? BN / 64 : 1;     // (this branch runs with BN >= 64 only)
+        constexpr int ROWS = 32 / QCH;
+        for (int r0 = 0; r0 < 32; r0 += ROWS) {
+          const int lr = r0 + lane / QCH;
+          const int ch = lane % QCH;
+          const int grow = tile_a * BM + q * 32 + lr;
+          if (grow < row_lim && b_row0 + ch * 64 + 64 <= col_lim)
+            *reinterpret_cast<uint4*>(p.q_out + static_cast<size_t>(grow) * p.q_ld + (b_row0 >> 2) + ch * 16) =
+                *reinterpret_cast<const uint4*>(tile + lr * PITCH + ch * 16);
+        }
+        // scale bytes: each lane writes its own row's BN / 32 groups (four groups of a K atom are one 32-bit word
+        // of the swizzled block; the feature count is a multiple of 64, so groups come in valid pairs)
+        const int grow = tile_a * BM + q * 32 + lane;
+        if (grow < row_lim) {
+#pragma unroll
+          for (int g2 = 0; g2 < BN / 64; ++g2) {
+            if (b_row0 + g2 * 64 + 64 <= col_lim)
+              *reinterpret_cast<uint16_t*>(p.q_sf + row_sf_off(grow, (b_row0 >> 5) + 2 * g2, p.q_ka)) =
+                  *reinterpret_cast<const uint16_t*>(my_row + BN / 4 + 2 * g2);
+          }
+        }
+      }
       const int out_cols = silu_mul ? BN / 2 : BN;            // columns this tile produces
       const int chunks = out_cols / 8;                          // 16-byte chunks per row
       const int rows_per_instr = 32 / chunks > 0 ? 32 / chunks : 1;
       const int col_base = silu_mul ? (b_row0 >> 1) : b_row0;   // first output column of the tile
       const int col_end = silu_mul ? (col_lim >> 1) : col_lim;
-      for (int r0 = 0; r0 < 32; r0 += rows_per_instr) {
+      for (int r0 = quant ? 32 : 0; r0 < 32; r0 += rows_per_instr) {   // (the quantising epilogue has stored)
         for (int cc = 0; cc < chunks; cc += 32) {
           const int lr = r0 + (chunks >= 32 ? 0 : lane / chunks);
           const int ch = chunks >= 32 ? cc + lane : lane % chunks;
@@ -1090,8 +1130,14 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   if (a.epilogue == kEpiSiluMulQuant) {
     // tokens on the N side, whole 128-row feature tiles, no grouped / peer variants; the staging tile of a split-K
     // CTA sits behind its fp32 partial, which the smallest ring must still hold
-    if (!a.swap || grouped || a.peer != nullptr || a.tok_scale != nullptr || a.ra % BM != 0 || a.q_out == nullptr ||
-        a.q_sf == nullptr || a.q_gscale == nullptr || a.q_ka * 64 < a.ra / 2 || a.bn > 128)
+    if (grouped || a.peer != nullptr || a.tok_scale != nullptr || a.q_out == nullptr || a.q_sf == nullptr ||
+        a.q_gscale == nullptr)
+      return cudaErrorInvalidValue;
+    if (a.swap && (a.ra % BM != 0 || a.q_ka * 64 < a.ra / 2 || a.bn > 128)) return cudaErrorInvalidValue;
+    // tokens on the 128-row side: the staged epilogue (output tiles of 128 or 256 columns, no split-K) writes the
+    // packed bytes as aligned 16-byte chunks of two groups: feature count a multiple of 64
+    if (!a.swap && (a.rb % 64 != 0 || a.q_ka * 64 < a.rb / 2 || a.splits != 1 || (a.bn != 128 && a.bn != 256) ||
+                    a.q_ld % 16 != 0 || (reinterpret_cast<uintptr_t>(a.q_out) & 15) != 0))
       return cudaErrorInvalidValue;
   }
   p.early_launch = g_pdl >= 2;
@@ -1165,6 +1211,24 @@ int hb_gemm_silu_quant(int kind, const void* a, const void* b, const void* sfa, 
   g.kind = kind; g.a = a; g.b = b; g.sfa = sfa; g.sfb = sfb; g.ra = n; g.rb = m; g.k = k;
   g.lda = lda; g.ldb = ldb; g.out = nullptr; g.ldo = 0; g.residual = nullptr; g.alpha = 1.f;
   g.alpha_ptr = static_cast<const float*>(alpha_ptr); g.epilogue = hb::kEpiSiluMulQuant; g.swap = 1; g.splits = splits;
+  g.workspace = nullptr; g.counters = nullptr; g.status = static_cast<int*>(status); g.bn = bn;
+  g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
+  g.grp_start = nullptr; g.grp_cnt = nullptr; g.grp_rows_a = 0; g.grp_experts = 0; g.grp_chunks = 0;
+  g.peer = nullptr;
+  g.q_out = q_out; g.q_sf = q_sf; g.q_gscale = static_cast<const float*>(q_gscale); g.q_ka = q_ka; g.q_ld = n / 4;
+  const cudaError_t e = hb::gemm_launch(g, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+// The same epilogue with the tokens on the 128-row side (a = activations [m, k], b = weights [n, k]): prefill-sized
+// calls. n a multiple of 64, no split-K.
+int hb_gemm_silu_quant_rows(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int m, int n,
+                            int k, long long lda, long long ldb, const void* alpha_ptr, void* q_out, void* q_sf,
+                            const void* q_gscale, int q_ka, void* status, int bn, int ka_a, int ka_b, void* stream) {
+  hb::GemmArgs g;
+  g.kind = kind; g.a = a; g.b = b; g.sfa = sfa; g.sfb = sfb; g.ra = m; g.rb = n; g.k = k;
+  g.lda = lda; g.ldb = ldb; g.out = nullptr; g.ldo = 0; g.residual = nullptr; g.alpha = 1.f;
+  g.alpha_ptr = static_cast<const float*>(alpha_ptr); g.epilogue = hb::kEpiSiluMulQuant; g.swap = 0; g.splits = 1;
   g.workspace = nullptr; g.counters = nullptr; g.status = static_cast<int*>(status); g.bn = bn;
   g.sf_k_atoms_a = ka_a; g.sf_k_atoms_b = ka_b;
   g.grp_start = nullptr; g.grp_cnt = nullptr; g.grp_rows_a = 0; g.grp_experts = 0; g.grp_chunks = 0;

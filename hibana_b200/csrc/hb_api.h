@@ -20,6 +20,11 @@ int hb_gemm_silu_quant(int kind, const void* a, const void* b, const void* sfa, 
                        long long lda, long long ldb, const void* alpha_ptr, void* q_out, void* q_sf,
                        const void* q_gscale, int q_ka, int splits, void* status, int bn, int ka_a, int ka_b,
                        void* stream);
+// The same epilogue for prefill-sized calls: a = activations [m, k] on the 128-row side, b = weights [n, k];
+// n a multiple of 32, no split-K.
+int hb_gemm_silu_quant_rows(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int m, int n,
+                            int k, long long lda, long long ldb, const void* alpha_ptr, void* q_out, void* q_sf,
+                            const void* q_gscale, int q_ka, void* status, int bn, int ka_a, int ka_b, void* stream);
 int hb_gemm_grouped(int kind, const void* a, const void* b, const void* sfa, const void* sfb, int experts,
                     int n_per_expert, int b_rows, int k, void* out, long long ldo, const void* alpha_ptr,
                     int epilogue, const void* start, const void* cnt, int max_rows_per_expert, void* status, int ka_a,

@@ -227,9 +227,14 @@ class DenseModel:
                                             quant_scale=layer.o.input_scale if fuse else None)
             h, slot = self._row_parallel(layer.o, att if isinstance(att, nvfp4.Nvfp4Tensor)
                                          else att.view(att.shape[0], -1), ctx)
+            # prefill-sized chunks requantise in the gate/up epilogue too (tokens on the 128-row side of the GEMM):
+            # the bf16 activation [rows, intermediate] is never written
+            fuse_mlp = fuse or (cfgmod.current().fuse_epilogues and q.is_cuda and layer.down.fmt == "nvfp4"
+                                and not layer.down.calibrating and layer.gate_up.fmt == "nvfp4"
+                                and gemm.requant_ok(q.shape[0], layer.gate_up.out_features))
             act = self._reduce_norm_linear(h, slot, res, layer.post_norm, layer.gate_up, ctx,
                                            epilogue=gemm.EPI_SILU_MUL,
-                                           requant=layer.down.input_scale if fuse else None)
+                                           requant=layer.down.input_scale if fuse_mlp else None)
             h, slot = self._row_parallel(layer.down, act, ctx)
         comm = ctx.comm
         if comm is not None and slot is not None:

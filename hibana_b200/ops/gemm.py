@@ -24,6 +24,8 @@ nv.register("hb_gemm_set_pdl", [nv.I], void=True)
 nv.register("hb_gemm_set_local_reduce", [nv.I], void=True)
 nv.register("hb_gemm_silu_quant", [nv.I, nv.P, nv.P, nv.P, nv.P, nv.I, nv.I, nv.I, nv.L, nv.L, nv.P, nv.P, nv.P, nv.P,
                                    nv.I, nv.I, nv.P, nv.I, nv.I, nv.I, nv.P])
+nv.register("hb_gemm_silu_quant_rows", [nv.I, nv.P, nv.P, nv.P, nv.P, nv.I, nv.I, nv.I, nv.L, nv.L, nv.P, nv.P, nv.P,
+                                        nv.P, nv.I, nv.P, nv.I, nv.I, nv.I, nv.P])
 
 
 _PDL_INIT = False
@@ -149,8 +151,10 @@ _REQUANT_BUFS: dict = {}
 
 
 def requant_ok(m: int, n: int) -> bool:
-    """Shapes the fused SiLU-mul + requant epilogue covers: weights on the 128-row side, whole feature tiles."""
-    return m <= 128 and n % 128 == 0
+    """Shapes the fused SiLU-mul + requant epilogue covers: decode-sized calls with the weights on the 128-row side
+    and whole feature tiles, and prefill-sized calls (tokens on the 128-row side, `_plan` picks that above 256 rows)
+    whose feature count is a multiple of 64 (aligned 16-byte chunks of packed values)."""
+    return (m <= 128 and n % 128 == 0) or (m > 256 and n % 64 == 0)
 
 
 def linear_nvfp4_silu_quant(x: Nvfp4Tensor, w: Nvfp4Tensor, alpha: torch.Tensor, out_scale: torch.Tensor, *,
@@ -164,6 +168,21 @@ def linear_nvfp4_silu_quant(x: Nvfp4Tensor, w: Nvfp4Tensor, alpha: torch.Tensor,
     if not nv.use_native(x.q, w.q) or not requant_ok(m, n):
         return nvfp4.quantize(linear_nvfp4(x, w, alpha, epilogue=EPI_SILU_MUL), out_scale)
     ko = n // 2
+    if m > 128:
+        # prefill-sized: fresh buffers (chunk lengths vary and nothing here is captured); scale bytes the kernel
+        # does not write (padding rows of the last 128-row block, padding groups of the last K atom) must read zero
+        q, sf = nvfp4._alloc(m, ko, x.q.device)
+        if m % 128 or ko % 64:
+            sf.zero_()
+        if not _PDL_INIT:
+            set_pdl(cfgmod.current().pdl)
+        st = nv.device_state(q.device)
+        code = nv.lib().hb_gemm_silu_quant_rows(1, x.q.data_ptr(), w.q.data_ptr(), x.sf.data_ptr(), w.sf.data_ptr(),
+                                                m, n, k, k, k, alpha.data_ptr(), q.data_ptr(), sf.data_ptr(),
+                                                out_scale.data_ptr(), sf.shape[1], st.status.data_ptr(),
+                                                256 if n >= 256 else 128, x.ka, w.ka, nv.stream())
+        nv.check(code, "hb_gemm_silu_quant_rows")
+        return Nvfp4Tensor(q, sf, out_scale, m, ko)
     key = (x.q.device, m, ko)
     bufs = _REQUANT_BUFS.get(key)
     if bufs is None:

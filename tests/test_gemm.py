@@ -194,11 +194,12 @@ def test_w3_dequant_fused_gemm(m, n, k):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (7, 1024, 5120), (64, 4352, 5120), (64, 34816, 1024), (100, 512, 768)])
+@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (7, 1024, 5120), (64, 4352, 5120), (64, 34816, 1024), (100, 512, 768),
+                                   (300, 192, 512), (300, 96, 512), (384, 4352, 1024), (1000, 2176, 768), (2048, 1024, 512)])
 def test_silu_mul_requant_epilogue_matches_two_kernels(m, n, k):
     """gate/up GEMM with the SiLU-mul + NVFP4 requant epilogue == the SiLU-mul GEMM followed by the quantiser,
-    byte for byte (packed values and every scale byte of real rows), for unsplit and cluster split-K launches;
-    and the dequantised result is close to the fp32 reference of the same op."""
+    byte for byte (packed values and every scale byte of real rows), for unsplit and cluster split-K launches and
+    for prefill-sized calls (more than 256 rows: tokens on the 128-row side of the MMA); and the dequantised result is close to the fp32 reference of the same op."""
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(m * 7 + n)
     w = torch.randn(n, k, device=dev, generator=g) * 0.05
