@@ -130,21 +130,26 @@ class LLM:
         """`comm`: tensor-parallel communicator (cfg.tp ranks run the same requests). `control` + `rank`: this
         process is replica `rank` of cfg.dp data-parallel replicas and `control(obj) -> list` all-gathers small
         host objects between them (engine/dp.py); with cfg.ep == cfg.dp the replicas share every MoE layer's experts
-        through the all-to-all of parallel/ep.py and run their forwards together."""
+        through the all-to-all of parallel/ep.py and run their forwards together. Both: replica `rank` is a
+        tensor-parallel group; `control` goes to the group's rank 0 only."""
         self.cfg = cfg = cfg or current()
         full = target or get_target(cfg.target)
         self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
         tp = comm.world if comm is not None and cfg.tp > 1 else 1
         self.lockstep = self.ep = None
         if cfg.dp > 1:
-            if cfg.tp != 1:
-                raise NotImplementedError("data-parallel replicas of tensor-parallel groups are not supported")
-            if control is None or rank is None:
-                raise ValueError("dp > 1 needs the replicas' control all-gather and this replica's rank")
-            from .dp import Lockstep
-            self.lockstep = Lockstep(control, rank, cfg.dp)
+            if tp > 1 and cfg.ep not in (1, cfg.tp):
+                raise NotImplementedError("expert parallelism across data-parallel replicas of tensor-parallel "
+                                          "groups is not supported (experts shard inside a group: ep = tp)")
+            # replicas of tensor-parallel groups: the group's rank 0 speaks for the replica, the others follow its
+            # commands (engine/loop.py) and take no part in the replicas' rounds
+            if not (tp > 1 and comm.rank != 0):
+                if control is None or rank is None:
+                    raise ValueError("dp > 1 needs the replicas' control all-gather and this replica's rank")
+                from .dp import Lockstep
+                self.lockstep = Lockstep(control, rank, cfg.dp)
         rank = comm.rank if comm is not None else (rank or 0)
-        ep = cfg.ep if cfg.dp > 1 and cfg.ep == cfg.dp else 1
+        ep = cfg.ep if cfg.dp > 1 and tp == 1 and cfg.ep == cfg.dp else 1
         self.model = model or build_model(full, self.device, cfg.seed, comm, cfg.weights, tp=tp, rank=rank, ep=ep)
         self.target = self.model.target
         if cfg.w3 and hasattr(self.model, "attach_w3") and model is None:

@@ -6,7 +6,8 @@ every publish point, so all ranks step their schedulers identically; a failure f
 engine unhealthy. With data-parallel replicas (`dp`, an engine/dp.py Lockstep) rank 0 still owns HTTP and the
 inbox but every request has ONE owner: rank 0 picks the replica (least outstanding work, conversations stay with
 their cached prefix), commands and generated tokens travel with the lockstep rounds, and the replicas schedule
-independently. Reference: hibana/engine/loop.py:47-320.
+independently. A replica that is itself a tensor-parallel group has both: its leader joins the rounds and
+broadcasts what it applies to its followers. Reference: hibana/engine/loop.py:47-320.
 """
 from __future__ import annotations
 
@@ -167,6 +168,8 @@ class EngineLoop:
                 self.sched.cancel(ticket.request)
         elif kind == "stop":
             self.stopping = True
+        elif kind == "failed":          # the leader of this tensor-parallel group gave up
+            raise RuntimeError(f"group leader failed: {cmd[1]}")
 
     def _gather_commands(self) -> list:
         cmds = []
@@ -285,11 +288,18 @@ class EngineLoop:
         try:
             while True:
                 cmds = self._route(self._gather_commands()) if self.rank == 0 else []
-                for c in cmds + self._take_mail():
+                cmds = cmds + self._take_mail()
+                if self.channel is not None:
+                    # this replica is a tensor-parallel group: its followers apply the same commands and so take
+                    # the same steps. `stop` reaches them when this loop ends, not when it is asked to.
+                    self.channel.broadcast([c for c in cmds if c[0] != "stop"])
+                for c in cmds:
                     self._apply(c)
                 if self.sched.idle():
                     states = ex.idle_round(LEAVING if self.stopping else RUNNING)
                     if self.stopping and all(s == LEAVING for s in states):
+                        if self.channel is not None:
+                            self.channel.broadcast([("stop",)])
                         break
                     if 1 not in states and not self._mail:
                         time.sleep(self.idle_sleep)
@@ -300,6 +310,8 @@ class EngineLoop:
         except Exception as e:  # noqa: BLE001 - every failure takes the engine down cleanly
             try:
                 self.dp.post(("failed", f"{type(e).__name__}: {e}"))
+                if self.channel is not None:
+                    self.channel.broadcast([("failed", f"{type(e).__name__}: {e}")])
             finally:
                 self._fail(f"{type(e).__name__}: {e}")
 

@@ -300,7 +300,7 @@ class Communicator:
 
     def broadcast(self, obj=None, src: int = 0):
         box = [obj]
-        dist.broadcast_object_list(box, src=src, group=self.group)
+        dist.broadcast_object_list(box, group_src=src, group=self.group)
         return box[0]
 
 
@@ -354,7 +354,7 @@ class GlooCommunicator:
 
     def broadcast(self, obj=None, src: int = 0):
         box = [obj]
-        dist.broadcast_object_list(box, src=src, group=self.group)
+        dist.broadcast_object_list(box, group_src=src, group=self.group)
         return box[0]
 
     def check_status(self) -> None:

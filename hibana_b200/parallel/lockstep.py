@@ -18,19 +18,56 @@ class BroadcastChannel:
     """Commands are plain picklable tuples; tickets and notifiers never cross ranks."""
 
     def __init__(self, group=None, src: int = 0):
+        """`src`: the sender's rank within `group` (a tensor-parallel group's leader is its rank 0)."""
         self.group, self.src = group, src
 
     def broadcast(self, obj=None):
         box = [obj]
-        dist.broadcast_object_list(box, src=self.src, group=self.group)
+        dist.broadcast_object_list(box, group_src=self.src, group=self.group)
         return box[0]
+
+
+class ThreadBroadcast:
+    """The same channel between threads of one process (tests): `view(0)` sends, the other views receive."""
+
+    def __init__(self, world: int, timeout: float = 60.0):
+        import queue
+        self.timeout = timeout
+        self.queues = [queue.Queue() for _ in range(world)]
+
+    def view(self, rank: int):
+        outer = self
+
+        class _View:
+            def broadcast(self, obj=None):
+                if rank == 0:
+                    for q in outer.queues[1:]:
+                        q.put(obj)
+                    return obj
+                return outer.queues[rank].get(timeout=outer.timeout)
+        return _View()
+
+
+def replica_groups(dp: int, tp: int, rank: int, device_backend: str = "nccl", timeout_s: float = 30.0):
+    """Process groups of data-parallel replicas that are tensor-parallel groups: ranks [g * tp, (g + 1) * tp) are
+    replica g. Returns (this rank's group for tensor collectives, the same ranks as a host group with a timeout for
+    the leader's command broadcast, the host group of the replicas' leaders). Collective over the world: every
+    rank creates every group, in the same order."""
+    import datetime
+    limit = datetime.timedelta(seconds=timeout_s)
+    members = [list(range(g * tp, (g + 1) * tp)) for g in range(dp)]
+    device = [dist.new_group(ranks=m, backend=device_backend) for m in members]
+    host = [dist.new_group(ranks=m, backend="gloo", timeout=limit) for m in members]
+    leaders = dist.new_group(ranks=[m[0] for m in members], backend="gloo", timeout=limit)
+    return device[rank // tp], host[rank // tp], leaders
 
 
 def serve_rank(cfg) -> int:
     """One rank of a multi-GPU server (rank 0 also serves HTTP). Tensor parallel (the default), every family: the
     dense decoder and the hybrids shard their mixers by head, MLPs by column and experts by expert range over the
-    ranks (`build_model`). With `dp` > 1 the ranks are data-parallel replicas instead. The engine stack itself
-    comes from the settings (`LLM`), the same as on one GPU."""
+    ranks (`build_model`). With `dp` > 1 the ranks are data-parallel replicas instead, each one GPU or (with `tp` > 1
+    too) a tensor-parallel group of `tp` GPUs. The engine stack itself comes from the settings (`LLM`), the same as
+    on one GPU."""
     import datetime
 
     from ..api.chat_template import ChatTemplate
@@ -49,11 +86,28 @@ def serve_rank(cfg) -> int:
     # the control plane has a timeout: a rank that stops answering ends the others' next broadcast with an error
     control = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=max(cfg.control_timeout_s, 5)))
     cfg = BroadcastChannel(control).broadcast(cfg if rank == 0 else None)     # every rank serves rank 0's settings
-    if cfg.dp > 1:
+    if cfg.dp * cfg.tp != world and cfg.dp > 1:
+        raise ValueError(f"dp={cfg.dp} x tp={cfg.tp} does not match the {world} ranks that were started")
+    if cfg.dp > 1 and cfg.tp > 1:
+        # data-parallel replicas of tensor-parallel groups: ranks [g * tp, (g + 1) * tp) are replica g. The group
+        # has its own NCCL group and peer heap; its rank 0 is the replica's leader: it takes part in the replicas'
+        # rounds and passes every command it applies on to its followers (engine/loop.py). Every rank takes part in
+        # the creation of every group.
+        tp, group, tp_rank = cfg.tp, rank // cfg.tp, rank % cfg.tp
+        device_group, host_group, leaders = replica_groups(cfg.dp, tp, rank, "nccl", max(cfg.control_timeout_s, 5))
+        comm = Communicator.create(tp_rank, tp, dev, slot_mb=cfg.comm_buffer_mb // 8 or 1,
+                                   timeout_ms=cfg.comm_timeout_ms, fused=cfg.fused_collectives, group=device_group)
+        from ..engine.dp import GroupAllGather
+        channel = BroadcastChannel(host_group)
+        if tp_rank == 0:
+            llm = LLM(cfg, device=dev, comm=comm, control=GroupAllGather(leaders), rank=group, warmup=True)
+            engine = EngineLoop(llm.scheduler, channel=channel, rank=group, dp=llm.lockstep).start()
+        else:
+            llm = LLM(cfg, device=dev, comm=comm, warmup=True)
+            engine = EngineLoop(llm.scheduler, channel=channel, rank=tp_rank).start()
+    elif cfg.dp > 1:
         # data-parallel replicas (one per GPU), expert-parallel MoE layers between them when cfg.ep == cfg.dp: every
         # replica schedules its own requests; rank 0 routes them and collects the tokens (engine/loop.py, engine/dp.py)
-        if cfg.dp * cfg.tp != world:
-            raise ValueError(f"dp={cfg.dp} x tp={cfg.tp} does not match the {world} ranks that were started")
         from ..engine.dp import GroupAllGather
         llm = LLM(cfg, device=dev, control=GroupAllGather(control), rank=rank, warmup=True)
         engine = EngineLoop(llm.scheduler, rank=rank, dp=llm.lockstep).start()

@@ -157,3 +157,83 @@ def test_engine_loops_of_two_replicas_route_requests_and_stream_back_to_rank0():
     loops[1].thread.join(30)
     assert not loops[0].thread.is_alive() and not loops[1].thread.is_alive()
     assert loops[0].healthy and loops[1].healthy
+
+
+def test_replicas_of_tensor_parallel_groups_route_follow_and_stop():
+    """dp = 2 replicas, each a tp = 2 group (four engine threads): rank 0 of replica 0 owns the inbox and routes;
+    each group's leader joins the replicas' rounds and its follower applies the commands the leader broadcasts, so
+    both ranks of a group take the same steps; tokens come back to rank 0's tickets; `stop` ends all four loops."""
+    import threading
+
+    from hibana_b200.config import EngineConfig
+    from hibana_b200.engine.dp import ThreadAllGather
+    from hibana_b200.engine.llm import LLM
+    from hibana_b200.engine.loop import EngineLoop
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.parallel.lockstep import ThreadBroadcast
+    from hibana_b200.target import dense_tiny, scaled
+    from test_tp import ThreadComm
+    t = scaled(dense_tiny(), weight_format="bf16")
+    base = EngineConfig(target="dense-tiny", max_batch=4, cuda_graphs=False, max_context=128, prefill_budget=64,
+                        prefill_chunk=32)
+    prompts = [[3 + i, 40 + i, 7, 9, 200 + i, 5] * (2 + i) for i in range(6)]
+    sp = SamplingParams(max_tokens=5, ignore_eos=True)
+    want = [r.output_ids for r in LLM(base, target=t, device="cpu").generate(prompts, sp)]
+    cfg = base.replace(dp=2, tp=2)
+    leaders = ThreadAllGather(2, timeout=120)
+    comms = [ThreadComm(2), ThreadComm(2)]
+    chans = [ThreadBroadcast(2, timeout=120), ThreadBroadcast(2, timeout=120)]
+    llms, loops, errs = {}, {}, []
+    built = threading.Barrier(5)
+
+    def rank_main(g, r):
+        try:
+            view = comms[g].view(r)
+            view.rank = r
+            if r == 0:
+                llm = LLM(cfg, target=t, device="cpu", comm=view, control=leaders.view(g), rank=g)
+                loop = EngineLoop(llm.scheduler, channel=chans[g].view(0), rank=g, dp=llm.lockstep, idle_sleep=0.001)
+            else:
+                llm = LLM(cfg, target=t, device="cpu", comm=view)
+                assert llm.lockstep is None
+                loop = EngineLoop(llm.scheduler, channel=chans[g].view(r), rank=r)
+            llms[g, r], loops[g, r] = llm, loop
+            built.wait(120)
+            loop.start()
+        except Exception as e:  # noqa: BLE001
+            errs.append(repr(e))
+            built.abort()
+
+    threads = [threading.Thread(target=rank_main, args=(g, r)) for g in range(2) for r in range(2)]
+    for th in threads:
+        th.start()
+    built.wait(120)
+    for th in threads:
+        th.join(60)
+    assert not errs, errs
+    assert llms[0, 0].model.target.tp_size == 2 and llms[1, 1].model.target.tp_rank == 1
+    tickets = [loops[0, 0].submit(p, sp) for p in prompts]
+    got = []
+    for tk in tickets:
+        toks = []
+        while True:
+            kind, val = tk.events.get(timeout=120)
+            if kind == "tokens":
+                toks += val
+            else:
+                assert kind == "done", (kind, val)
+                break
+        got.append(toks)
+    assert all(len(g_) == 5 for g_ in got)
+    assert sum(a[0] == b[0] for a, b in zip(got, want)) == len(want)      # reassociation only: first tokens match tp = 1
+    served = [llms[g, 0].scheduler.metrics.finished for g in range(2)]
+    assert sum(served) == 6 and min(served) >= 1, served
+    loops[0, 0].stop(timeout=60)
+    for key, loop in loops.items():
+        loop.thread.join(60)
+        assert not loop.thread.is_alive(), key
+        assert loop.healthy, (key, loop.failure)
+    for g in range(2):     # a follower took exactly its leader's steps
+        assert llms[g, 1].scheduler.metrics.finished == served[g]
+        assert llms[g, 1].executor.stats["decode_steps"] == llms[g, 0].executor.stats["decode_steps"]
+        assert loops[g, 1].steps == loops[g, 0].steps
