@@ -191,7 +191,8 @@ def load_dense(full: Target, directory: str, device="cpu", tp: int = 1, rank: in
 
 def load_hybrid(full: Target, directory: str, device="cpu", tp: int = 1, rank: int = 0, seed: int = 0):
     """A hybrid-family model from a checkpoint directory: the published Nemotron-class tensor layout
-    (weights/nemotron_layout.py), or this build's own snapshot (weights/snapshot.py: the model is built with this
+    (weights/nemotron_layout.py), the published Qwen3.8-class layout (weights/qwen_layout.py), or this build's own
+    snapshot (weights/snapshot.py: the model is built with this
     rank's geometry, then every tensor is overwritten with the stored one)."""
     from ..models.hybrid import HybridModel
     from . import snapshot
@@ -203,6 +204,14 @@ def load_hybrid(full: Target, directory: str, device="cpu", tp: int = 1, rank: i
                                       "snapshot of the loaded model for tensor-parallel serving")
         from . import nemotron_layout
         return nemotron_layout.load(full, directory, device, seed=seed)
+    if index.exists():
+        from . import qwen_layout
+        if qwen_layout.is_layout(json.loads(index.read_text())["weight_map"]):
+            # the published Qwen3.8-class layout (per-layer linear_attn / self_attn / mlp names)
+            if tp != 1:
+                raise NotImplementedError("the Qwen3.8-class checkpoint layout loads unsharded (tp = 1); save a "
+                                          "per-rank snapshot of the loaded model for tensor-parallel serving")
+            return qwen_layout.load(full, directory, device, seed=seed)
     model = HybridModel(full, device, seed=seed) if tp == 1 else HybridModel.sharded(full, tp, rank, device, seed=seed)
     snapshot.load_state(model, directory)
     return model

@@ -181,3 +181,74 @@ def test_nemotron_checkpoint_layout_round_trip_cpu(tmp_path, fmt):
     want = [r.output_ids for r in Executor(model, max_batch=2, max_ctx=96, use_graphs=False).generate_batch(prompts, sp)]
     got = [r.output_ids for r in Executor(other, max_batch=2, max_ctx=96, use_graphs=False).generate_batch(prompts, sp)]
     assert got == want
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "nvfp4"])
+def test_qwen_checkpoint_layout_round_trip_cpu(tmp_path, fmt):
+    """A Qwen3.8-class model written under the published checkpoint's tensor names (linear_attn / self_attn / mlp per
+    layer, separate in_proj_qkv | in_proj_z, q | k | v and gate | up tensors, the prediction head under `mtp.`) loads
+    back bit for bit through `load_hybrid`: same tensors, same tokens."""
+    import json
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import qwen38_hybrid, scaled
+    from hibana_b200.weights import qwen_layout as ql
+    from hibana_b200.weights.checkpoint import load_hybrid
+    t = scaled(qwen38_hybrid(), layers=4, hidden=256, vocab=512, q_heads=4, kv_heads=2, head_dim=64, ffn=512,
+               gdn_k_heads=2, gdn_v_heads=4, gdn_head_dim=64, weight_format=fmt, kv_dtype="bf16", max_context=512)
+    model = HybridModel(t, "cpu", seed=3)
+    assert model.mtp is not None
+    d = ql.save(model, tmp_path / "ckpt", layers_per_file=2)
+    index = json.loads((d / "model.safetensors.index.json").read_text())["weight_map"]
+    for name in ("model.language_model.layers.0.linear_attn.in_proj_qkv.weight",
+                 "model.language_model.layers.0.linear_attn.in_proj_z.weight",
+                 "model.language_model.layers.2.linear_attn.A_log",
+                 "model.language_model.layers.3.self_attn.q_proj.weight",
+                 "model.language_model.layers.3.self_attn.k_norm.weight",
+                 "model.language_model.layers.1.mlp.gate_proj.weight", "mtp.fc.weight",
+                 "mtp.layers.0.self_attn.o_proj.weight", "mtp.pre_fc_norm_hidden.weight"):
+        assert name in index, name
+    if fmt == "nvfp4":
+        assert "model.language_model.layers.1.mlp.up_proj.weight_scale_2" in index
+    other = load_hybrid(t, str(d), "cpu", seed=99)                 # another seed: nothing may survive from init
+    a, b = ql.tensors_of(model), ql.tensors_of(other)
+    assert a.keys() == b.keys()
+    for k in a:
+        assert torch.equal(a[k].view(torch.uint8) if a[k].dtype == torch.float8_e4m3fn else a[k],
+                           b[k].view(torch.uint8) if b[k].dtype == torch.float8_e4m3fn else b[k]), k
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, t.vocab, (n,), generator=g).tolist() for n in (24, 17)]
+    sp = SamplingParams(max_tokens=6)
+    want = [r.output_ids for r in Executor(model, max_batch=2, max_ctx=96, use_graphs=False).generate_batch(prompts, sp)]
+    got = [r.output_ids for r in Executor(other, max_batch=2, max_ctx=96, use_graphs=False).generate_batch(prompts, sp)]
+    assert got == want
+
+
+def test_qwen_checkpoint_layout_block_scaled_fp8_mixers_cpu(tmp_path):
+    """Mixer projections stored as FP8 with one scale per 128 x 128 block (`weight_scale_inv`) load as the bf16
+    expansion of exactly those values; the rest of the checkpoint is untouched."""
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import qwen38_hybrid, scaled
+    from hibana_b200.weights import qwen_layout as ql
+    w = torch.randn(200, 300, generator=torch.Generator().manual_seed(1)).bfloat16()
+    q, s = ql.fp8_block_quant(w)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (2, 3)
+    back = ql.fp8_block_dequant(q, s)
+    assert (back.float() - w.float()).abs().max() <= 0.07 * w.float().abs().max()
+    q2, s2 = ql.fp8_block_quant(back)                              # a fixed point: stored values survive a round trip
+    assert torch.equal(ql.fp8_block_dequant(q2, s2), back)
+    t = scaled(qwen38_hybrid(), layers=4, hidden=256, vocab=512, q_heads=4, kv_heads=2, head_dim=64, ffn=512,
+               gdn_k_heads=2, gdn_v_heads=4, gdn_head_dim=64, weight_format="bf16", kv_dtype="bf16", mtp_layers=0,
+               max_context=512)
+    model = HybridModel(t, "cpu", seed=5)
+    d = ql.save(model, tmp_path / "ckpt", fp8_mixers=True)
+    other = ql.load(t, d, "cpu", seed=9)
+    lin, src = other.blocks[0].mixer.in_qkvz, model.blocks[0].mixer.in_qkvz
+    qk, vd = 2 * 64, 4 * 64
+    parts = [src.weight[:2 * qk + vd], src.weight[2 * qk + vd:]]
+    want = torch.cat([ql.fp8_block_dequant(*ql.fp8_block_quant(p)) for p in parts], 0)
+    assert lin.fmt == "bf16" and torch.equal(lin.weight, want)
+    assert torch.equal(other.blocks[3].mixer.o.weight, ql.fp8_block_dequant(*ql.fp8_block_quant(model.blocks[3].mixer.o.weight)))
+    assert torch.equal(other.blocks[1].ffn.down.weight, model.blocks[1].ffn.down.weight)
+    assert torch.equal(other.blocks[2].mixer.conv_w, model.blocks[2].mixer.conv_w)
