@@ -59,9 +59,15 @@ class BoltMoeLayer:
     """Latent MoE block of the Bolt family: sigmoid router with selection bias, `t.experts` routed experts of width
     `t.expert_ffn` acting on the `t.latent`-wide projection (squared ReLU), a shared expert on the hidden state."""
 
-    def __init__(self, t: Target, init, name: str):
+    def __init__(self, t: Target, init, name: str, ep_rank: int = 0, ep_size: int = 1):
+        """Tensor parallel (`ep_size` = the ranks, activations replicated): this rank keeps the experts
+        [ep_rank * E / ep_size, ...) as block bytes of the full stacks and a column / row share of the shared
+        expert; its output is a partial sum (`partial`: the block's all-reduce adds the ranks), the projection back
+        from the latent being linear. A shared expert too narrow to split into whole Q8_0 blocks stays whole and only
+        rank 0 adds it."""
         from .layers import MlpLayer
-        self.t, self.partial, self.ep_size, self.tp = t, False, 1, 1
+        self.t, self.ep_size, self.tp = t, ep_size, init.tp
+        self.partial = ep_size > 1
         dev = init.device
         self.router = init.linear(t.experts, t.hidden, "bf16", name + ".router")
         self.sel_bias = torch.zeros(t.experts, device=dev)
@@ -76,7 +82,22 @@ class BoltMoeLayer:
         fc2 = PackedLinear(random_blocks("iq2_xs", t.experts * width, t.expert_ffn, seed + 1, scale=0.002).to(dev),
                            "iq2_xs", t.experts * width, t.expert_ffn, gs, name + ".fc2")
         self.experts = PackedExperts(fc1, fc2, t.experts)
-        self.shared = MlpLayer(t, init, name + ".shared", width=t.shared_ffn, act="relu2") if t.shared_ffn else None
+        per = t.experts // ep_size
+        self.e_lo = ep_rank * per
+        if ep_size > 1:
+            # every rank draws every expert (one seeded stream for every layout) and keeps its range
+            if t.experts % ep_size:
+                raise ValueError(f"{t.experts} experts do not divide over {ep_size} ranks")
+            self.experts = self.experts.slice(self.e_lo, per)
+        f = getattr(init, "full", None) or t
+        shared_init, self.shared_owner = init, True
+        if init.tp > 1 and t.shared_ffn and ((f.shared_ffn // init.tp) % 32 or f.shared_ffn % init.tp):
+            import copy
+            shared_init = copy.copy(init)          # same seeded stream, no sharding
+            shared_init.tp, shared_init.rank = 1, 0
+            self.shared_owner = init.rank == 0
+        self.shared = (MlpLayer(t, shared_init, name + ".shared", width=f.shared_ffn, act="relu2")
+                       if t.shared_ffn else None)
         self.fc1_latent = init.linear(t.latent, t.hidden, "q8_0", name + ".fc1_latent") if t.latent else None
         self.fc2_latent = init.linear(t.hidden, t.latent, "q8_0", name + ".fc2_latent") if t.latent else None
 
@@ -95,11 +116,11 @@ class BoltMoeLayer:
         with streams.Branch(x, enabled=overlap_ok(x, ctx)) as br:
             inp = self.fc1_latent(x) if t.latent else x
             lat_ready = br.mark()
-            shared = self.shared.forward(x) if self.shared is not None else None
+            shared = self.shared.forward(x) if self.shared is not None and self.shared_owner else None
         logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
         ids, w = moe.route(logits, t.top_k, sigmoid=True, sel_bias=self.sel_bias, renorm=True, scale=t.router_scale)
         br.wait(lat_ready, inp if t.latent else None)
-        y = self.experts.forward(inp, ids, w)
+        y = self.experts.forward(inp, ids, w, id_base=self.e_lo)
         out = self.fc2_latent(y) if t.latent else y
         br.join(shared)
         return basic.add(out, shared) if shared is not None else out

@@ -46,10 +46,11 @@ class Init:
         slice of the quantised full matrix. fmt "q8_0": GGML Q8_0 blocks served in place (models/bolt.py)."""
         w = self.normal(n, k)
         if fmt == "q8_0":
-            if rows is not None or cols is not None:
-                raise NotImplementedError("GGML-packed projections are not sharded (the family fits one GPU)")
             from .bolt import GgmlLinear
-            return GgmlLinear.from_weight(w, name=name).to(self.device)
+            lin = GgmlLinear.from_weight(w, name=name)
+            if rows is not None or cols is not None:
+                lin = lin.shard(rows=rows, cols=cols)      # block bytes of the full matrix: nothing requantised
+            return lin.to(self.device)
         if rows is None and cols is None:
             return Linear(w, fmt, name=name).to(self.device)
         if isinstance(rows, torch.Tensor):
@@ -588,6 +589,6 @@ def build_ffn(kind: str, t: Target, init: Init, name: str, ep_rank: int = 0, ep_
     if kind in (MOE, LATENT_MOE):
         if t.weight_format == "ggml":
             from .bolt import BoltMoeLayer
-            return BoltMoeLayer(t, init, name)
+            return BoltMoeLayer(t, init, name, ep_rank, ep_size)
         return MoeLayer(t, init, name, ep_rank, ep_size)
     return None

@@ -61,6 +61,22 @@ class PackedLinear:
         self.grid = self.grid.to(device) if self.grid is not None else None
         return self
 
+    def shard(self, rows=None, cols: Optional[slice] = None) -> "PackedLinear":
+        """A tensor-parallel shard as block bytes of this matrix, nothing requantised: `rows` (slice or index
+        tensor) keeps output features, `cols` (a contiguous slice of whole blocks) keeps input features."""
+        raw = self.raw
+        if rows is not None:
+            raw = raw[rows.to(raw.device) if isinstance(rows, torch.Tensor) else rows]
+        k = self.k
+        if cols is not None:
+            per, nbytes = fmt.BLOCK[self.gtype]
+            c0, c1, step = cols.indices(self.k)
+            if step != 1 or c0 % per or c1 % per:
+                raise ValueError(f"{self.fmt}: a column shard must be whole blocks of {per} weights, got [{c0}, {c1})")
+            raw, k = raw[:, c0 // per * nbytes:c1 // per * nbytes], c1 - c0
+        raw = raw.contiguous()
+        return type(self)(raw, self.gtype, raw.shape[0], k, self.grid, name=self.name)
+
     def dequantize(self, row0: int = 0, rows: Optional[int] = None) -> torch.Tensor:
         """bf16 [rows, K] of rows [row0, row0 + rows)."""
         rows = self.n - row0 if rows is None else rows
@@ -99,18 +115,38 @@ class PackedExperts:
         assert fc1.n % experts == 0 and fc2.n % experts == 0
         self.fc1, self.fc2, self.experts = fc1, fc2, experts
         self.inter, self.hidden = fc1.n // experts, fc2.n // experts
+        self.total = experts          # experts of the whole layer (more than `experts` on a rank that holds a range)
 
-    def forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
-        """x [T, H] bf16, ids int32 [T, k], weights fp32 [T, k] -> [T, H] bf16: sum_k w * fc2_e(relu(fc1_e x)^2)."""
+    def slice(self, e_lo: int, e_n: int) -> "PackedExperts":
+        """The experts [e_lo, e_lo + e_n): what one rank keeps when the experts are split by range."""
+        part = PackedExperts(self.fc1.shard(rows=slice(e_lo * self.inter, (e_lo + e_n) * self.inter)),
+                             self.fc2.shard(rows=slice(e_lo * self.hidden, (e_lo + e_n) * self.hidden)), e_n)
+        part.total = self.total
+        return part
+
+    def forward(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, id_base: int = 0) -> torch.Tensor:
+        """x [T, H] bf16, ids int32 [T, k], weights fp32 [T, k] -> [T, H] bf16: sum_k w * fc2_e(relu(fc1_e x)^2).
+        `id_base`: global id of this object's first expert; pairs routed to experts it does not hold add nothing
+        (the result is then this rank's partial sum)."""
         t, k = ids.shape
         pairs = t * k
+        gids, gweights = ids, weights
+        if id_base or self.total > self.experts:
+            local = ids - id_base
+            mine = (local >= 0) & (local < self.experts)
+            ids = torch.where(mine, local, torch.full_like(local, -1))
+            weights = torch.where(mine, weights, torch.zeros_like(weights))
+            sharded = True
+        else:
+            sharded = False
         if nv.use_native(x) and pairs <= 4096:
             dev = x.device
             pe = ids.reshape(-1).contiguous()
             pr = torch.arange(t, dtype=torch.int32, device=dev).repeat_interleave(k)
             own = torch.arange(pairs, dtype=torch.int32, device=dev)
             h1 = torch.empty(pairs, self.inter, dtype=torch.bfloat16, device=dev)
-            y = torch.empty(pairs, self.hidden, dtype=torch.bfloat16, device=dev)
+            # the kernel skips pairs with a negative expert: their rows must read zero in the weighted sum below
+            y = (torch.zeros if sharded else torch.empty)(pairs, self.hidden, dtype=torch.bfloat16, device=dev)
             lib = nv.lib()
             for lin, src, rows, relu2, out, n in ((self.fc1, x, pr, 1, h1, self.inter), (self.fc2, h1, own, 0, y, self.hidden)):
                 nv.check(lib.hb_ggml_gemv_pairs(lin.gtype, lin.raw.data_ptr(), lin.row_bytes, lin.row_bytes * n, n,
@@ -125,7 +161,7 @@ class PackedExperts:
             from . import moe
             ew = moe.ExpertWeights(self.experts, self.fc1.k, self.inter, "relu2", "bf16",
                                    self.fc1.dequantize(0, self.fc1.n), self.fc2.dequantize(0, self.fc2.n))
-            return moe.experts_forward(x, ids, weights, ew)
+            return moe.experts_forward(x, gids, gweights, ew, id_base=id_base)
         out = torch.zeros(t, self.hidden, dtype=torch.float32, device=x.device)
         for e in ids.unique().tolist():
             if e < 0:

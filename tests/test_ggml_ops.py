@@ -144,3 +144,94 @@ def test_bolt_decodes_on_gpu_with_graphs():
     torch.cuda.synchronize()
     assert nv.read_status() == 0
     assert [r.output_ids for r in got] == [r.output_ids for r in eager]
+
+
+def test_packed_linear_shards_are_block_bytes_of_the_full_matrix_cpu():
+    """Row and column shards of a GGML-packed matrix are slices of its block bytes: the dequantised shard equals the
+    same slice of the dequantised matrix; a column shard must be whole blocks."""
+    from hibana_b200.models.bolt import GgmlLinear
+    w = torch.randn(96, 256, generator=torch.Generator().manual_seed(0)) * 0.05
+    lin = GgmlLinear.from_weight(w, name="x")
+    full = lin.dequantize()
+    rows = torch.tensor([5, 6, 7, 40, 41, 95])
+    part = lin.shard(rows=rows, cols=slice(64, 192))
+    assert isinstance(part, GgmlLinear) and (part.n, part.k) == (6, 128)
+    assert torch.equal(part.dequantize(), full[rows][:, 64:192])
+    assert torch.equal(lin.shard(rows=slice(32, 64)).dequantize(), full[32:64])
+    with pytest.raises(ValueError):
+        lin.shard(cols=slice(16, 80))
+    x = torch.randn(3, 256, generator=torch.Generator().manual_seed(1)).bfloat16()
+    y = lin(x).float()
+    halves = lin.shard(cols=slice(0, 128))(x[:, :128].contiguous()).float() + lin.shard(cols=slice(128, 256))(x[:, 128:].contiguous()).float()
+    assert (y - halves).abs().max() <= 2e-2 * y.abs().max() + 1e-3
+
+
+def test_bolt_tensor_parallel_two_ranks_match_one_cpu():
+    """The Bolt family under tensor parallelism: Q8_0 projections sharded as block bytes, IQ2 experts split by
+    expert range with the block's all-reduce adding the ranks' partial sums. Two ranks (threads) emit the same tokens
+    as each other and the first token of every request equals the unsharded model's."""
+    import threading
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.hybrid import HybridModel
+    from test_tp import ThreadComm
+    t = _small_bolt()
+    full = HybridModel(t, "cpu", seed=0)
+    shards = [HybridModel.sharded(t, 2, r, "cpu", seed=0) for r in range(2)]
+    ffn_full = [b.ffn for b in full.blocks if b.ffn is not None]
+    for r in range(2):
+        ffns = [b.ffn for b in shards[r].blocks if b.ffn is not None]
+        assert [f.experts.experts for f in ffns] == [3, 5, 3, 4] and all(f.partial for f in ffns)
+        assert ffns[1].e_lo == 5 * r and ffns[1].experts.total == 10
+        # this rank's experts are the block bytes of its range of the full stacks
+        inter = ffn_full[1].experts.inter
+        assert torch.equal(ffns[1].experts.fc1.raw, ffn_full[1].experts.fc1.raw[5 * r * inter:5 * (r + 1) * inter])
+        assert ffns[0].shared.up.n == 128                           # the shared expert: half the columns each
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, t.vocab, (n,), generator=g).tolist() for n in (20, 9)]
+    sp = SamplingParams(max_tokens=4)
+    ref = Executor(full, max_batch=2, max_ctx=64, use_graphs=False).generate_batch(prompts, sp)
+    comm = ThreadComm(2)
+    outs, errs = [None, None], []
+
+    def run(rank):
+        try:
+            ex = Executor(shards[rank], max_batch=2, max_ctx=64, use_graphs=False, comm=comm.view(rank))
+            outs[rank] = ex.generate_batch(prompts, sp)
+        except Exception as e:  # noqa: BLE001
+            errs.append(repr(e))
+            comm.barrier.abort()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(2)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join(180)
+    assert not errs, errs
+    a = [r.output_ids for r in outs[0]]
+    assert a == [r.output_ids for r in outs[1]]
+    assert sum(x[0] == y.output_ids[0] for x, y in zip(a, ref)) == len(a)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tokens,k", [(5, 2), (1100, 4)])
+def test_packed_experts_by_range_partial_sums_add_up_on_gpu(tokens, k):
+    """Experts split by range over two ranks (decode-sized: the GEMV skips pairs of the other range; prefill-sized:
+    the grouped GEMMs take the range): the two partial sums add up to the whole layer's output."""
+    e, h, inter = 8, 512, 256
+    grid = _grid(256)
+    fc1 = ops.random_blocks("iq2_xxs", e * inter, h, seed=25, scale=0.01)
+    fc2 = ops.random_blocks("q8_0", e * h, inter, seed=26, scale=0.002)
+    g = torch.Generator().manual_seed(27)
+    x = torch.randn(tokens, h, generator=g).bfloat16().cuda()
+    ids = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(tokens)]).int().cuda()
+    wts = torch.rand(tokens, k, generator=g).cuda()
+    whole = ops.PackedExperts(ops.PackedLinear(fc1.cuda(), "iq2_xxs", e * inter, h, grid),
+                              ops.PackedLinear(fc2.cuda(), "q8_0", e * h, inter), e)
+    want = whole.forward(x, ids, wts).float()
+    parts = [whole.slice(r * 4, 4).forward(x, ids, wts, id_base=r * 4).float() for r in range(2)]
+    torch.cuda.synchronize()
+    from hibana_b200 import _native as nv
+    assert nv.read_status() == 0
+    assert torch.isfinite(parts[0]).all() and torch.isfinite(parts[1]).all()
+    assert (parts[0] + parts[1] - want).abs().max() <= 3e-2 * want.abs().max() + 1e-3
