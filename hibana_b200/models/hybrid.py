@@ -121,6 +121,24 @@ class HybridModel:
                     out += sub.linears()
         return out
 
+    def attach_w3(self) -> int:
+        """3-bit decode copies (settings `w3`) of every NVFP4 / bf16 projection whose shape the 3-bit kernel tiles and
+        of every MoE layer's routed experts: decode- and verify-sized calls stream 4 bits per weight, prefill keeps
+        the served formats. Returns the bytes the copies add. Reference: hibana/kernels/w3.py `attach_model`."""
+        from .linear import Linear
+        added = 0
+        for lin in self.linears():
+            if type(lin) is not Linear or lin.in_features % 64 or lin.fmt not in ("bf16", "nvfp4"):
+                continue
+            if lin.name.endswith(".router"):
+                continue            # fp32 logits: routing decisions stay those of the served weights
+            lin.attach_w3()
+            added += lin.w3.nbytes()
+        for blk in self.blocks:
+            if isinstance(blk.ffn, MoeLayer):
+                added += blk.ffn.attach_w3()
+        return added
+
     def state_pool_spec(self) -> Optional[dict]:
         """Shape of the recurrent-state pool this model needs (None = attention only)."""
         t = self.target
@@ -168,7 +186,7 @@ class HybridModel:
                 if partial:
                     x = self._reduce_norm(h, res, norm_w, ctx)
                 elif (first is not None and first.fmt == "nvfp4" and not first.calibrating and t.hidden <= 8192
-                      and nv.use_native(res)):
+                      and nv.use_native(res) and not first.takes_w3(res.shape[0])):
                     # the norm writes the first projection's NVFP4 input itself (one kernel instead of norm + quantise)
                     xq, x = nvfp4.rmsnorm_quantize(res if h is None else h, norm_w, t.norm_eps, first.input_scale,
                                                    residual=None if h is None else res, gemma=t.gemma_norm,

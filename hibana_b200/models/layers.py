@@ -222,7 +222,7 @@ class MambaLayer:
                                       d_state=t.mamba_state, q_indptr=ctx.q_indptr, has_init=ctx.has_initial_state,
                                       state_scale=states.ssm_scale[li] if getattr(states, "ssm_scale", None) is not None
                                       else None, sr_seed=ctx.extras.get("sr_seed", 0), host_rows=ctx.seq_starts_host)
-        if self.out_proj.fmt == "nvfp4" and not self.out_proj.calibrating:
+        if self.out_proj.fmt == "nvfp4" and not self.out_proj.calibrating and not self.out_proj.takes_w3(y.shape[0]):
             # the gated norm writes the output projection's NVFP4 input itself
             return self.out_proj(basic.gated_rmsnorm_quant(y, z, self.norm_w, t.norm_eps, inner // t.mamba_groups,
                                                            self.out_proj.input_scale))
@@ -334,7 +334,7 @@ class GdnLayer:
         if self._norm_w_key != key:
             self.norm_w_heads, self._norm_w_key = self.norm_w.repeat(t.gdn_v_heads), key
         w = self.norm_w_heads
-        if self.out_proj.fmt == "nvfp4" and not self.out_proj.calibrating:
+        if self.out_proj.fmt == "nvfp4" and not self.out_proj.calibrating and not self.out_proj.takes_w3(rows):
             return self.out_proj(basic.gated_rmsnorm_quant(o, z, w, t.norm_eps, kd, self.out_proj.input_scale,
                                                            norm_first=True, gemma=t.gemma_norm))
         y = basic.gated_rmsnorm(o, z, w, t.norm_eps, kd, norm_first=True, gemma=t.gemma_norm)
@@ -465,6 +465,29 @@ class MoeLayer:
         out += [l for l in (self.fc1_latent, self.fc2_latent) if l is not None]
         return out
 
+    experts_w3 = None      # optional 3-bit decode copy of the routed experts (attach_w3)
+
+    def attach_w3(self, fc1=None, fc2=None) -> int:
+        """3-bit decode copy of this rank's routed experts (int3, groups of 64, dequantisation fused into the grouped
+        GEMM): calls of up to `W3_MAX_ROWS` rows stream it instead of the served stacks. `fc1` / `fc2`: calibrated
+        `Int3G64` stacks over all experts' rows (weights/calibrate_model.py); default: nearest rounding of the served
+        weights. Returns the bytes the copy adds. Reference: hibana/kernels/w3_moe.py, flashnext_w3_experts.py."""
+        ew = self.experts
+        n1, n2 = ew.n1, ew.fc2_rows
+        if n1 % 128 or n2 % 128 or ew.hidden % 64 or ew.inter % 64:
+            return 0            # the 3-bit tiles cover 128 rows x 64 columns
+        dev = ew.fc1.q.device if ew.fmt == "nvfp4" else ew.fc1.device
+        if fc1 is None:
+            self.experts_w3 = moe.ExpertWeights.create(ew.dense(1), ew.dense(2), ew.act, "w3").to(dev)
+        else:
+            self.experts_w3 = moe.ExpertWeights.from_int3(fc1, fc2, ew.experts, ew.act, n2, dev)
+        return self.experts_w3.fc1.numel() + self.experts_w3.fc2.numel()
+
+    def _ew(self, x):
+        """The expert stacks a call of x's row count reads."""
+        from .linear import W3_MAX_ROWS
+        return self.experts_w3 if self.experts_w3 is not None and x.shape[0] <= W3_MAX_ROWS else self.experts
+
     def _route(self, logits: torch.Tensor):
         """Top-k routing; with `expert_budget` set, decode-sized calls share experts across their rows."""
         t = self.t
@@ -489,12 +512,12 @@ class MoeLayer:
             ids, w = self._route(logits)
             if t.latent:
                 br.wait(lat_ready, lat)
-                y = moe.experts_forward(lat, ids, w, self.experts, id_base=self.e_lo)
+                y = moe.experts_forward(lat, ids, w, self._ew(lat), id_base=self.e_lo)
                 out = self.fc2_latent(y)
                 br.join(shared)
                 return basic.add(out, shared) if shared is not None else out
             br.join(shared)
-            return moe.experts_forward(x, ids, w, self.experts, shared=shared, id_base=self.e_lo)
+            return moe.experts_forward(x, ids, w, self._ew(x), shared=shared, id_base=self.e_lo)
         logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
         ids, w = self._route(logits)
         shared = self.shared.forward(x) if self.shared is not None else None
@@ -502,10 +525,10 @@ class MoeLayer:
             shared = ctx.comm.all_reduce(shared)      # column / row split shared expert beside replicated experts
         if t.latent:
             lat = self.fc1_latent(x)
-            y = moe.experts_forward(lat, ids, w, self.experts, id_base=self.e_lo)
+            y = moe.experts_forward(lat, ids, w, self._ew(lat), id_base=self.e_lo)
             out = self.fc2_latent(y)
             return basic.add(out, shared) if shared is not None else out
-        return moe.experts_forward(x, ids, w, self.experts, shared=shared, id_base=self.e_lo)
+        return moe.experts_forward(x, ids, w, self._ew(x), shared=shared, id_base=self.e_lo)
 
 
 def _moe_forward_ep(self, x, comm) -> torch.Tensor:
@@ -522,7 +545,7 @@ def _moe_forward_ep(self, x, comm) -> torch.Tensor:
     logits = gemm.linear_bf16(x, self.router.weight, epilogue=gemm.EPI_STORE_F32)
     ids, w = self._route(logits)
     br.wait(lat_ready, inp if t.latent else None)
-    part = moe.experts_forward(inp, ids, w, self.experts, id_base=self.e_lo)
+    part = moe.experts_forward(inp, ids, w, self._ew(inp), id_base=self.e_lo)
     if getattr(self, "tp", 1) > 1:
         # tensor parallel: the shared expert is column / row split too, so its partial sum joins the routed
         # experts' before the layer's one all-reduce; the latent up-projection is linear and moves in front of it

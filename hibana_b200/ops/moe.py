@@ -159,10 +159,7 @@ class ExpertWeights:
             assert n1 % 128 == 0 and fc2.shape[1] % 128 == 0
             q1 = Int3G64.quantize(fc1.reshape(e * n1, h).float().cpu())
             q2 = Int3G64.quantize(fc2.reshape(e * fc2.shape[1], inter).float().cpu())
-            out = cls(e, h, inter, act, fmt, q1.tiles().to(dev), q2.tiles().to(dev))
-            out.w3 = (q1, q2)
-            out.fc2_rows_ = fc2.shape[1]
-            return out
+            return cls.from_int3(q1, q2, e, act, fc2.shape[1], dev)
 
         def quant(w):   # per-expert scale, stacked rows
             parts = [nvfp4.quantize_weight(w[i]) for i in range(w.shape[0])]
@@ -176,6 +173,16 @@ class ExpertWeights:
         s1 = torch.tensor([in_amax / (6 * 448.0)], dtype=torch.float32, device=dev)
         s2 = torch.tensor([mid_amax / (6 * 448.0)], dtype=torch.float32, device=dev)
         return cls(e, h, inter, act, fmt, q1, q2, (g1 * s1).contiguous(), (g2 * s2).contiguous(), s1, s2)
+
+    @classmethod
+    def from_int3(cls, q1, q2, experts: int, act: str, fc2_rows: int, device) -> "ExpertWeights":
+        """3-bit expert stacks from two `Int3G64` matrices over all experts' rows (fc1 [E * n1, H], fc2
+        [E * fc2_rows, I]): nearest-rounded (`create`) or calibrated (weights/calibrate_model.py)."""
+        h, inter = q1.shape[1], q2.shape[1]
+        out = cls(experts, h, inter, act, "w3", q1.tiles().to(device), q2.tiles().to(device))
+        out.w3 = (q1, q2)
+        out.fc2_rows_ = fc2_rows
+        return out
 
     def dense(self, which: int) -> torch.Tensor:
         """Dequantised stacked matrix [E, n, k] (fp32) for the reference path."""

@@ -15,7 +15,10 @@
    and sha256 digests; `load_directory` checks the digests before it hands a matrix out.
 4. Attach. `attach(model, directory)` replaces the uncalibrated decode copies (`Linear.attach_w3`) of the
    projections the directory names; the others keep theirs.
-Routed experts are stacked tensors, not `Linear`s: they are not fitted here (they keep their served format).
+Routed experts are stacked tensors, not `Linear`s: `ExpertCovariances` collects, per expert, the covariance of the
+rows routed to it (weighted by the routing weight) for both of its matrices, `fit_experts` runs the same GPTQ per
+expert (experts with too few rows keep nearest rounding) and the stacks are written as `<layer>.experts.fc1|fc2`;
+`attach` hands them to the layer (`MoeLayer.attach_w3`).
 Reference: hibana/weights/flashnext_w3_calibrate.py:1-115, nemotron_w3_calibrate.py, bolt_w3_calibrate.py (one driver
 per family there; the capture is the same in all three), hibana/weights/w3_checkpoint.py:57-208 (manifest + sha256).
 """
@@ -71,6 +74,107 @@ class Covariances:
         Linear.__call__ = self._original
 
 
+def expert_layers(model) -> dict:
+    """{name: MoE layer} of the layers whose routed experts are stacked tensors (`l{i}.ffn.experts`)."""
+    from ..models.layers import MoeLayer
+    out = {}
+    for blk in getattr(model, "blocks", []):
+        ffn = getattr(blk, "ffn", None)
+        if isinstance(ffn, MoeLayer):
+            out[ffn.router.name[:-len(".router")] + ".experts"] = ffn
+    return out
+
+
+class ExpertCovariances:
+    """Per-expert input covariances of the routed experts, from `moe.experts_forward` calls while the context is
+    open: for expert e of a layer, H1[e] = sum g^2 x x^T over the rows routed to it (x the expert's input, g the
+    routing weight) and H2[e] the same over h = act(fc1_e x), the input of its second matrix. Rows a token sends to
+    an expert it weighs lightly count lightly. Reference: hibana/weights/nemotron_w3_experts.py:17-22."""
+
+    def __init__(self, model):
+        self.layers = expert_layers(model)
+        self.names = {id(layer.experts): name for name, layer in self.layers.items()}
+        self.h1: dict = {}
+        self.h2: dict = {}
+        self.rows: dict = {}
+        self._dense: dict = {}
+
+    def _add(self, name, x, ids, weights, ew, id_base):
+        from ..ops.moe import _act
+        if name not in self.h1:
+            self.h1[name] = torch.zeros(ew.experts, ew.hidden, ew.hidden)
+            self.h2[name] = torch.zeros(ew.experts, ew.inter, ew.inter)
+            self.rows[name] = torch.zeros(ew.experts, dtype=torch.int64)
+            self._dense[name] = ew.dense(1).float().cpu()
+        xf, idc, wc = x.detach().float().cpu(), ids.detach().cpu().long() - id_base, weights.detach().float().cpu()
+        for e in idc.unique().tolist():
+            if e < 0 or e >= ew.experts:
+                continue
+            tok, slot = (idc == e).nonzero(as_tuple=True)
+            g = wc[tok, slot][:, None]
+            xe = xf[tok]
+            self.h1[name][e].addmm_((xe * g).t(), xe * g)
+            h = _act(xe @ self._dense[name][e].t(), ew.act).to(torch.bfloat16).float()
+            self.h2[name][e].addmm_((h * g).t(), h * g)
+            self.rows[name][e] += tok.numel()
+
+    def __enter__(self) -> "ExpertCovariances":
+        from ..ops import moe as moe_ops
+        self._original = moe_ops.experts_forward
+        cov = self
+
+        def forward(x, ids, weights, ew, **kw):
+            name = cov.names.get(id(ew))
+            if name is not None:
+                cov._add(name, x, ids, weights, ew, kw.get("id_base", 0))
+            return cov._original(x, ids, weights, ew, **kw)
+        moe_ops.experts_forward = forward
+        return self
+
+    def __exit__(self, *exc) -> None:
+        from ..ops import moe as moe_ops
+        moe_ops.experts_forward = self._original
+
+
+def fit_experts(model, ecov: ExpertCovariances, *, min_rows: int = 32, log=None) -> tuple[dict, list]:
+    """GPTQ every routed expert that saw at least `min_rows` rows on its own covariances; the others keep nearest
+    rounding. Returns ({"<layer>.experts.fc1" / ".fc2": Int3G64 over all experts' rows}, report rows)."""
+    fitted, report = {}, []
+    for name, layer in ecov.layers.items():
+        if name not in ecov.h1:
+            continue
+        ew = layer.experts
+        if ew.n1 % 128 or ew.fc2_rows % 128 or ew.hidden % 64 or ew.inter % 64:
+            continue
+        t0 = time.perf_counter()
+        row = {"name": name, "experts": ew.experts, "calibrated": 0}
+        for which, hs in ((1, ecov.h1[name]), (2, ecov.h2[name])):
+            dense = ew.dense(which).float().cpu()
+            parts, err_g, err_n, fitted_n = [], 0.0, 0.0, 0
+            for e in range(ew.experts):
+                w = dense[e]
+                plain = Int3G64.quantize(w)
+                if int(ecov.rows[name][e]) >= min_rows:
+                    q = gptq_int3g64(w, hs[e])
+                    err_g += relative_error(w, q.dequantize(), hs[e])
+                    err_n += relative_error(w, plain.dequantize(), hs[e])
+                    fitted_n += 1
+                else:
+                    q = plain
+                parts.append(q)
+            fitted[f"{name}.fc{which}"] = Int3G64(torch.cat([q.codes for q in parts]),
+                                                  torch.cat([q.scale for q in parts]),
+                                                  torch.cat([q.zero for q in parts]))
+            row[f"fc{which}_error_gptq"] = round(err_g / max(fitted_n, 1), 5)
+            row[f"fc{which}_error_nearest"] = round(err_n / max(fitted_n, 1), 5)
+            row["calibrated"] = fitted_n
+        row["seconds"] = round(time.perf_counter() - t0, 2)
+        report.append(row)
+        if log is not None:
+            log(json.dumps(row))
+    return fitted, report
+
+
 def to_bf16(model) -> None:
     """Puts every projection of `model` in bf16 in place (a capture model: activations reach the projections
     unquantised, so the covariances are those of the bf16 trunk)."""
@@ -89,7 +193,8 @@ def capture(model, samples: Sequence[Sequence[int]], *, max_batch: int = 4, chun
     longest = max(len(s) for s in samples)
     ex = Executor(model, max_batch=max_batch, max_ctx=longest + 16, use_graphs=False, radix_cache=False)
     cov = Covariances(model.linears())
-    with cov:
+    cov.experts = ExpertCovariances(model)        # the routed experts' own covariances, from the same prefills
+    with cov, cov.experts:
         for i in range(0, len(samples), max_batch):
             ex.generate_batch([list(s) for s in samples[i:i + max_batch]], SamplingParams(max_tokens=1))
     return cov
@@ -180,7 +285,9 @@ def attach(model, directory, *, strict: bool = False) -> int:
     from ..ops.w3gemm import W3Linear
     by_name = {lin.name: lin for lin in model.linears() if getattr(lin, "name", "")}
     fitted = load_directory(directory)
-    unknown = sorted(set(fitted) - set(by_name))
+    moes = expert_layers(model)
+    stacks = {f"{name}.fc{w}" for name in moes for w in (1, 2)}
+    unknown = sorted(set(fitted) - set(by_name) - stacks)
     if unknown and strict:
         raise ValueError(f"calibrated names not in this model: {unknown[:4]}")
     n = 0
@@ -194,6 +301,17 @@ def attach(model, directory, *, strict: bool = False) -> int:
             continue
         dev = lin.weight.device if lin.weight is not None else lin.wq.q.device
         lin.w3 = W3Linear(q, dev, name=name + ".w3", keep_codes=dev.type != "cuda")
+        n += 1
+    for name, layer in moes.items():
+        q1, q2 = fitted.get(f"{name}.fc1"), fitted.get(f"{name}.fc2")
+        if q1 is None or q2 is None:
+            continue
+        ew = layer.experts
+        if q1.shape != (ew.experts * ew.n1, ew.hidden) or q2.shape != (ew.experts * ew.fc2_rows, ew.inter):
+            if strict:
+                raise ValueError(f"{name}: calibrated expert stacks {q1.shape} / {q2.shape} do not match the layer")
+            continue
+        layer.attach_w3(q1, q2)
         n += 1
     return n
 
@@ -213,6 +331,8 @@ def main(argv=None) -> None:
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--layers", type=int, default=0, help="first N blocks only (smoke runs)")
     ap.add_argument("--max-batch", type=int, default=4)
+    ap.add_argument("--min-expert-rows", type=int, default=32,
+                    help="routed experts that saw fewer calibration rows keep nearest rounding")
     args = ap.parse_args(argv)
     from ..engine.llm import build_model
     from ..target import get_target, scaled
@@ -225,10 +345,16 @@ def main(argv=None) -> None:
     to_bf16(model)
     cov = capture(model, load_samples(args.inputs), max_batch=args.max_batch)
     fitted, report = fit(model, cov, log=print)
+    if cov.experts.h1:
+        efit, ereport = fit_experts(model, cov.experts, min_rows=args.min_expert_rows, log=print)
+        fitted.update(efit)
+        report += ereport
     out = write_directory(args.output, fitted, target=t.name, report=report)
+    lins = [r for r in report if "error_gptq" in r]
     print(json.dumps({"directory": str(out), "matrices": len(fitted),
-                      "mean_error_gptq": round(sum(r["error_gptq"] for r in report) / max(len(report), 1), 5),
-                      "mean_error_nearest": round(sum(r["error_nearest"] for r in report) / max(len(report), 1), 5)}))
+                      "mean_error_gptq": round(sum(r["error_gptq"] for r in lins) / max(len(lins), 1), 5),
+                      "mean_error_nearest": round(sum(r["error_nearest"] for r in lins) / max(len(lins), 1), 5),
+                      "expert_layers": len(report) - len(lins)}))
 
 
 if __name__ == "__main__":

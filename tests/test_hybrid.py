@@ -195,3 +195,58 @@ def test_hyper_connections_in_the_trunk_cpu():
     plain = HybridModel(scaled(tiny_hybrid_moe()), "cpu", seed=0)
     other = _run(Executor(plain, max_batch=4, max_ctx=160, use_graphs=False, radix_cache=False), prompts[:1], n=12)
     assert other != ref[:1]                      # the hyper trunk is a different function of the same seed
+
+
+def _w3_model(device):
+    t = scaled(tiny_hybrid_moe(), expert_ffn=128, mtp_layers=0, mtp_depth=0)
+    m = HybridModel(t, device, seed=0, init_device="cpu")
+    added = m.attach_w3()
+    return t, m, added
+
+
+def test_hybrid_w3_copies_cover_projections_and_experts_cpu():
+    """`attach_w3` on a hybrid: every tiled projection and every MoE layer's routed experts get a 3-bit decode copy;
+    decode-sized calls run on the copies (prefill chunks above the row limit keep the served weights) and the step's
+    logits stay close to the served model's."""
+    from hibana_b200.models.layers import MoeLayer
+    from hibana_b200.models.linear import W3_MAX_ROWS
+    t, m, added = _w3_model("cpu")
+    ref = HybridModel(t, "cpu", seed=0)
+    moes = [b.ffn for b in m.blocks if isinstance(b.ffn, MoeLayer)]
+    assert moes and all(f.experts_w3 is not None and f.experts_w3.fmt == "w3" for f in moes)
+    assert added > 0 and all(lin.w3 is not None for lin in m.linears() if not lin.name.endswith(".router"))
+    assert moes[0].router.w3 is None
+    x = torch.randn(3, t.hidden).bfloat16()
+    assert moes[0]._ew(x) is moes[0].experts_w3
+    assert moes[0]._ew(torch.zeros(W3_MAX_ROWS + 1, t.hidden)) is moes[0].experts
+    # one MoE layer: 3-bit experts against the served ones
+    a, b = moes[0].forward(x).float(), [bb.ffn for bb in ref.blocks if isinstance(bb.ffn, MoeLayer)][0].forward(x).float()
+    assert (a - b).norm() <= 0.35 * b.norm()
+    prompts = _workload(t, n=2)
+    sp = SamplingParams(max_tokens=4)
+    got = Executor(m, max_batch=2, max_ctx=128, use_graphs=False).generate_batch(prompts, sp)
+    assert all(len(r.output_ids) == 4 for r in got)
+
+
+@pytest.mark.gpu
+def test_hybrid_w3_copies_decode_on_gpu_matches_cpu_copies():
+    """The same 3-bit copies on the GPU (dequantisation fused into the plain and the grouped GEMM): a decode-sized
+    MoE layer call and a trunk forward agree with the CPU evaluation of the same copies."""
+    from hibana_b200 import _native as nv
+    from hibana_b200.models.layers import MoeLayer
+    t, cpu, _ = _w3_model("cpu")
+    _, gpu, _ = _w3_model("cuda")
+    x = torch.randn(5, t.hidden, generator=torch.Generator().manual_seed(3)).bfloat16()
+    fc = [b.ffn for b in cpu.blocks if isinstance(b.ffn, MoeLayer)][0]
+    fg = [b.ffn for b in gpu.blocks if isinstance(b.ffn, MoeLayer)][0]
+    a, b = fc.forward(x).float(), fg.forward(x.cuda()).float().cpu()
+    assert (a - b).abs().max() <= 3e-2 * a.abs().max() + 1e-3
+    prompts = _workload(t, n=2)
+    sp = SamplingParams(max_tokens=6)
+    want = Executor(cpu, max_batch=2, max_ctx=128, use_graphs=False).generate_batch(prompts, sp)
+    ex = Executor(gpu, max_batch=2, max_ctx=128, use_graphs=True)
+    ex.capture_graphs()
+    got = ex.generate_batch(prompts, sp)
+    torch.cuda.synchronize()
+    assert nv.read_status() == 0
+    assert [r.output_ids[0] for r in got] == [r.output_ids[0] for r in want]

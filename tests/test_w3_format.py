@@ -176,3 +176,47 @@ def test_model_calibration_capture_fit_write_attach_cpu(tmp_path):
     cm.main(["--target", "dense-tiny", "--inputs", str(tmp_path / "samples.json"), "--output", str(tmp_path / "cli"),
              "--device", "cpu", "--layers", "1"])
     assert set(cm.load_directory(tmp_path / "cli")) == {"l0.qkv", "l0.o", "l0.gate_up", "l0.down"}
+
+
+def test_routed_expert_calibration_capture_fit_attach_cpu(tmp_path):
+    """Routed experts of a hybrid MoE model: per-expert covariances of the rows routed to each expert (both matrices),
+    GPTQ per expert where enough rows were seen, stacks written next to the projections' and handed to the layers."""
+    from hibana_b200.engine.executor import Executor
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.models.hybrid import HybridModel
+    from hibana_b200.target import scaled, tiny_hybrid_moe
+    from hibana_b200.weights import calibrate_model as cm
+    t = scaled(tiny_hybrid_moe(), expert_ffn=128, mtp_layers=0, mtp_depth=0, weight_format="bf16")
+    model = HybridModel(t, "cpu", seed=0)
+    g = torch.Generator().manual_seed(0)
+    samples = [torch.randint(0, t.vocab, (n,), generator=g).tolist() for n in (160, 140, 180, 150)]
+    cov = cm.capture(model, samples, max_batch=2)
+    ec = cov.experts
+    layers = cm.expert_layers(model)
+    assert layers and set(ec.h1) == set(layers)
+    name = next(iter(layers))
+    ew = layers[name].experts
+    rows = sum(len(s) for s in samples)
+    assert int(ec.rows[name].sum()) == rows * t.top_k                      # every (token, choice) pair, once
+    assert ec.h1[name].shape == (ew.experts, ew.hidden, ew.hidden) and ec.h2[name].shape == (ew.experts, ew.inter, ew.inter)
+    e = int(ec.rows[name].argmax())
+    assert torch.allclose(ec.h1[name][e], ec.h1[name][e].t(), atol=1e-3) and float(ec.h1[name][e].diagonal().min()) >= 0
+    efit, ereport = cm.fit_experts(model, ec, min_rows=64)
+    assert set(efit) == {f"{n}.fc{w}" for n in layers for w in (1, 2)}
+    r0 = next(r for r in ereport if r["name"] == name)
+    assert r0["calibrated"] >= 1
+    assert r0["fc1_error_gptq"] < r0["fc1_error_nearest"] and r0["fc2_error_gptq"] < r0["fc2_error_nearest"], r0
+    assert efit[f"{name}.fc1"].shape == (ew.experts * ew.n1, ew.hidden)
+    fitted, report = cm.fit(model, cov)
+    fitted.update(efit)
+    d = cm.write_directory(tmp_path / "w3", fitted, target=t.name, report=report + ereport)
+    served = HybridModel(t, "cpu", seed=0)
+    served.attach_w3()
+    before = layers and cm.expert_layers(served)[name].experts_w3.dense(1).clone()
+    n = cm.attach(served, d, strict=True)
+    assert n == len(fitted) - len(layers)                                   # fc1 + fc2 of a layer attach as one
+    after = cm.expert_layers(served)[name].experts_w3.dense(1)
+    assert not torch.equal(before, after)
+    assert torch.allclose(after.reshape(-1, ew.hidden).float(), efit[f"{name}.fc1"].dequantize().float(), atol=1e-6)
+    out = Executor(served, max_batch=2, max_ctx=200, use_graphs=False).generate_batch(samples[:2], SamplingParams(max_tokens=4))
+    assert all(len(r.output_ids) == 4 for r in out)
