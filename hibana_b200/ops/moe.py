@@ -157,8 +157,9 @@ class ExpertWeights:
             # are a multiple of 128, so expert boundaries fall on tile boundaries
             from ..weights.w3 import Int3G64
             assert n1 % 128 == 0 and fc2.shape[1] % 128 == 0
-            q1 = Int3G64.quantize(fc1.reshape(e * n1, h).float().cpu())
-            q2 = Int3G64.quantize(fc2.reshape(e * fc2.shape[1], inter).float().cpu())
+            # quantised where the weights are (a full-size layer's stacks never visit the host)
+            q1 = Int3G64.quantize(fc1.reshape(e * n1, h))
+            q2 = Int3G64.quantize(fc2.reshape(e * fc2.shape[1], inter))
             return cls.from_int3(q1, q2, e, act, fc2.shape[1], dev)
 
         def quant(w):   # per-expert scale, stacked rows
