@@ -134,6 +134,22 @@ def main() -> None:
         return site.combine(blk, keep)
     op("hyper-connection mix + combine, 32 rows x 4 streams x 2560 (6 launches)",
        (rk_ + 16 + hc_ * hh_) * hc_ * hh_ * 2 * 0 + (site.down_inject.numel() + site.up.numel()) * 2, hyper_site)
+    # routed experts at a decode batch, Nemotron geometry (512 experts, 1024 -> 2688 -> 1024, squared ReLU, top-22,
+    # 16 rows): the served NVFP4 stacks against the 3-bit decode copy (grouped GEMMs, dequantisation fused). Built
+    # only when asked for by name: the stacks take a few GB.
+    if args.only and args.only in "routed experts":
+        e_, hid_, inter_, rows_, topk_ = 512, 1024, 2688, 16, 22
+        fc1, fc2 = rnd(e_, inter_, hid_, scale=0.02), rnd(e_, hid_, inter_, scale=0.02)
+        xe = rnd(rows_, hid_)
+        eids = torch.stack([torch.randperm(e_, generator=g, device=dev)[:topk_] for _ in range(rows_)]).int()
+        ew_ = torch.softmax(torch.randn(rows_, topk_, generator=g, device=dev), -1)
+        distinct = int(eids.unique().numel())
+        per_expert = 2 * inter_ * hid_
+        for fmt_, bits in (("nvfp4", 4.5), ("w3", 4.0)):
+            ew = moe.ExpertWeights.create(fc1, fc2, "relu2", fmt_).to(dev)
+            op(f"routed experts {rows_} rows top-{topk_} of {e_} ({distinct} distinct), 1024-2688-1024, {fmt_} stacks",
+               distinct * per_expert * bits / 8, lambda ew=ew: moe.experts_forward(xe, eids, ew_, ew))
+        del fc1, fc2
     for name, nbytes, fn in ops:
         if args.only and args.only not in name:
             continue
