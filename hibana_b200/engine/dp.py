@@ -75,6 +75,10 @@ def lockstep_plan(has_work: Sequence[bool]) -> tuple[bool, list[bool]]:
     return True, [not w for w in has_work]
 
 
+class ReplicaFailed(RuntimeError):
+    """Another replica reported that it gave up (its message arrived with a round)."""
+
+
 class Lockstep:
     """Round protocol of data-parallel ranks that share expert-parallel layers.
 
@@ -94,6 +98,7 @@ class Lockstep:
         self.outbox: list = []
         self.on_items: Optional[Callable[[int, list], None]] = None
         self.rounds = self.forward_rounds = self.empty_forwards = 0
+        self.broken = False          # a round's all-gather raised (a replica stopped answering): no more rounds
 
     def post(self, item) -> None:
         """Queues a picklable message for every other rank; it travels with the next round."""
@@ -101,7 +106,11 @@ class Lockstep:
 
     def round(self, state: int) -> list:
         mine, self.outbox = (int(state), self.outbox), []
-        got = self.allgather(mine)
+        try:
+            got = self.allgather(mine)
+        except BaseException:
+            self.broken = True
+            raise
         self.rounds += 1
         states = [g[0] for g in got]
         self.forward_rounds += FORWARD in states

@@ -279,7 +279,8 @@ class EngineLoop:
                     self.tickets.pop(tid, None)
                     self._finished(tid)
             elif item[0] == "failed":
-                raise RuntimeError(f"replica {_src} failed: {item[1]}")
+                from .dp import ReplicaFailed
+                raise ReplicaFailed(f"replica {_src} failed: {item[1]}")
         return cmds
 
     def _run_dp(self) -> None:
@@ -308,10 +309,18 @@ class EngineLoop:
                 self.steps += 1
                 self._deliver(touched)
         except Exception as e:  # noqa: BLE001 - every failure takes the engine down cleanly
+            from .dp import ReplicaFailed
             try:
-                self.dp.post(("failed", f"{type(e).__name__}: {e}"))
                 if self.channel is not None:
                     self.channel.broadcast([("failed", f"{type(e).__name__}: {e}")])
+                if not isinstance(e, ReplicaFailed) and not self.dp.broken:
+                    # this replica's own failure: one last round carries the news, so the others stop at their next
+                    # round instead of waiting for the control timeout. (A replica that stops because another one
+                    # failed joins no further round: nobody would be there.)
+                    self.dp.post(("failed", f"{type(e).__name__}: {e}"))
+                    self.dp.round(LEAVING)
+            except Exception:  # noqa: BLE001 - best effort: the peers' timeouts cover a round nobody joins
+                pass
             finally:
                 self._fail(f"{type(e).__name__}: {e}")
 

@@ -237,3 +237,61 @@ def test_replicas_of_tensor_parallel_groups_route_follow_and_stop():
         assert llms[g, 1].scheduler.metrics.finished == served[g]
         assert llms[g, 1].executor.stats["decode_steps"] == llms[g, 0].executor.stats["decode_steps"]
         assert loops[g, 1].steps == loops[g, 0].steps
+
+
+def test_a_failing_replica_leader_takes_its_follower_and_the_other_replicas_down():
+    """Failure on the host inside a replica that is a tensor-parallel group: the leader of replica 1 raises in a
+    step; it tells its follower (command channel) and the other replicas (next round); every loop ends unhealthy and
+    rank 0's open tickets get the error instead of hanging."""
+    import threading
+
+    from hibana_b200.config import EngineConfig
+    from hibana_b200.engine.dp import ThreadAllGather
+    from hibana_b200.engine.llm import LLM
+    from hibana_b200.engine.loop import EngineLoop
+    from hibana_b200.engine.request import SamplingParams
+    from hibana_b200.parallel.lockstep import ThreadBroadcast
+    from hibana_b200.target import dense_tiny, scaled
+    from test_tp import ThreadComm
+    t = scaled(dense_tiny(), weight_format="bf16")
+    cfg = EngineConfig(target="dense-tiny", max_batch=4, cuda_graphs=False, max_context=128, prefill_budget=64,
+                       prefill_chunk=32, dp=2, tp=2)
+    leaders = ThreadAllGather(2, timeout=20)
+    comms = [ThreadComm(2), ThreadComm(2)]
+    for c in comms:       # a collective nobody joins ends with an error, as a process-group timeout would
+        c.barrier = threading.Barrier(2, timeout=10)
+    chans = [ThreadBroadcast(2, timeout=20), ThreadBroadcast(2, timeout=20)]
+    llms, loops = {}, {}
+    for g in range(2):
+        for r in range(2):
+            view = comms[g].view(r)
+            view.rank = r
+            if r == 0:
+                llms[g, r] = LLM(cfg, target=t, device="cpu", comm=view, control=leaders.view(g), rank=g)
+                loops[g, r] = EngineLoop(llms[g, r].scheduler, channel=chans[g].view(0), rank=g, dp=llms[g, r].lockstep,
+                                         idle_sleep=0.001)
+            else:
+                llms[g, r] = LLM(cfg, target=t, device="cpu", comm=view)
+                loops[g, r] = EngineLoop(llms[g, r].scheduler, channel=chans[g].view(r), rank=r)
+
+    def boom():
+        raise RuntimeError("injected step failure")
+    llms[1, 0].scheduler.step = boom              # replica 1's leader fails before its forward starts
+    for loop in loops.values():
+        loop.start()
+    sp = SamplingParams(max_tokens=50, ignore_eos=True)
+    tickets = [loops[0, 0].submit([3 + i, 40 + i, 7, 9, 200 + i, 5] * 3, sp) for i in range(4)]
+    for loop in loops.values():
+        loop.thread.join(60)
+        assert not loop.thread.is_alive()
+    assert not any(loop.healthy for loop in loops.values())
+    assert "injected step failure" in loops[1, 0].failure
+    # replica 1's follower had started the step its leader never joined: its collective gave up, or the leader's
+    # message reached it first
+    assert "leader failed" in loops[1, 1].failure or "Barrier" in loops[1, 1].failure
+    assert "replica 1 failed" in loops[0, 0].failure and "leader failed" in loops[0, 1].failure
+    for tk in tickets:
+        last = None
+        while not tk.events.empty():
+            last = tk.events.get_nowait()
+        assert last is not None and last[0] == "error", last
