@@ -63,6 +63,11 @@ def run_engine(args) -> int:
         cfg = cfg.replace(weights=str(weights))
     if int(os.environ.get("RANK", "0")) == 0:
         print(preflight.summary(cfg, host, weights, w3_dir), file=sys.stderr)
+    if cfg.host_floor_gib > 0 and int(os.environ.get("LOCAL_RANK", "0")) == 0:
+        # one guard per host: under sustained host-memory pressure it asks this process to stop (the supervisor of
+        # a rank group then restarts or gives up by its policy) instead of letting the kernel's OOM killer choose
+        from .launch.guard import MemoryGuard
+        MemoryGuard(cfg.host_floor_gib).start()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
         from .parallel.lockstep import serve_rank

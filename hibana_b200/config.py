@@ -12,6 +12,8 @@ import os
 from dataclasses import dataclass
 from typing import Iterator, Optional
 
+from .hardware.b200 import HOST_FLOOR_GIB
+
 
 def _bool(v: str) -> bool:
     return v.strip().lower() in ("1", "true", "yes", "on")
@@ -43,6 +45,8 @@ class EngineConfig:
     max_waits: int = 8
     # memory
     gpu_memory_fraction: float = 0.90
+    host_floor_gib: float = HOST_FLOOR_GIB # free host memory left to the OS; the memory guard stops the engine when
+                                           # it stays under half of this (0 = no guard) (launch/guard.py)
     kv_pages: int = 0                      # 0 = plan from free memory
     state_slots: int = 0
     kv_dtype: str = ""                     # "" = target default, else bf16 | fp8 | nvfp4 (4.5 bits per element)

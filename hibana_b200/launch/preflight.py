@@ -13,6 +13,8 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Optional
 
+from ..hardware import b200
+
 HEADROOM_BYTES = 20 << 30        # disk space a download leaves free
 
 
@@ -161,9 +163,9 @@ def check_host(need_gpus: int = 1, min_free_gib: float = 8.0, require_b200: bool
     for i in range(rep.gpus):
         p = torch.cuda.get_device_properties(i)
         rep.names.append(p.name)
-        if require_b200 and (p.major, p.minor) != (10, 0):
+        if require_b200 and not b200.is_target(p.major, p.minor):
             rep.ok = False
-            rep.problems.append(f"GPU {i} is sm_{p.major}{p.minor} ({p.name}); the kernels are built for sm_100a")
+            rep.problems.append(f"GPU {i} is sm_{p.major}{p.minor} ({p.name}); the kernels are built for {b200.ARCH}")
         free, _ = torch.cuda.mem_get_info(i)
         rep.free_gib.append(free / (1 << 30))
         if free / (1 << 30) < min_free_gib:

@@ -32,7 +32,7 @@ nv.register("hb_attn_prefill_profile", [P], void=True)
 nv.register("hb_attn_decode_profile", [P], void=True)
 nv.register("hb_attn_prefill", [P, P, P, L, L, P, L, P, P, P, P, I, I, I, I, I, Fl, I, L, P, P])
 
-NUM_SMS = 148
+from ..hardware.b200 import NUM_SMS  # noqa: E402
 
 
 DECODE_CTAS_PER_SM = 2      # csrc/attn_decode.cu: 64-thread CTAs with ~100 KB of rings, two share an SM

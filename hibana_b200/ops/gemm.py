@@ -18,7 +18,7 @@ from .nvfp4 import Nvfp4Tensor
 EPI_STORE, EPI_RESIDUAL, EPI_SILU_MUL, EPI_STORE_F32 = 0, 1, 2, 3
 EPI_SILU_MUL_QUANT = 7   # decode shapes (tokens <= 128): SiLU-mul, then NVFP4 requantisation in the same epilogue
 EPI_RELU2 = 6       # grouped (weights on the 128-row side) GEMMs only: out = relu(x)^2
-NUM_SMS = 148
+from ..hardware.b200 import NUM_SMS  # noqa: E402
 
 nv.register("hb_gemm_set_pdl", [nv.I], void=True)
 nv.register("hb_gemm_set_local_reduce", [nv.I], void=True)
