@@ -26,9 +26,13 @@ def add_engine_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--max-batch", type=int, dest="max_batch")
     p.add_argument("--max-context", type=int, dest="max_context")
     p.add_argument("--weights")
-    p.add_argument("--spec", choices=("off", "mtp", "dflash2", "ngram"))
+    p.add_argument("--spec", choices=("off", "mtp", "dflash2", "ngram", "lilicorr"))
     p.add_argument("--spec-depth", type=int, dest="spec_depth")
     p.add_argument("--ssd-dir", dest="ssd_dir")
+    p.add_argument("--w3", action="store_const", const=True, dest="w3", help="3-bit decode copies beside the weights")
+    p.add_argument("--w3-checkpoint", dest="w3_checkpoint", help="calibrated 3-bit copies (weights/calibrate_model.py)")
+    p.add_argument("--kv-dtype", dest="kv_dtype", choices=("bf16", "fp8", "nvfp4"))
+    p.add_argument("--ssm-state", dest="ssm_state", choices=("fp32", "fp16_sr", "int8", "int8w"))
     p.add_argument("--no-graphs", action="store_const", const=False, dest="cuda_graphs")
     p.add_argument("--no-fused-collectives", action="store_const", const=False, dest="fused_collectives")
     p.add_argument("--trace-dir", dest="trace_dir")
@@ -36,7 +40,7 @@ def add_engine_args(p: argparse.ArgumentParser) -> None:
 
 def _flags(args) -> dict:
     keys = ("host", "port", "tp", "ep", "dp", "max_batch", "max_context", "weights", "spec", "spec_depth", "ssd_dir",
-            "cuda_graphs", "fused_collectives", "trace_dir")
+            "cuda_graphs", "fused_collectives", "trace_dir", "w3", "w3_checkpoint", "kv_dtype", "ssm_state")
     return {k: getattr(args, k, None) for k in keys}
 
 

@@ -138,3 +138,16 @@ def test_preflight_snapshot_lookup_w3_link_and_summary(tmp_path):
     text = pf.summary(cfg.replace(w3=True, tp=8, spec="ngram"), host, snap, d)
     assert "tp=8" in text and "ngram depth" in text and str(d) in text
     assert isinstance(pf.meminfo(), dict)
+
+
+def test_serve_flags_reach_the_settings():
+    """Flags the docs name (`--w3 --w3-checkpoint`, `--ssm-state`, `--kv-dtype`, `--dp` with `--tp`) are parsed and
+    land in the resolved settings; absent flags leave the defaults alone."""
+    from hibana_b200 import cli
+    ap = cli.build_parser()
+    cfg = cli._resolve(ap.parse_args(["serve", "dense-tiny", "--w3", "--w3-checkpoint", "/ckpt/w3", "--ssm-state", "int8w",
+                                      "--kv-dtype", "fp8", "--spec", "lilicorr", "--dp", "2", "--tp", "2"]))
+    assert (cfg.w3, cfg.w3_checkpoint, cfg.ssm_state, cfg.kv_dtype, cfg.spec, cfg.dp, cfg.tp) == \
+        (True, "/ckpt/w3", "int8w", "fp8", "lilicorr", 2, 2)
+    plain = cli._resolve(ap.parse_args(["serve", "dense-tiny"]))
+    assert plain.w3 is False and plain.ssm_state == "fp32" and plain.host_floor_gib == 6.0
